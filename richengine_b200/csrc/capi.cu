@@ -1,0 +1,563 @@
+// capi.cu — error reporting, the CUDA extent storage and the pinned-host tier
+// behind the C ABI of include/richkv.h.
+//
+// Storage mirrors the reference's kv::PageStorage (runtime/ops/PageStorage.hpp:27-102,
+// PageStorage.mm:12-167): extents of extentPages pages that only the pool
+// allocates and releases, page-table entries = extent address | index, a page's
+// spans per layer and tensor. B200-native differences: extents are physical
+// allocations mapped at fixed offsets of ONE reserved virtual range (CUDA
+// virtual memory management), so every page of the pool lies inside one
+// address window that a single TMA tensor map covers; page copies are a
+// kernel; the table lives in device memory and is patched by stream-ordered
+// copies.
+#include "common.cuh"
+
+#include <cuda.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+namespace rk {
+
+namespace {
+thread_local std::string g_error;
+}
+
+void set_error(const char *text) { g_error = text ? text : ""; }
+
+int cuda_status(cudaError_t error, const char *what) {
+  if (error == cudaSuccess) return kOk;
+  g_error = std::string(what) + ": " + cudaGetErrorString(error);
+  return kCudaError;
+}
+
+int move_pages(uint32_t format, uint32_t layers, uint32_t kv_heads, uint32_t head_dim, uint32_t extent_pages,
+               const rk_page_entry *from_entries, const rk_page_entry *to_entries, uint8_t *from_slots,
+               uint8_t *to_slots, uint32_t count, cudaStream_t stream);
+
+// ---- driver entry points, resolved at run time (the library links no libcuda) ----
+struct DriverApi {
+  CUresult (*memAddressReserve)(CUdeviceptr *, size_t, size_t, CUdeviceptr, unsigned long long) = nullptr;
+  CUresult (*memAddressFree)(CUdeviceptr, size_t) = nullptr;
+  CUresult (*memCreate)(CUmemGenericAllocationHandle *, size_t, const CUmemAllocationProp *, unsigned long long) = nullptr;
+  CUresult (*memRelease)(CUmemGenericAllocationHandle) = nullptr;
+  CUresult (*memMap)(CUdeviceptr, size_t, size_t, CUmemGenericAllocationHandle, unsigned long long) = nullptr;
+  CUresult (*memUnmap)(CUdeviceptr, size_t) = nullptr;
+  CUresult (*memSetAccess)(CUdeviceptr, size_t, const CUmemAccessDesc *, size_t) = nullptr;
+  CUresult (*memGetAllocationGranularity)(size_t *, const CUmemAllocationProp *, CUmemAllocationGranularity_flags) = nullptr;
+  CUresult (*tensorMapEncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill) = nullptr;
+  bool ready = false;
+};
+
+const DriverApi *driver_api() {
+  static DriverApi api;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    auto load = [](const char *name, auto &slot) {
+      void *fn = nullptr;
+      cudaDriverEntryPointQueryResult result;
+      if (cudaGetDriverEntryPoint(name, &fn, cudaEnableDefault, &result) != cudaSuccess ||
+          result != cudaDriverEntryPointSuccess || !fn)
+        return false;
+      slot = reinterpret_cast<std::remove_reference_t<decltype(slot)>>(fn);
+      return true;
+    };
+    bool ok = true;
+    ok &= load("cuMemAddressReserve", api.memAddressReserve);
+    ok &= load("cuMemAddressFree", api.memAddressFree);
+    ok &= load("cuMemCreate", api.memCreate);
+    ok &= load("cuMemRelease", api.memRelease);
+    ok &= load("cuMemMap", api.memMap);
+    ok &= load("cuMemUnmap", api.memUnmap);
+    ok &= load("cuMemSetAccess", api.memSetAccess);
+    ok &= load("cuMemGetAllocationGranularity", api.memGetAllocationGranularity);
+    ok &= load("cuTensorMapEncodeTiled", api.tensorMapEncodeTiled);
+    api.ready = ok;
+  });
+  return api.ready ? &api : nullptr;
+}
+
+int driver_status(CUresult result, const char *what) {
+  if (result == CUDA_SUCCESS) return kOk;
+  g_error = std::string(what) + ": CUresult " + std::to_string(int(result));
+  return result == CUDA_ERROR_OUT_OF_MEMORY ? kRefused : kCudaError;
+}
+
+// ---- extent storage -----------------------------------------------------------
+struct Storage {
+  uint32_t format = 0, layers = 0, kv_heads = 0, head_dim = 0;
+  uint32_t page_count = 0, extent_pages = 0;
+  uint32_t data_bytes = 0, scale_bytes = 0;
+  uint64_t page_bytes = 0;    // one page over all layers
+  uint64_t extent_bytes = 0;  // extent_pages * page_bytes
+  uint64_t extent_stride = 0; // extent_bytes rounded up to the mapping granularity
+  uint64_t budget_bytes = ~0ull;
+  int device = 0;
+  CUdeviceptr base = 0;
+  uint64_t reserved = 0;
+  std::vector<CUmemGenericAllocationHandle> handles;
+  std::vector<uint8_t> allocated;
+  std::vector<rk_kv_layer> places;
+
+  uint32_t extents() const { return page_count / extent_pages; }
+  uint64_t allocated_bytes() const {
+    return uint64_t(std::count(allocated.begin(), allocated.end(), uint8_t(1))) * extent_bytes;
+  }
+  bool page_allocated(uint32_t page) const { return page < page_count && allocated[page / extent_pages]; }
+  rk_page_entry entry(uint32_t page) const {
+    const uint32_t extent = page / extent_pages;
+    return rk_make_entry(uint64_t(base) + extent * extent_stride, page - extent * extent_pages);
+  }
+};
+
+uint64_t gcd64(uint64_t a, uint64_t b) { while (b) { const uint64_t r = a % b; a = b; b = r; } return a; }
+
+// Pages whose bytes of one tensor fill whole 64 KiB units (PagedKv.hpp:112-119).
+uint64_t pages_for_aligned_region(uint64_t bytes) { return bytes ? 65536 / gcd64(65536, bytes) : 0; }
+
+} // namespace rk
+
+using namespace rk;
+
+extern "C" const char *rk_last_error(void) { return g_error.c_str(); }
+
+extern "C" uint32_t rk_extent_alignment_pages(uint32_t format, uint32_t kv_heads, uint32_t head_dim) {
+  // Layout::extentAlignmentPages (PagedKv.hpp:175-183)
+  const uint64_t data = pages_for_aligned_region(rk_data_bytes(format, kv_heads, head_dim));
+  if (format == RK_FORMAT_BF16) return uint32_t(data);
+  const uint64_t scale = pages_for_aligned_region(rk_scale_bytes(format, kv_heads));
+  return uint32_t(data / gcd64(data, scale) * scale);
+}
+
+extern "C" void *rk_storage_create(uint32_t format, uint32_t layers, uint32_t kv_heads, uint32_t head_dim,
+                                   uint32_t page_count, uint32_t extent_pages) {
+  if (!rk_format_valid(format) || !layers || !kv_heads || !head_dim) {
+    set_error("KV page storage layout is invalid");
+    return nullptr;
+  }
+  auto s = std::make_unique<Storage>();
+  s->format = format; s->layers = layers; s->kv_heads = kv_heads; s->head_dim = head_dim;
+  s->page_count = page_count; s->extent_pages = extent_pages;
+  s->data_bytes = rk_data_bytes(format, kv_heads, head_dim);
+  s->scale_bytes = rk_scale_bytes(format, kv_heads);
+  s->page_bytes = uint64_t(layers) * rk_layer_page_bytes(format, kv_heads, head_dim);
+  s->extent_bytes = uint64_t(extent_pages) * s->page_bytes;
+  // PageStorage.mm:24-36: whole alignment units, index fits the entry's low
+  // bits, a layer offset fits 32 bits, a whole number of extents.
+  if (!extent_pages || extent_pages % rk_extent_alignment_pages(format, kv_heads, head_dim) ||
+      extent_pages > RK_PAGE_INDEX_MASK || s->extent_bytes > 0xffffffffull) {
+    set_error("KV extent geometry is invalid");
+    return nullptr;
+  }
+  if (!page_count || page_count % extent_pages) {
+    set_error("KV page pool is not a whole number of extents");
+    return nullptr;
+  }
+  const DriverApi *api = driver_api();
+  if (!api) {
+    set_error("CUDA driver entry points for virtual memory management are unavailable");
+    return nullptr;
+  }
+  if (cuda_status(cudaGetDevice(&s->device), "cudaGetDevice")) return nullptr;
+  if (cuda_status(cudaFree(nullptr), "context creation")) return nullptr;
+  CUmemAllocationProp prop{};
+  prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+  prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  prop.location.id = s->device;
+  size_t granularity = 0;
+  if (driver_status(api->memGetAllocationGranularity(&granularity, &prop, CU_MEM_ALLOC_GRANULARITY_MINIMUM),
+                    "cuMemGetAllocationGranularity"))
+    return nullptr;
+  s->extent_stride = (s->extent_bytes + granularity - 1) / granularity * granularity;
+  s->reserved = s->extent_stride * s->extents();
+  if (driver_status(api->memAddressReserve(&s->base, s->reserved, std::max<size_t>(granularity, 1u << 21), 0, 0),
+                    "cuMemAddressReserve"))
+    return nullptr;
+  s->handles.assign(s->extents(), 0);
+  s->allocated.assign(s->extents(), 0);
+  for (uint32_t layer = 0; layer < layers; ++layer)
+    s->places.push_back(rk_make_layer(extent_pages, s->data_bytes, s->scale_bytes, layer));
+  return s.release();
+}
+
+extern "C" int rk_storage_release_extent(void *storage, uint32_t extent);
+
+extern "C" void rk_storage_destroy(void *storage) {
+  auto *s = static_cast<Storage *>(storage);
+  if (!s) return;
+  cudaDeviceSynchronize();
+  for (uint32_t e = 0; e < s->extents(); ++e)
+    if (s->allocated[e]) rk_storage_release_extent(s, e);
+  if (const DriverApi *api = driver_api()) api->memAddressFree(s->base, s->reserved);
+  delete s;
+}
+
+// Grants the extent (0), refuses it with the budget or the driver as cause
+// (kRefused), or reports misuse: kInvalid for an extent that is already
+// allocated or past the pool (PageStorage.mm:61-80).
+extern "C" int rk_storage_allocate_extent(void *storage, uint32_t extent) {
+  auto *s = static_cast<Storage *>(storage);
+  if (!s || extent >= s->extents()) { set_error("invalid KV extent"); return kInvalid; }
+  if (s->allocated[extent]) { set_error("KV extent is already allocated"); return kInvalid; }
+  if (s->allocated_bytes() + s->extent_bytes > s->budget_bytes) {
+    set_error("engine memory budget exceeded");
+    return kRefused;
+  }
+  const DriverApi *api = driver_api();
+  CUmemAllocationProp prop{};
+  prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+  prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  prop.location.id = s->device;
+  CUmemGenericAllocationHandle handle = 0;
+  if (int status = driver_status(api->memCreate(&handle, s->extent_stride, &prop, 0), "cuMemCreate")) return status;
+  const CUdeviceptr address = s->base + uint64_t(extent) * s->extent_stride;
+  if (int status = driver_status(api->memMap(address, s->extent_stride, 0, handle, 0), "cuMemMap")) {
+    api->memRelease(handle);
+    return status;
+  }
+  CUmemAccessDesc access{};
+  access.location = prop.location;
+  access.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+  if (int status = driver_status(api->memSetAccess(address, s->extent_stride, &access, 1), "cuMemSetAccess")) {
+    api->memUnmap(address, s->extent_stride);
+    api->memRelease(handle);
+    return status;
+  }
+  // A fresh extent reads as zeros: stores write only their own slots, and
+  // tests hold every other byte to zero.
+  if (int status = cuda_status(cudaMemset(reinterpret_cast<void *>(address), 0, s->extent_stride), "extent clear")) {
+    api->memUnmap(address, s->extent_stride);
+    api->memRelease(handle);
+    return status;
+  }
+  s->handles[extent] = handle;
+  s->allocated[extent] = 1;
+  return kOk;
+}
+
+// The caller proves no table names a page of the extent and no launched work
+// still touches it; the device is drained before the mapping goes
+// (the reference refuses while a command is in flight, PageStorage.mm:82-93).
+extern "C" int rk_storage_release_extent(void *storage, uint32_t extent) {
+  auto *s = static_cast<Storage *>(storage);
+  if (!s || extent >= s->extents()) { set_error("invalid KV extent"); return kInvalid; }
+  if (!s->allocated[extent]) { set_error("KV extent is not allocated"); return kInvalid; }
+  const DriverApi *api = driver_api();
+  if (int status = cuda_status(cudaDeviceSynchronize(), "drain before extent release")) return status;
+  const CUdeviceptr address = s->base + uint64_t(extent) * s->extent_stride;
+  if (int status = driver_status(api->memUnmap(address, s->extent_stride), "cuMemUnmap")) return status;
+  api->memRelease(s->handles[extent]);
+  s->handles[extent] = 0;
+  s->allocated[extent] = 0;
+  return kOk;
+}
+
+extern "C" void rk_storage_set_budget(void *storage, uint64_t bytes) { static_cast<Storage *>(storage)->budget_bytes = bytes; }
+extern "C" uint32_t rk_storage_page_count(const void *storage) { return static_cast<const Storage *>(storage)->page_count; }
+extern "C" uint32_t rk_storage_extent_pages(const void *storage) { return static_cast<const Storage *>(storage)->extent_pages; }
+extern "C" uint64_t rk_storage_bytes_per_page(const void *storage) { return static_cast<const Storage *>(storage)->page_bytes; }
+extern "C" uint64_t rk_storage_extent_bytes(const void *storage) { return static_cast<const Storage *>(storage)->extent_bytes; }
+extern "C" uint64_t rk_storage_allocated_bytes(const void *storage) { return static_cast<const Storage *>(storage)->allocated_bytes(); }
+extern "C" int rk_storage_is_allocated(const void *storage, uint32_t page) { return static_cast<const Storage *>(storage)->page_allocated(page); }
+extern "C" void rk_storage_window(const void *storage, uint64_t *base, uint64_t *bytes) {
+  const auto *s = static_cast<const Storage *>(storage);
+  *base = uint64_t(s->base);
+  *bytes = s->reserved;
+}
+extern "C" uint32_t rk_storage_layers(const void *storage, rk_kv_layer *out, uint32_t capacity) {
+  const auto *s = static_cast<const Storage *>(storage);
+  for (uint32_t i = 0; i < s->layers && i < capacity; ++i) out[i] = s->places[i];
+  return s->layers;
+}
+// The table entry of a page; 0 for a page whose extent holds no memory.
+extern "C" rk_page_entry rk_storage_entry(const void *storage, uint32_t page) {
+  const auto *s = static_cast<const Storage *>(storage);
+  return s->page_allocated(page) ? s->entry(page) : 0;
+}
+
+// Host <-> extent byte copies for loaders, tests and tools: `offset` and
+// `bytes` address the extent's own bytes. Synchronous.
+extern "C" int rk_storage_read_extent(const void *storage, uint32_t extent, uint64_t offset, void *host, uint64_t bytes) {
+  const auto *s = static_cast<const Storage *>(storage);
+  if (!s || extent >= s->extents() || !s->allocated[extent] || offset + bytes > s->extent_bytes) {
+    set_error("extent read is out of range or the extent holds no memory");
+    return kInvalid;
+  }
+  return cuda_status(cudaMemcpy(host, reinterpret_cast<const void *>(s->base + extent * s->extent_stride + offset), bytes, cudaMemcpyDeviceToHost), "extent read");
+}
+extern "C" int rk_storage_write_extent(void *storage, uint32_t extent, uint64_t offset, const void *host, uint64_t bytes) {
+  auto *s = static_cast<Storage *>(storage);
+  if (!s || extent >= s->extents() || !s->allocated[extent] || offset + bytes > s->extent_bytes) {
+    set_error("extent write is out of range or the extent holds no memory");
+    return kInvalid;
+  }
+  return cuda_status(cudaMemcpy(reinterpret_cast<void *>(s->base + extent * s->extent_stride + offset), host, bytes, cudaMemcpyHostToDevice), "extent write");
+}
+
+// Writes the entries of pages[first..count) to the device table, leaving the
+// entries before `first` as they are (PageStorage.mm:127-141).
+extern "C" int rk_storage_write_entries(const void *storage, const uint32_t *pages, uint32_t count, uint32_t first,
+                                        rk_page_entry *device_table, uint32_t table_capacity, void *stream) {
+  const auto *s = static_cast<const Storage *>(storage);
+  if (!s || !device_table || table_capacity < count) {
+    set_error("KV page table is too small for its entries");
+    return kInvalid;
+  }
+  if (first > count) {
+    set_error("KV page table entries start past the end of its pages");
+    return kInvalid;
+  }
+  if (first == count) return kOk;
+  std::vector<rk_page_entry> entries(count - first);
+  for (uint32_t i = first; i < count; ++i) {
+    if (!s->page_allocated(pages[i])) {
+      set_error("KV page is in an extent that is not allocated");
+      return kInvalid;
+    }
+    entries[i - first] = s->entry(pages[i]);
+  }
+  // Pageable source: the runtime stages it before returning, so `entries`
+  // may go out of scope.
+  return cuda_status(cudaMemcpyAsync(device_table + first, entries.data(), entries.size() * sizeof(rk_page_entry),
+                                     cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)),
+                     "page table upload");
+}
+
+namespace {
+int upload_entries(const Storage *s, const uint32_t *pages, uint32_t count, rk_page_entry **device, cudaStream_t stream) {
+  std::vector<rk_page_entry> entries(count);
+  for (uint32_t i = 0; i < count; ++i) {
+    if (!s->page_allocated(pages[i])) {
+      set_error("cannot move a KV page of an extent that is not allocated");
+      return kInvalid;
+    }
+    entries[i] = s->entry(pages[i]);
+  }
+  if (int status = cuda_status(cudaMallocAsync(reinterpret_cast<void **>(device), count * sizeof(rk_page_entry), stream), "cudaMallocAsync")) return status;
+  return cuda_status(cudaMemcpyAsync(*device, entries.data(), count * sizeof(rk_page_entry), cudaMemcpyHostToDevice, stream), "entry upload");
+}
+} // namespace
+
+// Copies each page's content onto its destination, every tensor of every
+// layer, ordered on `stream` (PageStorage.mm:95-114). Nothing is copied when
+// any page lies in an unallocated extent.
+extern "C" int rk_storage_copy_pages(void *storage, const rk_page_copy *copies, uint32_t count, void *stream) {
+  auto *s = static_cast<Storage *>(storage);
+  if (!count) return kOk;
+  if (!s || !copies) return kInvalid;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  std::vector<uint32_t> ids(2 * size_t(count));
+  for (uint32_t i = 0; i < count; ++i) { ids[i] = copies[i].from; ids[count + i] = copies[i].to; }
+  rk_page_entry *device = nullptr;
+  if (int status = upload_entries(s, ids.data(), 2 * count, &device, st)) return status;
+  const int status = move_pages(s->format, s->layers, s->kv_heads, s->head_dim, s->extent_pages, device,
+                                device + count, nullptr, nullptr, count, st);
+  cudaFreeAsync(device, st);
+  return status;
+}
+
+// Packs pages into `count` contiguous device slots of bytes_per_page each
+// (spans in layer, tensor order: PageStorage.mm:143-167), or unpacks them.
+extern "C" int rk_storage_pack_pages(void *storage, const uint32_t *pages, uint32_t count, void *device_slots, int unpack, void *stream) {
+  auto *s = static_cast<Storage *>(storage);
+  if (!count) return kOk;
+  if (!s || !pages || !device_slots) return kInvalid;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  rk_page_entry *device = nullptr;
+  if (int status = upload_entries(s, pages, count, &device, st)) return status;
+  const int status = unpack ? move_pages(s->format, s->layers, s->kv_heads, s->head_dim, s->extent_pages, nullptr, device,
+                                         static_cast<uint8_t *>(device_slots), nullptr, count, st)
+                            : move_pages(s->format, s->layers, s->kv_heads, s->head_dim, s->extent_pages, device, nullptr,
+                                         nullptr, static_cast<uint8_t *>(device_slots), count, st);
+  cudaFreeAsync(device, st);
+  return status;
+}
+
+// ---- pinned-host tier ------------------------------------------------------------
+// The eviction tier the engine drives through engine::KvTier
+// (runtime/engine/cache/KvTier.hpp:34-63) with the transfer bounds of
+// KvPageTier (runtime/engine/cache/KvPageTier.cpp:38-132): a bounded number of
+// transfers in flight, demotions at most half of it, restores at most three
+// quarters. The slot store is pinned host memory instead of an SSD file: a
+// demotion packs the page's spans into a device staging slot and one DMA takes
+// it to the host slot; a restore is the reverse. A page stays valid until its
+// demotion reports success.
+namespace rk {
+namespace {
+
+struct Transfer {
+  bool demotion = false;
+  bool in_flight = false;
+  bool ready = false;
+  bool success = false;
+  bool forced_failure = false;
+  uint32_t page = 0, slot = 0;
+  cudaEvent_t done = nullptr;
+};
+
+struct HostTier {
+  Storage *storage = nullptr;
+  uint64_t slot_bytes = 0;
+  uint32_t slots = 0, transfer_limit = 0, demotion_limit = 0, restore_limit = 0;
+  uint32_t demotions = 0, restores = 0, in_flight = 0, fail_next = 0;
+  uint8_t *host = nullptr;    // slots * slot_bytes, pinned
+  uint8_t *staging = nullptr; // transfer_limit * slot_bytes, device
+  cudaStream_t stream = nullptr;
+  std::vector<uint8_t> slot_used;
+  std::vector<Transfer> transfers; // index = transfer id = staging slot
+  bool writable = true;
+};
+
+} // namespace
+} // namespace rk
+
+extern "C" void *rk_tier_create(void *storage, uint32_t slots, uint32_t transfer_limit) {
+  auto *s = static_cast<Storage *>(storage);
+  if (!s || !slots || !transfer_limit) { set_error("invalid host tier geometry"); return nullptr; }
+  auto t = std::make_unique<HostTier>();
+  t->storage = s;
+  t->slot_bytes = s->page_bytes;
+  t->slots = slots;
+  t->transfer_limit = transfer_limit;
+  t->demotion_limit = std::max<uint32_t>(1, transfer_limit / 2);
+  t->restore_limit = std::max<uint32_t>(1, transfer_limit - transfer_limit / 4);
+  t->slot_used.assign(slots, 0);
+  t->transfers.resize(transfer_limit);
+  if (cuda_status(cudaHostAlloc(reinterpret_cast<void **>(&t->host), uint64_t(slots) * t->slot_bytes, cudaHostAllocDefault), "pinned host arena")) return nullptr;
+  if (cuda_status(cudaMalloc(reinterpret_cast<void **>(&t->staging), uint64_t(transfer_limit) * t->slot_bytes), "tier staging")) { cudaFreeHost(t->host); return nullptr; }
+  if (cuda_status(cudaStreamCreateWithFlags(&t->stream, cudaStreamNonBlocking), "tier stream")) { cudaFree(t->staging); cudaFreeHost(t->host); return nullptr; }
+  for (Transfer &x : t->transfers) cudaEventCreateWithFlags(&x.done, cudaEventDisableTiming);
+  return t.release();
+}
+
+extern "C" void rk_tier_destroy(void *tier) {
+  auto *t = static_cast<HostTier *>(tier);
+  if (!t) return;
+  cudaStreamSynchronize(t->stream); // every transfer reads or writes its page in place
+  for (Transfer &x : t->transfers) cudaEventDestroy(x.done);
+  cudaStreamDestroy(t->stream);
+  cudaFree(t->staging);
+  cudaFreeHost(t->host);
+  delete t;
+}
+
+extern "C" uint64_t rk_tier_slot_bytes(const void *tier) { return static_cast<const HostTier *>(tier)->slot_bytes; }
+extern "C" int rk_tier_writable(const void *tier) { return static_cast<const HostTier *>(tier)->writable; }
+extern "C" int rk_tier_can_demote(const void *tier) {
+  const auto *t = static_cast<const HostTier *>(tier);
+  return t->demotions < t->demotion_limit && t->in_flight < t->transfer_limit && t->writable;
+}
+extern "C" int rk_tier_can_restore(const void *tier) {
+  const auto *t = static_cast<const HostTier *>(tier);
+  return t->restores < t->restore_limit && t->in_flight < t->transfer_limit;
+}
+// A free slot id, or -1 when the quota is full.
+extern "C" int64_t rk_tier_acquire_slot(void *tier) {
+  auto *t = static_cast<HostTier *>(tier);
+  for (uint32_t i = 0; i < t->slots; ++i)
+    if (!t->slot_used[i]) { t->slot_used[i] = 1; return i; }
+  return -1;
+}
+extern "C" void rk_tier_release_slot(void *tier, uint32_t slot) {
+  auto *t = static_cast<HostTier *>(tier);
+  if (slot < t->slots) t->slot_used[slot] = 0;
+}
+// Test seam, host side only: the next `count` transfers report failure when
+// they retire, as a failed write or read would.
+extern "C" void rk_tier_fail_next(void *tier, uint32_t count) { static_cast<HostTier *>(tier)->fail_next = count; }
+extern "C" const void *rk_tier_slot_host_pointer(const void *tier, uint32_t slot) {
+  const auto *t = static_cast<const HostTier *>(tier);
+  return slot < t->slots ? t->host + uint64_t(slot) * t->slot_bytes : nullptr;
+}
+
+namespace {
+int start_transfer(HostTier *t, bool demotion, uint32_t page, uint32_t slot, cudaStream_t after) {
+  if (demotion ? !rk_tier_can_demote(t) : !rk_tier_can_restore(t)) return kRefused;
+  if (slot >= t->slots || !t->slot_used[slot] || !t->storage->page_allocated(page)) {
+    set_error("host tier transfer names an invalid slot or page");
+    return kInvalid;
+  }
+  uint32_t id = 0;
+  while (id < t->transfer_limit && t->transfers[id].in_flight) ++id;
+  if (id == t->transfer_limit) return kRefused;
+  Transfer &x = t->transfers[id];
+  if (after) { // order the transfer after work already launched on the caller's stream
+    if (int status = cuda_status(cudaEventRecord(x.done, after), "tier order event")) return status;
+    if (int status = cuda_status(cudaStreamWaitEvent(t->stream, x.done, 0), "tier order wait")) return status;
+  }
+  uint8_t *stage = t->staging + uint64_t(id) * t->slot_bytes;
+  uint8_t *host = t->host + uint64_t(slot) * t->slot_bytes;
+  int status = kOk;
+  if (demotion) {
+    status = rk_storage_pack_pages(t->storage, &page, 1, stage, 0, t->stream);
+    if (!status) status = cuda_status(cudaMemcpyAsync(host, stage, t->slot_bytes, cudaMemcpyDeviceToHost, t->stream), "demotion copy");
+  } else {
+    status = cuda_status(cudaMemcpyAsync(stage, host, t->slot_bytes, cudaMemcpyHostToDevice, t->stream), "restore copy");
+    if (!status) status = rk_storage_pack_pages(t->storage, &page, 1, stage, 1, t->stream);
+  }
+  if (status) {
+    if (demotion) t->writable = false; // a failed write closes the tier to demotions
+    return status;
+  }
+  if (int s2 = cuda_status(cudaEventRecord(x.done, t->stream), "tier completion event")) return s2;
+  x.demotion = demotion; x.in_flight = true; x.ready = false; x.success = false;
+  x.forced_failure = t->fail_next > 0;
+  if (t->fail_next) --t->fail_next;
+  x.page = page; x.slot = slot;
+  ++t->in_flight;
+  ++(demotion ? t->demotions : t->restores);
+  return int(id);
+}
+} // namespace
+
+// Start moving `page` to `slot` (demote) or back (restore). Returns the
+// transfer id (>= 0), kRefused when the tier takes no more of that kind for
+// now, or an error. `after_stream`, when non-null, is a stream whose launched
+// work the transfer must follow.
+extern "C" int rk_tier_demote(void *tier, uint32_t page, uint32_t slot, void *after_stream) {
+  return start_transfer(static_cast<HostTier *>(tier), true, page, slot, static_cast<cudaStream_t>(after_stream));
+}
+extern "C" int rk_tier_restore(void *tier, uint32_t slot, uint32_t page, void *after_stream) {
+  return start_transfer(static_cast<HostTier *>(tier), false, page, slot, static_cast<cudaStream_t>(after_stream));
+}
+// Retires finished transfers; returns how many retired in this call.
+extern "C" int rk_tier_poll(void *tier) {
+  auto *t = static_cast<HostTier *>(tier);
+  int retired = 0;
+  for (Transfer &x : t->transfers) {
+    if (!x.in_flight || x.ready) continue;
+    const cudaError_t state = cudaEventQuery(x.done);
+    if (state == cudaErrorNotReady) continue;
+    x.ready = true;
+    x.success = state == cudaSuccess && !x.forced_failure;
+    if (x.demotion && !x.success) t->writable = false;
+    --t->in_flight;
+    --(x.demotion ? t->demotions : t->restores);
+    ++retired;
+  }
+  return retired;
+}
+extern "C" int rk_tier_transfer_ready(const void *tier, uint32_t id) {
+  const auto *t = static_cast<const HostTier *>(tier);
+  return id < t->transfer_limit && t->transfers[id].in_flight && t->transfers[id].ready;
+}
+// Reports the transfer's outcome (1 success, 0 failure) and frees its id.
+extern "C" int rk_tier_transfer_finish(void *tier, uint32_t id) {
+  auto *t = static_cast<HostTier *>(tier);
+  if (id >= t->transfer_limit || !t->transfers[id].in_flight || !t->transfers[id].ready) return kInvalid;
+  t->transfers[id].in_flight = false;
+  return t->transfers[id].success ? 1 : 0;
+}
+extern "C" int rk_tier_drain(void *tier) {
+  auto *t = static_cast<HostTier *>(tier);
+  if (int status = cuda_status(cudaStreamSynchronize(t->stream), "tier drain")) return status;
+  return rk_tier_poll(tier);
+}

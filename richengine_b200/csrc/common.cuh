@@ -1,0 +1,104 @@
+// common.cuh — device helpers shared by the paged-KV kernels.
+#pragma once
+
+#include "../../include/richkv_abi.h"
+
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace rk {
+
+constexpr uint32_t kPageTokens = RK_PAGE_TOKENS;
+
+// Status codes every C entry point returns (include/richkv.h).
+constexpr int kOk = 0;
+constexpr int kInvalid = -1;     // host-side contract violation, nothing launched
+constexpr int kCudaError = -2;   // a CUDA call failed; rk_last_error() has the text
+constexpr int kUnsupported = -3; // geometry or format without a kernel
+constexpr int kRefused = -4;     // capacity refusal (allocator, tier)
+constexpr int kTimeout = -5;     // a bounded device wait ran out
+
+void set_error(const char *text);
+int cuda_status(cudaError_t error, const char *what);
+
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t bits) { return __uint_as_float(bits << 16); }
+
+// Round-to-nearest-even fp32 -> bf16 bits; quiet NaNs stay NaN.
+__device__ __forceinline__ uint16_t float_to_bf16_bits(float value) {
+  uint32_t bits = __float_as_uint(value);
+  if ((bits & 0x7f800000u) == 0x7f800000u) {
+    uint16_t upper = uint16_t(bits >> 16);
+    if ((bits & 0x007fffffu) && !(upper & 0x007fu)) upper |= 1;
+    return upper;
+  }
+  return uint16_t((bits + 0x7fffu + ((bits >> 16) & 1u)) >> 16);
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Pointers to one KV head's slab of each tensor of one page in one layer
+// (runtime/metal/kernels/common/kv_extent.h:53-108).
+struct PageSlabs {
+  uint8_t *keys;
+  uint8_t *values;
+  float *key_scales;
+  float *value_scales;
+};
+
+template <uint32_t Format, uint32_t KvHeads, uint32_t HeadDim> struct PageGeometry {
+  static constexpr bool kQuantized = Format != RK_FORMAT_BF16;
+  static constexpr uint32_t kElementBits = Format == RK_FORMAT_BF16 ? 16 : (Format == RK_FORMAT_INT4 ? 4 : 8);
+  static constexpr uint32_t kDataBytes = kPageTokens * KvHeads * HeadDim * kElementBits / 8;
+  static constexpr uint32_t kScaleBytes = kQuantized ? kPageTokens * KvHeads * 4 : 0;
+  static constexpr uint32_t kHeadDataBytes = kDataBytes / KvHeads;
+  static constexpr uint32_t kRowBytes = HeadDim * kElementBits / 8; // one token-major row
+
+  __device__ __forceinline__ static PageSlabs slabs(rk_page_entry entry, rk_kv_layer layer, uint32_t head) {
+    const uint32_t index = rk_entry_index(entry);
+    uint8_t *region = reinterpret_cast<uint8_t *>(rk_entry_extent(entry)) + layer.offset;
+    const uint64_t pages = layer.extent_pages;
+    PageSlabs s;
+    s.keys = region + uint64_t(index) * kDataBytes + head * kHeadDataBytes;
+    s.values = region + pages * (uint64_t(kDataBytes) + kScaleBytes) + uint64_t(index) * kDataBytes +
+               head * kHeadDataBytes;
+    if (kQuantized) {
+      s.key_scales = reinterpret_cast<float *>(region + pages * kDataBytes + uint64_t(index) * kScaleBytes) +
+                     head * kPageTokens;
+      s.value_scales = reinterpret_cast<float *>(region + pages * (2ull * kDataBytes + kScaleBytes) +
+                                                 uint64_t(index) * kScaleBytes) +
+                       head * kPageTokens;
+    } else {
+      s.key_scales = nullptr;
+      s.value_scales = nullptr;
+    }
+    return s;
+  }
+};
+
+// One stored element's code as a float, before its scale
+// (K token-major for all formats; V token-major only for INT4).
+template <uint32_t Format>
+__device__ __forceinline__ float decode_element(const uint8_t *slab, uint32_t element) {
+  if (Format == RK_FORMAT_INT8) return float(reinterpret_cast<const int8_t *>(slab)[element]);
+  if (Format == RK_FORMAT_INT4) {
+    const int code = (slab[element >> 1] >> ((element & 1u) * 4u)) & 0xF;
+    return float(code - ((code & 8) ? 16 : 0));
+  }
+  if (Format == RK_FORMAT_FP8E4M3) {
+    const __half_raw h = __nv_cvt_fp8_to_halfraw(slab[element], __NV_E4M3);
+    return __half2float(__half(h));
+  }
+  return bf16_bits_to_float(reinterpret_cast<const uint16_t *>(slab)[element]);
+}
+
+} // namespace rk

@@ -1,0 +1,137 @@
+"""ctypes binding of librichkv.so — the C ABI declared in include/richkv.h.
+
+Loading never falls back to anything: a missing library raises, so a caller can
+not run on a silent CPU path. Build it with `python -m richengine_b200.build`.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIBRARY_PATH = Path(__file__).resolve().parent / "librichkv.so"
+
+OK, INVALID, CUDA_ERROR, UNSUPPORTED, REFUSED, TIMEOUT = 0, -1, -2, -3, -4, -5
+
+
+class KvLayer(C.Structure):
+    _fields_ = [("extent_pages", C.c_uint32), ("offset", C.c_uint32)]
+
+
+class ChunkParams(C.Structure):
+    _fields_ = [("committed_tokens", C.c_uint32), ("chunk_tokens", C.c_uint32), ("chunk_stride", C.c_uint32),
+                ("page_table_entries", C.c_uint32), ("kv", KvLayer)]
+
+
+class PrefillParams(C.Structure):
+    _fields_ = [("committed_tokens", C.c_uint32), ("rows", C.c_uint32), ("chunk_stride", C.c_uint32),
+                ("page_table_entries", C.c_uint32), ("kv", KvLayer), ("split_count", C.c_uint32),
+                ("score_scale", C.c_float)]
+
+
+class VerifyParams(C.Structure):
+    _fields_ = [("committed_tokens", C.c_uint32), ("page_table_entries", C.c_uint32), ("kv", KvLayer),
+                ("split_count", C.c_uint32), ("slot_splits", C.c_uint32), ("active_rows", C.c_uint32),
+                ("row_capacity", C.c_uint32), ("score_scale", C.c_float)]
+
+
+class PageCopy(C.Structure):
+    _fields_ = [("from_page", C.c_uint32), ("to_page", C.c_uint32)]
+
+
+class DecodePlan(C.Structure):
+    """rk_decode_plan (include/richkv.h)."""
+    _fields_ = [("lanes", C.c_uint32), ("ctas", C.c_uint32), ("max_segments", C.c_uint32), ("reserved", C.c_uint32),
+                ("partials_bytes", C.c_uint64), ("statistics_bytes", C.c_uint64), ("descriptor_bytes", C.c_uint64)]
+
+
+assert C.sizeof(ChunkParams) == 24 and C.sizeof(PrefillParams) == 32 and C.sizeof(VerifyParams) == 36
+
+u32, u64, i32, i64, vp, f32p = C.c_uint32, C.c_uint64, C.c_int, C.c_int64, C.c_void_p, C.c_void_p
+
+# name -> (restype, argtypes). Every symbol include/richkv.h declares is listed
+# here; tests check the library exports each of them.
+SIGNATURES = {
+    "rk_last_error": (C.c_char_p, []),
+    "rk_extent_alignment_pages": (u32, [u32, u32, u32]),
+    # kernels
+    "rk_store_verify": (i32, [u32, u32, u32, u32, u32, vp, vp, vp, vp, KvLayer, vp]),
+    "rk_store_chunk": (i32, [u32, u32, u32, vp, vp, vp, C.POINTER(ChunkParams), vp]),
+    "rk_attention_verify_split": (i32, [u32, u32, u32, u32, u32, u32, u32, vp, vp, vp, vp, vp, vp, KvLayer, vp]),
+    "rk_attention_verify_reduce": (i32, [u32, u32, u32, u32, u32, vp, vp, vp, vp, vp, vp]),
+    "rk_attention_prefill_split": (i32, [u32, u32, u32, u32, vp, vp, vp, vp, C.POINTER(PrefillParams), vp]),
+    "rk_attention_prefill_reduce": (i32, [u32, u32, u32, vp, vp, vp, vp, C.POINTER(PrefillParams), vp]),
+    "rk_copy_pages": (i32, [u32, u32, u32, u32, u32, vp, vp, u32, vp]),
+    "rk_pack_pages": (i32, [u32, u32, u32, u32, u32, vp, vp, u32, vp]),
+    "rk_unpack_pages": (i32, [u32, u32, u32, u32, u32, vp, vp, u32, vp]),
+    "rk_tree_compact": (i32, [u32, u32, u32, u32, vp, vp, KvLayer, vp, vp, vp]),
+    # storage
+    "rk_storage_create": (vp, [u32, u32, u32, u32, u32, u32]),
+    "rk_storage_destroy": (None, [vp]),
+    "rk_storage_allocate_extent": (i32, [vp, u32]),
+    "rk_storage_release_extent": (i32, [vp, u32]),
+    "rk_storage_set_budget": (None, [vp, u64]),
+    "rk_storage_page_count": (u32, [vp]),
+    "rk_storage_extent_pages": (u32, [vp]),
+    "rk_storage_bytes_per_page": (u64, [vp]),
+    "rk_storage_extent_bytes": (u64, [vp]),
+    "rk_storage_allocated_bytes": (u64, [vp]),
+    "rk_storage_is_allocated": (i32, [vp, u32]),
+    "rk_storage_window": (None, [vp, C.POINTER(u64), C.POINTER(u64)]),
+    "rk_storage_layers": (u32, [vp, C.POINTER(KvLayer), u32]),
+    "rk_storage_entry": (u64, [vp, u32]),
+    "rk_storage_read_extent": (i32, [vp, u32, u64, vp, u64]),
+    "rk_storage_write_extent": (i32, [vp, u32, u64, vp, u64]),
+    "rk_storage_write_entries": (i32, [vp, vp, u32, u32, vp, u32, vp]),
+    "rk_storage_copy_pages": (i32, [vp, vp, u32, vp]),
+    "rk_storage_pack_pages": (i32, [vp, vp, u32, vp, i32, vp]),
+    # pinned-host tier
+    "rk_tier_create": (vp, [vp, u32, u32]),
+    "rk_tier_destroy": (None, [vp]),
+    "rk_tier_slot_bytes": (u64, [vp]),
+    "rk_tier_writable": (i32, [vp]),
+    "rk_tier_can_demote": (i32, [vp]),
+    "rk_tier_can_restore": (i32, [vp]),
+    "rk_tier_acquire_slot": (i64, [vp]),
+    "rk_tier_release_slot": (None, [vp, u32]),
+    "rk_tier_fail_next": (None, [vp, u32]),
+    "rk_tier_slot_host_pointer": (vp, [vp, u32]),
+    "rk_tier_demote": (i32, [vp, u32, u32, vp]),
+    "rk_tier_restore": (i32, [vp, u32, u32, vp]),
+    "rk_tier_poll": (i32, [vp]),
+    "rk_tier_transfer_ready": (i32, [vp, u32]),
+    "rk_tier_transfer_finish": (i32, [vp, u32]),
+    "rk_tier_drain": (i32, [vp]),
+}
+
+_library = None
+
+
+def load() -> C.CDLL:
+    """Loads librichkv.so and types its entry points. Raises if it is missing."""
+    global _library
+    if _library is not None:
+        return _library
+    if not LIBRARY_PATH.exists():
+        raise ImportError(
+            f"{LIBRARY_PATH} is missing: build the CUDA library with `python -m richengine_b200.build`; "
+            "there is no CPU fallback")
+    library = C.CDLL(str(LIBRARY_PATH))
+    for name, (restype, argtypes) in SIGNATURES.items():
+        function = getattr(library, name)  # AttributeError names the missing symbol
+        function.restype = restype
+        function.argtypes = argtypes
+    _library = library
+    return library
+
+
+class RichKvError(RuntimeError):
+    def __init__(self, status: int, where: str):
+        text = load().rk_last_error().decode(errors="replace")
+        super().__init__(f"{where}: status {status}: {text}")
+        self.status = status
+
+
+def check(status: int, where: str) -> int:
+    if status < 0:
+        raise RichKvError(status, where)
+    return status

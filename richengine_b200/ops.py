@@ -1,0 +1,100 @@
+"""Kernel entry points over torch device tensors (thin: pointers and sizes only).
+
+Buffer layouts are the reference kernels' (runtime/metal/kernels/decode/
+paged_attention_store.metal:32-35, decode/paged_attention.metal:39-47):
+  chunk_keys   bf16 [lane][kv_head][stride][D]
+  chunk_values bf16 [lane][kv_head][D][stride]          (dimension-major)
+  queries/out  bf16 [lane][kv_head][stride][group][D]
+  tables       one device array of uint64 entries per lane; `table_pointers`
+               is a device array of their addresses
+  params       device array of the 24/36-byte parameter blocks, one per lane
+torch is used for device memory and streams only.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import lib
+from .abi import CHUNK_PARAMS, VERIFY_PARAMS, Layout
+
+
+def _stream(stream) -> int:
+    if stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    return stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream)
+
+
+def params_to_device(array: np.ndarray, device="cuda") -> torch.Tensor:
+    """Uploads a numpy structured array of parameter blocks as raw bytes."""
+    raw = np.ascontiguousarray(array).view(np.uint8).reshape(-1)
+    return torch.from_numpy(raw.copy()).to(device)
+
+
+def table_pointer_array(tables, device="cuda") -> torch.Tensor:
+    return torch.tensor([t.data_ptr() for t in tables], dtype=torch.int64, device=device)
+
+
+def store_verify(layout: Layout, chunk_keys, chunk_values, table_pointers, params, layer: lib.KvLayer,
+                 lanes: int, max_rows: int, stream=None) -> None:
+    status = lib.load().rk_store_verify(layout.format, layout.kv_heads, layout.head_dimension, lanes, max_rows,
+                                        chunk_keys.data_ptr(), chunk_values.data_ptr(), table_pointers.data_ptr(),
+                                        params.data_ptr(), layer, _stream(stream))
+    lib.check(status, "rk_store_verify")
+
+
+def store_chunk(layout: Layout, chunk_keys, chunk_values, table, params: lib.ChunkParams, stream=None) -> None:
+    status = lib.load().rk_store_chunk(layout.format, layout.kv_heads, layout.head_dimension, chunk_keys.data_ptr(),
+                                       chunk_values.data_ptr(), table.data_ptr(), C.byref(params), _stream(stream))
+    lib.check(status, "rk_store_chunk")
+
+
+def attention_verify_split(layout: Layout, query_heads: int, lanes: int, row_capacity: int, grid_splits: int,
+                           queries, partials, statistics, table_pointers, row_masks, params, layer: lib.KvLayer,
+                           stream=None) -> None:
+    status = lib.load().rk_attention_verify_split(
+        layout.format, layout.kv_heads, query_heads, layout.head_dimension, lanes, row_capacity, grid_splits,
+        queries.data_ptr(), partials.data_ptr(), statistics.data_ptr(), table_pointers.data_ptr(),
+        row_masks.data_ptr() if row_masks is not None else None, params.data_ptr(), layer, _stream(stream))
+    lib.check(status, "rk_attention_verify_split")
+
+
+def attention_verify_reduce(layout: Layout, query_heads: int, lanes: int, row_capacity: int, partials, statistics,
+                            output, params, output_f32=None, stream=None) -> None:
+    status = lib.load().rk_attention_verify_reduce(
+        layout.kv_heads, query_heads, layout.head_dimension, lanes, row_capacity, partials.data_ptr(),
+        statistics.data_ptr(), output.data_ptr(), output_f32.data_ptr() if output_f32 is not None else None,
+        params.data_ptr(), _stream(stream))
+    lib.check(status, "rk_attention_verify_reduce")
+
+
+def attention_prefill(layout: Layout, query_heads: int, queries, output, partials, statistics, table,
+                      params: lib.PrefillParams, output_f32=None, stream=None) -> None:
+    library = lib.load()
+    lib.check(library.rk_attention_prefill_split(layout.format, layout.kv_heads, query_heads, layout.head_dimension,
+                                                 queries.data_ptr(), partials.data_ptr(), statistics.data_ptr(),
+                                                 table.data_ptr(), C.byref(params), _stream(stream)),
+              "rk_attention_prefill_split")
+    lib.check(library.rk_attention_prefill_reduce(layout.kv_heads, query_heads, layout.head_dimension,
+                                                  partials.data_ptr(), statistics.data_ptr(), output.data_ptr(),
+                                                  output_f32.data_ptr() if output_f32 is not None else None,
+                                                  C.byref(params), _stream(stream)),
+              "rk_attention_prefill_reduce")
+
+
+def tree_compact(layout: Layout, lanes: int, table_pointers, params, layer: lib.KvLayer, retained_path,
+                 retained_count, stream=None) -> None:
+    status = lib.load().rk_tree_compact(layout.format, layout.kv_heads, layout.head_dimension, lanes,
+                                        table_pointers.data_ptr(), params.data_ptr(), layer,
+                                        retained_path.data_ptr(), retained_count.data_ptr(), _stream(stream))
+    lib.check(status, "rk_tree_compact")
+
+
+def chunk_params_array(lanes: int) -> np.ndarray:
+    return np.zeros(lanes, dtype=CHUNK_PARAMS)
+
+
+def verify_params_array(lanes: int) -> np.ndarray:
+    return np.zeros(lanes, dtype=VERIFY_PARAMS)

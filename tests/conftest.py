@@ -1,0 +1,39 @@
+"""pytest configuration: the `gpu` marker and one-time builds of the checker and the CUDA library."""
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "tests"))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+def pytest_collection_modifyitems(config, items):
+    """GPU tests are skipped, not failed, where no device exists."""
+    try:
+        import torch
+        has_gpu = torch.cuda.is_available()
+    except Exception:
+        has_gpu = False
+    if has_gpu:
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+@pytest.fixture(scope="session", autouse=True)
+def built_artifacts():
+    """The oracle (always rebuilt by make when stale) and the CUDA library (built only when missing)."""
+    subprocess.run(["make", "-C", str(ROOT / "oracle"), "-s"], check=True)
+    from richengine_b200 import build, lib
+    if not lib.LIBRARY_PATH.exists():
+        build.build()
+    yield

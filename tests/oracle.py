@@ -1,0 +1,85 @@
+"""ctypes access to the CPU checker (oracle/). Test infrastructure only."""
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+
+from richengine_b200.lib import ChunkParams, KvLayer, VerifyParams
+
+ROOT = Path(__file__).resolve().parent.parent
+ORACLE_PATH = ROOT / "oracle" / "_build" / "librk_oracle.so"
+REFERENCE_PATH = ROOT / "oracle" / "_ref" / "librk_ref.so"
+
+_oracle = None
+_reference = None
+u32, u64, vp = C.c_uint32, C.c_uint64, C.c_void_p
+
+
+def oracle() -> C.CDLL:
+    global _oracle
+    if _oracle is None:
+        o = C.CDLL(str(ORACLE_PATH))
+        o.rko_f32_to_bf16.restype, o.rko_f32_to_bf16.argtypes = C.c_uint16, [C.c_float]
+        o.rko_bf16_to_f32.restype, o.rko_bf16_to_f32.argtypes = C.c_float, [C.c_uint16]
+        o.rko_f32_to_e4m3.restype, o.rko_f32_to_e4m3.argtypes = C.c_uint8, [C.c_float]
+        o.rko_e4m3_to_f32.restype, o.rko_e4m3_to_f32.argtypes = C.c_float, [C.c_uint8]
+        o.rko_query_stage_f16.restype, o.rko_query_stage_f16.argtypes = C.c_float, [C.c_float]
+        o.rko_store_chunk.restype = C.c_int
+        o.rko_store_chunk.argtypes = [u32, u32, u32, vp, vp, vp, C.POINTER(ChunkParams)]
+        o.rko_store_verify.restype = C.c_int
+        o.rko_store_verify.argtypes = [u32, u32, u32, u32, vp, vp, vp, vp]
+        o.rko_attention_tile.restype = C.c_int
+        o.rko_attention_tile.argtypes = [u32, u32, u32, u32, u32, vp, vp, KvLayer, u32, u32, u32, vp, C.c_float,
+                                         C.c_int, vp]
+        o.rko_attention_verify.restype = C.c_int
+        o.rko_attention_verify.argtypes = [u32, u32, u32, u32, u32, vp, vp, vp, vp, vp, vp]
+        o.rko_merge_row.restype = None
+        o.rko_merge_row.argtypes = [vp, u64, vp, u64, u32, u32, vp]
+        o.rko_tree_compact.restype = C.c_int
+        o.rko_tree_compact.argtypes = [u32, u32, u32, vp, C.POINTER(ChunkParams), vp, u32]
+        o.rko_copy_page.restype = None
+        o.rko_copy_page.argtypes = [u32, u32, u32, u32, u32, u64, u64]
+        o.rko_threads.restype = C.c_int
+        _oracle = o
+    return _oracle
+
+
+def reference():
+    """The reference's own portable code compiled in place, or None where it was not built."""
+    global _reference
+    if _reference is None and REFERENCE_PATH.exists():
+        r = C.CDLL(str(REFERENCE_PATH))
+        r.ref_f32_to_bf16.restype, r.ref_f32_to_bf16.argtypes = C.c_uint16, [C.c_float]
+        r.ref_bf16_to_f32.restype, r.ref_bf16_to_f32.argtypes = C.c_float, [C.c_uint16]
+        r.ref_f32_to_e4m3.restype, r.ref_f32_to_e4m3.argtypes = C.c_uint8, [C.c_float]
+        r.ref_e4m3_to_f32.restype, r.ref_e4m3_to_f32.argtypes = C.c_float, [C.c_uint8]
+        r.ref_query_stage.restype, r.ref_query_stage.argtypes = C.c_float, [C.c_float]
+        r.ref_q8_quantize_page.restype, r.ref_q8_quantize_page.argtypes = C.c_int, [vp, vp, u32, vp]
+        r.ref_fp8_quantize_page.restype, r.ref_fp8_quantize_page.argtypes = C.c_int, [vp, vp, u32, vp]
+        r.ref_layout.restype, r.ref_layout.argtypes = None, [u32, u32, u32, u32, u64, vp]
+        r.ref_kv_offset.restype, r.ref_kv_offset.argtypes = u64, [u32] * 6
+        r.ref_key_element.restype, r.ref_key_element.argtypes = u64, [u32] * 4
+        r.ref_value_element.restype, r.ref_value_element.argtypes = u64, [u32] * 4
+        r.ref_scale_element.restype, r.ref_scale_element.argtypes = u64, [u32] * 2
+        r.ref_verify_splits.restype, r.ref_verify_splits.argtypes = u32, [u32, u32]
+        r.ref_chunk_validation.restype, r.ref_chunk_validation.argtypes = C.c_char_p, [u32] * 4
+        r.ref_verify_plan.restype = C.c_int
+        r.ref_verify_plan.argtypes = [u32, u32, u32, u32, u32, u32, vp, C.c_int, C.c_char_p, C.c_size_t, vp]
+        r.ref_prefill_plan.restype = C.c_int
+        r.ref_prefill_plan.argtypes = [u32, u32, u32, u32, u32, u32, C.c_char_p, C.c_size_t, vp]
+        r.ref_workspaces.restype, r.ref_workspaces.argtypes = C.c_int, [u32] * 7 + [vp]
+        r.ref_pool_create.restype, r.ref_pool_create.argtypes = vp, [u32, u64, u32, u32, u64]
+        r.ref_pool_destroy.restype, r.ref_pool_destroy.argtypes = None, [vp]
+        r.ref_pool_set_budget.restype, r.ref_pool_set_budget.argtypes = None, [vp, u64]
+        r.ref_pool_acquire.restype, r.ref_pool_acquire.argtypes = C.c_int, [vp, u32, vp]
+        r.ref_pool_retain.restype, r.ref_pool_retain.argtypes = C.c_int, [vp, u32, C.c_int]
+        r.ref_pool_release.restype, r.ref_pool_release.argtypes = C.c_int, [vp, u32, C.c_int]
+        r.ref_pool_reclaim.restype, r.ref_pool_reclaim.argtypes = u64, [vp, C.c_int, u32]
+        r.ref_pool_compact.restype, r.ref_pool_compact.argtypes = C.c_int64, [vp, vp, u32, vp]
+        r.ref_pool_snapshot.restype, r.ref_pool_snapshot.argtypes = None, [vp, vp]
+        _reference = r
+    return _reference
+
+
+def ptr(array: np.ndarray) -> int:
+    return array.ctypes.data
