@@ -73,7 +73,7 @@ class Scenario:
         self.contexts = [int(c) for c in contexts]
         self.lanes = len(self.contexts)
         self.rng = np.random.default_rng(seed)
-        need = sum(abi.pages_for(c + extra_tokens) for c in self.contexts) + 2
+        need = sum(abi.pages_for(c + extra_tokens) for c in self.contexts) + 8  # spare pages for copies
         self.extent_pages = extent_pages or layout.extent_alignment_pages()
         extents = max(min_extents, (need + self.extent_pages - 1) // self.extent_pages)
         self.host = HostPool(layout, self.extent_pages, extents)
