@@ -85,6 +85,27 @@ const DriverApi *driver_api() {
   return api.ready ? &api : nullptr;
 }
 
+int driver_status(CUresult result, const char *what);
+
+// A 2-D view of a device address window as rows of 128 bytes, loaded `box_rows`
+// rows at a time with the 128-byte shared-memory swizzle (no multicast).
+int encode_window_map(CUtensorMap *map, uint64_t base, uint64_t rows, uint32_t box_rows) {
+  const DriverApi *api = driver_api();
+  if (!api) {
+    set_error("cuTensorMapEncodeTiled is unavailable");
+    return kCudaError;
+  }
+  const cuuint64_t dims[2] = {128, rows};
+  const cuuint64_t strides[1] = {128};
+  const cuuint32_t box[2] = {128, box_rows};
+  const cuuint32_t element_strides[2] = {1, 1};
+  return driver_status(api->tensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, reinterpret_cast<void *>(base),
+                                                 dims, strides, box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
+                       "cuTensorMapEncodeTiled");
+}
+
 int driver_status(CUresult result, const char *what) {
   if (result == CUDA_SUCCESS) return kOk;
   g_error = std::string(what) + ": CUresult " + std::to_string(int(result));

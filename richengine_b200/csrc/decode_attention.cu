@@ -1,0 +1,642 @@
+// decode_attention.cu — paged GQA decode attention (one query row per lane)
+// streaming packed-INT4 pages at HBM speed.
+//
+// Semantics: the reference's tile with active_rows = 1
+//   runtime/metal/kernels/common/paged_attention_tile.h:85-189,208-349  (scores, scale fold, online softmax, P.V)
+//   runtime/metal/kernels/common/paged_attention_tile.h:362-404         (fixed-order merge)
+//   runtime/metal/kernels/decode/paged_attention.metal:23-60            (query / output placement)
+// The execution design is B200-native, not the reference's:
+//  * Work is every lane's pages laid end to end and cut into one equal,
+//    contiguous range per CTA (one CTA per SM); a range that crosses lanes
+//    yields one partial per (lane piece, KV head, warp). Every CTA derives the
+//    same partition from the lane parameters, so no plan is uploaded and the
+//    result is deterministic for a given grid.
+//  * A producer thread streams (page, KV head) units — the head's 4 KiB key
+//    slab, 4 KiB value slab and their two 128-byte scale rows — into a ring of
+//    shared-memory stages with TMA (128-byte swizzle, no multicast), completion
+//    on mbarriers. Consumer warps wait with bounded polls.
+//  * Eight consumer warps each run an independent online softmax over their own
+//    units. Group-of-6 query heads against 4-bit codes is 12 multiply-adds per
+//    KV byte — above what the fp32 pipes sustain at HBM speed — so the
+//    contractions run on the warp-level tensor path (mma.sync m16n8k16, fp16
+//    operands, fp32 accumulate) with the codes expanded in registers:
+//      S^T[token, head] = K[token, dim] . Q^T[dim, head]   (tokens are the M rows)
+//      O^T[dim, head]  += V^T[dim, token] . P^T[token, head]
+//    Key nibbles become fp16 bit patterns directly (u * 2^-24, u = code + 8); the
+//    +8 is removed exactly through 8 * sum(q). Value nibbles use the 1024 + u
+//    mantissa trick and an exact fp16 subtract. Codes, queries (bf16 -> fp16,
+//    exact in range) and products are exact; accumulation is fp32.
+//  * The token scale folds into the softmax as in the reference, and the value
+//    scale folds into the exponent: w = 2^(s + log2 vscale - m), so the fp16
+//    probabilities stay in (0, 2^14] whatever the value magnitudes are.
+#include "common.cuh"
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+namespace rk {
+
+struct DriverApi;
+const DriverApi *driver_api();
+int encode_window_map(CUtensorMap *map, uint64_t base, uint64_t rows, uint32_t box_rows);
+
+namespace {
+
+constexpr uint32_t kConsumerWarps = 8;
+constexpr uint32_t kThreads = (kConsumerWarps + 1) * 32;
+constexpr uint32_t kStages = 20;
+constexpr uint32_t kSlabBytes = 4096;               // one head's K (or V) of a page, int4
+constexpr uint32_t kStageBytes = 2 * kSlabBytes + 1024; // K | V | key scales | value scales | pad
+constexpr uint32_t kUnitBytes = 2 * kSlabBytes + 256;
+constexpr uint32_t kMaxLanes = 1024;
+constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr uint32_t kKvHeads = 4, kGroup = 6, kHeadDim = 256;
+
+struct DecodeArgs {
+  const uint16_t *queries;
+  float *partials;
+  float *statistics;
+  uint32_t *descriptors; // [lanes]{first segment, segments} then the error word
+  const rk_page_entry *const *tables;
+  const rk_verify_params *lane_params;
+  rk_kv_layer layer;
+  uint64_t window_base;
+  uint32_t lanes;
+};
+
+__device__ __forceinline__ uint32_t smem_address(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void barrier_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void barrier_expect(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void barrier_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool barrier_try(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+               : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+  return done != 0;
+}
+// Bounded wait: false when the limit ran out (the caller records the error and leaves).
+__device__ __forceinline__ bool barrier_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (barrier_try(bar, parity)) return true;
+    if (i > 32) __nanosleep(32);
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_rows(uint32_t dst, const CUtensorMap *map, int32_t row, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(0), "r"(row), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                        uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t transpose_8x8(uint32_t v) {
+  uint32_t r;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(v));
+  return r;
+}
+__device__ __forceinline__ uint32_t sub_f16x2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("sub.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ float exp2_fast(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ float log2_fast(float x) {
+  float r;
+  asm("lg2.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t *>(&h);
+}
+__device__ __forceinline__ uint4 load_shared_16(uint32_t address) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(address));
+  return v;
+}
+__device__ __forceinline__ float load_shared_f32(uint32_t address) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(address));
+  return v;
+}
+
+// The CTA that owns flattened page `x` of `total`, for `ctas` equal ranges
+// [b*total/ctas, (b+1)*total/ctas).
+__device__ __forceinline__ uint32_t cta_of(uint64_t x, uint64_t total, uint64_t ctas) {
+  return uint32_t(((x + 1) * ctas - 1) / total);
+}
+
+struct Shared {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint32_t lane_start[kMaxLanes + 1];   // pages before each lane
+  uint32_t segment_base[kMaxLanes + 1]; // partial segments before each lane
+  uint32_t scan[kThreads / 32 + 1];
+  uint32_t error;
+};
+
+// Block-wide exclusive prefix sum of values[0..n) in place (values[n] = total).
+__device__ void exclusive_scan(uint32_t *values, uint32_t n, uint32_t *scratch) {
+  const uint32_t tid = threadIdx.x, lane = tid % 32, warp = tid / 32;
+  uint32_t carry = 0;
+  for (uint32_t base = 0; base < n; base += kThreads) {
+    const uint32_t i = base + tid;
+    const uint32_t v = i < n ? values[i] : 0;
+    uint32_t inclusive = v;
+#pragma unroll
+    for (uint32_t o = 1; o < 32; o <<= 1) {
+      const uint32_t up = __shfl_up_sync(0xffffffffu, inclusive, o);
+      if (lane >= o) inclusive += up;
+    }
+    if (lane == 31) scratch[warp] = inclusive;
+    __syncthreads();
+    uint32_t before = 0;
+    for (uint32_t w = 0; w < warp; ++w) before += scratch[w];
+    uint32_t total = 0;
+    for (uint32_t w = 0; w < kThreads / 32; ++w) total += scratch[w];
+    if (i < n) values[i] = carry + before + inclusive - v;
+    carry += total;
+    __syncthreads();
+  }
+  if (tid == 0) values[n] = carry;
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs args) {
+  extern __shared__ uint8_t dynamic_shared[];
+  // Stages need 1024-byte alignment for the 128-byte swizzle pattern.
+  const uint32_t ring = (smem_address(dynamic_shared) + 1023u) & ~1023u;
+  Shared &sh = *reinterpret_cast<Shared *>(dynamic_shared + (ring - smem_address(dynamic_shared)) + kStages * kStageBytes);
+  const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const uint32_t lanes = args.lanes, cta = blockIdx.x;
+  uint32_t *error_word = args.descriptors + 2 * lanes;
+
+  // ---- partition: pages per lane -> prefix; segments per lane -> prefix -----------------
+  for (uint32_t i = tid; i < lanes; i += kThreads) {
+    rk_verify_params p = args.lane_params[i];
+    p.kv = args.layer;
+    const bool valid = rk_verify_contract_valid(&p) && p.active_rows == 1 && p.row_capacity == 1;
+    sh.lane_start[i] = valid ? rk_pages_for(p.committed_tokens + 1) : 0;
+  }
+  if (tid == 0) sh.error = 0;
+  __syncthreads();
+  exclusive_scan(sh.lane_start, lanes, sh.scan);
+  const uint64_t total_pages = sh.lane_start[lanes];
+  // Never more ranges than pages, so every range a lane spans is non-empty.
+  const uint32_t ctas = uint32_t(min(uint64_t(gridDim.x), total_pages));
+  if (cta >= ctas) return;
+  for (uint32_t i = tid; i < lanes; i += kThreads) {
+    const uint32_t begin = sh.lane_start[i], end = sh.lane_start[i + 1];
+    sh.segment_base[i] = end > begin ? cta_of(end - 1, total_pages, ctas) - cta_of(begin, total_pages, ctas) + 1 : 0;
+  }
+  __syncthreads();
+  exclusive_scan(sh.segment_base, lanes, sh.scan);
+  if (cta == 0)
+    for (uint32_t i = tid; i < lanes; i += kThreads) {
+      args.descriptors[2 * i] = sh.segment_base[i];
+      args.descriptors[2 * i + 1] = sh.segment_base[i + 1] - sh.segment_base[i];
+    }
+  const uint32_t range_begin = uint32_t(uint64_t(cta) * total_pages / ctas);
+  const uint32_t range_end = uint32_t(uint64_t(cta + 1) * total_pages / ctas);
+  if (tid == 0) {
+    for (uint32_t s = 0; s < kStages; ++s) {
+      barrier_init(smem_address(&sh.full[s]), 1);
+      barrier_init(smem_address(&sh.empty[s]), 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (range_begin >= range_end) return;
+  // first lane whose pages reach into this range
+  uint32_t first_lane;
+  {
+    uint32_t lo = 0, hi = lanes; // largest i with lane_start[i] <= range_begin
+    while (hi - lo > 1) {
+      const uint32_t mid = (lo + hi) / 2;
+      if (sh.lane_start[mid] <= range_begin) lo = mid; else hi = mid;
+    }
+    first_lane = lo;
+  }
+  const uint32_t data_bytes = kPageTokens * kKvHeads * kHeadDim / 2, scale_bytes = kPageTokens * kKvHeads * 4;
+
+  if (warp == kConsumerWarps) {
+    // ================= producer ==========================================================
+    if (lane != 0) return;
+    uint32_t unit = 0;
+    bool ok = true;
+    for (uint32_t l = first_lane; ok && l < lanes && sh.lane_start[l] < range_end; ++l) {
+      const uint32_t lane_begin = sh.lane_start[l], lane_end = sh.lane_start[l + 1];
+      const uint32_t pa = max(range_begin, lane_begin) - lane_begin;
+      const uint32_t pb = min(range_end, lane_end) - lane_begin;
+      if (pb <= pa || lane_end <= range_begin) continue;
+      const rk_page_entry *table = args.tables[l];
+      for (uint32_t page = pa; ok && page < pb; ++page) {
+        const rk_page_entry entry = table[page];
+        const uint32_t index = rk_entry_index(entry);
+        const uint64_t region = rk_entry_extent(entry) + args.layer.offset;
+        const uint64_t pages = args.layer.extent_pages;
+        const uint64_t keys = region + uint64_t(index) * data_bytes;
+        const uint64_t key_scales = region + pages * data_bytes + uint64_t(index) * scale_bytes;
+        const uint64_t values = region + pages * (uint64_t(data_bytes) + scale_bytes) + uint64_t(index) * data_bytes;
+        const uint64_t value_scales = region + pages * (2ull * data_bytes + scale_bytes) + uint64_t(index) * scale_bytes;
+        for (uint32_t head = 0; head < kKvHeads; ++head, ++unit) {
+          const uint32_t slot = unit % kStages, round = unit / kStages;
+          const uint32_t full = smem_address(&sh.full[slot]), stage = ring + slot * kStageBytes;
+          if (!barrier_wait(smem_address(&sh.empty[slot]), (round & 1u) ^ 1u)) { ok = false; break; }
+          barrier_expect(full, kUnitBytes);
+          tma_load_rows(stage, &window_map, int32_t((keys + head * kSlabBytes - args.window_base) >> 7), full);
+          tma_load_rows(stage + kSlabBytes, &window_map, int32_t((values + head * kSlabBytes - args.window_base) >> 7), full);
+          bulk_load(stage + 2 * kSlabBytes, reinterpret_cast<const void *>(key_scales + head * 128), 128, full);
+          bulk_load(stage + 2 * kSlabBytes + 128, reinterpret_cast<const void *>(value_scales + head * 128), 128, full);
+        }
+      }
+    }
+    if (!ok) {
+      atomicExch(error_word, 1u);
+      // Copies already issued must land before the block's shared memory goes.
+      const uint32_t armed = min(unit, kStages);
+      for (uint32_t back = 0; back < armed; ++back) {
+        const uint32_t u = unit - 1 - back;
+        barrier_wait(smem_address(&sh.full[u % kStages]), (u / kStages) & 1u);
+      }
+    }
+    return;
+  }
+
+  // ================= consumers =============================================================
+  const uint32_t head = warp & 3u, parity = warp >> 2;
+  const uint32_t g = lane >> 2, c = lane & 3u;
+  const uint32_t r3g = ((g & 1u) << 2) | (g >> 1); // row-in-8 swizzle partner: phase mates differ in bit 2
+
+  uint32_t units_before = 0; // units of this CTA in earlier segments
+  for (uint32_t l = first_lane; l < lanes && sh.lane_start[l] < range_end; ++l) {
+    const uint32_t lane_begin = sh.lane_start[l], lane_end = sh.lane_start[l + 1];
+    const uint32_t pa = max(range_begin, lane_begin) - lane_begin;
+    const uint32_t pb = min(range_end, lane_end) - lane_begin;
+    if (pb <= pa || lane_end <= range_begin) continue;
+    const rk_verify_params p = args.lane_params[l];
+    const uint32_t visible = p.committed_tokens + 1;
+    const uint32_t lane_pages = lane_end - lane_begin;
+
+    // ---- this warp's query fragments: B operand of S^T = K.Q^T, head g of the group -----
+    uint32_t qf[16][2];
+    float hfac[2], negoff[2];
+    {
+      const uint16_t *q = args.queries + ((uint64_t(l) * kKvHeads + head) * RK_VERIFY_CHUNK_STRIDE) * kGroup * kHeadDim +
+                          uint64_t(g) * kHeadDim;
+      float raw[2][4][8];
+      float amax = 0.0f;
+#pragma unroll
+      for (uint32_t j = 0; j < 2; ++j)
+#pragma unroll
+        for (uint32_t w = 0; w < 4; ++w) {
+          uint4 v = make_uint4(0, 0, 0, 0);
+          if (g < kGroup) v = __ldg(reinterpret_cast<const uint4 *>(q + 32 * (c + 4 * j) + 8 * w));
+          const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (uint32_t i = 0; i < 4; ++i) {
+            raw[j][w][2 * i] = bf16_bits_to_float(words[i] & 0xffffu);
+            raw[j][w][2 * i + 1] = bf16_bits_to_float(words[i] >> 16);
+            amax = fmaxf(amax, fmaxf(fabsf(raw[j][w][2 * i]), fabsf(raw[j][w][2 * i + 1])));
+          }
+        }
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      // Power-of-two prescale keeps every query inside fp16's range (exact).
+      int exponent = 0;
+      if (amax >= 8192.0f) exponent = ilogbf(amax) - 12;
+      const float down = ldexpf(1.0f, -exponent);
+      float qsum = 0.0f;
+#pragma unroll
+      for (uint32_t j = 0; j < 2; ++j)
+#pragma unroll
+        for (uint32_t w = 0; w < 4; ++w)
+#pragma unroll
+          for (uint32_t hs = 0; hs < 2; ++hs) {
+            const uint32_t s = (j * 4 + w) * 2 + hs;
+            const float e0 = raw[j][w][2 * hs] * down, e1 = raw[j][w][2 * hs + 4] * down;
+            const float o0 = raw[j][w][2 * hs + 1] * down * 0.0625f, o1 = raw[j][w][2 * hs + 5] * down * 0.0625f;
+            const __half2 even = __floats2half2_rn(e0, e1), odd = __floats2half2_rn(o0, o1);
+            qf[s][0] = *reinterpret_cast<const uint32_t *>(&even);
+            qf[s][1] = *reinterpret_cast<const uint32_t *>(&odd);
+            qsum += __low2float(even) + __high2float(even) + 16.0f * (__low2float(odd) + __high2float(odd));
+          }
+      qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
+      qsum += __shfl_xor_sync(0xffffffffu, qsum, 2);
+      // scores (log2 domain) = fma(acc, hfac, negoff) * key_scale
+      const float ss = rk_score_scale(p.score_scale, kHeadDim) * kLog2e;
+      const float my_hfac = ldexpf(ss, 24 + exponent);
+      const float my_negoff = -8.0f * qsum * ldexpf(ss, exponent);
+#pragma unroll
+      for (uint32_t j = 0; j < 2; ++j) { // C fragment columns are heads 2c, 2c+1
+        hfac[j] = __shfl_sync(0xffffffffu, my_hfac, 4 * (2 * c + j));
+        negoff[j] = __shfl_sync(0xffffffffu, my_negoff, 4 * (2 * c + j));
+      }
+    }
+
+    float m[2] = {-1.0e30f, -1.0e30f}, l_sum[2] = {0.0f, 0.0f};
+    float o[16][4];
+#pragma unroll
+    for (uint32_t t = 0; t < 16; ++t) { o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.0f; }
+
+    bool alive = true;
+    for (uint32_t page = pa + parity; alive && page < pb; page += 2) {
+      const uint32_t unit = units_before + (page - pa) * kKvHeads + head;
+      const uint32_t slot = unit % kStages, round = unit / kStages;
+      if (!barrier_wait(smem_address(&sh.full[slot]), round & 1u)) {
+        atomicExch(error_word, 2u);
+        alive = false;
+        break;
+      }
+      const uint32_t stage = ring + slot * kStageBytes;
+      const uint32_t valid = page + 1 == lane_pages ? visible - page * kPageTokens : kPageTokens;
+
+      // ---- S^T = K.Q^T : two 16-token tiles, 16 k-steps each --------------------------
+      float sacc[2][2][4];
+#pragma unroll
+      for (uint32_t mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (uint32_t h = 0; h < 2; ++h) sacc[mt][h][0] = sacc[mt][h][1] = sacc[mt][h][2] = sacc[mt][h][3] = 0.0f;
+#pragma unroll
+      for (uint32_t mt = 0; mt < 2; ++mt) {
+        const uint32_t row_a = 16 * mt + r3g, row_b = row_a + 8;
+#pragma unroll
+        for (uint32_t j = 0; j < 2; ++j) {
+          const uint32_t chunk = ((c + 4 * j) ^ r3g) * 16;
+          const uint4 ka = load_shared_16(stage + row_a * 128 + chunk);
+          const uint4 kb = load_shared_16(stage + row_b * 128 + chunk);
+          const uint32_t xa[4] = {ka.x, ka.y, ka.z, ka.w}, xb[4] = {kb.x, kb.y, kb.z, kb.w};
+#pragma unroll
+          for (uint32_t w = 0; w < 4; ++w) {
+            const uint32_t s = (j * 4 + w) * 2;
+            const uint32_t ya = xa[w] >> 8, yb = xb[w] >> 8;
+            mma_f16(sacc[mt][0], (xa[w] & 0x000F000Fu) ^ 0x00080008u, (xb[w] & 0x000F000Fu) ^ 0x00080008u,
+                    (xa[w] & 0x00F000F0u) ^ 0x00800080u, (xb[w] & 0x00F000F0u) ^ 0x00800080u, qf[s][0], qf[s][1]);
+            mma_f16(sacc[mt][1], (ya & 0x000F000Fu) ^ 0x00080008u, (yb & 0x000F000Fu) ^ 0x00080008u,
+                    (ya & 0x00F000F0u) ^ 0x00800080u, (yb & 0x00F000F0u) ^ 0x00800080u, qf[s + 1][0], qf[s + 1][1]);
+          }
+        }
+      }
+
+      // ---- online softmax over the page's 32 tokens -------------------------------------
+      float s2[2][2][2], lv[2][2];
+      float local_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (uint32_t mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (uint32_t half = 0; half < 2; ++half) {
+          const uint32_t token = 16 * mt + 8 * half + r3g;
+          const float ks = load_shared_f32(stage + 2 * kSlabBytes + token * 4);
+          const float vs = load_shared_f32(stage + 2 * kSlabBytes + 128 + token * 4);
+          const bool live = token < valid;
+          lv[mt][half] = live ? log2_fast(vs) : -INFINITY;
+          const float floor_lv = live ? fmaxf(lv[mt][half], -40.0f) : -INFINITY;
+#pragma unroll
+          for (uint32_t j = 0; j < 2; ++j) {
+            const float acc = sacc[mt][0][half * 2 + j] + sacc[mt][1][half * 2 + j];
+            const float score = live ? fmaf(acc, hfac[j], negoff[j]) * ks : -INFINITY;
+            s2[mt][half][j] = score;
+            local_max[j] = fmaxf(local_max[j], score + floor_lv);
+          }
+        }
+      if (__any_sync(0xffffffffu, local_max[0] > m[0] || local_max[1] > m[1])) {
+#pragma unroll
+        for (uint32_t j = 0; j < 2; ++j) {
+          float v = local_max[j];
+          v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+          v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+          v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+          const float next = fmaxf(m[j], v);
+          const float scale = exp2_fast(m[j] - next);
+          m[j] = next;
+          l_sum[j] *= scale;
+#pragma unroll
+          for (uint32_t t = 0; t < 16; ++t) { o[t][j] *= scale; o[t][2 + j] *= scale; }
+        }
+      }
+      uint32_t pb_frag[2][2];
+#pragma unroll
+      for (uint32_t mt = 0; mt < 2; ++mt) {
+        float w[2][2];
+#pragma unroll
+        for (uint32_t half = 0; half < 2; ++half)
+#pragma unroll
+          for (uint32_t j = 0; j < 2; ++j) {
+            const float score = s2[mt][half][j];
+            const bool live = score != -INFINITY;
+            // probabilities carry 2^14 so the smallest weights keep fp16 precision
+            w[half][j] = live ? exp2_fast(score + lv[mt][half] - m[j] + 14.0f) : 0.0f;
+            l_sum[j] += live ? exp2_fast(score - m[j]) : 0.0f;
+          }
+        pb_frag[mt][0] = transpose_8x8(pack_half2(w[0][0], w[0][1]));
+        pb_frag[mt][1] = transpose_8x8(pack_half2(w[1][0], w[1][1]));
+      }
+
+      // ---- O^T += V^T.P^T : 16 tiles of 16 dims, 2 k-steps of 16 tokens -----------------
+      const uint32_t values = stage + kSlabBytes;
+#pragma unroll
+      for (uint32_t s = 0; s < 2; ++s) {
+        const uint32_t ta = 16 * s + c;
+        const uint32_t chunk_a = (r3g ^ c) * 16, chunk_b = (r3g ^ (c + 4)) * 16;
+        const uint4 va = load_shared_16(values + ta * 128 + chunk_a);
+        const uint4 vb = load_shared_16(values + (ta + 4) * 128 + chunk_b);
+        const uint4 vc = load_shared_16(values + (ta + 8) * 128 + chunk_a);
+        const uint4 vd = load_shared_16(values + (ta + 12) * 128 + chunk_b);
+        const uint32_t xa[4] = {va.x, va.y, va.z, va.w}, xb[4] = {vb.x, vb.y, vb.z, vb.w};
+        const uint32_t xc[4] = {vc.x, vc.y, vc.z, vc.w}, xd[4] = {vd.x, vd.y, vd.z, vd.w};
+#pragma unroll
+        for (uint32_t w = 0; w < 4; ++w)
+#pragma unroll
+          for (uint32_t b = 0; b < 4; ++b) {
+            const uint32_t selector = b | (b << 4) | ((4 + b) << 8) | ((4 + b) << 12);
+            const uint32_t ab = __byte_perm(xa[w], xb[w], selector), cd = __byte_perm(xc[w], xd[w], selector);
+            // low nibble: 1024 + (n ^ 8), minus 1032 = code; high nibble: 1024 + 16 (n ^ 8), minus 1152 = 16 code
+            mma_f16(o[4 * w + b], sub_f16x2((ab & 0x000F000Fu) ^ 0x64086408u, 0x64086408u),
+                    sub_f16x2((ab & 0x00F000F0u) ^ 0x64806480u, 0x64806480u),
+                    sub_f16x2((cd & 0x000F000Fu) ^ 0x64086408u, 0x64086408u),
+                    sub_f16x2((cd & 0x00F000F0u) ^ 0x64806480u, 0x64806480u), pb_frag[s][0], pb_frag[s][1]);
+          }
+      }
+      __syncwarp();
+      if (lane == 0) barrier_arrive(smem_address(&sh.empty[slot]));
+    }
+    units_before += (pb - pa) * kKvHeads;
+
+    // ---- flush this warp's partial of (lane l, head, warp parity) --------------------------
+    {
+#pragma unroll
+      for (uint32_t j = 0; j < 2; ++j) {
+        l_sum[j] += __shfl_xor_sync(0xffffffffu, l_sum[j], 4);
+        l_sum[j] += __shfl_xor_sync(0xffffffffu, l_sum[j], 8);
+        l_sum[j] += __shfl_xor_sync(0xffffffffu, l_sum[j], 16);
+      }
+      const uint32_t segment = sh.segment_base[l] + (cta - cta_of(lane_begin, total_pages, ctas));
+      const uint64_t slot_index = (uint64_t(segment) * kKvHeads + head) * 2 + parity;
+      float *out = args.partials + slot_index * kGroup * kHeadDim;
+      float *stats = args.statistics + slot_index * kGroup * 2;
+      const float unscale = 6.103515625e-05f; // 2^-14
+#pragma unroll
+      for (uint32_t j = 0; j < 2; ++j) {
+        const uint32_t query_head = 2 * c + j;
+        if (query_head >= kGroup) continue;
+#pragma unroll
+        for (uint32_t t = 0; t < 16; ++t) {
+          const uint32_t dim = 32 * r3g + 8 * (t >> 2) + 2 * (t & 3u);
+          *reinterpret_cast<float2 *>(out + query_head * kHeadDim + dim) =
+              make_float2(o[t][j] * unscale, o[t][2 + j] * (unscale * 0.0625f));
+        }
+        if (g == 0) {
+          stats[query_head * 2] = alive ? m[j] * kLn2 : -INFINITY;
+          stats[query_head * 2 + 1] = alive ? l_sum[j] : 0.0f;
+        }
+      }
+    }
+    if (!alive) return;
+  }
+}
+
+// Merge a lane's partials in slot order and store bf16 (and optionally fp32).
+// grid (kv_heads, lanes), 256 threads = one per dimension.
+__global__ void __launch_bounds__(256)
+decode_reduce_kernel(const float *__restrict__ partials, const float *__restrict__ statistics,
+                     const uint32_t *__restrict__ descriptors, uint16_t *__restrict__ output,
+                     float *__restrict__ output_f32, const rk_verify_params *__restrict__ lane_params,
+                     rk_kv_layer layer) {
+  const uint32_t head = blockIdx.x, l = blockIdx.y, tid = threadIdx.x;
+  rk_verify_params p = lane_params[l];
+  p.kv = layer;
+  if (!rk_verify_contract_valid(&p) || p.active_rows != 1 || p.row_capacity != 1) return;
+  const uint32_t first = descriptors[2 * l], segments = descriptors[2 * l + 1];
+  const uint64_t tile = ((uint64_t(l) * kKvHeads + head) * RK_VERIFY_CHUNK_STRIDE) * kGroup * kHeadDim;
+  for (uint32_t query_head = 0; query_head < kGroup; ++query_head) {
+    float maximum = -INFINITY;
+    for (uint32_t s = 0; s < segments; ++s)
+      for (uint32_t w = 0; w < 2; ++w)
+        maximum = fmaxf(maximum, statistics[(((uint64_t(first + s) * kKvHeads + head) * 2 + w) * kGroup + query_head) * 2]);
+    float numerator = 0.0f, denominator = 0.0f;
+    for (uint32_t s = 0; s < segments; ++s)
+      for (uint32_t w = 0; w < 2; ++w) { // fixed order: segment, then warp
+        const uint64_t slot = (uint64_t(first + s) * kKvHeads + head) * 2 + w;
+        const float mx = statistics[(slot * kGroup + query_head) * 2];
+        const float weight = mx == -INFINITY ? 0.0f : expf(mx - maximum);
+        numerator += weight * partials[(slot * kGroup + query_head) * kHeadDim + tid];
+        denominator += weight * statistics[(slot * kGroup + query_head) * 2 + 1];
+      }
+    const float value = denominator > 0.0f ? numerator / denominator : 0.0f;
+    output[tile + query_head * kHeadDim + tid] = float_to_bf16_bits(value);
+    if (output_f32) output_f32[tile + query_head * kHeadDim + tid] = value;
+  }
+}
+
+struct Window {
+  uint64_t base = 0, bytes = 0;
+  CUtensorMap int4_map;
+};
+
+} // namespace
+} // namespace rk
+
+using namespace rk;
+
+extern "C" {
+
+typedef struct rk_decode_plan {
+  uint32_t lanes, ctas, max_segments, reserved;
+  uint64_t partials_bytes, statistics_bytes, descriptor_bytes;
+} rk_decode_plan;
+
+// Sizes the scratch of a decode step: `ctas` = 0 takes one CTA per SM of the current device.
+int rk_decode_plan_make(uint32_t format, uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim,
+                        uint32_t lanes, uint32_t ctas, rk_decode_plan *plan) {
+  if (!plan || !lanes || lanes > kMaxLanes) { set_error("rk_decode_plan_make: lanes out of range"); return kInvalid; }
+  if (format != RK_FORMAT_INT4 || kv_heads != kKvHeads || query_heads != kKvHeads * kGroup || head_dim != kHeadDim) {
+    set_error("rk_decode_plan_make: the streaming decode kernel is built for int4, 4 KV heads x 24 query heads x 256");
+    return kUnsupported;
+  }
+  if (!ctas) {
+    int device = 0, sms = 0;
+    if (int s = cuda_status(cudaGetDevice(&device), "cudaGetDevice")) return s;
+    if (int s = cuda_status(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device), "SM count")) return s;
+    ctas = uint32_t(sms);
+  }
+  plan->lanes = lanes;
+  plan->ctas = ctas;
+  plan->max_segments = lanes + ctas;
+  plan->reserved = 0;
+  const uint64_t slots = uint64_t(plan->max_segments) * kKvHeads * 2;
+  plan->partials_bytes = slots * kGroup * kHeadDim * sizeof(float);
+  plan->statistics_bytes = slots * kGroup * 2 * sizeof(float);
+  plan->descriptor_bytes = (2ull * lanes + 4) * sizeof(uint32_t);
+  return kOk;
+}
+
+// The device address window every page of a pool lies in (rk_storage_window).
+void *rk_window_create(uint64_t base, uint64_t bytes) {
+  if (!base || (base & 1023u) || !bytes || (bytes >> 7) > 0x7fffffffull) {
+    set_error("rk_window_create: the window must be 1 KiB-aligned and span less than 256 GiB");
+    return nullptr;
+  }
+  auto *w = new Window;
+  w->base = base;
+  w->bytes = bytes;
+  if (encode_window_map(&w->int4_map, base, bytes >> 7, 32)) { delete w; return nullptr; }
+  return w;
+}
+void rk_window_destroy(void *window) { delete static_cast<Window *>(window); }
+
+int rk_attention_decode(const void *window, const rk_decode_plan *plan, uint32_t format, const void *queries,
+                        void *output, float *output_f32, float *partials, float *statistics, uint32_t *descriptors,
+                        const rk_page_entry *const *tables, const rk_verify_params *lane_params, rk_kv_layer layer,
+                        void *stream) {
+  const auto *w = static_cast<const Window *>(window);
+  if (!w || !plan || !queries || !output || !partials || !statistics || !descriptors || !tables || !lane_params ||
+      !layer.extent_pages || format != RK_FORMAT_INT4) {
+    set_error("rk_attention_decode: invalid arguments");
+    return kInvalid;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  constexpr size_t shared_bytes = 1024 + kStages * kStageBytes + sizeof(Shared);
+  static bool configured = false;
+  if (!configured) {
+    if (int st = cuda_status(cudaFuncSetAttribute(decode_int4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(shared_bytes)), "decode shared memory")) return st;
+    configured = true;
+  }
+  DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, plan->lanes};
+  if (int st = cuda_status(cudaMemsetAsync(descriptors + 2 * plan->lanes, 0, sizeof(uint32_t), s), "decode status clear")) return st;
+  decode_int4_kernel<<<plan->ctas, kThreads, shared_bytes, s>>>(w->int4_map, args);
+  if (int st = cuda_status(cudaGetLastError(), "decode launch")) return st;
+  decode_reduce_kernel<<<dim3(kKvHeads, plan->lanes), 256, 0, s>>>(partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer);
+  return cuda_status(cudaGetLastError(), "decode reduce launch");
+}
+
+// Reads the step's device status word (synchronises the stream): 0, or kTimeout
+// when a bounded wait inside the kernel ran out.
+int rk_attention_decode_status(const rk_decode_plan *plan, const uint32_t *descriptors, void *stream) {
+  uint32_t word = 0;
+  if (int st = cuda_status(cudaMemcpyAsync(&word, descriptors + 2 * plan->lanes, sizeof(word), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)), "decode status read")) return st;
+  if (int st = cuda_status(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)), "decode status sync")) return st;
+  if (word) { set_error("a bounded wait in the decode kernel ran out"); return kTimeout; }
+  return kOk;
+}
+
+} // extern "C"

@@ -64,6 +64,12 @@ SIGNATURES = {
     "rk_pack_pages": (i32, [u32, u32, u32, u32, u32, vp, vp, u32, vp]),
     "rk_unpack_pages": (i32, [u32, u32, u32, u32, u32, vp, vp, u32, vp]),
     "rk_tree_compact": (i32, [u32, u32, u32, u32, vp, vp, KvLayer, vp, vp, vp]),
+    # streaming decode attention
+    "rk_decode_plan_make": (i32, [u32, u32, u32, u32, u32, u32, C.POINTER(DecodePlan)]),
+    "rk_window_create": (vp, [u64, u64]),
+    "rk_window_destroy": (None, [vp]),
+    "rk_attention_decode": (i32, [vp, C.POINTER(DecodePlan), u32, vp, vp, vp, vp, vp, vp, vp, vp, KvLayer, vp]),
+    "rk_attention_decode_status": (i32, [C.POINTER(DecodePlan), vp, vp]),
     # storage
     "rk_storage_create": (vp, [u32, u32, u32, u32, u32, u32]),
     "rk_storage_destroy": (None, [vp]),

@@ -98,3 +98,49 @@ def chunk_params_array(lanes: int) -> np.ndarray:
 
 def verify_params_array(lanes: int) -> np.ndarray:
     return np.zeros(lanes, dtype=VERIFY_PARAMS)
+
+
+class DecodeAttention:
+    """Streaming decode attention over one pool's address window (rk_attention_decode).
+
+    Holds the window's tensor map and the step's scratch, sized by the plan:
+    one query row per lane, row capacity 1; the lane parameter blocks and the
+    page tables live on the device.
+    """
+
+    def __init__(self, layout: Layout, query_heads: int, lanes: int, window: tuple[int, int], ctas: int = 0):
+        self._lib = lib.load()
+        self.layout, self.query_heads, self.lanes = layout, query_heads, lanes
+        self.plan = lib.DecodePlan()
+        lib.check(self._lib.rk_decode_plan_make(layout.format, layout.kv_heads, query_heads, layout.head_dimension,
+                                                lanes, ctas, C.byref(self.plan)), "rk_decode_plan_make")
+        self._window = self._lib.rk_window_create(window[0], window[1])
+        if not self._window:
+            raise lib.RichKvError(lib.INVALID, "rk_window_create")
+        self.partials = torch.empty(self.plan.partials_bytes // 4, dtype=torch.float32, device="cuda")
+        self.statistics = torch.empty(self.plan.statistics_bytes // 4, dtype=torch.float32, device="cuda")
+        self.descriptors = torch.zeros(self.plan.descriptor_bytes // 4, dtype=torch.int32, device="cuda")
+
+    def close(self):
+        if self._window:
+            self._lib.rk_window_destroy(self._window)
+            self._window = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def run(self, queries, output, table_pointers, params, layer: lib.KvLayer, output_f32=None, stream=None):
+        status = self._lib.rk_attention_decode(
+            self._window, C.byref(self.plan), self.layout.format, queries.data_ptr(), output.data_ptr(),
+            output_f32.data_ptr() if output_f32 is not None else None, self.partials.data_ptr(),
+            self.statistics.data_ptr(), self.descriptors.data_ptr(), table_pointers.data_ptr(), params.data_ptr(),
+            layer, _stream(stream))
+        lib.check(status, "rk_attention_decode")
+
+    def status(self, stream=None) -> None:
+        """Raises if a bounded device wait ran out during the steps launched so far."""
+        lib.check(self._lib.rk_attention_decode_status(C.byref(self.plan), self.descriptors.data_ptr(), _stream(stream)),
+                  "rk_attention_decode_status")

@@ -110,3 +110,21 @@ def assert_extents_equal(scenario: Scenario, what=""):
             where = np.nonzero(got != want)[0]
             raise AssertionError(f"{what}: extent {extent} differs at {len(where)} bytes, first {where[:8]} "
                                  f"got {got[where[:8]]} want {want[where[:8]]}")
+
+
+def run_decode_attention_gpu(scenario: Scenario, queries: np.ndarray, layer_index=0, committed=None, ctas=0):
+    """Streaming decode kernel: one query row per lane. Returns (bf16 bits, fp32) [lane][H][32][G][D]."""
+    layout = scenario.layout
+    params, _ = verify_params(scenario, 1, 1, 32, layer_index, committed)
+    d_params = struct_to_device(params)
+    q = dev(queries)
+    out = torch.zeros_like(q)
+    out32 = torch.zeros(q.shape, dtype=torch.float32, device="cuda")
+    runner = ops.DecodeAttention(layout, 24, scenario.lanes, scenario.storage.window(), ctas)
+    runner.partials.fill_(float("nan"))
+    runner.statistics.fill_(float("nan"))
+    runner.run(q, out, scenario.table_pointers, d_params, scenario.storage.layers()[layer_index], output_f32=out32)
+    runner.status()
+    torch.cuda.synchronize()
+    runner.close()
+    return host_u16(out), out32.cpu().numpy()

@@ -1,0 +1,102 @@
+"""GPU: the streaming int4 decode kernel (TMA page ring + warp-level MMA) against the checker,
+against the general tile, and through its size-independent properties."""
+import numpy as np
+import pytest
+import torch
+
+import oracle as om
+from gpuhelp import (assert_attention_close, chunk_params, run_decode_attention_gpu, run_verify_attention_gpu,
+                     run_verify_attention_oracle)
+from kvcase import Scenario, fill_history_with_store, make_queries, make_staging
+from richengine_b200.abi import INT4, Layout
+
+pytestmark = pytest.mark.gpu
+
+
+def prepared(contexts, seed=3, layers=1, layer=0):
+    s = Scenario(Layout(layers, 4, 256, INT4), contexts, extra_tokens=1, device=True, seed=seed)
+    fill_history_with_store(s, layer, seed=seed)
+    rng = np.random.default_rng(seed + 100)
+    k, v = make_staging(rng, s.lanes, s.layout)
+    params = chunk_params(s, 1, layer)
+    assert om.oracle().rko_store_verify(INT4, 4, 256, s.lanes, k.ctypes.data, v.ctypes.data, s.host_table_pointers(), params) == 0
+    s.upload()
+    return s, make_queries(rng, s.lanes, s.layout)
+
+
+@pytest.mark.parametrize("contexts", [[0], [1], [31], [32], [33], [0, 31, 32, 700], [4095, 17, 2048, 5, 64, 63, 999]])
+def test_decode_matches_checker(contexts):
+    s, q = prepared(contexts)
+    got16, got32 = run_decode_attention_gpu(s, q)
+    _, want32 = run_verify_attention_oracle(s, q, 1, 1)
+    assert_attention_close(got32, want32, got16, f"decode {contexts}")
+    assert not got16[:, :, 1:].any()  # only row 0 of each tile is written
+    s.close()
+
+
+@pytest.mark.parametrize("ctas", [1, 3, 7, 148, 1000])
+def test_partition_independent_of_grid(ctas):
+    """Any number of CTA ranges gives the same attention within the bar; one range is one tile."""
+    s, q = prepared([700, 33, 1500, 64], seed=9)
+    _, want32 = run_verify_attention_oracle(s, q, 1, 1)
+    got16, got32 = run_decode_attention_gpu(s, q, ctas=ctas)
+    assert_attention_close(got32, want32, got16, f"ctas {ctas}")
+    s.close()
+
+
+def test_decode_repeatable_and_agrees_with_general_tile():
+    s, q = prepared([3000, 257, 8191], seed=11, layers=2, layer=1)
+    a16, a32 = run_decode_attention_gpu(s, q, layer_index=1)
+    b16, b32 = run_decode_attention_gpu(s, q, layer_index=1)
+    assert np.array_equal(a16, b16) and np.array_equal(a32, b32)  # same grid, same bits
+    _, tile32, _ = run_verify_attention_gpu(s, q, 1, 1, layer_index=1)
+    assert_attention_close(a32, tile32, None, "decode vs general tile")
+    s.close()
+
+
+def test_zero_rows_and_extreme_scales():
+    """All-zero K or V rows (scale 0) and very large / very small value magnitudes."""
+    s = Scenario(Layout(1, 4, 256, INT4), [95, 40], extra_tokens=1, device=True, seed=4)
+    fill_history_with_store(s, 0, seed=4)
+    host = s.host
+    for lane, pages in enumerate(s.pages):
+        for page in pages[:2]:
+            vs = host.tensor_view(page, 0, 3).view(np.float32)
+            ks = host.tensor_view(page, 0, 1).view(np.float32)
+            vs[3] = 0.0; host.tensor_view(page, 0, 2)[3 * 128:(3 + 1) * 128] = 0  # zero V row (head 0, token 3)
+            ks[40] = 0.0                                                           # zero K row (head 1, token 8)
+            vs[64:96] *= np.float32(3.0e4)                                        # head 2: huge values
+            vs[96:128] *= np.float32(1.0e-6)                                       # head 3: tiny values
+    rng = np.random.default_rng(1)
+    k, v = make_staging(rng, s.lanes, s.layout)
+    params = chunk_params(s, 1, 0)
+    assert om.oracle().rko_store_verify(INT4, 4, 256, s.lanes, k.ctypes.data, v.ctypes.data, s.host_table_pointers(), params) == 0
+    s.upload()
+    q = make_queries(rng, s.lanes, s.layout)
+    got16, got32 = run_decode_attention_gpu(s, q)
+    _, want32 = run_verify_attention_oracle(s, q, 1, 1)
+    for head in range(4):  # per head: magnitudes differ by ten orders
+        assert_attention_close(got32[:, head] / max(1e-30, np.abs(want32[:, head]).max()),
+                               want32[:, head] / max(1e-30, np.abs(want32[:, head]).max()), None, f"head {head}")
+    s.close()
+
+
+def test_invalid_lane_is_skipped():
+    s, q = prepared([100, 50, 70])
+    from gpuhelp import dev, host_u16, struct_to_device, verify_params
+    from richengine_b200 import ops
+    params, _ = verify_params(s, 1, 1, 32)
+    params[1].page_table_entries = 0  # contract violation: lane 1 must not be touched
+    dq = dev(q)
+    out = torch.full_like(dq, 0x1234)
+    runner = ops.DecodeAttention(s.layout, 24, 3, s.storage.window())
+    runner.run(dq, out, s.table_pointers, struct_to_device(params), s.storage.layers()[0])
+    runner.status()
+    torch.cuda.synchronize()
+    got = host_u16(out)
+    assert (got[1] == 0x1234).all()
+    _, want32 = run_verify_attention_oracle(s, q, 1, 1)
+    from kvcase import bf16_to_f32
+    for lane in (0, 2):
+        assert np.abs(bf16_to_f32(got[lane, :, 0]) - want32[lane, :, 0]).max() < 2e-3 * max(1, np.abs(want32).max()) + 2 ** -8 * np.abs(want32).max()
+    s.close()
