@@ -1,0 +1,422 @@
+"""Benchmark of the paged, quantized KV-cache hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--batch B] [--context T] [--layers L] [--ragged]
+
+A step is one decode pass over the batch: for each attention layer, append one
+new K/V token per sequence (quantize into its page) and run one-query paged
+decode attention over the whole history. The default workload is the headline
+one: int4 KV, 27B geometry (16 layers x 4 KV heads x 256, 24 query heads),
+batch 64, 32 768-token contexts, random non-contiguous page tables, synthetic
+bf16 N(0,1) K/V with four x20 outlier channels per head (stored through the
+library's own append path).
+
+Prints ONE JSON line (rank 0). `value` is KV GB/s with everything resident in
+HBM; `e2e` the same metric through the host-buffer call; `roofline` the decode
+kernel against the measured HBM peak; `cpu_baseline` the CPU checker timed on a
+bounded sample of the same workload. With N > 1 (torchrun) every rank runs its
+own batch (requests are sharded, no collective on the data path): weak scaling.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+KV_HEADS, QUERY_HEADS, HEAD_DIM = 4, 24, 256
+METRIC = "int4_paged_decode_attention_kv_gbps"
+# dram__bytes_read.sum + dram__bytes_write.sum of the decode kernel per algorithmic KV byte, from the ncu
+# capture summarised under profiles/ (a smaller case of the same kernel; traffic grows with the pages read).
+DRAM_BYTES_PER_ALGORITHMIC_BYTE = None
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--context", type=int, default=32768)
+    ap.add_argument("--layers", type=int, default=16)
+    ap.add_argument("--ragged", action="store_true", help="contexts uniform in [context/4, context]")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    return ap.parse_args()
+
+
+def contexts_for(args, rank: int) -> list[int]:
+    if not args.ragged:
+        return [args.context] * args.batch
+    rng = np.random.default_rng(1000 + rank)
+    return [int(x) for x in rng.integers(args.context // 4, args.context + 1, size=args.batch)]
+
+
+def workload_name(args) -> str:
+    shape = f"ctx U[{args.context // 4},{args.context}]" if args.ragged else f"ctx {args.context}"
+    return (f"int4 KV, 27B geometry ({args.layers} layers x {KV_HEADS} KV heads x {HEAD_DIM}, {QUERY_HEADS} query heads), "
+            f"batch {args.batch}, {shape}, random page tables; per layer: append 1 token + 1-query decode attention")
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU leg (the checker): bounded sample of the same workload. Used by cpu_baseline and --impl reference.
+# ------------------------------------------------------------------------------------------------
+class CpuSample:
+    """`lanes` sequences of `context` tokens, one layer of int4 pages in host memory with the
+    production addressing, filled with seeded random codes and scales; one-query decode attention
+    through the checker, all host threads."""
+
+    def __init__(self, lanes: int, context: int, seed: int = 5):
+        sys.path.insert(0, str(ROOT / "tests"))
+        subprocess.run(["make", "-C", str(ROOT / "oracle"), "-s"], check=True)
+        import oracle as om
+        from kvcase import HostPool, f32_to_bf16
+        from richengine_b200 import lib
+        from richengine_b200.abi import INT4, Layout, pages_for
+        self.om, self.lib = om, lib
+        self.layout = Layout(1, KV_HEADS, HEAD_DIM, INT4)
+        self.lanes, self.context = lanes, context
+        rng = np.random.default_rng(seed)
+        pages_per_lane = pages_for(context + 1)
+        extent_pages = 256
+        extents = (lanes * pages_per_lane + extent_pages - 1) // extent_pages
+        self.pool = HostPool(self.layout, extent_pages, extents)
+        for extent in range(extents):  # codes in -7..7, scales like amax/7 of N(0,1) rows with outliers
+            raw = self.pool.bytes[extent]
+            nib = rng.integers(0, 15, size=(raw.size, 2), dtype=np.uint8)
+            raw[:] = (((nib[:, 0].astype(np.int16) - 7) & 0xF) | (((nib[:, 1].astype(np.int16) - 7) & 0xF) << 4)).astype(np.uint8)
+            data, scale = self.layout.data_bytes_per_layer_page(), self.layout.scale_bytes_per_layer_page()
+            for tensor in (1, 3):
+                start = self.layout.layer_offset(extent_pages, 0, tensor, 0)
+                view = raw[start:start + extent_pages * scale].view(np.float32)
+                view[:] = rng.uniform(0.4, 9.0, size=view.size).astype(np.float32)
+        order = rng.permutation(self.pool.page_count)
+        self.pages = [order[i * pages_per_lane:(i + 1) * pages_per_lane] for i in range(lanes)]
+        self.tables = [self.pool.table(p) for p in self.pages]
+        self.table_pointers = (C.c_void_p * lanes)(*[t.ctypes.data for t in self.tables])
+        self.params = (lib.VerifyParams * lanes)(*[
+            lib.VerifyParams(context, pages_per_lane, self.pool.layer(0), 32, 32, 1, 1, 0.0) for _ in range(lanes)])
+        self.queries = f32_to_bf16(rng.standard_normal((lanes, KV_HEADS, 32, QUERY_HEADS // KV_HEADS, HEAD_DIM)).astype(np.float32))
+        self.output = np.zeros(self.queries.shape, np.uint16)
+        self.kv_bytes = lanes * (context + 1) * self.layout.bytes_per_token_layer()
+        self.threads = om.oracle().rko_threads()
+
+    def run_once(self) -> float:
+        start = time.perf_counter()
+        status = self.om.oracle().rko_attention_verify(self.layout.format, KV_HEADS, QUERY_HEADS // KV_HEADS, HEAD_DIM,
+                                                       self.lanes, self.queries.ctypes.data, self.table_pointers,
+                                                       self.params, None, self.output.ctypes.data, None)
+        assert status == 0
+        return time.perf_counter() - start
+
+    def describe(self) -> str:
+        return (f"{self.lanes} sequences x {self.context} tokens, 1 layer, one-query decode attention "
+                f"(checker port of the reference tile, OpenMP)")
+
+
+def cpu_baseline(args, budget_seconds: float) -> dict:
+    lanes = min(args.batch, 16)
+    sample = CpuSample(lanes, args.context)
+    sample.run_once()  # warm-up
+    times, spent = [], 0.0
+    while spent < budget_seconds and len(times) < 64:
+        times.append(sample.run_once())
+        spent += times[-1]
+    median = statistics.median(times)
+    return {"value": round(sample.kv_bytes / median / 1e9, 3), "unit": "GB/s", "cores": sample.threads, "kind": "port",
+            "sample": f"{sample.describe()}; median of {len(times)} passes, {median * 1e3:.1f} ms each"}
+
+
+def run_reference(args):
+    """The reference's CPU implementation of the path = the checker port (its kernels are Metal and do not
+    build here). Rank 0 only."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    sample = CpuSample(min(args.batch, 16), args.context)
+    for _ in range(max(args.warmup, 1)):
+        sample.run_once()
+    times = [sample.run_once() for _ in range(args.steps)]
+    total = sum(times)
+    value = sample.kv_bytes * args.steps / total / 1e9
+    line = {
+        "metric": METRIC, "value": round(value, 3), "unit": "GB/s", "impl": "reference", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(total / args.steps * 1e3, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int4 codes, fp32 math",
+        "data": "synthetic", "config": {"workload": workload_name(args)},
+        "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": sample.threads, "kind": "port",
+                         "sample": sample.describe() + "; each step is one pass over the sample"},
+        "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU leg
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.samples = []
+        self.process = None
+        try:
+            self.process = subprocess.Popen(["nvidia-smi", f"--id={device_index}", f"--query-gpu={self.QUERY}",
+                                             "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                            stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.process = None
+
+    def _read(self):
+        for line in self.process.stdout:
+            self.samples.append((time.perf_counter(), line.strip()))
+
+    def stop(self, begin: float, end: float) -> dict:
+        if self.process is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.process.terminate()
+        clocks, maxima, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for stamp, line in self.samples:
+            if stamp < begin or stamp > end:
+                continue
+            fields = [f.strip() for f in line.split(",")]
+            if len(fields) < 7:
+                continue
+            try:
+                clocks.append(float(fields[0])); maxima.append(float(fields[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, fields[3:7]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max(maxima) if maxima else None,
+                "samples": len(clocks), "reasons": sorted(reasons)}
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from richengine_b200 import lib, ops
+    from richengine_b200.abi import INT4, Layout, pages_for
+    from richengine_b200.session import DecodeSession
+    from richengine_b200.storage import PageStorage
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    lib.load()
+
+    layout = Layout(args.layers, KV_HEADS, HEAD_DIM, INT4)
+    contexts = contexts_for(args, rank)
+    lanes = len(contexts)
+    steps_total = args.warmup + args.steps
+    # every lane keeps room for the tokens the run appends
+    lane_pages = [pages_for(c + 2 * steps_total + 2) for c in contexts]
+    extent_pages = layout.extent_pages_for(sum(lane_pages)) or layout.minimum_extent_pages()
+    extents = (sum(lane_pages) + extent_pages - 1) // extent_pages
+    storage = PageStorage(layout, extents * extent_pages, extent_pages)
+    for extent in range(extents):
+        if not storage.allocate_extent(extent):
+            raise RuntimeError("KV pool does not fit in device memory")
+    rng = np.random.default_rng(42 + rank)
+    order = rng.permutation(extents * extent_pages)
+    tables, cursor = [], 0
+    for count in lane_pages:
+        table = torch.zeros(count, dtype=torch.int64, device="cuda")
+        storage.write_entries(order[cursor:cursor + count], 0, table)
+        tables.append(table)
+        cursor += count
+    table_pointers = ops.table_pointer_array(tables)
+    places = storage.layers()
+
+    # ---- fill the history through the library's own chunk store -------------------------------
+    chunk = 2048
+    generator = torch.Generator(device="cuda").manual_seed(7 + rank)
+    def staging():
+        k = torch.randn((KV_HEADS, chunk, HEAD_DIM), generator=generator, device="cuda")
+        v = torch.randn((KV_HEADS, HEAD_DIM, chunk), generator=generator, device="cuda")
+        for head in range(KV_HEADS):
+            channels = torch.randperm(HEAD_DIM, generator=generator, device="cuda")[:4]
+            k[head][:, channels] *= 20.0
+            v[head][channels, :] *= 20.0
+        return k.to(torch.bfloat16).contiguous(), v.to(torch.bfloat16).contiguous()
+    stagings = [staging() for _ in range(4)]
+    for lane, context in enumerate(contexts):
+        done = 0
+        while done < context:
+            rows = min(chunk, context - done)
+            k, v = stagings[(lane + done // chunk) % len(stagings)]
+            for layer in range(args.layers):
+                ops.store_chunk(layout, k, v, tables[lane], lib.ChunkParams(done, rows, chunk, lane_pages[lane], places[layer]))
+            done += rows
+    torch.cuda.synchronize()
+
+    session = DecodeSession(storage, QUERY_HEADS, lanes)
+    session.queries.normal_(generator=generator)
+    session.chunk_keys.normal_(generator=generator)
+    session.chunk_values.normal_(generator=generator)
+
+    def params_for(step: int):
+        chunk_params = np.zeros(lanes, dtype=ops.CHUNK_PARAMS)
+        verify_params = np.zeros(lanes, dtype=ops.VERIFY_PARAMS)
+        for lane, context in enumerate(contexts):
+            committed = context + step
+            chunk_params[lane] = (committed, 1, 32, lane_pages[lane], (extent_pages, 0))
+            verify_params[lane] = (committed, lane_pages[lane], (extent_pages, 0), 1, 1, 1, 1, 0.0)
+        return ops.params_to_device(chunk_params), ops.params_to_device(verify_params)
+    device_params = [params_for(step) for step in range(2 * steps_total + 1)]
+    kv_bytes_per_step = lambda step: sum(c + step + 1 for c in contexts) * layout.bytes_per_token_layer() * args.layers
+
+    stream = torch.cuda.current_stream()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def device_step(step: int):
+        cp, vp = device_params[step]
+        for layer in range(args.layers):
+            session.step_device(layer, table_pointers, cp, vp)
+
+    # ---- device-resident timing: `value` -------------------------------------------------------
+    for step in range(args.warmup):
+        device_step(step)
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    launches_before = session.kernel_launches
+    begin_wall = time.perf_counter()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for step in range(args.warmup, steps_total):
+        device_step(step)
+    stop.record()
+    barrier()
+    end_wall = time.perf_counter()
+    elapsed_ms = start.elapsed_time(stop)
+    launches = session.kernel_launches - launches_before
+    session.attention.status()
+    clocks = sampler.stop(begin_wall, end_wall) if sampler else None
+    timed_bytes = sum(kv_bytes_per_step(s) for s in range(args.warmup, steps_total))
+
+    # ---- decode kernel alone: roofline -----------------------------------------------------------
+    cp, vp = device_params[steps_total]
+    events = []
+    for repeat in range(2):
+        for layer in range(args.layers):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            session.attend_device(layer, table_pointers, vp)
+            b.record()
+            if repeat:
+                events.append((a, b))
+    torch.cuda.synchronize()
+    kernel_ms = statistics.mean(a.elapsed_time(b) for a, b in events)
+    layer_bytes = sum(c + steps_total + 1 for c in contexts) * layout.bytes_per_token_layer()
+
+    # ---- end to end through the host-buffer call: `e2e` -----------------------------------------
+    q_host = torch.randn((lanes, QUERY_HEADS, HEAD_DIM)).to(torch.bfloat16).pin_memory()
+    k_host = torch.randn((lanes, KV_HEADS, HEAD_DIM)).to(torch.bfloat16).pin_memory()
+    v_host = torch.randn((lanes, KV_HEADS, HEAD_DIM)).to(torch.bfloat16).pin_memory()
+    out_host = torch.zeros((lanes, QUERY_HEADS, HEAD_DIM), dtype=torch.bfloat16).pin_memory()
+
+    def host_step(step: int):
+        cp, vp = device_params[step]
+        for layer in range(args.layers):
+            session.step_host(layer, q_host, k_host, v_host, out_host, table_pointers, cp, vp)
+        torch.cuda.current_stream().synchronize()  # the step's result is read on the host
+        return float(out_host[0, 0, 0])
+
+    base = steps_total
+    for step in range(args.warmup):
+        host_step(base + step)
+    barrier()
+    e2e_start = time.perf_counter()
+    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s2.record()
+    for step in range(args.warmup, steps_total):
+        host_step(base + step)
+    e2.record()
+    barrier()
+    e2e_ms = max(s2.elapsed_time(e2), 0.0)
+    e2e_wall_ms = (time.perf_counter() - e2e_start) * 1e3
+    e2e_bytes = sum(kv_bytes_per_step(base + s) for s in range(args.warmup, steps_total))
+    h2d, d2h = session.host_bytes_per_layer()
+    session.attention.status()
+
+    # ---- reduce over ranks: max time, summed bytes --------------------------------------------------
+    stats = torch.tensor([elapsed_ms, float(timed_bytes), max(e2e_ms, e2e_wall_ms), float(e2e_bytes)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        times = stats[[0, 2]].clone(); sums = stats[[1, 3]].clone()
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sums, op=dist.ReduceOp.SUM)
+        stats = torch.stack([times[0], sums[0], times[1], sums[1]])
+    elapsed_ms, timed_bytes, e2e_time_ms, e2e_bytes = [float(x) for x in stats.cpu()]
+
+    if rank == 0:
+        peaks_path = ROOT / "MEASURED_PEAKS.json"
+        if peaks_path.exists():
+            peak, peak_source = float(json.loads(peaks_path.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+        else:
+            peak, peak_source = 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+        achieved = layer_bytes / (kernel_ms * 1e-3) / 1e9
+        value = timed_bytes / (elapsed_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(elapsed_ms / args.steps, 4), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int4 codes, fp16 tensor operands, fp32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": workload_name(args), "l2": "inputs larger than L2 (KV per step >> 126 MB)",
+                       "us_per_layer_step": round(elapsed_ms / args.steps / args.layers * 1e3, 2),
+                       "kv_gb_per_step": round(timed_bytes / args.steps / world / 1e9, 3), "sharding": "by request"},
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(achieved / peak, 4), "traffic": DRAM_BYTES_PER_ALGORITHMIC_BYTE and round(DRAM_BYTES_PER_ALGORITHMIC_BYTE * layer_bytes), "peak_source": peak_source,
+                         "kernel": "decode_int4_kernel (+ its merge)", "us_per_launch": round(kernel_ms * 1e3, 2),
+                         "algorithmic_bytes_per_launch": layer_bytes},
+            "e2e": {"value": round(e2e_bytes / (e2e_time_ms * 1e-3) / 1e9, 1), "unit": "GB/s",
+                    "h2d_bytes_per_step": h2d * args.layers, "d2h_bytes_per_step": d2h * args.layers,
+                    "ms_per_step": round(e2e_time_ms / args.steps, 4)},
+            "gpu_launches": launches,
+            "clocks": clocks,
+        }
+        try:
+            line["cpu_baseline"] = cpu_baseline(args, args.cpu_seconds) if world == 1 and args.cpu_seconds > 0 else None
+        except Exception as error:  # the CPU leg never hides the GPU numbers
+            line["cpu_baseline"] = {"error": str(error)}
+        print(json.dumps(line), flush=True)
+    session.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
