@@ -1,0 +1,171 @@
+/* richkv.h — C ABI of the B200 paged, quantized KV-cache path.
+ *
+ * Plain pointers and sizes only. Every device pointer argument is a CUDA device
+ * address; `stream` is a cudaStream_t passed as void*. Functions return 0 (RK_OK)
+ * or a negative status; rk_last_error() gives the text of the calling thread's
+ * last failure. Nothing here falls back to the CPU.
+ *
+ * Each entry point names the reference interface it replaces (paths relative to
+ * the reference project root). The reference binds four lanes per dispatch as
+ * four table buffers (runtime/ops/PagedAttention.cpp:479-500); here `tables` is a
+ * device array of table addresses and `lane_params` a device array of parameter
+ * blocks, so any batch width runs in one launch, and the layer placement that the
+ * reference writes into every lane's block (PagedAttention.cpp:482,487) travels
+ * as the `layer` argument: the lane array is uploaded once per step, not once per
+ * layer. A block's own `kv` field is used only where no `layer` is passed.
+ */
+#ifndef RICHKV_H
+#define RICHKV_H
+
+#include "richkv_abi.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RK_OK 0
+#define RK_ERR_INVALID (-1)     /* contract violation detected on the host; nothing was launched */
+#define RK_ERR_CUDA (-2)        /* a CUDA call failed */
+#define RK_ERR_UNSUPPORTED (-3) /* no kernel for this geometry or format */
+#define RK_ERR_REFUSED (-4)     /* capacity refusal: budget, driver out of memory, tier limits */
+#define RK_ERR_TIMEOUT (-5)     /* a bounded wait inside a kernel ran out */
+
+const char *rk_last_error(void);
+
+/* Layout::extentAlignmentPages (runtime/ops/PagedKv.hpp:175-183). */
+uint32_t rk_extent_alignment_pages(uint32_t format, uint32_t kv_heads, uint32_t head_dim);
+
+/* ---- append and quantize ------------------------------------------------------------------ */
+/* verify_attention_{q8,int4,bf16,fp8}_store (runtime/metal/kernels/decode/paged_attention_store.metal:3-186,
+ * decode/fp8_attention_store.metal:8-70), encoded by PagedAttention::addVerify (PagedAttention.cpp:467-503).
+ * chunk_keys [lane][kv_head][32][D], chunk_values [lane][kv_head][D][32] bf16; each lane stores
+ * lane_params[lane].chunk_tokens (<= 16, <= max_rows) rows at committed_tokens + row. */
+int rk_store_verify(uint32_t format, uint32_t kv_heads, uint32_t head_dim, uint32_t lanes, uint32_t max_rows,
+                    const void *chunk_keys, const void *chunk_values, const rk_page_entry *const *tables,
+                    const rk_chunk_params *lane_params, rk_kv_layer layer, void *stream);
+/* prefill_attention_*_store (runtime/metal/kernels/prefill/paged_attention_store.metal:7-149), encoded by
+ * PagedAttention::addPrefillStore (PagedAttention.cpp:424-441). `params` is a HOST pointer (the reference
+ * passes the block by value); its kv field places the layer. */
+int rk_store_chunk(uint32_t format, uint32_t kv_heads, uint32_t head_dim, const void *chunk_keys,
+                   const void *chunk_values, const rk_page_entry *table, const rk_chunk_params *params,
+                   void *stream);
+
+/* ---- general attention tile: any row count, tree masks, prefill chunks ----------------------- */
+/* verify_attention_*_split / verify_tree_attention_*_split (decode/paged_attention.metal:23-192,
+ * decode/fp8_attention.metal:8-62). grid_splits = the plan's split count (max over lanes);
+ * row_capacity is 1, 8 or 16 and strides the partial slots; row_masks (tree) may be null. */
+int rk_attention_verify_split(uint32_t format, uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim,
+                              uint32_t lanes, uint32_t row_capacity, uint32_t grid_splits, const void *queries,
+                              float *partials, float *statistics, const rk_page_entry *const *tables,
+                              const uint32_t *row_masks, const rk_verify_params *lane_params, rk_kv_layer layer,
+                              void *stream);
+/* verify_attention_reduce / verify_tree_attention_reduce (decode/paged_attention.metal:198-263,415-531).
+ * output bf16 [lane][kv_head][32][group][D]; output_f32 (optional) receives the value before rounding. */
+int rk_attention_verify_reduce(uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim, uint32_t lanes,
+                               uint32_t row_capacity, const float *partials, const float *statistics,
+                               void *output, float *output_f32, const rk_verify_params *lane_params,
+                               void *stream);
+/* prefill_attention_*_split and prefill_attention_reduce (prefill/paged_attention.metal:7-206), encoded by
+ * PagedAttention::addPrefill (PagedAttention.cpp:443-465). `params` is a HOST pointer. */
+int rk_attention_prefill_split(uint32_t format, uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim,
+                               const void *queries, float *partials, float *statistics,
+                               const rk_page_entry *table, const rk_prefill_params *params, void *stream);
+int rk_attention_prefill_reduce(uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim, const float *partials,
+                                const float *statistics, void *output, float *output_f32,
+                                const rk_prefill_params *params, void *stream);
+
+/* ---- streaming decode attention (one query row per lane) ---------------------------------------- */
+/* The reference has no single-query kernel: a plain decode is its tile with one active row
+ * (runtime/metal/kernels/common/paged_attention_tile.h:108-110; tested as history 0, rows 1 in
+ * dev/tests/engine/paged_attention_plan_test.mm:1019). This entry replaces split + reduce for
+ * active_rows = row_capacity = 1 with the TMA-streamed kernel; scratch is sized by the plan. */
+typedef struct rk_decode_plan {
+  uint32_t lanes, ctas, max_segments, reserved;
+  uint64_t partials_bytes, statistics_bytes, descriptor_bytes;
+} rk_decode_plan;
+int rk_decode_plan_make(uint32_t format, uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim,
+                        uint32_t lanes, uint32_t ctas, rk_decode_plan *plan);
+/* The device address window that holds every page of a pool (rk_storage_window): the TMA tensor map. */
+void *rk_window_create(uint64_t base, uint64_t bytes);
+void rk_window_destroy(void *window);
+int rk_attention_decode(const void *window, const rk_decode_plan *plan, uint32_t format, const void *queries,
+                        void *output, float *output_f32, float *partials, float *statistics,
+                        uint32_t *descriptors, const rk_page_entry *const *tables,
+                        const rk_verify_params *lane_params, rk_kv_layer layer, void *stream);
+/* Synchronises `stream` and reports RK_ERR_TIMEOUT if a bounded wait ran out in a launched step. */
+int rk_attention_decode_status(const rk_decode_plan *plan, const uint32_t *descriptors, void *stream);
+/* Compact host-style rows <-> the 32-row stagings (row 0): queries [lane][query_head][D],
+ * keys / values [lane][kv_head][D]. The reference's QKV projection writes the stagings on the GPU
+ * (runtime/metal/kernels/decode/attention_qkv.metal:6-60); these serve callers that hold host rows. */
+int rk_stage_decode_rows(uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim, uint32_t lanes, const void *q,
+                         const void *k, const void *v, void *queries, void *chunk_keys, void *chunk_values,
+                         void *stream);
+int rk_gather_decode_rows(uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim, uint32_t lanes,
+                          const void *output, void *out, void *stream);
+
+/* ---- page moves --------------------------------------------------------------------------------- */
+/* kv::ExtentStorage::copyPages (runtime/ops/PagedKv.hpp:70-75, PageStorage.mm:95-114) on table entries:
+ * every tensor of every layer of from_entries[i] onto to_entries[i]. Also the copy-on-write fork. */
+int rk_copy_pages(uint32_t format, uint32_t layers, uint32_t kv_heads, uint32_t head_dim, uint32_t extent_pages,
+                  const rk_page_entry *from_entries, const rk_page_entry *to_entries, uint32_t count,
+                  void *stream);
+/* A page's spans (PageStorage::spans, PageStorage.mm:143-167) packed into / unpacked from contiguous
+ * slots of layers * layer-page bytes each: the staging of the host tier. */
+int rk_pack_pages(uint32_t format, uint32_t layers, uint32_t kv_heads, uint32_t head_dim, uint32_t extent_pages,
+                  const rk_page_entry *from_entries, void *slots, uint32_t count, void *stream);
+int rk_unpack_pages(uint32_t format, uint32_t layers, uint32_t kv_heads, uint32_t head_dim, uint32_t extent_pages,
+                    const void *slots, const rk_page_entry *to_entries, uint32_t count, void *stream);
+/* verify_tree_attention_*_compact (decode/paged_attention_store.metal:198-310), encoded by
+ * PagedAttention::addVerifyTreeCompact (PagedAttention.cpp:547-573). retained_path [lane][8]. */
+int rk_tree_compact(uint32_t format, uint32_t kv_heads, uint32_t head_dim, uint32_t lanes,
+                    const rk_page_entry *const *tables, const rk_chunk_params *lane_params, rk_kv_layer layer,
+                    const uint32_t *retained_path, const uint32_t *retained_count, void *stream);
+
+/* ---- extent storage: kv::PageStorage (runtime/ops/PageStorage.hpp:27-102, PageStorage.mm) --------- */
+void *rk_storage_create(uint32_t format, uint32_t layers, uint32_t kv_heads, uint32_t head_dim,
+                        uint32_t page_count, uint32_t extent_pages);
+void rk_storage_destroy(void *storage);
+int rk_storage_allocate_extent(void *storage, uint32_t extent); /* 0 granted, RK_ERR_REFUSED, RK_ERR_INVALID */
+int rk_storage_release_extent(void *storage, uint32_t extent);
+void rk_storage_set_budget(void *storage, uint64_t bytes); /* the admission the reference injects (PageStorage.hpp:31) */
+uint32_t rk_storage_page_count(const void *storage);
+uint32_t rk_storage_extent_pages(const void *storage);
+uint64_t rk_storage_bytes_per_page(const void *storage);
+uint64_t rk_storage_extent_bytes(const void *storage);
+uint64_t rk_storage_allocated_bytes(const void *storage);
+int rk_storage_is_allocated(const void *storage, uint32_t page);
+void rk_storage_window(const void *storage, uint64_t *base, uint64_t *bytes);
+uint32_t rk_storage_layers(const void *storage, rk_kv_layer *out, uint32_t capacity);
+rk_page_entry rk_storage_entry(const void *storage, uint32_t page);
+int rk_storage_read_extent(const void *storage, uint32_t extent, uint64_t offset, void *host, uint64_t bytes);
+int rk_storage_write_extent(void *storage, uint32_t extent, uint64_t offset, const void *host, uint64_t bytes);
+/* PageStorage::writeEntries (PageStorage.mm:127-141) into a device table. */
+int rk_storage_write_entries(const void *storage, const uint32_t *pages, uint32_t count, uint32_t first,
+                             rk_page_entry *device_table, uint32_t table_capacity, void *stream);
+int rk_storage_copy_pages(void *storage, const rk_page_copy *copies, uint32_t count, void *stream);
+int rk_storage_pack_pages(void *storage, const uint32_t *pages, uint32_t count, void *device_slots, int unpack,
+                          void *stream);
+
+/* ---- pinned-host eviction tier: engine::KvTier (runtime/engine/cache/KvTier.hpp:34-63) with the
+ * transfer bounds of KvPageTier (runtime/engine/cache/KvPageTier.cpp:38-132) ------------------------ */
+void *rk_tier_create(void *storage, uint32_t slots, uint32_t transfer_limit);
+void rk_tier_destroy(void *tier);
+uint64_t rk_tier_slot_bytes(const void *tier);
+int rk_tier_writable(const void *tier);
+int rk_tier_can_demote(const void *tier);
+int rk_tier_can_restore(const void *tier);
+int64_t rk_tier_acquire_slot(void *tier); /* -1 when the quota is full */
+void rk_tier_release_slot(void *tier, uint32_t slot);
+void rk_tier_fail_next(void *tier, uint32_t count); /* host-side fault injection for tests */
+const void *rk_tier_slot_host_pointer(const void *tier, uint32_t slot);
+int rk_tier_demote(void *tier, uint32_t page, uint32_t slot, void *after_stream);  /* transfer id or status */
+int rk_tier_restore(void *tier, uint32_t slot, uint32_t page, void *after_stream); /* transfer id or status */
+int rk_tier_poll(void *tier);
+int rk_tier_transfer_ready(const void *tier, uint32_t id);
+int rk_tier_transfer_finish(void *tier, uint32_t id); /* 1 success, 0 failure */
+int rk_tier_drain(void *tier);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RICHKV_H */

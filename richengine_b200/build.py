@@ -28,6 +28,7 @@ NVCC_FLAGS = [
     # fused multiply-add contraction across the (x*range)/amax recipe
     "--prec-div=true", "--prec-sqrt=true", "--ftz=false", "--fmad=true",
     f"-I{ROOT / 'include'}",
+    *os.environ.get("RICHKV_NVCC_FLAGS", "").split(),
 ]
 
 

@@ -1,7 +1,7 @@
 // common.cuh — device helpers shared by the paged-KV kernels.
 #pragma once
 
-#include "../../include/richkv_abi.h"
+#include "../../include/richkv.h"
 
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>

@@ -42,17 +42,20 @@ int encode_window_map(CUtensorMap *map, uint64_t base, uint64_t rows, uint32_t b
 
 namespace {
 
-constexpr uint32_t kConsumerWarps = 8;
+constexpr uint32_t kKvHeads = 4, kGroup = 6, kHeadDim = 256;
+constexpr uint32_t kPageWarps = 3;                          // warps per KV head, each takes every third page
+constexpr uint32_t kConsumerWarps = kKvHeads * kPageWarps;
 constexpr uint32_t kThreads = (kConsumerWarps + 1) * 32;
-constexpr uint32_t kStages = 20;
-constexpr uint32_t kSlabBytes = 4096;               // one head's K (or V) of a page, int4
-constexpr uint32_t kStageBytes = 2 * kSlabBytes + 1024; // K | V | key scales | value scales | pad
-constexpr uint32_t kUnitBytes = 2 * kSlabBytes + 256;
+constexpr uint32_t kStages = 6;
+constexpr uint32_t kSlabBytes = 4096;                       // one head's K (or V) of a page, int4
+constexpr uint32_t kTensorBytes = kKvHeads * kSlabBytes;    // all heads' K (or V) of a page
+constexpr uint32_t kScaleBytes = kKvHeads * kPageTokens * 4;
+constexpr uint32_t kStageBytes = 2 * kTensorBytes + 2 * kScaleBytes; // K | V | key scales | value scales
 constexpr uint32_t kMaxLanes = 1024;
 constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
-constexpr uint32_t kKvHeads = 4, kGroup = 6, kHeadDim = 256;
+static_assert(kStageBytes % 1024 == 0, "stages keep the 1 KiB swizzle alignment");
 
 struct DecodeArgs {
   const uint16_t *queries;
@@ -114,6 +117,19 @@ __device__ __forceinline__ uint32_t sub_f16x2(uint32_t a, uint32_t b) {
   asm("sub.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
   return r;
 }
+// (a & mask) ^ flip in ONE logic instruction: both constants must sit in
+// registers (an immediate pair would split it in two half-rate ALU operations).
+__device__ __forceinline__ uint32_t and_xor(uint32_t a, uint32_t mask, uint32_t flip) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(r) : "r"(a), "r"(mask), "r"(flip));
+  return r;
+}
+// A constant the compiler must keep in a register.
+__device__ __forceinline__ uint32_t register_constant(uint32_t value) {
+  uint32_t r;
+  asm volatile("mov.b32 %0, %1;" : "=r"(r) : "r"(value));
+  return r;
+}
 __device__ __forceinline__ float exp2_fast(float x) {
   float r;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
@@ -148,10 +164,13 @@ __device__ __forceinline__ uint32_t cta_of(uint64_t x, uint64_t total, uint64_t 
 struct Shared {
   uint64_t full[kStages];
   uint64_t empty[kStages];
+  uint2 query[kKvHeads][16][32];        // per KV head: B fragments of Q^T for the 16 k-steps
+  float head_factor[kKvHeads][8];       // per query head of the group: score factor ...
+  float head_offset[kKvHeads][8];       // ... and the -8*sum(q) correction
   uint32_t lane_start[kMaxLanes + 1];   // pages before each lane
   uint32_t segment_base[kMaxLanes + 1]; // partial segments before each lane
   uint32_t scan[kThreads / 32 + 1];
-  uint32_t error;
+  volatile uint32_t error;
 };
 
 // Block-wide exclusive prefix sum of values[0..n) in place (values[n] = total).
@@ -179,6 +198,10 @@ __device__ void exclusive_scan(uint32_t *values, uint32_t n, uint32_t *scratch) 
   }
   if (tid == 0) values[n] = carry;
   __syncthreads();
+}
+
+__device__ __forceinline__ void group_barrier(uint32_t id, uint32_t threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -221,7 +244,7 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
   if (tid == 0) {
     for (uint32_t s = 0; s < kStages; ++s) {
       barrier_init(smem_address(&sh.full[s]), 1);
-      barrier_init(smem_address(&sh.empty[s]), 1);
+      barrier_init(smem_address(&sh.empty[s]), kKvHeads); // one warp per head releases a page
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -237,12 +260,14 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
     }
     first_lane = lo;
   }
-  const uint32_t data_bytes = kPageTokens * kKvHeads * kHeadDim / 2, scale_bytes = kPageTokens * kKvHeads * 4;
 
   if (warp == kConsumerWarps) {
-    // ================= producer ==========================================================
+    // ================= producer: one thread streams whole pages =============================
     if (lane != 0) return;
-    uint32_t unit = 0;
+#ifdef RK_EXP_COMPUTE_ONLY
+    return;
+#endif
+    uint32_t unit = 0; // pages issued by this CTA
     bool ok = true;
     for (uint32_t l = first_lane; ok && l < lanes && sh.lane_start[l] < range_end; ++l) {
       const uint32_t lane_begin = sh.lane_start[l], lane_end = sh.lane_start[l + 1];
@@ -250,29 +275,30 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
       const uint32_t pb = min(range_end, lane_end) - lane_begin;
       if (pb <= pa || lane_end <= range_begin) continue;
       const rk_page_entry *table = args.tables[l];
-      for (uint32_t page = pa; ok && page < pb; ++page) {
-        const rk_page_entry entry = table[page];
+      rk_page_entry next_entry = table[pa];
+      for (uint32_t page = pa; ok && page < pb; ++page, ++unit) {
+        const rk_page_entry entry = next_entry;
+        if (page + 1 < pb) next_entry = table[page + 1]; // in flight while this page's copies are issued
         const uint32_t index = rk_entry_index(entry);
         const uint64_t region = rk_entry_extent(entry) + args.layer.offset;
         const uint64_t pages = args.layer.extent_pages;
-        const uint64_t keys = region + uint64_t(index) * data_bytes;
-        const uint64_t key_scales = region + pages * data_bytes + uint64_t(index) * scale_bytes;
-        const uint64_t values = region + pages * (uint64_t(data_bytes) + scale_bytes) + uint64_t(index) * data_bytes;
-        const uint64_t value_scales = region + pages * (2ull * data_bytes + scale_bytes) + uint64_t(index) * scale_bytes;
-        for (uint32_t head = 0; head < kKvHeads; ++head, ++unit) {
-          const uint32_t slot = unit % kStages, round = unit / kStages;
-          const uint32_t full = smem_address(&sh.full[slot]), stage = ring + slot * kStageBytes;
-          if (!barrier_wait(smem_address(&sh.empty[slot]), (round & 1u) ^ 1u)) { ok = false; break; }
-          barrier_expect(full, kUnitBytes);
-          tma_load_rows(stage, &window_map, int32_t((keys + head * kSlabBytes - args.window_base) >> 7), full);
-          tma_load_rows(stage + kSlabBytes, &window_map, int32_t((values + head * kSlabBytes - args.window_base) >> 7), full);
-          bulk_load(stage + 2 * kSlabBytes, reinterpret_cast<const void *>(key_scales + head * 128), 128, full);
-          bulk_load(stage + 2 * kSlabBytes + 128, reinterpret_cast<const void *>(value_scales + head * 128), 128, full);
-        }
+        const uint64_t keys = region + uint64_t(index) * kTensorBytes;
+        const uint64_t key_scales = region + pages * kTensorBytes + uint64_t(index) * kScaleBytes;
+        const uint64_t values = region + pages * (uint64_t(kTensorBytes) + kScaleBytes) + uint64_t(index) * kTensorBytes;
+        const uint64_t value_scales = region + pages * (2ull * kTensorBytes + kScaleBytes) + uint64_t(index) * kScaleBytes;
+        const uint32_t slot = unit % kStages, round = unit / kStages;
+        const uint32_t full = smem_address(&sh.full[slot]), stage = ring + slot * kStageBytes;
+        if (sh.error || !barrier_wait(smem_address(&sh.empty[slot]), (round & 1u) ^ 1u)) { ok = false; break; }
+        barrier_expect(full, kStageBytes);
+        tma_load_rows(stage, &window_map, int32_t((keys - args.window_base) >> 7), full);
+        tma_load_rows(stage + kTensorBytes, &window_map, int32_t((values - args.window_base) >> 7), full);
+        bulk_load(stage + 2 * kTensorBytes, reinterpret_cast<const void *>(key_scales), kScaleBytes, full);
+        bulk_load(stage + 2 * kTensorBytes + kScaleBytes, reinterpret_cast<const void *>(value_scales), kScaleBytes, full);
       }
     }
     if (!ok) {
       atomicExch(error_word, 1u);
+      sh.error = 1;
       // Copies already issued must land before the block's shared memory goes.
       const uint32_t armed = min(unit, kStages);
       for (uint32_t back = 0; back < armed; ++back) {
@@ -283,12 +309,16 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
     return;
   }
 
-  // ================= consumers =============================================================
-  const uint32_t head = warp & 3u, parity = warp >> 2;
+  // ================= consumers: warp = (KV head, page residue) ===============================
+  const uint32_t head = warp & 3u, residue = warp >> 2;
   const uint32_t g = lane >> 2, c = lane & 3u;
   const uint32_t r3g = ((g & 1u) << 2) | (g >> 1); // row-in-8 swizzle partner: phase mates differ in bit 2
+  const uint32_t kLowNibbles = register_constant(0x000F000Fu), kHighNibbles = register_constant(0x00F000F0u);
+  const uint32_t kFlipLow = register_constant(0x00080008u), kFlipHigh = register_constant(0x00800080u);
+  const uint32_t kMagicLow = register_constant(0x64086408u), kMagicHigh = register_constant(0x64806480u);
+  const uint32_t query_shared = smem_address(&sh.query[head][0][lane]);
 
-  uint32_t units_before = 0; // units of this CTA in earlier segments
+  uint32_t units_before = 0; // pages of this CTA in earlier segments
   for (uint32_t l = first_lane; l < lanes && sh.lane_start[l] < range_end; ++l) {
     const uint32_t lane_begin = sh.lane_start[l], lane_end = sh.lane_start[l + 1];
     const uint32_t pa = max(range_begin, lane_begin) - lane_begin;
@@ -298,10 +328,9 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
     const uint32_t visible = p.committed_tokens + 1;
     const uint32_t lane_pages = lane_end - lane_begin;
 
-    // ---- this warp's query fragments: B operand of S^T = K.Q^T, head g of the group -----
-    uint32_t qf[16][2];
-    float hfac[2], negoff[2];
-    {
+    // ---- the head's query fragments (B operand of S^T = K.Q^T), shared by its three warps ----
+    group_barrier(1 + head, kPageWarps * 32); // every warp of the head is done with the previous lane
+    if (residue == 0) {
       const uint16_t *q = args.queries + ((uint64_t(l) * kKvHeads + head) * RK_VERIFY_CHUNK_STRIDE) * kGroup * kHeadDim +
                           uint64_t(g) * kHeadDim;
       float raw[2][4][8];
@@ -337,21 +366,25 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
             const float e0 = raw[j][w][2 * hs] * down, e1 = raw[j][w][2 * hs + 4] * down;
             const float o0 = raw[j][w][2 * hs + 1] * down * 0.0625f, o1 = raw[j][w][2 * hs + 5] * down * 0.0625f;
             const __half2 even = __floats2half2_rn(e0, e1), odd = __floats2half2_rn(o0, o1);
-            qf[s][0] = *reinterpret_cast<const uint32_t *>(&even);
-            qf[s][1] = *reinterpret_cast<const uint32_t *>(&odd);
+            sh.query[head][s][lane] = make_uint2(*reinterpret_cast<const uint32_t *>(&even),
+                                                 *reinterpret_cast<const uint32_t *>(&odd));
             qsum += __low2float(even) + __high2float(even) + 16.0f * (__low2float(odd) + __high2float(odd));
           }
       qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
       qsum += __shfl_xor_sync(0xffffffffu, qsum, 2);
-      // scores (log2 domain) = fma(acc, hfac, negoff) * key_scale
+      // scores (log2 domain) = fma(acc, factor, offset) * key_scale
       const float ss = rk_score_scale(p.score_scale, kHeadDim) * kLog2e;
-      const float my_hfac = ldexpf(ss, 24 + exponent);
-      const float my_negoff = -8.0f * qsum * ldexpf(ss, exponent);
-#pragma unroll
-      for (uint32_t j = 0; j < 2; ++j) { // C fragment columns are heads 2c, 2c+1
-        hfac[j] = __shfl_sync(0xffffffffu, my_hfac, 4 * (2 * c + j));
-        negoff[j] = __shfl_sync(0xffffffffu, my_negoff, 4 * (2 * c + j));
+      if (c == 0) {
+        sh.head_factor[head][g] = ldexpf(ss, 24 + exponent);
+        sh.head_offset[head][g] = -8.0f * qsum * ldexpf(ss, exponent);
       }
+    }
+    group_barrier(1 + head, kPageWarps * 32); // fragments visible to the head's warps
+    float hfac[2], negoff[2];
+#pragma unroll
+    for (uint32_t j = 0; j < 2; ++j) { // C fragment columns are query heads 2c, 2c+1 of the group
+      hfac[j] = sh.head_factor[head][2 * c + j];
+      negoff[j] = sh.head_offset[head][2 * c + j];
     }
 
     float m[2] = {-1.0e30f, -1.0e30f}, l_sum[2] = {0.0f, 0.0f};
@@ -359,17 +392,24 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
 #pragma unroll
     for (uint32_t t = 0; t < 16; ++t) { o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.0f; }
 
-    bool alive = true;
-    for (uint32_t page = pa + parity; alive && page < pb; page += 2) {
-      const uint32_t unit = units_before + (page - pa) * kKvHeads + head;
+    for (uint32_t page = pa + residue; page < pb && !sh.error; page += kPageWarps) {
+      const uint32_t unit = units_before + (page - pa);
       const uint32_t slot = unit % kStages, round = unit / kStages;
+#ifndef RK_EXP_COMPUTE_ONLY
       if (!barrier_wait(smem_address(&sh.full[slot]), round & 1u)) {
         atomicExch(error_word, 2u);
-        alive = false;
+        sh.error = 2;
         break;
       }
       const uint32_t stage = ring + slot * kStageBytes;
+#else
+      const uint32_t stage = ring + (warp % kStages) * kStageBytes;
+#endif
+      const uint32_t keys = stage + head * kSlabBytes;
+      const uint32_t values = stage + kTensorBytes + head * kSlabBytes;
+      const uint32_t scales = stage + 2 * kTensorBytes + head * (kPageTokens * 4);
       const uint32_t valid = page + 1 == lane_pages ? visible - page * kPageTokens : kPageTokens;
+#ifndef RK_EXP_STREAM_ONLY
 
       // ---- S^T = K.Q^T : two 16-token tiles, 16 k-steps each --------------------------
       float sacc[2][2][4];
@@ -378,22 +418,29 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
 #pragma unroll
         for (uint32_t h = 0; h < 2; ++h) sacc[mt][h][0] = sacc[mt][h][1] = sacc[mt][h][2] = sacc[mt][h][3] = 0.0f;
 #pragma unroll
-      for (uint32_t mt = 0; mt < 2; ++mt) {
-        const uint32_t row_a = 16 * mt + r3g, row_b = row_a + 8;
+      for (uint32_t j = 0; j < 2; ++j) {
+        const uint32_t chunk = ((c + 4 * j) ^ r3g) * 16;
+        uint4 kr[2][2];
 #pragma unroll
-        for (uint32_t j = 0; j < 2; ++j) {
-          const uint32_t chunk = ((c + 4 * j) ^ r3g) * 16;
-          const uint4 ka = load_shared_16(stage + row_a * 128 + chunk);
-          const uint4 kb = load_shared_16(stage + row_b * 128 + chunk);
-          const uint32_t xa[4] = {ka.x, ka.y, ka.z, ka.w}, xb[4] = {kb.x, kb.y, kb.z, kb.w};
+        for (uint32_t mt = 0; mt < 2; ++mt) {
+          kr[mt][0] = load_shared_16(keys + (16 * mt + r3g) * 128 + chunk);
+          kr[mt][1] = load_shared_16(keys + (16 * mt + 8 + r3g) * 128 + chunk);
+        }
 #pragma unroll
-          for (uint32_t w = 0; w < 4; ++w) {
-            const uint32_t s = (j * 4 + w) * 2;
-            const uint32_t ya = xa[w] >> 8, yb = xb[w] >> 8;
-            mma_f16(sacc[mt][0], (xa[w] & 0x000F000Fu) ^ 0x00080008u, (xb[w] & 0x000F000Fu) ^ 0x00080008u,
-                    (xa[w] & 0x00F000F0u) ^ 0x00800080u, (xb[w] & 0x00F000F0u) ^ 0x00800080u, qf[s][0], qf[s][1]);
-            mma_f16(sacc[mt][1], (ya & 0x000F000Fu) ^ 0x00080008u, (yb & 0x000F000Fu) ^ 0x00080008u,
-                    (ya & 0x00F000F0u) ^ 0x00800080u, (yb & 0x00F000F0u) ^ 0x00800080u, qf[s + 1][0], qf[s + 1][1]);
+        for (uint32_t w = 0; w < 4; ++w) {
+          const uint32_t s = (j * 4 + w) * 2;
+          uint2 q0, q1;
+          asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(q0.x), "=r"(q0.y) : "r"(query_shared + s * 256));
+          asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(q1.x), "=r"(q1.y) : "r"(query_shared + (s + 1) * 256));
+#pragma unroll
+          for (uint32_t mt = 0; mt < 2; ++mt) {
+            const uint32_t xa = w == 0 ? kr[mt][0].x : w == 1 ? kr[mt][0].y : w == 2 ? kr[mt][0].z : kr[mt][0].w;
+            const uint32_t xb = w == 0 ? kr[mt][1].x : w == 1 ? kr[mt][1].y : w == 2 ? kr[mt][1].z : kr[mt][1].w;
+            const uint32_t ya = xa >> 8, yb = xb >> 8;
+            mma_f16(sacc[mt][0], and_xor(xa, kLowNibbles, kFlipLow), and_xor(xb, kLowNibbles, kFlipLow),
+                    and_xor(xa, kHighNibbles, kFlipHigh), and_xor(xb, kHighNibbles, kFlipHigh), q0.x, q0.y);
+            mma_f16(sacc[mt][1], and_xor(ya, kLowNibbles, kFlipLow), and_xor(yb, kLowNibbles, kFlipLow),
+                    and_xor(ya, kHighNibbles, kFlipHigh), and_xor(yb, kHighNibbles, kFlipHigh), q1.x, q1.y);
           }
         }
       }
@@ -406,8 +453,8 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
 #pragma unroll
         for (uint32_t half = 0; half < 2; ++half) {
           const uint32_t token = 16 * mt + 8 * half + r3g;
-          const float ks = load_shared_f32(stage + 2 * kSlabBytes + token * 4);
-          const float vs = load_shared_f32(stage + 2 * kSlabBytes + 128 + token * 4);
+          const float ks = load_shared_f32(scales + token * 4);
+          const float vs = load_shared_f32(scales + kScaleBytes + token * 4);
           const bool live = token < valid;
           lv[mt][half] = live ? log2_fast(vs) : -INFINITY;
           const float floor_lv = live ? fmaxf(lv[mt][half], -40.0f) : -INFINITY;
@@ -453,7 +500,6 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
       }
 
       // ---- O^T += V^T.P^T : 16 tiles of 16 dims, 2 k-steps of 16 tokens -----------------
-      const uint32_t values = stage + kSlabBytes;
 #pragma unroll
       for (uint32_t s = 0; s < 2; ++s) {
         const uint32_t ta = 16 * s + c;
@@ -471,18 +517,19 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
             const uint32_t selector = b | (b << 4) | ((4 + b) << 8) | ((4 + b) << 12);
             const uint32_t ab = __byte_perm(xa[w], xb[w], selector), cd = __byte_perm(xc[w], xd[w], selector);
             // low nibble: 1024 + (n ^ 8), minus 1032 = code; high nibble: 1024 + 16 (n ^ 8), minus 1152 = 16 code
-            mma_f16(o[4 * w + b], sub_f16x2((ab & 0x000F000Fu) ^ 0x64086408u, 0x64086408u),
-                    sub_f16x2((ab & 0x00F000F0u) ^ 0x64806480u, 0x64806480u),
-                    sub_f16x2((cd & 0x000F000Fu) ^ 0x64086408u, 0x64086408u),
-                    sub_f16x2((cd & 0x00F000F0u) ^ 0x64806480u, 0x64806480u), pb_frag[s][0], pb_frag[s][1]);
+            mma_f16(o[4 * w + b], sub_f16x2(and_xor(ab, kLowNibbles, kMagicLow), kMagicLow),
+                    sub_f16x2(and_xor(ab, kHighNibbles, kMagicHigh), kMagicHigh),
+                    sub_f16x2(and_xor(cd, kLowNibbles, kMagicLow), kMagicLow),
+                    sub_f16x2(and_xor(cd, kHighNibbles, kMagicHigh), kMagicHigh), pb_frag[s][0], pb_frag[s][1]);
           }
       }
+#endif
       __syncwarp();
       if (lane == 0) barrier_arrive(smem_address(&sh.empty[slot]));
     }
-    units_before += (pb - pa) * kKvHeads;
+    units_before += pb - pa;
 
-    // ---- flush this warp's partial of (lane l, head, warp parity) --------------------------
+    // ---- flush this warp's partial of (lane l, head, page residue) --------------------------
     {
 #pragma unroll
       for (uint32_t j = 0; j < 2; ++j) {
@@ -491,10 +538,11 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
         l_sum[j] += __shfl_xor_sync(0xffffffffu, l_sum[j], 16);
       }
       const uint32_t segment = sh.segment_base[l] + (cta - cta_of(lane_begin, total_pages, ctas));
-      const uint64_t slot_index = (uint64_t(segment) * kKvHeads + head) * 2 + parity;
+      const uint64_t slot_index = (uint64_t(segment) * kKvHeads + head) * kPageWarps + residue;
       float *out = args.partials + slot_index * kGroup * kHeadDim;
       float *stats = args.statistics + slot_index * kGroup * 2;
       const float unscale = 6.103515625e-05f; // 2^-14
+      const bool failed = sh.error != 0;
 #pragma unroll
       for (uint32_t j = 0; j < 2; ++j) {
         const uint32_t query_head = 2 * c + j;
@@ -506,12 +554,11 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
               make_float2(o[t][j] * unscale, o[t][2 + j] * (unscale * 0.0625f));
         }
         if (g == 0) {
-          stats[query_head * 2] = alive ? m[j] * kLn2 : -INFINITY;
-          stats[query_head * 2 + 1] = alive ? l_sum[j] : 0.0f;
+          stats[query_head * 2] = failed ? -INFINITY : m[j] * kLn2;
+          stats[query_head * 2 + 1] = failed ? 0.0f : l_sum[j];
         }
       }
     }
-    if (!alive) return;
   }
 }
 
@@ -531,12 +578,12 @@ decode_reduce_kernel(const float *__restrict__ partials, const float *__restrict
   for (uint32_t query_head = 0; query_head < kGroup; ++query_head) {
     float maximum = -INFINITY;
     for (uint32_t s = 0; s < segments; ++s)
-      for (uint32_t w = 0; w < 2; ++w)
-        maximum = fmaxf(maximum, statistics[(((uint64_t(first + s) * kKvHeads + head) * 2 + w) * kGroup + query_head) * 2]);
+      for (uint32_t w = 0; w < kPageWarps; ++w)
+        maximum = fmaxf(maximum, statistics[(((uint64_t(first + s) * kKvHeads + head) * kPageWarps + w) * kGroup + query_head) * 2]);
     float numerator = 0.0f, denominator = 0.0f;
     for (uint32_t s = 0; s < segments; ++s)
-      for (uint32_t w = 0; w < 2; ++w) { // fixed order: segment, then warp
-        const uint64_t slot = (uint64_t(first + s) * kKvHeads + head) * 2 + w;
+      for (uint32_t w = 0; w < kPageWarps; ++w) { // fixed order: segment, then warp
+        const uint64_t slot = (uint64_t(first + s) * kKvHeads + head) * kPageWarps + w;
         const float mx = statistics[(slot * kGroup + query_head) * 2];
         const float weight = mx == -INFINITY ? 0.0f : expf(mx - maximum);
         numerator += weight * partials[(slot * kGroup + query_head) * kHeadDim + tid];
@@ -560,11 +607,6 @@ using namespace rk;
 
 extern "C" {
 
-typedef struct rk_decode_plan {
-  uint32_t lanes, ctas, max_segments, reserved;
-  uint64_t partials_bytes, statistics_bytes, descriptor_bytes;
-} rk_decode_plan;
-
 // Sizes the scratch of a decode step: `ctas` = 0 takes one CTA per SM of the current device.
 int rk_decode_plan_make(uint32_t format, uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim,
                         uint32_t lanes, uint32_t ctas, rk_decode_plan *plan) {
@@ -583,7 +625,7 @@ int rk_decode_plan_make(uint32_t format, uint32_t kv_heads, uint32_t query_heads
   plan->ctas = ctas;
   plan->max_segments = lanes + ctas;
   plan->reserved = 0;
-  const uint64_t slots = uint64_t(plan->max_segments) * kKvHeads * 2;
+  const uint64_t slots = uint64_t(plan->max_segments) * kKvHeads * kPageWarps;
   plan->partials_bytes = slots * kGroup * kHeadDim * sizeof(float);
   plan->statistics_bytes = slots * kGroup * 2 * sizeof(float);
   plan->descriptor_bytes = (2ull * lanes + 4) * sizeof(uint32_t);

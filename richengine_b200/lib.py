@@ -6,9 +6,11 @@ not run on a silent CPU path. Build it with `python -m richengine_b200.build`.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
-LIBRARY_PATH = Path(__file__).resolve().parent / "librichkv.so"
+# RICHKV_LIBRARY names another build of the same library (e.g. a profiling build).
+LIBRARY_PATH = Path(os.environ.get("RICHKV_LIBRARY") or Path(__file__).resolve().parent / "librichkv.so")
 
 OK, INVALID, CUDA_ERROR, UNSUPPORTED, REFUSED, TIMEOUT = 0, -1, -2, -3, -4, -5
 
