@@ -303,6 +303,8 @@ def run_ours(args):
     # ---- device-resident timing: `value` -------------------------------------------------------
     for step in range(args.warmup):
         device_step(step)
+        if step == 0:
+            session.attention.status()  # a device-side timeout stops the run here, not after every launch
     barrier()
     sampler = ClockSampler(local) if rank == 0 else None
     launches_before = session.kernel_launches

@@ -52,7 +52,7 @@ constexpr uint32_t kTensorBytes = kKvHeads * kSlabBytes;    // all heads' K (or 
 constexpr uint32_t kScaleBytes = kKvHeads * kPageTokens * 4;
 constexpr uint32_t kStageBytes = 2 * kTensorBytes + 2 * kScaleBytes; // K | V | key scales | value scales
 constexpr uint32_t kMaxLanes = 1024;
-constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr uint32_t kSpinLimit = 1u << 20; // polls of ~100 ns: a wait gives up after roughly 0.1-0.2 s
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 static_assert(kStageBytes % 1024 == 0, "stages keep the 1 KiB swizzle alignment");
@@ -641,7 +641,7 @@ void *rk_window_create(uint64_t base, uint64_t bytes) {
   auto *w = new Window;
   w->base = base;
   w->bytes = bytes;
-  if (encode_window_map(&w->int4_map, base, bytes >> 7, 32)) { delete w; return nullptr; }
+  if (encode_window_map(&w->int4_map, base, bytes >> 7, kTensorBytes / 128)) { delete w; return nullptr; } // one copy = all heads of a page
   return w;
 }
 void rk_window_destroy(void *window) { delete static_cast<Window *>(window); }
