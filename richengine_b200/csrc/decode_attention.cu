@@ -595,6 +595,21 @@ decode_reduce_kernel(const float *__restrict__ partials, const float *__restrict
   }
 }
 
+constexpr size_t kDecodeSharedBytes = 1024 + kStages * kStageBytes + sizeof(Shared);
+
+// The kernel's dynamic shared-memory limit is a per-device function attribute.
+int configure_decode_kernel() {
+  static bool configured[64] = {};
+  int device = 0;
+  if (int st = cuda_status(cudaGetDevice(&device), "cudaGetDevice")) return st;
+  if (device < 0 || device >= 64) { set_error("device index out of range"); return kInvalid; }
+  if (!configured[device]) {
+    if (int st = cuda_status(cudaFuncSetAttribute(decode_int4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kDecodeSharedBytes)), "decode shared memory")) return st;
+    configured[device] = true;
+  }
+  return kOk;
+}
+
 struct Window {
   uint64_t base = 0, bytes = 0;
   CUtensorMap int4_map;
@@ -657,12 +672,8 @@ int rk_attention_decode(const void *window, const rk_decode_plan *plan, uint32_t
     return kInvalid;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  constexpr size_t shared_bytes = 1024 + kStages * kStageBytes + sizeof(Shared);
-  static bool configured = false;
-  if (!configured) {
-    if (int st = cuda_status(cudaFuncSetAttribute(decode_int4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(shared_bytes)), "decode shared memory")) return st;
-    configured = true;
-  }
+  constexpr size_t shared_bytes = kDecodeSharedBytes;
+  if (int st = configure_decode_kernel()) return st;
   DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, plan->lanes};
   if (int st = cuda_status(cudaMemsetAsync(descriptors + 2 * plan->lanes, 0, sizeof(uint32_t), s), "decode status clear")) return st;
   decode_int4_kernel<<<plan->ctas, kThreads, shared_bytes, s>>>(w->int4_map, args);
