@@ -92,6 +92,15 @@ int rk_attention_decode(const void *window, const rk_decode_plan *plan, uint32_t
                         void *output, float *output_f32, float *partials, float *statistics,
                         uint32_t *descriptors, const rk_page_entry *const *tables,
                         const rk_verify_params *lane_params, rk_kv_layer layer, void *stream);
+/* No counterpart in the reference. rk_attention_decode for callers that cannot allocate device
+ * memory (the pool owns the whole device, the calling thread may not enter the allocator, or
+ * allocation calls are not permitted where it runs): the step's scratch is a fixed array inside
+ * the library, about 12 MiB per GPU that loads it, which limits a call to 16 lanes; more are
+ * refused with RK_ERR_INVALID. The first call on a device resolves the array's address and should
+ * come before any stream capture. Calls share the array: calls that overlap on the GPU race. */
+int rk_attention_decode_static(const void *window, uint32_t format, uint32_t lanes, const void *queries,
+                               void *output, float *output_f32, const rk_page_entry *const *tables,
+                               const rk_verify_params *lane_params, rk_kv_layer layer, void *stream);
 /* Synchronises `stream` and reports RK_ERR_TIMEOUT if a bounded wait ran out in a launched step. */
 int rk_attention_decode_status(const rk_decode_plan *plan, const uint32_t *descriptors, void *stream);
 /* Compact host-style rows <-> the 32-row stagings (row 0): queries [lane][query_head][D],

@@ -682,6 +682,65 @@ int rk_attention_decode(const void *window, const rk_decode_plan *plan, uint32_t
   return cuda_status(cudaGetLastError(), "decode reduce launch");
 }
 
+// ---- decode attention without any allocation -----------------------------------------------------
+// Scratch of the no-allocation entry point: partial outputs, their statistics and the lane
+// descriptors of one step of at most kStaticLanes lanes on a kStaticCtas-wide grid. The array is
+// part of the library image, so every GPU that loads the library holds these bytes until exit.
+constexpr uint32_t kStaticLanes = 16, kStaticCtas = 148;
+constexpr size_t kStaticSlots = size_t(kStaticLanes + kStaticCtas) * kKvHeads * kPageWarps;
+constexpr size_t kStaticPartialBytes = kStaticSlots * kGroup * kHeadDim * sizeof(float);
+constexpr size_t kStaticStatisticBytes = (kStaticSlots * kGroup * 2 * sizeof(float) + 255) / 256 * 256;
+constexpr size_t kStaticDescriptorBytes = ((2 * kStaticLanes + 4) * sizeof(uint32_t) + 255) / 256 * 256;
+static __device__ __align__(256) unsigned char g_decode_scratch[kStaticPartialBytes + kStaticStatisticBytes + kStaticDescriptorBytes];
+
+// rk_attention_decode for callers that must not allocate device memory: an engine that gave the
+// whole device to its KV pool and has no allocator left to ask, a serving thread that may not
+// enter cudaMalloc because it can stall on a device-wide lock, a caller inside a region where
+// allocation calls are simply not permitted. The caller still passes queries, tables, lane
+// parameters and the output; the step's scratch lives in g_decode_scratch (about 12 MiB) and
+// that caps the step at kStaticLanes (16) lanes — more lanes are refused with an error text.
+//
+// The first call on a device looks the array's device address up (cudaGetSymbolAddress, with that
+// device current) and sets the kernel's shared-memory attribute; make that first call before any
+// stream capture begins. No call allocates or frees anything, on the device or through a library.
+// Every call on a device uses the same array: the status word is cleared on the stream at the
+// start of each call, every partial the merge reads is rewritten by the same call, and two calls
+// that overlap on the GPU (different streams, no ordering between them) race on it.
+int rk_attention_decode_static(const void *window, uint32_t format, uint32_t lanes, const void *queries, void *output,
+                               float *output_f32, const rk_page_entry *const *tables,
+                               const rk_verify_params *lane_params, rk_kv_layer layer, void *stream) {
+  const auto *w = static_cast<const Window *>(window);
+  if (!w || !queries || !output || !tables || !lane_params || !layer.extent_pages || format != RK_FORMAT_INT4 || !lanes) {
+    set_error("rk_attention_decode_static: invalid arguments");
+    return kInvalid;
+  }
+  if (lanes > kStaticLanes) {
+    set_error("rk_attention_decode_static: at most 16 lanes fit the built-in scratch; use rk_attention_decode with caller scratch");
+    return kInvalid;
+  }
+  static unsigned char *scratch_address[64] = {};
+  int device = 0;
+  if (int st = cuda_status(cudaGetDevice(&device), "cudaGetDevice")) return st;
+  if (device < 0 || device >= 64) { set_error("device index out of range"); return kInvalid; }
+  if (!scratch_address[device]) { // once per device, with that device current
+    void *address = nullptr;
+    if (int st = cuda_status(cudaGetSymbolAddress(&address, g_decode_scratch), "cudaGetSymbolAddress(decode scratch)")) return st;
+    if (int st = cuda_status(cudaFuncSetAttribute(decode_int4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kDecodeSharedBytes)), "decode shared memory")) return st;
+    scratch_address[device] = static_cast<unsigned char *>(address);
+  }
+  unsigned char *base = scratch_address[device];
+  float *partials = reinterpret_cast<float *>(base);
+  float *statistics = reinterpret_cast<float *>(base + kStaticPartialBytes);
+  uint32_t *descriptors = reinterpret_cast<uint32_t *>(base + kStaticPartialBytes + kStaticStatisticBytes);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, lanes};
+  if (int st = cuda_status(cudaMemsetAsync(descriptors + 2 * lanes, 0, sizeof(uint32_t), s), "decode status clear")) return st;
+  decode_int4_kernel<<<kStaticCtas, kThreads, kDecodeSharedBytes, s>>>(w->int4_map, args);
+  if (int st = cuda_status(cudaGetLastError(), "decode launch")) return st;
+  decode_reduce_kernel<<<dim3(kKvHeads, lanes), 256, 0, s>>>(partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer);
+  return cuda_status(cudaGetLastError(), "decode reduce launch");
+}
+
 // Reads the step's device status word (synchronises the stream): 0, or kTimeout
 // when a bounded wait inside the kernel ran out.
 int rk_attention_decode_status(const rk_decode_plan *plan, const uint32_t *descriptors, void *stream) {
