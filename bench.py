@@ -39,7 +39,7 @@ KV_HEADS, QUERY_HEADS, HEAD_DIM = 4, 24, 256
 METRIC = "int4_paged_decode_attention_kv_gbps"
 # dram__bytes_read.sum + dram__bytes_write.sum of the decode kernel per algorithmic KV byte, from the ncu
 # capture summarised under profiles/ (a smaller case of the same kernel; traffic grows with the pages read).
-DRAM_BYTES_PER_ALGORITHMIC_BYTE = None
+DRAM_BYTES_PER_ALGORITHMIC_BYTE = 1.024
 
 
 def parse():

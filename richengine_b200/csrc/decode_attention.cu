@@ -200,6 +200,66 @@ __device__ void exclusive_scan(uint32_t *values, uint32_t n, uint32_t *scratch) 
   __syncthreads();
 }
 
+// Online softmax of one page for this lane's 4 tokens x 2 query heads, and the fp16 probability
+// fragments (B operand of O^T += V^T.P^T). Masked = the page holds tokens past the visible ones.
+template <bool Masked>
+__device__ __forceinline__ void page_softmax(const float (&sacc)[2][2][4], const float (&hfac)[2],
+                                             const float (&negoff)[2], uint32_t scales, uint32_t r3g,
+                                             uint32_t valid, float (&m)[2], float (&l_sum)[2], float (&o)[16][4],
+                                             uint32_t (&pb_frag)[2][2]) {
+  float s2[2][2][2], lv[2][2];
+  float local_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (uint32_t mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (uint32_t half = 0; half < 2; ++half) {
+      const uint32_t token = 16 * mt + 8 * half + r3g;
+      const float ks = load_shared_f32(scales + token * 4);
+      const float vs = load_shared_f32(scales + kScaleBytes + token * 4);
+      const bool live = !Masked || token < valid;
+      lv[mt][half] = live ? log2_fast(vs) : -INFINITY; // a zero value row weighs nothing
+      const float floor_lv = live ? fmaxf(lv[mt][half], -40.0f) : -INFINITY;
+#pragma unroll
+      for (uint32_t j = 0; j < 2; ++j) {
+        const float acc = sacc[mt][0][half * 2 + j] + sacc[mt][1][half * 2 + j];
+        const float score = live ? fmaf(acc, hfac[j], negoff[j]) * ks : -INFINITY;
+        s2[mt][half][j] = score;
+        local_max[j] = fmaxf(local_max[j], score + floor_lv);
+      }
+    }
+  if (__any_sync(0xffffffffu, local_max[0] > m[0] || local_max[1] > m[1])) {
+#pragma unroll
+    for (uint32_t j = 0; j < 2; ++j) {
+      float v = local_max[j];
+      v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+      v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+      v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+      const float next = fmaxf(m[j], v);
+      const float scale = exp2_fast(m[j] - next);
+      m[j] = next;
+      l_sum[j] *= scale;
+#pragma unroll
+      for (uint32_t t = 0; t < 16; ++t) { o[t][j] *= scale; o[t][2 + j] *= scale; }
+    }
+  }
+#pragma unroll
+  for (uint32_t mt = 0; mt < 2; ++mt) {
+    float w[2][2];
+#pragma unroll
+    for (uint32_t half = 0; half < 2; ++half)
+#pragma unroll
+      for (uint32_t j = 0; j < 2; ++j) {
+        const float score = s2[mt][half][j];
+        const bool live = !Masked || score != -INFINITY;
+        // probabilities carry 2^14 so the smallest weights keep fp16 precision
+        w[half][j] = live ? exp2_fast(score + lv[mt][half] - m[j] + 14.0f) : 0.0f;
+        l_sum[j] += live ? exp2_fast(score - m[j]) : 0.0f;
+      }
+    pb_frag[mt][0] = transpose_8x8(pack_half2(w[0][0], w[0][1]));
+    pb_frag[mt][1] = transpose_8x8(pack_half2(w[1][0], w[1][1]));
+  }
+}
+
 __device__ __forceinline__ void group_barrier(uint32_t id, uint32_t threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -446,58 +506,11 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
       }
 
       // ---- online softmax over the page's 32 tokens -------------------------------------
-      float s2[2][2][2], lv[2][2];
-      float local_max[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-      for (uint32_t mt = 0; mt < 2; ++mt)
-#pragma unroll
-        for (uint32_t half = 0; half < 2; ++half) {
-          const uint32_t token = 16 * mt + 8 * half + r3g;
-          const float ks = load_shared_f32(scales + token * 4);
-          const float vs = load_shared_f32(scales + kScaleBytes + token * 4);
-          const bool live = token < valid;
-          lv[mt][half] = live ? log2_fast(vs) : -INFINITY;
-          const float floor_lv = live ? fmaxf(lv[mt][half], -40.0f) : -INFINITY;
-#pragma unroll
-          for (uint32_t j = 0; j < 2; ++j) {
-            const float acc = sacc[mt][0][half * 2 + j] + sacc[mt][1][half * 2 + j];
-            const float score = live ? fmaf(acc, hfac[j], negoff[j]) * ks : -INFINITY;
-            s2[mt][half][j] = score;
-            local_max[j] = fmaxf(local_max[j], score + floor_lv);
-          }
-        }
-      if (__any_sync(0xffffffffu, local_max[0] > m[0] || local_max[1] > m[1])) {
-#pragma unroll
-        for (uint32_t j = 0; j < 2; ++j) {
-          float v = local_max[j];
-          v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
-          v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
-          v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
-          const float next = fmaxf(m[j], v);
-          const float scale = exp2_fast(m[j] - next);
-          m[j] = next;
-          l_sum[j] *= scale;
-#pragma unroll
-          for (uint32_t t = 0; t < 16; ++t) { o[t][j] *= scale; o[t][2 + j] *= scale; }
-        }
-      }
       uint32_t pb_frag[2][2];
-#pragma unroll
-      for (uint32_t mt = 0; mt < 2; ++mt) {
-        float w[2][2];
-#pragma unroll
-        for (uint32_t half = 0; half < 2; ++half)
-#pragma unroll
-          for (uint32_t j = 0; j < 2; ++j) {
-            const float score = s2[mt][half][j];
-            const bool live = score != -INFINITY;
-            // probabilities carry 2^14 so the smallest weights keep fp16 precision
-            w[half][j] = live ? exp2_fast(score + lv[mt][half] - m[j] + 14.0f) : 0.0f;
-            l_sum[j] += live ? exp2_fast(score - m[j]) : 0.0f;
-          }
-        pb_frag[mt][0] = transpose_8x8(pack_half2(w[0][0], w[0][1]));
-        pb_frag[mt][1] = transpose_8x8(pack_half2(w[1][0], w[1][1]));
-      }
+      if (valid == kPageTokens)
+        page_softmax<false>(sacc, hfac, negoff, scales, r3g, valid, m, l_sum, o, pb_frag);
+      else
+        page_softmax<true>(sacc, hfac, negoff, scales, r3g, valid, m, l_sum, o, pb_frag);
 
       // ---- O^T += V^T.P^T : 16 tiles of 16 dims, 2 k-steps of 16 tokens -----------------
 #pragma unroll
@@ -562,37 +575,55 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
   }
 }
 
-// Merge a lane's partials in slot order and store bf16 (and optionally fp32).
-// grid (kv_heads, lanes), 256 threads = one per dimension.
+// Merge one query head's partials in slot order (segment, then warp) and store bf16 (and
+// optionally fp32). grid (group, kv_heads, lanes), 256 threads = one per dimension.
 __global__ void __launch_bounds__(256)
 decode_reduce_kernel(const float *__restrict__ partials, const float *__restrict__ statistics,
                      const uint32_t *__restrict__ descriptors, uint16_t *__restrict__ output,
                      float *__restrict__ output_f32, const rk_verify_params *__restrict__ lane_params,
                      rk_kv_layer layer) {
-  const uint32_t head = blockIdx.x, l = blockIdx.y, tid = threadIdx.x;
+  constexpr uint32_t kMaxSlots = 64;
+  __shared__ float weights[kMaxSlots];
+  __shared__ float denominator_shared;
+  const uint32_t query_head = blockIdx.x, head = blockIdx.y, l = blockIdx.z, tid = threadIdx.x;
   rk_verify_params p = lane_params[l];
   p.kv = layer;
   if (!rk_verify_contract_valid(&p) || p.active_rows != 1 || p.row_capacity != 1) return;
   const uint32_t first = descriptors[2 * l], segments = descriptors[2 * l + 1];
+  const uint32_t slots = segments * kPageWarps;
   const uint64_t tile = ((uint64_t(l) * kKvHeads + head) * RK_VERIFY_CHUNK_STRIDE) * kGroup * kHeadDim;
-  for (uint32_t query_head = 0; query_head < kGroup; ++query_head) {
-    float maximum = -INFINITY;
-    for (uint32_t s = 0; s < segments; ++s)
-      for (uint32_t w = 0; w < kPageWarps; ++w)
-        maximum = fmaxf(maximum, statistics[(((uint64_t(first + s) * kKvHeads + head) * kPageWarps + w) * kGroup + query_head) * 2]);
-    float numerator = 0.0f, denominator = 0.0f;
-    for (uint32_t s = 0; s < segments; ++s)
-      for (uint32_t w = 0; w < kPageWarps; ++w) { // fixed order: segment, then warp
-        const uint64_t slot = (uint64_t(first + s) * kKvHeads + head) * kPageWarps + w;
-        const float mx = statistics[(slot * kGroup + query_head) * 2];
-        const float weight = mx == -INFINITY ? 0.0f : expf(mx - maximum);
-        numerator += weight * partials[(slot * kGroup + query_head) * kHeadDim + tid];
-        denominator += weight * statistics[(slot * kGroup + query_head) * 2 + 1];
+  // slot s of this (lane, head): segment s / 3, warp s % 3
+  auto slot_of = [&](uint32_t s) { return (uint64_t(first + s / kPageWarps) * kKvHeads + head) * kPageWarps + s % kPageWarps; };
+  float numerator = 0.0f;
+  for (uint32_t base = 0; base < slots; base += kMaxSlots) { // one pass unless a lane spans > 21 ranges
+    const uint32_t count = min(kMaxSlots, slots - base);
+    if (tid < 32) {
+      // the maximum is over ALL slots, so every pass weighs against the same reference
+      float maximum = -INFINITY;
+      for (uint32_t t = tid; t < slots; t += 32)
+        maximum = fmaxf(maximum, statistics[(slot_of(t) * kGroup + query_head) * 2]);
+      maximum = warp_max(maximum);
+      for (uint32_t t = tid; t < count; t += 32) {
+        const float own = statistics[(slot_of(base + t) * kGroup + query_head) * 2];
+        weights[t] = own == -INFINITY ? 0.0f : expf(own - maximum);
       }
-    const float value = denominator > 0.0f ? numerator / denominator : 0.0f;
-    output[tile + query_head * kHeadDim + tid] = float_to_bf16_bits(value);
-    if (output_f32) output_f32[tile + query_head * kHeadDim + tid] = value;
+      __syncwarp();
+      if (tid == 0) { // the denominator accumulates in slot order
+        float denominator = base ? denominator_shared : 0.0f;
+        for (uint32_t t = 0; t < count; ++t)
+          denominator += weights[t] * statistics[(slot_of(base + t) * kGroup + query_head) * 2 + 1];
+        denominator_shared = denominator;
+      }
+    }
+    __syncthreads();
+    for (uint32_t s = 0; s < count; ++s) // slot order; loads are independent of one another
+      numerator += weights[s] * partials[(slot_of(base + s) * kGroup + query_head) * kHeadDim + tid];
+    __syncthreads();
   }
+  const float denominator = denominator_shared;
+  const float value = denominator > 0.0f ? numerator / denominator : 0.0f;
+  output[tile + query_head * kHeadDim + tid] = float_to_bf16_bits(value);
+  if (output_f32) output_f32[tile + query_head * kHeadDim + tid] = value;
 }
 
 constexpr size_t kDecodeSharedBytes = 1024 + kStages * kStageBytes + sizeof(Shared);
@@ -678,7 +709,7 @@ int rk_attention_decode(const void *window, const rk_decode_plan *plan, uint32_t
   if (int st = cuda_status(cudaMemsetAsync(descriptors + 2 * plan->lanes, 0, sizeof(uint32_t), s), "decode status clear")) return st;
   decode_int4_kernel<<<plan->ctas, kThreads, shared_bytes, s>>>(w->int4_map, args);
   if (int st = cuda_status(cudaGetLastError(), "decode launch")) return st;
-  decode_reduce_kernel<<<dim3(kKvHeads, plan->lanes), 256, 0, s>>>(partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer);
+  decode_reduce_kernel<<<dim3(kGroup, kKvHeads, plan->lanes), 256, 0, s>>>(partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer);
   return cuda_status(cudaGetLastError(), "decode reduce launch");
 }
 
@@ -737,7 +768,7 @@ int rk_attention_decode_static(const void *window, uint32_t format, uint32_t lan
   if (int st = cuda_status(cudaMemsetAsync(descriptors + 2 * lanes, 0, sizeof(uint32_t), s), "decode status clear")) return st;
   decode_int4_kernel<<<kStaticCtas, kThreads, kDecodeSharedBytes, s>>>(w->int4_map, args);
   if (int st = cuda_status(cudaGetLastError(), "decode launch")) return st;
-  decode_reduce_kernel<<<dim3(kKvHeads, lanes), 256, 0, s>>>(partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer);
+  decode_reduce_kernel<<<dim3(kGroup, kKvHeads, lanes), 256, 0, s>>>(partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer);
   return cuda_status(cudaGetLastError(), "decode reduce launch");
 }
 

@@ -1,0 +1,188 @@
+// kv_cache.hpp — request page lists, prefix-page sharing and eviction over the pool.
+//
+// PrefixIndex is the content-addressed chain of 32-token blocks of the reference
+// (runtime/engine/cache/KvCache.hpp:40-239, KvCache.cpp): key = (parent block, the page's 32
+// token ids, image identity), hash h ^= v + 0x9e3779b97f4a7c15 + (h<<6) + (h>>2) seeded with
+// 0x6a09e667f3bcc909, exact compare on a hit, one prefix reference per resident block.
+// Cache is the request-facing subset of the reference facade (runtime/engine/cache/Cache.hpp:213-436,
+// Cache.cpp:143-177,236-333,381-413,436-550,794-851,933-1021): page lists with revisions, ensureTokens,
+// publishCommittedBlocks (dedupe onto the shared page), lookup / attach of a cached prefix, reclaim of
+// the oldest idle leaf through the tier, transfer retirement. Two extensions BASELINE.json asks for that
+// the reference does not have: forkRequest (share full pages, copy the partial tail page) and truncate
+// (give back the pages past a rejected speculative tail). Composite recurrent states, image spans,
+// persistence and probes of the reference facade are outside this path.
+#pragma once
+
+#include "kv_pool.hpp"
+#include "kv_tier.hpp"
+
+#include <array>
+#include <cstdint>
+#include <memory>
+#include <optional>
+#include <span>
+#include <unordered_map>
+#include <vector>
+
+namespace rkb::engine {
+
+struct ImageIdentity final {
+  uint64_t lo = 0, hi = 0;
+  bool operator==(const ImageIdentity &) const = default;
+};
+
+class PrefixIndex final {
+public:
+  static constexpr uint32_t pageTokens = kv::kPageTokens;
+  static constexpr uint32_t noPage = 0xffffffffu;
+  struct Match { uint64_t id = 0; uint32_t page = noPage; };
+  struct Chain { std::vector<uint64_t> blocks; std::vector<uint32_t> pages; };
+  struct Candidate { uint64_t block = 0; uint64_t lastUsed = 0; };
+
+  explicit PrefixIndex(KvPool &pool) : pool_(pool), blockOnPage_(pool.pageCount()) {}
+  ~PrefixIndex();
+  PrefixIndex(const PrefixIndex &) = delete;
+  PrefixIndex &operator=(const PrefixIndex &) = delete;
+
+  std::optional<Match> find(uint64_t parent, std::span<const uint32_t> tokens, ImageIdentity images = {}) const;
+  // Existing content is returned as is; a host-only block adopts the writer's page; a block in
+  // transfer keeps its own page and the writer keeps its copy.
+  Match insert(uint64_t parent, std::span<const uint32_t> tokens, uint32_t page, ImageIdentity images = {});
+  void retainActive(uint64_t block);
+  void releaseActive(uint64_t block) noexcept;
+  void touch(uint64_t block) noexcept;
+  Chain chain(uint64_t block) const;
+  bool contains(uint64_t block) const noexcept { return blocks_.count(block) != 0; }
+  uint32_t page(uint64_t block) const { return at(block).page; }
+  std::shared_ptr<KvTierSlot> slot(uint64_t block) const { return at(block).slot; }
+  bool transferring(uint64_t block) const { return at(block).transferring; }
+  bool idle(uint64_t block) const { const Block &b = at(block); return !b.activeUsers && !b.transferring; }
+  bool residentLeaf(uint64_t block) const { const Block &b = at(block); return b.page != noPage && !b.residentChildren && !b.activeUsers && !b.transferring; }
+  uint64_t lastUsed(uint64_t block) const { return at(block).lastUsed; }
+  void setTransferring(uint64_t block, bool value) { at(block).transferring = value; }
+  void setSlot(uint64_t block, std::shared_ptr<KvTierSlot> slot) { at(block).slot = std::move(slot); }
+  // Returns the page of a resident leaf that has a tier copy to the pool.
+  void dropPage(uint64_t block);
+  // Gives a host-only block a page whose content follows (restore, or recomputation).
+  void adoptPage(uint64_t block, uint32_t page);
+  void followPages(const KvPageMoves &moves) noexcept;
+  void poison(uint64_t block);
+  void erase(uint64_t block); // only a block without children, users or transfer
+  std::optional<Candidate> evictionCandidate() const; // oldest resident leaf no request uses
+  uint32_t residentBlocks() const noexcept { return resident_; }
+  uint32_t tierBlocks() const noexcept;
+  size_t size() const noexcept { return blocks_.size(); }
+
+private:
+  struct Block {
+    uint64_t id = 0, parent = 0, hash = 0, lastUsed = 0;
+    std::array<uint32_t, pageTokens> tokens{};
+    ImageIdentity images;
+    uint32_t page = noPage;
+    std::shared_ptr<KvTierSlot> slot;
+    uint32_t children = 0, residentChildren = 0, activeUsers = 0;
+    bool transferring = false, poisoned = false;
+  };
+  Block &at(uint64_t block);
+  const Block &at(uint64_t block) const;
+
+  KvPool &pool_;
+  std::unordered_map<uint64_t, Block> blocks_;
+  std::unordered_multimap<uint64_t, uint64_t> index_;
+  std::vector<uint64_t> blockOnPage_;
+  uint64_t nextId_ = 1, clock_ = 0;
+  uint32_t resident_ = 0;
+};
+
+enum class TokenAdmissionFailure : uint8_t { None, Denied, Pending };
+struct TokenAdmission {
+  TokenAdmissionFailure failure = TokenAdmissionFailure::None;
+  uint32_t pagesNeeded = 0, pagesFree = 0;
+  AllocationFailure cause = AllocationFailure::None;
+  bool granted() const noexcept { return failure == TokenAdmissionFailure::None; }
+};
+
+// A request's logical page list as the GPU table sees it: equal to the previous revision's below
+// firstChanged (Cache.hpp:136-140; runtime/model/RuntimeBindings.hpp:205-233 patches from there).
+struct PageTableView {
+  std::span<const uint32_t> pages;
+  uint64_t revision = 0;
+  uint32_t firstChanged = 0;
+};
+
+struct CacheSnapshot {
+  uint32_t requests = 0, residentBlocks = 0, tierBlocks = 0, transfers = 0;
+  uint64_t demotions = 0, restores = 0, failedTransfers = 0, evictedBlocks = 0, forkCopies = 0, truncatedPages = 0;
+};
+
+class Cache final {
+public:
+  Cache(KvPool &pool, kv::ExtentStorage &storage, KvTier *tier = nullptr) : pool_(pool), storage_(storage), tier_(tier), index_(pool) {}
+  ~Cache();
+
+  void beginRequest(uint64_t request);
+  void endRequest(uint64_t request);
+  TokenAdmission ensureTokens(uint64_t request, uint64_t tokenCount);
+  PageTableView pageTable(uint64_t request) const;
+  // Hashes each newly complete page into the index; content that already exists swaps the request onto
+  // the shared page and releases the writer's copy (Cache.cpp:294-333).
+  void publishCommittedBlocks(uint64_t request, std::span<const uint32_t> exactTokens, uint32_t committedTokens);
+  // The cached chain matching the prompt: at most (n-1)/32 blocks, one real token is always left
+  // to recompute (Cache.cpp:179-199).
+  std::vector<uint64_t> lookup(std::span<const uint32_t> prompt);
+  // Attaches a matched chain to a request without pages: resident blocks are shared (one more
+  // active reference each), host-only blocks take fresh pages and start restores, root first
+  // (Cache.cpp:745-785). Returns the tokens the request resumes after, or Denied/Pending.
+  TokenAdmission attachPrefix(uint64_t request, std::span<const uint64_t> blocks, uint32_t *resumeTokens);
+  bool restoresPending(uint64_t request) const;
+
+  // Extension: `child` shares every full committed page of `parent` and gets its own copy of the
+  // partial tail page (copy-on-write of the only page both would write). Copies are ordered on the
+  // storage's stream. Returns the number of pages copied (0 or 1), or throws on refusal.
+  uint32_t forkRequest(uint64_t parent, uint64_t child, uint32_t committedTokens);
+  // Extension: after a verify step committed `committedTokens`, keep the pages that hold them plus
+  // `scratchTokens` ahead and give the rest back. Returns the pages released.
+  uint32_t truncate(uint64_t request, uint32_t committedTokens, uint32_t scratchTokens);
+
+  // Evicts the oldest idle leaf: with a tier, starts its demotion (the page stays until the copy
+  // lands); without one, or when the block already has a tier copy, drops it at once.
+  bool reclaimOne();
+  uint32_t reclaimForPages(uint32_t pages);
+  // Retires finished transfers (Cache.cpp:933-1021): a landed demotion drops the page, a failed one
+  // keeps it; a landed restore makes the block usable, a failed one poisons it.
+  void pollTransfers();
+  // Empties one extent (KvPool::compactExtent) and re-points every request and block.
+  bool compactExtent();
+  uint32_t pendingPages() const noexcept { return uint32_t(demotions_.size()); }
+
+  PrefixIndex &index() noexcept { return index_; }
+  CacheSnapshot snapshot() const;
+
+private:
+  struct Request {
+    std::vector<uint32_t> pages;
+    std::vector<uint64_t> blocks; // cached chain covering the first blocks.size() pages
+    uint64_t revision = 0;
+    uint32_t firstChanged = 0;
+  };
+  struct Transfer {
+    uint64_t block = 0;
+    uint32_t page = 0;
+    std::unique_ptr<KvTransfer> ticket;
+    std::shared_ptr<KvTierSlot> slot;
+  };
+  Request &request(uint64_t id);
+  const Request &request(uint64_t id) const;
+  static void changed(Request &r, uint32_t first) noexcept { ++r.revision; r.firstChanged = first; }
+  TokenAdmission admitPages(uint32_t count, std::vector<uint32_t> &pages);
+
+  KvPool &pool_;
+  kv::ExtentStorage &storage_;
+  KvTier *tier_;
+  PrefixIndex index_;
+  std::unordered_map<uint64_t, Request> requests_;
+  std::vector<Transfer> demotions_, restores_;
+  CacheSnapshot counters_;
+};
+
+} // namespace rkb::engine
