@@ -1,0 +1,87 @@
+/* richkv_host.h — C handles over the host control plane (C++ classes in richengine_b200/csrc/host):
+ * the page allocator, the request/prefix cache with its eviction tier, and the operator plans.
+ * They exist so that non-C++ hosts (the Python tests and benchmark here) can drive the same objects;
+ * a C++ host uses the classes directly. Reference interfaces mirrored:
+ *   engine::KvPool      runtime/engine/cache/KvPool.hpp:75-185
+ *   engine::Cache       runtime/engine/cache/Cache.hpp:213-436 (request / page-table / prefix / eviction subset)
+ *   ops::PagedAttention runtime/ops/PagedAttention.hpp:199-324 (plans)
+ * Status codes are those of richkv.h. */
+#ifndef RICHKV_HOST_H
+#define RICHKV_HOST_H
+
+#include "richkv.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- pool -------------------------------------------------------------------------------------- */
+/* Over a memory-less storage with a page budget (host-only use) or over a device storage handle. */
+void *rk_pool_create_budget(uint32_t pages, uint64_t bytes_per_page, uint32_t extent_pages, uint32_t runway_pages,
+                            uint64_t budget_pages);
+void *rk_pool_create_device(void *storage, uint32_t runway_pages, void *stream);
+void rk_pool_destroy(void *pool);
+void rk_pool_set_budget(void *pool, uint64_t budget_pages); /* budget storage only */
+int rk_pool_acquire(void *pool, uint32_t count, uint32_t *pages_out); /* count, or RK_ERR_REFUSED */
+int rk_pool_retain(void *pool, uint32_t page, int prefix_owner);
+int rk_pool_release(void *pool, uint32_t page, int prefix_owner);
+uint64_t rk_pool_reclaim_empty_extents(void *pool, int keep_runway, uint32_t limit);
+/* Destinations of the emptied extent into destinations_out (extent_pages entries); returns its first
+ * page, or -1 when nothing moved. */
+int64_t rk_pool_compact_extent(void *pool, const uint32_t *fixed, uint32_t fixed_count, uint32_t *destinations_out);
+/* out[10] = pagesAllocated, pagesFree, pagesActive, pagesPrefix, allocatedBytes, reclaimableBytes,
+ *           extentAllocations, extentReleases, extentCompactions, pagesMoved */
+void rk_pool_snapshot(const void *pool, uint64_t *out);
+uint64_t rk_pool_page_content(const void *pool, uint32_t page);       /* budget storage: the page's content tag */
+void rk_pool_set_page_content(void *pool, uint32_t page, uint64_t tag);
+
+/* ---- cache ------------------------------------------------------------------------------------- */
+/* tier_mode 0: no tier; 1: pinned-host tier (device pools) with `slots` slots and `transfers` in flight;
+ * 2: a host-only tier whose transfers finish when rk_cache_complete_transfer is called (tests). */
+void *rk_cache_create(void *pool, int tier_mode, uint32_t slots, uint32_t transfers);
+void rk_cache_destroy(void *cache);
+int rk_cache_begin_request(void *cache, uint64_t request);
+int rk_cache_end_request(void *cache, uint64_t request);
+/* 0 granted, 1 denied, 2 pending (demotions on their way cover the need) */
+int rk_cache_ensure_tokens(void *cache, uint64_t request, uint64_t tokens);
+/* Copies up to capacity page ids; returns the page count; revision and first_changed as Cache::pageTable. */
+int64_t rk_cache_page_table(const void *cache, uint64_t request, uint32_t *pages_out, uint32_t capacity,
+                            uint64_t *revision, uint32_t *first_changed);
+int rk_cache_publish(void *cache, uint64_t request, const uint32_t *tokens, uint32_t token_count, uint32_t committed);
+/* Matched blocks into blocks_out (capacity entries); returns how many. */
+int64_t rk_cache_lookup(void *cache, const uint32_t *prompt, uint32_t prompt_tokens, uint64_t *blocks_out, uint32_t capacity);
+int rk_cache_attach_prefix(void *cache, uint64_t request, const uint64_t *blocks, uint32_t count, uint32_t *resume_tokens);
+int rk_cache_restores_pending(const void *cache, uint64_t request);
+int rk_cache_fork(void *cache, uint64_t parent, uint64_t child, uint32_t committed_tokens); /* pages copied, or status */
+int64_t rk_cache_truncate(void *cache, uint64_t request, uint32_t committed_tokens, uint32_t scratch_tokens);
+int rk_cache_reclaim_one(void *cache);
+uint32_t rk_cache_reclaim_for_pages(void *cache, uint32_t pages);
+void rk_cache_poll_transfers(void *cache);
+int rk_cache_compact_extent(void *cache);
+int rk_cache_complete_transfer(void *cache, int success); /* tier_mode 2: finishes the oldest transfer; 0 if none */
+void rk_cache_fail_next_transfers(void *cache, uint32_t count); /* tier_mode 1: host-side fault injection */
+/* out[10] = requests, residentBlocks, tierBlocks, transfers, demotions, restores, failedTransfers,
+ *           evictedBlocks, forkCopies, truncatedPages */
+void rk_cache_snapshot(const void *cache, uint64_t *out);
+/* Block state: out[4] = page (0xffffffff = none), has tier copy, transferring, last used. -1 if unknown. */
+int rk_cache_block_state(const void *cache, uint64_t block, uint64_t *out);
+
+/* ---- plans -------------------------------------------------------------------------------------- */
+/* names: "split\nreduce\nstore"; out[14] = splits, lane splits of the first four lanes, splitGroups xyz,
+ * reduceGroups xyz, partialsBytes, statisticsBytes, rowCapacity. row_capacity 0 = 8 (chain) / 16 (tree). */
+int rk_plan_verify(uint32_t lanes, uint32_t query_heads, uint32_t layers, uint32_t kv_heads, uint32_t head_dim,
+                   uint32_t format, const uint32_t *history, int tree, uint32_t row_capacity, char *names,
+                   size_t names_bytes, uint64_t *out);
+/* out[10] = rows, splits, splitGroups xyz, reduceGroups xyz, partialsBytes, statisticsBytes */
+int rk_plan_prefill(uint32_t rows, uint32_t query_heads, uint32_t layers, uint32_t kv_heads, uint32_t head_dim,
+                    uint32_t format, char *names, size_t names_bytes, uint64_t *out);
+/* out[4] = verify partials, verify statistics, prefill partials, prefill statistics */
+int rk_plan_workspaces(uint32_t lanes, uint32_t max_rows, uint32_t query_heads, uint32_t layers, uint32_t kv_heads,
+                       uint32_t head_dim, uint32_t format, uint64_t *out);
+/* Empty string when valid, else the reference's tag (PagedAttention.hpp:75-95). */
+const char *rk_chunk_validation_error(uint32_t committed, uint32_t tokens, uint32_t stride, uint32_t entries);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RICHKV_HOST_H */

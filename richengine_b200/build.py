@@ -22,7 +22,7 @@ OBJ = PACKAGE / "build"
 LIBRARY = PACKAGE / "librichkv.so"
 
 NVCC_FLAGS = [
-    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++20",
     "-Xcompiler", "-fPIC,-Wall", "--expt-relaxed-constexpr",
     # bit-exact quantisation: IEEE division/sqrt, no flush-to-zero, and no
     # fused multiply-add contraction across the (x*range)/amax recipe

@@ -1,0 +1,320 @@
+// host_capi.cpp — C handles over the host control plane (include/richkv_host.h).
+#include "../../../include/richkv_host.h"
+
+#include "kv_cache.hpp"
+#include "kv_pool.hpp"
+#include "paged_attention.hpp"
+#include "storage_adapters.hpp"
+
+#include <cstring>
+#include <deque>
+#include <memory>
+#include <string>
+
+namespace rk { void set_error(const char *text); }
+
+using namespace rkb;
+
+namespace {
+
+struct PoolHandle {
+  std::unique_ptr<kv::BudgetExtentStorage> budget;
+  std::unique_ptr<kv::DeviceExtentStorage> device;
+  std::unique_ptr<engine::KvPool> pool;
+  kv::ExtentStorage &storage() { return budget ? static_cast<kv::ExtentStorage &>(*budget) : *device; }
+};
+
+// A tier without a device: slots hold content tags; transfers finish when the test says so
+// (the shape of the reference's test tier, dev/tests/engine/TestKvTier.hpp:17-127).
+class ManualTier final : public engine::KvTier {
+public:
+  ManualTier(kv::BudgetExtentStorage &storage, uint32_t slots, uint32_t transfers)
+      : storage_(storage), used_(slots, 0), tags_(slots, 0), limit_(transfers) {}
+  uint64_t slotBytes() const noexcept override { return storage_.bytesPerPage(); }
+  bool writable() const noexcept override { return writable_; }
+  bool canDemote() const noexcept override { return demotions_ < std::max(1u, limit_ / 2) && pending_.size() < limit_ && writable_; }
+  bool canRestore() const noexcept override { return restores_ < std::max(1u, limit_ - limit_ / 4) && pending_.size() < limit_; }
+  std::shared_ptr<engine::KvTierSlot> acquireSlot() override {
+    for (uint32_t i = 0; i < used_.size(); ++i)
+      if (!used_[i]) { used_[i] = 1; return std::make_shared<Slot>(this, i); }
+    return {};
+  }
+  std::unique_ptr<engine::KvTransfer> demote(uint32_t page, std::shared_ptr<engine::KvTierSlot> slot) override {
+    if (!canDemote()) return {};
+    auto state = std::make_shared<State>(State{true, page, std::dynamic_pointer_cast<Slot>(slot)->id});
+    pending_.push_back(state);
+    ++demotions_;
+    return std::make_unique<Ticket>(state);
+  }
+  std::unique_ptr<engine::KvTransfer> restore(std::shared_ptr<engine::KvTierSlot> slot, uint32_t page) override {
+    if (!canRestore()) return {};
+    auto state = std::make_shared<State>(State{false, page, std::dynamic_pointer_cast<Slot>(slot)->id});
+    pending_.push_back(state);
+    ++restores_;
+    return std::make_unique<Ticket>(state);
+  }
+  void poll() override {}
+  bool complete(bool success) {
+    if (pending_.empty()) return false;
+    auto state = pending_.front();
+    pending_.pop_front();
+    --(state->demotion ? demotions_ : restores_);
+    if (success) {
+      if (state->demotion) tags_[state->slot] = storage_.content.at(state->page);
+      else storage_.content.at(state->page) = tags_[state->slot];
+    } else if (state->demotion) {
+      writable_ = false;
+    }
+    state->ready = true;
+    state->success = success;
+    return true;
+  }
+
+private:
+  struct State { bool demotion; uint32_t page, slot; bool ready = false, success = false; };
+  struct Slot final : engine::KvTierSlot {
+    Slot(ManualTier *t, uint32_t i) : tier(t), id(i) {}
+    ~Slot() override { tier->used_[id] = 0; }
+    ManualTier *tier; uint32_t id;
+  };
+  struct Ticket final : engine::KvTransfer {
+    explicit Ticket(std::shared_ptr<State> s) : state(std::move(s)) {}
+    bool ready() const noexcept override { return state->ready; }
+    bool finish() override { return state->success; }
+    std::shared_ptr<State> state;
+  };
+  kv::BudgetExtentStorage &storage_;
+  std::vector<uint8_t> used_;
+  std::vector<uint64_t> tags_;
+  std::deque<std::shared_ptr<State>> pending_;
+  uint32_t limit_, demotions_ = 0, restores_ = 0;
+  bool writable_ = true;
+};
+
+struct CacheHandle {
+  PoolHandle *pool = nullptr;
+  std::unique_ptr<engine::KvTier> tier;
+  ManualTier *manual = nullptr;
+  engine::HostKvTier *host = nullptr;
+  std::unique_ptr<engine::Cache> cache;
+};
+
+template <typename F> int guarded(F &&body) {
+  try {
+    return body();
+  } catch (const std::invalid_argument &e) { rk::set_error(e.what()); return RK_ERR_INVALID;
+  } catch (const std::logic_error &e) { rk::set_error(e.what()); return RK_ERR_INVALID;
+  } catch (const std::exception &e) { rk::set_error(e.what()); return RK_ERR_REFUSED; }
+}
+
+kv::Layout layoutOf(uint32_t layers, uint32_t heads, uint32_t dim, uint32_t format) {
+  return kv::Layout{layers, heads, dim, static_cast<kv::Format>(format), 0.0f};
+}
+int joinNames(std::initializer_list<std::string> parts, char *names, size_t bytes) {
+  std::string joined;
+  for (const std::string &p : parts) { if (!joined.empty()) joined += "\n"; joined += p; }
+  if (joined.size() + 1 > bytes) return RK_ERR_INVALID;
+  std::memcpy(names, joined.c_str(), joined.size() + 1);
+  return RK_OK;
+}
+
+} // namespace
+
+extern "C" {
+
+void *rk_pool_create_budget(uint32_t pages, uint64_t bytes_per_page, uint32_t extent_pages, uint32_t runway_pages, uint64_t budget_pages) {
+  try {
+    if (!extent_pages || !pages || pages % extent_pages) throw std::invalid_argument("invalid KV extent storage");
+    auto h = std::make_unique<PoolHandle>();
+    h->budget = std::make_unique<kv::BudgetExtentStorage>(pages, bytes_per_page, extent_pages);
+    h->budget->budgetPages = budget_pages;
+    h->pool = std::make_unique<engine::KvPool>(*h->budget, runway_pages);
+    return h.release();
+  } catch (const std::exception &e) { rk::set_error(e.what()); return nullptr; }
+}
+void *rk_pool_create_device(void *storage, uint32_t runway_pages, void *stream) {
+  try {
+    auto h = std::make_unique<PoolHandle>();
+    h->device = std::make_unique<kv::DeviceExtentStorage>(storage, stream);
+    h->pool = std::make_unique<engine::KvPool>(*h->device, runway_pages);
+    return h.release();
+  } catch (const std::exception &e) { rk::set_error(e.what()); return nullptr; }
+}
+void rk_pool_destroy(void *pool) { delete static_cast<PoolHandle *>(pool); }
+void rk_pool_set_budget(void *pool, uint64_t budget_pages) {
+  auto *h = static_cast<PoolHandle *>(pool);
+  if (h->budget) h->budget->budgetPages = budget_pages;
+}
+int rk_pool_acquire(void *pool, uint32_t count, uint32_t *pages_out) {
+  return guarded([&] {
+    auto got = static_cast<PoolHandle *>(pool)->pool->acquirePages(count);
+    if (!got.granted()) { rk::set_error("the pool could not grow by an extent"); return RK_ERR_REFUSED; }
+    std::copy(got.pages.begin(), got.pages.end(), pages_out);
+    return int(got.pages.size());
+  });
+}
+int rk_pool_retain(void *pool, uint32_t page, int prefix_owner) {
+  return guarded([&] { static_cast<PoolHandle *>(pool)->pool->retainPage(page, prefix_owner != 0); return RK_OK; });
+}
+int rk_pool_release(void *pool, uint32_t page, int prefix_owner) {
+  return guarded([&] { static_cast<PoolHandle *>(pool)->pool->releasePage(page, prefix_owner != 0); return RK_OK; });
+}
+uint64_t rk_pool_reclaim_empty_extents(void *pool, int keep_runway, uint32_t limit) {
+  return static_cast<PoolHandle *>(pool)->pool->reclaimEmptyExtents(keep_runway != 0, limit);
+}
+int64_t rk_pool_compact_extent(void *pool, const uint32_t *fixed, uint32_t fixed_count, uint32_t *destinations_out) {
+  try {
+    auto moves = static_cast<PoolHandle *>(pool)->pool->compactExtent({fixed, fixed_count});
+    if (moves.empty()) return -1;
+    std::copy(moves.destinations.begin(), moves.destinations.end(), destinations_out);
+    return moves.firstPage;
+  } catch (const std::exception &e) { rk::set_error(e.what()); return -2; }
+}
+void rk_pool_snapshot(const void *pool, uint64_t *out) {
+  const auto s = static_cast<const PoolHandle *>(pool)->pool->snapshot();
+  out[0] = s.pagesAllocated; out[1] = s.pagesFree; out[2] = s.pagesActive; out[3] = s.pagesPrefix;
+  out[4] = s.allocatedBytes; out[5] = s.reclaimableBytes; out[6] = s.extentAllocations;
+  out[7] = s.extentReleases; out[8] = s.extentCompactions; out[9] = s.pagesMoved;
+}
+uint64_t rk_pool_page_content(const void *pool, uint32_t page) {
+  const auto *h = static_cast<const PoolHandle *>(pool);
+  return h->budget ? h->budget->content.at(page) : 0;
+}
+void rk_pool_set_page_content(void *pool, uint32_t page, uint64_t tag) {
+  auto *h = static_cast<PoolHandle *>(pool);
+  if (h->budget) h->budget->content.at(page) = tag;
+}
+
+void *rk_cache_create(void *pool, int tier_mode, uint32_t slots, uint32_t transfers) {
+  try {
+    auto *p = static_cast<PoolHandle *>(pool);
+    auto h = std::make_unique<CacheHandle>();
+    h->pool = p;
+    if (tier_mode == 1) {
+      if (!p->device) throw std::invalid_argument("the pinned-host tier needs a device pool");
+      auto tier = std::make_unique<engine::HostKvTier>(p->device->handle(), slots, transfers);
+      h->host = tier.get();
+      h->tier = std::move(tier);
+    } else if (tier_mode == 2) {
+      if (!p->budget) throw std::invalid_argument("the manual tier needs a budget pool");
+      auto tier = std::make_unique<ManualTier>(*p->budget, slots, transfers);
+      h->manual = tier.get();
+      h->tier = std::move(tier);
+    }
+    h->cache = std::make_unique<engine::Cache>(*p->pool, p->storage(), h->tier.get());
+    return h.release();
+  } catch (const std::exception &e) { rk::set_error(e.what()); return nullptr; }
+}
+void rk_cache_destroy(void *cache) {
+  auto *h = static_cast<CacheHandle *>(cache);
+  if (!h) return;
+  if (h->manual) while (h->manual->complete(true)) {} // nothing stays in flight
+  h->cache.reset();
+  delete h;
+}
+#define CACHE (static_cast<CacheHandle *>(cache)->cache)
+int rk_cache_begin_request(void *cache, uint64_t request) { return guarded([&] { CACHE->beginRequest(request); return RK_OK; }); }
+int rk_cache_end_request(void *cache, uint64_t request) { return guarded([&] { CACHE->endRequest(request); return RK_OK; }); }
+int rk_cache_ensure_tokens(void *cache, uint64_t request, uint64_t tokens) {
+  return guarded([&] { return int(CACHE->ensureTokens(request, tokens).failure); });
+}
+int64_t rk_cache_page_table(const void *cache, uint64_t request, uint32_t *pages_out, uint32_t capacity, uint64_t *revision, uint32_t *first_changed) {
+  try {
+    const auto view = static_cast<const CacheHandle *>(cache)->cache->pageTable(request);
+    for (size_t i = 0; i < view.pages.size() && i < capacity; ++i) pages_out[i] = view.pages[i];
+    if (revision) *revision = view.revision;
+    if (first_changed) *first_changed = view.firstChanged;
+    return int64_t(view.pages.size());
+  } catch (const std::exception &e) { rk::set_error(e.what()); return RK_ERR_INVALID; }
+}
+int rk_cache_publish(void *cache, uint64_t request, const uint32_t *tokens, uint32_t token_count, uint32_t committed) {
+  return guarded([&] { CACHE->publishCommittedBlocks(request, {tokens, token_count}, committed); return RK_OK; });
+}
+int64_t rk_cache_lookup(void *cache, const uint32_t *prompt, uint32_t prompt_tokens, uint64_t *blocks_out, uint32_t capacity) {
+  try {
+    const auto blocks = CACHE->lookup({prompt, prompt_tokens});
+    for (size_t i = 0; i < blocks.size() && i < capacity; ++i) blocks_out[i] = blocks[i];
+    return int64_t(blocks.size());
+  } catch (const std::exception &e) { rk::set_error(e.what()); return RK_ERR_INVALID; }
+}
+int rk_cache_attach_prefix(void *cache, uint64_t request, const uint64_t *blocks, uint32_t count, uint32_t *resume_tokens) {
+  return guarded([&] { return int(CACHE->attachPrefix(request, {blocks, count}, resume_tokens).failure); });
+}
+int rk_cache_restores_pending(const void *cache, uint64_t request) {
+  try { return static_cast<const CacheHandle *>(cache)->cache->restoresPending(request) ? 1 : 0; } catch (...) { return RK_ERR_INVALID; }
+}
+int rk_cache_fork(void *cache, uint64_t parent, uint64_t child, uint32_t committed_tokens) {
+  return guarded([&] { return int(CACHE->forkRequest(parent, child, committed_tokens)); });
+}
+int64_t rk_cache_truncate(void *cache, uint64_t request, uint32_t committed_tokens, uint32_t scratch_tokens) {
+  try { return CACHE->truncate(request, committed_tokens, scratch_tokens); } catch (const std::exception &e) { rk::set_error(e.what()); return RK_ERR_INVALID; }
+}
+int rk_cache_reclaim_one(void *cache) { return guarded([&] { return CACHE->reclaimOne() ? 1 : 0; }); }
+uint32_t rk_cache_reclaim_for_pages(void *cache, uint32_t pages) { return CACHE->reclaimForPages(pages); }
+void rk_cache_poll_transfers(void *cache) { CACHE->pollTransfers(); }
+int rk_cache_compact_extent(void *cache) { return guarded([&] { return CACHE->compactExtent() ? 1 : 0; }); }
+int rk_cache_complete_transfer(void *cache, int success) {
+  auto *h = static_cast<CacheHandle *>(cache);
+  return h->manual && h->manual->complete(success != 0) ? 1 : 0;
+}
+void rk_cache_fail_next_transfers(void *cache, uint32_t count) {
+  auto *h = static_cast<CacheHandle *>(cache);
+  if (h->host) h->host->failNext(count);
+}
+void rk_cache_snapshot(const void *cache, uint64_t *out) {
+  const auto s = static_cast<const CacheHandle *>(cache)->cache->snapshot();
+  out[0] = s.requests; out[1] = s.residentBlocks; out[2] = s.tierBlocks; out[3] = s.transfers; out[4] = s.demotions;
+  out[5] = s.restores; out[6] = s.failedTransfers; out[7] = s.evictedBlocks; out[8] = s.forkCopies; out[9] = s.truncatedPages;
+}
+int rk_cache_block_state(const void *cache, uint64_t block, uint64_t *out) {
+  auto &index = static_cast<const CacheHandle *>(cache)->cache->index();
+  if (!index.contains(block)) return -1;
+  out[0] = index.page(block); out[1] = index.slot(block) != nullptr; out[2] = index.transferring(block); out[3] = index.lastUsed(block);
+  return 0;
+}
+#undef CACHE
+
+int rk_plan_verify(uint32_t lanes, uint32_t query_heads, uint32_t layers, uint32_t kv_heads, uint32_t head_dim, uint32_t format,
+                   const uint32_t *history, int tree, uint32_t row_capacity, char *names, size_t names_bytes, uint64_t *out) {
+  return guarded([&] {
+    const auto plan = ops::PagedAttention::verifyPlan(lanes, query_heads, layoutOf(layers, kv_heads, head_dim, format), {history, lanes}, tree != 0, row_capacity);
+    if (int s = joinNames({plan.splitPipeline, plan.reducePipeline, plan.storePipeline}, names, names_bytes)) return s;
+    size_t i = 0;
+    out[i++] = plan.splits;
+    for (uint32_t l = 0; l < 4; ++l) out[i++] = l < lanes ? plan.laneSplits[l] : 0;
+    out[i++] = plan.splitGroups.x; out[i++] = plan.splitGroups.y; out[i++] = plan.splitGroups.z;
+    out[i++] = plan.reduceGroups.x; out[i++] = plan.reduceGroups.y; out[i++] = plan.reduceGroups.z;
+    out[i++] = plan.workspace.partialsBytes; out[i++] = plan.workspace.statisticsBytes; out[i++] = plan.rowCapacity;
+    return RK_OK;
+  });
+}
+int rk_plan_prefill(uint32_t rows, uint32_t query_heads, uint32_t layers, uint32_t kv_heads, uint32_t head_dim, uint32_t format,
+                    char *names, size_t names_bytes, uint64_t *out) {
+  return guarded([&] {
+    const auto plan = ops::PagedAttention::prefillPlan(rows, query_heads, layoutOf(layers, kv_heads, head_dim, format));
+    if (int s = joinNames({plan.splitPipeline, plan.reducePipeline}, names, names_bytes)) return s;
+    size_t i = 0;
+    out[i++] = plan.rows; out[i++] = plan.splits;
+    out[i++] = plan.splitGroups.x; out[i++] = plan.splitGroups.y; out[i++] = plan.splitGroups.z;
+    out[i++] = plan.reduceGroups.x; out[i++] = plan.reduceGroups.y; out[i++] = plan.reduceGroups.z;
+    out[i++] = plan.workspace.partialsBytes; out[i++] = plan.workspace.statisticsBytes;
+    return RK_OK;
+  });
+}
+int rk_plan_workspaces(uint32_t lanes, uint32_t max_rows, uint32_t query_heads, uint32_t layers, uint32_t kv_heads, uint32_t head_dim,
+                       uint32_t format, uint64_t *out) {
+  return guarded([&] {
+    const kv::Layout l = layoutOf(layers, kv_heads, head_dim, format);
+    const auto v = ops::PagedAttention::verifyWorkspace(lanes, query_heads, l);
+    const auto p = ops::PagedAttention::prefillWorkspace(max_rows, query_heads, l);
+    out[0] = v.partialsBytes; out[1] = v.statisticsBytes; out[2] = p.partialsBytes; out[3] = p.statisticsBytes;
+    return RK_OK;
+  });
+}
+const char *rk_chunk_validation_error(uint32_t committed, uint32_t tokens, uint32_t stride, uint32_t entries) {
+  static thread_local std::string text;
+  text = std::string(ops::chunkedPrefillValidationError(rk_chunk_params{committed, tokens, stride, entries, {0, 0}}));
+  return text.c_str();
+}
+
+} // extern "C"

@@ -1,0 +1,479 @@
+#include "kv_cache.hpp"
+
+#include <algorithm>
+#include <stdexcept>
+
+namespace rkb::engine {
+
+namespace {
+uint64_t mix(uint64_t hash, uint64_t value) noexcept {
+  return hash ^ (value + 0x9e3779b97f4a7c15ull + (hash << 6) + (hash >> 2));
+}
+uint64_t blockHash(uint64_t parentHash, std::span<const uint32_t> tokens, ImageIdentity images) noexcept {
+  uint64_t hash = mix(0x6a09e667f3bcc909ull, parentHash);
+  for (uint32_t token : tokens) hash = mix(hash, token);
+  return mix(mix(hash, images.lo), images.hi);
+}
+} // namespace
+
+// ============================== PrefixIndex ====================================================
+PrefixIndex::~PrefixIndex() {
+  for (auto &[id, block] : blocks_)
+    if (block.page != noPage) pool_.releasePage(block.page, true);
+}
+
+PrefixIndex::Block &PrefixIndex::at(uint64_t block) {
+  auto found = blocks_.find(block);
+  if (found == blocks_.end()) throw std::out_of_range("unknown KV cache block");
+  return found->second;
+}
+const PrefixIndex::Block &PrefixIndex::at(uint64_t block) const {
+  auto found = blocks_.find(block);
+  if (found == blocks_.end()) throw std::out_of_range("unknown KV cache block");
+  return found->second;
+}
+
+std::optional<PrefixIndex::Match> PrefixIndex::find(uint64_t parent, std::span<const uint32_t> tokens, ImageIdentity images) const {
+  if (tokens.size() != pageTokens) return std::nullopt;
+  if (parent && !blocks_.count(parent)) return std::nullopt;
+  const uint64_t hash = blockHash(parent ? at(parent).hash : 0, tokens, images);
+  const auto [first, last] = index_.equal_range(hash);
+  for (auto candidate = first; candidate != last; ++candidate) {
+    const Block &entry = at(candidate->second);
+    // The hash only filters; a hit needs the complete key.
+    if (!entry.poisoned && entry.parent == parent && entry.images == images &&
+        std::equal(entry.tokens.begin(), entry.tokens.end(), tokens.begin()))
+      return Match{entry.id, entry.page};
+  }
+  return std::nullopt;
+}
+
+PrefixIndex::Match PrefixIndex::insert(uint64_t parent, std::span<const uint32_t> tokens, uint32_t page, ImageIdentity images) {
+  if (tokens.size() != pageTokens) throw std::invalid_argument("KV cache block must contain one full page");
+  if (page >= pool_.pageCount()) throw std::out_of_range("KV cache physical page is out of range");
+  if (auto existing = find(parent, tokens, images)) {
+    Match result = *existing;
+    if (existing->page == noPage) {
+      adoptPage(existing->id, page);
+      result.page = page;
+    } else if (at(existing->id).transferring) {
+      result.page = page; // its page is still being filled; the writer keeps its own copy
+    }
+    return result;
+  }
+  if (parent && !blocks_.count(parent)) throw std::invalid_argument("KV cache parent block is unknown");
+  if (parent && at(parent).page == noPage) throw std::logic_error("KV cache parent block has no page");
+  if (blockOnPage_[page]) throw std::logic_error("KV cache page already holds a block");
+  Block entry;
+  entry.id = nextId_++;
+  entry.parent = parent;
+  entry.hash = blockHash(parent ? at(parent).hash : 0, tokens, images);
+  std::copy(tokens.begin(), tokens.end(), entry.tokens.begin());
+  entry.images = images;
+  entry.page = page;
+  entry.lastUsed = ++clock_;
+  pool_.retainPage(page, true);
+  const uint64_t id = entry.id;
+  index_.emplace(entry.hash, id);
+  blocks_.emplace(id, std::move(entry));
+  blockOnPage_[page] = id;
+  ++resident_;
+  if (parent) {
+    Block &above = at(parent);
+    ++above.children;
+    ++above.residentChildren;
+  }
+  return {id, page};
+}
+
+void PrefixIndex::retainActive(uint64_t block) { ++at(block).activeUsers; }
+void PrefixIndex::releaseActive(uint64_t block) noexcept {
+  auto found = blocks_.find(block);
+  if (found != blocks_.end() && found->second.activeUsers) --found->second.activeUsers;
+}
+void PrefixIndex::touch(uint64_t block) noexcept {
+  auto found = blocks_.find(block);
+  if (found != blocks_.end()) found->second.lastUsed = ++clock_;
+}
+
+PrefixIndex::Chain PrefixIndex::chain(uint64_t block) const {
+  Chain result;
+  for (uint64_t id = block; id; id = at(id).parent) {
+    result.blocks.push_back(id);
+    result.pages.push_back(at(id).page);
+  }
+  std::reverse(result.blocks.begin(), result.blocks.end());
+  std::reverse(result.pages.begin(), result.pages.end());
+  return result;
+}
+
+void PrefixIndex::dropPage(uint64_t block) {
+  Block &entry = at(block);
+  if (entry.page == noPage || entry.residentChildren || entry.activeUsers || !entry.slot)
+    throw std::logic_error("only an idle resident leaf with a tier copy can drop its page");
+  blockOnPage_[entry.page] = 0;
+  pool_.releasePage(entry.page, true);
+  entry.page = noPage;
+  --resident_;
+  if (entry.parent) {
+    Block &above = at(entry.parent);
+    --above.residentChildren;
+    above.lastUsed = std::max(above.lastUsed, entry.lastUsed); // a new leaf is as warm as what it lost
+  }
+}
+
+void PrefixIndex::adoptPage(uint64_t block, uint32_t page) {
+  Block &entry = at(block);
+  if (entry.page != noPage) throw std::logic_error("KV cache block already has a page");
+  if (entry.parent && at(entry.parent).page == noPage) throw std::logic_error("the parent block must be resident first");
+  if (blockOnPage_.at(page)) throw std::logic_error("KV cache page already holds a block");
+  pool_.retainPage(page, true);
+  entry.page = page;
+  blockOnPage_[page] = block;
+  ++resident_;
+  if (entry.parent) ++at(entry.parent).residentChildren;
+}
+
+void PrefixIndex::followPages(const KvPageMoves &moves) noexcept {
+  for (uint32_t offset = 0; offset < moves.destinations.size(); ++offset) {
+    const uint32_t from = moves.firstPage + offset, to = moves.destinations[offset];
+    if (from == to || !blockOnPage_[from]) continue;
+    const uint64_t id = blockOnPage_[from];
+    blockOnPage_[from] = 0;
+    blockOnPage_[to] = id;
+    blocks_.find(id)->second.page = to;
+  }
+}
+
+void PrefixIndex::poison(uint64_t block) { at(block).poisoned = true; }
+
+void PrefixIndex::erase(uint64_t block) {
+  Block &entry = at(block);
+  if (entry.children || entry.activeUsers || entry.transferring)
+    throw std::logic_error("only a block without children, users or transfer can be removed");
+  if (entry.page != noPage) {
+    blockOnPage_[entry.page] = 0;
+    pool_.releasePage(entry.page, true);
+    --resident_;
+  }
+  if (entry.parent) {
+    Block &above = at(entry.parent);
+    --above.children;
+    if (entry.page != noPage) --above.residentChildren;
+    above.lastUsed = std::max(above.lastUsed, entry.lastUsed);
+  }
+  const auto [first, last] = index_.equal_range(entry.hash);
+  for (auto it = first; it != last; ++it)
+    if (it->second == block) { index_.erase(it); break; }
+  blocks_.erase(block);
+}
+
+std::optional<PrefixIndex::Candidate> PrefixIndex::evictionCandidate() const {
+  std::optional<Candidate> best;
+  for (const auto &[id, entry] : blocks_) {
+    if (entry.page == noPage || entry.residentChildren || entry.activeUsers || entry.transferring) continue;
+    if (!best || entry.lastUsed < best->lastUsed) best = Candidate{id, entry.lastUsed};
+  }
+  return best;
+}
+
+uint32_t PrefixIndex::tierBlocks() const noexcept {
+  uint32_t count = 0;
+  for (const auto &[id, entry] : blocks_) count += entry.slot != nullptr;
+  return count;
+}
+
+// ================================== Cache ========================================================
+Cache::~Cache() {
+  // Transfers read or write their pages in place: they retire before the pages can go.
+  for (auto *list : {&demotions_, &restores_})
+    for (Transfer &t : *list) {
+      while (!t.ticket->ready()) tier_->poll();
+      t.ticket->finish();
+      if (index_.contains(t.block)) index_.setTransferring(t.block, false);
+    }
+  for (auto &[id, active] : requests_) {
+    for (uint32_t page : active.pages) pool_.releasePage(page, false);
+    if (!active.blocks.empty()) index_.releaseActive(active.blocks.back());
+  }
+}
+
+Cache::Request &Cache::request(uint64_t id) {
+  auto found = requests_.find(id);
+  if (found == requests_.end()) throw std::invalid_argument("unknown request id");
+  return found->second;
+}
+const Cache::Request &Cache::request(uint64_t id) const {
+  auto found = requests_.find(id);
+  if (found == requests_.end()) throw std::invalid_argument("unknown request id");
+  return found->second;
+}
+
+void Cache::beginRequest(uint64_t id) {
+  if (!id) throw std::invalid_argument("invalid request id");
+  if (!requests_.emplace(id, Request{}).second) throw std::invalid_argument("duplicate request id");
+}
+
+void Cache::endRequest(uint64_t id) {
+  auto found = requests_.find(id);
+  if (found == requests_.end()) return;
+  for (uint32_t page : found->second.pages) pool_.releasePage(page, false);
+  if (!found->second.blocks.empty()) index_.releaseActive(found->second.blocks.back());
+  requests_.erase(found);
+}
+
+TokenAdmission Cache::admitPages(uint32_t count, std::vector<uint32_t> &pages) {
+  KvPageAcquisition acquired = pool_.acquirePages(count);
+  if (!acquired.granted()) {
+    // Demoted pages free theirs when their copies land: wait once those on their way cover what
+    // the free pages do not; until then the caller reclaims (Cache.cpp:400-413).
+    const uint32_t missing = count - std::min(count, pool_.freePageCount());
+    const uint32_t pending = pendingPages();
+    const bool covered = pending > 0 && pending >= missing;
+    return {covered ? TokenAdmissionFailure::Pending : TokenAdmissionFailure::Denied, count, pool_.freePageCount(), acquired.failure};
+  }
+  pages = std::move(acquired.pages);
+  return {};
+}
+
+TokenAdmission Cache::ensureTokens(uint64_t id, uint64_t tokenCount) {
+  Request &active = request(id);
+  const uint64_t needed = (tokenCount + kv::kPageTokens - 1) / kv::kPageTokens;
+  if (needed > 0xffffffffull) throw std::invalid_argument("KV target exceeds the page id range");
+  const uint32_t previous = uint32_t(active.pages.size());
+  if (needed <= previous) return {};
+  std::vector<uint32_t> acquired;
+  if (const TokenAdmission admission = admitPages(uint32_t(needed) - previous, acquired); !admission.granted()) return admission;
+  active.pages.insert(active.pages.end(), acquired.begin(), acquired.end());
+  changed(active, previous);
+  return {};
+}
+
+PageTableView Cache::pageTable(uint64_t id) const {
+  const Request &active = request(id);
+  return {active.pages, active.revision, active.firstChanged};
+}
+
+void Cache::publishCommittedBlocks(uint64_t id, std::span<const uint32_t> exactTokens, uint32_t committedTokens) {
+  Request &active = request(id);
+  if (committedTokens > exactTokens.size()) throw std::invalid_argument("committed KV exceeds exact token history");
+  const uint32_t fullBlocks = committedTokens / kv::kPageTokens;
+  if ((uint64_t(committedTokens) + kv::kPageTokens - 1) / kv::kPageTokens > active.pages.size())
+    throw std::logic_error("committed KV has no physical request page");
+  if (fullBlocks < active.blocks.size()) throw std::logic_error("committed KV history moved backwards");
+  while (active.blocks.size() < fullBlocks) {
+    const uint32_t logical = uint32_t(active.blocks.size());
+    const uint64_t parent = logical ? active.blocks.back() : 0;
+    const uint32_t writerPage = active.pages[logical];
+    const PrefixIndex::Match placed = index_.insert(parent, exactTokens.subspan(size_t(logical) * kv::kPageTokens, kv::kPageTokens), writerPage);
+    const bool replace = placed.page != writerPage;
+    if (replace) pool_.retainPage(placed.page, false);
+    index_.retainActive(placed.id);
+    active.blocks.push_back(placed.id);
+    if (replace) { // identical content already lives on another page: move onto it
+      active.pages[logical] = placed.page;
+      changed(active, logical);
+      pool_.releasePage(writerPage, false);
+    }
+    if (parent) index_.releaseActive(parent);
+  }
+}
+
+std::vector<uint64_t> Cache::lookup(std::span<const uint32_t> prompt) {
+  std::vector<uint64_t> blocks;
+  if (prompt.empty()) return blocks;
+  const size_t maximum = (prompt.size() - 1) / kv::kPageTokens; // one real token stays to recompute
+  for (size_t i = 0; i < maximum; ++i) {
+    auto match = index_.find(blocks.empty() ? 0 : blocks.back(), prompt.subspan(i * kv::kPageTokens, kv::kPageTokens));
+    if (!match) break;
+    blocks.push_back(match->id);
+  }
+  if (!blocks.empty()) index_.touch(blocks.back());
+  return blocks;
+}
+
+TokenAdmission Cache::attachPrefix(uint64_t id, std::span<const uint64_t> blocks, uint32_t *resumeTokens) {
+  Request &active = request(id);
+  if (!active.pages.empty() || !active.blocks.empty()) throw std::logic_error("a prefix attaches to a request without pages");
+  if (resumeTokens) *resumeTokens = 0;
+  if (blocks.empty()) return {};
+  // Host-only blocks need fresh pages; take them all first so a refusal changes nothing.
+  uint32_t missing = 0;
+  for (uint64_t block : blocks) missing += index_.page(block) == PrefixIndex::noPage && !index_.transferring(block);
+  std::vector<uint32_t> fresh;
+  if (missing) {
+    if (!tier_) throw std::logic_error("host-only blocks need a tier");
+    if (const TokenAdmission admission = admitPages(missing, fresh); !admission.granted()) return admission;
+  }
+  size_t next = 0;
+  for (uint64_t block : blocks) { // root first: a parent is resident before its child adopts a page
+    uint32_t page = index_.page(block);
+    if (page == PrefixIndex::noPage) {
+      page = fresh[next++];
+      index_.adoptPage(block, page);
+      index_.setTransferring(block, true);
+      Transfer restore{block, page, nullptr, index_.slot(block)};
+      restore.ticket = tier_->canRestore() ? tier_->restore(restore.slot, page) : nullptr;
+      restores_.push_back(std::move(restore)); // a refused start is retried by pollTransfers
+      ++counters_.restores;
+      // the pool's acquisition gave the request an active reference already
+    } else {
+      pool_.retainPage(page, false);
+    }
+    active.pages.push_back(page);
+  }
+  active.blocks.assign(blocks.begin(), blocks.end());
+  index_.retainActive(blocks.back());
+  index_.touch(blocks.back());
+  changed(active, 0);
+  if (resumeTokens) *resumeTokens = uint32_t(blocks.size()) * kv::kPageTokens;
+  return {};
+}
+
+bool Cache::restoresPending(uint64_t id) const {
+  const Request &active = request(id);
+  for (uint64_t block : active.blocks)
+    if (index_.transferring(block) && index_.page(block) != PrefixIndex::noPage)
+      for (const Transfer &t : restores_)
+        if (t.block == block) return true;
+  return false;
+}
+
+uint32_t Cache::forkRequest(uint64_t parentId, uint64_t childId, uint32_t committedTokens) {
+  const Request &parent = request(parentId);
+  Request &child = request(childId);
+  if (!child.pages.empty()) throw std::logic_error("a fork target starts without pages");
+  const uint32_t fullPages = committedTokens / kv::kPageTokens;
+  const bool partial = committedTokens % kv::kPageTokens != 0;
+  if (fullPages + (partial ? 1u : 0u) > parent.pages.size()) throw std::logic_error("fork point lies past the parent's pages");
+  std::vector<uint32_t> own;
+  if (partial) {
+    const TokenAdmission admission = admitPages(1, own);
+    if (!admission.granted()) throw std::runtime_error("no page for the forked tail");
+  }
+  for (uint32_t i = 0; i < fullPages; ++i) { // full pages are immutable while shared
+    pool_.retainPage(parent.pages[i], false);
+    child.pages.push_back(parent.pages[i]);
+  }
+  const size_t cached = std::min<size_t>(parent.blocks.size(), fullPages);
+  child.blocks.assign(parent.blocks.begin(), parent.blocks.begin() + cached);
+  if (cached) index_.retainActive(child.blocks.back());
+  uint32_t copied = 0;
+  if (partial) { // both would append into this page: the child gets its own copy
+    const kv::PageCopy copy{parent.pages[fullPages], own[0]};
+    storage_.copyPages({&copy, 1});
+    child.pages.push_back(own[0]);
+    copied = 1;
+    ++counters_.forkCopies;
+  }
+  changed(child, 0);
+  return copied;
+}
+
+uint32_t Cache::truncate(uint64_t id, uint32_t committedTokens, uint32_t scratchTokens) {
+  Request &active = request(id);
+  const uint32_t keep = uint32_t((uint64_t(committedTokens) + scratchTokens + kv::kPageTokens - 1) / kv::kPageTokens);
+  if (keep >= active.pages.size()) return 0;
+  if (keep < active.blocks.size()) throw std::logic_error("published pages cannot be truncated");
+  const uint32_t released = uint32_t(active.pages.size()) - keep;
+  for (uint32_t i = keep; i < active.pages.size(); ++i) pool_.releasePage(active.pages[i], false);
+  active.pages.resize(keep);
+  changed(active, keep);
+  counters_.truncatedPages += released;
+  return released;
+}
+
+bool Cache::reclaimOne() {
+  const auto candidate = index_.evictionCandidate();
+  if (!candidate) return false;
+  const uint64_t block = candidate->block;
+  if (index_.slot(block)) { // a tier copy exists already: the page can go at once
+    index_.dropPage(block);
+    ++counters_.evictedBlocks;
+    return true;
+  }
+  if (tier_ && tier_->writable()) {
+    if (!tier_->canDemote()) return false; // the caller waits while transfers are in flight
+    std::shared_ptr<KvTierSlot> slot = tier_->acquireSlot();
+    if (slot) {
+      std::unique_ptr<KvTransfer> ticket = tier_->demote(index_.page(block), slot);
+      if (!ticket) return false;
+      index_.setTransferring(block, true);
+      demotions_.push_back({block, index_.page(block), std::move(ticket), std::move(slot)});
+      ++counters_.demotions;
+      return true;
+    }
+  }
+  index_.erase(block); // no tier (or its quota is full): the content is forgotten
+  ++counters_.evictedBlocks;
+  return true;
+}
+
+uint32_t Cache::reclaimForPages(uint32_t pages) {
+  uint32_t started = 0;
+  while (pool_.freePageCount() + pendingPages() < pages && reclaimOne()) ++started;
+  return started;
+}
+
+void Cache::pollTransfers() {
+  if (!tier_) return;
+  tier_->poll();
+  for (size_t i = 0; i < demotions_.size();) {
+    Transfer &t = demotions_[i];
+    if (!t.ticket->ready()) { ++i; continue; }
+    const bool landed = t.ticket->finish();
+    index_.setTransferring(t.block, false);
+    if (landed) {
+      index_.setSlot(t.block, t.slot);
+      if (index_.residentLeaf(t.block)) { index_.dropPage(t.block); ++counters_.evictedBlocks; }
+    } else {
+      ++counters_.failedTransfers; // the page stays: a failed demotion loses nothing
+    }
+    demotions_.erase(demotions_.begin() + long(i));
+  }
+  for (size_t i = 0; i < restores_.size();) {
+    Transfer &t = restores_[i];
+    if (!t.ticket) { // not started yet: the tier took no more restores then
+      if (tier_->canRestore()) t.ticket = tier_->restore(t.slot, t.page);
+      ++i;
+      continue;
+    }
+    if (!t.ticket->ready()) { ++i; continue; }
+    const bool landed = t.ticket->finish();
+    index_.setTransferring(t.block, false);
+    if (!landed) {
+      ++counters_.failedTransfers;
+      index_.poison(t.block); // it matches nothing any more; its users recompute
+    }
+    restores_.erase(restores_.begin() + long(i));
+  }
+}
+
+bool Cache::compactExtent() {
+  std::vector<uint32_t> fixed; // pages a transfer reads or writes in place stay where they are
+  for (const Transfer &t : demotions_) fixed.push_back(t.page);
+  for (const Transfer &t : restores_) fixed.push_back(t.page);
+  const KvPageMoves moves = pool_.compactExtent(fixed);
+  if (moves.empty()) return false;
+  index_.followPages(moves);
+  for (auto &[id, active] : requests_) {
+    uint32_t first = uint32_t(active.pages.size());
+    for (uint32_t i = 0; i < active.pages.size(); ++i) {
+      const uint32_t to = moves.follow(active.pages[i]);
+      if (to != active.pages[i]) { active.pages[i] = to; first = std::min(first, i); }
+    }
+    if (first < active.pages.size()) changed(active, first);
+  }
+  return true;
+}
+
+CacheSnapshot Cache::snapshot() const {
+  CacheSnapshot result = counters_;
+  result.requests = uint32_t(requests_.size());
+  result.residentBlocks = index_.residentBlocks();
+  result.tierBlocks = index_.tierBlocks();
+  result.transfers = uint32_t(demotions_.size() + restores_.size());
+  return result;
+}
+
+} // namespace rkb::engine

@@ -117,7 +117,10 @@ KvPageAcquisition KvPool::acquirePages(uint32_t count) {
     }
     uint32_t grow = 0;
     while (grow < extents_.size() && extents_[grow].allocated) ++grow; // the lowest unallocated extent
-    if (grow == extents_.size()) throw std::logic_error("KV page ids ran out before the memory budget did");
+    if (grow == extents_.size()) { // the budget must refuse growth before the page ids run out
+      for (auto page = taken.rbegin(); page != taken.rend(); ++page) listFree(*page);
+      throw std::logic_error("KV page ids ran out before the memory budget did");
+    }
     const AllocationResult granted = growBy(grow);
     if (!granted) {
       // Everything popped goes back in reverse; extents allocated on the way stay, reclaimable.

@@ -1,0 +1,171 @@
+"""Python handles over the host control plane (include/richkv_host.h): the page allocator
+(engine::KvPool), the request / prefix cache with its eviction tier (engine::Cache subset) and the
+operator plans (ops::PagedAttention). The objects live in C++ (richengine_b200/csrc/host)."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import lib
+
+GRANTED, DENIED, PENDING = 0, 1, 2
+NO_PAGE = 0xFFFFFFFF
+
+
+class KvPool:
+    def __init__(self, *, pages=None, bytes_per_page=None, extent_pages=None, runway_pages=0, budget_pages=2 ** 62,
+                 storage=None, stream=None):
+        self._lib = lib.load()
+        if storage is not None:
+            self._handle = self._lib.rk_pool_create_device(storage.handle, runway_pages, stream)
+            self.extent_pages = storage.extent_pages
+        else:
+            self._handle = self._lib.rk_pool_create_budget(pages, bytes_per_page, extent_pages, runway_pages, budget_pages)
+            self.extent_pages = extent_pages
+        if not self._handle:
+            raise ValueError(self._lib.rk_last_error().decode())
+
+    @property
+    def handle(self):
+        return self._handle
+
+    def close(self):
+        if self._handle:
+            self._lib.rk_pool_destroy(self._handle)
+            self._handle = None
+
+    def set_budget(self, pages: int):
+        self._lib.rk_pool_set_budget(self._handle, pages)
+
+    def acquire(self, count: int):
+        """The acquired page ids, or None when the pool could not grow."""
+        out = (C.c_uint32 * max(count, 1))()
+        got = self._lib.rk_pool_acquire(self._handle, count, out)
+        if got == lib.REFUSED:
+            return None
+        lib.check(got, "rk_pool_acquire")
+        return list(out[:got])
+
+    def retain(self, page: int, prefix_owner=False):
+        status = self._lib.rk_pool_retain(self._handle, page, int(prefix_owner))
+        if status:
+            raise RuntimeError(self._lib.rk_last_error().decode())
+
+    def release(self, page: int, prefix_owner=False):
+        status = self._lib.rk_pool_release(self._handle, page, int(prefix_owner))
+        if status:
+            raise RuntimeError(self._lib.rk_last_error().decode())
+
+    def reclaim_empty_extents(self, keep_runway: bool, limit: int) -> int:
+        return self._lib.rk_pool_reclaim_empty_extents(self._handle, int(keep_runway), limit)
+
+    def compact_extent(self, fixed=()):
+        fixed = np.ascontiguousarray(fixed, dtype=np.uint32)
+        out = (C.c_uint32 * self.extent_pages)()
+        first = self._lib.rk_pool_compact_extent(self._handle, fixed.ctypes.data, len(fixed), out)
+        return None if first < 0 else (first, list(out))
+
+    def snapshot(self) -> dict:
+        out = (C.c_uint64 * 10)()
+        self._lib.rk_pool_snapshot(self._handle, out)
+        names = ["pages_allocated", "pages_free", "pages_active", "pages_prefix", "allocated_bytes", "reclaimable_bytes",
+                 "extent_allocations", "extent_releases", "extent_compactions", "pages_moved"]
+        return dict(zip(names, out))
+
+    def page_content(self, page): return self._lib.rk_pool_page_content(self._handle, page)
+    def set_page_content(self, page, tag): self._lib.rk_pool_set_page_content(self._handle, page, tag)
+
+
+class Cache:
+    NO_TIER, HOST_TIER, MANUAL_TIER = 0, 1, 2
+
+    def __init__(self, pool: KvPool, tier_mode=0, slots=0, transfers=0):
+        self._lib = lib.load()
+        self.pool = pool
+        self._handle = self._lib.rk_cache_create(pool.handle, tier_mode, slots, transfers)
+        if not self._handle:
+            raise ValueError(self._lib.rk_last_error().decode())
+
+    def close(self):
+        if self._handle:
+            self._lib.rk_cache_destroy(self._handle)
+            self._handle = None
+
+    def _check(self, status, where):
+        if status < 0:
+            raise RuntimeError(f"{where}: {self._lib.rk_last_error().decode()}")
+        return status
+
+    def begin_request(self, request): self._check(self._lib.rk_cache_begin_request(self._handle, request), "begin_request")
+    def end_request(self, request): self._check(self._lib.rk_cache_end_request(self._handle, request), "end_request")
+    def ensure_tokens(self, request, tokens) -> int: return self._check(self._lib.rk_cache_ensure_tokens(self._handle, request, tokens), "ensure_tokens")
+
+    def page_table(self, request):
+        revision, first = C.c_uint64(), C.c_uint32()
+        count = self._check(self._lib.rk_cache_page_table(self._handle, request, None, 0, C.byref(revision), C.byref(first)), "page_table")
+        out = (C.c_uint32 * max(count, 1))()
+        self._lib.rk_cache_page_table(self._handle, request, out, count, None, None)
+        return list(out[:count]), revision.value, first.value
+
+    def publish(self, request, tokens, committed):
+        t = np.ascontiguousarray(tokens, dtype=np.uint32)
+        self._check(self._lib.rk_cache_publish(self._handle, request, t.ctypes.data, len(t), committed), "publish")
+
+    def lookup(self, prompt):
+        t = np.ascontiguousarray(prompt, dtype=np.uint32)
+        out = (C.c_uint64 * (len(t) // 32 + 1))()
+        count = self._check(self._lib.rk_cache_lookup(self._handle, t.ctypes.data, len(t), out, len(out)), "lookup")
+        return list(out[:count])
+
+    def attach_prefix(self, request, blocks):
+        b = (C.c_uint64 * max(len(blocks), 1))(*blocks)
+        resume = C.c_uint32()
+        status = self._check(self._lib.rk_cache_attach_prefix(self._handle, request, b, len(blocks), C.byref(resume)), "attach_prefix")
+        return status, resume.value
+
+    def restores_pending(self, request) -> bool: return bool(self._check(self._lib.rk_cache_restores_pending(self._handle, request), "restores_pending"))
+    def fork(self, parent, child, committed) -> int: return self._check(self._lib.rk_cache_fork(self._handle, parent, child, committed), "fork")
+    def truncate(self, request, committed, scratch) -> int: return self._check(self._lib.rk_cache_truncate(self._handle, request, committed, scratch), "truncate")
+    def reclaim_one(self) -> bool: return bool(self._check(self._lib.rk_cache_reclaim_one(self._handle), "reclaim_one"))
+    def reclaim_for_pages(self, pages) -> int: return self._lib.rk_cache_reclaim_for_pages(self._handle, pages)
+    def poll_transfers(self): self._lib.rk_cache_poll_transfers(self._handle)
+    def compact_extent(self) -> bool: return bool(self._check(self._lib.rk_cache_compact_extent(self._handle), "compact_extent"))
+    def complete_transfer(self, success=True) -> bool: return bool(self._lib.rk_cache_complete_transfer(self._handle, int(success)))
+    def fail_next_transfers(self, count): self._lib.rk_cache_fail_next_transfers(self._handle, count)
+
+    def snapshot(self) -> dict:
+        out = (C.c_uint64 * 10)()
+        self._lib.rk_cache_snapshot(self._handle, out)
+        names = ["requests", "resident_blocks", "tier_blocks", "transfers", "demotions", "restores", "failed_transfers",
+                 "evicted_blocks", "fork_copies", "truncated_pages"]
+        return dict(zip(names, out))
+
+    def block_state(self, block):
+        out = (C.c_uint64 * 4)()
+        if self._lib.rk_cache_block_state(self._handle, block, out) < 0:
+            return None
+        return {"page": out[0], "tier_copy": bool(out[1]), "transferring": bool(out[2]), "last_used": out[3]}
+
+
+def verify_plan(lanes, query_heads, layout, history, tree=False, row_capacity=0):
+    library = lib.load()
+    names = C.create_string_buffer(512)
+    out = (C.c_uint64 * 16)()
+    h = (C.c_uint32 * lanes)(*history)
+    status = library.rk_plan_verify(lanes, query_heads, layout.attention_layers, layout.kv_heads, layout.head_dimension,
+                                    layout.format, h, int(tree), row_capacity, names, 512, out)
+    if status:
+        raise ValueError(library.rk_last_error().decode())
+    return names.value.decode().split("\n"), list(out[:14])
+
+
+def prefill_plan(rows, query_heads, layout):
+    library = lib.load()
+    names = C.create_string_buffer(512)
+    out = (C.c_uint64 * 16)()
+    status = library.rk_plan_prefill(rows, query_heads, layout.attention_layers, layout.kv_heads, layout.head_dimension,
+                                     layout.format, names, 512, out)
+    if status:
+        raise ValueError(library.rk_last_error().decode())
+    return names.value.decode().split("\n"), list(out[:10])

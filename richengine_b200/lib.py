@@ -112,6 +112,43 @@ SIGNATURES = {
     "rk_tier_transfer_ready": (i32, [vp, u32]),
     "rk_tier_transfer_finish": (i32, [vp, u32]),
     "rk_tier_drain": (i32, [vp]),
+    # host control plane (include/richkv_host.h)
+    "rk_pool_create_budget": (vp, [u32, u64, u32, u32, u64]),
+    "rk_pool_create_device": (vp, [vp, u32, vp]),
+    "rk_pool_destroy": (None, [vp]),
+    "rk_pool_set_budget": (None, [vp, u64]),
+    "rk_pool_acquire": (i32, [vp, u32, vp]),
+    "rk_pool_retain": (i32, [vp, u32, i32]),
+    "rk_pool_release": (i32, [vp, u32, i32]),
+    "rk_pool_reclaim_empty_extents": (u64, [vp, i32, u32]),
+    "rk_pool_compact_extent": (i64, [vp, vp, u32, vp]),
+    "rk_pool_snapshot": (None, [vp, vp]),
+    "rk_pool_page_content": (u64, [vp, u32]),
+    "rk_pool_set_page_content": (None, [vp, u32, u64]),
+    "rk_cache_create": (vp, [vp, i32, u32, u32]),
+    "rk_cache_destroy": (None, [vp]),
+    "rk_cache_begin_request": (i32, [vp, u64]),
+    "rk_cache_end_request": (i32, [vp, u64]),
+    "rk_cache_ensure_tokens": (i32, [vp, u64, u64]),
+    "rk_cache_page_table": (i64, [vp, u64, vp, u32, C.POINTER(u64), C.POINTER(u32)]),
+    "rk_cache_publish": (i32, [vp, u64, vp, u32, u32]),
+    "rk_cache_lookup": (i64, [vp, vp, u32, vp, u32]),
+    "rk_cache_attach_prefix": (i32, [vp, u64, vp, u32, C.POINTER(u32)]),
+    "rk_cache_restores_pending": (i32, [vp, u64]),
+    "rk_cache_fork": (i32, [vp, u64, u64, u32]),
+    "rk_cache_truncate": (i64, [vp, u64, u32, u32]),
+    "rk_cache_reclaim_one": (i32, [vp]),
+    "rk_cache_reclaim_for_pages": (u32, [vp, u32]),
+    "rk_cache_poll_transfers": (None, [vp]),
+    "rk_cache_compact_extent": (i32, [vp]),
+    "rk_cache_complete_transfer": (i32, [vp, i32]),
+    "rk_cache_fail_next_transfers": (None, [vp, u32]),
+    "rk_cache_snapshot": (None, [vp, vp]),
+    "rk_cache_block_state": (i32, [vp, u64, vp]),
+    "rk_plan_verify": (i32, [u32, u32, u32, u32, u32, u32, vp, i32, u32, C.c_char_p, C.c_size_t, vp]),
+    "rk_plan_prefill": (i32, [u32, u32, u32, u32, u32, u32, C.c_char_p, C.c_size_t, vp]),
+    "rk_plan_workspaces": (i32, [u32, u32, u32, u32, u32, u32, u32, vp]),
+    "rk_chunk_validation_error": (C.c_char_p, [u32, u32, u32, u32]),
 }
 
 _library = None

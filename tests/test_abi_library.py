@@ -12,7 +12,7 @@ ROOT = Path(__file__).resolve().parent.parent
 
 
 def declared_symbols():
-    text = (ROOT / "include" / "richkv.h").read_text()
+    text = (ROOT / "include" / "richkv.h").read_text() + (ROOT / "include" / "richkv_host.h").read_text()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(rk_[a-z0-9_]+)\s*\(", text)))
 
