@@ -123,9 +123,12 @@ def test_evict_cold_pages_to_pinned_host_and_refetch():
     assert snap["tier_blocks"] == 2 and snap["resident_blocks"] == 6 and w.pool.snapshot()["pages_prefix"] == 6
     # scribble over the freed pages so a restore cannot pass by leftovers
     taken = w.pool.acquire(w.pool.snapshot()["pages_free"])
-    for extent in range(1):
-        raw = w.storage.read_extent(extent)
+    junk = torch.full((w.storage.bytes_per_page(),), 0x5A, dtype=torch.uint8, device="cuda")
     for p in taken:
+        ids32 = np.array([p], dtype=np.uint32)
+        lib.check(lib.load().rk_storage_pack_pages(w.storage.handle, ids32.ctypes.data, 1, junk.data_ptr(), 1, None), "unpack")
+    torch.cuda.synchronize()
+    for p in reversed(taken):
         w.pool.release(p)
     chain = w.cache.lookup(ids)
     assert len(chain) == 8
@@ -140,11 +143,14 @@ def test_evict_cold_pages_to_pinned_host_and_refetch():
         assert np.array_equal(w.device_page(p), content[i]), i
     # a failed demotion loses nothing: the page stays resident and matchable
     w.cache.end_request(2)
+    assert w.cache.reclaim_one() and w.cache.reclaim_one()  # both leaves still have their host copies: dropped at once
+    assert w.cache.snapshot()["transfers"] == 0 and w.pool.snapshot()["pages_prefix"] == 6
     w.cache.fail_next_transfers(1)
-    assert w.cache.reclaim_one()
+    assert w.cache.reclaim_one()                             # the next leaf has no copy yet: a demotion, which fails
     while w.cache.snapshot()["transfers"]:
         w.cache.poll_transfers()
-    assert w.cache.snapshot()["failed_transfers"] == 1 and len(w.cache.lookup(ids)) == 8
+    assert w.cache.snapshot()["failed_transfers"] == 1 and w.pool.snapshot()["pages_prefix"] == 6
+    assert len(w.cache.lookup(ids)) == 8
     w.close()
 
 
