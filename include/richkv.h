@@ -92,6 +92,17 @@ int rk_attention_decode(const void *window, const rk_decode_plan *plan, uint32_t
                         void *output, float *output_f32, float *partials, float *statistics,
                         uint32_t *descriptors, const rk_page_entry *const *tables,
                         const rk_verify_params *lane_params, rk_kv_layer layer, void *stream);
+/* Sequence split of one long context over several GPUs (new here; the reference is single-GPU, its
+ * split merge paged_attention_tile.h:362-404 is the combine). Each rank attends the pages it holds and
+ * leaves {max, sum, un-normalised output} per (lane, query head) in `triples`
+ * ([lane][query_head][2 + D] fp32); after an all-gather every rank merges the shards in rank order. */
+int rk_attention_decode_shard(const void *window, const rk_decode_plan *plan, uint32_t format, const void *queries,
+                              float *triples, float *partials, float *statistics, uint32_t *descriptors,
+                              const rk_page_entry *const *tables, const rk_verify_params *lane_params,
+                              rk_kv_layer layer, void *stream);
+int rk_attention_merge_shards(uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim, uint32_t lanes,
+                              uint32_t shards, const float *triples, void *output, float *output_f32,
+                              void *stream);
 /* No counterpart in the reference. rk_attention_decode for callers that cannot allocate device
  * memory (the pool owns the whole device, the calling thread may not enter the allocator, or
  * allocation calls are not permitted where it runs): the step's scratch is a fixed array inside

@@ -581,10 +581,10 @@ __global__ void __launch_bounds__(256)
 decode_reduce_kernel(const float *__restrict__ partials, const float *__restrict__ statistics,
                      const uint32_t *__restrict__ descriptors, uint16_t *__restrict__ output,
                      float *__restrict__ output_f32, const rk_verify_params *__restrict__ lane_params,
-                     rk_kv_layer layer) {
+                     rk_kv_layer layer, float *__restrict__ shard_out) {
   constexpr uint32_t kMaxSlots = 64;
   __shared__ float weights[kMaxSlots];
-  __shared__ float denominator_shared;
+  __shared__ float denominator_shared, maximum_shared;
   const uint32_t query_head = blockIdx.x, head = blockIdx.y, l = blockIdx.z, tid = threadIdx.x;
   rk_verify_params p = lane_params[l];
   p.kv = layer;
@@ -603,6 +603,7 @@ decode_reduce_kernel(const float *__restrict__ partials, const float *__restrict
       for (uint32_t t = tid; t < slots; t += 32)
         maximum = fmaxf(maximum, statistics[(slot_of(t) * kGroup + query_head) * 2]);
       maximum = warp_max(maximum);
+      if (tid == 0) maximum_shared = maximum;
       for (uint32_t t = tid; t < count; t += 32) {
         const float own = statistics[(slot_of(base + t) * kGroup + query_head) * 2];
         weights[t] = own == -INFINITY ? 0.0f : expf(own - maximum);
@@ -621,9 +622,42 @@ decode_reduce_kernel(const float *__restrict__ partials, const float *__restrict
     __syncthreads();
   }
   const float denominator = denominator_shared;
+  if (shard_out) { // this rank's piece of a sequence split: {max, sum, un-normalised output} per query head
+    float *triple = shard_out + ((uint64_t(l) * kKvHeads + head) * kGroup + query_head) * (kHeadDim + 2);
+    if (tid == 0) { triple[0] = maximum_shared; triple[1] = denominator; }
+    triple[2 + tid] = numerator;
+    return;
+  }
   const float value = denominator > 0.0f ? numerator / denominator : 0.0f;
   output[tile + query_head * kHeadDim + tid] = float_to_bf16_bits(value);
   if (output_f32) output_f32[tile + query_head * kHeadDim + tid] = value;
+}
+
+// Combine the shards of a sequence split: shard r holds {max, sum, un-normalised output} per
+// (lane, query head); the merge of the split kernel (paged_attention_tile.h:362-404) with
+// "split" = rank, in rank order, so every rank computes identical bits.
+// grid (query_heads, lanes), 256 threads.
+__global__ void __launch_bounds__(256)
+merge_shards_kernel(const float *__restrict__ triples, uint32_t shards, uint32_t lanes, uint16_t *__restrict__ output,
+                    float *__restrict__ output_f32) {
+  const uint32_t query_head = blockIdx.x, l = blockIdx.y, tid = threadIdx.x;
+  constexpr uint32_t kQueryHeads = kKvHeads * kGroup, kTriple = kHeadDim + 2;
+  const uint64_t stride = uint64_t(lanes) * kQueryHeads * kTriple;
+  const float *mine = triples + (uint64_t(l) * kQueryHeads + query_head) * kTriple;
+  float maximum = -INFINITY;
+  for (uint32_t r = 0; r < shards; ++r) maximum = fmaxf(maximum, mine[r * stride]);
+  float numerator = 0.0f, denominator = 0.0f;
+  for (uint32_t r = 0; r < shards; ++r) {
+    const float own = mine[r * stride];
+    const float weight = own == -INFINITY ? 0.0f : expf(own - maximum);
+    numerator += weight * mine[r * stride + 2 + tid];
+    denominator += weight * mine[r * stride + 1];
+  }
+  const float value = denominator > 0.0f ? numerator / denominator : 0.0f;
+  const uint32_t head = query_head / kGroup, g = query_head % kGroup;
+  const uint64_t at = ((uint64_t(l) * kKvHeads + head) * RK_VERIFY_CHUNK_STRIDE) * kGroup * kHeadDim + g * kHeadDim + tid;
+  output[at] = float_to_bf16_bits(value);
+  if (output_f32) output_f32[at] = value;
 }
 
 constexpr size_t kDecodeSharedBytes = 1024 + kStages * kStageBytes + sizeof(Shared);
@@ -709,8 +743,41 @@ int rk_attention_decode(const void *window, const rk_decode_plan *plan, uint32_t
   if (int st = cuda_status(cudaMemsetAsync(descriptors + 2 * plan->lanes, 0, sizeof(uint32_t), s), "decode status clear")) return st;
   decode_int4_kernel<<<plan->ctas, kThreads, shared_bytes, s>>>(w->int4_map, args);
   if (int st = cuda_status(cudaGetLastError(), "decode launch")) return st;
-  decode_reduce_kernel<<<dim3(kGroup, kKvHeads, plan->lanes), 256, 0, s>>>(partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer);
+  decode_reduce_kernel<<<dim3(kGroup, kKvHeads, plan->lanes), 256, 0, s>>>(partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer, nullptr);
   return cuda_status(cudaGetLastError(), "decode reduce launch");
+}
+
+// One rank's part of a sequence-split decode: attention over the pages this rank holds, left as
+// {max, sum, un-normalised output} per (lane, query head) in `triples`
+// ([lane][query_head][2 + D] fp32, 24 768 bytes per lane at 24 x 256) for an all-gather.
+int rk_attention_decode_shard(const void *window, const rk_decode_plan *plan, uint32_t format, const void *queries,
+                              float *triples, float *partials, float *statistics, uint32_t *descriptors,
+                              const rk_page_entry *const *tables, const rk_verify_params *lane_params,
+                              rk_kv_layer layer, void *stream) {
+  const auto *w = static_cast<const Window *>(window);
+  if (!w || !plan || !queries || !triples || !partials || !statistics || !descriptors || !tables || !lane_params ||
+      !layer.extent_pages || format != RK_FORMAT_INT4) {
+    set_error("rk_attention_decode_shard: invalid arguments");
+    return kInvalid;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (int st = configure_decode_kernel()) return st;
+  DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, plan->lanes};
+  if (int st = cuda_status(cudaMemsetAsync(descriptors + 2 * plan->lanes, 0, sizeof(uint32_t), s), "decode status clear")) return st;
+  decode_int4_kernel<<<plan->ctas, kThreads, kDecodeSharedBytes, s>>>(w->int4_map, args);
+  if (int st = cuda_status(cudaGetLastError(), "decode launch")) return st;
+  decode_reduce_kernel<<<dim3(kGroup, kKvHeads, plan->lanes), 256, 0, s>>>(partials, statistics, descriptors, nullptr, nullptr, lane_params, layer, triples);
+  return cuda_status(cudaGetLastError(), "decode shard reduce launch");
+}
+
+// Merges `shards` gathered triples ([shard][lane][query_head][2 + D]) in shard order into the bf16
+// output [lane][kv_head][32][group][D] (row 0) and optionally the fp32 value before rounding.
+int rk_attention_merge_shards(uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim, uint32_t lanes, uint32_t shards,
+                              const float *triples, void *output, float *output_f32, void *stream) {
+  if (kv_heads != kKvHeads || query_heads != kKvHeads * kGroup || head_dim != kHeadDim) return kUnsupported;
+  if (!lanes || !shards || !triples || !output) { set_error("rk_attention_merge_shards: invalid arguments"); return kInvalid; }
+  merge_shards_kernel<<<dim3(query_heads, lanes), 256, 0, static_cast<cudaStream_t>(stream)>>>(triples, shards, lanes, static_cast<uint16_t *>(output), output_f32);
+  return cuda_status(cudaGetLastError(), "merge shards launch");
 }
 
 // ---- decode attention without any allocation -----------------------------------------------------
@@ -768,7 +835,7 @@ int rk_attention_decode_static(const void *window, uint32_t format, uint32_t lan
   if (int st = cuda_status(cudaMemsetAsync(descriptors + 2 * lanes, 0, sizeof(uint32_t), s), "decode status clear")) return st;
   decode_int4_kernel<<<kStaticCtas, kThreads, kDecodeSharedBytes, s>>>(w->int4_map, args);
   if (int st = cuda_status(cudaGetLastError(), "decode launch")) return st;
-  decode_reduce_kernel<<<dim3(kGroup, kKvHeads, lanes), 256, 0, s>>>(partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer);
+  decode_reduce_kernel<<<dim3(kGroup, kKvHeads, lanes), 256, 0, s>>>(partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer, nullptr);
   return cuda_status(cudaGetLastError(), "decode reduce launch");
 }
 

@@ -71,6 +71,8 @@ SIGNATURES = {
     "rk_window_create": (vp, [u64, u64]),
     "rk_window_destroy": (None, [vp]),
     "rk_attention_decode": (i32, [vp, C.POINTER(DecodePlan), u32, vp, vp, vp, vp, vp, vp, vp, vp, KvLayer, vp]),
+    "rk_attention_decode_shard": (i32, [vp, C.POINTER(DecodePlan), u32, vp, vp, vp, vp, vp, vp, vp, KvLayer, vp]),
+    "rk_attention_merge_shards": (i32, [u32, u32, u32, u32, u32, vp, vp, vp, vp]),
     "rk_attention_decode_static": (i32, [vp, u32, u32, vp, vp, vp, vp, vp, KvLayer, vp]),
     "rk_attention_decode_status": (i32, [C.POINTER(DecodePlan), vp, vp]),
     "rk_stage_decode_rows": (i32, [u32, u32, u32, u32, vp, vp, vp, vp, vp, vp, vp]),

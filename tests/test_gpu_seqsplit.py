@@ -1,0 +1,55 @@
+"""GPU: sequence-split decode on one GPU — the shards of one long context run one after another
+(each over its own slice of the page table), their triples are stacked as an all-gather would, and the
+rank-order merge equals the checker's attention over the whole sequence and the unsplit kernel."""
+import numpy as np
+import pytest
+import torch
+
+import oracle as om
+from gpuhelp import (assert_attention_close, chunk_params, dev, host_u16, run_decode_attention_gpu,
+                     run_verify_attention_oracle, struct_to_device)
+from kvcase import Scenario, fill_history_with_store, make_queries, make_staging
+from richengine_b200 import lib, ops, parallel
+from richengine_b200.abi import INT4, Layout
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("context,ranks", [(5000, 2), (5000, 4), (40, 8), (1023, 3)])
+def test_sequence_split_matches_whole_sequence(context, ranks):
+    layout = Layout(1, 4, 256, INT4)
+    s = Scenario(layout, [context], extra_tokens=1, device=True, seed=5)
+    fill_history_with_store(s, 0, seed=5)
+    rng = np.random.default_rng(9)
+    k, v = make_staging(rng, 1, layout)
+    params = chunk_params(s, 1)
+    assert om.oracle().rko_store_verify(INT4, 4, 256, 1, k.ctypes.data, v.ctypes.data, s.host_table_pointers(), params) == 0
+    s.upload()
+    q = make_queries(rng, 1, layout)
+    visible = context + 1
+    dq = dev(q)
+    decoder = parallel.SequenceSplitDecoder(layout, 24, 1, s.storage.window())
+    shards = []
+    for r in range(ranks):
+        first, last = parallel.shard_page_range(len(s.pages[0]), r, ranks)
+        begin, count = parallel.shard_tokens(visible, r, ranks)
+        if count == 0:  # a rank without pages contributes an empty triple
+            empty = torch.zeros((1, 24, 258), dtype=torch.float32, device="cuda")
+            empty[:, :, 0] = float("-inf")
+            shards.append(empty)
+            continue
+        table = s.device_tables[0][first:last].contiguous()
+        pointers = ops.table_pointer_array([table])
+        lane = (lib.VerifyParams * 1)(lib.VerifyParams(count - 1, last - first, s.storage.layers()[0], 1, 1, 1, 1, 0.0))
+        shards.append(decoder.shard(dq, pointers, struct_to_device(lane), s.storage.layers()[0]).clone())
+        decoder.inner.status()
+    gathered = torch.stack(shards).contiguous()
+    out = torch.zeros_like(dq)
+    out32 = torch.zeros(dq.shape, dtype=torch.float32, device="cuda")
+    decoder.merge(gathered, out, out32)
+    torch.cuda.synchronize()
+    _, want32 = run_verify_attention_oracle(s, q, 1, 1)
+    assert_attention_close(out32.cpu().numpy(), want32, host_u16(out), f"seqsplit {ranks}")
+    _, whole32 = run_decode_attention_gpu(s, q)
+    assert_attention_close(out32.cpu().numpy(), whole32, None, "split vs whole")
+    decoder.close(); s.close()
