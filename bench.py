@@ -53,6 +53,9 @@ def parse():
     ap.add_argument("--layers", type=int, default=16)
     ap.add_argument("--ragged", action="store_true", help="contexts uniform in [context/4, context]")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--mode", default="requests", choices=["requests", "seqsplit"],
+                    help="requests: every rank runs its own batch (default); seqsplit: ONE sequence of --context "
+                         "tokens split along the sequence over the ranks, all-gather of (max, sum, O), rank-order merge")
     return ap.parse_args()
 
 
@@ -412,10 +415,95 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_seqsplit(args):
+    """One long int4 sequence split along the sequence over the ranks (strong scaling): per layer each rank
+    attends its pages, the triples are all-gathered over NCCL and merged in rank order."""
+    import torch
+    import torch.distributed as dist
+
+    from richengine_b200 import lib, ops, parallel
+    from richengine_b200.abi import INT4, Layout, pages_for
+    from richengine_b200.storage import PageStorage
+
+    rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local)) if world > 1 else dist.init_process_group(
+        "nccl", init_method="tcp://127.0.0.1:29533", rank=0, world_size=1, device_id=torch.device("cuda", local))
+    layout = Layout(args.layers, KV_HEADS, HEAD_DIM, INT4)
+    visible = args.context + 1
+    begin, count = parallel.shard_tokens(visible, rank, world)
+    first, last = parallel.shard_page_range(pages_for(visible), rank, world)
+    local_pages = max(last - first, 1)
+    extent_pages = layout.minimum_extent_pages()
+    extents = (local_pages + extent_pages - 1) // extent_pages
+    storage = PageStorage(layout, extents * extent_pages, extent_pages)
+    for extent in range(extents):
+        assert storage.allocate_extent(extent)
+    order = np.random.default_rng(3 + rank).permutation(extents * extent_pages)[:local_pages]
+    table = torch.zeros(local_pages, dtype=torch.int64, device="cuda")
+    storage.write_entries(order, 0, table)
+    pointers = ops.table_pointer_array([table])
+    generator = torch.Generator(device="cuda").manual_seed(11 + rank)
+    k = torch.randn((KV_HEADS, 2048, HEAD_DIM), generator=generator, device="cuda").to(torch.bfloat16)
+    v = torch.randn((KV_HEADS, HEAD_DIM, 2048), generator=generator, device="cuda").to(torch.bfloat16)
+    done = 0
+    while done < count:
+        rows = min(2048, count - done)
+        for layer in range(args.layers):
+            ops.store_chunk(layout, k, v, table, lib.ChunkParams(done, rows, 2048, local_pages, storage.layers()[layer]))
+        done += rows
+    decoder = parallel.SequenceSplitDecoder(layout, QUERY_HEADS, 1, storage.window())
+    queries = torch.randn((1, KV_HEADS, 32, QUERY_HEADS // KV_HEADS, HEAD_DIM), generator=generator, device="cuda").to(torch.bfloat16)
+    if world > 1:
+        dist.broadcast(queries, 0)  # every rank attends with the same query
+    output = torch.zeros_like(queries)
+    lane = np.zeros(1, dtype=ops.VERIFY_PARAMS)
+    lane[0] = (max(count, 1) - 1, local_pages, (extent_pages, 0), 1, 1, 1, 1, 0.0)
+    params = ops.params_to_device(lane)
+    places = storage.layers()
+
+    def step():
+        for layer in range(args.layers):
+            decoder.step(queries, output, pointers, params, places[layer])
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        step()
+    stop.record()
+    torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
+    decoder.inner.status()
+    elapsed = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64, device="cuda")
+    dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+    check = output.float().sum().reshape(1).double()
+    sums = [torch.zeros_like(check) for _ in range(world)]
+    dist.all_gather(sums, check)
+    if rank == 0:
+        total_bytes = visible * layout.bytes_per_token_layer() * args.layers * args.steps
+        ms = float(elapsed.item())
+        print(json.dumps({
+            "metric": METRIC, "value": round(total_bytes / (ms * 1e-3) / 1e9, 1), "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "int4 codes, fp16 tensor operands, fp32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": f"one int4 sequence of {args.context} tokens split along the sequence over {world} GPU(s), "
+                                   f"{args.layers} layers, all-gather of (max, sum, O) = {QUERY_HEADS * (HEAD_DIM + 2) * 4} B per rank per layer",
+                       "us_per_layer_step": round(ms / args.steps / args.layers * 1e3, 2),
+                       "ranks_agree": bool(all(float(x) == float(sums[0]) for x in sums))},
+        }), flush=True)
+    decoder.close()
+    dist.destroy_process_group()
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         run_reference(args)
+    elif args.mode == "seqsplit":
+        run_seqsplit(args)
     else:
         run_ours(args)
 
