@@ -61,6 +61,18 @@ def attention_verify_split(layout: Layout, query_heads: int, lanes: int, row_cap
     lib.check(status, "rk_attention_verify_split")
 
 
+def attention_verify_split_tc(layout: Layout, query_heads: int, lanes: int, row_capacity: int, grid_splits: int,
+                              queries, partials, statistics, table_pointers, row_masks, params, layer: lib.KvLayer,
+                              status_word, stream=None) -> None:
+    """8/16-row int4 windows on the tcgen05 kernel; `status_word` is a zeroed int32 device tensor."""
+    status = lib.load().rk_attention_verify_split_tc(
+        layout.format, layout.kv_heads, query_heads, layout.head_dimension, lanes, row_capacity, grid_splits,
+        queries.data_ptr(), partials.data_ptr(), statistics.data_ptr(), table_pointers.data_ptr(),
+        row_masks.data_ptr() if row_masks is not None else None, params.data_ptr(), layer, status_word.data_ptr(),
+        _stream(stream))
+    lib.check(status, "rk_attention_verify_split_tc")
+
+
 def attention_verify_reduce(layout: Layout, query_heads: int, lanes: int, row_capacity: int, partials, statistics,
                             output, params, output_f32=None, stream=None) -> None:
     status = lib.load().rk_attention_verify_reduce(

@@ -55,8 +55,8 @@ def struct_to_device(array) -> torch.Tensor:
 
 
 def run_verify_attention_gpu(scenario: Scenario, queries: np.ndarray, active_rows, row_capacity, row_masks=None,
-                             splits=None, layer_index=0, committed=None):
-    """General tile path: split + reduce. Returns (bf16 bits, fp32) outputs [lane][H][32][G][D]."""
+                             splits=None, layer_index=0, committed=None, tensor_core=False):
+    """Split + reduce (general tile, or the tcgen05 split). Returns (bf16 bits, fp32) outputs [lane][H][32][G][D]."""
     layout = scenario.layout
     params, slot = verify_params(scenario, active_rows, row_capacity, splits, layer_index, committed)
     d_params = struct_to_device(params)
@@ -69,10 +69,17 @@ def run_verify_attention_gpu(scenario: Scenario, queries: np.ndarray, active_row
     out32 = torch.zeros(q.shape, dtype=torch.float32, device="cuda")
     masks = dev(row_masks) if row_masks is not None else None
     layer = scenario.storage.layers()[layer_index]
-    ops.attention_verify_split(layout, 24, lanes, row_capacity, slot, q, partials, stats, scenario.table_pointers,
-                               masks, d_params, layer)
+    if tensor_core:
+        word = torch.zeros(1, dtype=torch.int32, device="cuda")
+        ops.attention_verify_split_tc(layout, 24, lanes, row_capacity, slot, q, partials, stats,
+                                      scenario.table_pointers, masks, d_params, layer, word)
+    else:
+        ops.attention_verify_split(layout, 24, lanes, row_capacity, slot, q, partials, stats, scenario.table_pointers,
+                                   masks, d_params, layer)
     ops.attention_verify_reduce(layout, 24, lanes, row_capacity, partials, stats, out, d_params, output_f32=out32)
     torch.cuda.synchronize()
+    if tensor_core:
+        assert int(word.item()) == 0, "a bounded wait ran out in the tcgen05 verify kernel"
     return host_u16(out), out32.cpu().numpy(), (partials, stats)
 
 
