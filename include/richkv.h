@@ -59,16 +59,6 @@ int rk_attention_verify_split(uint32_t format, uint32_t kv_heads, uint32_t query
                               float *partials, float *statistics, const rk_page_entry *const *tables,
                               const uint32_t *row_masks, const rk_verify_params *lane_params, rk_kv_layer layer,
                               void *stream);
-/* The same split kernels for 8- or 16-row windows over int4 pages as a tcgen05 contraction (fused rows
- * on the M side of a 128-row tensor-core tile, accumulators in tensor memory). Arguments and scratch
- * layout as rk_attention_verify_split; merge with rk_attention_verify_reduce. `status` is one device
- * word the caller zeroes: it turns non-zero when a bounded wait inside a kernel ran out (the step's
- * output is then invalid). RK_ERR_UNSUPPORTED for other formats, geometries or row counts. */
-int rk_attention_verify_split_tc(uint32_t format, uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim,
-                                 uint32_t lanes, uint32_t row_capacity, uint32_t grid_splits, const void *queries,
-                                 float *partials, float *statistics, const rk_page_entry *const *tables,
-                                 const uint32_t *row_masks, const rk_verify_params *lane_params, rk_kv_layer layer,
-                                 uint32_t *status, void *stream);
 /* verify_attention_reduce / verify_tree_attention_reduce (decode/paged_attention.metal:198-263,415-531).
  * output bf16 [lane][kv_head][32][group][D]; output_f32 (optional) receives the value before rounding. */
 int rk_attention_verify_reduce(uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim, uint32_t lanes,
@@ -98,6 +88,20 @@ int rk_decode_plan_make(uint32_t format, uint32_t kv_heads, uint32_t query_heads
 /* The device address window that holds every page of a pool (rk_storage_window): the TMA tensor map. */
 void *rk_window_create(uint64_t base, uint64_t bytes);
 void rk_window_destroy(void *window);
+/* verify_attention_int4_split / verify_tree_attention_int4_split (decode/paged_attention.metal:23-192)
+ * for 8- or 16-row windows as a tcgen05 contraction: the fused rows are the M side of a 128-row
+ * tensor-core tile with accumulators in tensor memory, pages arrive by TMA through the pool's window.
+ * Arguments and scratch layout as rk_attention_verify_split; merge with rk_attention_verify_reduce.
+ * Any split count the contract allows is valid; about two CTAs' worth of (lane, head, split) per SM
+ * is the efficient choice. `status` is one device word the caller zeroes: it turns non-zero when a
+ * bounded wait inside a kernel ran out (the step's output is then invalid). RK_ERR_UNSUPPORTED for
+ * other formats, geometries or row counts. */
+int rk_attention_verify_split_tc(const void *window, uint32_t format, uint32_t kv_heads, uint32_t query_heads,
+                                 uint32_t head_dim, uint32_t lanes, uint32_t row_capacity, uint32_t grid_splits,
+                                 const void *queries, float *partials, float *statistics,
+                                 const rk_page_entry *const *tables, const uint32_t *row_masks,
+                                 const rk_verify_params *lane_params, rk_kv_layer layer, uint32_t *status,
+                                 void *stream);
 int rk_attention_decode(const void *window, const rk_decode_plan *plan, uint32_t format, const void *queries,
                         void *output, float *output_f32, float *partials, float *statistics,
                         uint32_t *descriptors, const rk_page_entry *const *tables,

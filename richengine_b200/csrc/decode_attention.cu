@@ -30,6 +30,7 @@
 //    scale folds into the exponent: w = 2^(s + log2 vscale - m), so the fp16
 //    probabilities stay in (0, 2^14] whatever the value magnitudes are.
 #include "common.cuh"
+#include "window.cuh"
 
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -38,7 +39,6 @@ namespace rk {
 
 struct DriverApi;
 const DriverApi *driver_api();
-int encode_window_map(CUtensorMap *map, uint64_t base, uint64_t rows, uint32_t box_rows);
 
 namespace {
 
@@ -675,11 +675,6 @@ int configure_decode_kernel() {
   return kOk;
 }
 
-struct Window {
-  uint64_t base = 0, bytes = 0;
-  CUtensorMap int4_map;
-};
-
 } // namespace
 } // namespace rk
 
@@ -721,7 +716,11 @@ void *rk_window_create(uint64_t base, uint64_t bytes) {
   auto *w = new Window;
   w->base = base;
   w->bytes = bytes;
-  if (encode_window_map(&w->int4_map, base, bytes >> 7, kTensorBytes / 128)) { delete w; return nullptr; } // one copy = all heads of a page
+  if (encode_window_map(&w->int4_map, base, bytes >> 7, kTensorBytes / 128) ||
+      encode_window_map(&w->int4_head_map, base, bytes >> 7, kSlabBytes / 128)) {
+    delete w;
+    return nullptr;
+  }
   return w;
 }
 void rk_window_destroy(void *window) { delete static_cast<Window *>(window); }

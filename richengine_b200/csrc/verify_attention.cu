@@ -1,5 +1,5 @@
-// verify_attention.cu — the speculative-verify window (8 or 16 query rows per lane) over quantized
-// pages as a dense tcgen05 contraction with TMEM accumulators.
+// verify_attention.cu — the speculative-verify window (8 or 16 query rows per lane) over int4 pages as
+// a dense tcgen05 contraction with TMEM accumulators, warp-specialised and pipelined.
 //
 // Semantics: the reference's verify tile
 //   runtime/metal/kernels/common/paged_attention_tile.h:85-189   (scale fold, admission, online softmax)
@@ -8,27 +8,38 @@
 // with partials and statistics in the layout of attention_tile.cu, so the same reduce merges them.
 //
 // One CTA owns (KV head, split, lane) like the reference grid. The fused rows (rows x 6 query heads,
-// 48 or 96) are the M side of a 128-row UMMA tile (padding rows hold zero queries). Per group of 64
-// tokens (two pages):
-//   1. all eight warps expand the two pages' codes to fp16 — exact: int4/int8 codes and e4m3 values fit
-//      fp16 — into K-major shared tiles with the 128-byte swizzle: K[token][dim], V^T[dim][token];
-//   2. one thread issues S = Q.K^T: 16 x tcgen05.mma (M128, N64, K16), fp32 accumulators in TMEM;
-//   3. warps 0-3 (one thread per row = one TMEM lane) read S, fold key scale and 1/16, apply the row's
-//      admission rule, run the online softmax without any shuffle, fold the value scale into the
-//      exponent (as decode_attention.cu) and write P as fp16 into its K-major tile; a row whose maximum
-//      grew by more than 2^8 rescales its O row in TMEM (rows of a warp move together);
-//   4. one thread issues O += P.V: 4 x tcgen05.mma (M128, N256, K16).
+// 48 or 96) are the M side of a 128-row UMMA tile (padding rows hold zero queries). The pages of the
+// split are taken in groups of 64 tokens (two pages). Roles:
+//   warp 8  (one thread)  TMA: the two pages' K and V slabs of this head (32-row boxes of the window
+//                         map, 128-byte swizzle) and their scales into a ring of three raw stages.
+//   warps 4-7             expand the raw nibbles to fp16 — exact — into the K-major swizzled operand
+//                         tiles K[token][dim] and V^T[dim][token] (an 8x8 transpose in registers), and
+//                         prepare the per-token scale triples.
+//   warp 9  (one thread)  tcgen05.mma: S = Q.K^T (16 x M128 N64 K16) and O += P.V (4 x M128 N256 K16),
+//                         ordered QK(g+1) before PV(g) so the tensor pipe works while the softmax runs.
+//   warps 0-3             softmax, one thread per row = one TMEM lane: read S, fold key scale and
+//                         1/16, admit, online maximum without any shuffle, value scale folded into the
+//                         exponent, P as fp16 into its operand tile; a row whose maximum grew by more
+//                         than 2^8 rescales its O row in TMEM (rows of a warp move together).
 // Key codes travel as fp16 bit patterns (u * 2^-24 with u = code + 8, high nibbles x16 with the query
-// carrying 1/16), the +8 leaves through 8 * sum(q) per row; value codes are centred exactly.
-// Every mbarrier wait is bounded; TMEM is released on every path.
+// carrying 1/16), the +8 leaves through 8 * sum(q) per row; value codes are centred exactly. Inside a
+// group the contraction index of P.V is a fixed permutation of the tokens (position 8r+j holds token
+// 8j+r), which makes every shared-memory access of the transpose conflict-free.
+// Every mbarrier wait is bounded and gives up at once after any wait failed; TMEM is released on
+// every path.
 #include "common.cuh"
+#include "window.cuh"
 
 #include <cuda_fp16.h>
 
 namespace rk {
 namespace {
 
-constexpr uint32_t kThreads = 256;
+constexpr uint32_t kSoftmaxWarps = 8, kExpandWarps = 4; // softmax: two warps per 32-row quarter, 32 tokens each
+constexpr uint32_t kSoftmaxThreads = kSoftmaxWarps * 32;
+constexpr uint32_t kExpandThreads = kExpandWarps * 32;
+constexpr uint32_t kThreads = (kSoftmaxWarps + kExpandWarps + 2) * 32;
+constexpr uint32_t kTmaWarp = kSoftmaxWarps + kExpandWarps, kMmaWarp = kTmaWarp + 1;
 constexpr uint32_t kGroupTokens = 64;
 constexpr uint32_t kM = 128, kD = 256, kG = 6, kHeads = 4;
 constexpr uint32_t kSpinLimit = 1u << 20;
@@ -39,29 +50,58 @@ constexpr uint32_t kQBytes = kM * kD * 2;            // 4 column blocks of [128 
 constexpr uint32_t kKBytes = kGroupTokens * kD * 2;  // 4 column blocks of [64 rows][64 elements]
 constexpr uint32_t kVBytes = kD * kGroupTokens * 2;  // 1 column block of [256 rows][64 elements]
 constexpr uint32_t kPBytes = kM * kGroupTokens * 2;  // 1 column block of [128 rows][64 elements]
-constexpr uint32_t kTileBytes = kQBytes + kKBytes + kVBytes + kPBytes;
+constexpr uint32_t kSlabBytes = 4096;                // one head's K (or V) of a page
+constexpr uint32_t kRawStages = 3;
+constexpr uint32_t kRawStageBytes = 17 * 1024;       // K0 | K1 | V0 | V1 | ks0 ks1 vs0 vs1 (128 B each) | pad
+constexpr uint32_t kRawScaleOffset = 4 * kSlabBytes;
+constexpr uint32_t kTileBytes = kQBytes + kKBytes + kVBytes + kPBytes + kRawStages * kRawStageBytes;
 
 struct Control {
-  uint64_t s_done, o_done;
+  uint64_t raw_full[kRawStages], raw_free[kRawStages];
+  uint64_t k_full, k_free, v_full, v_free, s_full, s_free, p_full, scale_free[2];
   uint32_t tmem_base;
   uint32_t error;
-  float key_scale[kGroupTokens];
-  float value_log2[kGroupTokens];
+  float q_sums[kM];
+  float exchange[2][kM][2];       // the two half-row maxima of a group (and, at the end, the half-row sums)
+  float4 scales[2][kGroupTokens]; // {key scale, log2 value scale, 2^-6 / value scale, -}
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void barrier_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void barrier_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void barrier_expect(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ bool barrier_try(uint32_t bar, uint32_t parity) {
   uint32_t done;
   asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
                : "=r"(done) : "r"(bar), "r"(parity) : "memory");
   return done != 0;
 }
-__device__ __forceinline__ bool barrier_wait(uint32_t bar, uint32_t parity) {
+// Waits for completion number `count` (0-based) of a barrier. Bounded: gives up after kSpinLimit polls,
+// or at once when another wait of this CTA already gave up; either way `error` ends non-zero.
+__device__ __forceinline__ void barrier_wait(uint64_t *barrier, uint32_t count, volatile uint32_t *error) {
+  const uint32_t bar = smem_u32(barrier), parity = count & 1u;
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (barrier_try(bar, parity)) return true;
-    if (i > 16) __nanosleep(64);
+    if (barrier_try(bar, parity)) return;
+    if (i > 8) {
+      if (*error) return;
+      __nanosleep(20);
+    }
   }
-  return false;
+  *error = 1;
+}
+__device__ __forceinline__ void tma_load_rows(uint32_t dst, const CUtensorMap *map, int32_t row, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(0), "r"(row), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 // K-major, 128-byte swizzle shared-memory descriptor: 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t umma_descriptor(uint32_t address) {
@@ -82,9 +122,12 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint6
                "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
                ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
 }
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+__device__ __forceinline__ void umma_commit(uint64_t *barrier) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(barrier)) : "memory");
 }
+__device__ __forceinline__ void tmem_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void async_proxy_fence() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tmem_load32(uint32_t address, float (&v)[32]) {
   uint32_t r[32];
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -117,25 +160,24 @@ __device__ __forceinline__ float log2_fast(float x) { float r; asm("lg2.approx.f
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) { const __half2 h = __floats2half2_rn(lo, hi); return *reinterpret_cast<const uint32_t *>(&h); }
 __device__ __forceinline__ uint32_t sub_f16x2(uint32_t a, uint32_t b) { uint32_t r; asm("sub.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b)); return r; }
 __device__ __forceinline__ uint32_t fma_f16x2(uint32_t a, uint32_t b, uint32_t c) { uint32_t r; asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c)); return r; }
+// (a & mask) ^ flip in one logic instruction; both constants sit in registers.
+__device__ __forceinline__ uint32_t and_xor(uint32_t a, uint32_t mask, uint32_t flip) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(r) : "r"(a), "r"(mask), "r"(flip));
+  return r;
+}
+__device__ __forceinline__ uint32_t register_constant(uint32_t value) {
+  uint32_t r;
+  asm volatile("mov.b32 %0, %1;" : "=r"(r) : "r"(value));
+  return r;
+}
 
-// Byte offset of 16-byte chunk `chunk` (0..7) of row `row` inside one column block.
+// Byte offset of 16-byte chunk `chunk` (0..7) of row `row` inside one 128-byte-swizzled block.
 __device__ __forceinline__ uint32_t swizzled(uint32_t row, uint32_t chunk) { return row * 128u + ((chunk ^ (row & 7u)) << 4); }
 
-// Within a 16-byte chunk of 8 dims the element order is (0,4,1,5,2,6,3,7): the order in which an int4
-// word yields its nibble pairs; queries and keys use the same order, so the contraction is unchanged.
-// Positions 2,3,6,7 of that order (dims 1,5,3,7) carry the 16x of a high nibble for int4 keys.
-
-template <uint32_t Format> struct Expand;
-
-// int4: one 32-bit word = 8 dims of one token.
-template <> struct Expand<RK_FORMAT_INT4> {
-  // 8 key codes -> one 16-byte chunk of fp16 bit patterns (subnormal u * 2^-24; odd dims x16)
-  __device__ static uint4 key_chunk(uint32_t x) {
-    const uint32_t y = x >> 8;
-    return make_uint4((x & 0x000F000Fu) ^ 0x00080008u, (x & 0x00F000F0u) ^ 0x00800080u,
-                      (y & 0x000F000Fu) ^ 0x00080008u, (y & 0x00F000F0u) ^ 0x00800080u);
-  }
-};
+// Within a 16-byte operand chunk of 8 dims the element order is (0,4,1,5,2,6,3,7): the order in which
+// an int4 word yields its nibble pairs; queries and keys use the same order, so the contraction is
+// unchanged. Dims 1,5,3,7 of each 8 carry the 16x of a high nibble on the key side, 1/16 on the query.
 
 struct VerifyArgs {
   const uint16_t *queries;
@@ -145,21 +187,25 @@ struct VerifyArgs {
   const uint32_t *row_masks;
   const rk_verify_params *lane_params;
   rk_kv_layer layer;
+  uint64_t window_base;
   uint32_t *status; // one word: non-zero when a bounded wait ran out
 };
 
-template <uint32_t Rows>
+template <uint32_t Rows, bool kTree>
 __global__ void __launch_bounds__(kThreads, 1)
-verify_int4_kernel(VerifyArgs args) {
+verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args) {
   constexpr uint32_t kRealRows = Rows * kG; // fused rows that exist
   extern __shared__ uint8_t dynamic_shared[];
   const uint32_t tiles = (smem_u32(dynamic_shared) + 1023u) & ~1023u;
   uint8_t *tile_ptr = dynamic_shared + (tiles - smem_u32(dynamic_shared));
   Control &ctl = *reinterpret_cast<Control *>(tile_ptr + kTileBytes);
+  volatile uint32_t *error = &ctl.error;
   const uint32_t q_tile = tiles, k_tile = tiles + kQBytes, v_tile = k_tile + kKBytes, p_tile = v_tile + kVBytes;
+  const uint32_t raw_tile = p_tile + kPBytes;
   uint8_t *q_ptr = tile_ptr, *k_ptr = tile_ptr + kQBytes, *v_ptr = k_ptr + kKBytes, *p_ptr = v_ptr + kVBytes;
+  const uint8_t *raw_ptr = p_ptr + kPBytes;
 
-  const uint32_t tid = threadIdx.x, warp = tid / 32;
+  const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const uint32_t kv_head = blockIdx.x, split = blockIdx.y, lane_index = blockIdx.z;
   rk_verify_params p = args.lane_params[lane_index];
   p.kv = args.layer;
@@ -170,162 +216,248 @@ verify_int4_kernel(VerifyArgs args) {
   const uint32_t page_begin = split * per_split;
   if (page_begin >= pages) return; // a split without pages writes nothing
   const uint32_t page_end = min(pages, page_begin + per_split);
+  const uint32_t groups = (page_end - page_begin + 1) / 2;
   const rk_page_entry *table = args.tables[lane_index];
-  const uint32_t *row_masks = args.row_masks ? args.row_masks + uint64_t(lane_index) * p.row_capacity : nullptr;
+  const uint32_t *row_masks = kTree ? args.row_masks + uint64_t(lane_index) * p.row_capacity : nullptr;
 
   // ---- setup: barriers, TMEM, query tile ----------------------------------------------------------
   if (tid == 0) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&ctl.s_done)));
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&ctl.o_done)));
+    for (uint32_t r = 0; r < kRawStages; ++r) {
+      barrier_init(smem_u32(&ctl.raw_full[r]), 1);
+      barrier_init(smem_u32(&ctl.raw_free[r]), kExpandThreads);
+    }
+    barrier_init(smem_u32(&ctl.k_full), kExpandThreads);
+    barrier_init(smem_u32(&ctl.v_full), kExpandThreads);
+    barrier_init(smem_u32(&ctl.k_free), 1);
+    barrier_init(smem_u32(&ctl.v_free), 1);
+    barrier_init(smem_u32(&ctl.s_full), 1);
+    barrier_init(smem_u32(&ctl.s_free), kSoftmaxThreads);
+    barrier_init(smem_u32(&ctl.p_full), kSoftmaxThreads);
+    barrier_init(smem_u32(&ctl.scale_free[0]), kSoftmaxThreads);
+    barrier_init(smem_u32(&ctl.scale_free[1]), kSoftmaxThreads);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     ctl.error = 0;
   }
-  if (warp == 0) {
+  if (warp == kTmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl.tmem_base)), "r"(512u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   // Query tile: row m = row*6 + g of this (lane, head); fp16, chunk order (0,4,1,5,2,6,3,7), odd dims /16.
-  const uint16_t *queries = args.queries + (uint64_t(lane_index) * kHeads + kv_head) * (uint64_t(RK_VERIFY_CHUNK_STRIDE) * kG * kD);
-  float q_sum = 0.0f; // of this thread's row (threads 0..127), for the +8 correction
   {
-    // thread t handles row t/2 (all 128 rows), half of the 32 chunks each
-    const uint32_t row = tid >> 1;
-    const bool real = row < p.active_rows * kG;
-    for (uint32_t c = (tid & 1u) * 16; c < (tid & 1u) * 16 + 16; ++c) { // chunk c = dims 8c..8c+7
-      uint4 raw = make_uint4(0, 0, 0, 0);
-      if (real) raw = __ldg(reinterpret_cast<const uint4 *>(queries + uint64_t(row) * kD + 8 * c));
-      const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
-      float d[8];
+    const uint16_t *queries = args.queries + (uint64_t(lane_index) * kHeads + kv_head) * (uint64_t(RK_VERIFY_CHUNK_STRIDE) * kG * kD);
+    for (uint32_t item = tid; item < kM * 2; item += kThreads) { // half a row (16 chunks) per item
+      const uint32_t row = item >> 1;
+      const bool real = row < p.active_rows * kG;
+      float q_sum = 0.0f; // over the fp16 values the tensor core will see, for the +8 correction
+      for (uint32_t c = (item & 1u) * 16; c < (item & 1u) * 16 + 16; ++c) { // chunk c = dims 8c..8c+7
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if (real) raw = __ldg(reinterpret_cast<const uint4 *>(queries + uint64_t(row) * kD + 8 * c));
+        const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+        float d[8];
 #pragma unroll
-      for (uint32_t i = 0; i < 4; ++i) { d[2 * i] = bf16_bits_to_float(words[i] & 0xffffu); d[2 * i + 1] = bf16_bits_to_float(words[i] >> 16); }
-      const uint4 chunk = make_uint4(pack_half2(d[0], d[4]), pack_half2(d[1] * 0.0625f, d[5] * 0.0625f),
-                                     pack_half2(d[2], d[6]), pack_half2(d[3] * 0.0625f, d[7] * 0.0625f));
-      *reinterpret_cast<uint4 *>(q_ptr + (c >> 3) * (kM * 128) + swizzled(row, c & 7u)) = chunk;
-      const __half2 *h = reinterpret_cast<const __half2 *>(&chunk);
-      q_sum += __low2float(h[0]) + __high2float(h[0]) + __low2float(h[2]) + __high2float(h[2]) +
-               16.0f * (__low2float(h[1]) + __high2float(h[1]) + __low2float(h[3]) + __high2float(h[3]));
+        for (uint32_t i = 0; i < 4; ++i) { d[2 * i] = bf16_bits_to_float(words[i] & 0xffffu); d[2 * i + 1] = bf16_bits_to_float(words[i] >> 16); }
+        const uint4 chunk = make_uint4(pack_half2(d[0], d[4]), pack_half2(d[1] * 0.0625f, d[5] * 0.0625f),
+                                       pack_half2(d[2], d[6]), pack_half2(d[3] * 0.0625f, d[7] * 0.0625f));
+        *reinterpret_cast<uint4 *>(q_ptr + (c >> 3) * (kM * 128) + swizzled(row, c & 7u)) = chunk;
+        const __half2 *h = reinterpret_cast<const __half2 *>(&chunk);
+        q_sum += __low2float(h[0]) + __high2float(h[0]) + __low2float(h[2]) + __high2float(h[2]) +
+                 16.0f * (__low2float(h[1]) + __high2float(h[1]) + __low2float(h[3]) + __high2float(h[3]));
+      }
+      q_sum += __shfl_xor_sync(0xffffffffu, q_sum, 1); // the two halves of a row sit in neighbouring lanes
+      if ((item & 1u) == 0) ctl.q_sums[row] = q_sum;
     }
-    q_sum += __shfl_xor_sync(0xffffffffu, q_sum, 1); // the two threads of a row
   }
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  async_proxy_fence();
+  tmem_fence_before();
   __syncthreads();
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  tmem_fence_after();
   const uint32_t tmem = ctl.tmem_base;
   const uint32_t tmem_s = tmem, tmem_o = tmem + 64;
-  // softmax threads: thread i < 128 owns fused row i = TMEM lane i
-  __shared__ float q_sums[kM];
-  if ((tid & 1u) == 0) q_sums[tid >> 1] = q_sum;
-  __syncthreads();
-  const uint32_t my_row = tid; // for tid < 128
-  const float score_scale = rk_score_scale(p.score_scale, kD) * kLog2e;
-  const float row_factor = ldexpf(score_scale, 24);
-  const float row_offset = tid < kM ? -8.0f * q_sums[tid] * score_scale : 0.0f;
-  const uint32_t query_row = my_row / kG;
-  const uint32_t causal_limit = min(visible, p.committed_tokens + min(query_row, p.active_rows - 1) + 1);
-  const uint32_t tree_mask = row_masks && query_row < p.row_capacity ? row_masks[query_row] : 0u;
-
-  float row_max = -1.0e30f, row_sum = 0.0f;
-  const uint32_t idesc_qk = umma_instruction(kM, kGroupTokens), idesc_pv = umma_instruction(kM, kD);
   const uint32_t data_bytes = kPageTokens * kHeads * kD / 2, scale_bytes = kPageTokens * kHeads * 4;
-  uint32_t phase = 0;
-  bool failed = false;
 
-  for (uint32_t group_page = page_begin; group_page < page_end; group_page += 2, phase ^= 1u) {
-    const uint32_t group_pages = min(2u, page_end - group_page);
-    // ---- 1. expand the group's pages into the K and V^T tiles ---------------------------------------
-    const uint8_t *keys[2] = {nullptr, nullptr}, *values[2] = {nullptr, nullptr};
-#pragma unroll
-    for (uint32_t local = 0; local < 2; ++local) {
-      if (local >= group_pages) continue;
-      const rk_page_entry entry = table[group_page + local];
-      const uint32_t index = rk_entry_index(entry);
-      const uint8_t *region = reinterpret_cast<const uint8_t *>(rk_entry_extent(entry)) + args.layer.offset;
-      const uint64_t extent_pages = args.layer.extent_pages;
-      keys[local] = region + uint64_t(index) * data_bytes + kv_head * 4096u;
-      values[local] = region + extent_pages * (uint64_t(data_bytes) + scale_bytes) + uint64_t(index) * data_bytes + kv_head * 4096u;
-      if (tid < kPageTokens) {
-        const float *key_scales = reinterpret_cast<const float *>(region + extent_pages * data_bytes + uint64_t(index) * scale_bytes) + kv_head * kPageTokens;
-        const float *value_scales = reinterpret_cast<const float *>(region + extent_pages * (2ull * data_bytes + scale_bytes) + uint64_t(index) * scale_bytes) + kv_head * kPageTokens;
-        ctl.key_scale[local * kPageTokens + tid] = key_scales[tid];
-        ctl.value_log2[local * kPageTokens + tid] = log2_fast(value_scales[tid]);
-      }
-    }
-    // keys: a thread takes word w (8 dims) of a token; a warp reads whole 128-byte rows and writes whole
-    // swizzled rows. An absent second page leaves finite codes behind (its tokens are never admitted).
-#pragma unroll
-    for (uint32_t i = 0; i < 8; ++i) {
-      const uint32_t local = i >> 2, word = tid + (i & 3u) * kThreads, token = word >> 5, w = word & 31u;
-      const uint32_t x = keys[local] ? __ldg(reinterpret_cast<const uint32_t *>(keys[local]) + word) : 0u;
-      *reinterpret_cast<uint4 *>(k_ptr + (w >> 3) * (kGroupTokens * 128) + swizzled(local * kPageTokens + token, w & 7u)) =
-          Expand<RK_FORMAT_INT4>::key_chunk(x);
-    }
-    // values: thread = (8 tokens, word w of 8 dims); an 8x8 transpose in registers turns the token-major
-    // nibbles into 16-byte runs of 8 tokens for the dim-major tile. The eight lanes of a store phase
-    // differ in their token run, so they fill one 128-byte row: no bank conflict.
-    {
-      const uint32_t run = tid & 7u, w = tid >> 3, local = run >> 2; // run = 16-byte chunk along the 64 tokens
-      const uint8_t *source = local ? values[1] : values[0];
-      uint32_t x[8];
-#pragma unroll
-      for (uint32_t t = 0; t < 8; ++t)
-        x[t] = source ? __ldg(reinterpret_cast<const uint32_t *>(source) + ((run & 3u) * 8 + t) * 32 + w) : 0u;
-#pragma unroll
-      for (uint32_t b = 0; b < 4; ++b) { // byte b of each word = dims 8w+2b (low nibble), 8w+2b+1 (high nibble)
-        uint32_t lo[4], hi[4];
-        const uint32_t selector = b | (b << 4) | ((4 + b) << 8) | ((4 + b) << 12);
-#pragma unroll
-        for (uint32_t pair = 0; pair < 4; ++pair) {
-          const uint32_t joined = __byte_perm(x[2 * pair], x[2 * pair + 1], selector);
-          lo[pair] = sub_f16x2((joined & 0x000F000Fu) ^ 0x64086408u, 0x64086408u);                                  // 1024+u - 1032
-          hi[pair] = fma_f16x2((joined & 0x00F000F0u) ^ 0x64806480u, 0x2C002C00u /* 1/16 */, 0xD480D480u /* -72 */); // (1024+16u)/16 - 72
+  if (warp == kTmaWarp) {
+    // ---- TMA producer ---------------------------------------------------------------------------------
+    if (lane == 0) {
+      rk_page_entry next[2] = {table[page_begin], page_begin + 1 < page_end ? table[page_begin + 1] : 0};
+      for (uint32_t g = 0; g < groups; ++g) {
+        const uint32_t r = g % kRawStages, use = g / kRawStages;
+        const uint32_t first = page_begin + 2 * g, group_pages = min(2u, page_end - first);
+        const rk_page_entry entries[2] = {next[0], next[1]};
+        if (g + 1 < groups) { // the next group's entries travel while this group is issued
+          next[0] = table[first + 2];
+          next[1] = first + 3 < page_end ? table[first + 3] : 0;
         }
-        const uint32_t dim = 8 * w + 2 * b;
-        *reinterpret_cast<uint4 *>(v_ptr + swizzled(dim, run)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-        *reinterpret_cast<uint4 *>(v_ptr + swizzled(dim + 1, run)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-      }
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-
-    // ---- 2. S = Q.K^T ---------------------------------------------------------------------------------
-    if (tid == 128) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (use) barrier_wait(&ctl.raw_free[r], use - 1, error);
+        const uint32_t full = smem_u32(&ctl.raw_full[r]), stage = raw_tile + r * kRawStageBytes;
+        barrier_expect(full, group_pages * (2 * kSlabBytes + 256));
 #pragma unroll
-      for (uint32_t j = 0; j < 16; ++j) {
-        const uint64_t a = umma_descriptor(q_tile + (j >> 2) * (kM * 128) + (j & 3u) * 32);
-        const uint64_t b = umma_descriptor(k_tile + (j >> 2) * (kGroupTokens * 128) + (j & 3u) * 32);
-        umma_f16(tmem_s, a, b, idesc_qk, j ? 1u : 0u);
+        for (uint32_t local = 0; local < 2; ++local) {
+          if (local >= group_pages) break;
+          const uint32_t index = rk_entry_index(entries[local]);
+          const uint64_t region = rk_entry_extent(entries[local]) + args.layer.offset;
+          const uint64_t extent_pages = args.layer.extent_pages;
+          const uint64_t keys = region + uint64_t(index) * data_bytes + kv_head * kSlabBytes;
+          const uint64_t values = region + extent_pages * (uint64_t(data_bytes) + scale_bytes) + uint64_t(index) * data_bytes + kv_head * kSlabBytes;
+          const uint64_t key_scales = region + extent_pages * data_bytes + uint64_t(index) * scale_bytes + kv_head * 128u;
+          const uint64_t value_scales = region + extent_pages * (2ull * data_bytes + scale_bytes) + uint64_t(index) * scale_bytes + kv_head * 128u;
+          tma_load_rows(stage + local * kSlabBytes, &head_map, int32_t((keys - args.window_base) >> 7), full);
+          tma_load_rows(stage + (2 + local) * kSlabBytes, &head_map, int32_t((values - args.window_base) >> 7), full);
+          bulk_load(stage + kRawScaleOffset + local * 128, reinterpret_cast<const void *>(key_scales), 128, full);
+          bulk_load(stage + kRawScaleOffset + (2 + local) * 128, reinterpret_cast<const void *>(value_scales), 128, full);
+        }
       }
-      umma_commit(smem_u32(&ctl.s_done));
+      // Every copy this thread started has landed before the CTA may leave (also after a failed wait).
+      for (uint32_t g = groups > kRawStages ? groups - kRawStages : 0; g < groups; ++g) {
+        const uint32_t bar = smem_u32(&ctl.raw_full[g % kRawStages]), parity = (g / kRawStages) & 1u;
+        for (uint32_t i = 0; i < kSpinLimit && !barrier_try(bar, parity); ++i) __nanosleep(64);
+      }
     }
-
-    // ---- 3. softmax: one thread per row ---------------------------------------------------------------
-    if (warp < 4) {
-      if (!failed && !barrier_wait(smem_u32(&ctl.s_done), phase)) { failed = true; ctl.error = 1; }
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t lane_address = (warp * 32u) << 16;
-      const uint32_t token_base = group_page * kPageTokens;
-      const uint32_t group_tokens = group_pages * kPageTokens; // a split may end inside the group
-      float scores[kGroupTokens];
-      float group_max = -INFINITY;
+  } else if (warp == kMmaWarp) {
+    // ---- tensor-core issue --------------------------------------------------------------------------------
+    if (lane == 0) {
+      const uint32_t idesc_qk = umma_instruction(kM, kGroupTokens), idesc_pv = umma_instruction(kM, kD);
+      auto scores = [&](uint32_t g) {
+        barrier_wait(&ctl.k_full, g, error);
+        if (g) barrier_wait(&ctl.s_free, g - 1, error);
+        tmem_fence_after();
+#pragma unroll
+        for (uint32_t j = 0; j < 16; ++j) {
+          const uint64_t a = umma_descriptor(q_tile + (j >> 2) * (kM * 128) + (j & 3u) * 32);
+          const uint64_t b = umma_descriptor(k_tile + (j >> 2) * (kGroupTokens * 128) + (j & 3u) * 32);
+          umma_f16(tmem_s, a, b, idesc_qk, j ? 1u : 0u);
+        }
+        umma_commit(&ctl.s_full);
+        umma_commit(&ctl.k_free);
+      };
+      scores(0);
+      for (uint32_t g = 0; g < groups; ++g) {
+        if (g + 1 < groups) scores(g + 1);
+        barrier_wait(&ctl.v_full, g, error);
+        barrier_wait(&ctl.p_full, g, error);
+        tmem_fence_after();
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j)
+          umma_f16(tmem_o, umma_descriptor(p_tile + j * 32), umma_descriptor(v_tile + j * 32), idesc_pv, (g || j) ? 1u : 0u);
+        umma_commit(&ctl.v_free);
+      }
+    }
+  } else if (warp >= kSoftmaxWarps) {
+    // ---- expanders: raw nibbles -> fp16 operand tiles ---------------------------------------------------------
+    const uint32_t e = tid - kSoftmaxThreads;
+    const uint32_t low_mask = register_constant(0x000F000Fu), high_mask = register_constant(0x00F000F0u);
+    const uint32_t key_low = register_constant(0x00080008u), key_high = register_constant(0x00800080u);
+    const uint32_t value_low = register_constant(0x64086408u), value_high = register_constant(0x64806480u);
+    for (uint32_t g = 0; g < groups; ++g) {
+      const uint32_t r = g % kRawStages, use = g / kRawStages;
+      const uint32_t group_pages = min(2u, page_end - (page_begin + 2 * g));
+      const uint8_t *raw = raw_ptr + r * kRawStageBytes;
+      barrier_wait(&ctl.raw_full[r], use, error);
+      // per-token scale triples; tokens of an absent page get harmless zeros
+      if (e < kGroupTokens) {
+        if (g >= 2) barrier_wait(&ctl.scale_free[g & 1u], (g >> 1) - 1, error);
+        const uint32_t local = e >> 5, token = e & 31u;
+        float4 triple = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (local < group_pages) {
+          const float ks = reinterpret_cast<const float *>(raw + kRawScaleOffset)[local * 32 + token];
+          const float vs = fmaxf(reinterpret_cast<const float *>(raw + kRawScaleOffset)[(2 + local) * 32 + token], 9.094947e-13f); // 2^-40
+          triple = make_float4(ks, log2_fast(vs), __fdividef(0.015625f, vs), 0.0f);
+        }
+        ctl.scales[g & 1u][e] = triple;
+      }
+      if (g) barrier_wait(&ctl.k_free, g - 1, error);
+      // keys: a thread takes a raw 16-byte chunk (32 dims of one token) = four operand chunks. The
+      // eight lanes of an access phase differ in token % 8: conflict-free on both swizzled sides.
+#pragma unroll
+      for (uint32_t i = 0; i < 4; ++i) {
+        const uint32_t item = e + i * kExpandThreads;
+        const uint32_t token = (item & 7u) | ((item >> 6) << 3), c = (item >> 3) & 7u;
+        const uint4 x = *reinterpret_cast<const uint4 *>(raw + (token >> 5) * kSlabBytes + swizzled(token & 31u, c));
+        const uint32_t words[4] = {x.x, x.y, x.z, x.w};
+        uint8_t *block = k_ptr + (c >> 1) * (kGroupTokens * 128);
+#pragma unroll
+        for (uint32_t w = 0; w < 4; ++w) {
+          const uint32_t y = words[w] >> 8;
+          *reinterpret_cast<uint4 *>(block + swizzled(token, ((c & 1u) << 2) + w)) =
+              make_uint4(and_xor(words[w], low_mask, key_low), and_xor(words[w], high_mask, key_high),
+                         and_xor(y, low_mask, key_low), and_xor(y, high_mask, key_high));
+        }
+      }
+      async_proxy_fence();
+      barrier_arrive(smem_u32(&ctl.k_full));
+      if (g) barrier_wait(&ctl.v_free, g - 1, error);
+      // values: thread = (r8, word w of 8 dims) takes tokens 8j + r8, j = 0..7, and transposes 8x8 in
+      // registers: each dim gets a 16-byte run of eight tokens at contraction positions 8*r8 + j.
 #pragma unroll
       for (uint32_t half = 0; half < 2; ++half) {
-        float raw[32];
-        tmem_load32(tmem_s + lane_address + half * 32, raw);
+        const uint32_t unit = e + half * kExpandThreads, r8 = unit & 7u, w = unit >> 3;
+        uint32_t x[8];
 #pragma unroll
-        for (uint32_t i = 0; i < 32; ++i) {
-          const uint32_t t = half * 32 + i, token = token_base + t;
-          const bool admitted = t < group_tokens &&
-                                (!row_masks ? token < causal_limit
-                                            : (token < p.committed_tokens || (token < visible && ((tree_mask >> (token - p.committed_tokens)) & 1u))));
-          const float s = fmaf(raw[i], row_factor, row_offset) * ctl.key_scale[t];
-          scores[t] = admitted ? s : -INFINITY;
-          group_max = fmaxf(group_max, admitted ? s + fmaxf(ctl.value_log2[t], -40.0f) : -INFINITY);
+        for (uint32_t j = 0; j < 8; ++j)
+          x[j] = *reinterpret_cast<const uint32_t *>(raw + (2 + (j >> 2)) * kSlabBytes + swizzled(8 * (j & 3u) + r8, w >> 2) + (w & 3u) * 4);
+#pragma unroll
+        for (uint32_t b = 0; b < 4; ++b) { // byte b of each word = dims 8w+2b (low nibble), 8w+2b+1 (high nibble)
+          uint32_t lo[4], hi[4];
+          const uint32_t selector = b | (b << 4) | ((4 + b) << 8) | ((4 + b) << 12);
+#pragma unroll
+          for (uint32_t pair = 0; pair < 4; ++pair) {
+            const uint32_t joined = __byte_perm(x[2 * pair], x[2 * pair + 1], selector);
+            lo[pair] = sub_f16x2(and_xor(joined, low_mask, value_low), value_low);                                   // 1024+u - 1032
+            hi[pair] = fma_f16x2(and_xor(joined, high_mask, value_high), 0x2C002C00u /* 1/16 */, 0xD480D480u /* -72 */); // (1024+16u)/16 - 72
+          }
+          const uint32_t dim = 8 * w + 2 * b;
+          *reinterpret_cast<uint4 *>(v_ptr + swizzled(dim, r8)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+          *reinterpret_cast<uint4 *>(v_ptr + swizzled(dim + 1, r8)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
         }
       }
-      // Lazy rescale: the reference value only moves when the maximum grew by more than 2^8, so the
+      async_proxy_fence();
+      barrier_arrive(smem_u32(&ctl.v_full));
+      barrier_arrive(smem_u32(&ctl.raw_free[r]));
+    }
+  } else {
+    // ---- softmax: two threads per fused row (= TMEM lane), 32 tokens of the group each -----------------------
+    const uint32_t quarter = warp & 3u, half = warp >> 2;
+    const uint32_t my_row = quarter * 32 + lane;
+    const float score_scale = rk_score_scale(p.score_scale, kD) * kLog2e;
+    const float row_factor = ldexpf(score_scale, 24);
+    const float row_offset = -8.0f * ctl.q_sums[my_row] * score_scale;
+    const uint32_t query_row = my_row / kG;
+    const uint32_t causal_limit = min(visible, p.committed_tokens + min(query_row, p.active_rows - 1) + 1);
+    const uint32_t tree_mask = kTree && query_row < p.row_capacity ? row_masks[query_row] : 0u;
+    const uint32_t lane_address = (quarter * 32u) << 16;
+    float row_max = -1.0e30f, row_sum = 0.0f; // row_sum: this thread's tokens only
+
+    for (uint32_t g = 0; g < groups; ++g) {
+      const uint32_t first = page_begin + 2 * g;
+      const uint32_t token_base = first * kPageTokens + half * 32;
+      // tokens of this half that exist in the group (a split may end inside it) and pass the causal rule
+      const uint32_t present = min(2u, page_end - first) > half ? 32u : 0u;
+      const uint32_t limit = kTree ? present : min(present, causal_limit > token_base ? causal_limit - token_base : 0u);
+      const float4 *triples = ctl.scales[g & 1u] + half * 32;
+      barrier_wait(&ctl.s_full, g, error);
+      tmem_fence_after();
+      float scores[32];
+      tmem_load32(tmem_s + lane_address + half * 32, scores);
+      tmem_fence_before();
+      barrier_arrive(smem_u32(&ctl.s_free));
+
+      float group_max = -INFINITY;
+#pragma unroll
+      for (uint32_t t = 0; t < 32; ++t) {
+        bool admitted = t < limit;
+        if (kTree) {
+          const uint32_t token = token_base + t;
+          admitted = admitted && (token < p.committed_tokens || (token < visible && ((tree_mask >> (token - p.committed_tokens)) & 1u)));
+        }
+        const float4 triple = triples[t];
+        const float s = fmaf(scores[t], row_factor, row_offset) * triple.x + triple.y; // score + log2(value scale)
+        scores[t] = admitted ? s : -INFINITY;
+        group_max = fmaxf(group_max, scores[t]);
+      }
+      // the row's other half
+      ctl.exchange[g & 1u][my_row][half] = group_max;
+      asm volatile("bar.sync %0, 64;" ::"r"(1u + quarter) : "memory");
+      group_max = fmaxf(group_max, ctl.exchange[g & 1u][my_row][half ^ 1u]);
+      // Lazy rescale: the reference exponent only moves when the maximum grew by more than 2^8, so the
       // fp16 probabilities stay below 2^(8+6); rows of a warp move together (collective TMEM access).
       const bool grow = group_max > row_max + 8.0f;
       float scale = 1.0f;
@@ -334,80 +466,74 @@ verify_int4_kernel(VerifyArgs args) {
         row_max = group_max;
         row_sum *= scale;
       }
-      if (__any_sync(0xffffffffu, grow) && group_page != page_begin) {
-#pragma unroll 1
-        for (uint32_t c = 0; c < kD / 32; ++c) {
-          float o[32];
-          tmem_load32(tmem_o + lane_address + c * 32, o);
+      const float exponent_base = row_max - 6.0f;
+      // position 8*r8 + j of the contraction holds token 8*j + r8 (the order the value tile is built in):
+      // this half owns j = 4*half .. 4*half+3 of every 16-byte run, i.e. 8 bytes of each
+      uint32_t packed[16];
 #pragma unroll
-          for (uint32_t i = 0; i < 32; ++i) o[i] *= scale;
-          tmem_store32(tmem_o + lane_address + c * 32, o);
-        }
-      }
+      for (uint32_t r8 = 0; r8 < 8; ++r8) {
 #pragma unroll
-      for (uint32_t c = 0; c < kGroupTokens / 8; ++c) {
-        uint32_t packed[4];
-#pragma unroll
-        for (uint32_t i = 0; i < 4; ++i) {
+        for (uint32_t i = 0; i < 2; ++i) {
           float w[2];
 #pragma unroll
-          for (uint32_t e = 0; e < 2; ++e) {
-            const uint32_t t = c * 8 + 2 * i + e;
-            const float s = scores[t];
-            const bool live = s != -INFINITY;
-            w[e] = live ? exp2_fast(s + ctl.value_log2[t] - row_max + 6.0f) : 0.0f;
-            row_sum += live ? exp2_fast(s - row_max) : 0.0f;
+          for (uint32_t h = 0; h < 2; ++h) {
+            const uint32_t t = 8 * (2 * i + h) + r8;
+            w[h] = exp2_fast(scores[t] - exponent_base);     // 0 for a masked token
+            row_sum = fmaf(w[h], triples[t].z, row_sum);     // 2^(score - row_max)
           }
-          packed[i] = pack_half2(w[0], w[1]);
+          packed[r8 * 2 + i] = pack_half2(w[0], w[1]);
         }
-        *reinterpret_cast<uint4 *>(p_ptr + swizzled(my_row, c)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
       }
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-
-    // ---- 4. O += P.V -------------------------------------------------------------------------------------
-    if (tid == 128) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-      for (uint32_t j = 0; j < 4; ++j)
-        umma_f16(tmem_o, umma_descriptor(p_tile + j * 32), umma_descriptor(v_tile + j * 32), idesc_pv,
-                 (group_page != page_begin || j) ? 1u : 0u);
-      umma_commit(smem_u32(&ctl.o_done));
-    }
-    // every thread waits: the tiles are rewritten by the next group
-    if (!failed && !barrier_wait(smem_u32(&ctl.o_done), phase)) { failed = true; ctl.error = 3; }
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (ctl.error) failed = true;
-  }
-
-  // ---- partial output: row i of O, un-normalised; statistics {reference exponent, sum} -------------------
-  if (warp < 4) {
-    const uint64_t slot = (uint64_t(lane_index) * kHeads + kv_head) * p.slot_splits + split;
-    const uint32_t lane_address = (warp * 32u) << 16;
-    float *out = args.partials + (slot * kRealRows + my_row) * kD;
+      // O and the P tile belong to the previous group's P.V until it has landed
+      if (g) barrier_wait(&ctl.v_free, g - 1, error);
+      if (g && __any_sync(0xffffffffu, grow)) { // this half rescales its 128 columns of O
+        tmem_fence_after();
 #pragma unroll 1
-    for (uint32_t c = 0; c < kD / 32; ++c) {
+        for (uint32_t c = 0; c < 4; ++c) {
+          float o[32];
+          tmem_load32(tmem_o + lane_address + half * 128 + c * 32, o);
+#pragma unroll
+          for (uint32_t i = 0; i < 32; ++i) o[i] *= scale;
+          tmem_store32(tmem_o + lane_address + half * 128 + c * 32, o);
+        }
+      }
+#pragma unroll
+      for (uint32_t r8 = 0; r8 < 8; ++r8)
+        *reinterpret_cast<uint2 *>(p_ptr + swizzled(my_row, r8) + half * 8) = make_uint2(packed[r8 * 2], packed[r8 * 2 + 1]);
+      async_proxy_fence();
+      tmem_fence_before();
+      barrier_arrive(smem_u32(&ctl.p_full));
+      barrier_arrive(smem_u32(&ctl.scale_free[g & 1u]));
+    }
+
+    // ---- partial output: row i of O, un-normalised; statistics {reference exponent, sum} -------------------
+    barrier_wait(&ctl.v_free, groups - 1, error);
+    tmem_fence_after();
+    const bool failed = *error != 0;
+    const uint64_t slot = (uint64_t(lane_index) * kHeads + kv_head) * p.slot_splits + split;
+    float *out = args.partials + (slot * kRealRows + my_row) * kD + half * 128;
+#pragma unroll 1
+    for (uint32_t c = 0; c < 4; ++c) {
       float o[32];
-      tmem_load32(tmem_o + lane_address + c * 32, o);
+      tmem_load32(tmem_o + lane_address + half * 128 + c * 32, o);
       if (my_row < kRealRows) {
 #pragma unroll
         for (uint32_t i = 0; i < 32; i += 4)
           *reinterpret_cast<float4 *>(out + c * 32 + i) = make_float4(o[i] * 0.015625f, o[i + 1] * 0.015625f, o[i + 2] * 0.015625f, o[i + 3] * 0.015625f);
       }
     }
-    if (my_row < kRealRows) {
+    ctl.exchange[groups & 1u][my_row][half] = row_sum;
+    asm volatile("bar.sync %0, 64;" ::"r"(1u + quarter) : "memory");
+    if (half == 0 && my_row < kRealRows) {
       float *stats = args.statistics + (slot * kRealRows + my_row) * 2;
       stats[0] = failed ? -INFINITY : row_max * kLn2;
-      stats[1] = failed ? 0.0f : row_sum;
+      stats[1] = failed ? 0.0f : row_sum + ctl.exchange[groups & 1u][my_row][1];
     }
   }
-  if (failed && tid == 0) atomicExch(args.status, 1u);
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  tmem_fence_before();
   __syncthreads();
-  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+  if (tid == 0 && ctl.error) atomicExch(args.status, 1u);
+  if (warp == kTmaWarp) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
 }
 
 } // namespace
@@ -416,34 +542,38 @@ verify_int4_kernel(VerifyArgs args) {
 using namespace rk;
 
 // verify_attention_int4_split / verify_tree_attention_int4_split for 8 or 16 rows as a tcgen05
-// contraction (decode/paged_attention.metal:23-192). Same arguments and scratch layout as
-// rk_attention_verify_split; `status` (one device word, may be null-initialised by the caller) turns
-// non-zero when a bounded wait ran out. Merge with rk_attention_verify_reduce.
-extern "C" int rk_attention_verify_split_tc(uint32_t format, uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim,
-                                            uint32_t lanes, uint32_t row_capacity, uint32_t grid_splits, const void *queries,
-                                            float *partials, float *statistics, const rk_page_entry *const *tables,
-                                            const uint32_t *row_masks, const rk_verify_params *lane_params,
-                                            rk_kv_layer layer, uint32_t *status, void *stream) {
+// contraction (decode/paged_attention.metal:23-192). Arguments and scratch layout as
+// rk_attention_verify_split plus the pool's window (rk_window_create); `status` is one device word the
+// caller zeroes, non-zero after a bounded wait ran out. Merge with rk_attention_verify_reduce.
+extern "C" int rk_attention_verify_split_tc(const void *window, uint32_t format, uint32_t kv_heads, uint32_t query_heads,
+                                            uint32_t head_dim, uint32_t lanes, uint32_t row_capacity, uint32_t grid_splits,
+                                            const void *queries, float *partials, float *statistics,
+                                            const rk_page_entry *const *tables, const uint32_t *row_masks,
+                                            const rk_verify_params *lane_params, rk_kv_layer layer, uint32_t *status,
+                                            void *stream) {
   if (kv_heads != kHeads || query_heads != kHeads * kG || head_dim != kD || format != RK_FORMAT_INT4 ||
       (row_capacity != 8 && row_capacity != 16)) {
     set_error("rk_attention_verify_split_tc: built for int4, 4 KV heads x 24 query heads x 256, 8 or 16 rows");
     return kUnsupported;
   }
-  if (!lanes || !grid_splits || grid_splits > RK_VERIFY_MAX_SPLITS || !queries || !partials || !statistics || !tables ||
+  const auto *w = static_cast<const Window *>(window);
+  if (!w || !lanes || !grid_splits || grid_splits > RK_VERIFY_MAX_SPLITS || !queries || !partials || !statistics || !tables ||
       !lane_params || !layer.extent_pages || !status) {
     set_error("rk_attention_verify_split_tc: invalid arguments");
     return kInvalid;
   }
   constexpr size_t shared_bytes = 1024 + kTileBytes + sizeof(Control);
-  VerifyArgs args{static_cast<const uint16_t *>(queries), partials, statistics, tables, row_masks, lane_params, layer, status};
+  VerifyArgs args{static_cast<const uint16_t *>(queries), partials, statistics, tables, row_masks, lane_params, layer, w->base, status};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const dim3 grid(kHeads, grid_splits, lanes);
-  if (row_capacity == 8) {
-    if (int st = cuda_status(cudaFuncSetAttribute(verify_int4_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(shared_bytes)), "verify shared memory")) return st;
-    verify_int4_kernel<8><<<grid, kThreads, shared_bytes, s>>>(args);
-  } else {
-    if (int st = cuda_status(cudaFuncSetAttribute(verify_int4_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(shared_bytes)), "verify shared memory")) return st;
-    verify_int4_kernel<16><<<grid, kThreads, shared_bytes, s>>>(args);
-  }
+  auto launch = [&](auto kernel) -> int {
+    if (int st = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(shared_bytes)), "verify shared memory")) return st;
+    kernel<<<grid, kThreads, shared_bytes, s>>>(w->int4_head_map, args);
+    return kOk;
+  };
+  int st;
+  if (row_capacity == 8) st = row_masks ? launch(verify_int4_kernel<8, true>) : launch(verify_int4_kernel<8, false>);
+  else st = row_masks ? launch(verify_int4_kernel<16, true>) : launch(verify_int4_kernel<16, false>);
+  if (st) return st;
   return cuda_status(cudaGetLastError(), "verify tcgen05 launch");
 }

@@ -61,16 +61,41 @@ def attention_verify_split(layout: Layout, query_heads: int, lanes: int, row_cap
     lib.check(status, "rk_attention_verify_split")
 
 
-def attention_verify_split_tc(layout: Layout, query_heads: int, lanes: int, row_capacity: int, grid_splits: int,
-                              queries, partials, statistics, table_pointers, row_masks, params, layer: lib.KvLayer,
-                              status_word, stream=None) -> None:
-    """8/16-row int4 windows on the tcgen05 kernel; `status_word` is a zeroed int32 device tensor."""
-    status = lib.load().rk_attention_verify_split_tc(
-        layout.format, layout.kv_heads, query_heads, layout.head_dimension, lanes, row_capacity, grid_splits,
-        queries.data_ptr(), partials.data_ptr(), statistics.data_ptr(), table_pointers.data_ptr(),
-        row_masks.data_ptr() if row_masks is not None else None, params.data_ptr(), layer, status_word.data_ptr(),
-        _stream(stream))
-    lib.check(status, "rk_attention_verify_split_tc")
+class VerifyWindowAttention:
+    """8/16-row int4 verify windows on the tcgen05 split kernel (rk_attention_verify_split_tc).
+
+    Holds the pool window's tensor maps and the status word; partials and statistics stay the
+    caller's, in the layout of attention_verify_split, and attention_verify_reduce merges them."""
+
+    def __init__(self, layout: Layout, query_heads: int, window: tuple[int, int]):
+        self._lib = lib.load()
+        self.layout, self.query_heads = layout, query_heads
+        self._window = self._lib.rk_window_create(window[0], window[1])
+        if not self._window:
+            raise lib.RichKvError(lib.INVALID, "rk_window_create")
+        self.status_word = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def close(self) -> None:
+        if self._window:
+            self._lib.rk_window_destroy(self._window)
+            self._window = None
+
+    def __del__(self):
+        self.close()
+
+    def split(self, lanes: int, row_capacity: int, grid_splits: int, queries, partials, statistics, table_pointers,
+              row_masks, params, layer: lib.KvLayer, stream=None) -> None:
+        status = self._lib.rk_attention_verify_split_tc(
+            self._window, self.layout.format, self.layout.kv_heads, self.query_heads, self.layout.head_dimension,
+            lanes, row_capacity, grid_splits, queries.data_ptr(), partials.data_ptr(), statistics.data_ptr(),
+            table_pointers.data_ptr(), row_masks.data_ptr() if row_masks is not None else None, params.data_ptr(),
+            layer, self.status_word.data_ptr(), _stream(stream))
+        lib.check(status, "rk_attention_verify_split_tc")
+
+    def check(self) -> None:
+        """Synchronises and raises if a bounded wait ran out in a launched step."""
+        if int(self.status_word.item()) != 0:
+            raise lib.RichKvError(lib.TIMEOUT, "rk_attention_verify_split_tc: a bounded wait ran out")
 
 
 def attention_verify_reduce(layout: Layout, query_heads: int, lanes: int, row_capacity: int, partials, statistics,

@@ -70,16 +70,16 @@ def run_verify_attention_gpu(scenario: Scenario, queries: np.ndarray, active_row
     masks = dev(row_masks) if row_masks is not None else None
     layer = scenario.storage.layers()[layer_index]
     if tensor_core:
-        word = torch.zeros(1, dtype=torch.int32, device="cuda")
-        ops.attention_verify_split_tc(layout, 24, lanes, row_capacity, slot, q, partials, stats,
-                                      scenario.table_pointers, masks, d_params, layer, word)
+        runner = ops.VerifyWindowAttention(layout, 24, scenario.storage.window())
+        runner.split(lanes, row_capacity, slot, q, partials, stats, scenario.table_pointers, masks, d_params, layer)
     else:
         ops.attention_verify_split(layout, 24, lanes, row_capacity, slot, q, partials, stats, scenario.table_pointers,
                                    masks, d_params, layer)
     ops.attention_verify_reduce(layout, 24, lanes, row_capacity, partials, stats, out, d_params, output_f32=out32)
     torch.cuda.synchronize()
     if tensor_core:
-        assert int(word.item()) == 0, "a bounded wait ran out in the tcgen05 verify kernel"
+        runner.check()
+        runner.close()
     return host_u16(out), out32.cpu().numpy(), (partials, stats)
 
 
