@@ -9,22 +9,25 @@
 //
 // One CTA owns (KV head, split, lane) like the reference grid. The fused rows (rows x 6 query heads,
 // 48 or 96) are the M side of a 128-row UMMA tile (padding rows hold zero queries). The pages of the
-// split are taken in groups of 64 tokens (two pages). Roles:
-//   warp 8  (one thread)  TMA: the two pages' K and V slabs of this head (32-row boxes of the window
-//                         map, 128-byte swizzle) and their scales into a ring of three raw stages.
-//   warps 4-7             expand the raw nibbles to fp16 — exact — into the K-major swizzled operand
-//                         tiles K[token][dim] and V^T[dim][token] (an 8x8 transpose in registers), and
-//                         prepare the per-token scale triples.
-//   warp 9  (one thread)  tcgen05.mma: S = Q.K^T (16 x M128 N64 K16) and O += P.V (4 x M128 N256 K16),
+// split are taken in groups of 64 tokens (two pages). Tensor memory holds O (256 columns), S (64), the
+// fp16 probabilities P twice (2 x 32) and the query tile itself (128): both contractions take their A
+// operand from tensor memory, shared memory only carries the page data. Roles:
+//   warp 12 (one thread)  TMA: the two pages' K and V slabs of this head (32-row boxes of the window
+//                         map, 128-byte swizzle) and their scales into a ring of four raw stages.
+//   warps 8-11            expand the raw nibbles to fp16 — exact — into double-buffered K-major swizzled
+//                         operand tiles K[position][dim] and V^T[dim][position] (an 8x8 transpose in
+//                         registers), and prepare the per-token scale triples.
+//   warp 13 (one thread)  tcgen05.mma: S = Q.K^T (16 x M128 N64 K16) and O += P.V (4 x M128 N256 K16),
 //                         ordered QK(g+1) before PV(g) so the tensor pipe works while the softmax runs.
-//   warps 0-3             softmax, one thread per row = one TMEM lane: read S, fold key scale and
-//                         1/16, admit, online maximum without any shuffle, value scale folded into the
-//                         exponent, P as fp16 into its operand tile; a row whose maximum grew by more
-//                         than 2^8 rescales its O row in TMEM (rows of a warp move together).
+//   warps 0-7             softmax, two threads per row (= TMEM lane), 32 tokens each: read S, fold key
+//                         scale and 1/16, admit, online maximum (one exchange through shared memory),
+//                         value scale folded into the exponent, P as fp16 back into tensor memory; a row
+//                         whose maximum grew by more than 2^8 rescales its O row (rows of a warp move
+//                         together).
 // Key codes travel as fp16 bit patterns (u * 2^-24 with u = code + 8, high nibbles x16 with the query
 // carrying 1/16), the +8 leaves through 8 * sum(q) per row; value codes are centred exactly. Inside a
-// group the contraction index of P.V is a fixed permutation of the tokens (position 8r+j holds token
-// 8j+r), which makes every shared-memory access of the transpose conflict-free.
+// group both contractions index the tokens through one fixed permutation (position 8r+j holds token
+// 8j+r), which makes every shared-memory access of the two expansions conflict-free.
 // Every mbarrier wait is bounded and gives up at once after any wait failed; TMEM is released on
 // every path.
 #include "common.cuh"
@@ -46,19 +49,19 @@ constexpr uint32_t kSpinLimit = 1u << 20;
 constexpr float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
 
 // shared-memory tiles (bytes); every tile starts 1024-aligned
-constexpr uint32_t kQBytes = kM * kD * 2;            // 4 column blocks of [128 rows][64 elements]
 constexpr uint32_t kKBytes = kGroupTokens * kD * 2;  // 4 column blocks of [64 rows][64 elements]
 constexpr uint32_t kVBytes = kD * kGroupTokens * 2;  // 1 column block of [256 rows][64 elements]
-constexpr uint32_t kPBytes = kM * kGroupTokens * 2;  // 1 column block of [128 rows][64 elements]
 constexpr uint32_t kSlabBytes = 4096;                // one head's K (or V) of a page
-constexpr uint32_t kRawStages = 3;
+constexpr uint32_t kRawStages = 4;
 constexpr uint32_t kRawStageBytes = 17 * 1024;       // K0 | K1 | V0 | V1 | ks0 ks1 vs0 vs1 (128 B each) | pad
 constexpr uint32_t kRawScaleOffset = 4 * kSlabBytes;
-constexpr uint32_t kTileBytes = kQBytes + kKBytes + kVBytes + kPBytes + kRawStages * kRawStageBytes;
+constexpr uint32_t kTileBytes = 2 * kKBytes + 2 * kVBytes + kRawStages * kRawStageBytes;
+// tensor-memory columns
+constexpr uint32_t kTmemO = 0, kTmemS = 256, kTmemP = 320, kTmemQ = 384;
 
 struct Control {
   uint64_t raw_full[kRawStages], raw_free[kRawStages];
-  uint64_t k_full, k_free, v_full, v_free, s_full, s_free, p_full, scale_free[2];
+  uint64_t k_full[2], k_free[2], v_full[2], v_free[2], p_full[2], scale_free[2], s_full, s_free;
   uint32_t tmem_base;
   uint32_t error;
   float q_sums[kM];
@@ -117,10 +120,11 @@ __device__ __forceinline__ uint64_t umma_descriptor(uint32_t address) {
 __host__ __device__ constexpr uint32_t umma_instruction(uint32_t m, uint32_t n) {
   return (1u << 4) | (0u << 7) | (0u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+// A operand from tensor memory: lane = row, each 32-bit column two consecutive K elements.
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
   asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-               ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}"
+               ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t *barrier) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(barrier)) : "memory");
@@ -152,6 +156,13 @@ __device__ __forceinline__ void tmem_store32(uint32_t address, const float (&v)[
                  "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
                  "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
                  "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+               : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_store16(uint32_t address, const uint32_t (&v)[16]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+               ::"r"(address), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+                 "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
                : "memory");
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
@@ -200,10 +211,9 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
   uint8_t *tile_ptr = dynamic_shared + (tiles - smem_u32(dynamic_shared));
   Control &ctl = *reinterpret_cast<Control *>(tile_ptr + kTileBytes);
   volatile uint32_t *error = &ctl.error;
-  const uint32_t q_tile = tiles, k_tile = tiles + kQBytes, v_tile = k_tile + kKBytes, p_tile = v_tile + kVBytes;
-  const uint32_t raw_tile = p_tile + kPBytes;
-  uint8_t *q_ptr = tile_ptr, *k_ptr = tile_ptr + kQBytes, *v_ptr = k_ptr + kKBytes, *p_ptr = v_ptr + kVBytes;
-  const uint8_t *raw_ptr = p_ptr + kPBytes;
+  const uint32_t k_tile = tiles, v_tile = k_tile + 2 * kKBytes, raw_tile = v_tile + 2 * kVBytes; // K[2] | V[2] | raw ring
+  uint8_t *k_ptr = tile_ptr, *v_ptr = k_ptr + 2 * kKBytes;
+  const uint8_t *raw_ptr = v_ptr + 2 * kVBytes;
 
   const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const uint32_t kv_head = blockIdx.x, split = blockIdx.y, lane_index = blockIdx.z;
@@ -226,15 +236,16 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
       barrier_init(smem_u32(&ctl.raw_full[r]), 1);
       barrier_init(smem_u32(&ctl.raw_free[r]), kExpandThreads);
     }
-    barrier_init(smem_u32(&ctl.k_full), kExpandThreads);
-    barrier_init(smem_u32(&ctl.v_full), kExpandThreads);
-    barrier_init(smem_u32(&ctl.k_free), 1);
-    barrier_init(smem_u32(&ctl.v_free), 1);
+    for (uint32_t b = 0; b < 2; ++b) {
+      barrier_init(smem_u32(&ctl.k_full[b]), kExpandThreads);
+      barrier_init(smem_u32(&ctl.v_full[b]), kExpandThreads);
+      barrier_init(smem_u32(&ctl.k_free[b]), 1);
+      barrier_init(smem_u32(&ctl.v_free[b]), 1);
+      barrier_init(smem_u32(&ctl.p_full[b]), kSoftmaxThreads);
+      barrier_init(smem_u32(&ctl.scale_free[b]), kSoftmaxThreads);
+    }
     barrier_init(smem_u32(&ctl.s_full), 1);
     barrier_init(smem_u32(&ctl.s_free), kSoftmaxThreads);
-    barrier_init(smem_u32(&ctl.p_full), kSoftmaxThreads);
-    barrier_init(smem_u32(&ctl.scale_free[0]), kSoftmaxThreads);
-    barrier_init(smem_u32(&ctl.scale_free[1]), kSoftmaxThreads);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     ctl.error = 0;
   }
@@ -242,38 +253,49 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl.tmem_base)), "r"(512u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  // Query tile: row m = row*6 + g of this (lane, head); fp16, chunk order (0,4,1,5,2,6,3,7), odd dims /16.
-  {
-    const uint16_t *queries = args.queries + (uint64_t(lane_index) * kHeads + kv_head) * (uint64_t(RK_VERIFY_CHUNK_STRIDE) * kG * kD);
-    for (uint32_t item = tid; item < kM * 2; item += kThreads) { // half a row (16 chunks) per item
-      const uint32_t row = item >> 1;
-      const bool real = row < p.active_rows * kG;
-      float q_sum = 0.0f; // over the fp16 values the tensor core will see, for the +8 correction
-      for (uint32_t c = (item & 1u) * 16; c < (item & 1u) * 16 + 16; ++c) { // chunk c = dims 8c..8c+7
-        uint4 raw = make_uint4(0, 0, 0, 0);
-        if (real) raw = __ldg(reinterpret_cast<const uint4 *>(queries + uint64_t(row) * kD + 8 * c));
-        const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
-        float d[8];
-#pragma unroll
-        for (uint32_t i = 0; i < 4; ++i) { d[2 * i] = bf16_bits_to_float(words[i] & 0xffffu); d[2 * i + 1] = bf16_bits_to_float(words[i] >> 16); }
-        const uint4 chunk = make_uint4(pack_half2(d[0], d[4]), pack_half2(d[1] * 0.0625f, d[5] * 0.0625f),
-                                       pack_half2(d[2], d[6]), pack_half2(d[3] * 0.0625f, d[7] * 0.0625f));
-        *reinterpret_cast<uint4 *>(q_ptr + (c >> 3) * (kM * 128) + swizzled(row, c & 7u)) = chunk;
-        const __half2 *h = reinterpret_cast<const __half2 *>(&chunk);
-        q_sum += __low2float(h[0]) + __high2float(h[0]) + __low2float(h[2]) + __high2float(h[2]) +
-                 16.0f * (__low2float(h[1]) + __high2float(h[1]) + __low2float(h[3]) + __high2float(h[3]));
-      }
-      q_sum += __shfl_xor_sync(0xffffffffu, q_sum, 1); // the two halves of a row sit in neighbouring lanes
-      if ((item & 1u) == 0) ctl.q_sums[row] = q_sum;
-    }
-  }
-  async_proxy_fence();
   tmem_fence_before();
   __syncthreads();
   tmem_fence_after();
   const uint32_t tmem = ctl.tmem_base;
-  const uint32_t tmem_s = tmem, tmem_o = tmem + 64;
+  const uint32_t tmem_o = tmem + kTmemO, tmem_s = tmem + kTmemS, tmem_p = tmem + kTmemP, tmem_q = tmem + kTmemQ;
   const uint32_t data_bytes = kPageTokens * kHeads * kD / 2, scale_bytes = kPageTokens * kHeads * 4;
+
+  // Query tile into tensor memory: thread (row, half) converts half a row (128 dims = 64 columns): fp16,
+  // element order (0,4,1,5,2,6,3,7) inside every 8 dims, dims 1,5,3,7 divided by 16.
+  if (warp < kSoftmaxWarps) {
+    const uint32_t quarter = warp & 3u, half = warp >> 2, row = quarter * 32 + lane;
+    const uint16_t *queries = args.queries + (uint64_t(lane_index) * kHeads + kv_head) * (uint64_t(RK_VERIFY_CHUNK_STRIDE) * kG * kD);
+    const bool real = row < p.active_rows * kG;
+    float q_sum = 0.0f; // over the fp16 values the tensor core will see, for the +8 correction
+#pragma unroll 1
+    for (uint32_t part = 0; part < 2; ++part) { // 32 columns = 8 chunks of 8 dims
+      float columns[32];
+#pragma unroll
+      for (uint32_t c = 0; c < 8; ++c) {
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if (real) raw = __ldg(reinterpret_cast<const uint4 *>(queries + uint64_t(row) * kD + half * 128 + part * 64 + 8 * c));
+        const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+        float d[8];
+#pragma unroll
+        for (uint32_t i = 0; i < 4; ++i) { d[2 * i] = bf16_bits_to_float(words[i] & 0xffffu); d[2 * i + 1] = bf16_bits_to_float(words[i] >> 16); }
+        const uint32_t chunk[4] = {pack_half2(d[0], d[4]), pack_half2(d[1] * 0.0625f, d[5] * 0.0625f),
+                                   pack_half2(d[2], d[6]), pack_half2(d[3] * 0.0625f, d[7] * 0.0625f)};
+#pragma unroll
+        for (uint32_t i = 0; i < 4; ++i) {
+          const __half2 h = *reinterpret_cast<const __half2 *>(&chunk[i]);
+          q_sum += ((i & 1u) ? 16.0f : 1.0f) * (__low2float(h) + __high2float(h));
+          columns[c * 4 + i] = __uint_as_float(chunk[i]);
+        }
+      }
+      tmem_store32(tmem_q + ((quarter * 32u) << 16) + half * 64 + part * 32, columns);
+    }
+    ctl.exchange[0][row][half] = q_sum;
+  }
+  tmem_fence_before();
+  __syncthreads();
+  tmem_fence_after();
+  if (tid < kM) ctl.q_sums[tid] = ctl.exchange[0][tid][0] + ctl.exchange[0][tid][1];
+  __syncthreads();
 
   if (warp == kTmaWarp) {
     // ---- TMA producer ---------------------------------------------------------------------------------
@@ -317,28 +339,28 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
     if (lane == 0) {
       const uint32_t idesc_qk = umma_instruction(kM, kGroupTokens), idesc_pv = umma_instruction(kM, kD);
       auto scores = [&](uint32_t g) {
-        barrier_wait(&ctl.k_full, g, error);
+        const uint32_t b = g & 1u;
+        barrier_wait(&ctl.k_full[b], g >> 1, error);
         if (g) barrier_wait(&ctl.s_free, g - 1, error);
         tmem_fence_after();
 #pragma unroll
-        for (uint32_t j = 0; j < 16; ++j) {
-          const uint64_t a = umma_descriptor(q_tile + (j >> 2) * (kM * 128) + (j & 3u) * 32);
-          const uint64_t b = umma_descriptor(k_tile + (j >> 2) * (kGroupTokens * 128) + (j & 3u) * 32);
-          umma_f16(tmem_s, a, b, idesc_qk, j ? 1u : 0u);
-        }
+        for (uint32_t j = 0; j < 16; ++j)
+          umma_f16_ts(tmem_s, tmem_q + 8 * j, umma_descriptor(k_tile + b * kKBytes + (j >> 2) * (kGroupTokens * 128) + (j & 3u) * 32),
+                      idesc_qk, j ? 1u : 0u);
         umma_commit(&ctl.s_full);
-        umma_commit(&ctl.k_free);
+        umma_commit(&ctl.k_free[b]);
       };
       scores(0);
       for (uint32_t g = 0; g < groups; ++g) {
+        const uint32_t b = g & 1u;
         if (g + 1 < groups) scores(g + 1);
-        barrier_wait(&ctl.v_full, g, error);
-        barrier_wait(&ctl.p_full, g, error);
+        barrier_wait(&ctl.v_full[b], g >> 1, error);
+        barrier_wait(&ctl.p_full[b], g >> 1, error);
         tmem_fence_after();
 #pragma unroll
         for (uint32_t j = 0; j < 4; ++j)
-          umma_f16(tmem_o, umma_descriptor(p_tile + j * 32), umma_descriptor(v_tile + j * 32), idesc_pv, (g || j) ? 1u : 0u);
-        umma_commit(&ctl.v_free);
+          umma_f16_ts(tmem_o, tmem_p + b * 32 + 8 * j, umma_descriptor(v_tile + b * kVBytes + j * 32), idesc_pv, (g || j) ? 1u : 0u);
+        umma_commit(&ctl.v_free[b]);
       }
     }
   } else if (warp >= kSoftmaxWarps) {
@@ -348,45 +370,49 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
     const uint32_t key_low = register_constant(0x00080008u), key_high = register_constant(0x00800080u);
     const uint32_t value_low = register_constant(0x64086408u), value_high = register_constant(0x64806480u);
     for (uint32_t g = 0; g < groups; ++g) {
-      const uint32_t r = g % kRawStages, use = g / kRawStages;
+      const uint32_t r = g % kRawStages, use = g / kRawStages, b = g & 1u;
       const uint32_t group_pages = min(2u, page_end - (page_begin + 2 * g));
       const uint8_t *raw = raw_ptr + r * kRawStageBytes;
       barrier_wait(&ctl.raw_full[r], use, error);
-      // per-token scale triples; tokens of an absent page get harmless zeros
+      // per-position scale triples; tokens of an absent page get harmless zeros
       if (e < kGroupTokens) {
-        if (g >= 2) barrier_wait(&ctl.scale_free[g & 1u], (g >> 1) - 1, error);
-        const uint32_t local = e >> 5, token = e & 31u;
+        if (g >= 2) barrier_wait(&ctl.scale_free[b], (g >> 1) - 1, error);
+        const uint32_t token = 8 * (e & 7u) + (e >> 3), local = token >> 5;
         float4 triple = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         if (local < group_pages) {
-          const float ks = reinterpret_cast<const float *>(raw + kRawScaleOffset)[local * 32 + token];
-          const float vs = fmaxf(reinterpret_cast<const float *>(raw + kRawScaleOffset)[(2 + local) * 32 + token], 9.094947e-13f); // 2^-40
+          const float ks = reinterpret_cast<const float *>(raw + kRawScaleOffset)[token];
+          const float vs = fmaxf(reinterpret_cast<const float *>(raw + kRawScaleOffset)[64 + token], 9.094947e-13f); // 2^-40
           triple = make_float4(ks, log2_fast(vs), __fdividef(0.015625f, vs), 0.0f);
         }
-        ctl.scales[g & 1u][e] = triple;
+        ctl.scales[b][e] = triple;
       }
-      if (g) barrier_wait(&ctl.k_free, g - 1, error);
-      // keys: a thread takes a raw 16-byte chunk (32 dims of one token) = four operand chunks. The
-      // eight lanes of an access phase differ in token % 8: conflict-free on both swizzled sides.
+      if (g >= 2) barrier_wait(&ctl.k_free[b], (g >> 1) - 1, error);
+      // keys: a thread takes a raw 16-byte chunk (32 dims of one token) = four operand chunks; the token
+      // goes to row `position`. The eight lanes of an access phase take tokens 8k + t and chunks c0 ^ k:
+      // conflict-free on the swizzled raw side and on the swizzled operand side.
+      uint8_t *k_stage = k_ptr + b * kKBytes;
 #pragma unroll
       for (uint32_t i = 0; i < 4; ++i) {
         const uint32_t item = e + i * kExpandThreads;
-        const uint32_t token = (item & 7u) | ((item >> 6) << 3), c = (item >> 3) & 7u;
+        const uint32_t k8 = item & 7u, c = ((item >> 3) & 7u) ^ k8, t = item >> 6;
+        const uint32_t token = 8 * k8 + t, position = 8 * t + k8;
         const uint4 x = *reinterpret_cast<const uint4 *>(raw + (token >> 5) * kSlabBytes + swizzled(token & 31u, c));
         const uint32_t words[4] = {x.x, x.y, x.z, x.w};
-        uint8_t *block = k_ptr + (c >> 1) * (kGroupTokens * 128);
+        uint8_t *block = k_stage + (c >> 1) * (kGroupTokens * 128);
 #pragma unroll
         for (uint32_t w = 0; w < 4; ++w) {
           const uint32_t y = words[w] >> 8;
-          *reinterpret_cast<uint4 *>(block + swizzled(token, ((c & 1u) << 2) + w)) =
+          *reinterpret_cast<uint4 *>(block + swizzled(position, ((c & 1u) << 2) + w)) =
               make_uint4(and_xor(words[w], low_mask, key_low), and_xor(words[w], high_mask, key_high),
                          and_xor(y, low_mask, key_low), and_xor(y, high_mask, key_high));
         }
       }
       async_proxy_fence();
-      barrier_arrive(smem_u32(&ctl.k_full));
-      if (g) barrier_wait(&ctl.v_free, g - 1, error);
+      barrier_arrive(smem_u32(&ctl.k_full[b]));
+      if (g >= 2) barrier_wait(&ctl.v_free[b], (g >> 1) - 1, error);
       // values: thread = (r8, word w of 8 dims) takes tokens 8j + r8, j = 0..7, and transposes 8x8 in
       // registers: each dim gets a 16-byte run of eight tokens at contraction positions 8*r8 + j.
+      uint8_t *v_stage = v_ptr + b * kVBytes;
 #pragma unroll
       for (uint32_t half = 0; half < 2; ++half) {
         const uint32_t unit = e + half * kExpandThreads, r8 = unit & 7u, w = unit >> 3;
@@ -395,26 +421,26 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
         for (uint32_t j = 0; j < 8; ++j)
           x[j] = *reinterpret_cast<const uint32_t *>(raw + (2 + (j >> 2)) * kSlabBytes + swizzled(8 * (j & 3u) + r8, w >> 2) + (w & 3u) * 4);
 #pragma unroll
-        for (uint32_t b = 0; b < 4; ++b) { // byte b of each word = dims 8w+2b (low nibble), 8w+2b+1 (high nibble)
+        for (uint32_t byte = 0; byte < 4; ++byte) { // byte of each word = dims 8w+2*byte (low nibble), +1 (high nibble)
           uint32_t lo[4], hi[4];
-          const uint32_t selector = b | (b << 4) | ((4 + b) << 8) | ((4 + b) << 12);
+          const uint32_t selector = byte | (byte << 4) | ((4 + byte) << 8) | ((4 + byte) << 12);
 #pragma unroll
           for (uint32_t pair = 0; pair < 4; ++pair) {
             const uint32_t joined = __byte_perm(x[2 * pair], x[2 * pair + 1], selector);
             lo[pair] = sub_f16x2(and_xor(joined, low_mask, value_low), value_low);                                   // 1024+u - 1032
             hi[pair] = fma_f16x2(and_xor(joined, high_mask, value_high), 0x2C002C00u /* 1/16 */, 0xD480D480u /* -72 */); // (1024+16u)/16 - 72
           }
-          const uint32_t dim = 8 * w + 2 * b;
-          *reinterpret_cast<uint4 *>(v_ptr + swizzled(dim, r8)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-          *reinterpret_cast<uint4 *>(v_ptr + swizzled(dim + 1, r8)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+          const uint32_t dim = 8 * w + 2 * byte;
+          *reinterpret_cast<uint4 *>(v_stage + swizzled(dim, r8)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+          *reinterpret_cast<uint4 *>(v_stage + swizzled(dim + 1, r8)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
         }
       }
       async_proxy_fence();
-      barrier_arrive(smem_u32(&ctl.v_full));
+      barrier_arrive(smem_u32(&ctl.v_full[b]));
       barrier_arrive(smem_u32(&ctl.raw_free[r]));
     }
   } else {
-    // ---- softmax: two threads per fused row (= TMEM lane), 32 tokens of the group each -----------------------
+    // ---- softmax: two threads per fused row (= TMEM lane), 32 contraction positions of the group each ----------
     const uint32_t quarter = warp & 3u, half = warp >> 2;
     const uint32_t my_row = quarter * 32 + lane;
     const float score_scale = rk_score_scale(p.score_scale, kD) * kLog2e;
@@ -427,12 +453,14 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
     float row_max = -1.0e30f, row_sum = 0.0f; // row_sum: this thread's tokens only
 
     for (uint32_t g = 0; g < groups; ++g) {
-      const uint32_t first = page_begin + 2 * g;
-      const uint32_t token_base = first * kPageTokens + half * 32;
-      // tokens of this half that exist in the group (a split may end inside it) and pass the causal rule
-      const uint32_t present = min(2u, page_end - first) > half ? 32u : 0u;
+      const uint32_t first = page_begin + 2 * g, b = g & 1u;
+      const uint32_t token_base = first * kPageTokens;
+      // tokens of the group that exist (a split may end inside it) and, on a chain, pass the causal rule;
+      // position 32*half + i holds token 8*(i%8) + 4*half + i/8: compare i's part against limit - 4*half
+      const uint32_t present = min(2u, page_end - first) * kPageTokens;
       const uint32_t limit = kTree ? present : min(present, causal_limit > token_base ? causal_limit - token_base : 0u);
-      const float4 *triples = ctl.scales[g & 1u] + half * 32;
+      const int32_t bound = int32_t(limit) - int32_t(4 * half);
+      const float4 *triples = ctl.scales[b] + half * 32;
       barrier_wait(&ctl.s_full, g, error);
       tmem_fence_after();
       float scores[32];
@@ -442,21 +470,22 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
 
       float group_max = -INFINITY;
 #pragma unroll
-      for (uint32_t t = 0; t < 32; ++t) {
-        bool admitted = t < limit;
+      for (uint32_t i = 0; i < 32; ++i) {
+        const int32_t part = int32_t(8 * (i & 7u) + (i >> 3));
+        bool admitted = part < bound;
         if (kTree) {
-          const uint32_t token = token_base + t;
+          const uint32_t token = token_base + uint32_t(part) + 4 * half;
           admitted = admitted && (token < p.committed_tokens || (token < visible && ((tree_mask >> (token - p.committed_tokens)) & 1u)));
         }
-        const float4 triple = triples[t];
-        const float s = fmaf(scores[t], row_factor, row_offset) * triple.x + triple.y; // score + log2(value scale)
-        scores[t] = admitted ? s : -INFINITY;
-        group_max = fmaxf(group_max, scores[t]);
+        const float4 triple = triples[i];
+        const float s = fmaf(scores[i], row_factor, row_offset) * triple.x + triple.y; // score + log2(value scale)
+        scores[i] = admitted ? s : -INFINITY;
+        group_max = fmaxf(group_max, scores[i]);
       }
       // the row's other half
-      ctl.exchange[g & 1u][my_row][half] = group_max;
+      ctl.exchange[b][my_row][half] = group_max;
       asm volatile("bar.sync %0, 64;" ::"r"(1u + quarter) : "memory");
-      group_max = fmaxf(group_max, ctl.exchange[g & 1u][my_row][half ^ 1u]);
+      group_max = fmaxf(group_max, ctl.exchange[b][my_row][half ^ 1u]);
       // Lazy rescale: the reference exponent only moves when the maximum grew by more than 2^8, so the
       // fp16 probabilities stay below 2^(8+6); rows of a warp move together (collective TMEM access).
       const bool grow = group_max > row_max + 8.0f;
@@ -467,26 +496,19 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
         row_sum *= scale;
       }
       const float exponent_base = row_max - 6.0f;
-      // position 8*r8 + j of the contraction holds token 8*j + r8 (the order the value tile is built in):
-      // this half owns j = 4*half .. 4*half+3 of every 16-byte run, i.e. 8 bytes of each
       uint32_t packed[16];
 #pragma unroll
-      for (uint32_t r8 = 0; r8 < 8; ++r8) {
+      for (uint32_t c = 0; c < 16; ++c) {
+        float w[2];
 #pragma unroll
-        for (uint32_t i = 0; i < 2; ++i) {
-          float w[2];
-#pragma unroll
-          for (uint32_t h = 0; h < 2; ++h) {
-            const uint32_t t = 8 * (2 * i + h) + r8;
-            w[h] = exp2_fast(scores[t] - exponent_base);     // 0 for a masked token
-            row_sum = fmaf(w[h], triples[t].z, row_sum);     // 2^(score - row_max)
-          }
-          packed[r8 * 2 + i] = pack_half2(w[0], w[1]);
+        for (uint32_t h = 0; h < 2; ++h) {
+          w[h] = exp2_fast(scores[2 * c + h] - exponent_base);     // 0 for a masked token
+          row_sum = fmaf(w[h], triples[2 * c + h].z, row_sum);     // 2^(score - row_max)
         }
+        packed[c] = pack_half2(w[0], w[1]);
       }
-      // O and the P tile belong to the previous group's P.V until it has landed
-      if (g) barrier_wait(&ctl.v_free, g - 1, error);
-      if (g && __any_sync(0xffffffffu, grow)) { // this half rescales its 128 columns of O
+      if (g && __any_sync(0xffffffffu, grow)) { // this half rescales its 128 columns of O once P.V(g-1) has landed
+        barrier_wait(&ctl.v_free[b ^ 1u], (g - 1) >> 1, error);
         tmem_fence_after();
 #pragma unroll 1
         for (uint32_t c = 0; c < 4; ++c) {
@@ -497,17 +519,17 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
           tmem_store32(tmem_o + lane_address + half * 128 + c * 32, o);
         }
       }
-#pragma unroll
-      for (uint32_t r8 = 0; r8 < 8; ++r8)
-        *reinterpret_cast<uint2 *>(p_ptr + swizzled(my_row, r8) + half * 8) = make_uint2(packed[r8 * 2], packed[r8 * 2 + 1]);
-      async_proxy_fence();
+      // P buffer b belonged to P.V(g-2)
+      if (g >= 2) barrier_wait(&ctl.v_free[b], (g >> 1) - 1, error);
+      tmem_fence_after();
+      tmem_store16(tmem_p + lane_address + b * 32 + half * 16, packed);
       tmem_fence_before();
-      barrier_arrive(smem_u32(&ctl.p_full));
-      barrier_arrive(smem_u32(&ctl.scale_free[g & 1u]));
+      barrier_arrive(smem_u32(&ctl.p_full[b]));
+      barrier_arrive(smem_u32(&ctl.scale_free[b]));
     }
 
     // ---- partial output: row i of O, un-normalised; statistics {reference exponent, sum} -------------------
-    barrier_wait(&ctl.v_free, groups - 1, error);
+    barrier_wait(&ctl.v_free[(groups - 1) & 1u], (groups - 1) >> 1, error);
     tmem_fence_after();
     const bool failed = *error != 0;
     const uint64_t slot = (uint64_t(lane_index) * kHeads + kv_head) * p.slot_splits + split;
