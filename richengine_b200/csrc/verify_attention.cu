@@ -38,11 +38,13 @@
 namespace rk {
 namespace {
 
-constexpr uint32_t kSoftmaxWarps = 8, kExpandWarps = 4; // softmax: two warps per 32-row quarter, 32 tokens each
+constexpr uint32_t kSoftmaxWarps = 8;  // two warps per 32-row quarter, 32 tokens of a group each
+constexpr uint32_t kExpandWarps = 8;   // two teams of four warps: team t expands the groups g = t (mod 2) into stage t
 constexpr uint32_t kSoftmaxThreads = kSoftmaxWarps * 32;
-constexpr uint32_t kExpandThreads = kExpandWarps * 32;
-constexpr uint32_t kThreads = (kSoftmaxWarps + kExpandWarps + 2) * 32;
-constexpr uint32_t kTmaWarp = kSoftmaxWarps + kExpandWarps, kMmaWarp = kTmaWarp + 1;
+constexpr uint32_t kExpandThreads = kExpandWarps * 32 / 2; // threads of one team
+constexpr uint32_t kThreads = (kSoftmaxWarps + kExpandWarps + 3) * 32;
+constexpr uint32_t kTmaWarp = kSoftmaxWarps + kExpandWarps, kScoreWarp = kTmaWarp + 1, kValueWarp = kTmaWarp + 2;
+constexpr uint32_t kScaleStages = 4;
 constexpr uint32_t kGroupTokens = 64;
 constexpr uint32_t kM = 128, kD = 256, kG = 6, kHeads = 4;
 constexpr uint32_t kSpinLimit = 1u << 20;
@@ -57,16 +59,16 @@ constexpr uint32_t kRawStageBytes = 17 * 1024;       // K0 | K1 | V0 | V1 | ks0 
 constexpr uint32_t kRawScaleOffset = 4 * kSlabBytes;
 constexpr uint32_t kTileBytes = 2 * kKBytes + 2 * kVBytes + kRawStages * kRawStageBytes;
 // tensor-memory columns
-constexpr uint32_t kTmemO = 0, kTmemS = 256, kTmemP = 320, kTmemQ = 384;
+constexpr uint32_t kTmemO = 0, kTmemS = 256, kTmemQ = 384; // S twice (64 columns each); P(g) overwrites the first half of S(g)
 
 struct Control {
   uint64_t raw_full[kRawStages], raw_free[kRawStages];
-  uint64_t k_full[2], k_free[2], v_full[2], v_free[2], p_full[2], scale_free[2], s_full, s_free;
+  uint64_t k_full[2], k_free[2], v_full[2], v_free[2], s_full[2], p_full[2], scale_free[kScaleStages];
   uint32_t tmem_base;
   uint32_t error;
   float q_sums[kM];
   float exchange[2][kM][2];       // the two half-row maxima of a group (and, at the end, the half-row sums)
-  float4 scales[2][kGroupTokens]; // {key scale, log2 value scale, 2^-6 / value scale, -}
+  float4 scales[kScaleStages][kGroupTokens]; // {key scale, log2 value scale, 2^-6 / value scale, -}
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -90,10 +92,10 @@ __device__ __forceinline__ bool barrier_try(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ void barrier_wait(uint64_t *barrier, uint32_t count, volatile uint32_t *error) {
   const uint32_t bar = smem_u32(barrier), parity = count & 1u;
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (barrier_try(bar, parity)) return;
-    if (i > 8) {
+    if (barrier_try(bar, parity)) return; // try_wait itself suspends the thread for a while
+    if ((i & 63u) == 63u) {
       if (*error) return;
-      __nanosleep(20);
+      if (i > 4096) __nanosleep(256);
     }
   }
   *error = 1;
@@ -119,6 +121,13 @@ __device__ __forceinline__ uint64_t umma_descriptor(uint32_t address) {
 // kind::f16 instruction descriptor: fp16 x fp16 -> fp32, both operands K-major.
 __host__ __device__ constexpr uint32_t umma_instruction(uint32_t m, uint32_t n) {
   return (1u << 4) | (0u << 7) | (0u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+// True in exactly one lane of a converged warp; unlike a test of the lane index it keeps the surrounding
+// control flow warp-uniform, so descriptors and addresses stay on the uniform datapath.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(pred));
+  return pred != 0;
 }
 // A operand from tensor memory: lane = row, each 32-bit column two consecutive K elements.
 __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
@@ -190,6 +199,12 @@ __device__ __forceinline__ uint32_t swizzled(uint32_t row, uint32_t chunk) { ret
 // an int4 word yields its nibble pairs; queries and keys use the same order, so the contraction is
 // unchanged. Dims 1,5,3,7 of each 8 carry the 16x of a high nibble on the key side, 1/16 on the query.
 
+#ifdef RK_EXP_TRACE
+#define TRACE(role, g, k) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (g) < 64) args.status[16 + ((role) * 64 + (g)) * 8 + (k)] = uint32_t(clock64()); } while (0)
+#else
+#define TRACE(role, g, k) do { } while (0)
+#endif
+
 struct VerifyArgs {
   const uint16_t *queries;
   float *partials;
@@ -241,11 +256,10 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
       barrier_init(smem_u32(&ctl.v_full[b]), kExpandThreads);
       barrier_init(smem_u32(&ctl.k_free[b]), 1);
       barrier_init(smem_u32(&ctl.v_free[b]), 1);
+      barrier_init(smem_u32(&ctl.s_full[b]), 1);
       barrier_init(smem_u32(&ctl.p_full[b]), kSoftmaxThreads);
-      barrier_init(smem_u32(&ctl.scale_free[b]), kSoftmaxThreads);
     }
-    barrier_init(smem_u32(&ctl.s_full), 1);
-    barrier_init(smem_u32(&ctl.s_free), kSoftmaxThreads);
+    for (uint32_t b = 0; b < kScaleStages; ++b) barrier_init(smem_u32(&ctl.scale_free[b]), kSoftmaxThreads);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     ctl.error = 0;
   }
@@ -257,7 +271,7 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
   __syncthreads();
   tmem_fence_after();
   const uint32_t tmem = ctl.tmem_base;
-  const uint32_t tmem_o = tmem + kTmemO, tmem_s = tmem + kTmemS, tmem_p = tmem + kTmemP, tmem_q = tmem + kTmemQ;
+  const uint32_t tmem_o = tmem + kTmemO, tmem_s = tmem + kTmemS, tmem_q = tmem + kTmemQ;
   const uint32_t data_bytes = kPageTokens * kHeads * kD / 2, scale_bytes = kPageTokens * kHeads * 4;
 
   // Query tile into tensor memory: thread (row, half) converts half a row (128 dims = 64 columns): fp16,
@@ -309,7 +323,9 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
           next[0] = table[first + 2];
           next[1] = first + 3 < page_end ? table[first + 3] : 0;
         }
+        TRACE(0, g, 0);
         if (use) barrier_wait(&ctl.raw_free[r], use - 1, error);
+        TRACE(0, g, 1);
         const uint32_t full = smem_u32(&ctl.raw_full[r]), stage = raw_tile + r * kRawStageBytes;
         barrier_expect(full, group_pages * (2 * kSlabBytes + 256));
 #pragma unroll
@@ -334,49 +350,69 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
         for (uint32_t i = 0; i < kSpinLimit && !barrier_try(bar, parity); ++i) __nanosleep(64);
       }
     }
-  } else if (warp == kMmaWarp) {
-    // ---- tensor-core issue --------------------------------------------------------------------------------
-    if (lane == 0) {
-      const uint32_t idesc_qk = umma_instruction(kM, kGroupTokens), idesc_pv = umma_instruction(kM, kD);
-      auto scores = [&](uint32_t g) {
-        const uint32_t b = g & 1u;
-        barrier_wait(&ctl.k_full[b], g >> 1, error);
-        if (g) barrier_wait(&ctl.s_free, g - 1, error);
-        tmem_fence_after();
+  } else if (warp == kScoreWarp) {
+    // ---- tensor-core issue, S = Q.K^T: S buffer g&1 is free once PV(g-2), which read P(g-2) from it, has landed ----
+    // The whole warp walks the loop (uniform control flow); one elected lane issues.
+    const uint32_t idesc_qk = umma_instruction(kM, kGroupTokens);
+    // a descriptor advances by (bytes >> 4) in its low word; nothing here carries out of the 14-bit field
+    const uint64_t k_desc0 = umma_descriptor(k_tile), k_desc1 = umma_descriptor(k_tile + kKBytes);
+    for (uint32_t g = 0; g < groups; ++g) {
+      const uint32_t b = g & 1u;
+      if (lane == 0) TRACE(1, g, 0);
+      barrier_wait(&ctl.k_full[b], g >> 1, error);
+      if (g >= 2) barrier_wait(&ctl.v_free[b], (g >> 1) - 1, error);
+      if (lane == 0) TRACE(1, g, 1);
+      tmem_fence_after();
+      const uint64_t desc = b ? k_desc1 : k_desc0;
+      const uint32_t target = tmem_s + b * 64;
+      if (elect_one()) {
 #pragma unroll
         for (uint32_t j = 0; j < 16; ++j)
-          umma_f16_ts(tmem_s, tmem_q + 8 * j, umma_descriptor(k_tile + b * kKBytes + (j >> 2) * (kGroupTokens * 128) + (j & 3u) * 32),
-                      idesc_qk, j ? 1u : 0u);
-        umma_commit(&ctl.s_full);
+          umma_f16_ts(target, tmem_q + 8 * j, desc + (((j >> 2) * (kGroupTokens * 128) + (j & 3u) * 32) >> 4), idesc_qk, j ? 1u : 0u);
+        umma_commit(&ctl.s_full[b]);
         umma_commit(&ctl.k_free[b]);
-      };
-      scores(0);
-      for (uint32_t g = 0; g < groups; ++g) {
-        const uint32_t b = g & 1u;
-        if (g + 1 < groups) scores(g + 1);
-        barrier_wait(&ctl.v_full[b], g >> 1, error);
-        barrier_wait(&ctl.p_full[b], g >> 1, error);
-        tmem_fence_after();
+      }
+      __syncwarp();
+      if (lane == 0) TRACE(1, g, 2);
+    }
+  } else if (warp == kValueWarp) {
+    // ---- tensor-core issue, O += P.V ------------------------------------------------------------------------------
+    const uint32_t idesc_pv = umma_instruction(kM, kD);
+    const uint64_t v_desc0 = umma_descriptor(v_tile), v_desc1 = umma_descriptor(v_tile + kVBytes);
+    for (uint32_t g = 0; g < groups; ++g) {
+      const uint32_t b = g & 1u;
+      if (lane == 0) TRACE(1, g, 3);
+      barrier_wait(&ctl.v_full[b], g >> 1, error);
+      if (lane == 0) TRACE(1, g, 4);
+      barrier_wait(&ctl.p_full[b], g >> 1, error);
+      if (lane == 0) TRACE(1, g, 5);
+      tmem_fence_after();
+      const uint64_t desc = b ? v_desc1 : v_desc0;
+      const uint32_t source = tmem_s + b * 64;
+      if (elect_one()) {
 #pragma unroll
-        for (uint32_t j = 0; j < 4; ++j)
-          umma_f16_ts(tmem_o, tmem_p + b * 32 + 8 * j, umma_descriptor(v_tile + b * kVBytes + j * 32), idesc_pv, (g || j) ? 1u : 0u);
+        for (uint32_t j = 0; j < 4; ++j) umma_f16_ts(tmem_o, source + 8 * j, desc + ((j * 32) >> 4), idesc_pv, (g || j) ? 1u : 0u);
         umma_commit(&ctl.v_free[b]);
       }
+      __syncwarp();
+      if (lane == 0) TRACE(1, g, 6);
     }
   } else if (warp >= kSoftmaxWarps) {
     // ---- expanders: raw nibbles -> fp16 operand tiles ---------------------------------------------------------
-    const uint32_t e = tid - kSoftmaxThreads;
+    const uint32_t team = (warp - kSoftmaxWarps) >> 2, e = tid - kSoftmaxThreads - team * kExpandThreads;
     const uint32_t low_mask = register_constant(0x000F000Fu), high_mask = register_constant(0x00F000F0u);
     const uint32_t key_low = register_constant(0x00080008u), key_high = register_constant(0x00800080u);
     const uint32_t value_low = register_constant(0x64086408u), value_high = register_constant(0x64806480u);
-    for (uint32_t g = 0; g < groups; ++g) {
-      const uint32_t r = g % kRawStages, use = g / kRawStages, b = g & 1u;
+    for (uint32_t g = team; g < groups; g += 2) {
+      const uint32_t r = g % kRawStages, use = g / kRawStages, b = team;
       const uint32_t group_pages = min(2u, page_end - (page_begin + 2 * g));
       const uint8_t *raw = raw_ptr + r * kRawStageBytes;
+      if (e == 0) TRACE(2, g, 0);
       barrier_wait(&ctl.raw_full[r], use, error);
+      if (e == 0) TRACE(2, g, 1);
       // per-position scale triples; tokens of an absent page get harmless zeros
       if (e < kGroupTokens) {
-        if (g >= 2) barrier_wait(&ctl.scale_free[b], (g >> 1) - 1, error);
+        if (g >= kScaleStages) barrier_wait(&ctl.scale_free[g % kScaleStages], g / kScaleStages - 1, error);
         const uint32_t token = 8 * (e & 7u) + (e >> 3), local = token >> 5;
         float4 triple = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         if (local < group_pages) {
@@ -384,13 +420,17 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
           const float vs = fmaxf(reinterpret_cast<const float *>(raw + kRawScaleOffset)[64 + token], 9.094947e-13f); // 2^-40
           triple = make_float4(ks, log2_fast(vs), __fdividef(0.015625f, vs), 0.0f);
         }
-        ctl.scales[b][e] = triple;
+        ctl.scales[g % kScaleStages][e] = triple;
       }
       if (g >= 2) barrier_wait(&ctl.k_free[b], (g >> 1) - 1, error);
+      if (e == 0) TRACE(2, g, 2);
       // keys: a thread takes a raw 16-byte chunk (32 dims of one token) = four operand chunks; the token
       // goes to row `position`. The eight lanes of an access phase take tokens 8k + t and chunks c0 ^ k:
       // conflict-free on the swizzled raw side and on the swizzled operand side.
       uint8_t *k_stage = k_ptr + b * kKBytes;
+#ifdef RK_EXP_NO_EXPAND
+      if (error == nullptr)
+#endif
 #pragma unroll
       for (uint32_t i = 0; i < 4; ++i) {
         const uint32_t item = e + i * kExpandThreads;
@@ -409,10 +449,15 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
       }
       async_proxy_fence();
       barrier_arrive(smem_u32(&ctl.k_full[b]));
+      if (e == 0) TRACE(2, g, 3);
       if (g >= 2) barrier_wait(&ctl.v_free[b], (g >> 1) - 1, error);
+      if (e == 0) TRACE(2, g, 4);
       // values: thread = (r8, word w of 8 dims) takes tokens 8j + r8, j = 0..7, and transposes 8x8 in
       // registers: each dim gets a 16-byte run of eight tokens at contraction positions 8*r8 + j.
       uint8_t *v_stage = v_ptr + b * kVBytes;
+#ifdef RK_EXP_NO_EXPAND
+      if (error == nullptr)
+#endif
 #pragma unroll
       for (uint32_t half = 0; half < 2; ++half) {
         const uint32_t unit = e + half * kExpandThreads, r8 = unit & 7u, w = unit >> 3;
@@ -438,6 +483,7 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
       async_proxy_fence();
       barrier_arrive(smem_u32(&ctl.v_full[b]));
       barrier_arrive(smem_u32(&ctl.raw_free[r]));
+      if (e == 0) TRACE(2, g, 5);
     }
   } else {
     // ---- softmax: two threads per fused row (= TMEM lane), 32 contraction positions of the group each ----------
@@ -460,15 +506,19 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
       const uint32_t present = min(2u, page_end - first) * kPageTokens;
       const uint32_t limit = kTree ? present : min(present, causal_limit > token_base ? causal_limit - token_base : 0u);
       const int32_t bound = int32_t(limit) - int32_t(4 * half);
-      const float4 *triples = ctl.scales[b] + half * 32;
-      barrier_wait(&ctl.s_full, g, error);
+      const float4 *triples = ctl.scales[g % kScaleStages] + half * 32;
+      if (tid == 0) TRACE(3, g, 0);
+      barrier_wait(&ctl.s_full[b], g >> 1, error);
+      if (tid == 0) TRACE(3, g, 1);
       tmem_fence_after();
       float scores[32];
-      tmem_load32(tmem_s + lane_address + half * 32, scores);
-      tmem_fence_before();
-      barrier_arrive(smem_u32(&ctl.s_free));
+      tmem_load32(tmem_s + b * 64 + lane_address + half * 32, scores);
+      if (tid == 0) TRACE(3, g, 2);
 
       float group_max = -INFINITY;
+#ifdef RK_EXP_NO_SOFTMAX
+      if (error == nullptr)
+#endif
 #pragma unroll
       for (uint32_t i = 0; i < 32; ++i) {
         const int32_t part = int32_t(8 * (i & 7u) + (i >> 3));
@@ -482,10 +532,15 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
         scores[i] = admitted ? s : -INFINITY;
         group_max = fmaxf(group_max, scores[i]);
       }
-      // the row's other half
+      // the row's other half; past this barrier both halves hold their scores in registers, so the
+      // probabilities may overwrite the first 32 columns of the buffer
+      if (tid == 0) TRACE(3, g, 3);
       ctl.exchange[b][my_row][half] = group_max;
+      tmem_fence_before();
       asm volatile("bar.sync %0, 64;" ::"r"(1u + quarter) : "memory");
+      tmem_fence_after();
       group_max = fmaxf(group_max, ctl.exchange[b][my_row][half ^ 1u]);
+      if (tid == 0) TRACE(3, g, 4);
       // Lazy rescale: the reference exponent only moves when the maximum grew by more than 2^8, so the
       // fp16 probabilities stay below 2^(8+6); rows of a warp move together (collective TMEM access).
       const bool grow = group_max > row_max + 8.0f;
@@ -497,12 +552,21 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
       }
       const float exponent_base = row_max - 6.0f;
       uint32_t packed[16];
+#ifdef RK_EXP_NO_SOFTMAX
+#pragma unroll
+      for (uint32_t c = 0; c < 16; ++c) packed[c] = 0;
+      if (error == nullptr)
+#endif
 #pragma unroll
       for (uint32_t c = 0; c < 16; ++c) {
         float w[2];
 #pragma unroll
         for (uint32_t h = 0; h < 2; ++h) {
+#ifdef RK_EXP_NO_EXP
+          w[h] = fmaxf(scores[2 * c + h] - exponent_base, 0.0f);
+#else
           w[h] = exp2_fast(scores[2 * c + h] - exponent_base);     // 0 for a masked token
+#endif
           row_sum = fmaf(w[h], triples[2 * c + h].z, row_sum);     // 2^(score - row_max)
         }
         packed[c] = pack_half2(w[0], w[1]);
@@ -519,13 +583,13 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
           tmem_store32(tmem_o + lane_address + half * 128 + c * 32, o);
         }
       }
-      // P buffer b belonged to P.V(g-2)
-      if (g >= 2) barrier_wait(&ctl.v_free[b], (g >> 1) - 1, error);
-      tmem_fence_after();
-      tmem_store16(tmem_p + lane_address + b * 32 + half * 16, packed);
+      if (tid == 0) TRACE(3, g, 5);
+      tmem_store16(tmem_s + b * 64 + lane_address + half * 16, packed);
+      if (tid == 0) TRACE(3, g, 6);
       tmem_fence_before();
       barrier_arrive(smem_u32(&ctl.p_full[b]));
-      barrier_arrive(smem_u32(&ctl.scale_free[b]));
+      barrier_arrive(smem_u32(&ctl.scale_free[g % kScaleStages]));
+      if (tid == 0) TRACE(3, g, 7);
     }
 
     // ---- partial output: row i of O, un-normalised; statistics {reference exponent, sum} -------------------
