@@ -53,7 +53,8 @@ def parse():
     ap.add_argument("--layers", type=int, default=16)
     ap.add_argument("--ragged", action="store_true", help="contexts uniform in [context/4, context]")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
-    ap.add_argument("--mode", default="requests", choices=["requests", "seqsplit"],
+    ap.add_argument("--rows", type=int, default=16, choices=[8, 16], help="--mode verify: window rows per sequence")
+    ap.add_argument("--mode", default="requests", choices=["requests", "seqsplit", "verify"],
                     help="requests: every rank runs its own batch (default); seqsplit: ONE sequence of --context "
                          "tokens split along the sequence over the ranks, all-gather of (max, sum, O), rank-order merge")
     return ap.parse_args()
@@ -189,6 +190,15 @@ class ClockSampler:
         for line in self.process.stdout:
             self.samples.append((time.perf_counter(), line.strip()))
 
+    def keep_loaded(self, begin: float, work, minimum: int = 3, budget_seconds: float = 3.0) -> None:
+        """nvidia-smi samples every 100 ms; a timed region shorter than that sees none. Repeat the same work,
+        untimed, until `minimum` samples fall inside the window that started at `begin`."""
+        if self.process is None:
+            return
+        deadline = time.perf_counter() + budget_seconds
+        while time.perf_counter() < deadline and sum(1 for stamp, _ in self.samples if stamp >= begin) < minimum:
+            work()
+
     def stop(self, begin: float, end: float) -> dict:
         if self.process is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -322,7 +332,6 @@ def run_ours(args):
     elapsed_ms = start.elapsed_time(stop)
     launches = session.kernel_launches - launches_before
     session.attention.status()
-    clocks = sampler.stop(begin_wall, end_wall) if sampler else None
     timed_bytes = sum(kv_bytes_per_step(s) for s in range(args.warmup, steps_total))
 
     # ---- decode kernel alone: roofline -----------------------------------------------------------
@@ -369,6 +378,13 @@ def run_ours(args):
     e2e_bytes = sum(kv_bytes_per_step(base + s) for s in range(args.warmup, steps_total))
     h2d, d2h = session.host_bytes_per_layer()
     session.attention.status()
+    # clocks over all three timed regions (device-resident steps, decode kernel alone, host-buffer steps)
+    if sampler:
+        def same_load():
+            device_step(steps_total)
+            torch.cuda.synchronize()
+        sampler.keep_loaded(begin_wall, same_load)
+    clocks = sampler.stop(begin_wall, time.perf_counter()) if sampler else None
 
     # ---- reduce over ranks: max time, summed bytes --------------------------------------------------
     stats = torch.tensor([elapsed_ms, float(timed_bytes), max(e2e_ms, e2e_wall_ms), float(e2e_bytes)], dtype=torch.float64, device="cuda")
@@ -498,10 +514,146 @@ def run_seqsplit(args):
     dist.destroy_process_group()
 
 
+def run_verify(args):
+    """Speculative verify on int4 pages: per step and layer, append the window's rows (quantize into the pages)
+    and attend them causally over the whole history on the tcgen05 window kernel; then a seeded number of rows
+    is accepted and the rest rolled back (the next step starts at committed + accepted). One GPU."""
+    import torch
+
+    from richengine_b200 import hostplane, lib, ops
+    from richengine_b200.abi import INT4, Layout, pages_for
+    from richengine_b200.storage import PageStorage
+
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    rows, lanes = args.rows, args.batch
+    layout = Layout(args.layers, KV_HEADS, HEAD_DIM, INT4)
+    steps_total = args.warmup + args.steps
+    lane_pages = pages_for(args.context + rows * (steps_total + 1))
+    extent_pages = layout.extent_pages_for(lanes * lane_pages) or layout.minimum_extent_pages()
+    extents = (lanes * lane_pages + extent_pages - 1) // extent_pages
+    storage = PageStorage(layout, extents * extent_pages, extent_pages)
+    for extent in range(extents):
+        if not storage.allocate_extent(extent):
+            raise RuntimeError("KV pool does not fit in device memory")
+    order = np.random.default_rng(42).permutation(extents * extent_pages)
+    tables = []
+    for lane in range(lanes):
+        table = torch.zeros(lane_pages, dtype=torch.int64, device="cuda")
+        storage.write_entries(order[lane * lane_pages:(lane + 1) * lane_pages], 0, table)
+        tables.append(table)
+    pointers = ops.table_pointer_array(tables)
+    places = storage.layers()
+    generator = torch.Generator(device="cuda").manual_seed(7)
+    k = torch.randn((KV_HEADS, 2048, HEAD_DIM), generator=generator, device="cuda").to(torch.bfloat16)
+    v = torch.randn((KV_HEADS, HEAD_DIM, 2048), generator=generator, device="cuda").to(torch.bfloat16)
+    for lane in range(lanes):
+        done = 0
+        while done < args.context:
+            count = min(2048, args.context - done)
+            for layer in range(args.layers):
+                ops.store_chunk(layout, k, v, tables[lane], lib.ChunkParams(done, count, 2048, lane_pages, places[layer]))
+            done += count
+    group = QUERY_HEADS // KV_HEADS
+    queries = torch.randn((lanes, KV_HEADS, 32, group, HEAD_DIM), generator=generator, device="cuda").to(torch.bfloat16)
+    chunk_keys = torch.randn((lanes, KV_HEADS, 32, HEAD_DIM), generator=generator, device="cuda").to(torch.bfloat16)
+    chunk_values = torch.randn((lanes, KV_HEADS, HEAD_DIM, 32), generator=generator, device="cuda").to(torch.bfloat16)
+    output = torch.zeros_like(queries)
+    runner = ops.VerifyWindowAttention(layout, QUERY_HEADS, storage.window())
+
+    # accepted rows per (step, lane), seeded 0..rows; a step's committed length = context + what was accepted before
+    accepted = np.random.default_rng(9).integers(0, rows + 1, size=(steps_total, lanes))
+    committed = args.context + np.concatenate([np.zeros((1, lanes), np.int64), np.cumsum(accepted, axis=0)[:-1]])
+    step_params, slots = [], 0
+    for step in range(steps_total):
+        history = [int(x) for x in committed[step]]
+        _, plan = hostplane.verify_plan(lanes, QUERY_HEADS, layout, history, row_capacity=rows, ctas=0)
+        assert plan[15] == 1, "the window plan was not selected"
+        lane_splits = [hostplane.window_splits(lanes, KV_HEADS, h + rows, 0) for h in history]
+        chunk_params = np.zeros(lanes, dtype=ops.CHUNK_PARAMS)
+        verify_params = np.zeros(lanes, dtype=ops.VERIFY_PARAMS)
+        slot = max(lane_splits)
+        for lane in range(lanes):
+            chunk_params[lane] = (history[lane], rows, 32, lane_pages, (extent_pages, 0))
+            verify_params[lane] = (history[lane], lane_pages, (extent_pages, 0), lane_splits[lane], slot, rows, rows, 0.0)
+        step_params.append((ops.params_to_device(chunk_params), ops.params_to_device(verify_params), slot))
+        slots = max(slots, slot)
+    fused = rows * group
+    partials = torch.empty(lanes * KV_HEADS * slots * fused * HEAD_DIM, dtype=torch.float32, device="cuda")
+    statistics_buffer = torch.empty(lanes * KV_HEADS * slots * fused * 2, dtype=torch.float32, device="cuda")
+
+    def step_once(step: int):
+        cp, vp, slot = step_params[step]
+        for layer in range(args.layers):
+            ops.store_verify(layout, chunk_keys, chunk_values, pointers, cp, places[layer], lanes, rows)
+            runner.split(lanes, rows, slot, queries, partials, statistics_buffer, pointers, None, vp, places[layer])
+            ops.attention_verify_reduce(layout, QUERY_HEADS, lanes, rows, partials, statistics_buffer, output, vp)
+
+    for step in range(args.warmup):
+        step_once(step)
+    torch.cuda.synchronize()
+    runner.check()
+    sampler = ClockSampler(torch.cuda.current_device())
+    begin_wall = time.perf_counter()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for step in range(args.warmup, steps_total):
+        step_once(step)
+    stop.record()
+    torch.cuda.synchronize()
+    elapsed_ms = start.elapsed_time(stop)
+    # the window kernel alone, per layer
+    cp, vp, slot = step_params[steps_total - 1]
+    events = []
+    for repeat in range(3):
+        for layer in range(args.layers):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            runner.split(lanes, rows, slot, queries, partials, statistics_buffer, pointers, None, vp, places[layer])
+            b.record()
+            if repeat:
+                events.append((a, b))
+    torch.cuda.synchronize()
+    runner.check()
+    def same_load():
+        step_once(steps_total - 1)
+        torch.cuda.synchronize()
+    sampler.keep_loaded(begin_wall, same_load)
+    clocks = sampler.stop(begin_wall, time.perf_counter())
+    kernel_ms = statistics.mean(a.elapsed_time(b) for a, b in events)
+    tokens = [int(committed[s].sum()) + rows * lanes for s in range(args.warmup, steps_total)]
+    timed_bytes = sum(tokens) * layout.bytes_per_token_layer() * args.layers
+    layer_tokens = int(committed[steps_total - 1].sum()) + rows * lanes
+    flops = 4.0 * rows * QUERY_HEADS * HEAD_DIM * layer_tokens  # QK^T and PV, 2 flop per multiply-add
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    peak = float(json.loads(peaks_path.read_text())["bf16_tflops"]) if peaks_path.exists() else 1590.0
+    print(json.dumps({
+        "metric": "int4_paged_verify_attention_kv_gbps", "value": round(timed_bytes / (elapsed_ms * 1e-3) / 1e9, 1), "unit": "GB/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(elapsed_ms / args.steps, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int4 codes, fp16 tcgen05 operands, fp32 accumulate in tensor memory", "data": "synthetic",
+        "config": {"workload": f"speculative verify, int4 KV, 27B geometry ({args.layers} layers), batch {lanes}, {args.context}-token contexts, "
+                               f"{rows}-row window: per layer append {rows} rows + window attention + merge; seeded acceptance 0..{rows}, rejected rows rolled back",
+                   "l2": "inputs larger than L2", "us_per_layer_step": round(elapsed_ms / args.steps / args.layers * 1e3, 2),
+                   "splits_per_lane": slot},
+        "roofline": {"bound": "tensor", "achieved": round(flops / (kernel_ms * 1e-3) / 1e12, 1), "peak": peak, "unit": "TFLOP/s",
+                     "frac": round(flops / (kernel_ms * 1e-3) / 1e12 / peak, 4), "traffic": None,
+                     "peak_source": "measured (MEASURED_PEAKS.json bf16_tflops)" if peaks_path.exists() else "fallback",
+                     "kernel": "verify_int4_kernel", "us_per_launch": round(kernel_ms * 1e3, 2),
+                     "algorithmic_flops_per_launch": flops,
+                     "kv_gbps_of_launch": round(layer_tokens * layout.bytes_per_token_layer() / (kernel_ms * 1e-3) / 1e9, 1)},
+        "gpu_launches": 3 * args.layers * args.steps, "clocks": clocks,
+    }), flush=True)
+    runner.close()
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         run_reference(args)
+    elif args.mode == "verify":
+        if args.batch == 64 and args.context == 32768:  # the headline defaults: take this mode's own
+            args.batch, args.context = 4, 65536
+        run_verify(args)
     elif args.mode == "seqsplit":
         run_seqsplit(args)
     else:

@@ -67,11 +67,16 @@ void rk_cache_snapshot(const void *cache, uint64_t *out);
 int rk_cache_block_state(const void *cache, uint64_t block, uint64_t *out);
 
 /* ---- plans -------------------------------------------------------------------------------------- */
-/* names: "split\nreduce\nstore"; out[14] = splits, lane splits of the first four lanes, splitGroups xyz,
- * reduceGroups xyz, partialsBytes, statisticsBytes, rowCapacity. row_capacity 0 = 8 (chain) / 16 (tree). */
+/* names: "split\nreduce\nstore"; out[16] = splits, lane splits of the first four lanes, splitGroups xyz,
+ * reduceGroups xyz, partialsBytes, statisticsBytes, rowCapacity, streamingDecode, tensorCoreWindow.
+ * row_capacity 0 = 8 (chain) / 16 (tree). `ctas` = CTAs the B200 kernels may fill (0 = the current device's
+ * SM count; without a device the plan is the reference's: PagedAttention::verifyPlan, PagedAttention.cpp:331-381). */
 int rk_plan_verify(uint32_t lanes, uint32_t query_heads, uint32_t layers, uint32_t kv_heads, uint32_t head_dim,
-                   uint32_t format, const uint32_t *history, int tree, uint32_t row_capacity, char *names,
-                   size_t names_bytes, uint64_t *out);
+                   uint32_t format, const uint32_t *history, int tree, uint32_t row_capacity, uint32_t ctas,
+                   char *names, size_t names_bytes, uint64_t *out);
+/* Split count of one lane for the tcgen05 window kernel (new here): (lanes x kv_heads x splits) CTAs fill `ctas`
+ * SMs once (0 = the current device's), whole 64-token groups per split. Negative status on error. */
+int rk_plan_window_splits(uint32_t lanes, uint32_t kv_heads, uint32_t visible_tokens, uint32_t ctas);
 /* out[10] = rows, splits, splitGroups xyz, reduceGroups xyz, partialsBytes, statisticsBytes */
 int rk_plan_prefill(uint32_t rows, uint32_t query_heads, uint32_t layers, uint32_t kv_heads, uint32_t head_dim,
                     uint32_t format, char *names, size_t names_bytes, uint64_t *out);

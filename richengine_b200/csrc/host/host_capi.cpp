@@ -6,6 +6,8 @@
 #include "paged_attention.hpp"
 #include "storage_adapters.hpp"
 
+#include <cuda_runtime.h>
+
 #include <cstring>
 #include <deque>
 #include <memory>
@@ -275,9 +277,9 @@ int rk_cache_block_state(const void *cache, uint64_t block, uint64_t *out) {
 #undef CACHE
 
 int rk_plan_verify(uint32_t lanes, uint32_t query_heads, uint32_t layers, uint32_t kv_heads, uint32_t head_dim, uint32_t format,
-                   const uint32_t *history, int tree, uint32_t row_capacity, char *names, size_t names_bytes, uint64_t *out) {
+                   const uint32_t *history, int tree, uint32_t row_capacity, uint32_t ctas, char *names, size_t names_bytes, uint64_t *out) {
   return guarded([&] {
-    const auto plan = ops::PagedAttention::verifyPlan(lanes, query_heads, layoutOf(layers, kv_heads, head_dim, format), {history, lanes}, tree != 0, row_capacity);
+    const auto plan = ops::PagedAttention::verifyPlan(lanes, query_heads, layoutOf(layers, kv_heads, head_dim, format), {history, lanes}, tree != 0, row_capacity, ctas);
     if (int s = joinNames({plan.splitPipeline, plan.reducePipeline, plan.storePipeline}, names, names_bytes)) return s;
     size_t i = 0;
     out[i++] = plan.splits;
@@ -285,8 +287,21 @@ int rk_plan_verify(uint32_t lanes, uint32_t query_heads, uint32_t layers, uint32
     out[i++] = plan.splitGroups.x; out[i++] = plan.splitGroups.y; out[i++] = plan.splitGroups.z;
     out[i++] = plan.reduceGroups.x; out[i++] = plan.reduceGroups.y; out[i++] = plan.reduceGroups.z;
     out[i++] = plan.workspace.partialsBytes; out[i++] = plan.workspace.statisticsBytes; out[i++] = plan.rowCapacity;
+    out[i++] = plan.streamingDecode; out[i++] = plan.tensorCoreWindow;
     return RK_OK;
   });
+}
+int rk_plan_window_splits(uint32_t lanes, uint32_t kv_heads, uint32_t visible_tokens, uint32_t ctas) {
+  if (!ctas) {
+    int device = 0, sms = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) {
+      (void)cudaGetLastError();
+      rk::set_error("rk_plan_window_splits: no device to size the plan for");
+      return RK_ERR_INVALID;
+    }
+    ctas = uint32_t(sms);
+  }
+  return int(ops::PagedAttention::windowSplits(lanes, kv_heads, visible_tokens, ctas));
 }
 int rk_plan_prefill(uint32_t rows, uint32_t query_heads, uint32_t layers, uint32_t kv_heads, uint32_t head_dim, uint32_t format,
                     char *names, size_t names_bytes, uint64_t *out) {

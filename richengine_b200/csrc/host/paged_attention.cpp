@@ -1,5 +1,7 @@
 #include "paged_attention.hpp"
 
+#include <cuda_runtime.h>
+
 #include <algorithm>
 #include <limits>
 #include <stdexcept>
@@ -92,6 +94,27 @@ PrefillAttentionPlan PagedAttention::prefillPlan(uint32_t rows, uint32_t queryHe
   return plan;
 }
 
+// Multiprocessors of the current device; 0 where there is none (a host without a GPU keeps the reference plan).
+static uint32_t deviceMultiprocessors() {
+  int device = 0, sms = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  return uint32_t(sms);
+}
+
+// Split count of one lane for the tcgen05 window kernel: (lanes x heads x splits) CTAs fill the SMs once, a
+// split holds an even number of pages (whole 64-token groups) unless it is the lane's only one.
+uint32_t PagedAttention::windowSplits(uint32_t lanes, uint32_t kvHeads, uint32_t visibleTokens, uint32_t ctas) {
+  const uint32_t pages = rk_pages_for(visibleTokens);
+  uint32_t splits = std::clamp<uint32_t>(ctas / std::max<uint32_t>(1, lanes * kvHeads), 1, RK_VERIFY_MAX_SPLITS);
+  splits = std::min(splits, std::max<uint32_t>(1, (pages + 1) / 2));
+  uint32_t perSplit = (pages + splits - 1) / splits;
+  if (splits > 1 && (perSplit & 1u)) ++perSplit;
+  return std::max<uint32_t>(1, (pages + perSplit - 1) / perSplit);
+}
+
 VerifyAttentionPlan PagedAttention::verifyPlan(uint32_t lanes, uint32_t queryHeads, kv::Layout layout,
                                                std::span<const uint32_t> historyTokens, bool tree, uint32_t rowCapacity, uint32_t ctas) {
   const std::string suffix(attentionSuffix(layout, queryHeads));
@@ -124,6 +147,19 @@ VerifyAttentionPlan PagedAttention::verifyPlan(uint32_t lanes, uint32_t queryHea
       rk_decode_plan_make(formatCode(layout.format), layout.kvHeads, queryHeads, layout.headDimension, lanes, ctas, &plan.decode) == RK_OK) {
     plan.streamingDecode = true;
     plan.workspace = {plan.decode.partials_bytes, plan.decode.statistics_bytes};
+  }
+  if ((rows == kVerifyRows || rows == RK_TREE_NODES) && layout.format == kv::Format::Int4 && layout.kvHeads == 4 &&
+      queryHeads == 24 && layout.headDimension == 256) {
+    if (!ctas) ctas = deviceMultiprocessors();
+    if (ctas) {
+      plan.tensorCoreWindow = true;
+      plan.splits = 0;
+      for (uint32_t lane = 0; lane < lanes; ++lane) {
+        plan.laneSplits[lane] = windowSplits(lanes, layout.kvHeads, historyTokens[lane] + liveRows, ctas);
+        plan.splits = std::max(plan.splits, plan.laneSplits[lane]);
+      }
+      plan.splitGroups = {layout.kvHeads, plan.splits, lanes};
+    }
   }
   return plan;
 }
@@ -181,8 +217,15 @@ void PagedAttention::addVerify(void *stream, rk_kv_layer layer, const PagedVerif
                               b.pageTables, deviceAttention, layer, stream));
     return;
   }
-  check(rk_attention_verify_split(format, layout.kvHeads, queryHeads, layout.headDimension, plan.lanes, plan.rowCapacity, plan.splits,
-                                  b.queries, b.partials, b.statistics, b.pageTables, tree ? b.treeMasks : nullptr, deviceAttention, layer, stream));
+  if (plan.tensorCoreWindow) {
+    if (!window || !b.status) throw std::invalid_argument("the window kernel needs the pool window and a status word");
+    check(rk_attention_verify_split_tc(window, format, layout.kvHeads, queryHeads, layout.headDimension, plan.lanes, plan.rowCapacity,
+                                       plan.splits, b.queries, b.partials, b.statistics, b.pageTables, tree ? b.treeMasks : nullptr,
+                                       deviceAttention, layer, b.status, stream));
+  } else {
+    check(rk_attention_verify_split(format, layout.kvHeads, queryHeads, layout.headDimension, plan.lanes, plan.rowCapacity, plan.splits,
+                                    b.queries, b.partials, b.statistics, b.pageTables, tree ? b.treeMasks : nullptr, deviceAttention, layer, stream));
+  }
   check(rk_attention_verify_reduce(layout.kvHeads, queryHeads, layout.headDimension, plan.lanes, plan.rowCapacity, b.partials, b.statistics,
                                    b.output, nullptr, deviceAttention, stream));
 }

@@ -54,12 +54,16 @@ struct VerifyAttentionPlan {
   // Row capacity 1 on int4 pages runs the streaming decode kernel instead of split + reduce.
   bool streamingDecode = false;
   rk_decode_plan decode{};
+  // Row capacity 8 or 16 on int4 pages runs the tcgen05 split kernel; laneSplits / splits / splitGroups then
+  // hold its partition (one CTA per (lane, head, split), the SMs filled once) instead of the reference's.
+  bool tensorCoreWindow = false;
 };
 
 struct PagedVerifyBuffers {
   void *chunkKeys = nullptr, *chunkValues = nullptr, *queries = nullptr, *output = nullptr;
   float *partials = nullptr, *statistics = nullptr;
   uint32_t *descriptors = nullptr;                   // streaming decode only
+  uint32_t *status = nullptr;                        // tcgen05 window kernel only: one zeroed device word
   const rk_page_entry *const *pageTables = nullptr;  // device array, one table address per lane
   const uint32_t *treeMasks = nullptr;
   uint64_t partialsBytes = 0, statisticsBytes = 0;   // sizes of the scratch actually bound
@@ -70,6 +74,7 @@ public:
   static PrefillAttentionPlan prefillPlan(uint32_t rows, uint32_t queryHeads, kv::Layout layout);
   // historyTokens: each lane's committed tokens before its rows. rowCapacity 0 selects the
   // reference's 8 (chain) or 16 (tree); 1 is the plain decode. ctas sizes the streaming grid (0 = SMs).
+  static uint32_t windowSplits(uint32_t lanes, uint32_t kvHeads, uint32_t visibleTokens, uint32_t ctas);
   static VerifyAttentionPlan verifyPlan(uint32_t lanes, uint32_t queryHeads, kv::Layout layout,
                                         std::span<const uint32_t> historyTokens, bool tree = false,
                                         uint32_t rowCapacity = 0, uint32_t ctas = 148);

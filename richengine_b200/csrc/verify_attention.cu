@@ -9,17 +9,21 @@
 //
 // One CTA owns (KV head, split, lane) like the reference grid. The fused rows (rows x 6 query heads,
 // 48 or 96) are the M side of a 128-row UMMA tile (padding rows hold zero queries). The pages of the
-// split are taken in groups of 64 tokens (two pages). Tensor memory holds O (256 columns), S (64), the
-// fp16 probabilities P twice (2 x 32) and the query tile itself (128): both contractions take their A
-// operand from tensor memory, shared memory only carries the page data. Roles:
-//   warp 12 (one thread)  TMA: the two pages' K and V slabs of this head (32-row boxes of the window
+// split are taken in groups of 64 tokens (two pages). Tensor memory holds O (256 columns), S twice
+// (2 x 64, the fp16 probabilities overwrite the first half of their S) and the query tile itself (128):
+// both contractions take their A operand from tensor memory, shared memory only carries the page data.
+// Roles:
+//   warp 24 (one thread)  TMA: the two pages' K and V slabs of this head (32-row boxes of the window
 //                         map, 128-byte swizzle) and their scales into a ring of four raw stages.
-//   warps 8-11            expand the raw nibbles to fp16 — exact — into double-buffered K-major swizzled
-//                         operand tiles K[position][dim] and V^T[dim][position] (an 8x8 transpose in
-//                         registers), and prepare the per-token scale triples.
-//   warp 13 (one thread)  tcgen05.mma: S = Q.K^T (16 x M128 N64 K16) and O += P.V (4 x M128 N256 K16),
-//                         ordered QK(g+1) before PV(g) so the tensor pipe works while the softmax runs.
-//   warps 0-7             softmax, two threads per row (= TMEM lane), 32 tokens each: read S, fold key
+//   warps 16-23           two teams of four warps, team t takes the groups g = t (mod 2): expand the raw
+//                         nibbles to fp16 — exact — into stage t of the K-major swizzled operand tiles
+//                         K[position][dim] and V^T[dim][position] (an 8x8 transpose in registers), and
+//                         prepare the per-token scale triples.
+//   warp 25               tcgen05.mma S(g) = Q.K^T (16 x M128 N64 K16) into S buffer g&1;
+//   warp 26               tcgen05.mma O += P.V (4 x M128 N256 K16). Both walk their loop as a whole warp
+//                         and one elected lane issues, which keeps descriptors on the uniform datapath.
+//                         P(g) overwrites the first half of S(g); QK(g+2) waits for PV(g) to land.
+//   warps 0-15            softmax, four threads per row (= TMEM lane), 16 tokens each: read S, fold key
 //                         scale and 1/16, admit, online maximum (one exchange through shared memory),
 //                         value scale folded into the exponent, P as fp16 back into tensor memory; a row
 //                         whose maximum grew by more than 2^8 rescales its O row (rows of a warp move
@@ -38,7 +42,9 @@
 namespace rk {
 namespace {
 
-constexpr uint32_t kSoftmaxWarps = 8;  // two warps per 32-row quarter, 32 tokens of a group each
+constexpr uint32_t kRowThreads = 4;                      // softmax threads per fused row (one per warp of the row's quarter)
+constexpr uint32_t kSoftmaxWarps = 4 * kRowThreads;
+constexpr uint32_t kRowTokens = 64 / kRowThreads;         // contraction positions of a group per softmax thread
 constexpr uint32_t kExpandWarps = 8;   // two teams of four warps: team t expands the groups g = t (mod 2) into stage t
 constexpr uint32_t kSoftmaxThreads = kSoftmaxWarps * 32;
 constexpr uint32_t kExpandThreads = kExpandWarps * 32 / 2; // threads of one team
@@ -67,7 +73,7 @@ struct Control {
   uint32_t tmem_base;
   uint32_t error;
   float q_sums[kM];
-  float exchange[2][kM][2];       // the two half-row maxima of a group (and, at the end, the half-row sums)
+  float exchange[2][kM][kRowThreads]; // the part-row maxima of a group (and, at the end, the part-row sums)
   float4 scales[kScaleStages][kGroupTokens]; // {key scale, log2 value scale, 2^-6 / value scale, -}
 };
 
@@ -168,13 +174,23 @@ __device__ __forceinline__ void tmem_store32(uint32_t address, const float (&v)[
                : "memory");
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
-__device__ __forceinline__ void tmem_store16(uint32_t address, const uint32_t (&v)[16]) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-               ::"r"(address), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
-                 "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
-               : "memory");
+__device__ __forceinline__ void tmem_load16(uint32_t address, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(address));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_store8(uint32_t address, const uint32_t (&v)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+               ::"r"(address), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_load_scores(uint32_t address, float (&v)[16]) { tmem_load16(address, v); }
+__device__ __forceinline__ void tmem_store_packed(uint32_t address, const uint32_t (&v)[8]) { tmem_store8(address, v); }
 __device__ __forceinline__ float exp2_fast(float x) { float r; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
 __device__ __forceinline__ float log2_fast(float x) { float r; asm("lg2.approx.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) { const __half2 h = __floats2half2_rn(lo, hi); return *reinterpret_cast<const uint32_t *>(&h); }
@@ -198,12 +214,6 @@ __device__ __forceinline__ uint32_t swizzled(uint32_t row, uint32_t chunk) { ret
 // Within a 16-byte operand chunk of 8 dims the element order is (0,4,1,5,2,6,3,7): the order in which
 // an int4 word yields its nibble pairs; queries and keys use the same order, so the contraction is
 // unchanged. Dims 1,5,3,7 of each 8 carry the 16x of a high nibble on the key side, 1/16 on the query.
-
-#ifdef RK_EXP_TRACE
-#define TRACE(role, g, k) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (g) < 64) args.status[16 + ((role) * 64 + (g)) * 8 + (k)] = uint32_t(clock64()); } while (0)
-#else
-#define TRACE(role, g, k) do { } while (0)
-#endif
 
 struct VerifyArgs {
   const uint16_t *queries;
@@ -274,20 +284,21 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
   const uint32_t tmem_o = tmem + kTmemO, tmem_s = tmem + kTmemS, tmem_q = tmem + kTmemQ;
   const uint32_t data_bytes = kPageTokens * kHeads * kD / 2, scale_bytes = kPageTokens * kHeads * 4;
 
-  // Query tile into tensor memory: thread (row, half) converts half a row (128 dims = 64 columns): fp16,
-  // element order (0,4,1,5,2,6,3,7) inside every 8 dims, dims 1,5,3,7 divided by 16.
+  // Query tile into tensor memory: the row's threads convert 128/kRowThreads columns each: fp16, element
+  // order (0,4,1,5,2,6,3,7) inside every 8 dims, dims 1,5,3,7 divided by 16.
   if (warp < kSoftmaxWarps) {
-    const uint32_t quarter = warp & 3u, half = warp >> 2, row = quarter * 32 + lane;
+    const uint32_t quarter = warp & 3u, part = warp >> 2, row = quarter * 32 + lane;
     const uint16_t *queries = args.queries + (uint64_t(lane_index) * kHeads + kv_head) * (uint64_t(RK_VERIFY_CHUNK_STRIDE) * kG * kD);
     const bool real = row < p.active_rows * kG;
     float q_sum = 0.0f; // over the fp16 values the tensor core will see, for the +8 correction
 #pragma unroll 1
-    for (uint32_t part = 0; part < 2; ++part) { // 32 columns = 8 chunks of 8 dims
+    for (uint32_t piece = 0; piece < 4 / kRowThreads; ++piece) { // 32 columns = 8 chunks of 8 dims
+      const uint32_t column = part * (128 / kRowThreads) + piece * 32;
       float columns[32];
 #pragma unroll
       for (uint32_t c = 0; c < 8; ++c) {
         uint4 raw = make_uint4(0, 0, 0, 0);
-        if (real) raw = __ldg(reinterpret_cast<const uint4 *>(queries + uint64_t(row) * kD + half * 128 + part * 64 + 8 * c));
+        if (real) raw = __ldg(reinterpret_cast<const uint4 *>(queries + uint64_t(row) * kD + 2 * column + 8 * c));
         const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
         float d[8];
 #pragma unroll
@@ -301,14 +312,19 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
           columns[c * 4 + i] = __uint_as_float(chunk[i]);
         }
       }
-      tmem_store32(tmem_q + ((quarter * 32u) << 16) + half * 64 + part * 32, columns);
+      tmem_store32(tmem_q + ((quarter * 32u) << 16) + column, columns);
     }
-    ctl.exchange[0][row][half] = q_sum;
+    ctl.exchange[0][row][part] = q_sum;
   }
   tmem_fence_before();
   __syncthreads();
   tmem_fence_after();
-  if (tid < kM) ctl.q_sums[tid] = ctl.exchange[0][tid][0] + ctl.exchange[0][tid][1];
+  if (tid < kM) {
+    float total = 0.0f;
+#pragma unroll
+    for (uint32_t i = 0; i < kRowThreads; ++i) total += ctl.exchange[0][tid][i];
+    ctl.q_sums[tid] = total;
+  }
   __syncthreads();
 
   if (warp == kTmaWarp) {
@@ -323,9 +339,7 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
           next[0] = table[first + 2];
           next[1] = first + 3 < page_end ? table[first + 3] : 0;
         }
-        TRACE(0, g, 0);
         if (use) barrier_wait(&ctl.raw_free[r], use - 1, error);
-        TRACE(0, g, 1);
         const uint32_t full = smem_u32(&ctl.raw_full[r]), stage = raw_tile + r * kRawStageBytes;
         barrier_expect(full, group_pages * (2 * kSlabBytes + 256));
 #pragma unroll
@@ -358,10 +372,8 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
     const uint64_t k_desc0 = umma_descriptor(k_tile), k_desc1 = umma_descriptor(k_tile + kKBytes);
     for (uint32_t g = 0; g < groups; ++g) {
       const uint32_t b = g & 1u;
-      if (lane == 0) TRACE(1, g, 0);
       barrier_wait(&ctl.k_full[b], g >> 1, error);
       if (g >= 2) barrier_wait(&ctl.v_free[b], (g >> 1) - 1, error);
-      if (lane == 0) TRACE(1, g, 1);
       tmem_fence_after();
       const uint64_t desc = b ? k_desc1 : k_desc0;
       const uint32_t target = tmem_s + b * 64;
@@ -373,7 +385,6 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
         umma_commit(&ctl.k_free[b]);
       }
       __syncwarp();
-      if (lane == 0) TRACE(1, g, 2);
     }
   } else if (warp == kValueWarp) {
     // ---- tensor-core issue, O += P.V ------------------------------------------------------------------------------
@@ -381,11 +392,8 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
     const uint64_t v_desc0 = umma_descriptor(v_tile), v_desc1 = umma_descriptor(v_tile + kVBytes);
     for (uint32_t g = 0; g < groups; ++g) {
       const uint32_t b = g & 1u;
-      if (lane == 0) TRACE(1, g, 3);
       barrier_wait(&ctl.v_full[b], g >> 1, error);
-      if (lane == 0) TRACE(1, g, 4);
       barrier_wait(&ctl.p_full[b], g >> 1, error);
-      if (lane == 0) TRACE(1, g, 5);
       tmem_fence_after();
       const uint64_t desc = b ? v_desc1 : v_desc0;
       const uint32_t source = tmem_s + b * 64;
@@ -395,7 +403,6 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
         umma_commit(&ctl.v_free[b]);
       }
       __syncwarp();
-      if (lane == 0) TRACE(1, g, 6);
     }
   } else if (warp >= kSoftmaxWarps) {
     // ---- expanders: raw nibbles -> fp16 operand tiles ---------------------------------------------------------
@@ -407,9 +414,7 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
       const uint32_t r = g % kRawStages, use = g / kRawStages, b = team;
       const uint32_t group_pages = min(2u, page_end - (page_begin + 2 * g));
       const uint8_t *raw = raw_ptr + r * kRawStageBytes;
-      if (e == 0) TRACE(2, g, 0);
       barrier_wait(&ctl.raw_full[r], use, error);
-      if (e == 0) TRACE(2, g, 1);
       // per-position scale triples; tokens of an absent page get harmless zeros
       if (e < kGroupTokens) {
         if (g >= kScaleStages) barrier_wait(&ctl.scale_free[g % kScaleStages], g / kScaleStages - 1, error);
@@ -423,14 +428,10 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
         ctl.scales[g % kScaleStages][e] = triple;
       }
       if (g >= 2) barrier_wait(&ctl.k_free[b], (g >> 1) - 1, error);
-      if (e == 0) TRACE(2, g, 2);
       // keys: a thread takes a raw 16-byte chunk (32 dims of one token) = four operand chunks; the token
       // goes to row `position`. The eight lanes of an access phase take tokens 8k + t and chunks c0 ^ k:
       // conflict-free on the swizzled raw side and on the swizzled operand side.
       uint8_t *k_stage = k_ptr + b * kKBytes;
-#ifdef RK_EXP_NO_EXPAND
-      if (error == nullptr)
-#endif
 #pragma unroll
       for (uint32_t i = 0; i < 4; ++i) {
         const uint32_t item = e + i * kExpandThreads;
@@ -449,15 +450,10 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
       }
       async_proxy_fence();
       barrier_arrive(smem_u32(&ctl.k_full[b]));
-      if (e == 0) TRACE(2, g, 3);
       if (g >= 2) barrier_wait(&ctl.v_free[b], (g >> 1) - 1, error);
-      if (e == 0) TRACE(2, g, 4);
       // values: thread = (r8, word w of 8 dims) takes tokens 8j + r8, j = 0..7, and transposes 8x8 in
       // registers: each dim gets a 16-byte run of eight tokens at contraction positions 8*r8 + j.
       uint8_t *v_stage = v_ptr + b * kVBytes;
-#ifdef RK_EXP_NO_EXPAND
-      if (error == nullptr)
-#endif
 #pragma unroll
       for (uint32_t half = 0; half < 2; ++half) {
         const uint32_t unit = e + half * kExpandThreads, r8 = unit & 7u, w = unit >> 3;
@@ -483,11 +479,10 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
       async_proxy_fence();
       barrier_arrive(smem_u32(&ctl.v_full[b]));
       barrier_arrive(smem_u32(&ctl.raw_free[r]));
-      if (e == 0) TRACE(2, g, 5);
     }
   } else {
-    // ---- softmax: two threads per fused row (= TMEM lane), 32 contraction positions of the group each ----------
-    const uint32_t quarter = warp & 3u, half = warp >> 2;
+    // ---- softmax: kRowThreads threads per fused row (= TMEM lane), kRowTokens contraction positions each ----
+    const uint32_t quarter = warp & 3u, part = warp >> 2;
     const uint32_t my_row = quarter * 32 + lane;
     const float score_scale = rk_score_scale(p.score_scale, kD) * kLog2e;
     const float row_factor = ldexpf(score_scale, 24);
@@ -496,51 +491,54 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
     const uint32_t causal_limit = min(visible, p.committed_tokens + min(query_row, p.active_rows - 1) + 1);
     const uint32_t tree_mask = kTree && query_row < p.row_capacity ? row_masks[query_row] : 0u;
     const uint32_t lane_address = (quarter * 32u) << 16;
-    float row_max = -1.0e30f, row_sum = 0.0f; // row_sum: this thread's tokens only
+    constexpr uint32_t kOutColumns = kD / kRowThreads; // columns of O this thread rescales and writes out
+    float row_max = -1.0e30f, row_sum = 0.0f;          // row_sum: this thread's tokens only
 
     for (uint32_t g = 0; g < groups; ++g) {
       const uint32_t first = page_begin + 2 * g, b = g & 1u;
       const uint32_t token_base = first * kPageTokens;
       // tokens of the group that exist (a split may end inside it) and, on a chain, pass the causal rule;
-      // position 32*half + i holds token 8*(i%8) + 4*half + i/8: compare i's part against limit - 4*half
+      // position kRowTokens*part + i holds token 8*(i%8) + i/8 + (kRowTokens/8)*part
       const uint32_t present = min(2u, page_end - first) * kPageTokens;
       const uint32_t limit = kTree ? present : min(present, causal_limit > token_base ? causal_limit - token_base : 0u);
-      const int32_t bound = int32_t(limit) - int32_t(4 * half);
-      const float4 *triples = ctl.scales[g % kScaleStages] + half * 32;
-      if (tid == 0) TRACE(3, g, 0);
+      const int32_t bound = int32_t(limit) - int32_t((kRowTokens / 8) * part);
+      const float4 *triples = ctl.scales[g % kScaleStages] + part * kRowTokens;
       barrier_wait(&ctl.s_full[b], g >> 1, error);
-      if (tid == 0) TRACE(3, g, 1);
       tmem_fence_after();
-      float scores[32];
-      tmem_load32(tmem_s + b * 64 + lane_address + half * 32, scores);
-      if (tid == 0) TRACE(3, g, 2);
+      float scores[kRowTokens];
+      tmem_load_scores(tmem_s + b * 64 + lane_address + part * kRowTokens, scores);
 
       float group_max = -INFINITY;
-#ifdef RK_EXP_NO_SOFTMAX
-      if (error == nullptr)
-#endif
+      if (!kTree && bound >= 64) { // every token of the group is admitted (all but the last groups of a lane)
 #pragma unroll
-      for (uint32_t i = 0; i < 32; ++i) {
-        const int32_t part = int32_t(8 * (i & 7u) + (i >> 3));
-        bool admitted = part < bound;
-        if (kTree) {
-          const uint32_t token = token_base + uint32_t(part) + 4 * half;
-          admitted = admitted && (token < p.committed_tokens || (token < visible && ((tree_mask >> (token - p.committed_tokens)) & 1u)));
+        for (uint32_t i = 0; i < kRowTokens; ++i) {
+          const float4 triple = triples[i];
+          scores[i] = fmaf(scores[i], row_factor, row_offset) * triple.x + triple.y; // score + log2(value scale)
+          group_max = fmaxf(group_max, scores[i]);
         }
-        const float4 triple = triples[i];
-        const float s = fmaf(scores[i], row_factor, row_offset) * triple.x + triple.y; // score + log2(value scale)
-        scores[i] = admitted ? s : -INFINITY;
-        group_max = fmaxf(group_max, scores[i]);
+      } else {
+#pragma unroll
+        for (uint32_t i = 0; i < kRowTokens; ++i) {
+          const int32_t local = int32_t(8 * (i & 7u) + (i >> 3));
+          bool admitted = local < bound;
+          if (kTree) {
+            const uint32_t token = token_base + uint32_t(local) + (kRowTokens / 8) * part;
+            admitted = admitted && (token < p.committed_tokens || (token < visible && ((tree_mask >> (token - p.committed_tokens)) & 1u)));
+          }
+          const float4 triple = triples[i];
+          const float s = fmaf(scores[i], row_factor, row_offset) * triple.x + triple.y;
+          scores[i] = admitted ? s : -INFINITY;
+          group_max = fmaxf(group_max, scores[i]);
+        }
       }
-      // the row's other half; past this barrier both halves hold their scores in registers, so the
+      // the row's other parts; past this barrier every part holds its scores in registers, so the
       // probabilities may overwrite the first 32 columns of the buffer
-      if (tid == 0) TRACE(3, g, 3);
-      ctl.exchange[b][my_row][half] = group_max;
+      ctl.exchange[b][my_row][part] = group_max;
       tmem_fence_before();
-      asm volatile("bar.sync %0, 64;" ::"r"(1u + quarter) : "memory");
+      asm volatile("bar.sync %0, %1;" ::"r"(1u + quarter), "n"(32 * kRowThreads) : "memory");
       tmem_fence_after();
-      group_max = fmaxf(group_max, ctl.exchange[b][my_row][half ^ 1u]);
-      if (tid == 0) TRACE(3, g, 4);
+#pragma unroll
+      for (uint32_t i = 0; i < kRowThreads; ++i) group_max = fmaxf(group_max, ctl.exchange[b][my_row][i]);
       // Lazy rescale: the reference exponent only moves when the maximum grew by more than 2^8, so the
       // fp16 probabilities stay below 2^(8+6); rows of a warp move together (collective TMEM access).
       const bool grow = group_max > row_max + 8.0f;
@@ -551,45 +549,33 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
         row_sum *= scale;
       }
       const float exponent_base = row_max - 6.0f;
-      uint32_t packed[16];
-#ifdef RK_EXP_NO_SOFTMAX
+      uint32_t packed[kRowTokens / 2];
 #pragma unroll
-      for (uint32_t c = 0; c < 16; ++c) packed[c] = 0;
-      if (error == nullptr)
-#endif
-#pragma unroll
-      for (uint32_t c = 0; c < 16; ++c) {
+      for (uint32_t c = 0; c < kRowTokens / 2; ++c) {
         float w[2];
 #pragma unroll
         for (uint32_t h = 0; h < 2; ++h) {
-#ifdef RK_EXP_NO_EXP
-          w[h] = fmaxf(scores[2 * c + h] - exponent_base, 0.0f);
-#else
           w[h] = exp2_fast(scores[2 * c + h] - exponent_base);     // 0 for a masked token
-#endif
           row_sum = fmaf(w[h], triples[2 * c + h].z, row_sum);     // 2^(score - row_max)
         }
         packed[c] = pack_half2(w[0], w[1]);
       }
-      if (g && __any_sync(0xffffffffu, grow)) { // this half rescales its 128 columns of O once P.V(g-1) has landed
+      if (g && __any_sync(0xffffffffu, grow)) { // this part rescales its columns of O once P.V(g-1) has landed
         barrier_wait(&ctl.v_free[b ^ 1u], (g - 1) >> 1, error);
         tmem_fence_after();
 #pragma unroll 1
-        for (uint32_t c = 0; c < 4; ++c) {
+        for (uint32_t c = 0; c < kOutColumns / 32; ++c) {
           float o[32];
-          tmem_load32(tmem_o + lane_address + half * 128 + c * 32, o);
+          tmem_load32(tmem_o + lane_address + part * kOutColumns + c * 32, o);
 #pragma unroll
           for (uint32_t i = 0; i < 32; ++i) o[i] *= scale;
-          tmem_store32(tmem_o + lane_address + half * 128 + c * 32, o);
+          tmem_store32(tmem_o + lane_address + part * kOutColumns + c * 32, o);
         }
       }
-      if (tid == 0) TRACE(3, g, 5);
-      tmem_store16(tmem_s + b * 64 + lane_address + half * 16, packed);
-      if (tid == 0) TRACE(3, g, 6);
+      tmem_store_packed(tmem_s + b * 64 + lane_address + part * (kRowTokens / 2), packed);
       tmem_fence_before();
       barrier_arrive(smem_u32(&ctl.p_full[b]));
       barrier_arrive(smem_u32(&ctl.scale_free[g % kScaleStages]));
-      if (tid == 0) TRACE(3, g, 7);
     }
 
     // ---- partial output: row i of O, un-normalised; statistics {reference exponent, sum} -------------------
@@ -597,23 +583,26 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
     tmem_fence_after();
     const bool failed = *error != 0;
     const uint64_t slot = (uint64_t(lane_index) * kHeads + kv_head) * p.slot_splits + split;
-    float *out = args.partials + (slot * kRealRows + my_row) * kD + half * 128;
+    float *out = args.partials + (slot * kRealRows + my_row) * kD + part * kOutColumns;
 #pragma unroll 1
-    for (uint32_t c = 0; c < 4; ++c) {
+    for (uint32_t c = 0; c < kOutColumns / 32; ++c) {
       float o[32];
-      tmem_load32(tmem_o + lane_address + half * 128 + c * 32, o);
+      tmem_load32(tmem_o + lane_address + part * kOutColumns + c * 32, o);
       if (my_row < kRealRows) {
 #pragma unroll
         for (uint32_t i = 0; i < 32; i += 4)
           *reinterpret_cast<float4 *>(out + c * 32 + i) = make_float4(o[i] * 0.015625f, o[i + 1] * 0.015625f, o[i + 2] * 0.015625f, o[i + 3] * 0.015625f);
       }
     }
-    ctl.exchange[groups & 1u][my_row][half] = row_sum;
-    asm volatile("bar.sync %0, 64;" ::"r"(1u + quarter) : "memory");
-    if (half == 0 && my_row < kRealRows) {
+    ctl.exchange[groups & 1u][my_row][part] = row_sum;
+    asm volatile("bar.sync %0, %1;" ::"r"(1u + quarter), "n"(32 * kRowThreads) : "memory");
+    if (part == 0 && my_row < kRealRows) {
+      float total = 0.0f;
+#pragma unroll
+      for (uint32_t i = 0; i < kRowThreads; ++i) total += ctl.exchange[groups & 1u][my_row][i];
       float *stats = args.statistics + (slot * kRealRows + my_row) * 2;
       stats[0] = failed ? -INFINITY : row_max * kLn2;
-      stats[1] = failed ? 0.0f : row_sum + ctl.exchange[groups & 1u][my_row][1];
+      stats[1] = failed ? 0.0f : total;
     }
   }
   tmem_fence_before();

@@ -148,16 +148,26 @@ class Cache:
         return {"page": out[0], "tier_copy": bool(out[1]), "transferring": bool(out[2]), "last_used": out[3]}
 
 
-def verify_plan(lanes, query_heads, layout, history, tree=False, row_capacity=0):
+def verify_plan(lanes, query_heads, layout, history, tree=False, row_capacity=0, ctas=0):
+    """(pipeline names, numbers): out[0] splits, [1:5] lane splits, ..., [13] row capacity, [14] streaming
+    decode, [15] tcgen05 window kernel. `ctas` 0 = the device's SM count (no device: the reference plan)."""
     library = lib.load()
     names = C.create_string_buffer(512)
     out = (C.c_uint64 * 16)()
     h = (C.c_uint32 * lanes)(*history)
     status = library.rk_plan_verify(lanes, query_heads, layout.attention_layers, layout.kv_heads, layout.head_dimension,
-                                    layout.format, h, int(tree), row_capacity, names, 512, out)
+                                    layout.format, h, int(tree), row_capacity, ctas, names, 512, out)
     if status:
         raise ValueError(library.rk_last_error().decode())
-    return names.value.decode().split("\n"), list(out[:14])
+    return names.value.decode().split("\n"), list(out[:16])
+
+
+def window_splits(lanes, kv_heads, visible_tokens, ctas=0):
+    """Split count of one lane for the tcgen05 window kernel (PagedAttention::windowSplits); ctas 0 = this device."""
+    value = lib.load().rk_plan_window_splits(lanes, kv_heads, visible_tokens, ctas)
+    if value <= 0:
+        raise ValueError(lib.load().rk_last_error().decode())
+    return int(value)
 
 
 def prefill_plan(rows, query_heads, layout):

@@ -148,7 +148,8 @@ SIGNATURES = {
     "rk_cache_fail_next_transfers": (None, [vp, u32]),
     "rk_cache_snapshot": (None, [vp, vp]),
     "rk_cache_block_state": (i32, [vp, u64, vp]),
-    "rk_plan_verify": (i32, [u32, u32, u32, u32, u32, u32, vp, i32, u32, C.c_char_p, C.c_size_t, vp]),
+    "rk_plan_window_splits": (i32, [u32, u32, u32, u32]),
+    "rk_plan_verify": (i32, [u32, u32, u32, u32, u32, u32, vp, i32, u32, u32, C.c_char_p, C.c_size_t, vp]),
     "rk_plan_prefill": (i32, [u32, u32, u32, u32, u32, u32, C.c_char_p, C.c_size_t, vp]),
     "rk_plan_workspaces": (i32, [u32, u32, u32, u32, u32, u32, u32, vp]),
     "rk_chunk_validation_error": (C.c_char_p, [u32, u32, u32, u32]),

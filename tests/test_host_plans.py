@@ -8,6 +8,7 @@ import pytest
 import oracle as om
 from richengine_b200 import lib
 from richengine_b200.abi import BF16, FP8E4M3, INT4, INT8, Layout
+from richengine_b200 import abi
 from richengine_b200.hostplane import prefill_plan, verify_plan
 
 needs_reference = pytest.mark.skipif(om.reference() is None, reason="reference checkout was not compiled here")
@@ -30,8 +31,26 @@ def test_plan_known_values():
     with pytest.raises(ValueError):
         verify_plan(1, 24, Layout(16, 4, 256, INT8), [262144 + 8])  # history exceeds the physical context
     # the plain decode plan sizes the streaming kernel's scratch instead
-    names, n = verify_plan(64, 24, Layout(16, 4, 256, INT4), [32768] * 64, row_capacity=1)
-    assert n[13] == 1 and n[11] == (64 + 148) * 4 * 3 * 6 * 256 * 4
+    names, n = verify_plan(64, 24, Layout(16, 4, 256, INT4), [32768] * 64, row_capacity=1, ctas=148)
+    assert n[13] == 1 and n[14] == 1 and n[11] == (64 + 148) * 4 * 3 * 6 * 256 * 4
+
+
+def test_window_plan_fills_the_sms_once():
+    """8/16-row int4 windows on a B200: (lanes x heads x splits) CTAs <= SMs, whole 64-token groups per split."""
+    layout = Layout(16, 4, 256, INT4)
+    names, n = verify_plan(4, 24, layout, [65536] * 4, row_capacity=16, ctas=148)
+    assert n[15] == 1 and n[0] == 9 and n[1:5] == [9, 9, 9, 9] and n[5:8] == [4, 9, 4]
+    pages = abi.pages_for(65536 + 16)
+    per_split = -(-pages // 9)
+    assert per_split % 2 == 0 and per_split * 9 >= pages
+    # short lanes get fewer splits (at least one group each), one lane alone takes up to 37
+    names, n = verify_plan(2, 24, layout, [40, 100000], row_capacity=8, ctas=148)
+    assert n[15] == 1 and n[1:3] == [1, 18]
+    names, n = verify_plan(1, 24, layout, [262144 - 8], row_capacity=8, ctas=148)
+    assert n[15] == 1 and n[0] <= 37 and n[0] * 4 <= 148
+    # other formats and the host-only default keep the reference's plan
+    assert verify_plan(4, 24, Layout(16, 4, 256, INT8), [65536] * 4, row_capacity=16, ctas=148)[1][15] == 0
+    assert verify_plan(4, 24, layout, [65536] * 4, row_capacity=16)[1][15] in (0, 1)
 
 
 @needs_reference
@@ -52,7 +71,7 @@ def test_plans_match_reference(fmt):
                 continue
             mine_names, mine = verify_plan(lanes, 24, layout, history, tree)
             assert mine_names[:2] == names.value.decode().split("\n")
-            assert mine == list(out[:14])
+            assert mine[:14] == list(out[:14])
     for rows in (1, 7, 8, 9, 70, 256, 2047, 2048):
         assert r.ref_prefill_plan(rows, 24, 16, 4, 256, fmt, names, 256, out) == 0
         mine_names, mine = prefill_plan(rows, 24, layout)
