@@ -717,7 +717,8 @@ void *rk_window_create(uint64_t base, uint64_t bytes) {
   w->base = base;
   w->bytes = bytes;
   if (encode_window_map(&w->int4_map, base, bytes >> 7, kTensorBytes / 128) ||
-      encode_window_map(&w->int4_head_map, base, bytes >> 7, kSlabBytes / 128)) {
+      encode_window_map(&w->int4_head_map, base, bytes >> 7, kSlabBytes / 128) ||
+      encode_window_map(&w->byte_head_map, base, bytes >> 7, 2 * kSlabBytes / 128)) {
     delete w;
     return nullptr;
   }

@@ -37,6 +37,7 @@
 #include "common.cuh"
 #include "window.cuh"
 
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 namespace rk {
@@ -59,16 +60,50 @@ constexpr float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
 // shared-memory tiles (bytes); every tile starts 1024-aligned
 constexpr uint32_t kKBytes = kGroupTokens * kD * 2;  // 4 column blocks of [64 rows][64 elements]
 constexpr uint32_t kVBytes = kD * kGroupTokens * 2;  // 1 column block of [256 rows][64 elements]
-constexpr uint32_t kSlabBytes = 4096;                // one head's K (or V) of a page
-constexpr uint32_t kRawStages = 4;
-constexpr uint32_t kRawStageBytes = 17 * 1024;       // K0 | K1 | V0 | V1 | ks0 ks1 vs0 vs1 (128 B each) | pad
-constexpr uint32_t kRawScaleOffset = 4 * kSlabBytes;
-constexpr uint32_t kTileBytes = 2 * kKBytes + 2 * kVBytes + kRawStages * kRawStageBytes;
+constexpr uint32_t kMaxRawStages = 4;
+
+// What differs between the stored formats: the size of one head's K (or V) slab of a page, whether
+// scales exist, how codes become 16-bit tensor-core operands, and the depth of the raw ring that fits.
+//   int4      fp16 operands; key codes as u * 2^-24 with u = code + 8 (the +8 leaves through sum(q)),
+//             odd dims x16 against queries / 16, dims of every 8 in the order (0,4,1,5,2,6,3,7).
+//   int8      fp16 operands; key codes as u * 2^-24 with u = code + 128; values exact (1024 + u - 1152).
+//   fp8 e4m3  fp16 operands, exact (cvt); queries staged as fp16 like the reference's fp8 tile
+//             (paged_attention_fp8_tile.h:34-60).
+//   bf16      bf16 operands (bits as stored); the probabilities are rounded to bf16 too, as the reference's
+//             tile does (paged_attention_tile.h:176-186): both operands of a contraction are of one kind.
+template <uint32_t Format> struct Traits;
+template <> struct Traits<RK_FORMAT_INT4> {
+  static constexpr uint32_t kSlab = 4096, kRawStages = 4;
+  static constexpr bool kScales = true, kBf16 = false;
+  static constexpr float kKeyOffset = 8.0f;
+  static constexpr int kKeyShift = 24;
+};
+template <> struct Traits<RK_FORMAT_INT8> {
+  static constexpr uint32_t kSlab = 8192, kRawStages = 2;
+  static constexpr bool kScales = true, kBf16 = false;
+  static constexpr float kKeyOffset = 128.0f;
+  static constexpr int kKeyShift = 24;
+};
+template <> struct Traits<RK_FORMAT_FP8E4M3> {
+  static constexpr uint32_t kSlab = 8192, kRawStages = 2;
+  static constexpr bool kScales = true, kBf16 = false;
+  static constexpr float kKeyOffset = 0.0f;
+  static constexpr int kKeyShift = 0;
+};
+template <> struct Traits<RK_FORMAT_BF16> {
+  static constexpr uint32_t kSlab = 16384, kRawStages = 1;
+  static constexpr bool kScales = false, kBf16 = true;
+  static constexpr float kKeyOffset = 0.0f;
+  static constexpr int kKeyShift = 0;
+};
+// raw stage: K0 | K1 | V0 | V1 | ks0 ks1 vs0 vs1 (128 B each) | pad to 1 KiB
+template <uint32_t Format> __host__ __device__ constexpr uint32_t raw_stage_bytes() { return 4 * Traits<Format>::kSlab + 1024; }
+template <uint32_t Format> __host__ __device__ constexpr uint32_t tile_bytes() { return 2 * kKBytes + 2 * kVBytes + Traits<Format>::kRawStages * raw_stage_bytes<Format>(); }
 // tensor-memory columns
 constexpr uint32_t kTmemO = 0, kTmemS = 256, kTmemQ = 384; // S twice (64 columns each); P(g) overwrites the first half of S(g)
 
 struct Control {
-  uint64_t raw_full[kRawStages], raw_free[kRawStages];
+  uint64_t raw_full[kMaxRawStages], raw_free[kMaxRawStages];
   uint64_t k_full[2], k_free[2], v_full[2], v_free[2], s_full[2], p_full[2], scale_free[kScaleStages];
   uint32_t tmem_base;
   uint32_t error;
@@ -124,9 +159,9 @@ __device__ __forceinline__ uint64_t umma_descriptor(uint32_t address) {
   desc |= uint64_t(2) << 61;                      // SWIZZLE_128B
   return desc;
 }
-// kind::f16 instruction descriptor: fp16 x fp16 -> fp32, both operands K-major.
-__host__ __device__ constexpr uint32_t umma_instruction(uint32_t m, uint32_t n) {
-  return (1u << 4) | (0u << 7) | (0u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+// kind::f16 instruction descriptor: 16-bit operands (0 = fp16, 1 = bf16) -> fp32, both operands K-major.
+__host__ __device__ constexpr uint32_t umma_instruction(uint32_t m, uint32_t n, uint32_t a_format = 0, uint32_t b_format = 0) {
+  return (1u << 4) | (a_format << 7) | (b_format << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 // True in exactly one lane of a converged warp; unlike a test of the lane index it keeps the surrounding
 // control flow warp-uniform, so descriptors and addresses stay on the uniform datapath.
@@ -194,6 +229,7 @@ __device__ __forceinline__ void tmem_store_packed(uint32_t address, const uint32
 __device__ __forceinline__ float exp2_fast(float x) { float r; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
 __device__ __forceinline__ float log2_fast(float x) { float r; asm("lg2.approx.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) { const __half2 h = __floats2half2_rn(lo, hi); return *reinterpret_cast<const uint32_t *>(&h); }
+__device__ __forceinline__ uint32_t pack_bfloat2(float lo, float hi) { const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi); return *reinterpret_cast<const uint32_t *>(&h); }
 __device__ __forceinline__ uint32_t sub_f16x2(uint32_t a, uint32_t b) { uint32_t r; asm("sub.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b)); return r; }
 __device__ __forceinline__ uint32_t fma_f16x2(uint32_t a, uint32_t b, uint32_t c) { uint32_t r; asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c)); return r; }
 // (a & mask) ^ flip in one logic instruction; both constants sit in registers.
@@ -227,14 +263,178 @@ struct VerifyArgs {
   uint32_t *status; // one word: non-zero when a bounded wait ran out
 };
 
-template <uint32_t Rows, bool kTree>
+
+// ---- raw codes -> 16-bit operand tiles, one team of 128 threads (e = 0..127) per 64-token group -------------
+// K tile: four column blocks of [64 positions][64 dims], 128-byte rows, 128-byte swizzle. V^T tile: one block
+// of [256 dims][64 positions]. `raw` = K0 | K1 | V0 | V1 slabs as TMA left them (128-byte rows, swizzled).
+// `valid` = positions of the group whose tokens exist; formats whose stale bytes can decode to NaN or
+// infinity (fp8, bf16) get zeros at value positions past it, so a zero probability meets a finite value.
+
+template <uint32_t Format> struct Expand;
+
+__device__ __forceinline__ uint32_t mask_pair(uint32_t value, uint32_t position, uint32_t valid) {
+  return value & ((position < valid ? 0x0000FFFFu : 0u) | (position + 1 < valid ? 0xFFFF0000u : 0u));
+}
+
+template <> struct Expand<RK_FORMAT_INT4> {
+  // position 8r+j holds token 8j+r: every access of both transposes is conflict-free
+  __device__ static uint32_t token_of(uint32_t position) { return 8 * (position & 7u) + (position >> 3); }
+  __device__ static void keys(const uint8_t *raw, uint8_t *k_stage, uint32_t e) {
+    const uint32_t low_mask = register_constant(0x000F000Fu), high_mask = register_constant(0x00F000F0u);
+    const uint32_t key_low = register_constant(0x00080008u), key_high = register_constant(0x00800080u);
+    // a thread takes a raw 16-byte chunk (32 dims of one token) = four operand chunks. The eight lanes of an
+    // access phase take tokens 8k + t and chunks c0 ^ k.
+#pragma unroll
+    for (uint32_t i = 0; i < 4; ++i) {
+      const uint32_t item = e + i * kExpandThreads;
+      const uint32_t k8 = item & 7u, c = ((item >> 3) & 7u) ^ k8, t = item >> 6;
+      const uint32_t token = 8 * k8 + t, position = 8 * t + k8;
+      const uint4 x = *reinterpret_cast<const uint4 *>(raw + (token >> 5) * 4096 + swizzled(token & 31u, c));
+      const uint32_t words[4] = {x.x, x.y, x.z, x.w};
+      uint8_t *block = k_stage + (c >> 1) * (kGroupTokens * 128);
+#pragma unroll
+      for (uint32_t w = 0; w < 4; ++w) {
+        const uint32_t y = words[w] >> 8;
+        *reinterpret_cast<uint4 *>(block + swizzled(position, ((c & 1u) << 2) + w)) =
+            make_uint4(and_xor(words[w], low_mask, key_low), and_xor(words[w], high_mask, key_high),
+                       and_xor(y, low_mask, key_low), and_xor(y, high_mask, key_high));
+      }
+    }
+  }
+  __device__ static void values(const uint8_t *raw, uint8_t *v_stage, uint32_t e, uint32_t) {
+    const uint32_t low_mask = register_constant(0x000F000Fu), high_mask = register_constant(0x00F000F0u);
+    const uint32_t value_low = register_constant(0x64086408u), value_high = register_constant(0x64806480u);
+    // thread = (r8, word w of 8 dims) takes tokens 8j + r8, j = 0..7, and transposes 8x8 in registers: each
+    // dim gets a 16-byte run of eight tokens at contraction positions 8*r8 + j.
+#pragma unroll
+    for (uint32_t half = 0; half < 2; ++half) {
+      const uint32_t unit = e + half * kExpandThreads, r8 = unit & 7u, w = unit >> 3;
+      uint32_t x[8];
+#pragma unroll
+      for (uint32_t j = 0; j < 8; ++j)
+        x[j] = *reinterpret_cast<const uint32_t *>(raw + (2 + (j >> 2)) * 4096 + swizzled(8 * (j & 3u) + r8, w >> 2) + (w & 3u) * 4);
+#pragma unroll
+      for (uint32_t byte = 0; byte < 4; ++byte) { // byte of each word = dims 8w+2*byte (low nibble), +1 (high nibble)
+        uint32_t lo[4], hi[4];
+        const uint32_t selector = byte | (byte << 4) | ((4 + byte) << 8) | ((4 + byte) << 12);
+#pragma unroll
+        for (uint32_t pair = 0; pair < 4; ++pair) {
+          const uint32_t joined = __byte_perm(x[2 * pair], x[2 * pair + 1], selector);
+          lo[pair] = sub_f16x2(and_xor(joined, low_mask, value_low), value_low);                                   // 1024+u - 1032
+          hi[pair] = fma_f16x2(and_xor(joined, high_mask, value_high), 0x2C002C00u /* 1/16 */, 0xD480D480u /* -72 */); // (1024+16u)/16 - 72
+        }
+        const uint32_t dim = 8 * w + 2 * byte;
+        *reinterpret_cast<uint4 *>(v_stage + swizzled(dim, r8)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        *reinterpret_cast<uint4 *>(v_stage + swizzled(dim + 1, r8)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+      }
+    }
+  }
+};
+
+// One-byte codes (int8, fp8): K rows are 256 bytes = two 128-byte TMA rows; V rows (one dim) are 32 bytes, four
+// dims to a TMA row. Positions are the tokens in order.
+template <bool kFloat8> struct ExpandBytes {
+  __device__ static uint32_t token_of(uint32_t position) { return position; }
+  // four codes -> two registers of two 16-bit operands
+  __device__ static void key_pairs(uint32_t word, uint32_t &first, uint32_t &second) {
+    if (kFloat8) {
+      asm("{\n.reg .b16 lo, hi;\nmov.b32 {lo, hi}, %2;\ncvt.rn.f16x2.e4m3x2 %0, lo;\ncvt.rn.f16x2.e4m3x2 %1, hi;\n}" : "=r"(first), "=r"(second) : "r"(word));
+    } else { // u = code + 128 as fp16 bits: u * 2^-24
+      const uint32_t flipped = word ^ 0x80808080u;
+      first = __byte_perm(flipped, 0, 0x4140);
+      second = __byte_perm(flipped, 0, 0x4342);
+    }
+  }
+  __device__ static void value_pairs(uint32_t word, uint32_t &first, uint32_t &second) {
+    if (kFloat8) {
+      key_pairs(word, first, second);
+    } else { // 1024 + u, minus 1152: the code itself
+      const uint32_t flipped = word ^ 0x80808080u;
+      first = sub_f16x2(__byte_perm(flipped, 0x64646464u, 0x4140), 0x64806480u);
+      second = sub_f16x2(__byte_perm(flipped, 0x64646464u, 0x4342), 0x64806480u);
+    }
+  }
+  __device__ static void keys(const uint8_t *raw, uint8_t *k_stage, uint32_t e) {
+    // item = (token, 16-byte chunk c of its 256-byte row): 16 dims -> two operand chunks
+#pragma unroll
+    for (uint32_t i = 0; i < 8; ++i) {
+      const uint32_t item = e + i * kExpandThreads, c = item & 15u, token = item >> 4;
+      const uint32_t row = 2 * (token & 31u) + (c >> 3);
+      const uint4 x = *reinterpret_cast<const uint4 *>(raw + (token >> 5) * 8192 + swizzled(row, c & 7u));
+      uint32_t out[8];
+      key_pairs(x.x, out[0], out[1]); key_pairs(x.y, out[2], out[3]);
+      key_pairs(x.z, out[4], out[5]); key_pairs(x.w, out[6], out[7]);
+      uint8_t *block = k_stage + (c >> 2) * (kGroupTokens * 128);
+      *reinterpret_cast<uint4 *>(block + swizzled(token, 2 * (c & 3u))) = make_uint4(out[0], out[1], out[2], out[3]);
+      *reinterpret_cast<uint4 *>(block + swizzled(token, 2 * (c & 3u) + 1)) = make_uint4(out[4], out[5], out[6], out[7]);
+    }
+  }
+  __device__ static void values(const uint8_t *raw, uint8_t *v_stage, uint32_t e, uint32_t valid) {
+    // item = (page, dim, half h of its 32 tokens): 16 tokens -> two operand chunks of the dim's row
+#pragma unroll
+    for (uint32_t i = 0; i < 8; ++i) {
+      const uint32_t item = e + i * kExpandThreads, h = item & 1u, dim = (item >> 1) & 255u, page = item >> 9;
+      const uint4 x = *reinterpret_cast<const uint4 *>(raw + (2 + page) * 8192 + swizzled(dim >> 2, 2 * (dim & 3u) + h));
+      uint32_t out[8];
+      value_pairs(x.x, out[0], out[1]); value_pairs(x.y, out[2], out[3]);
+      value_pairs(x.z, out[4], out[5]); value_pairs(x.w, out[6], out[7]);
+      const uint32_t position = 32 * page + 16 * h;
+      if (kFloat8 && position + 16 > valid) {
+#pragma unroll
+        for (uint32_t r = 0; r < 8; ++r) out[r] = mask_pair(out[r], position + 2 * r, valid);
+      }
+      *reinterpret_cast<uint4 *>(v_stage + swizzled(dim, 4 * page + 2 * h)) = make_uint4(out[0], out[1], out[2], out[3]);
+      *reinterpret_cast<uint4 *>(v_stage + swizzled(dim, 4 * page + 2 * h + 1)) = make_uint4(out[4], out[5], out[6], out[7]);
+    }
+  }
+};
+template <> struct Expand<RK_FORMAT_INT8> : ExpandBytes<false> {};
+template <> struct Expand<RK_FORMAT_FP8E4M3> : ExpandBytes<true> {};
+
+// bf16: the stored bits are the operands; the expansion is a re-tiling copy. K rows are 512 bytes = four TMA
+// rows (= the four column blocks); V rows (one dim) are 64 bytes, two dims to a TMA row.
+template <> struct Expand<RK_FORMAT_BF16> {
+  __device__ static uint32_t token_of(uint32_t position) { return position; }
+  __device__ static void keys(const uint8_t *raw, uint8_t *k_stage, uint32_t e) {
+#pragma unroll
+    for (uint32_t i = 0; i < 16; ++i) {
+      const uint32_t item = e + i * kExpandThreads, c = item & 31u, token = item >> 5;
+      const uint32_t row = 4 * (token & 31u) + (c >> 3);
+      const uint4 x = *reinterpret_cast<const uint4 *>(raw + (token >> 5) * 16384 + swizzled(row, c & 7u));
+      *reinterpret_cast<uint4 *>(k_stage + (c >> 3) * (kGroupTokens * 128) + swizzled(token, c & 7u)) = x;
+    }
+  }
+  __device__ static void values(const uint8_t *raw, uint8_t *v_stage, uint32_t e, uint32_t valid) {
+#pragma unroll
+    for (uint32_t i = 0; i < 16; ++i) {
+      const uint32_t item = e + i * kExpandThreads, q = item & 3u, dim = (item >> 2) & 255u, page = item >> 10;
+      uint4 x = *reinterpret_cast<const uint4 *>(raw + (2 + page) * 16384 + swizzled(dim >> 1, 4 * (dim & 1u) + q));
+      const uint32_t position = 32 * page + 8 * q;
+      if (position + 8 > valid) {
+        x.x = mask_pair(x.x, position, valid); x.y = mask_pair(x.y, position + 2, valid);
+        x.z = mask_pair(x.z, position + 4, valid); x.w = mask_pair(x.w, position + 6, valid);
+      }
+      *reinterpret_cast<uint4 *>(v_stage + swizzled(dim, 4 * page + q)) = x;
+    }
+  }
+};
+
+template <uint32_t Format, uint32_t Rows, bool kTree>
 __global__ void __launch_bounds__(kThreads, 1)
-verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args) {
-  constexpr uint32_t kRealRows = Rows * kG; // fused rows that exist
+window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args) {
+  using Kind = Traits<Format>;
+  constexpr uint32_t kRealRows = Rows * kG;                       // fused rows that exist
+  constexpr uint32_t kQuarters = (kRealRows + 31) / 32;           // 32-row quarters of the tile that hold real rows
+  constexpr uint32_t kActiveSoftmax = kQuarters * kRowThreads * 32; // softmax threads that take part
+  constexpr uint32_t kSlab = Kind::kSlab, kRawStages = Kind::kRawStages, kRawStageBytes = raw_stage_bytes<Format>();
+  constexpr uint32_t kRawScaleOffset = 4 * kSlab;
+  // Barriers of the raw ring: one pair per stage, but never fewer than two, so that the two expander teams,
+  // which alternate groups, never wait on the same barrier (a waiter two completions behind would misread parity).
+  constexpr uint32_t kRawBarriers = kRawStages < 2 ? 2 : kRawStages;
   extern __shared__ uint8_t dynamic_shared[];
   const uint32_t tiles = (smem_u32(dynamic_shared) + 1023u) & ~1023u;
   uint8_t *tile_ptr = dynamic_shared + (tiles - smem_u32(dynamic_shared));
-  Control &ctl = *reinterpret_cast<Control *>(tile_ptr + kTileBytes);
+  Control &ctl = *reinterpret_cast<Control *>(tile_ptr + tile_bytes<Format>());
   volatile uint32_t *error = &ctl.error;
   const uint32_t k_tile = tiles, v_tile = k_tile + 2 * kKBytes, raw_tile = v_tile + 2 * kVBytes; // K[2] | V[2] | raw ring
   uint8_t *k_ptr = tile_ptr, *v_ptr = k_ptr + 2 * kKBytes;
@@ -257,7 +457,7 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
 
   // ---- setup: barriers, TMEM, query tile ----------------------------------------------------------
   if (tid == 0) {
-    for (uint32_t r = 0; r < kRawStages; ++r) {
+    for (uint32_t r = 0; r < kRawBarriers; ++r) {
       barrier_init(smem_u32(&ctl.raw_full[r]), 1);
       barrier_init(smem_u32(&ctl.raw_free[r]), kExpandThreads);
     }
@@ -267,9 +467,9 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
       barrier_init(smem_u32(&ctl.k_free[b]), 1);
       barrier_init(smem_u32(&ctl.v_free[b]), 1);
       barrier_init(smem_u32(&ctl.s_full[b]), 1);
-      barrier_init(smem_u32(&ctl.p_full[b]), kSoftmaxThreads);
+      barrier_init(smem_u32(&ctl.p_full[b]), kActiveSoftmax);
     }
-    for (uint32_t b = 0; b < kScaleStages; ++b) barrier_init(smem_u32(&ctl.scale_free[b]), kSoftmaxThreads);
+    for (uint32_t b = 0; b < kScaleStages; ++b) barrier_init(smem_u32(&ctl.scale_free[b]), kActiveSoftmax);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     ctl.error = 0;
   }
@@ -282,15 +482,15 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
   tmem_fence_after();
   const uint32_t tmem = ctl.tmem_base;
   const uint32_t tmem_o = tmem + kTmemO, tmem_s = tmem + kTmemS, tmem_q = tmem + kTmemQ;
-  const uint32_t data_bytes = kPageTokens * kHeads * kD / 2, scale_bytes = kPageTokens * kHeads * 4;
+  const uint32_t data_bytes = kHeads * kSlab, scale_bytes = Kind::kScales ? kPageTokens * kHeads * 4 : 0;
 
-  // Query tile into tensor memory: the row's threads convert 128/kRowThreads columns each: fp16, element
-  // order (0,4,1,5,2,6,3,7) inside every 8 dims, dims 1,5,3,7 divided by 16.
+  // Query tile into tensor memory: the row's threads convert 128/kRowThreads columns each. int4: fp16, element
+  // order (0,4,1,5,2,6,3,7) inside every 8 dims, dims 1,5,3,7 divided by 16; int8, fp8: fp16 in order; bf16: the bits.
   if (warp < kSoftmaxWarps) {
     const uint32_t quarter = warp & 3u, part = warp >> 2, row = quarter * 32 + lane;
     const uint16_t *queries = args.queries + (uint64_t(lane_index) * kHeads + kv_head) * (uint64_t(RK_VERIFY_CHUNK_STRIDE) * kG * kD);
     const bool real = row < p.active_rows * kG;
-    float q_sum = 0.0f; // over the fp16 values the tensor core will see, for the +8 correction
+    float q_sum = 0.0f; // over the values the tensor core will see, for the key-offset correction
 #pragma unroll 1
     for (uint32_t piece = 0; piece < 4 / kRowThreads; ++piece) { // 32 columns = 8 chunks of 8 dims
       const uint32_t column = part * (128 / kRowThreads) + piece * 32;
@@ -300,17 +500,29 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
         uint4 raw = make_uint4(0, 0, 0, 0);
         if (real) raw = __ldg(reinterpret_cast<const uint4 *>(queries + uint64_t(row) * kD + 2 * column + 8 * c));
         const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
-        float d[8];
+        uint32_t chunk[4];
+        if (Kind::kBf16) {
 #pragma unroll
-        for (uint32_t i = 0; i < 4; ++i) { d[2 * i] = bf16_bits_to_float(words[i] & 0xffffu); d[2 * i + 1] = bf16_bits_to_float(words[i] >> 16); }
-        const uint32_t chunk[4] = {pack_half2(d[0], d[4]), pack_half2(d[1] * 0.0625f, d[5] * 0.0625f),
-                                   pack_half2(d[2], d[6]), pack_half2(d[3] * 0.0625f, d[7] * 0.0625f)};
+          for (uint32_t i = 0; i < 4; ++i) chunk[i] = words[i];
+        } else {
+          float d[8];
 #pragma unroll
-        for (uint32_t i = 0; i < 4; ++i) {
-          const __half2 h = *reinterpret_cast<const __half2 *>(&chunk[i]);
-          q_sum += ((i & 1u) ? 16.0f : 1.0f) * (__low2float(h) + __high2float(h));
-          columns[c * 4 + i] = __uint_as_float(chunk[i]);
+          for (uint32_t i = 0; i < 4; ++i) { d[2 * i] = bf16_bits_to_float(words[i] & 0xffffu); d[2 * i + 1] = bf16_bits_to_float(words[i] >> 16); }
+          if (Format == RK_FORMAT_INT4) {
+            chunk[0] = pack_half2(d[0], d[4]); chunk[1] = pack_half2(d[1] * 0.0625f, d[5] * 0.0625f);
+            chunk[2] = pack_half2(d[2], d[6]); chunk[3] = pack_half2(d[3] * 0.0625f, d[7] * 0.0625f);
+          } else {
+#pragma unroll
+            for (uint32_t i = 0; i < 4; ++i) chunk[i] = pack_half2(d[2 * i], d[2 * i + 1]);
+          }
+#pragma unroll
+          for (uint32_t i = 0; i < 4; ++i) {
+            const __half2 h = *reinterpret_cast<const __half2 *>(&chunk[i]);
+            q_sum += ((Format == RK_FORMAT_INT4 && (i & 1u)) ? 16.0f : 1.0f) * (__low2float(h) + __high2float(h));
+          }
         }
+#pragma unroll
+        for (uint32_t i = 0; i < 4; ++i) columns[c * 4 + i] = __uint_as_float(chunk[i]);
       }
       tmem_store32(tmem_q + ((quarter * 32u) << 16) + column, columns);
     }
@@ -332,42 +544,44 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
     if (lane == 0) {
       rk_page_entry next[2] = {table[page_begin], page_begin + 1 < page_end ? table[page_begin + 1] : 0};
       for (uint32_t g = 0; g < groups; ++g) {
-        const uint32_t r = g % kRawStages, use = g / kRawStages;
+        const uint32_t r = g % kRawStages, slot = g % kRawBarriers;
         const uint32_t first = page_begin + 2 * g, group_pages = min(2u, page_end - first);
         const rk_page_entry entries[2] = {next[0], next[1]};
         if (g + 1 < groups) { // the next group's entries travel while this group is issued
           next[0] = table[first + 2];
           next[1] = first + 3 < page_end ? table[first + 3] : 0;
         }
-        if (use) barrier_wait(&ctl.raw_free[r], use - 1, error);
-        const uint32_t full = smem_u32(&ctl.raw_full[r]), stage = raw_tile + r * kRawStageBytes;
-        barrier_expect(full, group_pages * (2 * kSlabBytes + 256));
+        if (g >= kRawStages) barrier_wait(&ctl.raw_free[(g - kRawStages) % kRawBarriers], (g - kRawStages) / kRawBarriers, error); // the stage's last reader
+        const uint32_t full = smem_u32(&ctl.raw_full[slot]), stage = raw_tile + r * kRawStageBytes;
+        barrier_expect(full, group_pages * (2 * kSlab + (Kind::kScales ? 256 : 0)));
 #pragma unroll
         for (uint32_t local = 0; local < 2; ++local) {
           if (local >= group_pages) break;
           const uint32_t index = rk_entry_index(entries[local]);
           const uint64_t region = rk_entry_extent(entries[local]) + args.layer.offset;
           const uint64_t extent_pages = args.layer.extent_pages;
-          const uint64_t keys = region + uint64_t(index) * data_bytes + kv_head * kSlabBytes;
-          const uint64_t values = region + extent_pages * (uint64_t(data_bytes) + scale_bytes) + uint64_t(index) * data_bytes + kv_head * kSlabBytes;
+          const uint64_t keys = region + uint64_t(index) * data_bytes + kv_head * kSlab;
+          const uint64_t values = region + extent_pages * (uint64_t(data_bytes) + scale_bytes) + uint64_t(index) * data_bytes + kv_head * kSlab;
           const uint64_t key_scales = region + extent_pages * data_bytes + uint64_t(index) * scale_bytes + kv_head * 128u;
           const uint64_t value_scales = region + extent_pages * (2ull * data_bytes + scale_bytes) + uint64_t(index) * scale_bytes + kv_head * 128u;
-          tma_load_rows(stage + local * kSlabBytes, &head_map, int32_t((keys - args.window_base) >> 7), full);
-          tma_load_rows(stage + (2 + local) * kSlabBytes, &head_map, int32_t((values - args.window_base) >> 7), full);
-          bulk_load(stage + kRawScaleOffset + local * 128, reinterpret_cast<const void *>(key_scales), 128, full);
-          bulk_load(stage + kRawScaleOffset + (2 + local) * 128, reinterpret_cast<const void *>(value_scales), 128, full);
+          tma_load_rows(stage + local * kSlab, &head_map, int32_t((keys - args.window_base) >> 7), full);
+          tma_load_rows(stage + (2 + local) * kSlab, &head_map, int32_t((values - args.window_base) >> 7), full);
+          if (Kind::kScales) {
+            bulk_load(stage + kRawScaleOffset + local * 128, reinterpret_cast<const void *>(key_scales), 128, full);
+            bulk_load(stage + kRawScaleOffset + (2 + local) * 128, reinterpret_cast<const void *>(value_scales), 128, full);
+          }
         }
       }
       // Every copy this thread started has landed before the CTA may leave (also after a failed wait).
       for (uint32_t g = groups > kRawStages ? groups - kRawStages : 0; g < groups; ++g) {
-        const uint32_t bar = smem_u32(&ctl.raw_full[g % kRawStages]), parity = (g / kRawStages) & 1u;
+        const uint32_t bar = smem_u32(&ctl.raw_full[g % kRawBarriers]), parity = (g / kRawBarriers) & 1u;
         for (uint32_t i = 0; i < kSpinLimit && !barrier_try(bar, parity); ++i) __nanosleep(64);
       }
     }
   } else if (warp == kScoreWarp) {
     // ---- tensor-core issue, S = Q.K^T: S buffer g&1 is free once PV(g-2), which read P(g-2) from it, has landed ----
     // The whole warp walks the loop (uniform control flow); one elected lane issues.
-    const uint32_t idesc_qk = umma_instruction(kM, kGroupTokens);
+    const uint32_t idesc_qk = umma_instruction(kM, kGroupTokens, Kind::kBf16, Kind::kBf16);
     // a descriptor advances by (bytes >> 4) in its low word; nothing here carries out of the 14-bit field
     const uint64_t k_desc0 = umma_descriptor(k_tile), k_desc1 = umma_descriptor(k_tile + kKBytes);
     for (uint32_t g = 0; g < groups; ++g) {
@@ -388,7 +602,7 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
     }
   } else if (warp == kValueWarp) {
     // ---- tensor-core issue, O += P.V ------------------------------------------------------------------------------
-    const uint32_t idesc_pv = umma_instruction(kM, kD);
+    const uint32_t idesc_pv = umma_instruction(kM, kD, Kind::kBf16, Kind::kBf16); // both operands of one kind: bf16 values take bf16 probabilities
     const uint64_t v_desc0 = umma_descriptor(v_tile), v_desc1 = umma_descriptor(v_tile + kVBytes);
     for (uint32_t g = 0; g < groups; ++g) {
       const uint32_t b = g & 1u;
@@ -405,88 +619,50 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
       __syncwarp();
     }
   } else if (warp >= kSoftmaxWarps) {
-    // ---- expanders: raw nibbles -> fp16 operand tiles ---------------------------------------------------------
+    // ---- expanders: raw codes -> 16-bit operand tiles --------------------------------------------------------------
     const uint32_t team = (warp - kSoftmaxWarps) >> 2, e = tid - kSoftmaxThreads - team * kExpandThreads;
-    const uint32_t low_mask = register_constant(0x000F000Fu), high_mask = register_constant(0x00F000F0u);
-    const uint32_t key_low = register_constant(0x00080008u), key_high = register_constant(0x00800080u);
-    const uint32_t value_low = register_constant(0x64086408u), value_high = register_constant(0x64806480u);
     for (uint32_t g = team; g < groups; g += 2) {
-      const uint32_t r = g % kRawStages, use = g / kRawStages, b = team;
-      const uint32_t group_pages = min(2u, page_end - (page_begin + 2 * g));
+      const uint32_t r = g % kRawStages, slot = g % kRawBarriers, b = team;
+      const uint32_t first = page_begin + 2 * g;
+      // positions of the group whose tokens exist: the split may end inside the group, the lane inside the page
+      const uint32_t valid = min(min(2u, page_end - first) * kPageTokens, visible - first * kPageTokens);
       const uint8_t *raw = raw_ptr + r * kRawStageBytes;
-      barrier_wait(&ctl.raw_full[r], use, error);
-      // per-position scale triples; tokens of an absent page get harmless zeros
+      barrier_wait(&ctl.raw_full[slot], g / kRawBarriers, error);
+      // per-position scale triples {key scale, log2 value scale, 2^-6 / value scale}; zeros past the valid tokens
+      // (stale scale bytes never reach the arithmetic)
       if (e < kGroupTokens) {
         if (g >= kScaleStages) barrier_wait(&ctl.scale_free[g % kScaleStages], g / kScaleStages - 1, error);
-        const uint32_t token = 8 * (e & 7u) + (e >> 3), local = token >> 5;
+        const uint32_t token = Expand<Format>::token_of(e);
         float4 triple = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        if (local < group_pages) {
-          const float ks = reinterpret_cast<const float *>(raw + kRawScaleOffset)[token];
-          const float vs = fmaxf(reinterpret_cast<const float *>(raw + kRawScaleOffset)[64 + token], 9.094947e-13f); // 2^-40
-          triple = make_float4(ks, log2_fast(vs), __fdividef(0.015625f, vs), 0.0f);
+        if (token < valid) {
+          if (Kind::kScales) {
+            const float ks = reinterpret_cast<const float *>(raw + kRawScaleOffset)[token];
+            const float vs = fmaxf(reinterpret_cast<const float *>(raw + kRawScaleOffset)[64 + token], 9.094947e-13f); // 2^-40
+            triple = make_float4(ks, log2_fast(vs), __fdividef(0.015625f, vs), 0.0f);
+          } else {
+            triple = make_float4(1.0f, 0.0f, 0.015625f, 0.0f);
+          }
         }
         ctl.scales[g % kScaleStages][e] = triple;
       }
       if (g >= 2) barrier_wait(&ctl.k_free[b], (g >> 1) - 1, error);
-      // keys: a thread takes a raw 16-byte chunk (32 dims of one token) = four operand chunks; the token
-      // goes to row `position`. The eight lanes of an access phase take tokens 8k + t and chunks c0 ^ k:
-      // conflict-free on the swizzled raw side and on the swizzled operand side.
-      uint8_t *k_stage = k_ptr + b * kKBytes;
-#pragma unroll
-      for (uint32_t i = 0; i < 4; ++i) {
-        const uint32_t item = e + i * kExpandThreads;
-        const uint32_t k8 = item & 7u, c = ((item >> 3) & 7u) ^ k8, t = item >> 6;
-        const uint32_t token = 8 * k8 + t, position = 8 * t + k8;
-        const uint4 x = *reinterpret_cast<const uint4 *>(raw + (token >> 5) * kSlabBytes + swizzled(token & 31u, c));
-        const uint32_t words[4] = {x.x, x.y, x.z, x.w};
-        uint8_t *block = k_stage + (c >> 1) * (kGroupTokens * 128);
-#pragma unroll
-        for (uint32_t w = 0; w < 4; ++w) {
-          const uint32_t y = words[w] >> 8;
-          *reinterpret_cast<uint4 *>(block + swizzled(position, ((c & 1u) << 2) + w)) =
-              make_uint4(and_xor(words[w], low_mask, key_low), and_xor(words[w], high_mask, key_high),
-                         and_xor(y, low_mask, key_low), and_xor(y, high_mask, key_high));
-        }
-      }
+      Expand<Format>::keys(raw, k_ptr + b * kKBytes, e);
       async_proxy_fence();
       barrier_arrive(smem_u32(&ctl.k_full[b]));
       if (g >= 2) barrier_wait(&ctl.v_free[b], (g >> 1) - 1, error);
-      // values: thread = (r8, word w of 8 dims) takes tokens 8j + r8, j = 0..7, and transposes 8x8 in
-      // registers: each dim gets a 16-byte run of eight tokens at contraction positions 8*r8 + j.
-      uint8_t *v_stage = v_ptr + b * kVBytes;
-#pragma unroll
-      for (uint32_t half = 0; half < 2; ++half) {
-        const uint32_t unit = e + half * kExpandThreads, r8 = unit & 7u, w = unit >> 3;
-        uint32_t x[8];
-#pragma unroll
-        for (uint32_t j = 0; j < 8; ++j)
-          x[j] = *reinterpret_cast<const uint32_t *>(raw + (2 + (j >> 2)) * kSlabBytes + swizzled(8 * (j & 3u) + r8, w >> 2) + (w & 3u) * 4);
-#pragma unroll
-        for (uint32_t byte = 0; byte < 4; ++byte) { // byte of each word = dims 8w+2*byte (low nibble), +1 (high nibble)
-          uint32_t lo[4], hi[4];
-          const uint32_t selector = byte | (byte << 4) | ((4 + byte) << 8) | ((4 + byte) << 12);
-#pragma unroll
-          for (uint32_t pair = 0; pair < 4; ++pair) {
-            const uint32_t joined = __byte_perm(x[2 * pair], x[2 * pair + 1], selector);
-            lo[pair] = sub_f16x2(and_xor(joined, low_mask, value_low), value_low);                                   // 1024+u - 1032
-            hi[pair] = fma_f16x2(and_xor(joined, high_mask, value_high), 0x2C002C00u /* 1/16 */, 0xD480D480u /* -72 */); // (1024+16u)/16 - 72
-          }
-          const uint32_t dim = 8 * w + 2 * byte;
-          *reinterpret_cast<uint4 *>(v_stage + swizzled(dim, r8)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-          *reinterpret_cast<uint4 *>(v_stage + swizzled(dim + 1, r8)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-        }
-      }
+      Expand<Format>::values(raw, v_ptr + b * kVBytes, e, valid);
       async_proxy_fence();
       barrier_arrive(smem_u32(&ctl.v_full[b]));
-      barrier_arrive(smem_u32(&ctl.raw_free[r]));
+      barrier_arrive(smem_u32(&ctl.raw_free[slot]));
     }
-  } else {
-    // ---- softmax: kRowThreads threads per fused row (= TMEM lane), kRowTokens contraction positions each ----
+  } else if ((warp & 3u) < kQuarters) {
+    // ---- softmax: kRowThreads threads per fused row (= TMEM lane), kRowTokens contraction positions each;
+    // quarters of the tile without a real row sit the loop out ----
     const uint32_t quarter = warp & 3u, part = warp >> 2;
     const uint32_t my_row = quarter * 32 + lane;
     const float score_scale = rk_score_scale(p.score_scale, kD) * kLog2e;
-    const float row_factor = ldexpf(score_scale, 24);
-    const float row_offset = -8.0f * ctl.q_sums[my_row] * score_scale;
+    const float row_factor = ldexpf(score_scale, Kind::kKeyShift);
+    const float row_offset = -Kind::kKeyOffset * ctl.q_sums[my_row] * score_scale;
     const uint32_t query_row = my_row / kG;
     const uint32_t causal_limit = min(visible, p.committed_tokens + min(query_row, p.active_rows - 1) + 1);
     const uint32_t tree_mask = kTree && query_row < p.row_capacity ? row_masks[query_row] : 0u;
@@ -497,11 +673,13 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
     for (uint32_t g = 0; g < groups; ++g) {
       const uint32_t first = page_begin + 2 * g, b = g & 1u;
       const uint32_t token_base = first * kPageTokens;
-      // tokens of the group that exist (a split may end inside it) and, on a chain, pass the causal rule;
-      // position kRowTokens*part + i holds token 8*(i%8) + i/8 + (kRowTokens/8)*part
+      // tokens of the group that exist (a split may end inside it) and, on a chain, pass the causal rule.
+      // int4: position kRowTokens*part + i holds token 8*(i%8) + i/8 + (kRowTokens/8)*part; else token = position
       const uint32_t present = min(2u, page_end - first) * kPageTokens;
       const uint32_t limit = kTree ? present : min(present, causal_limit > token_base ? causal_limit - token_base : 0u);
-      const int32_t bound = int32_t(limit) - int32_t((kRowTokens / 8) * part);
+      constexpr bool kPermuted = Format == RK_FORMAT_INT4;
+      const uint32_t part_token = kPermuted ? (kRowTokens / 8) * part : kRowTokens * part;
+      const int32_t bound = int32_t(limit) - int32_t(part_token);
       const float4 *triples = ctl.scales[g % kScaleStages] + part * kRowTokens;
       barrier_wait(&ctl.s_full[b], g >> 1, error);
       tmem_fence_after();
@@ -509,7 +687,7 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
       tmem_load_scores(tmem_s + b * 64 + lane_address + part * kRowTokens, scores);
 
       float group_max = -INFINITY;
-      if (!kTree && bound >= 64) { // every token of the group is admitted (all but the last groups of a lane)
+      if (!kTree && limit >= kGroupTokens) { // every token of the group is admitted (all but the last groups of a lane)
 #pragma unroll
         for (uint32_t i = 0; i < kRowTokens; ++i) {
           const float4 triple = triples[i];
@@ -519,10 +697,10 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
       } else {
 #pragma unroll
         for (uint32_t i = 0; i < kRowTokens; ++i) {
-          const int32_t local = int32_t(8 * (i & 7u) + (i >> 3));
+          const int32_t local = kPermuted ? int32_t(8 * (i & 7u) + (i >> 3)) : int32_t(i);
           bool admitted = local < bound;
           if (kTree) {
-            const uint32_t token = token_base + uint32_t(local) + (kRowTokens / 8) * part;
+            const uint32_t token = token_base + uint32_t(local) + part_token;
             admitted = admitted && (token < p.committed_tokens || (token < visible && ((tree_mask >> (token - p.committed_tokens)) & 1u)));
           }
           const float4 triple = triples[i];
@@ -558,7 +736,7 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
           w[h] = exp2_fast(scores[2 * c + h] - exponent_base);     // 0 for a masked token
           row_sum = fmaf(w[h], triples[2 * c + h].z, row_sum);     // 2^(score - row_max)
         }
-        packed[c] = pack_half2(w[0], w[1]);
+        packed[c] = Kind::kBf16 ? pack_bfloat2(w[0], w[1]) : pack_half2(w[0], w[1]);
       }
       if (g && __any_sync(0xffffffffu, grow)) { // this part rescales its columns of O once P.V(g-1) has landed
         barrier_wait(&ctl.v_free[b ^ 1u], (g - 1) >> 1, error);
@@ -616,19 +794,39 @@ verify_int4_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args
 
 using namespace rk;
 
-// verify_attention_int4_split / verify_tree_attention_int4_split for 8 or 16 rows as a tcgen05
-// contraction (decode/paged_attention.metal:23-192). Arguments and scratch layout as
-// rk_attention_verify_split plus the pool's window (rk_window_create); `status` is one device word the
-// caller zeroes, non-zero after a bounded wait ran out. Merge with rk_attention_verify_reduce.
+// verify_attention_{int4,q8,fp8,bf16}_split and the tree variants (decode/paged_attention.metal:23-192,
+// decode/fp8_attention.metal:8-62) as a tcgen05 contraction for row capacity 1 (plain decode), 8 or 16.
+// Arguments and scratch layout as rk_attention_verify_split plus the pool's window (rk_window_create);
+// `status` is one device word the caller zeroes, non-zero after a bounded wait ran out. Merge with
+// rk_attention_verify_reduce.
+namespace {
+template <uint32_t Format>
+int launch_window(const Window *w, uint32_t lanes, uint32_t row_capacity, uint32_t grid_splits, const VerifyArgs &args, cudaStream_t s) {
+  constexpr size_t shared_bytes = 1024 + tile_bytes<Format>() + sizeof(Control);
+  const CUtensorMap &map = Format == RK_FORMAT_INT4 ? w->int4_head_map : Format == RK_FORMAT_BF16 ? w->int4_map : w->byte_head_map;
+  const dim3 grid(kHeads, grid_splits, lanes);
+  auto launch = [&](auto kernel) -> int {
+    if (int st = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(shared_bytes)), "window kernel shared memory")) return st;
+    kernel<<<grid, kThreads, shared_bytes, s>>>(map, args);
+    return kOk;
+  };
+  const bool tree = args.row_masks != nullptr;
+  if (row_capacity == 1) return launch(window_attention_kernel<Format, 1, false>);
+  if (row_capacity == 8) return tree ? launch(window_attention_kernel<Format, 8, true>) : launch(window_attention_kernel<Format, 8, false>);
+  return tree ? launch(window_attention_kernel<Format, 16, true>) : launch(window_attention_kernel<Format, 16, false>);
+}
+} // namespace
+
 extern "C" int rk_attention_verify_split_tc(const void *window, uint32_t format, uint32_t kv_heads, uint32_t query_heads,
                                             uint32_t head_dim, uint32_t lanes, uint32_t row_capacity, uint32_t grid_splits,
                                             const void *queries, float *partials, float *statistics,
                                             const rk_page_entry *const *tables, const uint32_t *row_masks,
                                             const rk_verify_params *lane_params, rk_kv_layer layer, uint32_t *status,
                                             void *stream) {
-  if (kv_heads != kHeads || query_heads != kHeads * kG || head_dim != kD || format != RK_FORMAT_INT4 ||
-      (row_capacity != 8 && row_capacity != 16)) {
-    set_error("rk_attention_verify_split_tc: built for int4, 4 KV heads x 24 query heads x 256, 8 or 16 rows");
+  if (kv_heads != kHeads || query_heads != kHeads * kG || head_dim != kD || !rk_format_valid(format) ||
+      (row_capacity != 1 && row_capacity != 8 && row_capacity != 16) || (row_capacity == 1 && row_masks) ||
+      (format == RK_FORMAT_FP8E4M3 && row_masks)) {
+    set_error("rk_attention_verify_split_tc: built for 4 KV heads x 24 query heads x 256, row capacity 1, 8 or 16 (tree: 8 or 16, not fp8)");
     return kUnsupported;
   }
   const auto *w = static_cast<const Window *>(window);
@@ -637,18 +835,15 @@ extern "C" int rk_attention_verify_split_tc(const void *window, uint32_t format,
     set_error("rk_attention_verify_split_tc: invalid arguments");
     return kInvalid;
   }
-  constexpr size_t shared_bytes = 1024 + kTileBytes + sizeof(Control);
   VerifyArgs args{static_cast<const uint16_t *>(queries), partials, statistics, tables, row_masks, lane_params, layer, w->base, status};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const dim3 grid(kHeads, grid_splits, lanes);
-  auto launch = [&](auto kernel) -> int {
-    if (int st = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(shared_bytes)), "verify shared memory")) return st;
-    kernel<<<grid, kThreads, shared_bytes, s>>>(w->int4_head_map, args);
-    return kOk;
-  };
-  int st;
-  if (row_capacity == 8) st = row_masks ? launch(verify_int4_kernel<8, true>) : launch(verify_int4_kernel<8, false>);
-  else st = row_masks ? launch(verify_int4_kernel<16, true>) : launch(verify_int4_kernel<16, false>);
+  int st = kUnsupported;
+  switch (format) {
+  case RK_FORMAT_INT4: st = launch_window<RK_FORMAT_INT4>(w, lanes, row_capacity, grid_splits, args, s); break;
+  case RK_FORMAT_INT8: st = launch_window<RK_FORMAT_INT8>(w, lanes, row_capacity, grid_splits, args, s); break;
+  case RK_FORMAT_FP8E4M3: st = launch_window<RK_FORMAT_FP8E4M3>(w, lanes, row_capacity, grid_splits, args, s); break;
+  case RK_FORMAT_BF16: st = launch_window<RK_FORMAT_BF16>(w, lanes, row_capacity, grid_splits, args, s); break;
+  }
   if (st) return st;
-  return cuda_status(cudaGetLastError(), "verify tcgen05 launch");
+  return cuda_status(cudaGetLastError(), "window kernel launch");
 }

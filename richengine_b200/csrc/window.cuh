@@ -1,9 +1,9 @@
 // window.cuh — the device address window of a pool and its TMA tensor maps.
 //
-// Every extent of a pool is mapped inside one virtual address range (rk_storage_window), so a single
-// tensor map of 128-byte rows covers every int4 page: a page's K (or V) data of all four heads is 128
-// consecutive rows, one head's slab 32 of them. Two maps over the same rows differ only in the box:
-// 128 rows (the decode kernel copies all heads of a page at once) and 32 rows (one head's slab).
+// Every extent of a pool is mapped inside one virtual address range (rk_storage_window), so a tensor
+// map of 128-byte rows covers every page whatever the format: one head's K (or V) slab of a page is 32
+// (int4), 64 (int8, fp8) or 128 (bf16) consecutive rows, all four heads of an int4 page 128. The maps
+// over the same rows differ only in the box.
 #pragma once
 
 #include <cuda.h>
@@ -13,8 +13,9 @@ namespace rk {
 
 struct Window {
   uint64_t base = 0, bytes = 0;
-  CUtensorMap int4_map;      // box = 128 rows: all heads of a page
-  CUtensorMap int4_head_map; // box = 32 rows: one head's slab
+  CUtensorMap int4_map;      // box = 128 rows: all heads of an int4 page (also one head's bf16 slab)
+  CUtensorMap int4_head_map; // box = 32 rows: one head's int4 slab
+  CUtensorMap byte_head_map; // box = 64 rows: one head's int8 / fp8 slab
 };
 
 int encode_window_map(CUtensorMap *map, uint64_t base, uint64_t rows, uint32_t box_rows);
