@@ -46,9 +46,8 @@ namespace {
 constexpr uint32_t kRowThreads = 4;                      // softmax threads per fused row (one per warp of the row's quarter)
 constexpr uint32_t kSoftmaxWarps = 4 * kRowThreads;
 constexpr uint32_t kRowTokens = 64 / kRowThreads;         // contraction positions of a group per softmax thread
-constexpr uint32_t kExpandWarps = 8;   // two teams of four warps: team t expands the groups g = t (mod 2) into stage t
+constexpr uint32_t kExpandWarps = 8;   // kTileStages teams: team t expands the groups g = t (mod kTileStages) into operand stage t
 constexpr uint32_t kSoftmaxThreads = kSoftmaxWarps * 32;
-constexpr uint32_t kExpandThreads = kExpandWarps * 32 / 2; // threads of one team
 constexpr uint32_t kThreads = (kSoftmaxWarps + kExpandWarps + 3) * 32;
 constexpr uint32_t kTmaWarp = kSoftmaxWarps + kExpandWarps, kScoreWarp = kTmaWarp + 1, kValueWarp = kTmaWarp + 2;
 constexpr uint32_t kScaleStages = 4;
@@ -73,38 +72,40 @@ constexpr uint32_t kMaxRawStages = 4;
 //             tile does (paged_attention_tile.h:176-186): both operands of a contraction are of one kind.
 template <uint32_t Format> struct Traits;
 template <> struct Traits<RK_FORMAT_INT4> {
-  static constexpr uint32_t kSlab = 4096, kRawStages = 4;
+  static constexpr uint32_t kSlab = 4096, kRawStages = 4, kTileStages = 2;
   static constexpr bool kScales = true, kBf16 = false;
   static constexpr float kKeyOffset = 8.0f;
   static constexpr int kKeyShift = 24;
 };
 template <> struct Traits<RK_FORMAT_INT8> {
-  static constexpr uint32_t kSlab = 8192, kRawStages = 2;
+  static constexpr uint32_t kSlab = 8192, kRawStages = 2, kTileStages = 2;
   static constexpr bool kScales = true, kBf16 = false;
   static constexpr float kKeyOffset = 128.0f;
   static constexpr int kKeyShift = 24;
 };
 template <> struct Traits<RK_FORMAT_FP8E4M3> {
-  static constexpr uint32_t kSlab = 8192, kRawStages = 2;
+  static constexpr uint32_t kSlab = 8192, kRawStages = 2, kTileStages = 2;
   static constexpr bool kScales = true, kBf16 = false;
   static constexpr float kKeyOffset = 0.0f;
   static constexpr int kKeyShift = 0;
 };
 template <> struct Traits<RK_FORMAT_BF16> {
-  static constexpr uint32_t kSlab = 16384, kRawStages = 1;
+  static constexpr uint32_t kSlab = 16384, kRawStages = 2, kTileStages = 1; // the slabs are large: one operand stage, two raw stages
   static constexpr bool kScales = false, kBf16 = true;
   static constexpr float kKeyOffset = 0.0f;
   static constexpr int kKeyShift = 0;
 };
 // raw stage: K0 | K1 | V0 | V1 | ks0 ks1 vs0 vs1 (128 B each) | pad to 1 KiB
 template <uint32_t Format> __host__ __device__ constexpr uint32_t raw_stage_bytes() { return 4 * Traits<Format>::kSlab + 1024; }
-template <uint32_t Format> __host__ __device__ constexpr uint32_t tile_bytes() { return 2 * kKBytes + 2 * kVBytes + Traits<Format>::kRawStages * raw_stage_bytes<Format>(); }
+template <uint32_t Format> __host__ __device__ constexpr uint32_t tile_bytes() {
+  return Traits<Format>::kTileStages * (kKBytes + kVBytes) + Traits<Format>::kRawStages * raw_stage_bytes<Format>();
+}
 // tensor-memory columns
 constexpr uint32_t kTmemO = 0, kTmemS = 256, kTmemQ = 384; // S twice (64 columns each); P(g) overwrites the first half of S(g)
 
 struct Control {
   uint64_t raw_full[kMaxRawStages], raw_free[kMaxRawStages];
-  uint64_t k_full[2], k_free[2], v_full[2], v_free[2], s_full[2], p_full[2], scale_free[kScaleStages];
+  uint64_t k_full[2], k_free[2], v_full[2], v_free[2], s_full[2], p_full[2], p_free[2], scale_free[kScaleStages];
   uint32_t tmem_base;
   uint32_t error;
   float q_sums[kM];
@@ -264,7 +265,7 @@ struct VerifyArgs {
 };
 
 
-// ---- raw codes -> 16-bit operand tiles, one team of 128 threads (e = 0..127) per 64-token group -------------
+// ---- raw codes -> 16-bit operand tiles, one team of `Team` threads (e = 0..Team-1) per 64-token group ---------
 // K tile: four column blocks of [64 positions][64 dims], 128-byte rows, 128-byte swizzle. V^T tile: one block
 // of [256 dims][64 positions]. `raw` = K0 | K1 | V0 | V1 slabs as TMA left them (128-byte rows, swizzled).
 // `valid` = positions of the group whose tokens exist; formats whose stale bytes can decode to NaN or
@@ -279,14 +280,14 @@ __device__ __forceinline__ uint32_t mask_pair(uint32_t value, uint32_t position,
 template <> struct Expand<RK_FORMAT_INT4> {
   // position 8r+j holds token 8j+r: every access of both transposes is conflict-free
   __device__ static uint32_t token_of(uint32_t position) { return 8 * (position & 7u) + (position >> 3); }
-  __device__ static void keys(const uint8_t *raw, uint8_t *k_stage, uint32_t e) {
+  template <uint32_t Team> __device__ static void keys(const uint8_t *raw, uint8_t *k_stage, uint32_t e) {
     const uint32_t low_mask = register_constant(0x000F000Fu), high_mask = register_constant(0x00F000F0u);
     const uint32_t key_low = register_constant(0x00080008u), key_high = register_constant(0x00800080u);
     // a thread takes a raw 16-byte chunk (32 dims of one token) = four operand chunks. The eight lanes of an
     // access phase take tokens 8k + t and chunks c0 ^ k.
 #pragma unroll
-    for (uint32_t i = 0; i < 4; ++i) {
-      const uint32_t item = e + i * kExpandThreads;
+    for (uint32_t i = 0; i < 512 / Team; ++i) {
+      const uint32_t item = e + i * Team;
       const uint32_t k8 = item & 7u, c = ((item >> 3) & 7u) ^ k8, t = item >> 6;
       const uint32_t token = 8 * k8 + t, position = 8 * t + k8;
       const uint4 x = *reinterpret_cast<const uint4 *>(raw + (token >> 5) * 4096 + swizzled(token & 31u, c));
@@ -301,14 +302,14 @@ template <> struct Expand<RK_FORMAT_INT4> {
       }
     }
   }
-  __device__ static void values(const uint8_t *raw, uint8_t *v_stage, uint32_t e, uint32_t) {
+  template <uint32_t Team> __device__ static void values(const uint8_t *raw, uint8_t *v_stage, uint32_t e, uint32_t) {
     const uint32_t low_mask = register_constant(0x000F000Fu), high_mask = register_constant(0x00F000F0u);
     const uint32_t value_low = register_constant(0x64086408u), value_high = register_constant(0x64806480u);
     // thread = (r8, word w of 8 dims) takes tokens 8j + r8, j = 0..7, and transposes 8x8 in registers: each
     // dim gets a 16-byte run of eight tokens at contraction positions 8*r8 + j.
 #pragma unroll
-    for (uint32_t half = 0; half < 2; ++half) {
-      const uint32_t unit = e + half * kExpandThreads, r8 = unit & 7u, w = unit >> 3;
+    for (uint32_t half = 0; half < 256 / Team; ++half) {
+      const uint32_t unit = e + half * Team, r8 = unit & 7u, w = unit >> 3;
       uint32_t x[8];
 #pragma unroll
       for (uint32_t j = 0; j < 8; ++j)
@@ -354,11 +355,11 @@ template <bool kFloat8> struct ExpandBytes {
       second = sub_f16x2(__byte_perm(flipped, 0x64646464u, 0x4342), 0x64806480u);
     }
   }
-  __device__ static void keys(const uint8_t *raw, uint8_t *k_stage, uint32_t e) {
+  template <uint32_t Team> __device__ static void keys(const uint8_t *raw, uint8_t *k_stage, uint32_t e) {
     // item = (token, 16-byte chunk c of its 256-byte row): 16 dims -> two operand chunks
 #pragma unroll
-    for (uint32_t i = 0; i < 8; ++i) {
-      const uint32_t item = e + i * kExpandThreads, c = item & 15u, token = item >> 4;
+    for (uint32_t i = 0; i < 1024 / Team; ++i) {
+      const uint32_t item = e + i * Team, c = item & 15u, token = item >> 4;
       const uint32_t row = 2 * (token & 31u) + (c >> 3);
       const uint4 x = *reinterpret_cast<const uint4 *>(raw + (token >> 5) * 8192 + swizzled(row, c & 7u));
       uint32_t out[8];
@@ -369,11 +370,11 @@ template <bool kFloat8> struct ExpandBytes {
       *reinterpret_cast<uint4 *>(block + swizzled(token, 2 * (c & 3u) + 1)) = make_uint4(out[4], out[5], out[6], out[7]);
     }
   }
-  __device__ static void values(const uint8_t *raw, uint8_t *v_stage, uint32_t e, uint32_t valid) {
+  template <uint32_t Team> __device__ static void values(const uint8_t *raw, uint8_t *v_stage, uint32_t e, uint32_t valid) {
     // item = (page, dim, half h of its 32 tokens): 16 tokens -> two operand chunks of the dim's row
 #pragma unroll
-    for (uint32_t i = 0; i < 8; ++i) {
-      const uint32_t item = e + i * kExpandThreads, h = item & 1u, dim = (item >> 1) & 255u, page = item >> 9;
+    for (uint32_t i = 0; i < 1024 / Team; ++i) {
+      const uint32_t item = e + i * Team, h = item & 1u, dim = (item >> 1) & 255u, page = item >> 9;
       const uint4 x = *reinterpret_cast<const uint4 *>(raw + (2 + page) * 8192 + swizzled(dim >> 2, 2 * (dim & 3u) + h));
       uint32_t out[8];
       value_pairs(x.x, out[0], out[1]); value_pairs(x.y, out[2], out[3]);
@@ -395,19 +396,19 @@ template <> struct Expand<RK_FORMAT_FP8E4M3> : ExpandBytes<true> {};
 // rows (= the four column blocks); V rows (one dim) are 64 bytes, two dims to a TMA row.
 template <> struct Expand<RK_FORMAT_BF16> {
   __device__ static uint32_t token_of(uint32_t position) { return position; }
-  __device__ static void keys(const uint8_t *raw, uint8_t *k_stage, uint32_t e) {
+  template <uint32_t Team> __device__ static void keys(const uint8_t *raw, uint8_t *k_stage, uint32_t e) {
 #pragma unroll
-    for (uint32_t i = 0; i < 16; ++i) {
-      const uint32_t item = e + i * kExpandThreads, c = item & 31u, token = item >> 5;
+    for (uint32_t i = 0; i < 2048 / Team; ++i) {
+      const uint32_t item = e + i * Team, c = item & 31u, token = item >> 5;
       const uint32_t row = 4 * (token & 31u) + (c >> 3);
       const uint4 x = *reinterpret_cast<const uint4 *>(raw + (token >> 5) * 16384 + swizzled(row, c & 7u));
       *reinterpret_cast<uint4 *>(k_stage + (c >> 3) * (kGroupTokens * 128) + swizzled(token, c & 7u)) = x;
     }
   }
-  __device__ static void values(const uint8_t *raw, uint8_t *v_stage, uint32_t e, uint32_t valid) {
+  template <uint32_t Team> __device__ static void values(const uint8_t *raw, uint8_t *v_stage, uint32_t e, uint32_t valid) {
 #pragma unroll
-    for (uint32_t i = 0; i < 16; ++i) {
-      const uint32_t item = e + i * kExpandThreads, q = item & 3u, dim = (item >> 2) & 255u, page = item >> 10;
+    for (uint32_t i = 0; i < 2048 / Team; ++i) {
+      const uint32_t item = e + i * Team, q = item & 3u, dim = (item >> 2) & 255u, page = item >> 10;
       uint4 x = *reinterpret_cast<const uint4 *>(raw + (2 + page) * 16384 + swizzled(dim >> 1, 4 * (dim & 1u) + q));
       const uint32_t position = 32 * page + 8 * q;
       if (position + 8 > valid) {
@@ -428,17 +429,16 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
   constexpr uint32_t kActiveSoftmax = kQuarters * kRowThreads * 32; // softmax threads that take part
   constexpr uint32_t kSlab = Kind::kSlab, kRawStages = Kind::kRawStages, kRawStageBytes = raw_stage_bytes<Format>();
   constexpr uint32_t kRawScaleOffset = 4 * kSlab;
-  // Barriers of the raw ring: one pair per stage, but never fewer than two, so that the two expander teams,
-  // which alternate groups, never wait on the same barrier (a waiter two completions behind would misread parity).
-  constexpr uint32_t kRawBarriers = kRawStages < 2 ? 2 : kRawStages;
+  constexpr uint32_t kTileStages = Kind::kTileStages, kExpandThreads = kExpandWarps * 32 / kTileStages; // threads of one team
+  static_assert(kRawStages % kTileStages == 0, "a raw stage belongs to one expander team: its barrier is never waited on two completions behind");
   extern __shared__ uint8_t dynamic_shared[];
   const uint32_t tiles = (smem_u32(dynamic_shared) + 1023u) & ~1023u;
   uint8_t *tile_ptr = dynamic_shared + (tiles - smem_u32(dynamic_shared));
   Control &ctl = *reinterpret_cast<Control *>(tile_ptr + tile_bytes<Format>());
   volatile uint32_t *error = &ctl.error;
-  const uint32_t k_tile = tiles, v_tile = k_tile + 2 * kKBytes, raw_tile = v_tile + 2 * kVBytes; // K[2] | V[2] | raw ring
-  uint8_t *k_ptr = tile_ptr, *v_ptr = k_ptr + 2 * kKBytes;
-  const uint8_t *raw_ptr = v_ptr + 2 * kVBytes;
+  const uint32_t k_tile = tiles, v_tile = k_tile + kTileStages * kKBytes, raw_tile = v_tile + kTileStages * kVBytes; // K stages | V stages | raw ring
+  uint8_t *k_ptr = tile_ptr, *v_ptr = k_ptr + kTileStages * kKBytes;
+  const uint8_t *raw_ptr = v_ptr + kTileStages * kVBytes;
 
   const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const uint32_t kv_head = blockIdx.x, split = blockIdx.y, lane_index = blockIdx.z;
@@ -457,7 +457,7 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
 
   // ---- setup: barriers, TMEM, query tile ----------------------------------------------------------
   if (tid == 0) {
-    for (uint32_t r = 0; r < kRawBarriers; ++r) {
+    for (uint32_t r = 0; r < kRawStages; ++r) {
       barrier_init(smem_u32(&ctl.raw_full[r]), 1);
       barrier_init(smem_u32(&ctl.raw_free[r]), kExpandThreads);
     }
@@ -467,6 +467,7 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
       barrier_init(smem_u32(&ctl.k_free[b]), 1);
       barrier_init(smem_u32(&ctl.v_free[b]), 1);
       barrier_init(smem_u32(&ctl.s_full[b]), 1);
+      barrier_init(smem_u32(&ctl.p_free[b]), 1);
       barrier_init(smem_u32(&ctl.p_full[b]), kActiveSoftmax);
     }
     for (uint32_t b = 0; b < kScaleStages; ++b) barrier_init(smem_u32(&ctl.scale_free[b]), kActiveSoftmax);
@@ -544,14 +545,14 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
     if (lane == 0) {
       rk_page_entry next[2] = {table[page_begin], page_begin + 1 < page_end ? table[page_begin + 1] : 0};
       for (uint32_t g = 0; g < groups; ++g) {
-        const uint32_t r = g % kRawStages, slot = g % kRawBarriers;
+        const uint32_t r = g % kRawStages, slot = g % kRawStages;
         const uint32_t first = page_begin + 2 * g, group_pages = min(2u, page_end - first);
         const rk_page_entry entries[2] = {next[0], next[1]};
         if (g + 1 < groups) { // the next group's entries travel while this group is issued
           next[0] = table[first + 2];
           next[1] = first + 3 < page_end ? table[first + 3] : 0;
         }
-        if (g >= kRawStages) barrier_wait(&ctl.raw_free[(g - kRawStages) % kRawBarriers], (g - kRawStages) / kRawBarriers, error); // the stage's last reader
+        if (g >= kRawStages) barrier_wait(&ctl.raw_free[(g - kRawStages) % kRawStages], (g - kRawStages) / kRawStages, error); // the stage's last reader
         const uint32_t full = smem_u32(&ctl.raw_full[slot]), stage = raw_tile + r * kRawStageBytes;
         barrier_expect(full, group_pages * (2 * kSlab + (Kind::kScales ? 256 : 0)));
 #pragma unroll
@@ -574,29 +575,29 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
       }
       // Every copy this thread started has landed before the CTA may leave (also after a failed wait).
       for (uint32_t g = groups > kRawStages ? groups - kRawStages : 0; g < groups; ++g) {
-        const uint32_t bar = smem_u32(&ctl.raw_full[g % kRawBarriers]), parity = (g / kRawBarriers) & 1u;
+        const uint32_t bar = smem_u32(&ctl.raw_full[g % kRawStages]), parity = (g / kRawStages) & 1u;
         for (uint32_t i = 0; i < kSpinLimit && !barrier_try(bar, parity); ++i) __nanosleep(64);
       }
     }
   } else if (warp == kScoreWarp) {
-    // ---- tensor-core issue, S = Q.K^T: S buffer g&1 is free once PV(g-2), which read P(g-2) from it, has landed ----
+    // ---- tensor-core issue, S = Q.K^T: S buffer g&1 is free once PV(g-2), which read P(g-2) from it, has landed (p_free) ----
     // The whole warp walks the loop (uniform control flow); one elected lane issues.
     const uint32_t idesc_qk = umma_instruction(kM, kGroupTokens, Kind::kBf16, Kind::kBf16);
     // a descriptor advances by (bytes >> 4) in its low word; nothing here carries out of the 14-bit field
     const uint64_t k_desc0 = umma_descriptor(k_tile), k_desc1 = umma_descriptor(k_tile + kKBytes);
     for (uint32_t g = 0; g < groups; ++g) {
-      const uint32_t b = g & 1u;
-      barrier_wait(&ctl.k_full[b], g >> 1, error);
-      if (g >= 2) barrier_wait(&ctl.v_free[b], (g >> 1) - 1, error);
+      const uint32_t b = g & 1u, t = g % kTileStages; // S buffer, operand stage
+      barrier_wait(&ctl.k_full[t], g / kTileStages, error);
+      if (g >= 2) barrier_wait(&ctl.p_free[b], (g >> 1) - 1, error);
       tmem_fence_after();
-      const uint64_t desc = b ? k_desc1 : k_desc0;
+      const uint64_t desc = t ? k_desc1 : k_desc0;
       const uint32_t target = tmem_s + b * 64;
       if (elect_one()) {
 #pragma unroll
         for (uint32_t j = 0; j < 16; ++j)
           umma_f16_ts(target, tmem_q + 8 * j, desc + (((j >> 2) * (kGroupTokens * 128) + (j & 3u) * 32) >> 4), idesc_qk, j ? 1u : 0u);
         umma_commit(&ctl.s_full[b]);
-        umma_commit(&ctl.k_free[b]);
+        umma_commit(&ctl.k_free[t]);
       }
       __syncwarp();
     }
@@ -605,29 +606,30 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
     const uint32_t idesc_pv = umma_instruction(kM, kD, Kind::kBf16, Kind::kBf16); // both operands of one kind: bf16 values take bf16 probabilities
     const uint64_t v_desc0 = umma_descriptor(v_tile), v_desc1 = umma_descriptor(v_tile + kVBytes);
     for (uint32_t g = 0; g < groups; ++g) {
-      const uint32_t b = g & 1u;
-      barrier_wait(&ctl.v_full[b], g >> 1, error);
+      const uint32_t b = g & 1u, t = g % kTileStages;
+      barrier_wait(&ctl.v_full[t], g / kTileStages, error);
       barrier_wait(&ctl.p_full[b], g >> 1, error);
       tmem_fence_after();
-      const uint64_t desc = b ? v_desc1 : v_desc0;
+      const uint64_t desc = t ? v_desc1 : v_desc0;
       const uint32_t source = tmem_s + b * 64;
       if (elect_one()) {
 #pragma unroll
         for (uint32_t j = 0; j < 4; ++j) umma_f16_ts(tmem_o, source + 8 * j, desc + ((j * 32) >> 4), idesc_pv, (g || j) ? 1u : 0u);
-        umma_commit(&ctl.v_free[b]);
+        umma_commit(&ctl.v_free[t]);
+        umma_commit(&ctl.p_free[b]);
       }
       __syncwarp();
     }
   } else if (warp >= kSoftmaxWarps) {
     // ---- expanders: raw codes -> 16-bit operand tiles --------------------------------------------------------------
-    const uint32_t team = (warp - kSoftmaxWarps) >> 2, e = tid - kSoftmaxThreads - team * kExpandThreads;
-    for (uint32_t g = team; g < groups; g += 2) {
-      const uint32_t r = g % kRawStages, slot = g % kRawBarriers, b = team;
+    const uint32_t team = (tid - kSoftmaxThreads) / kExpandThreads, e = tid - kSoftmaxThreads - team * kExpandThreads;
+    for (uint32_t g = team; g < groups; g += kTileStages) {
+      const uint32_t r = g % kRawStages, slot = r, b = team, round = g / kTileStages;
       const uint32_t first = page_begin + 2 * g;
       // positions of the group whose tokens exist: the split may end inside the group, the lane inside the page
       const uint32_t valid = min(min(2u, page_end - first) * kPageTokens, visible - first * kPageTokens);
       const uint8_t *raw = raw_ptr + r * kRawStageBytes;
-      barrier_wait(&ctl.raw_full[slot], g / kRawBarriers, error);
+      barrier_wait(&ctl.raw_full[slot], g / kRawStages, error);
       // per-position scale triples {key scale, log2 value scale, 2^-6 / value scale}; zeros past the valid tokens
       // (stale scale bytes never reach the arithmetic)
       if (e < kGroupTokens) {
@@ -645,12 +647,12 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
         }
         ctl.scales[g % kScaleStages][e] = triple;
       }
-      if (g >= 2) barrier_wait(&ctl.k_free[b], (g >> 1) - 1, error);
-      Expand<Format>::keys(raw, k_ptr + b * kKBytes, e);
+      if (round) barrier_wait(&ctl.k_free[b], round - 1, error);
+      Expand<Format>::template keys<kExpandThreads>(raw, k_ptr + b * kKBytes, e);
       async_proxy_fence();
       barrier_arrive(smem_u32(&ctl.k_full[b]));
-      if (g >= 2) barrier_wait(&ctl.v_free[b], (g >> 1) - 1, error);
-      Expand<Format>::values(raw, v_ptr + b * kVBytes, e, valid);
+      if (round) barrier_wait(&ctl.v_free[b], round - 1, error);
+      Expand<Format>::template values<kExpandThreads>(raw, v_ptr + b * kVBytes, e, valid);
       async_proxy_fence();
       barrier_arrive(smem_u32(&ctl.v_full[b]));
       barrier_arrive(smem_u32(&ctl.raw_free[slot]));
@@ -739,7 +741,7 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
         packed[c] = Kind::kBf16 ? pack_bfloat2(w[0], w[1]) : pack_half2(w[0], w[1]);
       }
       if (g && __any_sync(0xffffffffu, grow)) { // this part rescales its columns of O once P.V(g-1) has landed
-        barrier_wait(&ctl.v_free[b ^ 1u], (g - 1) >> 1, error);
+        barrier_wait(&ctl.v_free[(g - 1) % kTileStages], (g - 1) / kTileStages, error);
         tmem_fence_after();
 #pragma unroll 1
         for (uint32_t c = 0; c < kOutColumns / 32; ++c) {
@@ -757,7 +759,7 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
     }
 
     // ---- partial output: row i of O, un-normalised; statistics {reference exponent, sum} -------------------
-    barrier_wait(&ctl.v_free[(groups - 1) & 1u], (groups - 1) >> 1, error);
+    barrier_wait(&ctl.v_free[(groups - 1) % kTileStages], (groups - 1) / kTileStages, error);
     tmem_fence_after();
     const bool failed = *error != 0;
     const uint64_t slot = (uint64_t(lane_index) * kHeads + kv_head) * p.slot_splits + split;
