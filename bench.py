@@ -53,6 +53,8 @@ def parse():
     ap.add_argument("--layers", type=int, default=16)
     ap.add_argument("--ragged", action="store_true", help="contexts uniform in [context/4, context]")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--format", default="int4", choices=["int4", "int8", "fp8e4m3", "bf16"],
+                    help="stored KV format of the decode workload (the headline is int4)")
     ap.add_argument("--rows", type=int, default=16, choices=[8, 16], help="--mode verify: window rows per sequence")
     ap.add_argument("--mode", default="requests", choices=["requests", "seqsplit", "verify"],
                     help="requests: every rank runs its own batch (default); seqsplit: ONE sequence of --context "
@@ -69,7 +71,7 @@ def contexts_for(args, rank: int) -> list[int]:
 
 def workload_name(args) -> str:
     shape = f"ctx U[{args.context // 4},{args.context}]" if args.ragged else f"ctx {args.context}"
-    return (f"int4 KV, 27B geometry ({args.layers} layers x {KV_HEADS} KV heads x {HEAD_DIM}, {QUERY_HEADS} query heads), "
+    return (f"{args.format} KV, 27B geometry ({args.layers} layers x {KV_HEADS} KV heads x {HEAD_DIM}, {QUERY_HEADS} query heads), "
             f"batch {args.batch}, {shape}, random page tables; per layer: append 1 token + 1-query decode attention")
 
 
@@ -227,10 +229,11 @@ def run_ours(args):
     import torch.distributed as dist
 
     from richengine_b200 import lib, ops
-    from richengine_b200.abi import INT4, Layout, pages_for
+    from richengine_b200.abi import BF16, FP8E4M3, INT4, INT8, Layout, pages_for
     from richengine_b200.session import DecodeSession
     from richengine_b200.storage import PageStorage
 
+    fmt = {"int4": INT4, "int8": INT8, "fp8e4m3": FP8E4M3, "bf16": BF16}[args.format]
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -239,7 +242,7 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     lib.load()
 
-    layout = Layout(args.layers, KV_HEADS, HEAD_DIM, INT4)
+    layout = Layout(args.layers, KV_HEADS, HEAD_DIM, fmt)
     contexts = contexts_for(args, rank)
     lanes = len(contexts)
     steps_total = args.warmup + args.steps
@@ -404,16 +407,18 @@ def run_ours(args):
         achieved = layer_bytes / (kernel_ms * 1e-3) / 1e9
         value = timed_bytes / (elapsed_ms * 1e-3) / 1e9
         line = {
-            "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "metric": METRIC if fmt == INT4 else METRIC.replace("int4", args.format), "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(elapsed_ms / args.steps, 4), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "int4 codes, fp16 tensor operands, fp32 accumulate",
+            "scaling": "weak", "vs_baseline": None,
+            "dtype": f"{args.format} codes, {'bf16' if fmt == BF16 else 'fp16'} tensor operands, fp32 accumulate",
             "data": "synthetic",
             "config": {"workload": workload_name(args), "l2": "inputs larger than L2 (KV per step >> 126 MB)",
                        "us_per_layer_step": round(elapsed_ms / args.steps / args.layers * 1e3, 2),
                        "kv_gb_per_step": round(timed_bytes / args.steps / world / 1e9, 3), "sharding": "by request"},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                         "frac": round(achieved / peak, 4), "traffic": DRAM_BYTES_PER_ALGORITHMIC_BYTE and round(DRAM_BYTES_PER_ALGORITHMIC_BYTE * layer_bytes), "peak_source": peak_source,
-                         "kernel": "decode_int4_kernel (+ its merge)", "us_per_launch": round(kernel_ms * 1e3, 2),
+                         "frac": round(achieved / peak, 4),
+                         "traffic": round(DRAM_BYTES_PER_ALGORITHMIC_BYTE * layer_bytes) if fmt == INT4 else None, "peak_source": peak_source,
+                         "kernel": "decode_int4_kernel (+ its merge)" if fmt == INT4 else "window_attention_kernel, one row (+ its merge)", "us_per_launch": round(kernel_ms * 1e3, 2),
                          "algorithmic_bytes_per_launch": layer_bytes},
             "e2e": {"value": round(e2e_bytes / (e2e_time_ms * 1e-3) / 1e9, 1), "unit": "GB/s",
                     "h2d_bytes_per_step": h2d * args.layers, "d2h_bytes_per_step": d2h * args.layers,
@@ -422,7 +427,7 @@ def run_ours(args):
             "clocks": clocks,
         }
         try:
-            line["cpu_baseline"] = cpu_baseline(args, args.cpu_seconds) if world == 1 and args.cpu_seconds > 0 else None
+            line["cpu_baseline"] = cpu_baseline(args, args.cpu_seconds) if world == 1 and args.cpu_seconds > 0 and fmt == INT4 else None
         except Exception as error:  # the CPU leg never hides the GPU numbers
             line["cpu_baseline"] = {"error": str(error)}
         print(json.dumps(line), flush=True)

@@ -98,6 +98,32 @@ class VerifyWindowAttention:
             raise lib.RichKvError(lib.TIMEOUT, "rk_attention_verify_split_tc: a bounded wait ran out")
 
 
+class WindowDecodeAttention:
+    """One-query decode on the tcgen05 window kernel (row capacity 1) + the split merge: the decode path of the
+    int8, fp8 and bf16 pools (int4 has the streaming kernel, DecodeAttention). Same call shape as DecodeAttention;
+    the lanes' parameters carry split_count = slot_splits = `splits`."""
+
+    def __init__(self, layout: Layout, query_heads: int, lanes: int, window: tuple[int, int], splits: int = 1):
+        self.layout, self.query_heads, self.lanes, self.splits = layout, query_heads, lanes, splits
+        self.inner = VerifyWindowAttention(layout, query_heads, window)
+        group = query_heads // layout.kv_heads
+        slots = lanes * layout.kv_heads * splits * group
+        self.partials = torch.empty(slots * layout.head_dimension, dtype=torch.float32, device="cuda")
+        self.statistics = torch.empty(slots * 2, dtype=torch.float32, device="cuda")
+
+    def close(self) -> None:
+        self.inner.close()
+
+    def run(self, queries, output, table_pointers, params, layer: lib.KvLayer, output_f32=None, stream=None) -> None:
+        self.inner.split(self.lanes, 1, self.splits, queries, self.partials, self.statistics, table_pointers, None, params,
+                         layer, stream)
+        attention_verify_reduce(self.layout, self.query_heads, self.lanes, 1, self.partials, self.statistics, output,
+                                params, output_f32, stream)
+
+    def status(self) -> None:
+        self.inner.check()
+
+
 def attention_verify_reduce(layout: Layout, query_heads: int, lanes: int, row_capacity: int, partials, statistics,
                             output, params, output_f32=None, stream=None) -> None:
     status = lib.load().rk_attention_verify_reduce(

@@ -16,7 +16,7 @@ import ctypes as C
 import torch
 
 from . import lib, ops
-from .abi import VERIFY_CHUNK_STRIDE, Layout
+from .abi import INT4, VERIFY_CHUNK_STRIDE, Layout
 from .storage import PageStorage
 
 
@@ -36,7 +36,11 @@ class DecodeSession:
         self.k_rows = torch.zeros((lanes, H, D), dtype=torch.bfloat16, device=device)
         self.v_rows = torch.zeros((lanes, H, D), dtype=torch.bfloat16, device=device)
         self.out_rows = torch.zeros((lanes, query_heads, D), dtype=torch.bfloat16, device=device)
-        self.attention = ops.DecodeAttention(layout, query_heads, lanes, storage.window(), ctas)
+        # int4 pools decode on the streaming kernel; the other formats on the tcgen05 window kernel with one row
+        if layout.format == INT4:
+            self.attention = ops.DecodeAttention(layout, query_heads, lanes, storage.window(), ctas)
+        else:
+            self.attention = ops.WindowDecodeAttention(layout, query_heads, lanes, storage.window())
         self.layers = storage.layers()
         self.kernel_launches = 0
 
