@@ -324,9 +324,6 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
   if (warp == kConsumerWarps) {
     // ================= producer: one thread streams whole pages =============================
     if (lane != 0) return;
-#ifdef RK_EXP_COMPUTE_ONLY
-    return;
-#endif
     uint32_t unit = 0; // pages issued by this CTA
     bool ok = true;
     for (uint32_t l = first_lane; ok && l < lanes && sh.lane_start[l] < range_end; ++l) {
@@ -455,21 +452,16 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
     for (uint32_t page = pa + residue; page < pb && !sh.error; page += kPageWarps) {
       const uint32_t unit = units_before + (page - pa);
       const uint32_t slot = unit % kStages, round = unit / kStages;
-#ifndef RK_EXP_COMPUTE_ONLY
       if (!barrier_wait(smem_address(&sh.full[slot]), round & 1u)) {
         atomicExch(error_word, 2u);
         sh.error = 2;
         break;
       }
       const uint32_t stage = ring + slot * kStageBytes;
-#else
-      const uint32_t stage = ring + (warp % kStages) * kStageBytes;
-#endif
       const uint32_t keys = stage + head * kSlabBytes;
       const uint32_t values = stage + kTensorBytes + head * kSlabBytes;
       const uint32_t scales = stage + 2 * kTensorBytes + head * (kPageTokens * 4);
       const uint32_t valid = page + 1 == lane_pages ? visible - page * kPageTokens : kPageTokens;
-#ifndef RK_EXP_STREAM_ONLY
 
       // ---- S^T = K.Q^T : two 16-token tiles, 16 k-steps each --------------------------
       float sacc[2][2][4];
@@ -536,7 +528,6 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
                     sub_f16x2(and_xor(cd, kHighNibbles, kMagicHigh), kMagicHigh), pb_frag[s][0], pb_frag[s][1]);
           }
       }
-#endif
       __syncwarp();
       if (lane == 0) barrier_arrive(smem_address(&sh.empty[slot]));
     }

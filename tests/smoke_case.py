@@ -1,5 +1,6 @@
-"""The smoke scenario: append one token per lane, then paged decode attention, on the GPU,
-compared with the CPU checker (codes bit-exact, attention within the parity bar)."""
+"""The smoke scenario: append one token per lane, then paged decode attention (general tile, streaming decode
+kernel, tcgen05 window kernel), on the GPU, compared with the CPU checker (codes bit-exact, attention within the
+parity bar)."""
 import numpy as np
 import torch
 
@@ -26,11 +27,10 @@ def run(layout):
     got16, got32, _ = run_verify_attention_gpu(s, q, 1, 1, layer_index=1)
     _, want32 = run_verify_attention_oracle(s, q, 1, 1, layer_index=1)
     assert_attention_close(got32, want32, got16, "smoke decode")
-    try:
-        from gpuhelp import run_decode_attention_gpu
-    except ImportError:
-        run_decode_attention_gpu = None
-    if run_decode_attention_gpu is not None:
-        d16, d32 = run_decode_attention_gpu(s, q, layer_index=1)
-        assert_attention_close(d32, want32, d16, "smoke decode (streaming kernel)")
+    from gpuhelp import run_decode_attention_gpu
+    d16, d32 = run_decode_attention_gpu(s, q, layer_index=1)
+    assert_attention_close(d32, want32, d16, "smoke decode (streaming kernel)")
+    # an 8-row verify window on the tcgen05 kernel over the same pages (7 of its rows read zero staging rows)
+    w16, w32, _ = run_verify_attention_gpu(s, q, 1, 8, layer_index=1, tensor_core=True)
+    assert_attention_close(w32, want32, w16, "smoke window (tcgen05 kernel)")
     s.close()
