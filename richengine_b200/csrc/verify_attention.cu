@@ -146,6 +146,11 @@ __device__ __forceinline__ void tma_load_rows(uint32_t dst, const CUtensorMap *m
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                ::"r"(dst), "l"(map), "r"(0), "r"(row), "r"(bar) : "memory");
 }
+// Asks L2 for `bytes` of global memory (16-byte granular) without a destination: the later copy of the same
+// bytes into shared memory then pays the L2 latency, not the HBM one.
+__device__ __forceinline__ void prefetch_l2(uint64_t address, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(address), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
@@ -429,6 +434,10 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
   constexpr uint32_t kActiveSoftmax = kQuarters * kRowThreads * 32; // softmax threads that take part
   constexpr uint32_t kSlab = Kind::kSlab, kRawStages = Kind::kRawStages, kRawStageBytes = raw_stage_bytes<Format>();
   constexpr uint32_t kRawScaleOffset = 4 * kSlab;
+  // int8 and fp8 keep only two raw stages (66 KB) in flight per SM, short of what HBM latency asks for: they also
+  // request the groups behind the ring from HBM into L2. The other formats measured slower with it.
+  constexpr bool kPrefetch = Kind::kSlab == 8192;
+  constexpr uint32_t kPrefetchGroups = kRawStages + 4; // groups between the shared-memory copy and the L2 request
   constexpr uint32_t kTileStages = Kind::kTileStages, kExpandThreads = kExpandWarps * 32 / kTileStages; // threads of one team
   static_assert(kRawStages % kTileStages == 0, "a raw stage belongs to one expander team: its barrier is never waited on two completions behind");
   extern __shared__ uint8_t dynamic_shared[];
@@ -570,6 +579,23 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
           if (Kind::kScales) {
             bulk_load(stage + kRawScaleOffset + local * 128, reinterpret_cast<const void *>(key_scales), 128, full);
             bulk_load(stage + kRawScaleOffset + (2 + local) * 128, reinterpret_cast<const void *>(value_scales), 128, full);
+          }
+        }
+        // The raw ring holds at most kRawStages groups; the groups behind it are already requested from HBM
+        // into L2, kPrefetchGroups ahead, so the ring is refilled at L2 latency.
+        const uint32_t ahead = first + 2 * kPrefetchGroups;
+#pragma unroll
+        for (uint32_t local = 0; local < 2; ++local) {
+          if (!kPrefetch || ahead + local >= page_end) break;
+          const rk_page_entry entry = table[ahead + local];
+          const uint32_t index = rk_entry_index(entry);
+          const uint64_t region = rk_entry_extent(entry) + args.layer.offset;
+          const uint64_t extent_pages = args.layer.extent_pages;
+          prefetch_l2(region + uint64_t(index) * data_bytes + kv_head * kSlab, kSlab);
+          prefetch_l2(region + extent_pages * (uint64_t(data_bytes) + scale_bytes) + uint64_t(index) * data_bytes + kv_head * kSlab, kSlab);
+          if (Kind::kScales) {
+            prefetch_l2(region + extent_pages * data_bytes + uint64_t(index) * scale_bytes + kv_head * 128u, 128);
+            prefetch_l2(region + extent_pages * (2ull * data_bytes + scale_bytes) + uint64_t(index) * scale_bytes + kv_head * 128u, 128);
           }
         }
       }
