@@ -291,8 +291,9 @@ template <> struct Expand<RK_FORMAT_INT4> {
     // a thread takes a raw 16-byte chunk (32 dims of one token) = four operand chunks. The eight lanes of an
     // access phase take tokens 8k + t and chunks c0 ^ k.
 #pragma unroll
-    for (uint32_t i = 0; i < 512 / Team; ++i) {
+    for (uint32_t i = 0; i < (512 + Team - 1) / Team; ++i) {
       const uint32_t item = e + i * Team;
+      if (512 % Team && item >= 512) break;
       const uint32_t k8 = item & 7u, c = ((item >> 3) & 7u) ^ k8, t = item >> 6;
       const uint32_t token = 8 * k8 + t, position = 8 * t + k8;
       const uint4 x = *reinterpret_cast<const uint4 *>(raw + (token >> 5) * 4096 + swizzled(token & 31u, c));
@@ -313,8 +314,9 @@ template <> struct Expand<RK_FORMAT_INT4> {
     // thread = (r8, word w of 8 dims) takes tokens 8j + r8, j = 0..7, and transposes 8x8 in registers: each
     // dim gets a 16-byte run of eight tokens at contraction positions 8*r8 + j.
 #pragma unroll
-    for (uint32_t half = 0; half < 256 / Team; ++half) {
+    for (uint32_t half = 0; half < (256 + Team - 1) / Team; ++half) {
       const uint32_t unit = e + half * Team, r8 = unit & 7u, w = unit >> 3;
+      if ((256 % Team || Team > 256) && unit >= 256) break;
       uint32_t x[8];
 #pragma unroll
       for (uint32_t j = 0; j < 8; ++j)
@@ -363,8 +365,9 @@ template <bool kFloat8> struct ExpandBytes {
   template <uint32_t Team> __device__ static void keys(const uint8_t *raw, uint8_t *k_stage, uint32_t e) {
     // item = (token, 16-byte chunk c of its 256-byte row): 16 dims -> two operand chunks
 #pragma unroll
-    for (uint32_t i = 0; i < 1024 / Team; ++i) {
+    for (uint32_t i = 0; i < (1024 + Team - 1) / Team; ++i) {
       const uint32_t item = e + i * Team, c = item & 15u, token = item >> 4;
+      if (1024 % Team && item >= 1024) break;
       const uint32_t row = 2 * (token & 31u) + (c >> 3);
       const uint4 x = *reinterpret_cast<const uint4 *>(raw + (token >> 5) * 8192 + swizzled(row, c & 7u));
       uint32_t out[8];
@@ -378,8 +381,9 @@ template <bool kFloat8> struct ExpandBytes {
   template <uint32_t Team> __device__ static void values(const uint8_t *raw, uint8_t *v_stage, uint32_t e, uint32_t valid) {
     // item = (page, dim, half h of its 32 tokens): 16 tokens -> two operand chunks of the dim's row
 #pragma unroll
-    for (uint32_t i = 0; i < 1024 / Team; ++i) {
+    for (uint32_t i = 0; i < (1024 + Team - 1) / Team; ++i) {
       const uint32_t item = e + i * Team, h = item & 1u, dim = (item >> 1) & 255u, page = item >> 9;
+      if (1024 % Team && item >= 1024) break;
       const uint4 x = *reinterpret_cast<const uint4 *>(raw + (2 + page) * 8192 + swizzled(dim >> 2, 2 * (dim & 3u) + h));
       uint32_t out[8];
       value_pairs(x.x, out[0], out[1]); value_pairs(x.y, out[2], out[3]);
@@ -403,8 +407,9 @@ template <> struct Expand<RK_FORMAT_BF16> {
   __device__ static uint32_t token_of(uint32_t position) { return position; }
   template <uint32_t Team> __device__ static void keys(const uint8_t *raw, uint8_t *k_stage, uint32_t e) {
 #pragma unroll
-    for (uint32_t i = 0; i < 2048 / Team; ++i) {
+    for (uint32_t i = 0; i < (2048 + Team - 1) / Team; ++i) {
       const uint32_t item = e + i * Team, c = item & 31u, token = item >> 5;
+      if (2048 % Team && item >= 2048) break;
       const uint32_t row = 4 * (token & 31u) + (c >> 3);
       const uint4 x = *reinterpret_cast<const uint4 *>(raw + (token >> 5) * 16384 + swizzled(row, c & 7u));
       *reinterpret_cast<uint4 *>(k_stage + (c >> 3) * (kGroupTokens * 128) + swizzled(token, c & 7u)) = x;
@@ -412,8 +417,9 @@ template <> struct Expand<RK_FORMAT_BF16> {
   }
   template <uint32_t Team> __device__ static void values(const uint8_t *raw, uint8_t *v_stage, uint32_t e, uint32_t valid) {
 #pragma unroll
-    for (uint32_t i = 0; i < 2048 / Team; ++i) {
+    for (uint32_t i = 0; i < (2048 + Team - 1) / Team; ++i) {
       const uint32_t item = e + i * Team, q = item & 3u, dim = (item >> 2) & 255u, page = item >> 10;
+      if (2048 % Team && item >= 2048) break;
       uint4 x = *reinterpret_cast<const uint4 *>(raw + (2 + page) * 16384 + swizzled(dim >> 1, 4 * (dim & 1u) + q));
       const uint32_t position = 32 * page + 8 * q;
       if (position + 8 > valid) {
@@ -438,7 +444,9 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
   // request the groups behind the ring from HBM into L2. The other formats measured slower with it.
   constexpr bool kPrefetch = Kind::kSlab == 8192;
   constexpr uint32_t kPrefetchGroups = kRawStages + 4; // groups between the shared-memory copy and the L2 request
-  constexpr uint32_t kTileStages = Kind::kTileStages, kExpandThreads = kExpandWarps * 32 / kTileStages; // threads of one team
+  // Softmax warps of quarters without a real row (12 of 16 for one row, 8 for eight rows, 4 for sixteen) expand too.
+  constexpr uint32_t kIdleWarps = (4 - kQuarters) * kRowThreads;
+  constexpr uint32_t kTileStages = Kind::kTileStages, kExpandThreads = (kExpandWarps + kIdleWarps) * 32 / kTileStages; // threads of one team
   static_assert(kRawStages % kTileStages == 0, "a raw stage belongs to one expander team: its barrier is never waited on two completions behind");
   extern __shared__ uint8_t dynamic_shared[];
   const uint32_t tiles = (smem_u32(dynamic_shared) + 1023u) & ~1023u;
@@ -550,61 +558,53 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
   __syncthreads();
 
   if (warp == kTmaWarp) {
-    // ---- TMA producer ---------------------------------------------------------------------------------
-    if (lane == 0) {
-      rk_page_entry next[2] = {table[page_begin], page_begin + 1 < page_end ? table[page_begin + 1] : 0};
-      for (uint32_t g = 0; g < groups; ++g) {
-        const uint32_t r = g % kRawStages, slot = g % kRawStages;
-        const uint32_t first = page_begin + 2 * g, group_pages = min(2u, page_end - first);
-        const rk_page_entry entries[2] = {next[0], next[1]};
-        if (g + 1 < groups) { // the next group's entries travel while this group is issued
-          next[0] = table[first + 2];
-          next[1] = first + 3 < page_end ? table[first + 3] : 0;
-        }
-        if (g >= kRawStages) barrier_wait(&ctl.raw_free[(g - kRawStages) % kRawStages], (g - kRawStages) / kRawStages, error); // the stage's last reader
-        const uint32_t full = smem_u32(&ctl.raw_full[slot]), stage = raw_tile + r * kRawStageBytes;
-        barrier_expect(full, group_pages * (2 * kSlab + (Kind::kScales ? 256 : 0)));
-#pragma unroll
-        for (uint32_t local = 0; local < 2; ++local) {
-          if (local >= group_pages) break;
-          const uint32_t index = rk_entry_index(entries[local]);
-          const uint64_t region = rk_entry_extent(entries[local]) + args.layer.offset;
-          const uint64_t extent_pages = args.layer.extent_pages;
-          const uint64_t keys = region + uint64_t(index) * data_bytes + kv_head * kSlab;
-          const uint64_t values = region + extent_pages * (uint64_t(data_bytes) + scale_bytes) + uint64_t(index) * data_bytes + kv_head * kSlab;
-          const uint64_t key_scales = region + extent_pages * data_bytes + uint64_t(index) * scale_bytes + kv_head * 128u;
-          const uint64_t value_scales = region + extent_pages * (2ull * data_bytes + scale_bytes) + uint64_t(index) * scale_bytes + kv_head * 128u;
-          tma_load_rows(stage + local * kSlab, &head_map, int32_t((keys - args.window_base) >> 7), full);
-          tma_load_rows(stage + (2 + local) * kSlab, &head_map, int32_t((values - args.window_base) >> 7), full);
-          if (Kind::kScales) {
-            bulk_load(stage + kRawScaleOffset + local * 128, reinterpret_cast<const void *>(key_scales), 128, full);
-            bulk_load(stage + kRawScaleOffset + (2 + local) * 128, reinterpret_cast<const void *>(value_scales), 128, full);
-          }
-        }
-        // The raw ring holds at most kRawStages groups; the groups behind it are already requested from HBM
-        // into L2, kPrefetchGroups ahead, so the ring is refilled at L2 latency.
-        const uint32_t ahead = first + 2 * kPrefetchGroups;
-#pragma unroll
-        for (uint32_t local = 0; local < 2; ++local) {
-          if (!kPrefetch || ahead + local >= page_end) break;
-          const rk_page_entry entry = table[ahead + local];
-          const uint32_t index = rk_entry_index(entry);
-          const uint64_t region = rk_entry_extent(entry) + args.layer.offset;
-          const uint64_t extent_pages = args.layer.extent_pages;
-          prefetch_l2(region + uint64_t(index) * data_bytes + kv_head * kSlab, kSlab);
-          prefetch_l2(region + extent_pages * (uint64_t(data_bytes) + scale_bytes) + uint64_t(index) * data_bytes + kv_head * kSlab, kSlab);
-          if (Kind::kScales) {
-            prefetch_l2(region + extent_pages * data_bytes + uint64_t(index) * scale_bytes + kv_head * 128u, 128);
-            prefetch_l2(region + extent_pages * (2ull * data_bytes + scale_bytes) + uint64_t(index) * scale_bytes + kv_head * 128u, 128);
-          }
-        }
+    // ---- TMA producer: lanes 0-7 issue one copy each (page, {K, V, key scales, value scales}) of the group, lanes
+    // 8-15 the matching L2 requests of a later group; one thread alone spent ~1 000 cycles per group on them ----
+    const uint32_t local = (lane >> 2) & 1u, kind = lane & 3u; // page of the group, copy of the page
+    const bool copier = lane < 8, prefetcher = kPrefetch && lane >= 8 && lane < 16;
+    auto source = [&](rk_page_entry entry, uint32_t &bytes) -> uint64_t { // global address and size of this lane's copy
+      const uint32_t index = rk_entry_index(entry);
+      const uint64_t region = rk_entry_extent(entry) + args.layer.offset;
+      const uint64_t extent_pages = args.layer.extent_pages;
+      bytes = kind < 2 ? kSlab : 128u;
+      switch (kind) {
+      case 0: return region + uint64_t(index) * data_bytes + kv_head * kSlab;
+      case 1: return region + extent_pages * (uint64_t(data_bytes) + scale_bytes) + uint64_t(index) * data_bytes + kv_head * kSlab;
+      case 2: return region + extent_pages * data_bytes + uint64_t(index) * scale_bytes + kv_head * 128u;
+      default: return region + extent_pages * (2ull * data_bytes + scale_bytes) + uint64_t(index) * scale_bytes + kv_head * 128u;
       }
-      // Every copy this thread started has landed before the CTA may leave (also after a failed wait).
+    };
+    rk_page_entry next = copier && page_begin + local < page_end ? table[page_begin + local] : 0;
+    for (uint32_t g = 0; g < groups; ++g) {
+      const uint32_t r = g % kRawStages;
+      const uint32_t first = page_begin + 2 * g, group_pages = min(2u, page_end - first);
+      const rk_page_entry entry = next;
+      if (copier && g + 1 < groups && first + 2 + local < page_end) next = table[first + 2 + local]; // travels while this group is issued
+      if (g >= kRawStages) barrier_wait(&ctl.raw_free[r], g / kRawStages - 1, error); // the stage's last readers
+      const uint32_t full = smem_u32(&ctl.raw_full[r]), stage = raw_tile + r * kRawStageBytes;
+      if (lane == 0) barrier_expect(full, group_pages * (2 * kSlab + (Kind::kScales ? 256 : 0)));
+      __syncwarp();
+      if (copier && local < group_pages && (kind < 2 || Kind::kScales)) {
+        uint32_t bytes;
+        const uint64_t address = source(entry, bytes);
+        if (kind < 2) tma_load_rows(stage + (2 * kind + local) * kSlab, &head_map, int32_t((address - args.window_base) >> 7), full);
+        else bulk_load(stage + kRawScaleOffset + (2 * (kind - 2) + local) * 128, reinterpret_cast<const void *>(address), 128, full);
+      }
+      // The raw ring holds at most kRawStages groups; the groups behind it are already requested from HBM into L2,
+      // kPrefetchGroups ahead, so the ring is refilled at L2 latency.
+      const uint32_t ahead = first + 2 * kPrefetchGroups + local;
+      if (prefetcher && ahead < page_end && (kind < 2 || Kind::kScales)) {
+        uint32_t bytes;
+        const uint64_t address = source(table[ahead], bytes);
+        prefetch_l2(address, bytes);
+      }
+    }
+    // Every copy this warp started has landed before the CTA may leave (also after a failed wait).
+    if (lane == 0)
       for (uint32_t g = groups > kRawStages ? groups - kRawStages : 0; g < groups; ++g) {
         const uint32_t bar = smem_u32(&ctl.raw_full[g % kRawStages]), parity = (g / kRawStages) & 1u;
         for (uint32_t i = 0; i < kSpinLimit && !barrier_try(bar, parity); ++i) __nanosleep(64);
       }
-    }
   } else if (warp == kScoreWarp) {
     // ---- tensor-core issue, S = Q.K^T: S buffer g&1 is free once PV(g-2), which read P(g-2) from it, has landed (p_free) ----
     // The whole warp walks the loop (uniform control flow); one elected lane issues.
@@ -646,9 +646,11 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
       }
       __syncwarp();
     }
-  } else if (warp >= kSoftmaxWarps) {
+  } else if (warp >= kSoftmaxWarps || (warp & 3u) >= kQuarters) {
     // ---- expanders: raw codes -> 16-bit operand tiles --------------------------------------------------------------
-    const uint32_t team = (tid - kSoftmaxThreads) / kExpandThreads, e = tid - kSoftmaxThreads - team * kExpandThreads;
+    const uint32_t index = warp >= kSoftmaxWarps ? tid - kSoftmaxThreads
+                                                  : kExpandWarps * 32 + ((warp >> 2) * (4 - kQuarters) + (warp & 3u) - kQuarters) * 32 + lane;
+    const uint32_t team = index / kExpandThreads, e = index - team * kExpandThreads;
     for (uint32_t g = team; g < groups; g += kTileStages) {
       const uint32_t r = g % kRawStages, slot = r, b = team, round = g / kTileStages;
       const uint32_t first = page_begin + 2 * g;
@@ -683,9 +685,9 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
       barrier_arrive(smem_u32(&ctl.v_full[b]));
       barrier_arrive(smem_u32(&ctl.raw_free[slot]));
     }
-  } else if ((warp & 3u) < kQuarters) {
+  } else {
     // ---- softmax: kRowThreads threads per fused row (= TMEM lane), kRowTokens contraction positions each;
-    // quarters of the tile without a real row sit the loop out ----
+    // the warps of quarters without a real row work as expanders instead ----
     const uint32_t quarter = warp & 3u, part = warp >> 2;
     const uint32_t my_row = quarter * 32 + lane;
     const float score_scale = rk_score_scale(p.score_scale, kD) * kLog2e;
