@@ -560,44 +560,38 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
   if (warp == kTmaWarp) {
     // ---- TMA producer: lanes 0-7 issue one copy each (page, {K, V, key scales, value scales}) of the group, lanes
     // 8-15 the matching L2 requests of a later group; one thread alone spent ~1 000 cycles per group on them ----
-    const uint32_t local = (lane >> 2) & 1u, kind = lane & 3u; // page of the group, copy of the page
-    const bool copier = lane < 8, prefetcher = kPrefetch && lane >= 8 && lane < 16;
-    auto source = [&](rk_page_entry entry, uint32_t &bytes) -> uint64_t { // global address and size of this lane's copy
-      const uint32_t index = rk_entry_index(entry);
-      const uint64_t region = rk_entry_extent(entry) + args.layer.offset;
-      const uint64_t extent_pages = args.layer.extent_pages;
-      bytes = kind < 2 ? kSlab : 128u;
-      switch (kind) {
-      case 0: return region + uint64_t(index) * data_bytes + kv_head * kSlab;
-      case 1: return region + extent_pages * (uint64_t(data_bytes) + scale_bytes) + uint64_t(index) * data_bytes + kv_head * kSlab;
-      case 2: return region + extent_pages * data_bytes + uint64_t(index) * scale_bytes + kv_head * 128u;
-      default: return region + extent_pages * (2ull * data_bytes + scale_bytes) + uint64_t(index) * scale_bytes + kv_head * 128u;
-      }
-    };
-    rk_page_entry next = copier && page_begin + local < page_end ? table[page_begin + local] : 0;
+    const uint32_t local = (lane >> 2) & 1u, kind = lane & 3u; // page of the group; {K, V, key scales, value scales}
+    const bool copier = lane < 8 && (kind < 2 || Kind::kScales), prefetcher = kPrefetch && lane >= 8 && lane < 16;
+    // this lane's tensor inside a layer region ([K data][K scales][V data][V scales], each x extent pages) and head
+    const uint64_t extent_pages = args.layer.extent_pages;
+    const uint64_t tensor_base = args.layer.offset +
+                                 extent_pages * (kind == 0 ? 0ull : kind == 2 ? uint64_t(data_bytes)
+                                                  : kind == 1 ? uint64_t(data_bytes) + scale_bytes : 2ull * data_bytes + scale_bytes) +
+                                 kv_head * (kind < 2 ? kSlab : 128u);
+    const uint32_t page_stride = kind < 2 ? data_bytes : scale_bytes, copy_bytes = kind < 2 ? kSlab : 128u;
+    auto source = [&](rk_page_entry entry) { return rk_entry_extent(entry) + tensor_base + uint64_t(rk_entry_index(entry)) * page_stride; };
+    // table entries travel one group ahead of their use (copies) and of their L2 request (prefetch)
+    rk_page_entry next = lane < 8 && page_begin + local < page_end ? table[page_begin + local] : 0;
+    rk_page_entry next_ahead = prefetcher && page_begin + 2 * kPrefetchGroups + local < page_end ? table[page_begin + 2 * kPrefetchGroups + local] : 0;
     for (uint32_t g = 0; g < groups; ++g) {
       const uint32_t r = g % kRawStages;
       const uint32_t first = page_begin + 2 * g, group_pages = min(2u, page_end - first);
-      const rk_page_entry entry = next;
-      if (copier && g + 1 < groups && first + 2 + local < page_end) next = table[first + 2 + local]; // travels while this group is issued
+      const rk_page_entry entry = next, entry_ahead = next_ahead;
+      const uint32_t ahead = first + 2 * kPrefetchGroups + local;
+      if (lane < 8 && first + 2 + local < page_end) next = table[first + 2 + local];
+      if (prefetcher && ahead + 2 < page_end) next_ahead = table[ahead + 2];
       if (g >= kRawStages) barrier_wait(&ctl.raw_free[r], g / kRawStages - 1, error); // the stage's last readers
       const uint32_t full = smem_u32(&ctl.raw_full[r]), stage = raw_tile + r * kRawStageBytes;
       if (lane == 0) barrier_expect(full, group_pages * (2 * kSlab + (Kind::kScales ? 256 : 0)));
       __syncwarp();
-      if (copier && local < group_pages && (kind < 2 || Kind::kScales)) {
-        uint32_t bytes;
-        const uint64_t address = source(entry, bytes);
+      if (copier && local < group_pages) {
+        const uint64_t address = source(entry);
         if (kind < 2) tma_load_rows(stage + (2 * kind + local) * kSlab, &head_map, int32_t((address - args.window_base) >> 7), full);
         else bulk_load(stage + kRawScaleOffset + (2 * (kind - 2) + local) * 128, reinterpret_cast<const void *>(address), 128, full);
       }
       // The raw ring holds at most kRawStages groups; the groups behind it are already requested from HBM into L2,
       // kPrefetchGroups ahead, so the ring is refilled at L2 latency.
-      const uint32_t ahead = first + 2 * kPrefetchGroups + local;
-      if (prefetcher && ahead < page_end && (kind < 2 || Kind::kScales)) {
-        uint32_t bytes;
-        const uint64_t address = source(table[ahead], bytes);
-        prefetch_l2(address, bytes);
-      }
+      if (prefetcher && ahead < page_end && (kind < 2 || Kind::kScales)) prefetch_l2(source(entry_ahead), copy_bytes);
     }
     // Every copy this warp started has landed before the CTA may leave (also after a failed wait).
     if (lane == 0)
