@@ -102,6 +102,13 @@ int rk_attention_verify_split_tc(const void *window, uint32_t format, uint32_t k
                                  const rk_page_entry *const *tables, const uint32_t *row_masks,
                                  const rk_verify_params *lane_params, rk_kv_layer layer, uint32_t *status,
                                  void *stream);
+/* prefill_attention_*_split (prefill/paged_attention.metal:7-67) on the same tcgen05 kernel: one CTA per (KV
+ * head, split, 8-row tile of the chunk). Arguments and scratch layout as rk_attention_prefill_split plus the
+ * window and the status word; merge with rk_attention_prefill_reduce. `params` is a HOST pointer. */
+int rk_attention_prefill_split_tc(const void *window, uint32_t format, uint32_t kv_heads, uint32_t query_heads,
+                                  uint32_t head_dim, const void *queries, float *partials, float *statistics,
+                                  const rk_page_entry *table, const rk_prefill_params *params, uint32_t *status,
+                                  void *stream);
 int rk_attention_decode(const void *window, const rk_decode_plan *plan, uint32_t format, const void *queries,
                         void *output, float *output_f32, float *partials, float *statistics,
                         uint32_t *descriptors, const rk_page_entry *const *tables,

@@ -188,14 +188,19 @@ void PagedAttention::addPrefillStore(void *stream, rk_kv_layer layer, const void
 
 void PagedAttention::addPrefill(void *stream, rk_kv_layer layer, const void *queries, void *output, float *partials, float *statistics,
                                 uint64_t partialsBytes, uint64_t statisticsBytes, const rk_page_entry *pageTable,
-                                const rk_chunk_params &chunk, const PrefillAttentionPlan &plan, uint32_t queryHeads, kv::Layout layout) {
+                                const rk_chunk_params &chunk, const PrefillAttentionPlan &plan, uint32_t queryHeads, kv::Layout layout,
+                                const void *window, uint32_t *status) {
   if (chunk.chunk_tokens != plan.rows) throw std::invalid_argument("prefill attention rows do not match plan");
   if (const std::string_view error = chunkedPrefillValidationError(chunk); !error.empty()) throw std::invalid_argument(std::string(error));
   if (partialsBytes < plan.workspace.partialsBytes || statisticsBytes < plan.workspace.statisticsBytes)
     throw std::invalid_argument("prefill attention scratch is smaller than its bound");
   if (queries == output) throw std::invalid_argument("queries and output must not alias");
   const rk_prefill_params attention{chunk.committed_tokens, chunk.chunk_tokens, chunk.chunk_stride, chunk.page_table_entries, layer, plan.splits, plan.scoreScale};
-  check(rk_attention_prefill_split(formatCode(layout.format), layout.kvHeads, queryHeads, layout.headDimension, queries, partials, statistics, pageTable, &attention, stream));
+  if (window && status && layout.kvHeads == 4 && queryHeads == 24 && layout.headDimension == 256)
+    check(rk_attention_prefill_split_tc(window, formatCode(layout.format), layout.kvHeads, queryHeads, layout.headDimension, queries, partials,
+                                        statistics, pageTable, &attention, status, stream));
+  else
+    check(rk_attention_prefill_split(formatCode(layout.format), layout.kvHeads, queryHeads, layout.headDimension, queries, partials, statistics, pageTable, &attention, stream));
   check(rk_attention_prefill_reduce(layout.kvHeads, queryHeads, layout.headDimension, partials, statistics, output, nullptr, &attention, stream));
 }
 

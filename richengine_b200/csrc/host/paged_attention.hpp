@@ -90,7 +90,9 @@ public:
   static void addPrefill(void *stream, rk_kv_layer layer, const void *queries, void *output, float *partials,
                          float *statistics, uint64_t partialsBytes, uint64_t statisticsBytes,
                          const rk_page_entry *pageTable, const rk_chunk_params &chunk, const PrefillAttentionPlan &plan,
-                         uint32_t queryHeads, kv::Layout layout);
+                         uint32_t queryHeads, kv::Layout layout,
+                         // the pool's window and one zeroed device word select the tcgen05 kernel for the tiles
+                         const void *window = nullptr, uint32_t *status = nullptr);
   // deviceChunks / deviceAttention: the lanes' parameter blocks in device memory (uploaded once per step).
   static void addVerify(void *stream, rk_kv_layer layer, const PagedVerifyBuffers &buffers,
                         const rk_chunk_params *deviceChunks, const rk_verify_params *deviceAttention,

@@ -68,8 +68,8 @@ constexpr uint32_t kMaxRawStages = 4;
 //   int8      fp16 operands; key codes as u * 2^-24 with u = code + 128; values exact (1024 + u - 1152).
 //   fp8 e4m3  fp16 operands, exact (cvt); queries staged as fp16 like the reference's fp8 tile
 //             (paged_attention_fp8_tile.h:34-60).
-//   bf16      bf16 operands (bits as stored); the probabilities are rounded to bf16 too, as the reference's
-//             tile does (paged_attention_tile.h:176-186): both operands of a contraction are of one kind.
+//   bf16      bf16 operands (bits as stored). Both operands of a contraction are of one kind, so the
+//             probabilities are bf16 too: a high and a low part, contracted one after the other (16 bits).
 template <uint32_t Format> struct Traits;
 template <> struct Traits<RK_FORMAT_INT4> {
   static constexpr uint32_t kSlab = 4096, kRawStages = 4, kTileStages = 2;
@@ -267,6 +267,9 @@ struct VerifyArgs {
   rk_kv_layer layer;
   uint64_t window_base;
   uint32_t *status; // one word: non-zero when a bounded wait ran out
+  // prefill launches (grid z = 8-row tile of the chunk): the sequence's table and parameters instead of per-lane ones
+  const rk_page_entry *prefill_table;
+  rk_prefill_params prefill;
 };
 
 
@@ -431,7 +434,9 @@ template <> struct Expand<RK_FORMAT_BF16> {
   }
 };
 
-template <uint32_t Format, uint32_t Rows, bool kTree>
+// kPrefill: the CTA's window is tile blockIdx.z of a prefill chunk (prefill/paged_attention.metal:7-67): eight rows
+// starting at row 8*tile of the chunk, queries [kv_head][stride][group][D], partial slot (tile*heads + head)*splits + split.
+template <uint32_t Format, uint32_t Rows, bool kTree, bool kPrefill = false>
 __global__ void __launch_bounds__(kThreads, 1)
 window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args) {
   using Kind = Traits<Format>;
@@ -459,7 +464,20 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
 
   const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const uint32_t kv_head = blockIdx.x, split = blockIdx.y, lane_index = blockIdx.z;
-  rk_verify_params p = args.lane_params[lane_index];
+  rk_verify_params p;
+  if (kPrefill) {
+    const rk_prefill_params &chunk = args.prefill;
+    const uint32_t tile_start = lane_index * RK_PREFILL_TILE_ROWS;
+    if (!rk_prefill_contract_valid(&chunk) || tile_start >= chunk.rows) return;
+    p.committed_tokens = chunk.committed_tokens + tile_start;
+    p.page_table_entries = chunk.page_table_entries;
+    p.split_count = p.slot_splits = chunk.split_count;
+    p.active_rows = min(RK_PREFILL_TILE_ROWS, chunk.rows - tile_start);
+    p.row_capacity = RK_PREFILL_TILE_ROWS;
+    p.score_scale = chunk.score_scale;
+  } else {
+    p = args.lane_params[lane_index];
+  }
   p.kv = args.layer;
   if (!rk_verify_contract_valid(&p) || p.row_capacity != Rows || split >= p.split_count) return;
   const uint32_t visible = p.committed_tokens + p.active_rows;
@@ -469,7 +487,7 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
   if (page_begin >= pages) return; // a split without pages writes nothing
   const uint32_t page_end = min(pages, page_begin + per_split);
   const uint32_t groups = (page_end - page_begin + 1) / 2;
-  const rk_page_entry *table = args.tables[lane_index];
+  const rk_page_entry *table = kPrefill ? args.prefill_table : args.tables[lane_index];
   const uint32_t *row_masks = kTree ? args.row_masks + uint64_t(lane_index) * p.row_capacity : nullptr;
 
   // ---- setup: barriers, TMEM, query tile ----------------------------------------------------------
@@ -506,7 +524,8 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
   // order (0,4,1,5,2,6,3,7) inside every 8 dims, dims 1,5,3,7 divided by 16; int8, fp8: fp16 in order; bf16: the bits.
   if (warp < kSoftmaxWarps) {
     const uint32_t quarter = warp & 3u, part = warp >> 2, row = quarter * 32 + lane;
-    const uint16_t *queries = args.queries + (uint64_t(lane_index) * kHeads + kv_head) * (uint64_t(RK_VERIFY_CHUNK_STRIDE) * kG * kD);
+    const uint16_t *queries = kPrefill ? args.queries + (uint64_t(kv_head) * args.prefill.chunk_stride + lane_index * RK_PREFILL_TILE_ROWS) * (kG * kD)
+                                       : args.queries + (uint64_t(lane_index) * kHeads + kv_head) * (uint64_t(RK_VERIFY_CHUNK_STRIDE) * kG * kD);
     const bool real = row < p.active_rows * kG;
     float q_sum = 0.0f; // over the values the tensor core will see, for the key-offset correction
 #pragma unroll 1
@@ -634,7 +653,10 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
       const uint32_t source = tmem_s + b * 64;
       if (elect_one()) {
 #pragma unroll
-        for (uint32_t j = 0; j < 4; ++j) umma_f16_ts(tmem_o, source + 8 * j, desc + ((j * 32) >> 4), idesc_pv, (g || j) ? 1u : 0u);
+        for (uint32_t j = 0; j < 4; ++j) {
+          umma_f16_ts(tmem_o, source + 8 * j, desc + ((j * 32) >> 4), idesc_pv, (g || j) ? 1u : 0u);
+          if (Kind::kBf16) umma_f16_ts(tmem_o, source + 32 + 8 * j, desc + ((j * 32) >> 4), idesc_pv, 1u); // the low parts
+        }
         umma_commit(&ctl.v_free[t]);
         umma_commit(&ctl.p_free[b]);
       }
@@ -751,7 +773,9 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
         row_sum *= scale;
       }
       const float exponent_base = row_max - 6.0f;
-      uint32_t packed[kRowTokens / 2];
+      // bf16 probabilities alone carry 8 bits: they travel as a high and a low bf16 part (two contractions), which
+      // restores 16 bits; the low parts take the second half of the S buffer
+      uint32_t packed[kRowTokens / 2], packed_low[Kind::kBf16 ? kRowTokens / 2 : 1];
 #pragma unroll
       for (uint32_t c = 0; c < kRowTokens / 2; ++c) {
         float w[2];
@@ -760,7 +784,12 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
           w[h] = exp2_fast(scores[2 * c + h] - exponent_base);     // 0 for a masked token
           row_sum = fmaf(w[h], triples[2 * c + h].z, row_sum);     // 2^(score - row_max)
         }
-        packed[c] = Kind::kBf16 ? pack_bfloat2(w[0], w[1]) : pack_half2(w[0], w[1]);
+        if (Kind::kBf16) {
+          packed[c] = pack_bfloat2(w[0], w[1]);
+          packed_low[c] = pack_bfloat2(w[0] - __uint_as_float(packed[c] << 16), w[1] - __uint_as_float(packed[c] & 0xffff0000u));
+        } else {
+          packed[c] = pack_half2(w[0], w[1]);
+        }
       }
       if (g && __any_sync(0xffffffffu, grow)) { // this part rescales its columns of O once P.V(g-1) has landed
         barrier_wait(&ctl.v_free[(g - 1) % kTileStages], (g - 1) / kTileStages, error);
@@ -775,6 +804,7 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
         }
       }
       tmem_store_packed(tmem_s + b * 64 + lane_address + part * (kRowTokens / 2), packed);
+      if constexpr (Kind::kBf16) tmem_store_packed(tmem_s + b * 64 + 32 + lane_address + part * (kRowTokens / 2), packed_low);
       tmem_fence_before();
       barrier_arrive(smem_u32(&ctl.p_full[b]));
       barrier_arrive(smem_u32(&ctl.scale_free[g % kScaleStages]));
@@ -784,7 +814,7 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
     barrier_wait(&ctl.v_free[(groups - 1) % kTileStages], (groups - 1) / kTileStages, error);
     tmem_fence_after();
     const bool failed = *error != 0;
-    const uint64_t slot = (uint64_t(lane_index) * kHeads + kv_head) * p.slot_splits + split;
+    const uint64_t slot = (uint64_t(lane_index) * kHeads + kv_head) * p.slot_splits + split; // prefill: lane_index = tile
     float *out = args.partials + (slot * kRealRows + my_row) * kD + part * kOutColumns;
 #pragma unroll 1
     for (uint32_t c = 0; c < kOutColumns / 32; ++c) {
@@ -859,7 +889,7 @@ extern "C" int rk_attention_verify_split_tc(const void *window, uint32_t format,
     set_error("rk_attention_verify_split_tc: invalid arguments");
     return kInvalid;
   }
-  VerifyArgs args{static_cast<const uint16_t *>(queries), partials, statistics, tables, row_masks, lane_params, layer, w->base, status};
+  VerifyArgs args{static_cast<const uint16_t *>(queries), partials, statistics, tables, row_masks, lane_params, layer, w->base, status, nullptr, {}};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int st = kUnsupported;
   switch (format) {
@@ -870,4 +900,37 @@ extern "C" int rk_attention_verify_split_tc(const void *window, uint32_t format,
   }
   if (st) return st;
   return cuda_status(cudaGetLastError(), "window kernel launch");
+}
+
+// prefill_attention_*_split (prefill/paged_attention.metal:7-67) on the tcgen05 kernel: one CTA per (KV head, split,
+// 8-row tile). Arguments and scratch layout as rk_attention_prefill_split plus the pool's window and the status
+// word; merge with rk_attention_prefill_reduce. `params` is a HOST pointer.
+extern "C" int rk_attention_prefill_split_tc(const void *window, uint32_t format, uint32_t kv_heads, uint32_t query_heads,
+                                             uint32_t head_dim, const void *queries, float *partials, float *statistics,
+                                             const rk_page_entry *table, const rk_prefill_params *params, uint32_t *status,
+                                             void *stream) {
+  if (kv_heads != kHeads || query_heads != kHeads * kG || head_dim != kD || !rk_format_valid(format)) {
+    set_error("rk_attention_prefill_split_tc: built for 4 KV heads x 24 query heads x 256");
+    return kUnsupported;
+  }
+  const auto *w = static_cast<const Window *>(window);
+  if (!w || !queries || !partials || !statistics || !table || !params || !status || !rk_prefill_contract_valid(params)) {
+    set_error("rk_attention_prefill_split_tc: invalid arguments");
+    return kInvalid;
+  }
+  VerifyArgs args{static_cast<const uint16_t *>(queries), partials, statistics, nullptr, nullptr, nullptr, params->kv, w->base, status, table, *params};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const uint32_t tiles = (params->rows + RK_PREFILL_TILE_ROWS - 1) / RK_PREFILL_TILE_ROWS;
+  const dim3 grid(kHeads, params->split_count, tiles);
+  auto launch = [&](auto kernel, size_t shared_bytes, const CUtensorMap &map) -> int {
+    if (int st = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(shared_bytes)), "window kernel shared memory")) return st;
+    kernel<<<grid, kThreads, shared_bytes, s>>>(map, args);
+    return cuda_status(cudaGetLastError(), "prefill window kernel launch");
+  };
+  switch (format) {
+  case RK_FORMAT_INT4: return launch(window_attention_kernel<RK_FORMAT_INT4, 8, false, true>, 1024 + tile_bytes<RK_FORMAT_INT4>() + sizeof(Control), w->int4_head_map);
+  case RK_FORMAT_INT8: return launch(window_attention_kernel<RK_FORMAT_INT8, 8, false, true>, 1024 + tile_bytes<RK_FORMAT_INT8>() + sizeof(Control), w->byte_head_map);
+  case RK_FORMAT_FP8E4M3: return launch(window_attention_kernel<RK_FORMAT_FP8E4M3, 8, false, true>, 1024 + tile_bytes<RK_FORMAT_FP8E4M3>() + sizeof(Control), w->byte_head_map);
+  default: return launch(window_attention_kernel<RK_FORMAT_BF16, 8, false, true>, 1024 + tile_bytes<RK_FORMAT_BF16>() + sizeof(Control), w->int4_map);
+  }
 }

@@ -92,6 +92,14 @@ class VerifyWindowAttention:
             layer, self.status_word.data_ptr(), _stream(stream))
         lib.check(status, "rk_attention_verify_split_tc")
 
+    def prefill_split(self, queries, partials, statistics, table, params: lib.PrefillParams, stream=None) -> None:
+        """The 8-row tiles of a prefill chunk (rk_attention_prefill_split_tc); merge with attention_prefill_reduce."""
+        status = self._lib.rk_attention_prefill_split_tc(
+            self._window, self.layout.format, self.layout.kv_heads, self.query_heads, self.layout.head_dimension,
+            queries.data_ptr(), partials.data_ptr(), statistics.data_ptr(), table.data_ptr(), C.byref(params),
+            self.status_word.data_ptr(), _stream(stream))
+        lib.check(status, "rk_attention_prefill_split_tc")
+
     def check(self) -> None:
         """Synchronises and raises if a bounded wait ran out in a launched step."""
         if int(self.status_word.item()) != 0:
@@ -144,6 +152,15 @@ def attention_prefill(layout: Layout, query_heads: int, queries, output, partial
                                                   partials.data_ptr(), statistics.data_ptr(), output.data_ptr(),
                                                   output_f32.data_ptr() if output_f32 is not None else None,
                                                   C.byref(params), _stream(stream)),
+              "rk_attention_prefill_reduce")
+
+
+def attention_prefill_reduce(layout: Layout, query_heads: int, partials, statistics, output, params: lib.PrefillParams,
+                             output_f32=None, stream=None) -> None:
+    lib.check(lib.load().rk_attention_prefill_reduce(layout.kv_heads, query_heads, layout.head_dimension,
+                                                     partials.data_ptr(), statistics.data_ptr(), output.data_ptr(),
+                                                     output_f32.data_ptr() if output_f32 is not None else None,
+                                                     C.byref(params), _stream(stream)),
               "rk_attention_prefill_reduce")
 
 

@@ -77,9 +77,10 @@ def test_tree_masks(fmt):
     s.close()
 
 
+@pytest.mark.parametrize("tensor_core", [False, True])
 @pytest.mark.parametrize("fmt", FORMATS)
-@pytest.mark.parametrize("rows,committed", [(1, 0), (1, 95), (70, 13), (8, 32)])
-def test_prefill_attention(fmt, rows, committed):
+@pytest.mark.parametrize("rows,committed", [(1, 0), (1, 95), (70, 13), (8, 32), (300, 1000)])
+def test_prefill_attention(fmt, rows, committed, tensor_core):
     """8-row tiles over a chunk; rows=1 is the plain one-query decode
     (runtime/metal/kernels/prefill/paged_attention.metal:7-67)."""
     s = Scenario(Layout(1, 4, 256, fmt), [committed], extra_tokens=rows, device=True)
@@ -101,7 +102,14 @@ def test_prefill_attention(fmt, rows, committed):
     dq = dev(q)
     out = torch.zeros_like(dq)
     out32 = torch.zeros(dq.shape, dtype=torch.float32, device="cuda")
-    ops.attention_prefill(s.layout, 24, dq, out, partials, stats, s.device_tables[0], pp, output_f32=out32)
+    if tensor_core:
+        runner = ops.VerifyWindowAttention(s.layout, 24, s.storage.window())
+        runner.prefill_split(dq, partials, stats, s.device_tables[0], pp)
+        ops.attention_prefill_reduce(s.layout, 24, partials, stats, out, pp, output_f32=out32)
+        runner.check()
+        runner.close()
+    else:
+        ops.attention_prefill(s.layout, 24, dq, out, partials, stats, s.device_tables[0], pp, output_f32=out32)
     torch.cuda.synchronize()
     got32 = out32.cpu().numpy()
     for tile in range(tiles):
