@@ -56,7 +56,8 @@ def parse():
     ap.add_argument("--format", default="int4", choices=["int4", "int8", "fp8e4m3", "bf16"],
                     help="stored KV format of the decode workload (the headline is int4)")
     ap.add_argument("--rows", type=int, default=16, choices=[8, 16], help="--mode verify: window rows per sequence")
-    ap.add_argument("--mode", default="requests", choices=["requests", "seqsplit", "verify"],
+    ap.add_argument("--chunk", type=int, default=2048, help="--mode prefill: rows of the prefill chunk")
+    ap.add_argument("--mode", default="requests", choices=["requests", "seqsplit", "verify", "prefill"],
                     help="requests: every rank runs its own batch (default); seqsplit: ONE sequence of --context "
                          "tokens split along the sequence over the ranks, all-gather of (max, sum, O), rank-order merge")
     return ap.parse_args()
@@ -651,6 +652,109 @@ def run_verify(args):
     runner.close()
 
 
+def run_prefill(args):
+    """Chunked prefill of one sequence on int4 pages: per step and layer, append the chunk's rows (quantize into the
+    pages) and attend them causally over the history in 8-row tiles on the tcgen05 window kernel. One GPU."""
+    import torch
+
+    from richengine_b200 import lib, ops
+    from richengine_b200.abi import INT4, Layout, pages_for, prefill_splits
+    from richengine_b200.storage import PageStorage
+
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    rows, history = args.chunk, args.context
+    layout = Layout(args.layers, KV_HEADS, HEAD_DIM, INT4)
+    pages = pages_for(history + rows)
+    extent_pages = layout.minimum_extent_pages()
+    extents = (pages + extent_pages - 1) // extent_pages
+    storage = PageStorage(layout, extents * extent_pages, extent_pages)
+    for extent in range(extents):
+        if not storage.allocate_extent(extent):
+            raise RuntimeError("KV pool does not fit in device memory")
+    table = torch.zeros(pages, dtype=torch.int64, device="cuda")
+    storage.write_entries(np.random.default_rng(42).permutation(extents * extent_pages)[:pages], 0, table)
+    places = storage.layers()
+    generator = torch.Generator(device="cuda").manual_seed(7)
+    group = QUERY_HEADS // KV_HEADS
+    stride = (rows + 31) // 32 * 32
+    k = torch.randn((KV_HEADS, 2048, HEAD_DIM), generator=generator, device="cuda").to(torch.bfloat16)
+    v = torch.randn((KV_HEADS, HEAD_DIM, 2048), generator=generator, device="cuda").to(torch.bfloat16)
+    done = 0
+    while done < history:
+        count = min(2048, history - done)
+        for layer in range(args.layers):
+            ops.store_chunk(layout, k, v, table, lib.ChunkParams(done, count, 2048, pages, places[layer]))
+        done += count
+    chunk_keys = torch.randn((KV_HEADS, stride, HEAD_DIM), generator=generator, device="cuda").to(torch.bfloat16)
+    chunk_values = torch.randn((KV_HEADS, HEAD_DIM, stride), generator=generator, device="cuda").to(torch.bfloat16)
+    queries = torch.randn((KV_HEADS, stride, group, HEAD_DIM), generator=generator, device="cuda").to(torch.bfloat16)
+    output = torch.zeros_like(queries)
+    tiles = (rows + 7) // 8
+    splits = prefill_splits(tiles)
+    partials = torch.empty(tiles * KV_HEADS * splits * 8 * group * HEAD_DIM, dtype=torch.float32, device="cuda")
+    statistics_buffer = torch.empty(tiles * KV_HEADS * splits * 8 * group * 2, dtype=torch.float32, device="cuda")
+    runner = ops.VerifyWindowAttention(layout, QUERY_HEADS, storage.window())
+
+    def step_once():  # the same chunk position every step: the rows are overwritten in place
+        for layer in range(args.layers):
+            ops.store_chunk(layout, chunk_keys, chunk_values, table, lib.ChunkParams(history, rows, stride, pages, places[layer]))
+            params = lib.PrefillParams(history, rows, stride, pages, places[layer], splits, 0.0)
+            runner.prefill_split(queries, partials, statistics_buffer, table, params)
+            ops.attention_prefill_reduce(layout, QUERY_HEADS, partials, statistics_buffer, output, params)
+
+    for _ in range(args.warmup):
+        step_once()
+    torch.cuda.synchronize()
+    runner.check()
+    sampler = ClockSampler(torch.cuda.current_device())
+    begin_wall = time.perf_counter()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        step_once()
+    stop.record()
+    torch.cuda.synchronize()
+    elapsed_ms = start.elapsed_time(stop)
+    events = []
+    params = lib.PrefillParams(history, rows, stride, pages, places[0], splits, 0.0)
+    for repeat in range(4):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        runner.prefill_split(queries, partials, statistics_buffer, table, params)
+        b.record()
+        if repeat:
+            events.append((a, b))
+    torch.cuda.synchronize()
+    runner.check()
+
+    def same_load():
+        step_once()
+        torch.cuda.synchronize()
+    sampler.keep_loaded(begin_wall, same_load)
+    clocks = sampler.stop(begin_wall, time.perf_counter())
+    kernel_ms = statistics.mean(a.elapsed_time(b) for a, b in events)
+    flops = 4.0 * QUERY_HEADS * HEAD_DIM * sum(history + r + 1 for r in range(rows))  # causal: row r sees history + r + 1 tokens
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    peak = float(json.loads(peaks_path.read_text())["bf16_tflops"]) if peaks_path.exists() else 1590.0
+    print(json.dumps({
+        "metric": "int4_paged_prefill_rows_per_s", "value": round(rows * args.steps / (elapsed_ms * 1e-3), 1), "unit": "rows/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(elapsed_ms / args.steps, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int4 codes, fp16 tcgen05 operands, fp32 accumulate in tensor memory", "data": "synthetic",
+        "config": {"workload": f"chunked prefill, int4 KV, 27B geometry ({args.layers} layers), one sequence, {history} tokens of history, "
+                               f"chunk of {rows} rows: per layer append the chunk + causal attention in 8-row tiles + merge",
+                   "l2": "the history is re-read by every tile; the KV of one layer fits L2", "us_per_layer_step": round(elapsed_ms / args.steps / args.layers * 1e3, 2),
+                   "tiles": tiles, "splits": splits},
+        "roofline": {"bound": "tensor", "achieved": round(flops / (kernel_ms * 1e-3) / 1e12, 1), "peak": peak, "unit": "TFLOP/s",
+                     "frac": round(flops / (kernel_ms * 1e-3) / 1e12 / peak, 4), "traffic": None,
+                     "peak_source": "measured (MEASURED_PEAKS.json bf16_tflops)" if peaks_path.exists() else "fallback",
+                     "kernel": "window_attention_kernel (prefill tiles)", "us_per_launch": round(kernel_ms * 1e3, 2),
+                     "algorithmic_flops_per_launch": flops},
+        "gpu_launches": 3 * args.layers * args.steps, "clocks": clocks,
+    }), flush=True)
+    runner.close()
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -659,6 +763,10 @@ def main():
         if args.batch == 64 and args.context == 32768:  # the headline defaults: take this mode's own
             args.batch, args.context = 4, 65536
         run_verify(args)
+    elif args.mode == "prefill":
+        if args.batch == 64 and args.context == 32768:  # the headline defaults: take this mode's own
+            args.context = 6144
+        run_prefill(args)
     elif args.mode == "seqsplit":
         run_seqsplit(args)
     else:

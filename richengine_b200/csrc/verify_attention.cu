@@ -38,6 +38,7 @@
 #include "window.cuh"
 
 #include <cuda_bf16.h>
+#include <type_traits>
 #include <cuda_fp16.h>
 
 namespace rk {
@@ -434,8 +435,10 @@ template <> struct Expand<RK_FORMAT_BF16> {
   }
 };
 
-// kPrefill: the CTA's window is tile blockIdx.z of a prefill chunk (prefill/paged_attention.metal:7-67): eight rows
-// starting at row 8*tile of the chunk, queries [kv_head][stride][group][D], partial slot (tile*heads + head)*splits + split.
+// kPrefill: the CTA's window is `Rows` consecutive rows of a prefill chunk (prefill/paged_attention.metal:7-67), starting
+// at row Rows*blockIdx.z: one 8-row tile, or, for unsplit plans, two tiles at once (a 16-row causal window is exactly
+// two consecutive tiles). Queries [kv_head][stride][group][D]; each tile keeps its own partial slot
+// (tile*heads + head)*splits + split of 48 fused rows.
 template <uint32_t Format, uint32_t Rows, bool kTree, bool kPrefill = false>
 __global__ void __launch_bounds__(kThreads, 1)
 window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs args) {
@@ -467,13 +470,13 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
   rk_verify_params p;
   if (kPrefill) {
     const rk_prefill_params &chunk = args.prefill;
-    const uint32_t tile_start = lane_index * RK_PREFILL_TILE_ROWS;
-    if (!rk_prefill_contract_valid(&chunk) || tile_start >= chunk.rows) return;
+    const uint32_t tile_start = lane_index * Rows;
+    if (!rk_prefill_contract_valid(&chunk) || tile_start >= chunk.rows || (Rows != RK_PREFILL_TILE_ROWS && chunk.split_count != 1)) return;
     p.committed_tokens = chunk.committed_tokens + tile_start;
     p.page_table_entries = chunk.page_table_entries;
     p.split_count = p.slot_splits = chunk.split_count;
-    p.active_rows = min(RK_PREFILL_TILE_ROWS, chunk.rows - tile_start);
-    p.row_capacity = RK_PREFILL_TILE_ROWS;
+    p.active_rows = min(Rows, chunk.rows - tile_start);
+    p.row_capacity = Rows;
     p.score_scale = chunk.score_scale;
   } else {
     p = args.lane_params[lane_index];
@@ -524,7 +527,7 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
   // order (0,4,1,5,2,6,3,7) inside every 8 dims, dims 1,5,3,7 divided by 16; int8, fp8: fp16 in order; bf16: the bits.
   if (warp < kSoftmaxWarps) {
     const uint32_t quarter = warp & 3u, part = warp >> 2, row = quarter * 32 + lane;
-    const uint16_t *queries = kPrefill ? args.queries + (uint64_t(kv_head) * args.prefill.chunk_stride + lane_index * RK_PREFILL_TILE_ROWS) * (kG * kD)
+    const uint16_t *queries = kPrefill ? args.queries + (uint64_t(kv_head) * args.prefill.chunk_stride + lane_index * Rows) * (kG * kD)
                                        : args.queries + (uint64_t(lane_index) * kHeads + kv_head) * (uint64_t(RK_VERIFY_CHUNK_STRIDE) * kG * kD);
     const bool real = row < p.active_rows * kG;
     float q_sum = 0.0f; // over the values the tensor core will see, for the key-offset correction
@@ -814,13 +817,19 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
     barrier_wait(&ctl.v_free[(groups - 1) % kTileStages], (groups - 1) / kTileStages, error);
     tmem_fence_after();
     const bool failed = *error != 0;
-    const uint64_t slot = (uint64_t(lane_index) * kHeads + kv_head) * p.slot_splits + split; // prefill: lane_index = tile
-    float *out = args.partials + (slot * kRealRows + my_row) * kD + part * kOutColumns;
+    // verify: one slot of kRealRows fused rows per (lane, head, split); prefill: one slot of 48 fused rows per tile
+    constexpr uint32_t kSlotRows = kPrefill ? RK_PREFILL_TILE_ROWS * kG : kRealRows;
+    const uint32_t sub_tile = kPrefill ? my_row / kSlotRows : 0, slot_row = my_row - sub_tile * kSlotRows;
+    const uint64_t slot_owner = kPrefill ? uint64_t(lane_index) * (Rows / RK_PREFILL_TILE_ROWS) + sub_tile : lane_index;
+    const uint64_t slot = (slot_owner * kHeads + kv_head) * p.slot_splits + split;
+    // a chunk with an odd number of tiles has no second tile in its last pair: nothing is written for it
+    const bool row_exists = my_row < kRealRows && (!kPrefill || sub_tile * RK_PREFILL_TILE_ROWS < p.active_rows);
+    float *out = args.partials + (slot * kSlotRows + slot_row) * kD + part * kOutColumns;
 #pragma unroll 1
     for (uint32_t c = 0; c < kOutColumns / 32; ++c) {
       float o[32];
       tmem_load32(tmem_o + lane_address + part * kOutColumns + c * 32, o);
-      if (my_row < kRealRows) {
+      if (row_exists) {
 #pragma unroll
         for (uint32_t i = 0; i < 32; i += 4)
           *reinterpret_cast<float4 *>(out + c * 32 + i) = make_float4(o[i] * 0.015625f, o[i + 1] * 0.015625f, o[i + 2] * 0.015625f, o[i + 3] * 0.015625f);
@@ -828,11 +837,11 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
     }
     ctl.exchange[groups & 1u][my_row][part] = row_sum;
     asm volatile("bar.sync %0, %1;" ::"r"(1u + quarter), "n"(32 * kRowThreads) : "memory");
-    if (part == 0 && my_row < kRealRows) {
+    if (part == 0 && row_exists) {
       float total = 0.0f;
 #pragma unroll
       for (uint32_t i = 0; i < kRowThreads; ++i) total += ctl.exchange[groups & 1u][my_row][i];
-      float *stats = args.statistics + (slot * kRealRows + my_row) * 2;
+      float *stats = args.statistics + (slot * kSlotRows + slot_row) * 2;
       stats[0] = failed ? -INFINITY : row_max * kLn2;
       stats[1] = failed ? 0.0f : total;
     }
@@ -921,16 +930,23 @@ extern "C" int rk_attention_prefill_split_tc(const void *window, uint32_t format
   VerifyArgs args{static_cast<const uint16_t *>(queries), partials, statistics, nullptr, nullptr, nullptr, params->kv, w->base, status, table, *params};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const uint32_t tiles = (params->rows + RK_PREFILL_TILE_ROWS - 1) / RK_PREFILL_TILE_ROWS;
-  const dim3 grid(kHeads, params->split_count, tiles);
+  const bool pairs = params->split_count == 1 && tiles > 1; // two tiles per CTA fill 96 of the 128 tensor-core rows
+  const dim3 grid(kHeads, params->split_count, pairs ? (tiles + 1) / 2 : tiles);
   auto launch = [&](auto kernel, size_t shared_bytes, const CUtensorMap &map) -> int {
     if (int st = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(shared_bytes)), "window kernel shared memory")) return st;
     kernel<<<grid, kThreads, shared_bytes, s>>>(map, args);
     return cuda_status(cudaGetLastError(), "prefill window kernel launch");
   };
+  auto launch_format = [&](auto format_tag, const CUtensorMap &map) -> int {
+    constexpr uint32_t F = decltype(format_tag)::value;
+    constexpr size_t shared_bytes = 1024 + tile_bytes<F>() + sizeof(Control);
+    return pairs ? launch(window_attention_kernel<F, 16, false, true>, shared_bytes, map)
+                 : launch(window_attention_kernel<F, 8, false, true>, shared_bytes, map);
+  };
   switch (format) {
-  case RK_FORMAT_INT4: return launch(window_attention_kernel<RK_FORMAT_INT4, 8, false, true>, 1024 + tile_bytes<RK_FORMAT_INT4>() + sizeof(Control), w->int4_head_map);
-  case RK_FORMAT_INT8: return launch(window_attention_kernel<RK_FORMAT_INT8, 8, false, true>, 1024 + tile_bytes<RK_FORMAT_INT8>() + sizeof(Control), w->byte_head_map);
-  case RK_FORMAT_FP8E4M3: return launch(window_attention_kernel<RK_FORMAT_FP8E4M3, 8, false, true>, 1024 + tile_bytes<RK_FORMAT_FP8E4M3>() + sizeof(Control), w->byte_head_map);
-  default: return launch(window_attention_kernel<RK_FORMAT_BF16, 8, false, true>, 1024 + tile_bytes<RK_FORMAT_BF16>() + sizeof(Control), w->int4_map);
+  case RK_FORMAT_INT4: return launch_format(std::integral_constant<uint32_t, RK_FORMAT_INT4>{}, w->int4_head_map);
+  case RK_FORMAT_INT8: return launch_format(std::integral_constant<uint32_t, RK_FORMAT_INT8>{}, w->byte_head_map);
+  case RK_FORMAT_FP8E4M3: return launch_format(std::integral_constant<uint32_t, RK_FORMAT_FP8E4M3>{}, w->byte_head_map);
+  default: return launch_format(std::integral_constant<uint32_t, RK_FORMAT_BF16>{}, w->int4_map);
   }
 }
