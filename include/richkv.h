@@ -65,6 +65,15 @@ int rk_attention_verify_reduce(uint32_t kv_heads, uint32_t query_heads, uint32_t
                                uint32_t row_capacity, const float *partials, const float *statistics,
                                void *output, float *output_f32, const rk_verify_params *lane_params,
                                void *stream);
+/* verify_attention_reduce_gate / verify_attention_reduce_gather (decode/paged_attention.metal:273-413), encoded by
+ * PagedAttention::addVerify when its gate buffers are bound (PagedAttention.hpp:299-311): the merge that also writes
+ * the out-projection's input `hidden` [lane][row][query head][D] bf16 = merged row x sigmoid(gate), the gate read from
+ * `packed_qkv` [lane][row][(q | gate) x query heads, k x KV heads, v x KV heads]; with `packed_qkv` null the merged row
+ * itself (gather form; `output` may then be null too). Rows per lane = row_capacity. */
+int rk_attention_verify_reduce_gate(uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim, uint32_t lanes,
+                                    uint32_t row_capacity, const float *partials, const float *statistics,
+                                    void *output, const void *packed_qkv, void *hidden,
+                                    const rk_verify_params *lane_params, void *stream);
 /* prefill_attention_*_split and prefill_attention_reduce (prefill/paged_attention.metal:7-206), encoded by
  * PagedAttention::addPrefill (PagedAttention.cpp:443-465). `params` is a HOST pointer. */
 int rk_attention_prefill_split(uint32_t format, uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim,

@@ -223,8 +223,10 @@ prefill_split_kernel(const uint16_t *__restrict__ queries, float *__restrict__ p
 
 // One fused row: merge the written splits in split order and store bf16
 // (paged_attention_tile.h:362-417). Block = D threads.
+// Returns the bf16 bits of the element this thread reduced (0 for rows past the live rows); a null
+// `tile_output` skips the store of the attention rows.
 template <uint32_t HeadDim>
-__device__ void reduce_row(const float *__restrict__ partials, const float *__restrict__ statistics,
+__device__ uint16_t reduce_row(const float *__restrict__ partials, const float *__restrict__ statistics,
                            uint16_t *__restrict__ tile_output, float *__restrict__ tile_output_f32,
                            uint32_t committed, uint32_t active_rows, uint32_t group, uint32_t M,
                            uint32_t splits, uint64_t head_slot, uint32_t fused_row) {
@@ -233,9 +235,9 @@ __device__ void reduce_row(const float *__restrict__ partials, const float *__re
   __shared__ float warp_values[D / 32];
   const uint32_t tid = threadIdx.x, lane = tid % 32, warp = tid / 32;
   if (fused_row / group >= active_rows) { // rows past the live rows are zeros
-    tile_output[fused_row * D + tid] = 0;
+    if (tile_output) tile_output[fused_row * D + tid] = 0;
     if (tile_output_f32) tile_output_f32[fused_row * D + tid] = 0.0f;
-    return;
+    return 0;
   }
   const uint32_t pages = rk_pages_for(committed + active_rows);
   const uint32_t per_split = rk_pages_per_split(pages, splits);
@@ -258,25 +260,46 @@ __device__ void reduce_row(const float *__restrict__ partials, const float *__re
     denominator += weight * statistics[((head_slot + s) * M + fused_row) * 2 + 1];
   }
   const float value = denominator > 0.0f ? numerator / denominator : 0.0f;
-  tile_output[fused_row * D + tid] = float_to_bf16_bits(value);
+  const uint16_t bits = float_to_bf16_bits(value);
+  if (tile_output) tile_output[fused_row * D + tid] = bits;
   if (tile_output_f32) tile_output_f32[fused_row * D + tid] = value;
+  return bits;
 }
+
+// The logistic sigmoid of the reference's kernels: 1 / (1 + 2^(-log2(e) x)) (kernels/common/activation.h:14-16).
+__device__ __forceinline__ float gate_sigmoid(float x) { return 1.0f / (1.0f + exp2f(-1.44269504089f * x)); }
 
 // grid (kv_heads, M, lanes), D threads.
 template <uint32_t KvHeads, uint32_t HeadDim>
 __global__ void __launch_bounds__(HeadDim)
 verify_reduce_kernel(const float *__restrict__ partials, const float *__restrict__ statistics,
                      uint16_t *__restrict__ output, float *__restrict__ output_f32,
-                     const rk_verify_params *__restrict__ lane_params, uint32_t group) {
+                     const rk_verify_params *__restrict__ lane_params, uint32_t group,
+                     const uint16_t *__restrict__ packed_qkv, uint16_t *__restrict__ hidden) {
   const uint32_t kv_head = blockIdx.x, fused_row = blockIdx.y, lane_index = blockIdx.z;
   rk_verify_params p = lane_params[lane_index];
   p.kv.extent_pages = 1; // placement plays no part in the merge
   const uint32_t M = p.row_capacity * group;
   if (!rk_verify_contract_valid(&p) || fused_row >= M) return;
   const uint64_t tile = (uint64_t(lane_index) * KvHeads + kv_head) * (uint64_t(RK_VERIFY_CHUNK_STRIDE) * group * HeadDim);
-  reduce_row<HeadDim>(partials, statistics, output + tile, output_f32 ? output_f32 + tile : nullptr,
-                      p.committed_tokens, p.active_rows, group, M, p.split_count,
-                      (uint64_t(lane_index) * KvHeads + kv_head) * p.slot_splits, fused_row);
+  const uint16_t bits = reduce_row<HeadDim>(partials, statistics, output ? output + tile : nullptr, output_f32 ? output_f32 + tile : nullptr,
+                                            p.committed_tokens, p.active_rows, group, M, p.split_count,
+                                            (uint64_t(lane_index) * KvHeads + kv_head) * p.slot_splits, fused_row);
+  if (hidden) {
+    // The epilogue of the out-projection's input (decode/paged_attention.metal:273-413): the row leaves in the
+    // [lane][row][query head][dim] layout, scaled by the sigmoid of its gate where the packed QKV rows
+    // ([q | gate] per query head, then k and v per KV head) are given, copied otherwise.
+    const uint32_t query_heads = KvHeads * group, row = fused_row / group, query_head = kv_head * group + fused_row % group;
+    const uint64_t target = ((uint64_t(lane_index) * p.row_capacity + row) * query_heads + query_head) * HeadDim + threadIdx.x;
+    if (packed_qkv) {
+      const uint64_t packed_stride = 2ull * query_heads * HeadDim + 2ull * KvHeads * HeadDim;
+      const float gate = bf16_bits_to_float(packed_qkv[(uint64_t(lane_index) * p.row_capacity + row) * packed_stride +
+                                                       uint64_t(query_head) * 2 * HeadDim + HeadDim + threadIdx.x]);
+      hidden[target] = float_to_bf16_bits(bf16_bits_to_float(bits) * gate_sigmoid(gate));
+    } else {
+      hidden[target] = bits;
+    }
+  }
 }
 
 // grid (kv_heads, 8*group, tiles), D threads.
@@ -390,8 +413,30 @@ extern "C" int rk_attention_verify_reduce(uint32_t kv_heads, uint32_t query_head
   }
   const uint32_t group = query_heads / kv_heads;
   verify_reduce_kernel<4, 256><<<dim3(kv_heads, row_capacity * group, lanes), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      partials, statistics, static_cast<uint16_t *>(output), output_f32, lane_params, group);
+      partials, statistics, static_cast<uint16_t *>(output), output_f32, lane_params, group, nullptr, nullptr);
   return cuda_status(cudaGetLastError(), "verify reduce launch");
+}
+
+// verify_attention_reduce_gate / verify_attention_reduce_gather (decode/paged_attention.metal:273-413; encoded by
+// PagedAttention::addVerify when its gate buffers are bound, PagedAttention.hpp:299-311): the split merge that also
+// writes the out-projection's input `hidden` [lane][row][query head][D] bf16 — the merged row times the sigmoid of
+// its gate, read from `packed_qkv` [lane][row][ (q | gate) x query heads, k x KV heads, v x KV heads ], or the merged
+// row itself when `packed_qkv` is null. `output` (the attention staging rows) may be null in the gather form.
+extern "C" int rk_attention_verify_reduce_gate(uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim, uint32_t lanes,
+                                               uint32_t row_capacity, const float *partials, const float *statistics,
+                                               void *output, const void *packed_qkv, void *hidden,
+                                               const rk_verify_params *lane_params, void *stream) {
+  if (!supported_geometry(kv_heads, query_heads, head_dim)) return kUnsupported;
+  if (!lanes || !row_capacity || row_capacity > RK_TREE_NODES || !partials || !statistics || !hidden || !lane_params ||
+      (packed_qkv && !output)) {
+    set_error("rk_attention_verify_reduce_gate: invalid arguments");
+    return kInvalid;
+  }
+  const uint32_t group = query_heads / kv_heads;
+  verify_reduce_kernel<4, 256><<<dim3(kv_heads, row_capacity * group, lanes), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      partials, statistics, static_cast<uint16_t *>(output), nullptr, lane_params, group,
+      static_cast<const uint16_t *>(packed_qkv), static_cast<uint16_t *>(hidden));
+  return cuda_status(cudaGetLastError(), "verify reduce-gate launch");
 }
 
 extern "C" int rk_attention_prefill_split(uint32_t format, uint32_t kv_heads, uint32_t query_heads,

@@ -155,6 +155,17 @@ def attention_prefill(layout: Layout, query_heads: int, queries, output, partial
               "rk_attention_prefill_reduce")
 
 
+def attention_verify_reduce_gate(layout: Layout, query_heads: int, lanes: int, row_capacity: int, partials, statistics,
+                                 output, packed_qkv, hidden, params, stream=None) -> None:
+    """Merge + out-projection input: hidden [lane][row][query head][D] = merged row x sigmoid(gate of packed_qkv), or
+    the merged row itself when packed_qkv is None (rk_attention_verify_reduce_gate)."""
+    status = lib.load().rk_attention_verify_reduce_gate(
+        layout.kv_heads, query_heads, layout.head_dimension, lanes, row_capacity, partials.data_ptr(),
+        statistics.data_ptr(), output.data_ptr() if output is not None else None,
+        packed_qkv.data_ptr() if packed_qkv is not None else None, hidden.data_ptr(), params.data_ptr(), _stream(stream))
+    lib.check(status, "rk_attention_verify_reduce_gate")
+
+
 def attention_prefill_reduce(layout: Layout, query_heads: int, partials, statistics, output, params: lib.PrefillParams,
                              output_f32=None, stream=None) -> None:
     lib.check(lib.load().rk_attention_prefill_reduce(layout.kv_heads, query_heads, layout.head_dimension,

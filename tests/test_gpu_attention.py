@@ -123,3 +123,38 @@ def test_prefill_attention(fmt, rows, committed, tensor_core):
             got = got32[head, start:start + 8].reshape(-1, 256)[: active * 6]
             assert_attention_close(got, want[: active * 6], None, f"tile {tile} head {head}")
     s.close()
+
+
+@pytest.mark.parametrize("rows,capacity", [(8, 8), (5, 8), (1, 1), (16, 16)])
+def test_reduce_gate_and_gather_epilogue(rows, capacity):
+    """The merge that also writes the out-projection's input (decode/paged_attention.metal:273-413): the gather
+    form is the merged bf16 row re-laid out, bit for bit; the gate form multiplies it by sigmoid(gate) in fp32."""
+    from kvcase import bf16_to_f32, f32_to_bf16
+    s, q = prepared(INT4, [100, 3000, 40], rows)
+    lanes = s.lanes
+    from gpuhelp import verify_params
+    lane_params, slot = verify_params(s, rows, capacity)
+    d_params = struct_to_device(lane_params)
+    got16, _, (partials, stats) = run_verify_attention_gpu(s, q, rows, capacity)
+    rng = np.random.default_rng(4)
+    stride = 2 * 24 * 256 + 2 * 4 * 256
+    packed = f32_to_bf16((rng.standard_normal((lanes, capacity, stride)) * 3).astype(np.float32))
+    hidden = torch.zeros((lanes, capacity, 24, 256), dtype=torch.int16, device="cuda")
+    out = torch.zeros((lanes, 4, 32, 6, 256), dtype=torch.int16, device="cuda")
+    ops.attention_verify_reduce_gate(s.layout, 24, lanes, capacity, partials, stats, out, dev(packed), hidden, d_params)
+    torch.cuda.synchronize()
+    assert np.array_equal(host_u16(out), got16)  # the attention rows are the plain merge's
+    merged = got16[:, :, :capacity].transpose(0, 2, 1, 3, 4).reshape(lanes, capacity, 24, 256)  # [lane][row][kv*6+g][D]
+    gate = bf16_to_f32(packed[:, :, : 2 * 24 * 256].reshape(lanes, capacity, 24, 2, 256)[:, :, :, 1, :])
+    sigmoid = (np.float32(1.0) / (np.float32(1.0) + np.exp2(np.float32(-1.44269504089) * gate))).astype(np.float32)
+    want = f32_to_bf16((bf16_to_f32(merged) * sigmoid).astype(np.float32))
+    got = host_u16(hidden)
+    mismatch = got != want
+    assert mismatch.mean() < 2e-3  # exp2 of the two libraries may differ in the last place before the bf16 rounding
+    close = np.abs(bf16_to_f32(got) - bf16_to_f32(want)) <= np.abs(bf16_to_f32(want)) * 2.0 ** -7 + 1e-30
+    assert close.all()
+    hidden.zero_()
+    ops.attention_verify_reduce_gate(s.layout, 24, lanes, capacity, partials, stats, None, None, hidden, d_params)
+    torch.cuda.synchronize()
+    assert np.array_equal(host_u16(hidden), merged)
+    s.close()
