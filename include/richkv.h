@@ -83,6 +83,26 @@ int rk_attention_prefill_reduce(uint32_t kv_heads, uint32_t query_heads, uint32_
                                 const float *statistics, void *output, float *output_f32,
                                 const rk_prefill_params *params, void *stream);
 
+/* ---- the step before the path: packed projection rows -> stagings (and pages) ---------------------- */
+/* verify_attention_qkv / verify_attention_qkv_f32 (runtime/metal/kernels/decode/attention_qkv.metal:33-60 over
+ * kernels/common/attention_qkv_prepare.h:13-83; encoded by the attention operator before PagedAttention::addVerify):
+ * per (lane, row) the packed row [(q | gate) x query heads, k x KV heads, v x KV heads] bf16 becomes
+ * queries [lane][kv][32][group][D], keys [lane][kv][32][D], values [lane][kv][D][32]: per-head RMS norm (eps) times
+ * the norm weight (bf16, or fp32 with norm_f32), rounded to bf16, rotary on the first 2 x 32 dims with
+ * rope_cos / rope_sin [lane][row][32] fp32; values are copied. rows <= 16, the same for every lane. */
+int rk_qkv_prepare(uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim, uint32_t lanes, uint32_t rows,
+                   const void *packed_qkv, const void *q_norm, const void *k_norm, int norm_f32,
+                   const float *rope_cos, const float *rope_sin, float eps, void *queries, void *chunk_keys,
+                   void *chunk_values, void *stream);
+/* The same with the page store merged in (the reference lists this merge as open work, TODO.md:14): the key and
+ * value rows are quantised into their page slots instead of being staged. Pages equal rk_qkv_prepare followed by
+ * rk_store_verify bit for bit; `lane_params` as for rk_store_verify (chunk_tokens = rows). */
+int rk_qkv_prepare_store(uint32_t format, uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim, uint32_t lanes,
+                         uint32_t rows, const void *packed_qkv, const void *q_norm, const void *k_norm, int norm_f32,
+                         const float *rope_cos, const float *rope_sin, float eps, void *queries,
+                         const rk_page_entry *const *tables, const rk_chunk_params *lane_params, rk_kv_layer layer,
+                         void *stream);
+
 /* ---- streaming decode attention (one query row per lane) ---------------------------------------- */
 /* The reference has no single-query kernel: a plain decode is its tile with one active row
  * (runtime/metal/kernels/common/paged_attention_tile.h:108-110; tested as history 0, rows 1 in

@@ -449,6 +449,68 @@ void rko_copy_page(uint32_t format, uint32_t layers, uint32_t kv_heads, uint32_t
     }
 }
 
+// No fused multiply-add anywhere in this function: every product and sum is rounded on its own, as the CUDA
+// kernel does with its _rn intrinsics.
+__attribute__((optimize("fp-contract=off")))
+int rko_qkv_prepare(uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim, uint32_t lanes, uint32_t rows,
+                    const uint16_t *packed_qkv, const void *q_norm, const void *k_norm, int norm_f32,
+                    const float *rope_cos, const float *rope_sin, float eps, uint16_t *queries, uint16_t *chunk_keys,
+                    uint16_t *chunk_values) {
+  constexpr uint32_t kRotaryPairs = 32, kStride = RK_VERIFY_CHUNK_STRIDE;
+  if (!kv_heads || query_heads % kv_heads || head_dim % 32 || head_dim < 2 * kRotaryPairs || !rows || rows > kStride) return -1;
+  const uint32_t D = head_dim, group = query_heads / kv_heads;
+  const uint64_t packed_stride = uint64_t(query_heads) * 2 * D + 2ull * kv_heads * D;
+  auto weight = [&](const void *w, uint32_t d) {
+    return norm_f32 ? static_cast<const float *>(w)[d] : rko_bf16_to_f32(static_cast<const uint16_t *>(w)[d]);
+  };
+  std::vector<float> x(D), sq(D);
+  std::vector<uint16_t> normalized(D);
+  for (uint32_t lane = 0; lane < lanes; ++lane)
+    for (uint32_t row = 0; row < rows; ++row) {
+      const uint16_t *source_row = packed_qkv + (uint64_t(lane) * rows + row) * packed_stride;
+      const float *cosine = rope_cos + (uint64_t(lane) * rows + row) * kRotaryPairs;
+      const float *sine = rope_sin + (uint64_t(lane) * rows + row) * kRotaryPairs;
+      for (uint32_t task = 0; task < query_heads + kv_heads; ++task) {
+        const bool query = task < query_heads;
+        const uint32_t head = query ? task : task - query_heads;
+        const uint16_t *source = query ? source_row + uint64_t(head) * 2 * D : source_row + uint64_t(query_heads) * 2 * D + uint64_t(head) * D;
+        for (uint32_t d = 0; d < D; ++d) { x[d] = rko_bf16_to_f32(source[d]); sq[d] = x[d] * x[d]; }
+        float total = 0.0f;
+        for (uint32_t base = 0; base < D; base += 32) { // per 32 dims: xor butterfly, every lane ends with the same sum
+          float v[32];
+          for (uint32_t i = 0; i < 32; ++i) v[i] = sq[base + i];
+          for (uint32_t offset = 16; offset; offset >>= 1) {
+            float next[32];
+            for (uint32_t i = 0; i < 32; ++i) next[i] = v[i] + v[i ^ offset];
+            for (uint32_t i = 0; i < 32; ++i) v[i] = next[i];
+          }
+          total += v[0];
+        }
+        const float inverse = 1.0f / std::sqrt(total / float(D) + eps);
+        const void *w = query ? q_norm : k_norm;
+        for (uint32_t d = 0; d < D; ++d) normalized[d] = rko_f32_to_bf16((x[d] * inverse) * weight(w, d));
+        uint16_t *destination;
+        if (query) {
+          const uint32_t kv = head / group, local = head % group;
+          destination = queries + (((uint64_t(lane) * kv_heads + kv) * kStride + row) * group + local) * D;
+        } else {
+          destination = chunk_keys + ((uint64_t(lane) * kv_heads + head) * kStride + row) * D;
+          const uint16_t *value_source = source + uint64_t(kv_heads) * D; // the head's v row follows all k rows
+          for (uint32_t d = 0; d < D; ++d)
+            chunk_values[((uint64_t(lane) * kv_heads + head) * D + d) * kStride + row] = value_source[d];
+        }
+        for (uint32_t i = 0; i < kRotaryPairs; ++i) {
+          const float first = rko_bf16_to_f32(normalized[i]), second = rko_bf16_to_f32(normalized[i + kRotaryPairs]);
+          const float a = first * cosine[i], b = second * sine[i], c = second * cosine[i], e = first * sine[i];
+          destination[i] = rko_f32_to_bf16(a - b);
+          destination[i + kRotaryPairs] = rko_f32_to_bf16(c + e);
+        }
+        for (uint32_t d = 2 * kRotaryPairs; d < D; ++d) destination[d] = normalized[d];
+      }
+    }
+  return 0;
+}
+
 int rko_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -88,6 +88,17 @@ int rko_tree_compact(uint32_t format, uint32_t kv_heads, uint32_t head_dim,
 void rko_copy_page(uint32_t format, uint32_t layers, uint32_t kv_heads, uint32_t head_dim,
                    uint32_t extent_pages, rk_page_entry from, rk_page_entry to);
 
+/* The step before the path (kernels/common/attention_qkv_prepare.h:13-83, kernels/decode/attention_qkv.metal:6-60):
+ * per (lane, row) the packed projection row [(q | gate) x query heads, k x KV heads, v x KV heads] becomes the stagings
+ * the store and the attention read: per-head RMS norm (sum of squares reduced per 32 dims by an xor butterfly
+ * 16,8,4,2,1 — the reference's simd_sum leaves the order open, this fixes one — then the partials in order,
+ * 1/sqrt(mean + eps)), times the norm weight, rounded to bf16, rotary on the first 2 x 32 dims (separately rounded
+ * products), queries [lane][kv][32][group][D], keys [lane][kv][32][D], values [lane][kv][D][32] (a copy of the bits).
+ * `norm_f32` selects fp32 norm weights (the _f32 pipelines). */
+int rko_qkv_prepare(uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim, uint32_t lanes, uint32_t rows,
+                    const uint16_t *packed_qkv, const void *q_norm, const void *k_norm, int norm_f32,
+                    const float *rope_cos, const float *rope_sin, float eps, uint16_t *queries, uint16_t *chunk_keys,
+                    uint16_t *chunk_values);
 int rko_threads(void);
 
 #ifdef __cplusplus

@@ -18,24 +18,6 @@
 namespace rk {
 namespace {
 
-template <uint32_t Format> struct Quantizer;
-template <> struct Quantizer<RK_FORMAT_INT8> { static constexpr float kRange = 127.0f; };
-template <> struct Quantizer<RK_FORMAT_INT4> { static constexpr float kRange = 7.0f; };
-template <> struct Quantizer<RK_FORMAT_FP8E4M3> { static constexpr float kRange = 448.0f; };
-
-// The stored code of one element: an int8/int4 two's-complement code or an
-// e4m3 byte. (x*range)/amax is two IEEE round-to-nearest operations; no
-// reciprocal and no fused multiply-add may replace them.
-template <uint32_t Format> __device__ __forceinline__ uint32_t encode(float value, float amax) {
-  if (amax == 0.0f) return 0u;
-  const float scaled = __fdiv_rn(__fmul_rn(value, Quantizer<Format>::kRange), amax);
-  if (Format == RK_FORMAT_FP8E4M3)
-    return uint32_t(__nv_cvt_float_to_fp8(scaled, __NV_SATFINITE, __NV_E4M3));
-  const int limit = int(Quantizer<Format>::kRange);
-  const int q = max(-limit, min(limit, __float2int_rn(scaled)));
-  return uint32_t(q) & (Format == RK_FORMAT_INT4 ? 0xFu : 0xFFu);
-}
-
 constexpr uint32_t kTileRows = 32;
 constexpr uint32_t kThreads = 256;
 

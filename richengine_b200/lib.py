@@ -61,6 +61,8 @@ SIGNATURES = {
     "rk_attention_verify_split": (i32, [u32, u32, u32, u32, u32, u32, u32, vp, vp, vp, vp, vp, vp, KvLayer, vp]),
     "rk_attention_verify_split_tc": (i32, [vp, u32, u32, u32, u32, u32, u32, u32, vp, vp, vp, vp, vp, vp, KvLayer, vp, vp]),
     "rk_attention_verify_reduce": (i32, [u32, u32, u32, u32, u32, vp, vp, vp, vp, vp, vp]),
+    "rk_qkv_prepare": (i32, [u32, u32, u32, u32, u32, vp, vp, vp, i32, vp, vp, C.c_float, vp, vp, vp, vp]),
+    "rk_qkv_prepare_store": (i32, [u32, u32, u32, u32, u32, u32, vp, vp, vp, i32, vp, vp, C.c_float, vp, vp, vp, KvLayer, vp]),
     "rk_attention_verify_reduce_gate": (i32, [u32, u32, u32, u32, u32, vp, vp, vp, vp, vp, vp, vp]),
     "rk_attention_prefill_split": (i32, [u32, u32, u32, u32, vp, vp, vp, vp, C.POINTER(PrefillParams), vp]),
     "rk_attention_prefill_split_tc": (i32, [vp, u32, u32, u32, u32, vp, vp, vp, vp, C.POINTER(PrefillParams), vp, vp]),

@@ -155,6 +155,27 @@ def attention_prefill(layout: Layout, query_heads: int, queries, output, partial
               "rk_attention_prefill_reduce")
 
 
+def qkv_prepare(layout: Layout, query_heads: int, lanes: int, rows: int, packed_qkv, q_norm, k_norm, rope_cos, rope_sin,
+                queries, chunk_keys, chunk_values, eps: float = 1e-6, stream=None) -> None:
+    """Packed projection rows -> the stagings of the store and the attention (rk_qkv_prepare)."""
+    status = lib.load().rk_qkv_prepare(layout.kv_heads, query_heads, layout.head_dimension, lanes, rows,
+                                       packed_qkv.data_ptr(), q_norm.data_ptr(), k_norm.data_ptr(),
+                                       int(q_norm.dtype == torch.float32), rope_cos.data_ptr(), rope_sin.data_ptr(), eps,
+                                       queries.data_ptr(), chunk_keys.data_ptr(), chunk_values.data_ptr(), _stream(stream))
+    lib.check(status, "rk_qkv_prepare")
+
+
+def qkv_prepare_store(layout: Layout, query_heads: int, lanes: int, rows: int, packed_qkv, q_norm, k_norm, rope_cos,
+                      rope_sin, queries, table_pointers, params, layer: lib.KvLayer, eps: float = 1e-6, stream=None) -> None:
+    """The same with the page store merged in: K/V rows go straight into their page slots (rk_qkv_prepare_store)."""
+    status = lib.load().rk_qkv_prepare_store(layout.format, layout.kv_heads, query_heads, layout.head_dimension, lanes, rows,
+                                             packed_qkv.data_ptr(), q_norm.data_ptr(), k_norm.data_ptr(),
+                                             int(q_norm.dtype == torch.float32), rope_cos.data_ptr(), rope_sin.data_ptr(),
+                                             eps, queries.data_ptr(), table_pointers.data_ptr(), params.data_ptr(), layer,
+                                             _stream(stream))
+    lib.check(status, "rk_qkv_prepare_store")
+
+
 def attention_verify_reduce_gate(layout: Layout, query_heads: int, lanes: int, row_capacity: int, partials, statistics,
                                  output, packed_qkv, hidden, params, stream=None) -> None:
     """Merge + out-projection input: hidden [lane][row][query head][D] = merged row x sigmoid(gate of packed_qkv), or
