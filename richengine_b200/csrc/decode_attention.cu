@@ -260,6 +260,12 @@ __device__ __forceinline__ void page_softmax(const float (&sacc)[2][2][4], const
   }
 }
 
+// Programmatic dependent launch: a kernel launched with the stream-serialization attribute may be scheduled while
+// its predecessor drains; it must not touch memory before the predecessor's writes are visible (wait), and it lets
+// its own successor be scheduled early (launch_dependents). Both are no-ops in an ordinary launch.
+__device__ __forceinline__ void dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void dependents_may_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void group_barrier(uint32_t id, uint32_t threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -273,6 +279,8 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
   const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const uint32_t lanes = args.lanes, cta = blockIdx.x;
   uint32_t *error_word = args.descriptors + 2 * lanes;
+  dependents_may_launch(); // the merge kernel's blocks may take their places; they wait for this grid to finish
+  dependency_wait();       // pages, queries and parameters may come from the kernel before this one
 
   // ---- partition: pages per lane -> prefix; segments per lane -> prefix -----------------
   for (uint32_t i = tid; i < lanes; i += kThreads) {
@@ -577,6 +585,7 @@ decode_reduce_kernel(const float *__restrict__ partials, const float *__restrict
   __shared__ float weights[kMaxSlots];
   __shared__ float denominator_shared, maximum_shared;
   const uint32_t query_head = blockIdx.x, head = blockIdx.y, l = blockIdx.z, tid = threadIdx.x;
+  dependency_wait(); // partials, statistics and descriptors come from the decode kernel launched just before
   rk_verify_params p = lane_params[l];
   p.kv = layer;
   if (!rk_verify_contract_valid(&p) || p.active_rows != 1 || p.row_capacity != 1) return;
@@ -671,6 +680,25 @@ int configure_decode_kernel() {
 
 using namespace rk;
 
+// The merge follows its decode kernel as a programmatic dependent launch: its blocks are placed while the decode
+// grid drains and start the moment that grid's writes are visible.
+static int launch_merge(uint32_t lanes, cudaStream_t stream, const float *partials, const float *statistics,
+                        const uint32_t *descriptors, uint16_t *output, float *output_f32,
+                        const rk_verify_params *lane_params, rk_kv_layer layer, float *triples) {
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(kGroup, kKvHeads, lanes);
+  config.blockDim = dim3(256);
+  config.stream = stream;
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  return cuda_status(cudaLaunchKernelEx(&config, decode_reduce_kernel, partials, statistics, descriptors, output, output_f32,
+                                        lane_params, layer, triples),
+                     "decode reduce launch");
+}
+
 extern "C" {
 
 // Sizes the scratch of a decode step: `ctas` = 0 takes one CTA per SM of the current device.
@@ -734,8 +762,7 @@ int rk_attention_decode(const void *window, const rk_decode_plan *plan, uint32_t
   if (int st = cuda_status(cudaMemsetAsync(descriptors + 2 * plan->lanes, 0, sizeof(uint32_t), s), "decode status clear")) return st;
   decode_int4_kernel<<<plan->ctas, kThreads, shared_bytes, s>>>(w->int4_map, args);
   if (int st = cuda_status(cudaGetLastError(), "decode launch")) return st;
-  decode_reduce_kernel<<<dim3(kGroup, kKvHeads, plan->lanes), 256, 0, s>>>(partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer, nullptr);
-  return cuda_status(cudaGetLastError(), "decode reduce launch");
+  return launch_merge(plan->lanes, s, partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer, nullptr);
 }
 
 // One rank's part of a sequence-split decode: attention over the pages this rank holds, left as
