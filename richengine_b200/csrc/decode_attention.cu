@@ -574,6 +574,342 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
   }
 }
 
+// ---- one-byte formats (int8, fp8 e4m3): the same streaming kernel with 8 KiB slabs and three stages -----------------
+constexpr uint32_t kByteStages = 3;
+constexpr uint32_t kByteSlabBytes = 8192;                          // one head's K (or V) of a page
+constexpr uint32_t kByteTensorBytes = kKvHeads * kByteSlabBytes;   // all heads' K (or V) of a page: two 128-row TMA boxes
+constexpr uint32_t kByteStageBytes = 2 * kByteTensorBytes + 2 * kScaleBytes;
+static_assert(kByteStageBytes % 1024 == 0, "stages keep the 1 KiB swizzle alignment");
+
+// Four key codes of one token row (dims d..d+3) -> the fragment halves (d, d+1) and (d+2, d+3).
+// int8: u = code + 128 as fp16 bits, u * 2^-24 (exact subnormals; the +128 leaves through sum(q)); fp8: cvt, exact.
+template <bool kFloat8> __device__ __forceinline__ void key_pairs(uint32_t word, uint32_t &first, uint32_t &second) {
+  if (kFloat8) {
+    asm("{\n.reg .b16 lo, hi;\nmov.b32 {lo, hi}, %2;\ncvt.rn.f16x2.e4m3x2 %0, lo;\ncvt.rn.f16x2.e4m3x2 %1, hi;\n}" : "=r"(first), "=r"(second) : "r"(word));
+  } else {
+    const uint32_t flipped = word ^ 0x80808080u;
+    first = __byte_perm(flipped, 0, 0x4140);
+    second = __byte_perm(flipped, 0, 0x4342);
+  }
+}
+// Two value codes of one dim (bytes c0 and c0 + 2 of a word of four tokens) -> one fragment register, exact:
+// int8 through 1024 + u minus 1152, fp8 through cvt.
+template <bool kFloat8> __device__ __forceinline__ uint32_t value_pair(uint32_t word, uint32_t selector) {
+  if (kFloat8) {
+    uint32_t result;
+    const uint32_t gathered = __byte_perm(word, 0, selector);
+    asm("{\n.reg .b16 lo, hi;\nmov.b32 {lo, hi}, %1;\ncvt.rn.f16x2.e4m3x2 %0, lo;\n}" : "=r"(result) : "r"(gathered));
+    return result;
+  }
+  return sub_f16x2(__byte_perm(word ^ 0x80808080u, 0x64646464u, selector), 0x64806480u);
+}
+
+template <bool kFloat8>
+__global__ void __launch_bounds__(kThreads, 1)
+decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs args) {
+  extern __shared__ uint8_t dynamic_shared[];
+  // Stages need 1024-byte alignment for the 128-byte swizzle pattern.
+  const uint32_t ring = (smem_address(dynamic_shared) + 1023u) & ~1023u;
+  Shared &sh = *reinterpret_cast<Shared *>(dynamic_shared + (ring - smem_address(dynamic_shared)) + kByteStages * kByteStageBytes);
+  const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const uint32_t lanes = args.lanes, cta = blockIdx.x;
+  uint32_t *error_word = args.descriptors + 2 * lanes;
+  dependents_may_launch(); // the merge kernel's blocks may take their places; they wait for this grid to finish
+  dependency_wait();       // pages, queries and parameters may come from the kernel before this one
+
+  // ---- partition: pages per lane -> prefix; segments per lane -> prefix -----------------
+  for (uint32_t i = tid; i < lanes; i += kThreads) {
+    rk_verify_params p = args.lane_params[i];
+    p.kv = args.layer;
+    const bool valid = rk_verify_contract_valid(&p) && p.active_rows == 1 && p.row_capacity == 1;
+    sh.lane_start[i] = valid ? rk_pages_for(p.committed_tokens + 1) : 0;
+  }
+  if (tid == 0) sh.error = 0;
+  __syncthreads();
+  exclusive_scan(sh.lane_start, lanes, sh.scan);
+  const uint64_t total_pages = sh.lane_start[lanes];
+  // Never more ranges than pages, so every range a lane spans is non-empty.
+  const uint32_t ctas = uint32_t(min(uint64_t(gridDim.x), total_pages));
+  if (cta >= ctas) return;
+  for (uint32_t i = tid; i < lanes; i += kThreads) {
+    const uint32_t begin = sh.lane_start[i], end = sh.lane_start[i + 1];
+    sh.segment_base[i] = end > begin ? cta_of(end - 1, total_pages, ctas) - cta_of(begin, total_pages, ctas) + 1 : 0;
+  }
+  __syncthreads();
+  exclusive_scan(sh.segment_base, lanes, sh.scan);
+  if (cta == 0)
+    for (uint32_t i = tid; i < lanes; i += kThreads) {
+      args.descriptors[2 * i] = sh.segment_base[i];
+      args.descriptors[2 * i + 1] = sh.segment_base[i + 1] - sh.segment_base[i];
+    }
+  const uint32_t range_begin = uint32_t(uint64_t(cta) * total_pages / ctas);
+  const uint32_t range_end = uint32_t(uint64_t(cta + 1) * total_pages / ctas);
+  if (tid == 0) {
+    for (uint32_t s = 0; s < kByteStages; ++s) {
+      barrier_init(smem_address(&sh.full[s]), 1);
+      barrier_init(smem_address(&sh.empty[s]), kKvHeads); // one warp per head releases a page
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (range_begin >= range_end) return;
+  // first lane whose pages reach into this range
+  uint32_t first_lane;
+  {
+    uint32_t lo = 0, hi = lanes; // largest i with lane_start[i] <= range_begin
+    while (hi - lo > 1) {
+      const uint32_t mid = (lo + hi) / 2;
+      if (sh.lane_start[mid] <= range_begin) lo = mid; else hi = mid;
+    }
+    first_lane = lo;
+  }
+
+  if (warp == kConsumerWarps) {
+    // ================= producer: one thread streams whole pages =============================
+    if (lane != 0) return;
+    uint32_t unit = 0; // pages issued by this CTA
+    bool ok = true;
+    for (uint32_t l = first_lane; ok && l < lanes && sh.lane_start[l] < range_end; ++l) {
+      const uint32_t lane_begin = sh.lane_start[l], lane_end = sh.lane_start[l + 1];
+      const uint32_t pa = max(range_begin, lane_begin) - lane_begin;
+      const uint32_t pb = min(range_end, lane_end) - lane_begin;
+      if (pb <= pa || lane_end <= range_begin) continue;
+      const rk_page_entry *table = args.tables[l];
+      rk_page_entry next_entry = table[pa];
+      for (uint32_t page = pa; ok && page < pb; ++page, ++unit) {
+        const rk_page_entry entry = next_entry;
+        if (page + 1 < pb) next_entry = table[page + 1]; // in flight while this page's copies are issued
+        const uint32_t index = rk_entry_index(entry);
+        const uint64_t region = rk_entry_extent(entry) + args.layer.offset;
+        const uint64_t pages = args.layer.extent_pages;
+        const uint64_t keys = region + uint64_t(index) * kByteTensorBytes;
+        const uint64_t key_scales = region + pages * kByteTensorBytes + uint64_t(index) * kScaleBytes;
+        const uint64_t values = region + pages * (uint64_t(kByteTensorBytes) + kScaleBytes) + uint64_t(index) * kByteTensorBytes;
+        const uint64_t value_scales = region + pages * (2ull * kByteTensorBytes + kScaleBytes) + uint64_t(index) * kScaleBytes;
+        const uint32_t slot = unit % kByteStages, round = unit / kByteStages;
+        const uint32_t full = smem_address(&sh.full[slot]), stage = ring + slot * kByteStageBytes;
+        if (sh.error || !barrier_wait(smem_address(&sh.empty[slot]), (round & 1u) ^ 1u)) { ok = false; break; }
+        barrier_expect(full, kByteStageBytes);
+        const int32_t key_row = int32_t((keys - args.window_base) >> 7), value_row = int32_t((values - args.window_base) >> 7);
+        tma_load_rows(stage, &window_map, key_row, full);                                   // heads 0-1 (128 rows of 128 bytes)
+        tma_load_rows(stage + kByteTensorBytes / 2, &window_map, key_row + 128, full);      // heads 2-3
+        tma_load_rows(stage + kByteTensorBytes, &window_map, value_row, full);
+        tma_load_rows(stage + kByteTensorBytes + kByteTensorBytes / 2, &window_map, value_row + 128, full);
+        bulk_load(stage + 2 * kByteTensorBytes, reinterpret_cast<const void *>(key_scales), kScaleBytes, full);
+        bulk_load(stage + 2 * kByteTensorBytes + kScaleBytes, reinterpret_cast<const void *>(value_scales), kScaleBytes, full);
+      }
+    }
+    if (!ok) {
+      atomicExch(error_word, 1u);
+      sh.error = 1;
+      // Copies already issued must land before the block's shared memory goes.
+      const uint32_t armed = min(unit, kByteStages);
+      for (uint32_t back = 0; back < armed; ++back) {
+        const uint32_t u = unit - 1 - back;
+        barrier_wait(smem_address(&sh.full[u % kByteStages]), (u / kByteStages) & 1u);
+      }
+    }
+    return;
+  }
+
+  // ================= consumers: warp = (KV head, page residue) ===============================
+  const uint32_t head = warp & 3u, residue = warp >> 2;
+  const uint32_t g = lane >> 2, c = lane & 3u;
+  // MMA row g (and g+8) of a 16-token tile is token r3g (and 8 + r3g) of its 16: bits 0 and 1 of g swapped. A token
+  // row is two 128-byte swizzle rows here, so the two rows a shared-memory phase reads (g, g^1) must differ by 2.
+  const uint32_t r3g = (g & 4u) | ((g & 1u) << 1) | ((g >> 1) & 1u);
+  const uint32_t c0 = c & 1u, c1 = c >> 1;
+  // value bytes of this lane inside a 32-bit word of four tokens: bytes c0 and c0 + 2
+  const uint32_t value_selector = kFloat8 ? (c0 | ((c0 + 2) << 4) | 0x4400u) : (c0 | (4u << 4) | ((c0 + 2) << 8) | (4u << 12));
+  const uint32_t query_shared = smem_address(&sh.query[head][0][lane]);
+
+  uint32_t units_before = 0; // pages of this CTA in earlier segments
+  for (uint32_t l = first_lane; l < lanes && sh.lane_start[l] < range_end; ++l) {
+    const uint32_t lane_begin = sh.lane_start[l], lane_end = sh.lane_start[l + 1];
+    const uint32_t pa = max(range_begin, lane_begin) - lane_begin;
+    const uint32_t pb = min(range_end, lane_end) - lane_begin;
+    if (pb <= pa || lane_end <= range_begin) continue;
+    const rk_verify_params p = args.lane_params[l];
+    const uint32_t visible = p.committed_tokens + 1;
+    const uint32_t lane_pages = lane_end - lane_begin;
+
+    // ---- the head's query fragments (B operand of S^T = K.Q^T), shared by its three warps ----
+    group_barrier(1 + head, kPageWarps * 32); // every warp of the head is done with the previous lane
+    if (residue == 0) {
+      const uint16_t *q = args.queries + ((uint64_t(l) * kKvHeads + head) * RK_VERIFY_CHUNK_STRIDE) * kGroup * kHeadDim +
+                          uint64_t(g) * kHeadDim;
+      // k-step s = 4j + w covers, for lane column c, dims 16(c + 4j) + 4w .. +3: b0 = the first two, b1 = the last two
+      float raw[4][4][4];
+      float amax = 0.0f;
+#pragma unroll
+      for (uint32_t j = 0; j < 4; ++j) {
+        uint4 v[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+        if (g < kGroup) {
+          v[0] = __ldg(reinterpret_cast<const uint4 *>(q + 16 * (c + 4 * j)));
+          v[1] = __ldg(reinterpret_cast<const uint4 *>(q + 16 * (c + 4 * j) + 8));
+        }
+        const uint32_t words[8] = {v[0].x, v[0].y, v[0].z, v[0].w, v[1].x, v[1].y, v[1].z, v[1].w};
+#pragma unroll
+        for (uint32_t w = 0; w < 4; ++w)
+#pragma unroll
+          for (uint32_t i = 0; i < 2; ++i) {
+            raw[j][w][2 * i] = bf16_bits_to_float(words[2 * w + i] & 0xffffu);
+            raw[j][w][2 * i + 1] = bf16_bits_to_float(words[2 * w + i] >> 16);
+            amax = fmaxf(amax, fmaxf(fabsf(raw[j][w][2 * i]), fabsf(raw[j][w][2 * i + 1])));
+          }
+      }
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      // Power-of-two prescale keeps every query inside fp16's range (exact).
+      int exponent = 0;
+      if (amax >= 8192.0f) exponent = ilogbf(amax) - 12;
+      const float down = ldexpf(1.0f, -exponent);
+      float qsum = 0.0f;
+#pragma unroll
+      for (uint32_t j = 0; j < 4; ++j)
+#pragma unroll
+        for (uint32_t w = 0; w < 4; ++w) {
+          const __half2 first = __floats2half2_rn(raw[j][w][0] * down, raw[j][w][1] * down);
+          const __half2 second = __floats2half2_rn(raw[j][w][2] * down, raw[j][w][3] * down);
+          sh.query[head][4 * j + w][lane] = make_uint2(*reinterpret_cast<const uint32_t *>(&first), *reinterpret_cast<const uint32_t *>(&second));
+          qsum += __low2float(first) + __high2float(first) + __low2float(second) + __high2float(second);
+        }
+      qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
+      qsum += __shfl_xor_sync(0xffffffffu, qsum, 2);
+      // scores (log2 domain) = fma(acc, factor, offset) * key_scale
+      const float ss = rk_score_scale(p.score_scale, kHeadDim) * kLog2e;
+      if (c == 0) {
+        // int8 keys travel as u * 2^-24 with u = code + 128; fp8 keys as their value
+        sh.head_factor[head][g] = ldexpf(ss, (kFloat8 ? 0 : 24) + exponent);
+        sh.head_offset[head][g] = kFloat8 ? 0.0f : -128.0f * qsum * ldexpf(ss, exponent);
+      }
+    }
+    group_barrier(1 + head, kPageWarps * 32); // fragments visible to the head's warps
+    float hfac[2], negoff[2];
+#pragma unroll
+    for (uint32_t j = 0; j < 2; ++j) { // C fragment columns are query heads 2c, 2c+1 of the group
+      hfac[j] = sh.head_factor[head][2 * c + j];
+      negoff[j] = sh.head_offset[head][2 * c + j];
+    }
+
+    float m[2] = {-1.0e30f, -1.0e30f}, l_sum[2] = {0.0f, 0.0f};
+    float o[16][4];
+#pragma unroll
+    for (uint32_t t = 0; t < 16; ++t) { o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.0f; }
+
+    for (uint32_t page = pa + residue; page < pb && !sh.error; page += kPageWarps) {
+      const uint32_t unit = units_before + (page - pa);
+      const uint32_t slot = unit % kByteStages, round = unit / kByteStages;
+      if (!barrier_wait(smem_address(&sh.full[slot]), round & 1u)) {
+        atomicExch(error_word, 2u);
+        sh.error = 2;
+        break;
+      }
+      const uint32_t stage = ring + slot * kByteStageBytes;
+      const uint32_t keys = stage + head * kByteSlabBytes;
+      const uint32_t values = stage + kByteTensorBytes + head * kByteSlabBytes;
+      const uint32_t scales = stage + 2 * kByteTensorBytes + head * (kPageTokens * 4);
+      const uint32_t valid = page + 1 == lane_pages ? visible - page * kPageTokens : kPageTokens;
+
+      // ---- S^T = K.Q^T : two 16-token tiles, 16 k-steps each --------------------------
+      float sacc[2][2][4];
+#pragma unroll
+      for (uint32_t mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (uint32_t h = 0; h < 2; ++h) sacc[mt][h][0] = sacc[mt][h][1] = sacc[mt][h][2] = sacc[mt][h][3] = 0.0f;
+#pragma unroll
+      for (uint32_t j = 0; j < 4; ++j) { // 16-byte chunk c + 4j of each token row: 16 dims = four k-steps
+        const uint32_t half_row = j >> 1, chunk = c + 4 * (j & 1u);
+        uint4 kr[2][2];
+#pragma unroll
+        for (uint32_t mt = 0; mt < 2; ++mt) {
+          const uint32_t row_a = 2 * (16 * mt + r3g) + half_row, row_b = 2 * (16 * mt + 8 + r3g) + half_row;
+          kr[mt][0] = load_shared_16(keys + row_a * 128 + ((chunk ^ (row_a & 7u)) << 4));
+          kr[mt][1] = load_shared_16(keys + row_b * 128 + ((chunk ^ (row_b & 7u)) << 4));
+        }
+#pragma unroll
+        for (uint32_t w = 0; w < 4; ++w) {
+          const uint32_t s = j * 4 + w;
+          uint2 q;
+          asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(q.x), "=r"(q.y) : "r"(query_shared + s * 256));
+#pragma unroll
+          for (uint32_t mt = 0; mt < 2; ++mt) {
+            const uint32_t xa = w == 0 ? kr[mt][0].x : w == 1 ? kr[mt][0].y : w == 2 ? kr[mt][0].z : kr[mt][0].w;
+            const uint32_t xb = w == 0 ? kr[mt][1].x : w == 1 ? kr[mt][1].y : w == 2 ? kr[mt][1].z : kr[mt][1].w;
+            uint32_t a0, a1, a2, a3;
+            key_pairs<kFloat8>(xa, a0, a2);
+            key_pairs<kFloat8>(xb, a1, a3);
+            mma_f16(sacc[mt][w & 1u], a0, a1, a2, a3, q.x, q.y);
+          }
+        }
+      }
+
+      // ---- online softmax over the page's 32 tokens -------------------------------------
+      uint32_t pb_frag[2][2];
+      if (valid == kPageTokens)
+        page_softmax<false>(sacc, hfac, negoff, scales, r3g, valid, m, l_sum, o, pb_frag);
+      else
+        page_softmax<true>(sacc, hfac, negoff, scales, r3g, valid, m, l_sum, o, pb_frag);
+
+      // ---- O^T += V^T.P^T : 16 tiles of 16 dims (rows g and g+8 of a tile = dims 16t+g, 16t+8+g), 2 k-steps of 16 tokens
+#pragma unroll
+      for (uint32_t s = 0; s < 2; ++s) {
+#pragma unroll
+        for (uint32_t t = 0; t < 16; ++t) {
+          // a dim's 32 token bytes are a quarter of a 128-byte swizzle row; this k-step reads its half s (16 bytes)
+          const uint32_t dim_a = 16 * t + g, dim_b = dim_a + 8;
+          const uint32_t row_a = dim_a >> 2, row_b = dim_b >> 2;
+          const uint4 va = load_shared_16(values + row_a * 128 + ((((dim_a & 3u) * 2 + s) ^ (row_a & 7u)) << 4));
+          const uint4 vb = load_shared_16(values + row_b * 128 + ((((dim_b & 3u) * 2 + s) ^ (row_b & 7u)) << 4));
+          // this lane's tokens of the 16: 4 c1 + c0 (+2) in word c1, 8 + the same in word c1 + 2
+          uint32_t a0 = value_pair<kFloat8>(c1 ? va.y : va.x, value_selector), a2 = value_pair<kFloat8>(c1 ? va.w : va.z, value_selector);
+          uint32_t a1 = value_pair<kFloat8>(c1 ? vb.y : vb.x, value_selector), a3 = value_pair<kFloat8>(c1 ? vb.w : vb.z, value_selector);
+          if (kFloat8 && valid != kPageTokens) { // stale bytes past the visible tokens may decode to NaN: a zero weight must meet a finite value
+            const uint32_t token = 16 * s + 4 * c1 + c0;
+            const uint32_t low = (token < valid ? 0x0000ffffu : 0u) | (token + 2 < valid ? 0xffff0000u : 0u);
+            const uint32_t high = (token + 8 < valid ? 0x0000ffffu : 0u) | (token + 10 < valid ? 0xffff0000u : 0u);
+            a0 &= low; a1 &= low; a2 &= high; a3 &= high;
+          }
+          mma_f16(o[t], a0, a1, a2, a3, pb_frag[s][0], pb_frag[s][1]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) barrier_arrive(smem_address(&sh.empty[slot]));
+    }
+    units_before += pb - pa;
+
+    // ---- flush this warp's partial of (lane l, head, page residue) --------------------------
+    {
+#pragma unroll
+      for (uint32_t j = 0; j < 2; ++j) {
+        l_sum[j] += __shfl_xor_sync(0xffffffffu, l_sum[j], 4);
+        l_sum[j] += __shfl_xor_sync(0xffffffffu, l_sum[j], 8);
+        l_sum[j] += __shfl_xor_sync(0xffffffffu, l_sum[j], 16);
+      }
+      const uint32_t segment = sh.segment_base[l] + (cta - cta_of(lane_begin, total_pages, ctas));
+      const uint64_t slot_index = (uint64_t(segment) * kKvHeads + head) * kPageWarps + residue;
+      float *out = args.partials + slot_index * kGroup * kHeadDim;
+      float *stats = args.statistics + slot_index * kGroup * 2;
+      const float unscale = 6.103515625e-05f; // 2^-14
+      const bool failed = sh.error != 0;
+#pragma unroll
+      for (uint32_t j = 0; j < 2; ++j) {
+        const uint32_t query_head = 2 * c + j;
+        if (query_head >= kGroup) continue;
+#pragma unroll
+        for (uint32_t t = 0; t < 16; ++t) {
+          out[query_head * kHeadDim + 16 * t + g] = o[t][j] * unscale;
+          out[query_head * kHeadDim + 16 * t + 8 + g] = o[t][2 + j] * unscale;
+        }
+        if (g == 0) {
+          stats[query_head * 2] = failed ? -INFINITY : m[j] * kLn2;
+          stats[query_head * 2 + 1] = failed ? 0.0f : l_sum[j];
+        }
+      }
+    }
+  }
+}
+
 // Merge one query head's partials in slot order (segment, then warp) and store bf16 (and
 // optionally fp32). grid (group, kv_heads, lanes), 256 threads = one per dimension.
 __global__ void __launch_bounds__(256)
@@ -661,6 +997,8 @@ merge_shards_kernel(const float *__restrict__ triples, uint32_t shards, uint32_t
 }
 
 constexpr size_t kDecodeSharedBytes = 1024 + kStages * kStageBytes + sizeof(Shared);
+constexpr size_t kByteDecodeSharedBytes = 1024 + kByteStages * kByteStageBytes + sizeof(Shared);
+static_assert(kByteDecodeSharedBytes <= 227 * 1024, "the byte-format ring fits one SM");
 
 // The kernel's dynamic shared-memory limit is a per-device function attribute.
 int configure_decode_kernel() {
@@ -670,6 +1008,8 @@ int configure_decode_kernel() {
   if (device < 0 || device >= 64) { set_error("device index out of range"); return kInvalid; }
   if (!configured[device]) {
     if (int st = cuda_status(cudaFuncSetAttribute(decode_int4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kDecodeSharedBytes)), "decode shared memory")) return st;
+    if (int st = cuda_status(cudaFuncSetAttribute(decode_bytes_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kByteDecodeSharedBytes)), "decode shared memory")) return st;
+    if (int st = cuda_status(cudaFuncSetAttribute(decode_bytes_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kByteDecodeSharedBytes)), "decode shared memory")) return st;
     configured[device] = true;
   }
   return kOk;
@@ -705,8 +1045,9 @@ extern "C" {
 int rk_decode_plan_make(uint32_t format, uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim,
                         uint32_t lanes, uint32_t ctas, rk_decode_plan *plan) {
   if (!plan || !lanes || lanes > kMaxLanes) { set_error("rk_decode_plan_make: lanes out of range"); return kInvalid; }
-  if (format != RK_FORMAT_INT4 || kv_heads != kKvHeads || query_heads != kKvHeads * kGroup || head_dim != kHeadDim) {
-    set_error("rk_decode_plan_make: the streaming decode kernel is built for int4, 4 KV heads x 24 query heads x 256");
+  if ((format != RK_FORMAT_INT4 && format != RK_FORMAT_INT8 && format != RK_FORMAT_FP8E4M3) || kv_heads != kKvHeads ||
+      query_heads != kKvHeads * kGroup || head_dim != kHeadDim) {
+    set_error("rk_decode_plan_make: the streaming decode kernels are built for int4, int8 and fp8, 4 KV heads x 24 query heads x 256");
     return kUnsupported;
   }
   if (!ctas) {
@@ -751,7 +1092,7 @@ int rk_attention_decode(const void *window, const rk_decode_plan *plan, uint32_t
                         void *stream) {
   const auto *w = static_cast<const Window *>(window);
   if (!w || !plan || !queries || !output || !partials || !statistics || !descriptors || !tables || !lane_params ||
-      !layer.extent_pages || format != RK_FORMAT_INT4) {
+      !layer.extent_pages || (format != RK_FORMAT_INT4 && format != RK_FORMAT_INT8 && format != RK_FORMAT_FP8E4M3)) {
     set_error("rk_attention_decode: invalid arguments");
     return kInvalid;
   }
@@ -760,7 +1101,9 @@ int rk_attention_decode(const void *window, const rk_decode_plan *plan, uint32_t
   if (int st = configure_decode_kernel()) return st;
   DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, plan->lanes};
   if (int st = cuda_status(cudaMemsetAsync(descriptors + 2 * plan->lanes, 0, sizeof(uint32_t), s), "decode status clear")) return st;
-  decode_int4_kernel<<<plan->ctas, kThreads, shared_bytes, s>>>(w->int4_map, args);
+  if (format == RK_FORMAT_INT4) decode_int4_kernel<<<plan->ctas, kThreads, shared_bytes, s>>>(w->int4_map, args);
+  else if (format == RK_FORMAT_INT8) decode_bytes_kernel<false><<<plan->ctas, kThreads, kByteDecodeSharedBytes, s>>>(w->int4_map, args);
+  else decode_bytes_kernel<true><<<plan->ctas, kThreads, kByteDecodeSharedBytes, s>>>(w->int4_map, args);
   if (int st = cuda_status(cudaGetLastError(), "decode launch")) return st;
   return launch_merge(plan->lanes, s, partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer, nullptr);
 }

@@ -51,7 +51,7 @@ struct VerifyAttentionPlan {
   DispatchSize splitGroups, reduceGroups, storeGroups;
   uint32_t rowCapacity = 0;
   float scoreScale = 0.0f;
-  // Row capacity 1 on int4 pages runs the streaming decode kernel instead of split + reduce.
+  // Row capacity 1 on int4, int8 or fp8 pages runs the streaming decode kernel instead of split + reduce.
   bool streamingDecode = false;
   rk_decode_plan decode{};
   // Row capacity 8 or 16 on int4 pages runs the tcgen05 split kernel; laneSplits / splits / splitGroups then

@@ -1,4 +1,4 @@
-"""GPU: the streaming int4 decode kernel (TMA page ring + warp-level MMA) against the checker,
+"""GPU: the streaming decode kernels (TMA page ring + warp-level MMA; int4, int8, fp8) against the checker,
 against the general tile, and through its size-independent properties."""
 import numpy as np
 import pytest
@@ -8,25 +8,28 @@ import oracle as om
 from gpuhelp import (assert_attention_close, chunk_params, run_decode_attention_gpu, run_verify_attention_gpu,
                      run_verify_attention_oracle)
 from kvcase import Scenario, fill_history_with_store, make_queries, make_staging
-from richengine_b200.abi import INT4, Layout
+from richengine_b200.abi import FP8E4M3, INT4, INT8, Layout
+
+STREAMING = [INT4, INT8, FP8E4M3]
 
 pytestmark = pytest.mark.gpu
 
 
-def prepared(contexts, seed=3, layers=1, layer=0):
-    s = Scenario(Layout(layers, 4, 256, INT4), contexts, extra_tokens=1, device=True, seed=seed)
+def prepared(contexts, seed=3, layers=1, layer=0, fmt=INT4):
+    s = Scenario(Layout(layers, 4, 256, fmt), contexts, extra_tokens=1, device=True, seed=seed)
     fill_history_with_store(s, layer, seed=seed)
     rng = np.random.default_rng(seed + 100)
     k, v = make_staging(rng, s.lanes, s.layout)
     params = chunk_params(s, 1, layer)
-    assert om.oracle().rko_store_verify(INT4, 4, 256, s.lanes, k.ctypes.data, v.ctypes.data, s.host_table_pointers(), params) == 0
+    assert om.oracle().rko_store_verify(fmt, 4, 256, s.lanes, k.ctypes.data, v.ctypes.data, s.host_table_pointers(), params) == 0
     s.upload()
     return s, make_queries(rng, s.lanes, s.layout)
 
 
+@pytest.mark.parametrize("fmt", STREAMING)
 @pytest.mark.parametrize("contexts", [[0], [1], [31], [32], [33], [0, 31, 32, 700], [4095, 17, 2048, 5, 64, 63, 999]])
-def test_decode_matches_checker(contexts):
-    s, q = prepared(contexts)
+def test_decode_matches_checker(contexts, fmt):
+    s, q = prepared(contexts, fmt=fmt)
     got16, got32 = run_decode_attention_gpu(s, q)
     _, want32 = run_verify_attention_oracle(s, q, 1, 1)
     assert_attention_close(got32, want32, got16, f"decode {contexts}")
@@ -34,18 +37,20 @@ def test_decode_matches_checker(contexts):
     s.close()
 
 
+@pytest.mark.parametrize("fmt", STREAMING)
 @pytest.mark.parametrize("ctas", [1, 3, 7, 148, 1000])
-def test_partition_independent_of_grid(ctas):
+def test_partition_independent_of_grid(ctas, fmt):
     """Any number of CTA ranges gives the same attention within the bar; one range is one tile."""
-    s, q = prepared([700, 33, 1500, 64], seed=9)
+    s, q = prepared([700, 33, 1500, 64], seed=9, fmt=fmt)
     _, want32 = run_verify_attention_oracle(s, q, 1, 1)
     got16, got32 = run_decode_attention_gpu(s, q, ctas=ctas)
     assert_attention_close(got32, want32, got16, f"ctas {ctas}")
     s.close()
 
 
-def test_decode_repeatable_and_agrees_with_general_tile():
-    s, q = prepared([3000, 257, 8191], seed=11, layers=2, layer=1)
+@pytest.mark.parametrize("fmt", STREAMING)
+def test_decode_repeatable_and_agrees_with_general_tile(fmt):
+    s, q = prepared([3000, 257, 8191], seed=11, layers=2, layer=1, fmt=fmt)
     a16, a32 = run_decode_attention_gpu(s, q, layer_index=1)
     b16, b32 = run_decode_attention_gpu(s, q, layer_index=1)
     assert np.array_equal(a16, b16) and np.array_equal(a32, b32)  # same grid, same bits
@@ -99,4 +104,21 @@ def test_invalid_lane_is_skipped():
     from kvcase import bf16_to_f32
     for lane in (0, 2):
         assert np.abs(bf16_to_f32(got[lane, :, 0]) - want32[lane, :, 0]).max() < 2e-3 * max(1, np.abs(want32).max()) + 2 ** -8 * np.abs(want32).max()
+    s.close()
+
+
+def test_fp8_stale_non_finite_bytes_in_the_tail_page():
+    """Recycled pages: bytes past the last visible token may decode to NaN and must not leak into the output."""
+    s = Scenario(Layout(1, 4, 256, FP8E4M3), [100, 40, 31], extra_tokens=1, device=True, seed=5)
+    for raw in s.host.bytes:
+        raw[:] = 0xFF
+    fill_history_with_store(s, 0, seed=5)
+    rng = np.random.default_rng(105)
+    k, v = make_staging(rng, s.lanes, s.layout)
+    assert om.oracle().rko_store_verify(FP8E4M3, 4, 256, s.lanes, k.ctypes.data, v.ctypes.data, s.host_table_pointers(), chunk_params(s, 1)) == 0
+    s.upload()
+    q = make_queries(rng, s.lanes, s.layout)
+    got16, got32 = run_decode_attention_gpu(s, q)
+    _, want32 = run_verify_attention_oracle(s, q, 1, 1)
+    assert_attention_close(got32, want32, got16, "stale bytes")
     s.close()
