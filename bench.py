@@ -419,7 +419,8 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4),
                          "traffic": round(DRAM_BYTES_PER_ALGORITHMIC_BYTE * layer_bytes) if fmt == INT4 else None, "peak_source": peak_source,
-                         "kernel": "decode_int4_kernel (+ its merge)" if fmt == INT4 else "window_attention_kernel, one row (+ its merge)", "us_per_launch": round(kernel_ms * 1e3, 2),
+                         "kernel": {INT4: "decode_int4_kernel", INT8: "decode_bytes_kernel<int8>", FP8E4M3: "decode_bytes_kernel<fp8>",
+                                    BF16: "decode_bf16_kernel"}[fmt] + " (+ its merge)", "us_per_launch": round(kernel_ms * 1e3, 2),
                          "algorithmic_bytes_per_launch": layer_bytes},
             "e2e": {"value": round(e2e_bytes / (e2e_time_ms * 1e-3) / 1e9, 1), "unit": "GB/s",
                     "h2d_bytes_per_step": h2d * args.layers, "d2h_bytes_per_step": d2h * args.layers,

@@ -144,6 +144,22 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   const __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<const uint32_t *>(&h);
 }
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ uint32_t load_shared_32(uint32_t address) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(address));
+  return v;
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 __device__ __forceinline__ uint4 load_shared_16(uint32_t address) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(address));
@@ -164,12 +180,14 @@ __device__ __forceinline__ uint32_t cta_of(uint64_t x, uint64_t total, uint64_t 
 struct Shared {
   uint64_t full[kStages];
   uint64_t empty[kStages];
+  uint64_t warp_full[kConsumerWarps];   // bf16 kernel: one barrier per consumer warp
   uint2 query[kKvHeads][16][32];        // per KV head: B fragments of Q^T for the 16 k-steps
   float head_factor[kKvHeads][8];       // per query head of the group: score factor ...
   float head_offset[kKvHeads][8];       // ... and the -8*sum(q) correction
   uint32_t lane_start[kMaxLanes + 1];   // pages before each lane
   uint32_t segment_base[kMaxLanes + 1]; // partial segments before each lane
   uint32_t scan[kThreads / 32 + 1];
+  float unit_scales[kScaleBytes / 4 + kPageTokens]; // ones: the scale rows of a format without scales
   volatile uint32_t error;
 };
 
@@ -202,11 +220,11 @@ __device__ void exclusive_scan(uint32_t *values, uint32_t n, uint32_t *scratch) 
 
 // Online softmax of one page for this lane's 4 tokens x 2 query heads, and the fp16 probability
 // fragments (B operand of O^T += V^T.P^T). Masked = the page holds tokens past the visible ones.
-template <bool Masked>
+template <bool Masked, bool Wide = false>
 __device__ __forceinline__ void page_softmax(const float (&sacc)[2][2][4], const float (&hfac)[2],
                                              const float (&negoff)[2], uint32_t scales, uint32_t r3g,
                                              uint32_t valid, float (&m)[2], float (&l_sum)[2], float (&o)[16][4],
-                                             uint32_t (&pb_frag)[2][2]) {
+                                             uint32_t (&pb_frag)[2][2], uint32_t (*pb_low)[2] = nullptr) {
   float s2[2][2][2], lv[2][2];
   float local_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -255,8 +273,18 @@ __device__ __forceinline__ void page_softmax(const float (&sacc)[2][2][4], const
         w[half][j] = live ? exp2_fast(score + lv[mt][half] - m[j] + 14.0f) : 0.0f;
         l_sum[j] += live ? exp2_fast(score - m[j]) : 0.0f;
       }
-    pb_frag[mt][0] = transpose_8x8(pack_half2(w[0][0], w[0][1]));
-    pb_frag[mt][1] = transpose_8x8(pack_half2(w[1][0], w[1][1]));
+    if (Wide) {
+      // bf16 values need bf16 probabilities: each weight travels as a truncated high part and the rest
+#pragma unroll
+      for (uint32_t half = 0; half < 2; ++half) {
+        const uint32_t hi0 = __float_as_uint(w[half][0]) & 0xffff0000u, hi1 = __float_as_uint(w[half][1]) & 0xffff0000u;
+        pb_frag[mt][half] = transpose_8x8((hi0 >> 16) | hi1);
+        pb_low[mt][half] = transpose_8x8(pack_bf16x2(w[half][0] - __uint_as_float(hi0), w[half][1] - __uint_as_float(hi1)));
+      }
+    } else {
+      pb_frag[mt][0] = transpose_8x8(pack_half2(w[0][0], w[0][1]));
+      pb_frag[mt][1] = transpose_8x8(pack_half2(w[1][0], w[1][1]));
+    }
   }
 }
 
@@ -910,6 +938,279 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
   }
 }
 
+// ---- bf16 pools: (page, KV head) units of 16 KiB keys + 16 KiB values, six stages, no scales --------------------------
+// Keys, values and queries stay bf16 (mma.sync bf16 operands, fp32 accumulate); a probability travels as two bf16
+// parts so its precision matches the fp16 probabilities of the other formats.
+constexpr uint32_t kWideStages = 6;
+constexpr uint32_t kWideSlabBytes = 16384; // one head's K (or V) of a page: one 128-row TMA box
+constexpr uint32_t kWideStageBytes = 2 * kWideSlabBytes;
+static_assert(kWideStages <= kStages, "the barrier arrays hold the stages");
+
+__global__ void __launch_bounds__(kThreads, 1)
+decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs args) {
+  extern __shared__ uint8_t dynamic_shared[];
+  // Stages need 1024-byte alignment for the 128-byte swizzle pattern.
+  const uint32_t ring = (smem_address(dynamic_shared) + 1023u) & ~1023u;
+  Shared &sh = *reinterpret_cast<Shared *>(dynamic_shared + (ring - smem_address(dynamic_shared)) + kWideStages * kWideStageBytes);
+  const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const uint32_t lanes = args.lanes, cta = blockIdx.x;
+  uint32_t *error_word = args.descriptors + 2 * lanes;
+  dependents_may_launch(); // the merge kernel's blocks may take their places; they wait for this grid to finish
+  dependency_wait();       // pages, queries and parameters may come from the kernel before this one
+
+  // ---- partition: pages per lane -> prefix; segments per lane -> prefix -----------------
+  for (uint32_t i = tid; i < lanes; i += kThreads) {
+    rk_verify_params p = args.lane_params[i];
+    p.kv = args.layer;
+    const bool valid = rk_verify_contract_valid(&p) && p.active_rows == 1 && p.row_capacity == 1;
+    sh.lane_start[i] = valid ? rk_pages_for(p.committed_tokens + 1) : 0;
+  }
+  if (tid == 0) sh.error = 0;
+  for (uint32_t i = tid; i < sizeof(sh.unit_scales) / sizeof(float); i += kThreads) sh.unit_scales[i] = 1.0f;
+  __syncthreads();
+  exclusive_scan(sh.lane_start, lanes, sh.scan);
+  const uint64_t total_pages = sh.lane_start[lanes];
+  // Never more ranges than pages, so every range a lane spans is non-empty.
+  const uint32_t ctas = uint32_t(min(uint64_t(gridDim.x), total_pages));
+  if (cta >= ctas) return;
+  for (uint32_t i = tid; i < lanes; i += kThreads) {
+    const uint32_t begin = sh.lane_start[i], end = sh.lane_start[i + 1];
+    sh.segment_base[i] = end > begin ? cta_of(end - 1, total_pages, ctas) - cta_of(begin, total_pages, ctas) + 1 : 0;
+  }
+  __syncthreads();
+  exclusive_scan(sh.segment_base, lanes, sh.scan);
+  if (cta == 0)
+    for (uint32_t i = tid; i < lanes; i += kThreads) {
+      args.descriptors[2 * i] = sh.segment_base[i];
+      args.descriptors[2 * i + 1] = sh.segment_base[i + 1] - sh.segment_base[i];
+    }
+  const uint32_t range_begin = uint32_t(uint64_t(cta) * total_pages / ctas);
+  const uint32_t range_end = uint32_t(uint64_t(cta + 1) * total_pages / ctas);
+  if (tid == 0) {
+    // A unit is one head's slabs of one page and has one consumer warp. Each warp waits on its own "full" barrier,
+    // so it sees every completion of the barrier it waits on (a parity wait cannot tell completions two apart);
+    // the stages themselves are released through per-stage "empty" barriers that only the producer waits on.
+    for (uint32_t s = 0; s < kWideStages; ++s) barrier_init(smem_address(&sh.empty[s]), 1);
+    for (uint32_t w = 0; w < kConsumerWarps; ++w) barrier_init(smem_address(&sh.warp_full[w]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (range_begin >= range_end) return;
+  // first lane whose pages reach into this range
+  uint32_t first_lane;
+  {
+    uint32_t lo = 0, hi = lanes; // largest i with lane_start[i] <= range_begin
+    while (hi - lo > 1) {
+      const uint32_t mid = (lo + hi) / 2;
+      if (sh.lane_start[mid] <= range_begin) lo = mid; else hi = mid;
+    }
+    first_lane = lo;
+  }
+
+  if (warp == kConsumerWarps) {
+    // ================= producer: one thread streams (page, KV head) units of 32 KiB =============
+    if (lane != 0) return;
+    uint32_t unit = 0, ordinal = 0; // units issued by this CTA; pages of this CTA before the current one
+    bool ok = true;
+    for (uint32_t l = first_lane; ok && l < lanes && sh.lane_start[l] < range_end; ++l) {
+      const uint32_t lane_begin = sh.lane_start[l], lane_end = sh.lane_start[l + 1];
+      const uint32_t pa = max(range_begin, lane_begin) - lane_begin;
+      const uint32_t pb = min(range_end, lane_end) - lane_begin;
+      if (pb <= pa || lane_end <= range_begin) continue;
+      const rk_page_entry *table = args.tables[l];
+      rk_page_entry next_entry = table[pa];
+      for (uint32_t page = pa; ok && page < pb; ++page, ++ordinal) {
+        const rk_page_entry entry = next_entry;
+        if (page + 1 < pb) next_entry = table[page + 1]; // in flight while this page's copies are issued
+        const uint32_t index = rk_entry_index(entry);
+        const uint64_t region = rk_entry_extent(entry) + args.layer.offset;
+        const uint64_t keys = region + uint64_t(index) * (kKvHeads * kWideSlabBytes);
+        const uint64_t values = keys + args.layer.extent_pages * uint64_t(kKvHeads * kWideSlabBytes);
+        const int32_t key_row = int32_t((keys - args.window_base) >> 7), value_row = int32_t((values - args.window_base) >> 7);
+        for (uint32_t head = 0; head < kKvHeads; ++head, ++unit) {
+          // page ordinal n of this CTA belongs to the warps of residue n % 3; a warp's units are 12 apart in issue
+          // order and the ring holds 6, so a warp's barrier never has two fills in flight
+          const uint32_t slot = unit % kWideStages, round = unit / kWideStages;
+          const uint32_t full = smem_address(&sh.warp_full[head + kKvHeads * (ordinal % kPageWarps)]), stage = ring + slot * kWideStageBytes;
+          if (sh.error || !barrier_wait(smem_address(&sh.empty[slot]), (round & 1u) ^ 1u)) { ok = false; break; }
+          barrier_expect(full, kWideStageBytes);
+          tma_load_rows(stage, &window_map, key_row + int32_t(head * (kWideSlabBytes / 128)), full); // 128 rows of 128 bytes
+          tma_load_rows(stage + kWideSlabBytes, &window_map, value_row + int32_t(head * (kWideSlabBytes / 128)), full);
+        }
+      }
+    }
+    if (!ok) {
+      atomicExch(error_word, 1u);
+      sh.error = 1;
+      // Copies already issued must land before the block's shared memory goes.
+      const uint32_t armed = min(unit, kWideStages);
+      for (uint32_t back = 0; back < armed; ++back) {
+        const uint32_t u = unit - 1 - back, n = u / kKvHeads;
+        barrier_wait(smem_address(&sh.warp_full[u % kKvHeads + kKvHeads * (n % kPageWarps)]), (n / kPageWarps) & 1u);
+      }
+    }
+    return;
+  }
+
+  // ================= consumers: warp = (KV head, page residue) ===============================
+  const uint32_t head = warp & 3u, residue = warp >> 2;
+  const uint32_t g = lane >> 2, c = lane & 3u;
+  // A token row is four 128-byte swizzle rows, so neighbouring tokens already differ in bit 2 of the row:
+  // MMA row g (and g+8) of a 16-token tile is simply token g (and 8 + g).
+  const uint32_t r3g = g;
+  const uint32_t query_shared = smem_address(&sh.query[head][0][lane]);
+  const uint32_t scales = smem_address(&sh.unit_scales[0]);
+
+  uint32_t units_before = 0; // pages of this CTA in earlier segments
+  for (uint32_t l = first_lane; l < lanes && sh.lane_start[l] < range_end; ++l) {
+    const uint32_t lane_begin = sh.lane_start[l], lane_end = sh.lane_start[l + 1];
+    const uint32_t pa = max(range_begin, lane_begin) - lane_begin;
+    const uint32_t pb = min(range_end, lane_end) - lane_begin;
+    if (pb <= pa || lane_end <= range_begin) continue;
+    const rk_verify_params p = args.lane_params[l];
+    const uint32_t visible = p.committed_tokens + 1;
+    const uint32_t lane_pages = lane_end - lane_begin;
+
+    // ---- the head's query fragments (B operand of S^T = K.Q^T), shared by its three warps ----
+    group_barrier(1 + head, kPageWarps * 32); // every warp of the head is done with the previous lane
+    if (residue == 0) {
+      const uint16_t *q = args.queries + ((uint64_t(l) * kKvHeads + head) * RK_VERIFY_CHUNK_STRIDE) * kGroup * kHeadDim +
+                          uint64_t(g) * kHeadDim;
+      // k-step s = 2j + w covers, for lane column c, dims 8(c + 4j) + 4w .. +3: b0 = the first two, b1 = the last two.
+      // Queries and keys are both bf16: nothing is converted.
+#pragma unroll
+      for (uint32_t j = 0; j < 8; ++j) {
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (g < kGroup) v = __ldg(reinterpret_cast<const uint4 *>(q + 8 * (c + 4 * j)));
+        sh.query[head][2 * j][lane] = make_uint2(v.x, v.y);
+        sh.query[head][2 * j + 1][lane] = make_uint2(v.z, v.w);
+      }
+      if (c == 0) {
+        sh.head_factor[head][g] = rk_score_scale(p.score_scale, kHeadDim) * kLog2e; // scores in the log2 domain
+        sh.head_offset[head][g] = 0.0f;
+      }
+    }
+    group_barrier(1 + head, kPageWarps * 32); // fragments visible to the head's warps
+    float hfac[2], negoff[2];
+#pragma unroll
+    for (uint32_t j = 0; j < 2; ++j) { // C fragment columns are query heads 2c, 2c+1 of the group
+      hfac[j] = sh.head_factor[head][2 * c + j];
+      negoff[j] = sh.head_offset[head][2 * c + j];
+    }
+
+    float m[2] = {-1.0e30f, -1.0e30f}, l_sum[2] = {0.0f, 0.0f};
+    float o[16][4];
+#pragma unroll
+    for (uint32_t t = 0; t < 16; ++t) { o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.0f; }
+
+    // this warp takes the pages whose ordinal inside the CTA's range is its residue modulo 3
+    for (uint32_t page = pa + (residue + kPageWarps - units_before % kPageWarps) % kPageWarps; page < pb && !sh.error; page += kPageWarps) {
+      const uint32_t ordinal = units_before + (page - pa);
+      const uint32_t slot = (ordinal * kKvHeads + head) % kWideStages;
+      if (!barrier_wait(smem_address(&sh.warp_full[warp]), (ordinal / kPageWarps) & 1u)) {
+        atomicExch(error_word, 2u);
+        sh.error = 2;
+        break;
+      }
+      const uint32_t keys = ring + slot * kWideStageBytes;
+      const uint32_t values = keys + kWideSlabBytes;
+      const uint32_t valid = page + 1 == lane_pages ? visible - page * kPageTokens : kPageTokens;
+
+      // ---- S^T = K.Q^T : two 16-token tiles, 16 k-steps each --------------------------
+      float sacc[2][2][4];
+#pragma unroll
+      for (uint32_t mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (uint32_t h = 0; h < 2; ++h) sacc[mt][h][0] = sacc[mt][h][1] = sacc[mt][h][2] = sacc[mt][h][3] = 0.0f;
+#pragma unroll
+      for (uint32_t j = 0; j < 8; ++j) { // 16-byte chunk c + 4j of each 512-byte token row: 8 dims = two k-steps
+        const uint32_t quarter = j >> 1, chunk = c + 4 * (j & 1u);
+        uint4 kr[2][2];
+#pragma unroll
+        for (uint32_t mt = 0; mt < 2; ++mt) {
+          const uint32_t row_a = 4 * (16 * mt + g) + quarter, row_b = 4 * (16 * mt + 8 + g) + quarter;
+          kr[mt][0] = load_shared_16(keys + row_a * 128 + ((chunk ^ (row_a & 7u)) << 4));
+          kr[mt][1] = load_shared_16(keys + row_b * 128 + ((chunk ^ (row_b & 7u)) << 4));
+        }
+#pragma unroll
+        for (uint32_t w = 0; w < 2; ++w) {
+          uint2 q;
+          asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(q.x), "=r"(q.y) : "r"(query_shared + (2 * j + w) * 256));
+#pragma unroll
+          for (uint32_t mt = 0; mt < 2; ++mt)
+            mma_bf16(sacc[mt][w], w ? kr[mt][0].z : kr[mt][0].x, w ? kr[mt][1].z : kr[mt][1].x,
+                     w ? kr[mt][0].w : kr[mt][0].y, w ? kr[mt][1].w : kr[mt][1].y, q.x, q.y);
+        }
+      }
+
+      // ---- online softmax over the page's 32 tokens -------------------------------------
+      uint32_t pb_frag[2][2], pb_low[2][2];
+      if (valid == kPageTokens)
+        page_softmax<false, true>(sacc, hfac, negoff, scales, r3g, valid, m, l_sum, o, pb_frag, pb_low);
+      else
+        page_softmax<true, true>(sacc, hfac, negoff, scales, r3g, valid, m, l_sum, o, pb_frag, pb_low);
+
+      // ---- O^T += V^T.P^T : 16 tiles of 16 dims (rows g and g+8 of a tile = dims 16t+g, 16t+8+g), 2 k-steps of 16 tokens
+#pragma unroll
+      for (uint32_t s = 0; s < 2; ++s) {
+        // this lane's tokens of the 16: 2c, 2c+1 (one word) and 8 + the same
+        uint32_t low = 0xffffffffu, high = 0xffffffffu;
+        if (valid != kPageTokens) { // stale bits past the visible tokens may be NaN: a zero weight must meet a finite value
+          const uint32_t token = 16 * s + 2 * c;
+          low = (token < valid ? 0x0000ffffu : 0u) | (token + 1 < valid ? 0xffff0000u : 0u);
+          high = (token + 8 < valid ? 0x0000ffffu : 0u) | (token + 9 < valid ? 0xffff0000u : 0u);
+        }
+#pragma unroll
+        for (uint32_t t = 0; t < 16; ++t) {
+          // a dim's 32 tokens are half of a 128-byte swizzle row; this k-step reads two 16-byte chunks of it
+          const uint32_t dim_a = 16 * t + g, dim_b = dim_a + 8;
+          const uint32_t row_a = dim_a >> 1, row_b = dim_b >> 1;
+          const uint32_t chunk_a = (dim_a & 1u) * 4 + 2 * s, chunk_b = (dim_b & 1u) * 4 + 2 * s;
+          const uint32_t a0 = load_shared_32(values + row_a * 128 + ((chunk_a ^ (row_a & 7u)) << 4) + 4 * c) & low;
+          const uint32_t a2 = load_shared_32(values + row_a * 128 + (((chunk_a + 1) ^ (row_a & 7u)) << 4) + 4 * c) & high;
+          const uint32_t a1 = load_shared_32(values + row_b * 128 + ((chunk_b ^ (row_b & 7u)) << 4) + 4 * c) & low;
+          const uint32_t a3 = load_shared_32(values + row_b * 128 + (((chunk_b + 1) ^ (row_b & 7u)) << 4) + 4 * c) & high;
+          mma_bf16(o[t], a0, a1, a2, a3, pb_frag[s][0], pb_frag[s][1]);
+          mma_bf16(o[t], a0, a1, a2, a3, pb_low[s][0], pb_low[s][1]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) barrier_arrive(smem_address(&sh.empty[slot]));
+    }
+    units_before += pb - pa;
+
+    // ---- flush this warp's partial of (lane l, head, page residue) --------------------------
+    {
+#pragma unroll
+      for (uint32_t j = 0; j < 2; ++j) {
+        l_sum[j] += __shfl_xor_sync(0xffffffffu, l_sum[j], 4);
+        l_sum[j] += __shfl_xor_sync(0xffffffffu, l_sum[j], 8);
+        l_sum[j] += __shfl_xor_sync(0xffffffffu, l_sum[j], 16);
+      }
+      const uint32_t segment = sh.segment_base[l] + (cta - cta_of(lane_begin, total_pages, ctas));
+      const uint64_t slot_index = (uint64_t(segment) * kKvHeads + head) * kPageWarps + residue;
+      float *out = args.partials + slot_index * kGroup * kHeadDim;
+      float *stats = args.statistics + slot_index * kGroup * 2;
+      const float unscale = 6.103515625e-05f; // 2^-14
+      const bool failed = sh.error != 0;
+#pragma unroll
+      for (uint32_t j = 0; j < 2; ++j) {
+        const uint32_t query_head = 2 * c + j;
+        if (query_head >= kGroup) continue;
+#pragma unroll
+        for (uint32_t t = 0; t < 16; ++t) {
+          out[query_head * kHeadDim + 16 * t + g] = o[t][j] * unscale;
+          out[query_head * kHeadDim + 16 * t + 8 + g] = o[t][2 + j] * unscale;
+        }
+        if (g == 0) {
+          stats[query_head * 2] = failed ? -INFINITY : m[j] * kLn2;
+          stats[query_head * 2 + 1] = failed ? 0.0f : l_sum[j];
+        }
+      }
+    }
+  }
+}
+
 // Merge one query head's partials in slot order (segment, then warp) and store bf16 (and
 // optionally fp32). grid (group, kv_heads, lanes), 256 threads = one per dimension.
 __global__ void __launch_bounds__(256)
@@ -998,7 +1299,9 @@ merge_shards_kernel(const float *__restrict__ triples, uint32_t shards, uint32_t
 
 constexpr size_t kDecodeSharedBytes = 1024 + kStages * kStageBytes + sizeof(Shared);
 constexpr size_t kByteDecodeSharedBytes = 1024 + kByteStages * kByteStageBytes + sizeof(Shared);
+constexpr size_t kWideDecodeSharedBytes = 1024 + kWideStages * kWideStageBytes + sizeof(Shared);
 static_assert(kByteDecodeSharedBytes <= 227 * 1024, "the byte-format ring fits one SM");
+static_assert(kWideDecodeSharedBytes <= 227 * 1024, "the bf16 ring fits one SM");
 
 // The kernel's dynamic shared-memory limit is a per-device function attribute.
 int configure_decode_kernel() {
@@ -1010,6 +1313,7 @@ int configure_decode_kernel() {
     if (int st = cuda_status(cudaFuncSetAttribute(decode_int4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kDecodeSharedBytes)), "decode shared memory")) return st;
     if (int st = cuda_status(cudaFuncSetAttribute(decode_bytes_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kByteDecodeSharedBytes)), "decode shared memory")) return st;
     if (int st = cuda_status(cudaFuncSetAttribute(decode_bytes_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kByteDecodeSharedBytes)), "decode shared memory")) return st;
+    if (int st = cuda_status(cudaFuncSetAttribute(decode_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kWideDecodeSharedBytes)), "decode shared memory")) return st;
     configured[device] = true;
   }
   return kOk;
@@ -1039,15 +1343,24 @@ static int launch_merge(uint32_t lanes, cudaStream_t stream, const float *partia
                      "decode reduce launch");
 }
 
+// The streaming kernel of a format on `ctas` CTAs.
+static int launch_decode(uint32_t format, uint32_t ctas, cudaStream_t s, const Window *w, const DecodeArgs &args) {
+  if (format == RK_FORMAT_INT4) decode_int4_kernel<<<ctas, kThreads, kDecodeSharedBytes, s>>>(w->int4_map, args);
+  else if (format == RK_FORMAT_INT8) decode_bytes_kernel<false><<<ctas, kThreads, kByteDecodeSharedBytes, s>>>(w->int4_map, args);
+  else if (format == RK_FORMAT_FP8E4M3) decode_bytes_kernel<true><<<ctas, kThreads, kByteDecodeSharedBytes, s>>>(w->int4_map, args);
+  else decode_bf16_kernel<<<ctas, kThreads, kWideDecodeSharedBytes, s>>>(w->int4_map, args);
+  return cuda_status(cudaGetLastError(), "decode launch");
+}
+
 extern "C" {
 
 // Sizes the scratch of a decode step: `ctas` = 0 takes one CTA per SM of the current device.
 int rk_decode_plan_make(uint32_t format, uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim,
                         uint32_t lanes, uint32_t ctas, rk_decode_plan *plan) {
   if (!plan || !lanes || lanes > kMaxLanes) { set_error("rk_decode_plan_make: lanes out of range"); return kInvalid; }
-  if ((format != RK_FORMAT_INT4 && format != RK_FORMAT_INT8 && format != RK_FORMAT_FP8E4M3) || kv_heads != kKvHeads ||
+  if (format < RK_FORMAT_INT8 || format > RK_FORMAT_FP8E4M3 || kv_heads != kKvHeads ||
       query_heads != kKvHeads * kGroup || head_dim != kHeadDim) {
-    set_error("rk_decode_plan_make: the streaming decode kernels are built for int4, int8 and fp8, 4 KV heads x 24 query heads x 256");
+    set_error("rk_decode_plan_make: the streaming decode kernels are built for 4 KV heads x 24 query heads x 256");
     return kUnsupported;
   }
   if (!ctas) {
@@ -1092,19 +1405,15 @@ int rk_attention_decode(const void *window, const rk_decode_plan *plan, uint32_t
                         void *stream) {
   const auto *w = static_cast<const Window *>(window);
   if (!w || !plan || !queries || !output || !partials || !statistics || !descriptors || !tables || !lane_params ||
-      !layer.extent_pages || (format != RK_FORMAT_INT4 && format != RK_FORMAT_INT8 && format != RK_FORMAT_FP8E4M3)) {
+      !layer.extent_pages || format < RK_FORMAT_INT8 || format > RK_FORMAT_FP8E4M3) {
     set_error("rk_attention_decode: invalid arguments");
     return kInvalid;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  constexpr size_t shared_bytes = kDecodeSharedBytes;
   if (int st = configure_decode_kernel()) return st;
   DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, plan->lanes};
   if (int st = cuda_status(cudaMemsetAsync(descriptors + 2 * plan->lanes, 0, sizeof(uint32_t), s), "decode status clear")) return st;
-  if (format == RK_FORMAT_INT4) decode_int4_kernel<<<plan->ctas, kThreads, shared_bytes, s>>>(w->int4_map, args);
-  else if (format == RK_FORMAT_INT8) decode_bytes_kernel<false><<<plan->ctas, kThreads, kByteDecodeSharedBytes, s>>>(w->int4_map, args);
-  else decode_bytes_kernel<true><<<plan->ctas, kThreads, kByteDecodeSharedBytes, s>>>(w->int4_map, args);
-  if (int st = cuda_status(cudaGetLastError(), "decode launch")) return st;
+  if (int st = launch_decode(format, plan->ctas, s, w, args)) return st;
   return launch_merge(plan->lanes, s, partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer, nullptr);
 }
 
@@ -1117,7 +1426,7 @@ int rk_attention_decode_shard(const void *window, const rk_decode_plan *plan, ui
                               rk_kv_layer layer, void *stream) {
   const auto *w = static_cast<const Window *>(window);
   if (!w || !plan || !queries || !triples || !partials || !statistics || !descriptors || !tables || !lane_params ||
-      !layer.extent_pages || format != RK_FORMAT_INT4) {
+      !layer.extent_pages || format < RK_FORMAT_INT8 || format > RK_FORMAT_FP8E4M3) {
     set_error("rk_attention_decode_shard: invalid arguments");
     return kInvalid;
   }
@@ -1125,8 +1434,7 @@ int rk_attention_decode_shard(const void *window, const rk_decode_plan *plan, ui
   if (int st = configure_decode_kernel()) return st;
   DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, plan->lanes};
   if (int st = cuda_status(cudaMemsetAsync(descriptors + 2 * plan->lanes, 0, sizeof(uint32_t), s), "decode status clear")) return st;
-  decode_int4_kernel<<<plan->ctas, kThreads, kDecodeSharedBytes, s>>>(w->int4_map, args);
-  if (int st = cuda_status(cudaGetLastError(), "decode launch")) return st;
+  if (int st = launch_decode(format, plan->ctas, s, w, args)) return st;
   decode_reduce_kernel<<<dim3(kGroup, kKvHeads, plan->lanes), 256, 0, s>>>(partials, statistics, descriptors, nullptr, nullptr, lane_params, layer, triples);
   return cuda_status(cudaGetLastError(), "decode shard reduce launch");
 }
@@ -1169,7 +1477,8 @@ int rk_attention_decode_static(const void *window, uint32_t format, uint32_t lan
                                float *output_f32, const rk_page_entry *const *tables,
                                const rk_verify_params *lane_params, rk_kv_layer layer, void *stream) {
   const auto *w = static_cast<const Window *>(window);
-  if (!w || !queries || !output || !tables || !lane_params || !layer.extent_pages || format != RK_FORMAT_INT4 || !lanes) {
+  if (!w || !queries || !output || !tables || !lane_params || !layer.extent_pages || format < RK_FORMAT_INT8 ||
+      format > RK_FORMAT_FP8E4M3 || !lanes) {
     set_error("rk_attention_decode_static: invalid arguments");
     return kInvalid;
   }
@@ -1184,7 +1493,7 @@ int rk_attention_decode_static(const void *window, uint32_t format, uint32_t lan
   if (!scratch_address[device]) { // once per device, with that device current
     void *address = nullptr;
     if (int st = cuda_status(cudaGetSymbolAddress(&address, g_decode_scratch), "cudaGetSymbolAddress(decode scratch)")) return st;
-    if (int st = cuda_status(cudaFuncSetAttribute(decode_int4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kDecodeSharedBytes)), "decode shared memory")) return st;
+    if (int st = configure_decode_kernel()) return st;
     scratch_address[device] = static_cast<unsigned char *>(address);
   }
   unsigned char *base = scratch_address[device];
@@ -1194,8 +1503,7 @@ int rk_attention_decode_static(const void *window, uint32_t format, uint32_t lan
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, lanes};
   if (int st = cuda_status(cudaMemsetAsync(descriptors + 2 * lanes, 0, sizeof(uint32_t), s), "decode status clear")) return st;
-  decode_int4_kernel<<<kStaticCtas, kThreads, kDecodeSharedBytes, s>>>(w->int4_map, args);
-  if (int st = cuda_status(cudaGetLastError(), "decode launch")) return st;
+  if (int st = launch_decode(format, kStaticCtas, s, w, args)) return st;
   decode_reduce_kernel<<<dim3(kGroup, kKvHeads, lanes), 256, 0, s>>>(partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer, nullptr);
   return cuda_status(cudaGetLastError(), "decode reduce launch");
 }

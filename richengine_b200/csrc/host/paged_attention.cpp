@@ -143,7 +143,7 @@ VerifyAttentionPlan PagedAttention::verifyPlan(uint32_t lanes, uint32_t queryHea
   plan.storeGroups = {uint64_t(lanes) * 2 * liveRows * layout.kvHeads, 1, 1};
   plan.rowCapacity = rows;
   plan.scoreScale = layout.scoreScale;
-  if (rows == 1 && (layout.format == kv::Format::Int4 || layout.format == kv::Format::Int8 || layout.format == kv::Format::Float8E4M3) &&
+  if (rows == 1 &&
       rk_decode_plan_make(formatCode(layout.format), layout.kvHeads, queryHeads, layout.headDimension, lanes, ctas, &plan.decode) == RK_OK) {
     plan.streamingDecode = true;
     plan.workspace = {plan.decode.partials_bytes, plan.decode.statistics_bytes};

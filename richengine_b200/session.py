@@ -16,7 +16,7 @@ import ctypes as C
 import torch
 
 from . import lib, ops
-from .abi import FP8E4M3, INT4, INT8, VERIFY_CHUNK_STRIDE, Layout
+from .abi import VERIFY_CHUNK_STRIDE, Layout
 from .storage import PageStorage
 
 
@@ -36,11 +36,8 @@ class DecodeSession:
         self.k_rows = torch.zeros((lanes, H, D), dtype=torch.bfloat16, device=device)
         self.v_rows = torch.zeros((lanes, H, D), dtype=torch.bfloat16, device=device)
         self.out_rows = torch.zeros((lanes, query_heads, D), dtype=torch.bfloat16, device=device)
-        # int4, int8 and fp8 pools decode on the streaming kernels; bf16 on the tcgen05 window kernel with one row
-        if layout.format in (INT4, INT8, FP8E4M3):
-            self.attention = ops.DecodeAttention(layout, query_heads, lanes, storage.window(), ctas)
-        else:
-            self.attention = ops.WindowDecodeAttention(layout, query_heads, lanes, storage.window())
+        # every format decodes on its streaming kernel
+        self.attention = ops.DecodeAttention(layout, query_heads, lanes, storage.window(), ctas)
         self.layers = storage.layers()
         self.kernel_launches = 0
 

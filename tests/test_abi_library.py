@@ -48,7 +48,8 @@ def test_host_side_refusals_without_a_gpu():
     assert library.rk_storage_create(abi.INT8, 16, 4, 256, 256, 100) is None  # not whole alignment units
     assert b"geometry" in library.rk_last_error()
     plan = lib.DecodePlan()
-    assert library.rk_decode_plan_make(abi.BF16, 4, 24, 256, 4, 148, C.byref(plan)) == lib.UNSUPPORTED  # bf16 decodes on the window kernel
+    assert library.rk_decode_plan_make(abi.BF16, 4, 24, 256, 4, 148, C.byref(plan)) == lib.OK
+    assert library.rk_decode_plan_make(abi.INT4, 8, 24, 256, 4, 148, C.byref(plan)) == lib.UNSUPPORTED  # another geometry
     assert library.rk_decode_plan_make(abi.INT8, 4, 24, 256, 4, 148, C.byref(plan)) == lib.OK
     assert library.rk_decode_plan_make(abi.INT4, 4, 24, 256, 64, 148, C.byref(plan)) == lib.OK
     assert plan.max_segments == 64 + 148 and plan.partials_bytes == (64 + 148) * 4 * 3 * 6 * 256 * 4

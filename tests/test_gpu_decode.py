@@ -1,4 +1,4 @@
-"""GPU: the streaming decode kernels (TMA page ring + warp-level MMA; int4, int8, fp8) against the checker,
+"""GPU: the streaming decode kernels (TMA page ring + warp-level MMA; all four formats) against the checker,
 against the general tile, and through its size-independent properties."""
 import numpy as np
 import pytest
@@ -8,9 +8,9 @@ import oracle as om
 from gpuhelp import (assert_attention_close, chunk_params, run_decode_attention_gpu, run_verify_attention_gpu,
                      run_verify_attention_oracle)
 from kvcase import Scenario, fill_history_with_store, make_queries, make_staging
-from richengine_b200.abi import FP8E4M3, INT4, INT8, Layout
+from richengine_b200.abi import BF16, FP8E4M3, INT4, INT8, Layout
 
-STREAMING = [INT4, INT8, FP8E4M3]
+STREAMING = [INT4, INT8, FP8E4M3, BF16]
 
 pytestmark = pytest.mark.gpu
 
@@ -107,15 +107,16 @@ def test_invalid_lane_is_skipped():
     s.close()
 
 
-def test_fp8_stale_non_finite_bytes_in_the_tail_page():
+@pytest.mark.parametrize("fmt", [FP8E4M3, BF16])
+def test_stale_non_finite_bytes_in_the_tail_page(fmt):
     """Recycled pages: bytes past the last visible token may decode to NaN and must not leak into the output."""
-    s = Scenario(Layout(1, 4, 256, FP8E4M3), [100, 40, 31], extra_tokens=1, device=True, seed=5)
+    s = Scenario(Layout(1, 4, 256, fmt), [100, 40, 31], extra_tokens=1, device=True, seed=5)
     for raw in s.host.bytes:
         raw[:] = 0xFF
     fill_history_with_store(s, 0, seed=5)
     rng = np.random.default_rng(105)
     k, v = make_staging(rng, s.lanes, s.layout)
-    assert om.oracle().rko_store_verify(FP8E4M3, 4, 256, s.lanes, k.ctypes.data, v.ctypes.data, s.host_table_pointers(), chunk_params(s, 1)) == 0
+    assert om.oracle().rko_store_verify(fmt, 4, 256, s.lanes, k.ctypes.data, v.ctypes.data, s.host_table_pointers(), chunk_params(s, 1)) == 0
     s.upload()
     q = make_queries(rng, s.lanes, s.layout)
     got16, got32 = run_decode_attention_gpu(s, q)

@@ -10,20 +10,21 @@ from gpuhelp import (assert_attention_close, chunk_params, dev, host_u16, run_de
                      run_verify_attention_oracle, struct_to_device)
 from kvcase import Scenario, fill_history_with_store, make_queries, make_staging
 from richengine_b200 import lib, ops, parallel
-from richengine_b200.abi import INT4, Layout
+from richengine_b200.abi import BF16, FP8E4M3, INT4, INT8, Layout
 
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("context,ranks", [(5000, 2), (5000, 4), (40, 8), (1023, 3)])
-def test_sequence_split_matches_whole_sequence(context, ranks):
-    layout = Layout(1, 4, 256, INT4)
+@pytest.mark.parametrize("context,ranks,fmt", [(5000, 2, INT4), (5000, 4, INT4), (40, 8, INT4), (1023, 3, INT4),
+                                                (5000, 4, INT8), (1023, 3, FP8E4M3), (5000, 2, BF16)])
+def test_sequence_split_matches_whole_sequence(context, ranks, fmt):
+    layout = Layout(1, 4, 256, fmt)
     s = Scenario(layout, [context], extra_tokens=1, device=True, seed=5)
     fill_history_with_store(s, 0, seed=5)
     rng = np.random.default_rng(9)
     k, v = make_staging(rng, 1, layout)
     params = chunk_params(s, 1)
-    assert om.oracle().rko_store_verify(INT4, 4, 256, 1, k.ctypes.data, v.ctypes.data, s.host_table_pointers(), params) == 0
+    assert om.oracle().rko_store_verify(fmt, 4, 256, 1, k.ctypes.data, v.ctypes.data, s.host_table_pointers(), params) == 0
     s.upload()
     q = make_queries(rng, 1, layout)
     visible = context + 1
