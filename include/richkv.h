@@ -107,7 +107,9 @@ int rk_qkv_prepare_store(uint32_t format, uint32_t kv_heads, uint32_t query_head
 /* The reference has no single-query kernel: a plain decode is its tile with one active row
  * (runtime/metal/kernels/common/paged_attention_tile.h:108-110; tested as history 0, rows 1 in
  * dev/tests/engine/paged_attention_plan_test.mm:1019). This entry replaces split + reduce for
- * active_rows = row_capacity = 1 with the TMA-streamed kernel; scratch is sized by the plan. */
+ * active_rows = row_capacity = 1 with the TMA-streamed kernel of the pool's format (int4, int8, fp8 e4m3,
+ * bf16; the fp8 kernel contracts fp16-staged queries as decode/fp8_attention.metal does); scratch is sized
+ * by the plan. */
 typedef struct rk_decode_plan {
   uint32_t lanes, ctas, max_segments, reserved;
   uint64_t partials_bytes, statistics_bytes, descriptor_bytes;
@@ -117,14 +119,14 @@ int rk_decode_plan_make(uint32_t format, uint32_t kv_heads, uint32_t query_heads
 /* The device address window that holds every page of a pool (rk_storage_window): the TMA tensor map. */
 void *rk_window_create(uint64_t base, uint64_t bytes);
 void rk_window_destroy(void *window);
-/* verify_attention_int4_split / verify_tree_attention_int4_split (decode/paged_attention.metal:23-192)
- * for 8- or 16-row windows as a tcgen05 contraction: the fused rows are the M side of a 128-row
+/* verify_attention_{q8,int4,bf16}_split / verify_tree_attention_*_split (decode/paged_attention.metal:23-192)
+ * and verify_attention_fp8_split (decode/fp8_attention.metal) for 1-, 8- or 16-row windows as a tcgen05 contraction: the fused rows are the M side of a 128-row
  * tensor-core tile with accumulators in tensor memory, pages arrive by TMA through the pool's window.
  * Arguments and scratch layout as rk_attention_verify_split; merge with rk_attention_verify_reduce.
  * Any split count the contract allows is valid; about two CTAs' worth of (lane, head, split) per SM
  * is the efficient choice. `status` is one device word the caller zeroes: it turns non-zero when a
  * bounded wait inside a kernel ran out (the step's output is then invalid). RK_ERR_UNSUPPORTED for
- * other formats, geometries or row counts. */
+ * other geometries or row counts. */
 int rk_attention_verify_split_tc(const void *window, uint32_t format, uint32_t kv_heads, uint32_t query_heads,
                                  uint32_t head_dim, uint32_t lanes, uint32_t row_capacity, uint32_t grid_splits,
                                  const void *queries, float *partials, float *statistics,

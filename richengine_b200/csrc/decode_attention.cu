@@ -1,5 +1,6 @@
 // decode_attention.cu — paged GQA decode attention (one query row per lane)
-// streaming packed-INT4 pages at HBM speed.
+// streaming pages at HBM speed: the int4 kernel described here, and its
+// int8 / fp8 and bf16 siblings further down.
 //
 // Semantics: the reference's tile with active_rows = 1
 //   runtime/metal/kernels/common/paged_attention_tile.h:85-189,208-349  (scores, scale fold, online softmax, P.V)
