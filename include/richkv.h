@@ -218,6 +218,15 @@ int rk_storage_copy_pages(void *storage, const rk_page_copy *copies, uint32_t co
 int rk_storage_pack_pages(void *storage, const uint32_t *pages, uint32_t count, void *device_slots, int unpack,
                           void *stream);
 
+/* ---- checksums of persistent payloads ----------------------------------------------------------------
+ * CRC-32C as the reference's slot file keeps it per payload and per record (runtime/model/Crc32c.hpp:12-29,
+ * runtime/model/SlotFile.cpp:715-735). rk_crc32c_pages: `count` payloads of `payload_bytes` (whole 512-byte rows,
+ * as every packed page is), `stride` bytes apart in DEVICE memory, one word each into out[count] (device);
+ * `ctas` = 0 takes one CTA per SM. rk_crc32c_host: a host buffer, continuing from `crc` (0 to start). */
+int rk_crc32c_pages(const void *data, uint64_t stride, uint64_t payload_bytes, uint32_t count, uint32_t *out,
+                    uint32_t ctas, void *stream);
+uint32_t rk_crc32c_host(const void *data, uint64_t bytes, uint32_t crc);
+
 /* ---- pinned-host eviction tier: engine::KvTier (runtime/engine/cache/KvTier.hpp:34-63) with the
  * transfer bounds of KvPageTier (runtime/engine/cache/KvPageTier.cpp:38-132) ------------------------ */
 void *rk_tier_create(void *storage, uint32_t slots, uint32_t transfer_limit);
@@ -229,6 +238,12 @@ int rk_tier_can_restore(const void *tier);
 int64_t rk_tier_acquire_slot(void *tier); /* -1 when the quota is full */
 void rk_tier_release_slot(void *tier, uint32_t slot);
 void rk_tier_fail_next(void *tier, uint32_t count); /* host-side fault injection for tests */
+/* CRC-32C of the payload the slot's last landed demotion stored, taken on the device when the page was packed. */
+uint32_t rk_tier_slot_checksum(const void *tier, uint32_t slot);
+/* model::SlotFile::adopt (runtime/model/SlotFile.hpp:196-200): a free slot takes a payload an earlier process
+ * stored; its first restore fails unless the CRC-32C of what reached the device equals `checksum`.
+ * Returns the slot id, -1 when the quota is full. */
+int64_t rk_tier_adopt_slot(void *tier, const void *payload, uint64_t bytes, uint32_t checksum);
 const void *rk_tier_slot_host_pointer(const void *tier, uint32_t slot);
 int rk_tier_demote(void *tier, uint32_t page, uint32_t slot, void *after_stream);  /* transfer id or status */
 int rk_tier_restore(void *tier, uint32_t slot, uint32_t page, void *after_stream); /* transfer id or status */

@@ -66,6 +66,38 @@ void rk_cache_snapshot(const void *cache, uint64_t *out);
 /* Block state: out[4] = page (0xffffffff = none), has tier copy, transferring, last used. -1 if unknown. */
 int rk_cache_block_state(const void *cache, uint64_t block, uint64_t *out);
 
+/* ---- KV that survives a restart: slot file + record file --------------------------------------------
+ * The reference's persistent slot file (runtime/model/SlotFile.hpp:98-219; records SlotFile.cpp:238-323, open
+ * :398-438) in its own byte format: a 4096-byte header area {"SPLASHSF", version 1, label bytes, slot bytes, tag
+ * bytes, CRC-32C} + tag, then per slot index a record {0x53524543, payload CRC-32C, payload bytes} + label +
+ * CRC-32C, rounded up to 64 bytes. A file written for another tag, slot size or label size is emptied when it
+ * opens; a damaged record, or one whose slot lies outside the slot file, is a free slot. Labels are
+ * engine::KvBlockLabel (168 bytes: id, parent, lastUsed, images lo/hi, 32 tokens) and engine::StateLabel
+ * (runtime/engine/cache/DiskLabels.hpp:22-37). `slot_bytes` is a multiple of 4096. */
+void *rk_slot_store_open(const char *slots_path, const char *records_path, const void *tag, uint32_t tag_bytes,
+                         uint32_t label_bytes, uint64_t slot_bytes);
+void rk_slot_store_close(void *store);
+uint32_t rk_slot_store_record_count(const void *store); /* the records found when the file opened */
+int rk_slot_store_record(const void *store, uint32_t at, uint32_t *index, uint64_t *payload_bytes, uint32_t *checksum,
+                         void *label);
+/* Payload from the start of the slot, zeros after it, then the record (SlotFile::write + label). */
+int rk_slot_store_write(void *store, uint32_t index, const void *payload, uint64_t payload_bytes, uint32_t checksum,
+                        const void *label);
+int rk_slot_store_read(const void *store, uint32_t index, void *destination, uint64_t bytes);
+int rk_slot_store_free(void *store, uint32_t index); /* clears the record, then returns the blocks */
+int rk_slot_store_synchronize(void *store);
+uint64_t rk_slot_record_bytes(uint32_t label_bytes);
+int rk_slot_record_encode(uint32_t label_bytes, uint64_t payload_bytes, uint32_t checksum, const void *label, void *out);
+int64_t rk_slot_records_header(uint64_t slot_bytes, uint32_t label_bytes, const void *tag, uint32_t tag_bytes, void *out,
+                               uint32_t capacity);
+/* Cache::labelBlock / Cache::adopt (runtime/engine/cache/Cache.cpp:38-140,852-870) over the pinned-host tier:
+ * persist seals every landed tier copy (payload, the CRC-32C taken on the GPU when the page was packed, its
+ * KvBlockLabel) and returns the slots written; adopt, on an empty cache, takes back every block under an unbroken
+ * chain (out[3] = blocks, dropped, bytes) — a payload is checked against its record on the GPU when it is first
+ * restored, and a mismatch is a failed restore (a cache miss). */
+int64_t rk_cache_persist(void *cache, void *store);
+int rk_cache_adopt(void *cache, void *store, uint64_t *out);
+
 /* ---- plans -------------------------------------------------------------------------------------- */
 /* names: "split\nreduce\nstore"; out[16] = splits, lane splits of the first four lanes, splitGroups xyz,
  * reduceGroups xyz, partialsBytes, statisticsBytes, rowCapacity, streamingDecode, tensorCoreWindow.

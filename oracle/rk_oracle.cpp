@@ -511,6 +511,16 @@ int rko_qkv_prepare(uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim, 
   return 0;
 }
 
+uint32_t rko_crc32c(const void *data, uint64_t bytes, uint32_t crc) {
+  const uint8_t *p = static_cast<const uint8_t *>(data);
+  uint32_t state = ~crc;
+  for (uint64_t i = 0; i < bytes; ++i) {
+    state ^= p[i];
+    for (int bit = 0; bit < 8; ++bit) state = (state & 1u) ? (state >> 1) ^ 0x82F63B78u : state >> 1;
+  }
+  return ~state;
+}
+
 int rko_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

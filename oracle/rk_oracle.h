@@ -99,6 +99,10 @@ int rko_qkv_prepare(uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim, 
                     const uint16_t *packed_qkv, const void *q_norm, const void *k_norm, int norm_f32,
                     const float *rope_cos, const float *rope_sin, float eps, uint16_t *queries, uint16_t *chunk_keys,
                     uint16_t *chunk_values);
+/* CRC-32C (Castagnoli, reflected polynomial 0x82F63B78, initial and final inversion) one bit at a time; `crc` continues
+ * a running value, 0 to start (runtime/model/Crc32c.hpp:12-29 computes the same function with the CPU's CRC
+ * instructions). Known answers: RFC 3720 B.4 and the check value of "123456789". */
+uint32_t rko_crc32c(const void *data, uint64_t bytes, uint32_t crc);
 int rko_threads(void);
 
 #ifdef __cplusplus

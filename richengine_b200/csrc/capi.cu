@@ -420,6 +420,8 @@ struct Transfer {
   bool ready = false;
   bool success = false;
   bool forced_failure = false;
+  bool verify = false;    // a restore of an adopted slot: its payload must match the record's checksum
+  uint32_t expected = 0;
   uint32_t page = 0, slot = 0;
   cudaEvent_t done = nullptr;
 };
@@ -431,8 +433,13 @@ struct HostTier {
   uint32_t demotions = 0, restores = 0, in_flight = 0, fail_next = 0;
   uint8_t *host = nullptr;    // slots * slot_bytes, pinned
   uint8_t *staging = nullptr; // transfer_limit * slot_bytes, device
+  uint32_t *slot_checksums = nullptr;    // pinned: CRC-32C of each slot's payload, taken on the device when it was packed
+  uint32_t *arrived_checksums = nullptr; // pinned: CRC-32C of a restored payload after it reached the device, per transfer
+  uint32_t *device_checksums = nullptr;  // device: one word per transfer
   cudaStream_t stream = nullptr;
   std::vector<uint8_t> slot_used;
+  std::vector<uint8_t> slot_verify;      // adopted from an earlier process and not read yet
+  std::vector<uint32_t> slot_expected;
   std::vector<Transfer> transfers; // index = transfer id = staging slot
   bool writable = true;
 };
@@ -451,10 +458,19 @@ extern "C" void *rk_tier_create(void *storage, uint32_t slots, uint32_t transfer
   t->demotion_limit = std::max<uint32_t>(1, transfer_limit / 2);
   t->restore_limit = std::max<uint32_t>(1, transfer_limit - transfer_limit / 4);
   t->slot_used.assign(slots, 0);
+  t->slot_verify.assign(slots, 0);
+  t->slot_expected.assign(slots, 0);
   t->transfers.resize(transfer_limit);
   if (cuda_status(cudaHostAlloc(reinterpret_cast<void **>(&t->host), uint64_t(slots) * t->slot_bytes, cudaHostAllocDefault), "pinned host arena")) return nullptr;
   if (cuda_status(cudaMalloc(reinterpret_cast<void **>(&t->staging), uint64_t(transfer_limit) * t->slot_bytes), "tier staging")) { cudaFreeHost(t->host); return nullptr; }
   if (cuda_status(cudaStreamCreateWithFlags(&t->stream, cudaStreamNonBlocking), "tier stream")) { cudaFree(t->staging); cudaFreeHost(t->host); return nullptr; }
+  if (cuda_status(cudaHostAlloc(reinterpret_cast<void **>(&t->slot_checksums), (uint64_t(slots) + transfer_limit) * 4, cudaHostAllocDefault), "tier checksums") ||
+      cuda_status(cudaMalloc(reinterpret_cast<void **>(&t->device_checksums), uint64_t(transfer_limit) * 4), "tier checksums")) {
+    cudaFreeHost(t->slot_checksums); cudaStreamDestroy(t->stream); cudaFree(t->staging); cudaFreeHost(t->host);
+    return nullptr;
+  }
+  memset(t->slot_checksums, 0, (uint64_t(slots) + transfer_limit) * 4);
+  t->arrived_checksums = t->slot_checksums + slots;
   for (Transfer &x : t->transfers) cudaEventCreateWithFlags(&x.done, cudaEventDisableTiming);
   return t.release();
 }
@@ -466,6 +482,8 @@ extern "C" void rk_tier_destroy(void *tier) {
   for (Transfer &x : t->transfers) cudaEventDestroy(x.done);
   cudaStreamDestroy(t->stream);
   cudaFree(t->staging);
+  cudaFree(t->device_checksums);
+  cudaFreeHost(t->slot_checksums);
   cudaFreeHost(t->host);
   delete t;
 }
@@ -489,7 +507,26 @@ extern "C" int64_t rk_tier_acquire_slot(void *tier) {
 }
 extern "C" void rk_tier_release_slot(void *tier, uint32_t slot) {
   auto *t = static_cast<HostTier *>(tier);
-  if (slot < t->slots) t->slot_used[slot] = 0;
+  if (slot < t->slots) { t->slot_used[slot] = 0; t->slot_verify[slot] = 0; }
+}
+// CRC-32C of the payload the slot's last completed demotion stored (taken on the device before the copy left).
+extern "C" uint32_t rk_tier_slot_checksum(const void *tier, uint32_t slot) {
+  const auto *t = static_cast<const HostTier *>(tier);
+  return slot < t->slots ? t->slot_checksums[slot] : 0;
+}
+// Takes a free slot for a payload an earlier process stored (model::SlotFile::adopt,
+// runtime/model/SlotFile.hpp:196-200): the first restore of the slot fails unless the payload's CRC-32C,
+// taken on the device after the upload, equals `checksum`. Returns the slot id, -1 when the quota is full.
+extern "C" int64_t rk_tier_adopt_slot(void *tier, const void *payload, uint64_t bytes, uint32_t checksum) {
+  auto *t = static_cast<HostTier *>(tier);
+  if (!payload || bytes != t->slot_bytes) { set_error("rk_tier_adopt_slot: the payload is not one slot"); return kInvalid; }
+  const int64_t slot = rk_tier_acquire_slot(tier);
+  if (slot < 0) return -1;
+  memcpy(t->host + uint64_t(slot) * t->slot_bytes, payload, bytes);
+  t->slot_checksums[slot] = checksum;
+  t->slot_expected[slot] = checksum;
+  t->slot_verify[slot] = 1;
+  return slot;
 }
 // Test seam, host side only: the next `count` transfers report failure when
 // they retire, as a failed write or read would.
@@ -499,6 +536,10 @@ extern "C" const void *rk_tier_slot_host_pointer(const void *tier, uint32_t slot
   return slot < t->slots ? t->host + uint64_t(slot) * t->slot_bytes : nullptr;
 }
 
+namespace rk {
+int launch_crc32c(const void *data, uint64_t stride, uint64_t payload_bytes, uint32_t count, uint32_t *out, uint32_t ctas,
+                  cudaStream_t stream);
+}
 namespace {
 int start_transfer(HostTier *t, bool demotion, uint32_t page, uint32_t slot, cudaStream_t after) {
   if (demotion ? !rk_tier_can_demote(t) : !rk_tier_can_restore(t)) return kRefused;
@@ -519,9 +560,19 @@ int start_transfer(HostTier *t, bool demotion, uint32_t page, uint32_t slot, cud
   int status = kOk;
   if (demotion) {
     status = rk_storage_pack_pages(t->storage, &page, 1, stage, 0, t->stream);
+    // the payload's checksum is taken where it was packed, before the bytes cross PCIe
+    if (!status) status = launch_crc32c(stage, t->slot_bytes, t->slot_bytes, 1, t->device_checksums + id, 0, t->stream);
+    if (!status) status = cuda_status(cudaMemcpyAsync(t->slot_checksums + slot, t->device_checksums + id, 4, cudaMemcpyDeviceToHost, t->stream), "demotion checksum");
     if (!status) status = cuda_status(cudaMemcpyAsync(host, stage, t->slot_bytes, cudaMemcpyDeviceToHost, t->stream), "demotion copy");
+    x.verify = false;
   } else {
     status = cuda_status(cudaMemcpyAsync(stage, host, t->slot_bytes, cudaMemcpyHostToDevice, t->stream), "restore copy");
+    x.verify = t->slot_verify[slot] != 0;
+    x.expected = t->slot_expected[slot];
+    if (!status && x.verify) { // an adopted slot's first read: check what arrived against its record
+      status = launch_crc32c(stage, t->slot_bytes, t->slot_bytes, 1, t->device_checksums + id, 0, t->stream);
+      if (!status) status = cuda_status(cudaMemcpyAsync(t->arrived_checksums + id, t->device_checksums + id, 4, cudaMemcpyDeviceToHost, t->stream), "restore checksum");
+    }
     if (!status) status = rk_storage_pack_pages(t->storage, &page, 1, stage, 1, t->stream);
   }
   if (status) {
@@ -559,6 +610,11 @@ extern "C" int rk_tier_poll(void *tier) {
     if (state == cudaErrorNotReady) continue;
     x.ready = true;
     x.success = state == cudaSuccess && !x.forced_failure;
+    if (!x.demotion && x.verify) { // a payload that does not match its record is a miss and nothing worse
+      const uint32_t id = uint32_t(&x - t->transfers.data());
+      if (t->arrived_checksums[id] != x.expected) x.success = false;
+      else if (x.success) t->slot_verify[x.slot] = 0; // trusted from now on, as this process's own slots are
+    }
     if (x.demotion && !x.success) t->writable = false;
     --t->in_flight;
     --(x.demotion ? t->demotions : t->restores);

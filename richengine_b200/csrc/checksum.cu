@@ -1,0 +1,261 @@
+// checksum.cu — CRC-32C (Castagnoli) of packed page payloads on the device, and of small host buffers.
+//
+// The reference keeps a CRC-32C of every persistent slot's payload and record (runtime/model/Crc32c.hpp:12-29,
+// computed by the slot file's IO worker while it writes, runtime/model/SlotFile.cpp:715-735,775-795) and checks an
+// adopted slot's first read against it. Here a demoted page is packed on the GPU, so its checksum is taken there,
+// at memory speed, before the bytes cross PCIe; a restored payload is checked the same way after it arrives.
+//
+// A CRC is linear over GF(2), which lets a warp read coalesced instead of giving every thread a contiguous run:
+//  * a warp walks its chunk in rows of 512 bytes, lane l loading 16 bytes = words 4l..4l+3 of the row; each of
+//    the warp's 128 word columns keeps its own remainder and advances it by a whole row per step:
+//      acc <- (acc ^ word) * x^4096 mod P        (four table lookups, as slicing-by-4 does for x^32)
+//    The lookup tables of that step are replicated 32 times in shared memory, one copy per bank, so the 32 lanes'
+//    data-dependent lookups never collide;
+//  * the 128 remainders are then a 128-word message of their own: three ordinary steps inside the thread, five
+//    shuffle levels across the warp (x^128 .. x^2048), one last step;
+//  * chunks combine through crc(A|B) = crc(A) * x^(8 len B) + crc(B): every chunk's multiplier depends only on
+//    the payload size, so the host computes them once per launch; contributions are XOR-ed into the result
+//    (atomicXor: order-free, so the result is deterministic), and the initial/final inversions are one more term.
+#include "common.cuh"
+
+#include <algorithm>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+namespace rk {
+namespace {
+
+constexpr uint32_t kPoly = 0x82F63B78u; // reflected Castagnoli polynomial
+constexpr uint32_t kRowBytes = 512;     // one warp step: 32 lanes x 16 bytes
+constexpr uint32_t kWarps = 32;
+constexpr uint32_t kMaxParts = 16;      // CTAs that may share one payload
+
+// Polynomials are bit-reversed as in the usual software CRC: bit 31 is x^0.
+constexpr uint32_t mul_mod(uint32_t a, uint32_t b) {
+  uint32_t product = 0;
+  for (uint32_t bit = 0x80000000u; bit; bit >>= 1) {
+    if (a & bit) product ^= b;
+    b = (b & 1u) ? (b >> 1) ^ kPoly : b >> 1;
+  }
+  return product;
+}
+// x^(8 * bytes) mod P
+uint32_t x_power_bytes(uint64_t bytes) {
+  uint32_t result = 0x80000000u;  // 1
+  uint32_t square = 0x00800000u;  // x^8
+  for (; bytes; bytes >>= 1) {
+    if (bytes & 1u) result = mul_mod(result, square);
+    square = mul_mod(square, square);
+  }
+  return result;
+}
+
+// table[k][b] = (b << 8k) * x^(8 * bytes) mod P: advancing a remainder by `bytes` zero bytes, one byte lane at a time
+void advance_table(uint64_t bytes, uint32_t *table) {
+  const uint32_t power = x_power_bytes(bytes);
+  for (uint32_t k = 0; k < 4; ++k)
+    for (uint32_t b = 0; b < 256; ++b) table[k * 256 + b] = mul_mod(power, b << (8 * k));
+}
+
+constexpr uint32_t kTableWords = 4 * 256;
+constexpr uint32_t kLevels = 5;
+// [0] row step (512 bytes), [1] word step (4 bytes), [2..6] 16, 32, 64, 128, 256 bytes
+constexpr uint32_t kTables = 2 + kLevels;
+__device__ uint32_t g_tables[kTables * kTableWords];
+
+const std::vector<uint32_t> &host_tables() {
+  static const std::vector<uint32_t> tables = [] {
+    std::vector<uint32_t> t(kTables * kTableWords);
+    advance_table(kRowBytes, &t[0]);
+    advance_table(4, &t[kTableWords]);
+    for (uint32_t level = 0; level < kLevels; ++level) advance_table(16ull << level, &t[(2 + level) * kTableWords]);
+    return t;
+  }();
+  return tables;
+}
+
+struct ChecksumArgs {
+  const uint8_t *data;
+  uint64_t stride;        // bytes between payloads
+  uint32_t *out;          // one word per payload, zeroed before the launch
+  uint32_t payloads, parts;
+  uint32_t rows_low, extra; // chunk g of a payload has rows_low + (g < extra) rows
+  uint32_t closing;       // the initial and final inversions as one term
+  uint32_t multiplier[kMaxParts * kWarps]; // x^(8 * bytes after chunk g)
+};
+
+constexpr uint32_t kReplicaBytes = kTableWords * 32 * 4;                       // the row-step table, one copy per bank
+constexpr uint32_t kSharedBytes = kReplicaBytes + (kTables - 1) * kTableWords * 4 + kWarps * 4;
+
+__device__ __forceinline__ uint32_t lookup4(const uint32_t *table, uint32_t x) {
+  return table[x & 0xffu] ^ table[256 + ((x >> 8) & 0xffu)] ^ table[512 + ((x >> 16) & 0xffu)] ^ table[768 + (x >> 24)];
+}
+
+__device__ __forceinline__ uint32_t mul_mod_device(uint32_t a, uint32_t b) {
+  uint32_t product = 0;
+#pragma unroll
+  for (uint32_t i = 0; i < 32; ++i) {
+    product ^= (a & (0x80000000u >> i)) ? b : 0u;
+    b = (b >> 1) ^ ((b & 1u) ? kPoly : 0u);
+  }
+  return product;
+}
+
+__global__ void __launch_bounds__(kWarps * 32, 1) crc32c_kernel(const __grid_constant__ ChecksumArgs args) {
+  extern __shared__ __align__(16) uint32_t shared_words[];
+  uint32_t *replica = shared_words;                       // [k][byte][lane]
+  uint32_t *tables = shared_words + kTableWords * 32;     // word step, then the five levels
+  uint32_t *warp_terms = tables + (kTables - 1) * kTableWords;
+  const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+  for (uint32_t i = tid; i < kTableWords * 32; i += blockDim.x) replica[i] = g_tables[i >> 5];
+  for (uint32_t i = tid; i < (kTables - 1) * kTableWords; i += blockDim.x) tables[i] = g_tables[kTableWords + i];
+  __syncthreads();
+  const uint32_t *mine = replica + lane; // this lane's copy: entry e at mine[32 e]
+  const uint32_t units = args.payloads * args.parts;
+  for (uint32_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
+    const uint32_t payload = unit / args.parts, part = unit - payload * args.parts;
+    const uint32_t chunk = part * kWarps + warp;
+    const uint32_t rows = args.rows_low + (chunk < args.extra ? 1u : 0u);
+    const uint64_t first_row = uint64_t(chunk) * args.rows_low + min(chunk, args.extra);
+    uint32_t term = 0;
+    if (rows) {
+      const uint4 *source = reinterpret_cast<const uint4 *>(args.data + uint64_t(payload) * args.stride + first_row * kRowBytes) + lane;
+      uint32_t acc[4] = {0, 0, 0, 0};
+      uint4 next = __ldcs(source);
+      for (uint32_t row = 0; row + 1 < rows; ++row) {
+        const uint4 v = next;
+        next = __ldcs(source + uint64_t(row + 1) * 32);
+        const uint32_t x[4] = {acc[0] ^ v.x, acc[1] ^ v.y, acc[2] ^ v.z, acc[3] ^ v.w};
+#pragma unroll
+        for (uint32_t k = 0; k < 4; ++k)
+          acc[k] = mine[(x[k] & 0xffu) << 5] ^ mine[(256u + ((x[k] >> 8) & 0xffu)) << 5] ^
+                   mine[(512u + ((x[k] >> 16) & 0xffu)) << 5] ^ mine[(768u + (x[k] >> 24)) << 5];
+      }
+      // the last row enters without the row step: the 128 remainders now form a 128-word message
+      uint32_t c = lookup4(tables, acc[0] ^ next.x) ^ acc[1] ^ next.y;
+      c = lookup4(tables, c) ^ acc[2] ^ next.z;
+      c = lookup4(tables, c) ^ acc[3] ^ next.w;
+#pragma unroll
+      for (uint32_t level = 0; level < kLevels; ++level) {
+        const uint32_t ahead = __shfl_down_sync(0xffffffffu, c, 1u << level);
+        c = lookup4(tables + (1 + level) * kTableWords, c) ^ ahead; // meaningful on lanes that are multiples of 2^(level+1)
+      }
+      if (lane == 0) term = mul_mod_device(lookup4(tables, c), args.multiplier[chunk]);
+    }
+    if (lane == 0) warp_terms[warp] = term;
+    __syncthreads();
+    if (warp == 0) {
+      uint32_t sum = warp_terms[lane];
+#pragma unroll
+      for (uint32_t o = 16; o; o >>= 1) sum ^= __shfl_xor_sync(0xffffffffu, sum, o);
+      if (lane == 0) atomicXor(args.out + payload, part == 0 ? sum ^ args.closing : sum);
+    }
+    __syncthreads();
+  }
+}
+
+uint32_t crc32c_bytes(const uint8_t *data, size_t bytes, uint32_t crc) {
+  static const std::vector<uint32_t> slices = [] { // slicing-by-8: slices[k][b] = b advanced by k + 1 bytes
+    std::vector<uint32_t> t(8 * 256);
+    for (uint32_t b = 0; b < 256; ++b) {
+      uint32_t r = b;
+      for (int i = 0; i < 8; ++i) r = (r & 1u) ? (r >> 1) ^ kPoly : r >> 1;
+      t[b] = r;
+    }
+    for (uint32_t k = 1; k < 8; ++k)
+      for (uint32_t b = 0; b < 256; ++b) t[k * 256 + b] = t[t[(k - 1) * 256 + b] & 0xffu] ^ (t[(k - 1) * 256 + b] >> 8);
+    return t;
+  }();
+  const uint32_t *t = slices.data();
+  uint32_t state = ~crc;
+  for (; bytes >= 8; data += 8, bytes -= 8) {
+    uint32_t lo, hi;
+    memcpy(&lo, data, 4);
+    memcpy(&hi, data + 4, 4);
+    lo ^= state;
+    state = t[7 * 256 + (lo & 0xffu)] ^ t[6 * 256 + ((lo >> 8) & 0xffu)] ^ t[5 * 256 + ((lo >> 16) & 0xffu)] ^ t[4 * 256 + (lo >> 24)] ^
+            t[3 * 256 + (hi & 0xffu)] ^ t[2 * 256 + ((hi >> 8) & 0xffu)] ^ t[1 * 256 + ((hi >> 16) & 0xffu)] ^ t[hi >> 24];
+  }
+  for (; bytes; ++data, --bytes) state = t[(state ^ *data) & 0xffu] ^ (state >> 8);
+  return ~state;
+}
+
+} // namespace
+
+// CRC-32C of `count` payloads of `payload_bytes` each, `stride` bytes apart in device memory, into out[count]
+// (device). `ctas` = 0 takes one CTA per SM. Payloads are whole 512-byte rows (every packed page is).
+int launch_crc32c(const void *data, uint64_t stride, uint64_t payload_bytes, uint32_t count, uint32_t *out, uint32_t ctas,
+                  cudaStream_t stream) {
+  if (!data || !out || !count || !payload_bytes || payload_bytes % kRowBytes || stride < payload_bytes || (stride & 15u) ||
+      (reinterpret_cast<uintptr_t>(data) & 15u)) {
+    set_error("rk_crc32c_pages: payloads must be whole 512-byte rows, 16-byte aligned");
+    return kInvalid;
+  }
+  int device = 0;
+  if (int st = cuda_status(cudaGetDevice(&device), "cudaGetDevice")) return st;
+  if (device < 0 || device >= 64) { set_error("device index out of range"); return kInvalid; }
+  static std::mutex guard;
+  static bool configured[64] = {};
+  static int multiprocessors[64] = {};
+  {
+    std::lock_guard<std::mutex> lock(guard);
+    if (!configured[device]) {
+      const std::vector<uint32_t> &tables = host_tables();
+      if (int st = cuda_status(cudaMemcpyToSymbol(g_tables, tables.data(), tables.size() * 4), "checksum tables")) return st;
+      if (int st = cuda_status(cudaFuncSetAttribute(crc32c_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSharedBytes)), "checksum shared memory")) return st;
+      if (int st = cuda_status(cudaDeviceGetAttribute(&multiprocessors[device], cudaDevAttrMultiProcessorCount, device), "SM count")) return st;
+      configured[device] = true;
+    }
+  }
+  if (!ctas) ctas = uint32_t(multiprocessors[device]);
+  const uint64_t rows = payload_bytes / kRowBytes;
+  // enough parts to occupy the grid, never chunks of less than four rows
+  const uint32_t parts = uint32_t(std::max<uint64_t>(1, std::min<uint64_t>({uint64_t(kMaxParts), (uint64_t(ctas) + count - 1) / count, rows / (4 * kWarps)})));
+  // The multipliers depend only on (payload size, parts): the last launch's set is kept.
+  static ChecksumArgs cached{};
+  static uint64_t cached_bytes = 0;
+  ChecksumArgs args;
+  {
+    std::lock_guard<std::mutex> lock(guard);
+    if (cached_bytes != payload_bytes || cached.parts != parts) {
+      cached.parts = parts;
+      const uint64_t chunks = uint64_t(parts) * kWarps;
+      cached.rows_low = uint32_t(rows / chunks);
+      cached.extra = uint32_t(rows % chunks);
+      // chunks have one of two lengths; walk from the last chunk backwards
+      const uint32_t step_low = x_power_bytes(uint64_t(cached.rows_low) * kRowBytes);
+      const uint32_t step_high = x_power_bytes((uint64_t(cached.rows_low) + 1) * kRowBytes);
+      uint32_t power = 0x80000000u; // x^0: nothing follows the last chunk
+      for (uint64_t g = chunks; g-- > 0;) {
+        cached.multiplier[g] = power;
+        power = mul_mod(power, g < cached.extra ? step_high : step_low);
+      }
+      // the state ~0 advanced over the payload, and the final inversion
+      cached.closing = mul_mod(x_power_bytes(payload_bytes), 0xffffffffu) ^ 0xffffffffu;
+      cached_bytes = payload_bytes;
+    }
+    args = cached;
+  }
+  args.data = static_cast<const uint8_t *>(data);
+  args.stride = stride;
+  args.out = out;
+  args.payloads = count;
+  if (int st = cuda_status(cudaMemsetAsync(out, 0, uint64_t(count) * 4, stream), "checksum clear")) return st;
+  const uint32_t grid = uint32_t(std::min<uint64_t>(ctas, uint64_t(count) * args.parts));
+  crc32c_kernel<<<grid, kWarps * 32, kSharedBytes, stream>>>(args);
+  return cuda_status(cudaGetLastError(), "checksum launch");
+}
+
+} // namespace rk
+
+extern "C" int rk_crc32c_pages(const void *data, uint64_t stride, uint64_t payload_bytes, uint32_t count, uint32_t *out,
+                               uint32_t ctas, void *stream) {
+  return rk::launch_crc32c(data, stride, payload_bytes, count, out, ctas, static_cast<cudaStream_t>(stream));
+}
+
+// CRC-32C of a host buffer, continuing from `crc` (0 to start): rk_crc32c_host(b, n, rk_crc32c_host(a, m, 0)) is the
+// checksum of a followed by b (runtime/model/Crc32c.hpp:12-29).
+extern "C" uint32_t rk_crc32c_host(const void *data, uint64_t bytes, uint32_t crc) {
+  return rk::crc32c_bytes(static_cast<const uint8_t *>(data), size_t(bytes), crc);
+}

@@ -31,7 +31,8 @@ struct PoolHandle {
 class ManualTier final : public engine::KvTier {
 public:
   ManualTier(kv::BudgetExtentStorage &storage, uint32_t slots, uint32_t transfers)
-      : storage_(storage), used_(slots, 0), tags_(slots, 0), limit_(transfers) {}
+      : storage_(storage), used_(slots, 0), tags_(slots, 0), expected_(slots, 0), arrived_(slots, 0), verify_(slots, 0),
+        payloads_(slots), limit_(transfers) {}
   uint64_t slotBytes() const noexcept override { return storage_.bytesPerPage(); }
   bool writable() const noexcept override { return writable_; }
   bool canDemote() const noexcept override { return demotions_ < std::max(1u, limit_ / 2) && pending_.size() < limit_ && writable_; }
@@ -56,11 +57,35 @@ public:
     return std::make_unique<Ticket>(state);
   }
   void poll() override {}
+  // A slot's payload is its content tag repeated over the slot, so that a slot store sees real bytes.
+  bool slotPayload(const engine::KvTierSlot &slot, SlotPayload *out) const override {
+    const auto *held = dynamic_cast<const Slot *>(&slot);
+    if (!held) return false;
+    std::vector<uint8_t> &bytes = payloads_[held->id];
+    bytes.resize(slotBytes());
+    for (size_t at = 0; at < bytes.size(); at += 8) std::memcpy(bytes.data() + at, &tags_[held->id], std::min<size_t>(8, bytes.size() - at));
+    *out = {bytes.data(), bytes.size(), rk_crc32c_host(bytes.data(), bytes.size(), 0)};
+    return true;
+  }
+  std::shared_ptr<engine::KvTierSlot> adoptSlot(const void *payload, uint64_t bytes, uint32_t checksum) override {
+    if (bytes != slotBytes()) throw std::invalid_argument("the payload is not one slot");
+    auto slot = std::dynamic_pointer_cast<Slot>(acquireSlot());
+    if (!slot) return {};
+    std::memcpy(&tags_[slot->id], payload, std::min<uint64_t>(8, bytes));
+    expected_[slot->id] = checksum;
+    arrived_[slot->id] = rk_crc32c_host(payload, bytes, 0);
+    verify_[slot->id] = 1;
+    return slot;
+  }
   bool complete(bool success) {
     if (pending_.empty()) return false;
     auto state = pending_.front();
     pending_.pop_front();
     --(state->demotion ? demotions_ : restores_);
+    if (success && !state->demotion && verify_[state->slot]) { // an adopted slot's first read is checked against its record
+      if (arrived_[state->slot] != expected_[state->slot]) success = false;
+      else verify_[state->slot] = 0;
+    }
     if (success) {
       if (state->demotion) tags_[state->slot] = storage_.content.at(state->page);
       else storage_.content.at(state->page) = tags_[state->slot];
@@ -76,7 +101,7 @@ private:
   struct State { bool demotion; uint32_t page, slot; bool ready = false, success = false; };
   struct Slot final : engine::KvTierSlot {
     Slot(ManualTier *t, uint32_t i) : tier(t), id(i) {}
-    ~Slot() override { tier->used_[id] = 0; }
+    ~Slot() override { tier->used_[id] = 0; tier->verify_[id] = 0; }
     ManualTier *tier; uint32_t id;
   };
   struct Ticket final : engine::KvTransfer {
@@ -88,6 +113,9 @@ private:
   kv::BudgetExtentStorage &storage_;
   std::vector<uint8_t> used_;
   std::vector<uint64_t> tags_;
+  std::vector<uint32_t> expected_, arrived_;
+  std::vector<uint8_t> verify_;
+  mutable std::vector<std::vector<uint8_t>> payloads_;
   std::deque<std::shared_ptr<State>> pending_;
   uint32_t limit_, demotions_ = 0, restores_ = 0;
   bool writable_ = true;
@@ -275,6 +303,73 @@ int rk_cache_block_state(const void *cache, uint64_t block, uint64_t *out) {
   return 0;
 }
 #undef CACHE
+
+// ---- the slot store: KV that survives a restart (runtime/model/SlotFile.hpp:98-219, records and labels) ----------
+void *rk_slot_store_open(const char *slots_path, const char *records_path, const void *tag, uint32_t tag_bytes,
+                         uint32_t label_bytes, uint64_t slot_bytes) {
+  try {
+    model::SlotStore::Persistence persistence;
+    persistence.slots = slots_path;
+    persistence.records = records_path;
+    persistence.tag.assign(static_cast<const uint8_t *>(tag), static_cast<const uint8_t *>(tag) + tag_bytes);
+    persistence.labelBytes = label_bytes;
+    return new model::SlotStore(slot_bytes, persistence);
+  } catch (const std::exception &e) { rk::set_error(e.what()); return nullptr; }
+}
+void rk_slot_store_close(void *store) { delete static_cast<model::SlotStore *>(store); }
+uint32_t rk_slot_store_record_count(const void *store) { return uint32_t(static_cast<const model::SlotStore *>(store)->records().size()); }
+int rk_slot_store_record(const void *store, uint32_t at, uint32_t *index, uint64_t *payload_bytes, uint32_t *checksum, void *label) {
+  const auto &records = static_cast<const model::SlotStore *>(store)->records();
+  if (at >= records.size()) return RK_ERR_INVALID;
+  *index = records[at].index;
+  *payload_bytes = records[at].payloadBytes;
+  *checksum = records[at].checksum;
+  if (label) std::memcpy(label, records[at].label.data(), records[at].label.size());
+  return RK_OK;
+}
+int rk_slot_store_write(void *store, uint32_t index, const void *payload, uint64_t payload_bytes, uint32_t checksum, const void *label) {
+  auto *s = static_cast<model::SlotStore *>(store);
+  return guarded([&] {
+    return s->write(index, {static_cast<const uint8_t *>(payload), size_t(payload_bytes)}, checksum,
+                    {static_cast<const uint8_t *>(label), s->labelBytes()}) ? RK_OK : RK_ERR_REFUSED;
+  });
+}
+int rk_slot_store_read(const void *store, uint32_t index, void *destination, uint64_t bytes) {
+  return guarded([&] { return static_cast<const model::SlotStore *>(store)->read(index, {static_cast<uint8_t *>(destination), size_t(bytes)}) ? RK_OK : RK_ERR_REFUSED; });
+}
+int rk_slot_store_free(void *store, uint32_t index) { return guarded([&] { return static_cast<model::SlotStore *>(store)->free(index) ? RK_OK : RK_ERR_REFUSED; }); }
+int rk_slot_store_synchronize(void *store) { return static_cast<model::SlotStore *>(store)->synchronize() ? RK_OK : RK_ERR_REFUSED; }
+uint64_t rk_slot_record_bytes(uint32_t label_bytes) { return model::recordBytesFor(label_bytes); }
+// One record / the record file's header as the file holds them (for readers of the format).
+int rk_slot_record_encode(uint32_t label_bytes, uint64_t payload_bytes, uint32_t checksum, const void *label, void *out) {
+  return guarded([&] {
+    const auto record = model::encodeRecord(model::recordBytesFor(label_bytes), payload_bytes, checksum, {static_cast<const uint8_t *>(label), label_bytes});
+    std::memcpy(out, record.data(), record.size());
+    return RK_OK;
+  });
+}
+int64_t rk_slot_records_header(uint64_t slot_bytes, uint32_t label_bytes, const void *tag, uint32_t tag_bytes, void *out, uint32_t capacity) {
+  try {
+    const auto header = model::encodeRecordsHeader(slot_bytes, label_bytes, {static_cast<const uint8_t *>(tag), tag_bytes});
+    if (header.size() > capacity) return RK_ERR_INVALID;
+    std::memcpy(out, header.data(), header.size());
+    return int64_t(header.size());
+  } catch (const std::exception &e) { rk::set_error(e.what()); return RK_ERR_INVALID; }
+}
+// Seals the cache's landed tier copies into the store; returns the slots written.
+int64_t rk_cache_persist(void *cache, void *store) {
+  int64_t written = 0;
+  const int status = guarded([&] { written = static_cast<CacheHandle *>(cache)->cache->persist(*static_cast<model::SlotStore *>(store)); return RK_OK; });
+  return status ? status : written;
+}
+// Takes back what an earlier process sealed; out = {blocks, dropped, bytes}.
+int rk_cache_adopt(void *cache, void *store, uint64_t *out) {
+  return guarded([&] {
+    const auto adoption = static_cast<CacheHandle *>(cache)->cache->adopt(*static_cast<model::SlotStore *>(store));
+    out[0] = adoption.blocks; out[1] = adoption.dropped; out[2] = adoption.bytes;
+    return RK_OK;
+  });
+}
 
 int rk_plan_verify(uint32_t lanes, uint32_t query_heads, uint32_t layers, uint32_t kv_heads, uint32_t head_dim, uint32_t format,
                    const uint32_t *history, int tree, uint32_t row_capacity, uint32_t ctas, char *names, size_t names_bytes, uint64_t *out) {

@@ -1,6 +1,8 @@
 #include "kv_cache.hpp"
 
 #include <algorithm>
+#include <cstring>
+#include <map>
 #include <stdexcept>
 
 namespace rkb::engine {
@@ -132,6 +134,43 @@ void PrefixIndex::adoptPage(uint64_t block, uint32_t page) {
   blockOnPage_[page] = block;
   ++resident_;
   if (entry.parent) ++at(entry.parent).residentChildren;
+}
+
+bool PrefixIndex::adoptTierBlock(uint64_t id, uint64_t parent, std::span<const uint32_t> tokens, ImageIdentity images,
+                                 std::shared_ptr<KvTierSlot> slot, uint64_t lastUsed) {
+  if (!id || id == ~0ull || blocks_.count(id) || tokens.size() != pageTokens || !slot) throw std::invalid_argument("invalid adopted KV cache block");
+  if (parent && !blocks_.count(parent)) throw std::invalid_argument("adopted KV cache block's parent is unknown");
+  if (find(parent, tokens, images)) return false;
+  Block entry;
+  entry.id = id;
+  entry.parent = parent;
+  entry.hash = blockHash(parent ? at(parent).hash : 0, tokens, images);
+  std::copy(tokens.begin(), tokens.end(), entry.tokens.begin());
+  entry.images = images;
+  entry.lastUsed = lastUsed;
+  entry.slot = std::move(slot);
+  index_.emplace(entry.hash, id);
+  blocks_.emplace(id, std::move(entry));
+  if (parent) ++at(parent).children;
+  nextId_ = std::max(nextId_, id + 1);
+  return true;
+}
+
+void PrefixIndex::continueAfter(uint64_t highestId, uint64_t lastUsed) noexcept {
+  nextId_ = std::max(nextId_, highestId + 1);
+  clock_ = std::max(clock_, lastUsed);
+}
+
+std::vector<std::pair<model::KvBlockLabel, std::shared_ptr<KvTierSlot>>> PrefixIndex::tierCopies() const {
+  std::vector<std::pair<model::KvBlockLabel, std::shared_ptr<KvTierSlot>>> copies;
+  for (const auto &[id, block] : blocks_) {
+    if (!block.slot || block.poisoned) continue;
+    if (block.transferring && block.page != noPage) continue; // a demotion that has not landed yet
+    model::KvBlockLabel label{block.id, block.parent, block.lastUsed, block.images.lo, block.images.hi, block.tokens};
+    copies.emplace_back(label, block.slot);
+  }
+  std::sort(copies.begin(), copies.end(), [](const auto &a, const auto &b) { return a.first.id < b.first.id; });
+  return copies;
 }
 
 void PrefixIndex::followPages(const KvPageMoves &moves) noexcept {
@@ -473,6 +512,72 @@ CacheSnapshot Cache::snapshot() const {
   result.residentBlocks = index_.residentBlocks();
   result.tierBlocks = index_.tierBlocks();
   result.transfers = uint32_t(demotions_.size() + restores_.size());
+  return result;
+}
+
+// ============================== persistence ====================================================
+uint32_t Cache::persist(model::SlotStore &store) {
+  if (!tier_) throw std::logic_error("only a cache with a tier keeps copies");
+  if (store.slotBytes() < tier_->slotBytes() || store.labelBytes() != sizeof(model::KvBlockLabel))
+    throw std::invalid_argument("the slot store was opened for another kind of slot");
+  if (!store.clear()) throw std::runtime_error("the slot store could not be emptied");
+  uint32_t written = 0;
+  for (const auto &[label, slot] : index_.tierCopies()) {
+    KvTier::SlotPayload payload;
+    if (!tier_->slotPayload(*slot, &payload)) continue;
+    const auto *bytes = static_cast<const uint8_t *>(payload.bytes);
+    const auto *raw = reinterpret_cast<const uint8_t *>(&label);
+    if (!store.write(written, {bytes, size_t(payload.size)}, payload.checksum, {raw, sizeof(label)}))
+      throw std::runtime_error("a slot write failed; the slots written so far keep their records");
+    ++written;
+  }
+  if (!store.synchronize()) throw std::runtime_error("the slot store could not be flushed");
+  return written;
+}
+
+Cache::Adoption Cache::adopt(model::SlotStore &store) {
+  if (!tier_) throw std::logic_error("a cache takes back copies only from a tier");
+  if (!requests_.empty() || index_.size()) throw std::logic_error("a cache takes back copies only before anything else is in it");
+  if (store.labelBytes() != sizeof(model::KvBlockLabel)) throw std::invalid_argument("the slot store holds another kind of label");
+  Adoption result;
+  struct Recorded { model::KvBlockLabel label; const model::SlotRecord *record = nullptr; uint32_t tokens = 0; };
+  std::map<uint64_t, Recorded> recorded;
+  uint64_t highestId = 0, lastUsed = 0;
+  for (const model::SlotRecord &record : store.records()) {
+    model::KvBlockLabel label;
+    const bool sized = record.label.size() == sizeof(label);
+    if (sized) {
+      std::memcpy(&label, record.label.data(), sizeof(label));
+      highestId = std::max(highestId, label.id);
+    }
+    if (!sized || !label.id || label.parent >= label.id || record.payloadBytes != tier_->slotBytes() ||
+        !recorded.emplace(label.id, Recorded{label, &record}).second) {
+      ++result.dropped;
+      store.free(record.index);
+    }
+  }
+  // A parent's id is lower than its children's, so a chain resolves in id order and a cycle cannot form.
+  std::vector<uint8_t> payload(tier_->slotBytes());
+  for (auto &[id, block] : recorded) {
+    bool taken = false;
+    const bool chained = !block.label.parent || (recorded.count(block.label.parent) && recorded.at(block.label.parent).tokens);
+    if (chained && store.read(block.record->index, payload)) {
+      if (auto slot = tier_->adoptSlot(payload.data(), payload.size(), block.record->checksum))
+        taken = index_.adoptTierBlock(id, block.label.parent, block.label.tokens, {block.label.imagesLo, block.label.imagesHi},
+                                      std::move(slot), block.label.lastUsed);
+    }
+    if (!taken) {
+      ++result.dropped;
+      store.free(block.record->index);
+      continue;
+    }
+    block.tokens = (block.label.parent ? recorded.at(block.label.parent).tokens : 0) + PrefixIndex::pageTokens;
+    lastUsed = std::max(lastUsed, block.label.lastUsed);
+    ++result.blocks;
+  }
+  // New ids continue after every id a record names, taken back or not.
+  index_.continueAfter(highestId, lastUsed);
+  result.bytes = uint64_t(result.blocks) * tier_->slotBytes();
   return result;
 }
 

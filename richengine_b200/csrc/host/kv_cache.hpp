@@ -15,6 +15,7 @@
 
 #include "kv_pool.hpp"
 #include "kv_tier.hpp"
+#include "slot_store.hpp"
 
 #include <array>
 #include <cstdint>
@@ -69,6 +70,14 @@ public:
   void poison(uint64_t block);
   void erase(uint64_t block); // only a block without children, users or transfer
   std::optional<Candidate> evictionCandidate() const; // oldest resident leaf no request uses
+  // Takes back a tier-only block an earlier process recorded (KvCache::adoptDiskBlock,
+  // runtime/engine/cache/KvCache.cpp:160-199): false when another block already holds its key.
+  bool adoptTierBlock(uint64_t id, uint64_t parent, std::span<const uint32_t> tokens, ImageIdentity images,
+                      std::shared_ptr<KvTierSlot> slot, uint64_t lastUsed);
+  // New ids and recency continue after everything a record names.
+  void continueAfter(uint64_t highestId, uint64_t lastUsed) noexcept;
+  // Every block whose tier copy has landed, in id order, as its record's label.
+  std::vector<std::pair<model::KvBlockLabel, std::shared_ptr<KvTierSlot>>> tierCopies() const;
   uint32_t residentBlocks() const noexcept { return resident_; }
   uint32_t tierBlocks() const noexcept;
   size_t size() const noexcept { return blocks_.size(); }
@@ -154,6 +163,18 @@ public:
   // Empties one extent (KvPool::compactExtent) and re-points every request and block.
   bool compactExtent();
   uint32_t pendingPages() const noexcept { return uint32_t(demotions_.size()); }
+
+  // Seals every landed tier copy into the store with its label (the record Cache::labelBlock keeps,
+  // runtime/engine/cache/Cache.cpp:852-870): payload, CRC-32C, KvBlockLabel. The store is rewritten whole and
+  // flushed. Returns the slots written.
+  uint32_t persist(model::SlotStore &store);
+  // Before anything else is in the cache: takes back the blocks an earlier process sealed (Cache::adopt,
+  // runtime/engine/cache/Cache.cpp:38-140): labels resolve in id order (a parent's id is lower than its
+  // children's), a block comes back only under an unbroken chain, a duplicate key or a damaged label stays
+  // behind, and the records that stay behind are freed. A payload is checked against its record's CRC-32C when
+  // it is first restored. Without the reference's composite-state layer every intact chain comes back.
+  struct Adoption { uint32_t blocks = 0, dropped = 0; uint64_t bytes = 0; };
+  Adoption adopt(model::SlotStore &store);
 
   PrefixIndex &index() noexcept { return index_; }
   CacheSnapshot snapshot() const;

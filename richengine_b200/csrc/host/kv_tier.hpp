@@ -38,6 +38,13 @@ public:
   virtual std::unique_ptr<KvTransfer> demote(uint32_t page, std::shared_ptr<KvTierSlot> slot) = 0;  // null = not now
   virtual std::unique_ptr<KvTransfer> restore(std::shared_ptr<KvTierSlot> slot, uint32_t page) = 0; // null = not now
   virtual void poll() = 0;
+  // Persistence (engine::KvTier::persistent / label, KvPageTier::adopt: runtime/engine/cache/KvTier.hpp:40-47,
+  // runtime/engine/cache/KvPageTier.hpp:38-43). A tier that can be sealed to a slot store exposes the host bytes
+  // of a landed slot with the CRC-32C taken when the page was packed, and takes a recorded payload back into a
+  // slot of its own whose first restore is checked against the record.
+  struct SlotPayload { const void *bytes = nullptr; uint64_t size = 0; uint32_t checksum = 0; };
+  virtual bool slotPayload(const KvTierSlot &, SlotPayload *) const { return false; }
+  virtual std::shared_ptr<KvTierSlot> adoptSlot(const void *, uint64_t, uint32_t) { return {}; }
 };
 
 // Pinned-host tier over the C ABI.
@@ -75,6 +82,17 @@ public:
     return std::make_unique<Ticket>(tier_, uint32_t(id), std::move(held));
   }
   void poll() override { rk_tier_poll(tier_); }
+  bool slotPayload(const KvTierSlot &slot, SlotPayload *out) const override {
+    const auto *held = dynamic_cast<const Slot *>(&slot);
+    if (!held) return false;
+    *out = {rk_tier_slot_host_pointer(tier_, held->id), rk_tier_slot_bytes(tier_), rk_tier_slot_checksum(tier_, held->id)};
+    return out->bytes != nullptr;
+  }
+  std::shared_ptr<KvTierSlot> adoptSlot(const void *payload, uint64_t bytes, uint32_t checksum) override {
+    const int64_t id = rk_tier_adopt_slot(tier_, payload, bytes, checksum);
+    if (id < 0) return {};
+    return std::make_shared<Slot>(tier_, uint32_t(id));
+  }
   void *handle() const noexcept { return tier_; }
   void failNext(uint32_t count) { rk_tier_fail_next(tier_, count); }
 

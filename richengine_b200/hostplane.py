@@ -141,11 +141,71 @@ class Cache:
                  "evicted_blocks", "fork_copies", "truncated_pages"]
         return dict(zip(names, out))
 
+    def persist(self, store: "SlotStore") -> int:
+        """Seals every landed tier copy into the store (payload, its device-computed CRC-32C, its KvBlockLabel)."""
+        return self._check(self._lib.rk_cache_persist(self._handle, store.handle), "persist")
+
+    def adopt(self, store: "SlotStore") -> dict:
+        """On an empty cache: takes back what an earlier process sealed. {blocks, dropped, bytes}."""
+        out = (C.c_uint64 * 3)()
+        self._check(self._lib.rk_cache_adopt(self._handle, store.handle, out), "adopt")
+        return {"blocks": out[0], "dropped": out[1], "bytes": out[2]}
+
     def block_state(self, block):
         out = (C.c_uint64 * 4)()
         if self._lib.rk_cache_block_state(self._handle, block, out) < 0:
             return None
         return {"page": out[0], "tier_copy": bool(out[1]), "transferring": bool(out[2]), "last_used": out[3]}
+
+
+KV_BLOCK_LABEL_BYTES = 168  # engine::KvBlockLabel: id, parent, lastUsed, images lo/hi (u64 each), 32 token ids (u32)
+
+
+def kv_block_label(block_id, parent, last_used, tokens, images=(0, 0)) -> bytes:
+    assert len(tokens) == 32
+    return np.array([block_id, parent, last_used, images[0], images[1]], dtype="<u8").tobytes() + np.asarray(tokens, dtype="<u4").tobytes()
+
+
+class SlotStore:
+    """Slots in one file and their records beside it, in the reference's byte format (model::SlotFile, persistent)."""
+
+    def __init__(self, slots_path, records_path, tag: bytes, label_bytes: int, slot_bytes: int):
+        self._lib = lib.load()
+        self.label_bytes, self.slot_bytes = label_bytes, slot_bytes
+        tag_buffer = C.create_string_buffer(tag, max(len(tag), 1))
+        self.handle = self._lib.rk_slot_store_open(str(slots_path).encode(), str(records_path).encode(), tag_buffer, len(tag),
+                                                   label_bytes, slot_bytes)
+        if not self.handle:
+            raise ValueError(self._lib.rk_last_error().decode())
+
+    def close(self):
+        if self.handle:
+            self._lib.rk_slot_store_close(self.handle)
+            self.handle = None
+
+    def records(self):
+        found = []
+        for at in range(self._lib.rk_slot_store_record_count(self.handle)):
+            index, size, checksum = C.c_uint32(), C.c_uint64(), C.c_uint32()
+            label = C.create_string_buffer(self.label_bytes)
+            self._lib.rk_slot_store_record(self.handle, at, C.byref(index), C.byref(size), C.byref(checksum), label)
+            found.append({"index": index.value, "payload_bytes": size.value, "checksum": checksum.value, "label": label.raw})
+        return found
+
+    def write(self, index, payload: np.ndarray, checksum: int, label: bytes) -> bool:
+        payload = np.ascontiguousarray(payload, dtype=np.uint8)
+        status = self._lib.rk_slot_store_write(self.handle, index, payload.ctypes.data, payload.size, checksum,
+                                               C.create_string_buffer(label, len(label)))
+        if status == lib.INVALID:
+            raise ValueError(self._lib.rk_last_error().decode())
+        return status == lib.OK
+
+    def read(self, index, size) -> np.ndarray | None:
+        out = np.empty(size, np.uint8)
+        return out if self._lib.rk_slot_store_read(self.handle, index, out.ctypes.data, size) == lib.OK else None
+
+    def free(self, index) -> bool: return self._lib.rk_slot_store_free(self.handle, index) == lib.OK
+    def synchronize(self) -> bool: return self._lib.rk_slot_store_synchronize(self.handle) == lib.OK
 
 
 def verify_plan(lanes, query_heads, layout, history, tree=False, row_capacity=0, ctas=0):

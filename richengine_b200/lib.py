@@ -63,6 +63,8 @@ SIGNATURES = {
     "rk_attention_verify_reduce": (i32, [u32, u32, u32, u32, u32, vp, vp, vp, vp, vp, vp]),
     "rk_qkv_prepare": (i32, [u32, u32, u32, u32, u32, vp, vp, vp, i32, vp, vp, C.c_float, vp, vp, vp, vp]),
     "rk_qkv_prepare_store": (i32, [u32, u32, u32, u32, u32, u32, vp, vp, vp, i32, vp, vp, C.c_float, vp, vp, vp, KvLayer, vp]),
+    "rk_crc32c_pages": (i32, [vp, u64, u64, u32, vp, u32, vp]),
+    "rk_crc32c_host": (u32, [vp, u64, u32]),
     "rk_attention_verify_reduce_gate": (i32, [u32, u32, u32, u32, u32, vp, vp, vp, vp, vp, vp, vp]),
     "rk_attention_prefill_split": (i32, [u32, u32, u32, u32, vp, vp, vp, vp, C.POINTER(PrefillParams), vp]),
     "rk_attention_prefill_split_tc": (i32, [vp, u32, u32, u32, u32, vp, vp, vp, vp, C.POINTER(PrefillParams), vp, vp]),
@@ -112,6 +114,8 @@ SIGNATURES = {
     "rk_tier_acquire_slot": (i64, [vp]),
     "rk_tier_release_slot": (None, [vp, u32]),
     "rk_tier_fail_next": (None, [vp, u32]),
+    "rk_tier_slot_checksum": (u32, [vp, u32]),
+    "rk_tier_adopt_slot": (i64, [vp, vp, u64, u32]),
     "rk_tier_slot_host_pointer": (vp, [vp, u32]),
     "rk_tier_demote": (i32, [vp, u32, u32, vp]),
     "rk_tier_restore": (i32, [vp, u32, u32, vp]),
@@ -152,6 +156,19 @@ SIGNATURES = {
     "rk_cache_fail_next_transfers": (None, [vp, u32]),
     "rk_cache_snapshot": (None, [vp, vp]),
     "rk_cache_block_state": (i32, [vp, u64, vp]),
+    "rk_slot_store_open": (vp, [C.c_char_p, C.c_char_p, vp, u32, u32, u64]),
+    "rk_slot_store_close": (None, [vp]),
+    "rk_slot_store_record_count": (u32, [vp]),
+    "rk_slot_store_record": (i32, [vp, u32, vp, vp, vp, vp]),
+    "rk_slot_store_write": (i32, [vp, u32, vp, u64, u32, vp]),
+    "rk_slot_store_read": (i32, [vp, u32, vp, u64]),
+    "rk_slot_store_free": (i32, [vp, u32]),
+    "rk_slot_store_synchronize": (i32, [vp]),
+    "rk_slot_record_bytes": (u64, [u32]),
+    "rk_slot_record_encode": (i32, [u32, u64, u32, vp, vp]),
+    "rk_slot_records_header": (i64, [u64, u32, vp, u32, vp, u32]),
+    "rk_cache_persist": (i64, [vp, vp]),
+    "rk_cache_adopt": (i32, [vp, vp, vp]),
     "rk_plan_window_splits": (i32, [u32, u32, u32, u32]),
     "rk_plan_verify": (i32, [u32, u32, u32, u32, u32, u32, vp, i32, u32, u32, C.c_char_p, C.c_size_t, vp]),
     "rk_plan_prefill": (i32, [u32, u32, u32, u32, u32, u32, C.c_char_p, C.c_size_t, vp]),

@@ -40,6 +40,8 @@ def oracle() -> C.CDLL:
         o.rko_copy_page.restype = None
         o.rko_copy_page.argtypes = [u32, u32, u32, u32, u32, u64, u64]
         o.rko_threads.restype = C.c_int
+        o.rko_crc32c.restype = C.c_uint32
+        o.rko_crc32c.argtypes = [vp, u64, u32]
         o.rko_qkv_prepare.restype = C.c_int
         o.rko_qkv_prepare.argtypes = [u32, u32, u32, u32, u32, vp, vp, vp, C.c_int, vp, vp, C.c_float, vp, vp, vp]
         _oracle = o

@@ -12,7 +12,7 @@ from gpuhelp import dev, struct_to_device
 from kvcase import HostPool, f32_to_bf16
 from richengine_b200 import lib, ops
 from richengine_b200.abi import INT4, INT8, Layout
-from richengine_b200.hostplane import GRANTED, NO_PAGE, Cache, KvPool
+from richengine_b200.hostplane import GRANTED, KV_BLOCK_LABEL_BYTES, NO_PAGE, Cache, KvPool, SlotStore
 from richengine_b200.storage import PageStorage
 
 pytestmark = pytest.mark.gpu
@@ -151,6 +151,67 @@ def test_evict_cold_pages_to_pinned_host_and_refetch():
         w.cache.poll_transfers()
     assert w.cache.snapshot()["failed_transfers"] == 1 and w.pool.snapshot()["pages_prefix"] == 6
     assert len(w.cache.lookup(ids)) == 8
+    w.close()
+
+
+def test_kv_survives_a_restart_through_the_slot_store(tmp_path):
+    """Every block goes to the pinned-host tier (its CRC-32C taken on the GPU when it is packed), the cache seals the
+    tier into a slot file, everything is torn down; new storage, pool, tier and cache adopt the file, a request matching
+    the prompt gets the bytes back exactly, and a payload changed on disk fails its first restore: a miss."""
+    layout = Layout(2, 4, 256, INT4)
+    tokens = 32 * 6
+    ids = np.random.default_rng(7).integers(0, 1000, size=tokens + 1, dtype=np.uint32)
+    w = World(layout, 256, 128, tier_slots=16)
+    w.cache.begin_request(1)
+    assert w.cache.ensure_tokens(1, tokens) == GRANTED
+    w.append(1, 0, tokens, mirror_too=False)
+    w.cache.publish(1, ids, tokens)
+    content = [w.device_page(p) for p in w.cache.page_table(1)[0]]
+    w.cache.end_request(1)
+    while w.cache.reclaim_one():
+        while w.cache.snapshot()["transfers"]:
+            w.cache.poll_transfers()
+    assert w.cache.snapshot()["tier_blocks"] == 6 and w.cache.snapshot()["resident_blocks"] == 0
+    slot_bytes = (w.storage.bytes_per_page() + 4095) // 4096 * 4096
+    files = dict(slots_path=tmp_path / "kv.slots", records_path=tmp_path / "kv.records", tag=b"int4 2x4x256",
+                 label_bytes=KV_BLOCK_LABEL_BYTES, slot_bytes=slot_bytes)
+    store = SlotStore(**files)
+    assert w.cache.persist(store) == 6
+    store.close()
+    w.close()
+
+    # the record's checksum is the device's CRC-32C of the packed page: the checker agrees on the file's bytes
+    store = SlotStore(**files)
+    records = store.records()
+    assert len(records) == 6
+    for record, page in zip(records, content):
+        payload = store.read(record["index"], record["payload_bytes"])
+        assert record["payload_bytes"] == len(page) and np.array_equal(payload, page)
+        assert record["checksum"] == om.oracle().rko_crc32c(payload.ctypes.data, len(payload), 0)
+    store.close()
+    with open(tmp_path / "kv.slots", "r+b") as f:  # one bit of the fifth block's payload changes on disk
+        f.seek(records[4]["index"] * slot_bytes + 12345)
+        byte = f.read(1)
+        f.seek(records[4]["index"] * slot_bytes + 12345)
+        f.write(bytes([byte[0] ^ 1]))
+
+    w = World(layout, 256, 128, tier_slots=16)
+    store = SlotStore(**files)
+    assert w.cache.adopt(store) == {"blocks": 6, "dropped": 0, "bytes": 6 * w.storage.bytes_per_page()}
+    chain = w.cache.lookup(ids)
+    assert len(chain) == 6
+    w.cache.begin_request(2)
+    status, resume = w.cache.attach_prefix(2, chain)
+    assert status == GRANTED and resume == tokens
+    while w.cache.restores_pending(2):
+        w.cache.poll_transfers()
+    assert w.cache.snapshot()["failed_transfers"] == 1  # the changed payload did not match its record
+    restored = w.cache.page_table(2)[0]
+    for i in range(4):
+        assert np.array_equal(w.device_page(restored[i]), content[i]), i
+    assert len(w.cache.lookup(ids)) == 4                 # the chain ends before the damaged block
+    w.cache.end_request(2)
+    store.close()
     w.close()
 
 
