@@ -57,7 +57,8 @@ def parse():
                     help="stored KV format of the decode workload (the headline is int4)")
     ap.add_argument("--rows", type=int, default=16, choices=[8, 16], help="--mode verify: window rows per sequence")
     ap.add_argument("--chunk", type=int, default=2048, help="--mode prefill: rows of the prefill chunk")
-    ap.add_argument("--mode", default="requests", choices=["requests", "seqsplit", "verify", "prefill"],
+    ap.add_argument("--pages", type=int, default=2048, help="--mode seal: model pages sealed per step")
+    ap.add_argument("--mode", default="requests", choices=["requests", "seqsplit", "verify", "prefill", "seal"],
                     help="requests: every rank runs its own batch (default); seqsplit: ONE sequence of --context "
                          "tokens split along the sequence over the ranks, all-gather of (max, sum, O), rank-order merge")
     return ap.parse_args()
@@ -756,6 +757,116 @@ def run_prefill(args):
     runner.close()
 
 
+def run_seal(args):
+    """Sealing model pages for the persistent tier: per step, pack --pages pages of an int4 pool (all layers) into
+    contiguous slots and take each slot's CRC-32C on the GPU; end to end the slots and checksums also cross to pinned
+    host memory. The dominant kernel is the checksum. One GPU."""
+    import torch
+
+    from richengine_b200 import lib
+    from richengine_b200.abi import INT4, Layout
+    from richengine_b200.storage import PageStorage
+
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    library = lib.load()
+    layout = Layout(args.layers, KV_HEADS, HEAD_DIM, INT4)
+    count = args.pages
+    extent_pages = layout.minimum_extent_pages()
+    extents = (count + extent_pages - 1) // extent_pages
+    storage = PageStorage(layout, extents * extent_pages, extent_pages)
+    for extent in range(extents):
+        if not storage.allocate_extent(extent):
+            raise RuntimeError("KV pool does not fit in device memory")
+        raw = torch.randint(0, 256, (storage.extent_bytes(),), dtype=torch.uint8, device="cuda")
+        storage.write_extent(extent, raw.cpu().numpy())
+    page_bytes = storage.bytes_per_page()
+    ids = np.random.default_rng(3).permutation(extents * extent_pages)[:count].astype(np.uint32)
+    slots = torch.empty(count * page_bytes, dtype=torch.uint8, device="cuda")
+    sums = torch.zeros(count, dtype=torch.int32, device="cuda")
+    host_slots = torch.empty(count * page_bytes, dtype=torch.uint8, pin_memory=True)
+    host_sums = torch.zeros(count, dtype=torch.int32, pin_memory=True)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def seal():
+        lib.check(library.rk_storage_pack_pages(storage.handle, ids.ctypes.data, count, slots.data_ptr(), 0, stream), "pack")
+        lib.check(library.rk_crc32c_pages(slots.data_ptr(), page_bytes, page_bytes, count, sums.data_ptr(), 0, stream), "checksum")
+
+    def seal_to_host():
+        seal()
+        host_slots.copy_(slots, non_blocking=True)
+        host_sums.copy_(sums, non_blocking=True)
+
+    for _ in range(args.warmup):
+        seal_to_host()
+    torch.cuda.synchronize()
+    # one slot against the checker before anything is timed
+    probe = host_slots[:page_bytes].numpy()
+    sys.path.insert(0, str(ROOT / "tests"))
+    subprocess.run(["make", "-C", str(ROOT / "oracle"), "-s"], check=True)
+    import oracle as om  # the checker: the cpu_baseline leg and one probe
+    want = om.oracle().rko_crc32c(probe.ctypes.data, page_bytes, 0)
+    if int(host_sums[0].item()) & 0xffffffff != want:
+        raise RuntimeError("device CRC-32C differs from the checker")
+    sampler = ClockSampler(torch.cuda.current_device())
+    begin_wall = time.perf_counter()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        seal()
+    stop.record()
+    torch.cuda.synchronize()
+    device_ms = start.elapsed_time(stop) / args.steps
+    start.record()
+    for _ in range(args.steps):
+        seal_to_host()
+    stop.record()
+    torch.cuda.synchronize()
+    host_ms = start.elapsed_time(stop) / args.steps
+    events = []
+    for repeat in range(6):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        lib.check(library.rk_crc32c_pages(slots.data_ptr(), page_bytes, page_bytes, count, sums.data_ptr(), 0, stream), "checksum")
+        b.record()
+        if repeat:
+            events.append((a, b))
+    torch.cuda.synchronize()
+
+    def same_load():
+        seal()
+        torch.cuda.synchronize()
+    sampler.keep_loaded(begin_wall, same_load)
+    clocks = sampler.stop(begin_wall, time.perf_counter())
+    kernel_ms = statistics.mean(a.elapsed_time(b) for a, b in events)
+    total = count * page_bytes
+    # the checker on the host cores, one thread, on a bounded sample of the same slots
+    sample_pages = max(1, min(count, int(args.cpu_seconds * 0.25e9) // page_bytes))
+    view = host_slots[:sample_pages * page_bytes].numpy()
+    t0 = time.perf_counter()
+    for i in range(sample_pages):
+        om.oracle().rko_crc32c(view[i * page_bytes:].ctypes.data, page_bytes, 0)
+    cpu_seconds = time.perf_counter() - t0
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    peak = float(json.loads(peaks_path.read_text())["hbm_gbs"]) if peaks_path.exists() else 6650.0
+    print(json.dumps({
+        "metric": "int4_model_page_seal_gbps", "value": round(total / (device_ms * 1e-3) / 1e9, 1), "unit": "GB/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(device_ms, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "u8 (CRC-32C over GF(2), 32-bit remainders)", "data": "synthetic",
+        "config": {"workload": f"seal {count} model pages of an int4 pool ({args.layers} layers, {page_bytes} B each): pack the page's spans "
+                               f"into a slot + CRC-32C of the slot, on the device", "l2": f"{total / 1e6:.0f} MB per step, larger than L2"},
+        "roofline": {"bound": "hbm", "achieved": round(total / (kernel_ms * 1e-3) / 1e9, 1), "peak": peak, "unit": "GB/s",
+                     "frac": round(total / (kernel_ms * 1e-3) / 1e9 / peak, 4), "traffic": None,
+                     "peak_source": "measured (MEASURED_PEAKS.json hbm_gbs)" if peaks_path.exists() else "fallback",
+                     "kernel": "crc32c_kernel", "us_per_launch": round(kernel_ms * 1e3, 2), "algorithmic_bytes_per_launch": total},
+        "e2e": {"value": round(total / (host_ms * 1e-3) / 1e9, 2), "unit": "GB/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": total + 4 * count, "ms_per_step": round(host_ms, 4)},
+        "cpu_baseline": {"value": round(sample_pages * page_bytes / cpu_seconds / 1e9, 3), "unit": "GB/s", "cores": 1, "kind": "port",
+                         "sample": f"bit-at-a-time CRC-32C of {sample_pages} of the same slots"},
+        "gpu_launches": 2 * args.steps, "clocks": clocks,
+    }), flush=True)
+    storage.close()
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -770,6 +881,8 @@ def main():
         run_prefill(args)
     elif args.mode == "seqsplit":
         run_seqsplit(args)
+    elif args.mode == "seal":
+        run_seal(args)
     else:
         run_ours(args)
 

@@ -92,6 +92,15 @@ __device__ __forceinline__ uint32_t lookup4(const uint32_t *table, uint32_t x) {
   return table[x & 0xffu] ^ table[256 + ((x >> 8) & 0xffu)] ^ table[512 + ((x >> 16) & 0xffu)] ^ table[768 + (x >> 24)];
 }
 
+// Entry (Byte, value of that byte of x) of the lane's copy of the row-step table: one byte permute, one multiply-add
+// for the address (the multiply-add pipe is otherwise idle here, the logic pipe is the busy one), one load.
+template <uint32_t Byte> __device__ __forceinline__ uint32_t row_lookup(uint32_t x, uint32_t lane_copy) {
+  uint32_t address, value;
+  asm("mad.lo.u32 %0, %1, 128, %2;" : "=r"(address) : "r"(__byte_perm(x, 0, 0x4440u + Byte)), "r"(lane_copy));
+  asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(value) : "r"(address), "n"(Byte * 256 * 128));
+  return value;
+}
+
 __device__ __forceinline__ uint32_t mul_mod_device(uint32_t a, uint32_t b) {
   uint32_t product = 0;
 #pragma unroll
@@ -111,7 +120,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) crc32c_kernel(const __grid_con
   for (uint32_t i = tid; i < kTableWords * 32; i += blockDim.x) replica[i] = g_tables[i >> 5];
   for (uint32_t i = tid; i < (kTables - 1) * kTableWords; i += blockDim.x) tables[i] = g_tables[kTableWords + i];
   __syncthreads();
-  const uint32_t *mine = replica + lane; // this lane's copy: entry e at mine[32 e]
+  // this lane's copy: entry e at byte 128 e behind it
+  const uint32_t mine_shared = uint32_t(__cvta_generic_to_shared(replica + lane));
   const uint32_t units = args.payloads * args.parts;
   for (uint32_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
     const uint32_t payload = unit / args.parts, part = unit - payload * args.parts;
@@ -122,15 +132,15 @@ __global__ void __launch_bounds__(kWarps * 32, 1) crc32c_kernel(const __grid_con
     if (rows) {
       const uint4 *source = reinterpret_cast<const uint4 *>(args.data + uint64_t(payload) * args.stride + first_row * kRowBytes) + lane;
       uint32_t acc[4] = {0, 0, 0, 0};
-      uint4 next = __ldcs(source);
+      uint4 next = __ldcs(source); // one row ahead (a second row in flight measured slower: the kernel sits at 64 registers)
       for (uint32_t row = 0; row + 1 < rows; ++row) {
         const uint4 v = next;
         next = __ldcs(source + uint64_t(row + 1) * 32);
         const uint32_t x[4] = {acc[0] ^ v.x, acc[1] ^ v.y, acc[2] ^ v.z, acc[3] ^ v.w};
 #pragma unroll
         for (uint32_t k = 0; k < 4; ++k)
-          acc[k] = mine[(x[k] & 0xffu) << 5] ^ mine[(256u + ((x[k] >> 8) & 0xffu)) << 5] ^
-                   mine[(512u + ((x[k] >> 16) & 0xffu)) << 5] ^ mine[(768u + (x[k] >> 24)) << 5];
+          acc[k] = row_lookup<0>(x[k], mine_shared) ^ row_lookup<1>(x[k], mine_shared) ^ row_lookup<2>(x[k], mine_shared) ^
+                   row_lookup<3>(x[k], mine_shared);
       }
       // the last row enters without the row step: the 128 remainders now form a 128-word message
       uint32_t c = lookup4(tables, acc[0] ^ next.x) ^ acc[1] ^ next.y;
