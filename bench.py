@@ -646,7 +646,7 @@ def run_verify(args):
         "roofline": {"bound": "tensor", "achieved": round(flops / (kernel_ms * 1e-3) / 1e12, 1), "peak": peak, "unit": "TFLOP/s",
                      "frac": round(flops / (kernel_ms * 1e-3) / 1e12 / peak, 4), "traffic": None,
                      "peak_source": "measured (MEASURED_PEAKS.json bf16_tflops)" if peaks_path.exists() else "fallback",
-                     "kernel": "verify_int4_kernel", "us_per_launch": round(kernel_ms * 1e3, 2),
+                     "kernel": "window_attention_kernel", "us_per_launch": round(kernel_ms * 1e3, 2),
                      "algorithmic_flops_per_launch": flops,
                      "kv_gbps_of_launch": round(layer_tokens * layout.bytes_per_token_layer() / (kernel_ms * 1e-3) / 1e9, 1)},
         "gpu_launches": 3 * args.layers * args.steps, "clocks": clocks,
