@@ -28,8 +28,10 @@ namespace {
 
 constexpr uint32_t kPoly = 0x82F63B78u; // reflected Castagnoli polynomial
 constexpr uint32_t kRowBytes = 512;     // one warp step: 32 lanes x 16 bytes
-constexpr uint32_t kWarps = 32;
-constexpr uint32_t kMaxParts = 16;      // CTAs that may share one payload
+constexpr uint32_t kWarps = 32;         // per CTA
+constexpr uint32_t kGroupWarps = 8;     // warps that share one payload part; a CTA runs kWarps / kGroupWarps parts at a time
+constexpr uint32_t kGroups = kWarps / kGroupWarps;
+constexpr uint32_t kMaxParts = 64;      // parts a payload may be cut into
 
 // Polynomials are bit-reversed as in the usual software CRC: bit 31 is x^0.
 constexpr uint32_t mul_mod(uint32_t a, uint32_t b) {
@@ -82,7 +84,7 @@ struct ChecksumArgs {
   uint32_t payloads, parts;
   uint32_t rows_low, extra; // chunk g of a payload has rows_low + (g < extra) rows
   uint32_t closing;       // the initial and final inversions as one term
-  uint32_t multiplier[kMaxParts * kWarps]; // x^(8 * bytes after chunk g)
+  uint32_t multiplier[kMaxParts * kGroupWarps]; // x^(8 * bytes after chunk g)
 };
 
 constexpr uint32_t kReplicaBytes = kTableWords * 32 * 4;                       // the row-step table, one copy per bank
@@ -122,10 +124,13 @@ __global__ void __launch_bounds__(kWarps * 32, 1) crc32c_kernel(const __grid_con
   __syncthreads();
   // this lane's copy: entry e at byte 128 e behind it
   const uint32_t mine_shared = uint32_t(__cvta_generic_to_shared(replica + lane));
+  // Each group of eight warps takes (payload, part) units on its own; long chunks keep the fold of the 128
+  // remainders (whose tables are not replicated) a small share of the lookups.
+  const uint32_t group = warp / kGroupWarps, member = warp % kGroupWarps;
   const uint32_t units = args.payloads * args.parts;
-  for (uint32_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
+  for (uint32_t unit = blockIdx.x * kGroups + group; unit < units; unit += gridDim.x * kGroups) {
     const uint32_t payload = unit / args.parts, part = unit - payload * args.parts;
-    const uint32_t chunk = part * kWarps + warp;
+    const uint32_t chunk = part * kGroupWarps + member;
     const uint32_t rows = args.rows_low + (chunk < args.extra ? 1u : 0u);
     const uint64_t first_row = uint64_t(chunk) * args.rows_low + min(chunk, args.extra);
     uint32_t term = 0;
@@ -154,14 +159,14 @@ __global__ void __launch_bounds__(kWarps * 32, 1) crc32c_kernel(const __grid_con
       if (lane == 0) term = mul_mod_device(lookup4(tables, c), args.multiplier[chunk]);
     }
     if (lane == 0) warp_terms[warp] = term;
-    __syncthreads();
-    if (warp == 0) {
-      uint32_t sum = warp_terms[lane];
+    asm volatile("bar.sync %0, %1;" ::"r"(1u + group), "r"(kGroupWarps * 32u) : "memory");
+    if (member == 0) {
+      uint32_t sum = lane < kGroupWarps ? warp_terms[warp + lane] : 0u;
 #pragma unroll
-      for (uint32_t o = 16; o; o >>= 1) sum ^= __shfl_xor_sync(0xffffffffu, sum, o);
+      for (uint32_t o = kGroupWarps / 2; o; o >>= 1) sum ^= __shfl_xor_sync(0xffffffffu, sum, o);
       if (lane == 0) atomicXor(args.out + payload, part == 0 ? sum ^ args.closing : sum);
     }
-    __syncthreads();
+    asm volatile("bar.sync %0, %1;" ::"r"(1u + group), "r"(kGroupWarps * 32u) : "memory");
   }
 }
 
@@ -221,7 +226,7 @@ int launch_crc32c(const void *data, uint64_t stride, uint64_t payload_bytes, uin
   if (!ctas) ctas = uint32_t(multiprocessors[device]);
   const uint64_t rows = payload_bytes / kRowBytes;
   // enough parts to occupy the grid, never chunks of less than four rows
-  const uint32_t parts = uint32_t(std::max<uint64_t>(1, std::min<uint64_t>({uint64_t(kMaxParts), (uint64_t(ctas) + count - 1) / count, rows / (4 * kWarps)})));
+  const uint32_t parts = uint32_t(std::max<uint64_t>(1, std::min<uint64_t>({uint64_t(kMaxParts), (uint64_t(ctas) * kGroups + count - 1) / count, rows / (4 * kGroupWarps)})));
   // The multipliers depend only on (payload size, parts): the last launch's set is kept.
   static ChecksumArgs cached{};
   static uint64_t cached_bytes = 0;
@@ -230,7 +235,7 @@ int launch_crc32c(const void *data, uint64_t stride, uint64_t payload_bytes, uin
     std::lock_guard<std::mutex> lock(guard);
     if (cached_bytes != payload_bytes || cached.parts != parts) {
       cached.parts = parts;
-      const uint64_t chunks = uint64_t(parts) * kWarps;
+      const uint64_t chunks = uint64_t(parts) * kGroupWarps;
       cached.rows_low = uint32_t(rows / chunks);
       cached.extra = uint32_t(rows % chunks);
       // chunks have one of two lengths; walk from the last chunk backwards
@@ -252,7 +257,7 @@ int launch_crc32c(const void *data, uint64_t stride, uint64_t payload_bytes, uin
   args.out = out;
   args.payloads = count;
   if (int st = cuda_status(cudaMemsetAsync(out, 0, uint64_t(count) * 4, stream), "checksum clear")) return st;
-  const uint32_t grid = uint32_t(std::min<uint64_t>(ctas, uint64_t(count) * args.parts));
+  const uint32_t grid = uint32_t(std::min<uint64_t>(ctas, (uint64_t(count) * args.parts + kGroups - 1) / kGroups));
   crc32c_kernel<<<grid, kWarps * 32, kSharedBytes, stream>>>(args);
   return cuda_status(cudaGetLastError(), "checksum launch");
 }
