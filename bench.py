@@ -151,6 +151,8 @@ def run_reference(args):
     build here). Rank 0 only."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
+    # all the host threads it can use: torchrun presets OMP_NUM_THREADS=1 for its workers
+    os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
     sample = CpuSample(min(args.batch, 16), args.context)
     for _ in range(max(args.warmup, 1)):
         sample.run_once()
