@@ -36,6 +36,8 @@
 #include <cuda.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 namespace rk {
 
 struct DriverApi;
@@ -58,6 +60,18 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 static_assert(kStageBytes % 1024 == 0, "stages keep the 1 KiB swizzle alignment");
 
+#ifdef RK_TRACE
+__device__ unsigned long long g_trace[256 * 8];
+__device__ __forceinline__ void trace(uint32_t slot) {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  g_trace[blockIdx.x * 8 + slot] = t;
+}
+#define RK_TRACE_POINT(slot, condition) do { if (condition) trace(slot); } while (0)
+#else
+#define RK_TRACE_POINT(slot, condition) do { } while (0)
+#endif
+
 struct DecodeArgs {
   const uint16_t *queries;
   float *partials;
@@ -68,6 +82,12 @@ struct DecodeArgs {
   rk_kv_layer layer;
   uint64_t window_base;
   uint32_t lanes;
+  // The merge inside the decode kernel: the CTA that completes a lane's last segment merges the lane.
+  // `counters` null = leave the partials for a merge kernel.
+  uint32_t *counters;   // [lanes], zeroed before the launch
+  uint16_t *output;     // bf16 [lane][kv_head][32][group][D], row 0
+  float *output_f32;    // optional, the value before rounding
+  float *triples;       // instead of output: {max, sum, un-normalised output} per (lane, query head)
 };
 
 __device__ __forceinline__ uint32_t smem_address(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -190,6 +210,7 @@ struct Shared {
   uint32_t scan[kThreads / 32 + 1];
   float unit_scales[kScaleBytes / 4 + kPageTokens]; // ones: the scale rows of a format without scales
   volatile uint32_t error;
+  uint32_t merge_lane; // epilogue: this CTA wrote the last segment of the lane in turn
 };
 
 // Block-wide exclusive prefix sum of values[0..n) in place (values[n] = total).
@@ -299,6 +320,76 @@ __device__ __forceinline__ void group_barrier(uint32_t id, uint32_t threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+// One (lane, query head) merged by one warp: the fixed-order merge of decode_reduce_kernel (maximum over all slots,
+// weights exp(m_s - M), numerator and denominator accumulated in slot order), 8 dimensions per lane.
+__device__ void merge_query_head(const DecodeArgs &args, uint32_t l, uint32_t head, uint32_t query_head, uint32_t first,
+                                 uint32_t segments, float *weights, uint32_t lane) {
+  constexpr uint32_t kMaxSlots = 64;
+  const uint32_t slots = segments * kPageWarps;
+  auto slot_of = [&](uint32_t s) { return (uint64_t(first + s / kPageWarps) * kKvHeads + head) * kPageWarps + s % kPageWarps; };
+  float maximum = -INFINITY;
+  for (uint32_t t = lane; t < slots; t += 32) maximum = fmaxf(maximum, __ldcg(args.statistics + (slot_of(t) * kGroup + query_head) * 2));
+  maximum = warp_max(maximum);
+  float numerator[8] = {0, 0, 0, 0, 0, 0, 0, 0}, denominator = 0.0f;
+  for (uint32_t base = 0; base < slots; base += kMaxSlots) {
+    const uint32_t count = min(kMaxSlots, slots - base);
+    __syncwarp();
+    for (uint32_t t = lane; t < count; t += 32) {
+      const float own = __ldcg(args.statistics + (slot_of(base + t) * kGroup + query_head) * 2);
+      weights[t] = own == -INFINITY ? 0.0f : expf(own - maximum);
+    }
+    __syncwarp();
+    for (uint32_t s = 0; s < count; ++s) { // slot order
+      const uint64_t slot = slot_of(base + s);
+      const float weight = weights[s];
+      denominator += weight * __ldcg(args.statistics + (slot * kGroup + query_head) * 2 + 1);
+      const float *partial = args.partials + (slot * kGroup + query_head) * kHeadDim + lane;
+#pragma unroll
+      for (uint32_t j = 0; j < 8; ++j) numerator[j] += weight * __ldcg(partial + 32 * j);
+    }
+  }
+  if (args.triples) {
+    float *triple = args.triples + ((uint64_t(l) * kKvHeads + head) * kGroup + query_head) * (kHeadDim + 2);
+    if (lane == 0) { triple[0] = maximum; triple[1] = denominator; }
+#pragma unroll
+    for (uint32_t j = 0; j < 8; ++j) triple[2 + lane + 32 * j] = numerator[j];
+    return;
+  }
+  const uint64_t tile = ((uint64_t(l) * kKvHeads + head) * RK_VERIFY_CHUNK_STRIDE) * kGroup * kHeadDim + query_head * kHeadDim + lane;
+#pragma unroll
+  for (uint32_t j = 0; j < 8; ++j) {
+    const float value = denominator > 0.0f ? numerator[j] / denominator : 0.0f;
+    args.output[tile + 32 * j] = float_to_bf16_bits(value);
+    if (args.output_f32) args.output_f32[tile + 32 * j] = value;
+  }
+}
+
+// After a CTA's consumer warps have flushed every partial: for each lane the CTA's range touches, count this CTA in;
+// the CTA that completes the count merges the lane (its twelve warps take two query heads each). Every CTA of a
+// lane adds exactly once, so the merge runs exactly once, reads only complete partials, and its result does not
+// depend on which CTA ran it. `scratch` is shared memory the consumer warps no longer need (64 floats per warp).
+__device__ void merge_epilogue(const DecodeArgs &args, Shared &sh, uint32_t first_lane, uint32_t range_begin, uint32_t range_end,
+                               float *scratch, uint32_t warp, uint32_t lane) {
+  if (!args.counters) return;
+  __threadfence(); // this thread's partials and statistics are visible before the CTA is counted in
+  group_barrier(5, kConsumerWarps * 32);
+  if (sh.error) return; // a step that timed out reports through the status word; its lanes stay unmerged
+  for (uint32_t l = first_lane; l < args.lanes && sh.lane_start[l] < range_end; ++l) {
+    const uint32_t lane_begin = sh.lane_start[l], lane_end = sh.lane_start[l + 1];
+    if (min(range_end, lane_end) <= max(range_begin, lane_begin) || lane_end <= range_begin) continue;
+    const uint32_t first = sh.segment_base[l], segments = sh.segment_base[l + 1] - first;
+    if (warp == 0 && lane == 0) sh.merge_lane = atomicAdd(args.counters + l, 1u) + 1 == segments ? 1u : 0u;
+    group_barrier(5, kConsumerWarps * 32);
+    const bool last = sh.merge_lane != 0;
+    if (last) {
+      __threadfence(); // the other CTAs' partials, published before their counts
+      for (uint32_t item = warp; item < kKvHeads * kGroup; item += kConsumerWarps)
+        merge_query_head(args, l, item / kGroup, item % kGroup, first, segments, scratch + warp * 64, lane);
+    }
+    group_barrier(5, kConsumerWarps * 32); // before the flag is written again
+  }
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs args) {
   extern __shared__ uint8_t dynamic_shared[];
@@ -308,6 +399,7 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
   const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const uint32_t lanes = args.lanes, cta = blockIdx.x;
   uint32_t *error_word = args.descriptors + 2 * lanes;
+  RK_TRACE_POINT(0, tid == 0);
   dependents_may_launch(); // the merge kernel's blocks may take their places; they wait for this grid to finish
   dependency_wait();       // pages, queries and parameters may come from the kernel before this one
 
@@ -358,6 +450,7 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
     first_lane = lo;
   }
 
+  RK_TRACE_POINT(1, tid == 0);
   if (warp == kConsumerWarps) {
     // ================= producer: one thread streams whole pages =============================
     if (lane != 0) return;
@@ -601,6 +694,10 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
       }
     }
   }
+  RK_TRACE_POINT(3, tid == 0);
+  // every consumer warp is past its lanes: the query fragments' shared memory serves the merge
+  merge_epilogue(args, sh, first_lane, range_begin, range_end, reinterpret_cast<float *>(&sh.query[0][0][0]), warp, lane);
+  RK_TRACE_POINT(4, tid == 0);
 }
 
 // ---- one-byte formats (int8, fp8 e4m3): the same streaming kernel with 8 KiB slabs and three stages -----------------
@@ -937,6 +1034,8 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
       }
     }
   }
+  // every consumer warp is past its lanes: the query fragments' shared memory serves the merge
+  merge_epilogue(args, sh, first_lane, range_begin, range_end, reinterpret_cast<float *>(&sh.query[0][0][0]), warp, lane);
 }
 
 // ---- bf16 pools: (page, KV head) units of 16 KiB keys + 16 KiB values, six stages, no scales --------------------------
@@ -1210,6 +1309,8 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
       }
     }
   }
+  // every consumer warp is past its lanes: the query fragments' shared memory serves the merge
+  merge_epilogue(args, sh, first_lane, range_begin, range_end, reinterpret_cast<float *>(&sh.query[0][0][0]), warp, lane);
 }
 
 // Merge one query head's partials in slot order (segment, then warp) and store bf16 (and
@@ -1224,6 +1325,9 @@ decode_reduce_kernel(const float *__restrict__ partials, const float *__restrict
   __shared__ float denominator_shared, maximum_shared;
   const uint32_t query_head = blockIdx.x, head = blockIdx.y, l = blockIdx.z, tid = threadIdx.x;
   dependency_wait(); // partials, statistics and descriptors come from the decode kernel launched just before
+#ifdef RK_TRACE
+  if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); g_trace[200 * 8 + (blockIdx.z & 7)] = t; }
+#endif
   rk_verify_params p = lane_params[l];
   p.kv = layer;
   if (!rk_verify_contract_valid(&p) || p.active_rows != 1 || p.row_capacity != 1) return;
@@ -1344,14 +1448,41 @@ static int launch_merge(uint32_t lanes, cudaStream_t stream, const float *partia
                      "decode reduce launch");
 }
 
-// The streaming kernel of a format on `ctas` CTAs.
-static int launch_decode(uint32_t format, uint32_t ctas, cudaStream_t s, const Window *w, const DecodeArgs &args) {
+// The streaming kernel of a format on `ctas` CTAs, then the merge as a programmatic dependent launch behind it.
+// RK_DECODE_FUSED_MERGE=1 in the environment moves the merge into the decode kernel (the CTA that completes a lane
+// merges it): one launch less, but the lanes' merges then all sit in the kernel's tail, and with a few CTAs per lane
+// that measured slower (416 us against 404 us per layer on 64 x 32 768 int4 tokens), so it is not the default.
+static bool fused_merge() {
+  static const bool value = [] { const char *v = getenv("RK_DECODE_FUSED_MERGE"); return v && v[0] == '1'; }();
+  return value;
+}
+static int launch_decode(uint32_t format, uint32_t ctas, cudaStream_t s, const Window *w, DecodeArgs args, uint32_t *descriptors,
+                         uint16_t *output, float *output_f32, float *triples, const rk_verify_params *lane_params, rk_kv_layer layer) {
+  const bool fused = fused_merge();
+  // status word (and the words beside it), then one merge counter per lane
+  if (int st = cuda_status(cudaMemsetAsync(descriptors + 2 * args.lanes, 0, (4 + size_t(args.lanes)) * sizeof(uint32_t), s), "decode status clear")) return st;
+  args.counters = fused ? descriptors + 2 * args.lanes + 4 : nullptr;
+  args.output = output;
+  args.output_f32 = output_f32;
+  args.triples = triples;
   if (format == RK_FORMAT_INT4) decode_int4_kernel<<<ctas, kThreads, kDecodeSharedBytes, s>>>(w->int4_map, args);
   else if (format == RK_FORMAT_INT8) decode_bytes_kernel<false><<<ctas, kThreads, kByteDecodeSharedBytes, s>>>(w->int4_map, args);
   else if (format == RK_FORMAT_FP8E4M3) decode_bytes_kernel<true><<<ctas, kThreads, kByteDecodeSharedBytes, s>>>(w->int4_map, args);
   else decode_bf16_kernel<<<ctas, kThreads, kWideDecodeSharedBytes, s>>>(w->int4_map, args);
-  return cuda_status(cudaGetLastError(), "decode launch");
+  if (int st = cuda_status(cudaGetLastError(), "decode launch")) return st;
+  if (fused) return kOk;
+  if (triples) {
+    decode_reduce_kernel<<<dim3(kGroup, kKvHeads, args.lanes), 256, 0, s>>>(args.partials, args.statistics, descriptors, nullptr, nullptr, lane_params, layer, triples);
+    return cuda_status(cudaGetLastError(), "decode shard reduce launch");
+  }
+  return launch_merge(args.lanes, s, args.partials, args.statistics, descriptors, output, output_f32, lane_params, layer, nullptr);
 }
+
+#ifdef RK_TRACE
+extern "C" int rk_debug_trace(unsigned long long *out) {
+  return cuda_status(cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace)), "trace");
+}
+#endif
 
 extern "C" {
 
@@ -1377,7 +1508,7 @@ int rk_decode_plan_make(uint32_t format, uint32_t kv_heads, uint32_t query_heads
   const uint64_t slots = uint64_t(plan->max_segments) * kKvHeads * kPageWarps;
   plan->partials_bytes = slots * kGroup * kHeadDim * sizeof(float);
   plan->statistics_bytes = slots * kGroup * 2 * sizeof(float);
-  plan->descriptor_bytes = (2ull * lanes + 4) * sizeof(uint32_t);
+  plan->descriptor_bytes = (3ull * lanes + 4) * sizeof(uint32_t); // {first segment, segments} per lane, status, merge counters
   return kOk;
 }
 
@@ -1413,9 +1544,7 @@ int rk_attention_decode(const void *window, const rk_decode_plan *plan, uint32_t
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (int st = configure_decode_kernel()) return st;
   DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, plan->lanes};
-  if (int st = cuda_status(cudaMemsetAsync(descriptors + 2 * plan->lanes, 0, sizeof(uint32_t), s), "decode status clear")) return st;
-  if (int st = launch_decode(format, plan->ctas, s, w, args)) return st;
-  return launch_merge(plan->lanes, s, partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer, nullptr);
+  return launch_decode(format, plan->ctas, s, w, args, descriptors, static_cast<uint16_t *>(output), output_f32, nullptr, lane_params, layer);
 }
 
 // One rank's part of a sequence-split decode: attention over the pages this rank holds, left as
@@ -1434,10 +1563,7 @@ int rk_attention_decode_shard(const void *window, const rk_decode_plan *plan, ui
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (int st = configure_decode_kernel()) return st;
   DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, plan->lanes};
-  if (int st = cuda_status(cudaMemsetAsync(descriptors + 2 * plan->lanes, 0, sizeof(uint32_t), s), "decode status clear")) return st;
-  if (int st = launch_decode(format, plan->ctas, s, w, args)) return st;
-  decode_reduce_kernel<<<dim3(kGroup, kKvHeads, plan->lanes), 256, 0, s>>>(partials, statistics, descriptors, nullptr, nullptr, lane_params, layer, triples);
-  return cuda_status(cudaGetLastError(), "decode shard reduce launch");
+  return launch_decode(format, plan->ctas, s, w, args, descriptors, nullptr, nullptr, triples, lane_params, layer);
 }
 
 // Merges `shards` gathered triples ([shard][lane][query_head][2 + D]) in shard order into the bf16
@@ -1458,7 +1584,7 @@ constexpr uint32_t kStaticLanes = 16, kStaticCtas = 148;
 constexpr size_t kStaticSlots = size_t(kStaticLanes + kStaticCtas) * kKvHeads * kPageWarps;
 constexpr size_t kStaticPartialBytes = kStaticSlots * kGroup * kHeadDim * sizeof(float);
 constexpr size_t kStaticStatisticBytes = (kStaticSlots * kGroup * 2 * sizeof(float) + 255) / 256 * 256;
-constexpr size_t kStaticDescriptorBytes = ((2 * kStaticLanes + 4) * sizeof(uint32_t) + 255) / 256 * 256;
+constexpr size_t kStaticDescriptorBytes = ((3 * kStaticLanes + 4) * sizeof(uint32_t) + 255) / 256 * 256;
 static __device__ __align__(256) unsigned char g_decode_scratch[kStaticPartialBytes + kStaticStatisticBytes + kStaticDescriptorBytes];
 
 // rk_attention_decode for callers that must not allocate device memory: an engine that gave the
@@ -1503,10 +1629,7 @@ int rk_attention_decode_static(const void *window, uint32_t format, uint32_t lan
   uint32_t *descriptors = reinterpret_cast<uint32_t *>(base + kStaticPartialBytes + kStaticStatisticBytes);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, lanes};
-  if (int st = cuda_status(cudaMemsetAsync(descriptors + 2 * lanes, 0, sizeof(uint32_t), s), "decode status clear")) return st;
-  if (int st = launch_decode(format, kStaticCtas, s, w, args)) return st;
-  decode_reduce_kernel<<<dim3(kGroup, kKvHeads, lanes), 256, 0, s>>>(partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer, nullptr);
-  return cuda_status(cudaGetLastError(), "decode reduce launch");
+  return launch_decode(format, kStaticCtas, s, w, args, descriptors, static_cast<uint16_t *>(output), output_f32, nullptr, lane_params, layer);
 }
 
 // Reads the step's device status word (synchronises the stream): 0, or kTimeout
