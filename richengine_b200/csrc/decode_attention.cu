@@ -321,31 +321,42 @@ __device__ __forceinline__ void group_barrier(uint32_t id, uint32_t threads) {
 }
 
 // One (lane, query head) merged by one warp: the fixed-order merge of decode_reduce_kernel (maximum over all slots,
-// weights exp(m_s - M), numerator and denominator accumulated in slot order), 8 dimensions per lane.
+// weights exp(m_s - M), numerator and denominator accumulated in slot order), 8 dimensions per lane. Lane t holds
+// the statistics of slot base + t and hands its weight round by shuffle; the partials of four slots are requested
+// together, so a lane's merge costs a handful of round trips to L2 rather than one per slot.
 __device__ void merge_query_head(const DecodeArgs &args, uint32_t l, uint32_t head, uint32_t query_head, uint32_t first,
-                                 uint32_t segments, float *weights, uint32_t lane) {
-  constexpr uint32_t kMaxSlots = 64;
+                                 uint32_t segments, uint32_t lane) {
   const uint32_t slots = segments * kPageWarps;
   auto slot_of = [&](uint32_t s) { return (uint64_t(first + s / kPageWarps) * kKvHeads + head) * kPageWarps + s % kPageWarps; };
+  auto statistics_of = [&](uint32_t s) {
+    return __ldcg(reinterpret_cast<const float2 *>(args.statistics + (slot_of(s) * kGroup + query_head) * 2));
+  };
   float maximum = -INFINITY;
-  for (uint32_t t = lane; t < slots; t += 32) maximum = fmaxf(maximum, __ldcg(args.statistics + (slot_of(t) * kGroup + query_head) * 2));
+  for (uint32_t t = lane; t < slots; t += 32) maximum = fmaxf(maximum, statistics_of(t).x);
   maximum = warp_max(maximum);
   float numerator[8] = {0, 0, 0, 0, 0, 0, 0, 0}, denominator = 0.0f;
-  for (uint32_t base = 0; base < slots; base += kMaxSlots) {
-    const uint32_t count = min(kMaxSlots, slots - base);
-    __syncwarp();
-    for (uint32_t t = lane; t < count; t += 32) {
-      const float own = __ldcg(args.statistics + (slot_of(base + t) * kGroup + query_head) * 2);
-      weights[t] = own == -INFINITY ? 0.0f : expf(own - maximum);
-    }
-    __syncwarp();
-    for (uint32_t s = 0; s < count; ++s) { // slot order
-      const uint64_t slot = slot_of(base + s);
-      const float weight = weights[s];
-      denominator += weight * __ldcg(args.statistics + (slot * kGroup + query_head) * 2 + 1);
-      const float *partial = args.partials + (slot * kGroup + query_head) * kHeadDim + lane;
+  for (uint32_t base = 0; base < slots; base += 32) {
+    const uint32_t count = min(32u, slots - base);
+    const float2 own = lane < count ? statistics_of(base + lane) : make_float2(-INFINITY, 0.0f);
+    const float weight_own = own.x == -INFINITY ? 0.0f : expf(own.x - maximum);
+    for (uint32_t s = 0; s < count; s += 4) { // slot order; four slots' loads in flight
+      float value[4][8];
 #pragma unroll
-      for (uint32_t j = 0; j < 8; ++j) numerator[j] += weight * __ldcg(partial + 32 * j);
+      for (uint32_t i = 0; i < 4; ++i) {
+        const float *partial = args.partials + (slot_of(base + min(s + i, count - 1)) * kGroup + query_head) * kHeadDim + lane;
+#pragma unroll
+        for (uint32_t j = 0; j < 8; ++j) value[i][j] = __ldcg(partial + 32 * j);
+      }
+#pragma unroll
+      for (uint32_t i = 0; i < 4; ++i) {
+        const float weight = __shfl_sync(0xffffffffu, weight_own, (s + i) & 31u);
+        const float sum = __shfl_sync(0xffffffffu, own.y, (s + i) & 31u);
+        if (s + i < count) {
+          denominator += weight * sum;
+#pragma unroll
+          for (uint32_t j = 0; j < 8; ++j) numerator[j] += weight * value[i][j];
+        }
+      }
     }
   }
   if (args.triples) {
@@ -367,9 +378,9 @@ __device__ void merge_query_head(const DecodeArgs &args, uint32_t l, uint32_t he
 // After a CTA's consumer warps have flushed every partial: for each lane the CTA's range touches, count this CTA in;
 // the CTA that completes the count merges the lane (its twelve warps take two query heads each). Every CTA of a
 // lane adds exactly once, so the merge runs exactly once, reads only complete partials, and its result does not
-// depend on which CTA ran it. `scratch` is shared memory the consumer warps no longer need (64 floats per warp).
+// depend on which CTA ran it.
 __device__ void merge_epilogue(const DecodeArgs &args, Shared &sh, uint32_t first_lane, uint32_t range_begin, uint32_t range_end,
-                               float *scratch, uint32_t warp, uint32_t lane) {
+                               uint32_t warp, uint32_t lane) {
   if (!args.counters) return;
   __threadfence(); // this thread's partials and statistics are visible before the CTA is counted in
   group_barrier(5, kConsumerWarps * 32);
@@ -384,7 +395,7 @@ __device__ void merge_epilogue(const DecodeArgs &args, Shared &sh, uint32_t firs
     if (last) {
       __threadfence(); // the other CTAs' partials, published before their counts
       for (uint32_t item = warp; item < kKvHeads * kGroup; item += kConsumerWarps)
-        merge_query_head(args, l, item / kGroup, item % kGroup, first, segments, scratch + warp * 64, lane);
+        merge_query_head(args, l, item / kGroup, item % kGroup, first, segments, lane);
     }
     group_barrier(5, kConsumerWarps * 32); // before the flag is written again
   }
@@ -695,8 +706,7 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
     }
   }
   RK_TRACE_POINT(3, tid == 0);
-  // every consumer warp is past its lanes: the query fragments' shared memory serves the merge
-  merge_epilogue(args, sh, first_lane, range_begin, range_end, reinterpret_cast<float *>(&sh.query[0][0][0]), warp, lane);
+  merge_epilogue(args, sh, first_lane, range_begin, range_end, warp, lane);
   RK_TRACE_POINT(4, tid == 0);
 }
 
@@ -1034,8 +1044,7 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
       }
     }
   }
-  // every consumer warp is past its lanes: the query fragments' shared memory serves the merge
-  merge_epilogue(args, sh, first_lane, range_begin, range_end, reinterpret_cast<float *>(&sh.query[0][0][0]), warp, lane);
+  merge_epilogue(args, sh, first_lane, range_begin, range_end, warp, lane);
 }
 
 // ---- bf16 pools: (page, KV head) units of 16 KiB keys + 16 KiB values, six stages, no scales --------------------------
@@ -1309,8 +1318,7 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
       }
     }
   }
-  // every consumer warp is past its lanes: the query fragments' shared memory serves the merge
-  merge_epilogue(args, sh, first_lane, range_begin, range_end, reinterpret_cast<float *>(&sh.query[0][0][0]), warp, lane);
+  merge_epilogue(args, sh, first_lane, range_begin, range_end, warp, lane);
 }
 
 // Merge one query head's partials in slot order (segment, then warp) and store bf16 (and
@@ -1450,8 +1458,9 @@ static int launch_merge(uint32_t lanes, cudaStream_t stream, const float *partia
 
 // The streaming kernel of a format on `ctas` CTAs, then the merge as a programmatic dependent launch behind it.
 // RK_DECODE_FUSED_MERGE=1 in the environment moves the merge into the decode kernel (the CTA that completes a lane
-// merges it): one launch less, but the lanes' merges then all sit in the kernel's tail, and with a few CTAs per lane
-// that measured slower (416 us against 404 us per layer on 64 x 32 768 int4 tokens), so it is not the default.
+// merges it): one launch less, but the lanes' merges then all sit in the kernel's tail on twelve warps each, about ten
+// round trips to L2, and that measured slower (413 us against 404 us per layer on 64 x 32 768 int4 tokens) than the
+// dependent launch, whose 1 536 blocks hide that latency; so it is not the default.
 static bool fused_merge() {
   static const bool value = [] { const char *v = getenv("RK_DECODE_FUSED_MERGE"); return v && v[0] == '1'; }();
   return value;
