@@ -36,8 +36,6 @@
 #include <cuda.h>
 #include <cuda_fp16.h>
 
-#include <cstdlib>
-
 namespace rk {
 
 struct DriverApi;
@@ -60,18 +58,6 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 static_assert(kStageBytes % 1024 == 0, "stages keep the 1 KiB swizzle alignment");
 
-#ifdef RK_TRACE
-__device__ unsigned long long g_trace[256 * 8];
-__device__ __forceinline__ void trace(uint32_t slot) {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  g_trace[blockIdx.x * 8 + slot] = t;
-}
-#define RK_TRACE_POINT(slot, condition) do { if (condition) trace(slot); } while (0)
-#else
-#define RK_TRACE_POINT(slot, condition) do { } while (0)
-#endif
-
 struct DecodeArgs {
   const uint16_t *queries;
   float *partials;
@@ -82,12 +68,6 @@ struct DecodeArgs {
   rk_kv_layer layer;
   uint64_t window_base;
   uint32_t lanes;
-  // The merge inside the decode kernel: the CTA that completes a lane's last segment merges the lane.
-  // `counters` null = leave the partials for a merge kernel.
-  uint32_t *counters;   // [lanes], zeroed before the launch
-  uint16_t *output;     // bf16 [lane][kv_head][32][group][D], row 0
-  float *output_f32;    // optional, the value before rounding
-  float *triples;       // instead of output: {max, sum, un-normalised output} per (lane, query head)
 };
 
 __device__ __forceinline__ uint32_t smem_address(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -210,7 +190,6 @@ struct Shared {
   uint32_t scan[kThreads / 32 + 1];
   float unit_scales[kScaleBytes / 4 + kPageTokens]; // ones: the scale rows of a format without scales
   volatile uint32_t error;
-  uint32_t merge_lane; // epilogue: this CTA wrote the last segment of the lane in turn
 };
 
 // Block-wide exclusive prefix sum of values[0..n) in place (values[n] = total).
@@ -320,87 +299,6 @@ __device__ __forceinline__ void group_barrier(uint32_t id, uint32_t threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-// One (lane, query head) merged by one warp: the fixed-order merge of decode_reduce_kernel (maximum over all slots,
-// weights exp(m_s - M), numerator and denominator accumulated in slot order), 8 dimensions per lane. Lane t holds
-// the statistics of slot base + t and hands its weight round by shuffle; the partials of four slots are requested
-// together, so a lane's merge costs a handful of round trips to L2 rather than one per slot.
-__device__ void merge_query_head(const DecodeArgs &args, uint32_t l, uint32_t head, uint32_t query_head, uint32_t first,
-                                 uint32_t segments, uint32_t lane) {
-  const uint32_t slots = segments * kPageWarps;
-  auto slot_of = [&](uint32_t s) { return (uint64_t(first + s / kPageWarps) * kKvHeads + head) * kPageWarps + s % kPageWarps; };
-  auto statistics_of = [&](uint32_t s) {
-    return __ldcg(reinterpret_cast<const float2 *>(args.statistics + (slot_of(s) * kGroup + query_head) * 2));
-  };
-  float maximum = -INFINITY;
-  for (uint32_t t = lane; t < slots; t += 32) maximum = fmaxf(maximum, statistics_of(t).x);
-  maximum = warp_max(maximum);
-  float numerator[8] = {0, 0, 0, 0, 0, 0, 0, 0}, denominator = 0.0f;
-  for (uint32_t base = 0; base < slots; base += 32) {
-    const uint32_t count = min(32u, slots - base);
-    const float2 own = lane < count ? statistics_of(base + lane) : make_float2(-INFINITY, 0.0f);
-    const float weight_own = own.x == -INFINITY ? 0.0f : expf(own.x - maximum);
-    for (uint32_t s = 0; s < count; s += 4) { // slot order; four slots' loads in flight
-      float value[4][8];
-#pragma unroll
-      for (uint32_t i = 0; i < 4; ++i) {
-        const float *partial = args.partials + (slot_of(base + min(s + i, count - 1)) * kGroup + query_head) * kHeadDim + lane;
-#pragma unroll
-        for (uint32_t j = 0; j < 8; ++j) value[i][j] = __ldcg(partial + 32 * j);
-      }
-#pragma unroll
-      for (uint32_t i = 0; i < 4; ++i) {
-        const float weight = __shfl_sync(0xffffffffu, weight_own, (s + i) & 31u);
-        const float sum = __shfl_sync(0xffffffffu, own.y, (s + i) & 31u);
-        if (s + i < count) {
-          denominator += weight * sum;
-#pragma unroll
-          for (uint32_t j = 0; j < 8; ++j) numerator[j] += weight * value[i][j];
-        }
-      }
-    }
-  }
-  if (args.triples) {
-    float *triple = args.triples + ((uint64_t(l) * kKvHeads + head) * kGroup + query_head) * (kHeadDim + 2);
-    if (lane == 0) { triple[0] = maximum; triple[1] = denominator; }
-#pragma unroll
-    for (uint32_t j = 0; j < 8; ++j) triple[2 + lane + 32 * j] = numerator[j];
-    return;
-  }
-  const uint64_t tile = ((uint64_t(l) * kKvHeads + head) * RK_VERIFY_CHUNK_STRIDE) * kGroup * kHeadDim + query_head * kHeadDim + lane;
-#pragma unroll
-  for (uint32_t j = 0; j < 8; ++j) {
-    const float value = denominator > 0.0f ? numerator[j] / denominator : 0.0f;
-    args.output[tile + 32 * j] = float_to_bf16_bits(value);
-    if (args.output_f32) args.output_f32[tile + 32 * j] = value;
-  }
-}
-
-// After a CTA's consumer warps have flushed every partial: for each lane the CTA's range touches, count this CTA in;
-// the CTA that completes the count merges the lane (its twelve warps take two query heads each). Every CTA of a
-// lane adds exactly once, so the merge runs exactly once, reads only complete partials, and its result does not
-// depend on which CTA ran it.
-__device__ void merge_epilogue(const DecodeArgs &args, Shared &sh, uint32_t first_lane, uint32_t range_begin, uint32_t range_end,
-                               uint32_t warp, uint32_t lane) {
-  if (!args.counters) return;
-  __threadfence(); // this thread's partials and statistics are visible before the CTA is counted in
-  group_barrier(5, kConsumerWarps * 32);
-  if (sh.error) return; // a step that timed out reports through the status word; its lanes stay unmerged
-  for (uint32_t l = first_lane; l < args.lanes && sh.lane_start[l] < range_end; ++l) {
-    const uint32_t lane_begin = sh.lane_start[l], lane_end = sh.lane_start[l + 1];
-    if (min(range_end, lane_end) <= max(range_begin, lane_begin) || lane_end <= range_begin) continue;
-    const uint32_t first = sh.segment_base[l], segments = sh.segment_base[l + 1] - first;
-    if (warp == 0 && lane == 0) sh.merge_lane = atomicAdd(args.counters + l, 1u) + 1 == segments ? 1u : 0u;
-    group_barrier(5, kConsumerWarps * 32);
-    const bool last = sh.merge_lane != 0;
-    if (last) {
-      __threadfence(); // the other CTAs' partials, published before their counts
-      for (uint32_t item = warp; item < kKvHeads * kGroup; item += kConsumerWarps)
-        merge_query_head(args, l, item / kGroup, item % kGroup, first, segments, lane);
-    }
-    group_barrier(5, kConsumerWarps * 32); // before the flag is written again
-  }
-}
-
 __global__ void __launch_bounds__(kThreads, 1)
 decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs args) {
   extern __shared__ uint8_t dynamic_shared[];
@@ -410,7 +308,6 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
   const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const uint32_t lanes = args.lanes, cta = blockIdx.x;
   uint32_t *error_word = args.descriptors + 2 * lanes;
-  RK_TRACE_POINT(0, tid == 0);
   dependents_may_launch(); // the merge kernel's blocks may take their places; they wait for this grid to finish
   dependency_wait();       // pages, queries and parameters may come from the kernel before this one
 
@@ -461,7 +358,6 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
     first_lane = lo;
   }
 
-  RK_TRACE_POINT(1, tid == 0);
   if (warp == kConsumerWarps) {
     // ================= producer: one thread streams whole pages =============================
     if (lane != 0) return;
@@ -705,9 +601,6 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
       }
     }
   }
-  RK_TRACE_POINT(3, tid == 0);
-  merge_epilogue(args, sh, first_lane, range_begin, range_end, warp, lane);
-  RK_TRACE_POINT(4, tid == 0);
 }
 
 // ---- one-byte formats (int8, fp8 e4m3): the same streaming kernel with 8 KiB slabs and three stages -----------------
@@ -1044,7 +937,6 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
       }
     }
   }
-  merge_epilogue(args, sh, first_lane, range_begin, range_end, warp, lane);
 }
 
 // ---- bf16 pools: (page, KV head) units of 16 KiB keys + 16 KiB values, six stages, no scales --------------------------
@@ -1318,7 +1210,6 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
       }
     }
   }
-  merge_epilogue(args, sh, first_lane, range_begin, range_end, warp, lane);
 }
 
 // Merge one query head's partials in slot order (segment, then warp) and store bf16 (and
@@ -1333,9 +1224,6 @@ decode_reduce_kernel(const float *__restrict__ partials, const float *__restrict
   __shared__ float denominator_shared, maximum_shared;
   const uint32_t query_head = blockIdx.x, head = blockIdx.y, l = blockIdx.z, tid = threadIdx.x;
   dependency_wait(); // partials, statistics and descriptors come from the decode kernel launched just before
-#ifdef RK_TRACE
-  if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); g_trace[200 * 8 + (blockIdx.z & 7)] = t; }
-#endif
   rk_verify_params p = lane_params[l];
   p.kv = layer;
   if (!rk_verify_contract_valid(&p) || p.active_rows != 1 || p.row_capacity != 1) return;
@@ -1456,42 +1344,14 @@ static int launch_merge(uint32_t lanes, cudaStream_t stream, const float *partia
                      "decode reduce launch");
 }
 
-// The streaming kernel of a format on `ctas` CTAs, then the merge as a programmatic dependent launch behind it.
-// RK_DECODE_FUSED_MERGE=1 in the environment moves the merge into the decode kernel (the CTA that completes a lane
-// merges it): one launch less, but the lanes' merges then all sit in the kernel's tail on twelve warps each, about ten
-// round trips to L2, and that measured slower (413 us against 404 us per layer on 64 x 32 768 int4 tokens) than the
-// dependent launch, whose 1 536 blocks hide that latency; so it is not the default.
-static bool fused_merge() {
-  static const bool value = [] { const char *v = getenv("RK_DECODE_FUSED_MERGE"); return v && v[0] == '1'; }();
-  return value;
-}
-static int launch_decode(uint32_t format, uint32_t ctas, cudaStream_t s, const Window *w, DecodeArgs args, uint32_t *descriptors,
-                         uint16_t *output, float *output_f32, float *triples, const rk_verify_params *lane_params, rk_kv_layer layer) {
-  const bool fused = fused_merge();
-  // status word (and the words beside it), then one merge counter per lane
-  if (int st = cuda_status(cudaMemsetAsync(descriptors + 2 * args.lanes, 0, (4 + size_t(args.lanes)) * sizeof(uint32_t), s), "decode status clear")) return st;
-  args.counters = fused ? descriptors + 2 * args.lanes + 4 : nullptr;
-  args.output = output;
-  args.output_f32 = output_f32;
-  args.triples = triples;
+// The streaming kernel of a format on `ctas` CTAs.
+static int launch_decode(uint32_t format, uint32_t ctas, cudaStream_t s, const Window *w, const DecodeArgs &args) {
   if (format == RK_FORMAT_INT4) decode_int4_kernel<<<ctas, kThreads, kDecodeSharedBytes, s>>>(w->int4_map, args);
   else if (format == RK_FORMAT_INT8) decode_bytes_kernel<false><<<ctas, kThreads, kByteDecodeSharedBytes, s>>>(w->int4_map, args);
   else if (format == RK_FORMAT_FP8E4M3) decode_bytes_kernel<true><<<ctas, kThreads, kByteDecodeSharedBytes, s>>>(w->int4_map, args);
   else decode_bf16_kernel<<<ctas, kThreads, kWideDecodeSharedBytes, s>>>(w->int4_map, args);
-  if (int st = cuda_status(cudaGetLastError(), "decode launch")) return st;
-  if (fused) return kOk;
-  if (triples) {
-    decode_reduce_kernel<<<dim3(kGroup, kKvHeads, args.lanes), 256, 0, s>>>(args.partials, args.statistics, descriptors, nullptr, nullptr, lane_params, layer, triples);
-    return cuda_status(cudaGetLastError(), "decode shard reduce launch");
-  }
-  return launch_merge(args.lanes, s, args.partials, args.statistics, descriptors, output, output_f32, lane_params, layer, nullptr);
+  return cuda_status(cudaGetLastError(), "decode launch");
 }
-
-#ifdef RK_TRACE
-extern "C" int rk_debug_trace(unsigned long long *out) {
-  return cuda_status(cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace)), "trace");
-}
-#endif
 
 extern "C" {
 
@@ -1517,7 +1377,7 @@ int rk_decode_plan_make(uint32_t format, uint32_t kv_heads, uint32_t query_heads
   const uint64_t slots = uint64_t(plan->max_segments) * kKvHeads * kPageWarps;
   plan->partials_bytes = slots * kGroup * kHeadDim * sizeof(float);
   plan->statistics_bytes = slots * kGroup * 2 * sizeof(float);
-  plan->descriptor_bytes = (3ull * lanes + 4) * sizeof(uint32_t); // {first segment, segments} per lane, status, merge counters
+  plan->descriptor_bytes = (2ull * lanes + 4) * sizeof(uint32_t);
   return kOk;
 }
 
@@ -1553,7 +1413,9 @@ int rk_attention_decode(const void *window, const rk_decode_plan *plan, uint32_t
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (int st = configure_decode_kernel()) return st;
   DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, plan->lanes};
-  return launch_decode(format, plan->ctas, s, w, args, descriptors, static_cast<uint16_t *>(output), output_f32, nullptr, lane_params, layer);
+  if (int st = cuda_status(cudaMemsetAsync(descriptors + 2 * plan->lanes, 0, sizeof(uint32_t), s), "decode status clear")) return st;
+  if (int st = launch_decode(format, plan->ctas, s, w, args)) return st;
+  return launch_merge(plan->lanes, s, partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer, nullptr);
 }
 
 // One rank's part of a sequence-split decode: attention over the pages this rank holds, left as
@@ -1572,7 +1434,10 @@ int rk_attention_decode_shard(const void *window, const rk_decode_plan *plan, ui
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (int st = configure_decode_kernel()) return st;
   DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, plan->lanes};
-  return launch_decode(format, plan->ctas, s, w, args, descriptors, nullptr, nullptr, triples, lane_params, layer);
+  if (int st = cuda_status(cudaMemsetAsync(descriptors + 2 * plan->lanes, 0, sizeof(uint32_t), s), "decode status clear")) return st;
+  if (int st = launch_decode(format, plan->ctas, s, w, args)) return st;
+  decode_reduce_kernel<<<dim3(kGroup, kKvHeads, plan->lanes), 256, 0, s>>>(partials, statistics, descriptors, nullptr, nullptr, lane_params, layer, triples);
+  return cuda_status(cudaGetLastError(), "decode shard reduce launch");
 }
 
 // Merges `shards` gathered triples ([shard][lane][query_head][2 + D]) in shard order into the bf16
@@ -1593,7 +1458,7 @@ constexpr uint32_t kStaticLanes = 16, kStaticCtas = 148;
 constexpr size_t kStaticSlots = size_t(kStaticLanes + kStaticCtas) * kKvHeads * kPageWarps;
 constexpr size_t kStaticPartialBytes = kStaticSlots * kGroup * kHeadDim * sizeof(float);
 constexpr size_t kStaticStatisticBytes = (kStaticSlots * kGroup * 2 * sizeof(float) + 255) / 256 * 256;
-constexpr size_t kStaticDescriptorBytes = ((3 * kStaticLanes + 4) * sizeof(uint32_t) + 255) / 256 * 256;
+constexpr size_t kStaticDescriptorBytes = ((2 * kStaticLanes + 4) * sizeof(uint32_t) + 255) / 256 * 256;
 static __device__ __align__(256) unsigned char g_decode_scratch[kStaticPartialBytes + kStaticStatisticBytes + kStaticDescriptorBytes];
 
 // rk_attention_decode for callers that must not allocate device memory: an engine that gave the
@@ -1638,7 +1503,10 @@ int rk_attention_decode_static(const void *window, uint32_t format, uint32_t lan
   uint32_t *descriptors = reinterpret_cast<uint32_t *>(base + kStaticPartialBytes + kStaticStatisticBytes);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, lanes};
-  return launch_decode(format, kStaticCtas, s, w, args, descriptors, static_cast<uint16_t *>(output), output_f32, nullptr, lane_params, layer);
+  if (int st = cuda_status(cudaMemsetAsync(descriptors + 2 * lanes, 0, sizeof(uint32_t), s), "decode status clear")) return st;
+  if (int st = launch_decode(format, kStaticCtas, s, w, args)) return st;
+  decode_reduce_kernel<<<dim3(kGroup, kKvHeads, lanes), 256, 0, s>>>(partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer, nullptr);
+  return cuda_status(cudaGetLastError(), "decode reduce launch");
 }
 
 // Reads the step's device status word (synchronises the stream): 0, or kTimeout

@@ -15,7 +15,6 @@ events between the streams). finish_host() makes the compute stream wait for the
 from __future__ import annotations
 
 import ctypes as C
-import os
 
 import torch
 
@@ -50,24 +49,22 @@ class DecodeSession:
         # every format decodes on its streaming kernel
         self.attention = ops.DecodeAttention(layout, query_heads, lanes, storage.window(), ctas)
         self.layers = storage.layers()
-        self.attention_launches = 1 if os.environ.get("RK_DECODE_FUSED_MERGE", "")[:1] == "1" else 2
         self.kernel_launches = 0
 
     def close(self):
         self.attention.close()
 
     def step_device(self, layer: int, table_pointers, chunk_params, verify_params, stream=None) -> None:
-        """Store row 0 of the stagings at each lane's committed position, then attend (3 kernels: store, decode, merge;
-        2 when RK_DECODE_FUSED_MERGE=1 moves the merge into the decode kernel)."""
+        """Store row 0 of the stagings at each lane's committed position, then attend (3 kernels)."""
         place = self.layers[layer]
         ops.store_verify(self.layout, self.chunk_keys, self.chunk_values, table_pointers, chunk_params, place,
                          self.lanes, 1, stream)
         self.attention.run(self.queries, self.output, table_pointers, verify_params, place, stream=stream)
-        self.kernel_launches += 1 + self.attention_launches
+        self.kernel_launches += 3
 
     def attend_device(self, layer: int, table_pointers, verify_params, stream=None) -> None:
         self.attention.run(self.queries, self.output, table_pointers, verify_params, self.layers[layer], stream=stream)
-        self.kernel_launches += self.attention_launches
+        self.kernel_launches += 2
 
     def step_host(self, layer: int, q_host, k_host, v_host, out_host, table_pointers, chunk_params, verify_params,
                   stream=None) -> None:

@@ -48,6 +48,21 @@ def test_partition_independent_of_grid(ctas, fmt):
     s.close()
 
 
+@pytest.mark.parametrize("fmt,repeats", [(INT4, 100), (INT8, 30), (FP8E4M3, 30), (BF16, 30)])
+@pytest.mark.parametrize("ctas", [1, 3])
+def test_small_grids_give_the_same_bits_every_time(ctas, fmt, repeats):
+    """One CTA walks several whole lanes back to back (lanes of 22, 2, 47 and 3 pages): every repeat must give the bits
+    of the first, and those must meet the bar. (A build whose code generation differed failed this one run in five.)"""
+    s, q = prepared([700, 33, 1500, 64], seed=9, fmt=fmt)
+    _, want32 = run_verify_attention_oracle(s, q, 1, 1)
+    first16, first32 = run_decode_attention_gpu(s, q, ctas=ctas)
+    assert_attention_close(first32, want32, first16, f"ctas {ctas}")
+    for repeat in range(repeats):
+        got16, got32 = run_decode_attention_gpu(s, q, ctas=ctas)
+        assert np.array_equal(got32, first32) and np.array_equal(got16, first16), f"repeat {repeat} differs"
+    s.close()
+
+
 @pytest.mark.parametrize("fmt", STREAMING)
 def test_decode_repeatable_and_agrees_with_general_tile(fmt):
     s, q = prepared([3000, 257, 8191], seed=11, layers=2, layer=1, fmt=fmt)
