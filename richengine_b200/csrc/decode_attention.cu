@@ -565,6 +565,9 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
                     sub_f16x2(and_xor(cd, kHighNibbles, kMagicHigh), kMagicHigh), pb_frag[s][0], pb_frag[s][1]);
           }
       }
+      // Every lane's reads of the stage are performed before the warp gives it back: the warps that share a scheduler
+      // with the producer release last, and their stage is refilled at once.
+      __threadfence_block();
       __syncwarp();
       if (lane == 0) barrier_arrive(smem_address(&sh.empty[slot]));
     }
@@ -902,6 +905,9 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
           mma_f16(o[t], a0, a1, a2, a3, pb_frag[s][0], pb_frag[s][1]);
         }
       }
+      // Every lane's reads of the stage are performed before the warp gives it back: the warps that share a scheduler
+      // with the producer release last, and their stage is refilled at once.
+      __threadfence_block();
       __syncwarp();
       if (lane == 0) barrier_arrive(smem_address(&sh.empty[slot]));
     }
@@ -1175,6 +1181,9 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
           mma_bf16(o[t], a0, a1, a2, a3, pb_low[s][0], pb_low[s][1]);
         }
       }
+      // Every lane's reads of the stage are performed before the warp gives it back: the warps that share a scheduler
+      // with the producer release last, and their stage is refilled at once.
+      __threadfence_block();
       __syncwarp();
       if (lane == 0) barrier_arrive(smem_address(&sh.empty[slot]));
     }
