@@ -140,6 +140,16 @@ int rk_attention_prefill_split_tc(const void *window, uint32_t format, uint32_t 
                                   uint32_t head_dim, const void *queries, float *partials, float *statistics,
                                   const rk_page_entry *table, const rk_prefill_params *params, uint32_t *status,
                                   void *stream);
+/* Test hook of the window kernel's timeout path, no counterpart in the reference: rk_attention_verify_split_tc
+ * (chain masks) whose waits give up after `spin_limit` polls (at most 2^20) and whose TMA warp never streams the
+ * last `withheld_groups` 64-token groups of each split. `status` turns non-zero, tensor memory is released and
+ * the kernel returns; nothing faults and no wait is unbounded. The step's output is invalid by construction. */
+int rk_attention_verify_probe_timeout(const void *window, uint32_t format, uint32_t kv_heads, uint32_t query_heads,
+                                      uint32_t head_dim, uint32_t lanes, uint32_t row_capacity, uint32_t grid_splits,
+                                      const void *queries, float *partials, float *statistics,
+                                      const rk_page_entry *const *tables, const rk_verify_params *lane_params,
+                                      rk_kv_layer layer, uint32_t *status, uint32_t spin_limit,
+                                      uint32_t withheld_groups, void *stream);
 int rk_attention_decode(const void *window, const rk_decode_plan *plan, uint32_t format, const void *queries,
                         void *output, float *output_f32, float *partials, float *statistics,
                         uint32_t *descriptors, const rk_page_entry *const *tables,
@@ -160,12 +170,30 @@ int rk_attention_merge_shards(uint32_t kv_heads, uint32_t query_heads, uint32_t 
  * allocation calls are not permitted where it runs): the step's scratch is a fixed array inside
  * the library, about 12 MiB per GPU that loads it, which limits a call to 16 lanes; more are
  * refused with RK_ERR_INVALID. The first call on a device resolves the array's address and should
- * come before any stream capture. Calls share the array: calls that overlap on the GPU race. */
+ * come before any stream capture. Calls share the array: calls that overlap on the GPU race.
+ * rk_attention_decode_static_status reports a wait that ran out. */
 int rk_attention_decode_static(const void *window, uint32_t format, uint32_t lanes, const void *queries,
                                void *output, float *output_f32, const rk_page_entry *const *tables,
                                const rk_verify_params *lane_params, rk_kv_layer layer, void *stream);
-/* Synchronises `stream` and reports RK_ERR_TIMEOUT if a bounded wait ran out in a launched step. */
-int rk_attention_decode_status(const rk_decode_plan *plan, const uint32_t *descriptors, void *stream);
+/* The decode kernels' status word (the word after the 2 x lanes descriptors; the caller zeroes `descriptors` once,
+ * before its first step) is sticky: a bounded wait that runs out in ANY launch raises it, no launch clears it.
+ * This call synchronises `stream`, reports RK_ERR_TIMEOUT if the word was raised since the last read, and clears
+ * it. A step whose wait ran out wrote zeros for the affected lanes. The reference's analogue is its command
+ * watchdog (runtime/metal/CommandWatchdog.hpp:11-35). */
+int rk_attention_decode_status(const rk_decode_plan *plan, uint32_t *descriptors, void *stream);
+/* The same for rk_attention_decode_static (its status word lives inside the library's own array). */
+int rk_attention_decode_static_status(void *stream);
+/* Test hook of the timeout path, no counterpart in the reference: rk_attention_decode whose waits give up after
+ * `spin_limit` polls (at most 2^20) and whose producers never stream the last `withheld_pages` pages of each
+ * CTA's range. The waiting warps run out of polls, raise the status word, copies in flight land and the kernel
+ * returns; nothing faults and no wait is unbounded. The step's output is invalid by construction. With `partials`,
+ * `statistics` and `descriptors` all null the probe runs on the library's own array, as rk_attention_decode_static
+ * does (plan->lanes <= 16), and rk_attention_decode_static_status reports it. */
+int rk_attention_decode_probe_timeout(const void *window, const rk_decode_plan *plan, uint32_t format,
+                                      const void *queries, void *output, float *partials, float *statistics,
+                                      uint32_t *descriptors, const rk_page_entry *const *tables,
+                                      const rk_verify_params *lane_params, rk_kv_layer layer, uint32_t spin_limit,
+                                      uint32_t withheld_pages, void *stream);
 /* Compact host-style rows <-> the 32-row stagings (row 0): queries [lane][query_head][D],
  * keys / values [lane][kv_head][D]. The reference's QKV projection writes the stagings on the GPU
  * (runtime/metal/kernels/decode/attention_qkv.metal:6-60); these serve callers that hold host rows. */

@@ -36,6 +36,8 @@
 #include <cuda.h>
 #include <cuda_fp16.h>
 
+#include <atomic>
+
 namespace rk {
 
 struct DriverApi;
@@ -68,6 +70,9 @@ struct DecodeArgs {
   rk_kv_layer layer;
   uint64_t window_base;
   uint32_t lanes;
+  uint32_t *status;     // sticky device status word: set when a bounded wait ran out, cleared by the status readers
+  uint32_t spin_limit;  // polls a wait may take (kSpinLimit in production; the timeout probe passes a few thousand)
+  uint32_t withheld;    // timeout probe only: the producer never streams the last `withheld` pages of its range
 };
 
 __device__ __forceinline__ uint32_t smem_address(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -87,8 +92,8 @@ __device__ __forceinline__ bool barrier_try(uint32_t bar, uint32_t parity) {
   return done != 0;
 }
 // Bounded wait: false when the limit ran out (the caller records the error and leaves).
-__device__ __forceinline__ bool barrier_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+__device__ __forceinline__ bool barrier_wait(uint32_t bar, uint32_t parity, uint32_t limit) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (barrier_try(bar, parity)) return true;
     if (i > 32) __nanosleep(32);
   }
@@ -152,7 +157,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 __device__ __forceinline__ uint32_t load_shared_32(uint32_t address) {
   uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(address));
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(address) : "memory");
   return v;
 }
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -163,12 +168,12 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
 }
 __device__ __forceinline__ uint4 load_shared_16(uint32_t address) {
   uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(address));
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(address) : "memory");
   return v;
 }
 __device__ __forceinline__ float load_shared_f32(uint32_t address) {
   float v;
-  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(address));
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(address) : "memory");
   return v;
 }
 
@@ -307,7 +312,8 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
   Shared &sh = *reinterpret_cast<Shared *>(dynamic_shared + (ring - smem_address(dynamic_shared)) + kStages * kStageBytes);
   const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const uint32_t lanes = args.lanes, cta = blockIdx.x;
-  uint32_t *error_word = args.descriptors + 2 * lanes;
+  uint32_t *error_word = args.status;
+  const uint32_t spin_limit = args.spin_limit;
   dependents_may_launch(); // the merge kernel's blocks may take their places; they wait for this grid to finish
   dependency_wait();       // pages, queries and parameters may come from the kernel before this one
 
@@ -341,7 +347,7 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
   if (tid == 0) {
     for (uint32_t s = 0; s < kStages; ++s) {
       barrier_init(smem_address(&sh.full[s]), 1);
-      barrier_init(smem_address(&sh.empty[s]), kKvHeads); // one warp per head releases a page
+      barrier_init(smem_address(&sh.empty[s]), kKvHeads * 32); // every lane of the page's four warps (one per head) releases it
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -363,14 +369,16 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
     if (lane != 0) return;
     uint32_t unit = 0; // pages issued by this CTA
     bool ok = true;
-    for (uint32_t l = first_lane; ok && l < lanes && sh.lane_start[l] < range_end; ++l) {
+    // the timeout probe withholds the last pages of the range: their consumers must give up, not hang
+    const uint32_t issue_limit = (range_end - range_begin) - min(args.withheld, range_end - range_begin);
+    for (uint32_t l = first_lane; ok && unit < issue_limit && l < lanes && sh.lane_start[l] < range_end; ++l) {
       const uint32_t lane_begin = sh.lane_start[l], lane_end = sh.lane_start[l + 1];
       const uint32_t pa = max(range_begin, lane_begin) - lane_begin;
       const uint32_t pb = min(range_end, lane_end) - lane_begin;
       if (pb <= pa || lane_end <= range_begin) continue;
       const rk_page_entry *table = args.tables[l];
       rk_page_entry next_entry = table[pa];
-      for (uint32_t page = pa; ok && page < pb; ++page, ++unit) {
+      for (uint32_t page = pa; ok && unit < issue_limit && page < pb; ++page, ++unit) {
         const rk_page_entry entry = next_entry;
         if (page + 1 < pb) next_entry = table[page + 1]; // in flight while this page's copies are issued
         const uint32_t index = rk_entry_index(entry);
@@ -382,7 +390,7 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
         const uint64_t value_scales = region + pages * (2ull * kTensorBytes + kScaleBytes) + uint64_t(index) * kScaleBytes;
         const uint32_t slot = unit % kStages, round = unit / kStages;
         const uint32_t full = smem_address(&sh.full[slot]), stage = ring + slot * kStageBytes;
-        if (sh.error || !barrier_wait(smem_address(&sh.empty[slot]), (round & 1u) ^ 1u)) { ok = false; break; }
+        if (sh.error || !barrier_wait(smem_address(&sh.empty[slot]), (round & 1u) ^ 1u, spin_limit)) { ok = false; break; }
         barrier_expect(full, kStageBytes);
         tma_load_rows(stage, &window_map, int32_t((keys - args.window_base) >> 7), full);
         tma_load_rows(stage + kTensorBytes, &window_map, int32_t((values - args.window_base) >> 7), full);
@@ -393,12 +401,13 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
     if (!ok) {
       atomicExch(error_word, 1u);
       sh.error = 1;
-      // Copies already issued must land before the block's shared memory goes.
-      const uint32_t armed = min(unit, kStages);
-      for (uint32_t back = 0; back < armed; ++back) {
-        const uint32_t u = unit - 1 - back;
-        barrier_wait(smem_address(&sh.full[u % kStages]), (u / kStages) & 1u);
-      }
+    }
+    // Copies already issued must land before the block's shared memory goes: consumers that gave up no longer wait
+    // for them. The last fill of each stage is the barrier's latest phase, so this returns at once when all went well.
+    const uint32_t armed = min(unit, kStages);
+    for (uint32_t back = 0; back < armed; ++back) {
+      const uint32_t u = unit - 1 - back;
+      barrier_wait(smem_address(&sh.full[u % kStages]), (u / kStages) & 1u, spin_limit);
     }
     return;
   }
@@ -489,7 +498,7 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
     for (uint32_t page = pa + residue; page < pb && !sh.error; page += kPageWarps) {
       const uint32_t unit = units_before + (page - pa);
       const uint32_t slot = unit % kStages, round = unit / kStages;
-      if (!barrier_wait(smem_address(&sh.full[slot]), round & 1u)) {
+      if (!barrier_wait(smem_address(&sh.full[slot]), round & 1u, spin_limit)) {
         atomicExch(error_word, 2u);
         sh.error = 2;
         break;
@@ -519,8 +528,8 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
         for (uint32_t w = 0; w < 4; ++w) {
           const uint32_t s = (j * 4 + w) * 2;
           uint2 q0, q1;
-          asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(q0.x), "=r"(q0.y) : "r"(query_shared + s * 256));
-          asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(q1.x), "=r"(q1.y) : "r"(query_shared + (s + 1) * 256));
+          asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(q0.x), "=r"(q0.y) : "r"(query_shared + s * 256) : "memory");
+          asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(q1.x), "=r"(q1.y) : "r"(query_shared + (s + 1) * 256) : "memory");
 #pragma unroll
           for (uint32_t mt = 0; mt < 2; ++mt) {
             const uint32_t xa = w == 0 ? kr[mt][0].x : w == 1 ? kr[mt][0].y : w == 2 ? kr[mt][0].z : kr[mt][0].w;
@@ -565,11 +574,9 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
                     sub_f16x2(and_xor(cd, kHighNibbles, kMagicHigh), kMagicHigh), pb_frag[s][0], pb_frag[s][1]);
           }
       }
-      // Every lane's reads of the stage are performed before the warp gives it back: the warps that share a scheduler
-      // with the producer release last, and their stage is refilled at once.
-      __threadfence_block();
-      __syncwarp();
-      if (lane == 0) barrier_arrive(smem_address(&sh.empty[slot]));
+      // Every lane gives the stage back itself: its own arrive (a release) follows its own last read of the stage, so
+      // no ordering between lanes is relied on before the producer refills the stage.
+      barrier_arrive(smem_address(&sh.empty[slot]));
     }
     units_before += pb - pa;
 
@@ -645,7 +652,8 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
   Shared &sh = *reinterpret_cast<Shared *>(dynamic_shared + (ring - smem_address(dynamic_shared)) + kByteStages * kByteStageBytes);
   const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const uint32_t lanes = args.lanes, cta = blockIdx.x;
-  uint32_t *error_word = args.descriptors + 2 * lanes;
+  uint32_t *error_word = args.status;
+  const uint32_t spin_limit = args.spin_limit;
   dependents_may_launch(); // the merge kernel's blocks may take their places; they wait for this grid to finish
   dependency_wait();       // pages, queries and parameters may come from the kernel before this one
 
@@ -679,7 +687,7 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
   if (tid == 0) {
     for (uint32_t s = 0; s < kByteStages; ++s) {
       barrier_init(smem_address(&sh.full[s]), 1);
-      barrier_init(smem_address(&sh.empty[s]), kKvHeads); // one warp per head releases a page
+      barrier_init(smem_address(&sh.empty[s]), kKvHeads * 32); // every lane of the page's four warps (one per head) releases it
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -701,14 +709,16 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
     if (lane != 0) return;
     uint32_t unit = 0; // pages issued by this CTA
     bool ok = true;
-    for (uint32_t l = first_lane; ok && l < lanes && sh.lane_start[l] < range_end; ++l) {
+    // the timeout probe withholds the last pages of the range: their consumers must give up, not hang
+    const uint32_t issue_limit = (range_end - range_begin) - min(args.withheld, range_end - range_begin);
+    for (uint32_t l = first_lane; ok && unit < issue_limit && l < lanes && sh.lane_start[l] < range_end; ++l) {
       const uint32_t lane_begin = sh.lane_start[l], lane_end = sh.lane_start[l + 1];
       const uint32_t pa = max(range_begin, lane_begin) - lane_begin;
       const uint32_t pb = min(range_end, lane_end) - lane_begin;
       if (pb <= pa || lane_end <= range_begin) continue;
       const rk_page_entry *table = args.tables[l];
       rk_page_entry next_entry = table[pa];
-      for (uint32_t page = pa; ok && page < pb; ++page, ++unit) {
+      for (uint32_t page = pa; ok && unit < issue_limit && page < pb; ++page, ++unit) {
         const rk_page_entry entry = next_entry;
         if (page + 1 < pb) next_entry = table[page + 1]; // in flight while this page's copies are issued
         const uint32_t index = rk_entry_index(entry);
@@ -720,7 +730,7 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
         const uint64_t value_scales = region + pages * (2ull * kByteTensorBytes + kScaleBytes) + uint64_t(index) * kScaleBytes;
         const uint32_t slot = unit % kByteStages, round = unit / kByteStages;
         const uint32_t full = smem_address(&sh.full[slot]), stage = ring + slot * kByteStageBytes;
-        if (sh.error || !barrier_wait(smem_address(&sh.empty[slot]), (round & 1u) ^ 1u)) { ok = false; break; }
+        if (sh.error || !barrier_wait(smem_address(&sh.empty[slot]), (round & 1u) ^ 1u, spin_limit)) { ok = false; break; }
         barrier_expect(full, kByteStageBytes);
         const int32_t key_row = int32_t((keys - args.window_base) >> 7), value_row = int32_t((values - args.window_base) >> 7);
         tma_load_rows(stage, &window_map, key_row, full);                                   // heads 0-1 (128 rows of 128 bytes)
@@ -734,12 +744,13 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
     if (!ok) {
       atomicExch(error_word, 1u);
       sh.error = 1;
-      // Copies already issued must land before the block's shared memory goes.
-      const uint32_t armed = min(unit, kByteStages);
-      for (uint32_t back = 0; back < armed; ++back) {
-        const uint32_t u = unit - 1 - back;
-        barrier_wait(smem_address(&sh.full[u % kByteStages]), (u / kByteStages) & 1u);
-      }
+    }
+    // Copies already issued must land before the block's shared memory goes: consumers that gave up no longer wait
+    // for them. The last fill of each stage is the barrier's latest phase, so this returns at once when all went well.
+    const uint32_t armed = min(unit, kByteStages);
+    for (uint32_t back = 0; back < armed; ++back) {
+      const uint32_t u = unit - 1 - back;
+      barrier_wait(smem_address(&sh.full[u % kByteStages]), (u / kByteStages) & 1u, spin_limit);
     }
     return;
   }
@@ -832,7 +843,7 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
     for (uint32_t page = pa + residue; page < pb && !sh.error; page += kPageWarps) {
       const uint32_t unit = units_before + (page - pa);
       const uint32_t slot = unit % kByteStages, round = unit / kByteStages;
-      if (!barrier_wait(smem_address(&sh.full[slot]), round & 1u)) {
+      if (!barrier_wait(smem_address(&sh.full[slot]), round & 1u, spin_limit)) {
         atomicExch(error_word, 2u);
         sh.error = 2;
         break;
@@ -863,7 +874,7 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
         for (uint32_t w = 0; w < 4; ++w) {
           const uint32_t s = j * 4 + w;
           uint2 q;
-          asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(q.x), "=r"(q.y) : "r"(query_shared + s * 256));
+          asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(q.x), "=r"(q.y) : "r"(query_shared + s * 256) : "memory");
 #pragma unroll
           for (uint32_t mt = 0; mt < 2; ++mt) {
             const uint32_t xa = w == 0 ? kr[mt][0].x : w == 1 ? kr[mt][0].y : w == 2 ? kr[mt][0].z : kr[mt][0].w;
@@ -905,11 +916,9 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
           mma_f16(o[t], a0, a1, a2, a3, pb_frag[s][0], pb_frag[s][1]);
         }
       }
-      // Every lane's reads of the stage are performed before the warp gives it back: the warps that share a scheduler
-      // with the producer release last, and their stage is refilled at once.
-      __threadfence_block();
-      __syncwarp();
-      if (lane == 0) barrier_arrive(smem_address(&sh.empty[slot]));
+      // Every lane gives the stage back itself: its own arrive (a release) follows its own last read of the stage, so
+      // no ordering between lanes is relied on before the producer refills the stage.
+      barrier_arrive(smem_address(&sh.empty[slot]));
     }
     units_before += pb - pa;
 
@@ -961,7 +970,8 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
   Shared &sh = *reinterpret_cast<Shared *>(dynamic_shared + (ring - smem_address(dynamic_shared)) + kWideStages * kWideStageBytes);
   const uint32_t tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const uint32_t lanes = args.lanes, cta = blockIdx.x;
-  uint32_t *error_word = args.descriptors + 2 * lanes;
+  uint32_t *error_word = args.status;
+  const uint32_t spin_limit = args.spin_limit;
   dependents_may_launch(); // the merge kernel's blocks may take their places; they wait for this grid to finish
   dependency_wait();       // pages, queries and parameters may come from the kernel before this one
 
@@ -997,7 +1007,7 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
     // A unit is one head's slabs of one page and has one consumer warp. Each warp waits on its own "full" barrier,
     // so it sees every completion of the barrier it waits on (a parity wait cannot tell completions two apart);
     // the stages themselves are released through per-stage "empty" barriers that only the producer waits on.
-    for (uint32_t s = 0; s < kWideStages; ++s) barrier_init(smem_address(&sh.empty[s]), 1);
+    for (uint32_t s = 0; s < kWideStages; ++s) barrier_init(smem_address(&sh.empty[s]), 32); // every lane of the unit's warp
     for (uint32_t w = 0; w < kConsumerWarps; ++w) barrier_init(smem_address(&sh.warp_full[w]), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -1019,14 +1029,16 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
     if (lane != 0) return;
     uint32_t unit = 0, ordinal = 0; // units issued by this CTA; pages of this CTA before the current one
     bool ok = true;
-    for (uint32_t l = first_lane; ok && l < lanes && sh.lane_start[l] < range_end; ++l) {
+    // the timeout probe withholds the last pages of the range: their consumers must give up, not hang
+    const uint32_t issue_limit = (range_end - range_begin) - min(args.withheld, range_end - range_begin);
+    for (uint32_t l = first_lane; ok && ordinal < issue_limit && l < lanes && sh.lane_start[l] < range_end; ++l) {
       const uint32_t lane_begin = sh.lane_start[l], lane_end = sh.lane_start[l + 1];
       const uint32_t pa = max(range_begin, lane_begin) - lane_begin;
       const uint32_t pb = min(range_end, lane_end) - lane_begin;
       if (pb <= pa || lane_end <= range_begin) continue;
       const rk_page_entry *table = args.tables[l];
       rk_page_entry next_entry = table[pa];
-      for (uint32_t page = pa; ok && page < pb; ++page, ++ordinal) {
+      for (uint32_t page = pa; ok && ordinal < issue_limit && page < pb; ++page, ++ordinal) {
         const rk_page_entry entry = next_entry;
         if (page + 1 < pb) next_entry = table[page + 1]; // in flight while this page's copies are issued
         const uint32_t index = rk_entry_index(entry);
@@ -1039,7 +1051,7 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
           // order and the ring holds 6, so a warp's barrier never has two fills in flight
           const uint32_t slot = unit % kWideStages, round = unit / kWideStages;
           const uint32_t full = smem_address(&sh.warp_full[head + kKvHeads * (ordinal % kPageWarps)]), stage = ring + slot * kWideStageBytes;
-          if (sh.error || !barrier_wait(smem_address(&sh.empty[slot]), (round & 1u) ^ 1u)) { ok = false; break; }
+          if (sh.error || !barrier_wait(smem_address(&sh.empty[slot]), (round & 1u) ^ 1u, spin_limit)) { ok = false; break; }
           barrier_expect(full, kWideStageBytes);
           tma_load_rows(stage, &window_map, key_row + int32_t(head * (kWideSlabBytes / 128)), full); // 128 rows of 128 bytes
           tma_load_rows(stage + kWideSlabBytes, &window_map, value_row + int32_t(head * (kWideSlabBytes / 128)), full);
@@ -1049,12 +1061,13 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
     if (!ok) {
       atomicExch(error_word, 1u);
       sh.error = 1;
-      // Copies already issued must land before the block's shared memory goes.
-      const uint32_t armed = min(unit, kWideStages);
-      for (uint32_t back = 0; back < armed; ++back) {
-        const uint32_t u = unit - 1 - back, n = u / kKvHeads;
-        barrier_wait(smem_address(&sh.warp_full[u % kKvHeads + kKvHeads * (n % kPageWarps)]), (n / kPageWarps) & 1u);
-      }
+    }
+    // Copies already issued must land before the block's shared memory goes: consumers that gave up no longer wait
+    // for them. The last six units are the latest fills of six different warp barriers.
+    const uint32_t armed = min(unit, kWideStages);
+    for (uint32_t back = 0; back < armed; ++back) {
+      const uint32_t u = unit - 1 - back, n = u / kKvHeads;
+      barrier_wait(smem_address(&sh.warp_full[u % kKvHeads + kKvHeads * (n % kPageWarps)]), (n / kPageWarps) & 1u, spin_limit);
     }
     return;
   }
@@ -1114,7 +1127,7 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
     for (uint32_t page = pa + (residue + kPageWarps - units_before % kPageWarps) % kPageWarps; page < pb && !sh.error; page += kPageWarps) {
       const uint32_t ordinal = units_before + (page - pa);
       const uint32_t slot = (ordinal * kKvHeads + head) % kWideStages;
-      if (!barrier_wait(smem_address(&sh.warp_full[warp]), (ordinal / kPageWarps) & 1u)) {
+      if (!barrier_wait(smem_address(&sh.warp_full[warp]), (ordinal / kPageWarps) & 1u, spin_limit)) {
         atomicExch(error_word, 2u);
         sh.error = 2;
         break;
@@ -1142,7 +1155,7 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
 #pragma unroll
         for (uint32_t w = 0; w < 2; ++w) {
           uint2 q;
-          asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(q.x), "=r"(q.y) : "r"(query_shared + (2 * j + w) * 256));
+          asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(q.x), "=r"(q.y) : "r"(query_shared + (2 * j + w) * 256) : "memory");
 #pragma unroll
           for (uint32_t mt = 0; mt < 2; ++mt)
             mma_bf16(sacc[mt][w], w ? kr[mt][0].z : kr[mt][0].x, w ? kr[mt][1].z : kr[mt][1].x,
@@ -1181,11 +1194,9 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
           mma_bf16(o[t], a0, a1, a2, a3, pb_low[s][0], pb_low[s][1]);
         }
       }
-      // Every lane's reads of the stage are performed before the warp gives it back: the warps that share a scheduler
-      // with the producer release last, and their stage is refilled at once.
-      __threadfence_block();
-      __syncwarp();
-      if (lane == 0) barrier_arrive(smem_address(&sh.empty[slot]));
+      // Every lane gives the stage back itself: its own arrive (a release) follows its own last read of the stage, so
+      // no ordering between lanes is relied on before the producer refills the stage.
+      barrier_arrive(smem_address(&sh.empty[slot]));
     }
     units_before += pb - pa;
 
@@ -1315,16 +1326,16 @@ static_assert(kWideDecodeSharedBytes <= 227 * 1024, "the bf16 ring fits one SM")
 
 // The kernel's dynamic shared-memory limit is a per-device function attribute.
 int configure_decode_kernel() {
-  static bool configured[64] = {};
+  static std::atomic<bool> configured[64] = {}; // setting the attribute twice is harmless: two threads may race here
   int device = 0;
   if (int st = cuda_status(cudaGetDevice(&device), "cudaGetDevice")) return st;
   if (device < 0 || device >= 64) { set_error("device index out of range"); return kInvalid; }
-  if (!configured[device]) {
+  if (!configured[device].load(std::memory_order_acquire)) {
     if (int st = cuda_status(cudaFuncSetAttribute(decode_int4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kDecodeSharedBytes)), "decode shared memory")) return st;
     if (int st = cuda_status(cudaFuncSetAttribute(decode_bytes_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kByteDecodeSharedBytes)), "decode shared memory")) return st;
     if (int st = cuda_status(cudaFuncSetAttribute(decode_bytes_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kByteDecodeSharedBytes)), "decode shared memory")) return st;
     if (int st = cuda_status(cudaFuncSetAttribute(decode_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kWideDecodeSharedBytes)), "decode shared memory")) return st;
-    configured[device] = true;
+    configured[device].store(true, std::memory_order_release);
   }
   return kOk;
 }
@@ -1421,8 +1432,8 @@ int rk_attention_decode(const void *window, const rk_decode_plan *plan, uint32_t
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (int st = configure_decode_kernel()) return st;
-  DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, plan->lanes};
-  if (int st = cuda_status(cudaMemsetAsync(descriptors + 2 * plan->lanes, 0, sizeof(uint32_t), s), "decode status clear")) return st;
+  DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, plan->lanes,
+                  descriptors + 2 * plan->lanes, kSpinLimit, 0};
   if (int st = launch_decode(format, plan->ctas, s, w, args)) return st;
   return launch_merge(plan->lanes, s, partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer, nullptr);
 }
@@ -1442,8 +1453,8 @@ int rk_attention_decode_shard(const void *window, const rk_decode_plan *plan, ui
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (int st = configure_decode_kernel()) return st;
-  DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, plan->lanes};
-  if (int st = cuda_status(cudaMemsetAsync(descriptors + 2 * plan->lanes, 0, sizeof(uint32_t), s), "decode status clear")) return st;
+  DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, plan->lanes,
+                  descriptors + 2 * plan->lanes, kSpinLimit, 0};
   if (int st = launch_decode(format, plan->ctas, s, w, args)) return st;
   decode_reduce_kernel<<<dim3(kGroup, kKvHeads, plan->lanes), 256, 0, s>>>(partials, statistics, descriptors, nullptr, nullptr, lane_params, layer, triples);
   return cuda_status(cudaGetLastError(), "decode shard reduce launch");
@@ -1470,6 +1481,29 @@ constexpr size_t kStaticStatisticBytes = (kStaticSlots * kGroup * 2 * sizeof(flo
 constexpr size_t kStaticDescriptorBytes = ((2 * kStaticLanes + 4) * sizeof(uint32_t) + 255) / 256 * 256;
 static __device__ __align__(256) unsigned char g_decode_scratch[kStaticPartialBytes + kStaticStatisticBytes + kStaticDescriptorBytes];
 
+// The device address of g_decode_scratch on the current device. In host code the array's name is only a handle
+// for the runtime, never an address a kernel may use: the address comes from cudaGetSymbolAddress, once per device,
+// with that device current. Two host threads may both do the first lookup; both get the same address.
+static int static_scratch(unsigned char **base) {
+  static std::atomic<unsigned char *> scratch_address[64] = {};
+  int device = 0;
+  if (int st = cuda_status(cudaGetDevice(&device), "cudaGetDevice")) return st;
+  if (device < 0 || device >= 64) { set_error("device index out of range"); return kInvalid; }
+  unsigned char *known = scratch_address[device].load(std::memory_order_acquire);
+  if (!known) {
+    void *address = nullptr;
+    if (int st = cuda_status(cudaGetSymbolAddress(&address, g_decode_scratch), "cudaGetSymbolAddress(decode scratch)")) return st;
+    if (int st = configure_decode_kernel()) return st;
+    known = static_cast<unsigned char *>(address);
+    scratch_address[device].store(known, std::memory_order_release);
+  }
+  *base = known;
+  return kOk;
+}
+static uint32_t *static_descriptors(unsigned char *base) {
+  return reinterpret_cast<uint32_t *>(base + kStaticPartialBytes + kStaticStatisticBytes);
+}
+
 // rk_attention_decode for callers that must not allocate device memory: an engine that gave the
 // whole device to its KV pool and has no allocator left to ask, a serving thread that may not
 // enter cudaMalloc because it can stall on a device-wide lock, a caller inside a region where
@@ -1480,9 +1514,10 @@ static __device__ __align__(256) unsigned char g_decode_scratch[kStaticPartialBy
 // The first call on a device looks the array's device address up (cudaGetSymbolAddress, with that
 // device current) and sets the kernel's shared-memory attribute; make that first call before any
 // stream capture begins. No call allocates or frees anything, on the device or through a library.
-// Every call on a device uses the same array: the status word is cleared on the stream at the
-// start of each call, every partial the merge reads is rewritten by the same call, and two calls
-// that overlap on the GPU (different streams, no ordering between them) race on it.
+// Every call on a device uses the same array: every partial the merge reads is rewritten by the
+// same call, the status word (fixed place, after the descriptors of 16 lanes) is sticky until
+// rk_attention_decode_static_status reads it, and two calls that overlap on the GPU (different
+// streams, no ordering between them) race on the array.
 int rk_attention_decode_static(const void *window, uint32_t format, uint32_t lanes, const void *queries, void *output,
                                float *output_f32, const rk_page_entry *const *tables,
                                const rk_verify_params *lane_params, rk_kv_layer layer, void *stream) {
@@ -1496,36 +1531,78 @@ int rk_attention_decode_static(const void *window, uint32_t format, uint32_t lan
     set_error("rk_attention_decode_static: at most 16 lanes fit the built-in scratch; use rk_attention_decode with caller scratch");
     return kInvalid;
   }
-  static unsigned char *scratch_address[64] = {};
-  int device = 0;
-  if (int st = cuda_status(cudaGetDevice(&device), "cudaGetDevice")) return st;
-  if (device < 0 || device >= 64) { set_error("device index out of range"); return kInvalid; }
-  if (!scratch_address[device]) { // once per device, with that device current
-    void *address = nullptr;
-    if (int st = cuda_status(cudaGetSymbolAddress(&address, g_decode_scratch), "cudaGetSymbolAddress(decode scratch)")) return st;
-    if (int st = configure_decode_kernel()) return st;
-    scratch_address[device] = static_cast<unsigned char *>(address);
-  }
-  unsigned char *base = scratch_address[device];
+  unsigned char *base = nullptr;
+  if (int st = static_scratch(&base)) return st;
   float *partials = reinterpret_cast<float *>(base);
   float *statistics = reinterpret_cast<float *>(base + kStaticPartialBytes);
-  uint32_t *descriptors = reinterpret_cast<uint32_t *>(base + kStaticPartialBytes + kStaticStatisticBytes);
+  uint32_t *descriptors = static_descriptors(base);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, lanes};
-  if (int st = cuda_status(cudaMemsetAsync(descriptors + 2 * lanes, 0, sizeof(uint32_t), s), "decode status clear")) return st;
+  DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, lanes,
+                  descriptors + 2 * kStaticLanes, kSpinLimit, 0};
   if (int st = launch_decode(format, kStaticCtas, s, w, args)) return st;
   decode_reduce_kernel<<<dim3(kGroup, kKvHeads, lanes), 256, 0, s>>>(partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer, nullptr);
   return cuda_status(cudaGetLastError(), "decode reduce launch");
 }
 
-// Reads the step's device status word (synchronises the stream): 0, or kTimeout
-// when a bounded wait inside the kernel ran out.
-int rk_attention_decode_status(const rk_decode_plan *plan, const uint32_t *descriptors, void *stream) {
+// Reads AND clears a sticky status word on `stream` (synchronises it): kTimeout when a bounded wait inside a decode
+// kernel ran out in any step launched since the last read.
+static int read_status_word(uint32_t *word_address, cudaStream_t s) {
   uint32_t word = 0;
-  if (int st = cuda_status(cudaMemcpyAsync(&word, descriptors + 2 * plan->lanes, sizeof(word), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)), "decode status read")) return st;
-  if (int st = cuda_status(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)), "decode status sync")) return st;
-  if (word) { set_error("a bounded wait in the decode kernel ran out"); return kTimeout; }
-  return kOk;
+  if (int st = cuda_status(cudaMemcpyAsync(&word, word_address, sizeof(word), cudaMemcpyDeviceToHost, s), "decode status read")) return st;
+  if (int st = cuda_status(cudaStreamSynchronize(s), "decode status sync")) return st;
+  if (!word) return kOk;
+  if (int st = cuda_status(cudaMemsetAsync(word_address, 0, sizeof(word), s), "decode status clear")) return st;
+  if (int st = cuda_status(cudaStreamSynchronize(s), "decode status sync")) return st;
+  set_error(word == 1 ? "a bounded wait in the decode kernel ran out (the producer waiting for a free stage)"
+                      : "a bounded wait in the decode kernel ran out (a consumer waiting for a page)");
+  return kTimeout;
+}
+
+int rk_attention_decode_status(const rk_decode_plan *plan, uint32_t *descriptors, void *stream) {
+  if (!plan || !descriptors) { set_error("rk_attention_decode_status: invalid arguments"); return kInvalid; }
+  return read_status_word(descriptors + 2 * plan->lanes, static_cast<cudaStream_t>(stream));
+}
+
+// The same for rk_attention_decode_static, whose status word lives in the library's own array.
+int rk_attention_decode_static_status(void *stream) {
+  unsigned char *base = nullptr;
+  if (int st = static_scratch(&base)) return st;
+  return read_status_word(static_descriptors(base) + 2 * kStaticLanes, static_cast<cudaStream_t>(stream));
+}
+
+// Test hook of the timeout path: rk_attention_decode whose waits give up after `spin_limit` polls and whose
+// producers never stream the last `withheld_pages` pages of their CTA's range. The consumers of those pages run
+// out of polls, the kernel raises its status word, lets copies in flight land and returns; nothing faults and
+// nothing waits without a bound. The step's output is invalid by construction.
+int rk_attention_decode_probe_timeout(const void *window, const rk_decode_plan *plan, uint32_t format, const void *queries,
+                                      void *output, float *partials, float *statistics, uint32_t *descriptors,
+                                      const rk_page_entry *const *tables, const rk_verify_params *lane_params,
+                                      rk_kv_layer layer, uint32_t spin_limit, uint32_t withheld_pages, void *stream) {
+  const auto *w = static_cast<const Window *>(window);
+  const bool own_scratch = !partials && !statistics && !descriptors; // probe the no-allocation entry's path
+  if (!w || !plan || !queries || !output || (!own_scratch && (!partials || !statistics || !descriptors)) || !tables || !lane_params ||
+      !layer.extent_pages || format < RK_FORMAT_INT8 || format > RK_FORMAT_FP8E4M3 || !spin_limit || spin_limit > kSpinLimit ||
+      (own_scratch && plan->lanes > kStaticLanes)) {
+    set_error("rk_attention_decode_probe_timeout: invalid arguments");
+    return kInvalid;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (int st = configure_decode_kernel()) return st;
+  uint32_t *status = own_scratch ? nullptr : descriptors + 2 * plan->lanes;
+  uint32_t ctas = plan->ctas;
+  if (own_scratch) {
+    unsigned char *base = nullptr;
+    if (int st = static_scratch(&base)) return st;
+    partials = reinterpret_cast<float *>(base);
+    statistics = reinterpret_cast<float *>(base + kStaticPartialBytes);
+    descriptors = static_descriptors(base);
+    status = descriptors + 2 * kStaticLanes;
+    ctas = min(ctas, kStaticCtas);
+  }
+  DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, plan->lanes,
+                  status, spin_limit, withheld_pages};
+  if (int st = launch_decode(format, ctas, s, w, args)) return st;
+  return launch_merge(plan->lanes, s, partials, statistics, descriptors, static_cast<uint16_t *>(output), nullptr, lane_params, layer, nullptr);
 }
 
 } // extern "C"

@@ -109,6 +109,7 @@ struct Control {
   uint64_t k_full[2], k_free[2], v_full[2], v_free[2], s_full[2], p_full[2], p_free[2], scale_free[kScaleStages];
   uint32_t tmem_base;
   uint32_t error;
+  uint32_t spin_limit; // directly after `error`: barrier_wait reads it through the error pointer
   float q_sums[kM];
   float exchange[2][kM][kRowThreads]; // the part-row maxima of a group (and, at the end, the part-row sums)
   float4 scales[kScaleStages][kGroupTokens]; // {key scale, log2 value scale, 2^-6 / value scale, -}
@@ -130,11 +131,12 @@ __device__ __forceinline__ bool barrier_try(uint32_t bar, uint32_t parity) {
                : "=r"(done) : "r"(bar), "r"(parity) : "memory");
   return done != 0;
 }
-// Waits for completion number `count` (0-based) of a barrier. Bounded: gives up after kSpinLimit polls,
+// Waits for completion number `count` (0-based) of a barrier. Bounded: gives up after the launch's poll limit,
 // or at once when another wait of this CTA already gave up; either way `error` ends non-zero.
+// `error` points at Control::error; the word after it holds the poll limit of this launch.
 __device__ __forceinline__ void barrier_wait(uint64_t *barrier, uint32_t count, volatile uint32_t *error) {
-  const uint32_t bar = smem_u32(barrier), parity = count & 1u;
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+  const uint32_t bar = smem_u32(barrier), parity = count & 1u, limit = error[1];
+  for (uint32_t i = 0; i < limit; ++i) {
     if (barrier_try(bar, parity)) return; // try_wait itself suspends the thread for a while
     if ((i & 63u) == 63u) {
       if (*error) return;
@@ -268,6 +270,8 @@ struct VerifyArgs {
   rk_kv_layer layer;
   uint64_t window_base;
   uint32_t *status; // one word: non-zero when a bounded wait ran out
+  uint32_t spin_limit;      // polls a wait may take (kSpinLimit in production; the timeout probe passes a few thousand)
+  uint32_t withheld_groups; // timeout probe only: the TMA warp never streams the last groups of a split
   // prefill launches (grid z = 8-row tile of the chunk): the sequence's table and parameters instead of per-lane ones
   const rk_page_entry *prefill_table;
   rk_prefill_params prefill;
@@ -511,6 +515,7 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
     for (uint32_t b = 0; b < kScaleStages; ++b) barrier_init(smem_u32(&ctl.scale_free[b]), kActiveSoftmax);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     ctl.error = 0;
+    ctl.spin_limit = args.spin_limit;
   }
   if (warp == kTmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl.tmem_base)), "r"(512u) : "memory");
@@ -595,7 +600,8 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
     // table entries travel one group ahead of their use (copies) and of their L2 request (prefetch)
     rk_page_entry next = lane < 8 && page_begin + local < page_end ? table[page_begin + local] : 0;
     rk_page_entry next_ahead = prefetcher && page_begin + 2 * kPrefetchGroups + local < page_end ? table[page_begin + 2 * kPrefetchGroups + local] : 0;
-    for (uint32_t g = 0; g < groups; ++g) {
+    const uint32_t issued = groups - min(groups, args.withheld_groups); // all of them, except under the timeout probe
+    for (uint32_t g = 0; g < issued; ++g) {
       const uint32_t r = g % kRawStages;
       const uint32_t first = page_begin + 2 * g, group_pages = min(2u, page_end - first);
       const rk_page_entry entry = next, entry_ahead = next_ahead;
@@ -617,7 +623,7 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
     }
     // Every copy this warp started has landed before the CTA may leave (also after a failed wait).
     if (lane == 0)
-      for (uint32_t g = groups > kRawStages ? groups - kRawStages : 0; g < groups; ++g) {
+      for (uint32_t g = issued > kRawStages ? issued - kRawStages : 0; g < issued; ++g) {
         const uint32_t bar = smem_u32(&ctl.raw_full[g % kRawStages]), parity = (g / kRawStages) & 1u;
         for (uint32_t i = 0; i < kSpinLimit && !barrier_try(bar, parity); ++i) __nanosleep(64);
       }
@@ -880,12 +886,12 @@ int launch_window(const Window *w, uint32_t lanes, uint32_t row_capacity, uint32
 }
 } // namespace
 
-extern "C" int rk_attention_verify_split_tc(const void *window, uint32_t format, uint32_t kv_heads, uint32_t query_heads,
-                                            uint32_t head_dim, uint32_t lanes, uint32_t row_capacity, uint32_t grid_splits,
-                                            const void *queries, float *partials, float *statistics,
-                                            const rk_page_entry *const *tables, const uint32_t *row_masks,
-                                            const rk_verify_params *lane_params, rk_kv_layer layer, uint32_t *status,
-                                            void *stream) {
+static int verify_split_tc(const void *window, uint32_t format, uint32_t kv_heads, uint32_t query_heads,
+                           uint32_t head_dim, uint32_t lanes, uint32_t row_capacity, uint32_t grid_splits,
+                           const void *queries, float *partials, float *statistics,
+                           const rk_page_entry *const *tables, const uint32_t *row_masks,
+                           const rk_verify_params *lane_params, rk_kv_layer layer, uint32_t *status,
+                           uint32_t spin_limit, uint32_t withheld_groups, void *stream) {
   if (kv_heads != kHeads || query_heads != kHeads * kG || head_dim != kD || !rk_format_valid(format) ||
       (row_capacity != 1 && row_capacity != 8 && row_capacity != 16) || (row_capacity == 1 && row_masks) ||
       (format == RK_FORMAT_FP8E4M3 && row_masks)) {
@@ -898,7 +904,8 @@ extern "C" int rk_attention_verify_split_tc(const void *window, uint32_t format,
     set_error("rk_attention_verify_split_tc: invalid arguments");
     return kInvalid;
   }
-  VerifyArgs args{static_cast<const uint16_t *>(queries), partials, statistics, tables, row_masks, lane_params, layer, w->base, status, nullptr, {}};
+  VerifyArgs args{static_cast<const uint16_t *>(queries), partials, statistics, tables, row_masks, lane_params, layer, w->base, status,
+                  spin_limit, withheld_groups, nullptr, {}};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int st = kUnsupported;
   switch (format) {
@@ -909,6 +916,31 @@ extern "C" int rk_attention_verify_split_tc(const void *window, uint32_t format,
   }
   if (st) return st;
   return cuda_status(cudaGetLastError(), "window kernel launch");
+}
+
+extern "C" int rk_attention_verify_split_tc(const void *window, uint32_t format, uint32_t kv_heads, uint32_t query_heads,
+                                            uint32_t head_dim, uint32_t lanes, uint32_t row_capacity, uint32_t grid_splits,
+                                            const void *queries, float *partials, float *statistics,
+                                            const rk_page_entry *const *tables, const uint32_t *row_masks,
+                                            const rk_verify_params *lane_params, rk_kv_layer layer, uint32_t *status,
+                                            void *stream) {
+  return verify_split_tc(window, format, kv_heads, query_heads, head_dim, lanes, row_capacity, grid_splits, queries, partials,
+                         statistics, tables, row_masks, lane_params, layer, status, kSpinLimit, 0, stream);
+}
+
+// Test hook of the window kernel's timeout path: the same launch with waits that give up after `spin_limit` polls
+// and a TMA warp that never streams the last `withheld_groups` 64-token groups of each split. The waiting warps run
+// out of polls, every other wait of the CTA then gives up at once, tensor memory is released, `status` turns
+// non-zero and the kernel returns; nothing faults and no wait is unbounded. The step's output is invalid.
+extern "C" int rk_attention_verify_probe_timeout(const void *window, uint32_t format, uint32_t kv_heads, uint32_t query_heads,
+                                                 uint32_t head_dim, uint32_t lanes, uint32_t row_capacity, uint32_t grid_splits,
+                                                 const void *queries, float *partials, float *statistics,
+                                                 const rk_page_entry *const *tables, const rk_verify_params *lane_params,
+                                                 rk_kv_layer layer, uint32_t *status, uint32_t spin_limit,
+                                                 uint32_t withheld_groups, void *stream) {
+  if (!spin_limit || spin_limit > kSpinLimit) { set_error("rk_attention_verify_probe_timeout: spin limit out of range"); return kInvalid; }
+  return verify_split_tc(window, format, kv_heads, query_heads, head_dim, lanes, row_capacity, grid_splits, queries, partials,
+                         statistics, tables, nullptr, lane_params, layer, status, spin_limit, withheld_groups, stream);
 }
 
 // prefill_attention_*_split (prefill/paged_attention.metal:7-67) on the tcgen05 kernel: one CTA per (KV head, split,
@@ -927,7 +959,8 @@ extern "C" int rk_attention_prefill_split_tc(const void *window, uint32_t format
     set_error("rk_attention_prefill_split_tc: invalid arguments");
     return kInvalid;
   }
-  VerifyArgs args{static_cast<const uint16_t *>(queries), partials, statistics, nullptr, nullptr, nullptr, params->kv, w->base, status, table, *params};
+  VerifyArgs args{static_cast<const uint16_t *>(queries), partials, statistics, nullptr, nullptr, nullptr, params->kv, w->base, status,
+                  kSpinLimit, 0, table, *params};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const uint32_t tiles = (params->rows + RK_PREFILL_TILE_ROWS - 1) / RK_PREFILL_TILE_ROWS;
   const bool pairs = params->split_count == 1 && tiles > 1; // two tiles per CTA fill 96 of the 128 tensor-core rows

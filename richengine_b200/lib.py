@@ -60,6 +60,7 @@ SIGNATURES = {
     "rk_store_chunk": (i32, [u32, u32, u32, vp, vp, vp, C.POINTER(ChunkParams), vp]),
     "rk_attention_verify_split": (i32, [u32, u32, u32, u32, u32, u32, u32, vp, vp, vp, vp, vp, vp, KvLayer, vp]),
     "rk_attention_verify_split_tc": (i32, [vp, u32, u32, u32, u32, u32, u32, u32, vp, vp, vp, vp, vp, vp, KvLayer, vp, vp]),
+    "rk_attention_verify_probe_timeout": (i32, [vp, u32, u32, u32, u32, u32, u32, u32, vp, vp, vp, vp, vp, KvLayer, vp, u32, u32, vp]),
     "rk_attention_verify_reduce": (i32, [u32, u32, u32, u32, u32, vp, vp, vp, vp, vp, vp]),
     "rk_qkv_prepare": (i32, [u32, u32, u32, u32, u32, vp, vp, vp, i32, vp, vp, C.c_float, vp, vp, vp, vp]),
     "rk_qkv_prepare_store": (i32, [u32, u32, u32, u32, u32, u32, vp, vp, vp, i32, vp, vp, C.c_float, vp, vp, vp, KvLayer, vp]),
@@ -82,6 +83,8 @@ SIGNATURES = {
     "rk_attention_merge_shards": (i32, [u32, u32, u32, u32, u32, vp, vp, vp, vp]),
     "rk_attention_decode_static": (i32, [vp, u32, u32, vp, vp, vp, vp, vp, KvLayer, vp]),
     "rk_attention_decode_status": (i32, [C.POINTER(DecodePlan), vp, vp]),
+    "rk_attention_decode_static_status": (i32, [vp]),
+    "rk_attention_decode_probe_timeout": (i32, [vp, C.POINTER(DecodePlan), u32, vp, vp, vp, vp, vp, vp, vp, KvLayer, u32, u32, vp]),
     "rk_stage_decode_rows": (i32, [u32, u32, u32, u32, vp, vp, vp, vp, vp, vp, vp]),
     "rk_gather_decode_rows": (i32, [u32, u32, u32, u32, vp, vp, vp]),
     # storage

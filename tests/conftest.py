@@ -31,9 +31,19 @@ def pytest_collection_modifyitems(config, items):
 
 @pytest.fixture(scope="session", autouse=True)
 def built_artifacts():
-    """The oracle (always rebuilt by make when stale) and the CUDA library (built only when missing)."""
+    """The oracle (rebuilt by make when stale) and the CUDA library (rebuilt when a source or header is newer than
+    its object, so the tests never run against a stale binary)."""
     subprocess.run(["make", "-C", str(ROOT / "oracle"), "-s"], check=True)
-    from richengine_b200 import build, lib
-    if not lib.LIBRARY_PATH.exists():
-        build.build()
+    from richengine_b200 import build
+    build.build()
     yield
+
+
+def pytest_report_header(config):
+    from richengine_b200 import lib
+    path = lib.LIBRARY_PATH
+    if not path.exists():
+        return f"librichkv: {path} (not built yet)"
+    import datetime
+    stamp = datetime.datetime.fromtimestamp(path.stat().st_mtime).isoformat(timespec="seconds")
+    return f"librichkv: {path} built {stamp}, {path.stat().st_size} bytes"
