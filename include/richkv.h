@@ -165,6 +165,23 @@ int rk_attention_decode_shard(const void *window, const rk_decode_plan *plan, ui
 int rk_attention_merge_shards(uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim, uint32_t lanes,
                               uint32_t shards, const float *triples, void *output, float *output_f32,
                               void *stream);
+/* The same step with the combine inside the library's own kernels instead of a collective library: after the
+ * streaming kernel one fused kernel reduces this rank's partials, writes its triple into every rank's exchange
+ * buffer with plain peer stores (NVLink), publishes it with system-scope releases, waits (bounded) for every
+ * rank's triple in its own buffer and merges them in rank order; `output` ends identical on all ranks.
+ * rk_exchange_create allocates this rank's buffer and returns its 64-byte CUDA IPC handle; the caller gathers all
+ * ranks' handles (ranks x 64 bytes, in rank order) and passes them to rk_exchange_connect. Every rank calls
+ * rk_attention_decode_exchange once per step, in the same order; loopback_rank is -1 (a value >= 0 emulates that
+ * rank of a step on ONE GPU over an unconnected exchange: all but the last rank only publish). A wait for a peer
+ * that runs out raises the decode status word. The epoch is a launch argument: not for replay from a graph. */
+void *rk_exchange_create(uint32_t rank, uint32_t ranks, uint32_t lanes, void *handle_out);
+int rk_exchange_connect(void *exchange, const void *handles);
+void rk_exchange_destroy(void *exchange);
+int rk_attention_decode_exchange(const void *window, const rk_decode_plan *plan, uint32_t format, const void *queries,
+                                 void *output, float *output_f32, float *partials, float *statistics,
+                                 uint32_t *descriptors, const rk_page_entry *const *tables,
+                                 const rk_verify_params *lane_params, rk_kv_layer layer, void *exchange,
+                                 int32_t loopback_rank, void *stream);
 /* No counterpart in the reference. rk_attention_decode for callers that cannot allocate device
  * memory (the pool owns the whole device, the calling thread may not enter the allocator, or
  * allocation calls are not permitted where it runs): the step's scratch is a fixed array inside

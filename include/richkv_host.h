@@ -115,6 +115,47 @@ int rk_plan_prefill(uint32_t rows, uint32_t query_heads, uint32_t layers, uint32
 /* out[4] = verify partials, verify statistics, prefill partials, prefill statistics */
 int rk_plan_workspaces(uint32_t lanes, uint32_t max_rows, uint32_t query_heads, uint32_t layers, uint32_t kv_heads,
                        uint32_t head_dim, uint32_t format, uint64_t *out);
+/* ---- the operator's encoders -------------------------------------------------------------------------
+ * ops::PagedAttention::addPrefillStore / addPrefill / addVerify / addVerifyTreeCompact
+ * (runtime/ops/PagedAttention.cpp:399-573; declared PagedAttention.hpp:262-324). The reference appends dispatches
+ * to a command graph; here a call launches on `stream`. Every check the reference makes before it encodes
+ * (PagedAttention.cpp:407-408,448-455,474-478: parameter blocks, plan rows, scratch sizes, aliasing of queries and
+ * output, missing tree masks) happens before the FIRST launch and returns RK_ERR_INVALID with the reference's
+ * text in rk_last_error(): a refused call has launched nothing (the reference tests that a rejected call never
+ * "partially encoded a graph", dev/tests/engine/paged_attention_plan_test.mm:748-761).
+ * A plan handle holds PagedAttention::verifyPlan / prefillPlan for one batch shape; rk_op_plan_workspace gives
+ * out[6] = partials bytes, statistics bytes, splits, row capacity (verify) or rows (prefill), bit 0 streaming
+ * decode | bit 1 tcgen05 window, descriptor bytes of the streaming decode. */
+typedef struct rk_verify_buffers {
+  void *chunk_keys, *chunk_values, *queries, *output;
+  float *partials, *statistics;
+  uint32_t *descriptors;                    /* streaming decode only (rk_decode_plan's descriptor bytes, zeroed once) */
+  uint32_t *status;                         /* tcgen05 window kernel only: one zeroed device word */
+  const rk_page_entry *const *page_tables; /* device array, one table address per lane */
+  const uint32_t *tree_masks;
+  uint64_t partials_bytes, statistics_bytes; /* sizes of the scratch actually bound */
+} rk_verify_buffers;
+void *rk_op_verify_plan(uint32_t lanes, uint32_t query_heads, uint32_t layers, uint32_t kv_heads, uint32_t head_dim,
+                        uint32_t format, const uint32_t *history, int tree, uint32_t row_capacity, uint32_t ctas);
+void *rk_op_prefill_plan(uint32_t rows, uint32_t query_heads, uint32_t layers, uint32_t kv_heads, uint32_t head_dim,
+                         uint32_t format);
+void rk_op_plan_destroy(void *plan);
+int rk_op_plan_workspace(const void *plan, uint64_t *out);
+uint32_t rk_op_plan_lane_splits(const void *plan, uint32_t lane);
+int rk_op_add_prefill_store(void *stream, rk_kv_layer layer, const void *chunk_keys, const void *chunk_values,
+                            const rk_page_entry *table, const rk_chunk_params *params, uint32_t layers,
+                            uint32_t kv_heads, uint32_t head_dim, uint32_t format);
+int rk_op_add_prefill(void *stream, rk_kv_layer layer, const void *queries, void *output, float *partials,
+                      float *statistics, uint64_t partials_bytes, uint64_t statistics_bytes,
+                      const rk_page_entry *table, const rk_chunk_params *chunk, const void *plan, const void *window,
+                      uint32_t *status);
+int rk_op_add_verify(void *stream, rk_kv_layer layer, const rk_verify_buffers *buffers,
+                     const rk_chunk_params *device_chunks, const rk_verify_params *device_attention, const void *plan,
+                     const void *window);
+int rk_op_add_verify_tree_compact(void *stream, rk_kv_layer layer, const rk_page_entry *const *page_tables,
+                                  const uint32_t *retained_path, const uint32_t *retained,
+                                  const rk_chunk_params *device_chunks, uint32_t lanes, uint32_t layers,
+                                  uint32_t kv_heads, uint32_t head_dim, uint32_t format);
 /* Empty string when valid, else the reference's tag (PagedAttention.hpp:75-95). */
 const char *rk_chunk_validation_error(uint32_t committed, uint32_t tokens, uint32_t stride, uint32_t entries);
 

@@ -37,6 +37,7 @@
 #include <cuda_fp16.h>
 
 #include <atomic>
+#include <cstring>
 
 namespace rk {
 
@@ -1232,63 +1233,226 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
   }
 }
 
-// Merge one query head's partials in slot order (segment, then warp) and store bf16 (and
-// optionally fp32). grid (group, kv_heads, lanes), 256 threads = one per dimension.
-__global__ void __launch_bounds__(256)
+// ---- merge of one (lane, KV head, query head): its partial slots -> {maximum, denominator, numerator} -------------
+// Slot s of a (lane, head) is segment s / 3, warp s % 3. The combination is a fixed function of the slot count
+// (same grid, same bits): slot s belongs to slot group s mod G, a group accumulates its slots in rising order, the
+// groups are added in group order; the denominator is summed per thread over slots t, t + threads, ..., then by a
+// fixed shuffle tree and in warp order.
+constexpr uint32_t kReduceChunk = 512; // slots whose weights sit in shared memory at a time
+template <uint32_t kGroups> struct ReduceShared {
+  float weights[kReduceChunk];
+  float4 sums[kGroups][kHeadDim / 4];
+  float warp_values[kGroups * 2];
+  float maximum, denominator;
+};
+
+// Threads = 64 * kGroups: thread = (slot group, four consecutive dims). Returns the numerator's four dims in the
+// threads of group 0 (tid < 64); maximum and denominator in shared memory.
+template <uint32_t kGroups>
+__device__ __forceinline__ float4 reduce_slots(const float *__restrict__ partials, const float *__restrict__ statistics,
+                                               uint32_t first, uint32_t segments, uint32_t head, uint32_t query_head,
+                                               ReduceShared<kGroups> &sh) {
+  constexpr uint32_t kReduceThreads = 64 * kGroups;
+  const uint32_t tid = threadIdx.x, group = tid >> 6, quad = tid & 63u;
+  const uint32_t slots = segments * kPageWarps;
+  auto slot_of = [&](uint32_t t) { return (uint64_t(first + t / kPageWarps) * kKvHeads + head) * kPageWarps + t % kPageWarps; };
+  // maximum over all slots
+  float maximum = -INFINITY;
+  for (uint32_t t = tid; t < slots; t += kReduceThreads)
+    maximum = fmaxf(maximum, __ldcg(statistics + (slot_of(t) * kGroup + query_head) * 2));
+  maximum = warp_max(maximum);
+  if ((tid & 31u) == 0) sh.warp_values[tid >> 5] = maximum;
+  __syncthreads();
+  maximum = sh.warp_values[0];
+#pragma unroll
+  for (uint32_t w = 1; w < kGroups * 2; ++w) maximum = fmaxf(maximum, sh.warp_values[w]);
+  __syncthreads();
+  float denominator = 0.0f;
+  float4 numerator = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  for (uint32_t base = 0; base < slots; base += kReduceChunk) {
+    const uint32_t count = min(kReduceChunk, slots - base);
+    for (uint32_t t = tid; t < count; t += kReduceThreads) {
+      const float2 stat = __ldcg(reinterpret_cast<const float2 *>(statistics + (slot_of(base + t) * kGroup + query_head) * 2));
+      const float weight = stat.x == -INFINITY ? 0.0f : expf(stat.x - maximum);
+      sh.weights[t] = weight;
+      denominator += weight * stat.y;
+    }
+    __syncthreads();
+    for (uint32_t t = group; t < count; t += kGroups) {
+      const float weight = sh.weights[t];
+      const float4 part = __ldcg(reinterpret_cast<const float4 *>(partials + (slot_of(base + t) * kGroup + query_head) * kHeadDim) + quad);
+      numerator.x += weight * part.x; numerator.y += weight * part.y; numerator.z += weight * part.z; numerator.w += weight * part.w;
+    }
+    __syncthreads();
+  }
+  denominator = warp_sum(denominator);
+  if ((tid & 31u) == 0) sh.warp_values[tid >> 5] = denominator;
+  sh.sums[group][quad] = numerator;
+  __syncthreads();
+  if (tid == 0) {
+    float total = 0.0f;
+#pragma unroll
+    for (uint32_t w = 0; w < kGroups * 2; ++w) total += sh.warp_values[w];
+    sh.denominator = total;
+    sh.maximum = maximum;
+  }
+  if (tid < 64) {
+#pragma unroll
+    for (uint32_t g = 1; g < kGroups; ++g) {
+      const float4 other = sh.sums[g][quad];
+      numerator.x += other.x; numerator.y += other.y; numerator.z += other.z; numerator.w += other.w;
+    }
+  }
+  __syncthreads();
+  return numerator;
+}
+
+__device__ __forceinline__ void store_output_quad(uint16_t *output, float *output_f32, uint64_t at, float4 value) {
+  const uint32_t low = uint32_t(float_to_bf16_bits(value.x)) | (uint32_t(float_to_bf16_bits(value.y)) << 16);
+  const uint32_t high = uint32_t(float_to_bf16_bits(value.z)) | (uint32_t(float_to_bf16_bits(value.w)) << 16);
+  *reinterpret_cast<uint2 *>(output + at) = make_uint2(low, high);
+  if (output_f32) *reinterpret_cast<float4 *>(output_f32 + at) = value;
+}
+
+// Merge one query head's partials and store bf16 (and optionally fp32), or leave the shard triple of a sequence
+// split. grid (group, kv_heads, lanes), 64 * kGroups threads.
+template <uint32_t kGroups>
+__global__ void __launch_bounds__(64 * kGroups)
 decode_reduce_kernel(const float *__restrict__ partials, const float *__restrict__ statistics,
                      const uint32_t *__restrict__ descriptors, uint16_t *__restrict__ output,
                      float *__restrict__ output_f32, const rk_verify_params *__restrict__ lane_params,
                      rk_kv_layer layer, float *__restrict__ shard_out) {
-  constexpr uint32_t kMaxSlots = 64;
-  __shared__ float weights[kMaxSlots];
-  __shared__ float denominator_shared, maximum_shared;
+  __shared__ ReduceShared<kGroups> sh;
   const uint32_t query_head = blockIdx.x, head = blockIdx.y, l = blockIdx.z, tid = threadIdx.x;
-  dependency_wait(); // partials, statistics and descriptors come from the decode kernel launched just before
+  dependents_may_launch(); // the next kernel of the stream may take its place; it waits for this grid's writes
+  dependency_wait();       // partials, statistics and descriptors come from the decode kernel launched just before
   rk_verify_params p = lane_params[l];
   p.kv = layer;
   if (!rk_verify_contract_valid(&p) || p.active_rows != 1 || p.row_capacity != 1) return;
-  const uint32_t first = descriptors[2 * l], segments = descriptors[2 * l + 1];
-  const uint32_t slots = segments * kPageWarps;
-  const uint64_t tile = ((uint64_t(l) * kKvHeads + head) * RK_VERIFY_CHUNK_STRIDE) * kGroup * kHeadDim;
-  // slot s of this (lane, head): segment s / 3, warp s % 3
-  auto slot_of = [&](uint32_t s) { return (uint64_t(first + s / kPageWarps) * kKvHeads + head) * kPageWarps + s % kPageWarps; };
-  float numerator = 0.0f;
-  for (uint32_t base = 0; base < slots; base += kMaxSlots) { // one pass unless a lane spans > 21 ranges
-    const uint32_t count = min(kMaxSlots, slots - base);
-    if (tid < 32) {
-      // the maximum is over ALL slots, so every pass weighs against the same reference
-      float maximum = -INFINITY;
-      for (uint32_t t = tid; t < slots; t += 32)
-        maximum = fmaxf(maximum, statistics[(slot_of(t) * kGroup + query_head) * 2]);
-      maximum = warp_max(maximum);
-      if (tid == 0) maximum_shared = maximum;
-      for (uint32_t t = tid; t < count; t += 32) {
-        const float own = statistics[(slot_of(base + t) * kGroup + query_head) * 2];
-        weights[t] = own == -INFINITY ? 0.0f : expf(own - maximum);
-      }
-      __syncwarp();
-      if (tid == 0) { // the denominator accumulates in slot order
-        float denominator = base ? denominator_shared : 0.0f;
-        for (uint32_t t = 0; t < count; ++t)
-          denominator += weights[t] * statistics[(slot_of(base + t) * kGroup + query_head) * 2 + 1];
-        denominator_shared = denominator;
-      }
-    }
-    __syncthreads();
-    for (uint32_t s = 0; s < count; ++s) // slot order; loads are independent of one another
-      numerator += weights[s] * partials[(slot_of(base + s) * kGroup + query_head) * kHeadDim + tid];
-    __syncthreads();
-  }
-  const float denominator = denominator_shared;
+  const float4 numerator = reduce_slots<kGroups>(partials, statistics, __ldcg(descriptors + 2 * l), __ldcg(descriptors + 2 * l + 1), head, query_head, sh);
+  const float denominator = sh.denominator;
   if (shard_out) { // this rank's piece of a sequence split: {max, sum, un-normalised output} per query head
     float *triple = shard_out + ((uint64_t(l) * kKvHeads + head) * kGroup + query_head) * (kHeadDim + 2);
-    if (tid == 0) { triple[0] = maximum_shared; triple[1] = denominator; }
-    triple[2 + tid] = numerator;
+    if (tid == 0) { triple[0] = sh.maximum; triple[1] = denominator; }
+    if (tid < 64) { // triples are 8-byte aligned (258 floats each): two 8-byte stores
+      *reinterpret_cast<float2 *>(triple + 2 + 4 * tid) = make_float2(numerator.x, numerator.y);
+      *reinterpret_cast<float2 *>(triple + 4 + 4 * tid) = make_float2(numerator.z, numerator.w);
+    }
     return;
   }
-  const float value = denominator > 0.0f ? numerator / denominator : 0.0f;
-  output[tile + query_head * kHeadDim + tid] = float_to_bf16_bits(value);
-  if (output_f32) output_f32[tile + query_head * kHeadDim + tid] = value;
+  if (tid < 64) {
+    const uint64_t tile = ((uint64_t(l) * kKvHeads + head) * RK_VERIFY_CHUNK_STRIDE) * kGroup * kHeadDim;
+    const float4 value = denominator > 0.0f ? make_float4(numerator.x / denominator, numerator.y / denominator,
+                                                          numerator.z / denominator, numerator.w / denominator)
+                                            : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    store_output_quad(output, output_f32, tile + query_head * kHeadDim + 4 * tid, value);
+  }
+}
+
+// ---- sequence split without a library collective: reduce -> peer stores -> flags -> rank-order merge, one kernel ----
+// Every rank owns one exchange buffer that its peers can address (CUDA IPC mappings): slots
+// [parity][source rank][lane][query head]{max, sum, D numerators} and flags [parity][source rank][lane][query head].
+// A block (query head, KV head, lane) reduces its own partials, writes its triple into slot [parity][my rank] of
+// EVERY rank's buffer with plain stores (NVLink for the peers), publishes it with one system-scope release per rank,
+// then waits (bounded) until every source rank's flag in ITS OWN buffer carries this step's epoch and merges the
+// sources in rank order (paged_attention_tile.h:362-404 with "split" = rank), so all ranks end with identical bits.
+// Parity = epoch & 1: a rank can only reach step k+2 after every rank published step k+1, which each rank does
+// after its own merge of step k, so a slot is never overwritten while someone still reads it. Only this kernel
+// touches peer memory; no TMA and no multicast is involved.
+constexpr uint32_t kMaxRanks = 8;
+constexpr uint32_t kTripleFloats = kHeadDim + 2;
+struct ExchangeArgs {
+  float *slots[kMaxRanks];    // every rank's slot area (own entry = local memory)
+  uint32_t *flags[kMaxRanks]; // every rank's flag area
+  uint32_t rank, ranks, lanes, epoch, spin_limit;
+  uint32_t post_only;         // single-GPU emulation of the earlier ranks: publish, do not wait or merge
+  uint32_t *status;
+};
+
+__device__ __forceinline__ void store_release_system(uint32_t *address, uint32_t value) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(address), "r"(value) : "memory");
+}
+__device__ __forceinline__ uint32_t load_acquire_system(const uint32_t *address) {
+  uint32_t value;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(value) : "l"(address) : "memory");
+  return value;
+}
+
+template <uint32_t kGroups>
+__global__ void __launch_bounds__(64 * kGroups)
+shard_exchange_kernel(const float *__restrict__ partials, const float *__restrict__ statistics,
+                      const uint32_t *__restrict__ descriptors, uint16_t *__restrict__ output,
+                      float *__restrict__ output_f32, const rk_verify_params *__restrict__ lane_params,
+                      rk_kv_layer layer, ExchangeArgs ex) {
+  __shared__ ReduceShared<kGroups> sh;
+  __shared__ uint32_t arrived;
+  const uint32_t query_head = blockIdx.x, head = blockIdx.y, l = blockIdx.z, tid = threadIdx.x;
+  dependents_may_launch();
+  dependency_wait();
+  rk_verify_params p = lane_params[l];
+  p.kv = layer;
+  // a lane this rank holds no pages of (an empty shard, or an invalid lane) still publishes an empty triple
+  const bool valid = rk_verify_contract_valid(&p) && p.active_rows == 1 && p.row_capacity == 1;
+  float4 numerator = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  float maximum = -INFINITY, denominator = 0.0f;
+  if (valid) {
+    numerator = reduce_slots<kGroups>(partials, statistics, __ldcg(descriptors + 2 * l), __ldcg(descriptors + 2 * l + 1), head, query_head, sh);
+    maximum = sh.maximum;
+    denominator = sh.denominator;
+  }
+  const uint32_t parity = ex.epoch & 1u, fused_head = head * kGroup + query_head;
+  const uint64_t cell = uint64_t(l) * (kKvHeads * kGroup) + fused_head;                     // (lane, query head)
+  const uint64_t cells = uint64_t(ex.lanes) * (kKvHeads * kGroup);
+  const uint64_t mine = (uint64_t(parity) * ex.ranks + ex.rank) * cells + cell;               // where my triple goes, in every buffer
+  for (uint32_t r = 0; r < ex.ranks; ++r) {
+    float *triple = ex.slots[r] + mine * kTripleFloats;
+    if (tid == 0) *reinterpret_cast<float2 *>(triple) = make_float2(maximum, denominator);
+    if (tid < 64) {
+      *reinterpret_cast<float2 *>(triple + 2 + 4 * tid) = make_float2(numerator.x, numerator.y);
+      *reinterpret_cast<float2 *>(triple + 4 + 4 * tid) = make_float2(numerator.z, numerator.w);
+    }
+  }
+  __syncthreads(); // every thread's stores are ordered before the fences and releases below
+  if (tid < ex.ranks) {
+    __threadfence_system();
+    store_release_system(ex.flags[tid] + mine, ex.epoch);
+  }
+  if (ex.post_only) return;
+  // wait for every source rank's triple of this step in my own buffer
+  if (tid == 0) arrived = 1;
+  __syncthreads();
+  if (tid < ex.ranks) {
+    const uint32_t *flag = ex.flags[ex.rank] + (uint64_t(parity) * ex.ranks + tid) * cells + cell;
+    bool seen = false;
+    for (uint32_t i = 0; i < ex.spin_limit; ++i) {
+      if (load_acquire_system(flag) == ex.epoch) { seen = true; break; }
+      if (i > 64) __nanosleep(64);
+    }
+    if (!seen) { arrived = 0; atomicExch(ex.status, 3u); }
+  }
+  __syncthreads();
+  if (tid >= 64) return;
+  float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  float total_denominator = 0.0f;
+  if (arrived) {
+    const float *local = ex.slots[ex.rank] + (uint64_t(parity) * ex.ranks * cells + cell) * kTripleFloats;
+    const uint64_t stride = cells * kTripleFloats;
+    float all_maximum = -INFINITY;
+    for (uint32_t r = 0; r < ex.ranks; ++r) all_maximum = fmaxf(all_maximum, __ldcg(local + r * stride));
+    for (uint32_t r = 0; r < ex.ranks; ++r) {
+      const float2 stat = __ldcg(reinterpret_cast<const float2 *>(local + r * stride));
+      const float weight = stat.x == -INFINITY ? 0.0f : expf(stat.x - all_maximum);
+      const float2 a = __ldcg(reinterpret_cast<const float2 *>(local + r * stride + 2 + 4 * tid));
+      const float2 b = __ldcg(reinterpret_cast<const float2 *>(local + r * stride + 4 + 4 * tid));
+      total.x += weight * a.x; total.y += weight * a.y; total.z += weight * b.x; total.w += weight * b.y;
+      total_denominator += weight * stat.y;
+    }
+  }
+  const float4 value = total_denominator > 0.0f ? make_float4(total.x / total_denominator, total.y / total_denominator,
+                                                              total.z / total_denominator, total.w / total_denominator)
+                                                : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  const uint64_t tile = ((uint64_t(l) * kKvHeads + head) * RK_VERIFY_CHUNK_STRIDE) * kGroup * kHeadDim;
+  store_output_quad(output, output_f32, tile + query_head * kHeadDim + 4 * tid, value);
 }
 
 // Combine the shards of a sequence split: shard r holds {max, sum, un-normalised output} per
@@ -1346,22 +1510,44 @@ int configure_decode_kernel() {
 using namespace rk;
 
 // The merge follows its decode kernel as a programmatic dependent launch: its blocks are placed while the decode
-// grid drains and start the moment that grid's writes are visible.
-static int launch_merge(uint32_t lanes, cudaStream_t stream, const float *partials, const float *statistics,
-                        const uint32_t *descriptors, uint16_t *output, float *output_f32,
-                        const rk_verify_params *lane_params, rk_kv_layer layer, float *triples) {
+// grid drains and start the moment that grid's writes are visible. Few lanes (a sequence split: one lane over every
+// CTA has hundreds of slots) take sixteen slot groups per block, batches four.
+static bool wide_merge(uint32_t lanes) { return lanes * kKvHeads * kGroup <= 2 * 148; }
+
+template <typename Kernel, typename... Args>
+static int launch_dependent(Kernel kernel, dim3 grid, uint32_t threads, cudaStream_t stream, const char *what, Args... args) {
   cudaLaunchConfig_t config{};
-  config.gridDim = dim3(kGroup, kKvHeads, lanes);
-  config.blockDim = dim3(256);
+  config.gridDim = grid;
+  config.blockDim = dim3(threads);
   config.stream = stream;
   cudaLaunchAttribute attribute{};
   attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attribute.val.programmaticStreamSerializationAllowed = 1;
   config.attrs = &attribute;
   config.numAttrs = 1;
-  return cuda_status(cudaLaunchKernelEx(&config, decode_reduce_kernel, partials, statistics, descriptors, output, output_f32,
-                                        lane_params, layer, triples),
-                     "decode reduce launch");
+  return cuda_status(cudaLaunchKernelEx(&config, kernel, args...), what);
+}
+
+static int launch_merge(uint32_t lanes, cudaStream_t stream, const float *partials, const float *statistics,
+                        const uint32_t *descriptors, uint16_t *output, float *output_f32,
+                        const rk_verify_params *lane_params, rk_kv_layer layer, float *triples) {
+  const dim3 grid(kGroup, kKvHeads, lanes);
+  if (wide_merge(lanes))
+    return launch_dependent(decode_reduce_kernel<16>, grid, 1024, stream, "decode reduce launch", partials, statistics, descriptors,
+                            output, output_f32, lane_params, layer, triples);
+  return launch_dependent(decode_reduce_kernel<4>, grid, 256, stream, "decode reduce launch", partials, statistics, descriptors,
+                          output, output_f32, lane_params, layer, triples);
+}
+
+static int launch_exchange(uint32_t lanes, cudaStream_t stream, const float *partials, const float *statistics,
+                           const uint32_t *descriptors, uint16_t *output, float *output_f32,
+                           const rk_verify_params *lane_params, rk_kv_layer layer, const ExchangeArgs &exchange) {
+  const dim3 grid(kGroup, kKvHeads, lanes);
+  if (wide_merge(lanes))
+    return launch_dependent(shard_exchange_kernel<16>, grid, 1024, stream, "shard exchange launch", partials, statistics, descriptors,
+                            output, output_f32, lane_params, layer, exchange);
+  return launch_dependent(shard_exchange_kernel<4>, grid, 256, stream, "shard exchange launch", partials, statistics, descriptors,
+                          output, output_f32, lane_params, layer, exchange);
 }
 
 // The streaming kernel of a format on `ctas` CTAs.
@@ -1456,8 +1642,7 @@ int rk_attention_decode_shard(const void *window, const rk_decode_plan *plan, ui
   DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, plan->lanes,
                   descriptors + 2 * plan->lanes, kSpinLimit, 0};
   if (int st = launch_decode(format, plan->ctas, s, w, args)) return st;
-  decode_reduce_kernel<<<dim3(kGroup, kKvHeads, plan->lanes), 256, 0, s>>>(partials, statistics, descriptors, nullptr, nullptr, lane_params, layer, triples);
-  return cuda_status(cudaGetLastError(), "decode shard reduce launch");
+  return launch_merge(plan->lanes, s, partials, statistics, descriptors, nullptr, nullptr, lane_params, layer, triples);
 }
 
 // Merges `shards` gathered triples ([shard][lane][query_head][2 + D]) in shard order into the bf16
@@ -1468,6 +1653,114 @@ int rk_attention_merge_shards(uint32_t kv_heads, uint32_t query_heads, uint32_t 
   if (!lanes || !shards || !triples || !output) { set_error("rk_attention_merge_shards: invalid arguments"); return kInvalid; }
   merge_shards_kernel<<<dim3(query_heads, lanes), 256, 0, static_cast<cudaStream_t>(stream)>>>(triples, shards, lanes, static_cast<uint16_t *>(output), output_f32);
   return cuda_status(cudaGetLastError(), "merge shards launch");
+}
+
+// ---- sequence split over peer memory ------------------------------------------------------------------------------
+// One rank's exchange buffer and its view of the peers' buffers (see shard_exchange_kernel).
+struct Exchange {
+  uint32_t rank = 0, ranks = 1, lanes = 1, epoch = 0;
+  unsigned char *local = nullptr;
+  size_t slot_bytes = 0, flag_bytes = 0;
+  unsigned char *mapped[kMaxRanks] = {}; // peers' buffers as this process sees them (own entry = local)
+  bool opened[kMaxRanks] = {};
+};
+
+void *rk_exchange_create(uint32_t rank, uint32_t ranks, uint32_t lanes, void *handle_out) {
+  if (!ranks || ranks > kMaxRanks || rank >= ranks || !lanes || lanes > kMaxLanes) {
+    set_error("rk_exchange_create: ranks 1..8, rank < ranks, lanes 1..1024");
+    return nullptr;
+  }
+  auto *ex = new Exchange;
+  ex->rank = rank; ex->ranks = ranks; ex->lanes = lanes;
+  const size_t cells = size_t(2) * ranks * lanes * kKvHeads * kGroup;
+  ex->slot_bytes = (cells * kTripleFloats * sizeof(float) + 255) / 256 * 256;
+  ex->flag_bytes = (cells * sizeof(uint32_t) + 255) / 256 * 256;
+  void *memory = nullptr;
+  if (cuda_status(cudaMalloc(&memory, ex->slot_bytes + ex->flag_bytes), "exchange buffer") ||
+      cuda_status(cudaMemset(memory, 0, ex->slot_bytes + ex->flag_bytes), "exchange buffer clear")) {
+    if (memory) cudaFree(memory);
+    delete ex;
+    return nullptr;
+  }
+  ex->local = static_cast<unsigned char *>(memory);
+  for (uint32_t r = 0; r < ranks; ++r) ex->mapped[r] = ex->local; // until connected: every "peer" is this buffer
+  if (handle_out) {
+    cudaIpcMemHandle_t handle;
+    if (cuda_status(cudaIpcGetMemHandle(&handle, memory), "cudaIpcGetMemHandle")) {
+      cudaFree(memory);
+      delete ex;
+      return nullptr;
+    }
+    static_assert(sizeof(handle) == 64, "the handle travels as 64 bytes");
+    memcpy(handle_out, &handle, sizeof(handle));
+  }
+  return ex;
+}
+
+// `handles`: ranks x 64 bytes, rank r's from its rk_exchange_create (gathered by the caller, e.g. over
+// torch.distributed). Maps every peer's buffer into this process.
+int rk_exchange_connect(void *exchange, const void *handles) {
+  auto *ex = static_cast<Exchange *>(exchange);
+  if (!ex || !handles) { set_error("rk_exchange_connect: invalid arguments"); return kInvalid; }
+  for (uint32_t r = 0; r < ex->ranks; ++r) {
+    if (r == ex->rank || ex->opened[r]) continue;
+    cudaIpcMemHandle_t handle;
+    memcpy(&handle, static_cast<const unsigned char *>(handles) + size_t(r) * sizeof(handle), sizeof(handle));
+    void *peer = nullptr;
+    if (int st = cuda_status(cudaIpcOpenMemHandle(&peer, handle, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle")) return st;
+    ex->mapped[r] = static_cast<unsigned char *>(peer);
+    ex->opened[r] = true;
+  }
+  return kOk;
+}
+
+void rk_exchange_destroy(void *exchange) {
+  auto *ex = static_cast<Exchange *>(exchange);
+  if (!ex) return;
+  for (uint32_t r = 0; r < ex->ranks; ++r)
+    if (ex->opened[r]) cudaIpcCloseMemHandle(ex->mapped[r]);
+  if (ex->local) cudaFree(ex->local);
+  delete ex;
+}
+
+// One rank's whole sequence-split decode step in two launches: the streaming decode kernel over the pages this
+// rank holds, then shard_exchange_kernel (reduce -> peer stores -> flags -> rank-order merge). Every rank calls it
+// once per step, in the same order; `output` ends identical on all ranks. loopback_rank < 0 in production. With
+// loopback_rank >= 0 (an unconnected exchange on ONE GPU) the call acts as that rank of an emulated step: ranks
+// 0 .. ranks-2 only publish, the call for the last rank waits (its flags are already there) and merges.
+// A wait for a peer that runs out raises the decode status word (rk_attention_decode_status) and writes zeros.
+// The step's epoch is a launch argument: do not replay these launches from a captured graph.
+int rk_attention_decode_exchange(const void *window, const rk_decode_plan *plan, uint32_t format, const void *queries,
+                                 void *output, float *output_f32, float *partials, float *statistics, uint32_t *descriptors,
+                                 const rk_page_entry *const *tables, const rk_verify_params *lane_params, rk_kv_layer layer,
+                                 void *exchange, int32_t loopback_rank, void *stream) {
+  const auto *w = static_cast<const Window *>(window);
+  auto *ex = static_cast<Exchange *>(exchange);
+  if (!w || !plan || !ex || !queries || !output || !partials || !statistics || !descriptors || !tables || !lane_params ||
+      !layer.extent_pages || format < RK_FORMAT_INT8 || format > RK_FORMAT_FP8E4M3 || plan->lanes != ex->lanes ||
+      loopback_rank >= int32_t(ex->ranks)) {
+    set_error("rk_attention_decode_exchange: invalid arguments");
+    return kInvalid;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (int st = configure_decode_kernel()) return st;
+  DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, plan->lanes,
+                  descriptors + 2 * plan->lanes, kSpinLimit, 0};
+  if (int st = launch_decode(format, plan->ctas, s, w, args)) return st;
+  ExchangeArgs e{};
+  for (uint32_t r = 0; r < ex->ranks; ++r) {
+    e.slots[r] = reinterpret_cast<float *>(ex->mapped[r]);
+    e.flags[r] = reinterpret_cast<uint32_t *>(ex->mapped[r] + ex->slot_bytes);
+  }
+  e.rank = loopback_rank >= 0 ? uint32_t(loopback_rank) : ex->rank;
+  if (loopback_rank <= 0) ++ex->epoch; // a new step (in an emulated step: when its rank 0 runs)
+  e.ranks = ex->ranks;
+  e.lanes = ex->lanes;
+  e.epoch = ex->epoch;
+  e.spin_limit = 1u << 22; // polls of ~0.1-0.3 us: a peer may lag by about a second before the wait gives up
+  e.post_only = loopback_rank >= 0 && uint32_t(loopback_rank) + 1 != ex->ranks;
+  e.status = descriptors + 2 * plan->lanes;
+  return launch_exchange(plan->lanes, s, partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer, e);
 }
 
 // ---- decode attention without any allocation -----------------------------------------------------
@@ -1540,8 +1833,7 @@ int rk_attention_decode_static(const void *window, uint32_t format, uint32_t lan
   DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, lanes,
                   descriptors + 2 * kStaticLanes, kSpinLimit, 0};
   if (int st = launch_decode(format, kStaticCtas, s, w, args)) return st;
-  decode_reduce_kernel<<<dim3(kGroup, kKvHeads, lanes), 256, 0, s>>>(partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer, nullptr);
-  return cuda_status(cudaGetLastError(), "decode reduce launch");
+  return launch_merge(lanes, s, partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer, nullptr);
 }
 
 // Reads AND clears a sticky status word on `stream` (synchronises it): kTimeout when a bounded wait inside a decode

@@ -11,6 +11,7 @@
 #include <cstring>
 #include <deque>
 #include <memory>
+#include <stdexcept>
 #include <string>
 
 namespace rk { void set_error(const char *text); }
@@ -421,6 +422,103 @@ int rk_plan_workspaces(uint32_t lanes, uint32_t max_rows, uint32_t query_heads, 
     return RK_OK;
   });
 }
+// ---- the operator's encoders (ops::PagedAttention::add*): validation first, then the launches ------------------
+namespace {
+struct OperatorPlan {
+  bool verify = false;
+  kv::Layout layout{};
+  uint32_t queryHeads = 0;
+  ops::VerifyAttentionPlan verifyPlan{};
+  ops::PrefillAttentionPlan prefillPlan{};
+};
+} // namespace
+
+void *rk_op_verify_plan(uint32_t lanes, uint32_t query_heads, uint32_t layers, uint32_t kv_heads, uint32_t head_dim, uint32_t format,
+                        const uint32_t *history, int tree, uint32_t row_capacity, uint32_t ctas) {
+  OperatorPlan *plan = nullptr;
+  guarded([&] {
+    auto made = std::make_unique<OperatorPlan>();
+    made->verify = true;
+    made->layout = layoutOf(layers, kv_heads, head_dim, format);
+    made->queryHeads = query_heads;
+    made->verifyPlan = ops::PagedAttention::verifyPlan(lanes, query_heads, made->layout, {history, lanes}, tree != 0, row_capacity, ctas);
+    plan = made.release();
+    return RK_OK;
+  });
+  return plan;
+}
+void *rk_op_prefill_plan(uint32_t rows, uint32_t query_heads, uint32_t layers, uint32_t kv_heads, uint32_t head_dim, uint32_t format) {
+  OperatorPlan *plan = nullptr;
+  guarded([&] {
+    auto made = std::make_unique<OperatorPlan>();
+    made->layout = layoutOf(layers, kv_heads, head_dim, format);
+    made->queryHeads = query_heads;
+    made->prefillPlan = ops::PagedAttention::prefillPlan(rows, query_heads, made->layout);
+    plan = made.release();
+    return RK_OK;
+  });
+  return plan;
+}
+void rk_op_plan_destroy(void *plan) { delete static_cast<OperatorPlan *>(plan); }
+int rk_op_plan_workspace(const void *plan, uint64_t *out) {
+  const auto *p = static_cast<const OperatorPlan *>(plan);
+  if (!p || !out) { rk::set_error("rk_op_plan_workspace: invalid arguments"); return RK_ERR_INVALID; }
+  const ops::AttentionWorkspace &w = p->verify ? p->verifyPlan.workspace : p->prefillPlan.workspace;
+  out[0] = w.partialsBytes; out[1] = w.statisticsBytes;
+  out[2] = p->verify ? p->verifyPlan.splits : p->prefillPlan.splits;
+  out[3] = p->verify ? p->verifyPlan.rowCapacity : p->prefillPlan.rows;
+  out[4] = p->verify ? uint64_t(p->verifyPlan.streamingDecode) | (uint64_t(p->verifyPlan.tensorCoreWindow) << 1) : 0;
+  out[5] = p->verify ? p->verifyPlan.decode.descriptor_bytes : 0;
+  return RK_OK;
+}
+uint32_t rk_op_plan_lane_splits(const void *plan, uint32_t lane) {
+  const auto *p = static_cast<const OperatorPlan *>(plan);
+  return p && p->verify && lane < p->verifyPlan.laneSplits.size() ? p->verifyPlan.laneSplits[lane] : 0;
+}
+
+int rk_op_add_prefill_store(void *stream, rk_kv_layer layer, const void *chunk_keys, const void *chunk_values, const rk_page_entry *table,
+                            const rk_chunk_params *params, uint32_t layers, uint32_t kv_heads, uint32_t head_dim, uint32_t format) {
+  return guarded([&] {
+    if (!params) throw std::invalid_argument("invalid paged prefill store");
+    ops::PagedAttention::addPrefillStore(stream, layer, chunk_keys, chunk_values, table, *params, layoutOf(layers, kv_heads, head_dim, format));
+    return RK_OK;
+  });
+}
+int rk_op_add_prefill(void *stream, rk_kv_layer layer, const void *queries, void *output, float *partials, float *statistics,
+                      uint64_t partials_bytes, uint64_t statistics_bytes, const rk_page_entry *table, const rk_chunk_params *chunk,
+                      const void *plan, const void *window, uint32_t *status) {
+  return guarded([&] {
+    const auto *p = static_cast<const OperatorPlan *>(plan);
+    if (!p || p->verify || !chunk) throw std::invalid_argument("prefill attention needs a prefill plan");
+    ops::PagedAttention::addPrefill(stream, layer, queries, output, partials, statistics, partials_bytes, statistics_bytes, table, *chunk,
+                                    p->prefillPlan, p->queryHeads, p->layout, window, status);
+    return RK_OK;
+  });
+}
+int rk_op_add_verify(void *stream, rk_kv_layer layer, const rk_verify_buffers *buffers, const rk_chunk_params *device_chunks,
+                     const rk_verify_params *device_attention, const void *plan, const void *window) {
+  return guarded([&] {
+    const auto *p = static_cast<const OperatorPlan *>(plan);
+    if (!p || !p->verify || !buffers) throw std::invalid_argument("verify attention needs a verify plan");
+    ops::PagedVerifyBuffers b;
+    b.chunkKeys = buffers->chunk_keys; b.chunkValues = buffers->chunk_values; b.queries = buffers->queries; b.output = buffers->output;
+    b.partials = buffers->partials; b.statistics = buffers->statistics; b.descriptors = buffers->descriptors; b.status = buffers->status;
+    b.pageTables = buffers->page_tables; b.treeMasks = buffers->tree_masks;
+    b.partialsBytes = buffers->partials_bytes; b.statisticsBytes = buffers->statistics_bytes;
+    ops::PagedAttention::addVerify(stream, layer, b, device_chunks, device_attention, p->verifyPlan, p->queryHeads, p->layout, window);
+    return RK_OK;
+  });
+}
+int rk_op_add_verify_tree_compact(void *stream, rk_kv_layer layer, const rk_page_entry *const *page_tables, const uint32_t *retained_path,
+                                  const uint32_t *retained, const rk_chunk_params *device_chunks, uint32_t lanes, uint32_t layers,
+                                  uint32_t kv_heads, uint32_t head_dim, uint32_t format) {
+  return guarded([&] {
+    ops::PagedAttention::addVerifyTreeCompact(stream, layer, page_tables, retained_path, retained, device_chunks, lanes,
+                                              layoutOf(layers, kv_heads, head_dim, format));
+    return RK_OK;
+  });
+}
+
 const char *rk_chunk_validation_error(uint32_t committed, uint32_t tokens, uint32_t stride, uint32_t entries) {
   static thread_local std::string text;
   text = std::string(ops::chunkedPrefillValidationError(rk_chunk_params{committed, tokens, stride, entries, {0, 0}}));

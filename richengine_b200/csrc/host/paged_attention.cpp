@@ -214,6 +214,10 @@ void PagedAttention::addVerify(void *stream, rk_kv_layer layer, const PagedVerif
   const bool tree = plan.rowCapacity > kVerifyRows;
   if (tree && !b.treeMasks) throw std::invalid_argument("tree verify requires its ancestor masks");
   if (plan.streamingDecode && (!window || !b.descriptors)) throw std::invalid_argument("streaming decode needs the pool window and its descriptors");
+  if (plan.tensorCoreWindow && !plan.streamingDecode && (!window || !b.status))
+    throw std::invalid_argument("the window kernel needs the pool window and a status word");
+  if (!b.chunkKeys || !b.chunkValues || !b.queries || !b.output || !b.partials || !b.statistics) throw std::invalid_argument("invalid paged verify batch");
+  // every check is done: from here on the call launches
   const uint32_t format = formatCode(layout.format);
   check(rk_store_verify(format, layout.kvHeads, layout.headDimension, plan.lanes, std::min<uint32_t>(plan.rowCapacity, RK_TREE_NODES),
                         b.chunkKeys, b.chunkValues, b.pageTables, deviceChunks, layer, stream));
@@ -223,7 +227,6 @@ void PagedAttention::addVerify(void *stream, rk_kv_layer layer, const PagedVerif
     return;
   }
   if (plan.tensorCoreWindow) {
-    if (!window || !b.status) throw std::invalid_argument("the window kernel needs the pool window and a status word");
     check(rk_attention_verify_split_tc(window, format, layout.kvHeads, queryHeads, layout.headDimension, plan.lanes, plan.rowCapacity,
                                        plan.splits, b.queries, b.partials, b.statistics, b.pageTables, tree ? b.treeMasks : nullptr,
                                        deviceAttention, layer, b.status, stream));

@@ -46,6 +46,14 @@ class DecodePlan(C.Structure):
                 ("partials_bytes", C.c_uint64), ("statistics_bytes", C.c_uint64), ("descriptor_bytes", C.c_uint64)]
 
 
+class VerifyBuffers(C.Structure):
+    """rk_verify_buffers (include/richkv_host.h)."""
+    _fields_ = [("chunk_keys", C.c_void_p), ("chunk_values", C.c_void_p), ("queries", C.c_void_p), ("output", C.c_void_p),
+                ("partials", C.c_void_p), ("statistics", C.c_void_p), ("descriptors", C.c_void_p), ("status", C.c_void_p),
+                ("page_tables", C.c_void_p), ("tree_masks", C.c_void_p), ("partials_bytes", C.c_uint64),
+                ("statistics_bytes", C.c_uint64)]
+
+
 assert C.sizeof(ChunkParams) == 24 and C.sizeof(PrefillParams) == 32 and C.sizeof(VerifyParams) == 36
 
 u32, u64, i32, i64, vp, f32p = C.c_uint32, C.c_uint64, C.c_int, C.c_int64, C.c_void_p, C.c_void_p
@@ -81,6 +89,10 @@ SIGNATURES = {
     "rk_attention_decode": (i32, [vp, C.POINTER(DecodePlan), u32, vp, vp, vp, vp, vp, vp, vp, vp, KvLayer, vp]),
     "rk_attention_decode_shard": (i32, [vp, C.POINTER(DecodePlan), u32, vp, vp, vp, vp, vp, vp, vp, KvLayer, vp]),
     "rk_attention_merge_shards": (i32, [u32, u32, u32, u32, u32, vp, vp, vp, vp]),
+    "rk_exchange_create": (vp, [u32, u32, u32, vp]),
+    "rk_exchange_connect": (i32, [vp, vp]),
+    "rk_exchange_destroy": (None, [vp]),
+    "rk_attention_decode_exchange": (i32, [vp, C.POINTER(DecodePlan), u32, vp, vp, vp, vp, vp, vp, vp, vp, KvLayer, vp, i32, vp]),
     "rk_attention_decode_static": (i32, [vp, u32, u32, vp, vp, vp, vp, vp, KvLayer, vp]),
     "rk_attention_decode_status": (i32, [C.POINTER(DecodePlan), vp, vp]),
     "rk_attention_decode_static_status": (i32, [vp]),
@@ -176,6 +188,15 @@ SIGNATURES = {
     "rk_plan_verify": (i32, [u32, u32, u32, u32, u32, u32, vp, i32, u32, u32, C.c_char_p, C.c_size_t, vp]),
     "rk_plan_prefill": (i32, [u32, u32, u32, u32, u32, u32, C.c_char_p, C.c_size_t, vp]),
     "rk_plan_workspaces": (i32, [u32, u32, u32, u32, u32, u32, u32, vp]),
+    "rk_op_verify_plan": (vp, [u32, u32, u32, u32, u32, u32, vp, i32, u32, u32]),
+    "rk_op_prefill_plan": (vp, [u32, u32, u32, u32, u32, u32]),
+    "rk_op_plan_destroy": (None, [vp]),
+    "rk_op_plan_workspace": (i32, [vp, vp]),
+    "rk_op_plan_lane_splits": (u32, [vp, u32]),
+    "rk_op_add_prefill_store": (i32, [vp, KvLayer, vp, vp, vp, C.POINTER(ChunkParams), u32, u32, u32, u32]),
+    "rk_op_add_prefill": (i32, [vp, KvLayer, vp, vp, vp, vp, u64, u64, vp, C.POINTER(ChunkParams), vp, vp, vp]),
+    "rk_op_add_verify": (i32, [vp, KvLayer, C.POINTER(VerifyBuffers), vp, vp, vp, vp]),
+    "rk_op_add_verify_tree_compact": (i32, [vp, KvLayer, vp, vp, vp, vp, u32, u32, u32, u32, u32]),
     "rk_chunk_validation_error": (C.c_char_p, [u32, u32, u32, u32]),
 }
 

@@ -57,11 +57,13 @@ def tail_owner(visible_tokens: int, ranks: int) -> int:
     return ranks - 1
 
 
-def gather_shards(triples: torch.Tensor, group=None) -> torch.Tensor:
-    """All-gathers each rank's [lanes][query_heads][2 + D] fp32 triples into [ranks][...], in rank order."""
+def gather_shards(triples: torch.Tensor, group=None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """All-gathers each rank's [lanes][query_heads][2 + D] fp32 triples into [ranks][...], in rank order.
+    `out` ([ranks * lanes][query_heads][2 + D]) avoids an allocation per call."""
     world = dist.get_world_size(group)
-    flat = torch.empty((world * triples.shape[0], *triples.shape[1:]), dtype=triples.dtype, device=triples.device)
-    dist.all_gather_into_tensor(flat, triples.contiguous(), group=group)  # concatenated along dim 0, rank by rank
+    flat = out if out is not None else torch.empty((world * triples.shape[0], *triples.shape[1:]), dtype=triples.dtype,
+                                                   device=triples.device)
+    dist.all_gather_into_tensor(flat, triples, group=group)  # concatenated along dim 0, rank by rank
     return flat.view(world, *triples.shape)
 
 
@@ -74,6 +76,7 @@ class SequenceSplitDecoder:
         self.layout, self.query_heads, self.lanes = layout, query_heads, lanes
         self.inner = ops.DecodeAttention(layout, query_heads, lanes, window, ctas)
         self.triples = torch.zeros((lanes, query_heads, layout.head_dimension + 2), dtype=torch.float32, device="cuda")
+        self.gathered = None  # the all-gather's destination, allocated once the group size is known
 
     def close(self):
         self.inner.close()
@@ -97,6 +100,54 @@ class SequenceSplitDecoder:
 
     def step(self, queries, output, table_pointers, params, layer, group=None, output_f32=None):
         """shard -> all-gather -> merge; every rank ends with the same output."""
-        gathered = gather_shards(self.shard(queries, table_pointers, params, layer), group)
+        world = dist.get_world_size(group)
+        if self.gathered is None or self.gathered.shape[0] != world * self.lanes:
+            self.gathered = torch.empty((world * self.lanes, *self.triples.shape[1:]), dtype=torch.float32, device="cuda")
+        gathered = gather_shards(self.shard(queries, table_pointers, params, layer), group, self.gathered)
         self.merge(gathered, output, output_f32)
         return gathered
+
+
+class PeerExchangeDecoder:
+    """The sequence split with the combine inside the library's own kernel (rk_attention_decode_exchange): per step
+    two launches, no collective library on the data path. Each rank's triple goes into every rank's exchange buffer
+    by plain peer stores over NVLink; the buffers are shared through CUDA IPC handles that the ranks gather once,
+    at construction, over `group` (a torch.distributed group; None with world size 1 needs no group at all)."""
+
+    def __init__(self, layout: Layout, query_heads: int, lanes: int, window, rank: int = 0, ranks: int = 1, group=None,
+                 ctas: int = 0, connect: bool = True):
+        from . import ops
+        self._lib = lib.load()
+        self.layout, self.query_heads, self.lanes, self.rank, self.ranks = layout, query_heads, lanes, rank, ranks
+        self.inner = ops.DecodeAttention(layout, query_heads, lanes, window, ctas)
+        handle = (C.c_ubyte * 64)()
+        self._exchange = self._lib.rk_exchange_create(rank, ranks, lanes, handle)
+        if not self._exchange:
+            raise lib.RichKvError(lib.CUDA_ERROR, "rk_exchange_create")
+        if ranks > 1 and connect:
+            mine = torch.tensor(list(handle), dtype=torch.uint8, device="cuda")
+            everyone = torch.empty(ranks * 64, dtype=torch.uint8, device="cuda")
+            dist.all_gather_into_tensor(everyone, mine, group=group)
+            handles = bytes(everyone.cpu().numpy().tobytes())
+            lib.check(self._lib.rk_exchange_connect(self._exchange, handles), "rk_exchange_connect")
+            dist.barrier(group)  # every rank has mapped every buffer before anyone's first step
+
+    def close(self):
+        if self._exchange:
+            self._lib.rk_exchange_destroy(self._exchange)
+            self._exchange = None
+        self.inner.close()
+
+    def step(self, queries, output, table_pointers, params, layer: lib.KvLayer, output_f32=None, loopback_rank: int = -1,
+             stream=None) -> None:
+        from .ops import _stream
+        a = self.inner
+        status = self._lib.rk_attention_decode_exchange(
+            a._window, C.byref(a.plan), self.layout.format, queries.data_ptr(), output.data_ptr(),
+            output_f32.data_ptr() if output_f32 is not None else None, a.partials.data_ptr(), a.statistics.data_ptr(),
+            a.descriptors.data_ptr(), table_pointers.data_ptr(), params.data_ptr(), layer, self._exchange, loopback_rank,
+            _stream(stream))
+        lib.check(status, "rk_attention_decode_exchange")
+
+    def status(self, stream=None) -> None:
+        self.inner.status(stream)

@@ -34,8 +34,10 @@ def built_artifacts():
     """The oracle (rebuilt by make when stale) and the CUDA library (rebuilt when a source or header is newer than
     its object, so the tests never run against a stale binary)."""
     subprocess.run(["make", "-C", str(ROOT / "oracle"), "-s"], check=True)
-    from richengine_b200 import build
-    build.build()
+    import shutil
+    from richengine_b200 import build, lib
+    if shutil.which("nvcc") or not lib.LIBRARY_PATH.exists():  # no compiler on this machine: test the library as shipped
+        build.build()
     yield
 
 

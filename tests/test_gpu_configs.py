@@ -122,9 +122,94 @@ def test_cfg3_format_sweep_decode(fmt):
     q = make_queries(rng, s.lanes, layout)
     committed = [c - 1 for c in s.contexts]  # the last stored token is the current row
     _, want32 = run_verify_attention_oracle(s, q, 1, 1, committed=committed)
-    if fmt == INT4:
-        d16, d32 = run_decode_attention_gpu(s, q, committed=committed)
-        assert_attention_close(d32, want32, d16, "cfg3 int4 decode (streaming kernel)")
+    d16, d32 = run_decode_attention_gpu(s, q, committed=committed)
+    assert_attention_close(d32, want32, d16, f"cfg3 format {fmt} decode (streaming kernel)")
     w16, w32, _ = run_verify_attention_gpu(s, q, 1, 1, committed=committed, splits=1, tensor_core=True)
     assert_attention_close(w32, want32, w16, f"cfg3 format {fmt} decode (window kernel)")
+    s.close()
+
+
+class TableView:
+    """What the attention helpers need of a scenario, over tables that came from the request cache."""
+
+    def __init__(self, layout, storage, mirror, page_lists, contexts):
+        self.layout, self.storage, self.host = layout, storage, mirror
+        self.pages, self.contexts, self.lanes = page_lists, contexts, len(page_lists)
+        self.device_tables = []
+        for pages in page_lists:
+            table = torch.zeros(len(pages), dtype=torch.int64, device="cuda")
+            storage.write_entries(pages, 0, table)
+            self.device_tables.append(table)
+        self.table_pointers = ops.table_pointer_array(self.device_tables)
+        self.host_tables = [mirror.table(p) for p in page_lists]
+
+    def host_table_pointers(self):
+        return (C.c_void_p * self.lanes)(*[t.ctypes.data for t in self.host_tables])
+
+
+def test_cfg3_prefix_shared_by_32_requests_fork_diverge_decode():
+    """32 requests fork one published prefix of 256 refcounted pages (the last one partial: copy-on-write), each
+    appends 512 tokens of its own, and every request decodes through its forked table: shared pages stay
+    bit-identical to the checker's mirror, refcounts add up, attention through shared + own pages meets the bar."""
+    from test_gpu_hostplane import World
+    from richengine_b200.hostplane import GRANTED
+    layout = Layout(1, 4, 256, INT4)
+    w = World(layout, 1024, 128)
+    prefix_tokens = 32 * 256 - 9  # 256 pages, the last one holds 23 tokens
+    children = list(range(2, 34))
+    ids = np.random.default_rng(3).integers(0, 50000, size=prefix_tokens + 1, dtype=np.uint32)
+    w.cache.begin_request(1)
+    assert w.cache.ensure_tokens(1, prefix_tokens) == GRANTED
+    done = 0
+    while done < prefix_tokens:  # chunk stores of at most 2048 rows
+        rows = min(2048, prefix_tokens - done)
+        w.append(1, done, rows)
+        done += rows
+    w.cache.publish(1, ids, prefix_tokens)
+    parent_pages = w.cache.page_table(1)[0]
+    assert len(parent_pages) == 256
+    for child in children:
+        w.cache.begin_request(child)
+        assert w.cache.fork(1, child, prefix_tokens) == 1  # one page copied: the partial tail
+        pages = w.cache.page_table(child)[0]
+        assert pages[:255] == parent_pages[:255] and pages[255] not in parent_pages
+        om.oracle().rko_copy_page(INT4, 1, 4, 256, 128, w.mirror.entry(parent_pages[255]), w.mirror.entry(pages[255]))
+        assert w.cache.ensure_tokens(child, prefix_tokens + 512 + 1) == GRANTED
+        w.append(child, prefix_tokens, 512, seed=child)
+    torch.cuda.synchronize()
+    snapshot = w.pool.snapshot()
+    own = len(w.cache.page_table(2)[0]) - 255
+    assert snapshot["pages_active"] == 256 + 32 * own and w.cache.snapshot()["fork_copies"] == 32
+    for extent in range(w.mirror.extents):  # every byte of the pool, shared and private pages alike
+        if w.storage.is_allocated(extent * 128):
+            assert np.array_equal(w.storage.read_extent(extent), w.mirror.bytes[extent]), f"extent {extent}"
+    # decode through the forked tables (the parent rides along as lane 0)
+    requests = [1] + children
+    page_lists = [w.cache.page_table(r)[0] for r in requests]
+    committed = [prefix_tokens - 1] + [prefix_tokens + 512 - 1] * 32  # the last stored token is the current row
+    view = TableView(layout, w.storage, w.mirror, page_lists, committed)
+    q = make_queries(np.random.default_rng(72), view.lanes, layout)
+    _, want32 = run_verify_attention_oracle(view, q, 1, 1, committed=committed)
+    d16, d32 = run_decode_attention_gpu(view, q, committed=committed)
+    assert_attention_close(d32, want32, d16, "cfg3 decode through forked tables")
+    # children share 255 pages but not their answers
+    assert not np.array_equal(d16[1], d16[2])
+    for r in requests:
+        w.cache.end_request(r)
+    assert w.pool.snapshot()["pages_active"] == 0
+    w.close()
+
+
+@pytest.mark.parametrize("history", [131072, 260096])
+def test_long_histories_decode(history):
+    """The longest histories the reference's plan tests run (dev/tests/engine/paged_attention_plan_test.mm:999-1012):
+    one int4 lane, streaming decode against the checker."""
+    layout = Layout(1, 4, 256, INT4)
+    s = Scenario(layout, [history], extra_tokens=1, device=True, seed=80, extent_pages=256)
+    fill_on_gpu_and_mirror(s, layers=[0])
+    q = make_queries(np.random.default_rng(81), 1, layout)
+    committed = [history - 1]
+    _, want32 = run_verify_attention_oracle(s, q, 1, 1, committed=committed)
+    d16, d32 = run_decode_attention_gpu(s, q, committed=committed)
+    assert_attention_close(d32, want32, d16, f"decode over {history} tokens")
     s.close()

@@ -54,3 +54,59 @@ def test_sequence_split_matches_whole_sequence(context, ranks, fmt):
     _, whole32 = run_decode_attention_gpu(s, q)
     assert_attention_close(out32.cpu().numpy(), whole32, None, "split vs whole")
     decoder.close(); s.close()
+
+
+@pytest.mark.parametrize("context,ranks,fmt", [(5000, 2, INT4), (9000, 8, INT4), (40, 8, INT4), (1023, 3, INT8), (5000, 4, BF16)])
+def test_peer_exchange_step_emulated_on_one_gpu(context, ranks, fmt):
+    """The fused reduce -> peer stores -> flags -> merge kernel with every "peer" buffer being the local one: the
+    emulated ranks run one after another (all but the last only publish, the last finds every flag set, waits for
+    nothing and merges). Two steps in a row use both parities of the buffer; the result equals the all-gather
+    variant's bit for bit and the checker's within the bar."""
+    layout = Layout(1, 4, 256, fmt)
+    s = Scenario(layout, [context], extra_tokens=1, device=True, seed=6)
+    fill_history_with_store(s, 0, seed=6)
+    rng = np.random.default_rng(10)
+    k, v = make_staging(rng, 1, layout)
+    assert om.oracle().rko_store_verify(fmt, 4, 256, 1, k.ctypes.data, v.ctypes.data, s.host_table_pointers(), chunk_params(s, 1)) == 0
+    s.upload()
+    visible = context + 1
+    place = s.storage.layers()[0]
+    shards = []
+    for r in range(ranks):
+        first, last = parallel.shard_page_range(len(s.pages[0]), r, ranks)
+        begin, count = parallel.shard_tokens(visible, r, ranks)
+        if count == 0:  # no pages on this rank: an invalid lane, which publishes an empty triple
+            table = s.device_tables[0][:1].contiguous()
+            lane = (lib.VerifyParams * 1)(lib.VerifyParams(0, 0, place, 1, 1, 1, 1, 0.0))
+        else:
+            table = s.device_tables[0][first:last].contiguous()
+            lane = (lib.VerifyParams * 1)(lib.VerifyParams(count - 1, last - first, place, 1, 1, 1, 1, 0.0))
+        shards.append((table, ops.table_pointer_array([table]), struct_to_device(lane), count))
+    exchange = parallel.PeerExchangeDecoder(layout, 24, 1, s.storage.window(), rank=0, ranks=ranks, connect=False)
+    reference = parallel.SequenceSplitDecoder(layout, 24, 1, s.storage.window())
+    for step in range(2):
+        q = make_queries(rng, 1, layout)
+        dq = dev(q)
+        out = torch.zeros_like(dq)
+        out32 = torch.zeros(dq.shape, dtype=torch.float32, device="cuda")
+        for r, (_, pointers, lane, _) in enumerate(shards):
+            exchange.step(dq, out, pointers, lane, place, output_f32=out32, loopback_rank=r)
+        exchange.status()
+        torch.cuda.synchronize()
+        # the all-gather variant on the same shards
+        triples = []
+        for _, pointers, lane, count in shards:
+            if count == 0:
+                empty = torch.zeros((1, 24, 258), dtype=torch.float32, device="cuda")
+                empty[:, :, 0] = float("-inf")
+                triples.append(empty)
+            else:
+                triples.append(reference.shard(dq, pointers, lane, place).clone())
+        want = torch.zeros_like(dq)
+        want32 = torch.zeros_like(out32)
+        reference.merge(torch.stack(triples).contiguous(), want, want32)
+        torch.cuda.synchronize()
+        assert torch.equal(out32, want32) and torch.equal(out, want), f"step {step}: exchange and all-gather variants differ"
+        _, oracle32 = run_verify_attention_oracle(s, q, 1, 1)
+        assert_attention_close(out32.cpu().numpy(), oracle32, host_u16(out), f"peer exchange, step {step}")
+    exchange.close(); reference.close(); s.close()
