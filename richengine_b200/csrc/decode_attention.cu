@@ -49,7 +49,12 @@ namespace {
 constexpr uint32_t kKvHeads = 4, kGroup = 6, kHeadDim = 256;
 constexpr uint32_t kPageWarps = 3;                          // warps per KV head, each takes every third page
 constexpr uint32_t kConsumerWarps = kKvHeads * kPageWarps;
-constexpr uint32_t kThreads = (kConsumerWarps + 1) * 32;
+// Sixteen warps = four warp groups: three of consumers and one that holds the producer warp and three idle warps.
+// A CTA of thirteen warps would put four warps on one of the SM's four schedulers, which caps every thread at 128
+// registers and spills the consumers' accumulators; with whole warp groups the producer's group hands its registers
+// back (setmaxnreg.dec) and the consumer groups take them (setmaxnreg.inc): 152 registers, no spill.
+constexpr uint32_t kProducerGroupWarps = 4;
+constexpr uint32_t kThreads = (kConsumerWarps + kProducerGroupWarps) * 32;
 constexpr uint32_t kStages = 6;
 constexpr uint32_t kSlabBytes = 4096;                       // one head's K (or V) of a page, int4
 constexpr uint32_t kTensorBytes = kKvHeads * kSlabBytes;    // all heads' K (or V) of a page
@@ -83,7 +88,13 @@ __device__ __forceinline__ void barrier_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void barrier_expect(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void barrier_arrive(uint32_t bar) {
+// Register hand-over between warp groups; every warp of a group executes its instruction.
+__device__ __forceinline__ void release_registers() { asm volatile("setmaxnreg.dec.sync.aligned.u32 40;"); }
+__device__ __forceinline__ void take_registers() { asm volatile("setmaxnreg.inc.sync.aligned.u32 152;"); }
+// A consumer lane is done with a stage that TMA will refill: its generic-proxy reads are ordered before later
+// async-proxy writes (fence.proxy.async), then it arrives on the stage's "empty" barrier.
+__device__ __forceinline__ void release_stage(uint32_t bar) {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool barrier_try(uint32_t bar, uint32_t parity) {
@@ -227,11 +238,11 @@ __device__ void exclusive_scan(uint32_t *values, uint32_t n, uint32_t *scratch) 
 
 // Online softmax of one page for this lane's 4 tokens x 2 query heads, and the fp16 probability
 // fragments (B operand of O^T += V^T.P^T). Masked = the page holds tokens past the visible ones.
-template <bool Masked, bool Wide = false>
+template <bool Masked, bool Wide = false, bool Ride = false>
 __device__ __forceinline__ void page_softmax(const float (&sacc)[2][2][4], const float (&hfac)[2],
                                              const float (&negoff)[2], uint32_t scales, uint32_t r3g,
                                              uint32_t valid, float (&m)[2], float (&l_sum)[2], float (&o)[16][4],
-                                             uint32_t (&pb_frag)[2][2], uint32_t (*pb_low)[2] = nullptr) {
+                                             uint32_t (&pb_frag)[2][2], uint32_t (*pb_low)[2] = nullptr, float *psum = nullptr) {
   float s2[2][2][2], lv[2][2];
   float local_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -263,6 +274,7 @@ __device__ __forceinline__ void page_softmax(const float (&sacc)[2][2][4], const
       const float scale = exp2_fast(m[j] - next);
       m[j] = next;
       l_sum[j] *= scale;
+      if (Ride) psum[j] *= scale;
 #pragma unroll
       for (uint32_t t = 0; t < 16; ++t) { o[t][j] *= scale; o[t][2 + j] *= scale; }
     }
@@ -287,6 +299,15 @@ __device__ __forceinline__ void page_softmax(const float (&sacc)[2][2][4], const
         const uint32_t hi0 = __float_as_uint(w[half][0]) & 0xffff0000u, hi1 = __float_as_uint(w[half][1]) & 0xffff0000u;
         pb_frag[mt][half] = transpose_8x8((hi0 >> 16) | hi1);
         pb_low[mt][half] = transpose_8x8(pack_bf16x2(w[half][0] - __uint_as_float(hi0), w[half][1] - __uint_as_float(hi1)));
+      }
+    } else if (Ride) {
+      // the value codes ride their +8 through the accumulation: keep the sum of the ROUNDED weights to take it out
+#pragma unroll
+      for (uint32_t half = 0; half < 2; ++half) {
+        const __half2 h = __floats2half2_rn(w[half][0], w[half][1]);
+        psum[0] += __low2float(h);
+        psum[1] += __high2float(h);
+        pb_frag[mt][half] = transpose_8x8(*reinterpret_cast<const uint32_t *>(&h));
       }
     } else {
       pb_frag[mt][0] = transpose_8x8(pack_half2(w[0][0], w[0][1]));
@@ -365,9 +386,10 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
     first_lane = lo;
   }
 
-  if (warp == kConsumerWarps) {
+  if (warp >= kConsumerWarps) {
     // ================= producer: one thread streams whole pages =============================
-    if (lane != 0) return;
+    release_registers();
+    if (warp != kConsumerWarps || lane != 0) return;
     uint32_t unit = 0; // pages issued by this CTA
     bool ok = true;
     // the timeout probe withholds the last pages of the range: their consumers must give up, not hang
@@ -414,12 +436,12 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
   }
 
   // ================= consumers: warp = (KV head, page residue) ===============================
+  take_registers();
   const uint32_t head = warp & 3u, residue = warp >> 2;
   const uint32_t g = lane >> 2, c = lane & 3u;
   const uint32_t r3g = ((g & 1u) << 2) | (g >> 1); // row-in-8 swizzle partner: phase mates differ in bit 2
   const uint32_t kLowNibbles = register_constant(0x000F000Fu), kHighNibbles = register_constant(0x00F000F0u);
   const uint32_t kFlipLow = register_constant(0x00080008u), kFlipHigh = register_constant(0x00800080u);
-  const uint32_t kMagicLow = register_constant(0x64086408u), kMagicHigh = register_constant(0x64806480u);
   const uint32_t query_shared = smem_address(&sh.query[head][0][lane]);
 
   uint32_t units_before = 0; // pages of this CTA in earlier segments
@@ -492,6 +514,8 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
     }
 
     float m[2] = {-1.0e30f, -1.0e30f}, l_sum[2] = {0.0f, 0.0f};
+    float psum[2] = {0.0f, 0.0f}; // this lane's share of the sum of the rounded weights since the last correction
+    uint32_t ridden = 0;          // pages since the last correction
     float o[16][4];
 #pragma unroll
     for (uint32_t t = 0; t < 16; ++t) { o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.0f; }
@@ -547,9 +571,9 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
       // ---- online softmax over the page's 32 tokens -------------------------------------
       uint32_t pb_frag[2][2];
       if (valid == kPageTokens)
-        page_softmax<false>(sacc, hfac, negoff, scales, r3g, valid, m, l_sum, o, pb_frag);
+        page_softmax<false, false, true>(sacc, hfac, negoff, scales, r3g, valid, m, l_sum, o, pb_frag, nullptr, psum);
       else
-        page_softmax<true>(sacc, hfac, negoff, scales, r3g, valid, m, l_sum, o, pb_frag);
+        page_softmax<true, false, true>(sacc, hfac, negoff, scales, r3g, valid, m, l_sum, o, pb_frag, nullptr, psum);
 
       // ---- O^T += V^T.P^T : 16 tiles of 16 dims, 2 k-steps of 16 tokens -----------------
 #pragma unroll
@@ -569,15 +593,29 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
             const uint32_t selector = b | (b << 4) | ((4 + b) << 8) | ((4 + b) << 12);
             const uint32_t ab = __byte_perm(xa[w], xb[w], selector), cd = __byte_perm(xc[w], xd[w], selector);
             // low nibble: 1024 + (n ^ 8), minus 1032 = code; high nibble: 1024 + 16 (n ^ 8), minus 1152 = 16 code
-            mma_f16(o[4 * w + b], sub_f16x2(and_xor(ab, kLowNibbles, kMagicLow), kMagicLow),
-                    sub_f16x2(and_xor(ab, kHighNibbles, kMagicHigh), kMagicHigh),
-                    sub_f16x2(and_xor(cd, kLowNibbles, kMagicLow), kMagicLow),
-                    sub_f16x2(and_xor(cd, kHighNibbles, kMagicHigh), kMagicHigh), pb_frag[s][0], pb_frag[s][1]);
+            // codes travel as u * 2^-24 (u = code + 8; high nibbles x16), exact fp16 subnormals like the keys
+            mma_f16(o[4 * w + b], and_xor(ab, kLowNibbles, kFlipLow), and_xor(ab, kHighNibbles, kFlipHigh),
+                    and_xor(cd, kLowNibbles, kFlipLow), and_xor(cd, kHighNibbles, kFlipHigh), pb_frag[s][0], pb_frag[s][1]);
           }
       }
-      // Every lane gives the stage back itself: its own arrive (a release) follows its own last read of the stage, so
-      // no ordering between lanes is relied on before the producer refills the stage.
-      barrier_arrive(smem_address(&sh.empty[slot]));
+      // Every lane gives the stage back itself, behind a generic-to-async proxy fence: the stage was read through the
+      // generic proxy (ld.shared) and is refilled through the async proxy (TMA), and an mbarrier arrive / wait pair alone
+      // orders generic-proxy accesses only. Without the fence the refill of the next page in this stage was seen to
+      // land under the last value rows the slowest warp was still reading.
+      release_stage(smem_address(&sh.empty[slot]));
+      if (++ridden == 64) { // the +8 never rides more than 64 pages of a warp's accumulation
+        ridden = 0;
+#pragma unroll
+        for (uint32_t j = 0; j < 2; ++j) {
+          float total = psum[j];
+          total += __shfl_xor_sync(0xffffffffu, total, 4);
+          total += __shfl_xor_sync(0xffffffffu, total, 8);
+          total += __shfl_xor_sync(0xffffffffu, total, 16);
+          psum[j] = 0.0f;
+#pragma unroll
+          for (uint32_t t = 0; t < 16; ++t) { o[t][j] = fmaf(total, -4.76837158203125e-07f, o[t][j]); o[t][2 + j] = fmaf(total, -7.62939453125e-06f, o[t][2 + j]); }
+        }
+      }
     }
     units_before += pb - pa;
 
@@ -593,17 +631,24 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
       const uint64_t slot_index = (uint64_t(segment) * kKvHeads + head) * kPageWarps + residue;
       float *out = args.partials + slot_index * kGroup * kHeadDim;
       float *stats = args.statistics + slot_index * kGroup * 2;
-      const float unscale = 6.103515625e-05f; // 2^-14
       const bool failed = sh.error != 0;
+#pragma unroll
+      for (uint32_t j = 0; j < 2; ++j) {
+        psum[j] += __shfl_xor_sync(0xffffffffu, psum[j], 4);
+        psum[j] += __shfl_xor_sync(0xffffffffu, psum[j], 8);
+        psum[j] += __shfl_xor_sync(0xffffffffu, psum[j], 16);
+      }
 #pragma unroll
       for (uint32_t j = 0; j < 2; ++j) {
         const uint32_t query_head = 2 * c + j;
         if (query_head >= kGroup) continue;
+        // accumulators hold 2^-24 * sum(u * w) (x16 for the odd dims), weights carry 2^14: take the +8 out, then 2^24 * 2^-14
+        const float offset = psum[j] * 4.76837158203125e-07f; // 8 * 2^-24 * sum of weights
 #pragma unroll
         for (uint32_t t = 0; t < 16; ++t) {
           const uint32_t dim = 32 * r3g + 8 * (t >> 2) + 2 * (t & 3u);
           *reinterpret_cast<float2 *>(out + query_head * kHeadDim + dim) =
-              make_float2(o[t][j] * unscale, o[t][2 + j] * (unscale * 0.0625f));
+              make_float2((o[t][j] - offset) * 1024.0f, (o[t][2 + j] - 16.0f * offset) * 64.0f);
         }
         if (g == 0) {
           stats[query_head * 2] = failed ? -INFINITY : m[j] * kLn2;
@@ -705,9 +750,10 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
     first_lane = lo;
   }
 
-  if (warp == kConsumerWarps) {
+  if (warp >= kConsumerWarps) {
     // ================= producer: one thread streams whole pages =============================
-    if (lane != 0) return;
+    release_registers();
+    if (warp != kConsumerWarps || lane != 0) return;
     uint32_t unit = 0; // pages issued by this CTA
     bool ok = true;
     // the timeout probe withholds the last pages of the range: their consumers must give up, not hang
@@ -757,6 +803,7 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
   }
 
   // ================= consumers: warp = (KV head, page residue) ===============================
+  take_registers();
   const uint32_t head = warp & 3u, residue = warp >> 2;
   const uint32_t g = lane >> 2, c = lane & 3u;
   // MMA row g (and g+8) of a 16-token tile is token r3g (and 8 + r3g) of its 16: bits 0 and 1 of g swapped. A token
@@ -917,9 +964,11 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
           mma_f16(o[t], a0, a1, a2, a3, pb_frag[s][0], pb_frag[s][1]);
         }
       }
-      // Every lane gives the stage back itself: its own arrive (a release) follows its own last read of the stage, so
-      // no ordering between lanes is relied on before the producer refills the stage.
-      barrier_arrive(smem_address(&sh.empty[slot]));
+      // Every lane gives the stage back itself, behind a generic-to-async proxy fence: the stage was read through the
+      // generic proxy (ld.shared) and is refilled through the async proxy (TMA), and an mbarrier arrive / wait pair alone
+      // orders generic-proxy accesses only. Without the fence the refill of the next page in this stage was seen to
+      // land under the last value rows the slowest warp was still reading.
+      release_stage(smem_address(&sh.empty[slot]));
     }
     units_before += pb - pa;
 
@@ -1025,9 +1074,10 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
     first_lane = lo;
   }
 
-  if (warp == kConsumerWarps) {
+  if (warp >= kConsumerWarps) {
     // ================= producer: one thread streams (page, KV head) units of 32 KiB =============
-    if (lane != 0) return;
+    release_registers();
+    if (warp != kConsumerWarps || lane != 0) return;
     uint32_t unit = 0, ordinal = 0; // units issued by this CTA; pages of this CTA before the current one
     bool ok = true;
     // the timeout probe withholds the last pages of the range: their consumers must give up, not hang
@@ -1074,6 +1124,7 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
   }
 
   // ================= consumers: warp = (KV head, page residue) ===============================
+  take_registers();
   const uint32_t head = warp & 3u, residue = warp >> 2;
   const uint32_t g = lane >> 2, c = lane & 3u;
   // A token row is four 128-byte swizzle rows, so neighbouring tokens already differ in bit 2 of the row:
@@ -1195,9 +1246,11 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
           mma_bf16(o[t], a0, a1, a2, a3, pb_low[s][0], pb_low[s][1]);
         }
       }
-      // Every lane gives the stage back itself: its own arrive (a release) follows its own last read of the stage, so
-      // no ordering between lanes is relied on before the producer refills the stage.
-      barrier_arrive(smem_address(&sh.empty[slot]));
+      // Every lane gives the stage back itself, behind a generic-to-async proxy fence: the stage was read through the
+      // generic proxy (ld.shared) and is refilled through the async proxy (TMA), and an mbarrier arrive / wait pair alone
+      // orders generic-proxy accesses only. Without the fence the refill of the next page in this stage was seen to
+      // land under the last value rows the slowest warp was still reading.
+      release_stage(smem_address(&sh.empty[slot]));
     }
     units_before += pb - pa;
 
@@ -1253,13 +1306,22 @@ __device__ __forceinline__ float4 reduce_slots(const float *__restrict__ partial
                                                uint32_t first, uint32_t segments, uint32_t head, uint32_t query_head,
                                                ReduceShared<kGroups> &sh) {
   constexpr uint32_t kReduceThreads = 64 * kGroups;
+  constexpr uint32_t kHeld = 2; // statistics a thread keeps in registers from the first pass
+  constexpr uint32_t kBatch = 8; // partial rows a thread has in flight at a time
   const uint32_t tid = threadIdx.x, group = tid >> 6, quad = tid & 63u;
   const uint32_t slots = segments * kPageWarps;
   auto slot_of = [&](uint32_t t) { return (uint64_t(first + t / kPageWarps) * kKvHeads + head) * kPageWarps + t % kPageWarps; };
-  // maximum over all slots
+  auto statistic = [&](uint32_t t) { return __ldcg(reinterpret_cast<const float2 *>(statistics + (slot_of(t) * kGroup + query_head) * 2)); };
+  // first pass: {max, sum} of slots tid, tid + threads (one round trip for nearly every shape); maximum over all slots
+  float2 held[kHeld];
   float maximum = -INFINITY;
-  for (uint32_t t = tid; t < slots; t += kReduceThreads)
-    maximum = fmaxf(maximum, __ldcg(statistics + (slot_of(t) * kGroup + query_head) * 2));
+#pragma unroll
+  for (uint32_t i = 0; i < kHeld; ++i) {
+    const uint32_t t = tid + i * kReduceThreads;
+    held[i] = t < slots ? statistic(t) : make_float2(-INFINITY, 0.0f);
+    maximum = fmaxf(maximum, held[i].x);
+  }
+  for (uint32_t t = tid + kHeld * kReduceThreads; t < slots; t += kReduceThreads) maximum = fmaxf(maximum, statistic(t).x);
   maximum = warp_max(maximum);
   if ((tid & 31u) == 0) sh.warp_values[tid >> 5] = maximum;
   __syncthreads();
@@ -1271,17 +1333,32 @@ __device__ __forceinline__ float4 reduce_slots(const float *__restrict__ partial
   float4 numerator = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
   for (uint32_t base = 0; base < slots; base += kReduceChunk) {
     const uint32_t count = min(kReduceChunk, slots - base);
-    for (uint32_t t = tid; t < count; t += kReduceThreads) {
-      const float2 stat = __ldcg(reinterpret_cast<const float2 *>(statistics + (slot_of(base + t) * kGroup + query_head) * 2));
+    for (uint32_t t = base + tid; t < base + count; t += kReduceThreads) { // a thread's slots in rising order
+      const uint32_t nth = (t - tid) / kReduceThreads;
+      const float2 stat = nth == 0 ? held[0] : nth == 1 ? held[1] : statistic(t);
       const float weight = stat.x == -INFINITY ? 0.0f : expf(stat.x - maximum);
-      sh.weights[t] = weight;
+      sh.weights[t - base] = weight;
       denominator += weight * stat.y;
     }
     __syncthreads();
-    for (uint32_t t = group; t < count; t += kGroups) {
-      const float weight = sh.weights[t];
-      const float4 part = __ldcg(reinterpret_cast<const float4 *>(partials + (slot_of(base + t) * kGroup + query_head) * kHeadDim) + quad);
-      numerator.x += weight * part.x; numerator.y += weight * part.y; numerator.z += weight * part.z; numerator.w += weight * part.w;
+    for (uint32_t t = group; t < count; t += kGroups * kBatch) { // the loads of a batch are all in flight before the first add
+      float4 part[kBatch];
+      float weight[kBatch];
+#pragma unroll
+      for (uint32_t k = 0; k < kBatch; ++k) {
+        const uint32_t at = t + k * kGroups;
+        const bool live = at < count;
+        weight[k] = live ? sh.weights[at] : 0.0f;
+        part[k] = live ? __ldcg(reinterpret_cast<const float4 *>(partials + (slot_of(base + at) * kGroup + query_head) * kHeadDim) + quad)
+                       : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      }
+#pragma unroll
+      for (uint32_t k = 0; k < kBatch; ++k) {
+        if (t + k * kGroups < count) { // the sum runs over the group's slots in rising order, nothing else
+          numerator.x += weight[k] * part[k].x; numerator.y += weight[k] * part[k].y;
+          numerator.z += weight[k] * part[k].z; numerator.w += weight[k] * part[k].w;
+        }
+      }
     }
     __syncthreads();
   }
@@ -1551,12 +1628,24 @@ static int launch_exchange(uint32_t lanes, cudaStream_t stream, const float *par
 }
 
 // The streaming kernel of a format on `ctas` CTAs.
+// Launched as a programmatic dependent of whatever precedes it on the stream: its CTAs may be placed while that
+// kernel drains (the kernel waits for its predecessor's writes before it reads anything).
 static int launch_decode(uint32_t format, uint32_t ctas, cudaStream_t s, const Window *w, const DecodeArgs &args) {
-  if (format == RK_FORMAT_INT4) decode_int4_kernel<<<ctas, kThreads, kDecodeSharedBytes, s>>>(w->int4_map, args);
-  else if (format == RK_FORMAT_INT8) decode_bytes_kernel<false><<<ctas, kThreads, kByteDecodeSharedBytes, s>>>(w->int4_map, args);
-  else if (format == RK_FORMAT_FP8E4M3) decode_bytes_kernel<true><<<ctas, kThreads, kByteDecodeSharedBytes, s>>>(w->int4_map, args);
-  else decode_bf16_kernel<<<ctas, kThreads, kWideDecodeSharedBytes, s>>>(w->int4_map, args);
-  return cuda_status(cudaGetLastError(), "decode launch");
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(ctas);
+  config.blockDim = dim3(kThreads);
+  config.stream = s;
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  cudaError_t error;
+  if (format == RK_FORMAT_INT4) { config.dynamicSmemBytes = kDecodeSharedBytes; error = cudaLaunchKernelEx(&config, decode_int4_kernel, w->int4_map, args); }
+  else if (format == RK_FORMAT_INT8) { config.dynamicSmemBytes = kByteDecodeSharedBytes; error = cudaLaunchKernelEx(&config, decode_bytes_kernel<false>, w->int4_map, args); }
+  else if (format == RK_FORMAT_FP8E4M3) { config.dynamicSmemBytes = kByteDecodeSharedBytes; error = cudaLaunchKernelEx(&config, decode_bytes_kernel<true>, w->int4_map, args); }
+  else { config.dynamicSmemBytes = kWideDecodeSharedBytes; error = cudaLaunchKernelEx(&config, decode_bf16_kernel, w->int4_map, args); }
+  return cuda_status(error, "decode launch");
 }
 
 extern "C" {

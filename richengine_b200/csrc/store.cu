@@ -28,6 +28,10 @@ store_rows_kernel(const uint16_t *__restrict__ chunk_keys, const uint16_t *__res
                   const rk_chunk_params *__restrict__ lane_params, rk_chunk_params single,
                   rk_kv_layer layer, uint64_t lane_stride, uint32_t verify_row_limit) {
   static_assert(HeadDim == 256, "one warp lane owns eight dimensions of a 256-wide row");
+  // Launched as a programmatic dependent: wait for the preceding kernel's writes (the stagings may be its output, and
+  // the pages may still be read by it), and let the next kernel of the stream be placed early.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   using Geometry = PageGeometry<Format, KvHeads, HeadDim>;
   constexpr bool kTokenMajorValues = Format == RK_FORMAT_INT4;
   constexpr uint32_t kPitch = HeadDim + 8; // halfwords per transposed value row (16-byte pad)
@@ -171,10 +175,18 @@ int launch_store(uint32_t kv_heads, uint32_t head_dim, uint32_t lanes, uint32_t 
   if (head_dim != 256) return kUnsupported;
   const dim3 grid((max_rows + kTileRows - 1) / kTileRows, kv_heads, lanes);
   auto run = [&](auto kernel) {
-    kernel<<<grid, kThreads, 0, stream>>>(static_cast<const uint16_t *>(keys),
-                                          static_cast<const uint16_t *>(values), tables, single_table,
-                                          lane_params, single, layer, lane_stride, verify_limit);
-    return cuda_status(cudaGetLastError(), "store launch");
+    cudaLaunchConfig_t config{};
+    config.gridDim = grid;
+    config.blockDim = dim3(kThreads);
+    config.stream = stream;
+    cudaLaunchAttribute attribute{};
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    return cuda_status(cudaLaunchKernelEx(&config, kernel, static_cast<const uint16_t *>(keys), static_cast<const uint16_t *>(values),
+                                          tables, single_table, lane_params, single, layer, lane_stride, verify_limit),
+                       "store launch");
   };
   switch (kv_heads) {
   case 4: return run(store_rows_kernel<Format, 4, 256>);

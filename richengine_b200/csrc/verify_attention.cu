@@ -107,6 +107,7 @@ constexpr uint32_t kTmemO = 0, kTmemS = 256, kTmemQ = 384; // S twice (64 column
 struct Control {
   uint64_t raw_full[kMaxRawStages], raw_free[kMaxRawStages];
   uint64_t k_full[2], k_free[2], v_full[2], v_free[2], s_full[2], p_full[2], p_free[2], scale_free[kScaleStages];
+  uint64_t drained[2]; // one per issue warp: every contraction it issued has completed
   uint32_t tmem_base;
   uint32_t error;
   uint32_t spin_limit; // directly after `error`: barrier_wait reads it through the error pointer
@@ -513,6 +514,8 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
       barrier_init(smem_u32(&ctl.p_full[b]), kActiveSoftmax);
     }
     for (uint32_t b = 0; b < kScaleStages; ++b) barrier_init(smem_u32(&ctl.scale_free[b]), kActiveSoftmax);
+    barrier_init(smem_u32(&ctl.drained[0]), 1);
+    barrier_init(smem_u32(&ctl.drained[1]), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     ctl.error = 0;
     ctl.spin_limit = args.spin_limit;
@@ -649,6 +652,11 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
       }
       __syncwarp();
     }
+    // Tensor memory is released at the end of the kernel: every contraction this warp issued has completed by then,
+    // also when a wait gave up and nobody else waits for them any more.
+    if (elect_one()) umma_commit(&ctl.drained[0]);
+    __syncwarp();
+    for (uint32_t i = 0; i < kSpinLimit && !barrier_try(smem_u32(&ctl.drained[0]), 0); ++i) __nanosleep(64);
   } else if (warp == kValueWarp) {
     // ---- tensor-core issue, O += P.V ------------------------------------------------------------------------------
     const uint32_t idesc_pv = umma_instruction(kM, kD, Kind::kBf16, Kind::kBf16); // both operands of one kind: bf16 values take bf16 probabilities
@@ -671,6 +679,9 @@ window_attention_kernel(const __grid_constant__ CUtensorMap head_map, VerifyArgs
       }
       __syncwarp();
     }
+    if (elect_one()) umma_commit(&ctl.drained[1]);
+    __syncwarp();
+    for (uint32_t i = 0; i < kSpinLimit && !barrier_try(smem_u32(&ctl.drained[1]), 0); ++i) __nanosleep(64);
   } else if (warp >= kSoftmaxWarps || (warp & 3u) >= kQuarters) {
     // ---- expanders: raw codes -> 16-bit operand tiles --------------------------------------------------------------
     const uint32_t index = warp >= kSoftmaxWarps ? tid - kSoftmaxThreads
