@@ -262,6 +262,11 @@ int rk_storage_write_entries(const void *storage, const uint32_t *pages, uint32_
 int rk_storage_copy_pages(void *storage, const rk_page_copy *copies, uint32_t count, void *stream);
 int rk_storage_pack_pages(void *storage, const uint32_t *pages, uint32_t count, void *device_slots, int unpack,
                           void *stream);
+/* Pack + CRC-32C in one pass over each page (what the reference's slot-file IO worker does while it writes a
+ * payload, runtime/model/SlotFile.cpp:715-735): slots as rk_storage_pack_pages, `checksums` a device array of
+ * `count` words. The host tier's demotions use it. */
+int rk_storage_seal_pages(void *storage, const uint32_t *pages, uint32_t count, void *device_slots,
+                          uint32_t *checksums, void *stream);
 
 /* ---- checksums of persistent payloads ----------------------------------------------------------------
  * CRC-32C as the reference's slot file keeps it per payload and per record (runtime/model/Crc32c.hpp:12-29,

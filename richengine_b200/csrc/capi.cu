@@ -385,6 +385,29 @@ extern "C" int rk_storage_copy_pages(void *storage, const rk_page_copy *copies, 
   return status;
 }
 
+namespace rk {
+int launch_crc32c(const void *data, uint64_t stride, uint64_t payload_bytes, uint32_t count, uint32_t *out, uint32_t ctas,
+                  cudaStream_t stream, const GatherSource *gather);
+}
+
+// Seals pages for the host tier or the persistent store: every page's spans are packed into its contiguous device slot
+// (as rk_storage_pack_pages does) and the slot's CRC-32C is taken in the same pass, so a page is read once
+// (the reference's IO worker checksums a payload while it writes it, runtime/model/SlotFile.cpp:715-735).
+// `checksums` is a device array of `count` words.
+extern "C" int rk_storage_seal_pages(void *storage, const uint32_t *pages, uint32_t count, void *device_slots, uint32_t *checksums,
+                                     void *stream) {
+  auto *s = static_cast<Storage *>(storage);
+  if (!count) return kOk;
+  if (!s || !pages || !device_slots || !checksums) { set_error("rk_storage_seal_pages: invalid arguments"); return kInvalid; }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  rk_page_entry *device = nullptr;
+  if (int status = upload_entries(s, pages, count, &device, st)) return status;
+  const GatherSource source{device, s->layers, s->extent_pages, s->data_bytes, s->scale_bytes};
+  const int status = launch_crc32c(device_slots, s->page_bytes, s->page_bytes, count, checksums, 0, st, &source);
+  cudaFreeAsync(device, st);
+  return status;
+}
+
 // Packs pages into `count` contiguous device slots of bytes_per_page each
 // (spans in layer, tensor order: PageStorage.mm:143-167), or unpacks them.
 extern "C" int rk_storage_pack_pages(void *storage, const uint32_t *pages, uint32_t count, void *device_slots, int unpack, void *stream) {
@@ -536,10 +559,6 @@ extern "C" const void *rk_tier_slot_host_pointer(const void *tier, uint32_t slot
   return slot < t->slots ? t->host + uint64_t(slot) * t->slot_bytes : nullptr;
 }
 
-namespace rk {
-int launch_crc32c(const void *data, uint64_t stride, uint64_t payload_bytes, uint32_t count, uint32_t *out, uint32_t ctas,
-                  cudaStream_t stream);
-}
 namespace {
 int start_transfer(HostTier *t, bool demotion, uint32_t page, uint32_t slot, cudaStream_t after) {
   if (demotion ? !rk_tier_can_demote(t) : !rk_tier_can_restore(t)) return kRefused;
@@ -559,9 +578,8 @@ int start_transfer(HostTier *t, bool demotion, uint32_t page, uint32_t slot, cud
   uint8_t *host = t->host + uint64_t(slot) * t->slot_bytes;
   int status = kOk;
   if (demotion) {
-    status = rk_storage_pack_pages(t->storage, &page, 1, stage, 0, t->stream);
-    // the payload's checksum is taken where it was packed, before the bytes cross PCIe
-    if (!status) status = launch_crc32c(stage, t->slot_bytes, t->slot_bytes, 1, t->device_checksums + id, 0, t->stream);
+    // packed and checksummed in one pass over the page, before the bytes cross PCIe
+    status = rk_storage_seal_pages(t->storage, &page, 1, stage, t->device_checksums + id, t->stream);
     if (!status) status = cuda_status(cudaMemcpyAsync(t->slot_checksums + slot, t->device_checksums + id, 4, cudaMemcpyDeviceToHost, t->stream), "demotion checksum");
     if (!status) status = cuda_status(cudaMemcpyAsync(host, stage, t->slot_bytes, cudaMemcpyDeviceToHost, t->stream), "demotion copy");
     x.verify = false;
@@ -570,7 +588,7 @@ int start_transfer(HostTier *t, bool demotion, uint32_t page, uint32_t slot, cud
     x.verify = t->slot_verify[slot] != 0;
     x.expected = t->slot_expected[slot];
     if (!status && x.verify) { // an adopted slot's first read: check what arrived against its record
-      status = launch_crc32c(stage, t->slot_bytes, t->slot_bytes, 1, t->device_checksums + id, 0, t->stream);
+      status = launch_crc32c(stage, t->slot_bytes, t->slot_bytes, 1, t->device_checksums + id, 0, t->stream, nullptr);
       if (!status) status = cuda_status(cudaMemcpyAsync(t->arrived_checksums + id, t->device_checksums + id, 4, cudaMemcpyDeviceToHost, t->stream), "restore checksum");
     }
     if (!status) status = rk_storage_pack_pages(t->storage, &page, 1, stage, 1, t->stream);

@@ -24,6 +24,8 @@
 #include <vector>
 
 namespace rk {
+
+
 namespace {
 
 constexpr uint32_t kPoly = 0x82F63B78u; // reflected Castagnoli polynomial
@@ -77,9 +79,19 @@ const std::vector<uint32_t> &host_tables() {
   return tables;
 }
 
+// Seal mode: the payload is not read from `data` but gathered from a page's spans in the pool (layer by layer,
+// tensor by tensor: the order of a packed slot) and written to `data` on the way, so a page is read once for both
+// its packed copy and its checksum. Every span is a whole number of 512-byte rows.
+struct GatherArgs {
+  const rk_page_entry *entries; // one per payload; null = plain mode
+  uint32_t extent_pages, data_bytes, scale_bytes;
+  uint32_t rows_per_layer, data_rows, scale_rows;
+};
+
 struct ChecksumArgs {
   const uint8_t *data;
   uint64_t stride;        // bytes between payloads
+  GatherArgs gather;
   uint32_t *out;          // one word per payload, zeroed before the launch
   uint32_t payloads, parts;
   uint32_t rows_low, extra; // chunk g of a payload has rows_low + (g < extra) rows
@@ -113,6 +125,20 @@ __device__ __forceinline__ uint32_t mul_mod_device(uint32_t a, uint32_t b) {
   return product;
 }
 
+// Where row `q` of layer `layer` of a page lives in the pool: the spans follow each other as
+// [K data][K scales][V data][V scales] inside a packed layer.
+__device__ __forceinline__ const uint4 *gathered_row(const GatherArgs &g, rk_page_entry entry, uint32_t layer, uint32_t q) {
+  uint32_t tensor = 0, within = q;
+  if (q >= g.data_rows) { tensor = 1; within = q - g.data_rows; }
+  if (q >= g.data_rows + g.scale_rows) { tensor = 2; within = q - g.data_rows - g.scale_rows; }
+  if (q >= 2 * g.data_rows + g.scale_rows) { tensor = 3; within = q - 2 * g.data_rows - g.scale_rows; }
+  const uint64_t address = rk_entry_extent(entry) +
+                           rk_extent_offset(g.extent_pages, g.data_bytes, g.scale_bytes, layer, tensor, rk_entry_index(entry)) +
+                           uint64_t(within) * kRowBytes;
+  return reinterpret_cast<const uint4 *>(address);
+}
+
+template <bool kGather>
 __global__ void __launch_bounds__(kWarps * 32, 1) crc32c_kernel(const __grid_constant__ ChecksumArgs args) {
   extern __shared__ __align__(16) uint32_t shared_words[];
   uint32_t *replica = shared_words;                       // [k][byte][lane]
@@ -136,11 +162,22 @@ __global__ void __launch_bounds__(kWarps * 32, 1) crc32c_kernel(const __grid_con
     uint32_t term = 0;
     if (rows) {
       const uint4 *source = reinterpret_cast<const uint4 *>(args.data + uint64_t(payload) * args.stride + first_row * kRowBytes) + lane;
+      // seal mode: rows come from the page's spans and leave for the packed slot (`source` is then the destination)
+      const rk_page_entry entry = kGather ? args.gather.entries[payload] : 0;
+      uint32_t layer = kGather ? uint32_t(first_row / args.gather.rows_per_layer) : 0;
+      uint32_t q = kGather ? uint32_t(first_row - uint64_t(layer) * args.gather.rows_per_layer) : 0;
+      auto load_row = [&](uint32_t row) {
+        if (!kGather) return __ldcs(source + uint64_t(row) * 32);
+        const uint4 v = __ldcs(gathered_row(args.gather, entry, layer, q) + lane);
+        __stcs(const_cast<uint4 *>(source) + uint64_t(row) * 32, v);
+        if (++q == args.gather.rows_per_layer) { q = 0; ++layer; }
+        return v;
+      };
       uint32_t acc[4] = {0, 0, 0, 0};
-      uint4 next = __ldcs(source); // one row ahead (a second row in flight measured slower: the kernel sits at 64 registers)
+      uint4 next = load_row(0); // one row ahead (a second row in flight measured slower: the kernel sits at 64 registers)
       for (uint32_t row = 0; row + 1 < rows; ++row) {
         const uint4 v = next;
-        next = __ldcs(source + uint64_t(row + 1) * 32);
+        next = load_row(row + 1);
         const uint32_t x[4] = {acc[0] ^ v.x, acc[1] ^ v.y, acc[2] ^ v.z, acc[3] ^ v.w};
 #pragma unroll
         for (uint32_t k = 0; k < 4; ++k)
@@ -201,7 +238,7 @@ uint32_t crc32c_bytes(const uint8_t *data, size_t bytes, uint32_t crc) {
 // CRC-32C of `count` payloads of `payload_bytes` each, `stride` bytes apart in device memory, into out[count]
 // (device). `ctas` = 0 takes one CTA per SM. Payloads are whole 512-byte rows (every packed page is).
 int launch_crc32c(const void *data, uint64_t stride, uint64_t payload_bytes, uint32_t count, uint32_t *out, uint32_t ctas,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, const GatherSource *gather) {
   if (!data || !out || !count || !payload_bytes || payload_bytes % kRowBytes || stride < payload_bytes || (stride & 15u) ||
       (reinterpret_cast<uintptr_t>(data) & 15u)) {
     set_error("rk_crc32c_pages: payloads must be whole 512-byte rows, 16-byte aligned");
@@ -218,7 +255,8 @@ int launch_crc32c(const void *data, uint64_t stride, uint64_t payload_bytes, uin
     if (!configured[device]) {
       const std::vector<uint32_t> &tables = host_tables();
       if (int st = cuda_status(cudaMemcpyToSymbol(g_tables, tables.data(), tables.size() * 4), "checksum tables")) return st;
-      if (int st = cuda_status(cudaFuncSetAttribute(crc32c_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSharedBytes)), "checksum shared memory")) return st;
+      if (int st = cuda_status(cudaFuncSetAttribute(crc32c_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSharedBytes)), "checksum shared memory")) return st;
+      if (int st = cuda_status(cudaFuncSetAttribute(crc32c_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSharedBytes)), "checksum shared memory")) return st;
       if (int st = cuda_status(cudaDeviceGetAttribute(&multiprocessors[device], cudaDevAttrMultiProcessorCount, device), "SM count")) return st;
       configured[device] = true;
     }
@@ -256,9 +294,21 @@ int launch_crc32c(const void *data, uint64_t stride, uint64_t payload_bytes, uin
   args.stride = stride;
   args.out = out;
   args.payloads = count;
+  args.gather = GatherArgs{};
+  if (gather) {
+    const uint32_t data_bytes = gather->data_bytes, scale_bytes = gather->scale_bytes;
+    if (!gather->entries || data_bytes % kRowBytes || scale_bytes % kRowBytes || !gather->layers ||
+        payload_bytes != uint64_t(gather->layers) * 2 * (uint64_t(data_bytes) + scale_bytes)) {
+      set_error("seal: the payload is not a packed page of this pool");
+      return kInvalid;
+    }
+    args.gather = GatherArgs{gather->entries, gather->extent_pages, data_bytes, scale_bytes,
+                             2 * (data_bytes + scale_bytes) / kRowBytes, data_bytes / kRowBytes, scale_bytes / kRowBytes};
+  }
   if (int st = cuda_status(cudaMemsetAsync(out, 0, uint64_t(count) * 4, stream), "checksum clear")) return st;
   const uint32_t grid = uint32_t(std::min<uint64_t>(ctas, (uint64_t(count) * args.parts + kGroups - 1) / kGroups));
-  crc32c_kernel<<<grid, kWarps * 32, kSharedBytes, stream>>>(args);
+  if (gather) crc32c_kernel<true><<<grid, kWarps * 32, kSharedBytes, stream>>>(args);
+  else crc32c_kernel<false><<<grid, kWarps * 32, kSharedBytes, stream>>>(args);
   return cuda_status(cudaGetLastError(), "checksum launch");
 }
 
@@ -266,7 +316,7 @@ int launch_crc32c(const void *data, uint64_t stride, uint64_t payload_bytes, uin
 
 extern "C" int rk_crc32c_pages(const void *data, uint64_t stride, uint64_t payload_bytes, uint32_t count, uint32_t *out,
                                uint32_t ctas, void *stream) {
-  return rk::launch_crc32c(data, stride, payload_bytes, count, out, ctas, static_cast<cudaStream_t>(stream));
+  return rk::launch_crc32c(data, stride, payload_bytes, count, out, ctas, static_cast<cudaStream_t>(stream), nullptr);
 }
 
 // CRC-32C of a host buffer, continuing from `crc` (0 to start): rk_crc32c_host(b, n, rk_crc32c_host(a, m, 0)) is the

@@ -22,6 +22,13 @@ constexpr int kTimeout = -5;     // a bounded device wait ran out
 void set_error(const char *text);
 int cuda_status(cudaError_t error, const char *what);
 
+// Host-side description of a seal (pack + checksum in one pass): the pages' table entries (device memory) and the
+// pool's span geometry.
+struct GatherSource {
+  const rk_page_entry *entries;
+  uint32_t layers, extent_pages, data_bytes, scale_bytes;
+};
+
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t bits) { return __uint_as_float(bits << 16); }
 
 // Round-to-nearest-even fp32 -> bf16 bits; quiet NaNs stay NaN.

@@ -119,6 +119,7 @@ SIGNATURES = {
     "rk_storage_write_entries": (i32, [vp, vp, u32, u32, vp, u32, vp]),
     "rk_storage_copy_pages": (i32, [vp, vp, u32, vp]),
     "rk_storage_pack_pages": (i32, [vp, vp, u32, vp, i32, vp]),
+    "rk_storage_seal_pages": (i32, [vp, vp, u32, vp, vp, vp]),
     # pinned-host tier
     "rk_tier_create": (vp, [vp, u32, u32]),
     "rk_tier_destroy": (None, [vp]),

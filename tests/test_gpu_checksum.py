@@ -63,3 +63,34 @@ def test_refusals():
     assert library.rk_crc32c_pages(data.data_ptr(), 1000, 1000, 1, out.data_ptr(), 0, None) == lib.INVALID  # not whole rows
     assert library.rk_crc32c_pages(data.data_ptr() + 4, 512, 512, 1, out.data_ptr(), 0, None) == lib.INVALID  # unaligned
     assert library.rk_crc32c_pages(data.data_ptr(), 256, 512, 2, out.data_ptr(), 0, None) == lib.INVALID  # overlapping
+
+
+@pytest.mark.parametrize("fmt,layers,count", [(3, 16, 5), (1, 2, 3), (4, 3, 2), (2, 2, 2)])
+def test_seal_packs_and_checksums_in_one_pass(fmt, layers, count):
+    """rk_storage_seal_pages: the slots equal rk_storage_pack_pages byte for byte and every checksum equals the
+    checker's CRC-32C of its slot (int4, int8, fp8, bf16 pools; random page ids; pages of different extents)."""
+    from richengine_b200.abi import Layout
+    from richengine_b200.storage import PageStorage
+    library = lib.load()
+    layout = Layout(layers, 4, 256, fmt)
+    extent_pages = layout.minimum_extent_pages()
+    storage = PageStorage(layout, 2 * extent_pages, extent_pages)
+    rng = np.random.default_rng(fmt * 100 + layers)
+    for extent in range(2):
+        assert storage.allocate_extent(extent)
+        storage.write_extent(extent, rng.integers(0, 256, size=storage.extent_bytes(), dtype=np.uint8))
+    page_bytes = storage.bytes_per_page()
+    ids = rng.permutation(2 * extent_pages)[:count].astype(np.uint32)
+    packed = torch.zeros(count * page_bytes, dtype=torch.uint8, device="cuda")
+    sealed = torch.zeros(count * page_bytes, dtype=torch.uint8, device="cuda")
+    sums = torch.zeros(count, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    lib.check(library.rk_storage_pack_pages(storage.handle, ids.ctypes.data, count, packed.data_ptr(), 0, stream), "pack")
+    lib.check(library.rk_storage_seal_pages(storage.handle, ids.ctypes.data, count, sealed.data_ptr(), sums.data_ptr(), stream), "seal")
+    torch.cuda.synchronize()
+    assert torch.equal(packed, sealed)
+    host = sealed.cpu().numpy()
+    for i in range(count):
+        want = om.oracle().rko_crc32c(host[i * page_bytes:].ctypes.data, page_bytes, 0)
+        assert int(sums[i].item()) & 0xffffffff == want, f"slot {i}"
+    storage.close()
