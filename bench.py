@@ -64,7 +64,7 @@ def parse():
     ap.add_argument("--skip-config4", action="store_true", help="leave the config-4 blocks (batch 256 dealt to the ranks, "
                     "262144-token sequence split) out of the line")
     ap.add_argument("--skip-check", action="store_true", help="leave the sampled comparison with the CPU checker out")
-    ap.add_argument("--mode", default="requests", choices=["requests", "seqsplit", "verify", "prefill", "seal", "evict"],
+    ap.add_argument("--mode", default="requests", choices=["requests", "seqsplit", "verify", "prefill", "seal", "evict", "prepare"],
                     help="requests: every rank runs its own batch (default); seqsplit: ONE sequence of --context "
                          "tokens split along the sequence over the ranks, all-gather of (max, sum, O), rank-order merge")
     return ap.parse_args()
@@ -858,12 +858,13 @@ def run_verify(args):
     import torch
 
     from richengine_b200 import hostplane, lib, ops
-    from richengine_b200.abi import INT4, Layout, pages_for
+    from richengine_b200.abi import BF16, FP8E4M3, INT4, INT8, Layout, pages_for
     from richengine_b200.storage import PageStorage
 
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     rows, lanes = args.rows, args.batch
-    layout = Layout(args.layers, KV_HEADS, HEAD_DIM, INT4)
+    fmt = {"int4": INT4, "int8": INT8, "fp8e4m3": FP8E4M3, "bf16": BF16}[args.format]
+    layout = Layout(args.layers, KV_HEADS, HEAD_DIM, fmt)
     steps_total = args.warmup + args.steps
     lane_pages = pages_for(args.context + rows * (steps_total + 1))
     extent_pages = layout.extent_pages_for(lanes * lane_pages) or layout.minimum_extent_pages()
@@ -904,7 +905,7 @@ def run_verify(args):
     for step in range(steps_total):
         history = [int(x) for x in committed[step]]
         _, plan = hostplane.verify_plan(lanes, QUERY_HEADS, layout, history, row_capacity=rows, ctas=0)
-        assert plan[15] == 1, "the window plan was not selected"
+        assert fmt != INT4 or plan[15] == 1, "the window plan was not selected"
         lane_splits = [hostplane.window_splits(lanes, KV_HEADS, h + rows, 0) for h in history]
         chunk_params = np.zeros(lanes, dtype=ops.CHUNK_PARAMS)
         verify_params = np.zeros(lanes, dtype=ops.VERIFY_PARAMS)
@@ -964,11 +965,11 @@ def run_verify(args):
     peaks_path = ROOT / "MEASURED_PEAKS.json"
     peak = float(json.loads(peaks_path.read_text())["bf16_tflops"]) if peaks_path.exists() else 1590.0
     print(json.dumps({
-        "metric": "int4_paged_verify_attention_kv_gbps", "value": round(timed_bytes / (elapsed_ms * 1e-3) / 1e9, 1), "unit": "GB/s",
+        "metric": f"{args.format}_paged_verify_attention_kv_gbps", "value": round(timed_bytes / (elapsed_ms * 1e-3) / 1e9, 1), "unit": "GB/s",
         "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(elapsed_ms / args.steps, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "int4 codes, fp16 tcgen05 operands, fp32 accumulate in tensor memory", "data": "synthetic",
-        "config": {"workload": f"speculative verify, int4 KV, 27B geometry ({args.layers} layers), batch {lanes}, {args.context}-token contexts, "
+        "dtype": f"{args.format} codes, {'bf16' if fmt == BF16 else 'fp16'} tcgen05 operands, fp32 accumulate in tensor memory", "data": "synthetic",
+        "config": {"workload": f"speculative verify, {args.format} KV, 27B geometry ({args.layers} layers), batch {lanes}, {args.context}-token contexts, "
                                f"{rows}-row window: per layer append {rows} rows + window attention + merge; seeded acceptance 0..{rows}, rejected rows rolled back",
                    "l2": "inputs larger than L2", "us_per_layer_step": round(elapsed_ms / args.steps / args.layers * 1e3, 2),
                    "splits_per_lane": slot},
@@ -1208,6 +1209,75 @@ def run_seal(args):
     storage.close()
 
 
+def run_prepare(args):
+    """The step before the path: packed projection rows -> query staging + K/V quantised straight into their page slots
+    (rk_qkv_prepare_store), for a decode batch (one row per lane) and for 16-row verify windows. One GPU."""
+    import torch
+
+    from richengine_b200 import lib, ops
+    from richengine_b200.abi import BF16, FP8E4M3, INT4, INT8, Layout, pages_for
+
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    fmt = {"int4": INT4, "int8": INT8, "fp8e4m3": FP8E4M3, "bf16": BF16}[args.format]
+    rows, lanes = (1 if args.rows == 16 and args.batch == 64 else args.rows), args.batch
+    layout = Layout(args.layers, KV_HEADS, HEAD_DIM, fmt)
+    contexts = [1024] * lanes
+    lane_pages = [pages_for(c + rows + 1) for c in contexts]
+    storage, tables, pointers, extent_pages, _ = build_pool(layout, lane_pages, 5)
+    places = storage.layers()
+    generator = torch.Generator(device="cuda").manual_seed(5)
+    packed_width = 2 * QUERY_HEADS * HEAD_DIM + 2 * KV_HEADS * HEAD_DIM
+    packed = torch.randn((lanes, rows, packed_width), generator=generator, device="cuda").to(torch.bfloat16)
+    q_norm = torch.ones(HEAD_DIM, device="cuda").to(torch.bfloat16)
+    k_norm = torch.ones(HEAD_DIM, device="cuda").to(torch.bfloat16)
+    angle = torch.rand((lanes, rows, 32), generator=generator, device="cuda") * 6.28
+    cosine, sine = torch.cos(angle).contiguous(), torch.sin(angle).contiguous()
+    queries = torch.zeros((lanes, KV_HEADS, 32, QUERY_HEADS // KV_HEADS, HEAD_DIM), dtype=torch.bfloat16, device="cuda")
+    chunk = np.zeros(lanes, dtype=ops.CHUNK_PARAMS)
+    for lane, context in enumerate(contexts):
+        chunk[lane] = (context, rows, 32, lane_pages[lane], (extent_pages, 0))
+    params = ops.params_to_device(chunk)
+
+    def step():
+        for layer in range(args.layers):
+            ops.qkv_prepare_store(layout, QUERY_HEADS, lanes, rows, packed, q_norm, k_norm, cosine, sine, queries, pointers, params, places[layer])
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(torch.cuda.current_device())
+    begin_wall = time.perf_counter()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        step()
+    stop.record()
+    torch.cuda.synchronize()
+    elapsed_ms = start.elapsed_time(stop)
+
+    def same_load():
+        step(); torch.cuda.synchronize()
+    sampler.keep_loaded(begin_wall, same_load)
+    clocks = sampler.stop(begin_wall, time.perf_counter())
+    per_row = packed_width * 2 + QUERY_HEADS * HEAD_DIM * 2 + layout.bytes_per_token_layer()  # packed row in, query rows + page bytes out
+    total = per_row * lanes * rows * args.layers * args.steps
+    peak, source = peak_hbm()
+    us = elapsed_ms / args.steps / args.layers * 1e3
+    print(json.dumps({
+        "metric": "qkv_prepare_store_rows_per_s", "value": round(lanes * rows * args.layers * args.steps / (elapsed_ms * 1e-3), 1), "unit": "rows/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(elapsed_ms / args.steps, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": f"bf16 rows, fp32 norm and rotary, {args.format} pages", "data": "synthetic",
+        "config": {"workload": f"{lanes} lanes x {rows} row(s): per layer one fused RMS-norm + rotary + split + quantise-into-pages launch "
+                               f"({args.layers} layers, {args.format} pool)", "us_per_layer_step": round(us, 2),
+                   "l2": "tiny: launch-latency bound, the rows fit L2"},
+        "roofline": {"bound": "hbm", "achieved": round(total / (elapsed_ms * 1e-3) / 1e9, 1), "peak": peak, "unit": "GB/s",
+                     "frac": round(total / (elapsed_ms * 1e-3) / 1e9 / peak, 4), "traffic": None, "peak_source": source,
+                     "kernel": "qkv_prepare_kernel (fused store)", "us_per_launch": round(us, 2), "algorithmic_bytes_per_launch": per_row * lanes * rows},
+        "gpu_launches": args.layers * args.steps, "clocks": clocks,
+    }), flush=True)
+    storage.close()
+
+
 def run_evict(args):
     """BASELINE config 4(iii): evict the coldest quarter of a resident int4 pool to pinned host memory and fetch it
     back on access, through the request cache (oldest idle leaf first, page valid until its copy lands, at most 128
@@ -1262,18 +1332,17 @@ def run_evict(args):
     begin_wall = time.perf_counter()
     # ---- demote the coldest quarter --------------------------------------------------------------------------
     t0 = time.perf_counter()
-    started = 0
     peak_in_flight = 0
-    while started < evict:
-        if cache.reclaim_one():
-            started += 1
-            in_flight = cache.snapshot()["transfers"]
-        else:
-            in_flight = cache.snapshot()["transfers"]
-            if not in_flight:
-                raise RuntimeError("nothing left to evict before the quarter was reached")
-            cache.poll_transfers()  # the tier is at its demotion limit: retire what has landed
+    target_free = pool.snapshot()["pages_free"] + evict
+    idle_rounds = 0
+    while pool.snapshot()["pages_free"] < target_free:
+        started = cache.reclaim_for_pages(target_free)  # the loop over the candidates runs in the library
+        in_flight = cache.snapshot()["transfers"]
         peak_in_flight = max(peak_in_flight, in_flight)
+        idle_rounds = 0 if (started or in_flight) else idle_rounds + 1
+        if idle_rounds > 1000:
+            raise RuntimeError("nothing left to evict before the quarter was reached")
+        cache.poll_transfers()  # retire what has landed: its pages return to the pool
     while cache.snapshot()["transfers"]:
         cache.poll_transfers()
     demote_seconds = time.perf_counter() - t0
@@ -1340,6 +1409,8 @@ def main():
         run_seal(args)
     elif args.mode == "evict":
         run_evict(args)
+    elif args.mode == "prepare":
+        run_prepare(args)
     else:
         run_ours(args)
 

@@ -459,6 +459,8 @@ struct HostTier {
   uint32_t *slot_checksums = nullptr;    // pinned: CRC-32C of each slot's payload, taken on the device when it was packed
   uint32_t *arrived_checksums = nullptr; // pinned: CRC-32C of a restored payload after it reached the device, per transfer
   uint32_t *device_checksums = nullptr;  // device: one word per transfer
+  rk_page_entry *device_entries = nullptr; // device: the page's table entry, one per transfer (no allocation per transfer)
+  rk_page_entry *host_entries = nullptr;   // pinned mirror the entries are copied from
   cudaStream_t stream = nullptr;
   std::vector<uint8_t> slot_used;
   std::vector<uint8_t> slot_verify;      // adopted from an earlier process and not read yet
@@ -494,6 +496,12 @@ extern "C" void *rk_tier_create(void *storage, uint32_t slots, uint32_t transfer
   }
   memset(t->slot_checksums, 0, (uint64_t(slots) + transfer_limit) * 4);
   t->arrived_checksums = t->slot_checksums + slots;
+  if (cuda_status(cudaMalloc(reinterpret_cast<void **>(&t->device_entries), uint64_t(transfer_limit) * sizeof(rk_page_entry)), "tier entries") ||
+      cuda_status(cudaHostAlloc(reinterpret_cast<void **>(&t->host_entries), uint64_t(transfer_limit) * sizeof(rk_page_entry), cudaHostAllocDefault), "tier entries")) {
+    cudaFree(t->device_entries); cudaFree(t->device_checksums); cudaFreeHost(t->slot_checksums); cudaStreamDestroy(t->stream);
+    cudaFree(t->staging); cudaFreeHost(t->host);
+    return nullptr;
+  }
   for (Transfer &x : t->transfers) cudaEventCreateWithFlags(&x.done, cudaEventDisableTiming);
   return t.release();
 }
@@ -506,6 +514,8 @@ extern "C" void rk_tier_destroy(void *tier) {
   cudaStreamDestroy(t->stream);
   cudaFree(t->staging);
   cudaFree(t->device_checksums);
+  cudaFree(t->device_entries);
+  cudaFreeHost(t->host_entries);
   cudaFreeHost(t->slot_checksums);
   cudaFreeHost(t->host);
   delete t;
@@ -576,10 +586,15 @@ int start_transfer(HostTier *t, bool demotion, uint32_t page, uint32_t slot, cud
   }
   uint8_t *stage = t->staging + uint64_t(id) * t->slot_bytes;
   uint8_t *host = t->host + uint64_t(slot) * t->slot_bytes;
-  int status = kOk;
+  const Storage *s = t->storage;
+  // the page's table entry travels through the transfer's own pinned / device words: nothing is allocated per transfer
+  t->host_entries[id] = s->entry(page);
+  int status = cuda_status(cudaMemcpyAsync(t->device_entries + id, t->host_entries + id, sizeof(rk_page_entry), cudaMemcpyHostToDevice, t->stream), "tier entry");
+  if (status) return status;
   if (demotion) {
     // packed and checksummed in one pass over the page, before the bytes cross PCIe
-    status = rk_storage_seal_pages(t->storage, &page, 1, stage, t->device_checksums + id, t->stream);
+    const GatherSource source{t->device_entries + id, s->layers, s->extent_pages, s->data_bytes, s->scale_bytes};
+    status = launch_crc32c(stage, t->slot_bytes, t->slot_bytes, 1, t->device_checksums + id, 0, t->stream, &source);
     if (!status) status = cuda_status(cudaMemcpyAsync(t->slot_checksums + slot, t->device_checksums + id, 4, cudaMemcpyDeviceToHost, t->stream), "demotion checksum");
     if (!status) status = cuda_status(cudaMemcpyAsync(host, stage, t->slot_bytes, cudaMemcpyDeviceToHost, t->stream), "demotion copy");
     x.verify = false;
@@ -591,7 +606,7 @@ int start_transfer(HostTier *t, bool demotion, uint32_t page, uint32_t slot, cud
       status = launch_crc32c(stage, t->slot_bytes, t->slot_bytes, 1, t->device_checksums + id, 0, t->stream, nullptr);
       if (!status) status = cuda_status(cudaMemcpyAsync(t->arrived_checksums + id, t->device_checksums + id, 4, cudaMemcpyDeviceToHost, t->stream), "restore checksum");
     }
-    if (!status) status = rk_storage_pack_pages(t->storage, &page, 1, stage, 1, t->stream);
+    if (!status) status = move_pages(s->format, s->layers, s->kv_heads, s->head_dim, s->extent_pages, nullptr, t->device_entries + id, stage, nullptr, 1, t->stream);
   }
   if (status) {
     if (demotion) t->writable = false; // a failed write closes the tier to demotions

@@ -1288,14 +1288,13 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
 
 // ---- merge of one (lane, KV head, query head): its partial slots -> {maximum, denominator, numerator} -------------
 // Slot s of a (lane, head) is segment s / 3, warp s % 3. The combination is a fixed function of the slot count
-// (same grid, same bits): slot s belongs to slot group s mod G, a group accumulates its slots in rising order, the
-// groups are added in group order; the denominator is summed per thread over slots t, t + threads, ..., then by a
-// fixed shuffle tree and in warp order.
-constexpr uint32_t kReduceChunk = 512; // slots whose weights sit in shared memory at a time
+// (same grid, same bits): slot s belongs to slot group s mod G; a group folds its slots in rising order with a
+// running maximum (an online merge: statistics and partial rows of a batch of slots are loaded together, one round
+// trip to L2 per batch instead of one for the statistics and another for the rows); the G group results are then
+// merged in group order against their common maximum.
 template <uint32_t kGroups> struct ReduceShared {
-  float weights[kReduceChunk];
   float4 sums[kGroups][kHeadDim / 4];
-  float warp_values[kGroups * 2];
+  float group_maximum[kGroups], group_denominator[kGroups];
   float maximum, denominator;
 };
 
@@ -1305,83 +1304,60 @@ template <uint32_t kGroups>
 __device__ __forceinline__ float4 reduce_slots(const float *__restrict__ partials, const float *__restrict__ statistics,
                                                uint32_t first, uint32_t segments, uint32_t head, uint32_t query_head,
                                                ReduceShared<kGroups> &sh) {
-  constexpr uint32_t kReduceThreads = 64 * kGroups;
-  constexpr uint32_t kHeld = 2; // statistics a thread keeps in registers from the first pass
-  constexpr uint32_t kBatch = 8; // partial rows a thread has in flight at a time
+  constexpr uint32_t kBatch = 8; // slots a thread has in flight at a time
   const uint32_t tid = threadIdx.x, group = tid >> 6, quad = tid & 63u;
   const uint32_t slots = segments * kPageWarps;
   auto slot_of = [&](uint32_t t) { return (uint64_t(first + t / kPageWarps) * kKvHeads + head) * kPageWarps + t % kPageWarps; };
-  auto statistic = [&](uint32_t t) { return __ldcg(reinterpret_cast<const float2 *>(statistics + (slot_of(t) * kGroup + query_head) * 2)); };
-  // first pass: {max, sum} of slots tid, tid + threads (one round trip for nearly every shape); maximum over all slots
-  float2 held[kHeld];
-  float maximum = -INFINITY;
-#pragma unroll
-  for (uint32_t i = 0; i < kHeld; ++i) {
-    const uint32_t t = tid + i * kReduceThreads;
-    held[i] = t < slots ? statistic(t) : make_float2(-INFINITY, 0.0f);
-    maximum = fmaxf(maximum, held[i].x);
-  }
-  for (uint32_t t = tid + kHeld * kReduceThreads; t < slots; t += kReduceThreads) maximum = fmaxf(maximum, statistic(t).x);
-  maximum = warp_max(maximum);
-  if ((tid & 31u) == 0) sh.warp_values[tid >> 5] = maximum;
-  __syncthreads();
-  maximum = sh.warp_values[0];
-#pragma unroll
-  for (uint32_t w = 1; w < kGroups * 2; ++w) maximum = fmaxf(maximum, sh.warp_values[w]);
-  __syncthreads();
-  float denominator = 0.0f;
+  float running = -INFINITY, denominator = 0.0f;
   float4 numerator = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-  for (uint32_t base = 0; base < slots; base += kReduceChunk) {
-    const uint32_t count = min(kReduceChunk, slots - base);
-    for (uint32_t t = base + tid; t < base + count; t += kReduceThreads) { // a thread's slots in rising order
-      const uint32_t nth = (t - tid) / kReduceThreads;
-      const float2 stat = nth == 0 ? held[0] : nth == 1 ? held[1] : statistic(t);
-      const float weight = stat.x == -INFINITY ? 0.0f : expf(stat.x - maximum);
-      sh.weights[t - base] = weight;
-      denominator += weight * stat.y;
-    }
-    __syncthreads();
-    for (uint32_t t = group; t < count; t += kGroups * kBatch) { // the loads of a batch are all in flight before the first add
-      float4 part[kBatch];
-      float weight[kBatch];
+  for (uint32_t t = group; t < slots; t += kGroups * kBatch) {
+    float2 stat[kBatch];
+    float4 part[kBatch];
 #pragma unroll
-      for (uint32_t k = 0; k < kBatch; ++k) {
-        const uint32_t at = t + k * kGroups;
-        const bool live = at < count;
-        weight[k] = live ? sh.weights[at] : 0.0f;
-        part[k] = live ? __ldcg(reinterpret_cast<const float4 *>(partials + (slot_of(base + at) * kGroup + query_head) * kHeadDim) + quad)
-                       : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-      }
-#pragma unroll
-      for (uint32_t k = 0; k < kBatch; ++k) {
-        if (t + k * kGroups < count) { // the sum runs over the group's slots in rising order, nothing else
-          numerator.x += weight[k] * part[k].x; numerator.y += weight[k] * part[k].y;
-          numerator.z += weight[k] * part[k].z; numerator.w += weight[k] * part[k].w;
-        }
-      }
+    for (uint32_t k = 0; k < kBatch; ++k) { // every load of the batch is in flight before the first fold
+      const uint32_t at = t + k * kGroups;
+      const bool live = at < slots;
+      const uint64_t slot = live ? slot_of(at) : 0;
+      stat[k] = live ? __ldcg(reinterpret_cast<const float2 *>(statistics + (slot * kGroup + query_head) * 2)) : make_float2(-INFINITY, 0.0f);
+      part[k] = live ? __ldcg(reinterpret_cast<const float4 *>(partials + (slot * kGroup + query_head) * kHeadDim) + quad)
+                     : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     }
-    __syncthreads();
+#pragma unroll
+    for (uint32_t k = 0; k < kBatch; ++k) {
+      if (stat[k].x == -INFINITY) continue; // an empty partial (or past the last slot) weighs nothing
+      if (stat[k].x > running) {
+        const float scale = expf(running - stat[k].x); // 0 for the first slot
+        numerator.x *= scale; numerator.y *= scale; numerator.z *= scale; numerator.w *= scale;
+        denominator *= scale;
+        running = stat[k].x;
+      }
+      const float weight = expf(stat[k].x - running);
+      numerator.x += weight * part[k].x; numerator.y += weight * part[k].y;
+      numerator.z += weight * part[k].z; numerator.w += weight * part[k].w;
+      denominator += weight * stat[k].y;
+    }
   }
-  denominator = warp_sum(denominator);
-  if ((tid & 31u) == 0) sh.warp_values[tid >> 5] = denominator;
   sh.sums[group][quad] = numerator;
+  if (quad == 0) { sh.group_maximum[group] = running; sh.group_denominator[group] = denominator; }
   __syncthreads();
-  if (tid == 0) {
-    float total = 0.0f;
+  float maximum = sh.group_maximum[0];
 #pragma unroll
-    for (uint32_t w = 0; w < kGroups * 2; ++w) total += sh.warp_values[w];
-    sh.denominator = total;
-    sh.maximum = maximum;
-  }
+  for (uint32_t g = 1; g < kGroups; ++g) maximum = fmaxf(maximum, sh.group_maximum[g]);
+  float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  float total_denominator = 0.0f;
   if (tid < 64) {
 #pragma unroll
-    for (uint32_t g = 1; g < kGroups; ++g) {
+    for (uint32_t g = 0; g < kGroups; ++g) {
+      const float own = sh.group_maximum[g];
+      const float weight = own == -INFINITY ? 0.0f : expf(own - maximum);
       const float4 other = sh.sums[g][quad];
-      numerator.x += other.x; numerator.y += other.y; numerator.z += other.z; numerator.w += other.w;
+      total.x += weight * other.x; total.y += weight * other.y; total.z += weight * other.z; total.w += weight * other.w;
+      total_denominator += weight * sh.group_denominator[g];
     }
+    if (tid == 0) { sh.maximum = maximum; sh.denominator = total_denominator; }
   }
   __syncthreads();
-  return numerator;
+  return total;
 }
 
 __device__ __forceinline__ void store_output_quad(uint16_t *output, float *output_f32, uint64_t at, float4 value) {
@@ -1403,10 +1379,11 @@ decode_reduce_kernel(const float *__restrict__ partials, const float *__restrict
   const uint32_t query_head = blockIdx.x, head = blockIdx.y, l = blockIdx.z, tid = threadIdx.x;
   dependents_may_launch(); // the next kernel of the stream may take its place; it waits for this grid's writes
   dependency_wait();       // partials, statistics and descriptors come from the decode kernel launched just before
+  const uint2 descriptor = __ldcg(reinterpret_cast<const uint2 *>(descriptors + 2 * l)); // in flight beside the parameters
   rk_verify_params p = lane_params[l];
   p.kv = layer;
   if (!rk_verify_contract_valid(&p) || p.active_rows != 1 || p.row_capacity != 1) return;
-  const float4 numerator = reduce_slots<kGroups>(partials, statistics, __ldcg(descriptors + 2 * l), __ldcg(descriptors + 2 * l + 1), head, query_head, sh);
+  const float4 numerator = reduce_slots<kGroups>(partials, statistics, descriptor.x, descriptor.y, head, query_head, sh);
   const float denominator = sh.denominator;
   if (shard_out) { // this rank's piece of a sequence split: {max, sum, un-normalised output} per query head
     float *triple = shard_out + ((uint64_t(l) * kKvHeads + head) * kGroup + query_head) * (kHeadDim + 2);
@@ -1466,6 +1443,7 @@ shard_exchange_kernel(const float *__restrict__ partials, const float *__restric
   const uint32_t query_head = blockIdx.x, head = blockIdx.y, l = blockIdx.z, tid = threadIdx.x;
   dependents_may_launch();
   dependency_wait();
+  const uint2 descriptor = __ldcg(reinterpret_cast<const uint2 *>(descriptors + 2 * l)); // in flight beside the parameters
   rk_verify_params p = lane_params[l];
   p.kv = layer;
   // a lane this rank holds no pages of (an empty shard, or an invalid lane) still publishes an empty triple
@@ -1473,7 +1451,7 @@ shard_exchange_kernel(const float *__restrict__ partials, const float *__restric
   float4 numerator = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
   float maximum = -INFINITY, denominator = 0.0f;
   if (valid) {
-    numerator = reduce_slots<kGroups>(partials, statistics, __ldcg(descriptors + 2 * l), __ldcg(descriptors + 2 * l + 1), head, query_head, sh);
+    numerator = reduce_slots<kGroups>(partials, statistics, descriptor.x, descriptor.y, head, query_head, sh);
     maximum = sh.maximum;
     denominator = sh.denominator;
   }
