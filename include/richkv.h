@@ -192,10 +192,8 @@ int rk_attention_decode_exchange(const void *window, const rk_decode_plan *plan,
 int rk_attention_decode_static(const void *window, uint32_t format, uint32_t lanes, const void *queries,
                                void *output, float *output_f32, const rk_page_entry *const *tables,
                                const rk_verify_params *lane_params, rk_kv_layer layer, void *stream);
-/* `descriptors` (rk_decode_plan.descriptor_bytes; the caller zeroes it ONCE, before its first step) holds per lane
- * {first partial segment, segments}, an arrival counter and a merge counter (the merge of a lane starts when the
- * lane's partials are all counted, not when the whole grid has finished; the counters return to zero by
- * themselves), then the status word. The status word is sticky: a bounded wait that runs out in ANY launch raises it, no launch clears it.
+/* The decode kernels' status word (the word after the 2 x lanes descriptors; the caller zeroes `descriptors` once,
+ * before its first step) is sticky: a bounded wait that runs out in ANY launch raises it, no launch clears it.
  * This call synchronises `stream`, reports RK_ERR_TIMEOUT if the word was raised since the last read, and clears
  * it. A step whose wait ran out wrote zeros for the affected lanes. The reference's analogue is its command
  * watchdog (runtime/metal/CommandWatchdog.hpp:11-35). */

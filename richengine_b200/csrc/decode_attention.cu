@@ -322,57 +322,6 @@ __device__ __forceinline__ void page_softmax(const float (&sacc)[2][2][4], const
 __device__ __forceinline__ void dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void dependents_may_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-// Scratch words behind the 2 x lanes descriptors: one arrival counter and one merge counter per lane, then the sticky
-// status word (at 4 x lanes; the no-allocation entry keeps its status word at 4 x its lane capacity).
-__device__ __forceinline__ uint32_t *lane_arrivals(uint32_t *descriptors, uint32_t lanes) { return descriptors + 2 * lanes; }
-__device__ __forceinline__ uint32_t *lane_merges(uint32_t *descriptors, uint32_t lanes) { return descriptors + 3 * lanes; }
-
-// A consumer warp has written its partial of lane `l`: every lane's stores are ordered before the warp's count
-// (fence, warp barrier, one atomic). The merge block of lane l starts when all of the lane's partials are counted:
-// segments x 12 warps.
-__device__ __forceinline__ void lane_flushed(uint32_t *descriptors, uint32_t lanes, uint32_t l) {
-  __threadfence();
-  __syncwarp();
-  if ((threadIdx.x & 31u) == 0) atomicAdd(lane_arrivals(descriptors, lanes) + l, 1u);
-}
-
-__device__ __forceinline__ uint32_t load_acquire_gpu(const uint32_t *address) {
-  uint32_t value;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(value) : "l"(address) : "memory");
-  return value;
-}
-
-// The merge side: one thread polls the lane's arrival count until it reaches `expected` (bounded: about two seconds),
-// the block follows through a barrier. False when the wait ran out. The decode grid is resident in full before a merge
-// block can be placed (the merge kernel is its programmatic dependent and every decode CTA has passed its trigger), so
-// the decode never waits for the merge and the wait always ends.
-__device__ __forceinline__ bool wait_for_lane(uint32_t *descriptors, uint32_t lanes, uint32_t l, uint32_t expected, uint32_t *shared_flag) {
-  if (threadIdx.x == 0) {
-    const uint32_t *counter = lane_arrivals(descriptors, lanes) + l;
-    uint32_t seen = 0;
-    for (uint32_t i = 0; i < (1u << 24); ++i) {
-      seen = load_acquire_gpu(counter);
-      if (seen >= expected) break;
-      __nanosleep(i < 64 ? 20 : 100);
-    }
-    *shared_flag = seen >= expected;
-  }
-  __syncthreads();
-  return *shared_flag != 0;
-}
-
-// After its output is written a merge block counts itself; the last of the lane's blocks clears both counters for the
-// next launch (which cannot start before this grid has finished).
-__device__ __forceinline__ void lane_merged(uint32_t *descriptors, uint32_t lanes, uint32_t l, uint32_t blocks_per_lane) {
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    if (atomicAdd(lane_merges(descriptors, lanes) + l, 1u) + 1 == blocks_per_lane) {
-      lane_arrivals(descriptors, lanes)[l] = 0;
-      lane_merges(descriptors, lanes)[l] = 0;
-    }
-  }
-}
-
 __device__ __forceinline__ void group_barrier(uint32_t id, uint32_t threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -387,6 +336,7 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
   const uint32_t lanes = args.lanes, cta = blockIdx.x;
   uint32_t *error_word = args.status;
   const uint32_t spin_limit = args.spin_limit;
+  dependents_may_launch(); // the merge kernel's blocks may take their places; they wait for this grid to finish
   dependency_wait();       // pages, queries and parameters may come from the kernel before this one
 
   // ---- partition: pages per lane -> prefix; segments per lane -> prefix -----------------
@@ -409,17 +359,11 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
   }
   __syncthreads();
   exclusive_scan(sh.segment_base, lanes, sh.scan);
-  if (cta == 0) {
+  if (cta == 0)
     for (uint32_t i = tid; i < lanes; i += kThreads) {
       args.descriptors[2 * i] = sh.segment_base[i];
       args.descriptors[2 * i + 1] = sh.segment_base[i + 1] - sh.segment_base[i];
     }
-    __threadfence(); // the descriptors are in L2 before this CTA lets the merge kernel start
-    __syncthreads();
-  }
-  // The merge kernel's blocks may be placed from here on (once every CTA of this grid has come this far): they do
-  // not wait for this grid to finish but for the lane they merge, see lane_flushed() and decode_reduce_kernel.
-  dependents_may_launch();
   const uint32_t range_begin = uint32_t(uint64_t(cta) * total_pages / ctas);
   const uint32_t range_end = uint32_t(uint64_t(cta + 1) * total_pages / ctas);
   if (tid == 0) {
@@ -711,7 +655,6 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
           stats[query_head * 2 + 1] = failed ? 0.0f : l_sum[j];
         }
       }
-      lane_flushed(args.descriptors, lanes, l);
     }
   }
 }
@@ -757,6 +700,7 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
   const uint32_t lanes = args.lanes, cta = blockIdx.x;
   uint32_t *error_word = args.status;
   const uint32_t spin_limit = args.spin_limit;
+  dependents_may_launch(); // the merge kernel's blocks may take their places; they wait for this grid to finish
   dependency_wait();       // pages, queries and parameters may come from the kernel before this one
 
   // ---- partition: pages per lane -> prefix; segments per lane -> prefix -----------------
@@ -779,17 +723,11 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
   }
   __syncthreads();
   exclusive_scan(sh.segment_base, lanes, sh.scan);
-  if (cta == 0) {
+  if (cta == 0)
     for (uint32_t i = tid; i < lanes; i += kThreads) {
       args.descriptors[2 * i] = sh.segment_base[i];
       args.descriptors[2 * i + 1] = sh.segment_base[i + 1] - sh.segment_base[i];
     }
-    __threadfence(); // the descriptors are in L2 before this CTA lets the merge kernel start
-    __syncthreads();
-  }
-  // The merge kernel's blocks may be placed from here on (once every CTA of this grid has come this far): they do
-  // not wait for this grid to finish but for the lane they merge, see lane_flushed() and decode_reduce_kernel.
-  dependents_may_launch();
   const uint32_t range_begin = uint32_t(uint64_t(cta) * total_pages / ctas);
   const uint32_t range_end = uint32_t(uint64_t(cta + 1) * total_pages / ctas);
   if (tid == 0) {
@@ -1062,7 +1000,6 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
           stats[query_head * 2 + 1] = failed ? 0.0f : l_sum[j];
         }
       }
-      lane_flushed(args.descriptors, lanes, l);
     }
   }
 }
@@ -1085,6 +1022,7 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
   const uint32_t lanes = args.lanes, cta = blockIdx.x;
   uint32_t *error_word = args.status;
   const uint32_t spin_limit = args.spin_limit;
+  dependents_may_launch(); // the merge kernel's blocks may take their places; they wait for this grid to finish
   dependency_wait();       // pages, queries and parameters may come from the kernel before this one
 
   // ---- partition: pages per lane -> prefix; segments per lane -> prefix -----------------
@@ -1108,17 +1046,11 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
   }
   __syncthreads();
   exclusive_scan(sh.segment_base, lanes, sh.scan);
-  if (cta == 0) {
+  if (cta == 0)
     for (uint32_t i = tid; i < lanes; i += kThreads) {
       args.descriptors[2 * i] = sh.segment_base[i];
       args.descriptors[2 * i + 1] = sh.segment_base[i + 1] - sh.segment_base[i];
     }
-    __threadfence(); // the descriptors are in L2 before this CTA lets the merge kernel start
-    __syncthreads();
-  }
-  // The merge kernel's blocks may be placed from here on (once every CTA of this grid has come this far): they do
-  // not wait for this grid to finish but for the lane they merge, see lane_flushed() and decode_reduce_kernel.
-  dependents_may_launch();
   const uint32_t range_begin = uint32_t(uint64_t(cta) * total_pages / ctas);
   const uint32_t range_end = uint32_t(uint64_t(cta + 1) * total_pages / ctas);
   if (tid == 0) {
@@ -1350,7 +1282,6 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
           stats[query_head * 2 + 1] = failed ? 0.0f : l_sum[j];
         }
       }
-      lane_flushed(args.descriptors, lanes, l);
     }
   }
 }
@@ -1441,21 +1372,17 @@ __device__ __forceinline__ void store_output_quad(uint16_t *output, float *outpu
 template <uint32_t kGroups>
 __global__ void __launch_bounds__(64 * kGroups)
 decode_reduce_kernel(const float *__restrict__ partials, const float *__restrict__ statistics,
-                     uint32_t *descriptors, uint16_t *__restrict__ output,
+                     const uint32_t *__restrict__ descriptors, uint16_t *__restrict__ output,
                      float *__restrict__ output_f32, const rk_verify_params *__restrict__ lane_params,
-                     rk_kv_layer layer, float *__restrict__ shard_out, uint32_t lanes, uint32_t *status) {
+                     rk_kv_layer layer, float *__restrict__ shard_out) {
   __shared__ ReduceShared<kGroups> sh;
-  __shared__ uint32_t arrived;
   const uint32_t query_head = blockIdx.x, head = blockIdx.y, l = blockIdx.z, tid = threadIdx.x;
-  dependents_may_launch(); // the next kernel of the stream may take its place; it waits for this grid to finish
-  // No wait for the whole decode grid: this block starts as soon as ITS lane's partials are all counted, while
-  // other CTAs of the decode kernel may still stream. The descriptors were in L2 before the decode grid let this
-  // kernel start; lane parameters and everything older were complete before the decode kernel read them.
+  dependents_may_launch(); // the next kernel of the stream may take its place; it waits for this grid's writes
+  dependency_wait();       // partials, statistics and descriptors come from the decode kernel launched just before
   const uint2 descriptor = __ldcg(reinterpret_cast<const uint2 *>(descriptors + 2 * l)); // in flight beside the parameters
   rk_verify_params p = lane_params[l];
   p.kv = layer;
   if (!rk_verify_contract_valid(&p) || p.active_rows != 1 || p.row_capacity != 1) return;
-  if (!wait_for_lane(descriptors, lanes, l, descriptor.y * kConsumerWarps, &arrived) && tid == 0) atomicExch(status, 4u);
   const float4 numerator = reduce_slots<kGroups>(partials, statistics, descriptor.x, descriptor.y, head, query_head, sh);
   const float denominator = sh.denominator;
   if (shard_out) { // this rank's piece of a sequence split: {max, sum, un-normalised output} per query head
@@ -1465,7 +1392,6 @@ decode_reduce_kernel(const float *__restrict__ partials, const float *__restrict
       *reinterpret_cast<float2 *>(triple + 2 + 4 * tid) = make_float2(numerator.x, numerator.y);
       *reinterpret_cast<float2 *>(triple + 4 + 4 * tid) = make_float2(numerator.z, numerator.w);
     }
-    lane_merged(descriptors, lanes, l, kGroup * kKvHeads);
     return;
   }
   if (tid < 64) {
@@ -1475,7 +1401,60 @@ decode_reduce_kernel(const float *__restrict__ partials, const float *__restrict
                                             : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     store_output_quad(output, output_f32, tile + query_head * kHeadDim + 4 * tid, value);
   }
-  lane_merged(descriptors, lanes, l, kGroup * kKvHeads);
+}
+
+// The merge for batches of many lanes: one block per (lane, KV head), 384 threads = (query head of the group, four
+// consecutive dims). A thread folds every slot of its (lane, head, query head) in rising order with a running maximum,
+// statistics and partial rows of a batch of slots in flight together: two round trips to L2 for a lane that spans
+// up to four CTAs, no shared memory, no barrier, and few enough blocks (4 x lanes) to run in one wave.
+constexpr uint32_t kRowMergeThreads = kGroup * (kHeadDim / 4);
+__global__ void __launch_bounds__(kRowMergeThreads)
+decode_reduce_rows_kernel(const float *__restrict__ partials, const float *__restrict__ statistics,
+                          const uint32_t *__restrict__ descriptors, uint16_t *__restrict__ output,
+                          float *__restrict__ output_f32, const rk_verify_params *__restrict__ lane_params, rk_kv_layer layer) {
+  constexpr uint32_t kBatch = 12; // four CTAs' worth of slots in one round trip
+  const uint32_t head = blockIdx.x, l = blockIdx.y, tid = threadIdx.x, query_head = tid >> 6, quad = tid & 63u;
+  dependents_may_launch(); // the next kernel of the stream may take its place; it waits for this grid's writes
+  dependency_wait();       // partials, statistics and descriptors come from the decode kernel launched just before
+  const uint2 descriptor = __ldcg(reinterpret_cast<const uint2 *>(descriptors + 2 * l)); // in flight beside the parameters
+  rk_verify_params p = lane_params[l];
+  p.kv = layer;
+  if (!rk_verify_contract_valid(&p) || p.active_rows != 1 || p.row_capacity != 1) return;
+  const uint32_t first = descriptor.x, slots = descriptor.y * kPageWarps;
+  auto slot_of = [&](uint32_t t) { return (uint64_t(first + t / kPageWarps) * kKvHeads + head) * kPageWarps + t % kPageWarps; };
+  float running = -INFINITY, denominator = 0.0f;
+  float4 numerator = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  for (uint32_t t = 0; t < slots; t += kBatch) {
+    float2 stat[kBatch];
+    float4 part[kBatch];
+#pragma unroll
+    for (uint32_t k = 0; k < kBatch; ++k) { // every load of the batch is in flight before the first fold
+      const bool live = t + k < slots;
+      const uint64_t slot = live ? slot_of(t + k) : 0;
+      stat[k] = live ? __ldcg(reinterpret_cast<const float2 *>(statistics + (slot * kGroup + query_head) * 2)) : make_float2(-INFINITY, 0.0f);
+      part[k] = live ? __ldcg(reinterpret_cast<const float4 *>(partials + (slot * kGroup + query_head) * kHeadDim) + quad)
+                     : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+#pragma unroll
+    for (uint32_t k = 0; k < kBatch; ++k) {
+      if (stat[k].x == -INFINITY) continue; // an empty partial (or past the last slot) weighs nothing
+      if (stat[k].x > running) {
+        const float scale = expf(running - stat[k].x); // 0 for the first slot
+        numerator.x *= scale; numerator.y *= scale; numerator.z *= scale; numerator.w *= scale;
+        denominator *= scale;
+        running = stat[k].x;
+      }
+      const float weight = expf(stat[k].x - running);
+      numerator.x += weight * part[k].x; numerator.y += weight * part[k].y;
+      numerator.z += weight * part[k].z; numerator.w += weight * part[k].w;
+      denominator += weight * stat[k].y;
+    }
+  }
+  const float4 value = denominator > 0.0f ? make_float4(numerator.x / denominator, numerator.y / denominator,
+                                                        numerator.z / denominator, numerator.w / denominator)
+                                          : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  const uint64_t tile = ((uint64_t(l) * kKvHeads + head) * RK_VERIFY_CHUNK_STRIDE) * kGroup * kHeadDim;
+  store_output_quad(output, output_f32, tile + query_head * kHeadDim + 4 * quad, value);
 }
 
 // ---- sequence split without a library collective: reduce -> peer stores -> flags -> rank-order merge, one kernel ----
@@ -1510,13 +1489,14 @@ __device__ __forceinline__ uint32_t load_acquire_system(const uint32_t *address)
 template <uint32_t kGroups>
 __global__ void __launch_bounds__(64 * kGroups)
 shard_exchange_kernel(const float *__restrict__ partials, const float *__restrict__ statistics,
-                      uint32_t *descriptors, uint16_t *__restrict__ output,
+                      const uint32_t *__restrict__ descriptors, uint16_t *__restrict__ output,
                       float *__restrict__ output_f32, const rk_verify_params *__restrict__ lane_params,
                       rk_kv_layer layer, ExchangeArgs ex) {
   __shared__ ReduceShared<kGroups> sh;
   __shared__ uint32_t arrived;
   const uint32_t query_head = blockIdx.x, head = blockIdx.y, l = blockIdx.z, tid = threadIdx.x;
   dependents_may_launch();
+  dependency_wait();
   const uint2 descriptor = __ldcg(reinterpret_cast<const uint2 *>(descriptors + 2 * l)); // in flight beside the parameters
   rk_verify_params p = lane_params[l];
   p.kv = layer;
@@ -1525,8 +1505,6 @@ shard_exchange_kernel(const float *__restrict__ partials, const float *__restric
   float4 numerator = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
   float maximum = -INFINITY, denominator = 0.0f;
   if (valid) {
-    // as in decode_reduce_kernel: this block starts when its lane's partials are all counted
-    if (!wait_for_lane(descriptors, ex.lanes, l, descriptor.y * kConsumerWarps, &arrived) && tid == 0) atomicExch(ex.status, 4u);
     numerator = reduce_slots<kGroups>(partials, statistics, descriptor.x, descriptor.y, head, query_head, sh);
     maximum = sh.maximum;
     denominator = sh.denominator;
@@ -1548,10 +1526,7 @@ shard_exchange_kernel(const float *__restrict__ partials, const float *__restric
     __threadfence_system();
     store_release_system(ex.flags[tid] + mine, ex.epoch);
   }
-  if (ex.post_only) {
-    if (valid) lane_merged(descriptors, ex.lanes, l, kGroup * kKvHeads);
-    return;
-  }
+  if (ex.post_only) return;
   // wait for every source rank's triple of this step in my own buffer
   if (tid == 0) arrived = 1;
   __syncthreads();
@@ -1565,9 +1540,10 @@ shard_exchange_kernel(const float *__restrict__ partials, const float *__restric
     if (!seen) { arrived = 0; atomicExch(ex.status, 3u); }
   }
   __syncthreads();
+  if (tid >= 64) return;
   float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
   float total_denominator = 0.0f;
-  if (arrived && tid < 64) {
+  if (arrived) {
     const float *local = ex.slots[ex.rank] + (uint64_t(parity) * ex.ranks * cells + cell) * kTripleFloats;
     const uint64_t stride = cells * kTripleFloats;
     float all_maximum = -INFINITY;
@@ -1585,8 +1561,7 @@ shard_exchange_kernel(const float *__restrict__ partials, const float *__restric
                                                               total.z / total_denominator, total.w / total_denominator)
                                                 : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
   const uint64_t tile = ((uint64_t(l) * kKvHeads + head) * RK_VERIFY_CHUNK_STRIDE) * kGroup * kHeadDim;
-  if (tid < 64) store_output_quad(output, output_f32, tile + query_head * kHeadDim + 4 * tid, value);
-  if (valid) lane_merged(descriptors, ex.lanes, l, kGroup * kKvHeads);
+  store_output_quad(output, output_f32, tile + query_head * kHeadDim + 4 * tid, value);
 }
 
 // Combine the shards of a sequence split: shard r holds {max, sum, un-normalised output} per
@@ -1663,18 +1638,21 @@ static int launch_dependent(Kernel kernel, dim3 grid, uint32_t threads, cudaStre
 }
 
 static int launch_merge(uint32_t lanes, cudaStream_t stream, const float *partials, const float *statistics,
-                        uint32_t *descriptors, uint16_t *output, float *output_f32,
-                        const rk_verify_params *lane_params, rk_kv_layer layer, float *triples, uint32_t *status) {
+                        const uint32_t *descriptors, uint16_t *output, float *output_f32,
+                        const rk_verify_params *lane_params, rk_kv_layer layer, float *triples) {
   const dim3 grid(kGroup, kKvHeads, lanes);
   if (wide_merge(lanes))
     return launch_dependent(decode_reduce_kernel<16>, grid, 1024, stream, "decode reduce launch", partials, statistics, descriptors,
-                            output, output_f32, lane_params, layer, triples, lanes, status);
+                            output, output_f32, lane_params, layer, triples);
+  if (!triples)
+    return launch_dependent(decode_reduce_rows_kernel, dim3(kKvHeads, lanes), kRowMergeThreads, stream, "decode reduce launch", partials,
+                            statistics, descriptors, output, output_f32, lane_params, layer);
   return launch_dependent(decode_reduce_kernel<4>, grid, 256, stream, "decode reduce launch", partials, statistics, descriptors,
-                          output, output_f32, lane_params, layer, triples, lanes, status);
+                          output, output_f32, lane_params, layer, triples);
 }
 
 static int launch_exchange(uint32_t lanes, cudaStream_t stream, const float *partials, const float *statistics,
-                           uint32_t *descriptors, uint16_t *output, float *output_f32,
+                           const uint32_t *descriptors, uint16_t *output, float *output_f32,
                            const rk_verify_params *lane_params, rk_kv_layer layer, const ExchangeArgs &exchange) {
   const dim3 grid(kGroup, kKvHeads, lanes);
   if (wide_merge(lanes))
@@ -1729,7 +1707,7 @@ int rk_decode_plan_make(uint32_t format, uint32_t kv_heads, uint32_t query_heads
   const uint64_t slots = uint64_t(plan->max_segments) * kKvHeads * kPageWarps;
   plan->partials_bytes = slots * kGroup * kHeadDim * sizeof(float);
   plan->statistics_bytes = slots * kGroup * 2 * sizeof(float);
-  plan->descriptor_bytes = (4ull * lanes + 4) * sizeof(uint32_t); // descriptors, status block, arrival and merge counters
+  plan->descriptor_bytes = (2ull * lanes + 4) * sizeof(uint32_t);
   return kOk;
 }
 
@@ -1765,9 +1743,9 @@ int rk_attention_decode(const void *window, const rk_decode_plan *plan, uint32_t
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (int st = configure_decode_kernel()) return st;
   DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, plan->lanes,
-                  descriptors + 4 * plan->lanes, kSpinLimit, 0};
+                  descriptors + 2 * plan->lanes, kSpinLimit, 0};
   if (int st = launch_decode(format, plan->ctas, s, w, args)) return st;
-  return launch_merge(plan->lanes, s, partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer, nullptr, args.status);
+  return launch_merge(plan->lanes, s, partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer, nullptr);
 }
 
 // One rank's part of a sequence-split decode: attention over the pages this rank holds, left as
@@ -1786,9 +1764,9 @@ int rk_attention_decode_shard(const void *window, const rk_decode_plan *plan, ui
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (int st = configure_decode_kernel()) return st;
   DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, plan->lanes,
-                  descriptors + 4 * plan->lanes, kSpinLimit, 0};
+                  descriptors + 2 * plan->lanes, kSpinLimit, 0};
   if (int st = launch_decode(format, plan->ctas, s, w, args)) return st;
-  return launch_merge(plan->lanes, s, partials, statistics, descriptors, nullptr, nullptr, lane_params, layer, triples, args.status);
+  return launch_merge(plan->lanes, s, partials, statistics, descriptors, nullptr, nullptr, lane_params, layer, triples);
 }
 
 // Merges `shards` gathered triples ([shard][lane][query_head][2 + D]) in shard order into the bf16
@@ -1891,7 +1869,7 @@ int rk_attention_decode_exchange(const void *window, const rk_decode_plan *plan,
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (int st = configure_decode_kernel()) return st;
   DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, plan->lanes,
-                  descriptors + 4 * plan->lanes, kSpinLimit, 0};
+                  descriptors + 2 * plan->lanes, kSpinLimit, 0};
   if (int st = launch_decode(format, plan->ctas, s, w, args)) return st;
   ExchangeArgs e{};
   for (uint32_t r = 0; r < ex->ranks; ++r) {
@@ -1905,7 +1883,7 @@ int rk_attention_decode_exchange(const void *window, const rk_decode_plan *plan,
   e.epoch = ex->epoch;
   e.spin_limit = 1u << 22; // polls of ~0.1-0.3 us: a peer may lag by about a second before the wait gives up
   e.post_only = loopback_rank >= 0 && uint32_t(loopback_rank) + 1 != ex->ranks;
-  e.status = descriptors + 4 * plan->lanes;
+  e.status = descriptors + 2 * plan->lanes;
   return launch_exchange(plan->lanes, s, partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer, e);
 }
 
@@ -1917,7 +1895,7 @@ constexpr uint32_t kStaticLanes = 16, kStaticCtas = 148;
 constexpr size_t kStaticSlots = size_t(kStaticLanes + kStaticCtas) * kKvHeads * kPageWarps;
 constexpr size_t kStaticPartialBytes = kStaticSlots * kGroup * kHeadDim * sizeof(float);
 constexpr size_t kStaticStatisticBytes = (kStaticSlots * kGroup * 2 * sizeof(float) + 255) / 256 * 256;
-constexpr size_t kStaticDescriptorBytes = ((4 * kStaticLanes + 4) * sizeof(uint32_t) + 255) / 256 * 256;
+constexpr size_t kStaticDescriptorBytes = ((2 * kStaticLanes + 4) * sizeof(uint32_t) + 255) / 256 * 256;
 static __device__ __align__(256) unsigned char g_decode_scratch[kStaticPartialBytes + kStaticStatisticBytes + kStaticDescriptorBytes];
 
 // The device address of g_decode_scratch on the current device. In host code the array's name is only a handle
@@ -1977,39 +1955,35 @@ int rk_attention_decode_static(const void *window, uint32_t format, uint32_t lan
   uint32_t *descriptors = static_descriptors(base);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, lanes,
-                  descriptors + 4 * kStaticLanes, kSpinLimit, 0};
+                  descriptors + 2 * kStaticLanes, kSpinLimit, 0};
   if (int st = launch_decode(format, kStaticCtas, s, w, args)) return st;
-  return launch_merge(lanes, s, partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer, nullptr, args.status);
+  return launch_merge(lanes, s, partials, statistics, descriptors, static_cast<uint16_t *>(output), output_f32, lane_params, layer, nullptr);
 }
 
 // Reads AND clears a sticky status word on `stream` (synchronises it): kTimeout when a bounded wait inside a decode
 // kernel ran out in any step launched since the last read.
-static int read_status_word(uint32_t *word_address, uint32_t *counters, uint32_t counter_words, cudaStream_t s) {
+static int read_status_word(uint32_t *word_address, cudaStream_t s) {
   uint32_t word = 0;
   if (int st = cuda_status(cudaMemcpyAsync(&word, word_address, sizeof(word), cudaMemcpyDeviceToHost, s), "decode status read")) return st;
   if (int st = cuda_status(cudaStreamSynchronize(s), "decode status sync")) return st;
   if (!word) return kOk;
   if (int st = cuda_status(cudaMemsetAsync(word_address, 0, sizeof(word), s), "decode status clear")) return st;
-  // a step that gave up may have left its lane counters mid-count: the next step starts from zero again
-  if (int st = cuda_status(cudaMemsetAsync(counters, 0, counter_words * sizeof(uint32_t), s), "decode counter clear")) return st;
   if (int st = cuda_status(cudaStreamSynchronize(s), "decode status sync")) return st;
   set_error(word == 1 ? "a bounded wait in the decode kernel ran out (the producer waiting for a free stage)"
-            : word == 2 ? "a bounded wait in the decode kernel ran out (a consumer waiting for a page)"
-            : word == 3 ? "a bounded wait in the shard exchange ran out (a peer's triple did not arrive)"
-                        : "a bounded wait in the merge ran out (a lane's partials were not all counted)");
+                      : "a bounded wait in the decode kernel ran out (a consumer waiting for a page)");
   return kTimeout;
 }
 
 int rk_attention_decode_status(const rk_decode_plan *plan, uint32_t *descriptors, void *stream) {
   if (!plan || !descriptors) { set_error("rk_attention_decode_status: invalid arguments"); return kInvalid; }
-  return read_status_word(descriptors + 4 * plan->lanes, descriptors + 2 * plan->lanes, 2 * plan->lanes, static_cast<cudaStream_t>(stream));
+  return read_status_word(descriptors + 2 * plan->lanes, static_cast<cudaStream_t>(stream));
 }
 
 // The same for rk_attention_decode_static, whose status word lives in the library's own array.
 int rk_attention_decode_static_status(void *stream) {
   unsigned char *base = nullptr;
   if (int st = static_scratch(&base)) return st;
-  return read_status_word(static_descriptors(base) + 4 * kStaticLanes, static_descriptors(base), 4 * kStaticLanes, static_cast<cudaStream_t>(stream));
+  return read_status_word(static_descriptors(base) + 2 * kStaticLanes, static_cast<cudaStream_t>(stream));
 }
 
 // Test hook of the timeout path: rk_attention_decode whose waits give up after `spin_limit` polls and whose
@@ -2030,7 +2004,7 @@ int rk_attention_decode_probe_timeout(const void *window, const rk_decode_plan *
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (int st = configure_decode_kernel()) return st;
-  uint32_t *status = own_scratch ? nullptr : descriptors + 4 * plan->lanes;
+  uint32_t *status = own_scratch ? nullptr : descriptors + 2 * plan->lanes;
   uint32_t ctas = plan->ctas;
   if (own_scratch) {
     unsigned char *base = nullptr;
@@ -2038,13 +2012,13 @@ int rk_attention_decode_probe_timeout(const void *window, const rk_decode_plan *
     partials = reinterpret_cast<float *>(base);
     statistics = reinterpret_cast<float *>(base + kStaticPartialBytes);
     descriptors = static_descriptors(base);
-    status = descriptors + 4 * kStaticLanes;
+    status = descriptors + 2 * kStaticLanes;
     ctas = min(ctas, kStaticCtas);
   }
   DecodeArgs args{static_cast<const uint16_t *>(queries), partials, statistics, descriptors, tables, lane_params, layer, w->base, plan->lanes,
                   status, spin_limit, withheld_pages};
   if (int st = launch_decode(format, ctas, s, w, args)) return st;
-  return launch_merge(plan->lanes, s, partials, statistics, descriptors, static_cast<uint16_t *>(output), nullptr, lane_params, layer, nullptr, args.status);
+  return launch_merge(plan->lanes, s, partials, statistics, descriptors, static_cast<uint16_t *>(output), nullptr, lane_params, layer, nullptr);
 }
 
 } // extern "C"
