@@ -98,6 +98,24 @@ int64_t rk_slot_records_header(uint64_t slot_bytes, uint32_t label_bytes, const 
 int64_t rk_cache_persist(void *cache, void *store);
 int rk_cache_adopt(void *cache, void *store, uint64_t *out);
 
+/* ---- composite states and the reclaim order they impose (runtime/engine/cache/StateCache.hpp:137-379 as far as the
+ * KV path is coupled to it, Cache.hpp:549-556, Cache.cpp:451-628) ------------------------------------------------
+ * A state is a byte count published at a complete KV block, disposable (checkpoint) or ordinary, in use while an
+ * unfinished request resumes from it, pinned while a restore reads it. rk_cache_evict_one is Cache::evictOne:
+ * checkpoints first (not in a page scan), then KV leaves no state needs, then ordinary states and the leaves under
+ * them by shared recency, states in use and their KV last and only up_to_in_use; out[4] = made progress, pending,
+ * evicted a state, state bytes freed. rk_cache_reclaim_one_state is Cache::reclaimOneState (1 = a state went).
+ * rk_cache_state_info out[6] = contains, ordinary, in use, bytes, KV needed by a state, KV needed by a state in use;
+ * rk_cache_state_summary out[4] = states, resident bytes, evictable states, resume point. */
+int64_t rk_cache_block_at(void *cache, uint64_t request, uint32_t tokens);
+int rk_cache_state_publish(void *cache, uint64_t block, uint64_t bytes, int checkpoint);
+int rk_cache_state_use(void *cache, uint64_t block, int use);
+int rk_cache_state_pin(void *cache, uint64_t block, int pin);
+int rk_cache_state_info(void *cache, uint64_t block, uint64_t *out);
+int rk_cache_state_summary(void *cache, uint64_t *out);
+int rk_cache_evict_one(void *cache, int up_to_in_use, int keep_resume_point, int pages_only, uint64_t *out);
+int rk_cache_reclaim_one_state(void *cache, int checkpoints_only, uint64_t for_block);
+
 /* ---- plans -------------------------------------------------------------------------------------- */
 /* names: "split\nreduce\nstore"; out[16] = splits, lane splits of the first four lanes, splitGroups xyz,
  * reduceGroups xyz, partialsBytes, statisticsBytes, rowCapacity, streamingDecode, tensorCoreWindow.

@@ -20,6 +20,7 @@
 #include <memory>
 #include <mutex>
 #include <string>
+#include <deque>
 #include <vector>
 
 namespace rk {
@@ -461,7 +462,12 @@ struct HostTier {
   uint32_t *device_checksums = nullptr;  // device: one word per transfer
   rk_page_entry *device_entries = nullptr; // device: the page's table entry, one per transfer (no allocation per transfer)
   rk_page_entry *host_entries = nullptr;   // pinned mirror the entries are copied from
-  cudaStream_t stream = nullptr;
+  // Two streams taken in turn: while one transfer's bytes cross PCIe the next transfer's pack (or unpack) kernel
+  // runs. A stream retires its transfers in issue order, so a poll asks only about the oldest one of each.
+  static constexpr uint32_t kStreams = 2;
+  cudaStream_t streams[kStreams] = {};
+  std::deque<uint32_t> order[kStreams];
+  uint32_t next_stream = 0;
   std::vector<uint8_t> slot_used;
   std::vector<uint8_t> slot_verify;      // adopted from an earlier process and not read yet
   std::vector<uint32_t> slot_expected;
@@ -488,17 +494,18 @@ extern "C" void *rk_tier_create(void *storage, uint32_t slots, uint32_t transfer
   t->transfers.resize(transfer_limit);
   if (cuda_status(cudaHostAlloc(reinterpret_cast<void **>(&t->host), uint64_t(slots) * t->slot_bytes, cudaHostAllocDefault), "pinned host arena")) return nullptr;
   if (cuda_status(cudaMalloc(reinterpret_cast<void **>(&t->staging), uint64_t(transfer_limit) * t->slot_bytes), "tier staging")) { cudaFreeHost(t->host); return nullptr; }
-  if (cuda_status(cudaStreamCreateWithFlags(&t->stream, cudaStreamNonBlocking), "tier stream")) { cudaFree(t->staging); cudaFreeHost(t->host); return nullptr; }
+  for (cudaStream_t &stream : t->streams)
+    if (cuda_status(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking), "tier stream")) { cudaFree(t->staging); cudaFreeHost(t->host); return nullptr; }
   if (cuda_status(cudaHostAlloc(reinterpret_cast<void **>(&t->slot_checksums), (uint64_t(slots) + transfer_limit) * 4, cudaHostAllocDefault), "tier checksums") ||
       cuda_status(cudaMalloc(reinterpret_cast<void **>(&t->device_checksums), uint64_t(transfer_limit) * 4), "tier checksums")) {
-    cudaFreeHost(t->slot_checksums); cudaStreamDestroy(t->stream); cudaFree(t->staging); cudaFreeHost(t->host);
+    cudaFreeHost(t->slot_checksums); for (cudaStream_t stream : t->streams) cudaStreamDestroy(stream); cudaFree(t->staging); cudaFreeHost(t->host);
     return nullptr;
   }
   memset(t->slot_checksums, 0, (uint64_t(slots) + transfer_limit) * 4);
   t->arrived_checksums = t->slot_checksums + slots;
   if (cuda_status(cudaMalloc(reinterpret_cast<void **>(&t->device_entries), uint64_t(transfer_limit) * sizeof(rk_page_entry)), "tier entries") ||
       cuda_status(cudaHostAlloc(reinterpret_cast<void **>(&t->host_entries), uint64_t(transfer_limit) * sizeof(rk_page_entry), cudaHostAllocDefault), "tier entries")) {
-    cudaFree(t->device_entries); cudaFree(t->device_checksums); cudaFreeHost(t->slot_checksums); cudaStreamDestroy(t->stream);
+    cudaFree(t->device_entries); cudaFree(t->device_checksums); cudaFreeHost(t->slot_checksums); for (cudaStream_t stream : t->streams) cudaStreamDestroy(stream);
     cudaFree(t->staging); cudaFreeHost(t->host);
     return nullptr;
   }
@@ -509,9 +516,9 @@ extern "C" void *rk_tier_create(void *storage, uint32_t slots, uint32_t transfer
 extern "C" void rk_tier_destroy(void *tier) {
   auto *t = static_cast<HostTier *>(tier);
   if (!t) return;
-  cudaStreamSynchronize(t->stream); // every transfer reads or writes its page in place
+  for (cudaStream_t stream : t->streams) cudaStreamSynchronize(stream); // every transfer reads or writes its page in place
   for (Transfer &x : t->transfers) cudaEventDestroy(x.done);
-  cudaStreamDestroy(t->stream);
+  for (cudaStream_t stream : t->streams) cudaStreamDestroy(stream);
   cudaFree(t->staging);
   cudaFree(t->device_checksums);
   cudaFree(t->device_entries);
@@ -580,43 +587,47 @@ int start_transfer(HostTier *t, bool demotion, uint32_t page, uint32_t slot, cud
   while (id < t->transfer_limit && t->transfers[id].in_flight) ++id;
   if (id == t->transfer_limit) return kRefused;
   Transfer &x = t->transfers[id];
+  const uint32_t lane = t->next_stream;
+  cudaStream_t stream = t->streams[lane];
   if (after) { // order the transfer after work already launched on the caller's stream
     if (int status = cuda_status(cudaEventRecord(x.done, after), "tier order event")) return status;
-    if (int status = cuda_status(cudaStreamWaitEvent(t->stream, x.done, 0), "tier order wait")) return status;
+    if (int status = cuda_status(cudaStreamWaitEvent(stream, x.done, 0), "tier order wait")) return status;
   }
   uint8_t *stage = t->staging + uint64_t(id) * t->slot_bytes;
   uint8_t *host = t->host + uint64_t(slot) * t->slot_bytes;
   const Storage *s = t->storage;
   // the page's table entry travels through the transfer's own pinned / device words: nothing is allocated per transfer
   t->host_entries[id] = s->entry(page);
-  int status = cuda_status(cudaMemcpyAsync(t->device_entries + id, t->host_entries + id, sizeof(rk_page_entry), cudaMemcpyHostToDevice, t->stream), "tier entry");
+  int status = cuda_status(cudaMemcpyAsync(t->device_entries + id, t->host_entries + id, sizeof(rk_page_entry), cudaMemcpyHostToDevice, stream), "tier entry");
   if (status) return status;
   if (demotion) {
     // packed and checksummed in one pass over the page, before the bytes cross PCIe
     const GatherSource source{t->device_entries + id, s->layers, s->extent_pages, s->data_bytes, s->scale_bytes};
-    status = launch_crc32c(stage, t->slot_bytes, t->slot_bytes, 1, t->device_checksums + id, 0, t->stream, &source);
-    if (!status) status = cuda_status(cudaMemcpyAsync(t->slot_checksums + slot, t->device_checksums + id, 4, cudaMemcpyDeviceToHost, t->stream), "demotion checksum");
-    if (!status) status = cuda_status(cudaMemcpyAsync(host, stage, t->slot_bytes, cudaMemcpyDeviceToHost, t->stream), "demotion copy");
+    status = launch_crc32c(stage, t->slot_bytes, t->slot_bytes, 1, t->device_checksums + id, 0, stream, &source);
+    if (!status) status = cuda_status(cudaMemcpyAsync(t->slot_checksums + slot, t->device_checksums + id, 4, cudaMemcpyDeviceToHost, stream), "demotion checksum");
+    if (!status) status = cuda_status(cudaMemcpyAsync(host, stage, t->slot_bytes, cudaMemcpyDeviceToHost, stream), "demotion copy");
     x.verify = false;
   } else {
-    status = cuda_status(cudaMemcpyAsync(stage, host, t->slot_bytes, cudaMemcpyHostToDevice, t->stream), "restore copy");
+    status = cuda_status(cudaMemcpyAsync(stage, host, t->slot_bytes, cudaMemcpyHostToDevice, stream), "restore copy");
     x.verify = t->slot_verify[slot] != 0;
     x.expected = t->slot_expected[slot];
     if (!status && x.verify) { // an adopted slot's first read: check what arrived against its record
-      status = launch_crc32c(stage, t->slot_bytes, t->slot_bytes, 1, t->device_checksums + id, 0, t->stream, nullptr);
-      if (!status) status = cuda_status(cudaMemcpyAsync(t->arrived_checksums + id, t->device_checksums + id, 4, cudaMemcpyDeviceToHost, t->stream), "restore checksum");
+      status = launch_crc32c(stage, t->slot_bytes, t->slot_bytes, 1, t->device_checksums + id, 0, stream, nullptr);
+      if (!status) status = cuda_status(cudaMemcpyAsync(t->arrived_checksums + id, t->device_checksums + id, 4, cudaMemcpyDeviceToHost, stream), "restore checksum");
     }
-    if (!status) status = move_pages(s->format, s->layers, s->kv_heads, s->head_dim, s->extent_pages, nullptr, t->device_entries + id, stage, nullptr, 1, t->stream);
+    if (!status) status = move_pages(s->format, s->layers, s->kv_heads, s->head_dim, s->extent_pages, nullptr, t->device_entries + id, stage, nullptr, 1, stream);
   }
   if (status) {
     if (demotion) t->writable = false; // a failed write closes the tier to demotions
     return status;
   }
-  if (int s2 = cuda_status(cudaEventRecord(x.done, t->stream), "tier completion event")) return s2;
+  if (int s2 = cuda_status(cudaEventRecord(x.done, stream), "tier completion event")) return s2;
   x.demotion = demotion; x.in_flight = true; x.ready = false; x.success = false;
   x.forced_failure = t->fail_next > 0;
   if (t->fail_next) --t->fail_next;
   x.page = page; x.slot = slot;
+  t->order[lane].push_back(id);
+  t->next_stream = (lane + 1) % HostTier::kStreams;
   ++t->in_flight;
   ++(demotion ? t->demotions : t->restores);
   return int(id);
@@ -637,10 +648,12 @@ extern "C" int rk_tier_restore(void *tier, uint32_t slot, uint32_t page, void *a
 extern "C" int rk_tier_poll(void *tier) {
   auto *t = static_cast<HostTier *>(tier);
   int retired = 0;
-  for (Transfer &x : t->transfers) {
-    if (!x.in_flight || x.ready) continue;
+  for (std::deque<uint32_t> &order : t->order)
+  while (!order.empty()) { // a stream's transfers finish in issue order: the first one still running ends the scan
+    Transfer &x = t->transfers[order.front()];
     const cudaError_t state = cudaEventQuery(x.done);
-    if (state == cudaErrorNotReady) continue;
+    if (state == cudaErrorNotReady) break;
+    order.pop_front();
     x.ready = true;
     x.success = state == cudaSuccess && !x.forced_failure;
     if (!x.demotion && x.verify) { // a payload that does not match its record is a miss and nothing worse
@@ -668,6 +681,7 @@ extern "C" int rk_tier_transfer_finish(void *tier, uint32_t id) {
 }
 extern "C" int rk_tier_drain(void *tier) {
   auto *t = static_cast<HostTier *>(tier);
-  if (int status = cuda_status(cudaStreamSynchronize(t->stream), "tier drain")) return status;
+  for (cudaStream_t stream : t->streams)
+    if (int status = cuda_status(cudaStreamSynchronize(stream), "tier drain")) return status;
   return rk_tier_poll(tier);
 }

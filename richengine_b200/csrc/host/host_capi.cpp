@@ -422,6 +422,55 @@ int rk_plan_workspaces(uint32_t lanes, uint32_t max_rows, uint32_t query_heads, 
     return RK_OK;
   });
 }
+// ---- composite states and the reclaim order they impose --------------------------------------------------------
+#define CACHE (static_cast<CacheHandle *>(cache)->cache)
+int64_t rk_cache_block_at(void *cache, uint64_t request, uint32_t tokens) {
+  int64_t block = 0;
+  const int status = guarded([&] { block = int64_t(CACHE->blockAt(request, tokens)); return RK_OK; });
+  return status ? status : block;
+}
+int rk_cache_state_publish(void *cache, uint64_t block, uint64_t bytes, int checkpoint) {
+  return guarded([&] { CACHE->publishCompositeState(block, bytes, checkpoint != 0); return RK_OK; });
+}
+int rk_cache_state_use(void *cache, uint64_t block, int use) {
+  return guarded([&] { if (use) CACHE->states().use(block); else CACHE->states().unuse(block); return RK_OK; });
+}
+int rk_cache_state_pin(void *cache, uint64_t block, int pin) {
+  return guarded([&] { if (pin) CACHE->states().pin(block); else CACHE->states().unpin(block); return RK_OK; });
+}
+// out[6] = contains, ordinary, in use, bytes, KV needed by a state, KV needed by a state in use
+int rk_cache_state_info(void *cache, uint64_t block, uint64_t *out) {
+  return guarded([&] {
+    const engine::StateCache &states = CACHE->states();
+    out[0] = states.contains(block); out[1] = states.ordinary(block); out[2] = states.inUse(block); out[3] = states.bytes(block);
+    out[4] = CACHE->index().contains(block) && CACHE->kvNeededByState(block);
+    out[5] = CACHE->index().contains(block) && CACHE->kvNeededByStateInUse(block);
+    return RK_OK;
+  });
+}
+// out[4] = states, resident bytes, evictable states (with those in use), resume point
+int rk_cache_state_summary(void *cache, uint64_t *out) {
+  return guarded([&] {
+    const engine::StateCache &states = CACHE->states();
+    out[0] = states.size(); out[1] = states.residentBytes(); out[2] = states.evictableStates(true); out[3] = states.resumePoint();
+    return RK_OK;
+  });
+}
+// One eviction step in the reference's order; out[4] = made progress, pending, evicted a state, state bytes freed.
+int rk_cache_evict_one(void *cache, int up_to_in_use, int keep_resume_point, int pages_only, uint64_t *out) {
+  return guarded([&] {
+    const engine::ReclaimStep step = CACHE->evictOne(up_to_in_use ? engine::ReclaimClass::InUse : engine::ReclaimClass::Ordinary,
+                                                     keep_resume_point != 0, pages_only != 0);
+    out[0] = step.madeProgress; out[1] = step.pending; out[2] = step.evictedState; out[3] = step.reclaimedBytes;
+    return RK_OK;
+  });
+}
+int rk_cache_reclaim_one_state(void *cache, int checkpoints_only, uint64_t for_block) {
+  return guarded([&] { return CACHE->reclaimOneState(checkpoints_only != 0, for_block) ? 1 : 0; });
+}
+
+#undef CACHE
+
 // ---- the operator's encoders (ops::PagedAttention::add*): validation first, then the launches ------------------
 namespace {
 struct OperatorPlan {

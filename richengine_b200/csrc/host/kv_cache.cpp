@@ -216,6 +216,26 @@ std::optional<PrefixIndex::Candidate> PrefixIndex::evictionCandidate() const {
   return best;
 }
 
+std::optional<PrefixIndex::Candidate> PrefixIndex::evictionCandidate(const Candidate *after, const std::function<bool(uint64_t)> &accept) const {
+  std::optional<Candidate> best;
+  for (const auto &[id, entry] : blocks_) {
+    if (entry.page == noPage || entry.residentChildren || entry.activeUsers || entry.transferring) continue;
+    if (after && (entry.lastUsed < after->lastUsed || (entry.lastUsed == after->lastUsed && id <= after->block))) continue;
+    if (best && (entry.lastUsed > best->lastUsed || (entry.lastUsed == best->lastUsed && id > best->block))) continue;
+    if (!accept(id)) continue;
+    best = Candidate{id, entry.lastUsed};
+  }
+  return best;
+}
+
+void PrefixIndex::adjustStatesBelow(uint64_t block, int states, int inUse) {
+  for (uint64_t id = at(block).parent; id; id = at(id).parent) {
+    Block &above = at(id);
+    above.statesBelow = uint32_t(int(above.statesBelow) + states);
+    above.statesInUseBelow = uint32_t(int(above.statesInUseBelow) + inUse);
+  }
+}
+
 uint32_t PrefixIndex::tierBlocks() const noexcept {
   uint32_t count = 0;
   for (const auto &[id, entry] : blocks_) count += entry.slot != nullptr;
@@ -422,30 +442,105 @@ uint32_t Cache::truncate(uint64_t id, uint32_t committedTokens, uint32_t scratch
   return released;
 }
 
-bool Cache::reclaimOne() {
-  const auto candidate = index_.evictionCandidate();
-  if (!candidate) return false;
-  const uint64_t block = candidate->block;
+Cache::LeafReclaim Cache::reclaimKvLeaf(uint64_t block) {
   if (index_.slot(block)) { // a tier copy exists already: the page can go at once
     index_.dropPage(block);
     ++counters_.evictedBlocks;
-    return true;
+    return LeafReclaim::Started;
   }
   if (tier_ && tier_->writable()) {
-    if (!tier_->canDemote()) return false; // the caller waits while transfers are in flight
+    if (!tier_->canDemote()) return LeafReclaim::Pending; // the caller waits while transfers are in flight
     std::shared_ptr<KvTierSlot> slot = tier_->acquireSlot();
     if (slot) {
       std::unique_ptr<KvTransfer> ticket = tier_->demote(index_.page(block), slot);
-      if (!ticket) return false;
+      if (!ticket) return LeafReclaim::Pending;
       index_.setTransferring(block, true);
       demotions_.push_back({block, index_.page(block), std::move(ticket), std::move(slot)});
       ++counters_.demotions;
-      return true;
+      return LeafReclaim::Started;
     }
   }
-  index_.erase(block); // no tier (or its quota is full): the content is forgotten
+  // No tier (or its quota is full): the content is forgotten, and the state on it with it. A leaf whose children
+  // live on in the tier stays: they hang on it.
+  if (index_.children(block)) return LeafReclaim::Impossible;
+  states_.forget(block);
+  index_.erase(block);
   ++counters_.evictedBlocks;
-  return true;
+  return LeafReclaim::Started;
+}
+
+// Without composite states every idle leaf is a dead leaf, and this is "the oldest idle leaf first".
+bool Cache::reclaimOne() { return evictOne(ReclaimClass::InUse, false, true).madeProgress; }
+
+uint64_t Cache::blockAt(uint64_t id, uint32_t tokens) const {
+  const Request &active = request(id);
+  if (!tokens || tokens % kv::kPageTokens) return 0;
+  const uint32_t index = tokens / kv::kPageTokens - 1;
+  return index < active.blocks.size() ? active.blocks[index] : 0;
+}
+
+void Cache::publishCompositeState(uint64_t block, uint64_t bytes, bool checkpoint) {
+  if (!index_.contains(block)) throw std::invalid_argument("a composite state needs its KV block in the cache");
+  if (!bytes) throw std::invalid_argument("a composite state has a size");
+  states_.publish(block, bytes, checkpoint);
+}
+
+std::optional<Cache::Victim> Cache::reclaimOldest(bool inUse, bool keepResumePoint, bool pagesOnly) {
+  using Candidate = PrefixIndex::Candidate;
+  // A dead leaf (no state restores through it) goes before anything a state needs; one that cannot go now stays
+  // and the next goes.
+  if (!inUse) {
+    const auto dead = [this](uint64_t id) { return !kvNeededByState(id); };
+    for (auto leaf = index_.evictionCandidate(nullptr, dead); leaf; leaf = index_.evictionCandidate(&*leaf, dead))
+      if (reclaimKvLeaf(leaf->block) == LeafReclaim::Started) return Victim{true};
+  }
+  std::optional<StateCandidate> state;
+  if (!pagesOnly) state = inUse ? states_.inUseCandidate() : states_.ordinaryCandidate(keepResumePoint);
+  // the leaves a state needs: without a state in RAM on them (one goes first, in the order every victim goes in),
+  // or with one in a page scan
+  const auto needed = [&](uint64_t id) { return (pagesOnly || !states_.stateResident(id)) && kvNeededByStateInUse(id) == inUse; };
+  std::optional<Candidate> kv = index_.evictionCandidate(nullptr, needed);
+  while (state || kv) {
+    if (state && (!kv || state->lastUsed <= kv->lastUsed)) {
+      if (states_.reclaim(state->block)) return Victim{false};
+      state.reset();
+      continue;
+    }
+    if (states_.stateResident(kv->block)) { // a page scan's leaf gives up its state first; the resume point stays, and its leaf
+      if ((!keepResumePoint || kv->block != states_.resumePoint()) && states_.reclaim(kv->block)) return Victim{false};
+      kv = index_.evictionCandidate(&*kv, needed);
+      continue;
+    }
+    if (reclaimKvLeaf(kv->block) == LeafReclaim::Started) return Victim{true};
+    kv = index_.evictionCandidate(&*kv, needed);
+  }
+  return std::nullopt;
+}
+
+ReclaimStep Cache::evictOne(ReclaimClass upTo, bool keepResumePoint, bool pagesOnly) {
+  // Disposable checkpoints go first, except in a page scan, to which their buffers give no page.
+  if (!pagesOnly)
+    if (const auto oldest = states_.checkpointCandidate(keepResumePoint)) {
+      uint64_t freed = 0;
+      if (states_.reclaim(oldest->block, &freed)) return {true, false, true, freed};
+    }
+  for (const bool inUse : {false, true}) {
+    if (inUse && upTo == ReclaimClass::Ordinary) break;
+    if (inUse && transfersInFlight()) return {false, true, false, 0};
+    const uint64_t before = states_.residentBytes();
+    if (const auto victim = reclaimOldest(inUse, keepResumePoint, pagesOnly))
+      return {true, false, !victim->kv, before - states_.residentBytes()};
+  }
+  return {false, transfersInFlight(), false, 0};
+}
+
+bool Cache::reclaimOneState(bool checkpointsOnly, uint64_t forBlock) {
+  const auto recycle = [this](const std::optional<StateCandidate> &state) { return state && states_.reclaim(state->block); };
+  if (recycle(states_.checkpointCandidate(false))) return true;
+  if (checkpointsOnly) return false;
+  if (recycle(states_.ordinaryCandidate(false))) return true;
+  // only a publication that is itself in use may take a state in use
+  return states_.inUse(forBlock) && recycle(states_.inUseCandidate());
 }
 
 uint32_t Cache::reclaimForPages(uint32_t pages) {
@@ -464,7 +559,8 @@ void Cache::pollTransfers() {
     index_.setTransferring(t.block, false);
     if (landed) {
       index_.setSlot(t.block, t.slot);
-      if (index_.residentLeaf(t.block)) { index_.dropPage(t.block); ++counters_.evictedBlocks; }
+      // a state published on the block while its copy was in flight keeps the page under it
+      if (index_.residentLeaf(t.block) && !states_.stateResident(t.block)) { index_.dropPage(t.block); ++counters_.evictedBlocks; }
     } else {
       ++counters_.failedTransfers; // the page stays: a failed demotion loses nothing
     }

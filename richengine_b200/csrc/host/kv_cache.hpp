@@ -16,6 +16,9 @@
 #include "kv_pool.hpp"
 #include "kv_tier.hpp"
 #include "slot_store.hpp"
+#include "state_cache.hpp"
+
+#include <functional>
 
 #include <array>
 #include <cstdint>
@@ -70,6 +73,15 @@ public:
   void poison(uint64_t block);
   void erase(uint64_t block); // only a block without children, users or transfer
   std::optional<Candidate> evictionCandidate() const; // oldest resident leaf no request uses
+  // The oldest such leaf after `after` in (recency, id) order that `accept` takes (KvCache::evictionCandidate(after)).
+  std::optional<Candidate> evictionCandidate(const Candidate *after, const std::function<bool(uint64_t)> &accept) const;
+  // States on the blocks strictly below a block, all of them and those in use (KvCache::stateBelow,
+  // KvCache::stateInUseBelow): a state at `block` appeared or went.
+  void adjustStatesBelow(uint64_t block, int states, int inUse);
+  bool stateBelow(uint64_t block) const { return at(block).statesBelow != 0; }
+  bool stateInUseBelow(uint64_t block) const { return at(block).statesInUseBelow != 0; }
+  uint32_t children(uint64_t block) const { return at(block).children; }
+  uint64_t tick() noexcept { return ++clock_; }
   // Takes back a tier-only block an earlier process recorded (KvCache::adoptDiskBlock,
   // runtime/engine/cache/KvCache.cpp:160-199): false when another block already holds its key.
   bool adoptTierBlock(uint64_t id, uint64_t parent, std::span<const uint32_t> tokens, ImageIdentity images,
@@ -90,6 +102,7 @@ private:
     uint32_t page = noPage;
     std::shared_ptr<KvTierSlot> slot;
     uint32_t children = 0, residentChildren = 0, activeUsers = 0;
+    uint32_t statesBelow = 0, statesInUseBelow = 0;
     bool transferring = false, poisoned = false;
   };
   Block &at(uint64_t block);
@@ -124,10 +137,37 @@ struct CacheSnapshot {
   uint64_t demotions = 0, restores = 0, failedTransfers = 0, evictedBlocks = 0, forkCopies = 0, truncatedPages = 0;
 };
 
+// How far a reclaim may reach (Cache.hpp: ReclaimClass): states in use, and the KV they restore through, go only to
+// running work.
+enum class ReclaimClass : uint8_t { Ordinary, InUse };
+struct ReclaimStep { bool madeProgress = false, pending = false, evictedState = false; uint64_t reclaimedBytes = 0; };
+
 class Cache final {
 public:
-  Cache(KvPool &pool, kv::ExtentStorage &storage, KvTier *tier = nullptr) : pool_(pool), storage_(storage), tier_(tier), index_(pool) {}
+  Cache(KvPool &pool, kv::ExtentStorage &storage, KvTier *tier = nullptr)
+      : pool_(pool), storage_(storage), tier_(tier), index_(pool),
+        states_([this](uint64_t block, int states, int inUse) { index_.adjustStatesBelow(block, states, inUse); },
+                [this] { return index_.tick(); }) {}
   ~Cache();
+
+  // ---- composite states and the reclaim order they impose (runtime/engine/cache/Cache.cpp:451-628) ----------------
+  StateCache &states() noexcept { return states_; }
+  const StateCache &states() const noexcept { return states_; }
+  // A complete block of a request's chain (Cache::blockAt): the block that ends at `tokens`, 0 when not published.
+  uint64_t blockAt(uint64_t request, uint32_t tokens) const;
+  void publishCompositeState(uint64_t block, uint64_t bytes, bool checkpoint);
+  // Only a state restores a chain that has left the pool, through its own block and every block above
+  // (Cache.hpp:549-556): such KV is needed by that state, and in use when the state is.
+  bool kvNeededByState(uint64_t block) const { return states_.contains(block) || index_.stateBelow(block); }
+  bool kvNeededByStateInUse(uint64_t block) const { return (states_.inUse(block) && states_.contains(block)) || index_.stateInUseBelow(block); }
+  // One step of eviction in the reference's order (Cache::evictOne, Cache::reclaimOldest): disposable checkpoints
+  // first (not in a page scan); then KV leaves no state needs, oldest first; then ordinary states and the leaves
+  // under them by shared recency (a leaf gives up the state on it first); states in use and the KV they need
+  // last, only up to ReclaimClass::InUse and once no transfer in flight can return what is needed.
+  ReclaimStep evictOne(ReclaimClass upTo, bool keepResumePoint, bool pagesOnly);
+  // Room for one more state (Cache::reclaimOneState): a checkpoint; unless checkpointsOnly an ordinary state; a state
+  // in use only for a publication that is itself in use (forBlock).
+  bool reclaimOneState(bool checkpointsOnly, uint64_t forBlock);
 
   void beginRequest(uint64_t request);
   void endRequest(uint64_t request);
@@ -192,6 +232,11 @@ private:
     std::unique_ptr<KvTransfer> ticket;
     std::shared_ptr<KvTierSlot> slot;
   };
+  enum class LeafReclaim : uint8_t { Started, Pending, Impossible };
+  LeafReclaim reclaimKvLeaf(uint64_t block);
+  struct Victim { bool kv = false; };
+  std::optional<Victim> reclaimOldest(bool inUse, bool keepResumePoint, bool pagesOnly);
+  bool transfersInFlight() const noexcept { return !demotions_.empty() || !restores_.empty(); }
   Request &request(uint64_t id);
   const Request &request(uint64_t id) const;
   static void changed(Request &r, uint32_t first) noexcept { ++r.revision; r.firstChanged = first; }
@@ -201,6 +246,7 @@ private:
   kv::ExtentStorage &storage_;
   KvTier *tier_;
   PrefixIndex index_;
+  StateCache states_;
   std::unordered_map<uint64_t, Request> requests_;
   std::vector<Transfer> demotions_, restores_;
   CacheSnapshot counters_;

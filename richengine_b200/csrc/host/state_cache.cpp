@@ -1,0 +1,123 @@
+#include "state_cache.hpp"
+
+#include <algorithm>
+#include <stdexcept>
+
+namespace rkb::engine {
+
+StateCache::Class StateCache::classOf(uint64_t block, const State &state) const noexcept {
+  if (inUse(block)) return Class::InUse;
+  return state.checkpoint ? Class::Checkpoint : Class::Ordinary;
+}
+
+void StateCache::publish(uint64_t block, uint64_t bytes, bool checkpoint) {
+  if (!block) throw std::invalid_argument("a composite state sits on a KV block");
+  auto found = states_.find(block);
+  if (found != states_.end()) {
+    State &state = found->second;
+    bytes_ += bytes - state.bytes;
+    state.bytes = bytes;
+    state.checkpoint = state.checkpoint && checkpoint; // an ordinary state stays ordinary
+    state.lastUsed = clock_();
+    return;
+  }
+  // a state in use is reusable: a checkpoint published there is ordinary from the start
+  states_.emplace(block, State{bytes, clock_(), checkpoint && !inUse(block), 0});
+  bytes_ += bytes;
+  adjust_(block, +1, inUse(block) ? +1 : 0);
+}
+
+bool StateCache::ordinary(uint64_t block) const noexcept {
+  auto found = states_.find(block);
+  return found != states_.end() && !found->second.checkpoint;
+}
+uint64_t StateCache::bytes(uint64_t block) const noexcept {
+  auto found = states_.find(block);
+  return found == states_.end() ? 0 : found->second.bytes;
+}
+
+void StateCache::use(uint64_t block) {
+  const bool first = ++uses_[block] == 1;
+  auto found = states_.find(block);
+  if (found == states_.end()) return; // yet to be published: in use from the moment it appears
+  found->second.checkpoint = false;
+  if (first) adjust_(block, 0, +1);
+}
+void StateCache::unuse(uint64_t block) {
+  auto use = uses_.find(block);
+  if (use == uses_.end() || !use->second) throw std::logic_error("the state at this block is not in use");
+  if (--use->second) return;
+  uses_.erase(use);
+  auto found = states_.find(block);
+  if (found == states_.end()) return;
+  found->second.lastUsed = clock_(); // the conversation resumes there next
+  adjust_(block, 0, -1);
+}
+std::vector<uint64_t> StateCache::usedStates() const {
+  std::vector<uint64_t> blocks;
+  for (const auto &[block, count] : uses_)
+    if (count && contains(block)) blocks.push_back(block);
+  std::sort(blocks.begin(), blocks.end());
+  return blocks;
+}
+
+void StateCache::pin(uint64_t block) {
+  auto found = states_.find(block);
+  if (found == states_.end()) throw std::out_of_range("no composite state at this block");
+  ++found->second.pins;
+}
+void StateCache::unpin(uint64_t block) {
+  auto found = states_.find(block);
+  if (found == states_.end() || !found->second.pins) throw std::logic_error("the state at this block is not pinned");
+  --found->second.pins;
+}
+
+uint64_t StateCache::resumePoint() const noexcept {
+  uint64_t best = 0, bestUsed = 0;
+  bool bestOrdinary = false;
+  for (const auto &[block, state] : states_) {
+    if (state.pins || inUse(block)) continue;
+    const bool isOrdinary = !state.checkpoint;
+    if (!best || (isOrdinary && !bestOrdinary) || (isOrdinary == bestOrdinary && state.lastUsed > bestUsed)) {
+      best = block; bestUsed = state.lastUsed; bestOrdinary = isOrdinary;
+    }
+  }
+  return best;
+}
+
+std::optional<StateCandidate> StateCache::oldest(Class wanted, uint64_t withheld) const {
+  std::optional<StateCandidate> best;
+  for (const auto &[block, state] : states_) {
+    if (state.pins || block == withheld || classOf(block, state) != wanted) continue;
+    if (!best || state.lastUsed < best->lastUsed || (state.lastUsed == best->lastUsed && block < best->block))
+      best = StateCandidate{block, state.lastUsed};
+  }
+  return best;
+}
+std::optional<StateCandidate> StateCache::checkpointCandidate(bool keepResumePoint) const {
+  return oldest(Class::Checkpoint, keepResumePoint ? resumePoint() : 0);
+}
+std::optional<StateCandidate> StateCache::ordinaryCandidate(bool keepResumePoint) const {
+  return oldest(Class::Ordinary, keepResumePoint ? resumePoint() : 0);
+}
+std::optional<StateCandidate> StateCache::inUseCandidate() const { return oldest(Class::InUse, 0); }
+
+uint32_t StateCache::evictableStates(bool withInUse) const noexcept {
+  uint32_t count = 0;
+  for (const auto &[block, state] : states_)
+    if (!state.pins && (withInUse || !inUse(block))) ++count;
+  return count;
+}
+
+bool StateCache::reclaim(uint64_t block, uint64_t *freed) {
+  auto found = states_.find(block);
+  if (found == states_.end() || found->second.pins) return false;
+  if (freed) *freed = found->second.bytes;
+  bytes_ -= found->second.bytes;
+  const bool used = inUse(block);
+  states_.erase(found);
+  adjust_(block, -1, used ? -1 : 0);
+  return true;
+}
+
+} // namespace rkb::engine

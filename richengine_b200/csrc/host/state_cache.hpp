@@ -1,0 +1,76 @@
+// state_cache.hpp — composite states attached to KV blocks, and what the reclaim policy needs of them.
+//
+// In the reference a hybrid model's conversation resumes from a "composite state" (target-recurrent + draft-context
+// buffers) published at a complete KV block (runtime/engine/cache/StateCache.hpp:137-379, StateCache.cpp). The KV
+// path itself does not read those buffers; what couples them to it is the reclaim policy: KV that a state restores
+// through is "needed by a state", a state an unfinished request resumes from is "in use" together with the KV
+// above it, disposable checkpoints go before ordinary states, and states in use go last
+// (runtime/engine/cache/Cache.hpp:549-556, Cache.cpp:451-628). This is that subset: states live in RAM only (the
+// reference's disk tier for states, its writers, leases with restore pins and persistence are not rebuilt), a state
+// is a byte count on a block with a class (checkpoint or ordinary), a recency and a use count.
+#pragma once
+
+#include <cstdint>
+#include <functional>
+#include <optional>
+#include <unordered_map>
+#include <vector>
+
+namespace rkb::engine {
+
+struct StateCandidate { uint64_t block = 0; uint64_t lastUsed = 0; };
+
+class StateCache final {
+public:
+  // adjustBelow(block, states, inUse): a state appeared (+1) or went (-1) at `block`, in use or not; the KV index
+  // keeps, per block, how many states (in use) sit strictly below it (KvCache::stateBelow / stateInUseBelow).
+  using AdjustBelow = std::function<void(uint64_t block, int states, int inUse)>;
+  using Clock = std::function<uint64_t()>;
+  StateCache(AdjustBelow adjust, Clock clock) : adjust_(std::move(adjust)), clock_(std::move(clock)) {}
+
+  // Publishes a RAM copy at a block (StateCache::publishCompositeState). A normal boundary upgrades a checkpoint;
+  // a checkpoint cannot downgrade an ordinary state.
+  void publish(uint64_t block, uint64_t bytes, bool checkpoint);
+  bool contains(uint64_t block) const noexcept { return states_.count(block) != 0; }
+  bool ordinary(uint64_t block) const noexcept;
+  uint64_t bytes(uint64_t block) const noexcept;
+  bool stateResident(uint64_t block) const noexcept { return contains(block); } // RAM is the only tier here
+  // An unfinished request resumes from the state at this block, published or yet to be (StateCache::useState):
+  // until every use ends the state is in use, and a checkpoint there becomes ordinary.
+  void use(uint64_t block);
+  void unuse(uint64_t block);
+  bool inUse(uint64_t block) const noexcept { auto f = uses_.find(block); return f != uses_.end() && f->second > 0; }
+  std::vector<uint64_t> usedStates() const;
+  // Pins (a restore in progress): a pinned state is no candidate.
+  void pin(uint64_t block);
+  void unpin(uint64_t block);
+
+  // The oldest unpinned state of each class (StateCache::checkpointCandidate / ordinaryCandidate / inUseCandidate).
+  // keepResumePoint withholds the resume point: the newest unpinned ordinary state, else the newest checkpoint.
+  std::optional<StateCandidate> checkpointCandidate(bool keepResumePoint) const;
+  std::optional<StateCandidate> ordinaryCandidate(bool keepResumePoint) const;
+  std::optional<StateCandidate> inUseCandidate() const;
+  uint64_t resumePoint() const noexcept;
+  uint32_t evictableStates(bool withInUse) const noexcept;
+  // Frees the RAM copy: without a disk tier the state goes (the reference's Unwritten::Drop). False when pinned
+  // or absent. Returns the bytes freed through `freed`.
+  bool reclaim(uint64_t block, uint64_t *freed = nullptr);
+  // The block leaves the KV index: its state goes with it.
+  void forget(uint64_t block) { reclaim(block); uses_.erase(block); }
+  uint64_t residentBytes() const noexcept { return bytes_; }
+  size_t size() const noexcept { return states_.size(); }
+
+private:
+  struct State { uint64_t bytes = 0, lastUsed = 0; bool checkpoint = false; uint32_t pins = 0; };
+  enum class Class { Checkpoint, Ordinary, InUse };
+  Class classOf(uint64_t block, const State &state) const noexcept;
+  std::optional<StateCandidate> oldest(Class wanted, uint64_t withheld) const;
+
+  AdjustBelow adjust_;
+  Clock clock_;
+  std::unordered_map<uint64_t, State> states_;
+  std::unordered_map<uint64_t, uint32_t> uses_;
+  uint64_t bytes_ = 0;
+};
+
+} // namespace rkb::engine

@@ -134,6 +134,32 @@ class Cache:
     def complete_transfer(self, success=True) -> bool: return bool(self._lib.rk_cache_complete_transfer(self._handle, int(success)))
     def fail_next_transfers(self, count): self._lib.rk_cache_fail_next_transfers(self._handle, count)
 
+    # ---- composite states and the reclaim order they impose (engine::StateCache subset, Cache::evictOne) ----
+    def block_at(self, request, tokens) -> int: return self._check(self._lib.rk_cache_block_at(self._handle, request, tokens), "block_at")
+    def publish_state(self, block, size, checkpoint=False): self._check(self._lib.rk_cache_state_publish(self._handle, block, size, int(checkpoint)), "publish_state")
+    def use_state(self, block): self._check(self._lib.rk_cache_state_use(self._handle, block, 1), "use_state")
+    def unuse_state(self, block): self._check(self._lib.rk_cache_state_use(self._handle, block, 0), "unuse_state")
+    def pin_state(self, block): self._check(self._lib.rk_cache_state_pin(self._handle, block, 1), "pin_state")
+    def unpin_state(self, block): self._check(self._lib.rk_cache_state_pin(self._handle, block, 0), "unpin_state")
+
+    def state_info(self, block) -> dict:
+        out = (C.c_uint64 * 6)()
+        self._check(self._lib.rk_cache_state_info(self._handle, block, out), "state_info")
+        return dict(zip(["contains", "ordinary", "in_use", "bytes", "kv_needed", "kv_needed_in_use"], [int(x) for x in out]))
+
+    def state_summary(self) -> dict:
+        out = (C.c_uint64 * 4)()
+        self._check(self._lib.rk_cache_state_summary(self._handle, out), "state_summary")
+        return dict(zip(["states", "bytes", "evictable", "resume_point"], [int(x) for x in out]))
+
+    def evict_one(self, up_to_in_use=True, keep_resume_point=False, pages_only=False) -> dict:
+        out = (C.c_uint64 * 4)()
+        self._check(self._lib.rk_cache_evict_one(self._handle, int(up_to_in_use), int(keep_resume_point), int(pages_only), out), "evict_one")
+        return dict(zip(["progress", "pending", "evicted_state", "state_bytes"], [int(x) for x in out]))
+
+    def reclaim_one_state(self, checkpoints_only=False, for_block=0) -> bool:
+        return bool(self._check(self._lib.rk_cache_reclaim_one_state(self._handle, int(checkpoints_only), for_block), "reclaim_one_state"))
+
     def snapshot(self) -> dict:
         out = (C.c_uint64 * 10)()
         self._lib.rk_cache_snapshot(self._handle, out)

@@ -172,6 +172,14 @@ SIGNATURES = {
     "rk_cache_fail_next_transfers": (None, [vp, u32]),
     "rk_cache_snapshot": (None, [vp, vp]),
     "rk_cache_block_state": (i32, [vp, u64, vp]),
+    "rk_cache_block_at": (i64, [vp, u64, u32]),
+    "rk_cache_state_publish": (i32, [vp, u64, u64, i32]),
+    "rk_cache_state_use": (i32, [vp, u64, i32]),
+    "rk_cache_state_pin": (i32, [vp, u64, i32]),
+    "rk_cache_state_info": (i32, [vp, u64, vp]),
+    "rk_cache_state_summary": (i32, [vp, vp]),
+    "rk_cache_evict_one": (i32, [vp, i32, i32, i32, vp]),
+    "rk_cache_reclaim_one_state": (i32, [vp, i32, u64]),
     "rk_slot_store_open": (vp, [C.c_char_p, C.c_char_p, vp, u32, u32, u64]),
     "rk_slot_store_close": (None, [vp]),
     "rk_slot_store_record_count": (u32, [vp]),

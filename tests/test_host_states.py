@@ -1,0 +1,197 @@
+"""CPU: composite states on KV blocks and the reclaim order they impose (engine::StateCache as far as the KV path is
+coupled to it, Cache::evictOne / reclaimOldest / reclaimOneState: runtime/engine/cache/Cache.cpp:451-628,
+Cache.hpp:549-556). Behaviours follow the reference's facade tests, restated on this repo's handles:
+  dev/tests/engine/kv_first_cache_test.cpp:743-784  a finished request's tail KV goes before its state
+  :882-895, :897-909                                 checkpoints go before older KV; an optional reclaim leaves ordinary states
+  :617-633, :637-652                                 a speculative reclaim keeps the resume point; a checkpoint does not outrank it
+  :654-672                                           a state goes before the KV block under it; a pinned state protects its chain
+and the in-use rule of Cache.cpp:451-487 (states in use and their KV go last, only to running work)."""
+import numpy as np
+import pytest
+
+from richengine_b200.hostplane import GRANTED, Cache, KvPool
+
+
+def make(pages=16, extent=4, tier=Cache.NO_TIER, slots=16, transfers=8):
+    pool = KvPool(pages=pages, bytes_per_page=100, extent_pages=extent, runway_pages=0, budget_pages=pages)
+    return pool, Cache(pool, tier, slots, transfers)
+
+
+def chain(cache, request, prompt, tokens):
+    """Publishes `tokens` tokens of `prompt` for a new request; returns its block ids."""
+    cache.begin_request(request)
+    assert cache.ensure_tokens(request, tokens) == GRANTED
+    cache.publish(request, prompt, tokens)
+    return [cache.block_at(request, 32 * (i + 1)) for i in range(tokens // 32)]
+
+
+PROMPT = np.arange(5000, 5000 + 161, dtype=np.uint32)
+
+
+def test_finished_requests_tail_kv_goes_before_its_state():
+    pool, cache = make()
+    blocks = chain(cache, 1, PROMPT, 128)
+    cache.publish_state(blocks[1], 100)  # the conversation can resume after 64 tokens
+    cache.end_request(1)
+    assert pool.snapshot()["pages_prefix"] == 4 and cache.state_summary()["states"] == 1
+    info = [cache.state_info(b) for b in blocks]
+    assert [i["kv_needed"] for i in info] == [1, 1, 0, 0]  # the state's own block and the block above it
+    for remaining in (3, 2):  # the two tail leaves no state needs go first, the state stays
+        step = cache.evict_one()
+        assert step["progress"] and not step["evicted_state"] and step["state_bytes"] == 0
+        assert pool.snapshot()["pages_prefix"] == remaining and cache.state_summary()["states"] == 1
+    assert len(cache.lookup(PROMPT)) == 2  # what the state resumes through is still matchable
+    step = cache.evict_one()  # now the state's block is the oldest leaf: the state goes first ...
+    assert step["progress"] and step["evicted_state"] and step["state_bytes"] == 100
+    assert cache.state_summary()["states"] == 0 and pool.snapshot()["pages_prefix"] == 2
+    step = cache.evict_one()  # ... then its block
+    assert step["progress"] and not step["evicted_state"] and pool.snapshot()["pages_prefix"] == 1
+    cache.close(); pool.close()
+
+
+def test_checkpoints_go_before_older_kv_and_ordinary_states():
+    pool, cache = make()
+    blocks = chain(cache, 1, PROMPT, 128)
+    cache.publish_state(blocks[0], 150)                  # ordinary, oldest
+    cache.publish_state(blocks[2], 200, checkpoint=True)  # disposable, newer
+    cache.end_request(1)
+    step = cache.evict_one()
+    assert step["progress"] and step["evicted_state"] and step["state_bytes"] == 200  # the checkpoint, although newest
+    assert pool.snapshot()["pages_prefix"] == 4 and cache.state_info(blocks[0])["contains"]
+    # a page scan has no use for a checkpoint's buffers: it takes a dead leaf instead
+    cache.publish_state(blocks[2], 200, checkpoint=True)
+    step = cache.evict_one(pages_only=True)
+    assert step["progress"] and not step["evicted_state"] and pool.snapshot()["pages_prefix"] == 3
+    cache.close(); pool.close()
+
+
+def test_optional_reclaim_leaves_ordinary_states_intact():
+    pool, cache = make()
+    blocks = chain(cache, 1, PROMPT, 128)
+    cache.publish_state(blocks[0], 150)
+    cache.publish_state(blocks[2], 200, checkpoint=True)
+    cache.end_request(1)
+    assert cache.reclaim_one_state(checkpoints_only=True)  # the checkpoint is recycled for the new publication
+    summary = cache.state_summary()
+    assert summary["states"] == 1 and summary["bytes"] == 150
+    assert not cache.reclaim_one_state(checkpoints_only=True)  # nothing disposable is left: the ordinary state stays
+    assert cache.state_summary()["states"] == 1
+    assert cache.reclaim_one_state()                           # a demanded publication takes it
+    assert cache.state_summary()["states"] == 0
+    cache.close(); pool.close()
+
+
+def test_speculative_reclaim_keeps_the_resume_point_and_its_chain():
+    pool, cache = make()
+    blocks = chain(cache, 1, PROMPT, 128)
+    cache.publish_state(blocks[0], 100)
+    cache.publish_state(blocks[2], 100)  # the newest ordinary state: where the conversation resumes next
+    cache.end_request(1)
+    assert cache.state_summary()["resume_point"] == blocks[2]
+    while cache.evict_one(keep_resume_point=True)["progress"]:
+        pass
+    summary = cache.state_summary()
+    assert summary["states"] == 1 and cache.state_info(blocks[2])["contains"]
+    assert pool.snapshot()["pages_prefix"] == 3  # the chain the kept state restores through survives with it
+    assert len(cache.lookup(PROMPT)) == 3
+    while cache.evict_one()["progress"]:         # a demanded shrink reaches the resume point too
+        pass
+    assert cache.state_summary()["states"] == 0 and pool.snapshot()["pages_prefix"] == 0
+    cache.close(); pool.close()
+
+
+def test_a_checkpoint_does_not_outrank_the_resume_point():
+    pool, cache = make()
+    blocks = chain(cache, 1, PROMPT, 128)
+    cache.publish_state(blocks[0], 100)                   # a warmed ordinary state
+    cache.publish_state(blocks[2], 100, checkpoint=True)  # a newer disposable checkpoint
+    cache.end_request(1)
+    step = cache.evict_one(keep_resume_point=True)
+    assert step["progress"] and step["evicted_state"]
+    assert cache.state_info(blocks[0])["contains"] and not cache.state_info(blocks[2])["contains"]
+    cache.close(); pool.close()
+
+
+def test_a_pinned_state_protects_the_kv_it_restores_through():
+    pool, cache = make()
+    blocks = chain(cache, 1, PROMPT, 128)
+    cache.publish_state(blocks[2], 100)
+    cache.end_request(1)
+    cache.pin_state(blocks[2])  # a restore is reading it
+    while cache.evict_one()["progress"]:
+        pass
+    assert pool.snapshot()["pages_prefix"] == 3 and cache.state_summary()["states"] == 1  # only the dead tail leaf went
+    cache.unpin_state(blocks[2])
+    step = cache.evict_one()
+    assert step["evicted_state"] and step["state_bytes"] == 100  # the state first, its block after it
+    assert cache.evict_one()["progress"] and pool.snapshot()["pages_prefix"] == 2
+    cache.close(); pool.close()
+
+
+def test_states_in_use_and_their_kv_go_last_and_only_to_running_work():
+    pool, cache = make(pages=16)
+    other = np.arange(9000, 9000 + 161, dtype=np.uint32)
+    a = chain(cache, 1, PROMPT, 96)
+    b = chain(cache, 2, other, 96)
+    cache.publish_state(a[1], 100)
+    cache.publish_state(b[1], 100)
+    cache.use_state(a[1])  # an unfinished request of conversation A resumes from here
+    cache.end_request(1); cache.end_request(2)
+    assert cache.state_info(a[1])["in_use"] and cache.state_info(a[0])["kv_needed_in_use"] and not cache.state_info(a[2])["kv_needed_in_use"]
+    # an ordinary reclaim takes everything else, oldest first, and stops at what is in use
+    evicted = []
+    while True:
+        step = cache.evict_one(up_to_in_use=False)
+        if not step["progress"]:
+            break
+        evicted.append(step["evicted_state"])
+    assert cache.state_summary()["states"] == 1 and cache.state_info(a[1])["contains"]
+    assert pool.snapshot()["pages_prefix"] == 2  # A's two blocks under the state in use
+    assert len(cache.lookup(PROMPT)) == 2 and cache.lookup(other) == []
+    # running work may take them: the state first, then its chain
+    step = cache.evict_one(up_to_in_use=True)
+    assert step["progress"] and step["evicted_state"]
+    cache.unuse_state(a[1])
+    while cache.evict_one()["progress"]:
+        pass
+    assert pool.snapshot()["pages_prefix"] == 0
+    cache.close(); pool.close()
+
+
+def test_a_use_turns_a_checkpoint_into_an_ordinary_state_and_unuse_refreshes_it():
+    pool, cache = make()
+    blocks = chain(cache, 1, PROMPT, 128)
+    cache.publish_state(blocks[0], 10, checkpoint=True)
+    cache.publish_state(blocks[1], 20)
+    cache.end_request(1)
+    cache.use_state(blocks[0])
+    assert cache.state_info(blocks[0])["ordinary"]  # a state in use is reusable
+    cache.unuse_state(blocks[0])                    # the conversation resumes there next: it is the warmest now
+    assert cache.state_summary()["resume_point"] == blocks[0]
+    with pytest.raises(RuntimeError):
+        cache.unuse_state(blocks[0])
+    with pytest.raises(RuntimeError):
+        cache.publish_state(123456, 10)             # a state needs its KV block in the cache
+    # a boundary republished as ordinary stays ordinary when a checkpoint is offered later
+    cache.publish_state(blocks[1], 25, checkpoint=True)
+    info = cache.state_info(blocks[1])
+    assert info["ordinary"] and info["bytes"] == 25
+    cache.close(); pool.close()
+
+
+def test_with_a_tier_a_needed_leaf_is_demoted_and_its_state_kept_resumable():
+    """With a host tier a leaf a state needs is written out (its page returns when the copy lands); the state above it
+    still finds its chain by lookup, tier blocks included."""
+    pool, cache = make(tier=Cache.MANUAL_TIER)
+    blocks = chain(cache, 1, PROMPT, 128)
+    cache.publish_state(blocks[3], 100)
+    cache.end_request(1)
+    step = cache.evict_one()      # the state at the leaf goes first (its block is the oldest leaf with a state)
+    assert step["evicted_state"]
+    step = cache.evict_one()      # then the leaf: a demotion
+    assert step["progress"] and cache.snapshot()["transfers"] == 1
+    assert pool.snapshot()["pages_prefix"] == 4  # valid until its copy lands
+    assert cache.complete_transfer(True)
+    cache.poll_transfers()
+    assert pool.snapshot()["pages_prefix"] == 3 and len(cache.lookup(PROMPT)) == 4
+    cache.close(); pool.close()
