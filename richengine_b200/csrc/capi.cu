@@ -39,7 +39,8 @@ int cuda_status(cudaError_t error, const char *what) {
 
 int move_pages(uint32_t format, uint32_t layers, uint32_t kv_heads, uint32_t head_dim, uint32_t extent_pages,
                const rk_page_entry *from_entries, const rk_page_entry *to_entries, uint8_t *from_slots,
-               uint8_t *to_slots, uint32_t count, cudaStream_t stream);
+               uint8_t *to_slots, uint32_t count, cudaStream_t stream, rk_page_entry lone_from = 0,
+               rk_page_entry lone_to = 0);
 
 // ---- driver entry points, resolved at run time (the library links no libcuda) ----
 struct DriverApi {
@@ -459,12 +460,14 @@ struct HostTier {
   uint8_t *staging = nullptr; // transfer_limit * slot_bytes, device
   uint32_t *slot_checksums = nullptr;    // pinned: CRC-32C of each slot's payload, taken on the device when it was packed
   uint32_t *arrived_checksums = nullptr; // pinned: CRC-32C of a restored payload after it reached the device, per transfer
-  uint32_t *device_checksums = nullptr;  // device: one word per transfer
-  rk_page_entry *device_entries = nullptr; // device: the page's table entry, one per transfer (no allocation per transfer)
-  rk_page_entry *host_entries = nullptr;   // pinned mirror the entries are copied from
-  // Two streams taken in turn: while one transfer's bytes cross PCIe the next transfer's pack (or unpack) kernel
-  // runs. A stream retires its transfers in issue order, so a poll asks only about the oldest one of each.
-  static constexpr uint32_t kStreams = 2;
+  uint32_t *device_checksums = nullptr;  // device: per transfer a seal's accumulator (zero between launches), then a word for a restore's check
+  uint32_t *device_arrivals = nullptr;   // device: finished parts of a transfer's seal, zero between launches
+  uint32_t *published = nullptr;         // slot_checksums as the device addresses it: a seal stores its checksum there
+  // Streams taken in turn: while one transfer's bytes cross PCIe the next transfers' pack (or unpack) kernels run.
+  // A demotion is one kernel (entry by value, pack + CRC-32C, checksum stored to the pinned word) and one copy; a
+  // restore one copy and one kernel. A stream retires its transfers in issue order, so a poll asks only about the
+  // oldest one of each.
+  static constexpr uint32_t kStreams = 4;
   cudaStream_t streams[kStreams] = {};
   std::deque<uint32_t> order[kStreams];
   uint32_t next_stream = 0;
@@ -497,15 +500,17 @@ extern "C" void *rk_tier_create(void *storage, uint32_t slots, uint32_t transfer
   for (cudaStream_t &stream : t->streams)
     if (cuda_status(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking), "tier stream")) { cudaFree(t->staging); cudaFreeHost(t->host); return nullptr; }
   if (cuda_status(cudaHostAlloc(reinterpret_cast<void **>(&t->slot_checksums), (uint64_t(slots) + transfer_limit) * 4, cudaHostAllocDefault), "tier checksums") ||
-      cuda_status(cudaMalloc(reinterpret_cast<void **>(&t->device_checksums), uint64_t(transfer_limit) * 4), "tier checksums")) {
+      cuda_status(cudaMalloc(reinterpret_cast<void **>(&t->device_checksums), uint64_t(transfer_limit) * 8), "tier checksums")) {
     cudaFreeHost(t->slot_checksums); for (cudaStream_t stream : t->streams) cudaStreamDestroy(stream); cudaFree(t->staging); cudaFreeHost(t->host);
     return nullptr;
   }
   memset(t->slot_checksums, 0, (uint64_t(slots) + transfer_limit) * 4);
   t->arrived_checksums = t->slot_checksums + slots;
-  if (cuda_status(cudaMalloc(reinterpret_cast<void **>(&t->device_entries), uint64_t(transfer_limit) * sizeof(rk_page_entry)), "tier entries") ||
-      cuda_status(cudaHostAlloc(reinterpret_cast<void **>(&t->host_entries), uint64_t(transfer_limit) * sizeof(rk_page_entry), cudaHostAllocDefault), "tier entries")) {
-    cudaFree(t->device_entries); cudaFree(t->device_checksums); cudaFreeHost(t->slot_checksums); for (cudaStream_t stream : t->streams) cudaStreamDestroy(stream);
+  if (cuda_status(cudaMalloc(reinterpret_cast<void **>(&t->device_arrivals), uint64_t(transfer_limit) * 4), "tier counters") ||
+      cuda_status(cudaMemset(t->device_arrivals, 0, uint64_t(transfer_limit) * 4), "tier counters") ||
+      cuda_status(cudaMemset(t->device_checksums, 0, uint64_t(transfer_limit) * 4), "tier checksums") ||
+      cuda_status(cudaHostGetDevicePointer(reinterpret_cast<void **>(&t->published), t->slot_checksums, 0), "tier checksum words")) {
+    cudaFree(t->device_arrivals); cudaFree(t->device_checksums); cudaFreeHost(t->slot_checksums); for (cudaStream_t stream : t->streams) cudaStreamDestroy(stream);
     cudaFree(t->staging); cudaFreeHost(t->host);
     return nullptr;
   }
@@ -521,8 +526,7 @@ extern "C" void rk_tier_destroy(void *tier) {
   for (cudaStream_t stream : t->streams) cudaStreamDestroy(stream);
   cudaFree(t->staging);
   cudaFree(t->device_checksums);
-  cudaFree(t->device_entries);
-  cudaFreeHost(t->host_entries);
+  cudaFree(t->device_arrivals);
   cudaFreeHost(t->slot_checksums);
   cudaFreeHost(t->host);
   delete t;
@@ -596,15 +600,17 @@ int start_transfer(HostTier *t, bool demotion, uint32_t page, uint32_t slot, cud
   uint8_t *stage = t->staging + uint64_t(id) * t->slot_bytes;
   uint8_t *host = t->host + uint64_t(slot) * t->slot_bytes;
   const Storage *s = t->storage;
-  // the page's table entry travels through the transfer's own pinned / device words: nothing is allocated per transfer
-  t->host_entries[id] = s->entry(page);
-  int status = cuda_status(cudaMemcpyAsync(t->device_entries + id, t->host_entries + id, sizeof(rk_page_entry), cudaMemcpyHostToDevice, stream), "tier entry");
-  if (status) return status;
+  // the page's table entry travels in the kernel's arguments: nothing is allocated or copied per transfer
+  const rk_page_entry entry = s->entry(page);
+  int status = kOk;
   if (demotion) {
-    // packed and checksummed in one pass over the page, before the bytes cross PCIe
-    const GatherSource source{t->device_entries + id, s->layers, s->extent_pages, s->data_bytes, s->scale_bytes};
+    // packed and checksummed in one pass over the page, before the bytes cross PCIe; the kernel's last part stores
+    // the checksum to the slot's pinned word
+    GatherSource source{nullptr, s->layers, s->extent_pages, s->data_bytes, s->scale_bytes};
+    source.lone = entry;
+    source.publish = t->published + slot;
+    source.arrivals = t->device_arrivals + id;
     status = launch_crc32c(stage, t->slot_bytes, t->slot_bytes, 1, t->device_checksums + id, 0, stream, &source);
-    if (!status) status = cuda_status(cudaMemcpyAsync(t->slot_checksums + slot, t->device_checksums + id, 4, cudaMemcpyDeviceToHost, stream), "demotion checksum");
     if (!status) status = cuda_status(cudaMemcpyAsync(host, stage, t->slot_bytes, cudaMemcpyDeviceToHost, stream), "demotion copy");
     x.verify = false;
   } else {
@@ -612,10 +618,11 @@ int start_transfer(HostTier *t, bool demotion, uint32_t page, uint32_t slot, cud
     x.verify = t->slot_verify[slot] != 0;
     x.expected = t->slot_expected[slot];
     if (!status && x.verify) { // an adopted slot's first read: check what arrived against its record
-      status = launch_crc32c(stage, t->slot_bytes, t->slot_bytes, 1, t->device_checksums + id, 0, stream, nullptr);
-      if (!status) status = cuda_status(cudaMemcpyAsync(t->arrived_checksums + id, t->device_checksums + id, 4, cudaMemcpyDeviceToHost, stream), "restore checksum");
+      uint32_t *word = t->device_checksums + t->transfer_limit + id;
+      status = launch_crc32c(stage, t->slot_bytes, t->slot_bytes, 1, word, 0, stream, nullptr);
+      if (!status) status = cuda_status(cudaMemcpyAsync(t->arrived_checksums + id, word, 4, cudaMemcpyDeviceToHost, stream), "restore checksum");
     }
-    if (!status) status = move_pages(s->format, s->layers, s->kv_heads, s->head_dim, s->extent_pages, nullptr, t->device_entries + id, stage, nullptr, 1, stream);
+    if (!status) status = move_pages(s->format, s->layers, s->kv_heads, s->head_dim, s->extent_pages, nullptr, nullptr, stage, nullptr, 1, stream, 0, entry);
   }
   if (status) {
     if (demotion) t->writable = false; // a failed write closes the tier to demotions

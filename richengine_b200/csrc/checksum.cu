@@ -83,9 +83,11 @@ const std::vector<uint32_t> &host_tables() {
 // tensor by tensor: the order of a packed slot) and written to `data` on the way, so a page is read once for both
 // its packed copy and its checksum. Every span is a whole number of 512-byte rows.
 struct GatherArgs {
-  const rk_page_entry *entries; // one per payload; null = plain mode
+  const rk_page_entry *entries; // one per payload; null = the lone entry below
   uint32_t extent_pages, data_bytes, scale_bytes;
   uint32_t rows_per_layer, data_rows, scale_rows;
+  rk_page_entry lone;           // a single payload's entry by value
+  uint32_t *publish, *arrivals; // single payload: where the last part stores the checksum, and the count of finished parts
 };
 
 struct ChecksumArgs {
@@ -163,7 +165,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) crc32c_kernel(const __grid_con
     if (rows) {
       const uint4 *source = reinterpret_cast<const uint4 *>(args.data + uint64_t(payload) * args.stride + first_row * kRowBytes) + lane;
       // seal mode: rows come from the page's spans and leave for the packed slot (`source` is then the destination)
-      const rk_page_entry entry = kGather ? args.gather.entries[payload] : 0;
+      const rk_page_entry entry = !kGather ? 0 : args.gather.entries ? args.gather.entries[payload] : args.gather.lone;
       uint32_t layer = kGather ? uint32_t(first_row / args.gather.rows_per_layer) : 0;
       uint32_t q = kGather ? uint32_t(first_row - uint64_t(layer) * args.gather.rows_per_layer) : 0;
       auto load_row = [&](uint32_t row) {
@@ -201,7 +203,17 @@ __global__ void __launch_bounds__(kWarps * 32, 1) crc32c_kernel(const __grid_con
       uint32_t sum = lane < kGroupWarps ? warp_terms[warp + lane] : 0u;
 #pragma unroll
       for (uint32_t o = kGroupWarps / 2; o; o >>= 1) sum ^= __shfl_xor_sync(0xffffffffu, sum, o);
-      if (lane == 0) atomicXor(args.out + payload, part == 0 ? sum ^ args.closing : sum);
+      if (lane == 0) {
+        atomicXor(args.out + payload, part == 0 ? sum ^ args.closing : sum);
+        if (kGather && args.gather.publish) { // the last part hands the checksum over and leaves the words as it found them
+          __threadfence();
+          if (atomicAdd(args.gather.arrivals, 1u) + 1u == args.parts) {
+            __threadfence();
+            *args.gather.publish = atomicExch(args.out + payload, 0u);
+            atomicExch(args.gather.arrivals, 0u);
+          }
+        }
+      }
     }
     asm volatile("bar.sync %0, %1;" ::"r"(1u + group), "r"(kGroupWarps * 32u) : "memory");
   }
@@ -297,15 +309,19 @@ int launch_crc32c(const void *data, uint64_t stride, uint64_t payload_bytes, uin
   args.gather = GatherArgs{};
   if (gather) {
     const uint32_t data_bytes = gather->data_bytes, scale_bytes = gather->scale_bytes;
-    if (!gather->entries || data_bytes % kRowBytes || scale_bytes % kRowBytes || !gather->layers ||
+    if ((!gather->entries && (count != 1 || !gather->lone)) || (gather->publish && (count != 1 || !gather->arrivals)) ||
+        data_bytes % kRowBytes || scale_bytes % kRowBytes || !gather->layers ||
         payload_bytes != uint64_t(gather->layers) * 2 * (uint64_t(data_bytes) + scale_bytes)) {
       set_error("seal: the payload is not a packed page of this pool");
       return kInvalid;
     }
     args.gather = GatherArgs{gather->entries, gather->extent_pages, data_bytes, scale_bytes,
-                             2 * (data_bytes + scale_bytes) / kRowBytes, data_bytes / kRowBytes, scale_bytes / kRowBytes};
+                             2 * (data_bytes + scale_bytes) / kRowBytes, data_bytes / kRowBytes, scale_bytes / kRowBytes,
+                             gather->lone, gather->publish, gather->arrivals};
   }
-  if (int st = cuda_status(cudaMemsetAsync(out, 0, uint64_t(count) * 4, stream), "checksum clear")) return st;
+  // a publishing seal finds its accumulator zero: the launch before it left it so
+  if (!(gather && gather->publish))
+    if (int st = cuda_status(cudaMemsetAsync(out, 0, uint64_t(count) * 4, stream), "checksum clear")) return st;
   const uint32_t grid = uint32_t(std::min<uint64_t>(ctas, (uint64_t(count) * args.parts + kGroups - 1) / kGroups));
   if (gather) crc32c_kernel<true><<<grid, kWarps * 32, kSharedBytes, stream>>>(args);
   else crc32c_kernel<false><<<grid, kWarps * 32, kSharedBytes, stream>>>(args);

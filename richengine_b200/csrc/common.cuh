@@ -23,10 +23,15 @@ void set_error(const char *text);
 int cuda_status(cudaError_t error, const char *what);
 
 // Host-side description of a seal (pack + checksum in one pass): the pages' table entries (device memory) and the
-// pool's span geometry.
+// pool's span geometry. A seal of one page may carry its entry by value (`entries` null, `lone` set) and name a
+// host-visible word the finished checksum is stored to and a device counter of finished parts (zero between
+// launches: the last part to finish stores the checksum and clears both the accumulator and the counter), so one
+// launch replaces a copy of the entry, a clear, the kernel and a copy of the checksum.
 struct GatherSource {
   const rk_page_entry *entries;
   uint32_t layers, extent_pages, data_bytes, scale_bytes;
+  rk_page_entry lone = 0;
+  uint32_t *publish = nullptr, *arrivals = nullptr;
 };
 
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t bits) { return __uint_as_float(bits << 16); }

@@ -61,6 +61,12 @@ constexpr uint32_t kTensorBytes = kKvHeads * kSlabBytes;    // all heads' K (or 
 constexpr uint32_t kScaleBytes = kKvHeads * kPageTokens * 4;
 constexpr uint32_t kStageBytes = 2 * kTensorBytes + 2 * kScaleBytes; // K | V | key scales | value scales
 constexpr uint32_t kMaxLanes = 1024;
+#ifndef RK_SWITCH_PAGES
+#define RK_SWITCH_PAGES 14
+#endif
+// what a lane boundary inside a CTA's range costs, in pages of each kernel's format (a page of bytes takes twice,
+// a bf16 page four times as long to stream as an int4 page)
+constexpr uint32_t kSwitchPages = RK_SWITCH_PAGES, kByteSwitchPages = (RK_SWITCH_PAGES + 1) / 2, kWideSwitchPages = (RK_SWITCH_PAGES + 3) / 4;
 constexpr uint32_t kSpinLimit = 1u << 20; // polls of ~100 ns: a wait gives up after roughly 0.1-0.2 s
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
@@ -111,13 +117,20 @@ __device__ __forceinline__ bool barrier_wait(uint32_t bar, uint32_t parity, uint
   }
   return false;
 }
+// Pages are read once per step: they are marked first to leave L2, so that what is read again (queries, tables,
+// parameters, the partials on their way to the merge) stays.
+__device__ __forceinline__ uint64_t stream_policy() {
+  uint64_t policy;
+  asm("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
 __device__ __forceinline__ void tma_load_rows(uint32_t dst, const CUtensorMap *map, int32_t row, uint32_t bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-               ::"r"(dst), "l"(map), "r"(0), "r"(row), "r"(bar) : "memory");
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
+               ::"r"(dst), "l"(map), "r"(0), "r"(row), "r"(bar), "l"(stream_policy()) : "memory");
 }
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(stream_policy()) : "memory");
 }
 __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                         uint32_t b0, uint32_t b1) {
@@ -189,11 +202,37 @@ __device__ __forceinline__ float load_shared_f32(uint32_t address) {
   return v;
 }
 
-// The CTA that owns flattened page `x` of `total`, for `ctas` equal ranges
-// [b*total/ctas, (b+1)*total/ctas).
-__device__ __forceinline__ uint32_t cta_of(uint64_t x, uint64_t total, uint64_t ctas) {
-  return uint32_t(((x + 1) * ctas - 1) / total);
-}
+// How the flattened pages of all lanes are cut into one range per CTA. A lane boundary inside a range costs its CTA
+// about as much as streaming `pad` pages (the partial of the lane that ends is flushed and the next lane's queries are
+// fetched and laid out while the ring stands still), and a CTA that ends late holds the whole grid back. So the cut is
+// made in a stretched coordinate in which `pad` empty positions follow every lane but the last: page x of lane i
+// sits at x + pad * i, and the stretched line is cut into `ctas` equal ranges [b * length / ctas, (b + 1) * length /
+// ctas). A range that spans a boundary then holds `pad` pages fewer. The cut depends only on the lanes' page counts
+// and the grid, so a step is repeatable bit for bit.
+struct Cut {
+  uint64_t length; // stretched positions
+  uint32_t ctas, pad;
+  __device__ __forceinline__ Cut(uint64_t total_pages, uint32_t ctas_, uint32_t lanes, uint32_t switch_pages) : ctas(ctas_) {
+    // never more than a quarter of a range: short ranges keep their pages
+    pad = lanes > 1 ? uint32_t(min(uint64_t(switch_pages), total_pages / ctas_ / 4)) : 0;
+    length = total_pages + uint64_t(pad) * (lanes - (lanes ? 1 : 0));
+  }
+  // the CTA that owns flattened page `x`, a page of lane `lane`
+  __device__ __forceinline__ uint32_t cta_of(uint64_t x, uint32_t lane) const {
+    return uint32_t(((x + uint64_t(pad) * lane + 1) * ctas - 1) / length);
+  }
+  // the first flattened page of range `range` (the page count for range == ctas); `lane_start[0..lanes]` are the lanes' prefix sums
+  __device__ __forceinline__ uint32_t first_page(uint32_t range, const uint32_t *lane_start, uint32_t lanes) const {
+    const uint64_t position = uint64_t(range) * length / ctas;
+    uint32_t lo = 0, hi = lanes; // largest lane whose stretched start is <= position
+    while (hi - lo > 1) {
+      const uint32_t mid = (lo + hi) / 2;
+      if (lane_start[mid] + uint64_t(pad) * mid <= position) lo = mid; else hi = mid;
+    }
+    const uint64_t within = position - (lane_start[lo] + uint64_t(pad) * lo);
+    return lane_start[lo] + uint32_t(min(within, uint64_t(lane_start[lo + 1] - lane_start[lo])));
+  }
+};
 
 struct Shared {
   uint64_t full[kStages];
@@ -350,12 +389,13 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
   __syncthreads();
   exclusive_scan(sh.lane_start, lanes, sh.scan);
   const uint64_t total_pages = sh.lane_start[lanes];
-  // Never more ranges than pages, so every range a lane spans is non-empty.
+  // Never more ranges than pages, so every range between a lane's first and last is non-empty.
   const uint32_t ctas = uint32_t(min(uint64_t(gridDim.x), total_pages));
   if (cta >= ctas) return;
+  const Cut cut(total_pages, ctas, lanes, kSwitchPages);
   for (uint32_t i = tid; i < lanes; i += kThreads) {
     const uint32_t begin = sh.lane_start[i], end = sh.lane_start[i + 1];
-    sh.segment_base[i] = end > begin ? cta_of(end - 1, total_pages, ctas) - cta_of(begin, total_pages, ctas) + 1 : 0;
+    sh.segment_base[i] = end > begin ? cut.cta_of(end - 1, i) - cut.cta_of(begin, i) + 1 : 0;
   }
   __syncthreads();
   exclusive_scan(sh.segment_base, lanes, sh.scan);
@@ -364,8 +404,8 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
       args.descriptors[2 * i] = sh.segment_base[i];
       args.descriptors[2 * i + 1] = sh.segment_base[i + 1] - sh.segment_base[i];
     }
-  const uint32_t range_begin = uint32_t(uint64_t(cta) * total_pages / ctas);
-  const uint32_t range_end = uint32_t(uint64_t(cta + 1) * total_pages / ctas);
+  const uint32_t range_begin = cut.first_page(cta, sh.lane_start, lanes);
+  const uint32_t range_end = cut.first_page(cta + 1, sh.lane_start, lanes);
   if (tid == 0) {
     for (uint32_t s = 0; s < kStages; ++s) {
       barrier_init(smem_address(&sh.full[s]), 1);
@@ -394,16 +434,28 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
     bool ok = true;
     // the timeout probe withholds the last pages of the range: their consumers must give up, not hang
     const uint32_t issue_limit = (range_end - range_begin) - min(args.withheld, range_end - range_begin);
+    // The table pointer and the first entry of the lane after this one are fetched while this lane streams: under a
+    // saturated memory system each of the two dependent loads takes microseconds, more than the ring holds.
+    const rk_page_entry *upcoming_table = nullptr;
+    rk_page_entry upcoming_first = 0;
+    bool upcoming = false;
     for (uint32_t l = first_lane; ok && unit < issue_limit && l < lanes && sh.lane_start[l] < range_end; ++l) {
       const uint32_t lane_begin = sh.lane_start[l], lane_end = sh.lane_start[l + 1];
       const uint32_t pa = max(range_begin, lane_begin) - lane_begin;
       const uint32_t pb = min(range_end, lane_end) - lane_begin;
       if (pb <= pa || lane_end <= range_begin) continue;
-      const rk_page_entry *table = args.tables[l];
-      rk_page_entry next_entry = table[pa];
+      const rk_page_entry *table = upcoming ? upcoming_table : args.tables[l];
+      rk_page_entry next_entry = upcoming ? upcoming_first : table[pa];
+      // the next lane with pages in this range starts at its page 0
+      uint32_t after = l + 1;
+      while (after < lanes && sh.lane_start[after + 1] == sh.lane_start[after]) ++after;
+      upcoming = after < lanes && sh.lane_start[after] < range_end;
+      if (upcoming) upcoming_table = args.tables[after];
+      const uint32_t fetch_at = pa + min(8u, pb - pa - 1);
       for (uint32_t page = pa; ok && unit < issue_limit && page < pb; ++page, ++unit) {
         const rk_page_entry entry = next_entry;
         if (page + 1 < pb) next_entry = table[page + 1]; // in flight while this page's copies are issued
+        if (upcoming && page == fetch_at) upcoming_first = upcoming_table[0];
         const uint32_t index = rk_entry_index(entry);
         const uint64_t region = rk_entry_extent(entry) + args.layer.offset;
         const uint64_t pages = args.layer.extent_pages;
@@ -627,7 +679,7 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
         l_sum[j] += __shfl_xor_sync(0xffffffffu, l_sum[j], 8);
         l_sum[j] += __shfl_xor_sync(0xffffffffu, l_sum[j], 16);
       }
-      const uint32_t segment = sh.segment_base[l] + (cta - cta_of(lane_begin, total_pages, ctas));
+      const uint32_t segment = sh.segment_base[l] + (cta - cut.cta_of(lane_begin, l));
       const uint64_t slot_index = (uint64_t(segment) * kKvHeads + head) * kPageWarps + residue;
       float *out = args.partials + slot_index * kGroup * kHeadDim;
       float *stats = args.statistics + slot_index * kGroup * 2;
@@ -638,18 +690,39 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
         psum[j] += __shfl_xor_sync(0xffffffffu, psum[j], 8);
         psum[j] += __shfl_xor_sync(0xffffffffu, psum[j], 16);
       }
+      // A lane holds 32 consecutive dimensions (one 128-byte line) of each of its two query heads. Lanes g and g ^ 2
+      // hold neighbouring lines: they swap halves so that every store instruction writes whole 32-byte sectors (a
+      // lane's own 16-byte pieces would leave every sector half written, and the path to L2 counts sectors).
+      const bool upper = (g & 2u) != 0;
+      float *line_low = out + 32 * (r3g & ~1u) + 4 * (upper ? 1u : 0u); // both lanes: the lower line, then the upper one
 #pragma unroll
       for (uint32_t j = 0; j < 2; ++j) {
         const uint32_t query_head = 2 * c + j;
-        if (query_head >= kGroup) continue;
         // accumulators hold 2^-24 * sum(u * w) (x16 for the odd dims), weights carry 2^14: take the +8 out, then 2^24 * 2^-14
         const float offset = psum[j] * 4.76837158203125e-07f; // 8 * 2^-24 * sum of weights
 #pragma unroll
-        for (uint32_t t = 0; t < 16; ++t) {
-          const uint32_t dim = 32 * r3g + 8 * (t >> 2) + 2 * (t & 3u);
-          *reinterpret_cast<float2 *>(out + query_head * kHeadDim + dim) =
-              make_float2((o[t][j] - offset) * 1024.0f, (o[t][2 + j] - 16.0f * offset) * 64.0f);
+        for (uint32_t pair = 0; pair < 4; ++pair) { // 16-byte pieces 2 * pair and 2 * pair + 1 of the lane's line
+          float piece[2][4];
+#pragma unroll
+          for (uint32_t h = 0; h < 2; ++h)
+#pragma unroll
+            for (uint32_t e = 0; e < 2; ++e) {
+              const uint32_t t = 4 * pair + 2 * h + e;
+              piece[h][2 * e] = (o[t][j] - offset) * 1024.0f;
+              piece[h][2 * e + 1] = (o[t][2 + j] - 16.0f * offset) * 64.0f;
+            }
+          float theirs[4]; // the lower lane gives its odd piece away, the upper lane its even piece
+#pragma unroll
+          for (uint32_t e = 0; e < 4; ++e) theirs[e] = __shfl_xor_sync(0xffffffffu, upper ? piece[0][e] : piece[1][e], 8);
+          if (query_head < kGroup) {
+            float *target = line_low + query_head * kHeadDim + 8 * pair;
+            *reinterpret_cast<float4 *>(target) = upper ? make_float4(theirs[0], theirs[1], theirs[2], theirs[3])
+                                                        : make_float4(piece[0][0], piece[0][1], piece[0][2], piece[0][3]);
+            *reinterpret_cast<float4 *>(target + 32) = upper ? make_float4(piece[1][0], piece[1][1], piece[1][2], piece[1][3])
+                                                             : make_float4(theirs[0], theirs[1], theirs[2], theirs[3]);
+          }
         }
+        if (query_head >= kGroup) continue;
         if (g == 0) {
           stats[query_head * 2] = failed ? -INFINITY : m[j] * kLn2;
           stats[query_head * 2 + 1] = failed ? 0.0f : l_sum[j];
@@ -714,12 +787,13 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
   __syncthreads();
   exclusive_scan(sh.lane_start, lanes, sh.scan);
   const uint64_t total_pages = sh.lane_start[lanes];
-  // Never more ranges than pages, so every range a lane spans is non-empty.
+  // Never more ranges than pages, so every range between a lane's first and last is non-empty.
   const uint32_t ctas = uint32_t(min(uint64_t(gridDim.x), total_pages));
   if (cta >= ctas) return;
+  const Cut cut(total_pages, ctas, lanes, kByteSwitchPages);
   for (uint32_t i = tid; i < lanes; i += kThreads) {
     const uint32_t begin = sh.lane_start[i], end = sh.lane_start[i + 1];
-    sh.segment_base[i] = end > begin ? cta_of(end - 1, total_pages, ctas) - cta_of(begin, total_pages, ctas) + 1 : 0;
+    sh.segment_base[i] = end > begin ? cut.cta_of(end - 1, i) - cut.cta_of(begin, i) + 1 : 0;
   }
   __syncthreads();
   exclusive_scan(sh.segment_base, lanes, sh.scan);
@@ -728,8 +802,8 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
       args.descriptors[2 * i] = sh.segment_base[i];
       args.descriptors[2 * i + 1] = sh.segment_base[i + 1] - sh.segment_base[i];
     }
-  const uint32_t range_begin = uint32_t(uint64_t(cta) * total_pages / ctas);
-  const uint32_t range_end = uint32_t(uint64_t(cta + 1) * total_pages / ctas);
+  const uint32_t range_begin = cut.first_page(cta, sh.lane_start, lanes);
+  const uint32_t range_end = cut.first_page(cta + 1, sh.lane_start, lanes);
   if (tid == 0) {
     for (uint32_t s = 0; s < kByteStages; ++s) {
       barrier_init(smem_address(&sh.full[s]), 1);
@@ -980,7 +1054,7 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
         l_sum[j] += __shfl_xor_sync(0xffffffffu, l_sum[j], 8);
         l_sum[j] += __shfl_xor_sync(0xffffffffu, l_sum[j], 16);
       }
-      const uint32_t segment = sh.segment_base[l] + (cta - cta_of(lane_begin, total_pages, ctas));
+      const uint32_t segment = sh.segment_base[l] + (cta - cut.cta_of(lane_begin, l));
       const uint64_t slot_index = (uint64_t(segment) * kKvHeads + head) * kPageWarps + residue;
       float *out = args.partials + slot_index * kGroup * kHeadDim;
       float *stats = args.statistics + slot_index * kGroup * 2;
@@ -1037,12 +1111,13 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
   __syncthreads();
   exclusive_scan(sh.lane_start, lanes, sh.scan);
   const uint64_t total_pages = sh.lane_start[lanes];
-  // Never more ranges than pages, so every range a lane spans is non-empty.
+  // Never more ranges than pages, so every range between a lane's first and last is non-empty.
   const uint32_t ctas = uint32_t(min(uint64_t(gridDim.x), total_pages));
   if (cta >= ctas) return;
+  const Cut cut(total_pages, ctas, lanes, kWideSwitchPages);
   for (uint32_t i = tid; i < lanes; i += kThreads) {
     const uint32_t begin = sh.lane_start[i], end = sh.lane_start[i + 1];
-    sh.segment_base[i] = end > begin ? cta_of(end - 1, total_pages, ctas) - cta_of(begin, total_pages, ctas) + 1 : 0;
+    sh.segment_base[i] = end > begin ? cut.cta_of(end - 1, i) - cut.cta_of(begin, i) + 1 : 0;
   }
   __syncthreads();
   exclusive_scan(sh.segment_base, lanes, sh.scan);
@@ -1051,8 +1126,8 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
       args.descriptors[2 * i] = sh.segment_base[i];
       args.descriptors[2 * i + 1] = sh.segment_base[i + 1] - sh.segment_base[i];
     }
-  const uint32_t range_begin = uint32_t(uint64_t(cta) * total_pages / ctas);
-  const uint32_t range_end = uint32_t(uint64_t(cta + 1) * total_pages / ctas);
+  const uint32_t range_begin = cut.first_page(cta, sh.lane_start, lanes);
+  const uint32_t range_end = cut.first_page(cta + 1, sh.lane_start, lanes);
   if (tid == 0) {
     // A unit is one head's slabs of one page and has one consumer warp. Each warp waits on its own "full" barrier,
     // so it sees every completion of the barrier it waits on (a parity wait cannot tell completions two apart);
@@ -1262,7 +1337,7 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
         l_sum[j] += __shfl_xor_sync(0xffffffffu, l_sum[j], 8);
         l_sum[j] += __shfl_xor_sync(0xffffffffu, l_sum[j], 16);
       }
-      const uint32_t segment = sh.segment_base[l] + (cta - cta_of(lane_begin, total_pages, ctas));
+      const uint32_t segment = sh.segment_base[l] + (cta - cut.cta_of(lane_begin, l));
       const uint64_t slot_index = (uint64_t(segment) * kKvHeads + head) * kPageWarps + residue;
       float *out = args.partials + slot_index * kGroup * kHeadDim;
       float *stats = args.statistics + slot_index * kGroup * 2;

@@ -33,15 +33,17 @@ __device__ __forceinline__ uint8_t *span_pointer(const PageEnd &end, const SpanG
          rk_extent_offset(g.extent_pages, g.data_bytes, g.scale_bytes, layer, tensor, rk_entry_index(end.entry));
 }
 
-// grid (layers * 4, copies); each block moves one span.
+// grid (layers * 4, copies); each block moves one span. A single copy may carry its page entry by value
+// (`lone_from` / `lone_to`) instead of in device memory.
 __global__ void __launch_bounds__(256)
 move_pages_kernel(const rk_page_entry *__restrict__ from_entries, const rk_page_entry *__restrict__ to_entries,
-                  uint8_t *from_slots, uint8_t *to_slots, uint64_t slot_bytes, SpanGeometry g) {
+                  uint8_t *from_slots, uint8_t *to_slots, uint64_t slot_bytes, SpanGeometry g, rk_page_entry lone_from,
+                  rk_page_entry lone_to) {
   const uint32_t layer = blockIdx.x / 4, tensor = blockIdx.x % 4, copy = blockIdx.y;
   const uint32_t bytes = rk_tensor_page_bytes(g.data_bytes, g.scale_bytes, tensor);
   if (!bytes) return;
-  PageEnd from{from_entries ? from_entries[copy] : 0, from_slots ? from_slots + copy * slot_bytes : nullptr};
-  PageEnd to{to_entries ? to_entries[copy] : 0, to_slots ? to_slots + copy * slot_bytes : nullptr};
+  PageEnd from{from_entries ? from_entries[copy] : lone_from, from_slots ? from_slots + copy * slot_bytes : nullptr};
+  PageEnd to{to_entries ? to_entries[copy] : lone_to, to_slots ? to_slots + copy * slot_bytes : nullptr};
   const uint4 *source = reinterpret_cast<const uint4 *>(span_pointer(from, g, layer, tensor));
   uint4 *target = reinterpret_cast<uint4 *>(span_pointer(to, g, layer, tensor));
   for (uint32_t i = threadIdx.x; i < bytes / 16; i += blockDim.x) target[i] = source[i];
@@ -105,10 +107,10 @@ tree_compact_kernel(const rk_page_entry *const *__restrict__ tables, const rk_ch
 
 int move_pages(uint32_t format, uint32_t layers, uint32_t kv_heads, uint32_t head_dim, uint32_t extent_pages,
                const rk_page_entry *from_entries, const rk_page_entry *to_entries, uint8_t *from_slots,
-               uint8_t *to_slots, uint32_t count, cudaStream_t stream) {
+               uint8_t *to_slots, uint32_t count, cudaStream_t stream, rk_page_entry lone_from, rk_page_entry lone_to) {
   if (!count) return kOk;
-  if (!rk_format_valid(format) || !layers || !extent_pages || (!from_entries == !from_slots) ||
-      (!to_entries == !to_slots)) {
+  if (!rk_format_valid(format) || !layers || !extent_pages || ((!from_entries && !lone_from) == !from_slots) ||
+      ((!to_entries && !lone_to) == !to_slots) || ((lone_from || lone_to) && count != 1)) {
     set_error("page move: invalid arguments");
     return kInvalid;
   }
@@ -119,7 +121,7 @@ int move_pages(uint32_t format, uint32_t layers, uint32_t kv_heads, uint32_t hea
     move_pages_kernel<<<dim3(layers * 4, batch), 256, 0, stream>>>(
         from_entries ? from_entries + done : nullptr, to_entries ? to_entries + done : nullptr,
         from_slots ? from_slots + done * slot_bytes : nullptr, to_slots ? to_slots + done * slot_bytes : nullptr,
-        slot_bytes, g);
+        slot_bytes, g, lone_from, lone_to);
     if (int status = cuda_status(cudaGetLastError(), "page move launch")) return status;
     done += batch;
   }
@@ -134,14 +136,14 @@ extern "C" int rk_copy_pages(uint32_t format, uint32_t layers, uint32_t kv_heads
                              uint32_t extent_pages, const rk_page_entry *from_entries,
                              const rk_page_entry *to_entries, uint32_t count, void *stream) {
   return move_pages(format, layers, kv_heads, head_dim, extent_pages, from_entries, to_entries, nullptr, nullptr,
-                    count, static_cast<cudaStream_t>(stream));
+                    count, static_cast<cudaStream_t>(stream), 0, 0);
 }
 
 extern "C" int rk_pack_pages(uint32_t format, uint32_t layers, uint32_t kv_heads, uint32_t head_dim,
                              uint32_t extent_pages, const rk_page_entry *from_entries, void *slots,
                              uint32_t count, void *stream) {
   return move_pages(format, layers, kv_heads, head_dim, extent_pages, from_entries, nullptr, nullptr,
-                    static_cast<uint8_t *>(slots), count, static_cast<cudaStream_t>(stream));
+                    static_cast<uint8_t *>(slots), count, static_cast<cudaStream_t>(stream), 0, 0);
 }
 
 extern "C" int rk_unpack_pages(uint32_t format, uint32_t layers, uint32_t kv_heads, uint32_t head_dim,
@@ -149,7 +151,7 @@ extern "C" int rk_unpack_pages(uint32_t format, uint32_t layers, uint32_t kv_hea
                                uint32_t count, void *stream) {
   return move_pages(format, layers, kv_heads, head_dim, extent_pages, nullptr, to_entries,
                     static_cast<uint8_t *>(const_cast<void *>(slots)), nullptr, count,
-                    static_cast<cudaStream_t>(stream));
+                    static_cast<cudaStream_t>(stream), 0, 0);
 }
 
 extern "C" int rk_tree_compact(uint32_t format, uint32_t kv_heads, uint32_t head_dim, uint32_t lanes,
