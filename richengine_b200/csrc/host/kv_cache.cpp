@@ -35,6 +35,22 @@ const PrefixIndex::Block &PrefixIndex::at(uint64_t block) const {
   return found->second;
 }
 
+void PrefixIndex::refresh(uint64_t block) {
+  auto found = blocks_.find(block);
+  if (found == blocks_.end()) return;
+  Block &entry = found->second;
+  const bool eligible = entry.page != noPage && !entry.residentChildren && !entry.activeUsers && !entry.transferring;
+  if (entry.listed && (!eligible || entry.listedAt != entry.lastUsed)) {
+    idleLeaves_.erase({entry.listedAt, block});
+    entry.listed = false;
+  }
+  if (eligible && !entry.listed) {
+    idleLeaves_.emplace(entry.lastUsed, block);
+    entry.listed = true;
+    entry.listedAt = entry.lastUsed;
+  }
+}
+
 std::optional<PrefixIndex::Match> PrefixIndex::find(uint64_t parent, std::span<const uint32_t> tokens, ImageIdentity images) const {
   if (tokens.size() != pageTokens) return std::nullopt;
   if (parent && !blocks_.count(parent)) return std::nullopt;
@@ -84,18 +100,22 @@ PrefixIndex::Match PrefixIndex::insert(uint64_t parent, std::span<const uint32_t
     Block &above = at(parent);
     ++above.children;
     ++above.residentChildren;
+    refresh(parent);
   }
+  refresh(id);
   return {id, page};
 }
 
-void PrefixIndex::retainActive(uint64_t block) { ++at(block).activeUsers; }
+void PrefixIndex::retainActive(uint64_t block) { ++at(block).activeUsers; refresh(block); }
 void PrefixIndex::releaseActive(uint64_t block) noexcept {
   auto found = blocks_.find(block);
   if (found != blocks_.end() && found->second.activeUsers) --found->second.activeUsers;
+  refresh(block);
 }
 void PrefixIndex::touch(uint64_t block) noexcept {
   auto found = blocks_.find(block);
   if (found != blocks_.end()) found->second.lastUsed = ++clock_;
+  refresh(block);
 }
 
 PrefixIndex::Chain PrefixIndex::chain(uint64_t block) const {
@@ -121,7 +141,9 @@ void PrefixIndex::dropPage(uint64_t block) {
     Block &above = at(entry.parent);
     --above.residentChildren;
     above.lastUsed = std::max(above.lastUsed, entry.lastUsed); // a new leaf is as warm as what it lost
+    refresh(entry.parent);
   }
+  refresh(block);
 }
 
 void PrefixIndex::adoptPage(uint64_t block, uint32_t page) {
@@ -133,7 +155,11 @@ void PrefixIndex::adoptPage(uint64_t block, uint32_t page) {
   entry.page = page;
   blockOnPage_[page] = block;
   ++resident_;
-  if (entry.parent) ++at(entry.parent).residentChildren;
+  if (entry.parent) {
+    ++at(entry.parent).residentChildren;
+    refresh(entry.parent);
+  }
+  refresh(block);
 }
 
 bool PrefixIndex::adoptTierBlock(uint64_t id, uint64_t parent, std::span<const uint32_t> tokens, ImageIdentity images,
@@ -195,11 +221,13 @@ void PrefixIndex::erase(uint64_t block) {
     pool_.releasePage(entry.page, true);
     --resident_;
   }
+  if (entry.listed) idleLeaves_.erase({entry.listedAt, block});
   if (entry.parent) {
     Block &above = at(entry.parent);
     --above.children;
     if (entry.page != noPage) --above.residentChildren;
     above.lastUsed = std::max(above.lastUsed, entry.lastUsed);
+    refresh(entry.parent);
   }
   const auto [first, last] = index_.equal_range(entry.hash);
   for (auto it = first; it != last; ++it)
@@ -208,24 +236,15 @@ void PrefixIndex::erase(uint64_t block) {
 }
 
 std::optional<PrefixIndex::Candidate> PrefixIndex::evictionCandidate() const {
-  std::optional<Candidate> best;
-  for (const auto &[id, entry] : blocks_) {
-    if (entry.page == noPage || entry.residentChildren || entry.activeUsers || entry.transferring) continue;
-    if (!best || entry.lastUsed < best->lastUsed) best = Candidate{id, entry.lastUsed};
-  }
-  return best;
+  if (idleLeaves_.empty()) return std::nullopt;
+  return Candidate{idleLeaves_.begin()->second, idleLeaves_.begin()->first};
 }
 
 std::optional<PrefixIndex::Candidate> PrefixIndex::evictionCandidate(const Candidate *after, const std::function<bool(uint64_t)> &accept) const {
-  std::optional<Candidate> best;
-  for (const auto &[id, entry] : blocks_) {
-    if (entry.page == noPage || entry.residentChildren || entry.activeUsers || entry.transferring) continue;
-    if (after && (entry.lastUsed < after->lastUsed || (entry.lastUsed == after->lastUsed && id <= after->block))) continue;
-    if (best && (entry.lastUsed > best->lastUsed || (entry.lastUsed == best->lastUsed && id > best->block))) continue;
-    if (!accept(id)) continue;
-    best = Candidate{id, entry.lastUsed};
-  }
-  return best;
+  auto next = after ? idleLeaves_.upper_bound({after->lastUsed, after->block}) : idleLeaves_.begin();
+  for (; next != idleLeaves_.end(); ++next)
+    if (accept(next->second)) return Candidate{next->second, next->first};
+  return std::nullopt;
 }
 
 void PrefixIndex::adjustStatesBelow(uint64_t block, int states, int inUse) {

@@ -24,6 +24,7 @@
 #include <cstdint>
 #include <memory>
 #include <optional>
+#include <set>
 #include <span>
 #include <unordered_map>
 #include <vector>
@@ -63,7 +64,7 @@ public:
   bool idle(uint64_t block) const { const Block &b = at(block); return !b.activeUsers && !b.transferring; }
   bool residentLeaf(uint64_t block) const { const Block &b = at(block); return b.page != noPage && !b.residentChildren && !b.activeUsers && !b.transferring; }
   uint64_t lastUsed(uint64_t block) const { return at(block).lastUsed; }
-  void setTransferring(uint64_t block, bool value) { at(block).transferring = value; }
+  void setTransferring(uint64_t block, bool value) { at(block).transferring = value; refresh(block); }
   void setSlot(uint64_t block, std::shared_ptr<KvTierSlot> slot) { at(block).slot = std::move(slot); }
   // Returns the page of a resident leaf that has a tier copy to the pool.
   void dropPage(uint64_t block);
@@ -104,7 +105,11 @@ private:
     uint32_t children = 0, residentChildren = 0, activeUsers = 0;
     uint32_t statesBelow = 0, statesInUseBelow = 0;
     bool transferring = false, poisoned = false;
+    bool listed = false;   // in idleLeaves_ under (listedAt, id)
+    uint64_t listedAt = 0;
   };
+  // Keeps idleLeaves_ in step with a block whose page, children, users, transfer or recency changed.
+  void refresh(uint64_t block);
   Block &at(uint64_t block);
   const Block &at(uint64_t block) const;
 
@@ -112,6 +117,9 @@ private:
   std::unordered_map<uint64_t, Block> blocks_;
   std::unordered_multimap<uint64_t, uint64_t> index_;
   std::vector<uint64_t> blockOnPage_;
+  // The resident leaves no request uses and no transfer touches, oldest first: the order evictions go in. Kept
+  // current by every mutator, so a candidate costs a tree step instead of a pass over every block.
+  std::set<std::pair<uint64_t, uint64_t>> idleLeaves_; // (last used, id)
   uint64_t nextId_ = 1, clock_ = 0;
   uint32_t resident_ = 0;
 };
