@@ -212,10 +212,13 @@ __device__ __forceinline__ float load_shared_f32(uint32_t address) {
 struct Cut {
   uint64_t length; // stretched positions
   uint32_t ctas, pad;
-  __device__ __forceinline__ Cut(uint64_t total_pages, uint32_t ctas_, uint32_t lanes, uint32_t switch_pages) : ctas(ctas_) {
+  __device__ __forceinline__ static Cut make(uint64_t total_pages, uint32_t ctas, uint32_t lanes, uint32_t switch_pages) {
+    Cut cut;
+    cut.ctas = ctas;
     // never more than a quarter of a range: short ranges keep their pages
-    pad = lanes > 1 ? uint32_t(min(uint64_t(switch_pages), total_pages / ctas_ / 4)) : 0;
-    length = total_pages + uint64_t(pad) * (lanes - (lanes ? 1 : 0));
+    cut.pad = lanes > 1 ? uint32_t(min(uint64_t(switch_pages), total_pages / ctas / 4)) : 0;
+    cut.length = total_pages + uint64_t(cut.pad) * (lanes - (lanes ? 1 : 0));
+    return cut;
   }
   // the CTA that owns flattened page `x`, a page of lane `lane`
   __device__ __forceinline__ uint32_t cta_of(uint64_t x, uint32_t lane) const {
@@ -245,6 +248,8 @@ struct Shared {
   uint32_t segment_base[kMaxLanes + 1]; // partial segments before each lane
   uint32_t scan[kThreads / 32 + 1];
   float unit_scales[kScaleBytes / 4 + kPageTokens]; // ones: the scale rows of a format without scales
+  Cut cut;                                          // how the grid's ranges were cut
+  uint32_t range_begin, range_end, first_lane;      // this CTA's flattened pages and the first lane with pages among them
   volatile uint32_t error;
 };
 
@@ -361,6 +366,112 @@ __device__ __forceinline__ void page_softmax(const float (&sacc)[2][2][4], const
 __device__ __forceinline__ void dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void dependents_may_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// The prologue of the three decode kernels: pages per lane -> prefix, the cut, segments per lane -> prefix, this CTA's
+// range. A function of its own (not inlined) so that the kernels' streaming loops are compiled the same whatever
+// changes here: the int4 loop runs at the edge of what the SM issues, and its schedule moved by 2 % with unrelated
+// edits of a prologue compiled into the same body. Every thread of the CTA calls it; an empty range comes back as
+// range_begin == range_end.
+__device__ __noinline__ void cut_ranges(Shared &sh, const DecodeArgs &args, uint32_t switch_pages) {
+  const uint32_t tid = threadIdx.x, lanes = args.lanes, cta = blockIdx.x;
+  for (uint32_t i = tid; i < lanes; i += kThreads) {
+    rk_verify_params p = args.lane_params[i];
+    p.kv = args.layer;
+    const bool valid = rk_verify_contract_valid(&p) && p.active_rows == 1 && p.row_capacity == 1;
+    sh.lane_start[i] = valid ? rk_pages_for(p.committed_tokens + 1) : 0;
+  }
+  if (tid == 0) { sh.error = 0; sh.range_begin = sh.range_end = sh.first_lane = 0; }
+  __syncthreads();
+  exclusive_scan(sh.lane_start, lanes, sh.scan);
+  const uint64_t total_pages = sh.lane_start[lanes];
+  // Never more ranges than pages, so every range between a lane's first and last is non-empty.
+  const uint32_t ctas = uint32_t(min(uint64_t(gridDim.x), total_pages));
+  if (cta >= ctas) return; // the whole CTA: its range stays empty
+  const Cut cut = Cut::make(total_pages, ctas, lanes, switch_pages);
+  for (uint32_t i = tid; i < lanes; i += kThreads) {
+    const uint32_t begin = sh.lane_start[i], end = sh.lane_start[i + 1];
+    sh.segment_base[i] = end > begin ? cut.cta_of(end - 1, i) - cut.cta_of(begin, i) + 1 : 0;
+  }
+  __syncthreads();
+  exclusive_scan(sh.segment_base, lanes, sh.scan);
+  if (cta == 0)
+    for (uint32_t i = tid; i < lanes; i += kThreads) {
+      // a lane with pages gets its descriptor from the CTA that flushes its last segment; a lane without has no segment
+      if (sh.segment_base[i + 1] == sh.segment_base[i]) {
+        args.descriptors[2 * i] = sh.segment_base[i];
+        args.descriptors[2 * i + 1] = 0;
+      }
+    }
+  if (tid == 0) {
+    const uint32_t range_begin = cut.first_page(cta, sh.lane_start, lanes);
+    uint32_t lo = 0, hi = lanes; // first lane whose pages reach into the range: the largest i with lane_start[i] <= range_begin
+    while (hi - lo > 1) {
+      const uint32_t mid = (lo + hi) / 2;
+      if (sh.lane_start[mid] <= range_begin) lo = mid; else hi = mid;
+    }
+    sh.cut = cut;
+    sh.range_begin = range_begin;
+    sh.range_end = cut.first_page(cta + 1, sh.lane_start, lanes);
+    sh.first_lane = lo;
+  }
+  __syncthreads();
+}
+
+// ---- the fold of a CTA's last segment ---------------------------------------------------------------------------
+// When a CTA flushes the last segment of its range no page of it is in flight any more and the ring is free. The
+// twelve consumer warps leave their partials there (the flush's own stores, aimed at the ring) and the three warps
+// of a KV head fold their three page residues into ONE partial: a third of the bytes leave the SM, and the merge reads a third. Every segment of a lane but its
+// last is the last of its CTA (the lane goes on in the next CTA), so a lane's partials are one slot per segment, and
+// three for its last segment when that segment's CTA goes on into the next lane (then the ring is busy); the decode
+// kernel says which in bit 31 of the lane's descriptor.
+constexpr uint32_t kFoldRow = kHeadDim + 4; // a row's floats in the ring: the pad spreads the lanes' stores over all banks
+struct FoldScratch {
+  float rows[kConsumerWarps][kGroup * kFoldRow];
+  float stats[kConsumerWarps][kGroup * 2];
+};
+constexpr uint32_t kConsumersBarrier = 5; // named barriers 1..4 belong to the KV heads' warp triples
+// The three warps of `head` (96 threads, `member` = 32 * residue + lane) fold their rows and store the one partial.
+__device__ __forceinline__ void fold_and_store(const FoldScratch &fold, uint32_t head, uint32_t member, float *out, float *stats) {
+#pragma unroll
+  for (uint32_t i = 0; i < kGroup * (kHeadDim / 4) / (kPageWarps * 32); ++i) {
+    const uint32_t item = member + kPageWarps * 32 * i, query_head = item >> 6, quad = item & 63u;
+    float2 stat[kPageWarps];
+    float maximum = -INFINITY;
+#pragma unroll
+    for (uint32_t r = 0; r < kPageWarps; ++r) {
+      stat[r] = *reinterpret_cast<const float2 *>(&fold.stats[r * kKvHeads + head][query_head * 2]);
+      maximum = fmaxf(maximum, stat[r].x);
+    }
+    float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float denominator = 0.0f;
+#pragma unroll
+    for (uint32_t r = 0; r < kPageWarps; ++r) { // residues in rising order: the same bits every time
+      const float weight = stat[r].x == -INFINITY ? 0.0f : expf(stat[r].x - maximum);
+      const float4 v = *reinterpret_cast<const float4 *>(&fold.rows[r * kKvHeads + head][query_head * kFoldRow + 4 * quad]);
+      sum.x += weight * v.x; sum.y += weight * v.y; sum.z += weight * v.z; sum.w += weight * v.w;
+      denominator += weight * stat[r].y;
+    }
+    *reinterpret_cast<float4 *>(out + query_head * kHeadDim + 4 * quad) = sum;
+    if (quad == 0) { // a failed step left (-inf, 0) in every residue: it stays so
+      stats[query_head * 2] = maximum;
+      stats[query_head * 2 + 1] = denominator;
+    }
+  }
+}
+// A lane's descriptor {first segment, segments | last segment holds three slots << 31} -> its partial slots in order.
+struct LaneSlots {
+  uint32_t first, single, slots; // segments [first, first + single) hold one slot each; then up to three of segment first + single
+  __device__ __forceinline__ explicit LaneSlots(uint2 descriptor) {
+    const uint32_t segments = descriptor.y & 0x7fffffffu, triple = descriptor.y >> 31;
+    first = descriptor.x;
+    single = segments - (segments ? triple : 0u);
+    slots = single + (segments - single) * kPageWarps;
+  }
+  __device__ __forceinline__ uint64_t slot(uint32_t t, uint32_t head) const {
+    return t < single ? (uint64_t(first + t) * kKvHeads + head) * kPageWarps
+                      : (uint64_t(first + single) * kKvHeads + head) * kPageWarps + (t - single);
+  }
+};
+
 __device__ __forceinline__ void group_barrier(uint32_t id, uint32_t threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -378,34 +489,7 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
   dependents_may_launch(); // the merge kernel's blocks may take their places; they wait for this grid to finish
   dependency_wait();       // pages, queries and parameters may come from the kernel before this one
 
-  // ---- partition: pages per lane -> prefix; segments per lane -> prefix -----------------
-  for (uint32_t i = tid; i < lanes; i += kThreads) {
-    rk_verify_params p = args.lane_params[i];
-    p.kv = args.layer;
-    const bool valid = rk_verify_contract_valid(&p) && p.active_rows == 1 && p.row_capacity == 1;
-    sh.lane_start[i] = valid ? rk_pages_for(p.committed_tokens + 1) : 0;
-  }
-  if (tid == 0) sh.error = 0;
-  __syncthreads();
-  exclusive_scan(sh.lane_start, lanes, sh.scan);
-  const uint64_t total_pages = sh.lane_start[lanes];
-  // Never more ranges than pages, so every range between a lane's first and last is non-empty.
-  const uint32_t ctas = uint32_t(min(uint64_t(gridDim.x), total_pages));
-  if (cta >= ctas) return;
-  const Cut cut(total_pages, ctas, lanes, kSwitchPages);
-  for (uint32_t i = tid; i < lanes; i += kThreads) {
-    const uint32_t begin = sh.lane_start[i], end = sh.lane_start[i + 1];
-    sh.segment_base[i] = end > begin ? cut.cta_of(end - 1, i) - cut.cta_of(begin, i) + 1 : 0;
-  }
-  __syncthreads();
-  exclusive_scan(sh.segment_base, lanes, sh.scan);
-  if (cta == 0)
-    for (uint32_t i = tid; i < lanes; i += kThreads) {
-      args.descriptors[2 * i] = sh.segment_base[i];
-      args.descriptors[2 * i + 1] = sh.segment_base[i + 1] - sh.segment_base[i];
-    }
-  const uint32_t range_begin = cut.first_page(cta, sh.lane_start, lanes);
-  const uint32_t range_end = cut.first_page(cta + 1, sh.lane_start, lanes);
+  // ---- barriers, then the partition (the function's barriers publish both) --------------------
   if (tid == 0) {
     for (uint32_t s = 0; s < kStages; ++s) {
       barrier_init(smem_address(&sh.full[s]), 1);
@@ -413,18 +497,10 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  __syncthreads();
+  cut_ranges(sh, args, kSwitchPages);
+  const uint32_t range_begin = sh.range_begin, range_end = sh.range_end, first_lane = sh.first_lane;
   if (range_begin >= range_end) return;
-  // first lane whose pages reach into this range
-  uint32_t first_lane;
-  {
-    uint32_t lo = 0, hi = lanes; // largest i with lane_start[i] <= range_begin
-    while (hi - lo > 1) {
-      const uint32_t mid = (lo + hi) / 2;
-      if (sh.lane_start[mid] <= range_begin) lo = mid; else hi = mid;
-    }
-    first_lane = lo;
-  }
+  const Cut cut = sh.cut;
 
   if (warp >= kConsumerWarps) {
     // ================= producer: one thread streams whole pages =============================
@@ -681,8 +757,17 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
       }
       const uint32_t segment = sh.segment_base[l] + (cta - cut.cta_of(lane_begin, l));
       const uint64_t slot_index = (uint64_t(segment) * kKvHeads + head) * kPageWarps + residue;
-      float *out = args.partials + slot_index * kGroup * kHeadDim;
-      float *stats = args.statistics + slot_index * kGroup * 2;
+      // the CTA's last segment goes to the ring, to be folded there; any other straight to its slot
+      const bool fold_here = range_end <= lane_end;
+      FoldScratch &fold = *reinterpret_cast<FoldScratch *>(dynamic_shared + (ring - smem_address(dynamic_shared)));
+      if (fold_here) group_barrier(kConsumersBarrier, kConsumerWarps * 32); // every consumer warp has read its last page
+      if (warp == 0 && lane == 0 && pb == lane_pages) { // the lane's last segment: its descriptor, with how this segment is stored
+        args.descriptors[2 * l] = sh.segment_base[l];
+        args.descriptors[2 * l + 1] = (sh.segment_base[l + 1] - sh.segment_base[l]) | (fold_here ? 0u : 0x80000000u);
+      }
+      float *out = fold_here ? fold.rows[warp] : args.partials + slot_index * kGroup * kHeadDim;
+      float *stats = fold_here ? fold.stats[warp] : args.statistics + slot_index * kGroup * 2;
+      const uint32_t row_floats = fold_here ? kFoldRow : kHeadDim;
       const bool failed = sh.error != 0;
 #pragma unroll
       for (uint32_t j = 0; j < 2; ++j) {
@@ -715,7 +800,7 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
 #pragma unroll
           for (uint32_t e = 0; e < 4; ++e) theirs[e] = __shfl_xor_sync(0xffffffffu, upper ? piece[0][e] : piece[1][e], 8);
           if (query_head < kGroup) {
-            float *target = line_low + query_head * kHeadDim + 8 * pair;
+            float *target = line_low + query_head * row_floats + 8 * pair;
             *reinterpret_cast<float4 *>(target) = upper ? make_float4(theirs[0], theirs[1], theirs[2], theirs[3])
                                                         : make_float4(piece[0][0], piece[0][1], piece[0][2], piece[0][3]);
             *reinterpret_cast<float4 *>(target + 32) = upper ? make_float4(piece[1][0], piece[1][1], piece[1][2], piece[1][3])
@@ -727,6 +812,11 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
           stats[query_head * 2] = failed ? -INFINITY : m[j] * kLn2;
           stats[query_head * 2 + 1] = failed ? 0.0f : l_sum[j];
         }
+      }
+      if (fold_here) {
+        group_barrier(1 + head, kPageWarps * 32);
+        const uint64_t slot = (uint64_t(segment) * kKvHeads + head) * kPageWarps;
+        fold_and_store(fold, head, residue * 32 + lane, args.partials + slot * kGroup * kHeadDim, args.statistics + slot * kGroup * 2);
       }
     }
   }
@@ -776,34 +866,7 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
   dependents_may_launch(); // the merge kernel's blocks may take their places; they wait for this grid to finish
   dependency_wait();       // pages, queries and parameters may come from the kernel before this one
 
-  // ---- partition: pages per lane -> prefix; segments per lane -> prefix -----------------
-  for (uint32_t i = tid; i < lanes; i += kThreads) {
-    rk_verify_params p = args.lane_params[i];
-    p.kv = args.layer;
-    const bool valid = rk_verify_contract_valid(&p) && p.active_rows == 1 && p.row_capacity == 1;
-    sh.lane_start[i] = valid ? rk_pages_for(p.committed_tokens + 1) : 0;
-  }
-  if (tid == 0) sh.error = 0;
-  __syncthreads();
-  exclusive_scan(sh.lane_start, lanes, sh.scan);
-  const uint64_t total_pages = sh.lane_start[lanes];
-  // Never more ranges than pages, so every range between a lane's first and last is non-empty.
-  const uint32_t ctas = uint32_t(min(uint64_t(gridDim.x), total_pages));
-  if (cta >= ctas) return;
-  const Cut cut(total_pages, ctas, lanes, kByteSwitchPages);
-  for (uint32_t i = tid; i < lanes; i += kThreads) {
-    const uint32_t begin = sh.lane_start[i], end = sh.lane_start[i + 1];
-    sh.segment_base[i] = end > begin ? cut.cta_of(end - 1, i) - cut.cta_of(begin, i) + 1 : 0;
-  }
-  __syncthreads();
-  exclusive_scan(sh.segment_base, lanes, sh.scan);
-  if (cta == 0)
-    for (uint32_t i = tid; i < lanes; i += kThreads) {
-      args.descriptors[2 * i] = sh.segment_base[i];
-      args.descriptors[2 * i + 1] = sh.segment_base[i + 1] - sh.segment_base[i];
-    }
-  const uint32_t range_begin = cut.first_page(cta, sh.lane_start, lanes);
-  const uint32_t range_end = cut.first_page(cta + 1, sh.lane_start, lanes);
+  // ---- barriers, then the partition (the function's barriers publish both) --------------------
   if (tid == 0) {
     for (uint32_t s = 0; s < kByteStages; ++s) {
       barrier_init(smem_address(&sh.full[s]), 1);
@@ -811,18 +874,10 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  __syncthreads();
+  cut_ranges(sh, args, kByteSwitchPages);
+  const uint32_t range_begin = sh.range_begin, range_end = sh.range_end, first_lane = sh.first_lane;
   if (range_begin >= range_end) return;
-  // first lane whose pages reach into this range
-  uint32_t first_lane;
-  {
-    uint32_t lo = 0, hi = lanes; // largest i with lane_start[i] <= range_begin
-    while (hi - lo > 1) {
-      const uint32_t mid = (lo + hi) / 2;
-      if (sh.lane_start[mid] <= range_begin) lo = mid; else hi = mid;
-    }
-    first_lane = lo;
-  }
+  const Cut cut = sh.cut;
 
   if (warp >= kConsumerWarps) {
     // ================= producer: one thread streams whole pages =============================
@@ -1056,8 +1111,17 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
       }
       const uint32_t segment = sh.segment_base[l] + (cta - cut.cta_of(lane_begin, l));
       const uint64_t slot_index = (uint64_t(segment) * kKvHeads + head) * kPageWarps + residue;
-      float *out = args.partials + slot_index * kGroup * kHeadDim;
-      float *stats = args.statistics + slot_index * kGroup * 2;
+      // the CTA's last segment goes to the ring, to be folded there; any other straight to its slot
+      const bool fold_here = range_end <= lane_end;
+      FoldScratch &fold = *reinterpret_cast<FoldScratch *>(dynamic_shared + (ring - smem_address(dynamic_shared)));
+      if (fold_here) group_barrier(kConsumersBarrier, kConsumerWarps * 32); // every consumer warp has read its last page
+      if (warp == 0 && lane == 0 && pb == lane_pages) { // the lane's last segment: its descriptor, with how this segment is stored
+        args.descriptors[2 * l] = sh.segment_base[l];
+        args.descriptors[2 * l + 1] = (sh.segment_base[l + 1] - sh.segment_base[l]) | (fold_here ? 0u : 0x80000000u);
+      }
+      float *out = fold_here ? fold.rows[warp] : args.partials + slot_index * kGroup * kHeadDim;
+      float *stats = fold_here ? fold.stats[warp] : args.statistics + slot_index * kGroup * 2;
+      const uint32_t row_floats = fold_here ? kFoldRow : kHeadDim;
       const float unscale = 6.103515625e-05f; // 2^-14
       const bool failed = sh.error != 0;
 #pragma unroll
@@ -1066,13 +1130,18 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
         if (query_head >= kGroup) continue;
 #pragma unroll
         for (uint32_t t = 0; t < 16; ++t) {
-          out[query_head * kHeadDim + 16 * t + g] = o[t][j] * unscale;
-          out[query_head * kHeadDim + 16 * t + 8 + g] = o[t][2 + j] * unscale;
+          out[query_head * row_floats + 16 * t + g] = o[t][j] * unscale;
+          out[query_head * row_floats + 16 * t + 8 + g] = o[t][2 + j] * unscale;
         }
         if (g == 0) {
           stats[query_head * 2] = failed ? -INFINITY : m[j] * kLn2;
           stats[query_head * 2 + 1] = failed ? 0.0f : l_sum[j];
         }
+      }
+      if (fold_here) {
+        group_barrier(1 + head, kPageWarps * 32);
+        const uint64_t slot = (uint64_t(segment) * kKvHeads + head) * kPageWarps;
+        fold_and_store(fold, head, residue * 32 + lane, args.partials + slot * kGroup * kHeadDim, args.statistics + slot * kGroup * 2);
       }
     }
   }
@@ -1099,35 +1168,7 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
   dependents_may_launch(); // the merge kernel's blocks may take their places; they wait for this grid to finish
   dependency_wait();       // pages, queries and parameters may come from the kernel before this one
 
-  // ---- partition: pages per lane -> prefix; segments per lane -> prefix -----------------
-  for (uint32_t i = tid; i < lanes; i += kThreads) {
-    rk_verify_params p = args.lane_params[i];
-    p.kv = args.layer;
-    const bool valid = rk_verify_contract_valid(&p) && p.active_rows == 1 && p.row_capacity == 1;
-    sh.lane_start[i] = valid ? rk_pages_for(p.committed_tokens + 1) : 0;
-  }
-  if (tid == 0) sh.error = 0;
-  for (uint32_t i = tid; i < sizeof(sh.unit_scales) / sizeof(float); i += kThreads) sh.unit_scales[i] = 1.0f;
-  __syncthreads();
-  exclusive_scan(sh.lane_start, lanes, sh.scan);
-  const uint64_t total_pages = sh.lane_start[lanes];
-  // Never more ranges than pages, so every range between a lane's first and last is non-empty.
-  const uint32_t ctas = uint32_t(min(uint64_t(gridDim.x), total_pages));
-  if (cta >= ctas) return;
-  const Cut cut(total_pages, ctas, lanes, kWideSwitchPages);
-  for (uint32_t i = tid; i < lanes; i += kThreads) {
-    const uint32_t begin = sh.lane_start[i], end = sh.lane_start[i + 1];
-    sh.segment_base[i] = end > begin ? cut.cta_of(end - 1, i) - cut.cta_of(begin, i) + 1 : 0;
-  }
-  __syncthreads();
-  exclusive_scan(sh.segment_base, lanes, sh.scan);
-  if (cta == 0)
-    for (uint32_t i = tid; i < lanes; i += kThreads) {
-      args.descriptors[2 * i] = sh.segment_base[i];
-      args.descriptors[2 * i + 1] = sh.segment_base[i + 1] - sh.segment_base[i];
-    }
-  const uint32_t range_begin = cut.first_page(cta, sh.lane_start, lanes);
-  const uint32_t range_end = cut.first_page(cta + 1, sh.lane_start, lanes);
+  // ---- barriers, then the partition (the function's barriers publish both) --------------------
   if (tid == 0) {
     // A unit is one head's slabs of one page and has one consumer warp. Each warp waits on its own "full" barrier,
     // so it sees every completion of the barrier it waits on (a parity wait cannot tell completions two apart);
@@ -1136,18 +1177,10 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
     for (uint32_t w = 0; w < kConsumerWarps; ++w) barrier_init(smem_address(&sh.warp_full[w]), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  __syncthreads();
+  cut_ranges(sh, args, kWideSwitchPages);
+  const uint32_t range_begin = sh.range_begin, range_end = sh.range_end, first_lane = sh.first_lane;
   if (range_begin >= range_end) return;
-  // first lane whose pages reach into this range
-  uint32_t first_lane;
-  {
-    uint32_t lo = 0, hi = lanes; // largest i with lane_start[i] <= range_begin
-    while (hi - lo > 1) {
-      const uint32_t mid = (lo + hi) / 2;
-      if (sh.lane_start[mid] <= range_begin) lo = mid; else hi = mid;
-    }
-    first_lane = lo;
-  }
+  const Cut cut = sh.cut;
 
   if (warp >= kConsumerWarps) {
     // ================= producer: one thread streams (page, KV head) units of 32 KiB =============
@@ -1339,8 +1372,17 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
       }
       const uint32_t segment = sh.segment_base[l] + (cta - cut.cta_of(lane_begin, l));
       const uint64_t slot_index = (uint64_t(segment) * kKvHeads + head) * kPageWarps + residue;
-      float *out = args.partials + slot_index * kGroup * kHeadDim;
-      float *stats = args.statistics + slot_index * kGroup * 2;
+      // the CTA's last segment goes to the ring, to be folded there; any other straight to its slot
+      const bool fold_here = range_end <= lane_end;
+      FoldScratch &fold = *reinterpret_cast<FoldScratch *>(dynamic_shared + (ring - smem_address(dynamic_shared)));
+      if (fold_here) group_barrier(kConsumersBarrier, kConsumerWarps * 32); // every consumer warp has read its last page
+      if (warp == 0 && lane == 0 && pb == lane_pages) { // the lane's last segment: its descriptor, with how this segment is stored
+        args.descriptors[2 * l] = sh.segment_base[l];
+        args.descriptors[2 * l + 1] = (sh.segment_base[l + 1] - sh.segment_base[l]) | (fold_here ? 0u : 0x80000000u);
+      }
+      float *out = fold_here ? fold.rows[warp] : args.partials + slot_index * kGroup * kHeadDim;
+      float *stats = fold_here ? fold.stats[warp] : args.statistics + slot_index * kGroup * 2;
+      const uint32_t row_floats = fold_here ? kFoldRow : kHeadDim;
       const float unscale = 6.103515625e-05f; // 2^-14
       const bool failed = sh.error != 0;
 #pragma unroll
@@ -1349,20 +1391,26 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
         if (query_head >= kGroup) continue;
 #pragma unroll
         for (uint32_t t = 0; t < 16; ++t) {
-          out[query_head * kHeadDim + 16 * t + g] = o[t][j] * unscale;
-          out[query_head * kHeadDim + 16 * t + 8 + g] = o[t][2 + j] * unscale;
+          out[query_head * row_floats + 16 * t + g] = o[t][j] * unscale;
+          out[query_head * row_floats + 16 * t + 8 + g] = o[t][2 + j] * unscale;
         }
         if (g == 0) {
           stats[query_head * 2] = failed ? -INFINITY : m[j] * kLn2;
           stats[query_head * 2 + 1] = failed ? 0.0f : l_sum[j];
         }
       }
+      if (fold_here) {
+        group_barrier(1 + head, kPageWarps * 32);
+        const uint64_t slot = (uint64_t(segment) * kKvHeads + head) * kPageWarps;
+        fold_and_store(fold, head, residue * 32 + lane, args.partials + slot * kGroup * kHeadDim, args.statistics + slot * kGroup * 2);
+      }
     }
   }
 }
 
 // ---- merge of one (lane, KV head, query head): its partial slots -> {maximum, denominator, numerator} -------------
-// Slot s of a (lane, head) is segment s / 3, warp s % 3. The combination is a fixed function of the slot count
+// The slots of a (lane, head) are one per segment, in segment order, and the three page residues of the lane's last
+// segment when its CTA did not fold them (LaneSlots). The combination is a fixed function of the slot count
 // (same grid, same bits): slot s belongs to slot group s mod G; a group folds its slots in rising order with a
 // running maximum (an online merge: statistics and partial rows of a batch of slots are loaded together, one round
 // trip to L2 per batch instead of one for the statistics and another for the rows); the G group results are then
@@ -1377,12 +1425,13 @@ template <uint32_t kGroups> struct ReduceShared {
 // threads of group 0 (tid < 64); maximum and denominator in shared memory.
 template <uint32_t kGroups>
 __device__ __forceinline__ float4 reduce_slots(const float *__restrict__ partials, const float *__restrict__ statistics,
-                                               uint32_t first, uint32_t segments, uint32_t head, uint32_t query_head,
+                                               uint2 descriptor, uint32_t head, uint32_t query_head,
                                                ReduceShared<kGroups> &sh) {
   constexpr uint32_t kBatch = 8; // slots a thread has in flight at a time
   const uint32_t tid = threadIdx.x, group = tid >> 6, quad = tid & 63u;
-  const uint32_t slots = segments * kPageWarps;
-  auto slot_of = [&](uint32_t t) { return (uint64_t(first + t / kPageWarps) * kKvHeads + head) * kPageWarps + t % kPageWarps; };
+  const LaneSlots lane_slots(descriptor);
+  const uint32_t slots = lane_slots.slots;
+  auto slot_of = [&](uint32_t t) { return lane_slots.slot(t, head); };
   float running = -INFINITY, denominator = 0.0f;
   float4 numerator = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
   for (uint32_t t = group; t < slots; t += kGroups * kBatch) {
@@ -1458,7 +1507,7 @@ decode_reduce_kernel(const float *__restrict__ partials, const float *__restrict
   rk_verify_params p = lane_params[l];
   p.kv = layer;
   if (!rk_verify_contract_valid(&p) || p.active_rows != 1 || p.row_capacity != 1) return;
-  const float4 numerator = reduce_slots<kGroups>(partials, statistics, descriptor.x, descriptor.y, head, query_head, sh);
+  const float4 numerator = reduce_slots<kGroups>(partials, statistics, descriptor, head, query_head, sh);
   const float denominator = sh.denominator;
   if (shard_out) { // this rank's piece of a sequence split: {max, sum, un-normalised output} per query head
     float *triple = shard_out + ((uint64_t(l) * kKvHeads + head) * kGroup + query_head) * (kHeadDim + 2);
@@ -1495,8 +1544,9 @@ decode_reduce_rows_kernel(const float *__restrict__ partials, const float *__res
   rk_verify_params p = lane_params[l];
   p.kv = layer;
   if (!rk_verify_contract_valid(&p) || p.active_rows != 1 || p.row_capacity != 1) return;
-  const uint32_t first = descriptor.x, slots = descriptor.y * kPageWarps;
-  auto slot_of = [&](uint32_t t) { return (uint64_t(first + t / kPageWarps) * kKvHeads + head) * kPageWarps + t % kPageWarps; };
+  const LaneSlots lane_slots(descriptor);
+  const uint32_t slots = lane_slots.slots;
+  auto slot_of = [&](uint32_t t) { return lane_slots.slot(t, head); };
   float running = -INFINITY, denominator = 0.0f;
   float4 numerator = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
   for (uint32_t t = 0; t < slots; t += kBatch) {
@@ -1580,7 +1630,7 @@ shard_exchange_kernel(const float *__restrict__ partials, const float *__restric
   float4 numerator = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
   float maximum = -INFINITY, denominator = 0.0f;
   if (valid) {
-    numerator = reduce_slots<kGroups>(partials, statistics, descriptor.x, descriptor.y, head, query_head, sh);
+    numerator = reduce_slots<kGroups>(partials, statistics, descriptor, head, query_head, sh);
     maximum = sh.maximum;
     denominator = sh.denominator;
   }
