@@ -1177,6 +1177,7 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
     for (uint32_t w = 0; w < kConsumerWarps; ++w) barrier_init(smem_address(&sh.warp_full[w]), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  for (uint32_t i = tid; i < sizeof(sh.unit_scales) / sizeof(float); i += kThreads) sh.unit_scales[i] = 1.0f;
   cut_ranges(sh, args, kWideSwitchPages);
   const uint32_t range_begin = sh.range_begin, range_end = sh.range_end, first_lane = sh.first_lane;
   if (range_begin >= range_end) return;

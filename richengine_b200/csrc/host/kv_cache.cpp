@@ -635,17 +635,25 @@ uint32_t Cache::persist(model::SlotStore &store) {
   if (!tier_) throw std::logic_error("only a cache with a tier keeps copies");
   if (store.slotBytes() < tier_->slotBytes() || store.labelBytes() != sizeof(model::KvBlockLabel))
     throw std::invalid_argument("the slot store was opened for another kind of slot");
-  if (!store.clear()) throw std::runtime_error("the slot store could not be emptied");
+  // The new set is written beside the old one and flushed before the old one is freed: a crash or an IO error part
+  // way leaves the previous seal whole (plus some records of the new one, which adopt() takes or drops one by one).
+  // The new set goes below the old one when it fits there, else above it.
+  const auto copies = index_.tierCopies();
+  const std::set<uint32_t> previous = store.recorded();
+  const uint32_t base = previous.empty() || *previous.begin() >= copies.size() ? 0 : *previous.rbegin() + 1;
   uint32_t written = 0;
-  for (const auto &[label, slot] : index_.tierCopies()) {
+  for (const auto &[label, slot] : copies) {
     KvTier::SlotPayload payload;
     if (!tier_->slotPayload(*slot, &payload)) continue;
     const auto *bytes = static_cast<const uint8_t *>(payload.bytes);
     const auto *raw = reinterpret_cast<const uint8_t *>(&label);
-    if (!store.write(written, {bytes, size_t(payload.size)}, payload.checksum, {raw, sizeof(label)}))
-      throw std::runtime_error("a slot write failed; the slots written so far keep their records");
+    if (!store.write(base + written, {bytes, size_t(payload.size)}, payload.checksum, {raw, sizeof(label)}))
+      throw std::runtime_error("a slot write failed; the previous seal and the slots written so far keep their records");
     ++written;
   }
+  if (!store.synchronize()) throw std::runtime_error("the slot store could not be flushed");
+  for (uint32_t index : previous)
+    if (!store.free(index)) throw std::runtime_error("a slot of the previous seal could not be freed");
   if (!store.synchronize()) throw std::runtime_error("the slot store could not be flushed");
   return written;
 }

@@ -141,7 +141,10 @@ SlotStore::SlotStore(uint64_t slotBytes, const Persistence &persistence) : slotB
       throw std::system_error(errno, std::generic_category(), "read slot records");
     for (uint64_t index = 0; index < records.size() / recordBytes_; ++index) {
       const auto record = std::span<const uint8_t>(records).subspan(index * recordBytes_, recordBytes_);
-      if (auto slot = decodeRecord(record, uint32_t(index), labelBytes_, slotBytes_)) records_.push_back(std::move(*slot));
+      if (auto slot = decodeRecord(record, uint32_t(index), labelBytes_, slotBytes_)) {
+        recorded_.insert(slot->index);
+        records_.push_back(std::move(*slot));
+      }
     }
   } catch (...) {
     if (recordsFile_ >= 0) ::close(recordsFile_);
@@ -165,7 +168,9 @@ bool SlotStore::write(uint32_t index, std::span<const uint8_t> payload, uint32_t
   }
   // The record follows the slot's write: a record never names bytes that were not handed to the file.
   const std::vector<uint8_t> record = encodeRecord(recordBytes_, payload.size(), checksum, label);
-  return writeAll(recordsFile_, record.data(), record.size(), off_t(kRecordsHeaderBytes + uint64_t(index) * recordBytes_));
+  if (!writeAll(recordsFile_, record.data(), record.size(), off_t(kRecordsHeaderBytes + uint64_t(index) * recordBytes_))) return false;
+  recorded_.insert(index);
+  return true;
 }
 
 bool SlotStore::read(uint32_t index, std::span<uint8_t> destination) const {
@@ -182,12 +187,14 @@ bool SlotStore::free(uint32_t index) {
 #ifdef FALLOC_FL_PUNCH_HOLE
   ::fallocate(slots_, FALLOC_FL_PUNCH_HOLE | FALLOC_FL_KEEP_SIZE, off_t(uint64_t(index) * slotBytes_), off_t(slotBytes_)); // best effort
 #endif
+  recorded_.erase(index);
   return true;
 }
 
 bool SlotStore::clear() {
   if (::ftruncate(slots_, 0) < 0 || ::ftruncate(recordsFile_, off_t(kRecordsHeaderBytes)) < 0) return false;
   records_.clear();
+  recorded_.clear();
   return true;
 }
 

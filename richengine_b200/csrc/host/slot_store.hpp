@@ -16,6 +16,7 @@
 #include <array>
 #include <cstdint>
 #include <optional>
+#include <set>
 #include <span>
 #include <string>
 #include <vector>
@@ -68,14 +69,18 @@ public:
   uint32_t labelBytes() const noexcept { return labelBytes_; }
   // The slots an earlier process left, as read when the file opened.
   const std::vector<SlotRecord> &records() const noexcept { return records_; }
-  // Stores the payload from the start of the slot and zeros the rest, then, once that write has landed, the
-  // record. False on an IO failure: the slot then has no record.
+  // Stores the payload from the start of the slot and zeros the rest, then writes the record: a record never names
+  // bytes that were not handed to the file. Only synchronize() makes either durable; a record that reached the
+  // drive without its payload fails the payload checksum when it is adopted. False on an IO failure: the slot then
+  // has no record.
   bool write(uint32_t index, std::span<const uint8_t> payload, uint32_t checksum, std::span<const uint8_t> label);
   bool read(uint32_t index, std::span<uint8_t> destination) const;
   // Clears the slot's record, then returns its blocks to the volume.
   bool free(uint32_t index);
   // Frees every recorded slot: the store is empty afterwards.
   bool clear();
+  // The indices that hold a record now (those found at opening and those written since, minus those freed).
+  const std::set<uint32_t> &recorded() const noexcept { return recorded_; }
   // Flushes slots and records to the drive.
   bool synchronize();
 
@@ -85,6 +90,7 @@ private:
   uint64_t recordBytes_ = 0;
   int slots_ = -1, recordsFile_ = -1;
   std::vector<SlotRecord> records_;
+  std::set<uint32_t> recorded_;
   std::vector<uint8_t> zeros_;
 };
 

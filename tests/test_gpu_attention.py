@@ -125,6 +125,17 @@ def test_prefill_attention(fmt, rows, committed, tensor_core):
     s.close()
 
 
+def reduce_gate_checker():
+    """The CPU restatement of the gate epilogue lives with the other checkers, under oracle/."""
+    import importlib.util
+    from pathlib import Path
+    path = Path(__file__).resolve().parent.parent / "oracle" / "reduce_gate.py"
+    spec = importlib.util.spec_from_file_location("rk_reduce_gate_checker", path)
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    return module
+
+
 @pytest.mark.parametrize("rows,capacity", [(8, 8), (5, 8), (1, 1), (16, 16)])
 def test_reduce_gate_and_gather_epilogue(rows, capacity):
     """The merge that also writes the out-projection's input (decode/paged_attention.metal:273-413): the gather
@@ -145,9 +156,7 @@ def test_reduce_gate_and_gather_epilogue(rows, capacity):
     torch.cuda.synchronize()
     assert np.array_equal(host_u16(out), got16)  # the attention rows are the plain merge's
     merged = got16[:, :, :capacity].transpose(0, 2, 1, 3, 4).reshape(lanes, capacity, 24, 256)  # [lane][row][kv*6+g][D]
-    gate = bf16_to_f32(packed[:, :, : 2 * 24 * 256].reshape(lanes, capacity, 24, 2, 256)[:, :, :, 1, :])
-    sigmoid = (np.float32(1.0) / (np.float32(1.0) + np.exp2(np.float32(-1.44269504089) * gate))).astype(np.float32)
-    want = f32_to_bf16((bf16_to_f32(merged) * sigmoid).astype(np.float32))
+    want = reduce_gate_checker().reduce_gate(merged.astype(np.uint16), packed.astype(np.uint16))  # oracle/reduce_gate.py
     got = host_u16(hidden)
     mismatch = got != want
     assert mismatch.mean() < 2e-3  # exp2 of the two libraries may differ in the last place before the bf16 rounding

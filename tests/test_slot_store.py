@@ -205,3 +205,31 @@ def test_a_broken_chain_and_a_changed_payload_stay_behind(tmp_path):
     store = SlotStore(tmp_path / "slots", tmp_path / "records", b"manual", KV_BLOCK_LABEL_BYTES, 4096)
     assert sorted(int(np.frombuffer(r["label"], dtype="<u8", count=1)[0]) for r in store.records()) == [1, 2]
     store.close()
+
+
+def test_a_second_seal_is_written_beside_the_first_and_frees_it_afterwards(tmp_path):
+    """Cache::persist writes the new set at indices the previous seal does not use, flushes, and only then frees the
+    previous records (the reference frees a slot's record before its blocks: runtime/model/SlotFile.cpp:398-438): at no
+    point do the files hold less than one whole seal. The sets alternate between the bottom of the file and the
+    space above the previous set."""
+    a = tokens(129, 5)
+    pool, cache = make()
+    fill_and_evict(pool, cache, [a])
+    store = SlotStore(tmp_path / "slots", tmp_path / "records", b"manual", KV_BLOCK_LABEL_BYTES, 4096)
+    assert cache.persist(store) == 4
+    store.close()
+    store = SlotStore(tmp_path / "slots", tmp_path / "records", b"manual", KV_BLOCK_LABEL_BYTES, 4096)
+    assert sorted(r["index"] for r in store.records()) == [0, 1, 2, 3]
+    assert cache.persist(store) == 4          # the second seal cannot go below the first: it goes above
+    store.close()
+    store = SlotStore(tmp_path / "slots", tmp_path / "records", b"manual", KV_BLOCK_LABEL_BYTES, 4096)
+    assert sorted(r["index"] for r in store.records()) == [4, 5, 6, 7]
+    assert cache.persist(store) == 4          # the third fits below the second again
+    store.close()
+    store = SlotStore(tmp_path / "slots", tmp_path / "records", b"manual", KV_BLOCK_LABEL_BYTES, 4096)
+    assert sorted(r["index"] for r in store.records()) == [0, 1, 2, 3]
+    cache.close(); pool.close()
+    pool, cache = make()
+    assert cache.adopt(store) == {"blocks": 4, "dropped": 0, "bytes": 400}
+    assert cache.lookup(a) == [1, 2, 3, 4]
+    store.close(); cache.close(); pool.close()
