@@ -40,7 +40,7 @@ KV_HEADS, QUERY_HEADS, HEAD_DIM = 4, 24, 256
 METRIC = "int4_paged_decode_attention_kv_gbps"
 # dram__bytes_read.sum + dram__bytes_write.sum of the decode kernel per algorithmic KV byte, from the ncu
 # capture summarised under profiles/ (a smaller case of the same kernel; traffic grows with the pages read).
-DRAM_BYTES_PER_ALGORITHMIC_BYTE = 1.024
+DRAM_BYTES_PER_ALGORITHMIC_BYTE = 1.013
 TRAFFIC_SOURCE = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of decode_int4_kernel on the 16 x 32768-token case "
                   "(profiles/decode_int4_kernel_ncu_b16_ctx32k.md), scaled by the pages read")
 
