@@ -219,6 +219,27 @@ int rk_stage_decode_rows(uint32_t kv_heads, uint32_t query_heads, uint32_t head_
                          void *stream);
 int rk_gather_decode_rows(uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim, uint32_t lanes,
                           const void *output, void *out, void *stream);
+/* One layer of a decode step with HOST rows, as one call. The reference's host reaches its attention operator with
+ * rows the model runtime produced on the GPU (PagedAttention::addVerify, runtime/ops/PagedAttention.cpp:467-545,
+ * called per layer from runtime/model/QwenTarget.cpp:799-812); a caller that holds the rows in pinned host memory
+ * makes this call instead: q_host [lane][query_head][D], k_host / v_host [lane][kv_head][D] go up, the key / value
+ * rows are appended to the pages (rk_store_verify, row capacity 1), the query row attends (rk_attention_decode) and
+ * out_host [lane][query_head][D] comes back. Asynchronous: uploads run on the session's copy stream one call ahead
+ * of the kernels on `stream`, results leave on a second copy stream behind them; the host buffers must stay
+ * unchanged, and out_host is valid, only after rk_session_finish_host(session, stream) and a synchronise of
+ * `stream`. `tables`, `chunk_params` (chunk_tokens 1, chunk_stride RK_VERIFY_CHUNK_STRIDE) and `verify_params`
+ * (active_rows = row_capacity = 1) are device arrays, one entry per lane, as for the calls it makes. The session owns
+ * its device buffers (one allocation at creation, none per call). rk_session_status reads and clears the sticky
+ * status word of the session's decode scratch (RK_ERR_TIMEOUT when a bounded wait ran out in any step since the
+ * last read). */
+void *rk_session_create(uint32_t format, uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim, uint32_t lanes,
+                        const void *window, const rk_kv_layer *layers, uint32_t layer_count, uint32_t ctas);
+void rk_session_destroy(void *session);
+int rk_session_step_host(void *session, uint32_t layer, const void *q_host, const void *k_host, const void *v_host,
+                         void *out_host, const rk_page_entry *const *tables, const rk_chunk_params *chunk_params,
+                         const rk_verify_params *verify_params, void *stream);
+int rk_session_finish_host(void *session, void *stream);
+int rk_session_status(void *session, void *stream);
 
 /* ---- page moves --------------------------------------------------------------------------------- */
 /* kv::ExtentStorage::copyPages (runtime/ops/PagedKv.hpp:70-75, PageStorage.mm:95-114) on table entries:

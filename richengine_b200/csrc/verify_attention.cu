@@ -372,10 +372,14 @@ template <bool kFloat8> struct ExpandBytes {
     }
   }
   template <uint32_t Team> __device__ static void keys(const uint8_t *raw, uint8_t *k_stage, uint32_t e) {
-    // item = (token, 16-byte chunk c of its 256-byte row): 16 dims -> two operand chunks
+    // item = (token, 16-byte chunk c of its 256-byte row): 16 dims -> two operand chunks. The eight lanes of a
+    // shared-memory phase take chunks c..c+3 of token 2t and chunks (c..c+3) ^ 4 of token 2t + 1: their raw rows differ
+    // by 2 and their chunk sets by bit 2 (eight distinct chunks to read), and their operand rows differ in bit 0
+    // (eight distinct chunks to write).
 #pragma unroll
     for (uint32_t i = 0; i < (1024 + Team - 1) / Team; ++i) {
-      const uint32_t item = e + i * Team, c = item & 15u, token = item >> 4;
+      const uint32_t item = e + i * Team, odd = (item >> 2) & 1u;
+      const uint32_t c = ((item & 3u) | ((item >> 1) & 12u)) ^ (odd << 2), token = ((item >> 5) << 1) | odd;
       if (1024 % Team && item >= 1024) break;
       const uint32_t row = 2 * (token & 31u) + (c >> 3);
       const uint4 x = *reinterpret_cast<const uint4 *>(raw + (token >> 5) * 8192 + swizzled(row, c & 7u));
@@ -388,10 +392,12 @@ template <bool kFloat8> struct ExpandBytes {
     }
   }
   template <uint32_t Team> __device__ static void values(const uint8_t *raw, uint8_t *v_stage, uint32_t e, uint32_t valid) {
-    // item = (page, dim, half h of its 32 tokens): 16 tokens -> two operand chunks of the dim's row
+    // item = (page, dim, half h of its 32 tokens): 16 tokens -> two operand chunks of the dim's row. The eight lanes
+    // of a shared-memory phase take eight consecutive dims of one half: two raw rows whose chunk sets have opposite
+    // parity (eight distinct chunks to read), eight operand rows whose swizzles differ (eight distinct chunks to write).
 #pragma unroll
     for (uint32_t i = 0; i < (1024 + Team - 1) / Team; ++i) {
-      const uint32_t item = e + i * Team, h = item & 1u, dim = (item >> 1) & 255u, page = item >> 9;
+      const uint32_t item = e + i * Team, h = (item >> 3) & 1u, dim = (item & 7u) | ((item >> 1) & 248u), page = item >> 9;
       if (1024 % Team && item >= 1024) break;
       const uint4 x = *reinterpret_cast<const uint4 *>(raw + (2 + page) * 8192 + swizzled(dim >> 2, 2 * (dim & 3u) + h));
       uint32_t out[8];
@@ -427,7 +433,11 @@ template <> struct Expand<RK_FORMAT_BF16> {
   template <uint32_t Team> __device__ static void values(const uint8_t *raw, uint8_t *v_stage, uint32_t e, uint32_t valid) {
 #pragma unroll
     for (uint32_t i = 0; i < (2048 + Team - 1) / Team; ++i) {
-      const uint32_t item = e + i * Team, q = item & 3u, dim = (item >> 2) & 255u, page = item >> 10;
+      // the eight lanes of a shared-memory phase take the four 16-byte pieces of dim d and of dim d ^ 5: raw rows two
+      // apart with the other half of the row (eight distinct chunks to read), operand rows whose swizzles differ in
+      // bit 2 (eight distinct chunks to write)
+      const uint32_t item = e + i * Team, q = item & 3u, flip = (item >> 2) & 1u, page = item >> 10;
+      const uint32_t dim = (((item >> 5) & 31u) << 3) | (flip << 2) | (((item >> 4) & 1u) << 1) | (((item >> 3) & 1u) ^ flip);
       if (2048 % Team && item >= 2048) break;
       uint4 x = *reinterpret_cast<const uint4 *>(raw + (2 + page) * 16384 + swizzled(dim >> 1, 4 * (dim & 1u) + q));
       const uint32_t position = 32 * page + 8 * q;

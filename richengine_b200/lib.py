@@ -99,6 +99,11 @@ SIGNATURES = {
     "rk_attention_decode_probe_timeout": (i32, [vp, C.POINTER(DecodePlan), u32, vp, vp, vp, vp, vp, vp, vp, KvLayer, u32, u32, vp]),
     "rk_stage_decode_rows": (i32, [u32, u32, u32, u32, vp, vp, vp, vp, vp, vp, vp]),
     "rk_gather_decode_rows": (i32, [u32, u32, u32, u32, vp, vp, vp]),
+    "rk_session_create": (vp, [u32, u32, u32, u32, u32, vp, vp, u32, u32]),
+    "rk_session_destroy": (None, [vp]),
+    "rk_session_step_host": (i32, [vp, u32, vp, vp, vp, vp, vp, vp, vp, vp]),
+    "rk_session_finish_host": (i32, [vp, vp]),
+    "rk_session_status": (i32, [vp, vp]),
     # storage
     "rk_storage_create": (vp, [u32, u32, u32, u32, u32, u32]),
     "rk_storage_destroy": (None, [vp]),

@@ -8,9 +8,10 @@ reference's four to any batch width. Two entry points:
   step_device(...)  inputs already staged on the device (what a model runtime calls);
   step_host(...)    compact host rows in pinned memory in, compact host rows out
                     (copies, staging scatter and output gather inside the call).
-step_host calls pipeline: the upload of a call's rows runs on a copy stream while the previous call's kernels run,
-and a call's result goes back on a second copy stream while the next call computes (two sets of row buffers,
-events between the streams). finish_host() makes the compute stream wait for the copies still in flight.
+step_host is one call into the library (rk_session_step_host, include/richkv.h): calls pipeline there — the upload
+of a call's rows runs on a copy stream while the previous call's kernels run, and a call's result goes back on a
+second copy stream while the next call computes. finish_host() makes the compute stream wait for the copies still
+in flight.
 """
 from __future__ import annotations
 
@@ -21,6 +22,12 @@ import torch
 from . import lib, ops
 from .abi import VERIFY_CHUNK_STRIDE, Layout
 from .storage import PageStorage
+
+
+def _stream_handle(stream) -> int:
+    if stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    return stream.cuda_stream if isinstance(stream, torch.cuda.Stream) else int(stream)
 
 
 class DecodeSession:
@@ -35,23 +42,16 @@ class DecodeSession:
         self.output = torch.zeros_like(self.queries)
         self.chunk_keys = torch.zeros((lanes, H, stride, D), dtype=torch.bfloat16, device=device)
         self.chunk_values = torch.zeros((lanes, H, D, stride), dtype=torch.bfloat16, device=device)
-        # two sets of compact rows: one being filled or drained by a copy stream while the other is in use
-        self.q_rows = [torch.zeros((lanes, query_heads, D), dtype=torch.bfloat16, device=device) for _ in range(2)]
-        self.k_rows = [torch.zeros((lanes, H, D), dtype=torch.bfloat16, device=device) for _ in range(2)]
-        self.v_rows = [torch.zeros((lanes, H, D), dtype=torch.bfloat16, device=device) for _ in range(2)]
-        self.out_rows = [torch.zeros((lanes, query_heads, D), dtype=torch.bfloat16, device=device) for _ in range(2)]
-        self.upload_stream, self.download_stream = torch.cuda.Stream(), torch.cuda.Stream()
-        self.uploaded = [torch.cuda.Event() for _ in range(2)]    # the set's rows have arrived
-        self.consumed = [torch.cuda.Event() for _ in range(2)]    # the staging kernel has read the set
-        self.gathered = [torch.cuda.Event() for _ in range(2)]    # the set's output rows are complete
-        self.downloaded = [torch.cuda.Event() for _ in range(2)]  # the set's output rows have left
-        self.host_calls = 0
+        self._c_session, self._ctas = None, ctas  # the host-rows pipeline lives in the library (rk_session_*)
         # every format decodes on its streaming kernel
         self.attention = ops.DecodeAttention(layout, query_heads, lanes, storage.window(), ctas)
         self.layers = storage.layers()
         self.kernel_launches = 0
 
     def close(self):
+        if self._c_session:
+            self._lib.rk_session_destroy(self._c_session)
+            self._c_session = None
         self.attention.close()
 
     def step_device(self, layer: int, table_pointers, chunk_params, verify_params, stream=None) -> None:
@@ -69,47 +69,35 @@ class DecodeSession:
     def step_host(self, layer: int, q_host, k_host, v_host, out_host, table_pointers, chunk_params, verify_params,
                   stream=None) -> None:
         """q_host [lanes][query_heads][D], k_host / v_host [lanes][kv_heads][D], out_host like q_host:
-        pinned bf16 host tensors. Asynchronous; out_host is valid after finish_host() and a synchronise of the stream.
-        The host tensors must stay unchanged until then."""
-        compute = torch.cuda.current_stream() if stream is None else (
-            stream if isinstance(stream, torch.cuda.Stream) else torch.cuda.ExternalStream(int(stream)))
-        s = compute.cuda_stream
-        slot = self.host_calls & 1
-        self.host_calls += 1
-        with torch.cuda.stream(self.upload_stream):
-            self.upload_stream.wait_event(self.consumed[slot])  # the call before last has read this set
-            self.q_rows[slot].copy_(q_host, non_blocking=True)
-            self.k_rows[slot].copy_(k_host, non_blocking=True)
-            self.v_rows[slot].copy_(v_host, non_blocking=True)
-            self.uploaded[slot].record(self.upload_stream)
-        compute.wait_event(self.uploaded[slot])
-        layout = self.layout
-        lib.check(self._lib.rk_stage_decode_rows(layout.kv_heads, self.query_heads, layout.head_dimension, self.lanes,
-                                                 self.q_rows[slot].data_ptr(), self.k_rows[slot].data_ptr(),
-                                                 self.v_rows[slot].data_ptr(), self.queries.data_ptr(),
-                                                 self.chunk_keys.data_ptr(), self.chunk_values.data_ptr(), s),
-                  "rk_stage_decode_rows")
-        self.consumed[slot].record(compute)
-        self.step_device(layer, table_pointers, chunk_params, verify_params, compute)
-        compute.wait_event(self.downloaded[slot])  # the call before last has sent this set's output rows
-        lib.check(self._lib.rk_gather_decode_rows(layout.kv_heads, self.query_heads, layout.head_dimension, self.lanes,
-                                                  self.output.data_ptr(), self.out_rows[slot].data_ptr(), s),
-                  "rk_gather_decode_rows")
-        self.gathered[slot].record(compute)
-        with torch.cuda.stream(self.download_stream):
-            self.download_stream.wait_event(self.gathered[slot])
-            out_host.copy_(self.out_rows[slot], non_blocking=True)
-            self.downloaded[slot].record(self.download_stream)
-        self.kernel_launches += 2
+        pinned bf16 host tensors. One C call (rk_session_step_host: uploads, append, attention, download, all
+        asynchronous); out_host is valid after finish_host() and a synchronise of the stream. The host tensors must
+        stay unchanged until then."""
+        lib.check(self._lib.rk_session_step_host(self._host_session(), layer, q_host.data_ptr(), k_host.data_ptr(),
+                                                 v_host.data_ptr(), out_host.data_ptr(), table_pointers.data_ptr(),
+                                                 chunk_params.data_ptr(), verify_params.data_ptr(), _stream_handle(stream)),
+                  "rk_session_step_host")
+        self.kernel_launches += 5
 
     def finish_host(self, stream=None) -> None:
         """Orders `stream` after every result copy step_host has started: synchronising it then makes out_host valid."""
-        compute = torch.cuda.current_stream() if stream is None else (
-            stream if isinstance(stream, torch.cuda.Stream) else torch.cuda.ExternalStream(int(stream)))
-        for event in self.downloaded:
-            compute.wait_event(event)
+        lib.check(self._lib.rk_session_finish_host(self._host_session(), _stream_handle(stream)), "rk_session_finish_host")
+
+    def host_status(self, stream=None) -> None:
+        """Raises when a bounded wait ran out in any host step since the last call (sticky; cleared by this read)."""
+        lib.check(self._lib.rk_session_status(self._host_session(), _stream_handle(stream)), "rk_session_status")
+
+    def _host_session(self):
+        if self._c_session is None:
+            layers = (lib.KvLayer * len(self.layers))(*self.layers)
+            layout = self.layout
+            self._c_session = self._lib.rk_session_create(layout.format, layout.kv_heads, self.query_heads,
+                                                          layout.head_dimension, self.lanes, self.attention._window,
+                                                          layers, len(self.layers), self._ctas)
+            if not self._c_session:
+                raise lib.RichKvError(lib.INVALID, "rk_session_create")
+        return self._c_session
 
     def host_bytes_per_layer(self) -> tuple[int, int]:
         """(host->device, device->host) bytes one step_host call moves."""
-        h2d = (self.q_rows[0].numel() + self.k_rows[0].numel() + self.v_rows[0].numel()) * 2
-        return h2d, self.out_rows[0].numel() * 2
+        D, H = self.layout.head_dimension, self.layout.kv_heads
+        return self.lanes * (self.query_heads + 2 * H) * D * 2, self.lanes * self.query_heads * D * 2
