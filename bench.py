@@ -1352,19 +1352,29 @@ def run_evict(args):
     # ---- fetch them back on access: requests with the evicted prompts attach their chains ------------------
     t0 = time.perf_counter()
     restored_pages, request_id = 0, 1000
-    for r in range(requests):
-        chain = cache.lookup(prompts[r])
-        if not chain:
-            continue
-        request_id += 1
-        cache.begin_request(request_id)
-        status, _ = cache.attach_prefix(request_id, chain)
-        while status != GRANTED:  # out of pages or transfers for now: retire, then ask again
-            cache.poll_transfers()
-            status, _ = cache.attach_prefix(request_id, chain)
-        while cache.restores_pending(request_id):
-            cache.poll_transfers()
-        cache.end_request(request_id)
+    # Requests arrive as fast as the tier takes them: a request whose chain does not fit the transfers in flight waits
+    # its turn, the others' restores keep the link busy meanwhile (a request is done when none of its restores is pending).
+    waiting = [r for r in range(requests) if cache.lookup(prompts[r])]
+    running, blocked = [], None  # blocked: the request that asked and was told to wait (it asks again, as itself)
+    while waiting or running or blocked:
+        while waiting or blocked:
+            if blocked is None:
+                request_id += 1
+                cache.begin_request(request_id)
+                blocked = (request_id, cache.lookup(prompts[waiting.pop(0)]))
+            status, _ = cache.attach_prefix(*blocked)
+            if status != GRANTED:  # out of pages or transfers for now: retire some, then ask again
+                break
+            running.append(blocked[0])
+            blocked = None
+        cache.poll_transfers()
+        still = []
+        for rid in running:
+            if cache.restores_pending(rid):
+                still.append(rid)
+            else:
+                cache.end_request(rid)
+        running = still
     restore_seconds = time.perf_counter() - t0
     after = cache.snapshot()
     restored_pages = after["restores"]

@@ -39,8 +39,9 @@ int cuda_status(cudaError_t error, const char *what) {
 
 int move_pages(uint32_t format, uint32_t layers, uint32_t kv_heads, uint32_t head_dim, uint32_t extent_pages,
                const rk_page_entry *from_entries, const rk_page_entry *to_entries, uint8_t *from_slots,
-               uint8_t *to_slots, uint32_t count, cudaStream_t stream, rk_page_entry lone_from = 0,
-               rk_page_entry lone_to = 0);
+               uint8_t *to_slots, uint32_t count, cudaStream_t stream);
+int unpack_batch(uint32_t format, uint32_t layers, uint32_t kv_heads, uint32_t head_dim, uint32_t extent_pages,
+                 const PageBatch &batch, uint32_t count, cudaStream_t stream);
 
 // ---- driver entry points, resolved at run time (the library links no libcuda) ----
 struct DriverApi {
@@ -448,6 +449,7 @@ struct Transfer {
   bool verify = false;    // a restore of an adopted slot: its payload must match the record's checksum
   uint32_t expected = 0;
   uint32_t page = 0, slot = 0;
+  uint32_t owner = 0;     // the transfer of its batch whose event marks the batch done
   cudaEvent_t done = nullptr;
 };
 
@@ -457,24 +459,29 @@ struct HostTier {
   uint32_t slots = 0, transfer_limit = 0, demotion_limit = 0, restore_limit = 0;
   uint32_t demotions = 0, restores = 0, in_flight = 0, fail_next = 0;
   uint8_t *host = nullptr;    // slots * slot_bytes, pinned
-  uint8_t *staging = nullptr; // transfer_limit * slot_bytes, device
+  uint8_t *host_mapped = nullptr; // the same arena as the device addresses it (restores read it in place)
+  uint8_t *staging = nullptr; // kStreams * kTierBatch * slot_bytes, device: a batch's packed pages, side by side
   uint32_t *slot_checksums = nullptr;    // pinned: CRC-32C of each slot's payload, taken on the device when it was packed
   uint32_t *arrived_checksums = nullptr; // pinned: CRC-32C of a restored payload after it reached the device, per transfer
-  uint32_t *device_checksums = nullptr;  // device: per transfer a seal's accumulator (zero between launches), then a word for a restore's check
-  uint32_t *device_arrivals = nullptr;   // device: finished parts of a transfer's seal, zero between launches
-  uint32_t *published = nullptr;         // slot_checksums as the device addresses it: a seal stores its checksum there
-  // Streams taken in turn: while one transfer's bytes cross PCIe the next transfers' pack (or unpack) kernels run.
-  // A demotion is one kernel (entry by value, pack + CRC-32C, checksum stored to the pinned word) and one copy; a
-  // restore one copy and one kernel. A stream retires its transfers in issue order, so a poll asks only about the
-  // oldest one of each.
+  uint32_t *device_checksums = nullptr;  // device: per stream and batch position a seal's accumulator (zero between launches), then per transfer a word for a restore's check
+  uint32_t *device_arrivals = nullptr;   // device: per stream and batch position, finished parts of a seal (zero between launches)
+  uint32_t *published = nullptr;         // slot_checksums as the device addresses it: a seal stores its checksums there
+  // Transfers are started in batches: a demotion or restore the cache asks for is queued, and up to kTierBatch of a
+  // kind go out together when the batch is full, at the next poll or at a drain — ONE kernel for the batch (entries,
+  // slots and checksum words in its arguments: pack + CRC-32C in one pass for demotions, unpack for restores), one
+  // copy per page, one event. Streams are taken in turn: while one batch's bytes cross PCIe the next batch's kernel
+  // runs. A stream retires its batches in issue order, so a poll asks only about the oldest one of each.
   static constexpr uint32_t kStreams = 4;
   cudaStream_t streams[kStreams] = {};
   std::deque<uint32_t> order[kStreams];
   uint32_t next_stream = 0;
+  std::vector<uint32_t> pending[2];      // [0] demotions, [1] restores: asked for, not issued yet
+  cudaStream_t pending_after[2] = {};    // the caller's stream each pending batch must follow
   std::vector<uint8_t> slot_used;
+  uint32_t lowest_free = 0;              // no free slot lies below it
   std::vector<uint8_t> slot_verify;      // adopted from an earlier process and not read yet
   std::vector<uint32_t> slot_expected;
-  std::vector<Transfer> transfers; // index = transfer id = staging slot
+  std::vector<Transfer> transfers; // index = transfer id
   bool writable = true;
 };
 
@@ -496,25 +503,29 @@ extern "C" void *rk_tier_create(void *storage, uint32_t slots, uint32_t transfer
   t->slot_expected.assign(slots, 0);
   t->transfers.resize(transfer_limit);
   if (cuda_status(cudaHostAlloc(reinterpret_cast<void **>(&t->host), uint64_t(slots) * t->slot_bytes, cudaHostAllocDefault), "pinned host arena")) return nullptr;
-  if (cuda_status(cudaMalloc(reinterpret_cast<void **>(&t->staging), uint64_t(transfer_limit) * t->slot_bytes), "tier staging")) { cudaFreeHost(t->host); return nullptr; }
+  if (cuda_status(cudaMalloc(reinterpret_cast<void **>(&t->staging), uint64_t(HostTier::kStreams) * kTierBatch * t->slot_bytes), "tier staging")) { cudaFreeHost(t->host); return nullptr; }
   for (cudaStream_t &stream : t->streams)
     if (cuda_status(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking), "tier stream")) { cudaFree(t->staging); cudaFreeHost(t->host); return nullptr; }
   if (cuda_status(cudaHostAlloc(reinterpret_cast<void **>(&t->slot_checksums), (uint64_t(slots) + transfer_limit) * 4, cudaHostAllocDefault), "tier checksums") ||
-      cuda_status(cudaMalloc(reinterpret_cast<void **>(&t->device_checksums), uint64_t(transfer_limit) * 8), "tier checksums")) {
+      cuda_status(cudaMalloc(reinterpret_cast<void **>(&t->device_checksums), (uint64_t(transfer_limit) + HostTier::kStreams * kTierBatch) * 4), "tier checksums")) {
     cudaFreeHost(t->slot_checksums); for (cudaStream_t stream : t->streams) cudaStreamDestroy(stream); cudaFree(t->staging); cudaFreeHost(t->host);
     return nullptr;
   }
   memset(t->slot_checksums, 0, (uint64_t(slots) + transfer_limit) * 4);
   t->arrived_checksums = t->slot_checksums + slots;
-  if (cuda_status(cudaMalloc(reinterpret_cast<void **>(&t->device_arrivals), uint64_t(transfer_limit) * 4), "tier counters") ||
-      cuda_status(cudaMemset(t->device_arrivals, 0, uint64_t(transfer_limit) * 4), "tier counters") ||
-      cuda_status(cudaMemset(t->device_checksums, 0, uint64_t(transfer_limit) * 4), "tier checksums") ||
+  if (cuda_status(cudaMalloc(reinterpret_cast<void **>(&t->device_arrivals), uint64_t(HostTier::kStreams) * kTierBatch * 4), "tier counters") ||
+      cuda_status(cudaMemset(t->device_arrivals, 0, uint64_t(HostTier::kStreams) * kTierBatch * 4), "tier counters") ||
+      cuda_status(cudaMemset(t->device_checksums, 0, (uint64_t(transfer_limit) + HostTier::kStreams * kTierBatch) * 4), "tier checksums") ||
       cuda_status(cudaHostGetDevicePointer(reinterpret_cast<void **>(&t->published), t->slot_checksums, 0), "tier checksum words")) {
     cudaFree(t->device_arrivals); cudaFree(t->device_checksums); cudaFreeHost(t->slot_checksums); for (cudaStream_t stream : t->streams) cudaStreamDestroy(stream);
     cudaFree(t->staging); cudaFreeHost(t->host);
     return nullptr;
   }
   for (Transfer &x : t->transfers) cudaEventCreateWithFlags(&x.done, cudaEventDisableTiming);
+  if (cuda_status(cudaHostGetDevicePointer(reinterpret_cast<void **>(&t->host_mapped), t->host, 0), "pinned host arena")) {
+    rk_tier_destroy(t.release());
+    return nullptr;
+  }
   return t.release();
 }
 
@@ -545,13 +556,15 @@ extern "C" int rk_tier_can_restore(const void *tier) {
 // A free slot id, or -1 when the quota is full.
 extern "C" int64_t rk_tier_acquire_slot(void *tier) {
   auto *t = static_cast<HostTier *>(tier);
-  for (uint32_t i = 0; i < t->slots; ++i)
-    if (!t->slot_used[i]) { t->slot_used[i] = 1; return i; }
+  // the lowest free slot; every slot below `lowest_free` is in use
+  for (uint32_t i = t->lowest_free; i < t->slots; ++i)
+    if (!t->slot_used[i]) { t->slot_used[i] = 1; t->lowest_free = i + 1; return i; }
+  t->lowest_free = t->slots;
   return -1;
 }
 extern "C" void rk_tier_release_slot(void *tier, uint32_t slot) {
   auto *t = static_cast<HostTier *>(tier);
-  if (slot < t->slots) { t->slot_used[slot] = 0; t->slot_verify[slot] = 0; }
+  if (slot < t->slots) { t->slot_used[slot] = 0; t->slot_verify[slot] = 0; t->lowest_free = std::min(t->lowest_free, slot); }
 }
 // CRC-32C of the payload the slot's last completed demotion stored (taken on the device before the copy left).
 extern "C" uint32_t rk_tier_slot_checksum(const void *tier, uint32_t slot) {
@@ -581,6 +594,77 @@ extern "C" const void *rk_tier_slot_host_pointer(const void *tier, uint32_t slot
 }
 
 namespace {
+// Issues the pending transfers of one kind as a batch on the next stream.
+void flush_pending(HostTier *t, uint32_t kind) {
+  std::vector<uint32_t> &members = t->pending[kind];
+  if (members.empty()) return;
+  const bool demotion = kind == 0;
+  // In the order of their host slots, packed side by side in the stream's own staging area: pages whose host slots
+  // are neighbours (the usual case: slots are handed out lowest first) cross PCIe in ONE copy. A copy per page
+  // costs the copy engine about 5 us between copies, a third of what a 540 KB page takes to transfer.
+  std::sort(members.begin(), members.end(), [t](uint32_t a, uint32_t b) { return t->transfers[a].slot < t->transfers[b].slot; });
+  const uint32_t lane = t->next_stream, count = uint32_t(members.size()), owner = members.back();
+  t->next_stream = (lane + 1) % HostTier::kStreams;
+  cudaStream_t stream = t->streams[lane], after = t->pending_after[kind];
+  const Storage *s = t->storage;
+  int status = kOk;
+  if (after) { // order the batch after work already launched on the caller's stream
+    status = cuda_status(cudaEventRecord(t->transfers[owner].done, after), "tier order event");
+    if (!status) status = cuda_status(cudaStreamWaitEvent(stream, t->transfers[owner].done, 0), "tier order wait");
+  }
+  // pages from position i on whose host slots follow one another
+  auto run_from = [&](uint32_t i) {
+    uint32_t n = 1;
+    while (i + n < count && t->transfers[members[i + n]].slot == t->transfers[members[i]].slot + n) ++n;
+    return n;
+  };
+  PageBatch batch{};
+  for (uint32_t i = 0; i < count; ++i) {
+    const Transfer &x = t->transfers[members[i]];
+    batch.entry[i] = s->entry(x.page);
+    batch.slot[i] = t->staging + (uint64_t(lane) * kTierBatch + i) * t->slot_bytes;
+    batch.publish[i] = t->published + x.slot;
+  }
+  if (demotion) {
+    // packed and checksummed in one pass over the pages, before the bytes cross PCIe; the last part of every page
+    // stores its checksum to the slot's pinned word
+    GatherSource source{nullptr, s->layers, s->extent_pages, s->data_bytes, s->scale_bytes};
+    source.batch = &batch;
+    source.arrivals = t->device_arrivals + lane * kTierBatch;
+    if (!status) status = launch_crc32c(nullptr, t->slot_bytes, t->slot_bytes, count, t->device_checksums + lane * kTierBatch, 0, stream, &source);
+    for (uint32_t i = 0; i < count && !status; i += run_from(i))
+      status = cuda_status(cudaMemcpyAsync(t->host + uint64_t(t->transfers[members[i]].slot) * t->slot_bytes, batch.slot[i],
+                                           run_from(i) * t->slot_bytes, cudaMemcpyDeviceToHost, stream), "demotion copy");
+  } else {
+    // A page is unpacked straight out of pinned host memory: the unpack kernel's own loads cross PCIe (thousands in
+    // flight), without a staging copy and the copy engine's set-up per page (a chain's pages rarely sit in neighbouring
+    // host slots, so their copies cannot be merged the way a demotion's are). Only a page adopted from an earlier
+    // process goes through the staging area first: what ARRIVED on the device is checked against its record.
+    for (uint32_t i = 0; i < count && !status; ++i) {
+      const uint32_t id = members[i];
+      const Transfer &x = t->transfers[id];
+      if (!x.verify) {
+        batch.slot[i] = t->host_mapped + uint64_t(x.slot) * t->slot_bytes;
+        continue;
+      }
+      status = cuda_status(cudaMemcpyAsync(batch.slot[i], t->host + uint64_t(x.slot) * t->slot_bytes, t->slot_bytes, cudaMemcpyHostToDevice, stream), "restore copy");
+      uint32_t *word = t->device_checksums + HostTier::kStreams * kTierBatch + id;
+      if (!status) status = launch_crc32c(batch.slot[i], t->slot_bytes, t->slot_bytes, 1, word, 0, stream, nullptr);
+      if (!status) status = cuda_status(cudaMemcpyAsync(t->arrived_checksums + id, word, 4, cudaMemcpyDeviceToHost, stream), "restore checksum");
+    }
+    if (!status) status = unpack_batch(s->format, s->layers, s->kv_heads, s->head_dim, s->extent_pages, batch, count, stream);
+  }
+  if (!status) status = cuda_status(cudaEventRecord(t->transfers[owner].done, stream), "tier completion event");
+  for (uint32_t id : members) {
+    Transfer &x = t->transfers[id];
+    x.owner = owner;
+    if (status) x.forced_failure = true; // the batch did not go out whole: its transfers retire as failed
+    t->order[lane].push_back(id);
+  }
+  if (status && demotion) t->writable = false; // a failed write closes the tier to demotions
+  members.clear();
+}
+
 int start_transfer(HostTier *t, bool demotion, uint32_t page, uint32_t slot, cudaStream_t after) {
   if (demotion ? !rk_tier_can_demote(t) : !rk_tier_can_restore(t)) return kRefused;
   if (slot >= t->slots || !t->slot_used[slot] || !t->storage->page_allocated(page)) {
@@ -590,53 +674,20 @@ int start_transfer(HostTier *t, bool demotion, uint32_t page, uint32_t slot, cud
   uint32_t id = 0;
   while (id < t->transfer_limit && t->transfers[id].in_flight) ++id;
   if (id == t->transfer_limit) return kRefused;
+  const uint32_t kind = demotion ? 0 : 1;
+  if (!t->pending[kind].empty() && t->pending_after[kind] != after) flush_pending(t, kind);
   Transfer &x = t->transfers[id];
-  const uint32_t lane = t->next_stream;
-  cudaStream_t stream = t->streams[lane];
-  if (after) { // order the transfer after work already launched on the caller's stream
-    if (int status = cuda_status(cudaEventRecord(x.done, after), "tier order event")) return status;
-    if (int status = cuda_status(cudaStreamWaitEvent(stream, x.done, 0), "tier order wait")) return status;
-  }
-  uint8_t *stage = t->staging + uint64_t(id) * t->slot_bytes;
-  uint8_t *host = t->host + uint64_t(slot) * t->slot_bytes;
-  const Storage *s = t->storage;
-  // the page's table entry travels in the kernel's arguments: nothing is allocated or copied per transfer
-  const rk_page_entry entry = s->entry(page);
-  int status = kOk;
-  if (demotion) {
-    // packed and checksummed in one pass over the page, before the bytes cross PCIe; the kernel's last part stores
-    // the checksum to the slot's pinned word
-    GatherSource source{nullptr, s->layers, s->extent_pages, s->data_bytes, s->scale_bytes};
-    source.lone = entry;
-    source.publish = t->published + slot;
-    source.arrivals = t->device_arrivals + id;
-    status = launch_crc32c(stage, t->slot_bytes, t->slot_bytes, 1, t->device_checksums + id, 0, stream, &source);
-    if (!status) status = cuda_status(cudaMemcpyAsync(host, stage, t->slot_bytes, cudaMemcpyDeviceToHost, stream), "demotion copy");
-    x.verify = false;
-  } else {
-    status = cuda_status(cudaMemcpyAsync(stage, host, t->slot_bytes, cudaMemcpyHostToDevice, stream), "restore copy");
-    x.verify = t->slot_verify[slot] != 0;
-    x.expected = t->slot_expected[slot];
-    if (!status && x.verify) { // an adopted slot's first read: check what arrived against its record
-      uint32_t *word = t->device_checksums + t->transfer_limit + id;
-      status = launch_crc32c(stage, t->slot_bytes, t->slot_bytes, 1, word, 0, stream, nullptr);
-      if (!status) status = cuda_status(cudaMemcpyAsync(t->arrived_checksums + id, word, 4, cudaMemcpyDeviceToHost, stream), "restore checksum");
-    }
-    if (!status) status = move_pages(s->format, s->layers, s->kv_heads, s->head_dim, s->extent_pages, nullptr, nullptr, stage, nullptr, 1, stream, 0, entry);
-  }
-  if (status) {
-    if (demotion) t->writable = false; // a failed write closes the tier to demotions
-    return status;
-  }
-  if (int s2 = cuda_status(cudaEventRecord(x.done, stream), "tier completion event")) return s2;
   x.demotion = demotion; x.in_flight = true; x.ready = false; x.success = false;
   x.forced_failure = t->fail_next > 0;
   if (t->fail_next) --t->fail_next;
-  x.page = page; x.slot = slot;
-  t->order[lane].push_back(id);
-  t->next_stream = (lane + 1) % HostTier::kStreams;
+  x.page = page; x.slot = slot; x.owner = id;
+  x.verify = !demotion && t->slot_verify[slot] != 0;
+  x.expected = t->slot_expected[slot];
   ++t->in_flight;
   ++(demotion ? t->demotions : t->restores);
+  t->pending_after[kind] = after;
+  t->pending[kind].push_back(id);
+  if (t->pending[kind].size() == kTierBatch) flush_pending(t, kind);
   return int(id);
 }
 } // namespace
@@ -655,10 +706,12 @@ extern "C" int rk_tier_restore(void *tier, uint32_t slot, uint32_t page, void *a
 extern "C" int rk_tier_poll(void *tier) {
   auto *t = static_cast<HostTier *>(tier);
   int retired = 0;
+  flush_pending(t, 0);
+  flush_pending(t, 1);
   for (std::deque<uint32_t> &order : t->order)
-  while (!order.empty()) { // a stream's transfers finish in issue order: the first one still running ends the scan
+  while (!order.empty()) { // a stream's batches finish in issue order: the first one still running ends the scan
     Transfer &x = t->transfers[order.front()];
-    const cudaError_t state = cudaEventQuery(x.done);
+    const cudaError_t state = cudaEventQuery(t->transfers[x.owner].done);
     if (state == cudaErrorNotReady) break;
     order.pop_front();
     x.ready = true;
@@ -688,6 +741,8 @@ extern "C" int rk_tier_transfer_finish(void *tier, uint32_t id) {
 }
 extern "C" int rk_tier_drain(void *tier) {
   auto *t = static_cast<HostTier *>(tier);
+  flush_pending(t, 0);
+  flush_pending(t, 1);
   for (cudaStream_t stream : t->streams)
     if (int status = cuda_status(cudaStreamSynchronize(stream), "tier drain")) return status;
   return rk_tier_poll(tier);

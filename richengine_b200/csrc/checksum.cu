@@ -83,11 +83,11 @@ const std::vector<uint32_t> &host_tables() {
 // tensor by tensor: the order of a packed slot) and written to `data` on the way, so a page is read once for both
 // its packed copy and its checksum. Every span is a whole number of 512-byte rows.
 struct GatherArgs {
-  const rk_page_entry *entries; // one per payload; null = the lone entry below
+  const rk_page_entry *entries; // one per payload; null = the batch below
   uint32_t extent_pages, data_bytes, scale_bytes;
   uint32_t rows_per_layer, data_rows, scale_rows;
-  rk_page_entry lone;           // a single payload's entry by value
-  uint32_t *publish, *arrivals; // single payload: where the last part stores the checksum, and the count of finished parts
+  uint32_t *arrivals;           // batch: finished parts per payload (zero between launches)
+  PageBatch batch;              // entries, destination slots and checksum words by value
 };
 
 struct ChecksumArgs {
@@ -163,9 +163,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1) crc32c_kernel(const __grid_con
     const uint64_t first_row = uint64_t(chunk) * args.rows_low + min(chunk, args.extra);
     uint32_t term = 0;
     if (rows) {
-      const uint4 *source = reinterpret_cast<const uint4 *>(args.data + uint64_t(payload) * args.stride + first_row * kRowBytes) + lane;
       // seal mode: rows come from the page's spans and leave for the packed slot (`source` is then the destination)
-      const rk_page_entry entry = !kGather ? 0 : args.gather.entries ? args.gather.entries[payload] : args.gather.lone;
+      const bool batched = kGather && !args.gather.entries;
+      const uint8_t *base = batched ? args.gather.batch.slot[payload] : args.data + uint64_t(payload) * args.stride;
+      const uint4 *source = reinterpret_cast<const uint4 *>(base + first_row * kRowBytes) + lane;
+      const rk_page_entry entry = !kGather ? 0 : batched ? args.gather.batch.entry[payload] : args.gather.entries[payload];
       uint32_t layer = kGather ? uint32_t(first_row / args.gather.rows_per_layer) : 0;
       uint32_t q = kGather ? uint32_t(first_row - uint64_t(layer) * args.gather.rows_per_layer) : 0;
       auto load_row = [&](uint32_t row) {
@@ -205,12 +207,12 @@ __global__ void __launch_bounds__(kWarps * 32, 1) crc32c_kernel(const __grid_con
       for (uint32_t o = kGroupWarps / 2; o; o >>= 1) sum ^= __shfl_xor_sync(0xffffffffu, sum, o);
       if (lane == 0) {
         atomicXor(args.out + payload, part == 0 ? sum ^ args.closing : sum);
-        if (kGather && args.gather.publish) { // the last part hands the checksum over and leaves the words as it found them
+        if (kGather && !args.gather.entries) { // the payload's last part hands the checksum over and leaves the words as it found them
           __threadfence();
-          if (atomicAdd(args.gather.arrivals, 1u) + 1u == args.parts) {
+          if (atomicAdd(args.gather.arrivals + payload, 1u) + 1u == args.parts) {
             __threadfence();
-            *args.gather.publish = atomicExch(args.out + payload, 0u);
-            atomicExch(args.gather.arrivals, 0u);
+            *args.gather.batch.publish[payload] = atomicExch(args.out + payload, 0u);
+            atomicExch(args.gather.arrivals + payload, 0u);
           }
         }
       }
@@ -251,7 +253,8 @@ uint32_t crc32c_bytes(const uint8_t *data, size_t bytes, uint32_t crc) {
 // (device). `ctas` = 0 takes one CTA per SM. Payloads are whole 512-byte rows (every packed page is).
 int launch_crc32c(const void *data, uint64_t stride, uint64_t payload_bytes, uint32_t count, uint32_t *out, uint32_t ctas,
                   cudaStream_t stream, const GatherSource *gather) {
-  if (!data || !out || !count || !payload_bytes || payload_bytes % kRowBytes || stride < payload_bytes || (stride & 15u) ||
+  const bool batched = gather && !gather->entries;
+  if ((!data && !batched) || !out || !count || !payload_bytes || payload_bytes % kRowBytes || stride < payload_bytes || (stride & 15u) ||
       (reinterpret_cast<uintptr_t>(data) & 15u)) {
     set_error("rk_crc32c_pages: payloads must be whole 512-byte rows, 16-byte aligned");
     return kInvalid;
@@ -309,7 +312,7 @@ int launch_crc32c(const void *data, uint64_t stride, uint64_t payload_bytes, uin
   args.gather = GatherArgs{};
   if (gather) {
     const uint32_t data_bytes = gather->data_bytes, scale_bytes = gather->scale_bytes;
-    if ((!gather->entries && (count != 1 || !gather->lone)) || (gather->publish && (count != 1 || !gather->arrivals)) ||
+    if ((!gather->entries && (!gather->batch || !gather->arrivals || count > kTierBatch)) ||
         data_bytes % kRowBytes || scale_bytes % kRowBytes || !gather->layers ||
         payload_bytes != uint64_t(gather->layers) * 2 * (uint64_t(data_bytes) + scale_bytes)) {
       set_error("seal: the payload is not a packed page of this pool");
@@ -317,10 +320,10 @@ int launch_crc32c(const void *data, uint64_t stride, uint64_t payload_bytes, uin
     }
     args.gather = GatherArgs{gather->entries, gather->extent_pages, data_bytes, scale_bytes,
                              2 * (data_bytes + scale_bytes) / kRowBytes, data_bytes / kRowBytes, scale_bytes / kRowBytes,
-                             gather->lone, gather->publish, gather->arrivals};
+                             gather->arrivals, gather->entries ? PageBatch{} : *gather->batch};
   }
-  // a publishing seal finds its accumulator zero: the launch before it left it so
-  if (!(gather && gather->publish))
+  // a batched seal finds its accumulators zero: the launch before it left them so
+  if (!(gather && !gather->entries))
     if (int st = cuda_status(cudaMemsetAsync(out, 0, uint64_t(count) * 4, stream), "checksum clear")) return st;
   const uint32_t grid = uint32_t(std::min<uint64_t>(ctas, (uint64_t(count) * args.parts + kGroups - 1) / kGroups));
   if (gather) crc32c_kernel<true><<<grid, kWarps * 32, kSharedBytes, stream>>>(args);

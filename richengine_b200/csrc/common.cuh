@@ -22,16 +22,25 @@ constexpr int kTimeout = -5;     // a bounded device wait ran out
 void set_error(const char *text);
 int cuda_status(cudaError_t error, const char *what);
 
+// Pages of one host-tier batch, carried in a kernel's arguments: nothing is copied or allocated per transfer.
+constexpr uint32_t kTierBatch = 16;
+struct PageBatch {
+  rk_page_entry entry[kTierBatch]; // the pages' table entries
+  uint8_t *slot[kTierBatch];       // their packed device slots
+  uint32_t *publish[kTierBatch];   // seal only: the host-visible word each checksum is stored to
+};
+
 // Host-side description of a seal (pack + checksum in one pass): the pages' table entries (device memory) and the
-// pool's span geometry. A seal of one page may carry its entry by value (`entries` null, `lone` set) and name a
-// host-visible word the finished checksum is stored to and a device counter of finished parts (zero between
-// launches: the last part to finish stores the checksum and clears both the accumulator and the counter), so one
-// launch replaces a copy of the entry, a clear, the kernel and a copy of the checksum.
+// pool's span geometry. A seal for the host tier carries its pages in `batch` instead (`entries` null): every payload
+// has its own destination slot and a host-visible word its finished checksum is stored to; `arrivals` and the
+// accumulators are device words, one per payload, that are zero between launches (the last part of a payload to
+// finish stores the checksum and clears both), so one launch replaces a copy of the entries, a clear, the kernel and
+// the copies of the checksums.
 struct GatherSource {
   const rk_page_entry *entries;
   uint32_t layers, extent_pages, data_bytes, scale_bytes;
-  rk_page_entry lone = 0;
-  uint32_t *publish = nullptr, *arrivals = nullptr;
+  const PageBatch *batch = nullptr;
+  uint32_t *arrivals = nullptr;
 };
 
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t bits) { return __uint_as_float(bits << 16); }

@@ -33,19 +33,28 @@ __device__ __forceinline__ uint8_t *span_pointer(const PageEnd &end, const SpanG
          rk_extent_offset(g.extent_pages, g.data_bytes, g.scale_bytes, layer, tensor, rk_entry_index(end.entry));
 }
 
-// grid (layers * 4, copies); each block moves one span. A single copy may carry its page entry by value
-// (`lone_from` / `lone_to`) instead of in device memory.
+// grid (layers * 4, copies); each block moves one span.
 __global__ void __launch_bounds__(256)
 move_pages_kernel(const rk_page_entry *__restrict__ from_entries, const rk_page_entry *__restrict__ to_entries,
-                  uint8_t *from_slots, uint8_t *to_slots, uint64_t slot_bytes, SpanGeometry g, rk_page_entry lone_from,
-                  rk_page_entry lone_to) {
+                  uint8_t *from_slots, uint8_t *to_slots, uint64_t slot_bytes, SpanGeometry g) {
   const uint32_t layer = blockIdx.x / 4, tensor = blockIdx.x % 4, copy = blockIdx.y;
   const uint32_t bytes = rk_tensor_page_bytes(g.data_bytes, g.scale_bytes, tensor);
   if (!bytes) return;
-  PageEnd from{from_entries ? from_entries[copy] : lone_from, from_slots ? from_slots + copy * slot_bytes : nullptr};
-  PageEnd to{to_entries ? to_entries[copy] : lone_to, to_slots ? to_slots + copy * slot_bytes : nullptr};
+  PageEnd from{from_entries ? from_entries[copy] : 0, from_slots ? from_slots + copy * slot_bytes : nullptr};
+  PageEnd to{to_entries ? to_entries[copy] : 0, to_slots ? to_slots + copy * slot_bytes : nullptr};
   const uint4 *source = reinterpret_cast<const uint4 *>(span_pointer(from, g, layer, tensor));
   uint4 *target = reinterpret_cast<uint4 *>(span_pointer(to, g, layer, tensor));
+  for (uint32_t i = threadIdx.x; i < bytes / 16; i += blockDim.x) target[i] = source[i];
+}
+
+// The host tier's restores: packed slots -> the pages named in the batch (entries and slot addresses by value).
+// grid (layers * 4, batch.count).
+__global__ void __launch_bounds__(256) unpack_batch_kernel(const __grid_constant__ PageBatch batch, SpanGeometry g) {
+  const uint32_t layer = blockIdx.x / 4, tensor = blockIdx.x % 4, copy = blockIdx.y;
+  const uint32_t bytes = rk_tensor_page_bytes(g.data_bytes, g.scale_bytes, tensor);
+  if (!bytes) return;
+  const uint4 *source = reinterpret_cast<const uint4 *>(span_pointer(PageEnd{0, batch.slot[copy]}, g, layer, tensor));
+  uint4 *target = reinterpret_cast<uint4 *>(span_pointer(PageEnd{batch.entry[copy], nullptr}, g, layer, tensor));
   for (uint32_t i = threadIdx.x; i < bytes / 16; i += blockDim.x) target[i] = source[i];
 }
 
@@ -107,10 +116,10 @@ tree_compact_kernel(const rk_page_entry *const *__restrict__ tables, const rk_ch
 
 int move_pages(uint32_t format, uint32_t layers, uint32_t kv_heads, uint32_t head_dim, uint32_t extent_pages,
                const rk_page_entry *from_entries, const rk_page_entry *to_entries, uint8_t *from_slots,
-               uint8_t *to_slots, uint32_t count, cudaStream_t stream, rk_page_entry lone_from, rk_page_entry lone_to) {
+               uint8_t *to_slots, uint32_t count, cudaStream_t stream) {
   if (!count) return kOk;
-  if (!rk_format_valid(format) || !layers || !extent_pages || ((!from_entries && !lone_from) == !from_slots) ||
-      ((!to_entries && !lone_to) == !to_slots) || ((lone_from || lone_to) && count != 1)) {
+  if (!rk_format_valid(format) || !layers || !extent_pages || (!from_entries == !from_slots) ||
+      (!to_entries == !to_slots)) {
     set_error("page move: invalid arguments");
     return kInvalid;
   }
@@ -121,11 +130,23 @@ int move_pages(uint32_t format, uint32_t layers, uint32_t kv_heads, uint32_t hea
     move_pages_kernel<<<dim3(layers * 4, batch), 256, 0, stream>>>(
         from_entries ? from_entries + done : nullptr, to_entries ? to_entries + done : nullptr,
         from_slots ? from_slots + done * slot_bytes : nullptr, to_slots ? to_slots + done * slot_bytes : nullptr,
-        slot_bytes, g, lone_from, lone_to);
+        slot_bytes, g);
     if (int status = cuda_status(cudaGetLastError(), "page move launch")) return status;
     done += batch;
   }
   return kOk;
+}
+
+int unpack_batch(uint32_t format, uint32_t layers, uint32_t kv_heads, uint32_t head_dim, uint32_t extent_pages,
+                 const PageBatch &batch, uint32_t count, cudaStream_t stream) {
+  if (!count) return kOk;
+  if (!rk_format_valid(format) || !layers || !extent_pages || count > kTierBatch) {
+    set_error("page unpack: invalid arguments");
+    return kInvalid;
+  }
+  SpanGeometry g{layers, extent_pages, rk_data_bytes(format, kv_heads, head_dim), rk_scale_bytes(format, kv_heads)};
+  unpack_batch_kernel<<<dim3(layers * 4, count), 256, 0, stream>>>(batch, g);
+  return cuda_status(cudaGetLastError(), "page unpack launch");
 }
 
 } // namespace rk
@@ -136,14 +157,14 @@ extern "C" int rk_copy_pages(uint32_t format, uint32_t layers, uint32_t kv_heads
                              uint32_t extent_pages, const rk_page_entry *from_entries,
                              const rk_page_entry *to_entries, uint32_t count, void *stream) {
   return move_pages(format, layers, kv_heads, head_dim, extent_pages, from_entries, to_entries, nullptr, nullptr,
-                    count, static_cast<cudaStream_t>(stream), 0, 0);
+                    count, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int rk_pack_pages(uint32_t format, uint32_t layers, uint32_t kv_heads, uint32_t head_dim,
                              uint32_t extent_pages, const rk_page_entry *from_entries, void *slots,
                              uint32_t count, void *stream) {
   return move_pages(format, layers, kv_heads, head_dim, extent_pages, from_entries, nullptr, nullptr,
-                    static_cast<uint8_t *>(slots), count, static_cast<cudaStream_t>(stream), 0, 0);
+                    static_cast<uint8_t *>(slots), count, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int rk_unpack_pages(uint32_t format, uint32_t layers, uint32_t kv_heads, uint32_t head_dim,
@@ -151,7 +172,7 @@ extern "C" int rk_unpack_pages(uint32_t format, uint32_t layers, uint32_t kv_hea
                                uint32_t count, void *stream) {
   return move_pages(format, layers, kv_heads, head_dim, extent_pages, nullptr, to_entries,
                     static_cast<uint8_t *>(const_cast<void *>(slots)), nullptr, count,
-                    static_cast<cudaStream_t>(stream), 0, 0);
+                    static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int rk_tree_compact(uint32_t format, uint32_t kv_heads, uint32_t head_dim, uint32_t lanes,

@@ -373,13 +373,12 @@ template <bool kFloat8> struct ExpandBytes {
   }
   template <uint32_t Team> __device__ static void keys(const uint8_t *raw, uint8_t *k_stage, uint32_t e) {
     // item = (token, 16-byte chunk c of its 256-byte row): 16 dims -> two operand chunks. The eight lanes of a
-    // shared-memory phase take chunks c..c+3 of token 2t and chunks (c..c+3) ^ 4 of token 2t + 1: their raw rows differ
-    // by 2 and their chunk sets by bit 2 (eight distinct chunks to read), and their operand rows differ in bit 0
-    // (eight distinct chunks to write).
+    // shared-memory phase take chunks c..c+3 of token t and chunks c+4..c+7 of token t ^ 1: their raw rows differ by 2
+    // and their chunk sets by bit 2 (eight distinct chunks to read), and their operand rows differ in bit 0 (eight
+    // distinct chunks to write).
 #pragma unroll
     for (uint32_t i = 0; i < (1024 + Team - 1) / Team; ++i) {
-      const uint32_t item = e + i * Team, odd = (item >> 2) & 1u;
-      const uint32_t c = ((item & 3u) | ((item >> 1) & 12u)) ^ (odd << 2), token = ((item >> 5) << 1) | odd;
+      const uint32_t item = e + i * Team, c = item & 15u, token = (item >> 4) ^ ((item >> 2) & 1u);
       if (1024 % Team && item >= 1024) break;
       const uint32_t row = 2 * (token & 31u) + (c >> 3);
       const uint4 x = *reinterpret_cast<const uint4 *>(raw + (token >> 5) * 8192 + swizzled(row, c & 7u));
@@ -436,8 +435,8 @@ template <> struct Expand<RK_FORMAT_BF16> {
       // the eight lanes of a shared-memory phase take the four 16-byte pieces of dim d and of dim d ^ 5: raw rows two
       // apart with the other half of the row (eight distinct chunks to read), operand rows whose swizzles differ in
       // bit 2 (eight distinct chunks to write)
-      const uint32_t item = e + i * Team, q = item & 3u, flip = (item >> 2) & 1u, page = item >> 10;
-      const uint32_t dim = (((item >> 5) & 31u) << 3) | (flip << 2) | (((item >> 4) & 1u) << 1) | (((item >> 3) & 1u) ^ flip);
+      const uint32_t item = e + i * Team, q = item & 3u, page = item >> 10;
+      const uint32_t dim = ((item >> 2) & 255u) ^ (item & 4u); // odd dims trade places with the odd dim four further
       if (2048 % Team && item >= 2048) break;
       uint4 x = *reinterpret_cast<const uint4 *>(raw + (2 + page) * 16384 + swizzled(dim >> 1, 4 * (dim & 1u) + q));
       const uint32_t position = 32 * page + 8 * q;
