@@ -385,7 +385,7 @@ __device__ __noinline__ void cut_ranges(Shared &sh, const DecodeArgs &args, uint
   const uint64_t total_pages = sh.lane_start[lanes];
   // Never more ranges than pages, so every range between a lane's first and last is non-empty.
   const uint32_t ctas = uint32_t(min(uint64_t(gridDim.x), total_pages));
-  if (cta >= ctas) return; // the whole CTA: its range stays empty
+  if (cta >= ctas) return; // the whole CTA: its range stays empty (it never needed its predecessor's results)
   const Cut cut = Cut::make(total_pages, ctas, lanes, switch_pages);
   for (uint32_t i = tid; i < lanes; i += kThreads) {
     const uint32_t begin = sh.lane_start[i], end = sh.lane_start[i + 1];
@@ -393,6 +393,12 @@ __device__ __noinline__ void cut_ranges(Shared &sh, const DecodeArgs &args, uint
   }
   __syncthreads();
   exclusive_scan(sh.segment_base, lanes, sh.scan);
+  // Up to here the kernel has read only the lanes' parameter blocks, which no kernel of this library writes: when it
+  // was launched early (programmatic dependent launch behind this library's store, prepare or merge kernel) the
+  // partition above ran beside its predecessor's tail. Pages, queries and the scratch the predecessor's merge still
+  // reads are touched only from here on. (A predecessor that is not one of these kernels never lets a dependent start
+  // early, so a caller's own kernel that writes the parameter blocks is complete before this grid begins.)
+  dependency_wait();
   if (cta == 0)
     for (uint32_t i = tid; i < lanes; i += kThreads) {
       // a lane with pages gets its descriptor from the CTA that flushes its last segment; a lane without has no segment
@@ -487,7 +493,6 @@ decode_int4_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
   uint32_t *error_word = args.status;
   const uint32_t spin_limit = args.spin_limit;
   dependents_may_launch(); // the merge kernel's blocks may take their places; they wait for this grid to finish
-  dependency_wait();       // pages, queries and parameters may come from the kernel before this one
 
   // ---- barriers, then the partition (the function's barriers publish both) --------------------
   if (tid == 0) {
@@ -864,7 +869,6 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
   uint32_t *error_word = args.status;
   const uint32_t spin_limit = args.spin_limit;
   dependents_may_launch(); // the merge kernel's blocks may take their places; they wait for this grid to finish
-  dependency_wait();       // pages, queries and parameters may come from the kernel before this one
 
   // ---- barriers, then the partition (the function's barriers publish both) --------------------
   if (tid == 0) {
@@ -1166,7 +1170,6 @@ decode_bf16_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs ar
   uint32_t *error_word = args.status;
   const uint32_t spin_limit = args.spin_limit;
   dependents_may_launch(); // the merge kernel's blocks may take their places; they wait for this grid to finish
-  dependency_wait();       // pages, queries and parameters may come from the kernel before this one
 
   // ---- barriers, then the partition (the function's barriers publish both) --------------------
   if (tid == 0) {
@@ -1747,7 +1750,13 @@ using namespace rk;
 // The merge follows its decode kernel as a programmatic dependent launch: its blocks are placed while the decode
 // grid drains and start the moment that grid's writes are visible. Few lanes (a sequence split: one lane over every
 // CTA has hundreds of slots) take sixteen slot groups per block, batches four.
-static bool wide_merge(uint32_t lanes) { return lanes * kKvHeads * kGroup <= 2 * 148; }
+// The merge of few lanes runs in ONE wave: a block per (lane, query head) with sixteen slot groups (1 024 threads,
+// one block per SM) while the blocks do not outnumber the SMs, eight groups (512 threads, two blocks per SM) up to
+// twice that; beyond, the row merge (or four groups for the shards of a sequence split).
+static uint32_t merge_groups(uint32_t lanes) {
+  const uint32_t blocks = lanes * kKvHeads * kGroup;
+  return blocks <= 148 ? 16 : blocks <= 2 * 148 ? 8 : 4;
+}
 
 template <typename Kernel, typename... Args>
 static int launch_dependent(Kernel kernel, dim3 grid, uint32_t threads, cudaStream_t stream, const char *what, Args... args) {
@@ -1767,8 +1776,12 @@ static int launch_merge(uint32_t lanes, cudaStream_t stream, const float *partia
                         const uint32_t *descriptors, uint16_t *output, float *output_f32,
                         const rk_verify_params *lane_params, rk_kv_layer layer, float *triples) {
   const dim3 grid(kGroup, kKvHeads, lanes);
-  if (wide_merge(lanes))
+  const uint32_t groups = merge_groups(lanes);
+  if (groups == 16)
     return launch_dependent(decode_reduce_kernel<16>, grid, 1024, stream, "decode reduce launch", partials, statistics, descriptors,
+                            output, output_f32, lane_params, layer, triples);
+  if (groups == 8)
+    return launch_dependent(decode_reduce_kernel<8>, grid, 512, stream, "decode reduce launch", partials, statistics, descriptors,
                             output, output_f32, lane_params, layer, triples);
   if (!triples)
     return launch_dependent(decode_reduce_rows_kernel, dim3(kKvHeads, lanes), kRowMergeThreads, stream, "decode reduce launch", partials,
@@ -1781,8 +1794,12 @@ static int launch_exchange(uint32_t lanes, cudaStream_t stream, const float *par
                            const uint32_t *descriptors, uint16_t *output, float *output_f32,
                            const rk_verify_params *lane_params, rk_kv_layer layer, const ExchangeArgs &exchange) {
   const dim3 grid(kGroup, kKvHeads, lanes);
-  if (wide_merge(lanes))
+  const uint32_t groups = merge_groups(lanes);
+  if (groups == 16)
     return launch_dependent(shard_exchange_kernel<16>, grid, 1024, stream, "shard exchange launch", partials, statistics, descriptors,
+                            output, output_f32, lane_params, layer, exchange);
+  if (groups == 8)
+    return launch_dependent(shard_exchange_kernel<8>, grid, 512, stream, "shard exchange launch", partials, statistics, descriptors,
                             output, output_f32, lane_params, layer, exchange);
   return launch_dependent(shard_exchange_kernel<4>, grid, 256, stream, "shard exchange launch", partials, statistics, descriptors,
                           output, output_f32, lane_params, layer, exchange);
