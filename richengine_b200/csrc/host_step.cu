@@ -24,6 +24,10 @@ stage_rows_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict__ k
                   uint16_t *__restrict__ chunk_values, uint32_t group, uint32_t head_dim) {
   const uint64_t tile = blockIdx.x; // lane * kv_heads + kv_head
   const uint32_t d = threadIdx.x;
+  // the store and attention kernels behind this one may take their places and run their prologues; this kernel
+  // overwrites stagings the attention kernel before it read, so it waits for that one first
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (d >= head_dim) return;
   constexpr uint32_t stride = RK_VERIFY_CHUNK_STRIDE;
   for (uint32_t g = 0; g < group; ++g)
@@ -36,9 +40,27 @@ __global__ void __launch_bounds__(256)
 gather_rows_kernel(const uint16_t *__restrict__ output, uint16_t *__restrict__ out, uint32_t group, uint32_t head_dim) {
   const uint64_t tile = blockIdx.x;
   const uint32_t d = threadIdx.x;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory"); // the merge that writes `output` runs just before
   if (d >= head_dim) return;
   for (uint32_t g = 0; g < group; ++g)
     out[(tile * group + g) * head_dim + d] = output[(tile * RK_VERIFY_CHUNK_STRIDE * group + g) * head_dim + d];
+}
+
+// A launch that may begin before the kernel ahead of it in the stream has drained (programmatic dependent launch);
+// both kernels wait for it themselves before they touch its results.
+template <typename Kernel, typename... Args>
+int launch_chained(Kernel kernel, uint32_t blocks, cudaStream_t stream, const char *what, Args... args) {
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(blocks);
+  config.blockDim = dim3(256);
+  config.stream = stream;
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  return cuda_status(cudaLaunchKernelEx(&config, kernel, args...), what);
 }
 
 } // namespace
@@ -53,11 +75,10 @@ extern "C" int rk_stage_decode_rows(uint32_t kv_heads, uint32_t query_heads, uin
     set_error("rk_stage_decode_rows: invalid arguments");
     return kInvalid;
   }
-  stage_rows_kernel<<<lanes * kv_heads, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint16_t *>(q), static_cast<const uint16_t *>(k), static_cast<const uint16_t *>(v),
-      static_cast<uint16_t *>(queries), static_cast<uint16_t *>(chunk_keys), static_cast<uint16_t *>(chunk_values),
-      query_heads / kv_heads, head_dim);
-  return cuda_status(cudaGetLastError(), "stage rows launch");
+  return launch_chained(stage_rows_kernel, lanes * kv_heads, static_cast<cudaStream_t>(stream), "stage rows launch",
+                        static_cast<const uint16_t *>(q), static_cast<const uint16_t *>(k), static_cast<const uint16_t *>(v),
+                        static_cast<uint16_t *>(queries), static_cast<uint16_t *>(chunk_keys), static_cast<uint16_t *>(chunk_values),
+                        query_heads / kv_heads, head_dim);
 }
 
 extern "C" int rk_gather_decode_rows(uint32_t kv_heads, uint32_t query_heads, uint32_t head_dim, uint32_t lanes,
@@ -66,9 +87,8 @@ extern "C" int rk_gather_decode_rows(uint32_t kv_heads, uint32_t query_heads, ui
     set_error("rk_gather_decode_rows: invalid arguments");
     return kInvalid;
   }
-  gather_rows_kernel<<<lanes * kv_heads, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint16_t *>(output), static_cast<uint16_t *>(out), query_heads / kv_heads, head_dim);
-  return cuda_status(cudaGetLastError(), "gather rows launch");
+  return launch_chained(gather_rows_kernel, lanes * kv_heads, static_cast<cudaStream_t>(stream), "gather rows launch",
+                        static_cast<const uint16_t *>(output), static_cast<uint16_t *>(out), query_heads / kv_heads, head_dim);
 }
 
 // ---- one decode step with HOST rows, as a C entry -------------------------------------------------------------------
@@ -177,6 +197,9 @@ extern "C" int rk_session_step_host(void *session, uint32_t layer, const void *q
   if (int st = cuda_status(cudaMemcpyAsync(s->v_rows[slot], v_host, kv_rows, cudaMemcpyHostToDevice, s->upload), "session upload")) return st;
   if (int st = cuda_status(cudaEventRecord(s->uploaded[slot], s->upload), "session upload event")) return st;
   if (int st = cuda_status(cudaStreamWaitEvent(compute, s->uploaded[slot], 0), "session compute order")) return st;
+  // the output rows of the call before last must have left their buffer; waited for here, ahead of the kernels, so
+  // that the five kernels of the call follow one another without a host-side wait between them
+  if (int st = cuda_status(cudaStreamWaitEvent(compute, s->downloaded[slot], 0), "session download order")) return st;
   if (int st = rk_stage_decode_rows(s->kv_heads, s->query_heads, s->head_dim, s->lanes, s->q_rows[slot], s->k_rows[slot],
                                     s->v_rows[slot], s->queries, s->chunk_keys, s->chunk_values, compute)) return st;
   if (int st = cuda_status(cudaEventRecord(s->consumed[slot], compute), "session consumed event")) return st;
@@ -185,8 +208,6 @@ extern "C" int rk_session_step_host(void *session, uint32_t layer, const void *q
                                chunk_params, place, compute)) return st;
   if (int st = rk_attention_decode(s->window, &s->plan, s->format, s->queries, s->output, nullptr, s->partials,
                                    s->statistics, s->descriptors, tables, verify_params, place, compute)) return st;
-  // the output rows of the call before last must have left their buffer
-  if (int st = cuda_status(cudaStreamWaitEvent(compute, s->downloaded[slot], 0), "session download order")) return st;
   if (int st = rk_gather_decode_rows(s->kv_heads, s->query_heads, s->head_dim, s->lanes, s->output, s->out_rows[slot], compute)) return st;
   if (int st = cuda_status(cudaEventRecord(s->gathered[slot], compute), "session gathered event")) return st;
   if (int st = cuda_status(cudaStreamWaitEvent(s->download, s->gathered[slot], 0), "session download order")) return st;
