@@ -1075,6 +1075,21 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
       else
         page_softmax<true>(sacc, hfac, negoff, scales, r3g, valid, m, l_sum, o, pb_frag);
 
+      if (kFloat8 && valid != kPageTokens) {
+        // A lane's last page: stale bytes past the visible tokens may decode to NaN, and a zero weight must meet a
+        // finite value. The head's value slab belongs to this warp alone, so the stale bytes are zeroed in place,
+        // once, and the contraction below carries no mask. Word i of the slab: swizzle row i / 32, physical chunk
+        // (i % 32) / 4 = logical chunk ^ (row % 8), whose low bit is the half of the page; tokens rise with the bytes.
+        for (uint32_t i = lane; i < kByteSlabBytes / 4; i += 32) {
+          const uint32_t row = i >> 5, half = (((i >> 2) & 7u) ^ row) & 1u;
+          const uint32_t first_token = 16 * half + 4 * (i & 3u);
+          if (first_token + 4 <= valid) continue;
+          const uint32_t keep = first_token >= valid ? 0u : (1u << (8 * (valid - first_token))) - 1u;
+          const uint32_t word = load_shared_32(values + 4 * i) & keep;
+          asm volatile("st.shared.u32 [%0], %1;" ::"r"(values + 4 * i), "r"(word) : "memory");
+        }
+        __syncwarp();
+      }
       // ---- O^T += V^T.P^T : 16 tiles of 16 dims (rows g and g+8 of a tile = dims 16t+g, 16t+8+g), 2 k-steps of 16 tokens
 #pragma unroll
       for (uint32_t s = 0; s < 2; ++s) {
@@ -1088,12 +1103,6 @@ decode_bytes_kernel(const __grid_constant__ CUtensorMap window_map, DecodeArgs a
           // this lane's tokens of the 16: 4 c1 + c0 (+2) in word c1, 8 + the same in word c1 + 2
           uint32_t a0 = value_pair<kFloat8>(c1 ? va.y : va.x, value_selector), a2 = value_pair<kFloat8>(c1 ? va.w : va.z, value_selector);
           uint32_t a1 = value_pair<kFloat8>(c1 ? vb.y : vb.x, value_selector), a3 = value_pair<kFloat8>(c1 ? vb.w : vb.z, value_selector);
-          if (kFloat8 && valid != kPageTokens) { // stale bytes past the visible tokens may decode to NaN: a zero weight must meet a finite value
-            const uint32_t token = 16 * s + 4 * c1 + c0;
-            const uint32_t low = (token < valid ? 0x0000ffffu : 0u) | (token + 2 < valid ? 0xffff0000u : 0u);
-            const uint32_t high = (token + 8 < valid ? 0x0000ffffu : 0u) | (token + 10 < valid ? 0xffff0000u : 0u);
-            a0 &= low; a1 &= low; a2 &= high; a3 &= high;
-          }
           mma_f16(o[t], a0, a1, a2, a3, pb_frag[s][0], pb_frag[s][1]);
         }
       }
