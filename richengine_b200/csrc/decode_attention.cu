@@ -7,29 +7,28 @@
 //   runtime/metal/kernels/common/paged_attention_tile.h:362-404         (fixed-order merge)
 //   runtime/metal/kernels/decode/paged_attention.metal:23-60            (query / output placement)
 // The execution design is B200-native, not the reference's:
-//  * Work is every lane's pages laid end to end and cut into one equal,
-//    contiguous range per CTA (one CTA per SM); a range that crosses lanes
-//    yields one partial per (lane piece, KV head, warp). Every CTA derives the
-//    same partition from the lane parameters, so no plan is uploaded and the
-//    result is deterministic for a given grid.
-//  * A producer thread streams (page, KV head) units — the head's 4 KiB key
-//    slab, 4 KiB value slab and their two 128-byte scale rows — into a ring of
-//    shared-memory stages with TMA (128-byte swizzle, no multicast), completion
-//    on mbarriers. Consumer warps wait with bounded polls.
-//  * Eight consumer warps each run an independent online softmax over their own
-//    units. Group-of-6 query heads against 4-bit codes is 12 multiply-adds per
-//    KV byte — above what the fp32 pipes sustain at HBM speed — so the
-//    contractions run on the warp-level tensor path (mma.sync m16n8k16, fp16
-//    operands, fp32 accumulate) with the codes expanded in registers:
+//  * Work is every lane's pages laid end to end and cut into one contiguous range per CTA (one CTA per SM) in a
+//    coordinate stretched at lane boundaries (struct Cut); a range that crosses lanes yields one partial per lane
+//    piece. Every CTA derives the same cut from the lane parameters, so no plan is uploaded and the result is the
+//    same bits for a given grid.
+//  * One producer thread streams whole pages — all four heads' keys (16 KiB), all four heads' values (16 KiB) and the
+//    two 512-byte scale rows — into a ring of six shared-memory stages with TMA (128-byte swizzle, no multicast, L2
+//    evict-first), completion on mbarriers. Consumer warps wait with bounded polls and give a stage back lane by
+//    lane, behind a generic-to-async proxy fence.
+//  * Twelve consumer warps = 4 KV heads x 3 page residues; each runs an independent online softmax over its pages.
+//    Group-of-6 query heads against 4-bit codes is 12 multiply-adds per KV byte — above what the fp32 pipes sustain
+//    at HBM speed — so the contractions run on the warp-level tensor path (mma.sync m16n8k16, fp16 operands, fp32
+//    accumulate) with the codes expanded in registers:
 //      S^T[token, head] = K[token, dim] . Q^T[dim, head]   (tokens are the M rows)
 //      O^T[dim, head]  += V^T[dim, token] . P^T[token, head]
-//    Key nibbles become fp16 bit patterns directly (u * 2^-24, u = code + 8); the
-//    +8 is removed exactly through 8 * sum(q). Value nibbles use the 1024 + u
-//    mantissa trick and an exact fp16 subtract. Codes, queries (bf16 -> fp16,
-//    exact in range) and products are exact; accumulation is fp32.
+//    Key and value nibbles become fp16 bit patterns directly (u * 2^-24, u = code + 8); the keys' +8 is removed
+//    exactly through 8 * sum(q), the values' through 8 * the sum of the rounded weights. Codes, queries (bf16 ->
+//    fp16, exact in range) and products are exact; accumulation is fp32.
 //  * The token scale folds into the softmax as in the reference, and the value
 //    scale folds into the exponent: w = 2^(s + log2 vscale - m), so the fp16
 //    probabilities stay in (0, 2^14] whatever the value magnitudes are.
+//  * A CTA's last segment is folded in the (then idle) ring to one partial per KV head before it leaves the SM; the
+//    merge kernel that follows (a programmatic dependent launch) combines a lane's partials in segment order.
 #include "common.cuh"
 #include "window.cuh"
 
@@ -76,7 +75,7 @@ struct DecodeArgs {
   const uint16_t *queries;
   float *partials;
   float *statistics;
-  uint32_t *descriptors; // [lanes]{first segment, segments} then the error word
+  uint32_t *descriptors; // [lanes]{first segment, segments | last segment holds three slots << 31}, then the status word
   const rk_page_entry *const *tables;
   const rk_verify_params *lane_params;
   rk_kv_layer layer;
@@ -1757,8 +1756,7 @@ int configure_decode_kernel() {
 using namespace rk;
 
 // The merge follows its decode kernel as a programmatic dependent launch: its blocks are placed while the decode
-// grid drains and start the moment that grid's writes are visible. Few lanes (a sequence split: one lane over every
-// CTA has hundreds of slots) take sixteen slot groups per block, batches four.
+// grid drains and start the moment that grid's writes are visible.
 // The merge of few lanes runs in ONE wave: a block per (lane, query head) with sixteen slot groups (1 024 threads,
 // one block per SM) while the blocks do not outnumber the SMs, eight groups (512 threads, two blocks per SM) up to
 // twice that; beyond, the row merge (or four groups for the shards of a sequence split).
