@@ -299,7 +299,13 @@ int rk_crc32c_pages(const void *data, uint64_t stride, uint64_t payload_bytes, u
 uint32_t rk_crc32c_host(const void *data, uint64_t bytes, uint32_t crc);
 
 /* ---- pinned-host eviction tier: engine::KvTier (runtime/engine/cache/KvTier.hpp:34-63) with the
- * transfer bounds of KvPageTier (runtime/engine/cache/KvPageTier.cpp:38-132) ------------------------ */
+ * transfer bounds of KvPageTier (runtime/engine/cache/KvPageTier.cpp:38-132) ------------------------
+ * rk_tier_demote / rk_tier_restore accept a transfer and return its id at once; the copies themselves go out in
+ * batches of up to 16 of a kind — when a batch is full, at the next rk_tier_poll and at rk_tier_drain — so a caller
+ * that waits for a transfer polls, as the reference's cache does (Cache::pollTransfers). A batch of demotions is one
+ * kernel (pack + CRC-32C of every page in one pass) and one copy per run of neighbouring host slots; a batch of
+ * restores is one kernel that unpacks the pages straight out of the pinned arena. A page stays valid until its
+ * demotion has retired; a restored page is valid once its restore has retired. */
 void *rk_tier_create(void *storage, uint32_t slots, uint32_t transfer_limit);
 void rk_tier_destroy(void *tier);
 uint64_t rk_tier_slot_bytes(const void *tier);
