@@ -4,6 +4,8 @@ cfg 0  one int8 layer, 4096 tokens appended one at a time, then one decode query
 cfg 1  int4, batch 8, contexts uniform in 8K-32K: append one token, decode (two layers of the stack)
 cfg 2  int4, batch 4 x 64K: 16-row verify windows, seeded acceptance, rejected rows overwritten by the next window
 cfg 3  format sweep at batch 32 x 16K: decode of every format (the pool filled on the GPU, read back for the checker)
+north star  int4, batch 64 x 32K (one layer of the 16): every lane against the checker, the same bits on a second run,
+            the same answer within the bar from a grid cut differently
 """
 import ctypes as C
 
@@ -126,6 +128,27 @@ def test_cfg3_format_sweep_decode(fmt):
     assert_attention_close(d32, want32, d16, f"cfg3 format {fmt} decode (streaming kernel)")
     w16, w32, _ = run_verify_attention_gpu(s, q, 1, 1, committed=committed, splits=1, tensor_core=True)
     assert_attention_close(w32, want32, w16, f"cfg3 format {fmt} decode (window kernel)")
+    s.close()
+
+
+def test_north_star_size_int4_batch64_ctx32k_decode():
+    """The size the headline number is quoted on, one layer of it (2.2 GB of int4 pages): the streaming kernel's
+    output of ALL 64 lanes against the checker, bit-identical on a second run (the cut, the folds and the merge order
+    depend on the lanes' page counts and the grid alone), and within the bar again when the same pages are cut for 37
+    CTAs instead of one per SM (other ranges, other lane boundaries inside a range, other folds)."""
+    layout = Layout(1, 4, 256, INT4)
+    s = Scenario(layout, [32768] * 64, extra_tokens=1, device=True, seed=90)
+    fill_on_gpu_and_mirror(s, layers=[0])
+    rng = np.random.default_rng(91)
+    q = make_queries(rng, s.lanes, layout)
+    committed = [c - 1 for c in s.contexts]
+    _, want32 = run_verify_attention_oracle(s, q, 1, 1, committed=committed)
+    d16, d32 = run_decode_attention_gpu(s, q, committed=committed)
+    assert_attention_close(d32, want32, d16, "north-star size, one CTA per SM")
+    again16, again32 = run_decode_attention_gpu(s, q, committed=committed)
+    assert np.array_equal(d16, again16) and np.array_equal(d32.view(np.uint32), again32.view(np.uint32))
+    other16, other32 = run_decode_attention_gpu(s, q, committed=committed, ctas=37)
+    assert_attention_close(other32, want32, other16, "north-star size, 37 CTAs")
     s.close()
 
 
