@@ -37,6 +37,23 @@ def test_decode_matches_checker(contexts, fmt):
     s.close()
 
 
+@pytest.mark.parametrize("fmt,lanes", [(INT4, 1024), (INT8, 1024), (BF16, 300), (INT4, 9), (FP8E4M3, 12)])
+def test_widest_batches_and_the_merge_shapes_between(fmt, lanes):
+    """The widest batch a launch takes (1 024 lanes: every CTA's range spans several lanes, most lanes a single
+    segment, some none at all) and the widths at which the merge changes shape (up to 6 lanes sixteen slot groups
+    per block, up to 12 eight, beyond that the row merge)."""
+    rng = np.random.default_rng(lanes)
+    contexts = [int(c) for c in rng.integers(0, 260 if lanes > 100 else 3000, size=lanes)]
+    contexts[3] = 0  # a lane without history among the others
+    s, q = prepared(contexts, seed=lanes, fmt=fmt)
+    got16, got32 = run_decode_attention_gpu(s, q)
+    _, want32 = run_verify_attention_oracle(s, q, 1, 1)
+    assert_attention_close(got32, want32, got16, f"decode of {lanes} lanes")
+    again16, _ = run_decode_attention_gpu(s, q)
+    assert np.array_equal(got16, again16)
+    s.close()
+
+
 @pytest.mark.parametrize("fmt", STREAMING)
 @pytest.mark.parametrize("ctas", [1, 3, 7, 148, 1000])
 def test_partition_independent_of_grid(ctas, fmt):
