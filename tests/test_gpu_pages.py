@@ -160,3 +160,64 @@ def test_host_tier_round_trip_and_limits():
     assert library.rk_tier_can_restore(tier)  # existing copies stay readable
     library.rk_tier_destroy(tier)
     s.close()
+
+
+def test_host_tier_batches_of_transfers():
+    """Transfers go out in batches of up to 16 of a kind: 40 demotions (two full batches and a rest that leaves at the
+    poll) into host slots that are only partly neighbours, every slot's bytes and CRC-32C (taken by the pack kernel)
+    against the host's own routine, then all 40 pages wiped and restored in another order, three of them to other
+    pages, with a demotion of a further page in flight beside the restores."""
+    library = lib.load()
+    tokens = 41 * 32
+    s = Scenario(Layout(2, 4, 256, INT4), [tokens], extra_tokens=0, device=True, seed=12)
+    for layer in range(2):
+        fill_history_with_store(s, layer, seed=layer + 21)
+    s.upload()
+    page_bytes = s.storage.bytes_per_page()
+    tier = library.rk_tier_create(s.storage.handle, 64, 128)
+    pages = s.pages[0]
+    everything = [library.rk_tier_acquire_slot(tier) for _ in range(64)]
+    rng = np.random.default_rng(5)
+    chosen = sorted(rng.choice(64, size=41, replace=False).tolist())  # runs of neighbours and gaps between them
+    for slot in everything:
+        if slot not in chosen:
+            library.rk_tier_release_slot(tier, slot)
+    order = rng.permutation(40)
+    ids = {}
+    for i in order:  # asked for in any order: a batch sorts its pages by host slot
+        ids[i] = library.rk_tier_demote(tier, pages[i], chosen[i], None)
+        assert ids[i] >= 0, library.rk_last_error()
+    assert not any(library.rk_tier_transfer_ready(tier, t) for t in ids.values())
+    while not all(library.rk_tier_transfer_ready(tier, t) for t in ids.values()):
+        library.rk_tier_poll(tier)
+    assert all(library.rk_tier_transfer_finish(tier, t) == 1 for t in ids.values())
+    for i in range(40):
+        slot = np.ctypeslib.as_array(C.cast(library.rk_tier_slot_host_pointer(tier, chosen[i]), C.POINTER(C.c_uint8)), shape=(page_bytes,))
+        want = np.concatenate([s.host.tensor_view(pages[i], layer, t) for layer in range(2) for t in range(4)])
+        assert np.array_equal(slot, want), f"slot of page {i}"
+        assert library.rk_tier_slot_checksum(tier, chosen[i]) == library.rk_crc32c_host(want.ctypes.data, page_bytes, 0)
+    # wipe, then bring everything back: pages 0..2 land on each other's places, and a demotion runs beside the restores
+    for extent in range(s.host.extents):
+        s.storage.write_extent(extent, np.zeros_like(s.host.bytes[extent]))
+    destinations = {i: pages[i] for i in range(40)}
+    destinations[0], destinations[1], destinations[2] = pages[1], pages[2], pages[0]
+    restores = [library.rk_tier_restore(tier, chosen[i], destinations[i], None) for i in rng.permutation(40)]
+    assert all(r >= 0 for r in restores), library.rk_last_error()
+    beside = library.rk_tier_demote(tier, pages[40], chosen[40], None)  # its own batch, on another stream
+    assert beside >= 0
+    library.rk_tier_drain(tier)
+    assert all(library.rk_tier_transfer_finish(tier, r) == 1 for r in restores)
+    assert library.rk_tier_transfer_finish(tier, beside) == 1
+    assert library.rk_tier_slot_checksum(tier, chosen[40]) == library.rk_crc32c_host(np.zeros(page_bytes, np.uint8).ctypes.data, page_bytes, 0)
+    for extent in range(s.host.extents):
+        s.host.bytes[extent][:] = 0
+    shadow = Scenario(Layout(2, 4, 256, INT4), [tokens], extra_tokens=0, device=False, seed=12)
+    for layer in range(2):
+        fill_history_with_store(shadow, layer, seed=layer + 21)
+    for i in range(40):
+        for layer in range(2):
+            for t in range(4):
+                s.host.tensor_view(destinations[i], layer, t)[:] = shadow.host.tensor_view(pages[i], layer, t)
+    assert_extents_equal(s, "tier batches")
+    library.rk_tier_destroy(tier)
+    s.close()
