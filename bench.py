@@ -1,7 +1,8 @@
 """Benchmark of the paged, quantized KV-cache hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--batch B] [--context T] [--layers L] [--ragged]
+                    [--batch B] [--context T] [--layers L] [--ragged] [--format int4|int8|fp8e4m3|bf16]
+                    [--mode decode|verify|prefill|seqsplit|seal|evict|prepare] [--skip-config4] [--skip-check]
 
 A step is one decode pass over the batch: for each attention layer, append one
 new K/V token per sequence (quantize into its page) and run one-query paged
@@ -16,6 +17,14 @@ HBM; `e2e` the same metric through the host-buffer call; `roofline` the decode
 kernel against the measured HBM peak; `cpu_baseline` the CPU checker timed on a
 bounded sample of the same workload. With N > 1 (torchrun) every rank runs its
 own batch (requests are sharded, no collective on the data path): weak scaling.
+The default line also carries `checked` (two lanes of the measured pool recomputed by the CPU checker in fp64 and held
+to the parity bar) and two blocks for the multi-GPU configuration of the baseline: `config4_requests` (one global
+batch of 256 ragged requests dealt to the ranks by balanced total context; strong scaling) and `config4_seqsplit`
+(one 262 144-token sequence split along the sequence over the ranks, combined by one fused exchange kernel, with the
+NCCL all-gather variant timed beside it and compared bit for bit). The other modes print their own line: `verify`
+(16-row speculative window), `prefill` (2 048-row chunk), `seqsplit` (the sequence split alone), `seal` (pack +
+CRC-32C of model pages), `evict` (coldest quarter of a pool to pinned host memory and back through the request
+cache), `prepare` (QKV-prepare fused with the page store).
 """
 from __future__ import annotations
 
