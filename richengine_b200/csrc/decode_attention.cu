@@ -61,7 +61,7 @@ constexpr uint32_t kScaleBytes = kKvHeads * kPageTokens * 4;
 constexpr uint32_t kStageBytes = 2 * kTensorBytes + 2 * kScaleBytes; // K | V | key scales | value scales
 constexpr uint32_t kMaxLanes = 1024;
 #ifndef RK_SWITCH_PAGES
-#define RK_SWITCH_PAGES 14
+#define RK_SWITCH_PAGES 10
 #endif
 // what a lane boundary inside a CTA's range costs, in pages of each kernel's format (a page of bytes takes twice,
 // a bf16 page four times as long to stream as an int4 page)
