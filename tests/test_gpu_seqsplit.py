@@ -110,3 +110,61 @@ def test_peer_exchange_step_emulated_on_one_gpu(context, ranks, fmt):
         _, oracle32 = run_verify_attention_oracle(s, q, 1, 1)
         assert_attention_close(out32.cpu().numpy(), oracle32, host_u16(out), f"peer exchange, step {step}")
     exchange.close(); reference.close(); s.close()
+
+
+def _peer_exchange_rank(rank, ranks, port, context, fmt, results):
+    """One rank of the real thing: its own GPU, its own process, the exchange buffers mapped through CUDA IPC."""
+    import os
+    os.environ.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "NCCL_NVLS_ENABLE": "0"})
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=ranks, device_id=torch.device("cuda", rank))
+    try:
+        layout = Layout(1, 4, 256, fmt)
+        s = Scenario(layout, [context], extra_tokens=1, device=True, seed=6)  # every rank builds the same pages
+        fill_history_with_store(s, 0, seed=6)
+        rng = np.random.default_rng(10)
+        k, v = make_staging(rng, 1, layout)
+        assert om.oracle().rko_store_verify(fmt, 4, 256, 1, k.ctypes.data, v.ctypes.data, s.host_table_pointers(), chunk_params(s, 1)) == 0
+        s.upload()
+        visible, place = context + 1, s.storage.layers()[0]
+        first, last = parallel.shard_page_range(len(s.pages[0]), rank, ranks)
+        _, count = parallel.shard_tokens(visible, rank, ranks)
+        table = s.device_tables[0][first:last].contiguous()  # this rank attends only its token range
+        lane = struct_to_device((lib.VerifyParams * 1)(lib.VerifyParams(count - 1, last - first, place, 1, 1, 1, 1, 0.0)))
+        pointers = ops.table_pointer_array([table])
+        exchange = parallel.PeerExchangeDecoder(layout, 24, 1, s.storage.window(), rank=rank, ranks=ranks)
+        worst = 0.0
+        for step in range(3):  # three steps: both parities of the buffers, and one reuse
+            q = make_queries(rng, 1, layout)
+            dq = dev(q)
+            out = torch.zeros_like(dq)
+            out32 = torch.zeros(dq.shape, dtype=torch.float32, device="cuda")
+            exchange.step(dq, out, pointers, lane, place, output_f32=out32)
+            exchange.status()
+            torch.cuda.synchronize()
+            _, oracle32 = run_verify_attention_oracle(s, q, 1, 1)
+            assert_attention_close(out32.cpu().numpy(), oracle32, host_u16(out), f"rank {rank}, step {step}")
+            everyone = [torch.zeros_like(out32) for _ in range(ranks)]
+            dist.all_gather(everyone, out32)
+            assert all(torch.equal(everyone[0], other) for other in everyone), "the ranks hold different bits"
+            worst = max(worst, float(np.abs(out32.cpu().numpy() - oracle32).max()))
+        dist.barrier()  # nobody leaves while a peer may still store into its buffer
+        exchange.close(); s.close()
+        results[rank] = worst
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs of one node")
+@pytest.mark.parametrize("context,fmt", [(5000, INT4), (70000, INT4), (3000, INT8)])
+def test_peer_exchange_across_two_gpus(context, fmt):
+    """The sequence split as it runs in production: two processes, two GPUs, triples stored into the peer's buffer
+    over NVLink, flags, rank-order merge. Every rank's output equals the checker's answer over the WHOLE sequence
+    within the bar, and the ranks hold the same bits."""
+    import torch.multiprocessing as mp
+    manager = mp.get_context("spawn").Manager()
+    results = manager.dict()
+    port = 29600 + (context % 97)
+    mp.spawn(_peer_exchange_rank, args=(2, port, context, fmt, results), nprocs=2, join=True)
+    assert len(results) == 2
