@@ -131,3 +131,40 @@ def test_window_kernel_wait_runs_out_is_reported_and_recovers(fmt, rows):
     _, want32 = run_verify_attention_oracle(s, q, rows, rows, committed=committed)
     assert_attention_close(got32, want32, got16, "window kernel after a timeout")
     s.close()
+
+
+def test_exchange_wait_for_a_peer_runs_out_is_reported_and_recovers():
+    """The sequence split's fused exchange kernel waits for every rank's flag with a bounded number of polls (about a
+    second). Three emulated ranks on one GPU: rank 0 publishes, rank 1 never runs, rank 2 waits for a flag that nothing
+    sets, gives up, raises the step's status word and writes zeros; the next complete step on the same buffers is
+    right again. Nothing spins without a bound and nothing faults."""
+    from richengine_b200 import parallel
+    s, q = prepared([2600], INT4, seed=41)
+    ranks, visible, place = 3, 2601, None
+    place = s.storage.layers()[0]
+    shards = []
+    for r in range(ranks):
+        first, last = parallel.shard_page_range(len(s.pages[0]), r, ranks)
+        _, count = parallel.shard_tokens(visible, r, ranks)
+        table = s.device_tables[0][first:last].contiguous()
+        lane = struct_to_device((lib.VerifyParams * 1)(lib.VerifyParams(count - 1, last - first, place, 1, 1, 1, 1, 0.0)))
+        shards.append((table, ops.table_pointer_array([table]), lane))
+    exchange = parallel.PeerExchangeDecoder(s.layout, 24, 1, s.storage.window(), rank=0, ranks=ranks, connect=False)
+    dq = dev(q)
+    out = torch.zeros_like(dq)
+    out32 = torch.zeros(dq.shape, dtype=torch.float32, device="cuda")
+    out32[:, :, 0] = 1.0  # the rows the step writes
+    for r in (0, 2):  # rank 1 stays away
+        exchange.step(dq, out, shards[r][1], shards[r][2], place, output_f32=out32, loopback_rank=r)
+    torch.cuda.synchronize()  # the kernel came back on its own
+    with pytest.raises(lib.RichKvError) as caught:
+        exchange.status()
+    assert caught.value.status == lib.TIMEOUT
+    assert not out32[:, :, 0].any()  # a step that gave up leaves zeros, not a partial answer
+    for r in range(ranks):
+        exchange.step(dq, out, shards[r][1], shards[r][2], place, output_f32=out32, loopback_rank=r)
+    exchange.status()
+    torch.cuda.synchronize()
+    _, want32 = run_verify_attention_oracle(s, q, 1, 1)
+    assert_attention_close(out32.cpu().numpy(), want32, host_u16(out), "the complete step after a timeout")
+    exchange.close(); s.close()
