@@ -106,7 +106,14 @@ int rk_cache_adopt(void *cache, void *store, uint64_t *out);
  * them by shared recency, states in use and their KV last and only up_to_in_use; out[4] = made progress, pending,
  * evicted a state, state bytes freed. rk_cache_reclaim_one_state is Cache::reclaimOneState (1 = a state went).
  * rk_cache_state_info out[6] = contains, ordinary, in use, bytes, KV needed by a state, KV needed by a state in use;
- * rk_cache_state_summary out[4] = states, resident bytes, evictable states, resume point. */
+ * rk_cache_state_summary out[4] = states, resident bytes, evictable states, resume point.
+ * rk_cache_lookup_state is the lookup a hybrid model's admission makes (Cache::lookup, Cache.cpp:236-272; CacheLookup,
+ * Cache.hpp:20-36): the chain as rk_cache_lookup, out[5] = KV boundary in tokens, the deepest state's block on the
+ * chain (0 = none; it comes back pinned, as the reference's lease pins it: rk_cache_state_pin(block, 0) when the
+ * restore is done), the boundary the request resumes from, the junction boundary (the matched KV ends at a branch
+ * point past the state and another branch holds a state below it: a state materialised there serves both), and
+ * whether a matched block past the state once held a reusable state that is gone. `record` != 0 counts the lookup
+ * (Cache::recordLookup); rk_cache_lookup_counters out[3] = KV tokens hit, lazy junctions, lost-state misses. */
 int64_t rk_cache_block_at(void *cache, uint64_t request, uint32_t tokens);
 int rk_cache_state_publish(void *cache, uint64_t block, uint64_t bytes, int checkpoint);
 int rk_cache_state_use(void *cache, uint64_t block, int use);
@@ -115,6 +122,9 @@ int rk_cache_state_info(void *cache, uint64_t block, uint64_t *out);
 int rk_cache_state_summary(void *cache, uint64_t *out);
 int rk_cache_evict_one(void *cache, int up_to_in_use, int keep_resume_point, int pages_only, uint64_t *out);
 int rk_cache_reclaim_one_state(void *cache, int checkpoints_only, uint64_t for_block);
+int64_t rk_cache_lookup_state(void *cache, const uint32_t *prompt, uint32_t prompt_tokens, uint64_t *blocks_out, uint32_t capacity,
+                              uint64_t *out, int record);
+int rk_cache_lookup_counters(void *cache, uint64_t *out);
 
 /* ---- plans -------------------------------------------------------------------------------------- */
 /* names: "split\nreduce\nstore"; out[16] = splits, lane splits of the first four lanes, splitGroups xyz,

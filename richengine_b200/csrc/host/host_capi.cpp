@@ -468,6 +468,28 @@ int rk_cache_evict_one(void *cache, int up_to_in_use, int keep_resume_point, int
 int rk_cache_reclaim_one_state(void *cache, int checkpoints_only, uint64_t for_block) {
   return guarded([&] { return CACHE->reclaimOneState(checkpoints_only != 0, for_block) ? 1 : 0; });
 }
+// Cache::lookup of a hybrid model's admission: the chain into blocks_out (returns its length), out[5] = KV boundary,
+// state block (pinned for the caller; 0 = none), resume boundary, junction boundary, lost state. `record` counts the
+// lookup as Cache::recordLookup does.
+int64_t rk_cache_lookup_state(void *cache, const uint32_t *prompt, uint32_t prompt_tokens, uint64_t *blocks_out, uint32_t capacity,
+                              uint64_t *out, int record) {
+  try {
+    const auto found = CACHE->lookupWithState({prompt, prompt_tokens});
+    for (size_t i = 0; i < found.blocks.size() && i < capacity; ++i) blocks_out[i] = found.blocks[i];
+    out[0] = found.kvBoundary; out[1] = found.stateBlock; out[2] = found.resumeBoundary; out[3] = found.junctionBoundary;
+    out[4] = found.lostState;
+    if (record) CACHE->recordLookup(found);
+    return int64_t(found.blocks.size());
+  } catch (const std::exception &e) { rk::set_error(e.what()); return RK_ERR_INVALID; }
+}
+// out[3] = KV tokens hit, lookups at a branch point with a state below (lazy junctions), lookups that met a lost state
+int rk_cache_lookup_counters(void *cache, uint64_t *out) {
+  return guarded([&] {
+    const auto counters = CACHE->lookupCounters();
+    out[0] = counters.kvHitTokens; out[1] = counters.lazyJunctions; out[2] = counters.lostStateMisses;
+    return RK_OK;
+  });
+}
 
 #undef CACHE
 

@@ -370,6 +370,36 @@ std::vector<uint64_t> Cache::lookup(std::span<const uint32_t> prompt) {
   return blocks;
 }
 
+Cache::StateLookup Cache::lookupWithState(std::span<const uint32_t> prompt) {
+  StateLookup result;
+  result.blocks = lookup(prompt);
+  const std::vector<uint64_t> &blocks = result.blocks;
+  if (blocks.empty()) return result;
+  result.kvBoundary = uint32_t(blocks.size() * kv::kPageTokens);
+  for (size_t i = blocks.size(); i-- > 0;) // the deepest state on the chain (StateCache::acquireDeepest)
+    if (states_.contains(blocks[i])) {
+      result.stateBlock = blocks[i];
+      result.resumeBoundary = uint32_t((i + 1) * kv::kPageTokens);
+      states_.pin(blocks[i]);
+      break;
+    }
+  if (result.kvBoundary > result.resumeBoundary && index_.stateBelow(blocks.back())) result.junctionBoundary = result.kvBoundary;
+  for (size_t i = blocks.size(); i-- > 0;) {
+    if (blocks[i] == result.stateBlock) break;
+    if (index_.hadState(blocks[i]) && !states_.contains(blocks[i])) {
+      result.lostState = true;
+      break;
+    }
+  }
+  return result;
+}
+
+void Cache::recordLookup(const StateLookup &lookup) noexcept {
+  lookups_.kvHitTokens += lookup.kvBoundary;
+  if (lookup.junctionBoundary) ++lookups_.lazyJunctions;
+  if (lookup.lostState) ++lookups_.lostStateMisses;
+}
+
 TokenAdmission Cache::attachPrefix(uint64_t id, std::span<const uint64_t> blocks, uint32_t *resumeTokens) {
   Request &active = request(id);
   if (!active.pages.empty() || !active.blocks.empty()) throw std::logic_error("a prefix attaches to a request without pages");

@@ -82,6 +82,9 @@ public:
   bool stateBelow(uint64_t block) const { return at(block).statesBelow != 0; }
   bool stateInUseBelow(uint64_t block) const { return at(block).statesInUseBelow != 0; }
   uint32_t children(uint64_t block) const { return at(block).children; }
+  // A reusable state was published at the block at some time (KvCache::noteState / hadState).
+  void noteState(uint64_t block) { at(block).hadState = true; }
+  bool hadState(uint64_t block) const { return at(block).hadState; }
   uint64_t tick() noexcept { return ++clock_; }
   // Takes back a tier-only block an earlier process recorded (KvCache::adoptDiskBlock,
   // runtime/engine/cache/KvCache.cpp:160-199): false when another block already holds its key.
@@ -104,7 +107,7 @@ private:
     std::shared_ptr<KvTierSlot> slot;
     uint32_t children = 0, residentChildren = 0, activeUsers = 0;
     uint32_t statesBelow = 0, statesInUseBelow = 0;
-    bool transferring = false, poisoned = false;
+    bool transferring = false, poisoned = false, hadState = false;
     bool listed = false;   // in idleLeaves_ under (listedAt, id)
     uint64_t listedAt = 0;
   };
@@ -155,7 +158,8 @@ public:
   Cache(KvPool &pool, kv::ExtentStorage &storage, KvTier *tier = nullptr)
       : pool_(pool), storage_(storage), tier_(tier), index_(pool),
         states_([this](uint64_t block, int states, int inUse) { index_.adjustStatesBelow(block, states, inUse); },
-                [this] { return index_.tick(); }) {}
+                [this] { return index_.tick(); },
+                [this](uint64_t block) { if (index_.contains(block)) index_.noteState(block); }) {}
   ~Cache();
 
   // ---- composite states and the reclaim order they impose (runtime/engine/cache/Cache.cpp:451-628) ----------------
@@ -187,6 +191,22 @@ public:
   // The cached chain matching the prompt: at most (n-1)/32 blocks, one real token is always left
   // to recompute (Cache.cpp:179-199).
   std::vector<uint64_t> lookup(std::span<const uint32_t> prompt);
+  // The lookup a hybrid model's admission makes (Cache::lookup, Cache.cpp:236-272; CacheLookup, Cache.hpp:20-36):
+  // the matched chain, the deepest state on it (pinned for the caller, as the reference's lease pins it: unpin with
+  // states().unpin(stateBlock) once the restore is done), where the request resumes, whether the matched KV ends at
+  // a branch point past the state with another branch's state below it (a junction worth materialising a state
+  // at), and whether a matched block past the state once held a reusable state that is gone.
+  struct StateLookup {
+    std::vector<uint64_t> blocks;
+    uint32_t kvBoundary = 0, resumeBoundary = 0, junctionBoundary = 0;
+    uint64_t stateBlock = 0;
+    bool lostState = false;
+  };
+  StateLookup lookupWithState(std::span<const uint32_t> prompt);
+  // Counts a lookup that admission acted on (Cache::recordLookup, Cache.cpp:274-282).
+  struct LookupCounters { uint64_t kvHitTokens = 0, lazyJunctions = 0, lostStateMisses = 0; };
+  void recordLookup(const StateLookup &lookup) noexcept;
+  LookupCounters lookupCounters() const noexcept { return lookups_; }
   // Attaches a matched chain to a request without pages: resident blocks are shared (one more
   // active reference each), host-only blocks take fresh pages and start restores, root first
   // (Cache.cpp:745-785). Returns the tokens the request resumes after, or Denied/Pending.
@@ -255,6 +275,7 @@ private:
   KvTier *tier_;
   PrefixIndex index_;
   StateCache states_;
+  LookupCounters lookups_;
   std::unordered_map<uint64_t, Request> requests_;
   std::vector<Transfer> demotions_, restores_;
   CacheSnapshot counters_;

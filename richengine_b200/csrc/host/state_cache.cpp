@@ -19,11 +19,14 @@ void StateCache::publish(uint64_t block, uint64_t bytes, bool checkpoint) {
     state.bytes = bytes;
     state.checkpoint = state.checkpoint && checkpoint; // an ordinary state stays ordinary
     state.lastUsed = clock_();
+    if (!state.checkpoint && note_) note_(block);
     return;
   }
   // a state in use is reusable: a checkpoint published there is ordinary from the start
-  states_.emplace(block, State{bytes, clock_(), checkpoint && !inUse(block), 0});
+  const bool disposable = checkpoint && !inUse(block);
+  states_.emplace(block, State{bytes, clock_(), disposable, 0});
   bytes_ += bytes;
+  if (!disposable && note_) note_(block);
   adjust_(block, +1, inUse(block) ? +1 : 0);
 }
 
@@ -41,6 +44,7 @@ void StateCache::use(uint64_t block) {
   auto found = states_.find(block);
   if (found == states_.end()) return; // yet to be published: in use from the moment it appears
   found->second.checkpoint = false;
+  if (note_) note_(block);
   if (first) adjust_(block, 0, +1);
 }
 void StateCache::unuse(uint64_t block) {

@@ -26,7 +26,12 @@ public:
   // keeps, per block, how many states (in use) sit strictly below it (KvCache::stateBelow / stateInUseBelow).
   using AdjustBelow = std::function<void(uint64_t block, int states, int inUse)>;
   using Clock = std::function<uint64_t()>;
-  StateCache(AdjustBelow adjust, Clock clock) : adjust_(std::move(adjust)), clock_(std::move(clock)) {}
+  // noteReusable(block): a reusable (ordinary) state exists at the block now; the KV index remembers it beyond the
+  // state's life (KvCache::noteState, called from StateCache::makeOrdinary), so that a later lookup can tell a state
+  // that was lost from one that never was.
+  using NoteReusable = std::function<void(uint64_t block)>;
+  StateCache(AdjustBelow adjust, Clock clock, NoteReusable note = {})
+      : adjust_(std::move(adjust)), clock_(std::move(clock)), note_(std::move(note)) {}
 
   // Publishes a RAM copy at a block (StateCache::publishCompositeState). A normal boundary upgrades a checkpoint;
   // a checkpoint cannot downgrade an ordinary state.
@@ -68,6 +73,7 @@ private:
 
   AdjustBelow adjust_;
   Clock clock_;
+  NoteReusable note_;
   std::unordered_map<uint64_t, State> states_;
   std::unordered_map<uint64_t, uint32_t> uses_;
   uint64_t bytes_ = 0;

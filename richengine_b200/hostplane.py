@@ -157,6 +157,21 @@ class Cache:
         self._check(self._lib.rk_cache_evict_one(self._handle, int(up_to_in_use), int(keep_resume_point), int(pages_only), out), "evict_one")
         return dict(zip(["progress", "pending", "evicted_state", "state_bytes"], [int(x) for x in out]))
 
+    def lookup_state(self, prompt, record=False) -> dict:
+        """Cache::lookup with states: the chain, the deepest state on it (pinned: unpin_state when done), where the
+        request resumes, a junction worth a state, a state that was lost."""
+        t = np.ascontiguousarray(prompt, dtype=np.uint32)
+        blocks = (C.c_uint64 * (len(t) // 32 + 1))()
+        out = (C.c_uint64 * 5)()
+        count = self._check(self._lib.rk_cache_lookup_state(self._handle, t.ctypes.data, len(t), blocks, len(blocks), out, int(record)), "lookup_state")
+        return {"blocks": list(blocks[:count]), "kv_boundary": int(out[0]), "state_block": int(out[1]), "resume_boundary": int(out[2]),
+                "junction_boundary": int(out[3]), "lost_state": bool(out[4])}
+
+    def lookup_counters(self) -> dict:
+        out = (C.c_uint64 * 3)()
+        self._check(self._lib.rk_cache_lookup_counters(self._handle, out), "lookup_counters")
+        return dict(zip(["kv_hit_tokens", "lazy_junctions", "lost_state_misses"], [int(x) for x in out]))
+
     def reclaim_one_state(self, checkpoints_only=False, for_block=0) -> bool:
         return bool(self._check(self._lib.rk_cache_reclaim_one_state(self._handle, int(checkpoints_only), for_block), "reclaim_one_state"))
 

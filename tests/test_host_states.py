@@ -195,3 +195,61 @@ def test_with_a_tier_a_needed_leaf_is_demoted_and_its_state_kept_resumable():
     cache.poll_transfers()
     assert pool.snapshot()["pages_prefix"] == 3 and len(cache.lookup(PROMPT)) == 4
     cache.close(); pool.close()
+
+
+def test_a_lookup_asks_for_a_junction_only_at_a_branch_point_with_a_state_below():
+    """dev/tests/engine/kv_first_cache_test.cpp:543-586: a prompt that leaves the cached chain where the chain goes on
+    to a state of its own branches there; its lookup names the branch point as a junction worth a state, and once a
+    state is published there the next lookup resumes from it. Not at a chain end, and not inside a tail past the
+    state that holds no state."""
+    pool, cache = make()
+    blocks = chain(cache, 1, PROMPT, 128)
+    cache.publish_state(blocks[0], 100)   # resumable after 32 tokens
+    cache.end_request(1)
+    branch = np.concatenate([PROMPT[:64], np.full(33, 7, dtype=np.uint32)])  # leaves the chain after two pages
+
+    def junction(prompt):
+        found = cache.lookup_state(prompt, record=True)
+        assert found["resume_boundary"] == 32 and found["state_block"] == blocks[0]
+        cache.unpin_state(found["state_block"])
+        return found["junction_boundary"]
+
+    assert junction(PROMPT) == 0 and cache.lookup_counters()["lazy_junctions"] == 0       # a chain end
+    assert junction(branch) == 0 and cache.lookup_counters()["lazy_junctions"] == 0       # a dead tail past the state
+    cache.publish_state(blocks[3], 100)                                                   # the chain goes on to a state
+    assert junction(branch) == 64 and cache.lookup_counters()["lazy_junctions"] == 1
+    cache.publish_state(blocks[1], 100)                                                   # the junction materialises
+    found = cache.lookup_state(branch)
+    assert found["kv_boundary"] == 64 and found["resume_boundary"] == 64 and found["junction_boundary"] == 0
+    assert found["blocks"] == blocks[:2]
+    cache.unpin_state(found["state_block"])
+    assert cache.lookup_counters()["kv_hit_tokens"] == 128 + 64 + 64
+    cache.close(); pool.close()
+
+
+def test_a_lost_reusable_state_is_told_from_one_that_never_was():
+    """dev/tests/engine/kv_first_cache_test.cpp:1320-1351: a block remembers that it held a reusable state; a lookup
+    that finds the KV without it reports a lost state. A dropped checkpoint is not a lost state."""
+    pool, cache = make()
+    blocks = chain(cache, 1, PROMPT, 128)
+    cache.publish_state(blocks[3], 100)
+    cache.end_request(1)
+    assert cache.reclaim_one_state()                      # the state goes, its KV stays
+    found = cache.lookup_state(PROMPT[:129], record=True)
+    assert found["kv_boundary"] == 128 and found["state_block"] == 0 and found["lost_state"]
+    cache.publish_state(blocks[3], 100)                   # published again: found, not lost
+    found = cache.lookup_state(PROMPT[:129])
+    assert found["state_block"] == blocks[3] and not found["lost_state"]
+    cache.unpin_state(blocks[3])
+    cache.publish_state(blocks[1], 100, checkpoint=True)  # a disposable checkpoint that is dropped
+    assert cache.reclaim_one_state(checkpoints_only=True)
+    shallow = cache.lookup_state(PROMPT[:65])
+    assert shallow["state_block"] == 0 and not shallow["lost_state"]
+    assert cache.lookup_counters()["lost_state_misses"] == 1
+    # the state a lookup returns is pinned until the caller lets go of it: no reclaim takes it meanwhile
+    found = cache.lookup_state(PROMPT[:129])
+    assert found["state_block"] == blocks[3]
+    assert not cache.reclaim_one_state()
+    cache.unpin_state(blocks[3])
+    assert cache.reclaim_one_state()
+    cache.close(); pool.close()
