@@ -113,7 +113,16 @@ int rk_cache_adopt(void *cache, void *store, uint64_t *out);
  * restore is done), the boundary the request resumes from, the junction boundary (the matched KV ends at a branch
  * point past the state and another branch holds a state below it: a state materialised there serves both), and
  * whether a matched block past the state once held a reusable state that is gone. `record` != 0 counts the lookup
- * (Cache::recordLookup); rk_cache_lookup_counters out[3] = KV tokens hit, lazy junctions, lost-state misses. */
+ * (Cache::recordLookup); rk_cache_lookup_counters out[4] = KV tokens hit, lazy junctions, lost-state misses, pages
+ * hashed by scheduling probes.
+ * rk_cache_probe_* is the scheduling probe (CacheProbe, Cache.hpp:38-52; Cache::probe / Cache::refresh,
+ * Cache.cpp:210-234): what a scheduler keeps per waiting request between admission passes. It pins nothing, touches no
+ * recency and counts no hit. While the block graph's generation stands still (no new block, adopted record, poisoning
+ * or erase) a refresh hashes nothing; after a change the chain is cut at its first block that no longer matches and
+ * only the pages past the cut are hashed. rk_cache_probe_info out[2] = cached tokens (up to the deepest state on the
+ * matched chain; looked up again on every refresh), matched blocks. rk_cache_lookup_state given a current probe of the
+ * same cache reuses its chain; a stale probe or another cache's is ignored there, and another cache's is refused by
+ * rk_cache_probe_refresh (RK_ERR_INVALID). */
 int64_t rk_cache_block_at(void *cache, uint64_t request, uint32_t tokens);
 int rk_cache_state_publish(void *cache, uint64_t block, uint64_t bytes, int checkpoint);
 int rk_cache_state_use(void *cache, uint64_t block, int use);
@@ -123,8 +132,12 @@ int rk_cache_state_summary(void *cache, uint64_t *out);
 int rk_cache_evict_one(void *cache, int up_to_in_use, int keep_resume_point, int pages_only, uint64_t *out);
 int rk_cache_reclaim_one_state(void *cache, int checkpoints_only, uint64_t for_block);
 int64_t rk_cache_lookup_state(void *cache, const uint32_t *prompt, uint32_t prompt_tokens, uint64_t *blocks_out, uint32_t capacity,
-                              uint64_t *out, int record);
+                              uint64_t *out, int record, const void *probe);
 int rk_cache_lookup_counters(void *cache, uint64_t *out);
+void *rk_cache_probe_create(void *cache, const uint32_t *prompt, uint32_t prompt_tokens);
+int rk_cache_probe_refresh(void *cache, void *probe, const uint32_t *prompt, uint32_t prompt_tokens);
+int rk_cache_probe_info(const void *probe, uint64_t *out);
+void rk_cache_probe_destroy(void *probe);
 
 /* ---- plans -------------------------------------------------------------------------------------- */
 /* names: "split\nreduce\nstore"; out[16] = splits, lane splits of the first four lanes, splitGroups xyz,

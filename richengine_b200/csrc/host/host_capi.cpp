@@ -470,11 +470,12 @@ int rk_cache_reclaim_one_state(void *cache, int checkpoints_only, uint64_t for_b
 }
 // Cache::lookup of a hybrid model's admission: the chain into blocks_out (returns its length), out[5] = KV boundary,
 // state block (pinned for the caller; 0 = none), resume boundary, junction boundary, lost state. `record` counts the
-// lookup as Cache::recordLookup does.
+// lookup as Cache::recordLookup does. `probe` (may be null) is a handle of rk_cache_probe_create: while it is current
+// its chain is reused instead of hashing the prompt again.
 int64_t rk_cache_lookup_state(void *cache, const uint32_t *prompt, uint32_t prompt_tokens, uint64_t *blocks_out, uint32_t capacity,
-                              uint64_t *out, int record) {
+                              uint64_t *out, int record, const void *probe) {
   try {
-    const auto found = CACHE->lookupWithState({prompt, prompt_tokens});
+    const auto found = CACHE->lookupWithState({prompt, prompt_tokens}, static_cast<const engine::Cache::Probe *>(probe));
     for (size_t i = 0; i < found.blocks.size() && i < capacity; ++i) blocks_out[i] = found.blocks[i];
     out[0] = found.kvBoundary; out[1] = found.stateBlock; out[2] = found.resumeBoundary; out[3] = found.junctionBoundary;
     out[4] = found.lostState;
@@ -482,14 +483,33 @@ int64_t rk_cache_lookup_state(void *cache, const uint32_t *prompt, uint32_t prom
     return int64_t(found.blocks.size());
   } catch (const std::exception &e) { rk::set_error(e.what()); return RK_ERR_INVALID; }
 }
-// out[3] = KV tokens hit, lookups at a branch point with a state below (lazy junctions), lookups that met a lost state
+// out[4] = KV tokens hit, lookups at a branch point with a state below (lazy junctions), lookups that met a lost
+// state, pages hashed by scheduling probes
 int rk_cache_lookup_counters(void *cache, uint64_t *out) {
   return guarded([&] {
     const auto counters = CACHE->lookupCounters();
     out[0] = counters.kvHitTokens; out[1] = counters.lazyJunctions; out[2] = counters.lostStateMisses;
+    out[3] = counters.probeHashedBlocks;
     return RK_OK;
   });
 }
+// The scheduling probe (Cache::probe / Cache::refresh / CacheProbe): a handle the scheduler keeps per waiting request.
+void *rk_cache_probe_create(void *cache, const uint32_t *prompt, uint32_t prompt_tokens) {
+  try { return new engine::Cache::Probe(CACHE->probe({prompt, prompt_tokens})); }
+  catch (const std::exception &e) { rk::set_error(e.what()); return nullptr; }
+}
+int rk_cache_probe_refresh(void *cache, void *probe, const uint32_t *prompt, uint32_t prompt_tokens) {
+  return guarded([&] { CACHE->refresh(*static_cast<engine::Cache::Probe *>(probe), {prompt, prompt_tokens}); return RK_OK; });
+}
+// out[2] = cached tokens (up to the deepest state on the matched chain), matched blocks
+int rk_cache_probe_info(const void *probe, uint64_t *out) {
+  return guarded([&] {
+    const auto *held = static_cast<const engine::Cache::Probe *>(probe);
+    out[0] = held->cachedTokens(); out[1] = held->blocks().size();
+    return RK_OK;
+  });
+}
+void rk_cache_probe_destroy(void *probe) { delete static_cast<engine::Cache::Probe *>(probe); }
 
 #undef CACHE
 

@@ -103,6 +103,7 @@ PrefixIndex::Match PrefixIndex::insert(uint64_t parent, std::span<const uint32_t
     refresh(parent);
   }
   refresh(id);
+  ++generation_;
   return {id, page};
 }
 
@@ -179,6 +180,7 @@ bool PrefixIndex::adoptTierBlock(uint64_t id, uint64_t parent, std::span<const u
   blocks_.emplace(id, std::move(entry));
   if (parent) ++at(parent).children;
   nextId_ = std::max(nextId_, id + 1);
+  ++generation_;
   return true;
 }
 
@@ -210,7 +212,7 @@ void PrefixIndex::followPages(const KvPageMoves &moves) noexcept {
   }
 }
 
-void PrefixIndex::poison(uint64_t block) { at(block).poisoned = true; }
+void PrefixIndex::poison(uint64_t block) { at(block).poisoned = true; ++generation_; }
 
 void PrefixIndex::erase(uint64_t block) {
   Block &entry = at(block);
@@ -233,6 +235,7 @@ void PrefixIndex::erase(uint64_t block) {
   for (auto it = first; it != last; ++it)
     if (it->second == block) { index_.erase(it); break; }
   blocks_.erase(block);
+  ++generation_;
 }
 
 std::optional<PrefixIndex::Candidate> PrefixIndex::evictionCandidate() const {
@@ -357,22 +360,65 @@ void Cache::publishCommittedBlocks(uint64_t id, std::span<const uint32_t> exactT
   }
 }
 
-std::vector<uint64_t> Cache::lookup(std::span<const uint32_t> prompt) {
-  std::vector<uint64_t> blocks;
-  if (prompt.empty()) return blocks;
+// Extends a chain that matches the prompt's first pages by the pages that follow, at most (n-1)/32 in all; returns
+// the pages hashed (Cache::extendMatch, Cache.cpp:179-199).
+size_t Cache::extendMatch(std::vector<uint64_t> &blocks, std::span<const uint32_t> prompt) const {
+  if (prompt.empty()) return 0;
   const size_t maximum = (prompt.size() - 1) / kv::kPageTokens; // one real token stays to recompute
-  for (size_t i = 0; i < maximum; ++i) {
+  size_t hashed = 0;
+  for (size_t i = blocks.size(); i < maximum; ++i) {
+    ++hashed;
     auto match = index_.find(blocks.empty() ? 0 : blocks.back(), prompt.subspan(i * kv::kPageTokens, kv::kPageTokens));
     if (!match) break;
     blocks.push_back(match->id);
   }
-  if (!blocks.empty()) index_.touch(blocks.back());
+  return hashed;
+}
+
+// Tokens up to the deepest state on a chain (Cache::stateTokens, Cache.cpp:201-207).
+uint32_t Cache::stateTokens(std::span<const uint64_t> blocks) const {
+  for (size_t i = blocks.size(); i > 0; --i)
+    if (states_.contains(blocks[i - 1])) return uint32_t(i * kv::kPageTokens);
+  return 0;
+}
+
+Cache::Probe Cache::probe(std::span<const uint32_t> prompt) {
+  Probe result;
+  result.owner_ = this;
+  result.generation_ = index_.generation();
+  lookups_.probeHashedBlocks += extendMatch(result.blocks_, prompt);
+  result.cachedTokens_ = stateTokens(result.blocks_);
+  return result;
+}
+
+void Cache::refresh(Probe &probe, std::span<const uint32_t> prompt) {
+  if (probe.owner_ != this) throw std::logic_error("a scheduling probe belongs to another cache");
+  if (probe.generation_ != index_.generation()) {
+    auto cut = std::find_if(probe.blocks_.begin(), probe.blocks_.end(), [&](uint64_t block) { return !index_.matchable(block); });
+    probe.blocks_.erase(cut, probe.blocks_.end());
+    lookups_.probeHashedBlocks += extendMatch(probe.blocks_, prompt);
+    probe.generation_ = index_.generation();
+  }
+  probe.cachedTokens_ = stateTokens(probe.blocks_); // states come and go without a change of the graph
+}
+
+std::vector<uint64_t> Cache::lookup(std::span<const uint32_t> prompt, const Probe *probe) {
+  std::vector<uint64_t> blocks;
+  if (probe && probe->owner_ == this && probe->generation_ == index_.generation()) blocks = probe->blocks_;
+  else extendMatch(blocks, prompt);
+  if (!blocks.empty()) {
+    index_.touch(blocks.back());
+    // A chain that ends in tier-only blocks keeps its resident boundary as warm as its tip: a restore adopts the
+    // blocks below it (Cache.cpp:248-257).
+    auto resident = std::find_if(blocks.rbegin(), blocks.rend(), [&](uint64_t block) { return index_.page(block) != PrefixIndex::noPage; });
+    if (resident != blocks.rbegin() && resident != blocks.rend()) index_.touch(*resident);
+  }
   return blocks;
 }
 
-Cache::StateLookup Cache::lookupWithState(std::span<const uint32_t> prompt) {
+Cache::StateLookup Cache::lookupWithState(std::span<const uint32_t> prompt, const Probe *probe) {
   StateLookup result;
-  result.blocks = lookup(prompt);
+  result.blocks = lookup(prompt, probe);
   const std::vector<uint64_t> &blocks = result.blocks;
   if (blocks.empty()) return result;
   result.kvBoundary = uint32_t(blocks.size() * kv::kPageTokens);

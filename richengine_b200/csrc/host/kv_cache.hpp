@@ -58,6 +58,12 @@ public:
   void touch(uint64_t block) noexcept;
   Chain chain(uint64_t block) const;
   bool contains(uint64_t block) const noexcept { return blocks_.count(block) != 0; }
+  // In the graph and not poisoned (KvCache::matchable, KvCache.cpp:279-282).
+  bool matchable(uint64_t block) const noexcept { auto found = blocks_.find(block); return found != blocks_.end() && !found->second.poisoned; }
+  // Moves with every new block, adopted record, poisoning and erase (KvCache::generation, KvCache.hpp:228-233): while
+  // it stands still, every chain a probe matched still matches and nothing extends it. Blocks leave leaf first and a
+  // poisoned block hides those below it, so after a change a probe's chain holds up to its first unmatchable block.
+  uint64_t generation() const noexcept { return generation_; }
   uint32_t page(uint64_t block) const { return at(block).page; }
   std::shared_ptr<KvTierSlot> slot(uint64_t block) const { return at(block).slot; }
   bool transferring(uint64_t block) const { return at(block).transferring; }
@@ -123,7 +129,7 @@ private:
   // The resident leaves no request uses and no transfer touches, oldest first: the order evictions go in. Kept
   // current by every mutator, so a candidate costs a tree step instead of a pass over every block.
   std::set<std::pair<uint64_t, uint64_t>> idleLeaves_; // (last used, id)
-  uint64_t nextId_ = 1, clock_ = 0;
+  uint64_t nextId_ = 1, clock_ = 0, generation_ = 1;
   uint32_t resident_ = 0;
 };
 
@@ -190,7 +196,8 @@ public:
   void publishCommittedBlocks(uint64_t request, std::span<const uint32_t> exactTokens, uint32_t committedTokens);
   // The cached chain matching the prompt: at most (n-1)/32 blocks, one real token is always left
   // to recompute (Cache.cpp:179-199).
-  std::vector<uint64_t> lookup(std::span<const uint32_t> prompt);
+  struct Probe;
+  std::vector<uint64_t> lookup(std::span<const uint32_t> prompt, const Probe *probe = nullptr);
   // The lookup a hybrid model's admission makes (Cache::lookup, Cache.cpp:236-272; CacheLookup, Cache.hpp:20-36):
   // the matched chain, the deepest state on it (pinned for the caller, as the reference's lease pins it: unpin with
   // states().unpin(stateBlock) once the restore is done), where the request resumes, whether the matched KV ends at
@@ -202,9 +209,29 @@ public:
     uint64_t stateBlock = 0;
     bool lostState = false;
   };
-  StateLookup lookupWithState(std::span<const uint32_t> prompt);
-  // Counts a lookup that admission acted on (Cache::recordLookup, Cache.cpp:274-282).
-  struct LookupCounters { uint64_t kvHitTokens = 0, lazyJunctions = 0, lostStateMisses = 0; };
+  // What a scheduler keeps per waiting request between admission passes (CacheProbe, Cache.hpp:38-52; Cache::probe,
+  // Cache::refresh, Cache.cpp:210-234): the matched chain, the generation of the block graph it was matched under and
+  // the tokens up to the deepest state on it. A probe pins nothing, touches no recency and counts no hit. While the
+  // graph's generation stands still a refresh hashes nothing (states come and go without it, so the cached tokens
+  // are always looked up again); after a change the chain is cut at its first unmatchable block and only the pages
+  // past the cut are hashed. A lookup given a current probe of this cache reuses its chain; a stale or foreign probe
+  // is ignored there and a foreign one is refused by refresh.
+  struct Probe {
+    uint32_t cachedTokens() const noexcept { return cachedTokens_; }
+    const std::vector<uint64_t> &blocks() const noexcept { return blocks_; }
+   private:
+    friend class Cache;
+    std::vector<uint64_t> blocks_;
+    uint64_t generation_ = 0;
+    uint32_t cachedTokens_ = 0;
+    const Cache *owner_ = nullptr;
+  };
+  Probe probe(std::span<const uint32_t> prompt);
+  void refresh(Probe &probe, std::span<const uint32_t> prompt);
+  StateLookup lookupWithState(std::span<const uint32_t> prompt, const Probe *probe = nullptr);
+  // Counts a lookup that admission acted on (Cache::recordLookup, Cache.cpp:274-282); probeHashedBlocks counts the
+  // pages probes hashed (CacheLookupSnapshot::probeHashedBlocks).
+  struct LookupCounters { uint64_t kvHitTokens = 0, lazyJunctions = 0, lostStateMisses = 0, probeHashedBlocks = 0; };
   void recordLookup(const StateLookup &lookup) noexcept;
   LookupCounters lookupCounters() const noexcept { return lookups_; }
   // Attaches a matched chain to a request without pages: resident blocks are shared (one more
@@ -276,6 +303,8 @@ private:
   PrefixIndex index_;
   StateCache states_;
   LookupCounters lookups_;
+  size_t extendMatch(std::vector<uint64_t> &blocks, std::span<const uint32_t> prompt) const;
+  uint32_t stateTokens(std::span<const uint64_t> blocks) const;
   std::unordered_map<uint64_t, Request> requests_;
   std::vector<Transfer> demotions_, restores_;
   CacheSnapshot counters_;

@@ -157,20 +157,25 @@ class Cache:
         self._check(self._lib.rk_cache_evict_one(self._handle, int(up_to_in_use), int(keep_resume_point), int(pages_only), out), "evict_one")
         return dict(zip(["progress", "pending", "evicted_state", "state_bytes"], [int(x) for x in out]))
 
-    def lookup_state(self, prompt, record=False) -> dict:
+    def lookup_state(self, prompt, record=False, probe=None) -> dict:
         """Cache::lookup with states: the chain, the deepest state on it (pinned: unpin_state when done), where the
-        request resumes, a junction worth a state, a state that was lost."""
+        request resumes, a junction worth a state, a state that was lost. A current Probe's chain is reused."""
         t = np.ascontiguousarray(prompt, dtype=np.uint32)
         blocks = (C.c_uint64 * (len(t) // 32 + 1))()
         out = (C.c_uint64 * 5)()
-        count = self._check(self._lib.rk_cache_lookup_state(self._handle, t.ctypes.data, len(t), blocks, len(blocks), out, int(record)), "lookup_state")
+        count = self._check(self._lib.rk_cache_lookup_state(self._handle, t.ctypes.data, len(t), blocks, len(blocks), out, int(record),
+                                                            probe._handle if probe is not None else None), "lookup_state")
         return {"blocks": list(blocks[:count]), "kv_boundary": int(out[0]), "state_block": int(out[1]), "resume_boundary": int(out[2]),
                 "junction_boundary": int(out[3]), "lost_state": bool(out[4])}
 
     def lookup_counters(self) -> dict:
-        out = (C.c_uint64 * 3)()
+        out = (C.c_uint64 * 4)()
         self._check(self._lib.rk_cache_lookup_counters(self._handle, out), "lookup_counters")
-        return dict(zip(["kv_hit_tokens", "lazy_junctions", "lost_state_misses"], [int(x) for x in out]))
+        return dict(zip(["kv_hit_tokens", "lazy_junctions", "lost_state_misses", "probe_hashed_blocks"], [int(x) for x in out]))
+
+    def probe(self, prompt) -> "Probe":
+        """Cache::probe: what a scheduler keeps per waiting request between admission passes."""
+        return Probe(self, prompt)
 
     def reclaim_one_state(self, checkpoints_only=False, for_block=0) -> bool:
         return bool(self._check(self._lib.rk_cache_reclaim_one_state(self._handle, int(checkpoints_only), for_block), "reclaim_one_state"))
@@ -200,6 +205,42 @@ class Cache:
 
 
 KV_BLOCK_LABEL_BYTES = 168  # engine::KvBlockLabel: id, parent, lastUsed, images lo/hi (u64 each), 32 token ids (u32)
+
+
+class Probe:
+    """The scheduling probe of a waiting request (CacheProbe, runtime/engine/cache/Cache.hpp:38-52): pins nothing,
+    touches no recency, counts no hit; refresh() hashes only what a change of the block graph made necessary."""
+
+    def __init__(self, cache: Cache, prompt):
+        self._cache, self._lib = cache, cache._lib
+        t = np.ascontiguousarray(prompt, dtype=np.uint32)
+        self._handle = self._lib.rk_cache_probe_create(cache._handle, t.ctypes.data, len(t))
+        if not self._handle:
+            raise RuntimeError(f"probe: {self._lib.rk_last_error().decode()}")
+
+    def refresh(self, prompt, cache: Cache = None):
+        t = np.ascontiguousarray(prompt, dtype=np.uint32)
+        owner = cache if cache is not None else self._cache
+        owner._check(self._lib.rk_cache_probe_refresh(owner._handle, self._handle, t.ctypes.data, len(t)), "probe_refresh")
+
+    def _info(self):
+        out = (C.c_uint64 * 2)()
+        self._cache._check(self._lib.rk_cache_probe_info(self._handle, out), "probe_info")
+        return int(out[0]), int(out[1])
+
+    @property
+    def cached_tokens(self) -> int: return self._info()[0]
+
+    @property
+    def matched_blocks(self) -> int: return self._info()[1]
+
+    def close(self):
+        if self._handle:
+            self._lib.rk_cache_probe_destroy(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        self.close()
 
 
 def kv_block_label(block_id, parent, last_used, tokens, images=(0, 0)) -> bytes:

@@ -185,7 +185,11 @@ SIGNATURES = {
     "rk_cache_state_summary": (i32, [vp, vp]),
     "rk_cache_evict_one": (i32, [vp, i32, i32, i32, vp]),
     "rk_cache_reclaim_one_state": (i32, [vp, i32, u64]),
-    "rk_cache_lookup_state": (i64, [vp, vp, u32, vp, u32, vp, i32]),
+    "rk_cache_lookup_state": (i64, [vp, vp, u32, vp, u32, vp, i32, vp]),
+    "rk_cache_probe_create": (vp, [vp, vp, u32]),
+    "rk_cache_probe_refresh": (i32, [vp, vp, vp, u32]),
+    "rk_cache_probe_info": (i32, [vp, vp]),
+    "rk_cache_probe_destroy": (None, [vp]),
     "rk_cache_lookup_counters": (i32, [vp, vp]),
     "rk_slot_store_open": (vp, [C.c_char_p, C.c_char_p, vp, u32, u32, u64]),
     "rk_slot_store_close": (None, [vp]),

@@ -253,3 +253,167 @@ def test_a_lost_reusable_state_is_told_from_one_that_never_was():
     cache.unpin_state(blocks[3])
     assert cache.reclaim_one_state()
     cache.close(); pool.close()
+
+
+# ---- the scheduling probe (Cache::probe / Cache::refresh, runtime/engine/cache/Cache.cpp:210-234) ----------------
+# Behaviours follow dev/tests/engine/kv_first_cache_test.cpp:236-254 (a probe changes no policy), :256-273 (a valid
+# probe preserves lookup and accounting), :275-352 (a refresh follows the graph), :355-405 (an evicted state or block
+# is not reused; a cold probe hides nothing published later), :440-452 (another cache's probe).
+
+ASKED = PROMPT[:129]   # four full pages and the one token that is always left to recompute
+
+
+def hashed(cache):
+    return cache.lookup_counters()["probe_hashed_blocks"]
+
+
+def test_a_probe_changes_no_policy():
+    pool, cache = make()
+    blocks = chain(cache, 1, ASKED, 128)
+    cache.end_request(1)
+    probe = cache.probe(ASKED)
+    assert probe.cached_tokens == 0 and probe.matched_blocks == 4  # KV without a state is no reusable work
+    cache.publish_state(blocks[0], 100)
+    cache.publish_state(blocks[3], 100)
+    short, full = cache.probe(ASKED[:33]), cache.probe(ASKED)
+    assert short.cached_tokens == 32 and full.cached_tokens == 128
+    counters = cache.lookup_counters()
+    assert counters["kv_hit_tokens"] == 0 and not cache.state_info(blocks[3])["in_use"]  # no hit counted, nothing pinned
+    # the probes did not refresh the oldest state's eviction order: it is still the first to go
+    assert cache.reclaim_one_state()
+    assert cache.probe(ASKED[:33]).cached_tokens == 0 and cache.probe(ASKED).cached_tokens == 128
+    cache.close(); pool.close()
+
+
+def test_a_current_probe_preserves_lookup_and_accounting():
+    pool, cache = make()
+    blocks = chain(cache, 1, ASKED, 128)
+    cache.end_request(1)
+    cache.publish_state(blocks[0], 100)
+    cache.publish_state(blocks[2], 100)
+    probe = cache.probe(ASKED)
+    assert probe.cached_tokens == 96 and cache.lookup_counters()["kv_hit_tokens"] == 0
+    before = hashed(cache)
+    found = cache.lookup_state(ASKED, record=True, probe=probe)
+    assert found["blocks"] == blocks and found["kv_boundary"] == 128 and found["resume_boundary"] == 96
+    assert found["junction_boundary"] == 0 and found["state_block"] == blocks[2]
+    counters = cache.lookup_counters()
+    assert counters["kv_hit_tokens"] == 128 and counters["lazy_junctions"] == 0 and hashed(cache) == before
+    cache.unpin_state(blocks[2])
+    cache.close(); pool.close()
+
+
+def test_a_refresh_follows_the_states_without_hashing():
+    pool, cache = make()
+    blocks = chain(cache, 1, ASKED, 128)
+    cache.end_request(1)
+    cache.publish_state(blocks[1], 100)
+    probe = cache.probe(ASKED)
+    assert probe.cached_tokens == 64 and hashed(cache) == 4
+    cache.publish_state(blocks[3], 100)   # states come and go without a change of the block graph
+    probe.refresh(ASKED)
+    assert probe.cached_tokens == 128 and hashed(cache) == 4
+    assert cache.reclaim_one_state() and cache.reclaim_one_state()
+    probe.refresh(ASKED)
+    assert probe.cached_tokens == 0 and hashed(cache) == 4
+    cache.close(); pool.close()
+
+
+def test_a_refresh_hashes_only_past_the_first_block_that_went():
+    pool, cache = make()
+    blocks = chain(cache, 1, ASKED, 128)
+    cache.end_request(1)
+    cache.publish_state(blocks[2], 100)
+    probe = cache.probe(ASKED)
+    assert probe.cached_tokens == 96 and hashed(cache) == 4
+    step = cache.evict_one()   # the tail block no state needs goes (no tier: it is forgotten)
+    assert step["progress"] and not step["evicted_state"] and pool.snapshot()["pages_prefix"] == 3
+    # a stale probe is ignored by a lookup: it hashes the prompt itself and finds what is there now
+    stale = cache.lookup_state(ASKED, probe=probe)
+    assert stale["kv_boundary"] == 96
+    cache.unpin_state(blocks[2])
+    probe.refresh(ASKED)      # three blocks stay without hashing, one page past them is tried
+    assert probe.cached_tokens == 96 and probe.matched_blocks == 3 and hashed(cache) == 5
+    probed, fresh = cache.lookup_state(ASKED, probe=probe), cache.lookup_state(ASKED)
+    assert probed["kv_boundary"] == fresh["kv_boundary"] == 96 and probed["resume_boundary"] == fresh["resume_boundary"] == 96
+    cache.unpin_state(blocks[2]); cache.unpin_state(blocks[2])
+    # the tail comes back, written by a request that continues the chain
+    cache.begin_request(2)
+    status, resume = cache.attach_prefix(2, probed["blocks"])
+    assert status == GRANTED and resume == 96 and cache.ensure_tokens(2, 128) == GRANTED
+    cache.publish(2, ASKED, 128)
+    cache.end_request(2)
+    probe.refresh(ASKED)
+    assert hashed(cache) == 6 and probe.matched_blocks == 4    # only the page that came back was hashed
+    found = cache.lookup_state(ASKED, probe=probe)
+    assert found["kv_boundary"] == 128
+    cache.unpin_state(blocks[2])
+    cache.close(); pool.close()
+
+
+def test_a_refresh_does_not_match_through_a_poisoned_block():
+    pool, cache = make(pages=8, extent=8, tier=Cache.MANUAL_TIER, slots=8, transfers=4)
+    blocks = chain(cache, 1, ASKED, 128)
+    cache.end_request(1)
+    for _ in range(2):   # the two deepest blocks move to the tier
+        assert cache.reclaim_one() and cache.complete_transfer(True)
+        cache.poll_transfers()
+    assert [cache.block_state(b)["page"] == 0xffffffff for b in blocks] == [False, False, True, True]
+    cache.publish_state(blocks[3], 100)
+    probe = cache.probe(ASKED)
+    assert probe.cached_tokens == 128 and probe.matched_blocks == 4
+    cache.begin_request(2)
+    assert cache.attach_prefix(2, cache.lookup(ASKED))[0] == GRANTED
+    assert cache.complete_transfer(False)   # the third block's read fails: it is poisoned ...
+    cache.poll_transfers()
+    while cache.complete_transfer(True):    # ... while whatever else was started lands
+        cache.poll_transfers()
+    before = hashed(cache)
+    probe.refresh(ASKED)
+    assert probe.matched_blocks == 2 and probe.cached_tokens == 0 and hashed(cache) == before + 1
+    found = cache.lookup_state(ASKED, probe=probe)
+    assert found["kv_boundary"] == 64
+    cache.end_request(2)
+    cache.close(); pool.close()
+
+
+def test_a_probe_reuses_neither_an_evicted_state_nor_an_evicted_block_and_hides_nothing_new():
+    pool, cache = make()
+    blocks = chain(cache, 1, ASKED, 128)
+    cache.end_request(1)
+    cache.publish_state(blocks[3], 100)
+    probe = cache.probe(ASKED)
+    assert probe.cached_tokens == 128 and cache.reclaim_one_state()
+    found = cache.lookup_state(ASKED, probe=probe)   # the chain is current, the state is looked up again
+    assert found["kv_boundary"] == 128 and found["state_block"] == 0 and found["resume_boundary"] == 0
+    assert cache.evict_one()["progress"]              # now a block goes: the probe is stale and ignored
+    assert cache.lookup_state(ASKED, probe=probe)["kv_boundary"] == 96
+    # a probe taken while nothing was cached hides nothing published later
+    other = np.arange(90000, 90000 + 97, dtype=np.uint32)
+    cold = cache.probe(other)
+    assert cold.cached_tokens == 0 and cold.matched_blocks == 0
+    published = chain(cache, 2, other, 96)
+    cache.publish_state(published[1], 100)
+    cache.end_request(2)
+    found = cache.lookup_state(other, probe=cold)
+    assert found["kv_boundary"] == 96 and found["resume_boundary"] == 64
+    cache.unpin_state(published[1])
+    cold.refresh(other)
+    assert cold.cached_tokens == 64 and cold.matched_blocks == 3
+    cache.close(); pool.close()
+
+
+def test_another_caches_probe_is_ignored_by_a_lookup_and_refused_by_a_refresh():
+    pool_a, cache_a = make()
+    pool_b, cache_b = make()
+    first = np.arange(100, 100 + 65, dtype=np.uint32)
+    second = np.arange(700, 700 + 65, dtype=np.uint32)
+    chain(cache_a, 1, first, 64); cache_a.end_request(1)
+    chain(cache_b, 1, second, 64); cache_b.end_request(1)   # the same block ids, other content
+    probe = cache_a.probe(first)
+    assert probe.matched_blocks == 2
+    assert cache_b.lookup_state(first, probe=probe)["kv_boundary"] == 0
+    with pytest.raises(RuntimeError, match="another cache"):
+        probe.refresh(first, cache=cache_b)
+    probe.close()
+    cache_a.close(); pool_a.close(); cache_b.close(); pool_b.close()
