@@ -221,3 +221,39 @@ def test_host_tier_batches_of_transfers():
     assert_extents_equal(s, "tier batches")
     library.rk_tier_destroy(tier)
     s.close()
+
+
+@pytest.mark.gpu
+def test_host_tier_restores_a_chain_demoted_leaf_first():
+    """A chain demoted leaf first sits in descending host slots and is restored root first: a full batch of sixteen
+    and a rest of three, sorted by host slot inside each batch, unpacked straight out of pinned memory. Every byte of
+    every extent after: the chain's pages are back, everything else stays wiped."""
+    library = lib.load()
+    tokens = 22 * 32
+    s = Scenario(Layout(2, 4, 256, INT4), [tokens], extra_tokens=0, device=True, seed=14)
+    for layer in range(2):
+        fill_history_with_store(s, layer, seed=layer + 31)
+    s.upload()
+    tier = library.rk_tier_create(s.storage.handle, 32, 128)
+    pages = s.pages[0]
+    chain = list(range(19))                      # 19 = a full batch of 16 and a run of three
+    slots = {}
+    for i in reversed(chain):                    # leaf first: the leaf takes the lowest slot
+        slots[i] = library.rk_tier_acquire_slot(tier)
+        assert library.rk_tier_demote(tier, pages[i], slots[i], None) >= 0, library.rk_last_error()
+    assert [slots[i] for i in reversed(chain)] == list(range(19))
+    library.rk_tier_drain(tier)
+    for extent in range(s.host.extents):
+        s.storage.write_extent(extent, np.zeros_like(s.host.bytes[extent]))
+    restores = [library.rk_tier_restore(tier, slots[i], pages[i], None) for i in chain]   # root first
+    assert all(r >= 0 for r in restores), library.rk_last_error()
+    library.rk_tier_drain(tier)
+    assert all(library.rk_tier_transfer_finish(tier, r) == 1 for r in restores)
+    kept = {(i, layer, t): s.host.tensor_view(pages[i], layer, t).copy() for i in chain for layer in range(2) for t in range(4)}
+    for extent in range(s.host.extents):         # only the chain's pages come back; everything else stays wiped
+        s.host.bytes[extent][:] = 0
+    for (i, layer, t), content in kept.items():
+        s.host.tensor_view(pages[i], layer, t)[:] = content
+    assert_extents_equal(s, "chain restore")
+    library.rk_tier_destroy(tier)
+    s.close()
