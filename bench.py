@@ -1363,14 +1363,17 @@ def run_evict(args):
     restored_pages, request_id = 0, 1000
     # Requests arrive as fast as the tier takes them: a request whose chain does not fit the transfers in flight waits
     # its turn, the others' restores keep the link busy meanwhile (a request is done when none of its restores is pending).
-    waiting = [r for r in range(requests) if cache.lookup(prompts[r])]
+    waiting = list(range(requests))
     running, blocked = [], None  # blocked: the request that asked and was told to wait (it asks again, as itself)
     while waiting or running or blocked:
         while waiting or blocked:
-            if blocked is None:
+            if blocked is None:  # one match per request, made while the earlier requests' pages are on the link
+                chain = cache.lookup(prompts[waiting.pop(0)])
+                if not chain:
+                    continue
                 request_id += 1
                 cache.begin_request(request_id)
-                blocked = (request_id, cache.lookup(prompts[waiting.pop(0)]))
+                blocked = (request_id, chain)
             status, _ = cache.attach_prefix(*blocked)
             if status != GRANTED:  # out of pages or transfers for now: retire some, then ask again
                 break

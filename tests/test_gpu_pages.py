@@ -225,9 +225,10 @@ def test_host_tier_batches_of_transfers():
 
 @pytest.mark.gpu
 def test_host_tier_restores_a_chain_demoted_leaf_first():
-    """A chain demoted leaf first sits in descending host slots and is restored root first: a full batch of sixteen
-    and a rest of three, sorted by host slot inside each batch, unpacked straight out of pinned memory. Every byte of
-    every extent after: the chain's pages are back, everything else stays wiped."""
+    """A chain demoted leaf first sits in descending host slots; restored root first, a batch of its restores is one
+    run of neighbouring slots once sorted and crosses PCIe as one copy into the staging area (runs of four or more),
+    the rest of the chain (a run of three) is unpacked straight out of pinned memory. Every byte of every extent
+    after: the chain's pages are back, everything else stays wiped."""
     library = lib.load()
     tokens = 22 * 32
     s = Scenario(Layout(2, 4, 256, INT4), [tokens], extra_tokens=0, device=True, seed=14)
