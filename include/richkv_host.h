@@ -52,6 +52,12 @@ int rk_cache_publish(void *cache, uint64_t request, const uint32_t *tokens, uint
 int64_t rk_cache_lookup(void *cache, const uint32_t *prompt, uint32_t prompt_tokens, uint64_t *blocks_out, uint32_t capacity);
 int rk_cache_attach_prefix(void *cache, uint64_t request, const uint64_t *blocks, uint32_t count, uint32_t *resume_tokens);
 int rk_cache_restores_pending(const void *cache, uint64_t request);
+/* Cache::kvRestoreStatus (Cache.cpp:787-792): 0 nothing to wait for, 1 pending, 2 a read failed (the block matches
+ * nothing any more and leaves, with what hangs below it, once its last request has ended: Cache::dropPoisoned). */
+int rk_cache_restore_status(const void *cache, uint64_t request);
+/* 1: a chain resumes only through a composite state (a hybrid model), so KV no state needs is dropped instead of
+ * written to the tier, as Cache::reclaimKvLeaf does (Cache.cpp:629-659). 0 (default): every block is worth its copy. */
+void rk_cache_set_state_coupled(void *cache, int coupled);
 int rk_cache_fork(void *cache, uint64_t parent, uint64_t child, uint32_t committed_tokens); /* pages copied, or status */
 int64_t rk_cache_truncate(void *cache, uint64_t request, uint32_t committed_tokens, uint32_t scratch_tokens);
 int rk_cache_reclaim_one(void *cache);
@@ -60,6 +66,11 @@ void rk_cache_poll_transfers(void *cache);
 int rk_cache_compact_extent(void *cache);
 int rk_cache_complete_transfer(void *cache, int success); /* tier_mode 2: finishes the oldest transfer; 0 if none */
 void rk_cache_fail_next_transfers(void *cache, uint32_t count); /* tier_mode 1: host-side fault injection */
+/* tier_mode 2: changes how many transfers the tier takes at a time (0 = none) and whether it takes writes at all */
+void rk_cache_manual_tier_set(void *cache, uint32_t transfer_limit, int writable);
+/* out[3] = demotions the tier refused (Cache::demoteKv, Cache.cpp:824-851), tier copies replaced by a full tier
+ *          (Cache::freeDiskSpace, Cache.cpp:871-905), restores cancelled before they were submitted (Cache::endRequest) */
+void rk_cache_tier_counters(const void *cache, uint64_t *out);
 /* out[10] = requests, residentBlocks, tierBlocks, transfers, demotions, restores, failedTransfers,
  *           evictedBlocks, forkCopies, truncatedPages */
 void rk_cache_snapshot(const void *cache, uint64_t *out);

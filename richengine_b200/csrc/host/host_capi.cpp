@@ -78,6 +78,7 @@ public:
     verify_[slot->id] = 1;
     return slot;
   }
+  void set(uint32_t limit, bool writable) noexcept { limit_ = limit; writable_ = writable; }
   bool complete(bool success) {
     if (pending_.empty()) return false;
     auto state = pending_.front();
@@ -274,6 +275,10 @@ int rk_cache_attach_prefix(void *cache, uint64_t request, const uint64_t *blocks
 int rk_cache_restores_pending(const void *cache, uint64_t request) {
   try { return static_cast<const CacheHandle *>(cache)->cache->restoresPending(request) ? 1 : 0; } catch (...) { return RK_ERR_INVALID; }
 }
+int rk_cache_restore_status(const void *cache, uint64_t request) {
+  try { return static_cast<const CacheHandle *>(cache)->cache->restoreStatus(request); } catch (...) { return RK_ERR_INVALID; }
+}
+void rk_cache_set_state_coupled(void *cache, int coupled) { CACHE->setStateCoupled(coupled != 0); }
 int rk_cache_fork(void *cache, uint64_t parent, uint64_t child, uint32_t committed_tokens) {
   return guarded([&] { return int(CACHE->forkRequest(parent, child, committed_tokens)); });
 }
@@ -287,6 +292,14 @@ int rk_cache_compact_extent(void *cache) { return guarded([&] { return CACHE->co
 int rk_cache_complete_transfer(void *cache, int success) {
   auto *h = static_cast<CacheHandle *>(cache);
   return h->manual && h->manual->complete(success != 0) ? 1 : 0;
+}
+void rk_cache_manual_tier_set(void *cache, uint32_t transfer_limit, int writable) {
+  auto *h = static_cast<CacheHandle *>(cache);
+  if (h->manual) h->manual->set(transfer_limit, writable != 0);
+}
+void rk_cache_tier_counters(const void *cache, uint64_t *out) {
+  const auto s = static_cast<const CacheHandle *>(cache)->cache->snapshot();
+  out[0] = s.demotionsRefused; out[1] = s.replacedCopies; out[2] = s.cancelledRestores;
 }
 void rk_cache_fail_next_transfers(void *cache, uint32_t count) {
   auto *h = static_cast<CacheHandle *>(cache);

@@ -49,6 +49,57 @@ void PrefixIndex::refresh(uint64_t block) {
     entry.listed = true;
     entry.listedAt = entry.lastUsed;
   }
+  // the orders a full tier makes room in (KvCache::reindex, KvCache.cpp:577-592)
+  uint8_t wanted = 0;
+  if (entry.slot && !entry.activeUsers && !entry.transferring && !entry.poisoned)
+    wanted = entry.page != noPage ? 1 : (!entry.children ? 2 : 0);
+  if (entry.tierListed && (entry.tierListed != wanted || entry.tierListedAt != entry.lastUsed)) {
+    (entry.tierListed == 1 ? duplicates_ : tierLeaves_).erase({entry.tierListedAt, block});
+    entry.tierListed = 0;
+  }
+  if (wanted && !entry.tierListed) {
+    (wanted == 1 ? duplicates_ : tierLeaves_).emplace(entry.lastUsed, block);
+    entry.tierListed = wanted;
+    entry.tierListedAt = entry.lastUsed;
+  }
+}
+
+void PrefixIndex::setSlot(uint64_t block, std::shared_ptr<KvTierSlot> slot) {
+  Block &entry = at(block);
+  if (!slot && entry.page == noPage) throw std::logic_error("a tier-only KV cache block is erased, not stripped");
+  entry.slot = std::move(slot);
+  refresh(block);
+}
+
+std::optional<PrefixIndex::Candidate> PrefixIndex::tierCandidate(bool duplicate, const Candidate *after) const {
+  const auto &order = duplicate ? duplicates_ : tierLeaves_;
+  auto next = after ? order.upper_bound({after->lastUsed, after->block}) : order.begin();
+  if (next == order.end()) return std::nullopt;
+  return Candidate{next->second, next->first};
+}
+
+std::vector<uint64_t> PrefixIndex::subtree(uint64_t block) const {
+  // Blocks keep no list of their children: one pass gathers them. This runs only when a tier has closed or a
+  // restore has failed.
+  std::unordered_multimap<uint64_t, uint64_t> below;
+  for (const auto &[id, entry] : blocks_)
+    if (entry.parent) below.emplace(entry.parent, id);
+  std::vector<uint64_t> order;
+  std::vector<std::pair<uint64_t, bool>> pending{{block, false}};
+  while (!pending.empty()) {
+    const auto [id, expanded] = pending.back();
+    pending.pop_back();
+    if (expanded) {
+      if (id != block) order.push_back(id);
+      continue;
+    }
+    const Block &entry = at(id);
+    if (id != block && (entry.transferring || entry.activeUsers)) return {};
+    pending.push_back({id, true});
+    const auto [first, last] = below.equal_range(id);
+    for (auto child = first; child != last; ++child) pending.push_back({child->second, false});
+  }
+  return order;
 }
 
 std::optional<PrefixIndex::Match> PrefixIndex::find(uint64_t parent, std::span<const uint32_t> tokens, ImageIdentity images) const {
@@ -147,6 +198,14 @@ void PrefixIndex::dropPage(uint64_t block) {
   refresh(block);
 }
 
+bool PrefixIndex::abandonRestore(uint64_t block) {
+  Block &entry = at(block);
+  if (!entry.transferring || entry.residentChildren || entry.activeUsers) return false;
+  entry.transferring = false;
+  dropPage(block);
+  return true;
+}
+
 void PrefixIndex::adoptPage(uint64_t block, uint32_t page) {
   Block &entry = at(block);
   if (entry.page != noPage) throw std::logic_error("KV cache block already has a page");
@@ -178,7 +237,8 @@ bool PrefixIndex::adoptTierBlock(uint64_t id, uint64_t parent, std::span<const u
   entry.slot = std::move(slot);
   index_.emplace(entry.hash, id);
   blocks_.emplace(id, std::move(entry));
-  if (parent) ++at(parent).children;
+  if (parent) { ++at(parent).children; refresh(parent); }
+  refresh(id);
   nextId_ = std::max(nextId_, id + 1);
   ++generation_;
   return true;
@@ -212,7 +272,7 @@ void PrefixIndex::followPages(const KvPageMoves &moves) noexcept {
   }
 }
 
-void PrefixIndex::poison(uint64_t block) { at(block).poisoned = true; ++generation_; }
+void PrefixIndex::poison(uint64_t block) { at(block).poisoned = true; ++generation_; refresh(block); }
 
 void PrefixIndex::erase(uint64_t block) {
   Block &entry = at(block);
@@ -224,6 +284,7 @@ void PrefixIndex::erase(uint64_t block) {
     --resident_;
   }
   if (entry.listed) idleLeaves_.erase({entry.listedAt, block});
+  if (entry.tierListed) (entry.tierListed == 1 ? duplicates_ : tierLeaves_).erase({entry.tierListedAt, block});
   if (entry.parent) {
     Block &above = at(entry.parent);
     --above.children;
@@ -269,8 +330,10 @@ Cache::~Cache() {
   // Transfers read or write their pages in place: they retire before the pages can go.
   for (auto *list : {&demotions_, &restores_})
     for (Transfer &t : *list) {
-      while (!t.ticket->ready()) tier_->poll();
-      t.ticket->finish();
+      if (t.ticket) { // a restore that was never submitted has no IO to drain
+        while (!t.ticket->ready()) tier_->poll();
+        t.ticket->finish();
+      }
       if (index_.contains(t.block)) index_.setTransferring(t.block, false);
     }
   for (auto &[id, active] : requests_) {
@@ -300,7 +363,20 @@ void Cache::endRequest(uint64_t id) {
   if (found == requests_.end()) return;
   for (uint32_t page : found->second.pages) pool_.releasePage(page, false);
   if (!found->second.blocks.empty()) index_.releaseActive(found->second.blocks.back());
+  // Reads that were never submitted have no IO to drain: their pages return leaf first, unless another request
+  // waits for the block, a block below it is resident, or a state was published on it meanwhile (Cache::endRequest,
+  // Cache.cpp:160-175; KvCache::abandonRestore, KvCache.cpp:411-418).
+  const std::vector<uint64_t> &chain = found->second.blocks;
+  for (auto block = chain.rbegin(); block != chain.rend() && !restores_.empty(); ++block) {
+    auto queued = std::find_if(restores_.begin(), restores_.end(), [&](const Transfer &t) { return t.block == *block; });
+    if (queued == restores_.end() || queued->ticket || states_.stateResident(*block)) continue;
+    if (!index_.abandonRestore(*block)) continue;
+    restores_.erase(queued);
+    --counters_.restores;
+    ++counters_.cancelledRestores;
+  }
   requests_.erase(found);
+  dropPoisoned(); // a block whose restore failed leaves once its last request has let go
 }
 
 TokenAdmission Cache::admitPages(uint32_t count, std::vector<uint32_t> &pages) {
@@ -460,6 +536,7 @@ TokenAdmission Cache::attachPrefix(uint64_t id, std::span<const uint64_t> blocks
     if (const TokenAdmission admission = admitPages(missing, fresh); !admission.granted()) return admission;
   }
   size_t next = 0;
+  bool refused = false; // restores start in block order and stop at the first the tier refuses
   for (uint64_t block : blocks) { // root first: a parent is resident before its child adopts a page
     uint32_t page = index_.page(block);
     if (page == PrefixIndex::noPage) {
@@ -467,7 +544,8 @@ TokenAdmission Cache::attachPrefix(uint64_t id, std::span<const uint64_t> blocks
       index_.adoptPage(block, page);
       index_.setTransferring(block, true);
       Transfer restore{block, page, nullptr, index_.slot(block)};
-      restore.ticket = tier_->canRestore() ? tier_->restore(restore.slot, page) : nullptr;
+      if (!refused && tier_->canRestore()) restore.ticket = tier_->restore(restore.slot, page);
+      if (!restore.ticket) refused = true;
       restores_.push_back(std::move(restore)); // a refused start is retried by pollTransfers
       ++counters_.restores;
       // the pool's acquisition gave the request an active reference already
@@ -482,6 +560,15 @@ TokenAdmission Cache::attachPrefix(uint64_t id, std::span<const uint64_t> blocks
   changed(active, 0);
   if (resumeTokens) *resumeTokens = uint32_t(blocks.size()) * kv::kPageTokens;
   return {};
+}
+
+// Cache::kvRestoreStatus (Cache.cpp:787-792): 0 = nothing to wait for, 1 = pending, 2 = a read failed (the request
+// recomputes: the block matches nothing any more).
+int Cache::restoreStatus(uint64_t id) const {
+  const Request &active = request(id);
+  for (uint64_t block : active.blocks)
+    if (index_.poisoned(block)) return 2;
+  return restoresPending(id) ? 1 : 0;
 }
 
 bool Cache::restoresPending(uint64_t id) const {
@@ -537,31 +624,111 @@ uint32_t Cache::truncate(uint64_t id, uint32_t committedTokens, uint32_t scratch
   return released;
 }
 
-Cache::LeafReclaim Cache::reclaimKvLeaf(uint64_t block) {
+Cache::LeafReclaim Cache::reclaimKvLeaf(uint64_t block, bool immediate) {
   if (index_.slot(block)) { // a tier copy exists already: the page can go at once
     index_.dropPage(block);
     ++counters_.evictedBlocks;
     return LeafReclaim::Started;
   }
-  if (tier_ && tier_->writable()) {
-    if (!tier_->canDemote()) return LeafReclaim::Pending; // the caller waits while transfers are in flight
-    std::shared_ptr<KvTierSlot> slot = tier_->acquireSlot();
-    if (slot) {
-      std::unique_ptr<KvTransfer> ticket = tier_->demote(index_.page(block), slot);
-      if (!ticket) return LeafReclaim::Pending;
-      index_.setTransferring(block, true);
-      demotions_.push_back({block, index_.page(block), std::move(ticket), std::move(slot)});
-      ++counters_.demotions;
-      return LeafReclaim::Started;
-    }
+  // A leaf worth a copy is written (the page returns only when the copy lands); copies below that nothing needs go
+  // with a leaf that is not (Cache::reclaimKvLeaf, Cache.cpp:629-659).
+  if (worthACopy(block)) {
+    // the tier has said "not now" in this scan already: every leaf that needs a write would hear the same
+    if (immediate && tierWritable()) return LeafReclaim::Impossible;
+    const LeafReclaim demotion = demoteKv(block);
+    if (demotion != LeafReclaim::Impossible) return demotion;
+    // A leaf its tier subtree depends on stays in RAM while the tier may still write it: dropping it would orphan
+    // every copy below it. Once a failed write has closed the tier, the subtree goes with it, as without a tier.
+    if ((stateCoupled_ ? index_.stateBelow(block) : index_.tierChildren(block)) && tierWritable()) return LeafReclaim::Impossible;
   }
-  // No tier (or its quota is full): the content is forgotten, and the state on it with it. A leaf whose children
-  // live on in the tier stays: they hang on it.
+  if (index_.tierChildren(block) && !dropTierSubtree(block)) return LeafReclaim::Impossible;
   if (index_.children(block)) return LeafReclaim::Impossible;
   states_.forget(block);
   index_.erase(block);
   ++counters_.evictedBlocks;
   return LeafReclaim::Started;
+}
+
+// Cache::demoteKv (Cache.cpp:824-851): Pending = worth waiting for (transfers in flight will make room), Impossible =
+// nothing will, and the leaf goes as without a tier.
+Cache::LeafReclaim Cache::demoteKv(uint64_t block) {
+  if (!tierWritable()) return LeafReclaim::Impossible;
+  const auto waitOrGiveUp = [this] { return transfersInFlight() ? LeafReclaim::Pending : LeafReclaim::Impossible; };
+  if (!tier_->canDemote()) { // do not discard a copy for a transfer that cannot start yet
+    ++counters_.demotionsRefused;
+    return waitOrGiveUp();
+  }
+  std::shared_ptr<KvTierSlot> slot = acquireTierSlot(kvNeededByStateInUse(block));
+  if (!slot) return waitOrGiveUp();
+  // making room may have taken the states the leaf was kept for; it then goes like any leaf nothing needs
+  if (!worthACopy(block)) return LeafReclaim::Impossible;
+  std::unique_ptr<KvTransfer> ticket = tier_->demote(index_.page(block), slot);
+  if (!ticket) {
+    ++counters_.demotionsRefused;
+    return waitOrGiveUp();
+  }
+  index_.setTransferring(block, true);
+  demotions_.push_back({block, index_.page(block), std::move(ticket), std::move(slot)});
+  ++counters_.demotions;
+  return LeafReclaim::Started;
+}
+
+std::shared_ptr<KvTierSlot> Cache::acquireTierSlot(bool inUse) {
+  for (;;) {
+    if (auto slot = tier_->acquireSlot()) return slot;
+    if (!freeTierSpace(inUse)) return {};
+  }
+}
+
+// A full tier replaces by recency (Cache::freeDiskSpace, Cache.cpp:871-905, as far as KV copies go): the oldest copy
+// of a page that is resident too goes first (it loses nothing), then the oldest tier-only block without children,
+// with the state on it; a block that holds a state in use stays unless the writer is in use itself.
+bool Cache::freeTierSpace(bool inUse) {
+  if (const auto duplicate = index_.tierCandidate(true)) {
+    index_.setSlot(duplicate->block, nullptr);
+    ++counters_.replacedCopies;
+    return true;
+  }
+  auto leaf = index_.tierCandidate(false);
+  while (leaf && !inUse && kvNeededByStateInUse(leaf->block)) leaf = index_.tierCandidate(false, &*leaf);
+  if (!leaf) return false;
+  states_.forget(leaf->block);
+  index_.erase(leaf->block);
+  ++counters_.replacedCopies;
+  ++counters_.evictedBlocks;
+  return true;
+}
+
+// Everything below a block leaves with it, unless some of it is in use or in transfer (Cache::dropDiskSubtree,
+// Cache.cpp:661-672).
+bool Cache::dropTierSubtree(uint64_t block) {
+  const std::vector<uint64_t> below = index_.subtree(block);
+  if (below.empty()) return false;
+  for (uint64_t id : below) {
+    states_.forget(id);
+    index_.erase(id);
+    ++counters_.evictedBlocks;
+  }
+  return true;
+}
+
+// A block whose restore failed matches nothing any more; it and what hangs below it leave as soon as no request
+// holds them (Cache::dropPoisoned, Cache.cpp:674-686).
+void Cache::dropPoisoned() {
+  std::erase_if(poisoned_, [&](uint64_t block) {
+    if (!index_.contains(block)) return true;
+    for (uint64_t below : index_.subtree(block)) {
+      states_.forget(below);
+      index_.erase(below);
+      ++counters_.evictedBlocks;
+    }
+    if (!index_.children(block) && index_.idle(block)) {
+      states_.forget(block);
+      index_.erase(block);
+      ++counters_.evictedBlocks;
+    }
+    return !index_.contains(block);
+  });
 }
 
 // Without composite states every idle leaf is a dead leaf, and this is "the oldest idle leaf first".
@@ -583,17 +750,26 @@ void Cache::publishCompositeState(uint64_t block, uint64_t bytes, bool checkpoin
 std::optional<Cache::Victim> Cache::reclaimOldest(bool inUse, bool keepResumePoint, bool pagesOnly) {
   using Candidate = PrefixIndex::Candidate;
   // A dead leaf (no state restores through it) goes before anything a state needs; one that cannot go now stays
-  // and the next goes.
+  // and the next goes. Once the tier has answered "not now" the scan stops asking it: the leaves that need a write
+  // wait with that one, and those whose page frees at once still go (Cache::reclaimOldest, Cache.cpp:507-550).
+  bool immediate = false;
+  const auto step = [&](uint64_t block) {
+    const LeafReclaim outcome = reclaimKvLeaf(block, immediate);
+    if (outcome == LeafReclaim::Pending) immediate = true;
+    return outcome == LeafReclaim::Started;
+  };
   if (!inUse) {
     const auto dead = [this](uint64_t id) { return !kvNeededByState(id); };
     for (auto leaf = index_.evictionCandidate(nullptr, dead); leaf; leaf = index_.evictionCandidate(&*leaf, dead))
-      if (reclaimKvLeaf(leaf->block) == LeafReclaim::Started) return Victim{true};
+      if (step(leaf->block)) return Victim{true};
   }
   std::optional<StateCandidate> state;
   if (!pagesOnly) state = inUse ? states_.inUseCandidate() : states_.ordinaryCandidate(keepResumePoint);
-  // the leaves a state needs: without a state in RAM on them (one goes first, in the order every victim goes in),
-  // or with one in a page scan
-  const auto needed = [&](uint64_t id) { return (pagesOnly || !states_.stateResident(id)) && kvNeededByStateInUse(id) == inUse; };
+  // the leaves a state needs (the dead ones were asked above): without a state in RAM on them (one goes first, in the
+  // order every victim goes in), or with one in a page scan
+  const auto needed = [&](uint64_t id) {
+    return kvNeededByState(id) && (pagesOnly || !states_.stateResident(id)) && kvNeededByStateInUse(id) == inUse;
+  };
   std::optional<Candidate> kv = index_.evictionCandidate(nullptr, needed);
   while (state || kv) {
     if (state && (!kv || state->lastUsed <= kv->lastUsed)) {
@@ -606,7 +782,7 @@ std::optional<Cache::Victim> Cache::reclaimOldest(bool inUse, bool keepResumePoi
       kv = index_.evictionCandidate(&*kv, needed);
       continue;
     }
-    if (reclaimKvLeaf(kv->block) == LeafReclaim::Started) return Victim{true};
+    if (step(kv->block)) return Victim{true};
     kv = index_.evictionCandidate(&*kv, needed);
   }
   return std::nullopt;
@@ -661,10 +837,14 @@ void Cache::pollTransfers() {
     }
     demotions_.erase(demotions_.begin() + long(i));
   }
+  // Waiting restores start in block order and stop at the first the tier refuses: started ones stay a prefix of each
+  // chain, and a full tier is asked once per poll, not once per waiting block (Cache::pollTransfers, Cache.cpp:938-956).
+  bool refused = false;
   for (size_t i = 0; i < restores_.size();) {
     Transfer &t = restores_[i];
-    if (!t.ticket) { // not started yet: the tier took no more restores then
-      if (tier_->canRestore()) t.ticket = tier_->restore(t.slot, t.page);
+    if (!t.ticket) {
+      if (!refused && tier_->canRestore()) t.ticket = tier_->restore(t.slot, t.page);
+      if (!t.ticket) refused = true;
       ++i;
       continue;
     }
@@ -674,9 +854,11 @@ void Cache::pollTransfers() {
     if (!landed) {
       ++counters_.failedTransfers;
       index_.poison(t.block); // it matches nothing any more; its users recompute
+      poisoned_.push_back(t.block);
     }
     restores_.erase(restores_.begin() + long(i));
   }
+  dropPoisoned();
 }
 
 bool Cache::compactExtent() {

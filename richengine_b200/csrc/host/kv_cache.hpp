@@ -71,9 +71,23 @@ public:
   bool residentLeaf(uint64_t block) const { const Block &b = at(block); return b.page != noPage && !b.residentChildren && !b.activeUsers && !b.transferring; }
   uint64_t lastUsed(uint64_t block) const { return at(block).lastUsed; }
   void setTransferring(uint64_t block, bool value) { at(block).transferring = value; refresh(block); }
-  void setSlot(uint64_t block, std::shared_ptr<KvTierSlot> slot) { at(block).slot = std::move(slot); }
+  // A block without a page is erased, not stripped of its only copy (KvCache::setSlot, KvCache.cpp:379-385).
+  void setSlot(uint64_t block, std::shared_ptr<KvTierSlot> slot);
+  // The oldest idle block whose tier copy can make room in a full tier (KvCache::diskCandidate, KvCache.cpp:486-492):
+  // `duplicate` = a copy of a page that is resident too (dropping it loses nothing), else a tier-only block without
+  // children (dropping it loses the block). `after` continues in (recency, id) order.
+  std::optional<Candidate> tierCandidate(bool duplicate, const Candidate *after = nullptr) const;
+  // Children that live only in the tier (KvCache::hasDiskChildren, KvCache.cpp:294-297).
+  bool tierChildren(uint64_t block) const { const Block &b = at(block); return b.children > b.residentChildren; }
+  // Everything below a block, children before parents; empty when a block below is in use or in transfer
+  // (KvCache::subtree, KvCache.cpp:494-514).
+  std::vector<uint64_t> subtree(uint64_t block) const;
+  bool poisoned(uint64_t block) const { return at(block).poisoned; }
   // Returns the page of a resident leaf that has a tier copy to the pool.
   void dropPage(uint64_t block);
+  // A restore that was never submitted is taken back: the page returns and the block is tier-only again. False when
+  // a resident block below or a request depends on it (KvCache::abandonRestore, KvCache.cpp:411-418).
+  bool abandonRestore(uint64_t block);
   // Gives a host-only block a page whose content follows (restore, or recomputation).
   void adoptPage(uint64_t block, uint32_t page);
   void followPages(const KvPageMoves &moves) noexcept;
@@ -116,6 +130,8 @@ private:
     bool transferring = false, poisoned = false, hadState = false;
     bool listed = false;   // in idleLeaves_ under (listedAt, id)
     uint64_t listedAt = 0;
+    uint8_t tierListed = 0; // 1 = in duplicates_, 2 = in tierLeaves_, under (tierListedAt, id)
+    uint64_t tierListedAt = 0;
   };
   // Keeps idleLeaves_ in step with a block whose page, children, users, transfer or recency changed.
   void refresh(uint64_t block);
@@ -129,6 +145,8 @@ private:
   // The resident leaves no request uses and no transfer touches, oldest first: the order evictions go in. Kept
   // current by every mutator, so a candidate costs a tree step instead of a pass over every block.
   std::set<std::pair<uint64_t, uint64_t>> idleLeaves_; // (last used, id)
+  // Idle blocks with a tier copy, oldest first: copies of resident pages, and tier-only blocks without children.
+  std::set<std::pair<uint64_t, uint64_t>> duplicates_, tierLeaves_;
   uint64_t nextId_ = 1, clock_ = 0, generation_ = 1;
   uint32_t resident_ = 0;
 };
@@ -152,6 +170,7 @@ struct PageTableView {
 struct CacheSnapshot {
   uint32_t requests = 0, residentBlocks = 0, tierBlocks = 0, transfers = 0;
   uint64_t demotions = 0, restores = 0, failedTransfers = 0, evictedBlocks = 0, forkCopies = 0, truncatedPages = 0;
+  uint64_t demotionsRefused = 0, replacedCopies = 0, cancelledRestores = 0;
 };
 
 // How far a reclaim may reach (Cache.hpp: ReclaimClass): states in use, and the KV they restore through, go only to
@@ -239,6 +258,7 @@ public:
   // (Cache.cpp:745-785). Returns the tokens the request resumes after, or Denied/Pending.
   TokenAdmission attachPrefix(uint64_t request, std::span<const uint64_t> blocks, uint32_t *resumeTokens);
   bool restoresPending(uint64_t request) const;
+  int restoreStatus(uint64_t request) const;
 
   // Extension: `child` shares every full committed page of `parent` and gets its own copy of the
   // partial tail page (copy-on-write of the only page both would write). Copies are ordered on the
@@ -258,6 +278,10 @@ public:
   // Empties one extent (KvPool::compactExtent) and re-points every request and block.
   bool compactExtent();
   uint32_t pendingPages() const noexcept { return uint32_t(demotions_.size()); }
+  // A hybrid model resumes a chain only through a composite state: KV no state needs is then not worth a tier copy
+  // and is dropped instead of written, as the reference does (Cache::reclaimKvLeaf, Cache.cpp:629-659). Off (the
+  // default) every block is worth its copy: an attention-only model resumes from KV alone.
+  void setStateCoupled(bool coupled) noexcept { stateCoupled_ = coupled; }
 
   // Seals every landed tier copy into the store with its label (the record Cache::labelBlock keeps,
   // runtime/engine/cache/Cache.cpp:852-870): payload, CRC-32C, KvBlockLabel. The store is rewritten whole and
@@ -288,7 +312,14 @@ private:
     std::shared_ptr<KvTierSlot> slot;
   };
   enum class LeafReclaim : uint8_t { Started, Pending, Impossible };
-  LeafReclaim reclaimKvLeaf(uint64_t block);
+  LeafReclaim reclaimKvLeaf(uint64_t block, bool immediate = false);
+  LeafReclaim demoteKv(uint64_t block);
+  std::shared_ptr<KvTierSlot> acquireTierSlot(bool inUse);
+  bool freeTierSpace(bool inUse);
+  bool dropTierSubtree(uint64_t block);
+  void dropPoisoned();
+  bool tierWritable() const noexcept { return tier_ && tier_->writable(); }
+  bool worthACopy(uint64_t block) const { return !stateCoupled_ || kvNeededByState(block); }
   struct Victim { bool kv = false; };
   std::optional<Victim> reclaimOldest(bool inUse, bool keepResumePoint, bool pagesOnly);
   bool transfersInFlight() const noexcept { return !demotions_.empty() || !restores_.empty(); }
@@ -307,6 +338,8 @@ private:
   uint32_t stateTokens(std::span<const uint64_t> blocks) const;
   std::unordered_map<uint64_t, Request> requests_;
   std::vector<Transfer> demotions_, restores_;
+  std::vector<uint64_t> poisoned_; // blocks whose restore failed, until they and what hangs below them have gone
+  bool stateCoupled_ = false;
   CacheSnapshot counters_;
 };
 

@@ -125,6 +125,18 @@ class Cache:
         return status, resume.value
 
     def restores_pending(self, request) -> bool: return bool(self._check(self._lib.rk_cache_restores_pending(self._handle, request), "restores_pending"))
+    def restore_status(self, request) -> int:
+        """0 = nothing to wait for, 1 = pending, 2 = a read failed (Cache::kvRestoreStatus)."""
+        return self._check(self._lib.rk_cache_restore_status(self._handle, request), "restore_status")
+
+    def set_state_coupled(self, coupled=True): self._lib.rk_cache_set_state_coupled(self._handle, int(coupled))
+    def manual_tier_set(self, transfer_limit, writable=True): self._lib.rk_cache_manual_tier_set(self._handle, transfer_limit, int(writable))
+
+    def tier_counters(self) -> dict:
+        out = (C.c_uint64 * 3)()
+        self._lib.rk_cache_tier_counters(self._handle, out)
+        return dict(zip(["demotions_refused", "replaced_copies", "cancelled_restores"], [int(x) for x in out]))
+
     def fork(self, parent, child, committed) -> int: return self._check(self._lib.rk_cache_fork(self._handle, parent, child, committed), "fork")
     def truncate(self, request, committed, scratch) -> int: return self._check(self._lib.rk_cache_truncate(self._handle, request, committed, scratch), "truncate")
     def reclaim_one(self) -> bool: return bool(self._check(self._lib.rk_cache_reclaim_one(self._handle), "reclaim_one"))

@@ -167,6 +167,10 @@ SIGNATURES = {
     "rk_cache_lookup": (i64, [vp, vp, u32, vp, u32]),
     "rk_cache_attach_prefix": (i32, [vp, u64, vp, u32, C.POINTER(u32)]),
     "rk_cache_restores_pending": (i32, [vp, u64]),
+    "rk_cache_restore_status": (i32, [vp, u64]),
+    "rk_cache_set_state_coupled": (None, [vp, i32]),
+    "rk_cache_manual_tier_set": (None, [vp, u32, i32]),
+    "rk_cache_tier_counters": (None, [vp, vp]),
     "rk_cache_fork": (i32, [vp, u64, u64, u32]),
     "rk_cache_truncate": (i64, [vp, u64, u32, u32]),
     "rk_cache_reclaim_one": (i32, [vp]),
