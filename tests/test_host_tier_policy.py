@@ -272,3 +272,47 @@ def test_a_state_coupled_cache_drops_tails_no_state_needs_and_writes_what_a_stat
     step = cache.evict_one(up_to_in_use=True, pages_only=True)
     assert step["progress"]
     cache.close(); pool.close()
+
+
+def test_reclaim_for_pages_evicts_exactly_the_shortfall():
+    """dev/tests/engine/kv_first_cache_test.cpp:2488-2521 (the case without states)."""
+    pool = KvPool(pages=16, bytes_per_page=100, extent_pages=1, runway_pages=0, budget_pages=8)
+    cache = Cache(pool, Cache.NO_TIER, 0, 0)
+    for leaf in range(8):   # eight one-page leaves fill the budget
+        publish(cache, leaf + 1, np.full(33, 100 + leaf, dtype=np.uint32), 32)
+    assert pool.snapshot()["pages_free"] == 0 and pool.snapshot()["pages_prefix"] == 8
+    assert cache.reclaim_for_pages(3) == 3
+    assert pool.snapshot()["pages_free"] == 3 and pool.snapshot()["pages_prefix"] == 5
+    assert cache.reclaim_for_pages(3) == 0   # nothing more once the shortfall is covered
+    cache.close(); pool.close()
+
+
+def test_a_restore_keeps_the_block_it_extends_and_waits_for_the_room_being_made():
+    """dev/tests/engine/kv_first_cache_test.cpp:2566-2626: the lookup warmed the resident boundary, so the reclaim that
+    makes room for the restore takes an older leaf; while that leaf's copy is on its way the restore is Pending and
+    holds no page."""
+    pool, cache = make(pages=6, extent=2)
+    text, other = prompt(1), prompt(2, 65)
+    chain = publish(cache, 1, text, 128)
+    assert cache.evict_one()["progress"]                        # the last block goes to the tier
+    land(cache)
+    side = publish(cache, 2, other, 64)                         # a newer chain beside it
+    cache.begin_request(3)
+    assert cache.ensure_tokens(3, 32) == GRANTED                # and a request that holds the rest
+    assert pool.snapshot()["pages_free"] == 0
+    found = cache.lookup(text)                                  # tip and resident boundary are now the warmest blocks
+    assert len(found) == 4
+    cache.begin_request(4)
+    assert cache.attach_prefix(4, found)[0] == DENIED           # nothing free, nothing on its way
+    assert cache.reclaim_for_pages(1) == 1                      # making room demotes the OTHER chain's leaf, not the
+    assert cache.block_state(side[1])["transferring"]           # block the restore extends
+    assert resident(cache, chain) == [True, True, True, False]
+    status, _ = cache.attach_prefix(4, found)
+    assert status == PENDING and cache.page_table(4)[0] == []   # a restore without a page waits and holds none meanwhile
+    land(cache)
+    status, resume = cache.attach_prefix(4, found)
+    assert status == GRANTED and resume == 128 and NO_PAGE not in cache.page_table(4)[0]
+    land(cache)
+    assert cache.restore_status(4) == 0
+    cache.end_request(4); cache.end_request(3)
+    cache.close(); pool.close()
