@@ -141,6 +141,14 @@ int rk_cache_state_pin(void *cache, uint64_t block, int pin);
 int rk_cache_state_info(void *cache, uint64_t block, uint64_t *out);
 int rk_cache_state_summary(void *cache, uint64_t *out);
 int rk_cache_evict_one(void *cache, int up_to_in_use, int keep_resume_point, int pages_only, uint64_t *out);
+/* Cache::reclaimOne with its CacheReclaimMode (Cache.cpp:436-449): memory returns as whole extents. mode 0 (release
+ * extents): an empty extent goes as it is, else scattered free pages are gathered until they fill one and that one
+ * goes, else one victim is evicted and the extent it emptied goes with it; 1 (keep extents): evict only; 2 (reuse
+ * pages): evict in a page scan. keep_runway leaves the one empty extent a pass keeps. out[4] as rk_cache_evict_one,
+ * with the bytes of returned extents counted in out[3]. rk_cache_evict_all is Cache::evictAll (Cache.cpp:423-434):
+ * out[2] = made progress, extent bytes returned. */
+int rk_cache_reclaim_step(void *cache, int mode, int up_to_in_use, int keep_resume_point, int keep_runway, uint64_t *out);
+int rk_cache_evict_all(void *cache, uint64_t *out);
 int rk_cache_reclaim_one_state(void *cache, int checkpoints_only, uint64_t for_block);
 int64_t rk_cache_lookup_state(void *cache, const uint32_t *prompt, uint32_t prompt_tokens, uint64_t *blocks_out, uint32_t capacity,
                               uint64_t *out, int record, const void *probe);

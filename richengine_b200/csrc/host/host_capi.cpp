@@ -478,6 +478,25 @@ int rk_cache_evict_one(void *cache, int up_to_in_use, int keep_resume_point, int
     return RK_OK;
   });
 }
+// Cache::reclaimOne(mode, upTo, keepResumePoint, keepRunway): mode 0 = release extents, 1 = keep extents, 2 = reuse
+// pages. out[4] as rk_cache_evict_one, reclaimed bytes counting returned extents too.
+int rk_cache_reclaim_step(void *cache, int mode, int up_to_in_use, int keep_resume_point, int keep_runway, uint64_t *out) {
+  return guarded([&] {
+    if (mode < 0 || mode > 2) throw std::invalid_argument("unknown reclaim mode");
+    const engine::ReclaimStep step = CACHE->reclaimStep(engine::Cache::ReclaimMode(mode), up_to_in_use ? engine::ReclaimClass::InUse : engine::ReclaimClass::Ordinary,
+                                                        keep_resume_point != 0, keep_runway != 0);
+    out[0] = step.madeProgress; out[1] = step.pending; out[2] = step.evictedState; out[3] = step.reclaimedBytes;
+    return RK_OK;
+  });
+}
+// Cache::evictAll: out[2] = made progress, extent bytes returned
+int rk_cache_evict_all(void *cache, uint64_t *out) {
+  return guarded([&] {
+    const engine::ReclaimStep step = CACHE->evictAll();
+    out[0] = step.madeProgress; out[1] = step.reclaimedBytes;
+    return RK_OK;
+  });
+}
 int rk_cache_reclaim_one_state(void *cache, int checkpoints_only, uint64_t for_block) {
   return guarded([&] { return CACHE->reclaimOneState(checkpoints_only != 0, for_block) ? 1 : 0; });
 }

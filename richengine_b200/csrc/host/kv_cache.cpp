@@ -805,6 +805,30 @@ ReclaimStep Cache::evictOne(ReclaimClass upTo, bool keepResumePoint, bool pagesO
   return {false, transfersInFlight(), false, 0};
 }
 
+ReclaimStep Cache::releaseExtent(bool keepRunway) {
+  if (const uint64_t bytes = pool_.reclaimEmptyExtents(keepRunway, 1)) return {true, false, false, bytes};
+  if (compactExtent()) return {true, false, false, pool_.reclaimEmptyExtents(keepRunway, 1)};
+  return {};
+}
+
+ReclaimStep Cache::reclaimStep(ReclaimMode mode, ReclaimClass upTo, bool keepResumePoint, bool keepRunway) {
+  const bool release = mode == ReclaimMode::ReleaseExtents;
+  if (release)
+    if (const ReclaimStep released = releaseExtent(keepRunway); released.madeProgress) return released;
+  ReclaimStep evicted = evictOne(upTo, keepResumePoint, mode == ReclaimMode::ReusePages);
+  if (evicted.madeProgress && release) evicted.reclaimedBytes += pool_.reclaimEmptyExtents(keepRunway, 1);
+  return evicted;
+}
+
+ReclaimStep Cache::evictAll() {
+  uint64_t released = releaseEmptyExtents(false);
+  bool evicted = false;
+  while (evictOne(ReclaimClass::InUse, false, false).madeProgress) evicted = true;
+  do released += releaseEmptyExtents(false);
+  while (compactExtent());
+  return {evicted || released != 0, false, false, released};
+}
+
 bool Cache::reclaimOneState(bool checkpointsOnly, uint64_t forBlock) {
   const auto recycle = [this](const std::optional<StateCandidate> &state) { return state && states_.reclaim(state->block); };
   if (recycle(states_.checkpointCandidate(false))) return true;

@@ -272,6 +272,18 @@ public:
   // lands); without one, or when the block already has a tier copy, drops it at once.
   bool reclaimOne();
   uint32_t reclaimForPages(uint32_t pages);
+  // One step of making room, as the reference's governor asks for it (Cache::reclaimOne with CacheReclaimMode,
+  // Cache.cpp:436-449, releaseExtent :692-698): memory returns as whole extents. ReleaseExtents: an empty extent goes
+  // as it is; else the free pages scattered over the others are gathered until they fill one (compactExtent) and that
+  // one goes; else one victim is evicted (and the extent it may have emptied goes with it). KeepExtents only evicts;
+  // ReusePages evicts in a page scan (a state's buffers give no page). keepRunway leaves the one empty extent a pass
+  // keeps. reclaimedBytes counts extent bytes returned to the device and state bytes freed alike.
+  enum class ReclaimMode : uint8_t { ReleaseExtents, KeepExtents, ReusePages };
+  ReclaimStep reclaimStep(ReclaimMode mode, ReclaimClass upTo, bool keepResumePoint = false, bool keepRunway = false);
+  // Everything unpinned goes before anything moves, then every extent that can be emptied is (Cache::evictAll,
+  // Cache.cpp:423-434).
+  ReclaimStep evictAll();
+  uint64_t releaseEmptyExtents(bool keepRunway) { return pool_.reclaimEmptyExtents(keepRunway, 0xffffffffu); }
   // Retires finished transfers (Cache.cpp:933-1021): a landed demotion drops the page, a failed one
   // keeps it; a landed restore makes the block usable, a failed one poisons it.
   void pollTransfers();
@@ -317,6 +329,7 @@ private:
   std::shared_ptr<KvTierSlot> acquireTierSlot(bool inUse);
   bool freeTierSpace(bool inUse);
   bool dropTierSubtree(uint64_t block);
+  ReclaimStep releaseExtent(bool keepRunway);
   void dropPoisoned();
   bool tierWritable() const noexcept { return tier_ && tier_->writable(); }
   bool worthACopy(uint64_t block) const { return !stateCoupled_ || kvNeededByState(block); }

@@ -169,6 +169,19 @@ class Cache:
         self._check(self._lib.rk_cache_evict_one(self._handle, int(up_to_in_use), int(keep_resume_point), int(pages_only), out), "evict_one")
         return dict(zip(["progress", "pending", "evicted_state", "state_bytes"], [int(x) for x in out]))
 
+    RELEASE_EXTENTS, KEEP_EXTENTS, REUSE_PAGES = 0, 1, 2
+
+    def reclaim_step(self, mode=0, up_to_in_use=True, keep_resume_point=False, keep_runway=False) -> dict:
+        """Cache::reclaimOne(mode, ...): an empty extent, else a gathered one, else one victim."""
+        out = (C.c_uint64 * 4)()
+        self._check(self._lib.rk_cache_reclaim_step(self._handle, mode, int(up_to_in_use), int(keep_resume_point), int(keep_runway), out), "reclaim_step")
+        return dict(zip(["progress", "pending", "evicted_state", "bytes"], [int(x) for x in out]))
+
+    def evict_all(self) -> dict:
+        out = (C.c_uint64 * 2)()
+        self._check(self._lib.rk_cache_evict_all(self._handle, out), "evict_all")
+        return {"progress": bool(out[0]), "bytes": int(out[1])}
+
     def lookup_state(self, prompt, record=False, probe=None) -> dict:
         """Cache::lookup with states: the chain, the deepest state on it (pinned: unpin_state when done), where the
         request resumes, a junction worth a state, a state that was lost. A current Probe's chain is reused."""

@@ -168,6 +168,8 @@ SIGNATURES = {
     "rk_cache_attach_prefix": (i32, [vp, u64, vp, u32, C.POINTER(u32)]),
     "rk_cache_restores_pending": (i32, [vp, u64]),
     "rk_cache_restore_status": (i32, [vp, u64]),
+    "rk_cache_reclaim_step": (i32, [vp, i32, i32, i32, i32, vp]),
+    "rk_cache_evict_all": (i32, [vp, vp]),
     "rk_cache_set_state_coupled": (None, [vp, i32]),
     "rk_cache_manual_tier_set": (None, [vp, u32, i32]),
     "rk_cache_tier_counters": (None, [vp, vp]),

@@ -316,3 +316,137 @@ def test_a_restore_keeps_the_block_it_extends_and_waits_for_the_room_being_made(
     assert cache.restore_status(4) == 0
     cache.end_request(4); cache.end_request(3)
     cache.close(); pool.close()
+
+
+def test_a_reclaim_step_returns_whole_extents_before_it_evicts():
+    """dev/tests/engine/kv_first_cache_test.cpp:2858-2905 (Cache::reclaimOne with ReleaseExtents, Cache.cpp:436-449,
+    692-698): an empty extent goes as it is; scattered free pages are gathered into one before anything is evicted, and
+    requests and cached blocks follow the moved page; when the free pages cover no extent, the step evicts."""
+    pool = KvPool(pages=16, bytes_per_page=100, extent_pages=4, runway_pages=0, budget_pages=16)
+    cache = Cache(pool, Cache.NO_TIER, 0, 0)
+    texts = [prompt(10 + r, 97) for r in range(3)]
+    for r, text in enumerate(texts):              # nine pages over three extents, in order
+        cache.begin_request(r + 1)
+        assert cache.ensure_tokens(r + 1, 96) == GRANTED
+        for i, page in enumerate(cache.page_table(r + 1)[0]):
+            pool.set_page_content(page, 100 * r + i)
+        cache.publish(r + 1, text, 96)
+        cache.end_request(r + 1)
+    cache.begin_request(7)                        # a request that touched a fourth extent and left
+    assert cache.ensure_tokens(7, 32 * 7) == GRANTED
+    cache.end_request(7)
+    assert pool.snapshot()["pages_allocated"] == 16 and pool.snapshot()["pages_prefix"] == 9
+    cache.begin_request(4)                        # the second prompt is in use by a request
+    status, _ = cache.attach_prefix(4, cache.lookup(texts[1]))
+    assert status == GRANTED
+    table, revision, _ = cache.page_table(4)
+    for _ in range(3):                            # the first prompt is evicted: its extent keeps one page of the second
+        assert cache.evict_one()["progress"]
+    assert len(cache.lookup(texts[0])) == 0 and pool.snapshot()["pages_prefix"] == 6
+
+    step = cache.reclaim_step(Cache.RELEASE_EXTENTS)
+    assert step["progress"] and step["bytes"] == 400 and pool.snapshot()["pages_allocated"] == 12   # the empty extent, as it is
+    assert pool.snapshot()["extent_compactions"] == 0
+    step = cache.reclaim_step(Cache.RELEASE_EXTENTS)
+    snapshot = pool.snapshot()                    # scattered free pages are gathered before anything is evicted
+    assert step["progress"] and step["bytes"] == 400 and not step["evicted_state"]
+    assert snapshot["pages_allocated"] == 8 and snapshot["pages_prefix"] == 6 and snapshot["extent_compactions"] == 1
+    moved, revision_after, first_changed = cache.page_table(4)
+    assert revision_after == revision + 1 and first_changed == 0 and moved != table
+    assert [pool.page_content(page) for page in moved] == [100, 101, 102]   # the request follows its moved page
+    cache.end_request(4)
+    cache.begin_request(5)
+    status, _ = cache.attach_prefix(5, cache.lookup(texts[1]))
+    assert status == GRANTED and cache.page_table(5)[0] == moved           # and so does the cached block
+    cache.end_request(5)
+    step = cache.reclaim_step(Cache.RELEASE_EXTENTS)   # the two free pages left cover no extent: the next step evicts
+    assert step["progress"] and step["bytes"] == 0 and pool.snapshot()["pages_prefix"] == 5
+    assert pool.snapshot()["extent_compactions"] == 1
+
+    done = cache.evict_all()                       # everything unpinned goes, then every extent
+    assert done["progress"] and pool.snapshot()["pages_allocated"] == 0 and pool.snapshot()["pages_prefix"] == 0
+    cache.close(); pool.close()
+
+
+def test_evict_all_gathers_what_requests_hold_into_one_extent():
+    """dev/tests/engine/kv_first_cache_test.cpp:3019-3045 (Cache::evictAll): everything unpinned goes before anything
+    moves, so no page is moved and then evicted; what a request holds ends up in one extent."""
+    pool = KvPool(pages=16, bytes_per_page=100, extent_pages=4, runway_pages=0, budget_pages=16)
+    cache = Cache(pool, Cache.NO_TIER, 0, 0)
+    texts = [prompt(20 + r, 97) for r in range(3)]
+    for r, text in enumerate(texts):
+        cache.begin_request(r + 1)
+        assert cache.ensure_tokens(r + 1, 96) == GRANTED
+        for i, page in enumerate(cache.page_table(r + 1)[0]):
+            pool.set_page_content(page, 100 * r + i)
+        cache.publish(r + 1, text, 96)
+        cache.end_request(r + 1)
+    cache.begin_request(4)                        # the second prompt, whose pages straddle two extents, is held
+    assert cache.attach_prefix(4, cache.lookup(texts[1]))[0] == GRANTED
+    for _ in range(3):
+        assert cache.evict_one()["progress"]     # the first prompt goes
+    moves_before = pool.snapshot()["pages_moved"]
+    done = cache.evict_all()
+    snapshot = pool.snapshot()
+    assert done["progress"] and done["bytes"] == 800                       # two of the three extents return
+    assert snapshot["pages_allocated"] == 4 and snapshot["pages_prefix"] == 3 and snapshot["pages_free"] == 1
+    assert snapshot["pages_moved"] - moves_before == 1                     # only the one page outside the gathered extent moved
+    table = cache.page_table(4)[0]
+    assert len({page // 4 for page in table}) == 1
+    assert [pool.page_content(page) for page in table] == [100, 101, 102]
+    assert len(cache.lookup(texts[2])) == 0 and len(cache.lookup(texts[1])) == 3
+    cache.end_request(4)
+    cache.close(); pool.close()
+
+
+def test_compaction_leaves_pages_in_transfer_where_they_are():
+    """dev/tests/engine/kv_first_cache_test.cpp:3047-3126, 3128-3210: a page a restore reads into, or a demotion reads
+    from, stays put: the extent that holds it is passed over although it has the fewest pages, and the next one moves."""
+    pool = KvPool(pages=16, bytes_per_page=100, extent_pages=4, runway_pages=0, budget_pages=16)
+    cache = Cache(pool, Cache.MANUAL_TIER, 8, 8)
+    tiered, plain, kept = prompt(31, 33), prompt(32, 97), prompt(33, 97)
+    publish(cache, 1, tiered, 32)
+    assert cache.evict_one()["progress"]
+    land(cache)                                                  # one block lives in the tier only
+    publish(cache, 2, plain, 96)                                 # three plain blocks on the first extent
+    cache.begin_request(3)
+    assert cache.attach_prefix(3, cache.lookup(tiered))[0] == GRANTED and cache.restore_status(3) == 1
+    reading_into = cache.page_table(3)[0][0]                     # the restore takes the extent's last page and stays in flight
+    assert reading_into // 4 == cache.block_state(cache.lookup(plain)[0])["page"] // 4
+    cache.begin_request(4)
+    assert cache.ensure_tokens(4, 96) == GRANTED
+    for i, page in enumerate(cache.page_table(4)[0]):
+        pool.set_page_content(page, 40 + i)
+    cache.publish(4, kept, 96)
+    cache.end_request(4)
+    assert {cache.block_state(b)["page"] // 4 for b in cache.lookup(kept)} == {reading_into // 4 + 1}
+    cache.set_state_coupled(True)                                # from here on a leaf no state needs is dropped, not written
+    assert len(cache.lookup(kept)) == 3                          # the kept chain is the warmer one: the plain leaves go
+    for _ in range(3):
+        assert cache.evict_one()["progress"]
+    assert len(cache.lookup(plain)) == 0 and len(cache.lookup(kept)) == 3 and cache.snapshot()["transfers"] == 1
+    # the first extent keeps only the page being read into: it holds the fewest pages, and is passed over
+    moved_before = pool.snapshot()["pages_moved"]
+    assert cache.compact_extent()
+    assert pool.snapshot()["pages_moved"] - moved_before == 3 and cache.page_table(3)[0][0] == reading_into
+    land(cache)
+    assert cache.restore_status(3) == 0 and cache.page_table(3)[0][0] == reading_into
+    cache.end_request(3)
+    cache.begin_request(5)
+    assert cache.attach_prefix(5, cache.lookup(kept))[0] == GRANTED
+    table = cache.page_table(5)[0]                               # the kept chain followed its pages, next to the restored one
+    assert {page // 4 for page in table} == {reading_into // 4} and [pool.page_content(page) for page in table] == [40, 41, 42]
+    cache.end_request(5)
+    # the same for a page a demotion reads from
+    cache.set_state_coupled(False)
+    publish(cache, 6, prompt(34, 161), 160)                      # five more pages, spilling into a third extent
+    cache.lookup(prompt(34, 161))
+    while not cache.snapshot()["transfers"]:                     # (the restored block has its copy and goes at once)
+        assert cache.evict_one()["progress"]                     # now the oldest leaf's copy is in flight
+    victim = next(b for b in cache.lookup(kept) if cache.block_state(b)["transferring"])
+    being_written = cache.block_state(victim)["page"]
+    while cache.compact_extent():
+        assert cache.block_state(victim)["page"] == being_written
+    land(cache)
+    assert cache.block_state(victim)["page"] == NO_PAGE
+    cache.close(); pool.close()
