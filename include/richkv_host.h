@@ -68,6 +68,8 @@ int rk_cache_complete_transfer(void *cache, int success); /* tier_mode 2: finish
 void rk_cache_fail_next_transfers(void *cache, uint32_t count); /* tier_mode 1: host-side fault injection */
 /* tier_mode 2: changes how many transfers the tier takes at a time (0 = none) and whether it takes writes at all */
 void rk_cache_manual_tier_set(void *cache, uint32_t transfer_limit, int writable);
+/* tier_mode 2: 1 = one bound on demotions and restores together instead of the pinned-host tier's shares */
+void rk_cache_manual_tier_plain_limits(void *cache, int plain);
 /* out[3] = demotions the tier refused (Cache::demoteKv, Cache.cpp:824-851), tier copies replaced by a full tier
  *          (Cache::freeDiskSpace, Cache.cpp:871-905), restores cancelled before they were submitted (Cache::endRequest) */
 void rk_cache_tier_counters(const void *cache, uint64_t *out);
@@ -144,8 +146,8 @@ int rk_cache_evict_one(void *cache, int up_to_in_use, int keep_resume_point, int
 /* Cache::reclaimOne with its CacheReclaimMode (Cache.cpp:436-449): memory returns as whole extents. mode 0 (release
  * extents): an empty extent goes as it is, else scattered free pages are gathered until they fill one and that one
  * goes, else one victim is evicted and the extent it emptied goes with it; 1 (keep extents): evict only; 2 (reuse
- * pages): evict in a page scan. keep_runway leaves the one empty extent a pass keeps. out[4] as rk_cache_evict_one,
- * with the bytes of returned extents counted in out[3]. rk_cache_evict_all is Cache::evictAll (Cache.cpp:423-434):
+* pages): evict in a page scan. keep_runway leaves the one empty extent a pass keeps. out[4] = made progress, pending,
+ * evicted a state, bytes of the extents returned. rk_cache_evict_all is Cache::evictAll (Cache.cpp:423-434):
  * out[2] = made progress, extent bytes returned. */
 int rk_cache_reclaim_step(void *cache, int mode, int up_to_in_use, int keep_resume_point, int keep_runway, uint64_t *out);
 int rk_cache_evict_all(void *cache, uint64_t *out);

@@ -10,12 +10,18 @@
 //   runtime/metal/abi/KvExtent.h                 offsets and page entries
 //   runtime/ops/PagedAttention.{hpp,cpp}         plans: kernel names, grids, workspaces
 //   runtime/engine/cache/KvPool.{hpp,cpp}        the page allocator
+//   runtime/engine/cache/{Cache,KvCache,StateCache}.{hpp,cpp}  the request cache facade, its block graph and the
+//                                                state cache it couples KV reclaim to, over the reference's own test
+//                                                tier (dev/tests/engine/TestKvTier.hpp)
 #include "Q8PageFormatReference.hpp"
 #include "Fp8PageFormatReference.hpp"
+#include "engine/cache/Cache.hpp"
 #include "engine/cache/KvPool.hpp"
+#include "TestKvTier.hpp"
 #include "ops/PagedAttention.hpp"
 
 #include <cstring>
+#include <map>
 #include <memory>
 #include <vector>
 
@@ -84,6 +90,29 @@ private:
   uint64_t bytes_;
   uint32_t extent_;
   std::vector<bool> allocated_;
+};
+
+// A composite state that is a byte count in RAM, nothing else (the reference's own tests use the same, TestState).
+class ByteState final : public CompositeState {
+public:
+  explicit ByteState(uint64_t bytes) : bytes_(bytes) {}
+  uint64_t bytes() const noexcept override { return bytes_; }
+private:
+  uint64_t bytes_;
+};
+
+// The reference's facade over the budgeted storage and its test tier.
+struct Facade {
+  BudgetStorage storage;
+  engine::KvPool pool;
+  std::unique_ptr<test::TestKvTier> tier;
+  engine::Cache cache;
+  std::map<uint64_t, engine::StateUse> uses;      // one use handle per block
+  std::map<uint64_t, engine::CacheLookup> held;   // lookups kept alive: their leases pin the state
+  uint64_t nextHeld = 1;
+  Facade(uint32_t pages, uint64_t bytes, uint32_t extent, uint32_t runway, uint64_t budget, bool withTier)
+      : storage(pages, bytes, extent), pool((storage.budget = budget, storage), runway),
+        tier(withTier ? std::make_unique<test::TestKvTier>() : nullptr), cache(pool, tier.get(), nullptr) {}
 };
 
 struct Pool {
@@ -266,4 +295,127 @@ void ref_pool_snapshot(void *pool, uint64_t *out) {
   out[7] = s.extentReleases; out[8] = s.extentCompactions; out[9] = s.pagesMoved;
 }
 
+
+// ---- the reference's request cache facade -------------------------------------------------
+#define FACADE (static_cast<Facade *>(facade))
+void *ref_cache_create(uint32_t pages, uint64_t bytes_per_page, uint32_t extent_pages, uint32_t runway_pages,
+                       uint64_t budget_pages, int with_tier, uint32_t tier_capacity, uint32_t transfer_limit) {
+  try {
+    auto f = std::make_unique<Facade>(pages, bytes_per_page, extent_pages, runway_pages, budget_pages, with_tier != 0);
+    if (f->tier) { f->tier->capacity = tier_capacity; f->tier->transferLimit = transfer_limit; }
+    return f.release();
+  } catch (...) { return nullptr; }
+}
+void ref_cache_destroy(void *facade) {
+  if (!facade) return;
+  FACADE->held.clear();
+  FACADE->uses.clear();
+  if (FACADE->tier) FACADE->tier->complete();
+  delete FACADE;
+}
+void ref_cache_tier_set(void *facade, uint32_t transfer_limit, int writable) {
+  if (!FACADE->tier) return;
+  FACADE->tier->transferLimit = transfer_limit;
+  FACADE->tier->writableFile = writable != 0;
+}
+void ref_cache_tier_complete(void *facade, int success) { if (FACADE->tier) FACADE->tier->complete(success != 0); }
+int ref_cache_begin(void *facade, uint64_t request) { try { FACADE->cache.beginRequest(request); return 0; } catch (...) { return -1; } }
+int ref_cache_end(void *facade, uint64_t request) { try { FACADE->cache.endRequest(request); return 0; } catch (...) { return -1; } }
+// 0 granted, 1 denied, 2 pending, -1 threw
+int ref_cache_ensure(void *facade, uint64_t request, uint64_t tokens) {
+  try { return int(FACADE->cache.ensureTokens(request, tokens).failure); } catch (...) { return -1; }
+}
+int64_t ref_cache_page_table(void *facade, uint64_t request, uint32_t *pages, uint32_t capacity, uint64_t *revision, uint32_t *first_changed) {
+  try {
+    const auto view = FACADE->cache.pageTable(request);
+    for (size_t i = 0; i < view.pages.size() && i < capacity; ++i) pages[i] = view.pages[i];
+    *revision = view.revision; *first_changed = view.firstChanged;
+    return int64_t(view.pages.size());
+  } catch (...) { return -1; }
+}
+int ref_cache_publish(void *facade, uint64_t request, const uint32_t *tokens, uint32_t count, uint32_t committed) {
+  try { FACADE->cache.publishCommittedBlocks(request, {tokens, count}, committed, {}); return 0; } catch (...) { return -1; }
+}
+uint64_t ref_cache_block_at(void *facade, uint64_t request, uint32_t boundary) {
+  try { return FACADE->cache.blockAt(request, boundary); } catch (...) { return 0; }
+}
+// out[5] = kv boundary, state block, resume boundary, junction boundary, lost state. hold != 0 keeps the lookup (its
+// lease pins the state) and returns its handle in out[5]; attach_to != 0 gives that request the chain (restoreRequest)
+// and reports the admission in out[6] (0 granted, 1 denied, 2 pending).
+int ref_cache_lookup(void *facade, const uint32_t *prompt, uint32_t count, int record, int hold, uint64_t attach_to, uint64_t *out,
+                     const void *probe) {
+  try {
+    engine::CacheLookup found = FACADE->cache.lookup({prompt, count}, {}, static_cast<const engine::CacheProbe *>(probe));
+    out[0] = found.kvBoundary; out[1] = found.state ? found.state->kvBlock() : 0; out[2] = found.resumeBoundary();
+    out[3] = found.junctionBoundary; out[4] = found.lostState; out[5] = 0; out[6] = 0;
+    if (record) FACADE->cache.recordLookup(found);
+    if (attach_to) out[6] = uint64_t(FACADE->cache.restoreRequest(attach_to, found).failure);
+    if (hold) { out[5] = FACADE->nextHeld; FACADE->held.emplace(FACADE->nextHeld++, std::move(found)); }
+    return 0;
+  } catch (...) { return -1; }
+}
+void ref_cache_release_lookup(void *facade, uint64_t handle) { FACADE->held.erase(handle); }
+void *ref_cache_probe_create(void *facade, const uint32_t *prompt, uint32_t count) {
+  try { return new engine::CacheProbe(FACADE->cache.probe({prompt, count}, {})); } catch (...) { return nullptr; }
+}
+int ref_cache_probe_refresh(void *facade, void *probe, const uint32_t *prompt, uint32_t count) {
+  try { FACADE->cache.refresh(*static_cast<engine::CacheProbe *>(probe), {prompt, count}, {}); return 0; } catch (...) { return -1; }
+}
+uint32_t ref_cache_probe_cached_tokens(const void *probe) { return static_cast<const engine::CacheProbe *>(probe)->cachedTokens(); }
+void ref_cache_probe_destroy(void *probe) { delete static_cast<engine::CacheProbe *>(probe); }
+int ref_cache_restore_status(void *facade, uint64_t request) {
+  try { return int(FACADE->cache.kvRestoreStatus(request)); } catch (...) { return -1; }
+}
+int ref_cache_publish_state(void *facade, uint64_t block, uint64_t bytes, int checkpoint) {
+  try { // as the engine does: the state that is there is reused, a publication follows only without one
+    if (!FACADE->cache.reuseCompositeState(block, checkpoint != 0))
+      FACADE->cache.publishCompositeState(block, std::make_shared<ByteState>(bytes), checkpoint != 0);
+    return 0;
+  } catch (...) { return -1; }
+}
+int ref_cache_use_state(void *facade, uint64_t block, int use) {
+  try {
+    if (use) FACADE->uses[block] = FACADE->cache.useState(block);
+    else FACADE->uses.erase(block);
+    return 0;
+  } catch (...) { return -1; }
+}
+// out[4] = made progress, pending, evicted a state, reclaimed bytes
+int ref_cache_evict_one(void *facade, int up_to_in_use, int keep_resume_point, int pages_only, uint64_t *out) {
+  try {
+    // evictOne is private: reclaimOne(KeepExtents | ReusePages) is evictOne(upTo, keepResumePoint, pagesOnly)
+    const auto step = FACADE->cache.reclaimOne(pages_only ? engine::CacheReclaimMode::ReusePages : engine::CacheReclaimMode::KeepExtents,
+                                               up_to_in_use ? engine::ReclaimClass::InUse : engine::ReclaimClass::Ordinary, keep_resume_point != 0);
+    out[0] = step.madeProgress; out[1] = step.pending; out[2] = step.evictedState; out[3] = step.reclaimedBytes;
+    return 0;
+  } catch (...) { return -1; }
+}
+// mode 0 release extents, 1 keep extents, 2 reuse pages
+int ref_cache_reclaim_step(void *facade, int mode, int up_to_in_use, int keep_resume_point, int keep_runway, uint64_t *out) {
+  try {
+    const engine::CacheReclaimMode modes[3] = {engine::CacheReclaimMode::ReleaseExtents, engine::CacheReclaimMode::KeepExtents, engine::CacheReclaimMode::ReusePages};
+    const auto step = FACADE->cache.reclaimOne(modes[mode], up_to_in_use ? engine::ReclaimClass::InUse : engine::ReclaimClass::Ordinary,
+                                               keep_resume_point != 0, keep_runway != 0);
+    out[0] = step.madeProgress; out[1] = step.pending; out[2] = step.evictedState; out[3] = step.reclaimedBytes;
+    return 0;
+  } catch (...) { return -1; }
+}
+int ref_cache_reclaim_one_state(void *facade, int checkpoints_only, uint64_t for_block) {
+  try { return FACADE->cache.reclaimOneState(checkpoints_only != 0, for_block, false) ? 1 : 0; } catch (...) { return -1; }
+}
+int ref_cache_poll(void *facade) { try { return FACADE->cache.pollTransfers() ? 1 : 0; } catch (...) { return -1; } }
+// out[12] = pagesAllocated, pagesFree, pagesActive, pagesPrefix, state entries, state bytes, pinned states,
+//           tier blocks, pending pages, demotions, restores, demotions refused; out[12..15] = KV tokens hit, lazy
+//           junctions, lost-state misses, pages hashed by probes
+void ref_cache_snapshot(void *facade, uint64_t *out) {
+  const auto s = FACADE->cache.snapshot();
+  out[0] = s.pool.pagesAllocated; out[1] = s.pool.pagesFree; out[2] = s.pool.pagesActive; out[3] = s.pool.pagesPrefix;
+  out[4] = s.stateCache.entries; out[5] = s.stateCache.bytes; out[6] = s.stateCache.pinned;
+  out[7] = s.kvTier.diskBlocks; out[8] = s.kvTier.pendingPages; out[9] = s.kvTier.demotions; out[10] = s.kvTier.restores;
+  out[11] = s.kvTier.demotionsRefused;
+  out[12] = s.lookup.kvHitTokens; out[13] = s.lookup.lazyJunctions; out[14] = s.lookup.lostStateMisses; out[15] = s.lookup.probeHashedBlocks;
+}
+#undef FACADE
+
 } // extern "C"
+

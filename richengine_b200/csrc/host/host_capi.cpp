@@ -36,8 +36,11 @@ public:
         payloads_(slots), limit_(transfers) {}
   uint64_t slotBytes() const noexcept override { return storage_.bytesPerPage(); }
   bool writable() const noexcept override { return writable_; }
-  bool canDemote() const noexcept override { return demotions_ < std::max(1u, limit_ / 2) && pending_.size() < limit_ && writable_; }
-  bool canRestore() const noexcept override { return restores_ < std::max(1u, limit_ - limit_ / 4) && pending_.size() < limit_; }
+  // The shares of the pinned-host tier (demotions at most half, restores at most three quarters of the transfers in
+  // flight), or, with plain limits, one bound on both kinds together as the reference's test tier has it
+  // (dev/tests/engine/TestKvTier.hpp:35-36).
+  bool canDemote() const noexcept override { return (plain_ || demotions_ < std::max(1u, limit_ / 2)) && pending_.size() < limit_ && writable_; }
+  bool canRestore() const noexcept override { return (plain_ || restores_ < std::max(1u, limit_ - limit_ / 4)) && pending_.size() < limit_; }
   std::shared_ptr<engine::KvTierSlot> acquireSlot() override {
     for (uint32_t i = 0; i < used_.size(); ++i)
       if (!used_[i]) { used_[i] = 1; return std::make_shared<Slot>(this, i); }
@@ -79,6 +82,7 @@ public:
     return slot;
   }
   void set(uint32_t limit, bool writable) noexcept { limit_ = limit; writable_ = writable; }
+  void setPlainLimits(bool plain) noexcept { plain_ = plain; }
   bool complete(bool success) {
     if (pending_.empty()) return false;
     auto state = pending_.front();
@@ -120,7 +124,7 @@ private:
   mutable std::vector<std::vector<uint8_t>> payloads_;
   std::deque<std::shared_ptr<State>> pending_;
   uint32_t limit_, demotions_ = 0, restores_ = 0;
-  bool writable_ = true;
+  bool writable_ = true, plain_ = false;
 };
 
 struct CacheHandle {
@@ -296,6 +300,10 @@ int rk_cache_complete_transfer(void *cache, int success) {
 void rk_cache_manual_tier_set(void *cache, uint32_t transfer_limit, int writable) {
   auto *h = static_cast<CacheHandle *>(cache);
   if (h->manual) h->manual->set(transfer_limit, writable != 0);
+}
+void rk_cache_manual_tier_plain_limits(void *cache, int plain) {
+  auto *h = static_cast<CacheHandle *>(cache);
+  if (h->manual) h->manual->setPlainLimits(plain != 0);
 }
 void rk_cache_tier_counters(const void *cache, uint64_t *out) {
   const auto s = static_cast<const CacheHandle *>(cache)->cache->snapshot();

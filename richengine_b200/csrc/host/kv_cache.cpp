@@ -158,11 +158,27 @@ PrefixIndex::Match PrefixIndex::insert(uint64_t parent, std::span<const uint32_t
   return {id, page};
 }
 
-void PrefixIndex::retainActive(uint64_t block) { ++at(block).activeUsers; refresh(block); }
+// Recency as the reference keeps it (KvCache::retainActive / releaseActive, KvCache.cpp:227-249): a block is stamped
+// when a user takes it; a released leaf is the newest, a parent keeps the recency its children pass on.
+void PrefixIndex::retainActive(uint64_t block) {
+  Block &entry = at(block);
+  ++entry.activeUsers;
+  entry.lastUsed = ++clock_;
+  refresh(block);
+}
 void PrefixIndex::releaseActive(uint64_t block) noexcept {
   auto found = blocks_.find(block);
-  if (found != blocks_.end() && found->second.activeUsers) --found->second.activeUsers;
+  if (found == blocks_.end()) return;
+  Block &entry = found->second;
+  if (entry.activeUsers) --entry.activeUsers;
+  if (!entry.activeUsers && !entry.children) entry.lastUsed = ++clock_;
   refresh(block);
+}
+// A parent that has just become a leaf no request holds is as warm as the child it lost (KvCache::inherit,
+// KvCache.cpp:441-446).
+void PrefixIndex::inherit(Block &parent, uint64_t lastUsed) noexcept {
+  const bool leaf = parent.page != noPage ? !parent.residentChildren : !parent.children;
+  if (leaf && !parent.activeUsers) parent.lastUsed = std::max(parent.lastUsed, lastUsed);
 }
 void PrefixIndex::touch(uint64_t block) noexcept {
   auto found = blocks_.find(block);
@@ -192,7 +208,7 @@ void PrefixIndex::dropPage(uint64_t block) {
   if (entry.parent) {
     Block &above = at(entry.parent);
     --above.residentChildren;
-    above.lastUsed = std::max(above.lastUsed, entry.lastUsed); // a new leaf is as warm as what it lost
+    inherit(above, entry.lastUsed);
     refresh(entry.parent);
   }
   refresh(block);
@@ -289,7 +305,7 @@ void PrefixIndex::erase(uint64_t block) {
     Block &above = at(entry.parent);
     --above.children;
     if (entry.page != noPage) --above.residentChildren;
-    above.lastUsed = std::max(above.lastUsed, entry.lastUsed);
+    inherit(above, entry.lastUsed);
     refresh(entry.parent);
   }
   const auto [first, last] = index_.equal_range(entry.hash);
@@ -816,6 +832,7 @@ ReclaimStep Cache::reclaimStep(ReclaimMode mode, ReclaimClass upTo, bool keepRes
   if (release)
     if (const ReclaimStep released = releaseExtent(keepRunway); released.madeProgress) return released;
   ReclaimStep evicted = evictOne(upTo, keepResumePoint, mode == ReclaimMode::ReusePages);
+  evicted.reclaimedBytes = 0; // a state's buffers return to the model's pool, not to the device: only extents count here
   if (evicted.madeProgress && release) evicted.reclaimedBytes += pool_.reclaimEmptyExtents(keepRunway, 1);
   return evicted;
 }

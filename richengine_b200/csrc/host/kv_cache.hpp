@@ -135,6 +135,7 @@ private:
   };
   // Keeps idleLeaves_ in step with a block whose page, children, users, transfer or recency changed.
   void refresh(uint64_t block);
+  static void inherit(Block &parent, uint64_t lastUsed) noexcept;
   Block &at(uint64_t block);
   const Block &at(uint64_t block) const;
 
@@ -184,7 +185,11 @@ public:
       : pool_(pool), storage_(storage), tier_(tier), index_(pool),
         states_([this](uint64_t block, int states, int inUse) { index_.adjustStatesBelow(block, states, inUse); },
                 [this] { return index_.tick(); },
-                [this](uint64_t block) { if (index_.contains(block)) index_.noteState(block); }) {}
+                [this](uint64_t block) { if (index_.contains(block)) index_.noteState(block); },
+                [this](uint64_t block, bool held) {
+                  if (!index_.contains(block)) return;
+                  if (held) index_.retainActive(block); else index_.releaseActive(block);
+                }) {}
   ~Cache();
 
   // ---- composite states and the reclaim order they impose (runtime/engine/cache/Cache.cpp:451-628) ----------------
@@ -277,7 +282,8 @@ public:
   // as it is; else the free pages scattered over the others are gathered until they fill one (compactExtent) and that
   // one goes; else one victim is evicted (and the extent it may have emptied goes with it). KeepExtents only evicts;
   // ReusePages evicts in a page scan (a state's buffers give no page). keepRunway leaves the one empty extent a pass
-  // keeps. reclaimedBytes counts extent bytes returned to the device and state bytes freed alike.
+  // keeps. reclaimedBytes counts the bytes of the extents returned to the device (a step that evicts a state says so
+  // in evictedState; its buffers go back to the model's pool).
   enum class ReclaimMode : uint8_t { ReleaseExtents, KeepExtents, ReusePages };
   ReclaimStep reclaimStep(ReclaimMode mode, ReclaimClass upTo, bool keepResumePoint = false, bool keepRunway = false);
   // Everything unpinned goes before anything moves, then every extent that can be emptied is (Cache::evictAll,

@@ -14,11 +14,9 @@ void StateCache::publish(uint64_t block, uint64_t bytes, bool checkpoint) {
   if (!block) throw std::invalid_argument("a composite state sits on a KV block");
   auto found = states_.find(block);
   if (found != states_.end()) {
-    State &state = found->second;
-    bytes_ += bytes - state.bytes;
-    state.bytes = bytes;
+    State &state = found->second; // the copy that is there is reused: the same block is the same content
     state.checkpoint = state.checkpoint && checkpoint; // an ordinary state stays ordinary
-    state.lastUsed = clock_();
+    if (!state.pins) state.lastUsed = clock_();
     if (!state.checkpoint && note_) note_(block);
     return;
   }
@@ -54,7 +52,7 @@ void StateCache::unuse(uint64_t block) {
   uses_.erase(use);
   auto found = states_.find(block);
   if (found == states_.end()) return;
-  found->second.lastUsed = clock_(); // the conversation resumes there next
+  if (!found->second.pins) found->second.lastUsed = clock_(); // the conversation resumes there next
   adjust_(block, 0, -1);
 }
 std::vector<uint64_t> StateCache::usedStates() const {
@@ -69,11 +67,13 @@ void StateCache::pin(uint64_t block) {
   auto found = states_.find(block);
   if (found == states_.end()) throw std::out_of_range("no composite state at this block");
   ++found->second.pins;
+  if (hold_) hold_(block, true);
 }
 void StateCache::unpin(uint64_t block) {
   auto found = states_.find(block);
   if (found == states_.end() || !found->second.pins) throw std::logic_error("the state at this block is not pinned");
-  --found->second.pins;
+  if (!--found->second.pins) found->second.lastUsed = clock_();
+  if (hold_) hold_(block, false);
 }
 
 uint64_t StateCache::resumePoint() const noexcept {
@@ -111,6 +111,16 @@ uint32_t StateCache::evictableStates(bool withInUse) const noexcept {
   for (const auto &[block, state] : states_)
     if (!state.pins && (withInUse || !inUse(block))) ++count;
   return count;
+}
+
+void StateCache::forget(uint64_t block) {
+  auto found = states_.find(block);
+  if (found == states_.end()) return;
+  // a pinned state leaves too (the block under it is gone): its pins' holds on the block go with it
+  for (uint32_t pin = 0; pin < found->second.pins; ++pin)
+    if (hold_) hold_(block, false);
+  found->second.pins = 0;
+  reclaim(block);
 }
 
 bool StateCache::reclaim(uint64_t block, uint64_t *freed) {

@@ -30,11 +30,16 @@ public:
   // state's life (KvCache::noteState, called from StateCache::makeOrdinary), so that a later lookup can tell a state
   // that was lost from one that never was.
   using NoteReusable = std::function<void(uint64_t block)>;
-  StateCache(AdjustBelow adjust, Clock clock, NoteReusable note = {})
-      : adjust_(std::move(adjust)), clock_(std::move(clock)), note_(std::move(note)) {}
+  // hold(block, true/false): a pin takes / gives back an active reference on the state's KV block, so that the block
+  // is no eviction candidate while a restore reads the state (StateCache::acquireBlock / release: kv_.retainActive,
+  // kv_.releaseActive).
+  using Hold = std::function<void(uint64_t block, bool held)>;
+  StateCache(AdjustBelow adjust, Clock clock, NoteReusable note = {}, Hold hold = {})
+      : adjust_(std::move(adjust)), clock_(std::move(clock)), note_(std::move(note)), hold_(std::move(hold)) {}
 
-  // Publishes a RAM copy at a block (StateCache::publishCompositeState). A normal boundary upgrades a checkpoint;
-  // a checkpoint cannot downgrade an ordinary state.
+  // Publishes a RAM copy at a block (StateCache::publishCompositeState), or reuses the one that is there
+  // (StateCache::reuseCompositeState: the copy and its size stay, an ordinary boundary upgrades a checkpoint, a
+  // checkpoint cannot downgrade an ordinary state, and the recency moves unless a restore pins the state).
   void publish(uint64_t block, uint64_t bytes, bool checkpoint);
   bool contains(uint64_t block) const noexcept { return states_.count(block) != 0; }
   bool ordinary(uint64_t block) const noexcept;
@@ -46,7 +51,8 @@ public:
   void unuse(uint64_t block);
   bool inUse(uint64_t block) const noexcept { auto f = uses_.find(block); return f != uses_.end() && f->second > 0; }
   std::vector<uint64_t> usedStates() const;
-  // Pins (a restore in progress): a pinned state is no candidate.
+  // Pins (a restore in progress): a pinned state is no candidate and holds its KV block; when the last pin goes the
+  // state becomes the newest of its class (StateCache::release).
   void pin(uint64_t block);
   void unpin(uint64_t block);
 
@@ -61,7 +67,8 @@ public:
   // or absent. Returns the bytes freed through `freed`.
   bool reclaim(uint64_t block, uint64_t *freed = nullptr);
   // The block leaves the KV index: its state goes with it.
-  void forget(uint64_t block) { reclaim(block); uses_.erase(block); }
+  // A use outlives it: the request that resumes from the block still holds its handle.
+  void forget(uint64_t block);
   uint64_t residentBytes() const noexcept { return bytes_; }
   size_t size() const noexcept { return states_.size(); }
 
@@ -74,6 +81,7 @@ private:
   AdjustBelow adjust_;
   Clock clock_;
   NoteReusable note_;
+  Hold hold_;
   std::unordered_map<uint64_t, State> states_;
   std::unordered_map<uint64_t, uint32_t> uses_;
   uint64_t bytes_ = 0;

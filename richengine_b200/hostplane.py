@@ -130,6 +130,7 @@ class Cache:
         return self._check(self._lib.rk_cache_restore_status(self._handle, request), "restore_status")
 
     def set_state_coupled(self, coupled=True): self._lib.rk_cache_set_state_coupled(self._handle, int(coupled))
+    def manual_tier_plain_limits(self, plain=True): self._lib.rk_cache_manual_tier_plain_limits(self._handle, int(plain))
     def manual_tier_set(self, transfer_limit, writable=True): self._lib.rk_cache_manual_tier_set(self._handle, transfer_limit, int(writable))
 
     def tier_counters(self) -> dict:

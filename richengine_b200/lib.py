@@ -172,6 +172,7 @@ SIGNATURES = {
     "rk_cache_evict_all": (i32, [vp, vp]),
     "rk_cache_set_state_coupled": (None, [vp, i32]),
     "rk_cache_manual_tier_set": (None, [vp, u32, i32]),
+    "rk_cache_manual_tier_plain_limits": (None, [vp, i32]),
     "rk_cache_tier_counters": (None, [vp, vp]),
     "rk_cache_fork": (i32, [vp, u64, u64, u32]),
     "rk_cache_truncate": (i64, [vp, u64, u32, u32]),

@@ -81,6 +81,32 @@ def reference():
         r.ref_pool_reclaim.restype, r.ref_pool_reclaim.argtypes = u64, [vp, C.c_int, u32]
         r.ref_pool_compact.restype, r.ref_pool_compact.argtypes = C.c_int64, [vp, vp, u32, vp]
         r.ref_pool_snapshot.restype, r.ref_pool_snapshot.argtypes = None, [vp, vp]
+        if hasattr(r, "ref_cache_create"):  # the request cache facade (a library built before it was added has none)
+            i32, i64 = C.c_int, C.c_int64
+            r.ref_cache_create.restype, r.ref_cache_create.argtypes = vp, [u32, u64, u32, u32, u64, i32, u32, u32]
+            r.ref_cache_destroy.restype, r.ref_cache_destroy.argtypes = None, [vp]
+            r.ref_cache_tier_set.restype, r.ref_cache_tier_set.argtypes = None, [vp, u32, i32]
+            r.ref_cache_tier_complete.restype, r.ref_cache_tier_complete.argtypes = None, [vp, i32]
+            r.ref_cache_begin.restype, r.ref_cache_begin.argtypes = i32, [vp, u64]
+            r.ref_cache_end.restype, r.ref_cache_end.argtypes = i32, [vp, u64]
+            r.ref_cache_ensure.restype, r.ref_cache_ensure.argtypes = i32, [vp, u64, u64]
+            r.ref_cache_page_table.restype, r.ref_cache_page_table.argtypes = i64, [vp, u64, vp, u32, vp, vp]
+            r.ref_cache_publish.restype, r.ref_cache_publish.argtypes = i32, [vp, u64, vp, u32, u32]
+            r.ref_cache_block_at.restype, r.ref_cache_block_at.argtypes = u64, [vp, u64, u32]
+            r.ref_cache_lookup.restype, r.ref_cache_lookup.argtypes = i32, [vp, vp, u32, i32, i32, u64, vp, vp]
+            r.ref_cache_probe_create.restype, r.ref_cache_probe_create.argtypes = vp, [vp, vp, u32]
+            r.ref_cache_probe_refresh.restype, r.ref_cache_probe_refresh.argtypes = i32, [vp, vp, vp, u32]
+            r.ref_cache_probe_cached_tokens.restype, r.ref_cache_probe_cached_tokens.argtypes = u32, [vp]
+            r.ref_cache_probe_destroy.restype, r.ref_cache_probe_destroy.argtypes = None, [vp]
+            r.ref_cache_release_lookup.restype, r.ref_cache_release_lookup.argtypes = None, [vp, u64]
+            r.ref_cache_restore_status.restype, r.ref_cache_restore_status.argtypes = i32, [vp, u64]
+            r.ref_cache_publish_state.restype, r.ref_cache_publish_state.argtypes = i32, [vp, u64, u64, i32]
+            r.ref_cache_use_state.restype, r.ref_cache_use_state.argtypes = i32, [vp, u64, i32]
+            r.ref_cache_evict_one.restype, r.ref_cache_evict_one.argtypes = i32, [vp, i32, i32, i32, vp]
+            r.ref_cache_reclaim_step.restype, r.ref_cache_reclaim_step.argtypes = i32, [vp, i32, i32, i32, i32, vp]
+            r.ref_cache_reclaim_one_state.restype, r.ref_cache_reclaim_one_state.argtypes = i32, [vp, i32, u64]
+            r.ref_cache_poll.restype, r.ref_cache_poll.argtypes = i32, [vp]
+            r.ref_cache_snapshot.restype, r.ref_cache_snapshot.argtypes = None, [vp, vp]
         _reference = r
     return _reference
 
