@@ -70,13 +70,15 @@ void rk_cache_fail_next_transfers(void *cache, uint32_t count); /* tier_mode 1: 
 void rk_cache_manual_tier_set(void *cache, uint32_t transfer_limit, int writable);
 /* tier_mode 2: 1 = one bound on demotions and restores together instead of the pinned-host tier's shares */
 void rk_cache_manual_tier_plain_limits(void *cache, int plain);
-/* out[3] = demotions the tier refused (Cache::demoteKv, Cache.cpp:824-851), tier copies replaced by a full tier
- *          (Cache::freeDiskSpace, Cache.cpp:871-905), restores cancelled before they were submitted (Cache::endRequest) */
+/* out[6] = demotions the tier refused (Cache::demoteKv, Cache.cpp:824-851), tier copies replaced by a full tier
+ *          (Cache::freeDiskSpace, Cache.cpp:871-905), restores cancelled before they were submitted (Cache::endRequest),
+ *          pages whose demotion is in flight, demotions and restores that landed (rk_cache_snapshot counts the started) */
 void rk_cache_tier_counters(const void *cache, uint64_t *out);
 /* out[10] = requests, residentBlocks, tierBlocks, transfers, demotions, restores, failedTransfers,
  *           evictedBlocks, forkCopies, truncatedPages */
 void rk_cache_snapshot(const void *cache, uint64_t *out);
-/* Block state: out[4] = page (0xffffffff = none), has tier copy, transferring, last used. -1 if unknown. */
+/* Block state: out[5] = page (0xffffffff = none), has tier copy, transferring, last used, poisoned (a read of it
+ * failed: it matches nothing and leaves once nothing hangs on it). -1 if unknown. */
 int rk_cache_block_state(const void *cache, uint64_t block, uint64_t *out);
 
 /* ---- KV that survives a restart: slot file + record file --------------------------------------------
@@ -118,7 +120,8 @@ int rk_cache_adopt(void *cache, void *store, uint64_t *out);
  * checkpoints first (not in a page scan), then KV leaves no state needs, then ordinary states and the leaves under
  * them by shared recency, states in use and their KV last and only up_to_in_use; out[4] = made progress, pending,
  * evicted a state, state bytes freed. rk_cache_reclaim_one_state is Cache::reclaimOneState (1 = a state went).
- * rk_cache_state_info out[6] = contains, ordinary, in use, bytes, KV needed by a state, KV needed by a state in use;
+ * rk_cache_state_info out[7] = contains, ordinary, in use, bytes, KV needed by a state, KV needed by a state in use,
+ * has a RAM copy;
  * rk_cache_state_summary out[4] = states, resident bytes, evictable states, resume point.
  * rk_cache_lookup_state is the lookup a hybrid model's admission makes (Cache::lookup, Cache.cpp:236-272; CacheLookup,
  * Cache.hpp:20-36): the chain as rk_cache_lookup, out[5] = KV boundary in tokens, the deepest state's block on the
@@ -138,6 +141,9 @@ int rk_cache_adopt(void *cache, void *store, uint64_t *out);
  * rk_cache_probe_refresh (RK_ERR_INVALID). */
 int64_t rk_cache_block_at(void *cache, uint64_t request, uint32_t tokens);
 int rk_cache_state_publish(void *cache, uint64_t block, uint64_t bytes, int checkpoint);
+/* A state whose only copy the model stores elsewhere (StateCache::publishStateToDisk, StateCache.cpp:189-214): it costs
+ * no RAM and is no reclaim candidate, and the KV it restores through stays worth a tier copy. Published once per block. */
+int rk_cache_state_publish_stored(void *cache, uint64_t block, uint64_t bytes, int checkpoint);
 int rk_cache_state_use(void *cache, uint64_t block, int use);
 int rk_cache_state_pin(void *cache, uint64_t block, int pin);
 int rk_cache_state_info(void *cache, uint64_t block, uint64_t *out);

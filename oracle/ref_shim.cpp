@@ -101,6 +101,22 @@ private:
   uint64_t bytes_;
 };
 
+// A state whose only copy is stored elsewhere, and the ticket of a write that has landed already.
+class StoredState final : public CompositeState {
+public:
+  explicit StoredState(uint64_t bytes) : bytes_(bytes) {}
+  uint64_t bytes() const noexcept override { return bytes_; }
+  uint64_t residentBytes() const noexcept override { return 0; }
+private:
+  uint64_t bytes_;
+};
+struct LandedWrite final : StateOffload {
+  std::shared_ptr<const CompositeState> copy;
+  bool ready() const noexcept override { return true; }
+  bool finish() override { return true; }
+  const std::shared_ptr<const CompositeState> &state() const noexcept override { return copy; }
+};
+
 // The reference's facade over the budgeted storage and its test tier.
 struct Facade {
   BudgetStorage storage;
@@ -373,6 +389,17 @@ int ref_cache_publish_state(void *facade, uint64_t block, uint64_t bytes, int ch
     return 0;
   } catch (...) { return -1; }
 }
+// StateCache::publishStateToDisk with a write that lands at once; the poll that follows retires it.
+int ref_cache_publish_state_stored(void *facade, uint64_t block, uint64_t bytes, int checkpoint) {
+  try {
+    const bool taken = FACADE->cache.publishStateToDisk(block, [bytes](std::function<void()>) {
+      auto ticket = std::make_unique<LandedWrite>();
+      ticket->copy = std::make_shared<StoredState>(bytes);
+      return std::unique_ptr<StateOffload>(std::move(ticket));
+    }, checkpoint != 0);
+    return taken ? 0 : 1;
+  } catch (...) { return -1; }
+}
 int ref_cache_use_state(void *facade, uint64_t block, int use) {
   try {
     if (use) FACADE->uses[block] = FACADE->cache.useState(block);
@@ -402,6 +429,19 @@ int ref_cache_reclaim_step(void *facade, int mode, int up_to_in_use, int keep_re
 }
 int ref_cache_reclaim_one_state(void *facade, int checkpoints_only, uint64_t for_block) {
   try { return FACADE->cache.reclaimOneState(checkpoints_only != 0, for_block, false) ? 1 : 0; } catch (...) { return -1; }
+}
+// What the facade keeps private, read for the comparison (the shim is compiled with -fno-access-control).
+// out[8] = block known, page, has tier copy, transferring, matchable, state contained, state resident, state ordinary
+int ref_cache_block_info(void *facade, uint64_t block, uint64_t *out) {
+  try {
+    auto &cache = FACADE->cache;
+    for (int i = 0; i < 8; ++i) out[i] = 0;
+    if (!cache.kv_.contains(block)) return 0;
+    out[0] = 1; out[1] = cache.kv_.page(block); out[2] = cache.kv_.slot(block) != nullptr; out[3] = cache.kv_.transferring(block);
+    out[4] = cache.kv_.matchable(block); out[5] = cache.states_.contains(block); out[6] = cache.states_.stateResident(block);
+    out[7] = cache.states_.ordinary(block);
+    return 0;
+  } catch (...) { return -1; }
 }
 int ref_cache_poll(void *facade) { try { return FACADE->cache.pollTransfers() ? 1 : 0; } catch (...) { return -1; } }
 // out[12] = pagesAllocated, pagesFree, pagesActive, pagesPrefix, state entries, state bytes, pinned states,

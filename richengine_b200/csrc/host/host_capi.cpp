@@ -39,8 +39,9 @@ public:
   // The shares of the pinned-host tier (demotions at most half, restores at most three quarters of the transfers in
   // flight), or, with plain limits, one bound on both kinds together as the reference's test tier has it
   // (dev/tests/engine/TestKvTier.hpp:35-36).
-  bool canDemote() const noexcept override { return (plain_ || demotions_ < std::max(1u, limit_ / 2)) && pending_.size() < limit_ && writable_; }
-  bool canRestore() const noexcept override { return (plain_ || restores_ < std::max(1u, limit_ - limit_ / 4)) && pending_.size() < limit_; }
+  // A transfer holds its place until the cache has retired it (KvTransfer::finish), not only until it has landed.
+  bool canDemote() const noexcept override { return (plain_ || demotions_ < std::max(1u, limit_ / 2)) && inFlight_ < limit_ && writable_; }
+  bool canRestore() const noexcept override { return (plain_ || restores_ < std::max(1u, limit_ - limit_ / 4)) && inFlight_ < limit_; }
   std::shared_ptr<engine::KvTierSlot> acquireSlot() override {
     for (uint32_t i = 0; i < used_.size(); ++i)
       if (!used_[i]) { used_[i] = 1; return std::make_shared<Slot>(this, i); }
@@ -50,15 +51,15 @@ public:
     if (!canDemote()) return {};
     auto state = std::make_shared<State>(State{true, page, std::dynamic_pointer_cast<Slot>(slot)->id});
     pending_.push_back(state);
-    ++demotions_;
-    return std::make_unique<Ticket>(state);
+    ++demotions_; ++inFlight_;
+    return std::make_unique<Ticket>(this, state);
   }
   std::unique_ptr<engine::KvTransfer> restore(std::shared_ptr<engine::KvTierSlot> slot, uint32_t page) override {
     if (!canRestore()) return {};
     auto state = std::make_shared<State>(State{false, page, std::dynamic_pointer_cast<Slot>(slot)->id});
     pending_.push_back(state);
-    ++restores_;
-    return std::make_unique<Ticket>(state);
+    ++restores_; ++inFlight_;
+    return std::make_unique<Ticket>(this, state);
   }
   void poll() override {}
   // A slot's payload is its content tag repeated over the slot, so that a slot store sees real bytes.
@@ -87,7 +88,6 @@ public:
     if (pending_.empty()) return false;
     auto state = pending_.front();
     pending_.pop_front();
-    --(state->demotion ? demotions_ : restores_);
     if (success && !state->demotion && verify_[state->slot]) { // an adopted slot's first read is checked against its record
       if (arrived_[state->slot] != expected_[state->slot]) success = false;
       else verify_[state->slot] = 0;
@@ -95,8 +95,8 @@ public:
     if (success) {
       if (state->demotion) tags_[state->slot] = storage_.content.at(state->page);
       else storage_.content.at(state->page) = tags_[state->slot];
-    } else if (state->demotion) {
-      writable_ = false;
+    } else if (state->demotion && !plain_) {
+      writable_ = false; // a failed write closes the tier (the test tier with plain limits stays as the test set it)
     }
     state->ready = true;
     state->success = success;
@@ -104,16 +104,24 @@ public:
   }
 
 private:
-  struct State { bool demotion; uint32_t page, slot; bool ready = false, success = false; };
+  struct State { bool demotion; uint32_t page, slot; bool ready = false, success = false, retired = false; };
   struct Slot final : engine::KvTierSlot {
     Slot(ManualTier *t, uint32_t i) : tier(t), id(i) {}
     ~Slot() override { tier->used_[id] = 0; tier->verify_[id] = 0; }
     ManualTier *tier; uint32_t id;
   };
   struct Ticket final : engine::KvTransfer {
-    explicit Ticket(std::shared_ptr<State> s) : state(std::move(s)) {}
+    Ticket(ManualTier *t, std::shared_ptr<State> s) : tier(t), state(std::move(s)) {}
     bool ready() const noexcept override { return state->ready; }
-    bool finish() override { return state->success; }
+    bool finish() override {
+      if (!state->retired) {
+        state->retired = true;
+        --tier->inFlight_;
+        --(state->demotion ? tier->demotions_ : tier->restores_);
+      }
+      return state->success;
+    }
+    ManualTier *tier;
     std::shared_ptr<State> state;
   };
   kv::BudgetExtentStorage &storage_;
@@ -123,7 +131,7 @@ private:
   std::vector<uint8_t> verify_;
   mutable std::vector<std::vector<uint8_t>> payloads_;
   std::deque<std::shared_ptr<State>> pending_;
-  uint32_t limit_, demotions_ = 0, restores_ = 0;
+  uint32_t limit_, demotions_ = 0, restores_ = 0, inFlight_ = 0;
   bool writable_ = true, plain_ = false;
 };
 
@@ -291,7 +299,7 @@ int64_t rk_cache_truncate(void *cache, uint64_t request, uint32_t committed_toke
 }
 int rk_cache_reclaim_one(void *cache) { return guarded([&] { return CACHE->reclaimOne() ? 1 : 0; }); }
 uint32_t rk_cache_reclaim_for_pages(void *cache, uint32_t pages) { return CACHE->reclaimForPages(pages); }
-void rk_cache_poll_transfers(void *cache) { CACHE->pollTransfers(); }
+void rk_cache_poll_transfers(void *cache) { guarded([&] { CACHE->pollTransfers(); return RK_OK; }); }
 int rk_cache_compact_extent(void *cache) { return guarded([&] { return CACHE->compactExtent() ? 1 : 0; }); }
 int rk_cache_complete_transfer(void *cache, int success) {
   auto *h = static_cast<CacheHandle *>(cache);
@@ -308,6 +316,7 @@ void rk_cache_manual_tier_plain_limits(void *cache, int plain) {
 void rk_cache_tier_counters(const void *cache, uint64_t *out) {
   const auto s = static_cast<const CacheHandle *>(cache)->cache->snapshot();
   out[0] = s.demotionsRefused; out[1] = s.replacedCopies; out[2] = s.cancelledRestores;
+  out[3] = s.pendingPages; out[4] = s.demotionsLanded; out[5] = s.restoresLanded;
 }
 void rk_cache_fail_next_transfers(void *cache, uint32_t count) {
   auto *h = static_cast<CacheHandle *>(cache);
@@ -322,6 +331,7 @@ int rk_cache_block_state(const void *cache, uint64_t block, uint64_t *out) {
   auto &index = static_cast<const CacheHandle *>(cache)->cache->index();
   if (!index.contains(block)) return -1;
   out[0] = index.page(block); out[1] = index.slot(block) != nullptr; out[2] = index.transferring(block); out[3] = index.lastUsed(block);
+  out[4] = index.poisoned(block);
   return 0;
 }
 #undef CACHE
@@ -453,19 +463,30 @@ int64_t rk_cache_block_at(void *cache, uint64_t request, uint32_t tokens) {
 int rk_cache_state_publish(void *cache, uint64_t block, uint64_t bytes, int checkpoint) {
   return guarded([&] { CACHE->publishCompositeState(block, bytes, checkpoint != 0); return RK_OK; });
 }
+// A state whose only copy the model stores elsewhere (StateCache::publishStateToDisk): no RAM, no reclaim candidate,
+// but the KV it restores through stays worth a tier copy.
+int rk_cache_state_publish_stored(void *cache, uint64_t block, uint64_t bytes, int checkpoint) {
+  return guarded([&] {
+    if (!CACHE->index().contains(block)) throw std::invalid_argument("a composite state needs its KV block in the cache");
+    if (!bytes) throw std::invalid_argument("a composite state has a size");
+    CACHE->states().publishStored(block, bytes, checkpoint != 0);
+    return RK_OK;
+  });
+}
 int rk_cache_state_use(void *cache, uint64_t block, int use) {
   return guarded([&] { if (use) CACHE->states().use(block); else CACHE->states().unuse(block); return RK_OK; });
 }
 int rk_cache_state_pin(void *cache, uint64_t block, int pin) {
   return guarded([&] { if (pin) CACHE->states().pin(block); else CACHE->states().unpin(block); return RK_OK; });
 }
-// out[6] = contains, ordinary, in use, bytes, KV needed by a state, KV needed by a state in use
+// out[7] = contains, ordinary, in use, bytes, KV needed by a state, KV needed by a state in use, has a RAM copy
 int rk_cache_state_info(void *cache, uint64_t block, uint64_t *out) {
   return guarded([&] {
     const engine::StateCache &states = CACHE->states();
     out[0] = states.contains(block); out[1] = states.ordinary(block); out[2] = states.inUse(block); out[3] = states.bytes(block);
     out[4] = CACHE->index().contains(block) && CACHE->kvNeededByState(block);
     out[5] = CACHE->index().contains(block) && CACHE->kvNeededByStateInUse(block);
+    out[6] = states.stateResident(block);
     return RK_OK;
   });
 }

@@ -39,7 +39,8 @@ void PrefixIndex::refresh(uint64_t block) {
   auto found = blocks_.find(block);
   if (found == blocks_.end()) return;
   Block &entry = found->second;
-  const bool eligible = entry.page != noPage && !entry.residentChildren && !entry.activeUsers && !entry.transferring;
+  // a poisoned block is in no order: it leaves through erasePoisonedLeaf, not as a victim (KvCache::reindex)
+  const bool eligible = entry.page != noPage && !entry.residentChildren && !entry.activeUsers && !entry.transferring && !entry.poisoned;
   if (entry.listed && (!eligible || entry.listedAt != entry.lastUsed)) {
     idleLeaves_.erase({entry.listedAt, block});
     entry.listed = false;
@@ -81,9 +82,12 @@ std::optional<PrefixIndex::Candidate> PrefixIndex::tierCandidate(bool duplicate,
 std::vector<uint64_t> PrefixIndex::subtree(uint64_t block) const {
   // Blocks keep no list of their children: one pass gathers them. This runs only when a tier has closed or a
   // restore has failed.
-  std::unordered_multimap<uint64_t, uint64_t> below;
+  std::unordered_map<uint64_t, std::vector<uint64_t>> below;
   for (const auto &[id, entry] : blocks_)
-    if (entry.parent) below.emplace(entry.parent, id);
+    if (entry.parent) below[entry.parent].push_back(id);
+  // Siblings newest first, as the reference links them (a new child becomes its parent's first): with the stack below
+  // the oldest child's subtree is listed first, which fixes the order pages return to the pool in.
+  for (auto &[parent, children] : below) std::sort(children.begin(), children.end(), std::greater<uint64_t>());
   std::vector<uint64_t> order;
   std::vector<std::pair<uint64_t, bool>> pending{{block, false}};
   while (!pending.empty()) {
@@ -96,8 +100,8 @@ std::vector<uint64_t> PrefixIndex::subtree(uint64_t block) const {
     const Block &entry = at(id);
     if (id != block && (entry.transferring || entry.activeUsers)) return {};
     pending.push_back({id, true});
-    const auto [first, last] = below.equal_range(id);
-    for (auto child = first; child != last; ++child) pending.push_back({child->second, false});
+    if (auto children = below.find(id); children != below.end())
+      for (uint64_t child : children->second) pending.push_back({child, false});
   }
   return order;
 }
@@ -173,6 +177,7 @@ void PrefixIndex::releaseActive(uint64_t block) noexcept {
   if (entry.activeUsers) --entry.activeUsers;
   if (!entry.activeUsers && !entry.children) entry.lastUsed = ++clock_;
   refresh(block);
+  erasePoisonedLeaf(block);
 }
 // A parent that has just become a leaf no request holds is as warm as the child it lost (KvCache::inherit,
 // KvCache.cpp:441-446).
@@ -288,31 +293,53 @@ void PrefixIndex::followPages(const KvPageMoves &moves) noexcept {
   }
 }
 
-void PrefixIndex::poison(uint64_t block) { at(block).poisoned = true; ++generation_; refresh(block); }
+// It matches no lookup from now on, and the copy that failed to read is given up (KvCache::poison, KvCache.cpp:469-478).
+void PrefixIndex::poison(uint64_t block) {
+  Block &entry = at(block);
+  entry.poisoned = true;
+  ++generation_;
+  entry.slot.reset();
+  refresh(block);
+  erasePoisonedLeaf(block);
+}
 
+void PrefixIndex::erasePoisonedLeaf(uint64_t block) noexcept {
+  auto found = blocks_.find(block);
+  if (found == blocks_.end() || !found->second.poisoned || found->second.children || found->second.activeUsers ||
+      found->second.transferring)
+    return;
+  try { erase(block); } catch (...) { std::terminate(); }
+}
+
+// KvCache::erase (KvCache.cpp:515-558), in its order: the block leaves the graph, its parent inherits its recency and,
+// if it is a poisoned block nothing hangs on any more, leaves too (and so on up the chain); the page returns to the pool
+// last, after the pages of the ancestors that left with it.
 void PrefixIndex::erase(uint64_t block) {
   Block &entry = at(block);
   if (entry.children || entry.activeUsers || entry.transferring)
     throw std::logic_error("only a block without children, users or transfer can be removed");
-  if (entry.page != noPage) {
-    blockOnPage_[entry.page] = 0;
-    pool_.releasePage(entry.page, true);
-    --resident_;
-  }
+  const uint64_t parent = entry.parent, lastUsed = entry.lastUsed, hash = entry.hash;
+  const uint32_t page = entry.page;
   if (entry.listed) idleLeaves_.erase({entry.listedAt, block});
   if (entry.tierListed) (entry.tierListed == 1 ? duplicates_ : tierLeaves_).erase({entry.tierListedAt, block});
-  if (entry.parent) {
-    Block &above = at(entry.parent);
-    --above.children;
-    if (entry.page != noPage) --above.residentChildren;
-    inherit(above, entry.lastUsed);
-    refresh(entry.parent);
-  }
-  const auto [first, last] = index_.equal_range(entry.hash);
+  const auto [first, last] = index_.equal_range(hash);
   for (auto it = first; it != last; ++it)
     if (it->second == block) { index_.erase(it); break; }
   blocks_.erase(block);
   ++generation_;
+  if (page != noPage) {
+    blockOnPage_[page] = 0;
+    --resident_;
+  }
+  if (parent) {
+    Block &above = at(parent);
+    --above.children;
+    if (page != noPage) --above.residentChildren;
+    inherit(above, lastUsed);
+    refresh(parent);
+    erasePoisonedLeaf(parent);
+  }
+  if (page != noPage) pool_.releasePage(page, true);
 }
 
 std::optional<PrefixIndex::Candidate> PrefixIndex::evictionCandidate() const {
@@ -382,10 +409,13 @@ void Cache::endRequest(uint64_t id) {
   // Reads that were never submitted have no IO to drain: their pages return leaf first, unless another request
   // waits for the block, a block below it is resident, or a state was published on it meanwhile (Cache::endRequest,
   // Cache.cpp:160-175; KvCache::abandonRestore, KvCache.cpp:411-418).
+  if (found->second.pendingRestores)
+    for (Transfer &t : restores_) std::erase(t.waiters, id);
   const std::vector<uint64_t> &chain = found->second.blocks;
   for (auto block = chain.rbegin(); block != chain.rend() && !restores_.empty(); ++block) {
     auto queued = std::find_if(restores_.begin(), restores_.end(), [&](const Transfer &t) { return t.block == *block; });
-    if (queued == restores_.end() || queued->ticket || states_.stateResident(*block)) continue;
+    if (queued == restores_.end() || queued->ticket || !queued->waiters.empty() || states_.stateResident(*block)) continue;
+    if (!index_.contains(*block)) continue; // a poisoned tip left with the request's hold on it
     if (!index_.abandonRestore(*block)) continue;
     restores_.erase(queued);
     --counters_.restores;
@@ -562,13 +592,21 @@ TokenAdmission Cache::attachPrefix(uint64_t id, std::span<const uint64_t> blocks
       Transfer restore{block, page, nullptr, index_.slot(block)};
       if (!refused && tier_->canRestore()) restore.ticket = tier_->restore(restore.slot, page);
       if (!restore.ticket) refused = true;
-      restores_.push_back(std::move(restore)); // a refused start is retried by pollTransfers
+      // kept in block order (a parent's id is lower than its children's): a poll starts the waiting ones in that
+      // order, so started reads stay a prefix of each chain; a refused start is retried by pollTransfers
+      restores_.insert(std::upper_bound(restores_.begin(), restores_.end(), block, [](uint64_t id, const Transfer &t) { return id < t.block; }),
+                       std::move(restore));
       ++counters_.restores;
       // the pool's acquisition gave the request an active reference already
     } else {
       pool_.retainPage(page, false);
     }
     active.pages.push_back(page);
+    auto pending = std::find_if(restores_.begin(), restores_.end(), [&](const Transfer &t) { return t.block == block; });
+    if (pending != restores_.end()) { // its own read, or one another request started: both wait for it
+      pending->waiters.push_back(id);
+      ++active.pendingRestores;
+    }
   }
   active.blocks.assign(blocks.begin(), blocks.end());
   index_.retainActive(blocks.back());
@@ -582,19 +620,11 @@ TokenAdmission Cache::attachPrefix(uint64_t id, std::span<const uint64_t> blocks
 // recomputes: the block matches nothing any more).
 int Cache::restoreStatus(uint64_t id) const {
   const Request &active = request(id);
-  for (uint64_t block : active.blocks)
-    if (index_.poisoned(block)) return 2;
-  return restoresPending(id) ? 1 : 0;
+  if (active.restoreFailed) return 2;
+  return active.pendingRestores ? 1 : 0;
 }
 
-bool Cache::restoresPending(uint64_t id) const {
-  const Request &active = request(id);
-  for (uint64_t block : active.blocks)
-    if (index_.transferring(block) && index_.page(block) != PrefixIndex::noPage)
-      for (const Transfer &t : restores_)
-        if (t.block == block) return true;
-  return false;
-}
+bool Cache::restoresPending(uint64_t id) const { return request(id).pendingRestores != 0; }
 
 uint32_t Cache::forkRequest(uint64_t parentId, uint64_t childId, uint32_t committedTokens) {
   const Request &parent = request(parentId);
@@ -735,15 +765,11 @@ void Cache::dropPoisoned() {
     if (!index_.contains(block)) return true;
     for (uint64_t below : index_.subtree(block)) {
       states_.forget(below);
+      if (!index_.contains(below)) continue; // a poisoned block below may have left with its last child
       index_.erase(below);
       ++counters_.evictedBlocks;
     }
-    if (!index_.children(block) && index_.idle(block)) {
-      states_.forget(block);
-      index_.erase(block);
-      ++counters_.evictedBlocks;
-    }
-    return !index_.contains(block);
+    return !index_.contains(block); // it leaves with its last child, user or transfer (PrefixIndex::erasePoisonedLeaf)
   });
 }
 
@@ -864,23 +890,9 @@ uint32_t Cache::reclaimForPages(uint32_t pages) {
 void Cache::pollTransfers() {
   if (!tier_) return;
   tier_->poll();
-  for (size_t i = 0; i < demotions_.size();) {
-    Transfer &t = demotions_[i];
-    if (!t.ticket->ready()) { ++i; continue; }
-    const bool landed = t.ticket->finish();
-    index_.setTransferring(t.block, false);
-    if (landed) {
-      index_.setSlot(t.block, t.slot);
-      // a state published on the block while its copy was in flight keeps the page under it
-      if (index_.residentLeaf(t.block) && !states_.stateResident(t.block)) { index_.dropPage(t.block); ++counters_.evictedBlocks; }
-    } else {
-      ++counters_.failedTransfers; // the page stays: a failed demotion loses nothing
-    }
-    demotions_.erase(demotions_.begin() + long(i));
-  }
   // Waiting restores start in block order and stop at the first the tier refuses: started ones stay a prefix of each
   // chain, and a full tier is asked once per poll, not once per waiting block (Cache::pollTransfers, Cache.cpp:938-956).
-  bool refused = false;
+  bool refused = false, progressed = false;
   for (size_t i = 0; i < restores_.size();) {
     Transfer &t = restores_[i];
     if (!t.ticket) {
@@ -892,14 +904,42 @@ void Cache::pollTransfers() {
     if (!t.ticket->ready()) { ++i; continue; }
     const bool landed = t.ticket->finish();
     index_.setTransferring(t.block, false);
-    if (!landed) {
+    for (uint64_t waiter : t.waiters) {
+      auto waiting = requests_.find(waiter);
+      if (waiting == requests_.end()) continue;
+      --waiting->second.pendingRestores;
+      if (!landed) waiting->second.restoreFailed = true;
+    }
+    if (landed) {
+      ++counters_.restoresLanded;
+    } else {
       ++counters_.failedTransfers;
-      index_.poison(t.block); // it matches nothing any more; its users recompute
+      states_.invalidate(t.block); // so does any state it held
+      index_.poison(t.block);  // it matches nothing any more; its users recompute
       poisoned_.push_back(t.block);
     }
     restores_.erase(restores_.begin() + long(i));
+    progressed = true;
   }
-  dropPoisoned();
+  // demotions after the restores, as the reference retires them (Cache.cpp:978-998): a waiting read starts at the
+  // poll after the one that retired the write whose place it takes
+  for (size_t i = 0; i < demotions_.size();) {
+    Transfer &t = demotions_[i];
+    if (!t.ticket->ready()) { ++i; continue; }
+    const bool landed = t.ticket->finish();
+    index_.setTransferring(t.block, false);
+    if (landed) {
+      ++counters_.demotionsLanded;
+      index_.setSlot(t.block, t.slot);
+      // a state published on the block while its copy was in flight keeps the page under it
+      if (index_.residentLeaf(t.block) && !states_.stateResident(t.block)) { index_.dropPage(t.block); ++counters_.evictedBlocks; }
+    } else {
+      ++counters_.failedTransfers; // the page stays: a failed demotion loses nothing
+    }
+    demotions_.erase(demotions_.begin() + long(i));
+    progressed = true;
+  }
+  if (progressed) dropPoisoned(); // only a transfer that retired can have freed what a poisoned block waited for
 }
 
 bool Cache::compactExtent() {
@@ -926,6 +966,7 @@ CacheSnapshot Cache::snapshot() const {
   result.residentBlocks = index_.residentBlocks();
   result.tierBlocks = index_.tierBlocks();
   result.transfers = uint32_t(demotions_.size() + restores_.size());
+  result.pendingPages = pendingPages();
   return result;
 }
 

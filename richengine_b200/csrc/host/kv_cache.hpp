@@ -68,7 +68,7 @@ public:
   std::shared_ptr<KvTierSlot> slot(uint64_t block) const { return at(block).slot; }
   bool transferring(uint64_t block) const { return at(block).transferring; }
   bool idle(uint64_t block) const { const Block &b = at(block); return !b.activeUsers && !b.transferring; }
-  bool residentLeaf(uint64_t block) const { const Block &b = at(block); return b.page != noPage && !b.residentChildren && !b.activeUsers && !b.transferring; }
+  bool residentLeaf(uint64_t block) const { const Block &b = at(block); return b.page != noPage && !b.residentChildren && !b.activeUsers && !b.transferring && !b.poisoned; }
   uint64_t lastUsed(uint64_t block) const { return at(block).lastUsed; }
   void setTransferring(uint64_t block, bool value) { at(block).transferring = value; refresh(block); }
   // A block without a page is erased, not stripped of its only copy (KvCache::setSlot, KvCache.cpp:379-385).
@@ -136,6 +136,8 @@ private:
   // Keeps idleLeaves_ in step with a block whose page, children, users, transfer or recency changed.
   void refresh(uint64_t block);
   static void inherit(Block &parent, uint64_t lastUsed) noexcept;
+  // A poisoned block leaves as soon as nothing hangs on it: no child, no user, no transfer (KvCache::erasePoisonedLeaf).
+  void erasePoisonedLeaf(uint64_t block) noexcept;
   Block &at(uint64_t block);
   const Block &at(uint64_t block) const;
 
@@ -172,6 +174,8 @@ struct CacheSnapshot {
   uint32_t requests = 0, residentBlocks = 0, tierBlocks = 0, transfers = 0;
   uint64_t demotions = 0, restores = 0, failedTransfers = 0, evictedBlocks = 0, forkCopies = 0, truncatedPages = 0;
   uint64_t demotionsRefused = 0, replacedCopies = 0, cancelledRestores = 0;
+  uint64_t demotionsLanded = 0, restoresLanded = 0; // as the reference counts them (KvTierSnapshot::demotions / restores)
+  uint32_t pendingPages = 0;
 };
 
 // How far a reclaim may reach (Cache.hpp: ReclaimClass): states in use, and the KV they restore through, go only to
@@ -322,12 +326,15 @@ private:
     std::vector<uint64_t> blocks; // cached chain covering the first blocks.size() pages
     uint64_t revision = 0;
     uint32_t firstChanged = 0;
+    uint32_t pendingRestores = 0; // reads this request attached to and waits for (Cache::restoreRequest's waiters)
+    bool restoreFailed = false;
   };
   struct Transfer {
     uint64_t block = 0;
     uint32_t page = 0;
     std::unique_ptr<KvTransfer> ticket;
     std::shared_ptr<KvTierSlot> slot;
+    std::vector<uint64_t> waiters; // the requests that attached to a read
   };
   enum class LeafReclaim : uint8_t { Started, Pending, Impossible };
   LeafReclaim reclaimKvLeaf(uint64_t block, bool immediate = false);

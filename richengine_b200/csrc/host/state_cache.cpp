@@ -15,7 +15,19 @@ void StateCache::publish(uint64_t block, uint64_t bytes, bool checkpoint) {
   auto found = states_.find(block);
   if (found != states_.end()) {
     State &state = found->second; // the copy that is there is reused: the same block is the same content
-    state.checkpoint = state.checkpoint && checkpoint; // an ordinary state stays ordinary
+    const bool disposable = checkpoint && !inUse(block);
+    if (state.invalid) { // a condemned entry a reader still pins is taken over by the new publication
+      if (state.resident) bytes_ -= state.bytes;
+      state.invalid = false;
+      state.resident = false;
+      state.stored = false;
+    }
+    state.checkpoint = state.checkpoint && disposable; // an ordinary state stays ordinary
+    if (!state.resident) { // a stored state gains its RAM copy (StateCache::publishCompositeState over a disk entry)
+      state.resident = true;
+      state.bytes = bytes;
+      bytes_ += bytes;
+    }
     if (!state.pins) state.lastUsed = clock_();
     if (!state.checkpoint && note_) note_(block);
     return;
@@ -28,9 +40,21 @@ void StateCache::publish(uint64_t block, uint64_t bytes, bool checkpoint) {
   adjust_(block, +1, inUse(block) ? +1 : 0);
 }
 
+void StateCache::publishStored(uint64_t block, uint64_t bytes, bool checkpoint) {
+  if (!block) throw std::invalid_argument("a composite state sits on a KV block");
+  if (contains(block)) throw std::logic_error("a block's state is published once");
+  const bool disposable = checkpoint && !inUse(block);
+  State state{bytes, clock_(), disposable, 0};
+  state.resident = false;
+  state.stored = true;
+  states_.emplace(block, state);
+  if (!disposable && note_) note_(block);
+  adjust_(block, +1, inUse(block) ? +1 : 0);
+}
+
 bool StateCache::ordinary(uint64_t block) const noexcept {
   auto found = states_.find(block);
-  return found != states_.end() && !found->second.checkpoint;
+  return found != states_.end() && !found->second.invalid && !found->second.checkpoint;
 }
 uint64_t StateCache::bytes(uint64_t block) const noexcept {
   auto found = states_.find(block);
@@ -65,14 +89,17 @@ std::vector<uint64_t> StateCache::usedStates() const {
 
 void StateCache::pin(uint64_t block) {
   auto found = states_.find(block);
-  if (found == states_.end()) throw std::out_of_range("no composite state at this block");
+  if (found == states_.end() || found->second.invalid) throw std::out_of_range("no composite state at this block");
   ++found->second.pins;
   if (hold_) hold_(block, true);
 }
 void StateCache::unpin(uint64_t block) {
   auto found = states_.find(block);
   if (found == states_.end() || !found->second.pins) throw std::logic_error("the state at this block is not pinned");
-  if (!--found->second.pins) found->second.lastUsed = clock_();
+  if (!--found->second.pins) {
+    found->second.lastUsed = clock_();
+    if (found->second.invalid) erase(found);
+  }
   if (hold_) hold_(block, false);
 }
 
@@ -80,7 +107,7 @@ uint64_t StateCache::resumePoint() const noexcept {
   uint64_t best = 0, bestUsed = 0;
   bool bestOrdinary = false;
   for (const auto &[block, state] : states_) {
-    if (state.pins || inUse(block)) continue;
+    if (state.pins || state.invalid || inUse(block) || !state.resident) continue;
     const bool isOrdinary = !state.checkpoint;
     if (!best || (isOrdinary && !bestOrdinary) || (isOrdinary == bestOrdinary && state.lastUsed > bestUsed)) {
       best = block; bestUsed = state.lastUsed; bestOrdinary = isOrdinary;
@@ -92,7 +119,7 @@ uint64_t StateCache::resumePoint() const noexcept {
 std::optional<StateCandidate> StateCache::oldest(Class wanted, uint64_t withheld) const {
   std::optional<StateCandidate> best;
   for (const auto &[block, state] : states_) {
-    if (state.pins || block == withheld || classOf(block, state) != wanted) continue;
+    if (state.pins || state.invalid || !state.resident || block == withheld || classOf(block, state) != wanted) continue;
     if (!best || state.lastUsed < best->lastUsed || (state.lastUsed == best->lastUsed && block < best->block))
       best = StateCandidate{block, state.lastUsed};
   }
@@ -109,8 +136,16 @@ std::optional<StateCandidate> StateCache::inUseCandidate() const { return oldest
 uint32_t StateCache::evictableStates(bool withInUse) const noexcept {
   uint32_t count = 0;
   for (const auto &[block, state] : states_)
-    if (!state.pins && (withInUse || !inUse(block))) ++count;
+    if (!state.pins && !state.invalid && state.resident && (withInUse || !inUse(block))) ++count;
   return count;
+}
+
+void StateCache::erase(std::unordered_map<uint64_t, State>::iterator found) {
+  const uint64_t block = found->first;
+  if (found->second.resident) bytes_ -= found->second.bytes;
+  const bool used = inUse(block);
+  states_.erase(found);
+  adjust_(block, -1, used ? -1 : 0);
 }
 
 void StateCache::forget(uint64_t block) {
@@ -120,14 +155,25 @@ void StateCache::forget(uint64_t block) {
   for (uint32_t pin = 0; pin < found->second.pins; ++pin)
     if (hold_) hold_(block, false);
   found->second.pins = 0;
-  reclaim(block);
+  erase(found);
+}
+
+void StateCache::invalidate(uint64_t block) {
+  auto found = states_.find(block);
+  if (found == states_.end() || found->second.invalid) return;
+  if (found->second.pins) found->second.invalid = true; // the reader's copy stays until it lets go
+  else erase(found);
 }
 
 bool StateCache::reclaim(uint64_t block, uint64_t *freed) {
   auto found = states_.find(block);
-  if (found == states_.end() || found->second.pins) return false;
+  if (found == states_.end() || found->second.pins || found->second.invalid || !found->second.resident) return false;
   if (freed) *freed = found->second.bytes;
   bytes_ -= found->second.bytes;
+  if (found->second.stored) { // the copy stored elsewhere keeps the state: only the RAM goes
+    found->second.resident = false;
+    return true;
+  }
   const bool used = inUse(block);
   states_.erase(found);
   adjust_(block, -1, used ? -1 : 0);

@@ -5,9 +5,11 @@
 // path itself does not read those buffers; what couples them to it is the reclaim policy: KV that a state restores
 // through is "needed by a state", a state an unfinished request resumes from is "in use" together with the KV
 // above it, disposable checkpoints go before ordinary states, and states in use go last
-// (runtime/engine/cache/Cache.hpp:549-556, Cache.cpp:451-628). This is that subset: states live in RAM only (the
-// reference's disk tier for states, its writers, leases with restore pins and persistence are not rebuilt), a state
-// is a byte count on a block with a class (checkpoint or ordinary), a recency and a use count.
+// (runtime/engine/cache/Cache.hpp:549-556, Cache.cpp:451-628). This is that subset: a state is a byte count on a
+// block with a class (checkpoint or ordinary), a recency, a use count and where its copies are: in RAM (what the
+// reclaim order takes), stored elsewhere by the model (the reference's disk tier for states; its writers, quota and
+// persistence are not rebuilt, a stored copy is a flag), or both. A stored copy costs no RAM and is no reclaim
+// candidate; it keeps the KV it restores through worth a tier copy.
 #pragma once
 
 #include <cstdint>
@@ -41,10 +43,13 @@ public:
   // (StateCache::reuseCompositeState: the copy and its size stay, an ordinary boundary upgrades a checkpoint, a
   // checkpoint cannot downgrade an ordinary state, and the recency moves unless a restore pins the state).
   void publish(uint64_t block, uint64_t bytes, bool checkpoint);
-  bool contains(uint64_t block) const noexcept { return states_.count(block) != 0; }
+  // Publishes a state whose only copy the model stores elsewhere (StateCache::publishStateToDisk). A block's state
+  // is published once: a second publication is a logic error.
+  void publishStored(uint64_t block, uint64_t bytes, bool checkpoint);
+  bool contains(uint64_t block) const noexcept { auto f = states_.find(block); return f != states_.end() && !f->second.invalid; }
   bool ordinary(uint64_t block) const noexcept;
   uint64_t bytes(uint64_t block) const noexcept;
-  bool stateResident(uint64_t block) const noexcept { return contains(block); } // RAM is the only tier here
+  bool stateResident(uint64_t block) const noexcept { auto f = states_.find(block); return f != states_.end() && f->second.resident; }
   // An unfinished request resumes from the state at this block, published or yet to be (StateCache::useState):
   // until every use ends the state is in use, and a checkpoint there becomes ordinary.
   void use(uint64_t block);
@@ -63,19 +68,23 @@ public:
   std::optional<StateCandidate> inUseCandidate() const;
   uint64_t resumePoint() const noexcept;
   uint32_t evictableStates(bool withInUse) const noexcept;
-  // Frees the RAM copy: without a disk tier the state goes (the reference's Unwritten::Drop). False when pinned
-  // or absent. Returns the bytes freed through `freed`.
+  // Frees the RAM copy: a state that is stored elsewhere too stays, without it; one that is not goes (the
+  // reference's Unwritten::Drop). False when pinned or without a RAM copy. Returns the bytes freed through `freed`.
   bool reclaim(uint64_t block, uint64_t *freed = nullptr);
   // The block leaves the KV index: its state goes with it.
   // A use outlives it: the request that resumes from the block still holds its handle.
   void forget(uint64_t block);
+  // The block's content is lost (a failed read): the state is contained no more; while a restore still pins it the
+  // entry stays, condemned, and leaves with the last pin (StateCache::invalidate / discardState).
+  void invalidate(uint64_t block);
   uint64_t residentBytes() const noexcept { return bytes_; }
   size_t size() const noexcept { return states_.size(); }
 
 private:
-  struct State { uint64_t bytes = 0, lastUsed = 0; bool checkpoint = false; uint32_t pins = 0; };
+  struct State { uint64_t bytes = 0, lastUsed = 0; bool checkpoint = false; uint32_t pins = 0; bool resident = true, stored = false, invalid = false; };
   enum class Class { Checkpoint, Ordinary, InUse };
   Class classOf(uint64_t block, const State &state) const noexcept;
+  void erase(std::unordered_map<uint64_t, State>::iterator found);
   std::optional<StateCandidate> oldest(Class wanted, uint64_t withheld) const;
 
   AdjustBelow adjust_;

@@ -134,9 +134,10 @@ class Cache:
     def manual_tier_set(self, transfer_limit, writable=True): self._lib.rk_cache_manual_tier_set(self._handle, transfer_limit, int(writable))
 
     def tier_counters(self) -> dict:
-        out = (C.c_uint64 * 3)()
+        out = (C.c_uint64 * 6)()
         self._lib.rk_cache_tier_counters(self._handle, out)
-        return dict(zip(["demotions_refused", "replaced_copies", "cancelled_restores"], [int(x) for x in out]))
+        return dict(zip(["demotions_refused", "replaced_copies", "cancelled_restores", "pending_pages", "demotions_landed", "restores_landed"],
+                        [int(x) for x in out]))
 
     def fork(self, parent, child, committed) -> int: return self._check(self._lib.rk_cache_fork(self._handle, parent, child, committed), "fork")
     def truncate(self, request, committed, scratch) -> int: return self._check(self._lib.rk_cache_truncate(self._handle, request, committed, scratch), "truncate")
@@ -150,15 +151,16 @@ class Cache:
     # ---- composite states and the reclaim order they impose (engine::StateCache subset, Cache::evictOne) ----
     def block_at(self, request, tokens) -> int: return self._check(self._lib.rk_cache_block_at(self._handle, request, tokens), "block_at")
     def publish_state(self, block, size, checkpoint=False): self._check(self._lib.rk_cache_state_publish(self._handle, block, size, int(checkpoint)), "publish_state")
+    def publish_stored_state(self, block, size, checkpoint=False): self._check(self._lib.rk_cache_state_publish_stored(self._handle, block, size, int(checkpoint)), "publish_stored_state")
     def use_state(self, block): self._check(self._lib.rk_cache_state_use(self._handle, block, 1), "use_state")
     def unuse_state(self, block): self._check(self._lib.rk_cache_state_use(self._handle, block, 0), "unuse_state")
     def pin_state(self, block): self._check(self._lib.rk_cache_state_pin(self._handle, block, 1), "pin_state")
     def unpin_state(self, block): self._check(self._lib.rk_cache_state_pin(self._handle, block, 0), "unpin_state")
 
     def state_info(self, block) -> dict:
-        out = (C.c_uint64 * 6)()
+        out = (C.c_uint64 * 7)()
         self._check(self._lib.rk_cache_state_info(self._handle, block, out), "state_info")
-        return dict(zip(["contains", "ordinary", "in_use", "bytes", "kv_needed", "kv_needed_in_use"], [int(x) for x in out]))
+        return dict(zip(["contains", "ordinary", "in_use", "bytes", "kv_needed", "kv_needed_in_use", "resident"], [int(x) for x in out]))
 
     def state_summary(self) -> dict:
         out = (C.c_uint64 * 4)()
@@ -224,10 +226,10 @@ class Cache:
         return {"blocks": out[0], "dropped": out[1], "bytes": out[2]}
 
     def block_state(self, block):
-        out = (C.c_uint64 * 4)()
+        out = (C.c_uint64 * 5)()
         if self._lib.rk_cache_block_state(self._handle, block, out) < 0:
             return None
-        return {"page": out[0], "tier_copy": bool(out[1]), "transferring": bool(out[2]), "last_used": out[3]}
+        return {"page": out[0], "tier_copy": bool(out[1]), "transferring": bool(out[2]), "last_used": out[3], "poisoned": bool(out[4])}
 
 
 KV_BLOCK_LABEL_BYTES = 168  # engine::KvBlockLabel: id, parent, lastUsed, images lo/hi (u64 each), 32 token ids (u32)

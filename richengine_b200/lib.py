@@ -186,6 +186,7 @@ SIGNATURES = {
     "rk_cache_block_state": (i32, [vp, u64, vp]),
     "rk_cache_block_at": (i64, [vp, u64, u32]),
     "rk_cache_state_publish": (i32, [vp, u64, u64, i32]),
+    "rk_cache_state_publish_stored": (i32, [vp, u64, u64, i32]),
     "rk_cache_state_use": (i32, [vp, u64, i32]),
     "rk_cache_state_pin": (i32, [vp, u64, i32]),
     "rk_cache_state_info": (i32, [vp, u64, vp]),

@@ -101,10 +101,12 @@ def reference():
             r.ref_cache_release_lookup.restype, r.ref_cache_release_lookup.argtypes = None, [vp, u64]
             r.ref_cache_restore_status.restype, r.ref_cache_restore_status.argtypes = i32, [vp, u64]
             r.ref_cache_publish_state.restype, r.ref_cache_publish_state.argtypes = i32, [vp, u64, u64, i32]
+            r.ref_cache_publish_state_stored.restype, r.ref_cache_publish_state_stored.argtypes = i32, [vp, u64, u64, i32]
             r.ref_cache_use_state.restype, r.ref_cache_use_state.argtypes = i32, [vp, u64, i32]
             r.ref_cache_evict_one.restype, r.ref_cache_evict_one.argtypes = i32, [vp, i32, i32, i32, vp]
             r.ref_cache_reclaim_step.restype, r.ref_cache_reclaim_step.argtypes = i32, [vp, i32, i32, i32, i32, vp]
             r.ref_cache_reclaim_one_state.restype, r.ref_cache_reclaim_one_state.argtypes = i32, [vp, i32, u64]
+            r.ref_cache_block_info.restype, r.ref_cache_block_info.argtypes = i32, [vp, u64, vp]
             r.ref_cache_poll.restype, r.ref_cache_poll.argtypes = i32, [vp]
             r.ref_cache_snapshot.restype, r.ref_cache_snapshot.argtypes = None, [vp, vp]
         _reference = r

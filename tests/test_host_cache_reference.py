@@ -80,6 +80,10 @@ class Theirs:
     def publish_state(self, block, size, checkpoint): assert self.r.ref_cache_publish_state(self.h, block, size, int(checkpoint)) == 0
     def use(self, block, on): assert self.r.ref_cache_use_state(self.h, block, int(on)) == 0
 
+    def publish_stored(self, block, size, checkpoint):
+        assert self.r.ref_cache_publish_state_stored(self.h, block, size, int(checkpoint)) == 0
+        self.poll()   # retires the write that landed at once
+
     def evict_one(self, up_to_in_use, keep_resume_point, pages_only):
         out = (C.c_uint64 * 4)()
         assert self.r.ref_cache_evict_one(self.h, int(up_to_in_use), int(keep_resume_point), int(pages_only), out) == 0
@@ -94,6 +98,14 @@ class Theirs:
     def poll(self): self.r.ref_cache_poll(self.h)
     def complete(self, success=True): self.r.ref_cache_tier_complete(self.h, int(success))
     def tier_set(self, limit, writable=True): self.r.ref_cache_tier_set(self.h, limit, int(writable))
+
+    def block_info(self, block):
+        out = (C.c_uint64 * 8)()
+        assert self.r.ref_cache_block_info(self.h, block, out) == 0
+        if not out[0]:
+            return None
+        return {"page": int(out[1]), "transferring": bool(out[3]), "state": bool(out[5]), "state_resident": bool(out[6]),
+                "state_ordinary": bool(out[7]), "tier_copy": bool(out[2]), "poisoned": not out[4]}
 
     def snapshot(self):
         out = (C.c_uint64 * 16)()
@@ -150,6 +162,10 @@ class Mine:
     def publish_state(self, block, size, checkpoint): self.cache.publish_state(block, size, checkpoint)
     def use(self, block, on): (self.cache.use_state if on else self.cache.unuse_state)(block)
 
+    def publish_stored(self, block, size, checkpoint):
+        self.cache.publish_stored_state(block, size, checkpoint)
+        self.poll()
+
     def evict_one(self, up_to_in_use, keep_resume_point, pages_only):
         step = self.cache.evict_one(up_to_in_use, keep_resume_point, pages_only)
         return {k: step[k] for k in ("progress", "pending", "evicted_state")}
@@ -166,11 +182,25 @@ class Mine:
 
     def tier_set(self, limit, writable=True): self.cache.manual_tier_set(limit, writable)
 
+    def block_info(self, block):
+        found = self.cache.block_state(block)
+        if found is None:
+            return None
+        state = self.cache.state_info(block)
+        # a copy being written counts as a tier copy there from the start of the write
+        return {"page": int(found["page"]), "transferring": found["transferring"], "state": bool(state["contains"]),
+                "state_resident": bool(state["resident"]), "state_ordinary": bool(state["ordinary"]), "poisoned": found["poisoned"],
+                "tier_copy": found["tier_copy"] or (found["transferring"] and found["page"] != 0xFFFFFFFF and not self._restoring(block))}
+
+    def _restoring(self, block):
+        return False
+
     def snapshot(self):
         pool, cache, states, tier = self.pool.snapshot(), self.cache.snapshot(), self.cache.state_summary(), self.cache.tier_counters()
         return {"pages_allocated": int(pool["pages_allocated"]), "pages_free": int(pool["pages_free"]), "pages_active": int(pool["pages_active"]),
                 "pages_prefix": int(pool["pages_prefix"]), "states": int(states["states"]), "state_bytes": int(states["bytes"]),
-                "demotions": int(cache["demotions"]), "restores": int(cache["restores"]), "demotions_refused": tier["demotions_refused"],
+                "demotions": tier["demotions_landed"], "restores": tier["restores_landed"], "demotions_refused": tier["demotions_refused"],
+                "pending_pages": tier["pending_pages"], "tier_blocks": int(cache["tier_blocks"]) + tier["pending_pages"],
                 **self.cache.lookup_counters()}
 
 
@@ -196,6 +226,8 @@ def run_trace(seed, steps, tier):
     geometry = dict(pages=24, extent=int(rng.choice([1, 2, 4])), runway=0, budget=int(rng.choice([8, 12, 16])),
                     tier=tier, slots=int(rng.choice([2, 4, 16])), transfers=int(rng.choice([1, 2, 4])))
     geometry["budget"] -= geometry["budget"] % geometry["extent"]
+    if tier:
+        geometry["slots"] = 64   # a quota that never fills: replacement under a full quota involves the states' own tier
     mine, theirs = Mine(**geometry), Theirs(**geometry)
     prompts = make_prompts(rng, 10)
     active = {}      # request -> [prompt index, tokens ensured, tokens published]
@@ -213,13 +245,20 @@ def run_trace(seed, steps, tier):
         a, b = mine.snapshot(), theirs.snapshot()
         for key, value in a.items():
             assert value == b[key], (what, key, value, b[key], seed, log[-6:])
+        for block in sorted(blocks):
+            a, b = mine.block_info(block), theirs.block_info(block)
+            if a is not None and b is not None:
+                a, b = dict(a), dict(b)
+                a.pop("tier_copy"); b.pop("tier_copy")
+            assert a == b, (what, "block", block, a, b, seed, log[-6:])
         for request in active:
             assert mine.table(request) == theirs.table(request), (what, "page table", request, seed, log[-6:])
             assert mine.restore_status(request) == theirs.restore_status(request), (what, "restore status", request, seed, log[-6:])
 
     for step in range(steps):
         op = rng.choice(["begin", "grow", "publish", "end", "lookup", "state", "use", "evict", "poll", "pin", "reclaim", "state_reclaim", "probe"],
-                        p=[0.10, 0.22, 0.20, 0.06, 0.06, 0.10, 0.05, 0.05, 0.02, 0.04, 0.04, 0.02, 0.04])
+                        p=[0.10, 0.20, 0.18, 0.06, 0.05, 0.08, 0.04, 0.09, 0.08, 0.03, 0.04, 0.02, 0.03] if tier else
+                          [0.10, 0.22, 0.20, 0.06, 0.06, 0.10, 0.05, 0.05, 0.02, 0.04, 0.04, 0.02, 0.04])
         if op == "begin" and len(active) < 4:
             request, next_request = next_request, next_request + 1
             index = int(rng.integers(len(prompts)))
@@ -248,7 +287,10 @@ def run_trace(seed, steps, tier):
             active[request][2] = committed
             if committed >= 32 and rng.random() < 0.4:   # the engine publishes a state where the request stands
                 block = mine.block_at(request, committed // 32 * 32)
-                both("publish_state", block, 100, bool(rng.random() < 0.3))
+                if tier and rng.random() < 0.7 and not mine.cache.state_info(block)["contains"]:
+                    both("publish_stored", block, 100, bool(rng.random() < 0.2))   # a state the model stores elsewhere
+                else:
+                    both("publish_state", block, 100, bool(rng.random() < 0.3))
             for boundary in range(32, committed + 1, 32):
                 a, b = both("block_at", request, boundary)
                 assert a == b, ("block_at", seed, a, b)
@@ -264,7 +306,8 @@ def run_trace(seed, steps, tier):
             assert found_a == found_b, ("lookup", seed, found_a, found_b, log[-6:])
         elif op == "state" and blocks:
             block = int(rng.choice(sorted(blocks)))
-            if mine.cache.block_state(block) is None or mine.cache.block_state(block)["page"] == 0xFFFFFFFF or mine.cache.block_state(block)["transferring"]:
+            found = mine.cache.block_state(block)   # the engine publishes where a request stands: on a resident, readable block
+            if found is None or found["page"] == 0xFFFFFFFF or found["transferring"] or found["poisoned"]:
                 continue
             both("publish_state", block, int(rng.choice([100, 150, 200])), bool(rng.random() < 0.3))
         elif op == "use" and blocks:
@@ -272,7 +315,7 @@ def run_trace(seed, steps, tier):
             if block in used:
                 both("use", block, False)
                 used.discard(block)
-            elif mine.cache.state_info(block)["contains"]:
+            elif mine.cache.block_state(block) is not None and mine.cache.state_info(block)["contains"]:
                 both("use", block, True)
                 used.add(block)
         elif op == "pin":

@@ -172,7 +172,8 @@ def test_a_failed_restore_drops_the_blocks_below_it():
     land(cache); land(cache)                                    # ... the two below it land
     assert cache.restore_status(2) == 2 and cache.snapshot()["failed_transfers"] == 1
     assert len(cache.lookup(text)) == 1                         # the chain ends above the poisoned block at once
-    assert cache.snapshot()["tier_blocks"] == 3                 # while the request holds them, they stay
+    assert cache.snapshot()["tier_blocks"] == 2                 # the copy that failed to read is given up at once; the blocks
+    assert all(cache.block_state(b) is not None for b in chain)  # stay while the request holds them
     cache.end_request(2)
     # once the request has let go, the poisoned block and everything below it leave, pages and tier slots with them
     assert cache.snapshot()["tier_blocks"] == 0 and pool.snapshot()["pages_prefix"] == 1
