@@ -466,12 +466,7 @@ int rk_cache_state_publish(void *cache, uint64_t block, uint64_t bytes, int chec
 // A state whose only copy the model stores elsewhere (StateCache::publishStateToDisk): no RAM, no reclaim candidate,
 // but the KV it restores through stays worth a tier copy.
 int rk_cache_state_publish_stored(void *cache, uint64_t block, uint64_t bytes, int checkpoint) {
-  return guarded([&] {
-    if (!CACHE->index().contains(block)) throw std::invalid_argument("a composite state needs its KV block in the cache");
-    if (!bytes) throw std::invalid_argument("a composite state has a size");
-    CACHE->states().publishStored(block, bytes, checkpoint != 0);
-    return RK_OK;
-  });
+  return guarded([&] { CACHE->publishStoredState(block, bytes, checkpoint != 0); return RK_OK; });
 }
 int rk_cache_state_use(void *cache, uint64_t block, int use) {
   return guarded([&] { if (use) CACHE->states().use(block); else CACHE->states().unuse(block); return RK_OK; });

@@ -4,6 +4,7 @@
 #include <cstring>
 #include <map>
 #include <stdexcept>
+#include <utility>
 
 namespace rkb::engine {
 
@@ -789,6 +790,13 @@ void Cache::publishCompositeState(uint64_t block, uint64_t bytes, bool checkpoin
   states_.publish(block, bytes, checkpoint);
 }
 
+void Cache::publishStoredState(uint64_t block, uint64_t bytes, bool checkpoint) {
+  if (!index_.contains(block)) throw std::invalid_argument("a composite state needs its KV block in the cache");
+  if (!bytes) throw std::invalid_argument("a composite state has a size");
+  states_.publishStored(block, bytes, checkpoint);
+  stateWriteRetired_ = true;
+}
+
 std::optional<Cache::Victim> Cache::reclaimOldest(bool inUse, bool keepResumePoint, bool pagesOnly) {
   using Candidate = PrefixIndex::Candidate;
   // A dead leaf (no state restores through it) goes before anything a state needs; one that cannot go now stays
@@ -892,7 +900,7 @@ void Cache::pollTransfers() {
   tier_->poll();
   // Waiting restores start in block order and stop at the first the tier refuses: started ones stay a prefix of each
   // chain, and a full tier is asked once per poll, not once per waiting block (Cache::pollTransfers, Cache.cpp:938-956).
-  bool refused = false, progressed = false;
+  bool refused = false, progressed = std::exchange(stateWriteRetired_, false);
   for (size_t i = 0; i < restores_.size();) {
     Transfer &t = restores_[i];
     if (!t.ticket) {

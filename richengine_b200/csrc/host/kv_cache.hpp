@@ -202,6 +202,9 @@ public:
   // A complete block of a request's chain (Cache::blockAt): the block that ends at `tokens`, 0 when not published.
   uint64_t blockAt(uint64_t request, uint32_t tokens) const;
   void publishCompositeState(uint64_t block, uint64_t bytes, bool checkpoint);
+  // A state the model stores elsewhere (StateCache::publishStored). Its write counts as retired at the next poll,
+  // which therefore looks at the poisoned blocks again, as the reference's does after a state write (Cache.cpp:933-934).
+  void publishStoredState(uint64_t block, uint64_t bytes, bool checkpoint);
   // Only a state restores a chain that has left the pool, through its own block and every block above
   // (Cache.hpp:549-556): such KV is needed by that state, and in use when the state is.
   bool kvNeededByState(uint64_t block) const { return states_.contains(block) || index_.stateBelow(block); }
@@ -365,7 +368,7 @@ private:
   std::unordered_map<uint64_t, Request> requests_;
   std::vector<Transfer> demotions_, restores_;
   std::vector<uint64_t> poisoned_; // blocks whose restore failed, until they and what hangs below them have gone
-  bool stateCoupled_ = false;
+  bool stateCoupled_ = false, stateWriteRetired_ = false;
   CacheSnapshot counters_;
 };
 
