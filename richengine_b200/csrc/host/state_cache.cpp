@@ -44,6 +44,18 @@ void StateCache::publishStored(uint64_t block, uint64_t bytes, bool checkpoint) 
   if (!block) throw std::invalid_argument("a composite state sits on a KV block");
   if (contains(block)) throw std::logic_error("a block's state is published once");
   const bool disposable = checkpoint && !inUse(block);
+  auto found = states_.find(block);
+  if (found != states_.end()) { // a condemned entry a reader still pins is taken over by the new publication
+    State &state = found->second;
+    if (state.resident) bytes_ -= state.bytes;
+    state.invalid = false;
+    state.resident = false;
+    state.stored = true;
+    state.bytes = bytes;
+    state.checkpoint = state.checkpoint && disposable;
+    if (!state.checkpoint && note_) note_(block);
+    return;
+  }
   State state{bytes, clock_(), disposable, 0};
   state.resident = false;
   state.stored = true;

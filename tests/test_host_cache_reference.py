@@ -256,9 +256,9 @@ def run_trace(seed, steps, tier):
             assert mine.restore_status(request) == theirs.restore_status(request), (what, "restore status", request, seed, log[-6:])
 
     for step in range(steps):
-        op = rng.choice(["begin", "grow", "publish", "end", "lookup", "state", "use", "evict", "poll", "pin", "reclaim", "state_reclaim", "probe"],
-                        p=[0.10, 0.20, 0.18, 0.06, 0.05, 0.08, 0.04, 0.09, 0.08, 0.03, 0.04, 0.02, 0.03] if tier else
-                          [0.10, 0.22, 0.20, 0.06, 0.06, 0.10, 0.05, 0.05, 0.02, 0.04, 0.04, 0.02, 0.04])
+        op = rng.choice(["begin", "grow", "publish", "end", "lookup", "state", "use", "evict", "poll", "pin", "reclaim", "state_reclaim", "probe", "tier"],
+                        p=[0.10, 0.20, 0.18, 0.06, 0.05, 0.08, 0.04, 0.09, 0.07, 0.03, 0.04, 0.02, 0.03, 0.01] if tier else
+                          [0.10, 0.22, 0.20, 0.06, 0.06, 0.10, 0.05, 0.05, 0.02, 0.04, 0.04, 0.02, 0.04, 0.00])
         if op == "begin" and len(active) < 4:
             request, next_request = next_request, next_request + 1
             index = int(rng.integers(len(prompts)))
@@ -360,6 +360,8 @@ def run_trace(seed, steps, tier):
                 if slot is not None:
                     assert mine.probe_tokens(a) == theirs.probe_tokens(b), ("probe", seed, mine.probe_tokens(a), theirs.probe_tokens(b), log[-6:])
             log.append(("probe", (), {}, None, None))
+        elif op == "tier":   # the tier takes fewer or more transfers at a time, or no writes at all (a failed write closed it)
+            both("tier_set", int(rng.choice([0, 1, 2, 4])), bool(rng.random() < 0.8))
         elif op == "poll" and tier:
             if rng.random() < 0.7:
                 both("complete", bool(rng.random() < 0.9))
