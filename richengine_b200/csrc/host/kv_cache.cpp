@@ -372,14 +372,15 @@ uint32_t PrefixIndex::tierBlocks() const noexcept {
 // ================================== Cache ========================================================
 Cache::~Cache() {
   // Transfers read or write their pages in place: they retire before the pages can go.
-  for (auto *list : {&demotions_, &restores_})
-    for (Transfer &t : *list) {
-      if (t.ticket) { // a restore that was never submitted has no IO to drain
-        while (!t.ticket->ready()) tier_->poll();
-        t.ticket->finish();
-      }
-      if (index_.contains(t.block)) index_.setTransferring(t.block, false);
+  const auto drain = [this](Transfer &t) {
+    if (t.ticket) { // a restore that was never submitted has no IO to drain
+      while (!t.ticket->ready()) tier_->poll();
+      t.ticket->finish();
     }
+    if (index_.contains(t.block)) index_.setTransferring(t.block, false);
+  };
+  for (Transfer &t : demotions_) drain(t);
+  for (auto &[block, t] : restores_) drain(t);
   for (auto &[id, active] : requests_) {
     for (uint32_t page : active.pages) pool_.releasePage(page, false);
     if (!active.blocks.empty()) index_.releaseActive(active.blocks.back());
@@ -410,12 +411,13 @@ void Cache::endRequest(uint64_t id) {
   // Reads that were never submitted have no IO to drain: their pages return leaf first, unless another request
   // waits for the block, a block below it is resident, or a state was published on it meanwhile (Cache::endRequest,
   // Cache.cpp:160-175; KvCache::abandonRestore, KvCache.cpp:411-418).
-  if (found->second.pendingRestores)
-    for (Transfer &t : restores_) std::erase(t.waiters, id);
   const std::vector<uint64_t> &chain = found->second.blocks;
+  if (found->second.pendingRestores)
+    for (uint64_t block : chain)
+      if (auto waited = restores_.find(block); waited != restores_.end()) std::erase(waited->second.waiters, id);
   for (auto block = chain.rbegin(); block != chain.rend() && !restores_.empty(); ++block) {
-    auto queued = std::find_if(restores_.begin(), restores_.end(), [&](const Transfer &t) { return t.block == *block; });
-    if (queued == restores_.end() || queued->ticket || !queued->waiters.empty() || states_.stateResident(*block)) continue;
+    auto queued = restores_.find(*block);
+    if (queued == restores_.end() || queued->second.ticket || !queued->second.waiters.empty() || states_.stateResident(*block)) continue;
     if (!index_.contains(*block)) continue; // a poisoned tip left with the request's hold on it
     if (!index_.abandonRestore(*block)) continue;
     restores_.erase(queued);
@@ -593,19 +595,16 @@ TokenAdmission Cache::attachPrefix(uint64_t id, std::span<const uint64_t> blocks
       Transfer restore{block, page, nullptr, index_.slot(block)};
       if (!refused && tier_->canRestore()) restore.ticket = tier_->restore(restore.slot, page);
       if (!restore.ticket) refused = true;
-      // kept in block order (a parent's id is lower than its children's): a poll starts the waiting ones in that
-      // order, so started reads stay a prefix of each chain; a refused start is retried by pollTransfers
-      restores_.insert(std::upper_bound(restores_.begin(), restores_.end(), block, [](uint64_t id, const Transfer &t) { return id < t.block; }),
-                       std::move(restore));
+      restores_.emplace(block, std::move(restore)); // a refused start is retried by pollTransfers, in block order
       ++counters_.restores;
       // the pool's acquisition gave the request an active reference already
     } else {
       pool_.retainPage(page, false);
     }
     active.pages.push_back(page);
-    auto pending = std::find_if(restores_.begin(), restores_.end(), [&](const Transfer &t) { return t.block == block; });
+    auto pending = restores_.find(block);
     if (pending != restores_.end()) { // its own read, or one another request started: both wait for it
-      pending->waiters.push_back(id);
+      pending->second.waiters.push_back(id);
       ++active.pendingRestores;
     }
   }
@@ -901,15 +900,15 @@ void Cache::pollTransfers() {
   // Waiting restores start in block order and stop at the first the tier refuses: started ones stay a prefix of each
   // chain, and a full tier is asked once per poll, not once per waiting block (Cache::pollTransfers, Cache.cpp:938-956).
   bool refused = false, progressed = std::exchange(stateWriteRetired_, false);
-  for (size_t i = 0; i < restores_.size();) {
-    Transfer &t = restores_[i];
+  for (auto entry = restores_.begin(); entry != restores_.end();) {
+    Transfer &t = entry->second;
     if (!t.ticket) {
       if (!refused && tier_->canRestore()) t.ticket = tier_->restore(t.slot, t.page);
       if (!t.ticket) refused = true;
-      ++i;
+      ++entry;
       continue;
     }
-    if (!t.ticket->ready()) { ++i; continue; }
+    if (!t.ticket->ready()) { ++entry; continue; }
     const bool landed = t.ticket->finish();
     index_.setTransferring(t.block, false);
     for (uint64_t waiter : t.waiters) {
@@ -926,7 +925,7 @@ void Cache::pollTransfers() {
       index_.poison(t.block);  // it matches nothing any more; its users recompute
       poisoned_.push_back(t.block);
     }
-    restores_.erase(restores_.begin() + long(i));
+    entry = restores_.erase(entry);
     progressed = true;
   }
   // demotions after the restores, as the reference retires them (Cache.cpp:978-998): a waiting read starts at the
@@ -953,7 +952,7 @@ void Cache::pollTransfers() {
 bool Cache::compactExtent() {
   std::vector<uint32_t> fixed; // pages a transfer reads or writes in place stay where they are
   for (const Transfer &t : demotions_) fixed.push_back(t.page);
-  for (const Transfer &t : restores_) fixed.push_back(t.page);
+  for (const auto &[block, t] : restores_) fixed.push_back(t.page);
   const KvPageMoves moves = pool_.compactExtent(fixed);
   if (moves.empty()) return false;
   index_.followPages(moves);

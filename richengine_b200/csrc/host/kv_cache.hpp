@@ -19,6 +19,7 @@
 #include "state_cache.hpp"
 
 #include <functional>
+#include <map>
 
 #include <array>
 #include <cstdint>
@@ -366,7 +367,8 @@ private:
   size_t extendMatch(std::vector<uint64_t> &blocks, std::span<const uint32_t> prompt) const;
   uint32_t stateTokens(std::span<const uint64_t> blocks) const;
   std::unordered_map<uint64_t, Request> requests_;
-  std::vector<Transfer> demotions_, restores_;
+  std::vector<Transfer> demotions_;
+  std::map<uint64_t, Transfer> restores_; // by block: a parent's id is lower than its children's, so this is chain order
   std::vector<uint64_t> poisoned_; // blocks whose restore failed, until they and what hangs below them have gone
   bool stateCoupled_ = false, stateWriteRetired_ = false;
   CacheSnapshot counters_;
