@@ -415,7 +415,8 @@ void Cache::endRequest(uint64_t id) {
   if (found->second.pendingRestores)
     for (uint64_t block : chain)
       if (auto waited = restores_.find(block); waited != restores_.end()) std::erase(waited->second.waiters, id);
-  for (auto block = chain.rbegin(); block != chain.rend() && !restores_.empty(); ++block) {
+  // only a request that waited for reads takes any back
+  for (auto block = chain.rbegin(); found->second.pendingRestores && block != chain.rend() && !restores_.empty(); ++block) {
     auto queued = restores_.find(*block);
     if (queued == restores_.end() || queued->second.ticket || !queued->second.waiters.empty() || states_.stateResident(*block)) continue;
     if (!index_.contains(*block)) continue; // a poisoned tip left with the request's hold on it
