@@ -10,6 +10,9 @@
 //   runtime/metal/abi/KvExtent.h                 offsets and page entries
 //   runtime/ops/PagedAttention.{hpp,cpp}         plans: kernel names, grids, workspaces
 //   runtime/engine/cache/KvPool.{hpp,cpp}        the page allocator
+//   runtime/model/SlotFile.{hpp,cpp}, Crc32c.hpp   the persistent slot file and its record file (Darwin's fcntl
+//                                                commands and the ARM CRC intrinsics stood in for by
+//                                                darwin_clock_shim.h and darwin_shim/arm_acle.h)
 //   runtime/engine/cache/{Cache,KvCache,StateCache}.{hpp,cpp}  the request cache facade, its block graph and the
 //                                                state cache it couples KV reclaim to, over the reference's own test
 //                                                tier (dev/tests/engine/TestKvTier.hpp)
@@ -17,6 +20,7 @@
 #include "Fp8PageFormatReference.hpp"
 #include "engine/cache/Cache.hpp"
 #include "engine/cache/KvPool.hpp"
+#include "model/SlotFile.hpp"
 #include "TestKvTier.hpp"
 #include "ops/PagedAttention.hpp"
 
@@ -456,6 +460,74 @@ void ref_cache_snapshot(void *facade, uint64_t *out) {
   out[12] = s.lookup.kvHitTokens; out[13] = s.lookup.lazyJunctions; out[14] = s.lookup.lostStateMisses; out[15] = s.lookup.probeHashedBlocks;
 }
 #undef FACADE
+
+
+// ---- the reference's persistent slot file --------------------------------------------------
+namespace {
+model::SlotFile::Persistence persistence_of(const char *slots, const char *records, const void *tag, uint32_t tag_bytes, uint32_t label_bytes) {
+  model::SlotFile::Persistence p;
+  p.slots = slots; p.records = records; p.labelBytes = label_bytes;
+  p.tag.assign(static_cast<const std::byte *>(tag), static_cast<const std::byte *>(tag) + tag_bytes);
+  return p;
+}
+} // namespace
+
+// Opens (or creates) the pair of files, drops what an earlier process left, and writes `count` slots: payload i
+// (payload_bytes each) with label i (label_bytes each), each write waited for, then a flush to the drive and a clean
+// seal. Returns the slots written, or -1.
+int ref_slotfile_write(const char *slots, const char *records, const void *tag, uint32_t tag_bytes, uint32_t label_bytes,
+                       uint64_t slot_bytes, uint32_t count, const uint8_t *payloads, uint64_t payload_bytes, const uint8_t *labels) {
+  try {
+    auto budget = std::make_shared<model::DiskBudget>(uint64_t(1) << 40);
+    model::SlotFile file(slot_bytes, budget, persistence_of(slots, records, tag, tag_bytes, label_bytes));
+    file.finishAdoption();
+    std::vector<std::shared_ptr<model::SlotFile::Slot>> held;
+    int written = 0;
+    for (uint32_t i = 0; i < count; ++i) {
+      auto slot = file.acquire();
+      if (!slot) return -1;
+      const auto *bytes = reinterpret_cast<const std::byte *>(payloads + uint64_t(i) * payload_bytes);
+      auto operation = file.write(slot, {std::span<const std::byte>(bytes, payload_bytes)}, {});
+      if (!operation) return -1;
+      const auto *label = reinterpret_cast<const std::byte *>(labels + uint64_t(i) * label_bytes);
+      file.label(slot, std::vector<std::byte>(label, label + label_bytes));
+      if (!operation->wait()) return -1;
+      held.push_back(std::move(slot));
+      ++written;
+    }
+    auto flushed = file.synchronize({});
+    if (!flushed || !flushed->wait()) return -1;
+    file.seal();
+    return written;
+  } catch (...) { return -1; }
+}
+
+// Opens the pair of files and reports what an earlier process left: per record its slot index, payload size and
+// checksum, its label (label_bytes each into labels), and the payload read back through an adopted slot (whose first
+// read is checked against the record) into payloads (payload_capacity each); ok[i] = that read succeeded. Returns the
+// records found (at most capacity are reported), or -1. The files stay as they were.
+int ref_slotfile_read(const char *slots, const char *records, const void *tag, uint32_t tag_bytes, uint32_t label_bytes,
+                      uint64_t slot_bytes, uint32_t capacity, uint32_t *indices, uint64_t *payload_bytes, uint32_t *checksums,
+                      uint8_t *labels, uint8_t *payloads, uint64_t payload_capacity, uint8_t *ok) {
+  try {
+    auto budget = std::make_shared<model::DiskBudget>(uint64_t(1) << 40);
+    model::SlotFile file(slot_bytes, budget, persistence_of(slots, records, tag, tag_bytes, label_bytes));
+    const std::vector<model::SlotRecord> found = file.records();
+    std::vector<std::shared_ptr<model::SlotFile::Slot>> held;
+    for (const model::SlotRecord &record : found) held.push_back(file.adopt(record));
+    file.finishAdoption();
+    for (size_t i = 0; i < found.size() && i < capacity; ++i) {
+      indices[i] = found[i].index; payload_bytes[i] = found[i].payloadBytes; checksums[i] = found[i].checksum;
+      std::memcpy(labels + i * label_bytes, found[i].label.data(), std::min<size_t>(label_bytes, found[i].label.size()));
+      auto *destination = reinterpret_cast<std::byte *>(payloads + i * payload_capacity);
+      const uint64_t size = std::min<uint64_t>(payload_capacity, found[i].payloadBytes);
+      auto operation = file.read(held[i], {std::span<std::byte>(destination, size)}, {});
+      ok[i] = operation && operation->wait();
+    }
+    file.seal();
+    return int(found.size());
+  } catch (...) { return -1; }
+}
 
 } // extern "C"
 

@@ -233,3 +233,92 @@ def test_a_second_seal_is_written_beside_the_first_and_frees_it_afterwards(tmp_p
     assert cache.adopt(store) == {"blocks": 4, "dropped": 0, "bytes": 400}
     assert cache.lookup(a) == [1, 2, 3, 4]
     store.close(); cache.close(); pool.close()
+
+
+# ---- against the reference's OWN slot file, compiled in place (runtime/model/SlotFile.cpp into oracle/_ref) --------
+needs_slot_file = pytest.mark.skipif(om.reference() is None or not hasattr(om.reference(), "ref_slotfile_write"),
+                                     reason="the reference's slot file was not compiled here")
+SLOT_BYTES, LABEL_BYTES, TAG = 32768, KV_BLOCK_LABEL_BYTES, b"int4/16x4x256/v1"
+
+
+def reference_write(tmp_path, payloads, labels, payload_bytes):
+    r = om.reference()
+    flat = np.ascontiguousarray(np.stack(payloads), dtype=np.uint8)
+    flat_labels = np.frombuffer(b"".join(labels), dtype=np.uint8).copy()
+    tag = np.frombuffer(TAG, dtype=np.uint8).copy()
+    return r.ref_slotfile_write(str(tmp_path / "slots").encode(), str(tmp_path / "records").encode(), tag.ctypes.data, len(TAG),
+                                LABEL_BYTES, SLOT_BYTES, len(payloads), flat.ctypes.data, payload_bytes, flat_labels.ctypes.data)
+
+
+def reference_read(tmp_path, capacity=16):
+    r = om.reference()
+    tag = np.frombuffer(TAG, dtype=np.uint8).copy()
+    indices, sizes, sums = np.zeros(capacity, np.uint32), np.zeros(capacity, np.uint64), np.zeros(capacity, np.uint32)
+    labels, payloads, ok = np.zeros((capacity, LABEL_BYTES), np.uint8), np.zeros((capacity, SLOT_BYTES), np.uint8), np.zeros(capacity, np.uint8)
+    found = r.ref_slotfile_read(str(tmp_path / "slots").encode(), str(tmp_path / "records").encode(), tag.ctypes.data, len(TAG),
+                                LABEL_BYTES, SLOT_BYTES, capacity, indices.ctypes.data, sizes.ctypes.data, sums.ctypes.data,
+                                labels.ctypes.data, payloads.ctypes.data, SLOT_BYTES, ok.ctypes.data)
+    assert found >= 0
+    return [{"index": int(indices[i]), "payload_bytes": int(sizes[i]), "checksum": int(sums[i]), "label": labels[i].tobytes(),
+             "payload": payloads[i, : int(sizes[i])].copy(), "ok": bool(ok[i])} for i in range(min(found, capacity))]
+
+
+def some_slots(seed, count, payload_bytes):
+    rng = np.random.default_rng(seed)
+    payloads = [rng.integers(0, 256, payload_bytes, dtype=np.uint8) for _ in range(count)]
+    labels = [kv_block_label(10 + i, 9 + i if i else 0, 100 + i, rng.integers(0, 50000, 32).tolist(), images=(i, 2 * i)) for i in range(count)]
+    return payloads, labels
+
+
+@needs_slot_file
+def test_what_the_reference_writes_this_store_reads(tmp_path):
+    payloads, labels = some_slots(3, 5, 30000)
+    assert reference_write(tmp_path, payloads, labels, 30000) == 5
+    store = SlotStore(tmp_path / "slots", tmp_path / "records", TAG, LABEL_BYTES, SLOT_BYTES)
+    found = sorted(store.records(), key=lambda record: record["index"])
+    assert [record["index"] for record in found] == list(range(5))
+    for record, payload, label in zip(found, payloads, labels):
+        assert record["payload_bytes"] == 30000 and record["label"] == label
+        assert record["checksum"] == crc(payload.tobytes())     # the reference's worker took it while writing
+        assert np.array_equal(store.read(record["index"], 30000), payload)
+    store.close()
+
+
+@needs_slot_file
+def test_what_this_store_writes_the_reference_reads_and_verifies(tmp_path):
+    payloads, labels = some_slots(4, 6, 20000)
+    store = SlotStore(tmp_path / "slots", tmp_path / "records", TAG, LABEL_BYTES, SLOT_BYTES)
+    for index, (payload, label) in enumerate(zip(payloads, labels)):
+        assert store.write(index, payload, crc(payload.tobytes()), label)
+    assert store.free(2)                                         # a freed slot has no record for the next process
+    assert store.synchronize()
+    store.close()
+    found = sorted(reference_read(tmp_path), key=lambda record: record["index"])
+    assert [record["index"] for record in found] == [0, 1, 3, 4, 5]
+    for record in found:
+        assert record["ok"], "the reference's first read of an adopted slot checks the payload against its record"
+        assert record["payload_bytes"] == 20000 and record["label"] == labels[record["index"]]
+        assert record["checksum"] == crc(payloads[record["index"]].tobytes())
+        assert np.array_equal(record["payload"], payloads[record["index"]])
+    # a payload that changed after its record was written fails the reference's check: a cache miss, nothing worse
+    with open(tmp_path / "slots", "r+b") as slots:
+        slots.seek(3 * SLOT_BYTES + 100)
+        slots.write(b"\xff\xfe\xfd")
+    damaged = {record["index"]: record["ok"] for record in reference_read(tmp_path)}
+    assert damaged == {0: True, 1: True, 3: False, 4: True, 5: True}
+
+
+@needs_slot_file
+def test_both_write_the_same_bytes(tmp_path):
+    payloads, labels = some_slots(5, 4, 32768)                   # whole slots: no tail for either side to zero differently
+    (tmp_path / "theirs").mkdir(); (tmp_path / "mine").mkdir()
+    assert reference_write(tmp_path / "theirs", payloads, labels, 32768) == 4
+    store = SlotStore(tmp_path / "mine" / "slots", tmp_path / "mine" / "records", TAG, LABEL_BYTES, SLOT_BYTES)
+    for index, (payload, label) in enumerate(zip(payloads, labels)):
+        assert store.write(index, payload, crc(payload.tobytes()), label)
+    assert store.synchronize()
+    store.close()
+    assert (tmp_path / "mine" / "slots").read_bytes() == (tmp_path / "theirs" / "slots").read_bytes()
+    mine, theirs = (tmp_path / "mine" / "records").read_bytes(), (tmp_path / "theirs" / "records").read_bytes()
+    used = 4096 + 4 * 192                                        # header area and four records
+    assert mine[:used] == theirs[:used] and not any(mine[used:]) and not any(theirs[used:])
