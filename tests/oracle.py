@@ -114,6 +114,10 @@ def reference():
             r.ref_slotfile_write.argtypes = [C.c_char_p, C.c_char_p, vp, u32, u32, u64, u32, vp, u64, vp]
             r.ref_slotfile_read.restype = C.c_int
             r.ref_slotfile_read.argtypes = [C.c_char_p, C.c_char_p, vp, u32, u32, u64, u32, vp, vp, vp, vp, vp, u64, vp]
+        if hasattr(r, "ref_metal_store_verify"):  # the reference's Metal store and compaction kernels run on host threads
+            r.ref_metal_store_verify.restype, r.ref_metal_store_verify.argtypes = C.c_int, [u32, vp, vp, vp, vp, u32]
+            r.ref_metal_store_chunk.restype, r.ref_metal_store_chunk.argtypes = C.c_int, [u32, vp, vp, vp, vp]
+            r.ref_metal_tree_compact.restype, r.ref_metal_tree_compact.argtypes = C.c_int, [u32, vp, vp, vp, vp, u32]
         _reference = r
     return _reference
 
