@@ -1,0 +1,226 @@
+// ref_metal_kernels.cpp — the reference's OWN store, tree-compaction and attention kernels (Metal source), compiled as C++ in place
+// from the reference checkout and run on host threads: one std::thread per Metal thread of a threadgroup, barriers as
+// std::barrier, 32 consecutive threads a SIMD group. Address spaces and kernel attributes mean nothing on the host;
+// everything else — the row decode, the page addressing, the maximum reduction, the quantiser expressions, the nibble
+// packing, the copy order of the compaction, the attention tile's page loop with its admission rule, scale folds, online
+// softmax, bf16 probabilities and conditional rescale, and the fixed-order merge of the splits — is the reference's
+// text (never copied into this repository). The tensor operations the tile calls are stood in for by
+// metal_shim/MetalPerformancePrimitives (plain fp32 sums in index order; Metal's fast::exp is std::exp), so attention
+// agrees with the Metal kernels up to their arithmetic, not bit for bit.
+//
+// TEST INFRASTRUCTURE ONLY: built by oracle/Makefile into oracle/_ref/ where the reference checkout is present, used
+// by tests/ to pin the checker's stores and compaction against the reference kernels themselves.
+#include <barrier>
+#include <memory>
+#include <thread>
+#include <vector>
+
+#include "metal/kernels/common/paged_attention_tile.h"
+#include "metal/kernels/decode/paged_attention_store.metal"
+#include "metal/kernels/prefill/paged_attention_store.metal"
+
+thread_local uint rk_metal_thread_index = 0;
+
+namespace {
+constexpr uint kThreads = 256, kSimd = 32;
+struct Group {
+  std::barrier<> all{kThreads};
+  std::vector<std::unique_ptr<std::barrier<>>> simd;
+  float floats[kThreads];
+  uint words[kThreads];
+  float maxima[8]; // the kernels' `threadgroup float maxima[8]`
+  // the attention entries' threadgroup scratch, sized for sixteen rows of an eight-head group
+  static constexpr uint kRows = 128;
+  alignas(16) float scores[kRows * 32];
+  alignas(16) bfloat probabilities[2 * kRows * 32];
+  float row_max[kRows], row_sum[kRows], previous_scale[kRows];
+  std::atomic<uint> rescale{0};
+  float weights[RICHENGINE_VERIFY_ATTENTION_MAXIMUM_SPLITS], group_values[8];
+  Group() { for (uint i = 0; i < kThreads / kSimd; ++i) simd.push_back(std::make_unique<std::barrier<>>(kSimd)); }
+};
+thread_local Group *group_of_thread = nullptr;
+#define index_of_thread rk_metal_thread_index
+
+// Runs `groups` threadgroups one after another on 256 persistent host threads.
+template <typename Body> void dispatch(uint groups, Body body) {
+  auto holder = std::make_unique<Group>();
+  Group &shared = *holder;
+  std::vector<std::thread> threads;
+  for (uint t = 0; t < kThreads; ++t)
+    threads.emplace_back([&, t] {
+      group_of_thread = &shared;
+      index_of_thread = t;
+      for (uint g = 0; g < groups; ++g) {
+        body(g, t, t % kSimd, t / kSimd, shared);
+        shared.all.arrive_and_wait(); // the next threadgroup starts with this one's memory settled
+      }
+    });
+  for (std::thread &t : threads) t.join();
+}
+} // namespace
+
+namespace metal {
+void threadgroup_barrier(mem_flags) { group_of_thread->all.arrive_and_wait(); }
+void simdgroup_barrier(mem_flags) { group_of_thread->simd[index_of_thread / kSimd]->arrive_and_wait(); }
+float simd_max(float value) {
+  Group &g = *group_of_thread;
+  const uint base = index_of_thread / kSimd * kSimd;
+  g.floats[index_of_thread] = value;
+  g.simd[base / kSimd]->arrive_and_wait();
+  float result = g.floats[base];
+  for (uint lane = 1; lane < kSimd; ++lane) result = max(result, g.floats[base + lane]);
+  g.simd[base / kSimd]->arrive_and_wait();
+  return result;
+}
+float simd_sum(float value) {
+  Group &g = *group_of_thread;
+  const uint base = index_of_thread / kSimd * kSimd;
+  g.floats[index_of_thread] = value;
+  g.simd[base / kSimd]->arrive_and_wait();
+  float result = 0.0f;
+  for (uint lane = 0; lane < kSimd; ++lane) result += g.floats[base + lane];
+  g.simd[base / kSimd]->arrive_and_wait();
+  return result;
+}
+float simd_shuffle_xor(float value, ushort mask) {
+  Group &g = *group_of_thread;
+  const uint base = index_of_thread / kSimd * kSimd;
+  g.floats[index_of_thread] = value;
+  g.simd[base / kSimd]->arrive_and_wait();
+  const float result = g.floats[base + ((index_of_thread - base) ^ mask)];
+  g.simd[base / kSimd]->arrive_and_wait();
+  return result;
+}
+uint simd_shuffle_xor(uint value, ushort mask) {
+  Group &g = *group_of_thread;
+  const uint base = index_of_thread / kSimd * kSimd;
+  g.words[index_of_thread] = value;
+  g.simd[base / kSimd]->arrive_and_wait();
+  const uint result = g.words[base + ((index_of_thread - base) ^ mask)];
+  g.simd[base / kSimd]->arrive_and_wait();
+  return result;
+}
+} // namespace metal
+
+namespace {
+template <typename Element>
+void verify_store(const bfloat *keys, const bfloat *values, const RichKvPage *const *tables, const RichChunkedPrefillParams *params, uint lanes) {
+  const uint groups = lanes * 2 * params[0].chunk_tokens * 4;
+  dispatch(groups, [&](uint group, uint thread, uint lane, uint simd, Group &shared) {
+    richengine_store_verify_phase<4, Element>(keys, values, tables[0], tables[1], tables[2], tables[3], params, shared.maxima, group, thread, lane, simd);
+  });
+}
+template <typename Element>
+void chunk_store(const bfloat *keys, const bfloat *values, const RichKvPage *table, const RichChunkedPrefillParams &params) {
+  dispatch(2 * params.chunk_tokens * 4, [&](uint group, uint thread, uint lane, uint simd, Group &shared) {
+    richengine_store_chunk_phase<4, Element>(keys, values, table, params, shared.maxima, group, thread, lane, simd);
+  });
+}
+template <typename Element>
+void tree_compact(const RichKvPage *const *tables, const RichChunkedPrefillParams *params, const uint *path, const uint *count, uint lanes) {
+  dispatch(lanes * 4, [&](uint group, uint thread, uint, uint, Group &) {
+    richengine_compact_verify_tree_phase<4, Element>(tables[0], tables[1], tables[2], tables[3], params, path, count, group, thread);
+  });
+}
+// One verify step as the reference dispatches it (decode/paged_attention.metal): a threadgroup per (KV head, split,
+// lane) runs the tile, then a threadgroup per (KV head, fused row, lane) merges the splits. Rows = 8: the chain entries
+// (every tile processes all eight rows, the causal limit per row); Rows = 16: the tree entries (the lane's active rows
+// and its ancestor masks). Four KV heads of Q query heads each, head dimension 256.
+template <typename Element, uint Rows, uint Q>
+void verify_attention(bfloat *queries, const RichKvPage *const *tables, const RichVerifyAttentionParams *params, uint lanes,
+                      const uint *row_masks, float *partials, float *statistics, bfloat *output) {
+  constexpr uint KVHeads = 4, D = 256, M = Rows * Q;
+  constexpr ulong group_stride = ulong(RICHENGINE_VERIFY_CHUNK_STRIDE) * Q * D;
+  uint most_splits = 0;
+  for (uint lane = 0; lane < lanes; ++lane) most_splits = max(most_splits, params[lane].split_count);
+  dispatch(lanes * most_splits * KVHeads, [&](uint group, uint thread, uint, uint, Group &shared) {
+    const uint kv_head = group % KVHeads, split = group / KVHeads % most_splits, lane = group / (KVHeads * most_splits);
+    const RichVerifyAttentionParams &p = params[lane];
+    if (!richengine_verify_attention_contract_valid(p) || split >= p.split_count) return;
+    const ulong slot = (ulong(lane) * KVHeads + kv_head) * p.slot_splits + split;
+    const uint active = Rows == RICHENGINE_TARGET_VERIFY_ROWS ? Rows : p.active_rows;
+    const uint *masks = Rows == RICHENGINE_TARGET_VERIFY_ROWS ? nullptr : row_masks + ulong(lane) * p.row_capacity;
+    richengine_paged_attention_tile<KVHeads, Q, Rows, Element, D>(
+        queries + (ulong(lane) * KVHeads + kv_head) * group_stride, tables[lane], p.kv, kv_head, p.committed_tokens, active,
+        p.split_count, split, partials, statistics, slot, masks, p.score_scale, shared.scores, shared.probabilities,
+        shared.row_max, shared.row_sum, shared.previous_scale, &shared.rescale, thread);
+  });
+  dispatch(lanes * M * KVHeads, [&](uint group, uint thread, uint, uint, Group &shared) {
+    const uint kv_head = group % KVHeads, fused_row = group / KVHeads % M, lane = group / (KVHeads * M);
+    const RichVerifyAttentionParams &p = params[lane];
+    if (!richengine_verify_attention_contract_valid(p)) return;
+    const uint active = Rows == RICHENGINE_TARGET_VERIFY_ROWS ? Rows : p.active_rows;
+    richengine_attention_reduce_row<Q, Rows, D>(partials, statistics, output + (ulong(lane) * KVHeads + kv_head) * group_stride,
+                                                p.committed_tokens, active, p.split_count,
+                                                (ulong(lane) * KVHeads + kv_head) * p.slot_splits, fused_row, thread,
+                                                shared.weights, shared.group_values);
+  });
+}
+} // namespace
+
+extern "C" {
+// A verify step over `lanes` lanes (at most four) of four KV heads with `group` (6 or 4) query heads each: queries and
+// output are [lane][4][32][group][256] bf16; partials [(lane*4 + head)*slot_splits + split][rows*group][256] fp32 and
+// statistics [..][rows*group]{max, sum}, as the kernels lay them out. rows = 8 runs the chain entries, 16 the tree
+// entries (row_masks [lane][row_capacity]).
+int ref_metal_attention_verify(uint32_t format, uint32_t rows, uint32_t group, void *queries, const uint64_t *const *tables, const void *params,
+                               uint32_t lanes, const uint32_t *row_masks, float *partials, float *statistics, void *output) {
+  try {
+    auto *q = static_cast<bfloat *>(queries), *o = static_cast<bfloat *>(output);
+    const auto *t = reinterpret_cast<const RichKvPage *const *>(tables);
+    const auto *p = static_cast<const RichVerifyAttentionParams *>(params);
+    const auto run = [&](auto element, auto row_count, auto heads) {
+      verify_attention<typename decltype(element)::type, decltype(row_count)::value, decltype(heads)::value>(q, t, p, lanes, row_masks, partials, statistics, o);
+    };
+    const auto with_shape = [&](auto element) {
+      if (rows == 8 && group == 6) run(element, std::integral_constant<uint, 8>{}, std::integral_constant<uint, 6>{});
+      else if (rows == 8 && group == 4) run(element, std::integral_constant<uint, 8>{}, std::integral_constant<uint, 4>{});
+      else if (rows == 16 && group == 6) run(element, std::integral_constant<uint, 16>{}, std::integral_constant<uint, 6>{});
+      else if (rows == 16 && group == 4) run(element, std::integral_constant<uint, 16>{}, std::integral_constant<uint, 4>{});
+      else throw 0;
+    };
+    if (format == 1) with_shape(std::type_identity<int8_t>{});
+    else if (format == 2) with_shape(std::type_identity<bfloat>{});
+    else if (format == 3) with_shape(std::type_identity<RichKvPacked4>{});
+    else return -1;
+    return 0;
+  } catch (...) { return -1; }
+}
+// format: 1 int8, 2 bf16, 3 int4 (kv::Format). Four KV heads, head dimension 256. tables: four page-table pointers
+// (unused lanes may repeat the first). params: `lanes` RichChunkedPrefillParams.
+int ref_metal_store_verify(uint32_t format, const void *keys, const void *values, const uint64_t *const *tables, const void *params, uint32_t lanes) {
+  try {
+    const auto *k = static_cast<const bfloat *>(keys), *v = static_cast<const bfloat *>(values);
+    const auto *t = reinterpret_cast<const RichKvPage *const *>(tables);
+    const auto *p = static_cast<const RichChunkedPrefillParams *>(params);
+    if (format == 1) verify_store<int8_t>(k, v, t, p, lanes);
+    else if (format == 2) verify_store<bfloat>(k, v, t, p, lanes);
+    else if (format == 3) verify_store<RichKvPacked4>(k, v, t, p, lanes);
+    else return -1;
+    return 0;
+  } catch (...) { return -1; }
+}
+int ref_metal_store_chunk(uint32_t format, const void *keys, const void *values, const uint64_t *table, const void *params) {
+  try {
+    const auto *k = static_cast<const bfloat *>(keys), *v = static_cast<const bfloat *>(values);
+    const auto *t = reinterpret_cast<const RichKvPage *>(table);
+    const auto &p = *static_cast<const RichChunkedPrefillParams *>(params);
+    if (format == 1) chunk_store<int8_t>(k, v, t, p);
+    else if (format == 2) chunk_store<bfloat>(k, v, t, p);
+    else if (format == 3) chunk_store<RichKvPacked4>(k, v, t, p);
+    else return -1;
+    return 0;
+  } catch (...) { return -1; }
+}
+int ref_metal_tree_compact(uint32_t format, const uint64_t *const *tables, const void *params, const uint32_t *path, const uint32_t *count, uint32_t lanes) {
+  try {
+    const auto *t = reinterpret_cast<const RichKvPage *const *>(tables);
+    const auto *p = static_cast<const RichChunkedPrefillParams *>(params);
+    if (format == 1) tree_compact<int8_t>(t, p, path, count, lanes);
+    else if (format == 2) tree_compact<bfloat>(t, p, path, count, lanes);
+    else if (format == 3) tree_compact<RichKvPacked4>(t, p, path, count, lanes);
+    else return -1;
+    return 0;
+  } catch (...) { return -1; }
+}
+}

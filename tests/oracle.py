@@ -118,6 +118,9 @@ def reference():
             r.ref_metal_store_verify.restype, r.ref_metal_store_verify.argtypes = C.c_int, [u32, vp, vp, vp, vp, u32]
             r.ref_metal_store_chunk.restype, r.ref_metal_store_chunk.argtypes = C.c_int, [u32, vp, vp, vp, vp]
             r.ref_metal_tree_compact.restype, r.ref_metal_tree_compact.argtypes = C.c_int, [u32, vp, vp, vp, vp, u32]
+            if hasattr(r, "ref_metal_attention_verify"):
+                r.ref_metal_attention_verify.restype = C.c_int
+                r.ref_metal_attention_verify.argtypes = [u32, u32, u32, vp, vp, vp, u32, vp, vp, vp, vp]
         _reference = r
     return _reference
 

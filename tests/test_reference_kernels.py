@@ -1,9 +1,12 @@
-"""CPU: the checker's stores and tree compaction against the reference's OWN kernels. The Metal source of
-runtime/metal/kernels/common/paged_store_row.h, decode/paged_attention_store.metal and prefill/paged_attention_store.metal
-is compiled as C++ in place (oracle/ref_metal_store.cpp over oracle/metal_shim/metal_stdlib) and run on host threads,
-one per Metal thread: the row decode, the page addressing, the maximum reduction, the quantiser expressions, the nibble
-packing and the copy order are the reference's own text. Every byte of every extent must agree, for int8, int4 and
-bf16 (the fp8 store needs the hardware's fp8 pack; its encoder is pinned by the reference's C++ fp8 reference instead)."""
+"""CPU: the checker against the reference's OWN kernels. The Metal source of runtime/metal/kernels/common/
+paged_store_row.h, paged_attention_tile.h, decode/paged_attention_store.metal and prefill/paged_attention_store.metal is
+compiled as C++ in place (oracle/ref_metal_kernels.cpp over oracle/metal_shim) and run on host threads, one per Metal
+thread. Stores and tree compaction: the row decode, the page addressing, the maximum reduction, the quantiser
+expressions, the nibble packing and the copy order are the reference's own text, and every byte of every extent must
+agree, for int8, int4 and bf16 (the fp8 store needs the hardware's fp8 pack; its encoder is pinned by the reference's
+C++ fp8 reference instead). Attention: the reference's tile (admission rule, scale folds, online softmax with bf16
+probabilities, conditional rescale, partials and statistics per split) and its fixed-order merge, with the tensor
+operations stood in for by plain fp32 sums, against the checker's fp64 attention, chain and tree."""
 import ctypes as C
 
 import numpy as np
@@ -113,3 +116,115 @@ def test_tree_compaction_equals_the_reference_kernel(fmt):
         else:
             assert reference.ref_metal_tree_compact(fmt, four_tables(scenario), chunk, paths.ctypes.data, counts.ctypes.data, 3) == 0
     assert_same_bytes(mine, theirs, "tree compaction")
+
+
+# ---- attention: the reference's tile and its merge, run on host threads, against the checker's fp64 attention -------
+from kvcase import bf16_to_f32, fill_history_with_store, make_queries   # noqa: E402
+
+
+def reference_attention(fmt, rows, scenario, queries, params, masks, group=6):
+    lanes = scenario.lanes
+    slots = max(p.slot_splits for p in params)
+    partials = np.zeros((lanes * 4 * slots, rows * group, 256), np.float32)
+    statistics = np.zeros((lanes * 4 * slots, rows * group, 2), np.float32)
+    out = np.zeros((lanes, 4, 32, group, 256), np.uint16)
+    q = queries.copy()
+    assert reference.ref_metal_attention_verify(fmt, rows, group, q.ctypes.data, four_tables(scenario), params, lanes,
+                                                None if masks is None else masks.ctypes.data, partials.ctypes.data,
+                                                statistics.ctypes.data, out.ctypes.data) == 0
+    return out
+
+
+def checker_attention(fmt, scenario, queries, params, masks, group=6):
+    out = np.zeros((scenario.lanes, 4, 32, group, 256), np.float32)
+    out16 = np.zeros((scenario.lanes, 4, 32, group, 256), np.uint16)
+    assert om.oracle().rko_attention_verify(fmt, 4, group, 256, scenario.lanes, queries.ctypes.data, scenario.host_table_pointers(), params,
+                                            None if masks is None else masks.ctypes.data, out16.ctypes.data, out.ctypes.data) == 0
+    return out
+
+
+def store_rows(fmt, scenario, rows, seed):
+    k, v = make_staging(np.random.default_rng(seed), scenario.lanes, scenario.layout)
+    chunk = (lib.ChunkParams * scenario.lanes)(*[lib.ChunkParams(c, rows, 32, len(p), scenario.host.layer(0))
+                                                 for c, p in zip(scenario.contexts, scenario.pages)])
+    assert om.oracle().rko_store_verify(fmt, 4, 256, scenario.lanes, k.ctypes.data, v.ctypes.data, scenario.host_table_pointers(), chunk) == 0
+
+
+def assert_attention_close(theirs16, mine, active, what):
+    """The reference rounds each probability (times its value scale) to bf16 before the value contraction, so its own
+    output sits within 2^-8 of the largest magnitude of the exact fp64 attention (a convex combination of values each
+    off by at most 2^-9 relative, and a bf16 output). The bar is that bound: what is pinned is the algorithm (admission
+    rule, scale folds, online softmax across pages and splits, merge order, zero rows), not the last bit."""
+    for lane, rows in enumerate(active):
+        got, want = bf16_to_f32(theirs16[lane, :, :rows]), mine[lane, :, :rows]
+        bound = 2.0 ** -8 * max(1.0, float(np.abs(want).max())) + np.abs(want) * 2.0 ** -8
+        worst = float((np.abs(got - want) - bound).max())
+        assert worst <= 0, f"{what}: lane {lane} off by {worst} past the bar"
+        assert np.abs(want).max() > 0.05, "a comparison of zeros proves nothing"
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+@pytest.mark.parametrize("splits,group", [(1, 6), (3, 6), (2, 4)])
+def test_chain_verify_attention_agrees_with_the_reference_tile_and_merge(fmt, splits, group):
+    layout = Layout(1, 4, 256, fmt)
+    s = Scenario(layout, [150, 5, 0, 67], extra_tokens=8)
+    fill_history_with_store(s, 0)
+    store_rows(fmt, s, 8, 21)
+    q = make_queries(np.random.default_rng(6), s.lanes, layout, query_heads=4 * group)
+    params = (lib.VerifyParams * 4)(*[lib.VerifyParams(c, len(p), s.host.layer(0), splits, 4, 8, 8, 0.0) for c, p in zip(s.contexts, s.pages)])
+    theirs = reference_attention(fmt, 8, s, q, params, None, group)
+    mine = checker_attention(fmt, s, q, params, None, group)
+    assert_attention_close(theirs, mine, [8, 8, 8, 8], "chain verify")
+
+
+def tree_case(fmt, group):
+    layout = Layout(1, 4, 256, fmt)
+    s = Scenario(layout, [90, 31], extra_tokens=16)
+    fill_history_with_store(s, 0)
+    store_rows(fmt, s, 15, 22)
+    q = make_queries(np.random.default_rng(7), s.lanes, layout, query_heads=4 * group)
+    active = [11, 15]
+    params = (lib.VerifyParams * 2)(*[lib.VerifyParams(c, len(p), s.host.layer(0), 2, 2, a, 16, 0.0)
+                                      for c, p, a in zip(s.contexts, s.pages, active)])
+    rng = np.random.default_rng(8)
+    masks = np.zeros((2, 16), np.uint32)
+    for lane, rows in enumerate(active):       # a comb: every row sees itself and a random subset of the rows before it
+        for row in range(rows):
+            masks[lane, row] = (1 << row) | (int(rng.integers(0, 1 << row)) if row else 0)
+        masks[lane, 3] = 0                      # a row with an empty mask attends only committed history
+    return s, q, params, masks, active
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+def test_tree_verify_attention_agrees_with_the_reference_tile_and_merge(fmt):
+    """Four query heads per KV head: 64 fused rows, four softmax lanes of eight tokens per row, the shape the
+    reference's page softmax is written for."""
+    s, q, params, masks, active = tree_case(fmt, 4)
+    theirs = reference_attention(fmt, 16, s, q, params, masks, 4)
+    mine = checker_attention(fmt, s, q, params, masks, 4)
+    assert_attention_close(theirs, mine, active, "tree verify")
+    for lane, rows in enumerate(active):        # rows past the active ones are written as zeros by the reference's merge
+        assert not theirs[lane, :, rows:16].any() and not mine[lane, :, rows:16].any()
+
+
+def test_the_reference_tree_tile_of_six_heads_normalises_pairs_of_rows_together():
+    """A finding, recorded so that nobody mistakes it for a defect of this repository: with six query heads per KV head
+    a tree tile has 96 fused rows, more than 64, so the reference's page softmax takes sixteen tokens per lane, two
+    lanes per row (paged_attention_tile.h:308), but still folds the row maximum and the row sum over FOUR
+    neighbouring lanes (`simd_shuffle_xor(.., 1)` and `(.., 2)`, :147-148 and :162-163). Fused rows 2k and 2k+1 (two
+    query heads of one query row) therefore share one denominator: each comes out scaled by its share of the pair's
+    sum, and the two shares add up to one. The kernels and the checker of this repository normalise every row by its
+    own sum; the chain tile (48 rows) and the tree tile of four heads (64 rows) take the four-lane path and agree."""
+    s, q, params, masks, active = tree_case(INT8, 6)
+    theirs = bf16_to_f32(reference_attention(INT8, 16, s, q, params, masks, 6))
+    mine = checker_attention(INT8, s, q, params, masks, 6)
+    shares = []
+    for lane, rows in enumerate(active):
+        for row in range(rows):
+            for pair in range(3):
+                a, b = 2 * pair, 2 * pair + 1
+                strong = np.abs(mine[lane, 0, row, a]) > 1.0, np.abs(mine[lane, 0, row, b]) > 1.0
+                share_a = float(np.median(theirs[lane, 0, row, a][strong[0]] / mine[lane, 0, row, a][strong[0]]))
+                share_b = float(np.median(theirs[lane, 0, row, b][strong[1]] / mine[lane, 0, row, b][strong[1]]))
+                shares.append(share_a + share_b)
+    assert np.allclose(shares, 1.0, atol=0.02), (min(shares), max(shares))
