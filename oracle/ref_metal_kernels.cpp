@@ -17,6 +17,7 @@
 
 #include "metal/kernels/common/paged_attention_tile.h"
 #include "metal/kernels/decode/paged_attention_store.metal"
+#include "metal/kernels/prefill/paged_attention.metal"
 #include "metal/kernels/prefill/paged_attention_store.metal"
 
 thread_local uint rk_metal_thread_index = 0;
@@ -156,9 +157,40 @@ void verify_attention(bfloat *queries, const RichKvPage *const *tables, const Ri
                                                 shared.weights, shared.group_values);
   });
 }
+// A prefill chunk as the reference dispatches it (prefill/paged_attention.metal): its own split and reduce phases
+// place the tiles; a threadgroup per (KV head, tile, split), then one per (KV head, fused row, tile). One row is the
+// plain decode step.
+template <typename Element>
+void prefill_attention(bfloat *queries, const RichKvPage *table, const RichPrefillAttentionParams &params, float *partials, float *statistics, bfloat *output) {
+  constexpr uint KVHeads = 4, Q = 6, M = RICHENGINE_PREFILL_ATTENTION_TILE_ROWS * Q;
+  const uint tiles = (params.rows + RICHENGINE_PREFILL_ATTENTION_TILE_ROWS - 1) / RICHENGINE_PREFILL_ATTENTION_TILE_ROWS;
+  dispatch(KVHeads * tiles * params.split_count, [&](uint group, uint thread, uint, uint, Group &shared) {
+    const uint3 at{group % KVHeads, group / KVHeads % tiles, group / (KVHeads * tiles)};
+    richengine_prefill_attention_split_phase<KVHeads, Q, Element>(queries, partials, statistics, table, params, shared.scores, shared.probabilities,
+                                                                  shared.row_max, shared.row_sum, shared.previous_scale, &shared.rescale, at, thread);
+  });
+  dispatch(KVHeads * M * tiles, [&](uint group, uint thread, uint, uint, Group &shared) {
+    const uint3 at{group % KVHeads, group / KVHeads % M, group / (KVHeads * M)};
+    richengine_prefill_attention_reduce_phase<KVHeads, Q>(partials, statistics, output, params, at, thread, shared.weights, shared.group_values);
+  });
+}
 } // namespace
 
 extern "C" {
+// A prefill chunk (or, with one row, a decode step) of one sequence: queries and output are [4][chunk_stride][6][256]
+// bf16; partials [(tile*4 + head)*split_count + split][48][256] fp32, statistics [..][48]{max, sum}.
+int ref_metal_attention_prefill(uint32_t format, void *queries, const uint64_t *table, const void *params, float *partials, float *statistics, void *output) {
+  try {
+    auto *q = static_cast<bfloat *>(queries), *o = static_cast<bfloat *>(output);
+    const auto *t = reinterpret_cast<const RichKvPage *>(table);
+    const auto &p = *static_cast<const RichPrefillAttentionParams *>(params);
+    if (format == 1) prefill_attention<int8_t>(q, t, p, partials, statistics, o);
+    else if (format == 2) prefill_attention<bfloat>(q, t, p, partials, statistics, o);
+    else if (format == 3) prefill_attention<RichKvPacked4>(q, t, p, partials, statistics, o);
+    else return -1;
+    return 0;
+  } catch (...) { return -1; }
+}
 // A verify step over `lanes` lanes (at most four) of four KV heads with `group` (6 or 4) query heads each: queries and
 // output are [lane][4][32][group][256] bf16; partials [(lane*4 + head)*slot_splits + split][rows*group][256] fp32 and
 // statistics [..][rows*group]{max, sum}, as the kernels lay them out. rows = 8 runs the chain entries, 16 the tree

@@ -121,6 +121,8 @@ def reference():
             if hasattr(r, "ref_metal_attention_verify"):
                 r.ref_metal_attention_verify.restype = C.c_int
                 r.ref_metal_attention_verify.argtypes = [u32, u32, u32, vp, vp, vp, u32, vp, vp, vp, vp]
+                r.ref_metal_attention_prefill.restype = C.c_int
+                r.ref_metal_attention_prefill.argtypes = [u32, vp, vp, vp, vp, vp, vp]
         _reference = r
     return _reference
 

@@ -228,3 +228,35 @@ def test_the_reference_tree_tile_of_six_heads_normalises_pairs_of_rows_together(
                 share_b = float(np.median(theirs[lane, 0, row, b][strong[1]] / mine[lane, 0, row, b][strong[1]]))
                 shares.append(share_a + share_b)
     assert np.allclose(shares, 1.0, atol=0.02), (min(shares), max(shares))
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+@pytest.mark.parametrize("rows,committed,splits", [(21, 70, 2), (1, 150, 3), (1, 0, 1)])
+def test_prefill_and_decode_attention_agree_with_the_reference_phases(fmt, rows, committed, splits):
+    """The reference's own prefill split and reduce phases place the tiles (tile_start = 8 x tile, committed +
+    tile_start, active = min(8, rows - tile_start)); one row is the plain decode step."""
+    layout = Layout(1, 4, 256, fmt)
+    s = Scenario(layout, [committed], extra_tokens=rows)
+    fill_history_with_store(s, 0)
+    k, v = make_staging(np.random.default_rng(31), 1, layout, stride=32)
+    chunk = lib.ChunkParams(committed, rows, 32, len(s.pages[0]), s.host.layer(0))
+    assert om.oracle().rko_store_chunk(fmt, 4, 256, k.ctypes.data, v.ctypes.data, s.host_tables[0].ctypes.data, C.byref(chunk)) == 0
+    q = make_queries(np.random.default_rng(32), 1, layout)[0]            # [4][32][6][256], chunk stride 32
+    params = lib.PrefillParams(committed, rows, 32, len(s.pages[0]), s.host.layer(0), splits, 0.0)
+    tiles = (rows + 7) // 8
+    partials = np.zeros((tiles * 4 * splits, 48, 256), np.float32)
+    statistics = np.zeros((tiles * 4 * splits, 48, 2), np.float32)
+    theirs = np.zeros((4, 32, 6, 256), np.uint16)
+    assert reference.ref_metal_attention_prefill(fmt, q.copy().ctypes.data, s.host_tables[0].ctypes.data, C.byref(params),
+                                                 partials.ctypes.data, statistics.ctypes.data, theirs.ctypes.data) == 0
+    for tile in range(tiles):
+        start, active = 8 * tile, min(8, rows - 8 * tile)
+        for head in range(4):
+            mine = np.zeros((48, 256), np.float32)
+            assert om.oracle().rko_attention_tile(fmt, 4, 6, 256, head, q[head, start:].ctypes.data, s.host_tables[0].ctypes.data, s.host.layer(0),
+                                                  committed + start, active, 8, None, 0.0, 0, mine.ctypes.data) == 0
+            got = bf16_to_f32(theirs[head, start:start + 8]).reshape(48, 256)
+            bound = 2.0 ** -8 * max(1.0, float(np.abs(mine).max())) + np.abs(mine) * 2.0 ** -8
+            assert (np.abs(got - mine) <= bound).all(), (tile, head, float(np.abs(got - mine).max()))
+            assert not got[active * 6:].any() and not mine[active * 6:].any()   # rows past the chunk are zeros in both
+            assert np.abs(mine[: active * 6]).max() > 0.05
