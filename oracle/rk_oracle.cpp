@@ -4,9 +4,12 @@
 // smoke test, the benchmark's cpu_baseline leg). The product library never
 // links or calls it. Parity pinned: the int8 and fp8 quantizers, the bf16 and
 // e4m3 conversions and the page layout are checked against the reference's own
-// CPU headers compiled in place (oracle/ref_shim.cpp), and the int4 / bf16
-// stores, the merge and the attention against the closed-form fixtures of the
-// reference's tests (tests/test_oracle_pins.py).
+// CPU headers compiled in place (oracle/ref_shim.cpp); the int8 / int4 / bf16
+// stores, the tree compaction, the attention tile and the merge are checked
+// against the reference's own Metal kernel source compiled as C++ and run on
+// host threads (oracle/ref_metal_kernels.cpp, tests/test_reference_kernels.py),
+// and against the closed-form fixtures of the reference's tests
+// (tests/test_oracle_pins.py).
 //
 // Build: g++ -std=c++20 -O3 -march=native -fopenmp -shared -fPIC (oracle/Makefile).
 // -ffast-math must stay off: quantized codes are bit-exact by contract.
