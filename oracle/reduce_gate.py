@@ -6,8 +6,9 @@ attention row of (lane, row, query head) is multiplied, in fp32, by the logistic
 projection row carries beside that head's query (packed row layout per token: 24 heads x {query[256], gate[256]},
 then 4 key heads x 256, then 4 value heads x 256; indexing as :300-308), and stored as bf16 in the order the
 out-projection reads, [lane][row][query head][dim]. sigmoid(x) = 1 / (1 + exp2(-log2(e) * x)) as the shader writes
-it. Parity is pinned by the reference's closed form only (the reference has no CPU code for this epilogue): the
-exp2 of numpy and of the device may differ in the last place before the bf16 rounding, which the test bounds.
+it. Parity pinned: tests/test_reference_kernels.py runs the reference's own reduce/gate phase (its Metal source
+compiled as C++ on host threads) and finds these rows bit for bit; against the GPU the exp2 of numpy and of the device
+may differ in the last place before the bf16 rounding, which that test bounds.
 """
 import numpy as np
 

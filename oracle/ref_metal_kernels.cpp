@@ -16,6 +16,7 @@
 #include <vector>
 
 #include "metal/kernels/common/paged_attention_tile.h"
+#include "metal/kernels/decode/paged_attention.metal"
 #include "metal/kernels/decode/paged_attention_store.metal"
 #include "metal/kernels/prefill/paged_attention.metal"
 #include "metal/kernels/prefill/paged_attention_store.metal"
@@ -123,40 +124,40 @@ void tree_compact(const RichKvPage *const *tables, const RichChunkedPrefillParam
     richengine_compact_verify_tree_phase<4, Element>(tables[0], tables[1], tables[2], tables[3], params, path, count, group, thread);
   });
 }
-// One verify step as the reference dispatches it (decode/paged_attention.metal): a threadgroup per (KV head, split,
-// lane) runs the tile, then a threadgroup per (KV head, fused row, lane) merges the splits. Rows = 8: the chain entries
-// (every tile processes all eight rows, the causal limit per row); Rows = 16: the tree entries (the lane's active rows
-// and its ancestor masks). Four KV heads of Q query heads each, head dimension 256.
+// One verify step as the reference dispatches it (decode/paged_attention.metal): its own tile placement
+// (richengine_verify_attention_tile_at) for a threadgroup per (KV head, split, lane), the tile, then its own reduce phase
+// for a threadgroup per (KV head, fused row, lane). Rows = 8: the chain entries (every tile processes all eight rows,
+// the causal limit per row); Rows = 16: the tree entries (the lane's active rows and its ancestor masks). Four KV heads
+// of Q query heads each, head dimension 256. With gate buffers the chain's reduce is its reduce/gate phase.
 template <typename Element, uint Rows, uint Q>
 void verify_attention(bfloat *queries, const RichKvPage *const *tables, const RichVerifyAttentionParams *params, uint lanes,
-                      const uint *row_masks, float *partials, float *statistics, bfloat *output) {
+                      const uint *row_masks, float *partials, float *statistics, bfloat *output, const bfloat *packed_qkv = nullptr,
+                      bfloat *hidden = nullptr) {
   constexpr uint KVHeads = 4, D = 256, M = Rows * Q;
-  constexpr ulong group_stride = ulong(RICHENGINE_VERIFY_CHUNK_STRIDE) * Q * D;
+  constexpr bool chain = Rows == RICHENGINE_TARGET_VERIFY_ROWS;
   uint most_splits = 0;
   for (uint lane = 0; lane < lanes; ++lane) most_splits = max(most_splits, params[lane].split_count);
   dispatch(lanes * most_splits * KVHeads, [&](uint group, uint thread, uint, uint, Group &shared) {
-    const uint kv_head = group % KVHeads, split = group / KVHeads % most_splits, lane = group / (KVHeads * most_splits);
-    const RichVerifyAttentionParams &p = params[lane];
-    if (!richengine_verify_attention_contract_valid(p) || split >= p.split_count) return;
-    const ulong slot = (ulong(lane) * KVHeads + kv_head) * p.slot_splits + split;
-    const uint active = Rows == RICHENGINE_TARGET_VERIFY_ROWS ? Rows : p.active_rows;
-    const uint *masks = Rows == RICHENGINE_TARGET_VERIFY_ROWS ? nullptr : row_masks + ulong(lane) * p.row_capacity;
+    const uint3 at{group % KVHeads, group / KVHeads % most_splits, group / (KVHeads * most_splits)};
+    const RichVerifyTile tile = richengine_verify_attention_tile_at<KVHeads, Q, D>(queries, tables[0], tables[1], tables[2], tables[3], params, at);
+    if (!tile.active) return;
+    const uint *masks = chain ? nullptr : row_masks + ulong(at.z) * params[at.z].row_capacity;
     richengine_paged_attention_tile<KVHeads, Q, Rows, Element, D>(
-        queries + (ulong(lane) * KVHeads + kv_head) * group_stride, tables[lane], p.kv, kv_head, p.committed_tokens, active,
-        p.split_count, split, partials, statistics, slot, masks, p.score_scale, shared.scores, shared.probabilities,
+        tile.queries, tile.page_table, params[at.z].kv, tile.kv_head, tile.committed_tokens, chain ? Rows : tile.active_rows, tile.splits,
+        tile.split, partials, statistics, tile.slot, masks, params[at.z].score_scale, shared.scores, shared.probabilities,
         shared.row_max, shared.row_sum, shared.previous_scale, &shared.rescale, thread);
   });
   dispatch(lanes * M * KVHeads, [&](uint group, uint thread, uint, uint, Group &shared) {
-    const uint kv_head = group % KVHeads, fused_row = group / KVHeads % M, lane = group / (KVHeads * M);
-    const RichVerifyAttentionParams &p = params[lane];
-    if (!richengine_verify_attention_contract_valid(p)) return;
-    const uint active = Rows == RICHENGINE_TARGET_VERIFY_ROWS ? Rows : p.active_rows;
-    richengine_attention_reduce_row<Q, Rows, D>(partials, statistics, output + (ulong(lane) * KVHeads + kv_head) * group_stride,
-                                                p.committed_tokens, active, p.split_count,
-                                                (ulong(lane) * KVHeads + kv_head) * p.slot_splits, fused_row, thread,
-                                                shared.weights, shared.group_values);
+    const uint3 at{group % KVHeads, group / KVHeads % M, group / (KVHeads * M)};
+    if constexpr (chain) {
+      if (hidden) richengine_verify_attention_reduce_gate_phase<KVHeads, Q>(partials, statistics, output, packed_qkv, hidden, params, at, thread, shared.weights, shared.group_values);
+      else richengine_verify_attention_reduce_phase<KVHeads, Q, D>(partials, statistics, output, params, at, thread, shared.weights, shared.group_values);
+    } else {
+      richengine_verify_tree_attention_reduce_phase<KVHeads, Q, D>(partials, statistics, output, params, at, thread, shared.weights, shared.group_values);
+    }
   });
 }
+
 // A prefill chunk as the reference dispatches it (prefill/paged_attention.metal): its own split and reduce phases
 // place the tiles; a threadgroup per (KV head, tile, split), then one per (KV head, fused row, tile). One row is the
 // plain decode step.
@@ -195,14 +196,18 @@ int ref_metal_attention_prefill(uint32_t format, void *queries, const uint64_t *
 // output are [lane][4][32][group][256] bf16; partials [(lane*4 + head)*slot_splits + split][rows*group][256] fp32 and
 // statistics [..][rows*group]{max, sum}, as the kernels lay them out. rows = 8 runs the chain entries, 16 the tree
 // entries (row_masks [lane][row_capacity]).
+// packed_qkv and hidden (both or neither; chain entries of six heads only) bind the gate buffers: the merge is then the
+// reduce/gate phase, which also writes hidden [lane][8][24][256] bf16 from the gate values of packed_qkv [lane][8][stride].
 int ref_metal_attention_verify(uint32_t format, uint32_t rows, uint32_t group, void *queries, const uint64_t *const *tables, const void *params,
-                               uint32_t lanes, const uint32_t *row_masks, float *partials, float *statistics, void *output) {
+                               uint32_t lanes, const uint32_t *row_masks, float *partials, float *statistics, void *output,
+                               const void *packed_qkv, void *hidden) {
   try {
     auto *q = static_cast<bfloat *>(queries), *o = static_cast<bfloat *>(output);
     const auto *t = reinterpret_cast<const RichKvPage *const *>(tables);
     const auto *p = static_cast<const RichVerifyAttentionParams *>(params);
     const auto run = [&](auto element, auto row_count, auto heads) {
-      verify_attention<typename decltype(element)::type, decltype(row_count)::value, decltype(heads)::value>(q, t, p, lanes, row_masks, partials, statistics, o);
+      verify_attention<typename decltype(element)::type, decltype(row_count)::value, decltype(heads)::value>(
+          q, t, p, lanes, row_masks, partials, statistics, o, static_cast<const bfloat *>(packed_qkv), static_cast<bfloat *>(hidden));
     };
     const auto with_shape = [&](auto element) {
       if (rows == 8 && group == 6) run(element, std::integral_constant<uint, 8>{}, std::integral_constant<uint, 6>{});

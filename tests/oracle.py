@@ -120,7 +120,7 @@ def reference():
             r.ref_metal_tree_compact.restype, r.ref_metal_tree_compact.argtypes = C.c_int, [u32, vp, vp, vp, vp, u32]
             if hasattr(r, "ref_metal_attention_verify"):
                 r.ref_metal_attention_verify.restype = C.c_int
-                r.ref_metal_attention_verify.argtypes = [u32, u32, u32, vp, vp, vp, u32, vp, vp, vp, vp]
+                r.ref_metal_attention_verify.argtypes = [u32, u32, u32, vp, vp, vp, u32, vp, vp, vp, vp, vp, vp]
                 r.ref_metal_attention_prefill.restype = C.c_int
                 r.ref_metal_attention_prefill.argtypes = [u32, vp, vp, vp, vp, vp, vp]
         _reference = r

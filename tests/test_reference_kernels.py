@@ -122,17 +122,19 @@ def test_tree_compaction_equals_the_reference_kernel(fmt):
 from kvcase import bf16_to_f32, fill_history_with_store, make_queries   # noqa: E402
 
 
-def reference_attention(fmt, rows, scenario, queries, params, masks, group=6):
+def reference_attention(fmt, rows, scenario, queries, params, masks, group=6, packed=None):
     lanes = scenario.lanes
     slots = max(p.slot_splits for p in params)
     partials = np.zeros((lanes * 4 * slots, rows * group, 256), np.float32)
     statistics = np.zeros((lanes * 4 * slots, rows * group, 2), np.float32)
     out = np.zeros((lanes, 4, 32, group, 256), np.uint16)
     q = queries.copy()
+    hidden = None if packed is None else np.zeros((lanes, 8, 4 * group, 256), np.uint16)
     assert reference.ref_metal_attention_verify(fmt, rows, group, q.ctypes.data, four_tables(scenario), params, lanes,
                                                 None if masks is None else masks.ctypes.data, partials.ctypes.data,
-                                                statistics.ctypes.data, out.ctypes.data) == 0
-    return out
+                                                statistics.ctypes.data, out.ctypes.data,
+                                                None if packed is None else packed.ctypes.data, None if hidden is None else hidden.ctypes.data) == 0
+    return out if packed is None else (out, hidden)
 
 
 def checker_attention(fmt, scenario, queries, params, masks, group=6):
@@ -260,3 +262,28 @@ def test_prefill_and_decode_attention_agree_with_the_reference_phases(fmt, rows,
             assert (np.abs(got - mine) <= bound).all(), (tile, head, float(np.abs(got - mine).max()))
             assert not got[active * 6:].any() and not mine[active * 6:].any()   # rows past the chunk are zeros in both
             assert np.abs(mine[: active * 6]).max() > 0.05
+
+
+def test_the_reduce_gate_checker_equals_the_reference_phase():
+    """The merge with the gate buffers bound (decode/paged_attention.metal:273-311, run on host threads): the merged
+    rows it writes equal the plain merge's, and the gated hidden rows equal oracle/reduce_gate.py applied to them, bit
+    for bit (both take the logistic function as 1 / (1 + exp2(-log2(e) x)) in fp32)."""
+    import importlib.util
+    from pathlib import Path
+    spec = importlib.util.spec_from_file_location("rk_reduce_gate_checker", Path(__file__).resolve().parent.parent / "oracle" / "reduce_gate.py")
+    checker = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(checker)
+    layout = Layout(1, 4, 256, INT4)
+    s = Scenario(layout, [150, 5, 40], extra_tokens=8)
+    fill_history_with_store(s, 0)
+    store_rows(INT4, s, 8, 41)
+    q = make_queries(np.random.default_rng(42), s.lanes, layout)
+    params = (lib.VerifyParams * 3)(*[lib.VerifyParams(c, len(p), s.host.layer(0), 2, 2, 8, 8, 0.0) for c, p in zip(s.contexts, s.pages)])
+    stride = 2 * 24 * 256 + 2 * 4 * 256
+    packed = ((np.random.default_rng(43).standard_normal((3, 8, stride)).astype(np.float32) * 3).view(np.uint32) >> 16).astype(np.uint16)
+    plain = reference_attention(INT4, 8, s, q, params, None)
+    merged, hidden = reference_attention(INT4, 8, s, q, params, None, packed=packed)
+    assert np.array_equal(merged, plain)
+    rows = merged[:, :, :8].transpose(0, 2, 1, 3, 4).reshape(3, 8, 24, 256)      # [lane][row][kv head x group][dim]
+    want = checker.reduce_gate(rows, packed)
+    assert np.array_equal(hidden, want) and hidden.any()
