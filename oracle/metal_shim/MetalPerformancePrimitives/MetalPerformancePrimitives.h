@@ -1,6 +1,7 @@
 // Stands in for Metal Performance Primitives' tensor operations when the reference's attention tile
 // (runtime/metal/kernels/common/paged_attention_tile.h) is compiled as C++ for the test-only checker: tensor views over
-// plain memory (bf16, int8, fp32, and 4-bit two's-complement pairs with the even element in the low nibble), a
+// plain memory (bf16, fp16, int8, fp32, e4m3 bytes, and 4-bit two's-complement pairs with the even element in the low
+// nibble), a
 // matmul2d whose destination is a cooperative tensor spread evenly over the 256 threads of the threadgroup, products
 // widened to fp32 and summed in index order. Only what that header uses exists. TEST INFRASTRUCTURE ONLY.
 #pragma once
@@ -19,7 +20,9 @@ namespace rk_detail {
 inline float widen(float v) { return v; }
 inline float widen(bfloat v) { return float(v); }
 inline float widen(int8_t v) { return float(v); }
+inline float widen(half v) { return float(v); }
 inline void narrow(float &to, float v) { to = v; }
+inline void narrow(half &to, float v) { to = half(v); }
 inline void narrow(bfloat &to, float v) { to = bfloat(v); }
 } // namespace rk_detail
 
@@ -54,6 +57,19 @@ template <typename Extents, typename Tag> struct tensor<int4b_format, Extents, T
     const uint nibble = (data[at >> 1] >> ((at & 1) * 4)) & 0xFu;
     return float(int(nibble ^ 8u) - 8);
   }
+};
+// e4m3 operands: one byte per element, decoded by the reference's own conversion.
+template <typename Extents, typename Tag> struct tensor<metal_fp8_e4m3_format, Extents, Tag> {
+  const uchar *data;
+  int e0, e1, s0, s1;
+  tensor(const uchar *pointer, Extents extents, array<int, 2> strides) : data(pointer), e0(extents.e0), e1(extents.e1), s0(strides[0]), s1(strides[1]) {}
+  template <int A, int B> tensor slice(int i0, int i1) const {
+    tensor view = *this;
+    view.data = data + long(i0) * s0 + long(i1) * s1;
+    view.e0 = A; view.e1 = B;
+    return view;
+  }
+  float load(int i0, int i1) const { return ref_e4m3_to_f32(data[long(i0) * s0 + long(i1) * s1]); }
 };
 template <typename Element, typename Extents> tensor(Element *, Extents, array<int, 2>) -> tensor<Element, Extents, tensor_inline>;
 } // namespace metal

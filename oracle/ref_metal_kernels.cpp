@@ -16,8 +16,11 @@
 #include <vector>
 
 #include "metal/kernels/common/paged_attention_tile.h"
+#include "metal/kernels/decode/fp8_attention.metal"
+#include "metal/kernels/decode/fp8_attention_store.metal"
 #include "metal/kernels/decode/paged_attention.metal"
 #include "metal/kernels/decode/paged_attention_store.metal"
+#include "metal/kernels/prefill/fp8_attention_store.metal"
 #include "metal/kernels/prefill/paged_attention.metal"
 #include "metal/kernels/prefill/paged_attention_store.metal"
 
@@ -38,6 +41,8 @@ struct Group {
   float row_max[kRows], row_sum[kRows], previous_scale[kRows];
   std::atomic<uint> rescale{0};
   float weights[RICHENGINE_VERIFY_ATTENTION_MAXIMUM_SPLITS], group_values[8];
+  alignas(16) half half_probabilities[kRows * 32];   // the fp8 entries' fp16 probabilities and staged queries
+  alignas(16) half staged_queries[kRows / 2 * 256];
   Group() { for (uint i = 0; i < kThreads / kSimd; ++i) simd.push_back(std::make_unique<std::barrier<>>(kSimd)); }
 };
 thread_local Group *group_of_thread = nullptr;
@@ -116,6 +121,38 @@ template <typename Element>
 void chunk_store(const bfloat *keys, const bfloat *values, const RichKvPage *table, const RichChunkedPrefillParams &params) {
   dispatch(2 * params.chunk_tokens * 4, [&](uint group, uint thread, uint lane, uint simd, Group &shared) {
     richengine_store_chunk_phase<4, Element>(keys, values, table, params, shared.maxima, group, thread, lane, simd);
+  });
+}
+void verify_store_fp8(const bfloat *keys, const bfloat *values, const RichKvPage *const *tables, const RichChunkedPrefillParams *params, uint lanes) {
+  dispatch(lanes * 2 * RICHENGINE_TARGET_VERIFY_ROWS * 4, [&](uint group, uint thread, uint lane, uint simd, Group &shared) {
+    richengine_store_fp8_verify_phase<4>(keys, values, tables[0], tables[1], tables[2], tables[3], params, shared.maxima, group, thread, lane, simd);
+  });
+}
+void chunk_store_fp8(const bfloat *keys, const bfloat *values, const RichKvPage *table, const RichChunkedPrefillParams &params) {
+  dispatch(2 * params.chunk_tokens * 4, [&](uint group, uint thread, uint lane, uint simd, Group &shared) {
+    richengine_store_fp8_chunk_phase<4>(keys, values, table, params, shared.maxima, group, thread, lane, simd);
+  });
+}
+// The fp8 chain verify entry (decode/fp8_attention.metal:8-50, a macro body restated here: placement as the other
+// entries'), then the shared reduce phase.
+void verify_attention_fp8(bfloat *queries, const RichKvPage *const *tables, const RichVerifyAttentionParams *params, uint lanes,
+                          float *partials, float *statistics, bfloat *output) {
+  constexpr uint KVHeads = 4, Q = 6, D = 256, Rows = RICHENGINE_TARGET_VERIFY_ROWS, M = Rows * Q;
+  constexpr ulong group_stride = ulong(RICHENGINE_VERIFY_CHUNK_STRIDE) * Q * D;
+  uint most_splits = 0;
+  for (uint lane = 0; lane < lanes; ++lane) most_splits = max(most_splits, params[lane].split_count);
+  dispatch(lanes * most_splits * KVHeads, [&](uint group, uint thread, uint, uint, Group &shared) {
+    const uint kv_head = group % KVHeads, split = group / KVHeads % most_splits, lane = group / (KVHeads * most_splits);
+    const RichVerifyAttentionParams &p = params[lane];
+    if (!richengine_verify_attention_contract_valid(p) || split >= p.split_count) return;
+    richengine_paged_attention_tile_fp8<KVHeads, Q, Rows, D>(
+        queries + (ulong(lane) * KVHeads + kv_head) * group_stride, tables[lane], p.kv, kv_head, p.committed_tokens, Rows, p.split_count, split,
+        partials, statistics, (ulong(lane) * KVHeads + kv_head) * p.slot_splits + split, shared.scores, shared.half_probabilities,
+        shared.row_max, shared.row_sum, shared.previous_scale, &shared.rescale, shared.staged_queries, thread, p.score_scale);
+  });
+  dispatch(lanes * M * KVHeads, [&](uint group, uint thread, uint, uint, Group &shared) {
+    const uint3 at{group % KVHeads, group / KVHeads % M, group / (KVHeads * M)};
+    richengine_verify_attention_reduce_phase<KVHeads, Q, D>(partials, statistics, output, params, at, thread, shared.weights, shared.group_values);
   });
 }
 template <typename Element>
@@ -216,6 +253,7 @@ int ref_metal_attention_verify(uint32_t format, uint32_t rows, uint32_t group, v
       else if (rows == 16 && group == 4) run(element, std::integral_constant<uint, 16>{}, std::integral_constant<uint, 4>{});
       else throw 0;
     };
+    if (format == 4 && rows == 8 && group == 6 && !hidden) { verify_attention_fp8(q, t, p, lanes, partials, statistics, o); return 0; }
     if (format == 1) with_shape(std::type_identity<int8_t>{});
     else if (format == 2) with_shape(std::type_identity<bfloat>{});
     else if (format == 3) with_shape(std::type_identity<RichKvPacked4>{});
@@ -223,14 +261,15 @@ int ref_metal_attention_verify(uint32_t format, uint32_t rows, uint32_t group, v
     return 0;
   } catch (...) { return -1; }
 }
-// format: 1 int8, 2 bf16, 3 int4 (kv::Format). Four KV heads, head dimension 256. tables: four page-table pointers
+// format: 1 int8, 2 bf16, 3 int4, 4 fp8 e4m3 (kv::Format). Four KV heads, head dimension 256. tables: four page-table pointers
 // (unused lanes may repeat the first). params: `lanes` RichChunkedPrefillParams.
 int ref_metal_store_verify(uint32_t format, const void *keys, const void *values, const uint64_t *const *tables, const void *params, uint32_t lanes) {
   try {
     const auto *k = static_cast<const bfloat *>(keys), *v = static_cast<const bfloat *>(values);
     const auto *t = reinterpret_cast<const RichKvPage *const *>(tables);
     const auto *p = static_cast<const RichChunkedPrefillParams *>(params);
-    if (format == 1) verify_store<int8_t>(k, v, t, p, lanes);
+    if (format == 4) verify_store_fp8(k, v, t, p, lanes);
+    else if (format == 1) verify_store<int8_t>(k, v, t, p, lanes);
     else if (format == 2) verify_store<bfloat>(k, v, t, p, lanes);
     else if (format == 3) verify_store<RichKvPacked4>(k, v, t, p, lanes);
     else return -1;
@@ -242,7 +281,8 @@ int ref_metal_store_chunk(uint32_t format, const void *keys, const void *values,
     const auto *k = static_cast<const bfloat *>(keys), *v = static_cast<const bfloat *>(values);
     const auto *t = reinterpret_cast<const RichKvPage *>(table);
     const auto &p = *static_cast<const RichChunkedPrefillParams *>(params);
-    if (format == 1) chunk_store<int8_t>(k, v, t, p);
+    if (format == 4) chunk_store_fp8(k, v, t, p);
+    else if (format == 1) chunk_store<int8_t>(k, v, t, p);
     else if (format == 2) chunk_store<bfloat>(k, v, t, p);
     else if (format == 3) chunk_store<RichKvPacked4>(k, v, t, p);
     else return -1;

@@ -3,8 +3,7 @@ paged_store_row.h, paged_attention_tile.h, decode/paged_attention_store.metal an
 compiled as C++ in place (oracle/ref_metal_kernels.cpp over oracle/metal_shim) and run on host threads, one per Metal
 thread. Stores and tree compaction: the row decode, the page addressing, the maximum reduction, the quantiser
 expressions, the nibble packing and the copy order are the reference's own text, and every byte of every extent must
-agree, for int8, int4 and bf16 (the fp8 store needs the hardware's fp8 pack; its encoder is pinned by the reference's
-C++ fp8 reference instead). Attention: the reference's tile (admission rule, scale folds, online softmax with bf16
+agree, for int8, int4, bf16 and fp8 (the hardware's fp8 pack is the reference's own C++ e4m3 conversion). Attention: the reference's tile (admission rule, scale folds, online softmax with bf16
 probabilities, conditional rescale, partials and statistics per split) and its fixed-order merge, with the tensor
 operations stood in for by plain fp32 sums, against the checker's fp64 attention, chain and tree."""
 import ctypes as C
@@ -287,3 +286,46 @@ def test_the_reduce_gate_checker_equals_the_reference_phase():
     rows = merged[:, :, :8].transpose(0, 2, 1, 3, 4).reshape(3, 8, 24, 256)      # [lane][row][kv head x group][dim]
     want = checker.reduce_gate(rows, packed)
     assert np.array_equal(hidden, want) and hidden.any()
+
+
+# ---- fp8 e4m3: the reference's fp8 store rows and fp8 tile, with its own C++ e4m3 conversions as the hardware's pack ----
+from richengine_b200.abi import FP8E4M3   # noqa: E402
+
+
+def test_fp8_stores_equal_the_reference_kernels():
+    layout = Layout(2, 4, 256, FP8E4M3)
+    mine, theirs = pair(layout, [77, 5, 0, 31], 16)
+    k, v = make_staging(np.random.default_rng(3), 4, layout)
+    edge_rows(k, v)
+    for layer in range(2):
+        for scenario, store in ((mine, None), (theirs, reference)):
+            chunk = (lib.ChunkParams * 4)(*[lib.ChunkParams(c, 8, 32, len(p), scenario.host.layer(layer)) for c, p in zip(scenario.contexts, scenario.pages)])
+            if store is None:
+                assert om.oracle().rko_store_verify(FP8E4M3, 4, 256, 4, k.ctypes.data, v.ctypes.data, scenario.host_table_pointers(), chunk) == 0
+            else:
+                assert store.ref_metal_store_verify(FP8E4M3, k.ctypes.data, v.ctypes.data, four_tables(scenario), chunk, 4) == 0
+    assert_same_bytes(mine, theirs, "fp8 verify store")
+    mine, theirs = pair(Layout(1, 4, 256, FP8E4M3), [37], 100)
+    k, v = make_staging(np.random.default_rng(4), 1, layout, stride=128)
+    edge_rows(k, v)
+    for scenario, store in ((mine, None), (theirs, reference)):
+        params = lib.ChunkParams(37, 100, 128, len(scenario.pages[0]), scenario.host.layer(0))
+        if store is None:
+            assert om.oracle().rko_store_chunk(FP8E4M3, 4, 256, k.ctypes.data, v.ctypes.data, scenario.host_tables[0].ctypes.data, C.byref(params)) == 0
+        else:
+            assert store.ref_metal_store_chunk(FP8E4M3, k.ctypes.data, v.ctypes.data, scenario.host_tables[0].ctypes.data, C.byref(params)) == 0
+    assert_same_bytes(mine, theirs, "fp8 chunk store")
+
+
+@pytest.mark.parametrize("splits", [1, 3])
+def test_fp8_chain_verify_attention_agrees_with_the_reference_fp8_tile(splits):
+    """fp16-staged queries, fp16 probabilities, two passes of half the fused rows (paged_attention_fp8_tile.h:134-265)."""
+    layout = Layout(1, 4, 256, FP8E4M3)
+    s = Scenario(layout, [150, 5, 0, 67], extra_tokens=8)
+    fill_history_with_store(s, 0)
+    store_rows(FP8E4M3, s, 8, 21)
+    q = make_queries(np.random.default_rng(6), s.lanes, layout)
+    params = (lib.VerifyParams * 4)(*[lib.VerifyParams(c, len(p), s.host.layer(0), splits, 4, 8, 8, 0.0) for c, p in zip(s.contexts, s.pages)])
+    theirs = reference_attention(FP8E4M3, 8, s, q, params, None)
+    mine = checker_attention(FP8E4M3, s, q, params, None)
+    assert_attention_close(theirs, mine, [8, 8, 8, 8], "fp8 chain verify")
