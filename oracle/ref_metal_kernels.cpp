@@ -15,6 +15,7 @@
 #include <thread>
 #include <vector>
 
+#include "metal/kernels/common/attention_qkv_prepare.h"
 #include "metal/kernels/common/paged_attention_tile.h"
 #include "metal/kernels/decode/fp8_attention.metal"
 #include "metal/kernels/decode/fp8_attention_store.metal"
@@ -79,15 +80,18 @@ float simd_max(float value) {
   g.simd[base / kSimd]->arrive_and_wait();
   return result;
 }
+// Metal leaves the order of a SIMD-group sum to the hardware; this one is the xor butterfly 16, 8, 4, 2, 1 (every lane
+// ends with the same value), the order the checker fixes too.
 float simd_sum(float value) {
   Group &g = *group_of_thread;
-  const uint base = index_of_thread / kSimd * kSimd;
-  g.floats[index_of_thread] = value;
-  g.simd[base / kSimd]->arrive_and_wait();
-  float result = 0.0f;
-  for (uint lane = 0; lane < kSimd; ++lane) result += g.floats[base + lane];
-  g.simd[base / kSimd]->arrive_and_wait();
-  return result;
+  const uint base = index_of_thread / kSimd * kSimd, lane = index_of_thread - base;
+  for (uint step = kSimd / 2; step != 0; step >>= 1) {
+    g.floats[index_of_thread] = value;
+    g.simd[base / kSimd]->arrive_and_wait();
+    value += g.floats[base + (lane ^ step)];
+    g.simd[base / kSimd]->arrive_and_wait();
+  }
+  return value;
 }
 float simd_shuffle_xor(float value, ushort mask) {
   Group &g = *group_of_thread;
@@ -153,6 +157,26 @@ void verify_attention_fp8(bfloat *queries, const RichKvPage *const *tables, cons
   dispatch(lanes * M * KVHeads, [&](uint group, uint thread, uint, uint, Group &shared) {
     const uint3 at{group % KVHeads, group / KVHeads % M, group / (KVHeads * M)};
     richengine_verify_attention_reduce_phase<KVHeads, Q, D>(partials, statistics, output, params, at, thread, shared.weights, shared.group_values);
+  });
+}
+// The step before the path (decode/attention_qkv.metal:6-32, whose offsets per lane are restated here, over the
+// reference's full_qkv_storage_phase): per (lane, row) the packed projection row becomes the stagings the store and
+// the attention read. 24 query heads with their gates, 4 KV heads, fp32 or bf16 norm weights.
+template <typename Weight>
+void qkv_prepare(const bfloat *qkv, const Weight *q_norm, const Weight *k_norm, const float *rope_cos, const float *rope_sin,
+                 bfloat *queries, bfloat *keys, bfloat *values, uint lanes, uint rows) {
+  constexpr uint QHeads = 24, KHeads = 4, HeadDim = 256, RotaryPairs = 32, Stride = RICHENGINE_VERIFY_CHUNK_STRIDE;
+  constexpr uint PackedStride = QHeads * 2 * HeadDim + 2 * KHeads * HeadDim;
+  const uint tasks = rows * (QHeads + KHeads);
+  auto normalized = std::make_unique<bfloat[]>(256);
+  dispatch(lanes * tasks, [&](uint group, uint thread, uint lane, uint simd, Group &shared) {
+    const uint batch = group / tasks, task = group % tasks;
+    const ulong kv_lane_stride = ulong(KHeads) * Stride * HeadDim;
+    FullPrefillParams lane_params{rows, Stride};
+    full_qkv_storage_phase<QHeads, KHeads>(qkv + ulong(batch) * rows * PackedStride, q_norm, k_norm, rope_cos + ulong(batch) * rows * RotaryPairs,
+                                           rope_sin + ulong(batch) * rows * RotaryPairs, queries + ulong(batch) * QHeads * Stride * HeadDim,
+                                           keys + ulong(batch) * kv_lane_stride, values + ulong(batch) * kv_lane_stride, lane_params,
+                                           shared.group_values, normalized.get(), task, thread, lane, simd);
   });
 }
 template <typename Element>
@@ -233,6 +257,16 @@ int ref_metal_attention_prefill(uint32_t format, void *queries, const uint64_t *
 // output are [lane][4][32][group][256] bf16; partials [(lane*4 + head)*slot_splits + split][rows*group][256] fp32 and
 // statistics [..][rows*group]{max, sum}, as the kernels lay them out. rows = 8 runs the chain entries, 16 the tree
 // entries (row_masks [lane][row_capacity]).
+int ref_metal_qkv_prepare(const void *qkv, const void *q_norm, const void *k_norm, int norm_f32, const float *rope_cos, const float *rope_sin,
+                          void *queries, void *keys, void *values, uint32_t lanes, uint32_t rows) {
+  try {
+    const auto *packed = static_cast<const bfloat *>(qkv);
+    auto *q = static_cast<bfloat *>(queries), *k = static_cast<bfloat *>(keys), *v = static_cast<bfloat *>(values);
+    if (norm_f32) qkv_prepare(packed, static_cast<const float *>(q_norm), static_cast<const float *>(k_norm), rope_cos, rope_sin, q, k, v, lanes, rows);
+    else qkv_prepare(packed, static_cast<const bfloat *>(q_norm), static_cast<const bfloat *>(k_norm), rope_cos, rope_sin, q, k, v, lanes, rows);
+    return 0;
+  } catch (...) { return -1; }
+}
 // packed_qkv and hidden (both or neither; chain entries of six heads only) bind the gate buffers: the merge is then the
 // reduce/gate phase, which also writes hidden [lane][8][24][256] bf16 from the gate values of packed_qkv [lane][8][stride].
 int ref_metal_attention_verify(uint32_t format, uint32_t rows, uint32_t group, void *queries, const uint64_t *const *tables, const void *params,

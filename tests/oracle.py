@@ -121,6 +121,9 @@ def reference():
             if hasattr(r, "ref_metal_attention_verify"):
                 r.ref_metal_attention_verify.restype = C.c_int
                 r.ref_metal_attention_verify.argtypes = [u32, u32, u32, vp, vp, vp, u32, vp, vp, vp, vp, vp, vp]
+                if hasattr(r, "ref_metal_qkv_prepare"):
+                    r.ref_metal_qkv_prepare.restype = C.c_int
+                    r.ref_metal_qkv_prepare.argtypes = [vp, vp, vp, C.c_int, vp, vp, vp, vp, vp, u32, u32]
                 r.ref_metal_attention_prefill.restype = C.c_int
                 r.ref_metal_attention_prefill.argtypes = [u32, vp, vp, vp, vp, vp, vp]
         _reference = r

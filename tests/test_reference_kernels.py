@@ -329,3 +329,38 @@ def test_fp8_chain_verify_attention_agrees_with_the_reference_fp8_tile(splits):
     theirs = reference_attention(FP8E4M3, 8, s, q, params, None)
     mine = checker_attention(FP8E4M3, s, q, params, None)
     assert_attention_close(theirs, mine, [8, 8, 8, 8], "fp8 chain verify")
+
+
+@pytest.mark.parametrize("norm_f32", [1, 0])
+def test_qkv_prepare_checker_equals_the_reference_storage_phase(norm_f32):
+    """kernels/common/attention_qkv_prepare.h run on host threads (with rms_inverse.h): per-head RMS norm, norm weights,
+    bf16 rounding, rotary on the first 2 x 32 dims, gate skipped, the three stagings' layouts. The one freedom the
+    reference leaves, the order of its 32-wide sum, is the xor butterfly on both sides; everything else is its text.
+    Every bit of the three stagings must agree."""
+    from kvcase import f32_to_bf16
+    rng = np.random.default_rng(17)
+    lanes, rows, HQ, HKV, D = 3, 7, 24, 4, 256
+    packed_stride = HQ * 2 * D + 2 * HKV * D
+    packed = f32_to_bf16((rng.standard_normal((lanes, rows, packed_stride)) * 2).astype(np.float32))
+    packed[0, 0, : 2 * D] = 0                                       # a zero head: the norm of nothing
+    qn = (1 + 0.1 * rng.standard_normal(D)).astype(np.float32)
+    kn = (1 + 0.1 * rng.standard_normal(D)).astype(np.float32)
+    if not norm_f32:
+        qn, kn = f32_to_bf16(qn), f32_to_bf16(kn)
+    angle = rng.uniform(0, 6.28, (lanes, rows, 32)).astype(np.float32)
+    cosine, sine = np.cos(angle).astype(np.float32), np.sin(angle).astype(np.float32)
+    outputs = []
+    for side in ("mine", "theirs"):
+        q = np.zeros((lanes, HKV, 32, HQ // HKV, D), np.uint16)
+        k = np.zeros((lanes, HKV, 32, D), np.uint16)
+        v = np.zeros((lanes, HKV, D, 32), np.uint16)
+        if side == "mine":
+            assert om.oracle().rko_qkv_prepare(HKV, HQ, D, lanes, rows, packed.ctypes.data, qn.ctypes.data, kn.ctypes.data, norm_f32,
+                                               cosine.ctypes.data, sine.ctypes.data, 1e-6, q.ctypes.data, k.ctypes.data, v.ctypes.data) == 0
+        else:
+            assert reference.ref_metal_qkv_prepare(packed.ctypes.data, qn.ctypes.data, kn.ctypes.data, norm_f32, cosine.ctypes.data,
+                                                   sine.ctypes.data, q.ctypes.data, k.ctypes.data, v.ctypes.data, lanes, rows) == 0
+        outputs.append((q, k, v))
+    for name, a, b in zip(("queries", "keys", "values"), outputs[0], outputs[1]):
+        assert np.array_equal(a, b), f"{name}: {int((a != b).sum())} of {a.size} elements differ"
+        assert a.any()
