@@ -1,6 +1,6 @@
 // ref_metal_kernels.cpp — the reference's OWN store, tree-compaction and attention kernels (Metal source), compiled as C++ in place
-// from the reference checkout and run on host threads: one std::thread per Metal thread of a threadgroup, barriers as
-// std::barrier, 32 consecutive threads a SIMD group. Address spaces and kernel attributes mean nothing on the host;
+// from the reference checkout and run on the host: one fiber per Metal thread of a threadgroup, switched at barriers,
+// 32 consecutive threads a SIMD group, independent threadgroups on the host's cores. Address spaces and kernel attributes mean nothing on the host;
 // everything else — the row decode, the page addressing, the maximum reduction, the quantiser expressions, the nibble
 // packing, the copy order of the compaction, the attention tile's page loop with its admission rule, scale folds, online
 // softmax, bf16 probabilities and conditional rescale, and the fixed-order merge of the splits — is the reference's
@@ -10,7 +10,10 @@
 //
 // TEST INFRASTRUCTURE ONLY: built by oracle/Makefile into oracle/_ref/ where the reference checkout is present, used
 // by tests/ to pin the checker's stores and compaction against the reference kernels themselves.
-#include <barrier>
+#include <ucontext.h>
+
+#include <functional>
+#include <stdexcept>
 #include <memory>
 #include <thread>
 #include <vector>
@@ -29,9 +32,17 @@ thread_local uint rk_metal_thread_index = 0;
 
 namespace {
 constexpr uint kThreads = 256, kSimd = 32;
+// One threadgroup in flight: its 256 Metal threads are user-level fibers (ucontext) of ONE host thread, switched at
+// barriers only, so a barrier costs a context swap instead of a futex round over 256 host threads, and a threadgroup
+// runs deterministically. Independent threadgroups run on as many host threads as the machine has cores.
 struct Group {
-  std::barrier<> all{kThreads};
-  std::vector<std::unique_ptr<std::barrier<>>> simd;
+  enum class State : uint8_t { Ready, AtThreadgroupBarrier, AtSimdBarrier, Done };
+  ucontext_t scheduler;
+  ucontext_t contexts[kThreads];
+  State states[kThreads];
+  std::unique_ptr<char[]> stacks;
+  static constexpr size_t kStack = 128 * 1024;
+  std::function<void(uint)> body; // what fiber t runs
   float floats[kThreads];
   uint words[kThreads];
   float maxima[8]; // the kernels' `threadgroup float maxima[8]`
@@ -44,40 +55,104 @@ struct Group {
   float weights[RICHENGINE_VERIFY_ATTENTION_MAXIMUM_SPLITS], group_values[8];
   alignas(16) half half_probabilities[kRows * 32];   // the fp8 entries' fp16 probabilities and staged queries
   alignas(16) half staged_queries[kRows / 2 * 256];
-  Group() { for (uint i = 0; i < kThreads / kSimd; ++i) simd.push_back(std::make_unique<std::barrier<>>(kSimd)); }
+  bfloat normalized[256];                            // the QKV-prepare entries' normalised row
+  Group() : stacks(new char[kThreads * kStack]) {}
+  void run();
 };
 thread_local Group *group_of_thread = nullptr;
 #define index_of_thread rk_metal_thread_index
 
-// Runs `groups` threadgroups one after another on 256 persistent host threads.
-template <typename Body> void dispatch(uint groups, Body body) {
-  auto holder = std::make_unique<Group>();
-  Group &shared = *holder;
-  std::vector<std::thread> threads;
-  for (uint t = 0; t < kThreads; ++t)
-    threads.emplace_back([&, t] {
-      group_of_thread = &shared;
-      index_of_thread = t;
-      for (uint g = 0; g < groups; ++g) {
-        body(g, t, t % kSimd, t / kSimd, shared);
-        shared.all.arrive_and_wait(); // the next threadgroup starts with this one's memory settled
+void fiber_entry() {
+  Group &g = *group_of_thread;
+  const uint t = index_of_thread;
+  g.body(t);
+  g.states[t] = Group::State::Done;
+  swapcontext(&g.contexts[t], &g.scheduler);
+}
+
+// Runs the 256 fibers of one threadgroup to completion: every ready fiber runs until its next barrier; a SIMD-group
+// barrier opens when its 32 fibers (those not finished) wait at it, the threadgroup barrier when all of them do.
+void Group::run() {
+  for (uint t = 0; t < kThreads; ++t) {
+    getcontext(&contexts[t]);
+    contexts[t].uc_stack.ss_sp = stacks.get() + size_t(t) * kStack;
+    contexts[t].uc_stack.ss_size = kStack;
+    contexts[t].uc_link = &scheduler;
+    makecontext(&contexts[t], fiber_entry, 0);
+    states[t] = State::Ready;
+  }
+  for (;;) {
+    uint alive = 0;
+    for (uint t = 0; t < kThreads; ++t) {
+      if (states[t] == State::Ready) {
+        index_of_thread = t;
+        swapcontext(&scheduler, &contexts[t]);
       }
+      alive += states[t] != State::Done;
+    }
+    if (!alive) return;
+    bool released = false;
+    for (uint base = 0; base < kThreads; base += kSimd) {
+      uint waiting = 0, others = 0;
+      for (uint t = base; t < base + kSimd; ++t) {
+        waiting += states[t] == State::AtSimdBarrier;
+        others += states[t] == State::AtThreadgroupBarrier || states[t] == State::Ready;
+      }
+      if (waiting && !others) {
+        for (uint t = base; t < base + kSimd; ++t)
+          if (states[t] == State::AtSimdBarrier) states[t] = State::Ready;
+        released = true;
+      }
+    }
+    if (released) continue;
+    for (uint t = 0; t < kThreads; ++t)
+      if (states[t] == State::AtSimdBarrier) throw std::logic_error("a SIMD-group barrier some of its threads never reach");
+    for (uint t = 0; t < kThreads; ++t)
+      if (states[t] == State::AtThreadgroupBarrier) states[t] = State::Ready;
+  }
+}
+
+void wait_at(Group::State barrier) {
+  Group &g = *group_of_thread;
+  const uint t = index_of_thread;
+  g.states[t] = barrier;
+  swapcontext(&g.contexts[t], &g.scheduler);
+  index_of_thread = t;
+}
+
+// Runs `groups` threadgroups, independent of one another, over the host's cores.
+template <typename Body> void dispatch(uint groups, Body body) {
+  const uint workers = std::max(1u, std::min(groups, std::thread::hardware_concurrency()));
+  std::atomic<uint> next{0};
+  std::atomic<bool> failed{false};
+  std::vector<std::thread> threads;
+  for (uint w = 0; w < workers; ++w)
+    threads.emplace_back([&] {
+      auto shared = std::make_unique<Group>();
+      group_of_thread = shared.get();
+      try {
+        for (uint g = next.fetch_add(1); g < groups; g = next.fetch_add(1)) {
+          shared->body = [&, g](uint t) { body(g, t, t % kSimd, t / kSimd, *shared); };
+          shared->run();
+        }
+      } catch (...) { failed = true; }
     });
   for (std::thread &t : threads) t.join();
+  if (failed) throw std::runtime_error("a threadgroup failed");
 }
 } // namespace
 
 namespace metal {
-void threadgroup_barrier(mem_flags) { group_of_thread->all.arrive_and_wait(); }
-void simdgroup_barrier(mem_flags) { group_of_thread->simd[index_of_thread / kSimd]->arrive_and_wait(); }
+void threadgroup_barrier(mem_flags) { wait_at(Group::State::AtThreadgroupBarrier); }
+void simdgroup_barrier(mem_flags) { wait_at(Group::State::AtSimdBarrier); }
 float simd_max(float value) {
   Group &g = *group_of_thread;
   const uint base = index_of_thread / kSimd * kSimd;
   g.floats[index_of_thread] = value;
-  g.simd[base / kSimd]->arrive_and_wait();
+  wait_at(Group::State::AtSimdBarrier);
   float result = g.floats[base];
   for (uint lane = 1; lane < kSimd; ++lane) result = max(result, g.floats[base + lane]);
-  g.simd[base / kSimd]->arrive_and_wait();
+  wait_at(Group::State::AtSimdBarrier);
   return result;
 }
 // Metal leaves the order of a SIMD-group sum to the hardware; this one is the xor butterfly 16, 8, 4, 2, 1 (every lane
@@ -87,9 +162,9 @@ float simd_sum(float value) {
   const uint base = index_of_thread / kSimd * kSimd, lane = index_of_thread - base;
   for (uint step = kSimd / 2; step != 0; step >>= 1) {
     g.floats[index_of_thread] = value;
-    g.simd[base / kSimd]->arrive_and_wait();
+    wait_at(Group::State::AtSimdBarrier);
     value += g.floats[base + (lane ^ step)];
-    g.simd[base / kSimd]->arrive_and_wait();
+    wait_at(Group::State::AtSimdBarrier);
   }
   return value;
 }
@@ -97,18 +172,18 @@ float simd_shuffle_xor(float value, ushort mask) {
   Group &g = *group_of_thread;
   const uint base = index_of_thread / kSimd * kSimd;
   g.floats[index_of_thread] = value;
-  g.simd[base / kSimd]->arrive_and_wait();
+  wait_at(Group::State::AtSimdBarrier);
   const float result = g.floats[base + ((index_of_thread - base) ^ mask)];
-  g.simd[base / kSimd]->arrive_and_wait();
+  wait_at(Group::State::AtSimdBarrier);
   return result;
 }
 uint simd_shuffle_xor(uint value, ushort mask) {
   Group &g = *group_of_thread;
   const uint base = index_of_thread / kSimd * kSimd;
   g.words[index_of_thread] = value;
-  g.simd[base / kSimd]->arrive_and_wait();
+  wait_at(Group::State::AtSimdBarrier);
   const uint result = g.words[base + ((index_of_thread - base) ^ mask)];
-  g.simd[base / kSimd]->arrive_and_wait();
+  wait_at(Group::State::AtSimdBarrier);
   return result;
 }
 } // namespace metal
@@ -168,7 +243,6 @@ void qkv_prepare(const bfloat *qkv, const Weight *q_norm, const Weight *k_norm, 
   constexpr uint QHeads = 24, KHeads = 4, HeadDim = 256, RotaryPairs = 32, Stride = RICHENGINE_VERIFY_CHUNK_STRIDE;
   constexpr uint PackedStride = QHeads * 2 * HeadDim + 2 * KHeads * HeadDim;
   const uint tasks = rows * (QHeads + KHeads);
-  auto normalized = std::make_unique<bfloat[]>(256);
   dispatch(lanes * tasks, [&](uint group, uint thread, uint lane, uint simd, Group &shared) {
     const uint batch = group / tasks, task = group % tasks;
     const ulong kv_lane_stride = ulong(KHeads) * Stride * HeadDim;
@@ -176,7 +250,7 @@ void qkv_prepare(const bfloat *qkv, const Weight *q_norm, const Weight *k_norm, 
     full_qkv_storage_phase<QHeads, KHeads>(qkv + ulong(batch) * rows * PackedStride, q_norm, k_norm, rope_cos + ulong(batch) * rows * RotaryPairs,
                                            rope_sin + ulong(batch) * rows * RotaryPairs, queries + ulong(batch) * QHeads * Stride * HeadDim,
                                            keys + ulong(batch) * kv_lane_stride, values + ulong(batch) * kv_lane_stride, lane_params,
-                                           shared.group_values, normalized.get(), task, thread, lane, simd);
+                                           shared.group_values, shared.normalized, task, thread, lane, simd);
   });
 }
 template <typename Element>

@@ -1,6 +1,6 @@
 """CPU: the checker against the reference's OWN kernels. The Metal source of runtime/metal/kernels/common/
 paged_store_row.h, paged_attention_tile.h, decode/paged_attention_store.metal and prefill/paged_attention_store.metal is
-compiled as C++ in place (oracle/ref_metal_kernels.cpp over oracle/metal_shim) and run on host threads, one per Metal
+compiled as C++ in place (oracle/ref_metal_kernels.cpp over oracle/metal_shim) and run on the host, one fiber per Metal
 thread. Stores and tree compaction: the row decode, the page addressing, the maximum reduction, the quantiser
 expressions, the nibble packing and the copy order are the reference's own text, and every byte of every extent must
 agree, for int8, int4, bf16 and fp8 (the hardware's fp8 pack is the reference's own C++ e4m3 conversion). Attention: the reference's tile (admission rule, scale folds, online softmax with bf16
@@ -364,3 +364,18 @@ def test_qkv_prepare_checker_equals_the_reference_storage_phase(norm_f32):
     for name, a, b in zip(("queries", "keys", "values"), outputs[0], outputs[1]):
         assert np.array_equal(a, b), f"{name}: {int((a != b).sum())} of {a.size} elements differ"
         assert a.any()
+
+
+@pytest.mark.parametrize("fmt", [INT4, INT8])
+def test_long_contexts_and_the_plan_s_split_counts_agree_with_the_reference(fmt):
+    """Thousands of tokens over the split counts the reference's plan picks (32 at these lengths; a lane whose pages do
+    not fill them leaves splits unwritten, which the merge must skip)."""
+    layout = Layout(1, 4, 256, fmt)
+    s = Scenario(layout, [4100, 777, 33], extra_tokens=8)
+    fill_history_with_store(s, 0)
+    store_rows(fmt, s, 8, 51)
+    q = make_queries(np.random.default_rng(52), s.lanes, layout)
+    params = (lib.VerifyParams * 3)(*[lib.VerifyParams(c, len(p), s.host.layer(0), 32, 32, 8, 8, 0.0) for c, p in zip(s.contexts, s.pages)])
+    theirs = reference_attention(fmt, 8, s, q, params, None)
+    mine = checker_attention(fmt, s, q, params, None)
+    assert_attention_close(theirs, mine, [8, 8, 8], "long chain verify")
