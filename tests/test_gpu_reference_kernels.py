@@ -76,9 +76,9 @@ def test_cuda_verify_attention_against_the_reference_tile_and_merge(fmt, tensor_
     s.close()
 
 
-@pytest.mark.parametrize("fmt", [INT4, INT8, BF16])
-def test_cuda_streaming_decode_against_the_reference_prefill_phases_of_one_row(fmt):
-    contexts = [2100, 33, 1]
+@pytest.mark.parametrize("fmt,contexts", [(INT4, [2100, 33, 1]), (INT8, [2100, 33, 1]), (BF16, [2100, 33, 1]), (INT4, [32768, 8191])])
+def test_cuda_streaming_decode_against_the_reference_prefill_phases_of_one_row(fmt, contexts):
+    """The last case is the north-star context length: 32 768 tokens of int4 history through the reference's page loop."""
     s = Scenario(Layout(1, 4, 256, fmt), contexts, extra_tokens=0, device=True)
     fill_history_with_store(s, 0)
     s.upload()
