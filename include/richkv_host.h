@@ -47,9 +47,21 @@ int rk_cache_ensure_tokens(void *cache, uint64_t request, uint64_t tokens);
 /* Copies up to capacity page ids; returns the page count; revision and first_changed as Cache::pageTable. */
 int64_t rk_cache_page_table(const void *cache, uint64_t request, uint32_t *pages_out, uint32_t capacity,
                             uint64_t *revision, uint32_t *first_changed);
-int rk_cache_publish(void *cache, uint64_t request, const uint32_t *tokens, uint32_t token_count, uint32_t committed);
+/* One image in a prompt (ImageSpan, runtime/model/Model.hpp:130-146): the run of placeholder tokens it occupies, its
+ * patch grid and a 128-bit digest of its content. Every image has the same placeholder token ids, so the key of a block
+ * carries the identity of the images that overlap it (blockImageIdentity, runtime/engine/cache/KvCache.cpp:29-52).
+ * Spans are sorted and disjoint; null / 0 = text alone. The same spans go with every call that names the prompt. */
+typedef struct rk_image_span {
+  uint32_t offset, tokens, grid_height, grid_width;
+  uint64_t digest_lo, digest_hi;
+} rk_image_span;
+/* The identity a block at tokens [block_begin, block_begin + block_tokens) takes from the spans: out[2] = lo, hi (0, 0 for text). */
+void rk_block_image_identity(uint64_t block_begin, uint32_t block_tokens, const rk_image_span *images, uint32_t image_count, uint64_t *out);
+int rk_cache_publish(void *cache, uint64_t request, const uint32_t *tokens, uint32_t token_count, uint32_t committed,
+                     const rk_image_span *images, uint32_t image_count);
 /* Matched blocks into blocks_out (capacity entries); returns how many. */
-int64_t rk_cache_lookup(void *cache, const uint32_t *prompt, uint32_t prompt_tokens, uint64_t *blocks_out, uint32_t capacity);
+int64_t rk_cache_lookup(void *cache, const uint32_t *prompt, uint32_t prompt_tokens, uint64_t *blocks_out, uint32_t capacity,
+                        const rk_image_span *images, uint32_t image_count);
 int rk_cache_attach_prefix(void *cache, uint64_t request, const uint64_t *blocks, uint32_t count, uint32_t *resume_tokens);
 int rk_cache_restores_pending(const void *cache, uint64_t request);
 /* Cache::kvRestoreStatus (Cache.cpp:787-792): 0 nothing to wait for, 1 pending, 2 a read failed (the block matches
@@ -159,10 +171,11 @@ int rk_cache_reclaim_step(void *cache, int mode, int up_to_in_use, int keep_resu
 int rk_cache_evict_all(void *cache, uint64_t *out);
 int rk_cache_reclaim_one_state(void *cache, int checkpoints_only, uint64_t for_block);
 int64_t rk_cache_lookup_state(void *cache, const uint32_t *prompt, uint32_t prompt_tokens, uint64_t *blocks_out, uint32_t capacity,
-                              uint64_t *out, int record, const void *probe);
+                              uint64_t *out, int record, const void *probe, const rk_image_span *images, uint32_t image_count);
 int rk_cache_lookup_counters(void *cache, uint64_t *out);
-void *rk_cache_probe_create(void *cache, const uint32_t *prompt, uint32_t prompt_tokens);
-int rk_cache_probe_refresh(void *cache, void *probe, const uint32_t *prompt, uint32_t prompt_tokens);
+void *rk_cache_probe_create(void *cache, const uint32_t *prompt, uint32_t prompt_tokens, const rk_image_span *images, uint32_t image_count);
+int rk_cache_probe_refresh(void *cache, void *probe, const uint32_t *prompt, uint32_t prompt_tokens, const rk_image_span *images,
+                           uint32_t image_count);
 int rk_cache_probe_info(const void *probe, uint64_t *out);
 void rk_cache_probe_destroy(void *probe);
 

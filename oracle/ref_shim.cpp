@@ -353,8 +353,18 @@ int64_t ref_cache_page_table(void *facade, uint64_t request, uint32_t *pages, ui
     return int64_t(view.pages.size());
   } catch (...) { return -1; }
 }
-int ref_cache_publish(void *facade, uint64_t request, const uint32_t *tokens, uint32_t count, uint32_t committed) {
-  try { FACADE->cache.publishCommittedBlocks(request, {tokens, count}, committed, {}); return 0; } catch (...) { return -1; }
+// Image spans cross as the 32-byte records of include/richkv_host.h, which are ImageSpan's own fields in its order.
+static std::span<const ImageSpan> spans_of(const void *images, uint32_t count) {
+  static_assert(sizeof(ImageSpan) == 32);
+  return {static_cast<const ImageSpan *>(images), images ? count : 0u};
+}
+int ref_cache_publish(void *facade, uint64_t request, const uint32_t *tokens, uint32_t count, uint32_t committed, const void *images, uint32_t image_count) {
+  try { FACADE->cache.publishCommittedBlocks(request, {tokens, count}, committed, spans_of(images, image_count)); return 0; } catch (...) { return -1; }
+}
+// blockImageIdentity (runtime/engine/cache/KvCache.cpp:29-52): out[2] = lo, hi
+void ref_block_image_identity(uint64_t block_begin, uint32_t block_tokens, const void *images, uint32_t image_count, uint64_t *out) {
+  const engine::ImageIdentity identity = engine::blockImageIdentity(block_begin, block_tokens, spans_of(images, image_count));
+  out[0] = identity.lo; out[1] = identity.hi;
 }
 uint64_t ref_cache_block_at(void *facade, uint64_t request, uint32_t boundary) {
   try { return FACADE->cache.blockAt(request, boundary); } catch (...) { return 0; }
@@ -363,9 +373,9 @@ uint64_t ref_cache_block_at(void *facade, uint64_t request, uint32_t boundary) {
 // lease pins the state) and returns its handle in out[5]; attach_to != 0 gives that request the chain (restoreRequest)
 // and reports the admission in out[6] (0 granted, 1 denied, 2 pending).
 int ref_cache_lookup(void *facade, const uint32_t *prompt, uint32_t count, int record, int hold, uint64_t attach_to, uint64_t *out,
-                     const void *probe) {
+                     const void *probe, const void *images, uint32_t image_count) {
   try {
-    engine::CacheLookup found = FACADE->cache.lookup({prompt, count}, {}, static_cast<const engine::CacheProbe *>(probe));
+    engine::CacheLookup found = FACADE->cache.lookup({prompt, count}, spans_of(images, image_count), static_cast<const engine::CacheProbe *>(probe));
     out[0] = found.kvBoundary; out[1] = found.state ? found.state->kvBlock() : 0; out[2] = found.resumeBoundary();
     out[3] = found.junctionBoundary; out[4] = found.lostState; out[5] = 0; out[6] = 0;
     if (record) FACADE->cache.recordLookup(found);
@@ -375,11 +385,11 @@ int ref_cache_lookup(void *facade, const uint32_t *prompt, uint32_t count, int r
   } catch (...) { return -1; }
 }
 void ref_cache_release_lookup(void *facade, uint64_t handle) { FACADE->held.erase(handle); }
-void *ref_cache_probe_create(void *facade, const uint32_t *prompt, uint32_t count) {
-  try { return new engine::CacheProbe(FACADE->cache.probe({prompt, count}, {})); } catch (...) { return nullptr; }
+void *ref_cache_probe_create(void *facade, const uint32_t *prompt, uint32_t count, const void *images, uint32_t image_count) {
+  try { return new engine::CacheProbe(FACADE->cache.probe({prompt, count}, spans_of(images, image_count))); } catch (...) { return nullptr; }
 }
-int ref_cache_probe_refresh(void *facade, void *probe, const uint32_t *prompt, uint32_t count) {
-  try { FACADE->cache.refresh(*static_cast<engine::CacheProbe *>(probe), {prompt, count}, {}); return 0; } catch (...) { return -1; }
+int ref_cache_probe_refresh(void *facade, void *probe, const uint32_t *prompt, uint32_t count, const void *images, uint32_t image_count) {
+  try { FACADE->cache.refresh(*static_cast<engine::CacheProbe *>(probe), {prompt, count}, spans_of(images, image_count)); return 0; } catch (...) { return -1; }
 }
 uint32_t ref_cache_probe_cached_tokens(const void *probe) { return static_cast<const engine::CacheProbe *>(probe)->cachedTokens(); }
 void ref_cache_probe_destroy(void *probe) { delete static_cast<engine::CacheProbe *>(probe); }

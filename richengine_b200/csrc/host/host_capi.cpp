@@ -271,12 +271,24 @@ int64_t rk_cache_page_table(const void *cache, uint64_t request, uint32_t *pages
     return int64_t(view.pages.size());
   } catch (const std::exception &e) { rk::set_error(e.what()); return RK_ERR_INVALID; }
 }
-int rk_cache_publish(void *cache, uint64_t request, const uint32_t *tokens, uint32_t token_count, uint32_t committed) {
-  return guarded([&] { CACHE->publishCommittedBlocks(request, {tokens, token_count}, committed); return RK_OK; });
+// rk_image_span and engine::ImageSpan are the same 32 bytes.
+static std::span<const engine::ImageSpan> image_spans(const rk_image_span *images, uint32_t count) {
+  static_assert(sizeof(rk_image_span) == sizeof(engine::ImageSpan) && sizeof(rk_image_span) == 32);
+  return {reinterpret_cast<const engine::ImageSpan *>(images), images ? count : 0u};
 }
-int64_t rk_cache_lookup(void *cache, const uint32_t *prompt, uint32_t prompt_tokens, uint64_t *blocks_out, uint32_t capacity) {
+// blockImageIdentity: out[2] = lo, hi
+void rk_block_image_identity(uint64_t block_begin, uint32_t block_tokens, const rk_image_span *images, uint32_t image_count, uint64_t *out) {
+  const engine::ImageIdentity identity = engine::blockImageIdentity(block_begin, block_tokens, image_spans(images, image_count));
+  out[0] = identity.lo; out[1] = identity.hi;
+}
+int rk_cache_publish(void *cache, uint64_t request, const uint32_t *tokens, uint32_t token_count, uint32_t committed,
+                     const rk_image_span *images, uint32_t image_count) {
+  return guarded([&] { CACHE->publishCommittedBlocks(request, {tokens, token_count}, committed, image_spans(images, image_count)); return RK_OK; });
+}
+int64_t rk_cache_lookup(void *cache, const uint32_t *prompt, uint32_t prompt_tokens, uint64_t *blocks_out, uint32_t capacity,
+                        const rk_image_span *images, uint32_t image_count) {
   try {
-    const auto blocks = CACHE->lookup({prompt, prompt_tokens});
+    const auto blocks = CACHE->lookup({prompt, prompt_tokens}, nullptr, image_spans(images, image_count));
     for (size_t i = 0; i < blocks.size() && i < capacity; ++i) blocks_out[i] = blocks[i];
     return int64_t(blocks.size());
   } catch (const std::exception &e) { rk::set_error(e.what()); return RK_ERR_INVALID; }
@@ -529,9 +541,10 @@ int rk_cache_reclaim_one_state(void *cache, int checkpoints_only, uint64_t for_b
 // lookup as Cache::recordLookup does. `probe` (may be null) is a handle of rk_cache_probe_create: while it is current
 // its chain is reused instead of hashing the prompt again.
 int64_t rk_cache_lookup_state(void *cache, const uint32_t *prompt, uint32_t prompt_tokens, uint64_t *blocks_out, uint32_t capacity,
-                              uint64_t *out, int record, const void *probe) {
+                              uint64_t *out, int record, const void *probe, const rk_image_span *images, uint32_t image_count) {
   try {
-    const auto found = CACHE->lookupWithState({prompt, prompt_tokens}, static_cast<const engine::Cache::Probe *>(probe));
+    const auto found = CACHE->lookupWithState({prompt, prompt_tokens}, static_cast<const engine::Cache::Probe *>(probe),
+                                              image_spans(images, image_count));
     for (size_t i = 0; i < found.blocks.size() && i < capacity; ++i) blocks_out[i] = found.blocks[i];
     out[0] = found.kvBoundary; out[1] = found.stateBlock; out[2] = found.resumeBoundary; out[3] = found.junctionBoundary;
     out[4] = found.lostState;
@@ -550,12 +563,16 @@ int rk_cache_lookup_counters(void *cache, uint64_t *out) {
   });
 }
 // The scheduling probe (Cache::probe / Cache::refresh / CacheProbe): a handle the scheduler keeps per waiting request.
-void *rk_cache_probe_create(void *cache, const uint32_t *prompt, uint32_t prompt_tokens) {
-  try { return new engine::Cache::Probe(CACHE->probe({prompt, prompt_tokens})); }
+void *rk_cache_probe_create(void *cache, const uint32_t *prompt, uint32_t prompt_tokens, const rk_image_span *images, uint32_t image_count) {
+  try { return new engine::Cache::Probe(CACHE->probe({prompt, prompt_tokens}, image_spans(images, image_count))); }
   catch (const std::exception &e) { rk::set_error(e.what()); return nullptr; }
 }
-int rk_cache_probe_refresh(void *cache, void *probe, const uint32_t *prompt, uint32_t prompt_tokens) {
-  return guarded([&] { CACHE->refresh(*static_cast<engine::Cache::Probe *>(probe), {prompt, prompt_tokens}); return RK_OK; });
+int rk_cache_probe_refresh(void *cache, void *probe, const uint32_t *prompt, uint32_t prompt_tokens, const rk_image_span *images,
+                           uint32_t image_count) {
+  return guarded([&] {
+    CACHE->refresh(*static_cast<engine::Cache::Probe *>(probe), {prompt, prompt_tokens}, image_spans(images, image_count));
+    return RK_OK;
+  });
 }
 // out[2] = cached tokens (up to the deepest state on the matched chain), matched blocks
 int rk_cache_probe_info(const void *probe, uint64_t *out) {

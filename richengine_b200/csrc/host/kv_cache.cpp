@@ -12,12 +12,36 @@ namespace {
 uint64_t mix(uint64_t hash, uint64_t value) noexcept {
   return hash ^ (value + 0x9e3779b97f4a7c15ull + (hash << 6) + (hash >> 2));
 }
+// Sorted, disjoint spans: those that end at or before a block end before every later block too (spansFrom, Cache.cpp:19-22).
+std::span<const ImageSpan> spansFrom(std::span<const ImageSpan> images, uint64_t blockBegin) {
+  const auto ended = [&](const ImageSpan &span) { return span.end() <= blockBegin; };
+  return {std::partition_point(images.begin(), images.end(), ended), images.end()};
+}
+
 uint64_t blockHash(uint64_t parentHash, std::span<const uint32_t> tokens, ImageIdentity images) noexcept {
   uint64_t hash = mix(0x6a09e667f3bcc909ull, parentHash);
   for (uint32_t token : tokens) hash = mix(hash, token);
   return mix(mix(hash, images.lo), images.hi);
 }
 } // namespace
+
+ImageIdentity blockImageIdentity(uint64_t blockBegin, uint32_t blockTokens, std::span<const ImageSpan> spans) noexcept {
+  ImageIdentity identity;
+  const uint64_t blockEnd = blockBegin + blockTokens;
+  for (const ImageSpan &span : spans) {
+    if (span.offset >= blockEnd) break;
+    if (span.end() <= blockBegin) continue;
+    uint64_t lo = identity.lo ? identity.lo : 0x243f6a8885a308d3ull;
+    uint64_t hi = identity.hi ? identity.hi : 0x13198a2e03707344ull;
+    for (uint64_t value : {span.digestLo, span.digestHi, (uint64_t(span.gridHeight) << 32) | span.gridWidth,
+                           (uint64_t(span.offset) << 32) | span.tokens, blockBegin}) {
+      lo = mix(lo, value);
+      hi = mix(hi, ~value);
+    }
+    identity = {lo, hi};
+  }
+  return identity;
+}
 
 // ============================== PrefixIndex ====================================================
 PrefixIndex::~PrefixIndex() {
@@ -461,7 +485,8 @@ PageTableView Cache::pageTable(uint64_t id) const {
   return {active.pages, active.revision, active.firstChanged};
 }
 
-void Cache::publishCommittedBlocks(uint64_t id, std::span<const uint32_t> exactTokens, uint32_t committedTokens) {
+void Cache::publishCommittedBlocks(uint64_t id, std::span<const uint32_t> exactTokens, uint32_t committedTokens,
+                                   std::span<const ImageSpan> images) {
   Request &active = request(id);
   if (committedTokens > exactTokens.size()) throw std::invalid_argument("committed KV exceeds exact token history");
   const uint32_t fullBlocks = committedTokens / kv::kPageTokens;
@@ -472,7 +497,10 @@ void Cache::publishCommittedBlocks(uint64_t id, std::span<const uint32_t> exactT
     const uint32_t logical = uint32_t(active.blocks.size());
     const uint64_t parent = logical ? active.blocks.back() : 0;
     const uint32_t writerPage = active.pages[logical];
-    const PrefixIndex::Match placed = index_.insert(parent, exactTokens.subspan(size_t(logical) * kv::kPageTokens, kv::kPageTokens), writerPage);
+    const uint32_t begin = logical * kv::kPageTokens;
+    images = spansFrom(images, begin);
+    const PrefixIndex::Match placed = index_.insert(parent, exactTokens.subspan(begin, kv::kPageTokens), writerPage,
+                                                    blockImageIdentity(begin, kv::kPageTokens, images));
     const bool replace = placed.page != writerPage;
     if (replace) pool_.retainPage(placed.page, false);
     index_.retainActive(placed.id);
@@ -488,13 +516,15 @@ void Cache::publishCommittedBlocks(uint64_t id, std::span<const uint32_t> exactT
 
 // Extends a chain that matches the prompt's first pages by the pages that follow, at most (n-1)/32 in all; returns
 // the pages hashed (Cache::extendMatch, Cache.cpp:179-199).
-size_t Cache::extendMatch(std::vector<uint64_t> &blocks, std::span<const uint32_t> prompt) const {
+size_t Cache::extendMatch(std::vector<uint64_t> &blocks, std::span<const uint32_t> prompt, std::span<const ImageSpan> images) const {
   if (prompt.empty()) return 0;
   const size_t maximum = (prompt.size() - 1) / kv::kPageTokens; // one real token stays to recompute
   size_t hashed = 0;
   for (size_t i = blocks.size(); i < maximum; ++i) {
     ++hashed;
-    auto match = index_.find(blocks.empty() ? 0 : blocks.back(), prompt.subspan(i * kv::kPageTokens, kv::kPageTokens));
+    images = spansFrom(images, i * kv::kPageTokens);
+    auto match = index_.find(blocks.empty() ? 0 : blocks.back(), prompt.subspan(i * kv::kPageTokens, kv::kPageTokens),
+                             blockImageIdentity(i * kv::kPageTokens, kv::kPageTokens, images));
     if (!match) break;
     blocks.push_back(match->id);
   }
@@ -508,30 +538,30 @@ uint32_t Cache::stateTokens(std::span<const uint64_t> blocks) const {
   return 0;
 }
 
-Cache::Probe Cache::probe(std::span<const uint32_t> prompt) {
+Cache::Probe Cache::probe(std::span<const uint32_t> prompt, std::span<const ImageSpan> images) {
   Probe result;
   result.owner_ = this;
   result.generation_ = index_.generation();
-  lookups_.probeHashedBlocks += extendMatch(result.blocks_, prompt);
+  lookups_.probeHashedBlocks += extendMatch(result.blocks_, prompt, images);
   result.cachedTokens_ = stateTokens(result.blocks_);
   return result;
 }
 
-void Cache::refresh(Probe &probe, std::span<const uint32_t> prompt) {
+void Cache::refresh(Probe &probe, std::span<const uint32_t> prompt, std::span<const ImageSpan> images) {
   if (probe.owner_ != this) throw std::logic_error("a scheduling probe belongs to another cache");
   if (probe.generation_ != index_.generation()) {
     auto cut = std::find_if(probe.blocks_.begin(), probe.blocks_.end(), [&](uint64_t block) { return !index_.matchable(block); });
     probe.blocks_.erase(cut, probe.blocks_.end());
-    lookups_.probeHashedBlocks += extendMatch(probe.blocks_, prompt);
+    lookups_.probeHashedBlocks += extendMatch(probe.blocks_, prompt, images);
     probe.generation_ = index_.generation();
   }
   probe.cachedTokens_ = stateTokens(probe.blocks_); // states come and go without a change of the graph
 }
 
-std::vector<uint64_t> Cache::lookup(std::span<const uint32_t> prompt, const Probe *probe) {
+std::vector<uint64_t> Cache::lookup(std::span<const uint32_t> prompt, const Probe *probe, std::span<const ImageSpan> images) {
   std::vector<uint64_t> blocks;
   if (probe && probe->owner_ == this && probe->generation_ == index_.generation()) blocks = probe->blocks_;
-  else extendMatch(blocks, prompt);
+  else extendMatch(blocks, prompt, images);
   if (!blocks.empty()) {
     index_.touch(blocks.back());
     // A chain that ends in tier-only blocks keeps its resident boundary as warm as its tip: a restore adopts the
@@ -542,9 +572,9 @@ std::vector<uint64_t> Cache::lookup(std::span<const uint32_t> prompt, const Prob
   return blocks;
 }
 
-Cache::StateLookup Cache::lookupWithState(std::span<const uint32_t> prompt, const Probe *probe) {
+Cache::StateLookup Cache::lookupWithState(std::span<const uint32_t> prompt, const Probe *probe, std::span<const ImageSpan> images) {
   StateLookup result;
-  result.blocks = lookup(prompt, probe);
+  result.blocks = lookup(prompt, probe, images);
   const std::vector<uint64_t> &blocks = result.blocks;
   if (blocks.empty()) return result;
   result.kvBoundary = uint32_t(blocks.size() * kv::kPageTokens);

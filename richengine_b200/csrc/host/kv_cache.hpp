@@ -36,6 +36,18 @@ struct ImageIdentity final {
   uint64_t lo = 0, hi = 0;
   bool operator==(const ImageIdentity &) const = default;
 };
+// One image in a prompt (ImageSpan, runtime/model/Model.hpp:130-146): the run of placeholder tokens it occupies, the
+// patch grid of its resized pixels and a 128-bit digest of that content. Placeholder token ids are the same for every
+// image, so a block's key carries the identity of the images that overlap it. Spans are sorted and disjoint.
+struct ImageSpan final {
+  uint32_t offset = 0, tokens = 0, gridHeight = 0, gridWidth = 0;
+  uint64_t digestLo = 0, digestHi = 0;
+  uint32_t end() const noexcept { return offset + tokens; }
+};
+// The identity of the images that overlap tokens [blockBegin, blockBegin + blockTokens): zero for text alone; two
+// independently seeded chains fold each overlapping span's digest, grid, placement and the block's own position
+// (blockImageIdentity, runtime/engine/cache/KvCache.cpp:29-52).
+ImageIdentity blockImageIdentity(uint64_t blockBegin, uint32_t blockTokens, std::span<const ImageSpan> spans) noexcept;
 
 class PrefixIndex final {
 public:
@@ -188,7 +200,7 @@ class Cache final {
 public:
   Cache(KvPool &pool, kv::ExtentStorage &storage, KvTier *tier = nullptr)
       : pool_(pool), storage_(storage), tier_(tier), index_(pool),
-        states_([this](uint64_t block, int states, int inUse) { index_.adjustStatesBelow(block, states, inUse); },
+        states_([this](uint64_t block, int states, int inUse) { if (index_.contains(block)) index_.adjustStatesBelow(block, states, inUse); },
                 [this] { return index_.tick(); },
                 [this](uint64_t block) { if (index_.contains(block)) index_.noteState(block); },
                 [this](uint64_t block, bool held) {
@@ -225,11 +237,12 @@ public:
   PageTableView pageTable(uint64_t request) const;
   // Hashes each newly complete page into the index; content that already exists swaps the request onto
   // the shared page and releases the writer's copy (Cache.cpp:294-333).
-  void publishCommittedBlocks(uint64_t request, std::span<const uint32_t> exactTokens, uint32_t committedTokens);
+  void publishCommittedBlocks(uint64_t request, std::span<const uint32_t> exactTokens, uint32_t committedTokens,
+                              std::span<const ImageSpan> images = {});
   // The cached chain matching the prompt: at most (n-1)/32 blocks, one real token is always left
   // to recompute (Cache.cpp:179-199).
   struct Probe;
-  std::vector<uint64_t> lookup(std::span<const uint32_t> prompt, const Probe *probe = nullptr);
+  std::vector<uint64_t> lookup(std::span<const uint32_t> prompt, const Probe *probe = nullptr, std::span<const ImageSpan> images = {});
   // The lookup a hybrid model's admission makes (Cache::lookup, Cache.cpp:236-272; CacheLookup, Cache.hpp:20-36):
   // the matched chain, the deepest state on it (pinned for the caller, as the reference's lease pins it: unpin with
   // states().unpin(stateBlock) once the restore is done), where the request resumes, whether the matched KV ends at
@@ -258,9 +271,9 @@ public:
     uint32_t cachedTokens_ = 0;
     const Cache *owner_ = nullptr;
   };
-  Probe probe(std::span<const uint32_t> prompt);
-  void refresh(Probe &probe, std::span<const uint32_t> prompt);
-  StateLookup lookupWithState(std::span<const uint32_t> prompt, const Probe *probe = nullptr);
+  Probe probe(std::span<const uint32_t> prompt, std::span<const ImageSpan> images = {});
+  void refresh(Probe &probe, std::span<const uint32_t> prompt, std::span<const ImageSpan> images = {});
+  StateLookup lookupWithState(std::span<const uint32_t> prompt, const Probe *probe = nullptr, std::span<const ImageSpan> images = {});
   // Counts a lookup that admission acted on (Cache::recordLookup, Cache.cpp:274-282); probeHashedBlocks counts the
   // pages probes hashed (CacheLookupSnapshot::probeHashedBlocks).
   struct LookupCounters { uint64_t kvHitTokens = 0, lazyJunctions = 0, lostStateMisses = 0, probeHashedBlocks = 0; };
@@ -364,7 +377,7 @@ private:
   PrefixIndex index_;
   StateCache states_;
   LookupCounters lookups_;
-  size_t extendMatch(std::vector<uint64_t> &blocks, std::span<const uint32_t> prompt) const;
+  size_t extendMatch(std::vector<uint64_t> &blocks, std::span<const uint32_t> prompt, std::span<const ImageSpan> images) const;
   uint32_t stateTokens(std::span<const uint64_t> blocks) const;
   std::unordered_map<uint64_t, Request> requests_;
   std::vector<Transfer> demotions_;

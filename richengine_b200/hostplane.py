@@ -11,6 +11,15 @@ from . import lib
 
 GRANTED, DENIED, PENDING = 0, 1, 2
 NO_PAGE = 0xFFFFFFFF
+IMAGE_SPAN = np.dtype([("offset", "<u4"), ("tokens", "<u4"), ("grid_height", "<u4"), ("grid_width", "<u4"), ("digest_lo", "<u8"), ("digest_hi", "<u8")])
+
+
+def image_spans(images):
+    """rk_image_span records from (offset, tokens, grid_height, grid_width, digest_lo, digest_hi) tuples; (None, 0) for text."""
+    if not images:
+        return None, 0
+    array = np.array([tuple(image) for image in images], dtype=IMAGE_SPAN)
+    return array, len(array)
 
 
 class KvPool:
@@ -108,14 +117,17 @@ class Cache:
         self._lib.rk_cache_page_table(self._handle, request, out, count, None, None)
         return list(out[:count]), revision.value, first.value
 
-    def publish(self, request, tokens, committed):
+    def publish(self, request, tokens, committed, images=None):
         t = np.ascontiguousarray(tokens, dtype=np.uint32)
-        self._check(self._lib.rk_cache_publish(self._handle, request, t.ctypes.data, len(t), committed), "publish")
+        spans, count = image_spans(images)
+        self._check(self._lib.rk_cache_publish(self._handle, request, t.ctypes.data, len(t), committed,
+                                               spans.ctypes.data if count else None, count), "publish")
 
-    def lookup(self, prompt):
+    def lookup(self, prompt, images=None):
         t = np.ascontiguousarray(prompt, dtype=np.uint32)
         out = (C.c_uint64 * (len(t) // 32 + 1))()
-        count = self._check(self._lib.rk_cache_lookup(self._handle, t.ctypes.data, len(t), out, len(out)), "lookup")
+        spans, n = image_spans(images)
+        count = self._check(self._lib.rk_cache_lookup(self._handle, t.ctypes.data, len(t), out, len(out), spans.ctypes.data if n else None, n), "lookup")
         return list(out[:count])
 
     def attach_prefix(self, request, blocks):
@@ -185,14 +197,16 @@ class Cache:
         self._check(self._lib.rk_cache_evict_all(self._handle, out), "evict_all")
         return {"progress": bool(out[0]), "bytes": int(out[1])}
 
-    def lookup_state(self, prompt, record=False, probe=None) -> dict:
+    def lookup_state(self, prompt, record=False, probe=None, images=None) -> dict:
         """Cache::lookup with states: the chain, the deepest state on it (pinned: unpin_state when done), where the
         request resumes, a junction worth a state, a state that was lost. A current Probe's chain is reused."""
         t = np.ascontiguousarray(prompt, dtype=np.uint32)
         blocks = (C.c_uint64 * (len(t) // 32 + 1))()
         out = (C.c_uint64 * 5)()
+        spans, n = image_spans(images)
         count = self._check(self._lib.rk_cache_lookup_state(self._handle, t.ctypes.data, len(t), blocks, len(blocks), out, int(record),
-                                                            probe._handle if probe is not None else None), "lookup_state")
+                                                            probe._handle if probe is not None else None,
+                                                            spans.ctypes.data if n else None, n), "lookup_state")
         return {"blocks": list(blocks[:count]), "kv_boundary": int(out[0]), "state_block": int(out[1]), "resume_boundary": int(out[2]),
                 "junction_boundary": int(out[3]), "lost_state": bool(out[4])}
 
@@ -201,9 +215,9 @@ class Cache:
         self._check(self._lib.rk_cache_lookup_counters(self._handle, out), "lookup_counters")
         return dict(zip(["kv_hit_tokens", "lazy_junctions", "lost_state_misses", "probe_hashed_blocks"], [int(x) for x in out]))
 
-    def probe(self, prompt) -> "Probe":
+    def probe(self, prompt, images=None) -> "Probe":
         """Cache::probe: what a scheduler keeps per waiting request between admission passes."""
-        return Probe(self, prompt)
+        return Probe(self, prompt, images)
 
     def reclaim_one_state(self, checkpoints_only=False, for_block=0) -> bool:
         return bool(self._check(self._lib.rk_cache_reclaim_one_state(self._handle, int(checkpoints_only), for_block), "reclaim_one_state"))
@@ -239,17 +253,19 @@ class Probe:
     """The scheduling probe of a waiting request (CacheProbe, runtime/engine/cache/Cache.hpp:38-52): pins nothing,
     touches no recency, counts no hit; refresh() hashes only what a change of the block graph made necessary."""
 
-    def __init__(self, cache: Cache, prompt):
+    def __init__(self, cache: Cache, prompt, images=None):
         self._cache, self._lib = cache, cache._lib
         t = np.ascontiguousarray(prompt, dtype=np.uint32)
-        self._handle = self._lib.rk_cache_probe_create(cache._handle, t.ctypes.data, len(t))
+        spans, n = image_spans(images)
+        self._handle = self._lib.rk_cache_probe_create(cache._handle, t.ctypes.data, len(t), spans.ctypes.data if n else None, n)
         if not self._handle:
             raise RuntimeError(f"probe: {self._lib.rk_last_error().decode()}")
 
-    def refresh(self, prompt, cache: Cache = None):
+    def refresh(self, prompt, cache: Cache = None, images=None):
         t = np.ascontiguousarray(prompt, dtype=np.uint32)
         owner = cache if cache is not None else self._cache
-        owner._check(self._lib.rk_cache_probe_refresh(owner._handle, self._handle, t.ctypes.data, len(t)), "probe_refresh")
+        spans, n = image_spans(images)
+        owner._check(self._lib.rk_cache_probe_refresh(owner._handle, self._handle, t.ctypes.data, len(t), spans.ctypes.data if n else None, n), "probe_refresh")
 
     def _info(self):
         out = (C.c_uint64 * 2)()

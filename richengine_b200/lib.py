@@ -163,8 +163,9 @@ SIGNATURES = {
     "rk_cache_end_request": (i32, [vp, u64]),
     "rk_cache_ensure_tokens": (i32, [vp, u64, u64]),
     "rk_cache_page_table": (i64, [vp, u64, vp, u32, C.POINTER(u64), C.POINTER(u32)]),
-    "rk_cache_publish": (i32, [vp, u64, vp, u32, u32]),
-    "rk_cache_lookup": (i64, [vp, vp, u32, vp, u32]),
+    "rk_block_image_identity": (None, [u64, u32, vp, u32, vp]),
+    "rk_cache_publish": (i32, [vp, u64, vp, u32, u32, vp, u32]),
+    "rk_cache_lookup": (i64, [vp, vp, u32, vp, u32, vp, u32]),
     "rk_cache_attach_prefix": (i32, [vp, u64, vp, u32, C.POINTER(u32)]),
     "rk_cache_restores_pending": (i32, [vp, u64]),
     "rk_cache_restore_status": (i32, [vp, u64]),
@@ -193,9 +194,9 @@ SIGNATURES = {
     "rk_cache_state_summary": (i32, [vp, vp]),
     "rk_cache_evict_one": (i32, [vp, i32, i32, i32, vp]),
     "rk_cache_reclaim_one_state": (i32, [vp, i32, u64]),
-    "rk_cache_lookup_state": (i64, [vp, vp, u32, vp, u32, vp, i32, vp]),
-    "rk_cache_probe_create": (vp, [vp, vp, u32]),
-    "rk_cache_probe_refresh": (i32, [vp, vp, vp, u32]),
+    "rk_cache_lookup_state": (i64, [vp, vp, u32, vp, u32, vp, i32, vp, vp, u32]),
+    "rk_cache_probe_create": (vp, [vp, vp, u32, vp, u32]),
+    "rk_cache_probe_refresh": (i32, [vp, vp, vp, u32, vp, u32]),
     "rk_cache_probe_info": (i32, [vp, vp]),
     "rk_cache_probe_destroy": (None, [vp]),
     "rk_cache_lookup_counters": (i32, [vp, vp]),

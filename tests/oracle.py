@@ -91,11 +91,12 @@ def reference():
             r.ref_cache_end.restype, r.ref_cache_end.argtypes = i32, [vp, u64]
             r.ref_cache_ensure.restype, r.ref_cache_ensure.argtypes = i32, [vp, u64, u64]
             r.ref_cache_page_table.restype, r.ref_cache_page_table.argtypes = i64, [vp, u64, vp, u32, vp, vp]
-            r.ref_cache_publish.restype, r.ref_cache_publish.argtypes = i32, [vp, u64, vp, u32, u32]
+            r.ref_cache_publish.restype, r.ref_cache_publish.argtypes = i32, [vp, u64, vp, u32, u32, vp, u32]
+            r.ref_block_image_identity.restype, r.ref_block_image_identity.argtypes = None, [u64, u32, vp, u32, vp]
             r.ref_cache_block_at.restype, r.ref_cache_block_at.argtypes = u64, [vp, u64, u32]
-            r.ref_cache_lookup.restype, r.ref_cache_lookup.argtypes = i32, [vp, vp, u32, i32, i32, u64, vp, vp]
-            r.ref_cache_probe_create.restype, r.ref_cache_probe_create.argtypes = vp, [vp, vp, u32]
-            r.ref_cache_probe_refresh.restype, r.ref_cache_probe_refresh.argtypes = i32, [vp, vp, vp, u32]
+            r.ref_cache_lookup.restype, r.ref_cache_lookup.argtypes = i32, [vp, vp, u32, i32, i32, u64, vp, vp, vp, u32]
+            r.ref_cache_probe_create.restype, r.ref_cache_probe_create.argtypes = vp, [vp, vp, u32, vp, u32]
+            r.ref_cache_probe_refresh.restype, r.ref_cache_probe_refresh.argtypes = i32, [vp, vp, vp, u32, vp, u32]
             r.ref_cache_probe_cached_tokens.restype, r.ref_cache_probe_cached_tokens.argtypes = u32, [vp]
             r.ref_cache_probe_destroy.restype, r.ref_cache_probe_destroy.argtypes = None, [vp]
             r.ref_cache_release_lookup.restype, r.ref_cache_release_lookup.argtypes = None, [vp, u64]

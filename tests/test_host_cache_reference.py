@@ -10,7 +10,7 @@ import numpy as np
 import pytest
 
 import oracle as om
-from richengine_b200.hostplane import GRANTED, Cache, KvPool
+from richengine_b200.hostplane import GRANTED, Cache, KvPool, image_spans
 
 reference = om.reference()
 pytestmark = pytest.mark.skipif(reference is None or not hasattr(reference, "ref_cache_create"),
@@ -36,26 +36,29 @@ class Theirs:
         assert count >= 0
         return list(pages[:count]), revision.value, first.value
 
-    def publish(self, request, tokens, committed):
+    def publish(self, request, tokens, committed, images=None):
         t = np.ascontiguousarray(tokens, dtype=np.uint32)
-        assert self.r.ref_cache_publish(self.h, request, t.ctypes.data, len(t), committed) == 0
+        spans, n = image_spans(images)
+        assert self.r.ref_cache_publish(self.h, request, t.ctypes.data, len(t), committed, spans.ctypes.data if n else None, n) == 0
 
     def block_at(self, request, boundary): return self.r.ref_cache_block_at(self.h, request, boundary)
 
-    def lookup(self, prompt, record=False, hold=False, attach_to=0, probe=None):
+    def lookup(self, prompt, record=False, hold=False, attach_to=0, probe=None, images=None):
         t = np.ascontiguousarray(prompt, dtype=np.uint32)
         out = (C.c_uint64 * 7)()
-        assert self.r.ref_cache_lookup(self.h, t.ctypes.data, len(t), int(record), int(hold), attach_to, out, probe) == 0
+        spans, n = image_spans(images)
+        assert self.r.ref_cache_lookup(self.h, t.ctypes.data, len(t), int(record), int(hold), attach_to, out, probe,
+                                       spans.ctypes.data if n else None, n) == 0
         found = dict(zip(["kv_boundary", "state_block", "resume_boundary", "junction_boundary", "lost_state"], [int(x) for x in out[:5]]))
         found["lost_state"] = bool(found["lost_state"])
         return found, int(out[5]), int(out[6])
 
-    def attach(self, request, prompt):
-        found, _, status = self.lookup(prompt, attach_to=request)
+    def attach(self, request, prompt, images=None):
+        found, _, status = self.lookup(prompt, attach_to=request, images=images)
         return status, found
 
-    def pin(self, prompt):
-        found, handle, _ = self.lookup(prompt, hold=True)
+    def pin(self, prompt, images=None):
+        found, handle, _ = self.lookup(prompt, hold=True, images=images)
         if found["state_block"]:
             self.pins.setdefault(found["state_block"], []).append(handle)
         else:
@@ -64,15 +67,17 @@ class Theirs:
 
     def unpin(self, block): self.r.ref_cache_release_lookup(self.h, self.pins[block].pop())
 
-    def probe(self, prompt):
+    def probe(self, prompt, images=None):
         t = np.ascontiguousarray(prompt, dtype=np.uint32)
-        handle = self.r.ref_cache_probe_create(self.h, t.ctypes.data, len(t))
+        spans, n = image_spans(images)
+        handle = self.r.ref_cache_probe_create(self.h, t.ctypes.data, len(t), spans.ctypes.data if n else None, n)
         assert handle
         return handle
 
-    def probe_refresh(self, handle, prompt):
+    def probe_refresh(self, handle, prompt, images=None):
         t = np.ascontiguousarray(prompt, dtype=np.uint32)
-        assert self.r.ref_cache_probe_refresh(self.h, handle, t.ctypes.data, len(t)) == 0
+        spans, n = image_spans(images)
+        assert self.r.ref_cache_probe_refresh(self.h, handle, t.ctypes.data, len(t), spans.ctypes.data if n else None, n) == 0
 
     def probe_tokens(self, handle): return self.r.ref_cache_probe_cached_tokens(handle)
     def probe_close(self, handle): self.r.ref_cache_probe_destroy(handle)
@@ -130,18 +135,18 @@ class Mine:
     def end(self, request): self.cache.end_request(request)
     def ensure(self, request, tokens): return self.cache.ensure_tokens(request, tokens)
     def table(self, request): return self.cache.page_table(request)
-    def publish(self, request, tokens, committed): self.cache.publish(request, tokens, committed)
+    def publish(self, request, tokens, committed, images=None): self.cache.publish(request, tokens, committed, images)
     def block_at(self, request, boundary): return self.cache.block_at(request, boundary)
 
-    def lookup(self, prompt, record=False, probe=None):
-        found = self.cache.lookup_state(prompt, record=record, probe=probe)
+    def lookup(self, prompt, record=False, probe=None, images=None):
+        found = self.cache.lookup_state(prompt, record=record, probe=probe, images=images)
         if found["state_block"]:
             self.cache.unpin_state(found["state_block"])
         blocks = found.pop("blocks")
         return found, blocks
 
-    def attach(self, request, prompt):
-        found = self.cache.lookup_state(prompt)
+    def attach(self, request, prompt, images=None):
+        found = self.cache.lookup_state(prompt, images=images)
         blocks = found.pop("blocks")
         status = GRANTED
         if found["state_block"]:   # the chain up to its state; without a state nothing is restored
@@ -149,13 +154,13 @@ class Mine:
             self.cache.unpin_state(found["state_block"])
         return status, found
 
-    def pin(self, prompt):
-        found = self.cache.lookup_state(prompt)
+    def pin(self, prompt, images=None):
+        found = self.cache.lookup_state(prompt, images=images)
         return found["state_block"]
 
     def unpin(self, block): self.cache.unpin_state(block)
-    def probe(self, prompt): return self.cache.probe(prompt)
-    def probe_refresh(self, handle, prompt): handle.refresh(prompt)
+    def probe(self, prompt, images=None): return self.cache.probe(prompt, images)
+    def probe_refresh(self, handle, prompt, images=None): handle.refresh(prompt, images=images)
     def probe_tokens(self, handle): return handle.cached_tokens
     def probe_close(self, handle): handle.close()
     def restore_status(self, request): return self.cache.restore_status(request)
@@ -217,7 +222,21 @@ def make_prompts(rng, count):
             letters = "".join(rng.choice(list("abcd"), size=int(rng.integers(1, 6))))
         letters = letters[:6]
         tail = rng.integers(0, 50000, size=int(rng.integers(1, 32)), dtype=np.uint32)
-        prompts.append((letters, np.concatenate([pages[x] for x in letters] + [tail])))
+        tokens = np.concatenate([pages[x] for x in letters] + [tail])
+        # Some prompts carry images: token-identical pages then share a block only under the same image content. Two
+        # digests over a few placements, so that both equal and differing identities occur.
+        images = []
+        if rng.random() < 0.4:
+            at = 0
+            while at + 8 < len(tokens) and len(images) < 3:
+                at += int(rng.integers(0, 40))
+                length = int(rng.choice([8, 16, 40]))
+                if at + length > len(tokens):
+                    break
+                digest = int(rng.choice([0x1111, 0x3333]))
+                images.append((at, length, 8, length // 4 if length >= 8 else 2, digest, digest + 1))
+                at += length
+        prompts.append((letters, tokens, images or None))
     return prompts
 
 
@@ -265,7 +284,7 @@ def run_trace(seed, steps, tier):
             both("begin", request)
             active[request] = [index, 0, 0]
             if rng.random() < 0.7:   # resume from the cache
-                (status_a, found_a), (status_b, found_b) = both("attach", request, prompts[index][1])
+                (status_a, found_a), (status_b, found_b) = both("attach", request, prompts[index][1], images=prompts[index][2])
                 assert status_a == status_b and found_a == found_b, ("attach", seed, status_a, status_b, found_a, found_b, log[-6:])
                 if status_a == GRANTED:
                     active[request][1] = active[request][2] = len(mine.table(request)[0]) * 32
@@ -283,11 +302,13 @@ def run_trace(seed, steps, tier):
             if mine.restore_status(request) != 0:
                 continue
             committed = int(rng.integers(published, ensured + 1)) if ensured > published else published
-            both("publish", request, prompts[index][1], committed)
+            both("publish", request, prompts[index][1], committed, images=prompts[index][2])
             active[request][2] = committed
             if committed >= 32 and rng.random() < 0.4:   # the engine publishes a state where the request stands
                 block = mine.block_at(request, committed // 32 * 32)
-                if tier and rng.random() < 0.7 and not mine.cache.state_info(block)["contains"]:
+                if mine.cache.block_state(block)["poisoned"]:
+                    pass   # a request one of whose reads failed is ended, it publishes nothing more
+                elif tier and rng.random() < 0.7 and not mine.cache.state_info(block)["contains"]:
                     both("publish_stored", block, 100, bool(rng.random() < 0.2))   # a state the model stores elsewhere
                 else:
                     both("publish_state", block, 100, bool(rng.random() < 0.3))
@@ -302,7 +323,7 @@ def run_trace(seed, steps, tier):
         elif op == "lookup":
             index = int(rng.integers(len(prompts)))
             record = bool(rng.random() < 0.5)
-            (found_a, _), (found_b, _, _) = both("lookup", prompts[index][1], record=record)
+            (found_a, _), (found_b, _, _) = both("lookup", prompts[index][1], record=record, images=prompts[index][2])
             assert found_a == found_b, ("lookup", seed, found_a, found_b, log[-6:])
         elif op == "state" and blocks:
             block = int(rng.choice(sorted(blocks)))
@@ -324,7 +345,7 @@ def run_trace(seed, steps, tier):
                 both("unpin", block)
             else:
                 index = int(rng.integers(len(prompts)))
-                a, b = both("pin", prompts[index][1])
+                a, b = both("pin", prompts[index][1], images=prompts[index][2])
                 assert a == b, ("pin", seed, a, b)
                 if a:
                     pinned.append(a)
@@ -343,15 +364,15 @@ def run_trace(seed, steps, tier):
         elif op == "probe":   # what a scheduler keeps per waiting request between admission passes
             if len(probes) < 3 and rng.random() < 0.4:
                 index = int(rng.integers(len(prompts)))
-                probes.append((index, mine.probe(prompts[index][1]), theirs.probe(prompts[index][1])))
+                probes.append((index, mine.probe(prompts[index][1], prompts[index][2]), theirs.probe(prompts[index][1], prompts[index][2])))
             elif probes:
                 slot = int(rng.integers(len(probes)))
                 index, a, b = probes[slot]
                 choice = rng.random()
                 if choice < 0.5:
-                    mine.probe_refresh(a, prompts[index][1]); theirs.probe_refresh(b, prompts[index][1])
+                    mine.probe_refresh(a, prompts[index][1], prompts[index][2]); theirs.probe_refresh(b, prompts[index][1], prompts[index][2])
                 elif choice < 0.8:   # an admission that acts on the probe, current or stale
-                    (found_a, _), (found_b, _, _) = mine.lookup(prompts[index][1], record=True, probe=a), theirs.lookup(prompts[index][1], record=True, probe=b)
+                    (found_a, _), (found_b, _, _) = mine.lookup(prompts[index][1], record=True, probe=a, images=prompts[index][2]), theirs.lookup(prompts[index][1], record=True, probe=b, images=prompts[index][2])
                     assert found_a == found_b, ("probed lookup", seed, found_a, found_b, log[-6:])
                 else:
                     mine.probe_close(a); theirs.probe_close(b)
@@ -388,3 +409,37 @@ def test_random_traces_without_a_tier_match_the_reference_facade(seed):
 @pytest.mark.parametrize("seed", range(8))
 def test_random_traces_through_a_tier_match_the_reference_facade(seed):
     run_trace(100 + seed, 1500, tier=True)
+
+
+def test_block_image_identity_equals_the_reference():
+    """blockImageIdentity (runtime/engine/cache/KvCache.cpp:29-52) over random sorted spans and block positions, and
+    the cases of the reference's own test (dev/tests/engine/kv_page_cache_test.cpp:35-84): text alone is zero, a block
+    after the image carries nothing, the digest and the block's alignment inside the image both count, spans outside
+    the block do not."""
+    from richengine_b200 import lib as library
+    mine = library.load()
+    def identity_mine(begin, tokens, images):
+        spans, n = image_spans(images)
+        out = (C.c_uint64 * 2)()
+        mine.rk_block_image_identity(begin, tokens, spans.ctypes.data if n else None, n, out)
+        return int(out[0]), int(out[1])
+    def identity_theirs(begin, tokens, images):
+        spans, n = image_spans(images)
+        out = (C.c_uint64 * 2)()
+        reference.ref_block_image_identity(begin, tokens, spans.ctypes.data if n else None, n, out)
+        return int(out[0]), int(out[1])
+    red, blue, later, first = (8, 16, 8, 8, 0x1111, 0x2222), (8, 16, 8, 8, 0x3333, 0x4444), (40, 16, 8, 8, 0x1111, 0x2222), (0, 8, 4, 8, 0x5555, 0x6666)
+    assert identity_mine(0, 32, None) == (0, 0) and identity_mine(32, 32, [red]) == (0, 0)
+    assert identity_mine(0, 32, [red]) != (0, 0) and identity_mine(0, 32, [red]) != identity_mine(0, 32, [blue])
+    assert identity_mine(32, 32, [later]) != identity_mine(0, 32, [red])
+    assert identity_mine(32, 32, [first, blue, later]) == identity_mine(32, 32, [later]) and identity_mine(0, 8, [first, blue, later]) == identity_mine(0, 8, [first])
+    rng = np.random.default_rng(9)
+    for _ in range(300):
+        spans, at = [], 0
+        for _ in range(int(rng.integers(0, 5))):
+            at += int(rng.integers(0, 50))
+            length = int(rng.integers(1, 70))
+            spans.append((at, length, int(rng.integers(1, 30)), int(rng.integers(1, 30)), int(rng.integers(0, 2 ** 63)), int(rng.integers(0, 2 ** 63))))
+            at += length
+        begin, tokens = int(rng.integers(0, 8)) * 32, int(rng.choice([8, 32]))
+        assert identity_mine(begin, tokens, spans) == identity_theirs(begin, tokens, spans)
