@@ -441,6 +441,14 @@ int ref_cache_reclaim_step(void *facade, int mode, int up_to_in_use, int keep_re
     return 0;
   } catch (...) { return -1; }
 }
+// Cache::evictAll: out[2] = made progress, extent bytes returned
+int ref_cache_evict_all(void *facade, uint64_t *out) {
+  try {
+    const auto step = FACADE->cache.evictAll();
+    out[0] = step.madeProgress; out[1] = step.reclaimedBytes;
+    return 0;
+  } catch (...) { return -1; }
+}
 int ref_cache_reclaim_one_state(void *facade, int checkpoints_only, uint64_t for_block) {
   try { return FACADE->cache.reclaimOneState(checkpoints_only != 0, for_block, false) ? 1 : 0; } catch (...) { return -1; }
 }

@@ -106,6 +106,7 @@ def reference():
             r.ref_cache_use_state.restype, r.ref_cache_use_state.argtypes = i32, [vp, u64, i32]
             r.ref_cache_evict_one.restype, r.ref_cache_evict_one.argtypes = i32, [vp, i32, i32, i32, vp]
             r.ref_cache_reclaim_step.restype, r.ref_cache_reclaim_step.argtypes = i32, [vp, i32, i32, i32, i32, vp]
+            r.ref_cache_evict_all.restype, r.ref_cache_evict_all.argtypes = i32, [vp, vp]
             r.ref_cache_reclaim_one_state.restype, r.ref_cache_reclaim_one_state.argtypes = i32, [vp, i32, u64]
             r.ref_cache_block_info.restype, r.ref_cache_block_info.argtypes = i32, [vp, u64, vp]
             r.ref_cache_poll.restype, r.ref_cache_poll.argtypes = i32, [vp]

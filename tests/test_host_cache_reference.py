@@ -100,6 +100,12 @@ class Theirs:
         return {"progress": int(out[0]), "pending": int(out[1]), "evicted_state": int(out[2]), "bytes": int(out[3])}
 
     def reclaim_one_state(self, checkpoints_only, for_block): return bool(self.r.ref_cache_reclaim_one_state(self.h, int(checkpoints_only), for_block))
+
+    def evict_all(self):
+        out = (C.c_uint64 * 2)()
+        assert self.r.ref_cache_evict_all(self.h, out) == 0
+        return {"progress": bool(out[0]), "bytes": int(out[1])}
+
     def poll(self): self.r.ref_cache_poll(self.h)
     def complete(self, success=True): self.r.ref_cache_tier_complete(self.h, int(success))
     def tier_set(self, limit, writable=True): self.r.ref_cache_tier_set(self.h, limit, int(writable))
@@ -179,6 +185,7 @@ class Mine:
         return self.cache.reclaim_step(mode, up_to_in_use, keep_resume_point, keep_runway)
 
     def reclaim_one_state(self, checkpoints_only, for_block): return self.cache.reclaim_one_state(checkpoints_only, for_block)
+    def evict_all(self): return self.cache.evict_all()
     def poll(self): self.cache.poll_transfers()
 
     def complete(self, success=True):
@@ -275,9 +282,9 @@ def run_trace(seed, steps, tier):
             assert mine.restore_status(request) == theirs.restore_status(request), (what, "restore status", request, seed, log[-6:])
 
     for step in range(steps):
-        op = rng.choice(["begin", "grow", "publish", "end", "lookup", "state", "use", "evict", "poll", "pin", "reclaim", "state_reclaim", "probe", "tier"],
-                        p=[0.10, 0.20, 0.18, 0.06, 0.05, 0.08, 0.04, 0.09, 0.07, 0.03, 0.04, 0.02, 0.03, 0.01] if tier else
-                          [0.10, 0.22, 0.20, 0.06, 0.06, 0.10, 0.05, 0.05, 0.02, 0.04, 0.04, 0.02, 0.04, 0.00])
+        op = rng.choice(["begin", "grow", "publish", "end", "lookup", "state", "use", "evict", "poll", "pin", "reclaim", "state_reclaim", "probe", "tier", "evict_all"],
+                        p=[0.10, 0.20, 0.18, 0.06, 0.05, 0.08, 0.04, 0.09, 0.07, 0.03, 0.04, 0.02, 0.03, 0.007, 0.003] if tier else
+                          [0.10, 0.22, 0.20, 0.06, 0.06, 0.10, 0.05, 0.05, 0.02, 0.04, 0.04, 0.02, 0.037, 0.00, 0.003])
         if op == "begin" and len(active) < 4:
             request, next_request = next_request, next_request + 1
             index = int(rng.integers(len(prompts)))
@@ -381,6 +388,9 @@ def run_trace(seed, steps, tier):
                 if slot is not None:
                     assert mine.probe_tokens(a) == theirs.probe_tokens(b), ("probe", seed, mine.probe_tokens(a), theirs.probe_tokens(b), log[-6:])
             log.append(("probe", (), {}, None, None))
+        elif op == "evict_all":   # a pressure pass: everything unpinned goes, then every extent that can be emptied
+            a, b = both("evict_all")
+            assert a == b, ("evict_all", seed, a, b, log[-6:])
         elif op == "tier":   # the tier takes fewer or more transfers at a time, or no writes at all (a failed write closed it)
             both("tier_set", int(rng.choice([0, 1, 2, 4])), bool(rng.random() < 0.8))
         elif op == "poll" and tier:
