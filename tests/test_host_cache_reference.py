@@ -116,7 +116,7 @@ class Theirs:
         if not out[0]:
             return None
         return {"page": int(out[1]), "transferring": bool(out[3]), "state": bool(out[5]), "state_resident": bool(out[6]),
-                "state_ordinary": bool(out[7]), "tier_copy": bool(out[2]), "poisoned": not out[4]}
+                "state_ordinary": bool(out[7]), "poisoned": not out[4]}
 
     def snapshot(self):
         out = (C.c_uint64 * 16)()
@@ -199,13 +199,10 @@ class Mine:
         if found is None:
             return None
         state = self.cache.state_info(block)
-        # a copy being written counts as a tier copy there from the start of the write
+        # (whether a block has a tier copy is compared through the tier's block count: there a copy counts from the start
+        # of its write, here from its landing)
         return {"page": int(found["page"]), "transferring": found["transferring"], "state": bool(state["contains"]),
-                "state_resident": bool(state["resident"]), "state_ordinary": bool(state["ordinary"]), "poisoned": found["poisoned"],
-                "tier_copy": found["tier_copy"] or (found["transferring"] and found["page"] != 0xFFFFFFFF and not self._restoring(block))}
-
-    def _restoring(self, block):
-        return False
+                "state_resident": bool(state["resident"]), "state_ordinary": bool(state["ordinary"]), "poisoned": found["poisoned"]}
 
     def snapshot(self):
         pool, cache, states, tier = self.pool.snapshot(), self.cache.snapshot(), self.cache.state_summary(), self.cache.tier_counters()
@@ -273,9 +270,6 @@ def run_trace(seed, steps, tier):
             assert value == b[key], (what, key, value, b[key], seed, log[-6:])
         for block in sorted(blocks):
             a, b = mine.block_info(block), theirs.block_info(block)
-            if a is not None and b is not None:
-                a, b = dict(a), dict(b)
-                a.pop("tier_copy"); b.pop("tier_copy")
             assert a == b, (what, "block", block, a, b, seed, log[-6:])
         for request in active:
             assert mine.table(request) == theirs.table(request), (what, "page table", request, seed, log[-6:])
