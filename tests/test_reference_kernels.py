@@ -379,3 +379,19 @@ def test_long_contexts_and_the_plan_s_split_counts_agree_with_the_reference(fmt)
     theirs = reference_attention(fmt, 8, s, q, params, None)
     mine = checker_attention(fmt, s, q, params, None)
     assert_attention_close(theirs, mine, [8, 8, 8], "long chain verify")
+
+
+@pytest.mark.parametrize("fmt", [INT4, INT8])
+def test_the_largest_chunk_store_equals_the_reference_kernel(fmt):
+    """2 048 rows, the reference's prefill token budget, appended after 6 144 committed tokens (the prefill benchmark's
+    shape): 16 384 threadgroups of the reference's chunk store."""
+    layout = Layout(1, 4, 256, fmt)
+    mine, theirs = pair(layout, [6144], 2048)
+    k, v = make_staging(np.random.default_rng(71), 1, layout, stride=2048)
+    for scenario, store in ((mine, None), (theirs, reference)):
+        params = lib.ChunkParams(6144, 2048, 2048, len(scenario.pages[0]), scenario.host.layer(0))
+        if store is None:
+            assert om.oracle().rko_store_chunk(fmt, 4, 256, k.ctypes.data, v.ctypes.data, scenario.host_tables[0].ctypes.data, C.byref(params)) == 0
+        else:
+            assert store.ref_metal_store_chunk(fmt, k.ctypes.data, v.ctypes.data, scenario.host_tables[0].ctypes.data, C.byref(params)) == 0
+    assert_same_bytes(mine, theirs, "largest chunk store")
