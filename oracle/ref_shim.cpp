@@ -19,6 +19,7 @@
 #include "Q8PageFormatReference.hpp"
 #include "Fp8PageFormatReference.hpp"
 #include "engine/cache/Cache.hpp"
+#include "engine/cache/DiskLabels.hpp"
 #include "engine/cache/KvPool.hpp"
 #include "model/SlotFile.hpp"
 #include "TestKvTier.hpp"
@@ -130,9 +131,9 @@ struct Facade {
   std::map<uint64_t, engine::StateUse> uses;      // one use handle per block
   std::map<uint64_t, engine::CacheLookup> held;   // lookups kept alive: their leases pin the state
   uint64_t nextHeld = 1;
-  Facade(uint32_t pages, uint64_t bytes, uint32_t extent, uint32_t runway, uint64_t budget, bool withTier)
+  Facade(uint32_t pages, uint64_t bytes, uint32_t extent, uint32_t runway, uint64_t budget, int withTier)
       : storage(pages, bytes, extent), pool((storage.budget = budget, storage), runway),
-        tier(withTier ? std::make_unique<test::TestKvTier>() : nullptr), cache(pool, tier.get(), nullptr) {}
+        tier(withTier ? std::make_unique<test::TestKvTier>(withTier == 2) : nullptr), cache(pool, tier.get(), nullptr) {}
 };
 
 struct Pool {
@@ -321,7 +322,7 @@ void ref_pool_snapshot(void *pool, uint64_t *out) {
 void *ref_cache_create(uint32_t pages, uint64_t bytes_per_page, uint32_t extent_pages, uint32_t runway_pages,
                        uint64_t budget_pages, int with_tier, uint32_t tier_capacity, uint32_t transfer_limit) {
   try {
-    auto f = std::make_unique<Facade>(pages, bytes_per_page, extent_pages, runway_pages, budget_pages, with_tier != 0);
+    auto f = std::make_unique<Facade>(pages, bytes_per_page, extent_pages, runway_pages, budget_pages, with_tier); // 2: a persistent tier
     if (f->tier) { f->tier->capacity = tier_capacity; f->tier->transferLimit = transfer_limit; }
     return f.release();
   } catch (...) { return nullptr; }
@@ -476,6 +477,46 @@ void ref_cache_snapshot(void *facade, uint64_t *out) {
   out[7] = s.kvTier.diskBlocks; out[8] = s.kvTier.pendingPages; out[9] = s.kvTier.demotions; out[10] = s.kvTier.restores;
   out[11] = s.kvTier.demotionsRefused;
   out[12] = s.lookup.kvHitTokens; out[13] = s.lookup.lazyJunctions; out[14] = s.lookup.lostStateMisses; out[15] = s.lookup.probeHashedBlocks;
+}
+// Cache::adopt on a cache with a persistent tier (with_tier == 2 at creation). KV labels cross as they lie in a slot
+// file's records (label i has sizes[i] bytes, back to back); each adopted slot is a fresh slot of the test tier. One
+// stored state per (state_blocks[i], state_tokens[i]) names the restore points: the reference takes a chain back only
+// for a state. out[4] = states, blocks, bytes, dropped.
+int ref_cache_adopt(void *facade, const uint8_t *labels, const uint32_t *sizes, uint32_t count, const uint64_t *state_blocks,
+                    const uint32_t *state_tokens, const uint64_t *state_last_used, uint32_t states, uint64_t *out) {
+  try {
+    std::vector<engine::PersistedKv> blocks;
+    test::TestKvTier *tier = FACADE->tier.get();
+    for (uint32_t i = 0; i < count; ++i) {
+      engine::PersistedKv block;
+      block.label.assign(reinterpret_cast<const std::byte *>(labels), reinterpret_cast<const std::byte *>(labels) + sizes[i]);
+      block.adopt = [tier] { return tier->adopt(); };
+      blocks.push_back(std::move(block));
+      labels += sizes[i];
+    }
+    std::vector<engine::PersistedState> kept;
+    for (uint32_t i = 0; i < states; ++i) {
+      engine::PersistedState state;
+      state.label = engine::encodeLabel(engine::StateLabel{state_blocks[i], state_last_used[i], state_tokens[i], 0});
+      state.adopt = [](uint32_t) { return std::make_shared<StoredState>(64); };
+      kept.push_back(std::move(state));
+    }
+    const engine::CacheAdoption result = FACADE->cache.adopt(std::move(blocks), std::move(kept));
+    out[0] = result.states; out[1] = result.blocks; out[2] = result.bytes; out[3] = result.dropped;
+    return 0;
+  } catch (...) { return -1; }
+}
+// The labels a persistent test tier's slots carry (Cache labels a copy when it lands), 168 bytes each, in no order.
+int ref_cache_tier_labels(void *facade, uint8_t *out, uint32_t capacity) {
+  try {
+    uint32_t count = 0;
+    for (const auto &label : FACADE->tier->labels()) {
+      if (label.size() != sizeof(engine::KvBlockLabel)) return -2;
+      if (count < capacity) std::memcpy(out + size_t(count) * sizeof(engine::KvBlockLabel), label.data(), label.size());
+      ++count;
+    }
+    return int(count);
+  } catch (...) { return -1; }
 }
 #undef FACADE
 

@@ -9,8 +9,10 @@
 // publishCommittedBlocks (dedupe onto the shared page), lookup / attach of a cached prefix, reclaim of
 // the oldest idle leaf through the tier, transfer retirement. Two extensions BASELINE.json asks for that
 // the reference does not have: forkRequest (share full pages, copy the partial tail page) and truncate
-// (give back the pages past a rejected speculative tail). Composite recurrent states, image spans,
-// persistence and probes of the reference facade are outside this path.
+// (give back the pages past a rejected speculative tail). Also here: the coupling of composite recurrent states
+// to KV blocks (policy only: a state's buffers are a byte count), image identity in a block's key, lookup probes,
+// and sealing / adopting tier copies through the slot store. The recurrent-state buffers themselves and the
+// reference's disk directory (CacheDirectory) are outside this path.
 #pragma once
 
 #include "kv_pool.hpp"

@@ -111,6 +111,9 @@ def reference():
             r.ref_cache_block_info.restype, r.ref_cache_block_info.argtypes = i32, [vp, u64, vp]
             r.ref_cache_poll.restype, r.ref_cache_poll.argtypes = i32, [vp]
             r.ref_cache_snapshot.restype, r.ref_cache_snapshot.argtypes = None, [vp, vp]
+            if hasattr(r, "ref_cache_adopt"):
+                r.ref_cache_adopt.restype, r.ref_cache_adopt.argtypes = i32, [vp, vp, vp, u32, vp, vp, vp, u32, vp]
+                r.ref_cache_tier_labels.restype, r.ref_cache_tier_labels.argtypes = i32, [vp, vp, u32]
         if hasattr(r, "ref_slotfile_write"):  # the persistent slot file
             r.ref_slotfile_write.restype = C.c_int
             r.ref_slotfile_write.argtypes = [C.c_char_p, C.c_char_p, vp, u32, u32, u64, u32, vp, u64, vp]
