@@ -124,6 +124,15 @@ int64_t rk_slot_records_header(uint64_t slot_bytes, uint32_t label_bytes, const 
  * restored, and a mismatch is a failed restore (a cache miss). */
 int64_t rk_cache_persist(void *cache, void *store);
 int rk_cache_adopt(void *cache, void *store, uint64_t *out);
+/* Restore points, as the reference keeps them for models whose chains resume only through a composite state
+ * (Cache::adopt, runtime/engine/cache/Cache.cpp:70-127; StateLabel, DiskLabels.hpp:31-37): each stored state comes back
+ * with its whole chain and a block only for a state. state_labels = `count` records of 24 bytes {block u64, lastUsed
+ * u64, tokens u32, checkpoint u32}; state_bytes = each state's size. out[4] = blocks, dropped (records and states left
+ * behind), bytes, states. rk_cache_state_labels writes the label of every stored state as a clean stop records it
+ * (Cache::relabelStates, StateCache.cpp:307-311,619-625) and returns their number, or -1. */
+int rk_cache_adopt_restore_points(void *cache, void *store, const void *state_labels, const uint64_t *state_bytes, uint32_t count,
+                                  uint64_t *out);
+int64_t rk_cache_state_labels(void *cache, void *labels, uint64_t *state_bytes, uint32_t capacity);
 
 /* ---- composite states and the reclaim order they impose (runtime/engine/cache/StateCache.hpp:137-379 as far as the
  * KV path is coupled to it, Cache.hpp:549-556, Cache.cpp:451-628) ------------------------------------------------

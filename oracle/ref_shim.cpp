@@ -28,6 +28,7 @@
 #include <cstring>
 #include <map>
 #include <memory>
+#include <set>
 #include <vector>
 
 using namespace richengine;
@@ -106,14 +107,20 @@ private:
   uint64_t bytes_;
 };
 
-// A state whose only copy is stored elsewhere, and the ticket of a write that has landed already.
+// A state whose only copy is stored elsewhere (and, below, the ticket of a write that has landed already): a byte count, and the label a persistent cache keeps with it (CompositeState::label). The
+// copies alive are listed so that a test can read the labels as the next process would find them.
 class StoredState final : public CompositeState {
 public:
-  explicit StoredState(uint64_t bytes) : bytes_(bytes) {}
+  explicit StoredState(uint64_t bytes) : bytes_(bytes) { alive().insert(this); }
+  ~StoredState() override { alive().erase(this); }
   uint64_t bytes() const noexcept override { return bytes_; }
   uint64_t residentBytes() const noexcept override { return 0; }
+  void label(std::vector<std::byte> bytes) const override { label_ = std::move(bytes); }
+  const std::vector<std::byte> &kept() const noexcept { return label_; }
+  static std::set<const StoredState *> &alive() { static std::set<const StoredState *> copies; return copies; }
 private:
   uint64_t bytes_;
+  mutable std::vector<std::byte> label_;
 };
 struct LandedWrite final : StateOffload {
   std::shared_ptr<const CompositeState> copy;
@@ -498,12 +505,51 @@ int ref_cache_adopt(void *facade, const uint8_t *labels, const uint32_t *sizes, 
     for (uint32_t i = 0; i < states; ++i) {
       engine::PersistedState state;
       state.label = engine::encodeLabel(engine::StateLabel{state_blocks[i], state_last_used[i], state_tokens[i], 0});
+      state.adopt = [](uint32_t) { return std::make_shared<StoredState>(64); }; // every state is 64 bytes here
+      kept.push_back(std::move(state));
+    }
+    const engine::CacheAdoption result = FACADE->cache.adopt(std::move(blocks), std::move(kept));
+    out[0] = result.states; out[1] = result.blocks; out[2] = result.bytes; out[3] = result.dropped;
+    return 0;
+  } catch (...) { return -1; }
+}
+// The same with the state labels as they lie in a states' file: `states` StateLabel records of 24 bytes.
+int ref_cache_adopt_labelled(void *facade, const uint8_t *labels, const uint32_t *sizes, uint32_t count, const uint8_t *state_labels,
+                             uint32_t states, uint64_t *out) {
+  try {
+    std::vector<engine::PersistedKv> blocks;
+    test::TestKvTier *tier = FACADE->tier.get();
+    for (uint32_t i = 0; i < count; ++i) {
+      engine::PersistedKv block;
+      block.label.assign(reinterpret_cast<const std::byte *>(labels), reinterpret_cast<const std::byte *>(labels) + sizes[i]);
+      block.adopt = [tier] { return tier->adopt(); };
+      blocks.push_back(std::move(block));
+      labels += sizes[i];
+    }
+    std::vector<engine::PersistedState> kept;
+    for (uint32_t i = 0; i < states; ++i) {
+      engine::PersistedState state;
+      const auto *at = reinterpret_cast<const std::byte *>(state_labels) + size_t(i) * sizeof(engine::StateLabel);
+      state.label.assign(at, at + sizeof(engine::StateLabel));
       state.adopt = [](uint32_t) { return std::make_shared<StoredState>(64); };
       kept.push_back(std::move(state));
     }
     const engine::CacheAdoption result = FACADE->cache.adopt(std::move(blocks), std::move(kept));
     out[0] = result.states; out[1] = result.blocks; out[2] = result.bytes; out[3] = result.dropped;
     return 0;
+  } catch (...) { return -1; }
+}
+// Cache::relabelStates (what a clean stop does), then the label of every stored state alive, 24 bytes each, with its size.
+int ref_cache_state_labels(void *facade, uint8_t *out, uint64_t *sizes, uint32_t capacity) {
+  try {
+    FACADE->cache.relabelStates();
+    uint32_t count = 0;
+    for (const StoredState *state : StoredState::alive()) {
+      if (state->kept().size() != sizeof(engine::StateLabel)) continue;
+      if (count < capacity) { std::memcpy(out + size_t(count) * sizeof(engine::StateLabel), state->kept().data(), sizeof(engine::StateLabel)); sizes[count] = state->bytes(); }
+      ++count;
+    }
+    return int(count);
   } catch (...) { return -1; }
 }
 // The labels a persistent test tier's slots carry (Cache labels a copy when it lands), 168 bytes each, in no order.

@@ -415,6 +415,35 @@ int rk_cache_adopt(void *cache, void *store, uint64_t *out) {
   });
 }
 
+// The reference's rule for restore points: a stored state comes back with its whole chain, a block only for a state.
+// state_labels: `count` StateLabel records of 24 bytes; state_bytes: each state's size. out = {blocks, dropped, bytes, states}.
+int rk_cache_adopt_restore_points(void *cache, void *store, const void *state_labels, const uint64_t *state_bytes, uint32_t count, uint64_t *out) {
+  return guarded([&] {
+    std::vector<engine::Cache::PersistedState> states(count);
+    for (uint32_t i = 0; i < count; ++i) {
+      std::memcpy(&states[i].label, static_cast<const uint8_t *>(state_labels) + size_t(i) * sizeof(model::StateLabel), sizeof(model::StateLabel));
+      states[i].bytes = state_bytes[i];
+    }
+    const auto adoption = static_cast<CacheHandle *>(cache)->cache->adoptRestorePoints(*static_cast<model::SlotStore *>(store), states);
+    out[0] = adoption.blocks; out[1] = adoption.dropped; out[2] = adoption.bytes; out[3] = adoption.states;
+    return RK_OK;
+  });
+}
+// The label of every stored state as a clean stop writes it; returns how many there are (the first `capacity` are written).
+int64_t rk_cache_state_labels(void *cache, void *labels, uint64_t *state_bytes, uint32_t capacity) {
+  int64_t count = -1;
+  const int status = guarded([&] {
+    const auto found = static_cast<CacheHandle *>(cache)->cache->stateLabels();
+    for (size_t i = 0; i < found.size() && i < capacity; ++i) {
+      std::memcpy(static_cast<uint8_t *>(labels) + i * sizeof(model::StateLabel), &found[i].label, sizeof(model::StateLabel));
+      state_bytes[i] = found[i].bytes;
+    }
+    count = int64_t(found.size());
+    return RK_OK;
+  });
+  return status == RK_OK ? count : -1;
+}
+
 int rk_plan_verify(uint32_t lanes, uint32_t query_heads, uint32_t layers, uint32_t kv_heads, uint32_t head_dim, uint32_t format,
                    const uint32_t *history, int tree, uint32_t row_capacity, uint32_t ctas, char *names, size_t names_bytes, uint64_t *out) {
   return guarded([&] {

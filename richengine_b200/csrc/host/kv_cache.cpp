@@ -1036,12 +1036,16 @@ uint32_t Cache::persist(model::SlotStore &store) {
   return written;
 }
 
-Cache::Adoption Cache::adopt(model::SlotStore &store) {
+Cache::Adoption Cache::adopt(model::SlotStore &store) { return adoptRecords(store, nullptr); }
+Cache::Adoption Cache::adoptRestorePoints(model::SlotStore &store, std::span<const PersistedState> states) { return adoptRecords(store, &states); }
+
+Cache::Adoption Cache::adoptRecords(model::SlotStore &store, const std::span<const PersistedState> *states) {
   if (!tier_) throw std::logic_error("a cache takes back copies only from a tier");
-  if (!requests_.empty() || index_.size()) throw std::logic_error("a cache takes back copies only before anything else is in it");
+  if (!requests_.empty() || index_.size() || states_.size()) throw std::logic_error("a cache takes back copies only before anything else is in it");
   if (store.labelBytes() != sizeof(model::KvBlockLabel)) throw std::invalid_argument("the slot store holds another kind of label");
   Adoption result;
-  struct Recorded { model::KvBlockLabel label; const model::SlotRecord *record = nullptr; uint32_t tokens = 0; };
+  // tokens: up to and including the block by the labels alone; zero while its chain is broken.
+  struct Recorded { model::KvBlockLabel label; const model::SlotRecord *record = nullptr; uint32_t tokens = 0; bool needed = false; };
   std::map<uint64_t, Recorded> recorded;
   uint64_t highestId = 0, lastUsed = 0;
   for (const model::SlotRecord &record : store.records()) {
@@ -1058,11 +1062,34 @@ Cache::Adoption Cache::adopt(model::SlotStore &store) {
     }
   }
   // A parent's id is lower than its children's, so a chain resolves in id order and a cycle cannot form.
+  for (auto &[id, block] : recorded) {
+    if (!block.label.parent) {
+      block.tokens = PrefixIndex::pageTokens;
+    } else if (auto parent = recorded.find(block.label.parent); parent != recorded.end() && parent->second.tokens) {
+      block.tokens = parent->second.tokens + PrefixIndex::pageTokens;
+    }
+    block.needed = !states && block.tokens; // without the state layer every whole chain comes back
+  }
+  std::vector<const PersistedState *> kept;
+  if (states) {
+    for (const PersistedState &state : *states) {
+      highestId = std::max(highestId, state.label.block);
+      const auto block = recorded.find(state.label.block);
+      if (block == recorded.end() || !block->second.tokens || block->second.tokens != state.label.tokens || !state.bytes) {
+        ++result.dropped;
+        continue;
+      }
+      kept.push_back(&state);
+      for (auto above = block; above != recorded.end() && !above->second.needed; above = recorded.find(above->second.label.parent))
+        above->second.needed = true;
+    }
+  }
+  // A record whose payload cannot be read, or whose key another block took, stays behind, and so does everything below.
   std::vector<uint8_t> payload(tier_->slotBytes());
+  std::set<uint64_t> adopted;
   for (auto &[id, block] : recorded) {
     bool taken = false;
-    const bool chained = !block.label.parent || (recorded.count(block.label.parent) && recorded.at(block.label.parent).tokens);
-    if (chained && store.read(block.record->index, payload)) {
+    if (block.needed && (!block.label.parent || adopted.count(block.label.parent)) && store.read(block.record->index, payload)) {
       if (auto slot = tier_->adoptSlot(payload.data(), payload.size(), block.record->checksum))
         taken = index_.adoptTierBlock(id, block.label.parent, block.label.tokens, {block.label.imagesLo, block.label.imagesHi},
                                       std::move(slot), block.label.lastUsed);
@@ -1072,14 +1099,37 @@ Cache::Adoption Cache::adopt(model::SlotStore &store) {
       store.free(block.record->index);
       continue;
     }
-    block.tokens = (block.label.parent ? recorded.at(block.label.parent).tokens : 0) + PrefixIndex::pageTokens;
+    adopted.insert(id);
     lastUsed = std::max(lastUsed, block.label.lastUsed);
     ++result.blocks;
   }
+  // A block holds one state; a second label for it is a stale one.
+  uint64_t stateBytes = 0;
+  for (const PersistedState *state : kept) {
+    if (adopted.count(state->label.block) && !states_.contains(state->label.block)) {
+      states_.adoptStored(state->label.block, state->bytes, state->label.lastUsed, state->label.checkpoint != 0);
+      lastUsed = std::max(lastUsed, state->label.lastUsed);
+      stateBytes += state->bytes;
+      ++result.states;
+    } else {
+      ++result.dropped;
+    }
+  }
   // New ids continue after every id a record names, taken back or not.
   index_.continueAfter(highestId, lastUsed);
-  result.bytes = uint64_t(result.blocks) * tier_->slotBytes();
+  result.bytes = stateBytes + uint64_t(result.blocks) * tier_->slotBytes();
   return result;
+}
+
+std::vector<Cache::PersistedState> Cache::stateLabels() const {
+  std::vector<PersistedState> labels;
+  for (const StateCache::StoredState &state : states_.storedStates()) {
+    if (!index_.contains(state.block)) continue;
+    uint32_t blocks = 0;
+    for (uint64_t at = state.block; at; at = index_.parent(at)) ++blocks;
+    labels.push_back({model::StateLabel{state.block, state.lastUsed, blocks * PrefixIndex::pageTokens, state.checkpoint ? 1u : 0u}, state.bytes});
+  }
+  return labels;
 }
 
 } // namespace rkb::engine

@@ -80,6 +80,7 @@ public:
   // poisoned block hides those below it, so after a change a probe's chain holds up to its first unmatchable block.
   uint64_t generation() const noexcept { return generation_; }
   uint32_t page(uint64_t block) const { return at(block).page; }
+  uint64_t parent(uint64_t block) const { return at(block).parent; }
   std::shared_ptr<KvTierSlot> slot(uint64_t block) const { return at(block).slot; }
   bool transferring(uint64_t block) const { return at(block).transferring; }
   bool idle(uint64_t block) const { const Block &b = at(block); return !b.activeUsers && !b.transferring; }
@@ -333,13 +334,24 @@ public:
   // children's), a block comes back only under an unbroken chain, a duplicate key or a damaged label stays
   // behind, and the records that stay behind are freed. A payload is checked against its record's CRC-32C when
   // it is first restored. Without the reference's composite-state layer every intact chain comes back.
-  struct Adoption { uint32_t blocks = 0, dropped = 0; uint64_t bytes = 0; };
+  struct Adoption { uint32_t blocks = 0, dropped = 0; uint64_t bytes = 0; uint32_t states = 0; };
   Adoption adopt(model::SlotStore &store);
+  // The reference's rule for a cache whose chains resume only through composite states (Cache::adopt,
+  // runtime/engine/cache/Cache.cpp:70-127): a state comes back with its whole chain, stored; a block only for a state.
+  // A state whose block has no whole chain, or whose label names another boundary than the chain's length, stays
+  // behind, and so does a second state of one block; `dropped` counts those too. Ids continue after every id a block
+  // or state label names.
+  struct PersistedState { model::StateLabel label; uint64_t bytes = 0; };
+  Adoption adoptRestorePoints(model::SlotStore &store, std::span<const PersistedState> states);
+  // The label of every stored state as a clean stop writes it (Cache::relabelStates, StateCache::labelDisk): block,
+  // recency, the chain's length in tokens, class.
+  std::vector<PersistedState> stateLabels() const;
 
   PrefixIndex &index() noexcept { return index_; }
   CacheSnapshot snapshot() const;
 
 private:
+  Adoption adoptRecords(model::SlotStore &store, const std::span<const PersistedState> *states);
   struct Request {
     std::vector<uint32_t> pages;
     std::vector<uint64_t> blocks; // cached chain covering the first blocks.size() pages

@@ -64,6 +64,25 @@ void StateCache::publishStored(uint64_t block, uint64_t bytes, bool checkpoint) 
   adjust_(block, +1, inUse(block) ? +1 : 0);
 }
 
+void StateCache::adoptStored(uint64_t block, uint64_t bytes, uint64_t lastUsed, bool checkpoint) {
+  if (!block || !bytes) throw std::invalid_argument("an adopted composite state is a stored copy on a KV block");
+  if (states_.count(block)) throw std::invalid_argument("adopted composite state has no block of its own");
+  State state{bytes, lastUsed, checkpoint, 0};
+  state.resident = false;
+  state.stored = true;
+  states_.emplace(block, state);
+  if (!checkpoint && note_) note_(block);
+  adjust_(block, +1, 0);
+}
+
+std::vector<StateCache::StoredState> StateCache::storedStates() const {
+  std::vector<StoredState> found;
+  for (const auto &[block, state] : states_)
+    if (state.stored && !state.invalid) found.push_back({block, state.bytes, state.lastUsed, state.checkpoint});
+  std::sort(found.begin(), found.end(), [](const StoredState &a, const StoredState &b) { return a.block < b.block; });
+  return found;
+}
+
 bool StateCache::ordinary(uint64_t block) const noexcept {
   auto found = states_.find(block);
   return found != states_.end() && !found->second.invalid && !found->second.checkpoint;

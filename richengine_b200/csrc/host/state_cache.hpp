@@ -46,6 +46,11 @@ public:
   // Publishes a state whose only copy the model stores elsewhere (StateCache::publishStateToDisk). A block's state
   // is published once: a second publication is a logic error.
   void publishStored(uint64_t block, uint64_t bytes, bool checkpoint);
+  // A state an earlier process left stored, with the recency and class its label kept (StateCache::adoptDisk).
+  void adoptStored(uint64_t block, uint64_t bytes, uint64_t lastUsed, bool checkpoint);
+  // Every state with a stored copy: what a persistent tier's labels name (StateCache::relabel / labelDisk).
+  struct StoredState { uint64_t block, bytes, lastUsed; bool checkpoint; };
+  std::vector<StoredState> storedStates() const;
   bool contains(uint64_t block) const noexcept { auto f = states_.find(block); return f != states_.end() && !f->second.invalid; }
   bool ordinary(uint64_t block) const noexcept;
   uint64_t bytes(uint64_t block) const noexcept;

@@ -239,6 +239,23 @@ class Cache:
         self._check(self._lib.rk_cache_adopt(self._handle, store.handle, out), "adopt")
         return {"blocks": out[0], "dropped": out[1], "bytes": out[2]}
 
+    def adopt_restore_points(self, store: "SlotStore", states) -> dict:
+        """On an empty cache, the reference's rule: each stored state comes back with its whole chain, a block only for
+        a state. states = [(label bytes of a StateLabel, size in bytes)]. {blocks, dropped, bytes, states}."""
+        labels = C.create_string_buffer(b"".join(label for label, _ in states), max(1, STATE_LABEL_BYTES * len(states)))
+        sizes = (C.c_uint64 * max(1, len(states)))(*[size for _, size in states])
+        out = (C.c_uint64 * 4)()
+        self._check(self._lib.rk_cache_adopt_restore_points(self._handle, store.handle, labels, sizes, len(states), out), "adopt_restore_points")
+        return {"blocks": out[0], "dropped": out[1], "bytes": out[2], "states": out[3]}
+
+    def state_labels(self):
+        """[(StateLabel bytes, size)] of every stored state, as a clean stop records them."""
+        count = self._check(self._lib.rk_cache_state_labels(self._handle, None, None, 0), "state_labels")
+        labels = C.create_string_buffer(max(1, STATE_LABEL_BYTES * count))
+        sizes = (C.c_uint64 * max(1, count))()
+        self._check(self._lib.rk_cache_state_labels(self._handle, labels, sizes, count), "state_labels")
+        return [(labels.raw[i * STATE_LABEL_BYTES:(i + 1) * STATE_LABEL_BYTES], int(sizes[i])) for i in range(count)]
+
     def block_state(self, block):
         out = (C.c_uint64 * 5)()
         if self._lib.rk_cache_block_state(self._handle, block, out) < 0:
@@ -246,6 +263,7 @@ class Cache:
         return {"page": out[0], "tier_copy": bool(out[1]), "transferring": bool(out[2]), "last_used": out[3], "poisoned": bool(out[4])}
 
 
+STATE_LABEL_BYTES = 24  # engine::StateLabel: block, lastUsed (u64 each), tokens, checkpoint (u32 each)
 KV_BLOCK_LABEL_BYTES = 168  # engine::KvBlockLabel: id, parent, lastUsed, images lo/hi (u64 each), 32 token ids (u32)
 
 
@@ -285,6 +303,10 @@ class Probe:
 
     def __del__(self):
         self.close()
+
+
+def state_label(block, last_used, tokens, checkpoint=False) -> bytes:
+    return np.array([block, last_used], dtype="<u8").tobytes() + np.array([tokens, int(checkpoint)], dtype="<u4").tobytes()
 
 
 def kv_block_label(block_id, parent, last_used, tokens, images=(0, 0)) -> bytes:

@@ -213,6 +213,8 @@ SIGNATURES = {
     "rk_slot_records_header": (i64, [u64, u32, vp, u32, vp, u32]),
     "rk_cache_persist": (i64, [vp, vp]),
     "rk_cache_adopt": (i32, [vp, vp, vp]),
+    "rk_cache_adopt_restore_points": (i32, [vp, vp, vp, vp, u32, vp]),
+    "rk_cache_state_labels": (i64, [vp, vp, vp, u32]),
     "rk_plan_window_splits": (i32, [u32, u32, u32, u32]),
     "rk_plan_verify": (i32, [u32, u32, u32, u32, u32, u32, vp, i32, u32, u32, C.c_char_p, C.c_size_t, vp]),
     "rk_plan_prefill": (i32, [u32, u32, u32, u32, u32, u32, C.c_char_p, C.c_size_t, vp]),

@@ -114,6 +114,8 @@ def reference():
             if hasattr(r, "ref_cache_adopt"):
                 r.ref_cache_adopt.restype, r.ref_cache_adopt.argtypes = i32, [vp, vp, vp, u32, vp, vp, vp, u32, vp]
                 r.ref_cache_tier_labels.restype, r.ref_cache_tier_labels.argtypes = i32, [vp, vp, u32]
+                r.ref_cache_adopt_labelled.restype, r.ref_cache_adopt_labelled.argtypes = i32, [vp, vp, vp, u32, C.c_char_p, u32, vp]
+                r.ref_cache_state_labels.restype, r.ref_cache_state_labels.argtypes = i32, [vp, vp, vp, u32]
         if hasattr(r, "ref_slotfile_write"):  # the persistent slot file
             r.ref_slotfile_write.restype = C.c_int
             r.ref_slotfile_write.argtypes = [C.c_char_p, C.c_char_p, vp, u32, u32, u64, u32, vp, u64, vp]

@@ -13,7 +13,7 @@ import pytest
 
 import oracle as om
 from richengine_b200 import lib
-from richengine_b200.hostplane import GRANTED, KV_BLOCK_LABEL_BYTES, Cache, KvPool, SlotStore, kv_block_label
+from richengine_b200.hostplane import GRANTED, KV_BLOCK_LABEL_BYTES, STATE_LABEL_BYTES, Cache, KvPool, SlotStore, kv_block_label, state_label
 
 reference = om.reference()
 pytestmark = pytest.mark.skipif(reference is None or not hasattr(reference, "ref_cache_adopt"),
@@ -153,6 +153,73 @@ def test_adoption_of_a_damaged_record_set_equals_the_reference(tmp_path, seed):
         store.close(); cache.close(); pool.close()
 
 
+def random_states(rng, recorded):
+    """Stored states over a label forest: at some blocks with whole chains, plus the defects of a stale state file — a
+    boundary that is not the chain's length, a block no record names, a block whose chain is broken, a second state of
+    one block. (block, last used, tokens, checkpoint), the order of a StateLabel's fields."""
+    depth = depths(recorded)
+    states = []
+    for block, tokens in depth.items():
+        roll = rng.random()
+        if roll < 0.35:
+            states.append((block, int(rng.integers(1, 20_000)), tokens or 32, bool(rng.random() < 0.3)))  # a broken chain's state claims one page
+        elif roll < 0.40:
+            states.append((block, int(rng.integers(1, 20_000)), tokens + 32, False))
+        if roll < 0.05:
+            states.append((block, int(rng.integers(1, 20_000)), tokens or 32, bool(rng.random() < 0.5)))
+    if rng.random() < 0.5:
+        states.append((max(depth, default=0) + int(rng.integers(1, 40)), 7, 32, False))
+    return [states[i] for i in rng.permutation(len(states))]
+
+
+def reference_adopt_points(handle, labels, states):
+    blob = np.frombuffer(b"".join(labels), np.uint8) if labels else np.zeros(1, np.uint8)
+    sizes = np.array([len(label) for label in labels] or [0], np.uint32)
+    packed = b"".join(state_label(*state) for state in states)
+    out = (C.c_uint64 * 4)()
+    assert reference.ref_cache_adopt_labelled(handle, blob.ctypes.data, sizes.ctypes.data, len(labels), packed, len(states), out) == 0
+    return {"states": int(out[0]), "blocks": int(out[1]), "bytes": int(out[2]), "dropped": int(out[3])}
+
+
+@pytest.mark.parametrize("seed", range(60))
+def test_adoption_of_restore_points_equals_the_reference(tmp_path, seed):
+    """The reference's own rule (Cache.cpp:70-127): a state comes back with its whole chain, a block only for a state.
+    The same block labels and the same state labels on both sides: blocks and states taken back, everything left
+    behind, the bytes held, the next block id, and the labels a clean stop writes for the states afterwards."""
+    rng = np.random.default_rng(1000 + seed)
+    labels = random_forest(rng, int(rng.integers(1, 40)))
+    store = write_labels(tmp_path, labels)
+    recorded = [r["label"] for r in store.records()]
+    states = random_states(rng, recorded)
+    pool, cache = mine_fresh()
+    cache.set_state_coupled(True)
+    mine = cache.adopt_restore_points(store, [(state_label(*state), 64) for state in states])
+    handle = theirs_fresh()
+    theirs = reference_adopt_points(handle, recorded, states)
+    try:
+        every = {fields(label)["id"] for label in recorded} | {state[0] for state in states} | {0}
+        kept_mine = {block for block in every if block and cache.block_state(block) is not None}
+        kept_theirs = {block for block in every if block and reference_has(handle, block)}
+        assert kept_mine == kept_theirs, f"seed {seed}: mine only {sorted(kept_mine - kept_theirs)}, reference only {sorted(kept_theirs - kept_mine)}"
+        assert mine == theirs, (mine, theirs)
+        blob, sizes = np.zeros(256 * STATE_LABEL_BYTES, np.uint8), np.zeros(256, np.uint64)
+        count = reference.ref_cache_state_labels(handle, blob.ctypes.data, sizes.ctypes.data, 256)
+        assert count == theirs["states"]
+        written = sorted((blob[i * STATE_LABEL_BYTES:(i + 1) * STATE_LABEL_BYTES].tobytes(), int(sizes[i])) for i in range(count))
+        assert sorted(cache.state_labels()) == written
+        fresh = np.arange(900_000, 900_033, dtype=np.uint32)
+        cache.begin_request(1)
+        assert cache.ensure_tokens(1, 32) == GRANTED
+        cache.publish(1, fresh, 32)
+        assert reference.ref_cache_begin(handle, 1) == 0
+        assert reference.ref_cache_ensure(handle, 1, 32) == 0
+        assert reference.ref_cache_publish(handle, 1, fresh.ctypes.data, len(fresh), 32, None, 0) == 0
+        assert cache.block_at(1, 32) == reference.ref_cache_block_at(handle, 1, 32) > max(every)
+    finally:
+        reference.ref_cache_destroy(handle)
+        store.close(); cache.close(); pool.close()
+
+
 def reference_seals(prompts):
     """The reference, persistent: publishes each prompt's full pages, evicts everything to its tier and hands over the
     labels its slots carry (Cache::labelKv, Cache.cpp:853-860)."""
@@ -182,6 +249,13 @@ def reference_seals(prompts):
     return handle, sorted(labels, key=lambda label: fields(label)["id"])
 
 
+def reference_state_labels(handle):
+    blob, sizes = np.zeros(256 * STATE_LABEL_BYTES, np.uint8), np.zeros(256, np.uint64)
+    count = reference.ref_cache_state_labels(handle, blob.ctypes.data, sizes.ctypes.data, 256)
+    assert count >= 0
+    return sorted((blob[i * STATE_LABEL_BYTES:(i + 1) * STATE_LABEL_BYTES].tobytes(), int(sizes[i])) for i in range(count))
+
+
 def prompts_for(seed):
     rng = np.random.default_rng(seed)
     base = rng.integers(0, 50000, size=161, dtype=np.uint32)
@@ -193,8 +267,9 @@ def prompts_for(seed):
 def test_labels_the_reference_wrote_are_taken_back_here_and_sealed_again_byte_for_byte(tmp_path):
     prompts = prompts_for(3)
     handle, labels = reference_seals(prompts)
+    points = reference_state_labels(handle)   # what its clean stop writes for the three restore points
     reference.ref_cache_destroy(handle)
-    assert len(labels) == 5 + 2 + 3
+    assert len(labels) == 5 + 2 + 3 and len(points) == 3
     store = write_labels(tmp_path, labels)
     pool, cache = mine_fresh()
     assert cache.adopt(store) == {"blocks": len(labels), "dropped": 0, "bytes": len(labels) * SLOT}
@@ -207,6 +282,17 @@ def test_labels_the_reference_wrote_are_taken_back_here_and_sealed_again_byte_fo
     again.close()
     for prompt in prompts:
         assert len(cache.lookup(np.concatenate([prompt, [1]]))) == len(prompt) // 32
+    store.close(); cache.close(); pool.close()
+    # with the state labels, under the reference's rule: the three restore points and their chains, and a clean stop
+    # here writes the state labels the reference wrote
+    store = write_labels(tmp_path, labels, name="c")
+    pool, cache = mine_fresh()
+    cache.set_state_coupled(True)
+    assert cache.adopt_restore_points(store, points) == {"blocks": len(labels), "dropped": 0, "bytes": len(labels) * SLOT + 3 * 64, "states": 3}
+    assert sorted(cache.state_labels()) == points
+    for prompt in prompts:
+        found = cache.lookup_state(np.concatenate([prompt, [1]]))
+        assert found["kv_boundary"] == found["resume_boundary"] == len(prompt) // 32 * 32
     store.close(); cache.close(); pool.close()
 
 
@@ -242,3 +328,22 @@ def test_labels_sealed_here_equal_the_reference_s_own_for_the_same_history(tmp_p
     assert result["blocks"] == len(mine) and result["dropped"] == 0 and result["states"] == len(mine)
     reference.ref_cache_destroy(handle)
     store.close(); cache.close(); pool.close()
+
+
+def test_the_random_restore_point_sets_take_states_and_chains_back(tmp_path):
+    """The comparison above is not one of two empty caches: over its seeds hundreds of states and chains come back and
+    about as many records and states stay behind."""
+    taken = {"blocks": 0, "states": 0, "dropped": 0}
+    for seed in range(60):
+        rng = np.random.default_rng(1000 + seed)
+        labels = random_forest(rng, int(rng.integers(1, 40)))
+        folder = tmp_path / str(seed)
+        folder.mkdir()
+        store = write_labels(folder, labels)
+        states = random_states(rng, [r["label"] for r in store.records()])
+        pool, cache = mine_fresh()
+        result = cache.adopt_restore_points(store, [(state_label(*state), 64) for state in states])
+        for key in taken:
+            taken[key] += result[key]
+        store.close(); cache.close(); pool.close()
+    assert taken["states"] > 200 and taken["blocks"] > 300 and taken["dropped"] > 500, taken
