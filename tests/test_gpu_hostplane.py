@@ -215,6 +215,63 @@ def test_kv_survives_a_restart_through_the_slot_store(tmp_path):
     w.close()
 
 
+def test_restore_points_survive_a_restart_with_their_chains(tmp_path):
+    """State-coupled, as the reference's hybrid model runs: two stored composite states (after three and after six
+    pages) are the restore points. Everything goes to the pinned-host tier and into the slot file, the state labels are
+    written as a clean stop writes them; the next process takes both points back with their chains, a request resumes
+    at the deeper state and gets the device bytes back exactly."""
+    layout = Layout(2, 4, 256, INT4)
+    tokens = 32 * 6
+    ids = np.random.default_rng(9).integers(0, 1000, size=tokens + 1, dtype=np.uint32)
+    w = World(layout, 256, 128, tier_slots=16)
+    w.cache.set_state_coupled(True)
+    w.cache.begin_request(1)
+    assert w.cache.ensure_tokens(1, tokens) == GRANTED
+    w.append(1, 0, tokens, mirror_too=False)
+    w.cache.publish(1, ids, tokens)
+    content = [w.device_page(p) for p in w.cache.page_table(1)[0]]
+    w.cache.publish_stored_state(w.cache.block_at(1, 96), 4096)
+    w.cache.publish_stored_state(w.cache.block_at(1, tokens), 4096, checkpoint=True)
+    w.cache.poll_transfers()
+    w.cache.end_request(1)
+    for _ in range(64):
+        w.cache.evict_all()
+        while w.cache.snapshot()["transfers"]:
+            w.cache.poll_transfers()
+        if w.cache.snapshot()["resident_blocks"] == 0:
+            break
+    assert w.cache.snapshot()["tier_blocks"] == 6 and w.cache.snapshot()["resident_blocks"] == 0
+    slot_bytes = (w.storage.bytes_per_page() + 4095) // 4096 * 4096
+    files = dict(slots_path=tmp_path / "kv.slots", records_path=tmp_path / "kv.records", tag=b"int4 2x4x256",
+                 label_bytes=KV_BLOCK_LABEL_BYTES, slot_bytes=slot_bytes)
+    store = SlotStore(**files)
+    assert w.cache.persist(store) == 6
+    points = w.cache.state_labels()
+    assert [(np.frombuffer(label, "<u4", offset=16)[0], size) for label, size in points] == [(96, 4096), (tokens, 4096)]
+    store.close()
+    w.close()
+
+    w = World(layout, 256, 128, tier_slots=16)
+    w.cache.set_state_coupled(True)
+    store = SlotStore(**files)
+    assert w.cache.adopt_restore_points(store, points) == {"blocks": 6, "dropped": 0, "bytes": 6 * w.storage.bytes_per_page() + 2 * 4096, "states": 2}
+    found = w.cache.lookup_state(ids)
+    assert found["kv_boundary"] == found["resume_boundary"] == tokens and len(found["blocks"]) == 6
+    w.cache.begin_request(2)
+    status, resume = w.cache.attach_prefix(2, found["blocks"])
+    assert status == GRANTED and resume == tokens
+    while w.cache.restores_pending(2):
+        w.cache.poll_transfers()
+    assert w.cache.snapshot()["failed_transfers"] == 0
+    for page, want in zip(w.cache.page_table(2)[0], content):
+        assert np.array_equal(w.device_page(page), want)
+    if found["state_block"]:
+        w.cache.unpin_state(found["state_block"])
+    w.cache.end_request(2)
+    store.close()
+    w.close()
+
+
 def test_pool_compaction_moves_device_pages():
     layout = Layout(1, 4, 256, INT4)
     w = World(layout, 384, 128)
