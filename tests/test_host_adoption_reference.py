@@ -347,3 +347,22 @@ def test_the_random_restore_point_sets_take_states_and_chains_back(tmp_path):
             taken[key] += result[key]
         store.close(); cache.close(); pool.close()
     assert taken["states"] > 200 and taken["blocks"] > 300 and taken["dropped"] > 500, taken
+
+
+def test_restore_points_come_back_only_into_an_empty_cache(tmp_path):
+    """Cache::adopt refuses once anything is in the cache (Cache.cpp:41-42); a state without bytes is no stored copy and
+    stays behind with the chain only it wanted."""
+    tokens = np.arange(32, dtype=np.uint32)
+    labels = [kv_block_label(1, 0, 5, tokens), kv_block_label(2, 1, 6, tokens + 100)]
+    store = write_labels(tmp_path, labels)
+    pool, cache = mine_fresh()
+    cache.begin_request(1)
+    with pytest.raises(RuntimeError):
+        cache.adopt_restore_points(store, [(state_label(1, 5, 32), 64)])
+    cache.end_request(1)
+    assert cache.adopt_restore_points(store, [(state_label(1, 5, 32), 64), (state_label(2, 6, 64), 0)]) == \
+        {"blocks": 1, "dropped": 2, "bytes": SLOT + 64, "states": 1}
+    assert cache.block_state(1) is not None and cache.block_state(2) is None
+    with pytest.raises(RuntimeError):
+        cache.adopt_restore_points(store, [])
+    store.close(); cache.close(); pool.close()
